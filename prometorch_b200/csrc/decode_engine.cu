@@ -1,0 +1,574 @@
+// Host side of the decode path: launch planning for the GEMV, and the engine
+// that strings one token's kernels together, captures them into a CUDA graph
+// (with programmatic dependent launch edges so each kernel's weight prefetch
+// overlaps its predecessor's tail) and replays it per token.
+//
+// What the reference does in GGUFModel::forward_decode
+// (torch/io/gguf_model.h:2575-3113): ~10 kernels per layer, eager on token 1,
+// captured on token 2, replayed afterwards, arg-max in a separate launch plus an
+// 8-byte device-to-host copy per token.  Here a layer is five kernels, the
+// arg-max is the lm_head epilogue and a run of tokens needs no host round trip.
+#include "decode_kernels.cuh"
+#include <stdarg.h>
+#include <stdlib.h>
+#include <string.h>
+#include <string>
+#include <vector>
+#include <algorithm>
+
+static thread_local char g_err[1024];
+void ptb_set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+PTB_API const char* ptb_last_error() { return g_err; }
+
+using namespace ptb;
+
+// ------------------------------------------------------------------------------------------ C structs (mirrored in Python)
+struct PtbWeightDesc {
+    const void* w;
+    const void* bias;
+    int qtype, rows, cols, rowbytes;
+};
+struct PtbLayerDesc {
+    PtbWeightDesc q, k, v, o, gate, up, down;
+    const float* attn_norm;
+    const float* ffn_norm;
+    const float* q_norm;
+    const float* k_norm;
+    const float* cos;       // per-layer RoPE tables (sliding-window layers may use another base)
+    const float* sin;
+    int window;
+    int pad;
+};
+struct PtbModelDesc {
+    int n_layers, hidden, n_heads, n_kv_heads, head_dim, inter, vocab, max_seq;   // head counts are per rank
+    float eps, emb_scale;
+    int neox, act_gelu, norm_add_one, want_logits;
+    PtbWeightDesc embed, lm_head;
+    const float* out_norm;
+    int tp_rank, tp_world, vocab_offset, pad;
+    void* peer_inbox[3][MAX_PEERS];     // three receive buffers (attention out, FFN down, lm_head pair)
+    void* peer_flag[3][MAX_PEERS];
+    int slot_floats, pad2;
+};
+
+static int env_int(const char* name, int dflt) {
+    const char* v = getenv(name);
+    return v && *v ? atoi(v) : dflt;
+}
+
+static size_t gemv_header_bytes(int K) {
+    size_t h = 128 + (4 * GEMV_GROUPS + 64) * 4 + (size_t)K + (size_t)(K / 32) * 4 + (size_t)(K / 16) * 4;
+    return (h + 127) / 128 * 128;
+}
+
+// Choose rows-per-stage R and groups-per-row gpr for a matrix with `nblk` super-blocks per row.
+static void plan_job(GemvJob& j, int stage_cap) {
+    const int pairs = j.w2 ? 2 : 1;
+    double best = -1;
+    int bestR = 1, bestG = 1;
+    for (int gpr = 1; gpr <= std::min(GEMV_GROUPS, j.nblk); ++gpr) {
+        int R = GEMV_GROUPS / gpr;
+        const int capR = stage_cap / (j.rowbytes * pairs);
+        if (capR < 1) continue;
+        R = std::min(R, capR);
+        const int rounds = (j.nblk + gpr - 1) / gpr;
+        double eff = ((double)R * gpr / GEMV_GROUPS) * ((double)j.nblk / ((double)rounds * gpr));
+        // a stage that is too small spends its time on barriers
+        const double bytes = (double)R * j.rowbytes * pairs;
+        if (bytes < 8192) eff *= 0.5 + 0.5 * bytes / 8192.0;
+        if (eff > best + 1e-9 || (eff > best - 1e-9 && R > bestR)) { best = eff; bestR = R; bestG = gpr; }
+    }
+    j.R = bestR;
+    j.gpr = bestG;
+}
+
+struct GemvLaunch {
+    GemvParams p;
+    int grid;
+    size_t smem;
+};
+
+// Fill job geometry, CTA split and shared memory size.  `jobs` already carry w/w2/out/bias/qtype/N/rowbytes/nblk.
+static int plan_gemv(GemvLaunch& L, int njobs, int K, int n_ctas) {
+    const int stages = env_int("PTB_GEMV_STAGES", 4);
+    int stage_cap = env_int("PTB_GEMV_STAGE_KB", 32) * 1024;
+    GemvParams& p = L.p;
+    p.njobs = njobs;
+    p.K = K;
+    size_t max_row = 0;
+    for (int i = 0; i < njobs; ++i) max_row = std::max(max_row, (size_t)p.job[i].rowbytes * (p.job[i].w2 ? 2 : 1));
+    if ((size_t)stage_cap < max_row) stage_cap = (int)max_row;
+    double total = 0;
+    int stage_bytes = 0;
+    for (int i = 0; i < njobs; ++i) {
+        plan_job(p.job[i], stage_cap);
+        total += (double)p.job[i].N * p.job[i].rowbytes * (p.job[i].w2 ? 2 : 1);
+        stage_bytes = std::max(stage_bytes, p.job[i].R * p.job[i].rowbytes * (p.job[i].w2 ? 2 : 1));
+    }
+    stage_bytes = (stage_bytes + 127) / 128 * 128;
+    // CTAs proportional to bytes, at least one each, never more CTAs than rows
+    int left = n_ctas, begin = 0;
+    double left_bytes = total;
+    for (int i = 0; i < njobs; ++i) {
+        GemvJob& j = p.job[i];
+        const double b = (double)j.N * j.rowbytes * (j.w2 ? 2 : 1);
+        int c = (i == njobs - 1) ? left : (int)(left * b / left_bytes + 0.5);
+        c = std::max(1, std::min(c, left - (njobs - 1 - i)));
+        c = std::min(c, j.N);
+        j.cta_begin = begin;
+        j.cta_count = c;
+        begin += c;
+        left -= c;
+        left_bytes -= b;
+    }
+    L.grid = begin;
+    p.stages = stages;
+    p.stage_bytes = stage_bytes;
+    L.smem = gemv_header_bytes(K) + (size_t)stages * stage_bytes;
+    if (L.smem > 227 * 1024) {
+        ptb_set_error("gemv: %zu B of shared memory needed (K=%d, stage %d B x %d)", L.smem, K, stage_bytes, stages);
+        return -1;
+    }
+    return 0;
+}
+
+static void set_job(GemvJob& j, const PtbWeightDesc& w, const PtbWeightDesc* w2, float* out) {
+    memset(&j, 0, sizeof(j));
+    j.w = (const uint8_t*)w.w;
+    j.w2 = w2 ? (const uint8_t*)w2->w : nullptr;
+    j.bias = (const float*)w.bias;
+    j.out = out;
+    j.qtype = w.qtype;
+    j.N = w.rows;
+    j.rowbytes = w.rowbytes;
+    j.nblk = w.cols / 256;
+}
+
+static bool g_attr_done = false;
+static int ensure_attrs() {
+    if (g_attr_done) return 0;
+    PTB_CUDA_OK(cudaFuncSetAttribute(gemv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    g_attr_done = true;
+    return 0;
+}
+
+template <typename Kern, typename Params>
+static cudaError_t launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl, const Params& p) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, p);
+}
+
+// ------------------------------------------------------------------------------------------ standalone op entry points (tests, benches)
+
+// y = epilogue(W x).  Device pointers; w2/norm_w/resid/bias may be null.
+PTB_API int ptb_gemv(const void* w, const void* w2, int qtype, int rows, int cols, int rowbytes, const float* x,
+                     const float* norm_w, float eps, const float* bias, const float* resid, float* out, int epilogue,
+                     int act_gelu, int n_ctas, void* scratch /* >= 16 + 8*n_ctas bytes, zeroed */, int* status,
+                     cudaStream_t stream) {
+    if (ensure_attrs()) return -1;
+    GemvLaunch L;
+    memset(&L, 0, sizeof(L));
+    PtbWeightDesc d{w, bias, qtype, rows, cols, rowbytes};
+    PtbWeightDesc d2{w2, nullptr, qtype, rows, cols, rowbytes};
+    set_job(L.p.job[0], d, w2 ? &d2 : nullptr, out);
+    L.p.x = x;
+    L.p.norm_w = norm_w;
+    L.p.eps = eps;
+    L.p.epilogue = epilogue;
+    L.p.act_gelu = act_gelu;
+    L.p.resid = resid;
+    L.p.status = status;
+    L.p.peers.world = 1;
+    if (epilogue == EPI_ARGMAX) {
+        uint8_t* s = (uint8_t*)scratch;
+        L.p.ticket = (unsigned*)s;
+        L.p.result = (int*)(s + 8);
+        L.p.ctrl = nullptr;
+        L.p.amax_val = (float*)(s + 64);
+        L.p.amax_idx = (int*)(s + 64 + 4 * (size_t)n_ctas);
+        L.p.logits = out;
+    }
+    if (plan_gemv(L, 1, cols, n_ctas)) return -1;
+    PTB_CUDA_OK(launch_pdl(gemv_kernel, dim3(L.grid), dim3(GEMV_THREADS), L.smem, stream, false, L.p));
+    return 0;
+}
+
+PTB_API int ptb_attn_decode(const float* q, const float* k, const float* v, const float* q_norm, const float* k_norm,
+                            const float* cos, const float* sin, void* k_cache, void* v_cache, float* out, float* part_o,
+                            float* part_ml, unsigned* ticket, const int* ctrl, int n_kv_heads, int group, int max_seq,
+                            int neox, float eps, int window, cudaStream_t stream) {
+    if (group > ATT_MAX_GROUP) {
+        ptb_set_error("attn_decode: %d query heads per KV head, at most %d supported", group, ATT_MAX_GROUP);
+        return -1;
+    }
+    AttnParams a;
+    memset(&a, 0, sizeof(a));
+    a.q = q; a.k = k; a.v = v; a.q_norm = q_norm; a.k_norm = k_norm; a.cos = cos; a.sin = sin;
+    a.k_cache = (__half*)k_cache; a.v_cache = (__half*)v_cache; a.out = out; a.part_o = part_o; a.part_ml = part_ml;
+    a.ticket = ticket; a.ctrl = ctrl; a.group = group; a.max_seq = max_seq;
+    a.max_splits = (max_seq + ATT_CHUNK - 1) / ATT_CHUNK;
+    a.neox = neox; a.eps = eps; a.scale = 1.0f / sqrtf((float)ATT_D); a.window = window;
+    PTB_CUDA_OK(launch_pdl(attn_decode_kernel, dim3(n_kv_heads, a.max_splits), dim3(ATT_THREADS), 0, stream, false, a));
+    return 0;
+}
+
+// ------------------------------------------------------------------------------------------ engine
+
+struct Engine {
+    PtbModelDesc m;
+    std::vector<PtbLayerDesc> layers;
+    int dev = 0, n_sm = 148;
+    cudaStream_t stream = nullptr;
+    bool own_stream = true;
+    // device buffers
+    float *x = nullptr, *qkv = nullptr, *att = nullptr, *ffn = nullptr, *logits = nullptr;
+    __half *kc = nullptr, *vc = nullptr;
+    float *part_o = nullptr, *part_ml = nullptr;
+    unsigned* tickets = nullptr;      // [0] gemv, [1] spare, [8..] attention per kv head
+    float* amax_val = nullptr;
+    int* amax_idx = nullptr;
+    int* ctrl = nullptr;              // CTRL_WORDS ints
+    int* result = nullptr;            // {token, value bits}
+    int* token_log = nullptr;
+    int* script = nullptr;            // prompt tokens for scripted feeding [max_seq]
+    int log_cap = 0;
+    int* status = nullptr;
+    int* h_pinned = nullptr;          // pinned host staging: ctrl words + result
+    std::vector<GemvLaunch> gemvs;    // per layer: qkv, o, gateup, down ; last: lm_head
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    bool use_pdl = true;
+    long launches_per_token = 0;
+};
+
+static int engine_alloc(Engine* e) {
+    const PtbModelDesc& m = e->m;
+    const int qd = m.n_heads * m.head_dim, kvd = m.n_kv_heads * m.head_dim;
+    const int splits = (m.max_seq + ATT_CHUNK - 1) / ATT_CHUNK;
+    const int group = m.n_heads / m.n_kv_heads;
+    PTB_CUDA_OK(cudaMalloc(&e->x, sizeof(float) * m.hidden));
+    PTB_CUDA_OK(cudaMalloc(&e->qkv, sizeof(float) * (qd + 2 * kvd)));
+    PTB_CUDA_OK(cudaMalloc(&e->att, sizeof(float) * qd));
+    PTB_CUDA_OK(cudaMalloc(&e->ffn, sizeof(float) * m.inter));
+    PTB_CUDA_OK(cudaMalloc(&e->logits, sizeof(float) * m.lm_head.rows));
+    const size_t kvbytes = sizeof(__half) * (size_t)m.n_layers * m.n_kv_heads * m.max_seq * m.head_dim;
+    PTB_CUDA_OK(cudaMalloc(&e->kc, kvbytes));
+    PTB_CUDA_OK(cudaMalloc(&e->vc, kvbytes));
+    PTB_CUDA_OK(cudaMemset(e->kc, 0, kvbytes));
+    PTB_CUDA_OK(cudaMemset(e->vc, 0, kvbytes));
+    PTB_CUDA_OK(cudaMalloc(&e->part_o, sizeof(float) * (size_t)m.n_kv_heads * splits * group * ATT_D));
+    PTB_CUDA_OK(cudaMalloc(&e->part_ml, sizeof(float) * (size_t)m.n_kv_heads * splits * group * 2));
+    PTB_CUDA_OK(cudaMalloc(&e->tickets, sizeof(unsigned) * (8 + m.n_kv_heads)));
+    PTB_CUDA_OK(cudaMemset(e->tickets, 0, sizeof(unsigned) * (8 + m.n_kv_heads)));
+    PTB_CUDA_OK(cudaMalloc(&e->amax_val, sizeof(float) * 4096));
+    PTB_CUDA_OK(cudaMalloc(&e->amax_idx, sizeof(int) * 4096));
+    PTB_CUDA_OK(cudaMalloc(&e->ctrl, sizeof(int) * CTRL_WORDS));
+    PTB_CUDA_OK(cudaMemset(e->ctrl, 0, sizeof(int) * CTRL_WORDS));
+    PTB_CUDA_OK(cudaMalloc(&e->result, sizeof(int) * 4));
+    PTB_CUDA_OK(cudaMemset(e->result, 0, sizeof(int) * 4));
+    e->log_cap = 1 << 16;
+    PTB_CUDA_OK(cudaMalloc(&e->token_log, sizeof(int) * e->log_cap));
+    PTB_CUDA_OK(cudaMalloc(&e->script, sizeof(int) * m.max_seq));
+    PTB_CUDA_OK(cudaMalloc(&e->status, sizeof(int)));
+    PTB_CUDA_OK(cudaMemset(e->status, 0, sizeof(int)));
+    PTB_CUDA_OK(cudaMallocHost(&e->h_pinned, sizeof(int) * 16));
+    memset(e->h_pinned, 0, sizeof(int) * 16);
+    return 0;
+}
+
+static void fill_peers(const Engine* e, GemvParams& p, int which, int call_idx, int calls_per_token) {
+    const PtbModelDesc& m = e->m;
+    p.peers.rank = m.tp_rank;
+    p.peers.world = m.tp_world;
+    p.peers.slot_floats = m.slot_floats;
+    for (int r = 0; r < m.tp_world; ++r) {
+        p.peers.inbox[r] = (float*)m.peer_inbox[which][r];
+        p.peers.flag[r] = (uint32_t*)m.peer_flag[which][r];
+    }
+    p.gen = (const uint32_t*)(e->ctrl + CTRL_GEN);
+    p.peers.seq_mul = (uint32_t)calls_per_token;
+    p.peers.seq_add = (uint32_t)call_idx;
+}
+
+static int engine_plan(Engine* e) {
+    const PtbModelDesc& m = e->m;
+    const int qd = m.n_heads * m.head_dim, kvd = m.n_kv_heads * m.head_dim;
+    const int n_ctas = e->n_sm * env_int("PTB_GEMV_CTAS_PER_SM", 1);
+    const bool tp = m.tp_world > 1;
+    e->gemvs.clear();
+    for (int l = 0; l < m.n_layers; ++l) {
+        const PtbLayerDesc& L = e->layers[l];
+        {   // q, k, v from RMSNorm(x)
+            GemvLaunch g;
+            memset(&g, 0, sizeof(g));
+            set_job(g.p.job[0], L.q, nullptr, e->qkv);
+            set_job(g.p.job[1], L.k, nullptr, e->qkv + qd);
+            set_job(g.p.job[2], L.v, nullptr, e->qkv + qd + kvd);
+            g.p.x = e->x; g.p.norm_w = L.attn_norm; g.p.eps = m.eps; g.p.norm_add_one = m.norm_add_one;
+            g.p.epilogue = EPI_STORE; g.p.status = e->status; g.p.peers.world = 1;
+            if (plan_gemv(g, 3, m.hidden, n_ctas)) return -1;
+            e->gemvs.push_back(g);
+        }
+        {   // x += Wo att
+            GemvLaunch g;
+            memset(&g, 0, sizeof(g));
+            set_job(g.p.job[0], L.o, nullptr, e->x);
+            g.p.x = e->att; g.p.resid = e->x; g.p.status = e->status; g.p.ticket = e->tickets;
+            g.p.epilogue = tp ? EPI_ALLREDUCE : EPI_RESID;
+            g.p.peers.world = 1;
+            if (tp) fill_peers(e, g.p, 0, l, m.n_layers);
+            if (plan_gemv(g, 1, L.o.cols, n_ctas)) return -1;
+            e->gemvs.push_back(g);
+        }
+        {   // ffn = act(Wg h) * (Wu h), h = RMSNorm(x)
+            GemvLaunch g;
+            memset(&g, 0, sizeof(g));
+            set_job(g.p.job[0], L.gate, &L.up, e->ffn);
+            g.p.x = e->x; g.p.norm_w = L.ffn_norm; g.p.eps = m.eps; g.p.norm_add_one = m.norm_add_one;
+            g.p.epilogue = EPI_GATED; g.p.act_gelu = m.act_gelu; g.p.status = e->status; g.p.peers.world = 1;
+            if (plan_gemv(g, 1, m.hidden, n_ctas)) return -1;
+            e->gemvs.push_back(g);
+        }
+        {   // x += Wd ffn
+            GemvLaunch g;
+            memset(&g, 0, sizeof(g));
+            set_job(g.p.job[0], L.down, nullptr, e->x);
+            g.p.x = e->ffn; g.p.resid = e->x; g.p.status = e->status; g.p.ticket = e->tickets;
+            g.p.epilogue = tp ? EPI_ALLREDUCE : EPI_RESID;
+            g.p.peers.world = 1;
+            if (tp) fill_peers(e, g.p, 1, l, m.n_layers);
+            if (plan_gemv(g, 1, L.down.cols, n_ctas)) return -1;
+            e->gemvs.push_back(g);
+        }
+    }
+    {   // lm_head with fused arg-max
+        GemvLaunch g;
+        memset(&g, 0, sizeof(g));
+        set_job(g.p.job[0], m.lm_head, nullptr, e->logits);
+        g.p.x = e->x; g.p.norm_w = m.out_norm; g.p.eps = m.eps; g.p.norm_add_one = m.norm_add_one;
+        g.p.epilogue = EPI_ARGMAX; g.p.status = e->status;
+        g.p.amax_val = e->amax_val; g.p.amax_idx = e->amax_idx; g.p.ticket = e->tickets + 1;
+        g.p.logits = m.want_logits ? e->logits : nullptr;
+        g.p.result = e->result; g.p.ctrl = e->ctrl; g.p.token_log = e->token_log; g.p.token_script = e->script; g.p.row_offset = m.vocab_offset;
+        g.p.peers.world = 1;
+        if (tp) fill_peers(e, g.p, 2, 0, 1);
+        if (plan_gemv(g, 1, m.hidden, std::min(n_ctas, 4096))) return -1;
+        e->gemvs.push_back(g);
+    }
+    return 0;
+}
+
+// Enqueue one token's kernels on the engine stream.
+static int engine_enqueue(Engine* e) {
+    const PtbModelDesc& m = e->m;
+    const int qd = m.n_heads * m.head_dim, kvd = m.n_kv_heads * m.head_dim;
+    const int splits = (m.max_seq + ATT_CHUNK - 1) / ATT_CHUNK;
+    const bool pdl = e->use_pdl;
+    long n = 0;
+    EmbedParams ep;
+    memset(&ep, 0, sizeof(ep));
+    ep.table = (const uint8_t*)m.embed.w; ep.qtype = m.embed.qtype; ep.rowbytes = m.embed.rowbytes;
+    ep.nblk = m.embed.cols / 256; ep.H = m.hidden; ep.scale = m.emb_scale; ep.out = e->x; ep.ctrl = e->ctrl;
+    ep.vocab = m.embed.rows; ep.status = e->status;
+    ep.gen = m.tp_world > 1 ? (uint32_t*)(e->ctrl + CTRL_GEN) : nullptr;
+    // the first kernel of a token is launched without the programmatic edge: it must not
+    // overlap the previous token's lm_head, whose epilogue updates the control block
+    PTB_CUDA_OK(launch_pdl(embed_kernel, dim3((m.hidden + 255) / 256), dim3(256), 0, e->stream, false, ep));
+    ++n;
+    size_t gi = 0;
+    for (int l = 0; l < m.n_layers; ++l) {
+        const PtbLayerDesc& L = e->layers[l];
+        GemvLaunch& g0 = e->gemvs[gi++];
+        PTB_CUDA_OK(launch_pdl(gemv_kernel, dim3(g0.grid), dim3(GEMV_THREADS), g0.smem, e->stream, pdl, g0.p));
+        AttnParams a;
+        memset(&a, 0, sizeof(a));
+        a.q = e->qkv; a.k = e->qkv + qd; a.v = e->qkv + qd + kvd;
+        a.q_norm = L.q_norm; a.k_norm = L.k_norm; a.cos = L.cos; a.sin = L.sin;
+        a.k_cache = e->kc + (size_t)l * m.n_kv_heads * m.max_seq * m.head_dim;
+        a.v_cache = e->vc + (size_t)l * m.n_kv_heads * m.max_seq * m.head_dim;
+        a.out = e->att; a.part_o = e->part_o; a.part_ml = e->part_ml; a.ticket = e->tickets + 8; a.ctrl = e->ctrl;
+        a.group = m.n_heads / m.n_kv_heads; a.max_seq = m.max_seq; a.max_splits = splits; a.neox = m.neox;
+        a.eps = m.eps; a.scale = 1.0f / sqrtf((float)m.head_dim); a.window = L.window;
+        PTB_CUDA_OK(launch_pdl(attn_decode_kernel, dim3(m.n_kv_heads, splits), dim3(ATT_THREADS), 0, e->stream, pdl, a));
+        for (int k = 0; k < 3; ++k) {
+            GemvLaunch& g = e->gemvs[gi++];
+            PTB_CUDA_OK(launch_pdl(gemv_kernel, dim3(g.grid), dim3(GEMV_THREADS), g.smem, e->stream, pdl, g.p));
+        }
+        n += 5;
+    }
+    GemvLaunch& gl = e->gemvs[gi++];
+    PTB_CUDA_OK(launch_pdl(gemv_kernel, dim3(gl.grid), dim3(GEMV_THREADS), gl.smem, e->stream, pdl, gl.p));
+    ++n;
+    e->launches_per_token = n;
+    return 0;
+}
+
+PTB_API void* ptb_engine_create(const PtbModelDesc* m, const PtbLayerDesc* layers, void* ext_stream) {
+    if (m->head_dim != ATT_D) {
+        ptb_set_error("decode engine: head_dim %d not supported (kernels are built for %d)", m->head_dim, ATT_D);
+        return nullptr;
+    }
+    if (m->n_heads % m->n_kv_heads || m->n_heads / m->n_kv_heads > ATT_MAX_GROUP) {
+        ptb_set_error("decode engine: %d query heads over %d KV heads not supported", m->n_heads, m->n_kv_heads);
+        return nullptr;
+    }
+    if (m->hidden % 256 || m->inter % 256) {
+        ptb_set_error("decode engine: hidden (%d) and FFN (%d) sizes must be multiples of 256", m->hidden, m->inter);
+        return nullptr;
+    }
+    Engine* e = new Engine();
+    e->m = *m;
+    e->layers.assign(layers, layers + m->n_layers);
+    if (cudaGetDevice(&e->dev) != cudaSuccess) { ptb_set_error("no CUDA device"); delete e; return nullptr; }
+    cudaDeviceGetAttribute(&e->n_sm, cudaDevAttrMultiProcessorCount, e->dev);
+    e->use_pdl = env_int("PTB_PDL", 1) != 0;
+    if (ext_stream) { e->stream = (cudaStream_t)ext_stream; e->own_stream = false; }
+    else if (cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) != cudaSuccess) { ptb_set_error("stream create failed"); delete e; return nullptr; }
+    if (ensure_attrs() || engine_alloc(e) || engine_plan(e)) { delete e; return nullptr; }
+    return e;
+}
+
+PTB_API void ptb_engine_destroy(void* h) {
+    Engine* e = (Engine*)h;
+    if (!e) return;
+    cudaStreamSynchronize(e->stream);
+    if (e->exec) cudaGraphExecDestroy(e->exec);
+    if (e->graph) cudaGraphDestroy(e->graph);
+    cudaFree(e->x); cudaFree(e->qkv); cudaFree(e->att); cudaFree(e->ffn); cudaFree(e->logits);
+    cudaFree(e->kc); cudaFree(e->vc); cudaFree(e->part_o); cudaFree(e->part_ml); cudaFree(e->tickets);
+    cudaFree(e->amax_val); cudaFree(e->amax_idx); cudaFree(e->ctrl); cudaFree(e->result); cudaFree(e->token_log); cudaFree(e->script);
+    cudaFree(e->status);
+    cudaFreeHost(e->h_pinned);
+    if (e->own_stream) cudaStreamDestroy(e->stream);
+    delete e;
+}
+
+// Capture one token into a graph (call once, before the first replay).
+PTB_API int ptb_engine_capture(void* h) {
+    Engine* e = (Engine*)h;
+    if (e->exec) return 0;
+    PTB_CUDA_OK(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
+    if (engine_enqueue(e)) {
+        cudaGraph_t g = nullptr;
+        cudaStreamEndCapture(e->stream, &g);
+        if (g) cudaGraphDestroy(g);
+        return -1;
+    }
+    PTB_CUDA_OK(cudaStreamEndCapture(e->stream, &e->graph));
+    PTB_CUDA_OK(cudaGraphInstantiate(&e->exec, e->graph, 0));
+    return 0;
+}
+
+// Write {token, pos, self_feed} (and the log cursor) through pinned memory on the engine stream.
+PTB_API int ptb_engine_set_ctrl(void* h, int token, int pos, int self_feed, int reset_log) {
+    Engine* e = (Engine*)h;
+    int* p = e->h_pinned;
+    if (reset_log) {
+        int gen = 0;
+        PTB_CUDA_OK(cudaStreamSynchronize(e->stream));
+        PTB_CUDA_OK(cudaMemcpy(&gen, e->ctrl + CTRL_GEN, sizeof(int), cudaMemcpyDeviceToHost));
+        p[CTRL_TOKEN] = token; p[CTRL_POS] = pos; p[CTRL_STEP] = 0; p[CTRL_SELF_FEED] = self_feed;
+        p[CTRL_LOG_CAP] = e->log_cap; p[CTRL_GEN] = gen; p[6] = 0; p[7] = 0;
+        PTB_CUDA_OK(cudaMemcpyAsync(e->ctrl, p, sizeof(int) * CTRL_WORDS, cudaMemcpyHostToDevice, e->stream));
+    } else {
+        p[CTRL_TOKEN] = token; p[CTRL_POS] = pos;
+        PTB_CUDA_OK(cudaMemcpyAsync(e->ctrl, p, sizeof(int) * 2, cudaMemcpyHostToDevice, e->stream));
+    }
+    return 0;
+}
+
+// Enqueue `n` tokens (graph replays if captured, eager launches otherwise).  Asynchronous.
+PTB_API int ptb_engine_run(void* h, int n) {
+    Engine* e = (Engine*)h;
+    for (int i = 0; i < n; ++i) {
+        if (e->exec) PTB_CUDA_OK(cudaGraphLaunch(e->exec, e->stream));
+        else if (engine_enqueue(e)) return -1;
+    }
+    return 0;
+}
+
+// Host-fed step, the serving loop: copy {token,pos} in from pinned memory, run one token, copy the
+// sampled id back to pinned memory, wait.  Returns the id (or -1).
+PTB_API int ptb_engine_step(void* h, int token, int pos) {
+    Engine* e = (Engine*)h;
+    if (ptb_engine_set_ctrl(h, token, pos, 0, 0)) return -1;
+    if (ptb_engine_run(h, 1)) return -1;
+    PTB_CUDA_OK(cudaMemcpyAsync(e->h_pinned + 8, e->result, sizeof(int), cudaMemcpyDeviceToHost, e->stream));
+    PTB_CUDA_OK(cudaStreamSynchronize(e->stream));
+    return e->h_pinned[8];
+}
+
+// Scripted run: feed `n` prompt tokens starting at position pos0, then keep generating from the
+// arg-max.  Sets up the control block; follow with ptb_engine_run(h, n + n_new - 1).  log[n-1+i] is
+// the i-th generated token.
+PTB_API int ptb_engine_begin_script(void* h, const int* tokens, int n, int pos0) {
+    Engine* e = (Engine*)h;
+    if (n < 1 || pos0 + n > e->m.max_seq) { ptb_set_error("script of %d tokens at %d exceeds max_seq %d", n, pos0, e->m.max_seq); return -1; }
+    int gen = 0;
+    PTB_CUDA_OK(cudaStreamSynchronize(e->stream));
+    PTB_CUDA_OK(cudaMemcpy(&gen, e->ctrl + CTRL_GEN, sizeof(int), cudaMemcpyDeviceToHost));
+    PTB_CUDA_OK(cudaMemcpy(e->script, tokens, sizeof(int) * n, cudaMemcpyHostToDevice));
+    int c[CTRL_WORDS] = {tokens[0], pos0, 0, 2, e->log_cap, gen, n, 0};
+    PTB_CUDA_OK(cudaMemcpy(e->ctrl, c, sizeof(c), cudaMemcpyHostToDevice));
+    return 0;
+}
+
+PTB_API int ptb_engine_sync(void* h) {
+    Engine* e = (Engine*)h;
+    PTB_CUDA_OK(cudaStreamSynchronize(e->stream));
+    return 0;
+}
+
+// Copy the first n logged token ids to host memory; returns how many steps have run since the log reset.
+PTB_API int ptb_engine_read_log(void* h, int* out, int n) {
+    Engine* e = (Engine*)h;
+    PTB_CUDA_OK(cudaStreamSynchronize(e->stream));
+    int steps = 0;
+    PTB_CUDA_OK(cudaMemcpy(&steps, e->ctrl + CTRL_STEP, sizeof(int), cudaMemcpyDeviceToHost));
+    n = std::min(n, std::min(steps, e->log_cap));
+    if (n > 0) PTB_CUDA_OK(cudaMemcpy(out, e->token_log, sizeof(int) * n, cudaMemcpyDeviceToHost));
+    return steps;
+}
+
+PTB_API int ptb_engine_status(void* h) {
+    Engine* e = (Engine*)h;
+    int s = -1;
+    if (cudaMemcpy(&s, e->status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    return s;
+}
+PTB_API void* ptb_engine_stream(void* h) { return (void*)((Engine*)h)->stream; }
+PTB_API void* ptb_engine_logits(void* h) { return (void*)((Engine*)h)->logits; }
+PTB_API void* ptb_engine_hidden(void* h) { return (void*)((Engine*)h)->x; }
+PTB_API void* ptb_engine_result(void* h) { return (void*)((Engine*)h)->result; }
+PTB_API long ptb_engine_launches_per_token(void* h) { return ((Engine*)h)->launches_per_token; }
+PTB_API int ptb_engine_kv_bytes(void* h, long* out) {
+    Engine* e = (Engine*)h;
+    *out = 2L * sizeof(__half) * e->m.n_layers * e->m.n_kv_heads * e->m.max_seq * e->m.head_dim;
+    return 0;
+}
+
+// Geometry report for one GEMV (tests and notes): R, gpr, grid, smem, stage bytes.
+PTB_API int ptb_gemv_plan(int qtype, int rows, int cols, int rowbytes, int paired, int n_ctas, int* out5) {
+    GemvLaunch L;
+    memset(&L, 0, sizeof(L));
+    PtbWeightDesc d{(const void*)16, nullptr, qtype, rows, cols, rowbytes};
+    set_job(L.p.job[0], d, paired ? &d : nullptr, nullptr);
+    if (plan_gemv(L, 1, cols, n_ctas)) return -1;
+    out5[0] = L.p.job[0].R; out5[1] = L.p.job[0].gpr; out5[2] = L.grid; out5[3] = (int)L.smem; out5[4] = L.p.stage_bytes;
+    return 0;
+}

@@ -1,0 +1,356 @@
+"""GGUFModel: load a GGUF decoder, repack its weights for the sm_100a GEMV
+kernels, and drive the native decode engine.
+
+Public surface follows the reference's ``GGUFModel``
+(torch/io/gguf_model.h: ``load``, ``load_quantized_to_cuda``, ``forward``,
+``forward_decode``, ``init_tensor_parallel``, ``generate``, ``chat``,
+``sample_token``, ``apply_chat_template``) with these design differences:
+
+* weights go host→device once and are repacked on the GPU (Q6_K rows become a
+  16 B-aligned structure of arrays; Q4_K stays byte-identical to the file);
+* the KV cache is fp16 only, laid out ``[layer][kv_head][seq][128]``;
+* a whole run of tokens (prompt and generation) is enqueued as CUDA-graph
+  replays with the sampled token fed back on the device;
+* tensor parallelism shards Q/K/V/gate/up by rows and attn_output/ffn_down by
+  256-element super-blocks along K with the same non-uniform remainder rule
+  (torch/io/gguf_model.h:5239-5246) and runs on GPUs, with the partial-sum
+  all-reduce fused into the GEMV kernel over NVLink peer memory.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+import time
+from typing import Callable, Iterable, List, Optional, Sequence
+
+import torch
+
+from .. import _native as N
+from .config import TransformerConfig
+from .gguf import GGUFReader
+from .gguf_quant import GGMLType, dequantize, quantize
+
+QT_Q4K, QT_Q6K, QT_F16, QT_F32 = 0, 1, 2, 3
+
+
+def split_blocks(nblk: int, world: int, rank: int):
+    """Non-uniform block partition: the first ``nblk % world`` ranks take one extra."""
+    base, rem = divmod(nblk, world)
+    b0 = rank * base + min(rank, rem)
+    return b0, b0 + base + (1 if rank < rem else 0)
+
+
+def repack_q6k(raw: torch.Tensor, b0: int = 0, b1: Optional[int] = None) -> torch.Tensor:
+    """GGUF Q6_K rows ``[N, nblk*210]`` -> SoA rows ``ql | qh | scales | d(+pad)``, optionally K-sliced."""
+    n = raw.shape[0]
+    blk = raw.reshape(n, -1, 210)
+    blk = blk[:, b0:b1]
+    nb = blk.shape[1]
+    parts = [blk[:, :, 0:128].reshape(n, nb * 128), blk[:, :, 128:192].reshape(n, nb * 64),
+             blk[:, :, 192:208].reshape(n, nb * 16), blk[:, :, 208:210].reshape(n, nb * 2)]
+    pad = (-nb * 2) % 16
+    if pad:
+        parts.append(torch.zeros(n, pad, dtype=torch.uint8, device=raw.device))
+    return torch.cat(parts, dim=1).contiguous()
+
+
+def slice_q4k(raw: torch.Tensor, b0: int = 0, b1: Optional[int] = None) -> torch.Tensor:
+    n = raw.shape[0]
+    return raw.reshape(n, -1, 144)[:, b0:b1].reshape(n, -1).contiguous()
+
+
+class PackedWeight:
+    """A quantised matrix in the layout the GEMV kernel streams."""
+
+    def __init__(self, data: torch.Tensor, qtype: int, rows: int, cols: int, bias: Optional[torch.Tensor] = None):
+        self.data, self.qtype, self.rows, self.cols, self.bias = data, qtype, rows, cols, bias
+        self.rowbytes = data.shape[1]
+        assert self.rowbytes % 16 == 0 and data.data_ptr() % 16 == 0
+
+    def desc(self) -> N.WeightDesc:
+        return N.WeightDesc(self.data.data_ptr(), N.ptr(self.bias), self.qtype, self.rows, self.cols, self.rowbytes)
+
+    @property
+    def nbytes(self) -> int:
+        return self.data.numel()
+
+
+def pack_weight(raw: torch.Tensor, qtype: GGMLType, cols: int, device, rows=None, kblocks=None,
+                bias: Optional[torch.Tensor] = None) -> PackedWeight:
+    """``raw``: uint8 ``[N, row_bytes]`` as stored in the file.  ``rows=(r0,r1)`` row-slices,
+    ``kblocks=(b0,b1)`` slices super-blocks along K.  Types other than Q4_K/Q6_K are
+    transcoded to Q6_K blocks (the only lossy step, and only for such files)."""
+    if rows is not None:
+        raw = raw[rows[0]:rows[1]]
+    raw = raw.to(device, non_blocking=True)
+    qtype = GGMLType(qtype)
+    if qtype not in (GGMLType.Q4_K, GGMLType.Q6_K):
+        raw = quantize(dequantize(raw, qtype, cols), GGMLType.Q6_K)
+        qtype = GGMLType.Q6_K
+    b0, b1 = kblocks if kblocks is not None else (0, cols // 256)
+    if qtype == GGMLType.Q4_K:
+        data, qt = slice_q4k(raw, b0, b1), QT_Q4K
+    else:
+        data, qt = repack_q6k(raw, b0, b1), QT_Q6K
+    if bias is not None:
+        bias = bias.to(device).float().contiguous()
+        if rows is not None:
+            bias = bias[rows[0]:rows[1]].contiguous()
+    return PackedWeight(data, qt, data.shape[0], (b1 - b0) * 256, bias)
+
+
+class GGUFModel:
+    """Quantised decoder bound to the native decode engine on one GPU (or one TP rank)."""
+
+    def __init__(self, path: str, device: Optional[str] = None, max_seq: int = 4096, tp_rank: int = 0,
+                 tp_world: int = 1, symm=None, want_logits: bool = False):
+        self.path = path
+        self.reader = GGUFReader(path)
+        self.cfg = TransformerConfig.from_gguf(self.reader)
+        self.device = torch.device(device if device is not None else "cuda")
+        if self.device.type != "cuda":
+            raise RuntimeError("GGUFModel runs on a CUDA device; use models.gguf_oracle.OracleModel on the CPU")
+        self.max_seq = int(min(max_seq, self.cfg.context_length))
+        self.tp_rank, self.tp_world = tp_rank, tp_world
+        self.symm = symm
+        self.want_logits = want_logits
+        self._engine = None
+        self._keep: List[torch.Tensor] = []
+        self.load_seconds = 0.0
+        self.weight_bytes = 0
+        self._load()
+
+    # ------------------------------------------------------------------ loading
+    @classmethod
+    def load(cls, path: str, **kw) -> "GGUFModel":
+        return cls(path, **kw)
+
+    def _load(self):
+        t0 = time.time()
+        cfg, r, dev = self.cfg, self.reader, self.device
+        W, rk = self.tp_world, self.tp_rank
+        if cfg.num_heads % W or cfg.num_kv_heads % W or cfg.intermediate_size % 256:
+            raise ValueError(f"tensor parallel {W}: needs heads ({cfg.num_heads}), KV heads ({cfg.num_kv_heads}) "
+                             f"divisible and FFN size ({cfg.intermediate_size}) a multiple of 256")
+        if (cfg.num_heads // W * cfg.head_dim) % 256:
+            raise ValueError("tensor parallel: per-rank attention width must be a multiple of 256")
+        if cfg.has_post_norm:
+            raise NotImplementedError("post-attention/post-FFN norms (gemma3) are not wired into the fused engine yet")
+        torch.cuda.set_device(dev)
+        hq, hkv, d = cfg.num_heads // W, cfg.num_kv_heads // W, cfg.head_dim
+        fb0, fb1 = split_blocks(cfg.intermediate_size // 256, W, rk)
+        ob0, ob1 = rk * hq * d // 256, (rk + 1) * hq * d // 256
+        self.local_heads, self.local_kv_heads, self.local_inter = hq, hkv, (fb1 - fb0) * 256
+
+        def mat(name, rows=None, kblocks=None, bias_name=None):
+            ti = r.tensors[name]
+            bias = r.load(bias_name) if bias_name and r.has_tensor(bias_name) else None
+            pw = pack_weight(r.raw(name), ti.qtype, ti.shape[-1], dev, rows, kblocks, bias)
+            self.weight_bytes += pw.nbytes
+            return pw
+
+        def vec(name):
+            if not r.has_tensor(name):
+                return None
+            t = r.load(name).to(dev).float().contiguous()
+            self._keep.append(t)
+            return t
+
+        from ..models.gguf_oracle import rope_tables
+        cos, sin = rope_tables(cfg, self.max_seq, "cpu")
+        self.cos, self.sin = cos.to(dev).contiguous(), sin.to(dev).contiguous()
+        self.cos_swa = self.sin_swa = None
+        if cfg.swa_window and cfg.rope_swa_freq_base != cfg.rope_freq_base:
+            c2, s2 = rope_tables(cfg, self.max_seq, "cpu", freq_base=cfg.rope_swa_freq_base)
+            self.cos_swa, self.sin_swa = c2.to(dev).contiguous(), s2.to(dev).contiguous()
+
+        self.layers = []
+        descs = (N.LayerDesc * cfg.num_layers)()
+        for i in range(cfg.num_layers):
+            p = f"blk.{i}."
+            L = dict(
+                q=mat(p + "attn_q.weight", rows=(rk * hq * d, (rk + 1) * hq * d), bias_name=p + "attn_q.bias"),
+                k=mat(p + "attn_k.weight", rows=(rk * hkv * d, (rk + 1) * hkv * d), bias_name=p + "attn_k.bias"),
+                v=mat(p + "attn_v.weight", rows=(rk * hkv * d, (rk + 1) * hkv * d), bias_name=p + "attn_v.bias"),
+                o=mat(p + "attn_output.weight", kblocks=(ob0, ob1)),
+                gate=mat(p + "ffn_gate.weight", rows=(fb0 * 256, fb1 * 256)),
+                up=mat(p + "ffn_up.weight", rows=(fb0 * 256, fb1 * 256)),
+                down=mat(p + "ffn_down.weight", kblocks=(fb0, fb1)),
+                attn_norm=vec(p + "attn_norm.weight"), ffn_norm=vec(p + "ffn_norm.weight"),
+                q_norm=vec(p + "attn_q_norm.weight"), k_norm=vec(p + "attn_k_norm.weight"))
+            if L["gate"].qtype != L["up"].qtype:
+                raise NotImplementedError("ffn_gate and ffn_up with different quantisation types")
+            swa = bool(cfg.swa_window and cfg.swa_pattern and (i + 1) % cfg.swa_pattern != 0)
+            self.layers.append(L)
+            dsc = descs[i]
+            for k in ("q", "k", "v", "o", "gate", "up", "down"):
+                setattr(dsc, k, L[k].desc())
+            dsc.attn_norm, dsc.ffn_norm = N.ptr(L["attn_norm"]), N.ptr(L["ffn_norm"])
+            dsc.q_norm, dsc.k_norm = N.ptr(L["q_norm"]), N.ptr(L["k_norm"])
+            use_swa_tab = swa and self.cos_swa is not None
+            dsc.cos = (self.cos_swa if use_swa_tab else self.cos).data_ptr()
+            dsc.sin = (self.sin_swa if use_swa_tab else self.sin).data_ptr()
+            dsc.window = cfg.swa_window if swa else 0
+        self._layer_descs = descs
+        self.embed = mat("token_embd.weight")
+        head_name = "output.weight" if r.has_tensor("output.weight") else "token_embd.weight"
+        V = cfg.vocab_size
+        v0, v1 = (V * rk) // W, (V * (rk + 1)) // W
+        self.lm_head = mat(head_name, rows=(v0, v1)) if (W > 1 or head_name != "token_embd.weight") else self.embed
+        self.vocab_offset = v0
+        self.out_norm = vec("output_norm.weight")
+
+        m = N.ModelDesc()
+        m.n_layers, m.hidden, m.n_heads, m.n_kv_heads = cfg.num_layers, cfg.hidden_size, hq, hkv
+        m.head_dim, m.inter, m.vocab, m.max_seq = d, self.local_inter, V, self.max_seq
+        m.eps = cfg.rms_norm_eps
+        m.emb_scale = math.sqrt(cfg.hidden_size) if cfg.scale_embeddings else 1.0
+        m.neox, m.act_gelu, m.norm_add_one = int(cfg.rope_neox), int(cfg.ffn_gelu), int(cfg.gemma_norm_add_one)
+        m.want_logits = int(self.want_logits)
+        m.embed, m.lm_head, m.out_norm = self.embed.desc(), self.lm_head.desc(), N.ptr(self.out_norm)
+        m.tp_rank, m.tp_world, m.vocab_offset = rk, W, v0
+        if W > 1:
+            if self.symm is None:
+                raise ValueError("tensor parallel decode needs a symmetric-memory group (parallel.symm.SymmGroup)")
+            slot = max(cfg.hidden_size, 64)
+            self._tp_bufs = [self.symm.alloc(W * slot * 4) for _ in range(3)]
+            self._tp_flags = [self.symm.alloc(W * 4) for _ in range(3)]
+            for b in range(3):
+                for p in range(W):
+                    m.peer_inbox[b][p] = self._tp_bufs[b].peer_ptr(p)
+                    m.peer_flag[b][p] = self._tp_flags[b].peer_ptr(p)
+            m.slot_floats = slot
+            self.symm.barrier()
+        self._model_desc = m
+        torch.cuda.synchronize(dev)
+        lib = N.lib()
+        self._engine = lib.ptb_engine_create(C.byref(m), descs, None)
+        if not self._engine:
+            raise N.NativeError("engine: " + lib.ptb_last_error().decode())
+        self._lib = lib
+        self._captured = False
+        self.load_seconds = time.time() - t0
+
+    def close(self):
+        if self._engine:
+            self._lib.ptb_engine_destroy(self._engine)
+            self._engine = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ------------------------------------------------------------------ engine access
+    def capture(self):
+        """Capture the per-token CUDA graph (one warm-up token runs eagerly first)."""
+        if self._captured:
+            return
+        N.check(self._lib.ptb_engine_set_ctrl(self._engine, 0, 0, 0, 1), "set_ctrl")
+        N.check(self._lib.ptb_engine_run(self._engine, 1), "warm-up token")
+        N.check(self._lib.ptb_engine_sync(self._engine), "sync")
+        self.check_status()
+        N.check(self._lib.ptb_engine_capture(self._engine), "graph capture")
+        self._captured = True
+
+    def check_status(self):
+        s = self._lib.ptb_engine_status(self._engine)
+        if s != 0:
+            names = {1: "a weight copy never completed (mbarrier timeout)", 2: "a peer GPU never published its flag",
+                     3: "a token id fell outside the vocabulary"}
+            raise N.NativeError(f"decode kernels reported status {s}: {names.get(s, 'unknown')}")
+
+    @property
+    def stream(self) -> torch.cuda.Stream:
+        return torch.cuda.ExternalStream(self._lib.ptb_engine_stream(self._engine), device=self.device)
+
+    @property
+    def launches_per_token(self) -> int:
+        return int(self._lib.ptb_engine_launches_per_token(self._engine))
+
+    def _wrap(self, addr: int, n: int, dtype=torch.float32) -> torch.Tensor:
+        class _Arr:
+            pass
+        a = _Arr()
+        a.__cuda_array_interface__ = {"shape": (n,), "typestr": "<f4" if dtype == torch.float32 else "<i4",
+                                      "data": (addr, False), "version": 3}
+        return torch.as_tensor(a, device=self.device)
+
+    def logits_view(self) -> torch.Tensor:
+        """Device view of this rank's logits rows (valid when ``want_logits``)."""
+        return self._wrap(self._lib.ptb_engine_logits(self._engine), self.lm_head.rows)
+
+    def hidden_view(self) -> torch.Tensor:
+        return self._wrap(self._lib.ptb_engine_hidden(self._engine), self.cfg.hidden_size)
+
+    # ------------------------------------------------------------------ decoding
+    def forward_decode(self, token: int, pos: int) -> int:
+        """Serving step: token and position go host→device from pinned memory, one graph replay,
+        the arg-max id comes back device→host.  Returns the greedy next token."""
+        self.capture()
+        t = self._lib.ptb_engine_step(self._engine, int(token), int(pos))
+        if t < 0:
+            raise N.NativeError("decode step: " + self._lib.ptb_last_error().decode())
+        return t
+
+    def run_script(self, prompt: Sequence[int], n_new: int, pos0: int = 0, sync: bool = True) -> Optional[List[int]]:
+        """Enqueue prompt + ``n_new`` greedy tokens as back-to-back graph replays with the
+        sampled token fed back on the device; no host round trip until the end."""
+        self.capture()
+        n = len(prompt)
+        if pos0 + n + n_new > self.max_seq:
+            raise ValueError(f"{pos0 + n + n_new} positions exceed max_seq {self.max_seq}")
+        arr = (C.c_int * n)(*[int(t) for t in prompt])
+        N.check(self._lib.ptb_engine_begin_script(self._engine, arr, n, pos0), "begin_script")
+        N.check(self._lib.ptb_engine_run(self._engine, n + n_new - 1), "run")
+        if not sync:
+            return None
+        return self.read_generated(n, n_new)
+
+    def read_generated(self, n_prompt: int, n_new: int) -> List[int]:
+        total = n_prompt + n_new - 1
+        buf = (C.c_int * total)()
+        steps = self._lib.ptb_engine_read_log(self._engine, buf, total)
+        self.check_status()
+        if steps < total:
+            raise N.NativeError(f"only {steps} of {total} decode steps ran")
+        return list(buf[n_prompt - 1:total])
+
+    def generate(self, prompt: Sequence[int], max_new_tokens: int = 128, temperature: float = 0.0, top_k: int = 40,
+                 top_p: float = 0.9, repeat_penalty: float = 1.0, stop_ids: Iterable[int] = (),
+                 on_token: Optional[Callable[[int], bool]] = None, seed: int = 42) -> List[int]:
+        """Token-level generation.  Greedy without a callback runs entirely on the device; with a
+        callback (streaming) or sampling it steps token by token."""
+        stop = set(int(s) for s in stop_ids)
+        if self.cfg.eos_token_id >= 0:
+            stop.add(self.cfg.eos_token_id)
+        greedy = temperature <= 0.0 and repeat_penalty == 1.0
+        if greedy and on_token is None and not stop:
+            return self.run_script(prompt, max_new_tokens)
+        if not greedy and not self.want_logits:
+            raise RuntimeError("sampling needs the model opened with want_logits=True")
+        # prompt (all but the last token) in one scripted run, then step
+        out: List[int] = []
+        n = len(prompt)
+        if n > 1:
+            self.run_script(prompt[:-1], 1)
+        tok, pos = int(prompt[-1]), n - 1
+        from ..ops.sampling import sample_logits
+        gen = torch.Generator(device=self.device)
+        gen.manual_seed(seed)
+        history = list(int(t) for t in prompt)
+        for _ in range(max_new_tokens):
+            nxt = self.forward_decode(tok, pos)
+            if not greedy:
+                nxt = sample_logits(self.logits_view(), temperature, top_k, top_p, repeat_penalty, history, gen)
+            out.append(nxt)
+            history.append(nxt)
+            if on_token is not None and on_token(nxt) is False:
+                break
+            if nxt in stop:
+                break
+            tok, pos = nxt, pos + 1
+            if pos + 1 >= self.max_seq:
+                break
+        return out

@@ -1,0 +1,134 @@
+"""GPU numerics of the decode kernels against plain PyTorch fp32 references."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from prometorch_b200.io import gguf_quant as Q
+from prometorch_b200.io.config import tiny_qwen3_config
+from prometorch_b200.io.synthetic import write_synthetic_gguf
+
+
+def _packed(rows, cols, qt, seed=0):
+    from prometorch_b200.io.gguf_model import pack_weight
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    w = torch.randn(rows, cols, device="cuda", generator=g) * 0.02
+    raw = Q.quantize(w, qt)
+    wd = Q.dequantize(raw, qt, cols)
+    return pack_weight(raw, qt, cols, "cuda"), wd
+
+
+def _rel(a, b):
+    return float((a - b).norm() / b.norm())
+
+
+@pytest.mark.parametrize("qt", [Q.GGMLType.Q4_K, Q.GGMLType.Q6_K])
+@pytest.mark.parametrize("rows,cols", [(4096, 2560), (2560, 9728), (1024, 2560), (2560, 4096), (300, 512), (7, 256)])
+def test_gemv_matches_fp32(qt, rows, cols):
+    from prometorch_b200.ops.quant_gemv import quant_gemv
+    pw, wd = _packed(rows, cols, qt, seed=rows + cols)
+    x = torch.randn(cols, device="cuda")
+    y = quant_gemv(pw, x)
+    torch.cuda.synchronize()
+    ref_q8 = wd @ Q.quantize_activation_q8(x)        # same activation rounding as the kernel
+    ref = wd @ x
+    assert _rel(y, ref_q8) < 2e-4, _rel(y, ref_q8)
+    assert _rel(y, ref) < 2e-2, _rel(y, ref)
+
+
+def test_gemv_norm_resid_gated_argmax():
+    from prometorch_b200.ops.quant_gemv import quant_gemv
+    cols, rows = 2560, 1536
+    pw, wd = _packed(rows, cols, Q.GGMLType.Q4_K, 1)
+    pw2, wd2 = _packed(rows, cols, Q.GGMLType.Q4_K, 2)
+    x = torch.randn(cols, device="cuda") * 3
+    nw = 1 + 0.1 * torch.randn(cols, device="cuda")
+    xn = x * torch.rsqrt(x.pow(2).mean() + 1e-6) * nw
+    xq = Q.quantize_activation_q8(xn)
+    y = quant_gemv(pw, x, norm_weight=nw)
+    assert _rel(y, wd @ xq) < 2e-4
+    r = torch.randn(rows, device="cuda")
+    y = quant_gemv(pw, x, norm_weight=nw, resid=r)
+    assert _rel(y, r + wd @ xq) < 2e-4
+    y = quant_gemv(pw, x, norm_weight=nw, w2=pw2)
+    assert _rel(y, torch.nn.functional.silu(wd @ xq) * (wd2 @ xq)) < 5e-4
+    y, idx = quant_gemv(pw, x, norm_weight=nw, argmax=True)
+    torch.cuda.synchronize()
+    assert int(idx) == int(y.argmax()) == int((wd @ xq).argmax())
+
+
+@pytest.mark.parametrize("pos", [0, 5, 127, 128, 300, 1023])
+@pytest.mark.parametrize("neox", [True, False])
+def test_attn_decode(pos, neox):
+    from prometorch_b200.models.gguf_oracle import apply_rope, rms_norm, rope_tables
+    from prometorch_b200.ops.quant_gemv import attn_decode
+    cfg = tiny_qwen3_config()
+    H, KV, d, S = 8, 2, 128, 1024
+    cos, sin = rope_tables(cfg, S, "cuda")
+    torch.manual_seed(pos)
+    kc = (torch.randn(KV, S, d, device="cuda") * 0.5).half()
+    vc = (torch.randn(KV, S, d, device="cuda") * 0.5).half()
+    q, k, v = torch.randn(H * d, device="cuda"), torch.randn(KV * d, device="cuda"), torch.randn(KV * d, device="cuda")
+    qn, kn = 1 + 0.1 * torch.randn(d, device="cuda"), 1 + 0.1 * torch.randn(d, device="cuda")
+    kc2, vc2 = kc.clone(), vc.clone()
+    out = attn_decode(q, k, v, kc2, vc2, pos, cos, sin, q_norm=qn, k_norm=kn, neox=neox)
+    torch.cuda.synchronize()
+    # reference
+    qh = apply_rope(rms_norm(q.view(1, H, d), qn, 1e-6), cos[pos:pos + 1], sin[pos:pos + 1], neox)[0]
+    kh = apply_rope(rms_norm(k.view(1, KV, d), kn, 1e-6), cos[pos:pos + 1], sin[pos:pos + 1], neox)[0]
+    K = kc.float().clone()
+    V = vc.float().clone()
+    K[:, pos] = kh.half().float()
+    V[:, pos] = v.view(KV, d).half().float()
+    K, V = K[:, :pos + 1], V[:, :pos + 1]
+    g = H // KV
+    sc = torch.einsum("hd,hsd->hs", qh, K.repeat_interleave(g, 0)) / math.sqrt(d)
+    ref = torch.einsum("hs,hsd->hd", sc.softmax(-1), V.repeat_interleave(g, 0)).reshape(-1)
+    assert torch.allclose(kc2[:, pos].float(), K[:, pos], atol=2e-3)
+    assert _rel(out, ref) < 2e-3, _rel(out, ref)
+
+
+@pytest.fixture(scope="module")
+def tiny_model(tmp_path_factory):
+    cfg = tiny_qwen3_config(layers=3, hidden=512, heads=8, kv_heads=2, inter=1024, vocab=1000)
+    p = str(tmp_path_factory.mktemp("m") / "tiny.gguf")
+    write_synthetic_gguf(p, cfg, seed=11, device="cuda", std=0.05)
+    return p
+
+
+def test_engine_matches_oracle(tiny_model):
+    from prometorch_b200.io.gguf_model import GGUFModel
+    from prometorch_b200.models.gguf_oracle import OracleModel
+    m = GGUFModel(tiny_model, max_seq=512, want_logits=True)
+    o = OracleModel(tiny_model, device="cuda", max_seq=512, emulate_q8=True)
+    toks = [3, 77, 500, 999, 12, 64, 5, 5, 901]
+    for pos, t in enumerate(toks):
+        nxt = m.forward_decode(t, pos)
+        lg = m.logits_view().clone()
+        ref = o.forward([t])[0]
+        cos = torch.nn.functional.cosine_similarity(lg, ref, dim=0)
+        assert cos > 0.9995, (pos, float(cos))
+        assert nxt == int(lg.argmax())
+    m.check_status()
+    m.close()
+
+
+def test_engine_scripted_equals_stepped(tiny_model):
+    from prometorch_b200.io.gguf_model import GGUFModel
+    m = GGUFModel(tiny_model, max_seq=512)
+    prompt = [9, 8, 7, 600, 5]
+    a = m.run_script(prompt, 20)
+    # stepped, host-fed
+    seq = list(prompt)
+    out = []
+    for pos in range(len(prompt) + 19):
+        nxt = m.forward_decode(seq[pos], pos)
+        if pos >= len(prompt) - 1:
+            out.append(nxt)
+            seq.append(nxt)
+    assert a == out
+    b = m.generate(prompt, 20)
+    assert a == b
+    m.close()

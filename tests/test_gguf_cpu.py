@@ -1,0 +1,110 @@
+"""CPU tests of the GGUF stack: block formats, container I/O, config parsing, the fp32 oracle."""
+import os
+
+import pytest
+import torch
+
+from prometorch_b200.io import gguf_quant as Q
+from prometorch_b200.io.config import TransformerConfig, tiny_qwen3_config
+from prometorch_b200.io.gguf import GGUFReader, GGUFWriter
+from prometorch_b200.io.synthetic import write_synthetic_gguf
+
+
+@pytest.mark.parametrize("qt,tol", [(Q.GGMLType.Q4_K, 0.08), (Q.GGMLType.Q5_K, 0.04), (Q.GGMLType.Q6_K, 0.02),
+                                    (Q.GGMLType.Q8_0, 0.006), (Q.GGMLType.Q4_0, 0.12), (Q.GGMLType.F16, 1e-3)])
+def test_quant_roundtrip(qt, tol):
+    torch.manual_seed(0)
+    x = torch.randn(7, 512) * 0.02
+    b = Q.quantize(x, qt)
+    assert b.dtype == torch.uint8 and b.shape == (7, Q.row_bytes(qt, 512))
+    y = Q.dequantize(b, qt, 512)
+    rel = (y - x).norm() / x.norm()
+    assert rel < tol, rel
+
+
+def test_q4k_scalar_reference():
+    """Vectorised Q4_K dequant equals a scalar walk of the documented bit layout."""
+    torch.manual_seed(1)
+    x = torch.randn(1, 256)
+    b = Q.quantize_q4_k(x)[0].tolist()
+    import struct
+    d = struct.unpack("<e", bytes(b[0:2]))[0]
+    dmin = struct.unpack("<e", bytes(b[2:4]))[0]
+    sc = b[4:16]
+    qs = b[16:144]
+
+    def scale_min(j):
+        if j < 4:
+            return sc[j] & 63, sc[j + 4] & 63
+        return (sc[j + 4] & 0xF) | ((sc[j - 4] >> 6) << 4), (sc[j + 4] >> 4) | ((sc[j] >> 6) << 4)
+    ref = []
+    for j in range(4):
+        s1, m1 = scale_min(2 * j)
+        s2, m2 = scale_min(2 * j + 1)
+        chunk = qs[32 * j:32 * j + 32]
+        ref += [d * s1 * (q & 0xF) - dmin * m1 for q in chunk]
+        ref += [d * s2 * (q >> 4) - dmin * m2 for q in chunk]
+    y = Q.dequantize_q4_k(torch.tensor(b, dtype=torch.uint8)[None], 256)[0]
+    assert torch.allclose(y, torch.tensor(ref), atol=1e-6)
+
+
+def test_q6k_scalar_reference():
+    torch.manual_seed(2)
+    x = torch.randn(1, 256)
+    b = Q.quantize_q6_k(x)[0].tolist()
+    import struct
+    ql, qh, sc = b[0:128], b[128:192], b[192:208]
+    sc = [s - 256 if s > 127 else s for s in sc]
+    d = struct.unpack("<e", bytes(b[208:210]))[0]
+    ref = [0.0] * 256
+    for n in range(2):
+        for l in range(32):
+            isx = l // 16
+            q1 = ((ql[n * 64 + l] & 0xF) | (((qh[n * 32 + l] >> 0) & 3) << 4)) - 32
+            q2 = ((ql[n * 64 + l + 32] & 0xF) | (((qh[n * 32 + l] >> 2) & 3) << 4)) - 32
+            q3 = ((ql[n * 64 + l] >> 4) | (((qh[n * 32 + l] >> 4) & 3) << 4)) - 32
+            q4 = ((ql[n * 64 + l + 32] >> 4) | (((qh[n * 32 + l] >> 6) & 3) << 4)) - 32
+            ref[n * 128 + l] = d * sc[n * 8 + isx] * q1
+            ref[n * 128 + l + 32] = d * sc[n * 8 + isx + 2] * q2
+            ref[n * 128 + l + 64] = d * sc[n * 8 + isx + 4] * q3
+            ref[n * 128 + l + 96] = d * sc[n * 8 + isx + 6] * q4
+    y = Q.dequantize_q6_k(torch.tensor(b, dtype=torch.uint8)[None], 256)[0]
+    assert torch.allclose(y, torch.tensor(ref), atol=1e-6)
+
+
+def test_gguf_roundtrip(tmp_path):
+    p = str(tmp_path / "t.gguf")
+    w = GGUFWriter(p)
+    w.add("general.architecture", "llama")
+    w.add("llama.block_count", 3)
+    w.add("llama.rope.freq_base", 10000.0)
+    w.add("tokenizer.ggml.tokens", ["a", "b", "c"])
+    x = torch.randn(4, 256)
+    w.add_tensor("m.weight", (4, 256), Q.GGMLType.Q6_K, Q.quantize(x, Q.GGMLType.Q6_K))
+    w.add_tensor("n.weight", (5,), Q.GGMLType.F32, Q.quantize(torch.arange(5.0), Q.GGMLType.F32))
+    w.write()
+    r = GGUFReader(p)
+    assert r.get("llama.block_count") == 3 and r.get("tokenizer.ggml.tokens") == ["a", "b", "c"]
+    assert r.tensors["m.weight"].shape == (4, 256) and r.tensors["m.weight"].offset % 32 == 0
+    assert torch.equal(r.load("n.weight"), torch.arange(5.0))
+    assert (r.load("m.weight") - x).norm() / x.norm() < 0.02
+    r.close()
+
+
+def test_synthetic_model_and_oracle(tmp_path):
+    from prometorch_b200.models.gguf_oracle import OracleModel
+    cfg = tiny_qwen3_config(layers=2, hidden=256, heads=4, kv_heads=2, inter=512, vocab=300)
+    p = write_synthetic_gguf(str(tmp_path / "tiny.gguf"), cfg, seed=3, device="cpu")
+    r = GGUFReader(p)
+    c2 = TransformerConfig.from_gguf(r)
+    assert (c2.hidden_size, c2.num_layers, c2.num_heads, c2.num_kv_heads, c2.head_dim) == (256, 2, 4, 2, 128)
+    assert c2.has_qk_norm and c2.rope_neox and c2.vocab_size == 300
+    assert r.tensors["blk.0.attn_v.weight"].qtype == Q.GGMLType.Q6_K
+    assert r.tensors["blk.0.attn_q.weight"].qtype == Q.GGMLType.Q4_K
+    m = OracleModel(r)
+    toks = [5, 17, 42, 250]
+    full = m.forward(toks)
+    m.reset()
+    inc = torch.cat([m.forward([t]) for t in toks])
+    assert full.shape == (4, 300)
+    assert torch.allclose(full, inc, atol=1e-4), (full - inc).abs().max()
