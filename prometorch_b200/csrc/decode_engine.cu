@@ -56,35 +56,10 @@ struct PtbModelDesc {
     int slot_floats, pad2;
 };
 
+static size_t g_gemv_max_dyn = 200 * 1024;
 static int env_int(const char* name, int dflt) {
     const char* v = getenv(name);
     return v && *v ? atoi(v) : dflt;
-}
-
-static size_t gemv_header_bytes(int K) {
-    size_t h = 128 + (4 * GEMV_GROUPS + 64) * 4 + (size_t)K + (size_t)(K / 32) * 4 + (size_t)(K / 16) * 4;
-    return (h + 127) / 128 * 128;
-}
-
-// Choose rows-per-stage R and groups-per-row gpr for a matrix with `nblk` super-blocks per row.
-static void plan_job(GemvJob& j, int stage_cap) {
-    const int pairs = j.w2 ? 2 : 1;
-    double best = -1;
-    int bestR = 1, bestG = 1;
-    for (int gpr = 1; gpr <= std::min(GEMV_GROUPS, j.nblk); ++gpr) {
-        int R = GEMV_GROUPS / gpr;
-        const int capR = stage_cap / (j.rowbytes * pairs);
-        if (capR < 1) continue;
-        R = std::min(R, capR);
-        const int rounds = (j.nblk + gpr - 1) / gpr;
-        double eff = ((double)R * gpr / GEMV_GROUPS) * ((double)j.nblk / ((double)rounds * gpr));
-        // a stage that is too small spends its time on barriers
-        const double bytes = (double)R * j.rowbytes * pairs;
-        if (bytes < 8192) eff *= 0.5 + 0.5 * bytes / 8192.0;
-        if (eff > best + 1e-9 || (eff > best - 1e-9 && R > bestR)) { best = eff; bestR = R; bestG = gpr; }
-    }
-    j.R = bestR;
-    j.gpr = bestG;
 }
 
 struct GemvLaunch {
@@ -93,30 +68,29 @@ struct GemvLaunch {
     size_t smem;
 };
 
-// Fill job geometry, CTA split and shared memory size.  `jobs` already carry w/w2/out/bias/qtype/N/rowbytes/nblk.
+// Fill job geometry, CTA split, tile ring and shared memory size.  `jobs` already carry
+// w/w2/out/bias/qtype/N/nblk/KS/seg_base/seg_rem.
 static int plan_gemv(GemvLaunch& L, int njobs, int K, int n_ctas) {
-    const int stages = env_int("PTB_GEMV_STAGES", 4);
-    int stage_cap = env_int("PTB_GEMV_STAGE_KB", 32) * 1024;
+    const int want_stages = env_int("PTB_GEMV_STAGES", 4);
+    const int tile_cap = env_int("PTB_GEMV_TILE_KB", 6) * 1024;
+    const size_t budget = (size_t)env_int("PTB_GEMV_SMEM_KB", 100) * 1024;
     GemvParams& p = L.p;
     p.njobs = njobs;
     p.K = K;
-    size_t max_row = 0;
-    for (int i = 0; i < njobs; ++i) max_row = std::max(max_row, (size_t)p.job[i].rowbytes * (p.job[i].w2 ? 2 : 1));
-    if ((size_t)stage_cap < max_row) stage_cap = (int)max_row;
-    double total = 0;
-    int stage_bytes = 0;
-    for (int i = 0; i < njobs; ++i) {
-        plan_job(p.job[i], stage_cap);
-        total += (double)p.job[i].N * p.job[i].rowbytes * (p.job[i].w2 ? 2 : 1);
-        stage_bytes = std::max(stage_bytes, p.job[i].R * p.job[i].rowbytes * (p.job[i].w2 ? 2 : 1));
+    const int warps = env_int("PTB_GEMV_WARPS", 8) >= 16 ? 16 : 8;
+    p.warps = warps;
+    if (K % 256 || K > 5 * 8 * 256) {
+        ptb_set_error("gemv: input length %d must be a multiple of 256 and at most %d", K, 5 * 8 * 256);
+        return -1;
     }
-    stage_bytes = (stage_bytes + 127) / 128 * 128;
     // CTAs proportional to bytes, at least one each, never more CTAs than rows
+    double total = 0;
+    for (int i = 0; i < njobs; ++i) total += (double)p.job[i].N * p.job[i].nblk * (p.job[i].qtype == QT_Q4K ? 144 : 210) * (p.job[i].w2 ? 2 : 1);
     int left = n_ctas, begin = 0;
     double left_bytes = total;
     for (int i = 0; i < njobs; ++i) {
         GemvJob& j = p.job[i];
-        const double b = (double)j.N * j.rowbytes * (j.w2 ? 2 : 1);
+        const double b = (double)j.N * j.nblk * (j.qtype == QT_Q4K ? 144 : 210) * (j.w2 ? 2 : 1);
         int c = (i == njobs - 1) ? left : (int)(left * b / left_bytes + 0.5);
         c = std::max(1, std::min(c, left - (njobs - 1 - i)));
         c = std::min(c, j.N);
@@ -127,11 +101,38 @@ static int plan_gemv(GemvLaunch& L, int njobs, int K, int n_ctas) {
         left_bytes -= b;
     }
     L.grid = begin;
+    // rows per warp tile: minimise the per-warp critical path, counted in super-block visits
+    int tile_bytes = 0, acc_floats = 0;
+    for (int i = 0; i < njobs; ++i) {
+        GemvJob& j = p.job[i];
+        const int pairs = j.w2 ? 2 : 1;
+        const int nb = j.seg_base + (j.seg_rem ? 1 : 0);
+        const int sz = seg_bytes(j.qtype, nb);
+        const int rows_cta = (j.N + j.cta_count - 1) / j.cta_count;
+        double best = 1e30;
+        int bestRW = 1;
+        for (int RW = 8; RW >= 1; RW >>= 1) {
+            if (RW > 1 && RW * sz * pairs > tile_cap) continue;
+            const int gprw = 8 / RW;
+            const int items = ((rows_cta + RW - 1) / RW) * j.KS;
+            const int rounds = (items + warps - 1) / warps;
+            const double cost = rounds * ((double)((nb + gprw - 1) / gprw) * pairs + 1.0);
+            if (cost < best - 1e-9) { best = cost; bestRW = RW; }
+        }
+        j.RW = bestRW;
+        tile_bytes = std::max(tile_bytes, bestRW * sz * pairs);
+        if (j.KS > 1) acc_floats = std::max(acc_floats, rows_cta * j.KS * pairs);
+    }
+    tile_bytes = (tile_bytes + 127) / 128 * 128;
+    int stages = want_stages;
+    while (stages > 2 && gemv_smem_layout(K, warps, stages, tile_bytes, acc_floats).total > budget) --stages;
     p.stages = stages;
-    p.stage_bytes = stage_bytes;
-    L.smem = gemv_header_bytes(K) + (size_t)stages * stage_bytes;
-    if (L.smem > 227 * 1024) {
-        ptb_set_error("gemv: %zu B of shared memory needed (K=%d, stage %d B x %d)", L.smem, K, stage_bytes, stages);
+    p.tile_bytes = tile_bytes;
+    p.acc_floats = acc_floats;
+    L.smem = gemv_smem_layout(K, warps, stages, tile_bytes, acc_floats).total;
+    if (L.smem > g_gemv_max_dyn) {
+        ptb_set_error("gemv: %zu B of shared memory needed (K=%d, tile %d B x %d stages x %d warps, %d accumulators)", L.smem, K,
+                      tile_bytes, stages, warps, acc_floats);
         return -1;
     }
     return 0;
@@ -145,14 +146,24 @@ static void set_job(GemvJob& j, const PtbWeightDesc& w, const PtbWeightDesc* w2,
     j.out = out;
     j.qtype = w.qtype;
     j.N = w.rows;
-    j.rowbytes = w.rowbytes;
     j.nblk = w.cols / 256;
+    j.KS = (j.nblk + GEMV_SEG_BLOCKS - 1) / GEMV_SEG_BLOCKS;
+    j.seg_base = j.nblk / j.KS;
+    j.seg_rem = j.nblk % j.KS;
 }
 
 static bool g_attr_done = false;
 static int ensure_attrs() {
     if (g_attr_done) return 0;
-    PTB_CUDA_OK(cudaFuncSetAttribute(gemv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    // 227 KB per CTA is shared between the kernel's static and dynamic shared memory
+    cudaFuncAttributes fa;
+    PTB_CUDA_OK(cudaFuncGetAttributes(&fa, gemv_kernel<8>));
+    int optin = 0, dev = 0;
+    PTB_CUDA_OK(cudaGetDevice(&dev));
+    PTB_CUDA_OK(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    g_gemv_max_dyn = (size_t)optin - fa.sharedSizeBytes;
+    PTB_CUDA_OK(cudaFuncSetAttribute(gemv_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_gemv_max_dyn));
+    PTB_CUDA_OK(cudaFuncSetAttribute(gemv_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_gemv_max_dyn));
     g_attr_done = true;
     return 0;
 }
@@ -171,6 +182,46 @@ static cudaError_t launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cud
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kern, p);
+}
+
+template <int G>
+static cudaError_t launch_attn_g(const AttnParams& a, int n_kv_heads, cudaStream_t st, bool pdl) {
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(AttnShared));
+        if (e != cudaSuccess) return e;
+        attr_done = true;
+    }
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(n_kv_heads * ATT_CLUSTER);
+    cfg.blockDim = dim3(ATT_THREADS);
+    cfg.dynamicSmemBytes = sizeof(AttnShared);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = ATT_CLUSTER;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 2 : 1;
+    return cudaLaunchKernelEx(&cfg, attn_decode_kernel<G>, a);
+}
+static cudaError_t launch_attn(const AttnParams& a, int n_kv_heads, cudaStream_t st, bool pdl) {
+    switch (a.group) {
+        case 1: return launch_attn_g<1>(a, n_kv_heads, st, pdl);
+        case 2: return launch_attn_g<2>(a, n_kv_heads, st, pdl);
+        case 4: return launch_attn_g<4>(a, n_kv_heads, st, pdl);
+        case 8: return launch_attn_g<8>(a, n_kv_heads, st, pdl);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+static cudaError_t launch_gemv(const GemvLaunch& L, cudaStream_t st, bool pdl) {
+    if (L.p.warps == 16) return launch_pdl(gemv_kernel<16>, dim3(L.grid), dim3(512), L.smem, st, pdl, L.p);
+    return launch_pdl(gemv_kernel<8>, dim3(L.grid), dim3(256), L.smem, st, pdl, L.p);
 }
 
 // ------------------------------------------------------------------------------------------ standalone op entry points (tests, benches)
@@ -204,7 +255,8 @@ PTB_API int ptb_gemv(const void* w, const void* w2, int qtype, int rows, int col
         L.p.logits = out;
     }
     if (plan_gemv(L, 1, cols, n_ctas)) return -1;
-    PTB_CUDA_OK(launch_pdl(gemv_kernel, dim3(L.grid), dim3(GEMV_THREADS), L.smem, stream, false, L.p));
+    if (getenv("PTB_GEMV_TRACE") && epilogue != EPI_ARGMAX) L.p.trace = (unsigned long long*)scratch;
+    PTB_CUDA_OK(launch_gemv(L, stream, false));
     return 0;
 }
 
@@ -212,8 +264,8 @@ PTB_API int ptb_attn_decode(const float* q, const float* k, const float* v, cons
                             const float* cos, const float* sin, void* k_cache, void* v_cache, float* out, float* part_o,
                             float* part_ml, unsigned* ticket, const int* ctrl, int n_kv_heads, int group, int max_seq,
                             int neox, float eps, int window, cudaStream_t stream) {
-    if (group > ATT_MAX_GROUP) {
-        ptb_set_error("attn_decode: %d query heads per KV head, at most %d supported", group, ATT_MAX_GROUP);
+    if (!(group == 1 || group == 2 || group == 4 || group == 8)) {
+        ptb_set_error("attn_decode: %d query heads per KV head; supported: 1, 2, 4, %d", group, ATT_MAX_GROUP);
         return -1;
     }
     AttnParams a;
@@ -223,7 +275,7 @@ PTB_API int ptb_attn_decode(const float* q, const float* k, const float* v, cons
     a.ticket = ticket; a.ctrl = ctrl; a.group = group; a.max_seq = max_seq;
     a.max_splits = (max_seq + ATT_CHUNK - 1) / ATT_CHUNK;
     a.neox = neox; a.eps = eps; a.scale = 1.0f / sqrtf((float)ATT_D); a.window = window;
-    PTB_CUDA_OK(launch_pdl(attn_decode_kernel, dim3(n_kv_heads, a.max_splits), dim3(ATT_THREADS), 0, stream, false, a));
+    PTB_CUDA_OK(launch_attn(a, n_kv_heads, stream, false));
     return 0;
 }
 
@@ -253,6 +305,7 @@ struct Engine {
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
     bool use_pdl = true;
+    unsigned long long* trace = nullptr;   // PTB_TRACE=1: [kernels per token][8] phase stamps of the last token
     long launches_per_token = 0;
 };
 
@@ -286,6 +339,10 @@ static int engine_alloc(Engine* e) {
     PTB_CUDA_OK(cudaMalloc(&e->script, sizeof(int) * m.max_seq));
     PTB_CUDA_OK(cudaMalloc(&e->status, sizeof(int)));
     PTB_CUDA_OK(cudaMemset(e->status, 0, sizeof(int)));
+    if (env_int("PTB_TRACE", 0)) {
+        PTB_CUDA_OK(cudaMalloc(&e->trace, 8 * sizeof(unsigned long long) * (5 * m.n_layers + 2)));
+        PTB_CUDA_OK(cudaMemset(e->trace, 0, 8 * sizeof(unsigned long long) * (5 * m.n_layers + 2)));
+    }
     PTB_CUDA_OK(cudaMallocHost(&e->h_pinned, sizeof(int) * 16));
     memset(e->h_pinned, 0, sizeof(int) * 16);
     return 0;
@@ -308,7 +365,7 @@ static void fill_peers(const Engine* e, GemvParams& p, int which, int call_idx, 
 static int engine_plan(Engine* e) {
     const PtbModelDesc& m = e->m;
     const int qd = m.n_heads * m.head_dim, kvd = m.n_kv_heads * m.head_dim;
-    const int n_ctas = e->n_sm * env_int("PTB_GEMV_CTAS_PER_SM", 1);
+    const int n_ctas = e->n_sm * env_int("PTB_GEMV_CTAS_PER_SM", 2);
     const bool tp = m.tp_world > 1;
     e->gemvs.clear();
     for (int l = 0; l < m.n_layers; ++l) {
@@ -394,7 +451,8 @@ static int engine_enqueue(Engine* e) {
     for (int l = 0; l < m.n_layers; ++l) {
         const PtbLayerDesc& L = e->layers[l];
         GemvLaunch& g0 = e->gemvs[gi++];
-        PTB_CUDA_OK(launch_pdl(gemv_kernel, dim3(g0.grid), dim3(GEMV_THREADS), g0.smem, e->stream, pdl, g0.p));
+        if (e->trace) g0.p.trace = e->trace + 8 * (1 + 5 * l);
+        PTB_CUDA_OK(launch_gemv(g0, e->stream, pdl));
         AttnParams a;
         memset(&a, 0, sizeof(a));
         a.q = e->qkv; a.k = e->qkv + qd; a.v = e->qkv + qd + kvd;
@@ -404,15 +462,18 @@ static int engine_enqueue(Engine* e) {
         a.out = e->att; a.part_o = e->part_o; a.part_ml = e->part_ml; a.ticket = e->tickets + 8; a.ctrl = e->ctrl;
         a.group = m.n_heads / m.n_kv_heads; a.max_seq = m.max_seq; a.max_splits = splits; a.neox = m.neox;
         a.eps = m.eps; a.scale = 1.0f / sqrtf((float)m.head_dim); a.window = L.window;
-        PTB_CUDA_OK(launch_pdl(attn_decode_kernel, dim3(m.n_kv_heads, splits), dim3(ATT_THREADS), 0, e->stream, pdl, a));
+        if (e->trace) a.trace = e->trace + 8 * (2 + 5 * l);
+        PTB_CUDA_OK(launch_attn(a, m.n_kv_heads, e->stream, pdl));
         for (int k = 0; k < 3; ++k) {
             GemvLaunch& g = e->gemvs[gi++];
-            PTB_CUDA_OK(launch_pdl(gemv_kernel, dim3(g.grid), dim3(GEMV_THREADS), g.smem, e->stream, pdl, g.p));
+            if (e->trace) g.p.trace = e->trace + 8 * (3 + k + 5 * l);
+            PTB_CUDA_OK(launch_gemv(g, e->stream, pdl));
         }
         n += 5;
     }
     GemvLaunch& gl = e->gemvs[gi++];
-    PTB_CUDA_OK(launch_pdl(gemv_kernel, dim3(gl.grid), dim3(GEMV_THREADS), gl.smem, e->stream, pdl, gl.p));
+    if (e->trace) gl.p.trace = e->trace + 8 * (1 + 5 * m.n_layers);
+    PTB_CUDA_OK(launch_gemv(gl, e->stream, pdl));
     ++n;
     e->launches_per_token = n;
     return 0;
@@ -423,7 +484,8 @@ PTB_API void* ptb_engine_create(const PtbModelDesc* m, const PtbLayerDesc* layer
         ptb_set_error("decode engine: head_dim %d not supported (kernels are built for %d)", m->head_dim, ATT_D);
         return nullptr;
     }
-    if (m->n_heads % m->n_kv_heads || m->n_heads / m->n_kv_heads > ATT_MAX_GROUP) {
+    const int grp_ = m->n_kv_heads ? m->n_heads / m->n_kv_heads : 0;
+    if (m->n_heads % m->n_kv_heads || !(grp_ == 1 || grp_ == 2 || grp_ == 4 || grp_ == 8)) {
         ptb_set_error("decode engine: %d query heads over %d KV heads not supported", m->n_heads, m->n_kv_heads);
         return nullptr;
     }
@@ -551,6 +613,15 @@ PTB_API int ptb_engine_status(void* h) {
     if (cudaMemcpy(&s, e->status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
     return s;
 }
+// Copy the phase stamps of the last token ([kernels][8] uint64 nanoseconds) to `out`; returns the kernel count.
+PTB_API int ptb_engine_read_trace(void* h, unsigned long long* out, int max_kernels) {
+    Engine* e = (Engine*)h;
+    if (!e->trace) return 0;
+    const int n = std::min(max_kernels, 5 * e->m.n_layers + 2);
+    PTB_CUDA_OK(cudaStreamSynchronize(e->stream));
+    PTB_CUDA_OK(cudaMemcpy(out, e->trace, sizeof(unsigned long long) * 8 * n, cudaMemcpyDeviceToHost));
+    return n;
+}
 PTB_API void* ptb_engine_stream(void* h) { return (void*)((Engine*)h)->stream; }
 PTB_API void* ptb_engine_logits(void* h) { return (void*)((Engine*)h)->logits; }
 PTB_API void* ptb_engine_hidden(void* h) { return (void*)((Engine*)h)->x; }
@@ -562,13 +633,13 @@ PTB_API int ptb_engine_kv_bytes(void* h, long* out) {
     return 0;
 }
 
-// Geometry report for one GEMV (tests and notes): R, gpr, grid, smem, stage bytes.
+// Geometry report for one GEMV (tests and notes): rows per tile, stages, grid, smem, tile bytes.
 PTB_API int ptb_gemv_plan(int qtype, int rows, int cols, int rowbytes, int paired, int n_ctas, int* out5) {
     GemvLaunch L;
     memset(&L, 0, sizeof(L));
     PtbWeightDesc d{(const void*)16, nullptr, qtype, rows, cols, rowbytes};
     set_job(L.p.job[0], d, paired ? &d : nullptr, nullptr);
     if (plan_gemv(L, 1, cols, n_ctas)) return -1;
-    out5[0] = L.p.job[0].R; out5[1] = L.p.job[0].gpr; out5[2] = L.grid; out5[3] = (int)L.smem; out5[4] = L.p.stage_bytes;
+    out5[0] = L.p.job[0].RW; out5[1] = L.p.stages; out5[2] = L.grid; out5[3] = (int)L.smem; out5[4] = L.p.tile_bytes;
     return 0;
 }

@@ -16,29 +16,36 @@
 // aten/src/ATen/cuda/CUDAQuantGemv.cu and the 9 of FlashDecoding.cu.
 #pragma once
 #include "common.cuh"
+#include <cooperative_groups.h>
 
 namespace ptb {
 
-constexpr int GEMV_THREADS = 512;
-constexpr int GEMV_GROUPS = GEMV_THREADS / 8;   // one 8-lane group works on one (row, super-block)
+constexpr int GEMV_MAX_WARPS = 16;
 constexpr int GEMV_MAX_JOBS = 3;
+constexpr int GEMV_SEG_BLOCKS = 10;             // K is cut into segments of at most this many 256-value super-blocks
 constexpr int MAX_PEERS = 8;
 
 enum QType : int { QT_Q4K = 0, QT_Q6K = 1 };
 enum Epilogue : int { EPI_STORE = 0, EPI_RESID = 1, EPI_GATED = 2, EPI_ARGMAX = 3, EPI_ALLREDUCE = 4 };
 
-// Row layouts in device memory (produced once at load time):
-//   Q4_K: the GGUF bytes as they are: nblk x {fp16 d, fp16 dmin, 12 B scales, 128 B quants}.
-//   Q6_K: structure-of-arrays per row so every section is 16 B aligned:
-//         ql[nblk*128] | qh[nblk*64] | int8 scales[nblk*16] | fp16 d[nblk] padded to 16 B.
+// Weight layout in device memory (produced once at load time), "segment-major":
+//   K is cut into KS = ceil(nblk / 10) segments (the first nblk % KS of them one block longer);
+//   the matrix is stored as [segment][row][segment bytes], so the same K-segment of consecutive
+//   rows is contiguous and a warp's tile (1, 2 or 4 rows x one segment) is one bulk copy.
+//   Q4_K segment of nb blocks: nb x {fp16 d, fp16 dmin, 12 B scales, 128 B quants} (the GGUF bytes).
+//   Q6_K segment of nb blocks: ql[nb*128] | qh[nb*64] | int8 scales[nb*16] | fp16 d[nb] padded to 16 B.
+__host__ __device__ __forceinline__ int seg_bytes(int qtype, int nb) {
+    return qtype == QT_Q4K ? nb * 144 : nb * 208 + ((nb * 2 + 15) & ~15);
+}
+
 struct GemvJob {
     const uint8_t* w;
     const uint8_t* w2;      // second matrix of a gated pair (same shape and type) or null
     const float* bias;      // optional [N]
     float* out;
-    int qtype, N, rowbytes, nblk;
-    int R;                  // rows per pipeline stage
-    int gpr;                // 8-lane groups cooperating on one row
+    int qtype, N, nblk;
+    int KS, seg_base, seg_rem;
+    int RW;                 // rows per warp tile: 1, 2, 4 or 8 (8/RW four-lane groups share a row)
     int cta_begin, cta_count;
 };
 
@@ -76,7 +83,10 @@ struct GemvParams {
     PeerInfo peers;
     const uint32_t* gen;    // device generation counter (monotonic, one per token)
     int* status;
-    int stages, stage_bytes;
+    int warps;              // warps per CTA (8 or 16): selects the kernel instantiation
+    int stages, tile_bytes; // per-warp ring: `stages` slots of `tile_bytes`
+    int acc_floats;         // shared-memory accumulators for K-split jobs (0 if every job has KS == 1)
+    unsigned long long* trace;  // optional [8] %globaltimer stamps of CTA 0's phases (profiling aid)
 };
 
 // control block indices
@@ -84,70 +94,79 @@ enum { CTRL_TOKEN = 0, CTRL_POS = 1, CTRL_STEP = 2, CTRL_SELF_FEED = 3, CTRL_LOG
 
 __device__ __forceinline__ int dp4a_s(int a, int b, int c) { return __dp4a(a, b, c); }
 
-// One 8-lane group x one Q4_K super-block.  bp -> 144 B block in shared memory.
-__device__ __forceinline__ float q4k_dot(const uint8_t* bp, int lane8, const int8_t* xq, const float* xs, const float* xsf) {
+// ---- dot products: FOUR lanes cooperate on one 256-value super-block (64 weights per lane), so the
+// scale decoding and the int->float work are amortised over 16 dp4a.  `swap` flips the order of a
+// lane's two 16-byte loads so that the two groups sharing a shared-memory wavefront hit different banks.
+
+__device__ __forceinline__ float q4k_dot(const uint8_t* bp, int j, bool swap, const int8_t* xq, const float* xs,
+                                         const float* xsf32) {
     const uint4 hdr = *reinterpret_cast<const uint4*>(bp);
-    const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffffu)));
-    const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
-    const int j = lane8 >> 1, hf = lane8 & 1;
-    const uint4 qv = *reinterpret_cast<const uint4*>(bp + 16 + lane8 * 16);
-    const uint4 xl = *reinterpret_cast<const uint4*>(xq + j * 64 + hf * 16);
-    const uint4 xh = *reinterpret_cast<const uint4*>(xq + j * 64 + 32 + hf * 16);
-    int dlo = dp4a_s(qv.x & 0x0F0F0F0F, xl.x, 0);
-    dlo = dp4a_s(qv.y & 0x0F0F0F0F, xl.y, dlo);
-    dlo = dp4a_s(qv.z & 0x0F0F0F0F, xl.z, dlo);
-    dlo = dp4a_s(qv.w & 0x0F0F0F0F, xl.w, dlo);
-    int dhi = dp4a_s((qv.x >> 4) & 0x0F0F0F0F, xh.x, 0);
-    dhi = dp4a_s((qv.y >> 4) & 0x0F0F0F0F, xh.y, dhi);
-    dhi = dp4a_s((qv.z >> 4) & 0x0F0F0F0F, xh.z, dhi);
-    dhi = dp4a_s((qv.w >> 4) & 0x0F0F0F0F, xh.w, dhi);
-    const uint32_t s0 = hdr.y, s1 = hdr.z, s2 = hdr.w;
-    int sc_lo, m_lo, sc_hi, m_hi;
-    if (j < 2) {
-        const int sh = 16 * j;
-        sc_lo = (s0 >> sh) & 63;        m_lo = (s1 >> sh) & 63;
-        sc_hi = (s0 >> (sh + 8)) & 63;  m_hi = (s1 >> (sh + 8)) & 63;
-    } else {
-        const int sh = 16 * (j - 2);
-        sc_lo = ((s2 >> sh) & 0xF) | (((s0 >> (sh + 6)) & 3) << 4);
-        m_lo = ((s2 >> (sh + 4)) & 0xF) | (((s1 >> (sh + 6)) & 3) << 4);
-        sc_hi = ((s2 >> (sh + 8)) & 0xF) | (((s0 >> (sh + 14)) & 3) << 4);
-        m_hi = ((s2 >> (sh + 12)) & 0xF) | (((s1 >> (sh + 14)) & 3) << 4);
-    }
-    const float a = (float)sc_lo * xs[2 * j] * (float)dlo + (float)sc_hi * xs[2 * j + 1] * (float)dhi;
-    const float b = (float)m_lo * xsf[4 * j + hf] + (float)m_hi * xsf[4 * j + 2 + hf];
-    return d * a - dmin * b;
+    const float2 dm = __half22float2(*reinterpret_cast<const __half2*>(&hdr.x));
+    const uint8_t* qp = bp + 16 + j * 32;
+    const uint4 qa = *reinterpret_cast<const uint4*>(qp + (swap ? 16 : 0));
+    const uint4 qb = *reinterpret_cast<const uint4*>(qp + (swap ? 0 : 16));
+    const int8_t* xp = xq + j * 64 + (swap ? 16 : 0);
+    const int8_t* xr = xq + j * 64 + (swap ? 0 : 16);
+    const uint4 xla = *reinterpret_cast<const uint4*>(xp), xha = *reinterpret_cast<const uint4*>(xp + 32);
+    const uint4 xlb = *reinterpret_cast<const uint4*>(xr), xhb = *reinterpret_cast<const uint4*>(xr + 32);
+    int l0 = dp4a_s(qa.x & 0x0F0F0F0F, xla.x, 0), l1 = dp4a_s(qb.x & 0x0F0F0F0F, xlb.x, 0);
+    int h0 = dp4a_s((qa.x >> 4) & 0x0F0F0F0F, xha.x, 0), h1 = dp4a_s((qb.x >> 4) & 0x0F0F0F0F, xhb.x, 0);
+    l0 = dp4a_s(qa.y & 0x0F0F0F0F, xla.y, l0); l1 = dp4a_s(qb.y & 0x0F0F0F0F, xlb.y, l1);
+    h0 = dp4a_s((qa.y >> 4) & 0x0F0F0F0F, xha.y, h0); h1 = dp4a_s((qb.y >> 4) & 0x0F0F0F0F, xhb.y, h1);
+    l0 = dp4a_s(qa.z & 0x0F0F0F0F, xla.z, l0); l1 = dp4a_s(qb.z & 0x0F0F0F0F, xlb.z, l1);
+    h0 = dp4a_s((qa.z >> 4) & 0x0F0F0F0F, xha.z, h0); h1 = dp4a_s((qb.z >> 4) & 0x0F0F0F0F, xhb.z, h1);
+    l0 = dp4a_s(qa.w & 0x0F0F0F0F, xla.w, l0); l1 = dp4a_s(qb.w & 0x0F0F0F0F, xlb.w, l1);
+    h0 = dp4a_s((qa.w >> 4) & 0x0F0F0F0F, xha.w, h0); h1 = dp4a_s((qb.w >> 4) & 0x0F0F0F0F, xhb.w, h1);
+    // 6-bit scales/mins of sub-blocks 2j and 2j+1, two per 16-bit lane of the packed header
+    const int sh = 16 * (j & 1);
+    const uint32_t a = (hdr.y >> sh) & 0xffffu, b = (hdr.z >> sh) & 0xffffu, c = (hdr.w >> sh) & 0xffffu;
+    uint32_t sc2, mn2;
+    if (j < 2) { sc2 = a & 0x3f3fu; mn2 = b & 0x3f3fu; }
+    else { sc2 = (c & 0x0f0fu) | ((a & 0xc0c0u) >> 2); mn2 = ((c >> 4) & 0x0f0fu) | ((b & 0xc0c0u) >> 2); }
+    const float2 xs2 = *reinterpret_cast<const float2*>(xs + 2 * j);
+    const float2 sm2 = *reinterpret_cast<const float2*>(xsf32 + 2 * j);
+    const float va = (float)(int)((sc2 & 0xffu) * (uint32_t)(l0 + l1)) * xs2.x + (float)(int)((sc2 >> 8) * (uint32_t)(h0 + h1)) * xs2.y;
+    const float vb = (float)(mn2 & 0xffu) * sm2.x + (float)(mn2 >> 8) * sm2.y;
+    return dm.x * va - dm.y * vb;
 }
 
-// One 8-lane group x one Q6_K super-block of a structure-of-arrays row.
-__device__ __forceinline__ float q6k_dot(const uint8_t* row, int nblk, int blk, int lane8, const int8_t* xq, const float* xs,
-                                         const float* xsf) {
-    const uint8_t* ql = row + blk * 128;
-    const uint8_t* qh = row + nblk * 128 + blk * 64;
-    const int8_t* sc = reinterpret_cast<const int8_t*>(row + nblk * 192 + blk * 16);
-    const float d = __half2float(*reinterpret_cast<const __half*>(row + nblk * 208 + blk * 2));
-    const int n = lane8 >> 2, q = lane8 & 3, which = q >> 1, l0 = (q & 1) * 16;
-    const uint4 qlv = *reinterpret_cast<const uint4*>(ql + n * 64 + q * 16);
-    const uint4 qhv = *reinterpret_cast<const uint4*>(qh + n * 32 + l0);
-    const int e_lo = n * 128 + which * 32 + l0, e_hi = e_lo + 64;
-    const int sh_lo = which * 2, sh_hi = 4 + which * 2;
-    const uint4 xl = *reinterpret_cast<const uint4*>(xq + e_lo);
-    const uint4 xh = *reinterpret_cast<const uint4*>(xq + e_hi);
-#define PTB_Q6_LO(c) ((qlv.c & 0x0F0F0F0F) | (((qhv.c >> sh_lo) & 0x03030303) << 4))
-#define PTB_Q6_HI(c) (((qlv.c >> 4) & 0x0F0F0F0F) | (((qhv.c >> sh_hi) & 0x03030303) << 4))
-    int dlo = dp4a_s(PTB_Q6_LO(x), xl.x, 0);
-    dlo = dp4a_s(PTB_Q6_LO(y), xl.y, dlo);
-    dlo = dp4a_s(PTB_Q6_LO(z), xl.z, dlo);
-    dlo = dp4a_s(PTB_Q6_LO(w), xl.w, dlo);
-    int dhi = dp4a_s(PTB_Q6_HI(x), xh.x, 0);
-    dhi = dp4a_s(PTB_Q6_HI(y), xh.y, dhi);
-    dhi = dp4a_s(PTB_Q6_HI(z), xh.z, dhi);
-    dhi = dp4a_s(PTB_Q6_HI(w), xh.w, dhi);
+// Q6_K structure-of-arrays segment of `nblk` blocks; lane j4 of the group: half n = j4>>1, 32-byte slab which = j4&1.
+__device__ __forceinline__ float q6k_dot(const uint8_t* seg, int nblk, int blk, int j4, bool swap, const int8_t* xq,
+                                         const float* xs, const float* xsf16) {
+    const int n = j4 >> 1, which = j4 & 1;
+    const int o0 = swap ? 16 : 0, o1 = swap ? 0 : 16;
+    const uint8_t* ql = seg + blk * 128 + n * 64 + which * 32;
+    const uint8_t* qh = seg + nblk * 128 + blk * 64 + n * 32;
+    const int8_t* sc = reinterpret_cast<const int8_t*>(seg + nblk * 192 + blk * 16);
+    const float d = __half2float(*reinterpret_cast<const __half*>(seg + nblk * 208 + blk * 2));
+    const uint4 la = *reinterpret_cast<const uint4*>(ql + o0), lb = *reinterpret_cast<const uint4*>(ql + o1);
+    const uint4 ha = *reinterpret_cast<const uint4*>(qh + o0), hb = *reinterpret_cast<const uint4*>(qh + o1);
+    const int e_lo = n * 128 + which * 32, e_hi = e_lo + 64;
+    const uint4 xla = *reinterpret_cast<const uint4*>(xq + e_lo + o0), xlb = *reinterpret_cast<const uint4*>(xq + e_lo + o1);
+    const uint4 xha = *reinterpret_cast<const uint4*>(xq + e_hi + o0), xhb = *reinterpret_cast<const uint4*>(xq + e_hi + o1);
+    // bring the two high bits of each value to bit positions 4-5
+    const int shl = which ? 2 : 4;       // low nibbles use qh bits 0-1 (which=0) or 2-3 (which=1)
+    const int shr = which ? 2 : 0;       // high nibbles use qh bits 4-5 (which=0) or 6-7 (which=1)
+#define PTB_Q6_LO(L, H) (((L) & 0x0F0F0F0Fu) | (((H) << shl) & 0x30303030u))
+#define PTB_Q6_HI(L, H) ((((L) >> 4) & 0x0F0F0F0Fu) | (((H) >> shr) & 0x30303030u))
+    int dla = dp4a_s(PTB_Q6_LO(la.x, ha.x), xla.x, 0), dlb = dp4a_s(PTB_Q6_LO(lb.x, hb.x), xlb.x, 0);
+    int dha = dp4a_s(PTB_Q6_HI(la.x, ha.x), xha.x, 0), dhb = dp4a_s(PTB_Q6_HI(lb.x, hb.x), xhb.x, 0);
+    dla = dp4a_s(PTB_Q6_LO(la.y, ha.y), xla.y, dla); dlb = dp4a_s(PTB_Q6_LO(lb.y, hb.y), xlb.y, dlb);
+    dha = dp4a_s(PTB_Q6_HI(la.y, ha.y), xha.y, dha); dhb = dp4a_s(PTB_Q6_HI(lb.y, hb.y), xhb.y, dhb);
+    dla = dp4a_s(PTB_Q6_LO(la.z, ha.z), xla.z, dla); dlb = dp4a_s(PTB_Q6_LO(lb.z, hb.z), xlb.z, dlb);
+    dha = dp4a_s(PTB_Q6_HI(la.z, ha.z), xha.z, dha); dhb = dp4a_s(PTB_Q6_HI(lb.z, hb.z), xhb.z, dhb);
+    dla = dp4a_s(PTB_Q6_LO(la.w, ha.w), xla.w, dla); dlb = dp4a_s(PTB_Q6_LO(lb.w, hb.w), xlb.w, dlb);
+    dha = dp4a_s(PTB_Q6_HI(la.w, ha.w), xha.w, dha); dhb = dp4a_s(PTB_Q6_HI(lb.w, hb.w), xhb.w, dhb);
 #undef PTB_Q6_LO
 #undef PTB_Q6_HI
-    const float a = (float)sc[e_lo >> 4] * (xs[e_lo >> 5] * (float)dlo - 32.0f * xsf[e_lo >> 4]);
-    const float b = (float)sc[e_hi >> 4] * (xs[e_hi >> 5] * (float)dhi - 32.0f * xsf[e_hi >> 4]);
-    return d * (a + b);
+    // 16-value scale groups: (e + o)/16
+    const int ia = (e_lo + o0) >> 4, ib = (e_lo + o1) >> 4;
+    const float xsl = xs[e_lo >> 5], xsh = xs[e_hi >> 5];
+    float r = (float)sc[ia] * (xsl * (float)dla - 32.0f * xsf16[ia]);
+    r += (float)sc[ib] * (xsl * (float)dlb - 32.0f * xsf16[ib]);
+    r += (float)sc[ia + 4] * (xsh * (float)dha - 32.0f * xsf16[ia + 4]);
+    r += (float)sc[ib + 4] * (xsh * (float)dhb - 32.0f * xsf16[ib + 4]);
+    return d * r;
 }
 
 // Block-wide sum through shared memory; `buf` needs >= 32 floats.  All threads get the result.
@@ -162,77 +181,113 @@ __device__ __forceinline__ float block_sum(float v, float* buf) {
     return t;
 }
 
-// Load x[K], optionally RMS-normalise, quantise to int8 blocks of 32.
-//   xq[K] int8, xs[K/32] block scales, xsf[K/16] = scale * (sum of the 16 int8 values).
+// Load x[K] once into registers, optionally RMS-normalise, quantise to int8 blocks of 32.
+//   xq[K] int8, xs[K/32] block scales, xsf16[K/16] = scale * (sum of 16 int8), xsf32[K/32] = scale * (sum of 32).
+// Each thread keeps up to QIN_ITEMS 8-value items in registers: K <= QIN_ITEMS * 8 * blockDim.
+template <int QIN_ITEMS>
 __device__ __forceinline__ void quantize_input(const float* __restrict__ x, const float* __restrict__ norm_w, float eps,
-                                               int add_one, int K, int8_t* xq, float* xs, float* xsf, float* red) {
+                                               int add_one, int K, int8_t* xq, float* xs, float* xsf16, float* xsf32,
+                                               float* red) {
     const int tid = threadIdx.x, nt = blockDim.x;
+    const int items = K / 8;
+    float v[QIN_ITEMS][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int r = 0; r < QIN_ITEMS; ++r) {
+        const int i = r * nt + tid;
+        if (i < items) {
+            const float4 a = __ldcg(reinterpret_cast<const float4*>(x) + 2 * i), b = __ldcg(reinterpret_cast<const float4*>(x) + 2 * i + 1);
+            v[r][0] = a.x; v[r][1] = a.y; v[r][2] = a.z; v[r][3] = a.w; v[r][4] = b.x; v[r][5] = b.y; v[r][6] = b.z; v[r][7] = b.w;
+        } else {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) v[r][k] = 0.f;
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) ss += v[r][k] * v[r][k];
+    }
     float rs = 1.0f;
     if (norm_w) {
-        float ss = 0.f;
-        for (int i = tid; i < K / 4; i += nt) {
-            const float4 v = reinterpret_cast<const float4*>(x)[i];
-            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-        }
         ss = block_sum(ss, red);
         rs = rsqrtf(ss / (float)K + eps);
     }
-    const int items = K / 8;
-    const int rounds = (items + nt - 1) / nt;
-    for (int r = 0; r < rounds; ++r) {
+#pragma unroll
+    for (int r = 0; r < QIN_ITEMS; ++r) {
         const int i = r * nt + tid;
-        float v[8];
-        if (i < items) {
-            const float4 a = reinterpret_cast<const float4*>(x)[2 * i], b = reinterpret_cast<const float4*>(x)[2 * i + 1];
-            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-            if (norm_w) {
-                const float4 wa = reinterpret_cast<const float4*>(norm_w)[2 * i], wb = reinterpret_cast<const float4*>(norm_w)[2 * i + 1];
-                const float w[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+        if (r * nt >= items) break;
+        if (norm_w && i < items) {
+            const float4 wa = __ldg(reinterpret_cast<const float4*>(norm_w) + 2 * i), wb = __ldg(reinterpret_cast<const float4*>(norm_w) + 2 * i + 1);
+            const float w[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
 #pragma unroll
-                for (int k = 0; k < 8; ++k) v[k] = v[k] * rs * (add_one ? 1.0f + w[k] : w[k]);
-            }
-        } else {
-#pragma unroll
-            for (int k = 0; k < 8; ++k) v[k] = 0.f;
+            for (int k = 0; k < 8; ++k) v[r][k] = v[r][k] * rs * (add_one ? 1.0f + w[k] : w[k]);
         }
         float am = 0.f;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) am = fmaxf(am, fabsf(v[k]));
+        for (int k = 0; k < 8; ++k) am = fmaxf(am, fabsf(v[r][k]));
         am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
         am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
         const float sc = am / 127.0f;
         const float inv = am > 0.f ? 127.0f / am : 0.f;
         int q[8], s = 0;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) { q[k] = __float2int_rn(v[k] * inv); s += q[k]; }
+        for (int k = 0; k < 8; ++k) { q[k] = __float2int_rn(v[r][k] * inv); s += q[k]; }
         const int s16 = s + __shfl_xor_sync(0xffffffffu, s, 1);
+        const int s32 = s16 + __shfl_xor_sync(0xffffffffu, s16, 2);
         if (i < items) {
             uint2 pk;
             pk.x = (q[0] & 0xff) | ((q[1] & 0xff) << 8) | ((q[2] & 0xff) << 16) | ((q[3] & 0xff) << 24);
             pk.y = (q[4] & 0xff) | ((q[5] & 0xff) << 8) | ((q[6] & 0xff) << 16) | ((q[7] & 0xff) << 24);
             reinterpret_cast<uint2*>(xq)[i] = pk;
-            if ((i & 1) == 0) xsf[i >> 1] = sc * (float)s16;
-            if ((i & 3) == 0) xs[i >> 2] = sc;
+            if ((i & 1) == 0) xsf16[i >> 1] = sc * (float)s16;
+            if ((i & 3) == 0) { xs[i >> 2] = sc; xsf32[i >> 2] = sc * (float)s32; }
         }
     }
     __syncthreads();
 }
 
-__device__ __forceinline__ size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+__host__ __device__ __forceinline__ size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-__global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const __grid_constant__ GemvParams P) {
+// Shared memory carve-up, used by the kernel and by the host-side planner.
+struct GemvSmem {
+    size_t bars, misc, xq, xs, xsf, xsf32, acc, tiles, total;
+};
+__host__ __device__ __forceinline__ GemvSmem gemv_smem_layout(int K, int warps, int stages, int tile_bytes, int acc_floats) {
+    GemvSmem L;
+    L.bars = 0;
+    L.misc = align_up((size_t)warps * stages * 8, 128);
+    L.xq = L.misc + 64 * 4;
+    L.xs = L.xq + (size_t)K;
+    L.xsf = L.xs + (size_t)(K / 32) * 4;
+    L.xsf32 = L.xsf + (size_t)(K / 16) * 4;
+    L.acc = L.xsf32 + (size_t)(K / 32) * 4;
+    L.tiles = align_up(L.acc + (size_t)acc_floats * 4, 128);
+    L.total = L.tiles + (size_t)warps * stages * tile_bytes;
+    return L;
+}
+
+template <int GEMV_WARPS>
+__global__ void __launch_bounds__(GEMV_WARPS * 32, 2) gemv_kernel(const __grid_constant__ GemvParams P) {
+    constexpr int GEMV_THREADS = GEMV_WARPS * 32;
     extern __shared__ __align__(128) uint8_t smem[];
-    const int tid = threadIdx.x;
-    const int K = P.K;
-    // ---- shared memory carve-up
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem);                       // [stages]
-    float* red = reinterpret_cast<float*>(smem + 128);                        // [2][2*GROUPS] + 32 scratch
-    float* misc = red + 4 * GEMV_GROUPS;                                      // 64 floats
-    int8_t* xq = reinterpret_cast<int8_t*>(misc + 64);
-    float* xs = reinterpret_cast<float*>(xq + K);
-    float* xsf = xs + K / 32;
-    uint8_t* stage0 = smem + align_up(128 + (4 * GEMV_GROUPS + 64) * 4 + K + (K / 32) * 4 + (K / 16) * 4, 128);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int K = P.K, S = P.stages;
+    const GemvSmem L = gemv_smem_layout(K, GEMV_WARPS, S, P.tile_bytes, P.acc_floats);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.bars) + warp * S;    // this warp's ring
+    float* misc = reinterpret_cast<float*>(smem + L.misc);
+    int8_t* xq = reinterpret_cast<int8_t*>(smem + L.xq);
+    float* xs = reinterpret_cast<float*>(smem + L.xs);
+    float* xsf = reinterpret_cast<float*>(smem + L.xsf);
+    float* xsf32 = reinterpret_cast<float*>(smem + L.xsf32);
+    float* acc = reinterpret_cast<float*>(smem + L.acc);
+    uint8_t* ring = smem + L.tiles + (size_t)warp * S * P.tile_bytes;
 
+    auto stamp = [&](int k) {
+        if (P.trace && tid == 0 && blockIdx.x == 0) {
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            P.trace[k] = t;
+        }
+    };
+    stamp(0);
     // ---- which job and which rows are mine
     int ji = 0;
 #pragma unroll
@@ -242,110 +297,164 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const __grid_cons
     const int ci = blockIdx.x - J.cta_begin;
     const int r0 = (int)(((long long)J.N * ci) / J.cta_count);
     const int r1 = (int)(((long long)J.N * (ci + 1)) / J.cta_count);
-    const int R = J.R;
-    const int nchunks = (r1 - r0 + R - 1) / R;
+    const int RW = J.RW, KS = J.KS, qtype = J.qtype;
+    const int nrg = (r1 - r0 + RW - 1) / RW;
+    const int nitems = nrg * KS;
     const bool paired = J.w2 != nullptr;
-    const int S = P.stages;
-    const uint32_t mat_bytes = (uint32_t)R * J.rowbytes;   // one matrix's share of a full stage
+    const int sz0 = seg_bytes(qtype, J.seg_base), sz1 = seg_bytes(qtype, J.seg_base + 1);
 
-    auto issue = [&](int c) {   // thread 0 only
-        const int s = c % S;
-        const int rows = min(R, r1 - (r0 + c * R));
-        const uint32_t bytes = (uint32_t)rows * J.rowbytes;
-        uint8_t* dst = stage0 + (size_t)s * P.stage_bytes;
-        mbar_expect_tx(&full[s], paired ? 2 * bytes : bytes);
-        bulk_g2s(dst, J.w + (size_t)(r0 + c * R) * J.rowbytes, bytes, &full[s]);
-        if (paired) bulk_g2s(dst + mat_bytes, J.w2 + (size_t)(r0 + c * R) * J.rowbytes, bytes, &full[s]);
+    // item -> geometry
+    struct Item { int s, nb, boff, sb, row0, rows; size_t off; };
+    auto geom = [&](int it) {
+        Item g;
+        const int rg = it / KS;
+        g.s = it - rg * KS;
+        const int extra = min(g.s, J.seg_rem);
+        g.nb = J.seg_base + (g.s < J.seg_rem ? 1 : 0);
+        g.boff = g.s * J.seg_base + extra;
+        g.sb = g.s < J.seg_rem ? sz1 : sz0;
+        g.row0 = r0 + rg * RW;
+        g.rows = min(RW, r1 - g.row0);
+        g.off = (size_t)J.N * ((size_t)g.s * sz0 + (size_t)extra * (sz1 - sz0)) + (size_t)g.row0 * g.sb;
+        return g;
+    };
+    auto issue = [&](int it, int slot) {   // lane 0 of the warp
+        const Item g = geom(it);
+        const uint32_t bytes = (uint32_t)g.rows * g.sb;
+        uint8_t* dst = ring + (size_t)slot * P.tile_bytes;
+        mbar_expect_tx(&full[slot], paired ? 2 * bytes : bytes);
+        bulk_g2s(dst, J.w + g.off, bytes, &full[slot]);
+        if (paired) bulk_g2s(dst + RW * g.sb, J.w2 + g.off, bytes, &full[slot]);
     };
 
-    if (tid == 0) {
+    if (lane == 0) {
         for (int s = 0; s < S; ++s) mbar_init(&full[s], 1);
         mbar_fence_init();
         fence_proxy_async();
-        // weights do not depend on the previous kernel: start streaming them now
-        for (int c = 0; c < S && c < nchunks; ++c) issue(c);
+        // the weights do not depend on the previous kernel: start streaming them now
+        for (int k = 0; k < S; ++k) {
+            const int it = warp + k * GEMV_WARPS;
+            if (it < nitems) issue(it, k);
+        }
+    }
+    if (P.norm_w) {
+        for (int i = tid * 32; i < K; i += GEMV_THREADS * 32)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(P.norm_w + i));
     }
     pdl_launch_dependents();
     pdl_wait();
     __syncthreads();
+    stamp(1);
 
-    quantize_input(P.x, P.norm_w, P.eps, P.norm_add_one, K, xq, xs, xsf, misc);
+    // the RMSNorm weights are parameters too: pull them towards L1/L2 before the dependency wait
+    if (K <= 2 * 8 * GEMV_THREADS) quantize_input<2>(P.x, P.norm_w, P.eps, P.norm_add_one, K, xq, xs, xsf, xsf32, misc);
+    else quantize_input<(GEMV_WARPS >= 16 ? 3 : 5)>(P.x, P.norm_w, P.eps, P.norm_add_one, K, xq, xs, xsf, xsf32, misc);
+    stamp(2);
 
-    const int grp = tid >> 3, lane8 = tid & 7;
-    const int gpr = J.gpr;
-    const int my_row = grp / gpr, my_j = grp - my_row * gpr;
-    const bool grp_active = my_row < R;
-    const int nblk = J.nblk;
+    // eight 4-lane groups per warp; neighbouring groups take neighbouring rows (same x addresses -> broadcast)
+    const int grp = lane >> 2, lane4 = lane & 3;
+    const int gprw = 8 / RW;
+    const int my_row = grp % RW, my_j = grp / RW;
     float best_v = -INFINITY;
     int best_i = 0x7fffffff;
     bool ok = true;
 
-    for (int c = 0; c < nchunks; ++c) {
-        const int s = c % S;
-        const int rows = min(R, r1 - (r0 + c * R));
-        if (ok) ok = mbar_wait(&full[s], (uint32_t)((c / S) & 1), P.status);
-        const uint8_t* st = stage0 + (size_t)s * P.stage_bytes;
+    auto epilogue = [&](int n, float v0, float v1) {
+        if (J.bias) v0 += J.bias[n];
+        switch (P.epilogue) {
+            case EPI_STORE: J.out[n] = v0; break;
+            case EPI_RESID: J.out[n] = P.resid[n] + v0; break;
+            case EPI_GATED: J.out[n] = (P.act_gelu ? gelu_tanh(v0) : silu(v0)) * v1; break;
+            case EPI_ARGMAX:
+                if (P.logits) P.logits[n] = v0;
+                if (v0 > best_v || (v0 == best_v && n < best_i)) { best_v = v0; best_i = n; }
+                break;
+            case EPI_ALLREDUCE: {
+                // push my partial sum for element n to every rank's inbox slot [rank]
+                const PeerInfo& pi = P.peers;
+                for (int p = 0; p < pi.world; ++p) pi.inbox[p][(size_t)pi.rank * pi.slot_floats + n] = v0;
+            } break;
+        }
+    };
+
+    int k = 0;
+    for (int it = warp; it < nitems; it += GEMV_WARPS, ++k) {
+        const int slot = k % S;
+        const Item g = geom(it);
+        if (ok) ok = mbar_wait(&full[slot], (uint32_t)((k / S) & 1), P.status);
+        if (k == 0) stamp(3);
+        const uint8_t* tile = ring + (size_t)slot * P.tile_bytes;
         float a0 = 0.f, a1 = 0.f;
-        if (ok && grp_active && my_row < rows) {
-            const uint8_t* rowp = st + (size_t)my_row * J.rowbytes;
-            if (J.qtype == QT_Q4K) {
-                for (int b = my_j; b < nblk; b += gpr) {
-                    a0 += q4k_dot(rowp + b * 144, lane8, xq + b * 256, xs + b * 8, xsf + b * 16);
-                    if (paired) a1 += q4k_dot(rowp + mat_bytes + b * 144, lane8, xq + b * 256, xs + b * 8, xsf + b * 16);
+        if (ok && my_row < g.rows) {
+            const uint8_t* rowp = tile + (size_t)my_row * g.sb;
+            const int8_t* xq_s = xq + g.boff * 256;
+            const float* xs_s = xs + g.boff * 8;
+            const float* xsf_s = xsf + g.boff * 16;
+            const float* xsf32_s = xsf32 + g.boff * 8;
+            // odd groups flip their two 16-byte loads when the row stride is an even multiple of 16 B
+            const bool swap = (grp & 1) && (((g.sb >> 4) & 1) == 0);
+            if (qtype == QT_Q4K) {
+#pragma unroll 1
+                for (int b = my_j; b < g.nb; b += gprw) {
+                    a0 += q4k_dot(rowp + b * 144, lane4, swap, xq_s + b * 256, xs_s + b * 8, xsf32_s + b * 8);
+                    if (paired) a1 += q4k_dot(rowp + RW * g.sb + b * 144, lane4, swap, xq_s + b * 256, xs_s + b * 8, xsf32_s + b * 8);
                 }
             } else {
-                for (int b = my_j; b < nblk; b += gpr) {
-                    a0 += q6k_dot(rowp, nblk, b, lane8, xq + b * 256, xs + b * 8, xsf + b * 16);
-                    if (paired) a1 += q6k_dot(rowp + mat_bytes, nblk, b, lane8, xq + b * 256, xs + b * 8, xsf + b * 16);
+#pragma unroll 1
+                for (int b = my_j; b < g.nb; b += gprw) {
+                    a0 += q6k_dot(rowp, g.nb, b, lane4, swap, xq_s + b * 256, xs_s + b * 8, xsf_s + b * 16);
+                    if (paired) a1 += q6k_dot(rowp + RW * g.sb, g.nb, b, lane4, swap, xq_s + b * 256, xs_s + b * 8, xsf_s + b * 16);
                 }
             }
         }
+        __syncwarp();
+        if (lane == 0 && it + S * GEMV_WARPS < nitems) issue(it + S * GEMV_WARPS, slot);
+        // lanes of a group (xor 1, 2), then the groups sharing a row: they sit RW groups = 4*RW lanes apart
 #pragma unroll
-        for (int o = 4; o > 0; o >>= 1) {
-            a0 += __shfl_xor_sync(0xffffffffu, a0, o);
-            a1 += __shfl_xor_sync(0xffffffffu, a1, o);
+        for (int o = 1; o < 32; o <<= 1) {
+            if (o < 4 || o >= 4 * RW) {
+                a0 += __shfl_xor_sync(0xffffffffu, a0, o);
+                a1 += __shfl_xor_sync(0xffffffffu, a1, o);
+            }
         }
-        float* rb = red + (c & 1) * 2 * GEMV_GROUPS;
-        if (lane8 == 0) { rb[grp] = a0; rb[GEMV_GROUPS + grp] = a1; }
-        __syncthreads();
-        if (tid == 0 && c + S < nchunks) issue(c + S);
-        if (tid < rows) {
-            float v0 = 0.f, v1 = 0.f;
-            for (int j = 0; j < gpr; ++j) { v0 += rb[tid * gpr + j]; v1 += rb[GEMV_GROUPS + tid * gpr + j]; }
-            const int n = r0 + c * R + tid;
-            if (J.bias) v0 += J.bias[n];
-            switch (P.epilogue) {
-                case EPI_STORE: J.out[n] = v0; break;
-                case EPI_RESID: J.out[n] = P.resid[n] + v0; break;
-                case EPI_GATED: J.out[n] = (P.act_gelu ? gelu_tanh(v0) : silu(v0)) * v1; break;
-                case EPI_ARGMAX:
-                    if (P.logits) P.logits[n] = v0;
-                    if (v0 > best_v) { best_v = v0; best_i = n; }
-                    break;
-                case EPI_ALLREDUCE: {
-                    // push my partial sum for element n to every rank's inbox slot [rank]
-                    const PeerInfo& pi = P.peers;
-                    for (int p = 0; p < pi.world; ++p) pi.inbox[p][(size_t)pi.rank * pi.slot_floats + n] = v0;
-                } break;
+        if (lane4 == 0 && my_j == 0 && my_row < g.rows) {
+            const int n = g.row0 + my_row;
+            if (KS == 1) epilogue(n, a0, a1);
+            else {
+                acc[(size_t)(n - r0) * KS + g.s] = a0;
+                if (paired) acc[(size_t)(r1 - r0) * KS + (size_t)(n - r0) * KS + g.s] = a1;
             }
         }
     }
+    stamp(4);
+    if (KS > 1) {
+        __syncthreads();
+        for (int r = tid; r < r1 - r0; r += GEMV_THREADS) {
+            float v0 = 0.f, v1 = 0.f;
+            for (int s = 0; s < KS; ++s) {
+                v0 += acc[(size_t)r * KS + s];
+                if (paired) v1 += acc[(size_t)(r1 - r0) * KS + (size_t)r * KS + s];
+            }
+            epilogue(r0 + r, v0, v1);
+        }
+    }
 
+    stamp(5);
     if (P.epilogue == EPI_ARGMAX) {
         // CTA arg-max (ties -> lowest index), then the last CTA to arrive finishes across CTAs.
         __syncthreads();
-        float* sv = red;
-        int* si = reinterpret_cast<int*>(red + GEMV_GROUPS);
+        float* sv = misc;
+        int* si = reinterpret_cast<int*>(misc + 32);
         for (int o = 16; o > 0; o >>= 1) {
             const float ov = __shfl_xor_sync(0xffffffffu, best_v, o);
             const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
             if (ov > best_v || (ov == best_v && oi < best_i)) { best_v = ov; best_i = oi; }
         }
-        if ((tid & 31) == 0) { sv[tid >> 5] = best_v; si[tid >> 5] = best_i; }
+        if (lane == 0) { sv[warp] = best_v; si[warp] = best_i; }
         __syncthreads();
         __shared__ bool is_last;
         if (tid == 0) {
-            for (int w = 1; w < GEMV_THREADS / 32; ++w)
+            for (int w = 1; w < GEMV_WARPS; ++w)
                 if (sv[w] > best_v || (sv[w] == best_v && si[w] < best_i)) { best_v = sv[w]; best_i = si[w]; }
             P.amax_val[blockIdx.x] = best_v;
             P.amax_idx[blockIdx.x] = best_i;
@@ -369,10 +478,10 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const __grid_cons
                 if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
             }
             __syncthreads();
-            if ((tid & 31) == 0) { sv[tid >> 5] = bv; si[tid >> 5] = bi; }
+            if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
             __syncthreads();
             if (tid == 0) {
-                for (int w = 1; w < GEMV_THREADS / 32; ++w)
+                for (int w = 1; w < GEMV_WARPS; ++w)
                     if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) { bv = sv[w]; bi = si[w]; }
                 *P.ticket = 0u;
                 bi += P.row_offset;
@@ -484,6 +593,7 @@ struct AttnParams {
     float eps;
     float scale;
     int window;              // sliding window (0 = full)
+    unsigned long long* trace;   // optional [8] %globaltimer stamps (profiling aid)
 };
 
 __device__ __forceinline__ void norm_rope_head(const float* src, const float* nw, float eps, const float* cs, const float* sn,
@@ -516,179 +626,230 @@ __device__ __forceinline__ void norm_rope_head(const float* src, const float* nw
     }
 }
 
-__global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_constant__ AttnParams P) {
-    __shared__ __align__(16) float qs[ATT_MAX_GROUP][ATT_D];
-    __shared__ __align__(16) float kn[ATT_D];
-    __shared__ float sc[ATT_MAX_GROUP][ATT_CHUNK];
-    __shared__ float hm[ATT_MAX_GROUP], hl[ATT_MAX_GROUP];
-    __shared__ __align__(16) float red[ATT_THREADS / 32][ATT_MAX_GROUP][ATT_D];   // 32 KB
-    __shared__ bool last;
+// One thread-block cluster of ATT_CLUSTER CTAs per KV head.  CTA r of the cluster walks cache chunks
+// r, r+CL, r+2CL, ... (128 positions each) with an online softmax, then the CTAs exchange their partial
+// {max, sum, output} through distributed shared memory and each writes 1/CL of the head group's output.
+constexpr int ATT_CLUSTER = 8;
 
+struct AttnShared {
+    float qs[ATT_MAX_GROUP][ATT_D];                         // normalised, rotated, pre-scaled queries
+    float kn[ATT_D];
+    float sc[ATT_MAX_GROUP][ATT_CHUNK];                     // scores, then probabilities of the current chunk
+    float hm[ATT_MAX_GROUP], hl[ATT_MAX_GROUP];             // chunk max / sum
+    float M[ATT_MAX_GROUP], L[ATT_MAX_GROUP];               // running max / sum of this CTA (read by peers)
+    float O[ATT_MAX_GROUP][ATT_D];                          // this CTA's unnormalised output (read by peers)
+    float red[ATT_THREADS / 32][ATT_MAX_GROUP][ATT_D];      // cross-warp reduction
+};
+
+template <int G>
+__global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_constant__ AttnParams P) {
+    extern __shared__ __align__(16) uint8_t att_smem_raw[];
+    AttnShared& sh = *reinterpret_cast<AttnShared*>(att_smem_raw);
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    auto stamp = [&](int k) {
+        if (P.trace && threadIdx.x == 0 && blockIdx.x == 0) {
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            P.trace[k] = t;
+        }
+    };
+    stamp(0);
     pdl_launch_dependents();
     pdl_wait();
+    stamp(1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int kvh = blockIdx.x, split = blockIdx.y;
-    const int pos = P.ctrl[CTRL_POS];
+    const int crank = (int)cluster.block_rank();
+    const int kvh = blockIdx.x / ATT_CLUSTER;
+    const int pos = min(P.ctrl[CTRL_POS], P.max_seq - 1);
     const int T = pos + 1;
     const int lo = (P.window > 0 && T > P.window) ? T - P.window : 0;     // first visible position
-    const int first_split = lo / ATT_CHUNK;
-    const int nsplit = (T + ATT_CHUNK - 1) / ATT_CHUNK;
-    if (split >= nsplit || split < first_split || pos >= P.max_seq) return;
-    const int nactive = nsplit - first_split;
-    const int G = P.group;
-    const int t0 = max(split * ATT_CHUNK, lo), t1 = min(split * ATT_CHUNK + ATT_CHUNK, T);
-    const int base = split * ATT_CHUNK;
+    const int first_chunk = lo / ATT_CHUNK;
+    const int nchunk = (T + ATT_CHUNK - 1) / ATT_CHUNK;
     const float* cs = P.cos + (size_t)pos * (ATT_D / 2);
     const float* sn = P.sin + (size_t)pos * (ATT_D / 2);
     __half* kc = P.k_cache + (size_t)kvh * P.max_seq * ATT_D;
     __half* vc = P.v_cache + (size_t)kvh * P.max_seq * ATT_D;
+    // my first chunk: the smallest c >= first_chunk with c % CL == crank
+    int c0 = first_chunk + ((crank - first_chunk) % ATT_CLUSTER + ATT_CLUSTER) % ATT_CLUSTER;
+    const bool active = c0 < nchunk;
 
-    // ---- prologue: q heads of this group (normalised, rotated, pre-scaled); new K/V into the cache
-    if (warp < G) norm_rope_head(P.q + (size_t)(kvh * G + warp) * ATT_D, P.q_norm, P.eps, cs, sn, P.neox, P.scale, qs[warp], lane);
-    const bool owns_new = (pos >= base && pos < base + ATT_CHUNK);
+    // ---- prologue: q heads of this group (normalised, rotated, pre-scaled by 1/sqrt(d) * log2(e));
+    //      the CTA whose chunk holds `pos` normalises/rotates the new K and writes K,V into the cache
+    const bool owns_new = active && ((pos / ATT_CHUNK) % ATT_CLUSTER == crank);
+    if (active && warp < G)
+        norm_rope_head(P.q + (size_t)(kvh * G + warp) * ATT_D, P.q_norm, P.eps, cs, sn, P.neox, P.scale * 1.4426950408889634f,
+                       sh.qs[warp], lane);
     if (owns_new && warp == ATT_THREADS / 32 - 1) {
-        norm_rope_head(P.k + (size_t)kvh * ATT_D, P.k_norm, P.eps, cs, sn, P.neox, 1.0f, kn, lane);
+        norm_rope_head(P.k + (size_t)kvh * ATT_D, P.k_norm, P.eps, cs, sn, P.neox, 1.0f, sh.kn, lane);
         __syncwarp();
         for (int i = lane; i < ATT_D; i += 32) {
-            kc[(size_t)pos * ATT_D + i] = __float2half_rn(kn[i]);
+            kc[(size_t)pos * ATT_D + i] = __float2half_rn(sh.kn[i]);
             vc[(size_t)pos * ATT_D + i] = __float2half_rn(P.v[(size_t)kvh * ATT_D + i]);
         }
     }
+    if (tid < ATT_MAX_GROUP) { sh.M[tid] = -INFINITY; sh.L[tid] = 0.f; }
     __syncthreads();
+    stamp(2);
 
-    // ---- scores: two threads per cache position, 64 dims each
-    {
-        const int tl = tid >> 1, hf = tid & 1;
-        const int t = base + tl;
-        float s[ATT_MAX_GROUP];
+    const int rg = tid >> 4, dc = tid & 15;          // P@V mapping: 16 row-groups x 16 column-threads (8 dims each)
+    float acc[G][8];
 #pragma unroll
-        for (int g = 0; g < ATT_MAX_GROUP; ++g) s[g] = 0.f;
-        if (t >= t0 && t < t1) {
-            const uint4* kp = reinterpret_cast<const uint4*>(kc + (size_t)t * ATT_D + hf * 64);
+    for (int g = 0; g < G; ++g)
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const uint4 raw = kp[i];
-                const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
-                float kf[8];
+        for (int k = 0; k < 8; ++k) acc[g][k] = 0.f;
+    float run_m[G];                      // running max per head (same value in every thread)
 #pragma unroll
-                for (int k = 0; k < 4; ++k) { const float2 f = __half22float2(h2[k]); kf[2 * k] = f.x; kf[2 * k + 1] = f.y; }
+    for (int g = 0; g < G; ++g) run_m[g] = -INFINITY;
+
+    for (int c = c0; c < nchunk; c += ATT_CLUSTER) {
+        const int base = c * ATT_CHUNK;
+        const int t0 = max(base, lo), t1 = min(base + ATT_CHUNK, T);
+        // ---- scores: two threads per cache position, 64 dims each; all loads issued before any math
+        {
+            const int tl = tid >> 1, hf = tid & 1;
+            const int t = base + tl;
+            const bool valid = t >= t0 && t < t1;
+            uint4 raw[8];
+            if (valid) {
+                const uint4* kp = reinterpret_cast<const uint4*>(kc + (size_t)t * ATT_D + hf * 64);
 #pragma unroll
-                for (int g = 0; g < ATT_MAX_GROUP; ++g) {
-                    if (g < G) {
-                        const float* qp = &qs[g][hf * 64 + i * 8];
+                for (int i = 0; i < 8; ++i) raw[i] = kp[i];
+            }
+            float s[G];
 #pragma unroll
-                        for (int k = 0; k < 8; ++k) s[g] += kf[k] * qp[k];
+            for (int g = 0; g < G; ++g) s[g] = 0.f;
+            if (valid) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const __half2* h2 = reinterpret_cast<const __half2*>(&raw[i]);
+                    float kf[8];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) { const float2 f = __half22float2(h2[k]); kf[2 * k] = f.x; kf[2 * k + 1] = f.y; }
+#pragma unroll
+                    for (int g = 0; g < G; ++g) {
+                        {
+                            const float4 qa = *reinterpret_cast<const float4*>(&sh.qs[g][hf * 64 + i * 8]);
+                            const float4 qb = *reinterpret_cast<const float4*>(&sh.qs[g][hf * 64 + i * 8 + 4]);
+                            s[g] += kf[0] * qa.x + kf[1] * qa.y + kf[2] * qa.z + kf[3] * qa.w + kf[4] * qb.x + kf[5] * qb.y +
+                                    kf[6] * qb.z + kf[7] * qb.w;
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                {
+                    const float tot = s[g] + __shfl_xor_sync(0xffffffffu, s[g], 1);
+                    if (hf == 0) sh.sc[g][tl] = valid ? tot : -INFINITY;
+                }
+            }
+        }
+        // V for this chunk: issue the loads now, they land while the softmax statistics are computed
+        uint4 vraw[ATT_CHUNK / 16];
+#pragma unroll
+        for (int i = 0; i < ATT_CHUNK / 16; ++i) {
+            const int t = base + rg + 16 * i;
+            vraw[i] = (t >= t0 && t < t1) ? *reinterpret_cast<const uint4*>(vc + (size_t)t * ATT_D + dc * 8) : make_uint4(0, 0, 0, 0);
+        }
+        __syncthreads();
+        // ---- softmax statistics of this chunk (base 2): warp g handles head g
+        if (warp < G) {
+            float m = -INFINITY;
+            for (int i = lane; i < ATT_CHUNK; i += 32) m = fmaxf(m, sh.sc[warp][i]);
+            m = warp_max(m);
+            float l = 0.f;
+            for (int i = lane; i < ATT_CHUNK; i += 32) {
+                const float p = exp2f(sh.sc[warp][i] - m);
+                sh.sc[warp][i] = p;
+                l += p;
+            }
+            l = warp_sum(l);
+            if (lane == 0) { sh.hm[warp] = m; sh.hl[warp] = l; }
+        }
+        __syncthreads();
+        // ---- merge the chunk into the running state and accumulate P @ V
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            {
+                const float mc = sh.hm[g];
+                const float mn = fmaxf(run_m[g], mc);
+                const float so = exp2f(run_m[g] - mn), sc_ = exp2f(mc - mn);    // exp2f(-inf) = 0 on the first chunk
+                run_m[g] = mn;
+                if (tid == g) { sh.L[g] = sh.L[g] * so + sh.hl[g] * sc_; sh.M[g] = mn; }
+#pragma unroll
+                for (int k = 0; k < 8; ++k) acc[g][k] *= so;
+#pragma unroll
+                for (int i = 0; i < ATT_CHUNK / 16; ++i) {
+                    const float p = sh.sc[g][rg + 16 * i] * sc_;
+                    const __half2* h2 = reinterpret_cast<const __half2*>(&vraw[i]);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const float2 f = __half22float2(h2[k]);
+                        acc[g][2 * k] += p * f.x;
+                        acc[g][2 * k + 1] += p * f.y;
                     }
                 }
             }
         }
-#pragma unroll
-        for (int g = 0; g < ATT_MAX_GROUP; ++g) {
-            if (g < G) {
-                const float tot = s[g] + __shfl_xor_sync(0xffffffffu, s[g], 1);
-                if (hf == 0) sc[g][tl] = (t >= t0 && t < t1) ? tot : -INFINITY;
-            }
-        }
+        __syncthreads();       // sc/hm/hl are rewritten by the next chunk
     }
-    __syncthreads();
-    // ---- softmax statistics of this split: warp g handles head g
-    if (warp < G) {
-        float m = -INFINITY;
-        for (int i = lane; i < ATT_CHUNK; i += 32) m = fmaxf(m, sc[warp][i]);
-        m = warp_max(m);
-        float l = 0.f;
-        for (int i = lane; i < ATT_CHUNK; i += 32) {
-            const float p = __expf(sc[warp][i] - m);
-            sc[warp][i] = p;
-            l += p;
-        }
-        l = warp_sum(l);
-        if (lane == 0) { hm[warp] = m; hl[warp] = l; }
-    }
-    __syncthreads();
-    // ---- P @ V: 16 row-groups x 16 column-threads (8 dims each)
-    {
-        const int rg = tid >> 4, dc = tid & 15;
-        float acc[ATT_MAX_GROUP][8];
+    stamp(3);
+    // ---- combine the 16 row-groups: lanes l and l+16 first, then the 8 warps through shared memory
+    if (active) {
 #pragma unroll
-        for (int g = 0; g < ATT_MAX_GROUP; ++g)
-#pragma unroll
-            for (int k = 0; k < 8; ++k) acc[g][k] = 0.f;
-        for (int tl = rg; tl < ATT_CHUNK; tl += 16) {
-            const int t = base + tl;
-            if (t < t0 || t >= t1) continue;
-            const uint4 raw = *reinterpret_cast<const uint4*>(vc + (size_t)t * ATT_D + dc * 8);
-            const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
-            float vf[8];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) { const float2 f = __half22float2(h2[k]); vf[2 * k] = f.x; vf[2 * k + 1] = f.y; }
-#pragma unroll
-            for (int g = 0; g < ATT_MAX_GROUP; ++g) {
-                if (g < G) {
-                    const float p = sc[g][tl];
-#pragma unroll
-                    for (int k = 0; k < 8; ++k) acc[g][k] += p * vf[k];
-                }
-            }
-        }
-        // lanes l and l+16 hold different row-groups of the same columns
-#pragma unroll
-        for (int g = 0; g < ATT_MAX_GROUP; ++g)
+        for (int g = 0; g < G; ++g)
 #pragma unroll
             for (int k = 0; k < 8; ++k) acc[g][k] += __shfl_xor_sync(0xffffffffu, acc[g][k], 16);
         if (lane < 16) {
 #pragma unroll
-            for (int g = 0; g < ATT_MAX_GROUP; ++g)
-                if (g < G) {
+            for (int g = 0; g < G; ++g)
+                {
 #pragma unroll
-                    for (int k = 0; k < 8; ++k) red[warp][g][dc * 8 + k] = acc[g][k];
+                    for (int k = 0; k < 8; ++k) sh.red[warp][g][dc * 8 + k] = acc[g][k];
                 }
         }
-    }
-    __syncthreads();
-    // ---- combine the 8 warps; write either the final output (single split) or a partial
-    for (int i = tid; i < G * ATT_D; i += ATT_THREADS) {
-        const int g = i / ATT_D, d = i - g * ATT_D;
-        float o = 0.f;
+        __syncthreads();
+        for (int i = tid; i < G * ATT_D; i += ATT_THREADS) {
+            const int g = i / ATT_D, d = i - g * ATT_D;
+            float o = 0.f;
 #pragma unroll
-        for (int w = 0; w < ATT_THREADS / 32; ++w) o += red[w][g][d];
-        if (nactive == 1) {
-            P.out[(size_t)(kvh * G + g) * ATT_D + d] = o / hl[g];
-        } else {
-            P.part_o[(((size_t)kvh * P.max_splits + split) * G + g) * ATT_D + d] = o;
+            for (int w = 0; w < ATT_THREADS / 32; ++w) o += sh.red[w][g][d];
+            sh.O[g][d] = o;
         }
     }
-    if (nactive == 1) return;
-    if (tid < G) {
-        float* ml = P.part_ml + (((size_t)kvh * P.max_splits + split) * G + tid) * 2;
-        ml[0] = hm[tid];
-        ml[1] = hl[tid];
-    }
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-        const unsigned t = atomicAdd(P.ticket + kvh, 1u);
-        last = (t == (unsigned)nactive - 1);
-    }
-    __syncthreads();
-    if (!last) return;
-    __threadfence();
-    for (int i = tid; i < G * ATT_D; i += ATT_THREADS) {
-        const int g = i / ATT_D, d = i - g * ATT_D;
-        float M = -INFINITY;
-        for (int s = first_split; s < nsplit; ++s)
-            M = fmaxf(M, __ldcg(P.part_ml + (((size_t)kvh * P.max_splits + s) * G + g) * 2));
-        float L = 0.f, O = 0.f;
-        for (int s = first_split; s < nsplit; ++s) {
-            const size_t ix = ((size_t)kvh * P.max_splits + s) * G + g;
-            const float w = __expf(__ldcg(P.part_ml + ix * 2) - M);
-            L += w * __ldcg(P.part_ml + ix * 2 + 1);
-            O += w * __ldcg(P.part_o + ix * ATT_D + d);
+    cluster.sync();
+    stamp(4);
+    // ---- cluster merge: this CTA finishes G*128/CL outputs from every peer's {M, L, O}
+    {
+        const int per = G * ATT_D / ATT_CLUSTER;
+        if (tid < per) {
+            const int i = crank * per + tid;
+            const int g = i / ATT_D, d = i - g * ATT_D;
+            float Mx = -INFINITY;
+            float pm[ATT_CLUSTER];
+#pragma unroll
+            for (int p = 0; p < ATT_CLUSTER; ++p) {
+                const AttnShared* ps = cluster.map_shared_rank(&sh, p);
+                pm[p] = ps->M[g];
+                Mx = fmaxf(Mx, pm[p]);
+            }
+            float Lt = 0.f, Ot = 0.f;
+#pragma unroll
+            for (int p = 0; p < ATT_CLUSTER; ++p) {
+                if (pm[p] > -INFINITY) {
+                    const AttnShared* ps = cluster.map_shared_rank(&sh, p);
+                    const float w = exp2f(pm[p] - Mx);
+                    Lt += w * ps->L[g];
+                    Ot += w * ps->O[g][d];
+                }
+            }
+            P.out[(size_t)(kvh * G + g) * ATT_D + d] = Ot / Lt;
         }
-        P.out[(size_t)(kvh * G + g) * ATT_D + d] = O / L;
     }
-    if (tid == 0) P.ticket[kvh] = 0u;
+    cluster.sync();      // peers may still be reading this CTA's shared memory
+    stamp(5);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -40,18 +40,30 @@ def split_blocks(nblk: int, world: int, rank: int):
     return b0, b0 + base + (1 if rank < rem else 0)
 
 
-def repack_q6k(raw: torch.Tensor, b0: int = 0, b1: Optional[int] = None) -> torch.Tensor:
-    """GGUF Q6_K rows ``[N, nblk*210]`` -> SoA rows ``ql | qh | scales | d(+pad)``, optionally K-sliced."""
-    n = raw.shape[0]
-    blk = raw.reshape(n, -1, 210)
-    blk = blk[:, b0:b1]
-    nb = blk.shape[1]
+SEG_BLOCKS = 10     # must match GEMV_SEG_BLOCKS in csrc/decode_kernels.cuh
+
+
+def segments(nblk: int):
+    """Block ranges of the K segments: ``ceil(nblk/10)`` segments, the first ``nblk % KS`` one longer."""
+    ks = (nblk + SEG_BLOCKS - 1) // SEG_BLOCKS
+    return [split_blocks(nblk, ks, s) for s in range(ks)]
+
+
+def _q6k_soa(blk: torch.Tensor) -> torch.Tensor:
+    """Q6_K blocks ``[N, nb, 210]`` -> structure of arrays ``[N, nb*208 + pad16(nb*2)]``."""
+    n, nb = blk.shape[0], blk.shape[1]
     parts = [blk[:, :, 0:128].reshape(n, nb * 128), blk[:, :, 128:192].reshape(n, nb * 64),
              blk[:, :, 192:208].reshape(n, nb * 16), blk[:, :, 208:210].reshape(n, nb * 2)]
     pad = (-nb * 2) % 16
     if pad:
-        parts.append(torch.zeros(n, pad, dtype=torch.uint8, device=raw.device))
-    return torch.cat(parts, dim=1).contiguous()
+        parts.append(torch.zeros(n, pad, dtype=torch.uint8, device=blk.device))
+    return torch.cat(parts, dim=1)
+
+
+def repack_q6k(raw: torch.Tensor, b0: int = 0, b1: Optional[int] = None) -> torch.Tensor:
+    """Row-major SoA rows (the embedding-table layout): ``ql | qh | scales | d(+pad)`` per row."""
+    n = raw.shape[0]
+    return _q6k_soa(raw.reshape(n, -1, 210)[:, b0:b1]).contiguous()
 
 
 def slice_q4k(raw: torch.Tensor, b0: int = 0, b1: Optional[int] = None) -> torch.Tensor:
@@ -59,13 +71,25 @@ def slice_q4k(raw: torch.Tensor, b0: int = 0, b1: Optional[int] = None) -> torch
     return raw.reshape(n, -1, 144)[:, b0:b1].reshape(n, -1).contiguous()
 
 
-class PackedWeight:
-    """A quantised matrix in the layout the GEMV kernel streams."""
+def segment_major(raw: torch.Tensor, qtype: GGMLType, b0: int, b1: int) -> torch.Tensor:
+    """The GEMV streaming layout ``[segment][row][segment bytes]`` over blocks ``[b0, b1)`` of every row."""
+    n = raw.shape[0]
+    bb = 144 if qtype == GGMLType.Q4_K else 210
+    blk = raw.reshape(n, -1, bb)[:, b0:b1]
+    out = []
+    for s0, s1 in segments(b1 - b0):
+        seg = blk[:, s0:s1]
+        out.append(seg.reshape(n, -1).reshape(-1) if qtype == GGMLType.Q4_K else _q6k_soa(seg).reshape(-1))
+    return torch.cat(out).contiguous()
 
-    def __init__(self, data: torch.Tensor, qtype: int, rows: int, cols: int, bias: Optional[torch.Tensor] = None):
-        self.data, self.qtype, self.rows, self.cols, self.bias = data, qtype, rows, cols, bias
-        self.rowbytes = data.shape[1]
-        assert self.rowbytes % 16 == 0 and data.data_ptr() % 16 == 0
+
+class PackedWeight:
+    """A quantised matrix in the layout its kernel streams (``rowbytes`` > 0 only for row-major tables)."""
+
+    def __init__(self, data: torch.Tensor, qtype: int, rows: int, cols: int, bias: Optional[torch.Tensor] = None,
+                 rowbytes: int = 0):
+        self.data, self.qtype, self.rows, self.cols, self.bias, self.rowbytes = data, qtype, rows, cols, bias, rowbytes
+        assert data.data_ptr() % 16 == 0
 
     def desc(self) -> N.WeightDesc:
         return N.WeightDesc(self.data.data_ptr(), N.ptr(self.bias), self.qtype, self.rows, self.cols, self.rowbytes)
@@ -75,28 +99,39 @@ class PackedWeight:
         return self.data.numel()
 
 
-def pack_weight(raw: torch.Tensor, qtype: GGMLType, cols: int, device, rows=None, kblocks=None,
-                bias: Optional[torch.Tensor] = None) -> PackedWeight:
-    """``raw``: uint8 ``[N, row_bytes]`` as stored in the file.  ``rows=(r0,r1)`` row-slices,
-    ``kblocks=(b0,b1)`` slices super-blocks along K.  Types other than Q4_K/Q6_K are
-    transcoded to Q6_K blocks (the only lossy step, and only for such files)."""
-    if rows is not None:
-        raw = raw[rows[0]:rows[1]]
-    raw = raw.to(device, non_blocking=True)
+def _to_kernel_type(raw: torch.Tensor, qtype: GGMLType, cols: int):
+    """Types other than Q4_K/Q6_K are transcoded to Q6_K blocks (the only lossy step, and only for such files)."""
     qtype = GGMLType(qtype)
     if qtype not in (GGMLType.Q4_K, GGMLType.Q6_K):
         raw = quantize(dequantize(raw, qtype, cols), GGMLType.Q6_K)
         qtype = GGMLType.Q6_K
+    return raw, qtype
+
+
+def pack_weight(raw: torch.Tensor, qtype: GGMLType, cols: int, device, rows=None, kblocks=None,
+                bias: Optional[torch.Tensor] = None) -> PackedWeight:
+    """``raw``: uint8 ``[N, row_bytes]`` as stored in the file -> GEMV streaming layout on ``device``.
+    ``rows=(r0,r1)`` row-slices, ``kblocks=(b0,b1)`` slices super-blocks along K."""
+    if rows is not None:
+        raw = raw[rows[0]:rows[1]]
+    raw, qtype = _to_kernel_type(raw.to(device, non_blocking=True), qtype, cols)
     b0, b1 = kblocks if kblocks is not None else (0, cols // 256)
-    if qtype == GGMLType.Q4_K:
-        data, qt = slice_q4k(raw, b0, b1), QT_Q4K
-    else:
-        data, qt = repack_q6k(raw, b0, b1), QT_Q6K
+    data = segment_major(raw, qtype, b0, b1)
     if bias is not None:
         bias = bias.to(device).float().contiguous()
         if rows is not None:
             bias = bias[rows[0]:rows[1]].contiguous()
-    return PackedWeight(data, qt, data.shape[0], (b1 - b0) * 256, bias)
+    return PackedWeight(data, QT_Q4K if qtype == GGMLType.Q4_K else QT_Q6K, raw.shape[0], (b1 - b0) * 256, bias)
+
+
+def pack_table(raw: torch.Tensor, qtype: GGMLType, cols: int, device) -> PackedWeight:
+    """Row-major layout for row lookups (the embedding table)."""
+    raw, qtype = _to_kernel_type(raw.to(device, non_blocking=True), qtype, cols)
+    if qtype == GGMLType.Q4_K:
+        data, qt = raw.contiguous(), QT_Q4K
+    else:
+        data, qt = repack_q6k(raw), QT_Q6K
+    return PackedWeight(data, qt, data.shape[0], cols, None, rowbytes=data.shape[1])
 
 
 class GGUFModel:
@@ -110,6 +145,8 @@ class GGUFModel:
         self.device = torch.device(device if device is not None else "cuda")
         if self.device.type != "cuda":
             raise RuntimeError("GGUFModel runs on a CUDA device; use models.gguf_oracle.OracleModel on the CPU")
+        if self.device.index is None:
+            self.device = torch.device("cuda", torch.cuda.current_device())
         self.max_seq = int(min(max_seq, self.cfg.context_length))
         self.tp_rank, self.tp_world = tp_rank, tp_world
         self.symm = symm
@@ -192,11 +229,13 @@ class GGUFModel:
             dsc.sin = (self.sin_swa if use_swa_tab else self.sin).data_ptr()
             dsc.window = cfg.swa_window if swa else 0
         self._layer_descs = descs
-        self.embed = mat("token_embd.weight")
+        te = r.tensors["token_embd.weight"]
+        self.embed = pack_table(r.raw("token_embd.weight"), te.qtype, te.shape[-1], dev)
+        self.table_bytes = self.embed.nbytes
         head_name = "output.weight" if r.has_tensor("output.weight") else "token_embd.weight"
         V = cfg.vocab_size
         v0, v1 = (V * rk) // W, (V * (rk + 1)) // W
-        self.lm_head = mat(head_name, rows=(v0, v1)) if (W > 1 or head_name != "token_embd.weight") else self.embed
+        self.lm_head = mat(head_name, rows=(v0, v1))
         self.vocab_offset = v0
         self.out_norm = vec("output_norm.weight")
 
