@@ -40,8 +40,8 @@ class ModelDesc(C.Structure):
                 ("neox", C.c_int), ("act_gelu", C.c_int), ("norm_add_one", C.c_int), ("want_logits", C.c_int),
                 ("embed", WeightDesc), ("lm_head", WeightDesc), ("out_norm", C.c_void_p),
                 ("tp_rank", C.c_int), ("tp_world", C.c_int), ("vocab_offset", C.c_int), ("pad", C.c_int),
-                ("peer_inbox", (C.c_void_p * MAX_PEERS) * 3), ("peer_flag", (C.c_void_p * MAX_PEERS) * 3),
-                ("slot_floats", C.c_int), ("pad2", C.c_int)]
+                ("peer_inbox", (C.c_void_p * MAX_PEERS) * 3),
+                ("slot_elems", C.c_int), ("pad2", C.c_int)]
 
 
 def lib_path() -> Path:

@@ -131,6 +131,35 @@ __device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t want, i
     return false;
 }
 
+// ---- "data + sequence number" slots (8 bytes, written and read as one access): a reader that sees
+// the expected sequence number also sees the payload, so no fence and no separate flag is needed.
+__device__ __forceinline__ void st_ll(uint2* p, uint32_t data, uint32_t seq) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(data), "r"(seq) : "memory");
+}
+__device__ __forceinline__ uint2 ld_ll(const uint2* p) {
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
+// Poll a slot until it carries `seq`; bounded by a nanosecond budget.  Returns the payload (0 on timeout).
+__device__ __forceinline__ uint32_t wait_ll(const uint2* p, uint32_t seq, int* status, uint64_t budget_ns = 1000000000ull) {
+    uint2 v = ld_ll(p);
+    if (v.y == seq) return v.x;
+    uint64_t t0;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    for (uint32_t i = 0;; ++i) {
+        v = ld_ll(p);
+        if (v.y == seq) return v.x;
+        if ((i & 63u) == 63u) {
+            uint64_t t1;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+            if (t1 - t0 > budget_ns) break;
+        }
+    }
+    if (status) atomicExch(status, PTB_ERR_FLAG_TIMEOUT);
+    return 0u;
+}
+
 __device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
 __device__ __forceinline__ float gelu_tanh(float x) {
     const float k = 0.7978845608028654f;

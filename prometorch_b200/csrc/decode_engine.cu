@@ -52,8 +52,7 @@ struct PtbModelDesc {
     const float* out_norm;
     int tp_rank, tp_world, vocab_offset, pad;
     void* peer_inbox[3][MAX_PEERS];     // three receive buffers (attention out, FFN down, lm_head pair)
-    void* peer_flag[3][MAX_PEERS];
-    int slot_floats, pad2;
+    int slot_elems, pad2;
 };
 
 static size_t g_gemv_max_dyn = 200 * 1024;
@@ -352,11 +351,8 @@ static void fill_peers(const Engine* e, GemvParams& p, int which, int call_idx, 
     const PtbModelDesc& m = e->m;
     p.peers.rank = m.tp_rank;
     p.peers.world = m.tp_world;
-    p.peers.slot_floats = m.slot_floats;
-    for (int r = 0; r < m.tp_world; ++r) {
-        p.peers.inbox[r] = (float*)m.peer_inbox[which][r];
-        p.peers.flag[r] = (uint32_t*)m.peer_flag[which][r];
-    }
+    p.peers.slot_elems = m.slot_elems;
+    for (int r = 0; r < m.tp_world; ++r) p.peers.inbox[r] = (uint2*)m.peer_inbox[which][r];
     p.gen = (const uint32_t*)(e->ctrl + CTRL_GEN);
     p.peers.seq_mul = (uint32_t)calls_per_token;
     p.peers.seq_add = (uint32_t)call_idx;

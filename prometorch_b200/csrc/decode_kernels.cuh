@@ -49,12 +49,11 @@ struct GemvJob {
     int cta_begin, cta_count;
 };
 
-struct PeerInfo {           // tensor-parallel all-reduce wiring (EPI_ALLREDUCE)
-    float* inbox[MAX_PEERS];        // inbox[p]: peer p's receive buffer [world][slot_floats]; inbox[rank] is local
-    uint32_t* flag[MAX_PEERS];      // flag[p]: peer p's arrival counters [world]
-    int rank, world;
-    int slot_floats;
-    uint32_t seq_mul, seq_add;      // arrival number of this call = generation * seq_mul + seq_add
+struct PeerInfo {           // tensor-parallel all-reduce wiring (EPI_ALLREDUCE, row-split arg-max)
+    uint2* inbox[MAX_PEERS];        // inbox[p]: rank p's receive buffer [world][slot_elems] of {payload, sequence}
+    int rank, world;                //           slots; inbox[rank] is this GPU's own buffer
+    int slot_elems;
+    uint32_t seq_mul, seq_add;      // sequence number of this call = generation * seq_mul + seq_add (never 0)
 };
 
 struct GemvParams {
@@ -359,6 +358,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32, 2) gemv_kernel(const __grid_c
     int best_i = 0x7fffffff;
     bool ok = true;
 
+    const uint32_t seq = (P.peers.world > 1) ? (*P.gen * P.peers.seq_mul + P.peers.seq_add) : 0u;
     auto epilogue = [&](int n, float v0, float v1) {
         if (J.bias) v0 += J.bias[n];
         switch (P.epilogue) {
@@ -370,9 +370,9 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32, 2) gemv_kernel(const __grid_c
                 if (v0 > best_v || (v0 == best_v && n < best_i)) { best_v = v0; best_i = n; }
                 break;
             case EPI_ALLREDUCE: {
-                // push my partial sum for element n to every rank's inbox slot [rank]
+                // push {partial sum, sequence number} for element n into slot [rank][n] of every rank's inbox
                 const PeerInfo& pi = P.peers;
-                for (int p = 0; p < pi.world; ++p) pi.inbox[p][(size_t)pi.rank * pi.slot_floats + n] = v0;
+                for (int p = 0; p < pi.world; ++p) st_ll(pi.inbox[p] + (size_t)pi.rank * pi.slot_elems + n, __float_as_uint(v0), seq);
             } break;
         }
     };
@@ -487,23 +487,19 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32, 2) gemv_kernel(const __grid_c
                 bi += P.row_offset;
                 const PeerInfo& pi = P.peers;
                 if (pi.world > 1) {
-                    // every rank holds a slice of the vocabulary: exchange {value, id} pairs and
-                    // let each rank pick the same winner
-                    const uint32_t g = *P.gen * pi.seq_mul + pi.seq_add;
+                    // every rank holds a slice of the vocabulary: exchange {value, id} and let each rank
+                    // pick the same winner
                     for (int p = 0; p < pi.world; ++p) {
-                        float* slot = pi.inbox[p] + (size_t)pi.rank * pi.slot_floats;
-                        slot[0] = bv;
-                        slot[1] = __int_as_float(bi);
+                        uint2* slot = pi.inbox[p] + (size_t)pi.rank * pi.slot_elems;
+                        st_ll(slot, __float_as_uint(bv), seq);
+                        st_ll(slot + 1, (uint32_t)bi, seq);
                     }
-                    __threadfence_system();
-                    for (int p = 0; p < pi.world; ++p) st_release_sys(pi.flag[p] + pi.rank, g);
-                    for (int p = 0; p < pi.world; ++p) wait_flag_ge(pi.flag[pi.rank] + p, g, P.status);
                     bv = -INFINITY;
                     bi = 0x7fffffff;
                     for (int p = 0; p < pi.world; ++p) {
-                        const float* slot = pi.inbox[pi.rank] + (size_t)p * pi.slot_floats;
-                        const float v = __ldcg(slot);
-                        const int ix = __float_as_int(__ldcg(slot + 1));
+                        const uint2* slot = pi.inbox[pi.rank] + (size_t)p * pi.slot_elems;
+                        const float v = __uint_as_float(wait_ll(slot, seq, P.status));
+                        const int ix = (int)wait_ll(slot + 1, seq, P.status);
                         if (v > bv || (v == bv && ix < bi)) { bv = v; bi = ix; }
                     }
                 }
@@ -526,37 +522,17 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32, 2) gemv_kernel(const __grid_c
     }
 
     if (P.epilogue == EPI_ALLREDUCE) {
-        // All CTAs have pushed their slices; the last CTA of this rank publishes the
-        // arrival flag to every peer, waits for all peers, reduces the `world` partial
-        // vectors of its inbox in rank order (bitwise identical on every rank) and adds
-        // the residual.
+        // Every CTA reduces its own slice of the output: poll the `world` slots of each element (they are
+        // filled by CTAs of this kernel on every rank), sum in rank order so that all ranks get bitwise the
+        // same vector, add the residual.  No fence, ticket or flag: the sequence number travels with the data.
         const PeerInfo& pi = P.peers;
-        __shared__ bool last;
-        __syncthreads();
-        if (tid == 0) {
-            __threadfence_system();
-            const unsigned t = atomicAdd(P.ticket, 1u);
-            last = (t == gridDim.x - 1);
-            __threadfence();
-        }
-        __syncthreads();
-        if (last) {
-            const uint32_t g = *P.gen * pi.seq_mul + pi.seq_add;
-            if (tid < pi.world) {
-                __threadfence_system();
-                st_release_sys(pi.flag[tid] + pi.rank, g);
-            }
-            __syncthreads();
-            if (tid < pi.world) wait_flag_ge(pi.flag[pi.rank] + tid, g, P.status);
-            __syncthreads();
-            const float* in = pi.inbox[pi.rank];
-            const int N = J.N;
-            for (int n = tid; n < N; n += GEMV_THREADS) {
-                float v = P.resid ? P.resid[n] : 0.f;
-                for (int p = 0; p < pi.world; ++p) v += __ldcg(in + (size_t)p * pi.slot_floats + n);
-                J.out[n] = v;
-            }
-            if (tid == 0) *P.ticket = 0u;
+        const int N = J.N;
+        const int n0 = (int)(((long long)N * blockIdx.x) / gridDim.x), n1 = (int)(((long long)N * (blockIdx.x + 1)) / gridDim.x);
+        for (int n = n0 + tid; n < n1; n += GEMV_THREADS) {
+            float v = P.resid ? P.resid[n] : 0.f;
+            for (int p = 0; p < pi.world; ++p)
+                v += __uint_as_float(wait_ll(pi.inbox[pi.rank] + (size_t)p * pi.slot_elems + n, seq, P.status));
+            J.out[n] = v;
         }
     }
 }

@@ -252,13 +252,12 @@ class GGUFModel:
             if self.symm is None:
                 raise ValueError("tensor parallel decode needs a symmetric-memory group (parallel.symm.SymmGroup)")
             slot = max(cfg.hidden_size, 64)
-            self._tp_bufs = [self.symm.alloc(W * slot * 4) for _ in range(3)]
-            self._tp_flags = [self.symm.alloc(W * 4) for _ in range(3)]
+            # three inboxes of {payload, sequence} slots: attention output, FFN down, lm_head arg-max
+            self._tp_bufs = [self.symm.alloc(W * slot * 8) for _ in range(3)]
             for b in range(3):
                 for p in range(W):
                     m.peer_inbox[b][p] = self._tp_bufs[b].peer_ptr(p)
-                    m.peer_flag[b][p] = self._tp_flags[b].peer_ptr(p)
-            m.slot_floats = slot
+            m.slot_elems = slot
             self.symm.barrier()
         self._model_desc = m
         torch.cuda.synchronize(dev)
