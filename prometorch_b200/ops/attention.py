@@ -1,0 +1,90 @@
+"""Attention front end: ``flash_attention(q, k, v, causal)`` on ``[B, T, heads, D]`` tensors with
+grouped-query heads (``heads_q`` a multiple of ``heads_kv``).
+
+CUDA bf16 inputs with D in {64, 128} run the hand-written FlashAttention kernels
+(csrc/flash_attn.cu: tiled online-softmax forward that also returns the log-sum-exp, and a
+recompute-based backward with the GQA reduction of dK/dV done inside the kernel).  ``q_offset`` /
+``return_lse`` are the hooks a ring/context-parallel wrapper needs: blocks of K/V can be processed
+separately and merged by log-sum-exp.  CPU tensors use the plain softmax formulation.  The layout
+matches the reference's kernel, which also takes ``[B, N, H, D]`` (aten/src/ATen/native/Attention.h:244-250)."""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Optional
+
+import torch
+
+from .. import _native as N
+
+
+@N.register_decls
+def _decls(L):
+    vp, ci, cf = C.c_void_p, C.c_int, C.c_float
+    if hasattr(L, "ptb_flash_attn_fwd"):
+        L.ptb_flash_attn_fwd.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, cf, ci, vp]
+        L.ptb_flash_attn_fwd.restype = ci
+        L.ptb_flash_attn_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, cf, ci, vp]
+        L.ptb_flash_attn_bwd.restype = ci
+
+
+def attention_reference(q, k, v, causal=True, q_offset: int = 0, scale: Optional[float] = None):
+    """Plain softmax attention in fp32 (oracle and CPU path).  Returns ``(out, lse)``."""
+    B, Tq, H, D = q.shape
+    Tk, Hk = k.shape[1], k.shape[2]
+    g = H // Hk
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    qf = q.float().permute(0, 2, 1, 3)
+    kf = k.float().permute(0, 2, 1, 3).repeat_interleave(g, dim=1)
+    vf = v.float().permute(0, 2, 1, 3).repeat_interleave(g, dim=1)
+    s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+    if causal:
+        qi = torch.arange(Tq, device=q.device)[:, None] + q_offset
+        ki = torch.arange(Tk, device=q.device)[None, :]
+        s = s.masked_fill(ki > qi, float("-inf"))
+    lse = torch.logsumexp(s, dim=-1)
+    o = torch.matmul(torch.softmax(s, dim=-1), vf)
+    return o.permute(0, 2, 1, 3).to(q.dtype), lse
+
+
+class _Flash(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, causal, q_offset, scale):
+        B, Tq, H, D = q.shape
+        Tk, Hk = k.shape[1], k.shape[2]
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        o = torch.empty_like(q)
+        lse = torch.empty(B, H, Tq, dtype=torch.float32, device=q.device)
+        st = torch.cuda.current_stream(q.device).cuda_stream
+        N.check(N.lib().ptb_flash_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), B, Tq, Tk, H, Hk,
+                                           D, int(causal), scale, q_offset, st), "flash_attn_fwd")
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.causal, ctx.q_offset, ctx.scale = causal, q_offset, scale
+        ctx.mark_non_differentiable(lse)
+        return o, lse
+
+    @staticmethod
+    def backward(ctx, do, _dlse):
+        q, k, v, o, lse = ctx.saved_tensors
+        B, Tq, H, D = q.shape
+        Tk, Hk = k.shape[1], k.shape[2]
+        do = do.contiguous()
+        dq32 = torch.zeros(B, Tq, H, D, dtype=torch.float32, device=q.device)
+        dk, dv = torch.empty_like(k), torch.empty_like(v)
+        delta = torch.empty(B, H, Tq, dtype=torch.float32, device=q.device)
+        st = torch.cuda.current_stream(q.device).cuda_stream
+        N.check(N.lib().ptb_flash_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
+                                           delta.data_ptr(), dq32.data_ptr(), dk.data_ptr(), dv.data_ptr(), 0, B, Tq, Tk, H, Hk, D,
+                                           int(ctx.causal), ctx.scale, ctx.q_offset, st), "flash_attn_bwd")
+        return dq32.to(q.dtype), dk, dv, None, None, None
+
+
+def flash_attention(q, k, v, causal: bool = True, q_offset: int = 0, scale: Optional[float] = None, return_lse: bool = False):
+    D = q.shape[-1]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if q.is_cuda and q.dtype == torch.bfloat16 and D in (64, 128) and q.shape[2] % k.shape[2] == 0 and \
+            hasattr(N.lib(), "ptb_flash_attn_fwd"):
+        o, lse = _Flash.apply(q, k, v, causal, q_offset, scale)
+    else:
+        o, lse = attention_reference(q, k, v, causal, q_offset, scale)
+    return (o, lse) if return_lse else o

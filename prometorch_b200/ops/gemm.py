@@ -1,0 +1,107 @@
+"""bf16 GEMM on tcgen05 tensor cores (csrc/gemm_sm100.cuh) and the linear layer built on it.
+
+``gemm_bf16`` exposes the kernel's operand majors directly; ``linear`` is the autograd function
+``y = x W^T + b`` whose backward runs the other two products on the same kernel without materialising
+a transpose: ``dX = dY W`` reads ``W`` as an N-major operand and ``dW = dY^T X`` reads both operands
+M/N-major.  The reference's linear layers go through fp32 cublasSgemm
+(torch/csrc/autograd/autograd.h:931-940, aten/src/ATen/cuda/CUDABlas.cu:455-479)."""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from .. import _native as N
+
+EPI_BIAS, EPI_ACCUM, EPI_OUT_F32, EPI_GELU = 1, 2, 4, 8
+
+
+@N.register_decls
+def _decls(L):
+    vp, ci, ll = C.c_void_p, C.c_int, C.c_longlong
+    L.ptb_gemm_bf16.argtypes = [vp, ll, ci, vp, ll, ci, vp, ll, ci, ci, ci, vp, ci, vp, ci, vp]
+    L.ptb_gemm_bf16.restype = ci
+
+
+_STATUS = {}
+
+
+def _status(dev):
+    if dev not in _STATUS:
+        _STATUS[dev] = torch.zeros(1, dtype=torch.int32, device=dev)
+    return _STATUS[dev]
+
+
+def check_status(dev=None):
+    """Raise if any GEMM launched on ``dev`` reported a timed-out wait."""
+    for d, s in _STATUS.items():
+        if dev is None or d == dev:
+            if int(s) != 0:
+                s.zero_()
+                raise N.NativeError("tcgen05 GEMM: a pipeline wait timed out (status %d)" % int(s))
+
+
+def _rowmajor(t):
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise ValueError("operand must be a 2-D tensor with a contiguous last dimension")
+    return t
+
+
+def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, out: Optional[torch.Tensor] = None,
+              bias: Optional[torch.Tensor] = None, accumulate: bool = False, out_dtype=torch.bfloat16, gelu: bool = False):
+    """``C[M,N] (+)= A B^T``.  ``a``: ``[M,K]`` (or ``[K,M]`` with ``a_mn``); ``b``: ``[N,K]`` (or ``[K,N]`` with ``b_mn``)."""
+    a, b = _rowmajor(a), _rowmajor(b)
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16 or not a.is_cuda:
+        raise TypeError("gemm_bf16 takes CUDA bf16 operands")
+    M, K = (a.shape[1], a.shape[0]) if a_mn else a.shape
+    Nn, Kb = (b.shape[1], b.shape[0]) if b_mn else b.shape
+    if K != Kb:
+        raise ValueError(f"inner dimensions differ: {K} vs {Kb}")
+    if out is None:
+        if accumulate:
+            raise ValueError("accumulate needs an output tensor")
+        out = torch.empty(M, Nn, dtype=out_dtype, device=a.device)
+    flags = (EPI_BIAS if bias is not None else 0) | (EPI_ACCUM if accumulate else 0) | \
+        (EPI_OUT_F32 if out.dtype == torch.float32 else 0) | (EPI_GELU if gelu else 0)
+    if bias is not None:
+        bias = bias.float().contiguous()
+    st = torch.cuda.current_stream(a.device).cuda_stream
+    N.check(N.lib().ptb_gemm_bf16(a.data_ptr(), a.stride(0), int(a_mn), b.data_ptr(), b.stride(0), int(b_mn), out.data_ptr(),
+                                  out.stride(0), M, Nn, K, N.ptr(bias), flags, _status(a.device).data_ptr(), 0, st), "gemm_bf16")
+    return out
+
+
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, bias):
+        x2 = x.reshape(-1, x.shape[-1])
+        if x2.stride(1) != 1:
+            x2 = x2.contiguous()
+        y = gemm_bf16(x2, w, bias=bias)
+        ctx.save_for_backward(x2, w)
+        ctx.has_bias = bias is not None
+        ctx.xshape = x.shape
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if dy2.stride(1) != 1:
+            dy2 = dy2.contiguous()
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm_bf16(dy2, w, b_mn=True).view(ctx.xshape)          # dX[M,in] = dY[M,out] W[out,in]
+        if ctx.needs_input_grad[1]:
+            dw = gemm_bf16(dy2, x2, a_mn=True, b_mn=True)                 # dW[out,in] = dY^T X
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2.float().sum(0).to(dy.dtype)
+        return dx, dw, db
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x W^T + b``.  CUDA bf16 runs on the tcgen05 kernel; other inputs use ``torch.nn.functional.linear``."""
+    if x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 and weight.shape[0] % 8 == 0:
+        return _Linear.apply(x, weight, bias)
+    return torch.nn.functional.linear(x, weight, bias)

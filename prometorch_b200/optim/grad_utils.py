@@ -16,10 +16,28 @@ from .. import _native as N
 from .optimizers import TensorTable
 
 
+class _G:
+    """A (tensor, gradient) pair for gradients that do not live in ``.grad`` (bf16 buckets)."""
+
+    def __init__(self, grad):
+        self.grad = grad
+
+    def numel(self):
+        return self.grad.numel()
+
+    def data_ptr(self):
+        return self.grad.data_ptr()
+
+
 def _grads(params):
     if torch.is_tensor(params):
         params = [params]
     return [p for p in params if p.grad is not None]
+
+
+def grads_as_params(grads):
+    """Wrap bare gradient tensors so the norm/clip helpers accept them."""
+    return [_G(g) for g in grads]
 
 
 class GradNormClipper:
@@ -38,7 +56,7 @@ class GradNormClipper:
         ps = _grads(self.params)
         if not ps:
             return torch.zeros(2)
-        dev = ps[0].device
+        dev = ps[0].grad.device
         lib = N.lib()
         if self.out is None:
             self.out = torch.zeros(2, device=dev)

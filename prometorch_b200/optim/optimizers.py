@@ -94,6 +94,7 @@ class Optimizer(torch.optim.Optimizer):
         self.grad_scale: Optional[torch.Tensor] = None     # device scalar folded into every gradient
         self.skip_flag: Optional[torch.Tensor] = None      # device flag: non-zero => skip the step
         self.lowp_params: Dict[int, torch.Tensor] = {}     # id(param) -> bf16 shadow written by the step
+        self.ext_grads: Dict[int, torch.Tensor] = {}       # id(param) -> gradient held outside ``param.grad``
 
     # -- reference-style flat export: "state.<linear param index>.<key>" (optimizer.h:116-148)
     def flat_state_dict(self) -> Dict[str, torch.Tensor]:
@@ -111,6 +112,19 @@ class Optimizer(torch.optim.Optimizer):
             _, idx, name = key.split(".", 2)
             st = self.state[params[int(idx)]]
             st[name] = v.clone() if name != "step" else torch.as_tensor(float(v))
+
+    def set_grad_source(self, param: torch.Tensor, grad: Optional[torch.Tensor]):
+        """Read this parameter's gradient from ``grad`` instead of ``param.grad``.  PyTorch only lets
+        ``.grad`` hold the parameter's own dtype; fp32 master weights whose gradients arrive in bf16 (a
+        reduce-scattered bucket, a bf16 model replica) register the bf16 tensor here."""
+        if grad is None:
+            self.ext_grads.pop(id(param), None)
+        else:
+            self.ext_grads[id(param)] = grad
+
+    def _grad(self, p):
+        g = self.ext_grads.get(id(p))
+        return g if g is not None else p.grad
 
     def attach_lowp(self, param: torch.Tensor, shadow: torch.Tensor):
         """Have the fused step also write ``shadow`` (bf16, same shape) = the updated fp32 ``param``."""
@@ -134,7 +148,7 @@ class Optimizer(torch.optim.Optimizer):
             with torch.enable_grad():
                 loss = closure()
         for gi, group in enumerate(self.param_groups):
-            ps = [p for p in group["params"] if p.grad is not None]
+            ps = [p for p in group["params"] if self._grad(p) is not None]
             if not ps:
                 continue
             for p in ps:
@@ -148,20 +162,21 @@ class Optimizer(torch.optim.Optimizer):
                 self.state[p]["step"] += 1
             h = self._scalars(group, step)
             use_fused = self.kind is not None and all(
-                p.is_cuda and p.dtype == torch.float32 and p.is_contiguous() and p.grad.is_contiguous()
-                and p.grad.dtype in (torch.float32, torch.bfloat16) for p in ps)
+                p.is_cuda and p.dtype == torch.float32 and p.is_contiguous() and self._grad(p).is_contiguous()
+                and self._grad(p).dtype in (torch.float32, torch.bfloat16) for p in ps)
             if self.fused is False:
                 use_fused = False
             if self.fused is True and not use_fused and ps[0].is_cuda:
                 raise RuntimeError(f"{type(self).__name__}: fused step needs contiguous fp32 CUDA parameters with fp32/bf16 grads")
             if use_fused:
                 for dt in (torch.float32, torch.bfloat16):
-                    sub = [p for p in ps if p.grad.dtype == dt]
+                    sub = [p for p in ps if self._grad(p).dtype == dt]
                     if sub:
                         self._fused_step(gi * 2 + (dt == torch.bfloat16), sub, h, dt == torch.bfloat16)
             else:
                 for p in ps:
-                    g = p.grad.float() if p.grad.dtype != p.dtype else p.grad
+                    g = self._grad(p)
+                    g = g.float() if g.dtype != p.dtype else g
                     if self.grad_scale is not None:
                         g = g * self.grad_scale.to(g.device)
                     if self.skip_flag is not None and int(self.skip_flag) != 0:
@@ -177,7 +192,7 @@ class Optimizer(torch.optim.Optimizer):
         dev = ps[0].device
         tab = self._tables.setdefault(key, TensorTable())
         slots = [tuple(self.state[p].get(n) for n in self.slots) + (None,) * (3 - len(self.slots)) for p in ps]
-        tab.build(ps, [p.grad for p in ps], slots, [self.lowp_params.get(id(p)) for p in ps], dev)
+        tab.build(ps, [self._grad(p) for p in ps], slots, [self.lowp_params.get(id(p)) for p in ps], dev)
         harr = (C.c_float * 16)(*(list(h) + [0.0] * (16 - len(h))))
         st = torch.cuda.current_stream(dev).cuda_stream
         N.check(lib.ptb_multi_tensor_opt(tab.rows.data_ptr(), tab.chunks.data_ptr(), tab.n_chunks, self.kind, int(bf16), harr,

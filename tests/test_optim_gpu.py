@@ -38,7 +38,10 @@ def test_fused_matches_tensor_ops(cls, kw, gdtype):
     for step in range(7 if cls is not O.RAdam else 9):
         for p, q in zip(a, b):
             g = torch.randn(p.shape, generator=gen).to("cuda").to(gdtype)
-            p.grad, q.grad = g.clone(), g.clone()
+            if gdtype == torch.float32:
+                p.grad, q.grad = g.clone(), g.clone()
+            else:       # .grad must have the parameter's dtype: bf16 gradients are registered on the side
+                oa.set_grad_source(p, g.clone()); ob.set_grad_source(q, g.clone())
         oa.step(); ob.step()
     torch.cuda.synchronize()
     for p, q in zip(a, b):
@@ -76,8 +79,12 @@ def test_lowp_shadow_grad_scale_and_skip():
 @pytest.mark.parametrize("gdtype", [torch.float32, torch.bfloat16])
 def test_grad_norm_clip_and_inf(gdtype):
     ps = _params("cuda")
-    for p in ps:
-        p.grad = torch.randn_like(p).to(gdtype)
+    if gdtype == torch.float32:
+        for p in ps:
+            p.grad = torch.randn_like(p)
+    else:
+        from prometorch_b200.optim.grad_utils import grads_as_params
+        ps = grads_as_params([torch.randn_like(p).to(gdtype) for p in ps])
     ref = torch.linalg.vector_norm(torch.cat([p.grad.float().reshape(-1) for p in ps]))
     before = [p.grad.float().clone() for p in ps]
     n = O.clip_grad_norm_(ps, 1.0)

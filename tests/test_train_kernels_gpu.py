@@ -1,0 +1,134 @@
+"""GPU numerics of the training kernels (GEMM, RMSNorm, RoPE, gated activation, cross-entropy) vs PyTorch fp32."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    return float((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-12))
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 512), (300, 200, 136), (4096, 2048, 2048), (64, 96, 1000), (1000, 32000, 512)])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+def test_gemm_bf16(M, N, K, a_mn, b_mn):
+    from prometorch_b200.ops.gemm import check_status, gemm_bf16
+    if (a_mn and M % 8) or (b_mn and N % 8) or K % 8:
+        pytest.skip("pitch must be a multiple of 8 elements")
+    if M * N > 4e6 and (a_mn or b_mn):
+        pytest.skip("large case covered in the K-major layout")
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    A = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    B = torch.randn(N, K, device="cuda", generator=g).bfloat16()
+    a = A.t().contiguous() if a_mn else A
+    b = B.t().contiguous() if b_mn else B
+    ref = A.float() @ B.float().t()
+    out = gemm_bf16(a, b, a_mn=a_mn, b_mn=b_mn)
+    torch.cuda.synchronize()
+    check_status()
+    assert out.shape == (M, N)
+    assert _rel(out, ref) < 5e-3, _rel(out, ref)
+    out32 = gemm_bf16(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32)
+    assert _rel(out32, ref) < 1e-4, _rel(out32, ref)
+
+
+def test_gemm_epilogues():
+    from prometorch_b200.ops.gemm import gemm_bf16
+    A = torch.randn(200, 320, device="cuda").bfloat16()
+    B = torch.randn(264, 320, device="cuda").bfloat16()
+    bias = torch.randn(264, device="cuda")
+    ref = A.float() @ B.float().t()
+    assert _rel(gemm_bf16(A, B, bias=bias, out_dtype=torch.float32), ref + bias) < 1e-4
+    acc = torch.ones(200, 264, device="cuda")
+    gemm_bf16(A, B, out=acc, accumulate=True)
+    assert _rel(acc, ref + 1) < 1e-4
+    assert _rel(gemm_bf16(A, B, gelu=True, out_dtype=torch.float32), F.gelu(ref, approximate="tanh")) < 1e-3
+
+
+def test_linear_autograd():
+    from prometorch_b200.ops.gemm import linear
+    x = torch.randn(4, 96, 256, device="cuda").bfloat16().requires_grad_()
+    w = (torch.randn(512, 256, device="cuda") * 0.05).bfloat16().requires_grad_()
+    b = torch.randn(512, device="cuda").bfloat16().requires_grad_()
+    y = linear(x, w, b)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    xr, wr, br = x.detach().float().requires_grad_(), w.detach().float().requires_grad_(), b.detach().float().requires_grad_()
+    yr = F.linear(xr, wr, br)
+    yr.backward(gy.float())
+    assert _rel(y, yr) < 5e-3 and _rel(x.grad, xr.grad) < 5e-3 and _rel(w.grad, wr.grad) < 5e-3 and _rel(b.grad, br.grad) < 5e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("H", [384, 2048, 2560, 4096])
+def test_rmsnorm(dtype, H):
+    from prometorch_b200.ops.fused_ops import add_rms_norm, rms_norm
+    x = torch.randn(3, 37, H, device="cuda").to(dtype).requires_grad_()
+    w = (1 + 0.1 * torch.randn(H, device="cuda")).to(dtype).requires_grad_()
+    y = rms_norm(x, w, 1e-6)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    yr = xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + 1e-6) * wr
+    yr.backward(gy.float())
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
+    assert _rel(y, yr) < tol and _rel(x.grad, xr.grad) < tol and _rel(w.grad, wr.grad) < tol
+    # fused residual add
+    r = torch.randn_like(x).detach().requires_grad_()
+    x2 = x.detach().clone().requires_grad_()
+    yn, h = add_rms_norm(x2, r, w.detach(), 1e-6)
+    (yn.float().sum() + 2 * h.float().sum()).backward()
+    xr2, rr = x2.detach().float().requires_grad_(), r.detach().float().requires_grad_()
+    hr = xr2 + rr
+    ynr = hr * torch.rsqrt(hr.pow(2).mean(-1, keepdim=True) + 1e-6) * w.detach().float()
+    (ynr.sum() + 2 * hr.sum()).backward()
+    assert _rel(h, hr) < tol and _rel(yn, ynr) < tol and _rel(x2.grad, xr2.grad) < tol and _rel(r.grad, rr.grad) < tol
+
+
+@pytest.mark.parametrize("neox", [True, False])
+def test_rope(neox):
+    from prometorch_b200.io.config import tiny_qwen3_config
+    from prometorch_b200.models.gguf_oracle import apply_rope, rope_tables
+    from prometorch_b200.ops.fused_ops import rope
+    cos, sin = rope_tables(tiny_qwen3_config(), 64, "cuda")
+    x = torch.randn(2, 48, 6, 128, device="cuda").bfloat16().requires_grad_()
+    y = rope(x, cos, sin, neox)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    xr = x.detach().float().requires_grad_()
+    yr = torch.stack([apply_rope(xr[b], cos[:48], sin[:48], neox) for b in range(2)])
+    yr.backward(gy.float())
+    assert _rel(y, yr) < 1e-2 and _rel(x.grad, xr.grad) < 1e-2
+
+
+@pytest.mark.parametrize("gelu", [False, True])
+def test_swiglu(gelu):
+    from prometorch_b200.ops.fused_ops import swiglu
+    gu = torch.randn(5, 33, 2 * 1408, device="cuda").bfloat16().requires_grad_()
+    y = swiglu(gu, gelu)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    r = gu.detach().float().requires_grad_()
+    g, u = r.chunk(2, -1)
+    yr = (F.gelu(g, approximate="tanh") if gelu else F.silu(g)) * u
+    yr.backward(gy.float())
+    assert _rel(y, yr) < 1e-2 and _rel(gu.grad, r.grad) < 1.5e-2
+
+
+@pytest.mark.parametrize("V,dtype", [(65, torch.float32), (32000, torch.bfloat16), (1000, torch.float32), (151936, torch.bfloat16)])
+def test_cross_entropy(V, dtype):
+    from prometorch_b200.ops.fused_ops import cross_entropy
+    rows = 64
+    Vp = (V + 7) // 8 * 8
+    buf = torch.randn(rows, Vp, device="cuda").to(dtype) * 3
+    logits = buf[:, :V].detach().requires_grad_()
+    tgt = torch.randint(0, V, (rows,), device="cuda")
+    tgt[5] = -100
+    loss = cross_entropy(logits, tgt)
+    loss.backward()
+    lr = logits.detach().float().requires_grad_()
+    ref = F.cross_entropy(lr, tgt, ignore_index=-100)
+    ref.backward()
+    assert abs(float(loss) - float(ref)) < (2e-2 if dtype == torch.bfloat16 else 1e-4) * max(1.0, abs(float(ref)))
+    assert _rel(logits.grad, lr.grad) < (2e-2 if dtype == torch.bfloat16 else 1e-4)
