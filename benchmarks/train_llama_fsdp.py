@@ -1,0 +1,119 @@
+#!/usr/bin/env python
+"""Llama-1.1B-shape FSDP/ZeRO-3 training throughput (tokens/s), 1..8 GPUs of one node.
+
+    torchrun --nproc-per-node N benchmarks/train_llama_fsdp.py [--steps K] [--warmup W] [--impl fused|nccl]
+
+``fused``: parameter all-gather inside the tcgen05 GEMMs, reduce-scatter fused with AdamW
+(prometorch_b200.parallel.fsdp_fused).  ``nccl``: the same model under the process-group FSDP
+(all-gather / reduce-scatter through NCCL around local GEMMs) — the baseline the fused path is
+compared with.  Global batch 64 sequences of 2048 tokens (weak scaling below 8 GPUs keeps 8 sequences
+per GPU), bf16 compute, fp32 master weights, AdamW lr 3e-4 with warm-up + cosine."""
+import argparse
+import json
+import os
+import sys
+import time
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--seqs-per-gpu", type=int, default=8)
+    ap.add_argument("--micro", type=int, default=2)
+    ap.add_argument("--seq-len", type=int, default=2048)
+    ap.add_argument("--model", default="llama-1b", choices=["llama-1b", "tiny"])
+    args = ap.parse_args()
+    import torch.distributed as dist
+    from prometorch_b200.distributed import TorchProcessGroup
+    from prometorch_b200.models.llama import Llama, LlamaConfig
+    from prometorch_b200.optim import WarmupCosineAnnealingLR
+    rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29511")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    pg = TorchProcessGroup()
+    cfg = LlamaConfig.llama_1b() if args.model == "llama-1b" else LlamaConfig.tiny(hidden_size=512, num_heads=8, num_kv_heads=2,
+                                                                                 intermediate_size=1408, vocab_size=4096, max_seq=args.seq_len)
+    cfg.max_seq = max(cfg.max_seq, args.seq_len)
+    torch.manual_seed(0)
+    model = Llama(cfg).to(dev).to(torch.bfloat16)
+    nparams = model.num_parameters()
+    if args.impl == "fused":
+        from prometorch_b200.parallel.fsdp_fused import FusedFSDP
+        from prometorch_b200.parallel.symm import SymmGroup
+        symm = SymmGroup(dist.group.WORLD, dev)
+        eng = FusedFSDP(model, symm, pg, lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1)
+        sched = WarmupCosineAnnealingLR(eng, warmup_epochs=100, total_epochs=10000)
+    else:
+        from prometorch_b200.distributed import FullyShardedDataParallel
+        from prometorch_b200.optim import AdamW
+        eng = FullyShardedDataParallel(model, process_group=pg)
+        opt = AdamW(eng.local_shards(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1, fused=False)
+        sched = WarmupCosineAnnealingLR(opt, warmup_epochs=100, total_epochs=10000)
+    g = torch.Generator().manual_seed(rank)
+    n_micro = args.seqs_per_gpu // args.micro
+    host = [torch.randint(0, cfg.vocab_size, (args.micro, args.seq_len + 1), generator=g).pin_memory() for _ in range(n_micro)]
+
+    def step():
+        total = None
+        for mb in host:
+            tok = mb.to(dev, non_blocking=True)                 # host -> device every step
+            loss = eng(tok[:, :-1], tok[:, 1:]) / n_micro
+            loss.backward()
+            total = loss.detach() if total is None else total + loss.detach()
+        if args.impl == "fused":
+            eng.step()
+            eng.zero_grad()
+        else:
+            eng.reduce_scatter_grads()
+            opt.step()
+            opt.zero_grad()
+            eng.all_gather_params()
+        sched.step()
+        return total
+
+    for _ in range(args.warmup):
+        l = step()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record()
+    for _ in range(args.steps):
+        l = step()
+        lv = float(l)                                           # device -> host read of the loss every step
+    e1.record()
+    dist.barrier()
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    t = torch.tensor([e0.elapsed_time(e1), wall * 1e3], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if args.impl == "fused":
+        eng.check()
+    if rank == 0:
+        tokens = world * args.seqs_per_gpu * args.seq_len * args.steps
+        ms = float(t[0])
+        flops = 6.0 * nparams * tokens + 12.0 * cfg.num_layers * cfg.hidden_size * args.seq_len * tokens * 0.5
+        print(json.dumps({"metric": "Llama-1.1B-shape FSDP train tokens/s", "value": round(tokens / (ms / 1e3), 1), "unit": "tok/s",
+                          "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 2),
+                          "impl": args.impl, "loss": round(lv, 4), "params": nparams, "dtype": "bf16",
+                          "model_tflops_per_gpu": round(flops / (ms / 1e3) / 1e12 / world, 1),
+                          "e2e": {"value": round(tokens / (float(t[1]) / 1e3), 1), "unit": "tok/s",
+                                  "h2d_bytes_per_step": args.seqs_per_gpu * (args.seq_len + 1) * 8, "d2h_bytes_per_step": 4},
+                          "config": {"model": args.model, "global_batch": world * args.seqs_per_gpu, "seq_len": args.seq_len,
+                                     "parallelism": f"fsdp{world}", "micro_batch": args.micro}}))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -43,7 +43,7 @@ int ptb_make_tmap_bf16(CUtensorMap* map, const void* base, long long inner, long
 }
 
 template <int BN, int STAGES, bool A_MN, bool B_MN>
-static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, int n_sm, cudaStream_t st) {
+static int launch(const Operand& ta, const Operand& tb, const Params& p, int n_sm, cudaStream_t st) {
     auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN>;
     static bool attr = false;
     constexpr int smem = Smem<BN, STAGES>::TOTAL;
@@ -58,41 +58,82 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p,
 }
 
 template <int BN, int STAGES>
-static int launch_majors(int a_mn, int b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, int n_sm, cudaStream_t st) {
+static int launch_majors(int a_mn, int b_mn, const Operand& ta, const Operand& tb, const Params& p, int n_sm, cudaStream_t st) {
     if (!a_mn && !b_mn) return launch<BN, STAGES, false, false>(ta, tb, p, n_sm, st);
     if (!a_mn && b_mn) return launch<BN, STAGES, false, true>(ta, tb, p, n_sm, st);
     if (a_mn && !b_mn) return launch<BN, STAGES, true, false>(ta, tb, p, n_sm, st);
     return launch<BN, STAGES, true, true>(ta, tb, p, n_sm, st);
 }
 
-// C[M,N] (+)= op(A) op(B)^T with bf16 operands and fp32 accumulation.
+// Describe one operand.  ptrs: `nshards` base pointers (piece r in GPU r's memory, or one local pointer).
+//   K-major (mn == 0): stored [rows_total, K] row-major, split by rows into pieces of shard_rows.
+//   MN-major (mn == 1): stored [K, cols] row-major, split by rows (i.e. along K) into pieces of shard_rows.
+static int make_operand(Operand& op, void* const* ptrs, int nshards, int shard_rows, long long ld, int mn, int rows_total,
+                        int K, int box_rows) {
+    memset(&op, 0, sizeof(op));
+    op.nshards = nshards;
+    op.shard_rows = shard_rows;
+    if (nshards < 1 || nshards > MAX_SHARDS) { ptb_set_error("gemm: %d shards (1..%d supported)", nshards, MAX_SHARDS); return -1; }
+    const int box_outer = mn ? 64 : box_rows;
+    if (nshards > 1 && shard_rows % box_outer) {
+        ptb_set_error("gemm: shard of %d rows must be a multiple of the %d-row TMA box", shard_rows, box_outer);
+        return -1;
+    }
+    const long long stored_rows = mn ? K : rows_total;
+    for (int r = 0; r < nshards; ++r) {
+        long long rows_here = nshards > 1 ? std::min<long long>(shard_rows, stored_rows - (long long)r * shard_rows) : stored_rows;
+        if (rows_here <= 0) rows_here = 1;   // an empty trailing shard is never addressed
+        const long long inner = mn ? rows_total : K;
+        if (ptb_make_tmap_bf16(&op.map[r], ptrs[r], inner, rows_here, ld, 64, box_outer)) return -1;
+    }
+    return 0;
+}
+
+// General entry point.  a_ptrs/b_ptrs: arrays of a_shards/b_shards device pointers.  c_peers (EPI_SCATTER_ADD):
+// `c_shards` fp32 buffers [out_shard_rows, ldc], one per rank.
+PTB_API int ptb_gemm_bf16_ex(void* const* a_ptrs, int a_shards, int a_shard_rows, long long lda, int a_mn, void* const* b_ptrs,
+                             int b_shards, int b_shard_rows, long long ldb, int b_mn, void* C, long long ldc, void* const* c_peers,
+                             int c_shards, int out_shard_rows, int M, int N, int K, const float* bias, int flags, int* status,
+                             int n_sm, cudaStream_t st) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    {
+        int dev = 0;
+        PTB_CUDA_OK(cudaGetDevice(&dev));
+        PTB_CUDA_OK(cudaSetDevice(dev));     // the tensor-map encoder is a driver call: bind the primary context to this thread
+        if (n_sm <= 0) PTB_CUDA_OK(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
+    }
+    Params p;
+    memset(&p, 0, sizeof(p));
+    if (flags & EPI_SCATTER_ADD) {
+        if (c_shards < 1 || c_shards > MAX_SHARDS || out_shard_rows % BM) {
+            ptb_set_error("gemm: scatter-add needs 1..8 output shards of a multiple of %d rows", BM);
+            return -1;
+        }
+        for (int r = 0; r < c_shards; ++r) p.c_peer[r] = (float*)c_peers[r];
+        p.out_shard_rows = out_shard_rows;
+    } else {
+        const int out_elem = (flags & EPI_OUT_F32) ? 4 : 2;
+        if (((uintptr_t)C & 15) || ((ldc * out_elem) & 15)) { ptb_set_error("gemm: C needs a 16-byte aligned base and row pitch"); return -1; }
+    }
+    int BN = N > 128 ? 256 : 128;
+    if (!b_mn && b_shards > 1 && b_shard_rows % 256) BN = 128;
+    Operand oa, ob;
+    if (make_operand(oa, a_ptrs, a_shards, a_shard_rows, lda, a_mn, M, K, BM)) return -1;
+    if (make_operand(ob, b_ptrs, b_shards, b_shard_rows, ldb, b_mn, N, K, BN)) return -1;
+    p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.bias = bias; p.flags = flags; p.status = status;
+    p.tiles_m = (M + BM - 1) / BM;
+    p.tiles_n = (N + BN - 1) / BN;
+    if (BN == 256) return launch_majors<256, 4>(a_mn, b_mn, oa, ob, p, n_sm, st);
+    return launch_majors<128, 6>(a_mn, b_mn, oa, ob, p, n_sm, st);
+}
+
+// C[M,N] (+)= op(A) op(B)^T with bf16 operands and fp32 accumulation, all operands local.
 //   a_mn == 0: A is [M, K] row-major (pitch lda);  a_mn == 1: A is stored as [K, M] row-major.
 //   b_mn == 0: B is [N, K] row-major (pitch ldb);  b_mn == 1: B is stored as [K, N] row-major.
 //   flags: EPI_BIAS | EPI_ACCUM | EPI_OUT_F32 | EPI_GELU.  status: device int, set non-zero if a wait timed out.
 PTB_API int ptb_gemm_bf16(const void* A, long long lda, int a_mn, const void* B, long long ldb, int b_mn, void* C, long long ldc,
                           int M, int N, int K, const float* bias, int flags, int* status, int n_sm, cudaStream_t st) {
-    if (M <= 0 || N <= 0 || K <= 0) return 0;
-    const int out_elem = (flags & EPI_OUT_F32) ? 4 : 2;
-    if (((uintptr_t)C & 15) || ((ldc * out_elem) & 15)) { ptb_set_error("gemm: C needs a 16-byte aligned base and row pitch"); return -1; }
-    {
-        // the tensor-map encoder is a driver call: make sure this thread (e.g. an autograd worker) has the
-        // device's primary context current
-        int dev = 0;
-        PTB_CUDA_OK(cudaGetDevice(&dev));
-        PTB_CUDA_OK(cudaSetDevice(dev));
-        if (n_sm <= 0) PTB_CUDA_OK(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
-    }
-    const int BN = N > 128 ? 256 : 128;
-    CUtensorMap ta, tb;
-    if (a_mn) { if (ptb_make_tmap_bf16(&ta, A, M, K, lda, 64, 64)) return -1; }
-    else { if (ptb_make_tmap_bf16(&ta, A, K, M, lda, BK, BM)) return -1; }
-    if (b_mn) { if (ptb_make_tmap_bf16(&tb, B, N, K, ldb, 64, 64)) return -1; }
-    else { if (ptb_make_tmap_bf16(&tb, B, K, N, ldb, BK, BN)) return -1; }
-    Params p;
-    memset(&p, 0, sizeof(p));
-    p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.bias = bias; p.flags = flags; p.status = status;
-    p.tiles_m = (M + BM - 1) / BM;
-    p.tiles_n = (N + BN - 1) / BN;
-    if (BN == 256) return launch_majors<256, 4>(a_mn, b_mn, ta, tb, p, n_sm, st);
-    return launch_majors<128, 6>(a_mn, b_mn, ta, tb, p, n_sm, st);
+    void* ap[1] = {const_cast<void*>(A)};
+    void* bp[1] = {const_cast<void*>(B)};
+    return ptb_gemm_bf16_ex(ap, 1, 0, lda, a_mn, bp, 1, 0, ldb, b_mn, C, ldc, nullptr, 0, 0, M, N, K, bias, flags, status, n_sm, st);
 }

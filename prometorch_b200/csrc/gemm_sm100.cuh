@@ -24,7 +24,19 @@ constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
 constexpr int TMEM_COLS = 512;
 
-enum EpiFlags : int { EPI_BIAS = 1, EPI_ACCUM = 2, EPI_OUT_F32 = 4, EPI_GELU = 8 };
+constexpr int MAX_SHARDS = 8;
+
+enum EpiFlags : int { EPI_BIAS = 1, EPI_ACCUM = 2, EPI_OUT_F32 = 4, EPI_GELU = 8, EPI_SCATTER_ADD = 16 };
+
+// An operand whose stored matrix is split by rows over up to eight GPUs (each piece in that GPU's
+// memory, mapped here): piece r holds stored rows [r*shard_rows, (r+1)*shard_rows).  The producer warp
+// picks the tensor map from the row coordinate of the box it fetches, so the "all-gather" of a sharded
+// weight or activation happens tile by tile inside the GEMM's TMA pipeline (plain, non-multicast TMA
+// loads from peer memory).  nshards == 1 is the ordinary local operand.
+struct Operand {
+    CUtensorMap map[MAX_SHARDS];
+    int nshards, shard_rows;
+};
 
 struct Params {
     int M, N, K;
@@ -34,6 +46,10 @@ struct Params {
     int flags;
     int* status;
     int tiles_m, tiles_n;
+    // EPI_SCATTER_ADD (GEMM -> reduce-scatter): output rows [r*out_shard_rows, ...) belong to rank r and are
+    // added (fp32 atomics over NVLink) into that rank's buffer c_peer[r] of shape [out_shard_rows, ldc]
+    float* c_peer[MAX_SHARDS];
+    int out_shard_rows;
 };
 
 // ---- PTX wrappers -----------------------------------------------------------------------------
@@ -109,7 +125,7 @@ struct Smem {
 
 template <int BN, int STAGES, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(THREADS, 1)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ Params P) {
+gemm_bf16_kernel(const __grid_constant__ Operand opA, const __grid_constant__ Operand opB, const __grid_constant__ Params P) {
     using S = Smem<BN, STAGES>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -129,8 +145,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
         *abort_flag = 0;
         mbar_fence_init();
-        prefetch_tmap(&tmA);
-        prefetch_tmap(&tmB);
+        prefetch_tmap(&opA.map[0]);
+        prefetch_tmap(&opB.map[0]);
     }
     if (warp == 1) {
         tmem_alloc(tmem_slot, TMEM_COLS);
@@ -155,15 +171,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     uint8_t* sa = smem + s * S::STAGE_BYTES;
                     uint8_t* sb = sa + S::A_BYTES;
                     mbar_expect_tx(&full[s], S::STAGE_BYTES);
+                    // the box's row coordinate selects the shard (and so the GPU) it is fetched from
                     if (A_MN) {
-                        for (int c = 0; c < BM / 64; ++c) tma_load_2d(sa + c * 8192, &tmA, m0 + c * 64, kb * BK, &full[s]);
+                        const int r = kb * BK, sh = opA.nshards > 1 ? r / opA.shard_rows : 0;
+                        for (int c = 0; c < BM / 64; ++c) tma_load_2d(sa + c * 8192, &opA.map[sh], m0 + c * 64, r - sh * opA.shard_rows, &full[s]);
                     } else {
-                        tma_load_2d(sa, &tmA, kb * BK, m0, &full[s]);
+                        const int sh = opA.nshards > 1 ? m0 / opA.shard_rows : 0;
+                        tma_load_2d(sa, &opA.map[sh], kb * BK, m0 - sh * opA.shard_rows, &full[s]);
                     }
                     if (B_MN) {
-                        for (int c = 0; c < BN / 64; ++c) tma_load_2d(sb + c * 8192, &tmB, n0 + c * 64, kb * BK, &full[s]);
+                        const int r = kb * BK, sh = opB.nshards > 1 ? r / opB.shard_rows : 0;
+                        for (int c = 0; c < BN / 64; ++c) tma_load_2d(sb + c * 8192, &opB.map[sh], n0 + c * 64, r - sh * opB.shard_rows, &full[s]);
                     } else {
-                        tma_load_2d(sb, &tmB, kb * BK, n0, &full[s]);
+                        const int sh = opB.nshards > 1 ? n0 / opB.shard_rows : 0;
+                        tma_load_2d(sb, &opB.map[sh], kb * BK, n0 - sh * opB.shard_rows, &full[s]);
                     }
                 }
             }
@@ -231,7 +252,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
                     }
-                    if (P.flags & EPI_OUT_F32) {
+                    if (P.flags & EPI_SCATTER_ADD) {
+                        const int owner = row / P.out_shard_rows;
+                        float* cp = P.c_peer[owner] + (size_t)(row - owner * P.out_shard_rows) * P.ldc + col;
+                        for (int j = 0; j < 32 && col + j < P.N; ++j) atomicAdd(cp + j, v[j]);
+                    } else if (P.flags & EPI_OUT_F32) {
                         float* cp = reinterpret_cast<float*>(P.C) + (size_t)row * P.ldc + col;
                         if (col + 32 <= P.N) {
 #pragma unroll

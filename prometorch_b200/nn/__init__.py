@@ -14,6 +14,8 @@ from torch.nn import parameter, modules  # noqa: F401
 from .extras import (DiceLoss, FocalLoss, GlobalAvgPool2d, LowRankLinear, PositionalEncoding, QuantizedConv2d,
                      QuantizedLinear, num_parameters)
 from .fused import FlashSelfAttention, FusedCrossEntropyLoss, FusedRMSNorm, FusedSwiGLU
-from . import parallel  # noqa: E402
+import importlib as _importlib
+
+parallel = _importlib.import_module(__name__ + ".parallel")     # our package, not torch.nn.parallel from the star import
 
 F = functional

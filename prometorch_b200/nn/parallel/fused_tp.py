@@ -1,0 +1,180 @@
+"""Sequence-parallel column/row linear layers as autograd functions.
+
+Two implementations with the same numerics:
+
+* process-group path — all-gather / reduce-scatter collectives around a local GEMM (CPU ranks,
+  and the NCCL baseline on GPUs);
+* fused path (``tp.symm`` set, CUDA bf16) — the collective is folded into the tcgen05 GEMM:
+  all-gather -> GEMM reads each A (or B) tile straight from the peer that owns those tokens through
+  a per-peer TMA tensor map; GEMM -> reduce-scatter adds each output tile into its owner's fp32
+  buffer over NVLink from the epilogue.  Activations to be read by peers are staged in symmetric
+  memory (one local copy), and flag barriers order "written" before "read".
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Dict, Tuple
+
+import torch
+
+from ... import _native as N
+from ...distributed.ddp import PeerChannel, _ptr_array
+from ...ops.gemm import EPI_OUT_F32, EPI_SCATTER_ADD, _status, gemm_bf16, linear as fused_linear
+
+
+@N.register_decls
+def _decls(L):
+    vp, ci, ll = C.c_void_p, C.c_int, C.c_longlong
+    pp = C.POINTER(C.c_void_p)
+    L.ptb_gemm_bf16_ex.argtypes = [pp, ci, ci, ll, ci, pp, ci, ci, ll, ci, vp, ll, pp, ci, ci, ci, ci, ci, vp, ci, vp, ci, vp]
+    L.ptb_gemm_bf16_ex.restype = ci
+
+
+def gemm_ex(a_ptrs, a_shard_rows, lda, a_mn, b_ptrs, b_shard_rows, ldb, b_mn, M, Nn, K, device, out=None, c_peers=None,
+            out_shard_rows=0, ldc=None, out_dtype=torch.bfloat16, accumulate=False):
+    """Raw access to the sharded-operand GEMM.  ``a_ptrs`` / ``b_ptrs``: lists of device addresses."""
+    flags = 0
+    if c_peers is not None:
+        flags |= EPI_SCATTER_ADD
+        cp, nc, cptr = _ptr_array(c_peers), len(c_peers), 0
+    else:
+        if out is None:
+            out = torch.empty(M, Nn, dtype=out_dtype, device=device)
+        if out.dtype == torch.float32:
+            flags |= EPI_OUT_F32
+        if accumulate:
+            flags |= 2
+        cp, nc, cptr = _ptr_array([0]), 0, out.data_ptr()
+        ldc = out.stride(0)
+    st = torch.cuda.current_stream(device).cuda_stream
+    N.check(N.lib().ptb_gemm_bf16_ex(_ptr_array(a_ptrs), len(a_ptrs), a_shard_rows, lda, int(a_mn), _ptr_array(b_ptrs), len(b_ptrs),
+                                     b_shard_rows, ldb, int(b_mn), cptr, ldc, cp, nc, out_shard_rows, M, Nn, K, 0, flags,
+                                     _status(device).data_ptr(), 0, st), "gemm_bf16_ex")
+    return out
+
+
+class _Site:
+    """Symmetric staging for one layer call site: a bf16 activation buffer peers read, an fp32
+    accumulation buffer peers add into, and the flag channel for the barriers."""
+
+    def __init__(self, symm, rows: int, cols_act: int, cols_acc: int):
+        self.symm = symm
+        self.rows = rows
+        self.act = PeerChannel(symm, rows * cols_act * 2) if cols_act else None
+        self.acc = PeerChannel(symm, rows * cols_acc * 4) if cols_acc else None
+        self.chan = self.act or self.acc
+
+    def barrier(self):
+        ch = self.chan
+        st = torch.cuda.current_stream(self.symm.device).cuda_stream
+        N.check(N.lib().ptb_peer_barrier(ch.flag_ptrs, self.symm.rank, self.symm.world, ch.next_seq(), ch.ticket.data_ptr(),
+                                         ch.status.data_ptr(), st), "peer_barrier")
+
+
+_SITES: Dict[Tuple, _Site] = {}
+
+
+def _site(tp, key, rows, cols_act, cols_acc) -> _Site:
+    k = (id(tp.symm), key, rows, cols_act, cols_acc)
+    if k not in _SITES:
+        _SITES[k] = _Site(tp.symm, rows, cols_act, cols_acc)
+    return _SITES[k]
+
+
+def _fused_ok(x, tp):
+    return tp.symm is not None and x.is_cuda and x.dtype == torch.bfloat16 and x.shape[0] % 128 == 0
+
+
+class _ColumnSP(torch.autograd.Function):
+    """y[tokens_full, out/W] = gather_tokens(x) @ Wc^T (+ b)."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias, tp, key):
+        n, K = x.shape
+        W = tp.world_size
+        site = _site(tp, ("col", key), n, K, K)
+        xs = site.act.buf.tensor(torch.bfloat16)[:n * K].view(n, K)
+        xs.copy_(x)
+        site.barrier()                                   # every rank's tokens are in place
+        a_ptrs = [site.act.buf.peer_ptr(r) for r in range(W)]
+        y = gemm_ex(a_ptrs, n, K, False, [w.data_ptr()], 0, w.stride(0), False, n * W, w.shape[0], K, x.device)
+        if bias is not None:
+            y = y + bias
+        ctx.save_for_backward(w)
+        ctx.site, ctx.tp, ctx.n, ctx.has_bias = site, tp, n, bias is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        (w,) = ctx.saved_tensors
+        site, tp, n = ctx.site, ctx.tp, ctx.n
+        W, K, dev = tp.world_size, w.shape[1], dy.device
+        dy = dy.contiguous()
+        # dW[out/W, in] = dY^T gather(X): B = X stored [tokens (sharded over peers), in], read MN-major
+        b_ptrs = [site.act.buf.peer_ptr(r) for r in range(W)]
+        dw = gemm_ex([dy.data_ptr()], 0, dy.stride(0), True, b_ptrs, n, K, True, w.shape[0], K, n * W, dev)
+        # dX = reduce_scatter_tokens(dY Wc): the epilogue adds each tile into its owner's fp32 buffer
+        acc = site.acc.buf.tensor(torch.float32)[:n * K].view(n, K)
+        acc.zero_()
+        site.barrier()                                   # all accumulators are zero, all dW reads of X are done
+        c_peers = [site.acc.buf.peer_ptr(r) for r in range(W)]
+        gemm_ex([dy.data_ptr()], 0, dy.stride(0), False, [w.data_ptr()], 0, w.stride(0), True, n * W, K, w.shape[0], dev,
+                c_peers=c_peers, out_shard_rows=n, ldc=K)
+        site.barrier()                                   # every peer's contribution has landed
+        db = dy.float().sum(0).to(dy.dtype) if ctx.has_bias else None
+        return acc.to(torch.bfloat16), dw, db, None, None
+
+
+class _RowSP(torch.autograd.Function):
+    """y[tokens_local, out] = reduce_scatter_tokens(z @ Wr^T)."""
+
+    @staticmethod
+    def forward(ctx, z, w, tp, key):
+        nfull, Kl = z.shape
+        W = tp.world_size
+        n, out = nfull // W, w.shape[0]
+        site = _site(tp, ("row", key), n, out, out)
+        acc = site.acc.buf.tensor(torch.float32)[:n * out].view(n, out)
+        acc.zero_()
+        site.barrier()
+        c_peers = [site.acc.buf.peer_ptr(r) for r in range(W)]
+        z = z.contiguous()
+        gemm_ex([z.data_ptr()], 0, z.stride(0), False, [w.data_ptr()], 0, w.stride(0), False, nfull, out, Kl, z.device,
+                c_peers=c_peers, out_shard_rows=n, ldc=out)
+        site.barrier()
+        ctx.save_for_backward(z, w)
+        ctx.site, ctx.tp, ctx.n = site, tp, n
+        return acc.to(torch.bfloat16)
+
+    @staticmethod
+    def backward(ctx, dy):
+        z, w = ctx.saved_tensors
+        site, tp, n = ctx.site, ctx.tp, ctx.n
+        W, out, dev = tp.world_size, w.shape[0], dy.device
+        ds = site.act.buf.tensor(torch.bfloat16)[:n * out].view(n, out)
+        ds.copy_(dy)
+        site.barrier()
+        a_ptrs = [site.act.buf.peer_ptr(r) for r in range(W)]
+        # dZ[tokens_full, in/W] = gather(dY) Wr : A sharded by tokens, B = Wr read MN-major
+        dz = gemm_ex(a_ptrs, n, out, False, [w.data_ptr()], 0, w.stride(0), True, n * W, w.shape[1], out, dev)
+        # dWr[out, in/W] = gather(dY)^T Z : A = dY stored [tokens (sharded), out] MN-major, B = Z MN-major
+        dw = gemm_ex(a_ptrs, n, out, True, [z.data_ptr()], 0, z.stride(0), True, out, w.shape[1], n * W, dev)
+        site.barrier()                                   # peers are done reading my dY before it is reused
+        return dz, dw, None, None
+
+
+_counter = [0]
+
+
+def column_sp_forward(x, w, bias, tp, key=None):
+    if _fused_ok(x, tp):
+        return _ColumnSP.apply(x, w, bias, tp, key if key is not None else id(w))
+    from .tensor_parallel import _GatherTokens
+    return fused_linear(_GatherTokens.apply(x, tp), w, bias)
+
+
+def row_sp_forward(z, w, tp, key=None):
+    if _fused_ok(z, tp) and (z.shape[0] // tp.world_size) % 128 == 0:
+        return _RowSP.apply(z, w, tp, key if key is not None else id(w))
+    from .tensor_parallel import _ScatterTokens
+    return _ScatterTokens.apply(fused_linear(z, w, None), tp)

@@ -1,0 +1,197 @@
+"""ZeRO-3 / FSDP with the collectives fused into the compute kernels.
+
+Every ``nn.Linear`` weight ``W[out, in]`` is sharded by rows over the ranks (shard height rounded up to
+128 rows so GEMM tiles never straddle shards).  Each rank keeps, per weight:
+
+* its bf16 shard in symmetric memory — what every rank's GEMMs read;
+* the fp32 master shard and AdamW moments;
+* a full-size bf16 gradient buffer in symmetric memory.
+
+Forward  ``y = x W^T``: one tcgen05 GEMM whose TMA producer fetches each B tile from the rank that owns
+those rows (parameter all-gather fused into the consuming GEMM; no gathered copy ever exists).
+Backward ``dX = dY W``: the same, with ``W`` read as an N-major operand sharded along K.
+``dW = dY^T X`` accumulates into the local full-size gradient buffer.
+Step: one kernel per weight reads slice *r* of every peer's gradient buffer, sums in fp32 and applies
+AdamW to the master shard, writing the new bf16 shard in the same pass (reduce-scatter fused with the
+sharded optimizer).  Small replicated parameters (norm weights, embeddings) ride in one bucket that is
+all-reduced by the DDP kernel and stepped by the fused multi-tensor AdamW.
+
+Compare the reference: all parameters gathered before forward, never resharded, reduce-scatter by
+reading every rank's full gradient file (torch/distributed/fsdp.h:227-322).
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional
+
+import torch
+import torch.nn as nn
+
+from .. import _native as N
+from ..distributed.ddp import PeerChannel
+from ..nn.parallel.fused_tp import gemm_ex
+from ..optim import AdamW
+
+
+class _ShardedLinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, holder):
+        sh = holder
+        x2 = x.reshape(-1, x.shape[-1])
+        if x2.stride(1) != 1 or x2.stride(0) != x2.shape[1]:
+            x2 = x2.contiguous()
+        y = gemm_ex([x2.data_ptr()], 0, x2.stride(0), False, sh.shard_ptrs, sh.S, sh.inf, False, x2.shape[0], sh.out, sh.inf, x.device)
+        ctx.save_for_backward(x2)
+        ctx.sh, ctx.xshape = sh, x.shape
+        return y.view(*x.shape[:-1], sh.out)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x2,) = ctx.saved_tensors
+        sh = ctx.sh
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if dy2.stride(1) != 1 or dy2.stride(0) != dy2.shape[1]:
+            dy2 = dy2.contiguous()
+        dev = dy.device
+        # dX[M, in] = dY[M, out] W[out, in]: W stored [K=out (row-sharded over ranks), N=in], read N-major
+        dx = gemm_ex([dy2.data_ptr()], 0, dy2.stride(0), False, sh.shard_ptrs, sh.S, sh.inf, True, dy2.shape[0], sh.inf, sh.out, dev)
+        # dW[out, in] += dY^T X into the local full-size gradient buffer
+        gemm_ex([dy2.data_ptr()], 0, dy2.stride(0), True, [x2.data_ptr()], 0, x2.stride(0), True, sh.out, sh.inf, dy2.shape[0], dev,
+                out=sh.grad_full[:sh.out], accumulate=True)
+        return dx.view(ctx.xshape), None
+
+
+class ShardedLinear(nn.Module):
+    """Drop-in for a bias-free ``nn.Linear`` whose weight lives row-sharded across the ranks."""
+
+    def __init__(self, lin: nn.Linear, symm, pg):
+        super().__init__()
+        if lin.bias is not None:
+            raise NotImplementedError("ShardedLinear: bias-free layers only")
+        W, r = symm.world, symm.rank
+        self.out, self.inf = lin.out_features, lin.in_features
+        self.S = (math.ceil(self.out / W) + 127) // 128 * 128
+        dev = symm.device
+        full = lin.weight.detach().to(dev, torch.float32)
+        pg.broadcast(full, 0)
+        padded = torch.zeros(self.S * W, self.inf, device=dev)
+        padded[:self.out] = full
+        self.master = padded[r * self.S:(r + 1) * self.S].clone().contiguous()
+        self.m, self.v = torch.zeros_like(self.master), torch.zeros_like(self.master)
+        self.shard_ch = PeerChannel(symm, self.S * self.inf * 2)
+        self.shard = self.shard_ch.buf.tensor(torch.bfloat16)[:self.S * self.inf].view(self.S, self.inf)
+        self.shard.copy_(self.master)
+        self.grad_ch = PeerChannel(symm, self.S * W * self.inf * 2)
+        self.grad_full = self.grad_ch.buf.tensor(torch.bfloat16)[:self.S * W * self.inf].view(self.S * W, self.inf)
+        self.grad_full.zero_()
+        self.shard_ptrs = [self.shard_ch.buf.peer_ptr(k) for k in range(W)]
+        self.symm = symm
+        self.step_count = 0
+        symm.barrier()
+
+    def forward(self, x):
+        return _ShardedLinearFn.apply(x, self)
+
+    @torch.no_grad()
+    def step(self, lr, betas, eps, wd, grad_scale=1.0, n_ctas=64):
+        """Reduce-scatter the gradient and apply AdamW to the local shard (one kernel)."""
+        self.step_count += 1
+        ch = self.grad_ch
+        st = torch.cuda.current_stream(self.symm.device).cuda_stream
+        N.check(N.lib().ptb_fsdp_rs_adamw(ch.bufs, ch.flag_ptrs, self.symm.rank, self.symm.world, self.grad_full.numel(),
+                                          self.master.data_ptr(), self.m.data_ptr(), self.v.data_ptr(), self.shard.data_ptr(), lr,
+                                          betas[0], betas[1], eps, wd, self.step_count, grad_scale, ch.next_seq(),
+                                          ch.ticket.data_ptr(), ch.status.data_ptr(), n_ctas, st), "fsdp_rs_adamw")
+        self.grad_full.zero_()
+
+    def full_weight(self) -> torch.Tensor:
+        """Gather the bf16 weight (checkpointing / tests)."""
+        parts = [self.shard_ch.buf.tensor(torch.bfloat16, rank=k)[:self.S * self.inf].view(self.S, self.inf).clone()
+                 for k in range(self.symm.world)]
+        return torch.cat(parts)[:self.out]
+
+
+class FusedFSDP(nn.Module):
+    """Wraps a model: linear layers become :class:`ShardedLinear`; everything else is replicated and
+    kept in sync by the fused bucket all-reduce.  ``step()`` runs the sharded AdamW kernels and the
+    replicated-parameter AdamW; hyper-parameters follow an optional LR scheduler through ``param_groups``."""
+
+    def __init__(self, model: nn.Module, symm, pg, lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1,
+                 min_shard_numel: int = 1 << 16):
+        super().__init__()
+        self.symm, self.pg = symm, pg
+        self.sharded: List[ShardedLinear] = []
+        self._replace(model, min_shard_numel)
+        self.model = model
+        self.param_groups = [dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, params=[])]
+        rest = [p for p in model.parameters() if p.requires_grad]
+        self.rest = rest
+        with torch.no_grad():
+            for p in rest:
+                pg.broadcast(p.data, 0)
+        # fp32 masters for the replicated bf16 parameters; their gradients share one symmetric bucket
+        self.rest_master = [p.detach().float().clone().requires_grad_(False) for p in rest]
+        n = sum(p.numel() for p in rest)
+        self.bucket_numel = (n + 63) // 64 * 64
+        self.rest_opt = None
+        if rest:
+            self.bucket = PeerChannel(symm, self.bucket_numel * 2)
+            flat = self.bucket.buf.tensor(torch.bfloat16)[:self.bucket_numel]
+            flat.zero_()
+            self.rest_grads, off = [], 0
+            for p in rest:
+                self.rest_grads.append(flat[off:off + p.numel()].view_as(p))
+                off += p.numel()
+            masters = [nn.Parameter(m, requires_grad=False) for m in self.rest_master]
+            self.rest_opt = AdamW(masters, lr=lr, betas=betas, eps=eps, weight_decay=0.0, fused=True)
+            for mp, g, p in zip(masters, self.rest_grads, rest):
+                self.rest_opt.set_grad_source(mp, g)
+                if p.dtype == torch.bfloat16:
+                    self.rest_opt.attach_lowp(mp, p.data)
+            self._copy_back = [(mp, p) for mp, p in zip(masters, rest) if p.dtype != torch.bfloat16]
+            self.flat = flat
+
+    def _replace(self, mod: nn.Module, min_numel: int):
+        for name, child in list(mod.named_children()):
+            if isinstance(child, nn.Linear) and child.bias is None and child.weight.numel() >= min_numel \
+                    and child.in_features % 64 == 0:
+                sl = ShardedLinear(child, self.symm, self.pg)
+                setattr(mod, name, sl)
+                self.sharded.append(sl)
+            else:
+                self._replace(child, min_numel)
+
+    def forward(self, *a, **kw):
+        return self.model(*a, **kw)
+
+    @torch.no_grad()
+    def step(self, grad_scale: float = 1.0):
+        g = self.param_groups[0]
+        for sl in self.sharded:
+            sl.step(g["lr"], g["betas"], g["eps"], g["weight_decay"], grad_scale / self.symm.world)
+        if self.rest_opt is not None:
+            # fold .grad of the replicated parameters into the symmetric bucket, all-reduce it in one kernel
+            for p, gv in zip(self.rest, self.rest_grads):
+                if p.grad is not None:
+                    gv.copy_(p.grad)
+                    p.grad = None
+            ch = self.bucket
+            st = torch.cuda.current_stream(self.symm.device).cuda_stream
+            N.check(N.lib().ptb_ddp_allreduce(ch.bufs, ch.flag_ptrs, self.symm.rank, self.symm.world, self.bucket_numel, 1,
+                                              grad_scale / self.symm.world, ch.next_seq(), ch.ticket.data_ptr(), ch.status.data_ptr(),
+                                              32, st), "ddp_allreduce")
+            self.rest_opt.param_groups[0]["lr"] = g["lr"]
+            self.rest_opt.step()
+            for mp, p in self._copy_back:
+                p.data.copy_(mp.data)
+            self.flat.zero_()
+
+    def zero_grad(self):
+        for p in self.rest:
+            p.grad = None
+
+    def check(self):
+        for sl in self.sharded:
+            sl.grad_ch.check()
+        if self.rest_opt is not None:
+            self.bucket.check()

@@ -132,3 +132,41 @@ def test_cross_entropy(V, dtype):
     ref.backward()
     assert abs(float(loss) - float(ref)) < (2e-2 if dtype == torch.bfloat16 else 1e-4) * max(1.0, abs(float(ref)))
     assert _rel(logits.grad, lr.grad) < (2e-2 if dtype == torch.bfloat16 else 1e-4)
+
+
+@pytest.mark.parametrize("B,T,H,Hk,D,causal", [(2, 256, 6, 6, 64, True), (1, 300, 8, 2, 128, True), (2, 128, 4, 1, 128, False),
+                                               (1, 1000, 4, 4, 64, True), (1, 64, 32, 4, 64, True)])
+def test_flash_attention(B, T, H, Hk, D, causal):
+    from prometorch_b200.ops.attention import attention_reference, flash_attention
+    g = torch.Generator(device="cuda").manual_seed(T + H)
+    q = torch.randn(B, T, H, D, device="cuda", generator=g).bfloat16().requires_grad_()
+    k = torch.randn(B, T, Hk, D, device="cuda", generator=g).bfloat16().requires_grad_()
+    v = torch.randn(B, T, Hk, D, device="cuda", generator=g).bfloat16().requires_grad_()
+    o, lse = flash_attention(q, k, v, causal=causal, return_lse=True)
+    go = torch.randn_like(o)
+    o.backward(go)
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    orf, lser = attention_reference(qr, kr, vr, causal)
+    orf.backward(go.float())
+    assert _rel(o, orf) < 1e-2, _rel(o, orf)
+    assert torch.allclose(lse, lser, atol=2e-2, rtol=1e-3)
+    assert _rel(q.grad, qr.grad) < 2e-2, _rel(q.grad, qr.grad)
+    assert _rel(k.grad, kr.grad) < 2e-2, _rel(k.grad, kr.grad)
+    assert _rel(v.grad, vr.grad) < 2e-2, _rel(v.grad, vr.grad)
+
+
+def test_llama_tiny_forward_backward():
+    from prometorch_b200.models.llama import Llama, LlamaConfig
+    torch.manual_seed(0)
+    cfg = LlamaConfig.tiny(hidden_size=256, num_heads=4, num_kv_heads=2, intermediate_size=512, vocab_size=1024, max_seq=256)
+    m = Llama(cfg).cuda().bfloat16()
+    ref = Llama(cfg).float()
+    ref.load_state_dict({k: v.float().cpu() for k, v in m.state_dict().items()})
+    tok = torch.randint(0, 1024, (2, 129))
+    loss = m(tok[:, :-1].cuda(), tok[:, 1:].cuda())
+    loss.backward()
+    lr = ref(tok[:, :-1], tok[:, 1:])
+    lr.backward()
+    assert abs(float(loss) - float(lr)) < 0.05 * float(lr)
+    gm, gr = m.blocks[0].mlp.down.weight.grad.float().cpu(), ref.blocks[0].mlp.down.weight.grad
+    assert _rel(gm, gr) < 0.1, _rel(gm, gr)
