@@ -14,7 +14,7 @@ import torch
 
 from .. import _native as N
 
-EPI_BIAS, EPI_ACCUM, EPI_OUT_F32, EPI_GELU = 1, 2, 4, 8
+EPI_BIAS, EPI_ACCUM, EPI_OUT_F32, EPI_GELU, EPI_SCATTER_ADD = 1, 2, 4, 8, 16
 
 
 @N.register_decls
