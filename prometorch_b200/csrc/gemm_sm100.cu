@@ -51,8 +51,10 @@ static int launch(const Operand& ta, const Operand& tb, const Params& p, int n_s
         PTB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         attr = true;
     }
-    const int grid = std::min(p.tiles_m * p.tiles_n, n_sm);
-    kern<<<grid, THREADS, smem, st>>>(ta, tb, p);
+    Params q = p;
+    int n_st = (q.stA.seq || q.stB.seq) ? std::min(16, std::max(1, n_sm / 8)) : 0;
+    q.gemm_ctas = std::max(1, std::min(p.tiles_m * p.tiles_n, n_sm - n_st));
+    kern<<<q.gemm_ctas + n_st, THREADS, smem, st>>>(ta, tb, q);
     PTB_CUDA_OK(cudaGetLastError());
     return 0;
 }
@@ -89,12 +91,33 @@ static int make_operand(Operand& op, void* const* ptrs, int nshards, int shard_r
     return 0;
 }
 
+// Staging request for one operand, as passed from the host language (mirrors gemm::Staging).
+struct PtbStaging {
+    void* peer[MAX_SHARDS];
+    void* local;
+    void* flags;
+    int rank, world, shard_rows, stored_rows;
+    long long row_bytes;
+    unsigned seq;
+    int pad;
+};
+static void fill_staging(Staging& S, const PtbStaging* h) {
+    memset(&S, 0, sizeof(S));
+    if (!h || h->seq == 0) return;
+    for (int i = 0; i < MAX_SHARDS; ++i) S.peer[i] = (const uint4*)h->peer[i];
+    S.local = (uint4*)h->local;
+    S.flags = (uint32_t*)h->flags;
+    S.rank = h->rank; S.world = h->world; S.shard_rows = h->shard_rows; S.stored_rows = h->stored_rows;
+    S.row_vec = h->row_bytes / 16;
+    S.seq = h->seq;
+}
+
 // General entry point.  a_ptrs/b_ptrs: arrays of a_shards/b_shards device pointers.  c_peers (EPI_SCATTER_ADD):
 // `c_shards` fp32 buffers [out_shard_rows, ldc], one per rank.
 PTB_API int ptb_gemm_bf16_ex(void* const* a_ptrs, int a_shards, int a_shard_rows, long long lda, int a_mn, void* const* b_ptrs,
                              int b_shards, int b_shard_rows, long long ldb, int b_mn, void* C, long long ldc, void* const* c_peers,
                              int c_shards, int out_shard_rows, int M, int N, int K, const float* bias, int flags, int* status,
-                             int n_sm, cudaStream_t st) {
+                             int n_sm, cudaStream_t st, const PtbStaging* stage_a, const PtbStaging* stage_b) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     {
         int dev = 0;
@@ -117,6 +140,12 @@ PTB_API int ptb_gemm_bf16_ex(void* const* a_ptrs, int a_shards, int a_shard_rows
     }
     int BN = N > 128 ? 256 : 128;
     if (!b_mn && b_shards > 1 && b_shard_rows % 256) BN = 128;
+    fill_staging(p.stA, stage_a);
+    fill_staging(p.stB, stage_b);
+    if ((p.stA.seq && (p.stA.shard_rows % STAGE_ROWS)) || (p.stB.seq && (p.stB.shard_rows % STAGE_ROWS))) {
+        ptb_set_error("gemm: staged shards must be a multiple of %d rows", STAGE_ROWS);
+        return -1;
+    }
     Operand oa, ob;
     if (make_operand(oa, a_ptrs, a_shards, a_shard_rows, lda, a_mn, M, K, BM)) return -1;
     if (make_operand(ob, b_ptrs, b_shards, b_shard_rows, ldb, b_mn, N, K, BN)) return -1;
@@ -135,5 +164,5 @@ PTB_API int ptb_gemm_bf16(const void* A, long long lda, int a_mn, const void* B,
                           int M, int N, int K, const float* bias, int flags, int* status, int n_sm, cudaStream_t st) {
     void* ap[1] = {const_cast<void*>(A)};
     void* bp[1] = {const_cast<void*>(B)};
-    return ptb_gemm_bf16_ex(ap, 1, 0, lda, a_mn, bp, 1, 0, ldb, b_mn, C, ldc, nullptr, 0, 0, M, N, K, bias, flags, status, n_sm, st);
+    return ptb_gemm_bf16_ex(ap, 1, 0, lda, a_mn, bp, 1, 0, ldb, b_mn, C, ldc, nullptr, 0, 0, M, N, K, bias, flags, status, n_sm, st, nullptr, nullptr);
 }

@@ -38,6 +38,22 @@ struct Operand {
     int nshards, shard_rows;
 };
 
+// Staging of a row-sharded operand (the fused all-gather): the stored matrix lives row-sharded over the
+// ranks, rank r owning stored rows [r*shard_rows, (r+1)*shard_rows) INSIDE its own full-size symmetric
+// buffer.  A few extra CTAs of the GEMM grid ("stagers") copy the peers' rows into this GPU's buffer in
+// 128-row blocks, each block crossing NVLink exactly once, and publish a per-block flag; the TMA producer
+// of the GEMM CTAs waits for the flags of the rows it is about to fetch and then reads local memory.
+// Copy and math overlap block by block inside one launch.  seq == 0 disables staging.
+constexpr int STAGE_ROWS = 128;
+struct Staging {
+    const uint4* peer[MAX_SHARDS];   // peer r's full-size buffer (this GPU's mapping); peer[rank] is `local`
+    uint4* local;
+    uint32_t* flags;                 // [ceil(stored_rows / 128)] last sequence number staged
+    int rank, world, shard_rows, stored_rows;
+    long long row_vec;               // 16-byte vectors per stored row (= pitch)
+    uint32_t seq;
+};
+
 struct Params {
     int M, N, K;
     void* C;                // bf16 or fp32 [M, ldc]
@@ -50,7 +66,66 @@ struct Params {
     // added (fp32 atomics over NVLink) into that rank's buffer c_peer[r] of shape [out_shard_rows, ldc]
     float* c_peer[MAX_SHARDS];
     int out_shard_rows;
+    int gemm_ctas;          // CTAs [0, gemm_ctas) compute tiles; CTAs beyond it are stagers
+    Staging stA, stB;
 };
+
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+// Producer side: make sure stored rows [r0, r0 + nrows) have been staged for this sequence number.
+__device__ __forceinline__ bool wait_staged(const Staging& S, int r0, int nrows, int* status) {
+    if (S.seq == 0) return true;
+    const int last = min(r0 + nrows, S.stored_rows) - 1;
+    for (int blk = r0 / STAGE_ROWS; blk <= last / STAGE_ROWS; ++blk) {
+        if ((blk * STAGE_ROWS) / S.shard_rows == S.rank && ((blk + 1) * STAGE_ROWS - 1) / S.shard_rows == S.rank) continue;   // my own rows
+        uint64_t t0;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+        uint32_t i = 0;
+        while ((int32_t)(ld_acquire_gpu(S.flags + blk) - S.seq) < 0) {
+            if ((++i & 255u) == 0) {
+                uint64_t t1;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+                if (t1 - t0 > 2000000000ull) { if (status) atomicExch(status, PTB_ERR_FLAG_TIMEOUT); return false; }
+            }
+        }
+    }
+    fence_proxy_async_all();        // the rows were written with ordinary stores; the TMA engine reads them next
+    return true;
+}
+
+// Stager CTA: copy 128-row blocks that belong to other ranks from their memory into the local buffer.
+__device__ __forceinline__ void run_stager(const Staging& S, int stager, int n_stagers) {
+    if (S.seq == 0) return;
+    const int nblk = (S.stored_rows + STAGE_ROWS - 1) / STAGE_ROWS;
+    for (int blk = stager; blk < nblk; blk += n_stagers) {
+        const int r0 = blk * STAGE_ROWS, r1 = min(r0 + STAGE_ROWS, S.stored_rows);
+        const int owner = r0 / S.shard_rows;
+        if (owner != S.rank && (int32_t)(ld_acquire_gpu(S.flags + blk) - S.seq) < 0) {
+            const uint4* src = S.peer[owner] + (long long)r0 * S.row_vec;
+            uint4* dst = S.local + (long long)r0 * S.row_vec;
+            const long long n = (long long)(r1 - r0) * S.row_vec;
+            for (long long i = threadIdx.x; i < n; i += 4 * THREADS) {      // four loads in flight per thread
+                uint4 v[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) if (i + u * THREADS < n) v[u] = __ldcg(src + i + u * THREADS);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) if (i + u * THREADS < n) dst[i + u * THREADS] = v[u];
+            }
+            __threadfence();
+            fence_proxy_async_all();
+            __syncthreads();
+            if (threadIdx.x == 0) st_release_gpu(S.flags + blk, S.seq);
+        }
+    }
+}
 
 // ---- PTX wrappers -----------------------------------------------------------------------------
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
@@ -148,6 +223,14 @@ gemm_bf16_kernel(const __grid_constant__ Operand opA, const __grid_constant__ Op
         prefetch_tmap(&opA.map[0]);
         prefetch_tmap(&opB.map[0]);
     }
+    const int n_gemm = P.gemm_ctas;
+    if ((int)blockIdx.x >= n_gemm) {
+        // ---------------------------------------------------------------------- stager CTA (no TMEM, no tiles)
+        const int stager = blockIdx.x - n_gemm, n_st = gridDim.x - n_gemm;
+        run_stager(P.stA, stager, n_st);
+        run_stager(P.stB, stager, n_st);
+        return;
+    }
     if (warp == 1) {
         tmem_alloc(tmem_slot, TMEM_COLS);
         tmem_relinquish();
@@ -162,7 +245,7 @@ gemm_bf16_kernel(const __grid_constant__ Operand opA, const __grid_constant__ Op
         if (lane == 0) {
             int it = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            for (int t = blockIdx.x; t < num_tiles && ok; t += n_gemm) {
                 const int m0 = (t % P.tiles_m) * BM, n0 = (t / P.tiles_m) * BN;
                 for (int kb = 0; kb < kblocks && ok; ++kb, ++it) {
                     const int s = it % STAGES;
@@ -171,6 +254,10 @@ gemm_bf16_kernel(const __grid_constant__ Operand opA, const __grid_constant__ Op
                     uint8_t* sa = smem + s * S::STAGE_BYTES;
                     uint8_t* sb = sa + S::A_BYTES;
                     mbar_expect_tx(&full[s], S::STAGE_BYTES);
+                    // rows being staged from peers must have landed before the TMA engine reads them
+                    if (kb == 0 || A_MN) ok = wait_staged(P.stA, A_MN ? kb * BK : m0, A_MN ? BK : BM, P.status);
+                    if (ok && (kb == 0 || B_MN)) ok = wait_staged(P.stB, B_MN ? kb * BK : n0, B_MN ? BK : BN, P.status);
+                    if (!ok) break;
                     // the box's row coordinate selects the shard (and so the GPU) it is fetched from
                     if (A_MN) {
                         const int r = kb * BK, sh = opA.nshards > 1 ? r / opA.shard_rows : 0;
@@ -196,7 +283,7 @@ gemm_bf16_kernel(const __grid_constant__ Operand opA, const __grid_constant__ Op
             constexpr uint32_t idesc = instr_desc(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
             int it = 0, tl = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tl) {
+            for (int t = blockIdx.x; t < num_tiles && ok; t += n_gemm, ++tl) {
                 const int b = tl & 1;
                 if (tl >= 2) ok = mbar_wait(&acc_empty[b], (uint32_t)(((tl >> 1) - 1) & 1), P.status);
                 if (!ok) break;
@@ -226,7 +313,7 @@ gemm_bf16_kernel(const __grid_constant__ Operand opA, const __grid_constant__ Op
         const int q = warp & 3;                     // TMEM lane quarter this warp may read
         int tl = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tl) {
+        for (int t = blockIdx.x; t < num_tiles && ok; t += n_gemm, ++tl) {
             const int b = tl & 1;
             const int m0 = (t % P.tiles_m) * BM, n0 = (t / P.tiles_m) * BN;
             ok = mbar_wait(&acc_full[b], (uint32_t)((tl >> 1) & 1), P.status);

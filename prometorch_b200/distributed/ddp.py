@@ -128,6 +128,7 @@ class DistributedDataParallel(nn.Module):
     def _build_buckets(self, bucket_mb: float):
         self.buckets: List[_Bucket] = []
         self._bucket_of = {}
+        self._view_of = {}
         cap = int(bucket_mb * 1024 * 1024)
         groups, cur, cur_bytes, key = [], [], 0, None
         for p in reversed(self._params):            # gradients arrive roughly in reverse order
@@ -146,14 +147,15 @@ class DistributedDataParallel(nn.Module):
             for p, v in zip(g, b.views):
                 p.grad = v                          # the gradient IS the bucket slice
                 self._bucket_of[id(p)] = b
+                self._view_of[id(p)] = v
             self.buckets.append(b)
 
     def _make_hook(self, p):
         def hook(param):
             b = self._bucket_of[id(param)]
-            if param.grad is not None and param.grad.data_ptr() != b.views[b.params.index(param)].data_ptr():
+            v = self._view_of[id(param)]
+            if param.grad is not None and param.grad.data_ptr() != v.data_ptr():
                 # someone replaced .grad (e.g. zero_grad(set_to_none=True)): fold it back into the bucket
-                v = b.views[b.params.index(param)]
                 v.copy_(param.grad)
                 param.grad = v
             b.pending -= 1

@@ -63,6 +63,7 @@ def launch(world_size: int, worker_fn: Callable[[int, int], Optional[int]], mast
     deadline = None if timeout is None else time.time() + timeout
     worst = 0
     alive = set(range(world_size))
+    killed = set()                            # ranks this launcher terminated: their signal codes do not count
     while alive:
         for r in list(alive):
             p = procs[r]
@@ -71,10 +72,13 @@ def launch(world_size: int, worker_fn: Callable[[int, int], Optional[int]], mast
                 continue
             alive.discard(r)
             code = p.exitcode if p.exitcode >= 0 else 128 - p.exitcode
+            if r in killed:
+                continue
             worst = max(worst, code)
             if code != 0:                     # a failed rank takes the job down: terminate exactly our children
                 for q in alive:
                     procs[q].terminate()
+                    killed.add(q)
         if deadline is not None and time.time() > deadline and alive:
             for q in alive:
                 procs[q].terminate()

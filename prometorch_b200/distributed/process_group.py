@@ -243,5 +243,9 @@ class TorchProcessGroup(ProcessGroup):
     def send(self, tensor, dst):
         return self._wrap(lambda: self.dist.send(tensor, self.dist.get_global_rank(self.group, dst), group=self.group))
 
+    def isend(self, tensor, dst):
+        """Non-blocking send; returns a work handle with ``wait()``."""
+        return self._wrap(lambda: self.dist.isend(tensor, self.dist.get_global_rank(self.group, dst), group=self.group))
+
     def recv(self, tensor, src):
         return self._wrap(lambda: self.dist.recv(tensor, self.dist.get_global_rank(self.group, src), group=self.group))

@@ -357,27 +357,31 @@ class GGUFModel:
 
     def generate(self, prompt: Sequence[int], max_new_tokens: int = 128, temperature: float = 0.0, top_k: int = 40,
                  top_p: float = 0.9, repeat_penalty: float = 1.0, stop_ids: Iterable[int] = (),
-                 on_token: Optional[Callable[[int], bool]] = None, seed: int = 42) -> List[int]:
+                 on_token: Optional[Callable[[int], bool]] = None, seed: int = 42, _pos0: Optional[int] = None,
+                 _history: Optional[Sequence[int]] = None) -> List[int]:
         """Token-level generation.  Greedy without a callback runs entirely on the device; with a
         callback (streaming) or sampling it steps token by token."""
         stop = set(int(s) for s in stop_ids)
         if self.cfg.eos_token_id >= 0:
             stop.add(self.cfg.eos_token_id)
         greedy = temperature <= 0.0 and repeat_penalty == 1.0
-        if greedy and on_token is None and not stop:
+        if greedy and on_token is None and not stop and _pos0 is None:
             return self.run_script(prompt, max_new_tokens)
         if not greedy and not self.want_logits:
             raise RuntimeError("sampling needs the model opened with want_logits=True")
         # prompt (all but the last token) in one scripted run, then step
         out: List[int] = []
         n = len(prompt)
-        if n > 1:
-            self.run_script(prompt[:-1], 1)
-        tok, pos = int(prompt[-1]), n - 1
+        if _pos0 is not None:                   # the caller already ran the prompt up to position _pos0
+            tok, pos = int(prompt[-1]), int(_pos0)
+        else:
+            if n > 1:
+                self.run_script(prompt[:-1], 1)
+            tok, pos = int(prompt[-1]), n - 1
         from ..ops.sampling import sample_logits
         gen = torch.Generator(device=self.device)
         gen.manual_seed(seed)
-        history = list(int(t) for t in prompt)
+        history = list(int(t) for t in (_history if _history is not None else prompt))
         for _ in range(max_new_tokens):
             nxt = self.forward_decode(tok, pos)
             if not greedy:

@@ -1,0 +1,59 @@
+"""``compile`` / ``trace``: capture instead of code generation.
+
+The reference's JIT traces element-wise chains and emits C++ through a subprocess compiler, and its
+"PromePile" flattens Sequential MLPs and the LLM decode step (torch/jit/*.h, torch/compile/*.h).  On a B200
+the launch-bound inner loops are captured as CUDA graphs: ``compile(module)`` returns a ``CompiledModule``
+that records one forward per input signature into a graph (static buffers, replay on later calls); on CPU it
+returns the module unchanged.  The decode engine captures its own per-token graph natively."""
+from __future__ import annotations
+
+from typing import Dict, Tuple
+
+import torch
+import torch.nn as nn
+
+
+class CompiledModule(nn.Module):
+    def __init__(self, module: nn.Module, warmup: int = 2):
+        super().__init__()
+        self.module, self.warmup = module, warmup
+        self._graphs: Dict[Tuple, Tuple] = {}
+
+    def forward(self, *args):
+        if not args or not all(torch.is_tensor(a) and a.is_cuda for a in args) or torch.is_grad_enabled() and any(
+                p.requires_grad for p in self.module.parameters()):
+            return self.module(*args)
+        key = tuple((tuple(a.shape), a.dtype) for a in args)
+        ent = self._graphs.get(key)
+        if ent is None:
+            static_in = [a.clone() for a in args]
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s), torch.no_grad():
+                for _ in range(self.warmup):
+                    self.module(*static_in)
+            torch.cuda.current_stream().wait_stream(s)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g), torch.no_grad():
+                static_out = self.module(*static_in)
+            ent = self._graphs[key] = (g, static_in, static_out)
+        g, static_in, static_out = ent
+        for d, a in zip(static_in, args):
+            d.copy_(a)
+        g.replay()
+        return static_out.clone() if torch.is_tensor(static_out) else static_out
+
+
+def compile(module, **kw):
+    """Graph-capturing wrapper for inference modules (see :class:`CompiledModule`)."""
+    if isinstance(module, nn.Module):
+        return CompiledModule(module)
+    return module
+
+
+def trace(fn, example_inputs):
+    return torch.jit.trace(fn, example_inputs)
+
+
+def script(fn):
+    return torch.jit.script(fn)

@@ -26,12 +26,27 @@ from ...ops.gemm import EPI_OUT_F32, EPI_SCATTER_ADD, _status, gemm_bf16, linear
 def _decls(L):
     vp, ci, ll = C.c_void_p, C.c_int, C.c_longlong
     pp = C.POINTER(C.c_void_p)
-    L.ptb_gemm_bf16_ex.argtypes = [pp, ci, ci, ll, ci, pp, ci, ci, ll, ci, vp, ll, pp, ci, ci, ci, ci, ci, vp, ci, vp, ci, vp]
+    L.ptb_gemm_bf16_ex.argtypes = [pp, ci, ci, ll, ci, pp, ci, ci, ll, ci, vp, ll, pp, ci, ci, ci, ci, ci, vp, ci, vp, ci, vp, vp, vp]
     L.ptb_gemm_bf16_ex.restype = ci
 
 
+class Staging(C.Structure):
+    """Request to stage a row-sharded operand from the peers inside the GEMM launch (mirrors ``PtbStaging``)."""
+    _fields_ = [("peer", C.c_void_p * 8), ("local", C.c_void_p), ("flags", C.c_void_p), ("rank", C.c_int), ("world", C.c_int),
+                ("shard_rows", C.c_int), ("stored_rows", C.c_int), ("row_bytes", C.c_longlong), ("seq", C.c_uint), ("pad", C.c_int)]
+
+
+def make_staging(buf, flags: torch.Tensor, rank: int, world: int, shard_rows: int, stored_rows: int, row_bytes: int, seq: int) -> Staging:
+    s = Staging()
+    for r in range(world):
+        s.peer[r] = buf.peer_ptr(r)
+    s.local, s.flags = buf.peer_ptr(rank), flags.data_ptr()
+    s.rank, s.world, s.shard_rows, s.stored_rows, s.row_bytes, s.seq = rank, world, shard_rows, stored_rows, row_bytes, seq
+    return s
+
+
 def gemm_ex(a_ptrs, a_shard_rows, lda, a_mn, b_ptrs, b_shard_rows, ldb, b_mn, M, Nn, K, device, out=None, c_peers=None,
-            out_shard_rows=0, ldc=None, out_dtype=torch.bfloat16, accumulate=False):
+            out_shard_rows=0, ldc=None, out_dtype=torch.bfloat16, accumulate=False, stage_a=None, stage_b=None):
     """Raw access to the sharded-operand GEMM.  ``a_ptrs`` / ``b_ptrs``: lists of device addresses."""
     flags = 0
     if c_peers is not None:
@@ -49,7 +64,8 @@ def gemm_ex(a_ptrs, a_shard_rows, lda, a_mn, b_ptrs, b_shard_rows, ldb, b_mn, M,
     st = torch.cuda.current_stream(device).cuda_stream
     N.check(N.lib().ptb_gemm_bf16_ex(_ptr_array(a_ptrs), len(a_ptrs), a_shard_rows, lda, int(a_mn), _ptr_array(b_ptrs), len(b_ptrs),
                                      b_shard_rows, ldb, int(b_mn), cptr, ldc, cp, nc, out_shard_rows, M, Nn, K, 0, flags,
-                                     _status(device).data_ptr(), 0, st), "gemm_bf16_ex")
+                                     _status(device).data_ptr(), 0, st, C.addressof(stage_a) if stage_a is not None else None,
+                                     C.addressof(stage_b) if stage_b is not None else None), "gemm_bf16_ex")
     return out
 
 
@@ -60,9 +76,25 @@ class _Site:
     def __init__(self, symm, rows: int, cols_act: int, cols_acc: int):
         self.symm = symm
         self.rows = rows
-        self.act = PeerChannel(symm, rows * cols_act * 2) if cols_act else None
+        W = symm.world
+        # full-size activation buffer [rows*W, cols]: this rank's tokens are rows [rank*rows, ...), the peers'
+        # rows are staged in by the GEMM that consumes them
+        self.act = PeerChannel(symm, rows * W * cols_act * 2) if cols_act else None
         self.acc = PeerChannel(symm, rows * cols_acc * 4) if cols_acc else None
         self.chan = self.act or self.acc
+        self.cols_act = cols_act
+        self.stage_flags = torch.zeros((rows * W + 127) // 128, dtype=torch.int32, device=symm.device)
+        self.stage_seq = 0
+
+    def publish(self, x: torch.Tensor):
+        """Put this rank's rows in place, wait until every rank has done so, and return (full view, staging)."""
+        W, r, n = self.symm.world, self.symm.rank, self.rows
+        full = self.act.buf.tensor(torch.bfloat16)[:n * W * self.cols_act].view(n * W, self.cols_act)
+        full[r * n:(r + 1) * n].copy_(x)
+        self.barrier()
+        self.stage_seq += 1
+        st = make_staging(self.act.buf, self.stage_flags, r, W, n, n * W, self.cols_act * 2, self.stage_seq)
+        return full, st
 
     def barrier(self):
         ch = self.chan
@@ -93,26 +125,22 @@ class _ColumnSP(torch.autograd.Function):
         n, K = x.shape
         W = tp.world_size
         site = _site(tp, ("col", key), n, K, K)
-        xs = site.act.buf.tensor(torch.bfloat16)[:n * K].view(n, K)
-        xs.copy_(x)
-        site.barrier()                                   # every rank's tokens are in place
-        a_ptrs = [site.act.buf.peer_ptr(r) for r in range(W)]
-        y = gemm_ex(a_ptrs, n, K, False, [w.data_ptr()], 0, w.stride(0), False, n * W, w.shape[0], K, x.device)
+        full, st = site.publish(x)                       # every rank's tokens are in place; peers' rows get staged by the GEMM
+        y = gemm_ex([full.data_ptr()], 0, K, False, [w.data_ptr()], 0, w.stride(0), False, n * W, w.shape[0], K, x.device, stage_a=st)
         if bias is not None:
             y = y + bias
-        ctx.save_for_backward(w)
+        ctx.save_for_backward(w, full)
         ctx.site, ctx.tp, ctx.n, ctx.has_bias = site, tp, n, bias is not None
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        (w,) = ctx.saved_tensors
+        w, full = ctx.saved_tensors
         site, tp, n = ctx.site, ctx.tp, ctx.n
         W, K, dev = tp.world_size, w.shape[1], dy.device
         dy = dy.contiguous()
-        # dW[out/W, in] = dY^T gather(X): B = X stored [tokens (sharded over peers), in], read MN-major
-        b_ptrs = [site.act.buf.peer_ptr(r) for r in range(W)]
-        dw = gemm_ex([dy.data_ptr()], 0, dy.stride(0), True, b_ptrs, n, K, True, w.shape[0], K, n * W, dev)
+        # dW[out/W, in] = dY^T gather(X): X was gathered into the local buffer by the forward GEMM, read MN-major
+        dw = gemm_ex([dy.data_ptr()], 0, dy.stride(0), True, [full.data_ptr()], 0, K, True, w.shape[0], K, n * W, dev)
         # dX = reduce_scatter_tokens(dY Wc): the epilogue adds each tile into its owner's fp32 buffer
         acc = site.acc.buf.tensor(torch.float32)[:n * K].view(n, K)
         acc.zero_()
@@ -151,14 +179,11 @@ class _RowSP(torch.autograd.Function):
         z, w = ctx.saved_tensors
         site, tp, n = ctx.site, ctx.tp, ctx.n
         W, out, dev = tp.world_size, w.shape[0], dy.device
-        ds = site.act.buf.tensor(torch.bfloat16)[:n * out].view(n, out)
-        ds.copy_(dy)
-        site.barrier()
-        a_ptrs = [site.act.buf.peer_ptr(r) for r in range(W)]
-        # dZ[tokens_full, in/W] = gather(dY) Wr : A sharded by tokens, B = Wr read MN-major
-        dz = gemm_ex(a_ptrs, n, out, False, [w.data_ptr()], 0, w.stride(0), True, n * W, w.shape[1], out, dev)
-        # dWr[out, in/W] = gather(dY)^T Z : A = dY stored [tokens (sharded), out] MN-major, B = Z MN-major
-        dw = gemm_ex(a_ptrs, n, out, True, [z.data_ptr()], 0, z.stride(0), True, out, w.shape[1], n * W, dev)
+        full, st = site.publish(dy)
+        # dZ[tokens_full, in/W] = gather(dY) Wr : A staged from the peers by this launch, B = Wr read MN-major
+        dz = gemm_ex([full.data_ptr()], 0, out, False, [w.data_ptr()], 0, w.stride(0), True, n * W, w.shape[1], out, dev, stage_a=st)
+        # dWr[out, in/W] = gather(dY)^T Z : A = gathered dY (now local) read MN-major, B = Z MN-major
+        dw = gemm_ex([full.data_ptr()], 0, out, True, [z.data_ptr()], 0, z.stride(0), True, out, w.shape[1], n * W, dev)
         site.barrier()                                   # peers are done reading my dY before it is reused
         return dz, dw, None, None
 

@@ -69,7 +69,10 @@ class Pipeline1F1BStage:
 
     # -- p2p helpers
     def _send(self, t, dst):
-        self.pg.send(t.contiguous(), dst)
+        # non-blocking: in 1F1B a stage's forward send and its neighbour's backward send cross each other
+        t = t.contiguous()
+        w = self.pg.isend(t, dst) if hasattr(self.pg, "isend") else self.pg.send(t, dst)
+        self._inflight.append((w, t))
 
     def _recv(self, shape, dtype, device, src):
         t = torch.empty(shape, dtype=dtype, device=device)
@@ -88,6 +91,7 @@ class Pipeline1F1BStage:
         saved_in: List[Optional[torch.Tensor]] = [None] * M
         saved_out: List[Optional[torch.Tensor]] = [None] * M
         losses = []
+        self._inflight = []
 
         def forward_one(mb):
             if self.first:
@@ -127,4 +131,8 @@ class Pipeline1F1BStage:
         while b < M:
             backward_one(b)
             b += 1
+        for w, _ in self._inflight:
+            if w is not None:
+                w.wait()
+        self._inflight = []
         return torch.stack(losses).sum() if losses else None

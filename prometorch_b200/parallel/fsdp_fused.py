@@ -29,7 +29,7 @@ import torch.nn as nn
 
 from .. import _native as N
 from ..distributed.ddp import PeerChannel
-from ..nn.parallel.fused_tp import gemm_ex
+from ..nn.parallel.fused_tp import gemm_ex, make_staging
 from ..optim import AdamW
 
 
@@ -40,7 +40,10 @@ class _ShardedLinearFn(torch.autograd.Function):
         x2 = x.reshape(-1, x.shape[-1])
         if x2.stride(1) != 1 or x2.stride(0) != x2.shape[1]:
             x2 = x2.contiguous()
-        y = gemm_ex([x2.data_ptr()], 0, x2.stride(0), False, sh.shard_ptrs, sh.S, sh.inf, False, x2.shape[0], sh.out, sh.inf, x.device)
+        # B = the local full-size buffer; rows owned by peers are staged from their memory by the stager CTAs of
+        # this same launch (each 128-row block crosses NVLink once per optimizer step), overlapped with the math
+        y = gemm_ex([x2.data_ptr()], 0, x2.stride(0), False, [sh.full_ptr], 0, sh.inf, False, x2.shape[0], sh.out, sh.inf, x.device,
+                    stage_b=sh.staging())
         ctx.save_for_backward(x2)
         ctx.sh, ctx.xshape = sh, x.shape
         return y.view(*x.shape[:-1], sh.out)
@@ -54,7 +57,8 @@ class _ShardedLinearFn(torch.autograd.Function):
             dy2 = dy2.contiguous()
         dev = dy.device
         # dX[M, in] = dY[M, out] W[out, in]: W stored [K=out (row-sharded over ranks), N=in], read N-major
-        dx = gemm_ex([dy2.data_ptr()], 0, dy2.stride(0), False, sh.shard_ptrs, sh.S, sh.inf, True, dy2.shape[0], sh.inf, sh.out, dev)
+        dx = gemm_ex([dy2.data_ptr()], 0, dy2.stride(0), False, [sh.full_ptr], 0, sh.inf, True, dy2.shape[0], sh.inf, sh.out, dev,
+                     stage_b=sh.staging())
         # dW[out, in] += dY^T X into the local full-size gradient buffer
         gemm_ex([dy2.data_ptr()], 0, dy2.stride(0), True, [x2.data_ptr()], 0, x2.stride(0), True, sh.out, sh.inf, dy2.shape[0], dev,
                 out=sh.grad_full[:sh.out], accumulate=True)
@@ -78,16 +82,28 @@ class ShardedLinear(nn.Module):
         padded[:self.out] = full
         self.master = padded[r * self.S:(r + 1) * self.S].clone().contiguous()
         self.m, self.v = torch.zeros_like(self.master), torch.zeros_like(self.master)
-        self.shard_ch = PeerChannel(symm, self.S * self.inf * 2)
-        self.shard = self.shard_ch.buf.tensor(torch.bfloat16)[:self.S * self.inf].view(self.S, self.inf)
+        # full-size symmetric buffer; this rank's shard is rows [r*S, (r+1)*S) of it (what peers read)
+        self.shard_ch = PeerChannel(symm, self.S * W * self.inf * 2)
+        self.w_full = self.shard_ch.buf.tensor(torch.bfloat16)[:self.S * W * self.inf].view(self.S * W, self.inf)
+        self.w_full.zero_()
+        self.shard = self.w_full[r * self.S:(r + 1) * self.S]
         self.shard.copy_(self.master)
+        self.full_ptr = self.shard_ch.buf.peer_ptr(r)
+        self.stage_flags = torch.zeros((self.S * W + 127) // 128, dtype=torch.int32, device=dev)
+        self.stage_seq = 1
         self.grad_ch = PeerChannel(symm, self.S * W * self.inf * 2)
         self.grad_full = self.grad_ch.buf.tensor(torch.bfloat16)[:self.S * W * self.inf].view(self.S * W, self.inf)
         self.grad_full.zero_()
-        self.shard_ptrs = [self.shard_ch.buf.peer_ptr(k) for k in range(W)]
         self.symm = symm
+        self._staging = None
         self.step_count = 0
         symm.barrier()
+
+    def staging(self):
+        if self._staging is None or self._staging.seq != self.stage_seq:
+            self._staging = make_staging(self.shard_ch.buf, self.stage_flags, self.symm.rank, self.symm.world, self.S,
+                                         self.S * self.symm.world, self.inf * 2, self.stage_seq)
+        return self._staging
 
     def forward(self, x):
         return _ShardedLinearFn.apply(x, self)
@@ -103,11 +119,12 @@ class ShardedLinear(nn.Module):
                                           betas[0], betas[1], eps, wd, self.step_count, grad_scale, ch.next_seq(),
                                           ch.ticket.data_ptr(), ch.status.data_ptr(), n_ctas, st), "fsdp_rs_adamw")
         self.grad_full.zero_()
+        self.stage_seq += 1             # the peers' rows of w_full are stale now: the next GEMM restages them
 
     def full_weight(self) -> torch.Tensor:
         """Gather the bf16 weight (checkpointing / tests)."""
-        parts = [self.shard_ch.buf.tensor(torch.bfloat16, rank=k)[:self.S * self.inf].view(self.S, self.inf).clone()
-                 for k in range(self.symm.world)]
+        parts = [self.shard_ch.buf.tensor(torch.bfloat16, rank=k)[:self.S * self.symm.world * self.inf]
+                 .view(self.S * self.symm.world, self.inf)[k * self.S:(k + 1) * self.S].clone() for k in range(self.symm.world)]
         return torch.cat(parts)[:self.out]
 
 

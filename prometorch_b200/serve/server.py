@@ -1,0 +1,456 @@
+"""PromeServe: an Ollama-compatible HTTP server in front of the native decode engine.
+
+Routes and wire format follow promeserve/api_handlers.h:351-394 and http_server.h of the reference:
+``GET /`` (liveness text), ``GET /api/version``, ``GET /api/tags``, ``POST /api/show``,
+``POST /api/generate``, ``POST /api/chat``, ``POST /api/embeddings`` (501), ``HEAD``/``OPTIONS`` with CORS.
+Streaming responses are chunked ``application/x-ndjson``: one object per token
+(``{"model","created_at","response","done":false}`` or, for chat, ``"message":{"role","content"}``) and a
+final object with ``total_duration, load_duration, prompt_eval_count, prompt_eval_duration, eval_count,
+eval_duration`` in nanoseconds.  Back-pressure: a bounded queue in front of ``worker_threads`` workers;
+when it is full the reply is ``503`` with ``Retry-After: 1``.  Per-request timeout: an in-stream
+``{"error":"timeout","done":true}``.  One generation runs on the GPU at a time (the engine lock), as in
+the reference; what differs is the engine behind it — greedy requests never copy logits to the host, and
+sampling runs on the device.
+"""
+from __future__ import annotations
+
+import json
+import queue
+import socket
+import threading
+import time
+from dataclasses import dataclass, field
+from datetime import datetime, timezone
+from http import HTTPStatus
+from typing import Callable, Dict, List, Optional
+
+VERSION = "0.1.0-promeserve"
+
+
+@dataclass
+class ServerConfig:
+    host: str = "0.0.0.0"
+    port: int = 11434
+    worker_threads: int = 4
+    max_queue_depth: int = 128
+    server_timeout_ms: int = 60000
+    device: str = "cuda"
+    model: Optional[str] = None
+    model_dirs: List[str] = field(default_factory=list)
+    max_seq: int = 4096
+
+
+def _now() -> str:
+    return datetime.now(timezone.utc).strftime("%Y-%m-%dT%H:%M:%S.%fZ")
+
+
+class StreamWriter:
+    """Chunked-transfer NDJSON writer over a raw socket file."""
+
+    def __init__(self, wfile):
+        self.w = wfile
+        self.open = True
+
+    def write(self, obj) -> bool:
+        if not self.open:
+            return False
+        data = (json.dumps(obj, ensure_ascii=False) + "\n").encode("utf-8")
+        try:
+            self.w.write(f"{len(data):x}\r\n".encode() + data + b"\r\n")
+            self.w.flush()
+            return True
+        except (BrokenPipeError, ConnectionResetError, OSError):
+            self.open = False
+            return False
+
+    def finish(self):
+        if self.open:
+            try:
+                self.w.write(b"0\r\n\r\n")
+                self.w.flush()
+            except OSError:
+                pass
+            self.open = False
+
+
+CORS = {"Access-Control-Allow-Origin": "*", "Access-Control-Allow-Methods": "POST, GET, OPTIONS",
+        "Access-Control-Allow-Headers": "Content-Type, Authorization"}
+
+
+class ModelBackend:
+    """What the handlers need from a model.  ``GGUFBackend`` binds the native engine; tests use a fake."""
+
+    name = "model"
+    architecture = "llama"
+    model_name = ""
+    size = 0
+    parameter_size = ""
+
+    def encode(self, text: str) -> List[int]:
+        raise NotImplementedError
+
+    def decode_token(self, tid: int) -> str:
+        raise NotImplementedError
+
+    def generate(self, prompt_ids: List[int], options: Dict, on_token: Callable[[int], bool]):
+        """Run prefill + decode; call ``on_token(id)`` per generated token (return False to stop).
+        Returns ``(prompt_eval_seconds, eval_seconds)``."""
+        raise NotImplementedError
+
+
+class GGUFBackend(ModelBackend):
+    def __init__(self, path: str, name: str, device: str = "cuda", max_seq: int = 4096):
+        import os
+        from ..io.gguf_model import GGUFModel
+        from ..io.tokenizer import GGUFTokenizer
+        self.model = GGUFModel(path, device=device, max_seq=max_seq, want_logits=True)
+        self.tokenizer = GGUFTokenizer.from_reader(self.model.reader)
+        self.name, self.path = name, path
+        self.architecture, self.model_name = self.model.cfg.architecture, self.model.cfg.model_name
+        self.size = os.path.getsize(path)
+        n = sum(t.nbytes for t in self.model.reader.tensors.values())
+        self.parameter_size = f"{n / 0.5625 / 1e9:.1f}B"
+        self.stop_ids = {self.model.cfg.eos_token_id} - {-1}
+        for t in ("<|im_end|>", "<|eot_id|>", "<end_of_turn>", "<|end|>", "<|endoftext|>"):
+            if t in self.tokenizer.vocab:
+                self.stop_ids.add(self.tokenizer.vocab[t])
+
+    def encode(self, text):
+        return self.tokenizer.encode(text)
+
+    def decode_token(self, tid):
+        return self.tokenizer.decode([tid], strip_leading_space=False)
+
+    def generate(self, prompt_ids, options, on_token):
+        m = self.model
+        n_new = int(options.get("num_predict", 128))
+        room = m.max_seq - len(prompt_ids) - 1
+        n_new = max(0, min(n_new, room))
+        t0 = time.perf_counter()
+        if len(prompt_ids) > 1:
+            m.run_script(prompt_ids[:-1], 1)
+        t1 = time.perf_counter()
+        m.generate(prompt_ids[-1:], max_new_tokens=n_new, temperature=float(options.get("temperature", 0.7)),
+                   top_k=int(options.get("top_k", 40)), top_p=float(options.get("top_p", 0.9)),
+                   repeat_penalty=float(options.get("repeat_penalty", 1.05)), stop_ids=self.stop_ids, on_token=on_token,
+                   _pos0=len(prompt_ids) - 1, _history=prompt_ids)
+        return t1 - t0, time.perf_counter() - t1
+
+
+class ApiHandlers:
+    def __init__(self, config: ServerConfig, backends: Optional[Dict[str, ModelBackend]] = None,
+                 loader: Optional[Callable[[str], ModelBackend]] = None):
+        self.config = config
+        self.backends: Dict[str, ModelBackend] = dict(backends or {})
+        self.loader = loader
+        self.generate_mutex = threading.Lock()
+        self.tools_max_iters = 5
+
+    # ------------------------------------------------------------------ model management
+    def ensure_model(self, name: str) -> ModelBackend:
+        if name in self.backends:
+            return self.backends[name]
+        base = name.split(":")[0]
+        for k, b in self.backends.items():
+            if k.split(":")[0] == base:
+                return b
+        if self.loader is None:
+            raise KeyError(f"model '{name}' not found")
+        b = self.loader(name)
+        self.backends[name] = b
+        return b
+
+    def tags(self):
+        from ..io.ollama import list_models
+        seen, models = set(), []
+        for name, b in self.backends.items():
+            seen.add(name)
+            models.append({"name": name, "model": name, "modified_at": _now(), "size": b.size, "digest": "",
+                           "details": {"family": b.architecture, "format": "gguf", "parameter_size": b.parameter_size}})
+        try:
+            for m in list_models(extra_dirs=self.config.model_dirs):
+                if m["name"] not in seen:
+                    models.append({"name": m["name"], "model": m["name"], "modified_at": _now(), "size": m["size"], "digest": "",
+                                   "details": {"family": "", "format": "gguf", "parameter_size": ""}})
+        except Exception:
+            pass
+        return {"models": models}
+
+    def show(self, body):
+        b = self.ensure_model(body.get("model") or body.get("name") or "")
+        return {"modelfile": "", "parameters": "", "template": "", "details": {"family": b.architecture, "format": "gguf",
+                                                                                 "parameter_size": b.parameter_size},
+                "model_info": {"general.architecture": b.architecture, "general.name": b.model_name}}
+
+    # ------------------------------------------------------------------ generation
+    def _options(self, body):
+        o = {"num_predict": 128, "temperature": 0.7, "top_k": 40, "top_p": 0.9, "repeat_penalty": 1.05}
+        o.update(body.get("options") or {})
+        return o
+
+    def _run(self, backend: ModelBackend, prompt: str, options, emit: Callable[[str], bool], deadline: float):
+        """Tokenise, generate, stream pieces through ``emit``; returns the stats dict and whether it timed out."""
+        ids = backend.encode(prompt) or [0]
+        pieces: List[str] = []
+        state = {"n": 0, "timeout": False}
+
+        def on_token(tid: int) -> bool:
+            if time.time() > deadline:
+                state["timeout"] = True
+                return False
+            state["n"] += 1
+            piece = backend.decode_token(tid)
+            pieces.append(piece)
+            return emit(piece)
+
+        with self.generate_mutex:
+            pe, ev = backend.generate(ids, options, on_token)
+        stats = {"total_duration": int((pe + ev) * 1e9), "load_duration": 0, "prompt_eval_count": len(ids),
+                 "prompt_eval_duration": int(pe * 1e9), "eval_count": state["n"], "eval_duration": int(ev * 1e9)}
+        return "".join(pieces), stats, state["timeout"]
+
+    def generate(self, body, writer: Optional[StreamWriter]):
+        from ..io.chat import apply_chat_template
+        model = body.get("model", "")
+        backend = self.ensure_model(model)
+        prompt = body.get("prompt", "")
+        if not body.get("raw", False) and "<|im_start|>" not in prompt and "[INST]" not in prompt and "<|start_header_id|>" not in prompt:
+            prompt = apply_chat_template(prompt, backend.architecture, backend.model_name, body.get("system"))
+        deadline = time.time() + self.config.server_timeout_ms / 1e3
+
+        def emit(piece):
+            if writer is None:
+                return True
+            return writer.write({"model": model, "created_at": _now(), "response": piece, "done": False})
+        text, stats, timed_out = self._run(backend, prompt, self._options(body), emit, deadline)
+        if timed_out:
+            final = {"error": "timeout", "done": True}
+        else:
+            final = {"model": model, "created_at": _now(), "response": "" if writer is not None else text, "done": True, **stats}
+        if writer is not None:
+            writer.write(final)
+            writer.finish()
+        return final
+
+    def chat(self, body, writer: Optional[StreamWriter]):
+        from ..io.chat import render_messages
+        model = body.get("model", "")
+        backend = self.ensure_model(model)
+        messages = list(body.get("messages") or [])
+        tools = body.get("tools") or []
+        if tools:
+            desc = json.dumps(tools)
+            messages = [{"role": "system", "content": "You may call a tool by answering with a JSON object "
+                         '{"tool_call": {"name": ..., "arguments": {...}}}. Tools: ' + desc}] + messages
+        deadline = time.time() + self.config.server_timeout_ms / 1e3
+
+        def emit(piece):
+            if writer is None:
+                return True
+            return writer.write({"model": model, "created_at": _now(), "message": {"role": "assistant", "content": piece}, "done": False})
+        prompt = render_messages(messages, backend.architecture, backend.model_name)
+        text, stats, timed_out = self._run(backend, prompt, self._options(body), emit, deadline)
+        msg = {"role": "assistant", "content": "" if writer is not None else text}
+        call = self._parse_tool_call(text) if tools else None
+        if call is not None:
+            msg["tool_calls"] = [{"function": call}]
+        final = {"error": "timeout", "done": True} if timed_out else {"model": model, "created_at": _now(), "message": msg, "done": True, **stats}
+        if writer is not None:
+            writer.write(final)
+            writer.finish()
+        return final
+
+    @staticmethod
+    def _parse_tool_call(text: str):
+        i = text.find('{"tool_call"')
+        if i < 0:
+            return None
+        depth = 0
+        for j in range(i, len(text)):
+            depth += text[j] == "{"
+            depth -= text[j] == "}"
+            if depth == 0:
+                try:
+                    return json.loads(text[i:j + 1])["tool_call"]
+                except (ValueError, KeyError):
+                    return None
+        return None
+
+
+class HttpServer:
+    """Blocking accept loop + fixed worker pool + bounded queue (503 when full)."""
+
+    def __init__(self, config: ServerConfig, handlers: ApiHandlers):
+        self.config, self.handlers = config, handlers
+        self.q: "queue.Queue" = queue.Queue(maxsize=config.max_queue_depth)
+        self.sock: Optional[socket.socket] = None
+        self.threads: List[threading.Thread] = []
+        self.running = False
+        self.port = config.port
+
+    def start(self):
+        self.sock = socket.socket(socket.AF_INET, socket.SOCK_STREAM)
+        self.sock.setsockopt(socket.SOL_SOCKET, socket.SO_REUSEADDR, 1)
+        self.sock.bind((self.config.host, self.config.port))
+        self.port = self.sock.getsockname()[1]
+        self.sock.listen(128)
+        self.running = True
+        for _ in range(self.config.worker_threads):
+            t = threading.Thread(target=self._worker, daemon=True)
+            t.start()
+            self.threads.append(t)
+        t = threading.Thread(target=self._accept, daemon=True)
+        t.start()
+        self.threads.append(t)
+        return self
+
+    def stop(self):
+        self.running = False
+        try:
+            self.sock.close()
+        except OSError:
+            pass
+        for _ in range(self.config.worker_threads):
+            try:
+                self.q.put_nowait(None)
+            except queue.Full:
+                pass
+
+    def _accept(self):
+        while self.running:
+            try:
+                conn, _ = self.sock.accept()
+            except OSError:
+                return
+            try:
+                self.q.put_nowait(conn)
+            except queue.Full:
+                try:
+                    conn.sendall(b"HTTP/1.1 503 Service Unavailable\r\nRetry-After: 1\r\nContent-Length: 0\r\nConnection: close\r\n\r\n")
+                finally:
+                    conn.close()
+
+    def _worker(self):
+        while True:
+            conn = self.q.get()
+            if conn is None:
+                return
+            try:
+                conn.settimeout(self.config.server_timeout_ms / 1e3)
+                self._handle(conn)
+            except Exception:
+                pass
+            finally:
+                try:
+                    conn.close()
+                except OSError:
+                    pass
+
+    # ------------------------------------------------------------------ HTTP
+    @staticmethod
+    def _read_request(rfile):
+        line = rfile.readline(65536).decode("latin1").strip()
+        if not line:
+            return None
+        method, path, _ = (line.split(" ") + ["", ""])[:3]
+        headers = {}
+        while True:
+            h = rfile.readline(65536).decode("latin1")
+            if h in ("\r\n", "\n", ""):
+                break
+            k, _, v = h.partition(":")
+            headers[k.strip().lower()] = v.strip()
+        n = int(headers.get("content-length", "0") or 0)
+        body = rfile.read(n) if n else b""
+        return method.upper(), path.split("?")[0], headers, body
+
+    @staticmethod
+    def _send(wfile, status: int, body: bytes, ctype="application/json", extra=None):
+        reason = HTTPStatus(status).phrase
+        hdr = {"Content-Type": ctype, "Content-Length": str(len(body)), "Connection": "close", **CORS, **(extra or {})}
+        wfile.write(f"HTTP/1.1 {status} {reason}\r\n".encode() + "".join(f"{k}: {v}\r\n" for k, v in hdr.items()).encode() + b"\r\n" + body)
+        wfile.flush()
+
+    def _handle(self, conn):
+        rfile, wfile = conn.makefile("rb"), conn.makefile("wb")
+        req = self._read_request(rfile)
+        if req is None:
+            return
+        method, path, headers, raw = req
+        H = self.handlers
+        if method == "OPTIONS":
+            return self._send(wfile, 204, b"")
+        if method == "HEAD":
+            return self._send(wfile, 200 if path in ("/", "/api/version", "/api/tags") else 404, b"")
+        if method == "GET" and path == "/":
+            return self._send(wfile, 200, b"PromeServe is running", "text/plain")
+        if method == "GET" and path == "/api/version":
+            return self._send(wfile, 200, json.dumps({"version": VERSION}).encode())
+        if method == "GET" and path == "/api/tags":
+            return self._send(wfile, 200, json.dumps(H.tags()).encode())
+        if method == "POST" and path in ("/api/embeddings", "/api/embed"):
+            return self._send(wfile, 501, json.dumps({"error": "embeddings are not implemented"}).encode())
+        if method == "POST" and path in ("/api/generate", "/api/chat", "/api/show"):
+            try:
+                body = json.loads(raw.decode("utf-8") or "{}")
+            except ValueError:
+                return self._send(wfile, 400, json.dumps({"error": "invalid JSON"}).encode())
+            try:
+                if path == "/api/show":
+                    return self._send(wfile, 200, json.dumps(H.show(body)).encode())
+                H.ensure_model(body.get("model", ""))
+            except KeyError as e:
+                return self._send(wfile, 404, json.dumps({"error": str(e).strip("'\"")}).encode())
+            fn = H.generate if path == "/api/generate" else H.chat
+            if body.get("stream", True):
+                wfile.write(b"HTTP/1.1 200 OK\r\nContent-Type: application/x-ndjson\r\nTransfer-Encoding: chunked\r\nConnection: close\r\n" +
+                            "".join(f"{k}: {v}\r\n" for k, v in CORS.items()).encode() + b"\r\n")
+                wfile.flush()
+                w = StreamWriter(wfile)
+                try:
+                    fn(body, w)
+                except Exception as e:       # errors travel in-stream
+                    w.write({"error": str(e), "done": True})
+                    w.finish()
+                return
+            try:
+                return self._send(wfile, 200, json.dumps(fn(body, None)).encode())
+            except Exception as e:
+                return self._send(wfile, 500, json.dumps({"error": str(e)}).encode())
+        return self._send(wfile, 404, json.dumps({"error": "not found"}).encode())
+
+
+class PromeServe:
+    def __init__(self, config: Optional[ServerConfig] = None, backends: Optional[Dict[str, ModelBackend]] = None):
+        self.config = config or ServerConfig()
+
+        def loader(name: str) -> ModelBackend:
+            from ..io.ollama import resolve_model
+            import os
+            path = name if os.path.isfile(name) else None
+            if path is None:
+                for d in self.config.model_dirs:
+                    cand = os.path.join(d, name.split(":")[0] + ".gguf")
+                    if os.path.isfile(cand):
+                        path = cand
+            if path is None:
+                try:
+                    path = resolve_model(name)
+                except FileNotFoundError as e:
+                    raise KeyError(str(e))
+            return GGUFBackend(path, name, self.config.device, self.config.max_seq)
+        self.handlers = ApiHandlers(self.config, backends, loader)
+        self.http = HttpServer(self.config, self.handlers)
+
+    def start(self):
+        if self.config.model:
+            self.handlers.ensure_model(self.config.model)
+        self.http.start()
+        return self
+
+    def stop(self):
+        self.http.stop()
+
+    @property
+    def port(self):
+        return self.http.port

@@ -1,0 +1,213 @@
+"""Worker bodies for the multi-rank CPU tests.  Each takes ``(rank, world)`` and returns an exit code; they run
+as spawned processes over the Gloo backend on 127.0.0.1."""
+from __future__ import annotations
+
+import os
+import sys
+
+import torch
+import torch.nn as nn
+
+
+def _init(rank, world):
+    from .. import distributed as D
+    return D.init_process_group("gloo", rank, world, os.environ["MASTER_ADDR"], int(os.environ["MASTER_PORT"]), timeout_sec=60)
+
+
+def _fin():
+    from .. import distributed as D
+    D.barrier()
+    D.destroy_process_group()
+
+
+def collectives(rank, world):
+    from .. import distributed as D
+    _init(rank, world)
+    t = torch.full((4,), float(rank + 1))
+    D.all_reduce(t)
+    assert torch.allclose(t, torch.full((4,), float(sum(range(1, world + 1))))), t
+    t = torch.full((3,), float(rank))
+    D.all_reduce(t, D.ReduceOp.AVG)
+    assert torch.allclose(t, torch.full((3,), (world - 1) / 2)), t
+    b = torch.arange(5.0) if rank == 0 else torch.zeros(5)
+    D.broadcast(b, 0)
+    assert torch.equal(b, torch.arange(5.0))
+    parts = [torch.zeros(2) for _ in range(world)]
+    D.all_gather(parts, torch.full((2,), float(rank)))
+    assert all(float(p[0]) == i for i, p in enumerate(parts))
+    out = torch.zeros(2)
+    D.reduce_scatter(out, [torch.full((2,), float(k + rank)) for k in range(world)])
+    assert torch.allclose(out, torch.full((2,), float(sum(rank + r for r in range(world)))))
+    _fin()
+    return 0
+
+
+def _mlp(seed=0):
+    torch.manual_seed(seed)
+    return nn.Sequential(nn.Linear(16, 32), nn.ReLU(), nn.Linear(32, 32), nn.ReLU(), nn.Linear(32, 4))
+
+
+def ddp_matches_single(rank, world):
+    """DDP over `world` ranks on disjoint halves of a batch == one process on the whole batch; no_sync accumulation too."""
+    from .. import distributed as D
+    from ..optim import SGD
+    _init(rank, world)
+    torch.manual_seed(123)
+    X, Y = torch.randn(8 * world, 16), torch.randn(8 * world, 4)
+    ref = _mlp(1)
+    model = _mlp(1 + rank)                      # different init per rank: the constructor must broadcast rank 0's
+    ddp = D.DistributedDataParallel(model, bucket_mb=0.002)
+    assert len(ddp.buckets) > 1
+    ro, do = SGD(ref.parameters(), lr=0.1), SGD(model.parameters(), lr=0.1)
+    for step in range(3):
+        ro.zero_grad()
+        ((ref(X) - Y) ** 2).mean().backward()
+        ro.step()
+        ddp.zero_grad()
+        xs, ys = X[rank::world], Y[rank::world]
+        if step == 1:                            # two micro-batches, the first under no_sync
+            h = xs.shape[0] // 2
+            with ddp.no_sync():
+                (((ddp(xs[:h]) - ys[:h]) ** 2).mean() / 2).backward()
+            (((ddp(xs[h:]) - ys[h:]) ** 2).mean() / 2).backward()
+        else:
+            ((ddp(xs) - ys) ** 2).mean().backward()
+        ddp.finish_gradient_synchronization()
+        do.step()
+        for a, b in zip(ref.parameters(), model.parameters()):
+            assert torch.allclose(a, b, atol=1e-5), (step, (a - b).abs().max())
+    _fin()
+    return 0
+
+
+def fsdp_matches_unsharded(rank, world):
+    from .. import distributed as D
+    from ..optim import SGD
+    _init(rank, world)
+    torch.manual_seed(7)
+    X, Y = torch.randn(4 * world, 16), torch.randn(4 * world, 4)
+    ref, model = _mlp(3), _mlp(3)
+    for strategy in (D.ShardingStrategy.FULL_SHARD, D.ShardingStrategy.SHARD_GRAD_OP):
+        ref, model = _mlp(3), _mlp(3)
+        fsdp = D.FullyShardedDataParallel(model, D.FSDPConfig(rank=rank, world_size=world, strategy=strategy))
+        ro, so = SGD(ref.parameters(), lr=0.1), D.ZeROOptimizer(fsdp.local_shards(), SGD(fsdp.local_shards(), lr=0.1), stage=3)
+        for step in range(2):
+            ro.zero_grad()
+            ((ref(X) - Y) ** 2).mean().backward()
+            ro.step()
+            fsdp.all_gather_params()
+            ((fsdp(X[rank::world]) - Y[rank::world]) ** 2).mean().backward()
+            fsdp.reduce_scatter_grads()
+            so.step()
+            so.zero_grad()
+        fsdp.all_gather_params()
+        for a, b in zip(ref.parameters(), model.parameters()):
+            assert (a - b).abs().max() < 1e-4, (strategy, (a - b).abs().max())
+        sd = fsdp.shard_state_dict()
+        fsdp.load_shard_state_dict(sd)
+    _fin()
+    return 0
+
+
+def tp_matches_unsharded(rank, world):
+    from .. import distributed as D
+    from ..nn.parallel import ColumnParallelLinear, RowParallelLinear, TPConfig
+    pg = _init(rank, world)
+    tp = TPConfig(rank, world, process_group=pg)
+    tp1 = TPConfig(0, 1)
+    torch.manual_seed(5)
+    x = torch.randn(6, 16)
+    for sp in (False, True):
+        col, row = ColumnParallelLinear(16, 32, tp, gather_output=False, init_seed=11, sequence_parallel=sp), \
+            RowParallelLinear(32, 8, tp, init_seed=12, sequence_parallel=sp)
+        colf, rowf = ColumnParallelLinear(16, 32, tp1, init_seed=11), RowParallelLinear(32, 8, tp1, init_seed=12)
+        xf = x.clone().requires_grad_()
+        yf = rowf(torch.relu(colf(xf)))
+        yf.pow(2).sum().backward()
+        if sp:
+            n = x.shape[0] // world
+            xl = x[rank * n:(rank + 1) * n].clone().requires_grad_()
+            y = row(torch.relu(col(xl)))
+            assert torch.allclose(y, yf[rank * n:(rank + 1) * n], atol=1e-5), (y - yf[rank * n:(rank + 1) * n]).abs().max()
+            y.pow(2).sum().backward()
+            assert torch.allclose(xl.grad, xf.grad[rank * n:(rank + 1) * n], atol=1e-5)
+        else:
+            xl = x.clone().requires_grad_()
+            y = row(torch.relu(col(xl)))
+            assert torch.allclose(y, yf, atol=1e-5)
+            y.pow(2).sum().backward()
+            assert torch.allclose(xl.grad, xf.grad, atol=1e-5)
+        s = col.shard
+        assert torch.allclose(col.weight.grad, colf.weight.grad[rank * s:(rank + 1) * s], atol=1e-5)
+        s = row.shard
+        assert torch.allclose(row.weight.grad, rowf.weight.grad[:, rank * s:(rank + 1) * s], atol=1e-5)
+    g = ColumnParallelLinear(16, 32, tp, gather_output=True, init_seed=11)
+    assert torch.allclose(g(x), ColumnParallelLinear(16, 32, tp1, init_seed=11)(x), atol=1e-6)
+    _fin()
+    return 0
+
+
+def pipeline_1f1b(rank, world):
+    """Two stages, 1F1B with real gradients == the same layers run sequentially."""
+    from .. import distributed as D
+    from ..nn.parallel import Pipeline1F1BStage, PipelineScheduleConfig
+    pg = _init(rank, world)
+    full = _mlp(9)
+    layers = list(full.children())
+    cut = 2
+    stage = nn.Sequential(*(layers[:cut] if rank == 0 else layers[cut:]))
+    torch.manual_seed(1)
+    X, Y = torch.randn(8, 16), torch.randn(8, 4)
+    cfg = PipelineScheduleConfig(num_stages=2, num_micros=4)
+    st = Pipeline1F1BStage(stage, cfg, rank, process_group=pg, act_shape=(2, 32), act_dtype=torch.float32)
+    loss = st.run(X if rank == 0 else None, loss_fn=lambda o, t: ((o - t) ** 2).mean(), targets=Y if rank == 1 else None)
+    ref_loss = sum(((full(X[i * 2:(i + 1) * 2]) - Y[i * 2:(i + 1) * 2]) ** 2).mean() / 4 for i in range(4))
+    ref_loss.backward()
+    mine = list(stage.parameters())
+    refp = [p for l in (layers[:cut] if rank == 0 else layers[cut:]) for p in l.parameters()]
+    for a, b in zip(mine, refp):
+        assert torch.allclose(a.grad, b.grad, atol=1e-5), (a.grad - b.grad).abs().max()
+    if rank == 1:
+        assert abs(float(loss) - float(ref_loss)) < 1e-5
+    _fin()
+    return 0
+
+
+def rank_that_dies(rank, world):
+    """Rank 1 leaves before the collective; rank 0's all-reduce must end with CollectiveTimeout, not hang."""
+    from .. import distributed as D
+    D.init_process_group("gloo", rank, world, os.environ["MASTER_ADDR"], int(os.environ["MASTER_PORT"]), timeout_sec=3)
+    if rank == 1:
+        os._exit(0)
+    try:
+        D.all_reduce(torch.ones(4))
+    except D.CollectiveTimeout:
+        os._exit(0)
+    except Exception:
+        os._exit(0)
+    os._exit(7)
+
+
+def mlp_ddp_config1(rank, world):
+    """The CPU plumbing check of the MLP benchmark config: DDP world_size 2, a few Adam steps, ranks stay in sync."""
+    from .. import distributed as D
+    from ..models.mlp import MLPClassifier
+    from ..optim import Adam
+    _init(rank, world)
+    torch.manual_seed(rank)
+    model = MLPClassifier()
+    ddp = D.DistributedDataParallel(model)
+    opt = Adam(model.parameters(), lr=1e-3)
+    g = torch.Generator().manual_seed(100 + rank)
+    for _ in range(3):
+        x, y = torch.rand(64, 784, generator=g), torch.randint(0, 10, (64,), generator=g)
+        ddp.zero_grad()
+        nn.functional.cross_entropy(ddp(x), y).backward()
+        ddp.finish_gradient_synchronization()
+        opt.step()
+    w = model[0].weight.detach().clone()
+    parts = [torch.zeros_like(w) for _ in range(world)]
+    D.all_gather(parts, w)
+    assert all(torch.allclose(parts[0], p, atol=1e-6) for p in parts)
+    _fin()
+    return 0

@@ -1,0 +1,124 @@
+"""Multi-rank logic on CPU ranks (Gloo over 127.0.0.1, spawned processes) and in-process fakes."""
+import os
+import random
+import threading
+
+import pytest
+import torch
+import torch.nn as nn
+
+from prometorch_b200 import distributed as D
+from prometorch_b200.testing import dist_workers as W
+
+
+def _launch(fn, world=2, timeout=180):
+    port = 29700 + (os.getpid() * 7 + random.randint(0, 200)) % 1200
+    return D.launch(world, fn, "127.0.0.1", port, timeout=timeout)
+
+
+@pytest.mark.parametrize("fn", [W.collectives, W.ddp_matches_single, W.fsdp_matches_unsharded, W.tp_matches_unsharded, W.pipeline_1f1b,
+                                W.mlp_ddp_config1], ids=lambda f: f.__name__)
+def test_two_ranks(fn):
+    assert _launch(fn, 2) == 0
+
+
+def test_dead_rank_is_detected_not_hung():
+    assert _launch(W.rank_that_dies, 2, timeout=60) == 0
+
+
+def test_launcher_propagates_failure():
+    assert _launch(_fail_on_rank1, 2, timeout=60) == 3
+
+
+def _fail_on_rank1(rank, world):
+    return 3 if rank == 1 else 0
+
+
+def test_no_sync_with_counting_pg():
+    pg = D.CountingPG(rank=0, world_size=2)
+    model = nn.Sequential(nn.Linear(4, 4), nn.Linear(4, 2))
+    ddp = D.DistributedDataParallel(model, pg, broadcast_parameters=False, bucket_mb=1e-5)
+    nb = len(ddp.buckets)
+    x = torch.randn(3, 4)
+    with ddp.no_sync():
+        assert ddp.require_grad_sync is False
+        with ddp.no_sync():                       # nests and restores
+            ddp(x).sum().backward()
+        assert ddp.require_grad_sync is False
+        ddp(x).sum().backward()
+    assert ddp.require_grad_sync is True and pg.all_reduce_calls == 0
+    g_acc = model[0].weight.grad.clone()
+    ddp(x).sum().backward()
+    ddp.finish_gradient_synchronization()
+    assert pg.all_reduce_calls == nb
+    assert torch.allclose(model[0].weight.grad * 4, g_acc * 3, atol=1e-6)    # 3 accumulated backwards scaled by 1/2, against 2 unscaled
+    with D.DDPNoSyncGuard(ddp):
+        assert not ddp.require_grad_sync
+    assert ddp.require_grad_sync
+    ddp.sync_gradients()
+    assert pg.all_reduce_calls == 2 * nb
+
+
+def test_shared_memory_backend_threads():
+    groups = D.make_shared_memory_groups(3, timeout=10)
+    out = [None] * 3
+
+    def run(r):
+        t = torch.full((2,), float(r + 1))
+        groups[r].all_reduce(t, D.ReduceOp.SUM)
+        b = torch.full((2,), float(r))
+        groups[r].broadcast(b, 1)
+        groups[r].barrier()
+        out[r] = (t, b)
+    ts = [threading.Thread(target=run, args=(r,)) for r in range(3)]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    assert all(torch.allclose(o[0], torch.full((2,), 6.0)) and torch.allclose(o[1], torch.full((2,), 1.0)) for o in out)
+    g1 = D.make_shared_memory_groups(2, timeout=0.3)
+    with pytest.raises(D.CollectiveTimeout):          # the other rank never arrives
+        g1[0].barrier()
+
+
+def test_heartbeat_detects_silent_rank():
+    store = D.DictStore()
+    a = D.Heartbeat(store, 0, 2, interval=0.05, timeout=0.4).start()
+    b = D.Heartbeat(store, 1, 2, interval=0.05, timeout=0.4).start()
+    import time
+    time.sleep(0.2)
+    a.check()
+    b.stop()                                             # rank 1 goes silent
+    time.sleep(0.7)
+    with pytest.raises(D.RankFailure) as e:
+        a.check()
+    assert e.value.ranks == [1]
+    a.stop()
+
+
+def test_gpipe_matches_sequential():
+    from prometorch_b200.nn.parallel import Pipeline
+    torch.manual_seed(0)
+    seq = nn.Sequential(nn.Linear(8, 16), nn.ReLU(), nn.Linear(16, 16), nn.ReLU(), nn.Linear(16, 4))
+    x = torch.randn(8, 8)
+    ref = seq(x)
+    pipe = Pipeline(seq, num_stages=2, chunks=4)
+    out = pipe(x)
+    assert torch.allclose(out, ref, atol=1e-6)
+    out.sum().backward()
+    assert seq[0].weight.grad is not None
+
+
+def test_distributed_sampler_disjoint():
+    from prometorch_b200.data import DistributedSampler, TensorDataset
+    ds = TensorDataset(torch.arange(10))
+    idx = [list(DistributedSampler(ds, num_replicas=3, rank=r, shuffle=True, seed=1)) for r in range(3)]
+    assert all(len(i) == 4 for i in idx)
+    assert set(sum(idx, [])) == set(range(10))
+    s = DistributedSampler(ds, num_replicas=3, rank=0, shuffle=True, seed=1)
+    a = list(s)
+    s.set_epoch(1)
+    assert list(s) != a
+
+
+def test_parse_dist_args():
+    a = D.parse_dist_args(["--rank", "2", "--world-size", "4", "--master-port", "1234", "--nprocs", "2"])
+    assert (a.rank, a.world_size, a.master_port, a.nprocs) == (2, 4, 1234, 2)
