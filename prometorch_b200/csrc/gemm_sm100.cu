@@ -53,8 +53,10 @@ static int launch(const Operand& ta, const Operand& tb, const Params& p, int n_s
     }
     Params q = p;
     int n_st = (q.stA.seq || q.stB.seq) ? std::min(16, std::max(1, n_sm / 8)) : 0;
-    q.gemm_ctas = std::max(1, std::min(p.tiles_m * p.tiles_n, n_sm - n_st));
-    kern<<<q.gemm_ctas + n_st, THREADS, smem, st>>>(ta, tb, q);
+    // the stagers and the tile CTAs wait on one another, so the whole grid must be resident at once: one CTA per SM
+    const int gemm_ctas = std::max(1, std::min(p.tiles_m * p.tiles_n, n_sm - n_st));
+    q.stager_ctas = n_st;
+    kern<<<gemm_ctas + n_st, THREADS, smem, st>>>(ta, tb, q);
     PTB_CUDA_OK(cudaGetLastError());
     return 0;
 }

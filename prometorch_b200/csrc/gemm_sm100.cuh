@@ -66,7 +66,7 @@ struct Params {
     // added (fp32 atomics over NVLink) into that rank's buffer c_peer[r] of shape [out_shard_rows, ldc]
     float* c_peer[MAX_SHARDS];
     int out_shard_rows;
-    int gemm_ctas;          // CTAs [0, gemm_ctas) compute tiles; CTAs beyond it are stagers
+    int stager_ctas;        // CTAs [0, stager_ctas) are stagers (lowest indices: dispatched first); the rest compute tiles
     Staging stA, stB;
 };
 
@@ -223,12 +223,12 @@ gemm_bf16_kernel(const __grid_constant__ Operand opA, const __grid_constant__ Op
         prefetch_tmap(&opA.map[0]);
         prefetch_tmap(&opB.map[0]);
     }
-    const int n_gemm = P.gemm_ctas;
-    if ((int)blockIdx.x >= n_gemm) {
+    const int n_gemm = (int)gridDim.x - P.stager_ctas;
+    const int cta = (int)blockIdx.x - P.stager_ctas;
+    if (cta < 0) {
         // ---------------------------------------------------------------------- stager CTA (no TMEM, no tiles)
-        const int stager = blockIdx.x - n_gemm, n_st = gridDim.x - n_gemm;
-        run_stager(P.stA, stager, n_st);
-        run_stager(P.stB, stager, n_st);
+        run_stager(P.stA, blockIdx.x, P.stager_ctas);
+        run_stager(P.stB, blockIdx.x, P.stager_ctas);
         return;
     }
     if (warp == 1) {
@@ -245,7 +245,10 @@ gemm_bf16_kernel(const __grid_constant__ Operand opA, const __grid_constant__ Op
         if (lane == 0) {
             int it = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < num_tiles && ok; t += n_gemm) {
+            // an MN-major staged operand is walked along K in full by every tile: once the first tile has
+            // seen all of its blocks staged, later tiles need not look at the flags again
+            bool first_tile = true;
+            for (int t = cta; t < num_tiles && ok; t += n_gemm, first_tile = false) {
                 const int m0 = (t % P.tiles_m) * BM, n0 = (t / P.tiles_m) * BN;
                 for (int kb = 0; kb < kblocks && ok; ++kb, ++it) {
                     const int s = it % STAGES;
@@ -255,8 +258,8 @@ gemm_bf16_kernel(const __grid_constant__ Operand opA, const __grid_constant__ Op
                     uint8_t* sb = sa + S::A_BYTES;
                     mbar_expect_tx(&full[s], S::STAGE_BYTES);
                     // rows being staged from peers must have landed before the TMA engine reads them
-                    if (kb == 0 || A_MN) ok = wait_staged(P.stA, A_MN ? kb * BK : m0, A_MN ? BK : BM, P.status);
-                    if (ok && (kb == 0 || B_MN)) ok = wait_staged(P.stB, B_MN ? kb * BK : n0, B_MN ? BK : BN, P.status);
+                    if (A_MN ? first_tile : kb == 0) ok = wait_staged(P.stA, A_MN ? kb * BK : m0, A_MN ? BK : BM, P.status);
+                    if (ok && (B_MN ? first_tile : kb == 0)) ok = wait_staged(P.stB, B_MN ? kb * BK : n0, B_MN ? BK : BN, P.status);
                     if (!ok) break;
                     // the box's row coordinate selects the shard (and so the GPU) it is fetched from
                     if (A_MN) {
@@ -283,7 +286,7 @@ gemm_bf16_kernel(const __grid_constant__ Operand opA, const __grid_constant__ Op
             constexpr uint32_t idesc = instr_desc(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
             int it = 0, tl = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < num_tiles && ok; t += n_gemm, ++tl) {
+            for (int t = cta; t < num_tiles && ok; t += n_gemm, ++tl) {
                 const int b = tl & 1;
                 if (tl >= 2) ok = mbar_wait(&acc_empty[b], (uint32_t)(((tl >> 1) - 1) & 1), P.status);
                 if (!ok) break;
@@ -313,7 +316,7 @@ gemm_bf16_kernel(const __grid_constant__ Operand opA, const __grid_constant__ Op
         const int q = warp & 3;                     // TMEM lane quarter this warp may read
         int tl = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < num_tiles && ok; t += n_gemm, ++tl) {
+        for (int t = cta; t < num_tiles && ok; t += n_gemm, ++tl) {
             const int b = tl & 1;
             const int m0 = (t % P.tiles_m) * BM, n0 = (t / P.tiles_m) * BN;
             ok = mbar_wait(&acc_full[b], (uint32_t)((tl >> 1) & 1), P.status);

@@ -1,0 +1,44 @@
+"""Fused compute+collective training paths on 2 GPUs (staged GEMM, DDP bucket kernel, fused FSDP, sequence-parallel
+TP), and the bounded wait of the flag barrier on one GPU."""
+import ctypes as C
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.multigpu
+@pytest.mark.parametrize("case", ["staged_gemm", "ddp_fused", "fsdp_fused", "tp_sp_fused"])
+def test_fused_multi_gpu(case):
+    world = 2
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "multi_gpu_worker.py")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+           "127.0.0.1", "--master-port", str(29900 + os.getpid() % 90), worker, case]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0 and "MULTI_GPU_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+def test_flag_barrier_wait_runs_out():
+    """A barrier whose peer never arrives (a flag nothing sets) returns with a timeout status; the context stays usable."""
+    from prometorch_b200 import _native as N
+    from prometorch_b200.distributed import ddp as _ddp  # noqa: F401  (registers the prototypes)
+    dev = torch.device("cuda", 0)
+    mine = torch.zeros(16, dtype=torch.int32, device=dev)
+    ghost = torch.zeros(16, dtype=torch.int32, device=dev)          # stands for a peer that never runs
+    flags = (C.c_void_p * 2)(mine.data_ptr(), ghost.data_ptr())
+    ticket = torch.zeros(1, dtype=torch.int32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    st = torch.cuda.current_stream(dev).cuda_stream
+    N.check(N.lib().ptb_peer_barrier(flags, 0, 2, 1, ticket.data_ptr(), status.data_ptr(), st), "peer_barrier")
+    torch.cuda.synchronize()
+    assert int(status) == 2                                          # flag timeout
+    assert int(ghost[0]) == 1                                        # it did signal the peer before giving up
+    x = torch.ones(4, device=dev) * 2                                # the context still works
+    assert float(x.sum()) == 8.0
