@@ -413,3 +413,45 @@ PTB_API int ptb_xent(const void* logits, const long long* target, float* loss, f
     PTB_CUDA_OK(cudaGetLastError());
     return 0;
 }
+
+// ------------------------------------------------------------------------------------------ no-allocation variant
+// RMSNorm backward with its scratch in the library image instead of a caller's buffer (see no_alloc.h).
+// Host programs without an allocator of their own, and loops that must not touch the device allocator
+// while they run, call this one; the partial sums land in `g_rms_static_scratch`, shared by every call
+// on the device.
+#include "no_alloc.h"
+#include <mutex>
+
+static __device__ __align__(256) float g_rms_static_scratch[PTB_RMS_STATIC_SCRATCH_FLOATS];
+
+PTB_API int ptb_rmsnorm_bwd_static(const void* x, const void* w, const void* dy, const float* rstd, void* dx, void* dw, int n_ctas,
+                                   long long rows, int H, const void* dresid, int bf16, cudaStream_t st) {
+    constexpr int MAX_DEV = 64;
+    static float* scratch_of[MAX_DEV] = {nullptr};
+    static std::mutex mu;
+    if (H % 8 || H <= 0 || rms_threads(H) > 1024) { ptb_set_error("rmsnorm: hidden size %d not supported", H); return -1; }
+    if (n_ctas <= 0) { ptb_set_error("rmsnorm_bwd_static: n_ctas must be positive"); return -1; }
+    if ((long long)n_ctas * H > (long long)PTB_RMS_STATIC_SCRATCH_FLOATS) {
+        ptb_set_error("rmsnorm_bwd_static: n_ctas * H = %lld exceeds the static scratch of %d floats; use fewer CTAs or ptb_rmsnorm_bwd",
+                      (long long)n_ctas * H, (int)PTB_RMS_STATIC_SCRATCH_FLOATS);
+        return -1;
+    }
+    if (rows == 0) return 0;
+    int dev = 0;
+    PTB_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= MAX_DEV) { ptb_set_error("rmsnorm_bwd_static: device index %d out of range", dev); return -1; }
+    float* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(mu);
+        if (!scratch_of[dev]) {                       // once per device: where does this device keep the array?
+            float* p = nullptr;
+            PTB_CUDA_OK(cudaGetSymbolAddress((void**)&p, g_rms_static_scratch));
+            scratch_of[dev] = p;
+        }
+        scratch = scratch_of[dev];
+    }
+    PTB_DISPATCH_T(bf16, rmsnorm_bwd_kernel<T><<<n_ctas, rms_threads(H), 0, st>>>((const T*)x, (const T*)w, (const T*)dy, rstd, (T*)dx, scratch, (int)rows, H, (const T*)dresid);
+                   colsum_kernel<T><<<(H + 255) / 256, 256, 0, st>>>(scratch, n_ctas, H, (T*)dw));
+    PTB_CUDA_OK(cudaGetLastError());
+    return 0;
+}
