@@ -9,6 +9,7 @@
 // 8-byte device-to-host copy per token.  Here a layer is five kernels, the
 // arg-max is the lm_head epilogue and a run of tokens needs no host round trip.
 #include "decode_kernels.cuh"
+#include "decode_mega.cuh"
 #include <stdarg.h>
 #include <stdlib.h>
 #include <string.h>
@@ -306,6 +307,14 @@ struct Engine {
     bool use_pdl = true;
     unsigned long long* trace = nullptr;   // PTB_TRACE=1: [kernels per token][8] phase stamps of the last token
     long launches_per_token = 0;
+    // persistent single-launch path (one GPU): op list on the device, arrival counter, launch geometry
+    bool mega = false;
+    MegaParams mp;
+    MegaOp* d_ops = nullptr;
+    unsigned* d_bar = nullptr;
+    size_t mega_smem = 0;
+    int mega_warps = 15;
+    int n_ops = 0;
 };
 
 static int engine_alloc(Engine* e) {
@@ -339,8 +348,8 @@ static int engine_alloc(Engine* e) {
     PTB_CUDA_OK(cudaMalloc(&e->status, sizeof(int)));
     PTB_CUDA_OK(cudaMemset(e->status, 0, sizeof(int)));
     if (env_int("PTB_TRACE", 0)) {
-        PTB_CUDA_OK(cudaMalloc(&e->trace, 8 * sizeof(unsigned long long) * (5 * m.n_layers + 2)));
-        PTB_CUDA_OK(cudaMemset(e->trace, 0, 8 * sizeof(unsigned long long) * (5 * m.n_layers + 2)));
+        PTB_CUDA_OK(cudaMalloc(&e->trace, 8 * sizeof(unsigned long long) * (5 * m.n_layers + 4)));
+        PTB_CUDA_OK(cudaMemset(e->trace, 0, 8 * sizeof(unsigned long long) * (5 * m.n_layers + 4)));
     }
     PTB_CUDA_OK(cudaMallocHost(&e->h_pinned, sizeof(int) * 16));
     memset(e->h_pinned, 0, sizeof(int) * 16);
@@ -426,6 +435,184 @@ static int engine_plan(Engine* e) {
     return 0;
 }
 
+
+// ------------------------------------------------------------------------------------------ persistent single-launch path
+// CTA split and rows-per-tile of one GEMV op of the persistent kernel (same rules as plan_gemv, one CTA per SM).
+static int plan_mega_gemv(MegaOp& op, int njobs, int K, int n_ctas, int warps, int slot_bytes, int* acc_floats) {
+    op.kind = MK_GEMV;
+    op.njobs = njobs;
+    op.K = K;
+    if (K % 256 || K > 10240) { ptb_set_error("persistent decode: input length %d must be a multiple of 256 and at most 10240", K); return -1; }
+    double total = 0;
+    for (int i = 0; i < njobs; ++i) total += (double)op.job[i].N * op.job[i].nblk * (op.job[i].qtype == QT_Q4K ? 144 : 210) * (op.job[i].w2 ? 2 : 1);
+    int left = n_ctas, begin = 0;
+    double left_bytes = total;
+    for (int i = 0; i < njobs; ++i) {
+        GemvJob& j = op.job[i];
+        const double b = (double)j.N * j.nblk * (j.qtype == QT_Q4K ? 144 : 210) * (j.w2 ? 2 : 1);
+        int c = (i == njobs - 1) ? left : (int)(left * b / left_bytes + 0.5);
+        c = std::max(1, std::min(c, left - (njobs - 1 - i)));
+        c = std::min(c, j.N);
+        j.cta_begin = begin;
+        j.cta_count = c;
+        begin += c;
+        left -= c;
+        left_bytes -= b;
+    }
+    for (int i = 0; i < njobs; ++i) {
+        GemvJob& j = op.job[i];
+        const int pairs = j.w2 ? 2 : 1;
+        const int nb = j.seg_base + (j.seg_rem ? 1 : 0);
+        const int sz = seg_bytes(j.qtype, nb);
+        const int rows_cta = (j.N + j.cta_count - 1) / j.cta_count;
+        double best = 1e30;
+        int bestRW = 0;
+        for (int RW = 8; RW >= 1; RW >>= 1) {
+            if (RW * sz * pairs > slot_bytes) continue;
+            const int gprw = 8 / RW;
+            const int items = ((rows_cta + RW - 1) / RW) * j.KS;
+            const int rounds = (items + warps - 1) / warps;
+            const double cost = rounds * ((double)((nb + gprw - 1) / gprw) * pairs + 1.0);
+            if (cost < best - 1e-9) { best = cost; bestRW = RW; }
+        }
+        if (!bestRW) { ptb_set_error("persistent decode: a %d-byte segment does not fit a %d-byte ring slot", sz * pairs, slot_bytes); return -1; }
+        j.RW = bestRW;
+        if (j.KS > 1) *acc_floats = std::max(*acc_floats, rows_cta * j.KS * pairs);
+    }
+    return 0;
+}
+
+template <int NCONS>
+static cudaError_t launch_mega_n(const MegaParams& p, int grid, size_t smem, cudaStream_t st) {
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(decode_mega_kernel<NCONS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        attr_done = true;
+    }
+    decode_mega_kernel<NCONS><<<grid, (NCONS + 1) * 32, smem, st>>>(p);
+    return cudaGetLastError();
+}
+static cudaError_t launch_mega(const MegaParams& p, int warps, int grid, size_t smem, cudaStream_t st) {
+    // consumer warps + the producer warp fill whole register-allocation groups of four warps: 11+1 or 15+1
+    switch (warps) {
+        case 11: return launch_mega_n<11>(p, grid, smem, st);
+        default: return launch_mega_n<15>(p, grid, smem, st);
+    }
+}
+
+static size_t mega_attn_smem(int group) {
+    switch (group) {
+        case 1: return sizeof(MegaAttnShared<1>);
+        case 2: return sizeof(MegaAttnShared<2>);
+        case 4: return sizeof(MegaAttnShared<4>);
+        default: return sizeof(MegaAttnShared<8>);
+    }
+}
+
+// Build the op list of one token and the shared-memory layout; upload the list.
+static int engine_plan_mega(Engine* e) {
+    const PtbModelDesc& m = e->m;
+    const int qd = m.n_heads * m.head_dim, kvd = m.n_kv_heads * m.head_dim;
+    const int n_ctas = e->n_sm;
+    e->mega_warps = env_int("PTB_MEGA_WARPS", 15) <= 11 ? 11 : 15;
+    const int slot_bytes = (env_int("PTB_MEGA_SLOT_KB", 6) * 1024 + 127) / 128 * 128;
+    std::vector<MegaOp> ops;
+    int acc_floats = 0, kmax = 256;
+    auto gemv_op = [&](int njobs, int K) -> MegaOp& { ops.emplace_back(); MegaOp& o = ops.back(); memset(&o, 0, sizeof(o)); o.kind = MK_GEMV; o.njobs = njobs; o.K = K; kmax = std::max(kmax, K); return o; };
+    {
+        MegaOp o;
+        memset(&o, 0, sizeof(o));
+        o.kind = MK_EMBED;
+        ops.push_back(o);
+    }
+    for (int l = 0; l < m.n_layers; ++l) {
+        const PtbLayerDesc& L = e->layers[l];
+        {
+            MegaOp& o = gemv_op(3, m.hidden);
+            set_job(o.job[0], L.q, nullptr, e->qkv);
+            set_job(o.job[1], L.k, nullptr, e->qkv + qd);
+            set_job(o.job[2], L.v, nullptr, e->qkv + qd + kvd);
+            o.x = e->x; o.norm_w = L.attn_norm; o.eps = m.eps; o.norm_add_one = m.norm_add_one; o.epilogue = EPI_STORE;
+            if (plan_mega_gemv(o, 3, m.hidden, n_ctas, e->mega_warps, slot_bytes, &acc_floats)) return -1;
+        }
+        {
+            MegaOp o;
+            memset(&o, 0, sizeof(o));
+            o.kind = MK_ATTN;
+            o.q_norm = L.q_norm; o.k_norm = L.k_norm; o.cos = L.cos; o.sin = L.sin; o.window = L.window;
+            o.k_cache = e->kc + (size_t)l * m.n_kv_heads * m.max_seq * m.head_dim;
+            o.v_cache = e->vc + (size_t)l * m.n_kv_heads * m.max_seq * m.head_dim;
+            ops.push_back(o);
+        }
+        {
+            MegaOp& o = gemv_op(1, L.o.cols);
+            set_job(o.job[0], L.o, nullptr, e->x);
+            o.x = e->att; o.resid = e->x; o.epilogue = EPI_RESID;
+            if (plan_mega_gemv(o, 1, L.o.cols, n_ctas, e->mega_warps, slot_bytes, &acc_floats)) return -1;
+        }
+        {
+            MegaOp& o = gemv_op(1, m.hidden);
+            set_job(o.job[0], L.gate, &L.up, e->ffn);
+            o.x = e->x; o.norm_w = L.ffn_norm; o.eps = m.eps; o.norm_add_one = m.norm_add_one; o.epilogue = EPI_GATED; o.act_gelu = m.act_gelu;
+            if (plan_mega_gemv(o, 1, m.hidden, n_ctas, e->mega_warps, slot_bytes, &acc_floats)) return -1;
+        }
+        {
+            MegaOp& o = gemv_op(1, L.down.cols);
+            set_job(o.job[0], L.down, nullptr, e->x);
+            o.x = e->ffn; o.resid = e->x; o.epilogue = EPI_RESID;
+            if (plan_mega_gemv(o, 1, L.down.cols, n_ctas, e->mega_warps, slot_bytes, &acc_floats)) return -1;
+        }
+    }
+    {
+        MegaOp& o = gemv_op(1, m.hidden);
+        set_job(o.job[0], m.lm_head, nullptr, e->logits);
+        o.x = e->x; o.norm_w = m.out_norm; o.eps = m.eps; o.norm_add_one = m.norm_add_one; o.epilogue = EPI_ARGMAX;
+        if (plan_mega_gemv(o, 1, m.hidden, n_ctas, e->mega_warps, slot_bytes, &acc_floats)) return -1;
+    }
+    e->n_ops = (int)ops.size();
+    PTB_CUDA_OK(cudaMalloc(&e->d_ops, sizeof(MegaOp) * ops.size()));
+    PTB_CUDA_OK(cudaMemcpy(e->d_ops, ops.data(), sizeof(MegaOp) * ops.size(), cudaMemcpyHostToDevice));
+    PTB_CUDA_OK(cudaMalloc(&e->d_bar, 64));
+    PTB_CUDA_OK(cudaMemset(e->d_bar, 0, 64));
+
+    MegaParams& p = e->mp;
+    memset(&p, 0, sizeof(p));
+    p.ops = e->d_ops; p.n_ops = e->n_ops; p.bar = e->d_bar; p.status = e->status; p.ctrl = e->ctrl;
+    p.x = e->x; p.qkv = e->qkv; p.att = e->att;
+    p.emb_table = (const uint8_t*)m.embed.w; p.emb_qtype = m.embed.qtype; p.emb_rowbytes = m.embed.rowbytes; p.emb_nblk = m.embed.cols / 256;
+    p.hidden = m.hidden; p.vocab = m.embed.rows; p.emb_scale = m.emb_scale;
+    p.part_o = e->part_o; p.part_ml = e->part_ml; p.head_cnt = e->tickets + 8;
+    p.n_heads = m.n_heads; p.n_kv_heads = m.n_kv_heads; p.group = m.n_heads / m.n_kv_heads; p.max_seq = m.max_seq;
+    p.max_splits = (m.max_seq + ATT_CHUNK - 1) / ATT_CHUNK; p.neox = m.neox; p.attn_eps = m.eps; p.scale = 1.0f / sqrtf((float)m.head_dim);
+    p.amax_val = e->amax_val; p.amax_idx = e->amax_idx; p.ticket = e->tickets + 1; p.logits = m.want_logits ? e->logits : nullptr;
+    p.result = e->result; p.row_offset = m.vocab_offset; p.token_log = e->token_log; p.token_script = e->script;
+    // shared memory: barriers | misc | quantised input | K-split accumulators | attention scratch | ring
+    int optin = 0;
+    PTB_CUDA_OK(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, e->dev));
+    const size_t cap = (size_t)optin - 1024;          // room for the kernel's static shared memory
+    const int max_slots = 64;
+    size_t off = align_up((size_t)2 * max_slots * 8, 128);
+    p.off_misc = (int)off; off += 512;
+    p.off_xq = (int)off; off += (size_t)kmax;
+    p.off_xs = (int)off; off += (size_t)(kmax / 32) * 4;
+    p.off_xsf = (int)off; off += (size_t)(kmax / 16) * 4;
+    p.off_xsf32 = (int)off; off += (size_t)(kmax / 32) * 4;
+    p.off_acc = (int)off; off += (size_t)acc_floats * 4;
+    off = align_up(off, 16);
+    p.off_attn = (int)off; off += mega_attn_smem(p.group);
+    off = align_up(off, 128);
+    p.off_ring = (int)off;
+    if (off + 4 * (size_t)slot_bytes > cap) { ptb_set_error("persistent decode: %zu B of fixed shared memory leave no room for the ring", off); return -1; }
+    p.slot_bytes = slot_bytes;
+    p.nslots = (int)std::min<size_t>(max_slots, (cap - off) / slot_bytes);
+    const int want = env_int("PTB_MEGA_SLOTS", 0);
+    if (want >= 4 && want < p.nslots) p.nslots = want;
+    e->mega_smem = off + (size_t)p.nslots * slot_bytes;
+    if (e->trace) p.trace = e->trace;
+    return 0;
+}
+
 // Enqueue one token's kernels on the engine stream.
 static int engine_enqueue(Engine* e) {
     const PtbModelDesc& m = e->m;
@@ -433,6 +620,12 @@ static int engine_enqueue(Engine* e) {
     const int splits = (m.max_seq + ATT_CHUNK - 1) / ATT_CHUNK;
     const bool pdl = e->use_pdl;
     long n = 0;
+    if (e->mega) {
+        PTB_CUDA_OK(cudaMemsetAsync(e->d_bar, 0, sizeof(unsigned), e->stream));
+        PTB_CUDA_OK(launch_mega(e->mp, e->mega_warps, e->n_sm, e->mega_smem, e->stream));
+        e->launches_per_token = 1;
+        return 0;
+    }
     EmbedParams ep;
     memset(&ep, 0, sizeof(ep));
     ep.table = (const uint8_t*)m.embed.w; ep.qtype = m.embed.qtype; ep.rowbytes = m.embed.rowbytes;
@@ -498,6 +691,9 @@ PTB_API void* ptb_engine_create(const PtbModelDesc* m, const PtbLayerDesc* layer
     if (ext_stream) { e->stream = (cudaStream_t)ext_stream; e->own_stream = false; }
     else if (cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) != cudaSuccess) { ptb_set_error("stream create failed"); delete e; return nullptr; }
     if (ensure_attrs() || engine_alloc(e) || engine_plan(e)) { delete e; return nullptr; }
+    // one GPU: the whole token as one persistent launch (PTB_MEGA=1; the default is the kernel-per-op graph)
+    e->mega = m->tp_world <= 1 && env_int("PTB_MEGA", 0) != 0;
+    if (e->mega && engine_plan_mega(e)) { delete e; return nullptr; }
     return e;
 }
 
@@ -511,6 +707,7 @@ PTB_API void ptb_engine_destroy(void* h) {
     cudaFree(e->kc); cudaFree(e->vc); cudaFree(e->part_o); cudaFree(e->part_ml); cudaFree(e->tickets);
     cudaFree(e->amax_val); cudaFree(e->amax_idx); cudaFree(e->ctrl); cudaFree(e->result); cudaFree(e->token_log); cudaFree(e->script);
     cudaFree(e->status);
+    cudaFree(e->d_ops); cudaFree(e->d_bar);
     cudaFreeHost(e->h_pinned);
     if (e->own_stream) cudaStreamDestroy(e->stream);
     delete e;
