@@ -311,7 +311,8 @@ struct Engine {
     bool mega = false;
     MegaParams mp;
     MegaOp* d_ops = nullptr;
-    unsigned* d_bar = nullptr;
+    unsigned* d_bar = nullptr;        // [0] spare, [1] token generation
+    uint2 *x_ll = nullptr, *qkv_ll = nullptr, *att_ll = nullptr, *ffn_ll = nullptr, *part_o_ll = nullptr, *part_ml_ll = nullptr;
     size_t mega_smem = 0;
     int mega_warps = 15;
     int n_ops = 0;
@@ -517,8 +518,19 @@ static int engine_plan_mega(Engine* e) {
     const int n_ctas = e->n_sm;
     e->mega_warps = env_int("PTB_MEGA_WARPS", 15) <= 11 ? 11 : 15;
     const int slot_bytes = (env_int("PTB_MEGA_SLOT_KB", 6) * 1024 + 127) / 128 * 128;
+    {
+        const int splits = (m.max_seq + ATT_CHUNK - 1) / ATT_CHUNK, group = m.n_heads / m.n_kv_heads;
+        if (m.n_kv_heads > n_ctas) { ptb_set_error("persistent decode: %d KV heads exceed the %d CTAs", m.n_kv_heads, n_ctas); return -1; }
+        auto ll_alloc = [](uint2** p, size_t n) { return cudaMalloc(p, n * sizeof(uint2)) != cudaSuccess || cudaMemset(*p, 0, n * sizeof(uint2)) != cudaSuccess; };
+        if (ll_alloc(&e->x_ll, m.hidden) || ll_alloc(&e->qkv_ll, qd + 2 * kvd) || ll_alloc(&e->att_ll, qd) || ll_alloc(&e->ffn_ll, m.inter) ||
+            ll_alloc(&e->part_o_ll, (size_t)m.n_kv_heads * splits * group * ATT_D) || ll_alloc(&e->part_ml_ll, (size_t)m.n_kv_heads * splits * group * 2)) {
+            ptb_set_error("persistent decode: slot buffer allocation failed");
+            return -1;
+        }
+    }
     std::vector<MegaOp> ops;
     int acc_floats = 0, kmax = 256;
+    int last_x_op = 0;               // index of the op that produced the current residual stream
     auto gemv_op = [&](int njobs, int K) -> MegaOp& { ops.emplace_back(); MegaOp& o = ops.back(); memset(&o, 0, sizeof(o)); o.kind = MK_GEMV; o.njobs = njobs; o.K = K; kmax = std::max(kmax, K); return o; };
     {
         MegaOp o;
@@ -533,7 +545,8 @@ static int engine_plan_mega(Engine* e) {
             set_job(o.job[0], L.q, nullptr, e->qkv);
             set_job(o.job[1], L.k, nullptr, e->qkv + qd);
             set_job(o.job[2], L.v, nullptr, e->qkv + qd + kvd);
-            o.x = e->x; o.norm_w = L.attn_norm; o.eps = m.eps; o.norm_add_one = m.norm_add_one; o.epilogue = EPI_STORE;
+            o.x_ll = e->x_ll; o.src_op = last_x_op; o.norm_w = L.attn_norm; o.eps = m.eps; o.norm_add_one = m.norm_add_one; o.epilogue = EPI_STORE;
+            o.out_ll[0] = e->qkv_ll; o.out_ll[1] = e->qkv_ll + qd; o.out_ll[2] = e->qkv_ll + qd + kvd;
             if (plan_mega_gemv(o, 3, m.hidden, n_ctas, e->mega_warps, slot_bytes, &acc_floats)) return -1;
         }
         {
@@ -548,26 +561,29 @@ static int engine_plan_mega(Engine* e) {
         {
             MegaOp& o = gemv_op(1, L.o.cols);
             set_job(o.job[0], L.o, nullptr, e->x);
-            o.x = e->att; o.resid = e->x; o.epilogue = EPI_RESID;
+            o.x_ll = e->att_ll; o.src_op = (int)ops.size() - 2; o.resid_ll = e->x_ll; o.out_ll[0] = e->x_ll; o.epilogue = EPI_RESID;
             if (plan_mega_gemv(o, 1, L.o.cols, n_ctas, e->mega_warps, slot_bytes, &acc_floats)) return -1;
+            last_x_op = (int)ops.size() - 1;
         }
         {
             MegaOp& o = gemv_op(1, m.hidden);
             set_job(o.job[0], L.gate, &L.up, e->ffn);
-            o.x = e->x; o.norm_w = L.ffn_norm; o.eps = m.eps; o.norm_add_one = m.norm_add_one; o.epilogue = EPI_GATED; o.act_gelu = m.act_gelu;
+            o.x_ll = e->x_ll; o.src_op = last_x_op; o.norm_w = L.ffn_norm; o.eps = m.eps; o.norm_add_one = m.norm_add_one; o.epilogue = EPI_GATED;
+            o.act_gelu = m.act_gelu; o.out_ll[0] = e->ffn_ll;
             if (plan_mega_gemv(o, 1, m.hidden, n_ctas, e->mega_warps, slot_bytes, &acc_floats)) return -1;
         }
         {
             MegaOp& o = gemv_op(1, L.down.cols);
             set_job(o.job[0], L.down, nullptr, e->x);
-            o.x = e->ffn; o.resid = e->x; o.epilogue = EPI_RESID;
+            o.x_ll = e->ffn_ll; o.src_op = (int)ops.size() - 2; o.resid_ll = e->x_ll; o.out_ll[0] = e->x_ll; o.epilogue = EPI_RESID;
             if (plan_mega_gemv(o, 1, L.down.cols, n_ctas, e->mega_warps, slot_bytes, &acc_floats)) return -1;
+            last_x_op = (int)ops.size() - 1;
         }
     }
     {
         MegaOp& o = gemv_op(1, m.hidden);
         set_job(o.job[0], m.lm_head, nullptr, e->logits);
-        o.x = e->x; o.norm_w = m.out_norm; o.eps = m.eps; o.norm_add_one = m.norm_add_one; o.epilogue = EPI_ARGMAX;
+        o.x_ll = e->x_ll; o.src_op = last_x_op; o.norm_w = m.out_norm; o.eps = m.eps; o.norm_add_one = m.norm_add_one; o.epilogue = EPI_ARGMAX;
         if (plan_mega_gemv(o, 1, m.hidden, n_ctas, e->mega_warps, slot_bytes, &acc_floats)) return -1;
     }
     e->n_ops = (int)ops.size();
@@ -578,11 +594,11 @@ static int engine_plan_mega(Engine* e) {
 
     MegaParams& p = e->mp;
     memset(&p, 0, sizeof(p));
-    p.ops = e->d_ops; p.n_ops = e->n_ops; p.bar = e->d_bar; p.status = e->status; p.ctrl = e->ctrl;
-    p.x = e->x; p.qkv = e->qkv; p.att = e->att;
+    p.ops = e->d_ops; p.n_ops = e->n_ops; p.gen = e->d_bar + 1; p.status = e->status; p.ctrl = e->ctrl;
+    p.x = e->x; p.x_ll = e->x_ll; p.qkv_ll = e->qkv_ll; p.att_ll = e->att_ll;
     p.emb_table = (const uint8_t*)m.embed.w; p.emb_qtype = m.embed.qtype; p.emb_rowbytes = m.embed.rowbytes; p.emb_nblk = m.embed.cols / 256;
     p.hidden = m.hidden; p.vocab = m.embed.rows; p.emb_scale = m.emb_scale;
-    p.part_o = e->part_o; p.part_ml = e->part_ml; p.head_cnt = e->tickets + 8;
+    p.part_o = e->part_o_ll; p.part_ml = e->part_ml_ll;
     p.n_heads = m.n_heads; p.n_kv_heads = m.n_kv_heads; p.group = m.n_heads / m.n_kv_heads; p.max_seq = m.max_seq;
     p.max_splits = (m.max_seq + ATT_CHUNK - 1) / ATT_CHUNK; p.neox = m.neox; p.attn_eps = m.eps; p.scale = 1.0f / sqrtf((float)m.head_dim);
     p.amax_val = e->amax_val; p.amax_idx = e->amax_idx; p.ticket = e->tickets + 1; p.logits = m.want_logits ? e->logits : nullptr;
@@ -607,7 +623,8 @@ static int engine_plan_mega(Engine* e) {
     p.slot_bytes = slot_bytes;
     p.nslots = (int)std::min<size_t>(max_slots, (cap - off) / slot_bytes);
     const int want = env_int("PTB_MEGA_SLOTS", 0);
-    if (want >= 4 && want < p.nslots) p.nslots = want;
+    if (want >= 16 && want < p.nslots) p.nslots = want;
+    if (p.nslots < 16) { ptb_set_error("persistent decode: only %d ring slots fit; at least 16 are needed", p.nslots); return -1; }
     e->mega_smem = off + (size_t)p.nslots * slot_bytes;
     if (e->trace) p.trace = e->trace;
     return 0;
@@ -621,7 +638,6 @@ static int engine_enqueue(Engine* e) {
     const bool pdl = e->use_pdl;
     long n = 0;
     if (e->mega) {
-        PTB_CUDA_OK(cudaMemsetAsync(e->d_bar, 0, sizeof(unsigned), e->stream));
         PTB_CUDA_OK(launch_mega(e->mp, e->mega_warps, e->n_sm, e->mega_smem, e->stream));
         e->launches_per_token = 1;
         return 0;
@@ -708,6 +724,7 @@ PTB_API void ptb_engine_destroy(void* h) {
     cudaFree(e->amax_val); cudaFree(e->amax_idx); cudaFree(e->ctrl); cudaFree(e->result); cudaFree(e->token_log); cudaFree(e->script);
     cudaFree(e->status);
     cudaFree(e->d_ops); cudaFree(e->d_bar);
+    cudaFree(e->x_ll); cudaFree(e->qkv_ll); cudaFree(e->att_ll); cudaFree(e->ffn_ll); cudaFree(e->part_o_ll); cudaFree(e->part_ml_ll);
     cudaFreeHost(e->h_pinned);
     if (e->own_stream) cudaStreamDestroy(e->stream);
     delete e;

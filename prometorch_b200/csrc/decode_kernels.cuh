@@ -92,6 +92,12 @@ struct GemvParams {
 enum { CTRL_TOKEN = 0, CTRL_POS = 1, CTRL_STEP = 2, CTRL_SELF_FEED = 3, CTRL_LOG_CAP = 4, CTRL_GEN = 5, CTRL_SCRIPT_LEN = 6, CTRL_WORDS = 8 };
 
 __device__ __forceinline__ int dp4a_s(int a, int b, int c) { return __dp4a(a, b, c); }
+// unsigned bytes x signed bytes: used with (q & 0xF0F0F0F0), i.e. 16 x the high nibbles, the factor is divided out afterwards
+__device__ __forceinline__ int dp4a_us(unsigned a, int b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
 
 // ---- dot products: FOUR lanes cooperate on one 256-value super-block (64 weights per lane), so the
 // scale decoding and the int->float work are amortised over 16 dp4a.  `swap` flips the order of a
@@ -109,13 +115,15 @@ __device__ __forceinline__ float q4k_dot(const uint8_t* bp, int j, bool swap, co
     const uint4 xla = *reinterpret_cast<const uint4*>(xp), xha = *reinterpret_cast<const uint4*>(xp + 32);
     const uint4 xlb = *reinterpret_cast<const uint4*>(xr), xhb = *reinterpret_cast<const uint4*>(xr + 32);
     int l0 = dp4a_s(qa.x & 0x0F0F0F0F, xla.x, 0), l1 = dp4a_s(qb.x & 0x0F0F0F0F, xlb.x, 0);
-    int h0 = dp4a_s((qa.x >> 4) & 0x0F0F0F0F, xha.x, 0), h1 = dp4a_s((qb.x >> 4) & 0x0F0F0F0F, xhb.x, 0);
+    int h0 = dp4a_us(qa.x & 0xF0F0F0F0u, xha.x, 0), h1 = dp4a_us(qb.x & 0xF0F0F0F0u, xhb.x, 0);
     l0 = dp4a_s(qa.y & 0x0F0F0F0F, xla.y, l0); l1 = dp4a_s(qb.y & 0x0F0F0F0F, xlb.y, l1);
-    h0 = dp4a_s((qa.y >> 4) & 0x0F0F0F0F, xha.y, h0); h1 = dp4a_s((qb.y >> 4) & 0x0F0F0F0F, xhb.y, h1);
+    h0 = dp4a_us(qa.y & 0xF0F0F0F0u, xha.y, h0); h1 = dp4a_us(qb.y & 0xF0F0F0F0u, xhb.y, h1);
     l0 = dp4a_s(qa.z & 0x0F0F0F0F, xla.z, l0); l1 = dp4a_s(qb.z & 0x0F0F0F0F, xlb.z, l1);
-    h0 = dp4a_s((qa.z >> 4) & 0x0F0F0F0F, xha.z, h0); h1 = dp4a_s((qb.z >> 4) & 0x0F0F0F0F, xhb.z, h1);
+    h0 = dp4a_us(qa.z & 0xF0F0F0F0u, xha.z, h0); h1 = dp4a_us(qb.z & 0xF0F0F0F0u, xhb.z, h1);
     l0 = dp4a_s(qa.w & 0x0F0F0F0F, xla.w, l0); l1 = dp4a_s(qb.w & 0x0F0F0F0F, xlb.w, l1);
-    h0 = dp4a_s((qa.w >> 4) & 0x0F0F0F0F, xha.w, h0); h1 = dp4a_s((qb.w >> 4) & 0x0F0F0F0F, xhb.w, h1);
+    h0 = dp4a_us(qa.w & 0xF0F0F0F0u, xha.w, h0); h1 = dp4a_us(qb.w & 0xF0F0F0F0u, xhb.w, h1);
+    h0 = (h0 + h1) >> 4;            // exact: every term is a multiple of 16
+    h1 = 0;
     // 6-bit scales/mins of sub-blocks 2j and 2j+1, two per 16-bit lane of the packed header
     const int sh = 16 * (j & 1);
     const uint32_t a = (hdr.y >> sh) & 0xffffu, b = (hdr.z >> sh) & 0xffffu, c = (hdr.w >> sh) & 0xffffu;
@@ -166,6 +174,33 @@ __device__ __forceinline__ float q6k_dot(const uint8_t* seg, int nblk, int blk, 
     r += (float)sc[ia + 4] * (xsh * (float)dha - 32.0f * xsf16[ia + 4]);
     r += (float)sc[ib + 4] * (xsh * (float)dhb - 32.0f * xsf16[ib + 4]);
     return d * r;
+}
+
+// All the dot products one 4-lane group owes to a tile: blocks my_j, my_j + gprw, ... of its row, two blocks per
+// trip (and both matrices of a gated pair) so that independent dependency chains overlap in the pipeline.
+template <int QT, bool PAIRED>
+__device__ __forceinline__ void tile_dots(const uint8_t* rowp, size_t pair_off, int nb, int my_j, int gprw, int lane4, bool swap,
+                                          const int8_t* xq_s, const float* xs_s, const float* xsf_s, const float* xsf32_s,
+                                          float& a0, float& a1) {
+    auto dot = [&](const uint8_t* rp, int b) -> float {
+        if (QT == QT_Q4K) return q4k_dot(rp + b * 144, lane4, swap, xq_s + b * 256, xs_s + b * 8, xsf32_s + b * 8);
+        return q6k_dot(rp, nb, b, lane4, swap, xq_s + b * 256, xs_s + b * 8, xsf_s + b * 16);
+    };
+    int b = my_j;
+#pragma unroll 1
+    for (; b + gprw < nb; b += 2 * gprw) {
+        const float p0 = dot(rowp, b), p1 = dot(rowp, b + gprw);
+        if (PAIRED) {
+            const float q0 = dot(rowp + pair_off, b), q1 = dot(rowp + pair_off, b + gprw);
+            a1 += q0 + q1;
+        }
+        a0 += p0 + p1;
+    }
+    if (b < nb) {
+        const float p0 = dot(rowp, b);
+        if (PAIRED) a1 += dot(rowp + pair_off, b);
+        a0 += p0;
+    }
 }
 
 // Block-wide sum through shared memory; `buf` needs >= 32 floats.  All threads get the result.
@@ -393,18 +428,13 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32, 2) gemv_kernel(const __grid_c
             const float* xsf32_s = xsf32 + g.boff * 8;
             // odd groups flip their two 16-byte loads when the row stride is an even multiple of 16 B
             const bool swap = (grp & 1) && (((g.sb >> 4) & 1) == 0);
+            const size_t poff = (size_t)RW * g.sb;
             if (qtype == QT_Q4K) {
-#pragma unroll 1
-                for (int b = my_j; b < g.nb; b += gprw) {
-                    a0 += q4k_dot(rowp + b * 144, lane4, swap, xq_s + b * 256, xs_s + b * 8, xsf32_s + b * 8);
-                    if (paired) a1 += q4k_dot(rowp + RW * g.sb + b * 144, lane4, swap, xq_s + b * 256, xs_s + b * 8, xsf32_s + b * 8);
-                }
+                if (paired) tile_dots<QT_Q4K, true>(rowp, poff, g.nb, my_j, gprw, lane4, swap, xq_s, xs_s, xsf_s, xsf32_s, a0, a1);
+                else tile_dots<QT_Q4K, false>(rowp, poff, g.nb, my_j, gprw, lane4, swap, xq_s, xs_s, xsf_s, xsf32_s, a0, a1);
             } else {
-#pragma unroll 1
-                for (int b = my_j; b < g.nb; b += gprw) {
-                    a0 += q6k_dot(rowp, g.nb, b, lane4, swap, xq_s + b * 256, xs_s + b * 8, xsf_s + b * 16);
-                    if (paired) a1 += q6k_dot(rowp + RW * g.sb, g.nb, b, lane4, swap, xq_s + b * 256, xs_s + b * 8, xsf_s + b * 16);
-                }
+                if (paired) tile_dots<QT_Q6K, true>(rowp, poff, g.nb, my_j, gprw, lane4, swap, xq_s, xs_s, xsf_s, xsf32_s, a0, a1);
+                else tile_dots<QT_Q6K, false>(rowp, poff, g.nb, my_j, gprw, lane4, swap, xq_s, xs_s, xsf_s, xsf32_s, a0, a1);
             }
         }
         __syncwarp();

@@ -7,12 +7,17 @@
 //     matrix, op after op, into one shared-memory ring with untiled TMA bulk copies.  Weights do not
 //     depend on activations, so the producer runs ahead of the math by the depth of the ring
 //     (~180 KB per SM, ~26 MB over the GPU: about one whole op) and HBM never idles;
-//   * consumer warps that, per op, wait for the previous op's output (a grid-wide arrival counter),
-//     normalise + quantise the input vector into shared memory, eat the tiles from the ring with the
-//     same dp4a dot products as gemv_kernel, and run the epilogue (store / residual / SiLU·mul /
-//     arg-max + control-block update).
+//   * consumer warps that, per op, read the previous op's output vector, normalise + quantise it
+//     into shared memory, eat the tiles from the ring with the same dp4a dot products as gemv_kernel,
+//     and run the epilogue (store / residual / SiLU·mul / arg-max + control-block update).
 // Attention (QK-norm, RoPE, fp16 KV write, one 128-position chunk per work item, partial results
-// merged by the last CTA to finish a KV head) and the embedding look-up are ops of the same list.
+// merged by the CTA that owns the KV head) and the embedding look-up are ops of the same list.
+//
+// There is no grid-wide barrier.  Every activation element travels as an 8-byte {value, sequence
+// number} slot written and read as one access: a reader that sees the sequence number of the
+// producing op (token generation x ops per token + op index + 1, never repeated) has the value too,
+// so CTAs synchronise on exactly the data they need, with neither fences nor counters.  A value is
+// overwritten only by an op that (transitively) needed every reader of the old value to finish.
 //
 // Every wait is bounded; on expiry the status word is set, the CTA stops waiting and runs to the end.
 // The reference runs ~10 kernels per layer (torch/io/gguf_model.h:2575-3113).
@@ -29,9 +34,11 @@ struct MegaOp {
     float eps;
     int window;
     GemvJob job[GEMV_MAX_JOBS];
-    const float* x;          // GEMV input vector
+    const uint2* x_ll;       // GEMV input vector as {value, sequence} slots, written by op `src_op`
+    const uint2* resid_ll;   // EPI_RESID: slots whose value is added (already observed by this CTA)
+    uint2* out_ll[GEMV_MAX_JOBS];   // output slots of each job (null: plain output only)
+    int src_op, pad;
     const float* norm_w;     // RMSNorm weight or null
-    const float* resid;      // EPI_RESID
     const float* q_norm;     // attention
     const float* k_norm;
     const float* cos;
@@ -43,20 +50,20 @@ struct MegaOp {
 struct MegaParams {
     const MegaOp* ops;
     int n_ops, pad0;
-    unsigned* bar;           // arrival counter, zero when the kernel starts
     int* status;
     int* ctrl;
-    float* x;                // residual stream [hidden]
-    float* qkv;              // q | k | v rows of the current layer
-    float* att;              // attention output [heads * d]
+    float* x;                // residual stream [hidden] (plain copy, for readers outside the kernel)
+    uint2* x_ll;             // the same as slots
+    const uint2* qkv_ll;     // q | k | v rows of the current layer
+    uint2* att_ll;           // attention output [heads * d]
+    unsigned* gen;           // token generation: read at start, advanced by the CTA that finishes the token
     // embedding
     const uint8_t* emb_table;
     int emb_qtype, emb_rowbytes, emb_nblk, hidden, vocab;
     float emb_scale;
     // attention
-    float* part_o;           // [kv_heads][max_splits][group][d]
-    float* part_ml;          // [kv_heads][max_splits][group][2]
-    unsigned* head_cnt;      // [kv_heads], zero between tokens
+    uint2* part_o;           // [kv_heads][max_splits][group][d] slots
+    uint2* part_ml;          // [kv_heads][max_splits][group][2] slots
     int n_heads, n_kv_heads, group, max_seq, max_splits, neox;
     float attn_eps, scale;
     // arg-max
@@ -78,13 +85,38 @@ template <int NT>
 __device__ __forceinline__ void cons_sync() { asm volatile("bar.sync 1, %0;" ::"n"(NT) : "memory"); }
 __device__ __forceinline__ void attn_sync() { asm volatile("bar.sync 2, 256;" ::: "memory"); }
 
-__device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const unsigned* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ void red_release_gpu_add(unsigned* p, unsigned v) {
-    asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+
+// Wait budget shared by the polling loops of one CTA: the first loop to run out of time records the
+// timeout and raises the CTA's abort flag; after that no loop waits any more.
+struct MegaWait {
+    volatile int* abort_flag;
+    int* status;
+    __device__ __forceinline__ bool expired(uint32_t& spins, unsigned long long& t0) const {
+        if ((++spins & 255u) != 0) return false;
+        if (*abort_flag) return true;
+        unsigned long long t1;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+        if (t0 == 0) { t0 = t1; return false; }
+        if (t1 - t0 > 2000000000ull) { atomicExch(status, PTB_ERR_FLAG_TIMEOUT); *abort_flag = 1; return true; }
+        return false;
+    }
+};
+
+// One slot: spin until its sequence number is `seq`.
+__device__ __forceinline__ float ll_wait(const uint2* p, uint32_t seq, const MegaWait& W) {
+    uint32_t spins = 0;
+    unsigned long long t0 = 0;
+    uint2 v = ld_ll(p);
+    while (v.y != seq) {
+        if (W.expired(spins, t0)) break;
+        v = ld_ll(p);
+    }
+    return __uint_as_float(v.x);
 }
 
 // Sum over the consumer threads (NT of them); buf >= 32 floats.
@@ -99,28 +131,55 @@ __device__ __forceinline__ float cons_block_sum(float v, float* buf) {
     return warp_sum(t);
 }
 
-// x[K] -> optional RMSNorm -> int8 blocks of 32 (same outputs as quantize_input), by the NT consumer threads.
+// x (slots written by the producing op) -> optional RMSNorm -> int8 blocks of 32, by the NT consumer threads.
+// All of a thread's loads are in flight together; the loop repeats until every sequence number matches.
 template <int NT, int ITEMS>
-__device__ __forceinline__ void mega_quantize_input(const float* __restrict__ x, const float* __restrict__ norm_w, float eps,
-                                                    int add_one, int K, int8_t* xq, float* xs, float* xsf16, float* xsf32,
-                                                    float* red) {
+__device__ __forceinline__ void mega_quantize_input(const uint2* __restrict__ x_ll, uint32_t seq, const float* __restrict__ norm_w,
+                                                    float eps, int add_one, int K, int8_t* xq, float* xs, float* xsf16,
+                                                    float* xsf32, float* red, const MegaWait& W) {
     const int tid = threadIdx.x;
     const int items = K / 8;
     float v[ITEMS][8];
-    float ss = 0.f;
+    {
+        uint4 a[ITEMS][4];
+        uint32_t spins = 0;
+        unsigned long long t0 = 0;
+        while (true) {
+            bool good = true;
 #pragma unroll
-    for (int r = 0; r < ITEMS; ++r) {
-        const int i = r * NT + tid;
-        if (i < items) {
-            const float4 a = __ldcg(reinterpret_cast<const float4*>(x) + 2 * i), b = __ldcg(reinterpret_cast<const float4*>(x) + 2 * i + 1);
-            v[r][0] = a.x; v[r][1] = a.y; v[r][2] = a.z; v[r][3] = a.w; v[r][4] = b.x; v[r][5] = b.y; v[r][6] = b.z; v[r][7] = b.w;
-        } else {
+            for (int r = 0; r < ITEMS; ++r) {
+                const int i = r * NT + tid;
+                if (i < items) {
+                    const uint4* p = reinterpret_cast<const uint4*>(x_ll + (size_t)i * 8);
 #pragma unroll
-            for (int k = 0; k < 8; ++k) v[r][k] = 0.f;
+                    for (int j = 0; j < 4; ++j) a[r][j] = ld_volatile_v4(p + j);
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < ITEMS; ++r) {
+                const int i = r * NT + tid;
+                if (i < items) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) good = good && a[r][j].y == seq && a[r][j].w == seq;
+                }
+            }
+            if (good || W.expired(spins, t0)) break;
         }
 #pragma unroll
-        for (int k = 0; k < 8; ++k) ss += v[r][k] * v[r][k];
+        for (int r = 0; r < ITEMS; ++r) {
+            const int i = r * NT + tid;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                v[r][2 * j] = i < items ? __uint_as_float(a[r][j].x) : 0.f;
+                v[r][2 * j + 1] = i < items ? __uint_as_float(a[r][j].z) : 0.f;
+            }
+        }
     }
+    float ss = 0.f;
+#pragma unroll
+    for (int r = 0; r < ITEMS; ++r)
+#pragma unroll
+        for (int k = 0; k < 8; ++k) ss += v[r][k] * v[r][k];
     float rs = 1.0f;
     if (norm_w) {
         ss = cons_block_sum<NT>(ss, red);
@@ -182,6 +241,13 @@ __device__ __forceinline__ MegaShare mega_share(const MegaOp& op, int cta) {
 struct MegaItem { int s, nb, boff, sb, row0, rows; size_t off; };
 __device__ __forceinline__ MegaItem mega_geom(const GemvJob& J, int r0, int r1, int it, int sz0, int sz1) {
     MegaItem g;
+    if (J.KS == 1) {        // the common case (K <= 2560): one segment, no divisions
+        g.s = 0; g.nb = J.seg_base; g.boff = 0; g.sb = sz0;
+        g.row0 = r0 + it * J.RW;
+        g.rows = min(J.RW, r1 - g.row0);
+        g.off = (size_t)g.row0 * sz0;
+        return g;
+    }
     const int rg = it / J.KS;
     g.s = it - rg * J.KS;
     const int extra = min(g.s, J.seg_rem);
@@ -194,11 +260,17 @@ __device__ __forceinline__ MegaItem mega_geom(const GemvJob& J, int r0, int r1, 
     return g;
 }
 
-__device__ __forceinline__ void mega_norm_rope_head(const float* src, const float* nw, float eps, const float* cs, const float* sn,
-                                                    int neox, float mul, float* dst, int lane) {
+// One head of 128 values from slots: optional RMSNorm, rotation, scale; one warp, four values per lane.
+__device__ __forceinline__ void mega_norm_rope_head(const uint2* src, uint32_t seq, const MegaWait& W, const float* nw, float eps,
+                                                    const float* cs, const float* sn, int neox, float mul, float* dst, int lane) {
     float v[4];
-    if (neox) { v[0] = __ldcg(src + lane); v[1] = __ldcg(src + lane + 32); v[2] = __ldcg(src + lane + 64); v[3] = __ldcg(src + lane + 96); }
-    else { const float4 t = __ldcg(reinterpret_cast<const float4*>(src) + lane); v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w; }
+    if (neox) {
+        v[0] = ll_wait(src + lane, seq, W); v[1] = ll_wait(src + lane + 32, seq, W);
+        v[2] = ll_wait(src + lane + 64, seq, W); v[3] = ll_wait(src + lane + 96, seq, W);
+    } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) v[k] = ll_wait(src + 4 * lane + k, seq, W);
+    }
     if (nw) {
         float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
         ss = warp_sum(ss);
@@ -228,12 +300,13 @@ struct MegaAttnShared {
     float sc[G][ATT_CHUNK];
     float hm[G], hl[G];
     float red[8][G][ATT_D];
-    int last;
 };
 
-// One attention op: the first 256 consumer threads work through this CTA's (kv head, chunk) items.
+// One attention op: the first 256 consumer threads work through this CTA's (kv head, chunk) items; with more
+// than one chunk the partial {max, sum, output} of every chunk travel as slots to CTA `kv head`, which merges.
 template <int G>
-__device__ __forceinline__ void mega_attn(const MegaParams& P, const MegaOp& op, uint8_t* smem_attn, int cta, int n_ctas) {
+__device__ __forceinline__ void mega_attn(const MegaParams& P, const MegaOp& op, uint8_t* smem_attn, int cta, int n_ctas,
+                                          uint32_t seq_in, uint32_t seq_out, const MegaWait& W) {
     MegaAttnShared<G>& sh = *reinterpret_cast<MegaAttnShared<G>*>(smem_attn);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int pos = min(__ldcg(P.ctrl + CTRL_POS), P.max_seq - 1);
@@ -243,9 +316,9 @@ __device__ __forceinline__ void mega_attn(const MegaParams& P, const MegaOp& op,
     const int nchunk = (T + ATT_CHUNK - 1) / ATT_CHUNK;
     const int nact = nchunk - first_chunk;
     const int qd = P.n_heads * ATT_D, kvd = P.n_kv_heads * ATT_D;
-    const float* qv = P.qkv;
-    const float* kv = P.qkv + qd;
-    const float* vv = P.qkv + qd + kvd;
+    const uint2* qv = P.qkv_ll;
+    const uint2* kv = P.qkv_ll + qd;
+    const uint2* vv = P.qkv_ll + qd + kvd;
     const float* cs = op.cos + (size_t)pos * (ATT_D / 2);
     const float* sn = op.sin + (size_t)pos * (ATT_D / 2);
     const int rg = tid >> 4, dc = tid & 15;
@@ -257,14 +330,14 @@ __device__ __forceinline__ void mega_attn(const MegaParams& P, const MegaOp& op,
         const int base = c * ATT_CHUNK;
         const int t0 = max(base, lo), t1 = min(base + ATT_CHUNK, T);
         if (warp < G)
-            mega_norm_rope_head(qv + (size_t)(kvh * G + warp) * ATT_D, op.q_norm, P.attn_eps, cs, sn, P.neox,
+            mega_norm_rope_head(qv + (size_t)(kvh * G + warp) * ATT_D, seq_in, W, op.q_norm, P.attn_eps, cs, sn, P.neox,
                                 P.scale * 1.4426950408889634f, sh.qs[warp], lane);
         if (pos >= base && pos < base + ATT_CHUNK && warp == 7) {      // this chunk holds the new position: write K, V
-            mega_norm_rope_head(kv + (size_t)kvh * ATT_D, op.k_norm, P.attn_eps, cs, sn, P.neox, 1.0f, sh.kn, lane);
+            mega_norm_rope_head(kv + (size_t)kvh * ATT_D, seq_in, W, op.k_norm, P.attn_eps, cs, sn, P.neox, 1.0f, sh.kn, lane);
             __syncwarp();
             for (int i = lane; i < ATT_D; i += 32) {
                 kc[(size_t)pos * ATT_D + i] = __float2half_rn(sh.kn[i]);
-                vc[(size_t)pos * ATT_D + i] = __float2half_rn(__ldcg(vv + (size_t)kvh * ATT_D + i));
+                vc[(size_t)pos * ATT_D + i] = __float2half_rn(ll_wait(vv + (size_t)kvh * ATT_D + i, seq_in, W));
             }
         }
         attn_sync();
@@ -350,45 +423,53 @@ __device__ __forceinline__ void mega_attn(const MegaParams& P, const MegaOp& op,
                 for (int k = 0; k < 8; ++k) sh.red[warp][g][dc * 8 + k] = acc[g][k];
         }
         attn_sync();
-        float* po = P.part_o + ((size_t)kvh * P.max_splits + c) * G * ATT_D;
-        float* pml = P.part_ml + ((size_t)kvh * P.max_splits + c) * G * 2;
+        uint2* po = P.part_o + ((size_t)kvh * P.max_splits + c) * G * ATT_D;
+        uint2* pml = P.part_ml + ((size_t)kvh * P.max_splits + c) * G * 2;
         for (int i = tid; i < G * ATT_D; i += 256) {
             const int g = i / ATT_D, d = i - g * ATT_D;
             float o = 0.f;
 #pragma unroll
             for (int w = 0; w < 8; ++w) o += sh.red[w][g][d];
-            if (nact == 1) P.att[(size_t)(kvh * G + g) * ATT_D + d] = o / sh.hl[g];      // a single chunk needs no merge
-            else __stcg(po + i, o);
+            if (nact == 1) st_ll(P.att_ll + (size_t)(kvh * G + g) * ATT_D + d, __float_as_uint(o / sh.hl[g]), seq_out);   // no merge needed
+            else st_ll(po + i, __float_as_uint(o), seq_out);
         }
-        if (nact > 1) {
-            if (tid < G) { __stcg(pml + 2 * tid, sh.hm[tid]); __stcg(pml + 2 * tid + 1, sh.hl[tid]); }
-            __threadfence();
-            attn_sync();
-            if (tid == 0) {
-                const unsigned t = atomicAdd(P.head_cnt + kvh, 1u);
-                sh.last = (t == (unsigned)(nact - 1));
-            }
-            attn_sync();
-            if (sh.last) {      // every chunk of this KV head is in: merge them
-                __threadfence();
-                for (int i = tid; i < G * ATT_D; i += 256) {
-                    const int g = i / ATT_D;
-                    float Mx = -INFINITY;
-                    for (int cc = first_chunk; cc < nchunk; ++cc)
-                        Mx = fmaxf(Mx, __ldcg(P.part_ml + (((size_t)kvh * P.max_splits + cc) * G + g) * 2));
-                    float Lt = 0.f, Ot = 0.f;
-                    for (int cc = first_chunk; cc < nchunk; ++cc) {
-                        const float* ml = P.part_ml + (((size_t)kvh * P.max_splits + cc) * G + g) * 2;
-                        const float w = exp2f(__ldcg(ml) - Mx);
-                        Lt += w * __ldcg(ml + 1);
-                        Ot += w * __ldcg(P.part_o + ((size_t)kvh * P.max_splits + cc) * G * ATT_D + i);
-                    }
-                    P.att[(size_t)kvh * G * ATT_D + i] = Ot / Lt;
-                }
-                if (tid == 0) P.head_cnt[kvh] = 0u;
-            }
+        if (nact > 1 && tid < G) {
+            st_ll(pml + 2 * tid, __float_as_uint(sh.hm[tid]), seq_out);
+            st_ll(pml + 2 * tid + 1, __float_as_uint(sh.hl[tid]), seq_out);
         }
         attn_sync();      // shared memory is reused by the next item
+    }
+    // ---- merge (after ALL of this CTA's items, so that no CTA waits for a partial it has yet to produce)
+    if (nact > 1 && cta < P.n_kv_heads) {
+        const int kvh = cta;
+        for (int i = tid; i < G * ATT_D; i += 256) {
+            const int g = i / ATT_D;
+            uint32_t spins = 0;
+            unsigned long long t0 = 0;
+            float Mx, Lt, Ot;
+            while (true) {
+                bool good = true;
+                Mx = -INFINITY;
+                for (int cc = first_chunk; cc < nchunk; ++cc) {
+                    const uint2 m = ld_ll(P.part_ml + (((size_t)kvh * P.max_splits + cc) * G + g) * 2);
+                    good = good && m.y == seq_out;
+                    Mx = fmaxf(Mx, __uint_as_float(m.x));
+                }
+                Lt = 0.f;
+                Ot = 0.f;
+                for (int cc = first_chunk; cc < nchunk; ++cc) {
+                    const uint2* ml = P.part_ml + (((size_t)kvh * P.max_splits + cc) * G + g) * 2;
+                    const uint2 m = ld_ll(ml), l = ld_ll(ml + 1);
+                    const uint2 o = ld_ll(P.part_o + ((size_t)kvh * P.max_splits + cc) * G * ATT_D + i);
+                    good = good && l.y == seq_out && o.y == seq_out;
+                    const float w = exp2f(__uint_as_float(m.x) - Mx);
+                    Lt += w * __uint_as_float(l.x);
+                    Ot += w * __uint_as_float(o.x);
+                }
+                if (good || W.expired(spins, t0)) break;
+            }
+            st_ll(P.att_ll + (size_t)kvh * G * ATT_D + i, __float_as_uint(Ot / Lt), seq_out);
+        }
     }
 }
 
@@ -404,7 +485,6 @@ __global__ void __launch_bounds__((NCONS + 1) * 32, 1) decode_mega_kernel(const 
     uint64_t* empty = full + NS;
     float* misc = reinterpret_cast<float*>(smem + P.off_misc);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(misc + 96);
-    volatile int* uniform_abort = reinterpret_cast<volatile int*>(misc + 97);
     int8_t* xq = reinterpret_cast<int8_t*>(smem + P.off_xq);
     float* xs = reinterpret_cast<float*>(smem + P.off_xs);
     float* xsf = reinterpret_cast<float*>(smem + P.off_xsf);
@@ -459,9 +539,10 @@ __global__ void __launch_bounds__((NCONS + 1) * 32, 1) decode_mega_kernel(const 
         }
     } else {
         // ================================================================== consumers
+        const MegaWait W{abort_flag, P.status};
+        const uint32_t gen = __ldcg(P.gen);
+        const uint32_t seq0 = gen * (uint32_t)P.n_ops + 1u;          // sequence number of op 0 of this token
         uint32_t gbase = 0;              // ring position of this CTA's first tile of the current op
-        unsigned bar_target = 0;         // arrivals that complete the previous op
-        bool ok = true;
         auto stamp = [&](int oi, int k) {
             if (P.trace && tid == 0 && cta == 0) {
                 unsigned long long t;
@@ -471,30 +552,8 @@ __global__ void __launch_bounds__((NCONS + 1) * 32, 1) decode_mega_kernel(const 
         };
         for (int oi = 0; oi < P.n_ops; ++oi) {
             const MegaOp& op = P.ops[oi];
+            const uint32_t seq = seq0 + (uint32_t)oi;
             stamp(oi, 0);
-            // parameters do not depend on the previous op: pull the RMSNorm weight towards this SM before waiting
-            if (op.kind == MK_GEMV && op.norm_w) {
-                for (int i = tid * 32; i < op.K; i += NT * 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(op.norm_w + i));
-            }
-            // ---- wait until every CTA has finished the previous op
-            if (oi > 0) {
-                if (tid == 0 && !*abort_flag) {
-                    unsigned long long t0;
-                    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-                    uint32_t spins = 0;
-                    while ((int)(ld_acquire_gpu_u32(P.bar) - bar_target) < 0) {
-                        if ((++spins & 1023u) == 0) {
-                            unsigned long long t1;
-                            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-                            if (t1 - t0 > 2000000000ull) { atomicExch(P.status, PTB_ERR_FLAG_TIMEOUT); *abort_flag = 1; break; }
-                        }
-                    }
-                }
-                if (tid == 0) *uniform_abort = *abort_flag;      // one reader, so that every consumer thread sees the same value
-                cons_sync<NT>();
-                if (*uniform_abort) ok = false;
-            }
-            stamp(oi, 1);
             if (op.kind == MK_EMBED) {
                 int tok = __ldcg(P.ctrl + CTRL_TOKEN);
                 if (tok < 0 || tok >= P.vocab) {
@@ -532,15 +591,17 @@ __global__ void __launch_bounds__((NCONS + 1) * 32, 1) decode_mega_kernel(const 
                     } else {
                         v = reinterpret_cast<const float*>(row)[i];
                     }
-                    P.x[i] = v * P.emb_scale;
+                    v *= P.emb_scale;
+                    P.x[i] = v;
+                    st_ll(P.x_ll + i, __float_as_uint(v), seq);
                 }
             } else if (op.kind == MK_ATTN) {
-                if (ok && tid < 256) {
+                if (tid < 256) {
                     switch (P.group) {
-                        case 1: mega_attn<1>(P, op, smem + P.off_attn, cta, n_ctas); break;
-                        case 2: mega_attn<2>(P, op, smem + P.off_attn, cta, n_ctas); break;
-                        case 4: mega_attn<4>(P, op, smem + P.off_attn, cta, n_ctas); break;
-                        default: mega_attn<8>(P, op, smem + P.off_attn, cta, n_ctas); break;
+                        case 1: mega_attn<1>(P, op, smem + P.off_attn, cta, n_ctas, seq - 1, seq, W); break;
+                        case 2: mega_attn<2>(P, op, smem + P.off_attn, cta, n_ctas, seq - 1, seq, W); break;
+                        case 4: mega_attn<4>(P, op, smem + P.off_attn, cta, n_ctas, seq - 1, seq, W); break;
+                        default: mega_attn<8>(P, op, smem + P.off_attn, cta, n_ctas, seq - 1, seq, W); break;
                     }
                 }
             } else {
@@ -549,38 +610,48 @@ __global__ void __launch_bounds__((NCONS + 1) * 32, 1) decode_mega_kernel(const 
                 const GemvJob J = op.job[sh.ji];
                 const int r0 = sh.r0, r1 = sh.r1, RW = J.RW, KS = J.KS, qtype = J.qtype;
                 const int op_epi = op.epilogue, op_gelu = op.act_gelu;
-                const float* op_resid = op.resid;
+                const uint2* op_resid = op.resid_ll;
+                uint2* out_ll = op.out_ll[sh.ji];
                 const bool paired = J.w2 != nullptr;
                 const int sz0 = seg_bytes(qtype, J.seg_base), sz1 = seg_bytes(qtype, J.seg_base + 1);
-                mega_quantize_input<NT, QITEMS>(op.x, op.norm_w, op.eps, op.norm_add_one, op.K, xq, xs, xsf, xsf32, misc);
+                if (sh.nitems > 0)
+                    mega_quantize_input<NT, QITEMS>(op.x_ll, seq0 + (uint32_t)op.src_op, op.norm_w, op.eps, op.norm_add_one, op.K, xq, xs,
+                                                    xsf, xsf32, misc, W);
                 stamp(oi, 2);
                 const int grp = lane >> 2, lane4 = lane & 3;
                 const int gprw = 8 / RW;
                 const int my_row = grp % RW, my_j = grp / RW;
                 float best_v = -INFINITY;
                 int best_i = 0x7fffffff;
+                bool ok = true;
                 auto epilogue = [&](int n, float v0, float v1) {
                     if (J.bias) v0 += J.bias[n];
+                    float r = v0;
                     switch (op_epi) {
-                        case EPI_STORE: J.out[n] = v0; break;
-                        case EPI_RESID: J.out[n] = __ldcg(op_resid + n) + v0; break;
-                        case EPI_GATED: J.out[n] = (op_gelu ? gelu_tanh(v0) : silu(v0)) * v1; break;
+                        case EPI_STORE: break;
+                        case EPI_RESID: r = __uint_as_float(ld_ll(op_resid + n).x) + v0; break;
+                        case EPI_GATED: r = (op_gelu ? gelu_tanh(v0) : silu(v0)) * v1; break;
                         case EPI_ARGMAX:
                             if (P.logits) P.logits[n] = v0;
                             if (v0 > best_v || (v0 == best_v && n < best_i)) { best_v = v0; best_i = n; }
-                            break;
+                            return;
                     }
+                    if (J.out) J.out[n] = r;
+                    if (out_ll) st_ll(out_ll + n, __float_as_uint(r), seq);
                 };
+                long long c_wait = 0, c_dot = 0, c_epi = 0;
+                const bool prof = P.trace && cta == 0 && warp == 0;
+                uint32_t slot = (gbase + (uint32_t)warp) % NS, phase = ((gbase + (uint32_t)warp) / NS) & 1u;
                 for (int it = warp; it < sh.nitems; it += NCONS) {
-                    const uint32_t gidx = gbase + (uint32_t)it;
-                    const uint32_t slot = gidx % NS;
+                    const long long c0 = prof ? clock64() : 0;
                     const MegaItem g = mega_geom(J, r0, r1, it, sz0, sz1);
                     if (ok) {
                         if (*abort_flag) ok = false;
-                        else if (!mbar_wait(&full[slot], (gidx / NS) & 1u, P.status)) { *abort_flag = 1; ok = false; }
+                        else if (!mbar_wait(&full[slot], phase, P.status)) { *abort_flag = 1; ok = false; }
                     }
                     const uint8_t* tile = ring + (size_t)slot * P.slot_bytes;
                     float a0 = 0.f, a1 = 0.f;
+                    const long long c1 = prof ? clock64() : 0;
                     if (ok && my_row < g.rows) {
                         const uint8_t* rowp = tile + (size_t)my_row * g.sb;
                         const int8_t* xq_s = xq + g.boff * 256;
@@ -588,21 +659,17 @@ __global__ void __launch_bounds__((NCONS + 1) * 32, 1) decode_mega_kernel(const 
                         const float* xsf_s = xsf + g.boff * 16;
                         const float* xsf32_s = xsf32 + g.boff * 8;
                         const bool swap = (grp & 1) && (((g.sb >> 4) & 1) == 0);
+                        const size_t poff = (size_t)RW * g.sb;
                         if (qtype == QT_Q4K) {
-#pragma unroll 1
-                            for (int b = my_j; b < g.nb; b += gprw) {
-                                a0 += q4k_dot(rowp + b * 144, lane4, swap, xq_s + b * 256, xs_s + b * 8, xsf32_s + b * 8);
-                                if (paired) a1 += q4k_dot(rowp + RW * g.sb + b * 144, lane4, swap, xq_s + b * 256, xs_s + b * 8, xsf32_s + b * 8);
-                            }
+                            if (paired) tile_dots<QT_Q4K, true>(rowp, poff, g.nb, my_j, gprw, lane4, swap, xq_s, xs_s, xsf_s, xsf32_s, a0, a1);
+                            else tile_dots<QT_Q4K, false>(rowp, poff, g.nb, my_j, gprw, lane4, swap, xq_s, xs_s, xsf_s, xsf32_s, a0, a1);
                         } else {
-#pragma unroll 1
-                            for (int b = my_j; b < g.nb; b += gprw) {
-                                a0 += q6k_dot(rowp, g.nb, b, lane4, swap, xq_s + b * 256, xs_s + b * 8, xsf_s + b * 16);
-                                if (paired) a1 += q6k_dot(rowp + RW * g.sb, g.nb, b, lane4, swap, xq_s + b * 256, xs_s + b * 8, xsf_s + b * 16);
-                            }
+                            if (paired) tile_dots<QT_Q6K, true>(rowp, poff, g.nb, my_j, gprw, lane4, swap, xq_s, xs_s, xsf_s, xsf32_s, a0, a1);
+                            else tile_dots<QT_Q6K, false>(rowp, poff, g.nb, my_j, gprw, lane4, swap, xq_s, xs_s, xsf_s, xsf32_s, a0, a1);
                         }
                     }
                     __syncwarp();
+                    const long long c2 = prof ? clock64() : 0;
                     if (lane == 0 && ok) mbar_arrive(&empty[slot]);      // the slot may be refilled
 #pragma unroll
                     for (int o = 1; o < 32; o <<= 1) {
@@ -619,7 +686,11 @@ __global__ void __launch_bounds__((NCONS + 1) * 32, 1) decode_mega_kernel(const 
                             if (paired) acc[(size_t)(r1 - r0) * KS + (size_t)(n - r0) * KS + g.s] = a1;
                         }
                     }
+                    if (prof) { __syncwarp(); const long long c3 = clock64(); c_wait += c1 - c0; c_dot += c2 - c1; c_epi += c3 - c2; }
+                    slot += NCONS;                         // NCONS < NS: at most one wrap per step
+                    if (slot >= (uint32_t)NS) { slot -= NS; phase ^= 1u; }
                 }
+                if (prof && lane == 0) { P.trace[(size_t)oi * 8 + 5] = c_wait; P.trace[(size_t)oi * 8 + 6] = c_dot; P.trace[(size_t)oi * 8 + 7] = c_epi; }
                 gbase += (uint32_t)sh.nitems;
                 stamp(oi, 3);
                 if (KS > 1) {
@@ -677,6 +748,7 @@ __global__ void __launch_bounds__((NCONS + 1) * 32, 1) decode_mega_kernel(const 
                             for (int w = 1; w < NCONS; ++w)
                                 if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) { bv = sv[w]; bi = si[w]; }
                             *P.ticket = 0u;
+                            *P.gen = gen + 1u;
                             bi += P.row_offset;
                             P.result[0] = bi;
                             reinterpret_cast<float*>(P.result)[1] = bv;
@@ -695,12 +767,7 @@ __global__ void __launch_bounds__((NCONS + 1) * 32, 1) decode_mega_kernel(const 
                 }
             }
             stamp(oi, 4);
-            // ---- this CTA is done with the op: publish
-            if (oi + 1 < P.n_ops) {
-                cons_sync<NT>();                     // every consumer thread's stores are ordered before thread 0's release
-                if (tid == 0) { __threadfence(); red_release_gpu_add(P.bar, 1u); }
-                bar_target += (unsigned)n_ctas;
-            }
+            cons_sync<NT>();       // shared memory (quantised input, accumulators) is rewritten by the next op
         }
     }
     __syncthreads();
