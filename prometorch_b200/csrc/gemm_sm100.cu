@@ -129,7 +129,12 @@ PTB_API int ptb_gemm_bf16_ex(void* const* a_ptrs, int a_shards, int a_shard_rows
     }
     Params p;
     memset(&p, 0, sizeof(p));
-    if (flags & EPI_SCATTER_ADD) {
+    // flags bits 8..15: this rank's slot for EPI_SCATTER_STORE
+    const int scatter_rank = (flags >> 8) & 0xff;
+    flags &= 0xff;
+    if (flags & (EPI_SCATTER_ADD | EPI_SCATTER_STORE)) {
+        if ((flags & EPI_SCATTER_STORE) && ((ldc * 2) & 15)) { ptb_set_error("gemm: scatter-store needs a 16-byte row pitch"); return -1; }
+        p.scatter_rank = scatter_rank;
         if (c_shards < 1 || c_shards > MAX_SHARDS || out_shard_rows % BM) {
             ptb_set_error("gemm: scatter-add needs 1..8 output shards of a multiple of %d rows", BM);
             return -1;

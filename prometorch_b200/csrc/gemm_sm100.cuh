@@ -26,7 +26,7 @@ constexpr int TMEM_COLS = 512;
 
 constexpr int MAX_SHARDS = 8;
 
-enum EpiFlags : int { EPI_BIAS = 1, EPI_ACCUM = 2, EPI_OUT_F32 = 4, EPI_GELU = 8, EPI_SCATTER_ADD = 16 };
+enum EpiFlags : int { EPI_BIAS = 1, EPI_ACCUM = 2, EPI_OUT_F32 = 4, EPI_GELU = 8, EPI_SCATTER_ADD = 16, EPI_SCATTER_STORE = 32 };
 
 // An operand whose stored matrix is split by rows over up to eight GPUs (each piece in that GPU's
 // memory, mapped here): piece r holds stored rows [r*shard_rows, (r+1)*shard_rows).  The producer warp
@@ -64,8 +64,11 @@ struct Params {
     int tiles_m, tiles_n;
     // EPI_SCATTER_ADD (GEMM -> reduce-scatter): output rows [r*out_shard_rows, ...) belong to rank r and are
     // added (fp32 atomics over NVLink) into that rank's buffer c_peer[r] of shape [out_shard_rows, ldc]
+    // EPI_SCATTER_STORE: the same ownership, but each rank writes its bf16 partial tile into slot [scatter_rank] of
+    // the owner's buffer ([world][out_shard_rows][ldc] bf16) with 16-byte stores; the owner sums the slots afterwards
     float* c_peer[MAX_SHARDS];
     int out_shard_rows;
+    int scatter_rank;
     int stager_ctas;        // CTAs [0, stager_ctas) are stagers (lowest indices: dispatched first); the rest compute tiles
     Staging stA, stB;
 };
@@ -346,6 +349,22 @@ gemm_bf16_kernel(const __grid_constant__ Operand opA, const __grid_constant__ Op
                         const int owner = row / P.out_shard_rows;
                         float* cp = P.c_peer[owner] + (size_t)(row - owner * P.out_shard_rows) * P.ldc + col;
                         for (int j = 0; j < 32 && col + j < P.N; ++j) atomicAdd(cp + j, v[j]);
+                    } else if (P.flags & EPI_SCATTER_STORE) {
+                        const int owner = row / P.out_shard_rows;
+                        __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(P.c_peer[owner]) +
+                                            ((size_t)P.scatter_rank * P.out_shard_rows + (row - owner * P.out_shard_rows)) * P.ldc + col;
+                        if (col + 32 <= P.N) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                uint4 o;
+                                __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) oh[e] = __floats2bfloat162_rn(v[j + 2 * e], v[j + 2 * e + 1]);
+                                *reinterpret_cast<uint4*>(cp + j) = o;
+                            }
+                        } else {
+                            for (int j = 0; j < 32 && col + j < P.N; ++j) cp[j] = __float2bfloat16_rn(v[j]);
+                        }
                     } else if (P.flags & EPI_OUT_F32) {
                         float* cp = reinterpret_cast<float*>(P.C) + (size_t)row * P.ldc + col;
                         if (col + 32 <= P.N) {

@@ -6,8 +6,9 @@ Two implementations with the same numerics:
   and the NCCL baseline on GPUs);
 * fused path (``tp.symm`` set, CUDA bf16) — the collective is folded into the tcgen05 GEMM:
   all-gather -> GEMM reads each A (or B) tile straight from the peer that owns those tokens through
-  a per-peer TMA tensor map; GEMM -> reduce-scatter adds each output tile into its owner's fp32
-  buffer over NVLink from the epilogue.  Activations to be read by peers are staged in symmetric
+  a per-peer TMA tensor map or staged once per launch by a few CTAs; GEMM -> reduce-scatter stores each
+  bf16 output tile into this rank's slot of its owner's buffer over NVLink from the epilogue (16-byte
+  stores; the owner sums the slots).  Activations to be read by peers are staged in symmetric
   memory (one local copy), and flag barriers order "written" before "read".
 """
 from __future__ import annotations
@@ -19,7 +20,7 @@ import torch
 
 from ... import _native as N
 from ...distributed.ddp import PeerChannel, _ptr_array
-from ...ops.gemm import EPI_OUT_F32, EPI_SCATTER_ADD, _status, gemm_bf16, linear as fused_linear
+from ...ops.gemm import EPI_OUT_F32, EPI_SCATTER_ADD, EPI_SCATTER_STORE, _status, gemm_bf16, linear as fused_linear
 
 
 @N.register_decls
@@ -46,11 +47,13 @@ def make_staging(buf, flags: torch.Tensor, rank: int, world: int, shard_rows: in
 
 
 def gemm_ex(a_ptrs, a_shard_rows, lda, a_mn, b_ptrs, b_shard_rows, ldb, b_mn, M, Nn, K, device, out=None, c_peers=None,
-            out_shard_rows=0, ldc=None, out_dtype=torch.bfloat16, accumulate=False, stage_a=None, stage_b=None):
-    """Raw access to the sharded-operand GEMM.  ``a_ptrs`` / ``b_ptrs``: lists of device addresses."""
+            out_shard_rows=0, ldc=None, out_dtype=torch.bfloat16, accumulate=False, stage_a=None, stage_b=None, scatter_slot=None):
+    """Raw access to the sharded-operand GEMM.  ``a_ptrs`` / ``b_ptrs``: lists of device addresses.
+    ``c_peers``: the output is scattered to its owners, added with fp32 atomics, or (``scatter_slot`` = this rank)
+    stored as bf16 into slot ``scatter_slot`` of the owner's ``[world][out_shard_rows][ldc]`` buffer."""
     flags = 0
     if c_peers is not None:
-        flags |= EPI_SCATTER_ADD
+        flags |= EPI_SCATTER_ADD if scatter_slot is None else (EPI_SCATTER_STORE | (int(scatter_slot) << 8))
         cp, nc, cptr = _ptr_array(c_peers), len(c_peers), 0
     else:
         if out is None:
@@ -80,7 +83,7 @@ class _Site:
         # full-size activation buffer [rows*W, cols]: this rank's tokens are rows [rank*rows, ...), the peers'
         # rows are staged in by the GEMM that consumes them
         self.act = PeerChannel(symm, rows * W * cols_act * 2) if cols_act else None
-        self.acc = PeerChannel(symm, rows * cols_acc * 4) if cols_acc else None
+        self.acc = PeerChannel(symm, max(rows * cols_acc * 4, rows * W * cols_acc * 2)) if cols_acc else None
         self.chan = self.act or self.acc
         self.cols_act = cols_act
         self.stage_flags = torch.zeros((rows * W + 127) // 128, dtype=torch.int32, device=symm.device)
@@ -129,7 +132,9 @@ class _ColumnSP(torch.autograd.Function):
         y = gemm_ex([full.data_ptr()], 0, K, False, [w.data_ptr()], 0, w.stride(0), False, n * W, w.shape[0], K, x.device, stage_a=st)
         if bias is not None:
             y = y + bias
-        ctx.save_for_backward(w, full)
+        # the site's buffer is overwritten by the next call at this site (another micro-batch of a pipeline, a
+        # recomputation): the gathered activations that dW needs are kept in a tensor of their own
+        ctx.save_for_backward(w, full.clone())
         ctx.site, ctx.tp, ctx.n, ctx.has_bias = site, tp, n, bias is not None
         return y
 
@@ -141,16 +146,16 @@ class _ColumnSP(torch.autograd.Function):
         dy = dy.contiguous()
         # dW[out/W, in] = dY^T gather(X): X was gathered into the local buffer by the forward GEMM, read MN-major
         dw = gemm_ex([dy.data_ptr()], 0, dy.stride(0), True, [full.data_ptr()], 0, K, True, w.shape[0], K, n * W, dev)
-        # dX = reduce_scatter_tokens(dY Wc): the epilogue adds each tile into its owner's fp32 buffer
-        acc = site.acc.buf.tensor(torch.float32)[:n * K].view(n, K)
-        acc.zero_()
-        site.barrier()                                   # all accumulators are zero, all dW reads of X are done
+        # dX = reduce_scatter_tokens(dY Wc): the epilogue stores each bf16 tile into this rank's slot of the owner's
+        # buffer over NVLink; the owner then sums the slots (no atomics, nothing to zero)
+        parts = site.acc.buf.tensor(torch.bfloat16)[:W * n * K].view(W, n, K)
+        site.barrier()                                   # the owners are done reading the previous contents
         c_peers = [site.acc.buf.peer_ptr(r) for r in range(W)]
         gemm_ex([dy.data_ptr()], 0, dy.stride(0), False, [w.data_ptr()], 0, w.stride(0), True, n * W, K, w.shape[0], dev,
-                c_peers=c_peers, out_shard_rows=n, ldc=K)
+                c_peers=c_peers, out_shard_rows=n, ldc=K, scatter_slot=tp.rank)
         site.barrier()                                   # every peer's contribution has landed
         db = dy.float().sum(0).to(dy.dtype) if ctx.has_bias else None
-        return acc.to(torch.bfloat16), dw, db, None, None
+        return parts.sum(0, dtype=torch.float32).to(torch.bfloat16), dw, db, None, None
 
 
 class _RowSP(torch.autograd.Function):
@@ -162,17 +167,16 @@ class _RowSP(torch.autograd.Function):
         W = tp.world_size
         n, out = nfull // W, w.shape[0]
         site = _site(tp, ("row", key), n, out, out)
-        acc = site.acc.buf.tensor(torch.float32)[:n * out].view(n, out)
-        acc.zero_()
-        site.barrier()
+        parts = site.acc.buf.tensor(torch.bfloat16)[:W * n * out].view(W, n, out)
+        site.barrier()                                   # the owners are done reading the previous contents
         c_peers = [site.acc.buf.peer_ptr(r) for r in range(W)]
         z = z.contiguous()
         gemm_ex([z.data_ptr()], 0, z.stride(0), False, [w.data_ptr()], 0, w.stride(0), False, nfull, out, Kl, z.device,
-                c_peers=c_peers, out_shard_rows=n, ldc=out)
-        site.barrier()
+                c_peers=c_peers, out_shard_rows=n, ldc=out, scatter_slot=tp.rank)
+        site.barrier()                                   # every rank's partial tiles have landed
         ctx.save_for_backward(z, w)
         ctx.site, ctx.tp, ctx.n = site, tp, n
-        return acc.to(torch.bfloat16)
+        return parts.sum(0, dtype=torch.float32).to(torch.bfloat16)
 
     @staticmethod
     def backward(ctx, dy):

@@ -59,24 +59,30 @@ class PipelineScheduleConfig:
 
 class Pipeline1F1BStage:
     def __init__(self, stage_module: nn.Module, cfg: PipelineScheduleConfig, stage_id: int, process_group=None,
-                 prev_rank: Optional[int] = None, next_rank: Optional[int] = None, act_shape=None, act_dtype=None):
+                 prev_rank: Optional[int] = None, next_rank: Optional[int] = None, act_shape=None, act_dtype=None,
+                 grad_process_group=None):
+        """``grad_process_group``: a second group over the same ranks for the gradient traffic.  NCCL runs the
+        point-to-point calls of one communicator in issue order, and in 1F1B a stage's next activation send and
+        its neighbour's gradient send cross; on separate communicators neither waits for the other."""
         self.stage, self.cfg, self.id = stage_module, cfg, stage_id
         self.pg = process_group
+        self.pg_grad = grad_process_group if grad_process_group is not None else process_group
         self.prev = prev_rank if prev_rank is not None else stage_id - 1
         self.next = next_rank if next_rank is not None else stage_id + 1
         self.act_shape, self.act_dtype = act_shape, act_dtype
         self.first, self.last = stage_id == 0, stage_id == cfg.num_stages - 1
 
     # -- p2p helpers
-    def _send(self, t, dst):
+    def _send(self, t, dst, pg=None):
         # non-blocking: in 1F1B a stage's forward send and its neighbour's backward send cross each other
+        pg = pg if pg is not None else self.pg
         t = t.contiguous()
-        w = self.pg.isend(t, dst) if hasattr(self.pg, "isend") else self.pg.send(t, dst)
+        w = pg.isend(t, dst) if hasattr(pg, "isend") else pg.send(t, dst)
         self._inflight.append((w, t))
 
-    def _recv(self, shape, dtype, device, src):
+    def _recv(self, shape, dtype, device, src, pg=None):
         t = torch.empty(shape, dtype=dtype, device=device)
-        self.pg.recv(t, src)
+        (pg if pg is not None else self.pg).recv(t, src)
         return t
 
     def run(self, input_first_stage: Optional[torch.Tensor] = None, loss_fn: Optional[Callable] = None,
@@ -113,10 +119,10 @@ class Pipeline1F1BStage:
             if self.last:
                 y.backward()
             else:
-                g = self._recv(y.shape, y.dtype, dev, self.next)
+                g = self._recv(y.shape, y.dtype, dev, self.next, self.pg_grad)
                 y.backward(g)
             if not self.first:
-                self._send(saved_in[mb].grad, self.prev)
+                self._send(saved_in[mb].grad, self.prev, self.pg_grad)
             saved_in[mb] = saved_out[mb] = None
 
         f = b = 0

@@ -141,17 +141,23 @@ def _seeded_full(out_f: int, in_f: int, seed: int, with_bias: bool):
 
 class ColumnParallelLinear(nn.Module):
     def __init__(self, in_features: int, out_features: int, tp: TPConfig, gather_output: bool = True, bias: bool = True,
-                 init_seed: int = 1234567, sequence_parallel: bool = False):
+                 init_seed: Optional[int] = 1234567, sequence_parallel: bool = False, device=None, dtype=None):
+        """``init_seed=None`` initialises only the local shard, directly on ``device`` (large models: the full
+        matrix is never materialised); with a seed every rank cuts its shard out of the same full matrix."""
         super().__init__()
         if out_features % tp.world_size:
             raise ValueError("ColumnParallelLinear: out_features must be divisible by world_size")
         self.in_features, self.out_features, self.tp = in_features, out_features, tp
         self.gather_output, self.sequence_parallel = gather_output, sequence_parallel
         self.shard = out_features // tp.world_size
-        w, b = _seeded_full(out_features, in_features, init_seed, bias)
         r = tp.rank
-        self.weight = nn.Parameter(w[r * self.shard:(r + 1) * self.shard].clone())
-        self.bias = nn.Parameter(b[r * self.shard:(r + 1) * self.shard].clone()) if bias else None
+        if init_seed is None:
+            self.weight = nn.Parameter(torch.empty(self.shard, in_features, device=device, dtype=dtype).normal_(std=0.02))
+            self.bias = nn.Parameter(torch.zeros(self.shard, device=device, dtype=dtype)) if bias else None
+        else:
+            w, b = _seeded_full(out_features, in_features, init_seed, bias)
+            self.weight = nn.Parameter(w[r * self.shard:(r + 1) * self.shard].clone().to(device=device, dtype=dtype))
+            self.bias = nn.Parameter(b[r * self.shard:(r + 1) * self.shard].clone().to(device=device, dtype=dtype)) if bias else None
 
     def forward(self, x):
         tp = self.tp
@@ -173,17 +179,21 @@ class ColumnParallelLinear(nn.Module):
 
 class RowParallelLinear(nn.Module):
     def __init__(self, in_features: int, out_features: int, tp: TPConfig, input_is_parallel: bool = True, bias: bool = True,
-                 init_seed: int = 7654321, sequence_parallel: bool = False):
+                 init_seed: Optional[int] = 7654321, sequence_parallel: bool = False, device=None, dtype=None):
         super().__init__()
         if in_features % tp.world_size:
             raise ValueError("RowParallelLinear: in_features must be divisible by world_size")
         self.in_features, self.out_features, self.tp = in_features, out_features, tp
         self.input_is_parallel, self.sequence_parallel = input_is_parallel, sequence_parallel
         self.shard = in_features // tp.world_size
-        w, b = _seeded_full(out_features, in_features, init_seed, bias)
         r = tp.rank
-        self.weight = nn.Parameter(w[:, r * self.shard:(r + 1) * self.shard].clone())
-        self.bias = nn.Parameter(b.clone()) if bias else None       # added once, after the reduction
+        if init_seed is None:
+            self.weight = nn.Parameter(torch.empty(out_features, self.shard, device=device, dtype=dtype).normal_(std=0.02))
+            self.bias = nn.Parameter(torch.zeros(out_features, device=device, dtype=dtype)) if bias else None
+        else:
+            w, b = _seeded_full(out_features, in_features, init_seed, bias)
+            self.weight = nn.Parameter(w[:, r * self.shard:(r + 1) * self.shard].clone().to(device=device, dtype=dtype))
+            self.bias = nn.Parameter(b.clone().to(device=device, dtype=dtype)) if bias else None       # added once, after the reduction
 
     def forward(self, x):
         tp = self.tp

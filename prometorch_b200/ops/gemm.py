@@ -14,7 +14,7 @@ import torch
 
 from .. import _native as N
 
-EPI_BIAS, EPI_ACCUM, EPI_OUT_F32, EPI_GELU, EPI_SCATTER_ADD = 1, 2, 4, 8, 16
+EPI_BIAS, EPI_ACCUM, EPI_OUT_F32, EPI_GELU, EPI_SCATTER_ADD, EPI_SCATTER_STORE = 1, 2, 4, 8, 16, 32
 
 
 @N.register_decls

@@ -95,15 +95,19 @@ class ShardedLinear(nn.Module):
         self.grad_full = self.grad_ch.buf.tensor(torch.bfloat16)[:self.S * W * self.inf].view(self.S * W, self.inf)
         self.grad_full.zero_()
         self.symm = symm
-        self._staging = None
+        self._staged_seq = 0
         self.step_count = 0
         symm.barrier()
 
     def staging(self):
-        if self._staging is None or self._staging.seq != self.stage_seq:
-            self._staging = make_staging(self.shard_ch.buf, self.stage_flags, self.symm.rank, self.symm.world, self.S,
-                                         self.S * self.symm.world, self.inf * 2, self.stage_seq)
-        return self._staging
+        """Staging request for the first GEMM that touches the weight after an optimizer step; ``None`` afterwards:
+        that launch copied every peer block (its stagers walk the whole matrix), later launches on the same
+        stream read the local copy with the full grid."""
+        if self._staged_seq == self.stage_seq:
+            return None
+        self._staged_seq = self.stage_seq
+        return make_staging(self.shard_ch.buf, self.stage_flags, self.symm.rank, self.symm.world, self.S,
+                            self.S * self.symm.world, self.inf * 2, self.stage_seq)
 
     def forward(self, x):
         return _ShardedLinearFn.apply(x, self)
