@@ -27,9 +27,14 @@ class LightningModule(nn.Module):
         return self.validation_step(batch, batch_idx)
 
     def configure_optimizer(self):
+        """Return the optimizer, or ``(optimizer, scheduler)``.  ``configure_optimizers`` is the same hook under
+        the plural name; override either."""
+        if type(self).configure_optimizers is not LightningModule.configure_optimizers:
+            return self.configure_optimizers()
         raise NotImplementedError
 
-    configure_optimizers = configure_optimizer
+    def configure_optimizers(self):
+        return self.configure_optimizer()
 
     def on_train_start(self): ...
     def on_train_end(self): ...
@@ -120,7 +125,9 @@ class Trainer:
         for i, batch in enumerate(loader):
             out = module.validation_step(self._to(batch, dev), i)
             if out is not None:
-                tot += float(out if not isinstance(out, dict) else out.get("loss", 0.0))
+                if isinstance(out, dict):
+                    out = out["loss"] if "loss" in out else next(iter(out.values()))
+                tot += float(out)
                 n += 1
         return {f"{prefix}_loss": tot / max(n, 1)}
 

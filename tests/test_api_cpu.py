@@ -1,0 +1,298 @@
+"""CPU tests of the framework surface around the kernels: serialization, AMP, trainer, quantization, export,
+JIT wrapper, domain shims, metrics/profiler, tokenizer/chat/model resolution."""
+import json
+import math
+import os
+
+import pytest
+import torch
+import torch.nn as nn
+
+import prometorch_b200 as pt
+from prometorch_b200 import amp, audio, autograd, data, jit, mlir, mobile, onnx, quantization as Q, serialization as S, text, trainer
+from prometorch_b200.io import chat, ollama
+from prometorch_b200.io.tokenizer import GGUFTokenizer
+from prometorch_b200.utils import metrics, profiler
+
+
+# ----------------------------------------------------------------------------- serialization
+def test_ptor_roundtrip(tmp_path):
+    sd = {"w": torch.randn(3, 5), "b": torch.arange(4, dtype=torch.int64), "h": torch.randn(2, 2).to(torch.bfloat16)}
+    p = str(tmp_path / "m.ptor")
+    S.save_state_dict(sd, p)
+    with open(p, "rb") as f:
+        assert f.read(4) == b"PTOR"
+    back = S.load_state_dict(p)
+    assert list(back) == list(sd)
+    for k in sd:
+        assert back[k].dtype == sd[k].dtype and torch.equal(back[k], sd[k])
+    S.save(sd["w"], str(tmp_path / "t.ptor"))
+    assert torch.equal(S.load(str(tmp_path / "t.ptor")), sd["w"])
+
+
+def test_pytorch_checkpoint_interop(tmp_path):
+    m = nn.Linear(4, 3)
+    p = str(tmp_path / "m.pt")
+    S.save_pytorch(m.state_dict(), p)
+    theirs = torch.load(p, weights_only=True)              # a file we wrote is a regular PyTorch checkpoint
+    assert torch.equal(theirs["weight"], m.weight)
+    torch.save({"x": torch.ones(2)}, str(tmp_path / "t.pt"))
+    assert torch.equal(S.load_pytorch(str(tmp_path / "t.pt"))["x"], torch.ones(2))
+
+
+# ----------------------------------------------------------------------------- AMP
+def test_grad_scaler_skips_on_inf_and_backs_off():
+    w = nn.Parameter(torch.ones(4))
+    opt = pt.optim.SGD([w], lr=0.1)
+    sc = amp.GradScaler(init_scale=1024.0, growth_interval=2)
+    loss = (w * 2).sum()
+    sc.scale(loss).backward()
+    assert torch.allclose(w.grad, torch.full((4,), 2048.0))
+    sc.step(opt)
+    sc.update()
+    assert torch.allclose(w.detach(), torch.full((4,), 0.8))             # unscaled gradient 2 was applied
+    w.grad = torch.tensor([float("inf"), 0.0, 0.0, 0.0])
+    before = w.detach().clone()
+    sc.step(opt)
+    sc.update()
+    assert torch.equal(w.detach(), before) and sc.get_scale() == 512.0   # step skipped, scale halved
+    st = sc.state_dict()
+    sc2 = amp.GradScaler()
+    sc2.load_state_dict(st)
+    assert sc2.get_scale() == 512.0
+
+
+def test_autocast_guard_cpu():
+    a, b = torch.randn(8, 8), torch.randn(8, 8)
+    with amp.AutocastGuard("cpu", torch.bfloat16):
+        c = a @ b
+    assert c.dtype == torch.bfloat16
+
+
+# ----------------------------------------------------------------------------- autograd helpers
+def test_checkpoint_and_hooks_and_anomaly():
+    lin = nn.Linear(4, 4)
+    x = torch.randn(2, 4, requires_grad=True)
+    y = autograd.checkpoint(lambda t: torch.relu(lin(t)), x)
+    seen = []
+    autograd.register_hook(y, lambda g: seen.append(g.shape))
+    y.sum().backward()
+    assert seen == [y.shape] and x.grad is not None and lin.weight.grad is not None
+    autograd.AnomalyMode.set_enabled(True)
+    assert autograd.AnomalyMode.is_enabled()
+    autograd.AnomalyMode.set_enabled(False)
+
+
+# ----------------------------------------------------------------------------- trainer + data
+class _Lit(trainer.LightningModule):
+    def __init__(self):
+        super().__init__()
+        self.net = nn.Sequential(nn.Linear(16, 32), nn.ReLU(), nn.Linear(32, 4))
+
+    def forward(self, x):
+        return self.net(x)
+
+    def training_step(self, batch, idx):
+        x, y = batch
+        return nn.functional.cross_entropy(self(x), y)
+
+    def validation_step(self, batch, idx):
+        x, y = batch
+        return {"val_loss": nn.functional.cross_entropy(self(x), y)}
+
+    def configure_optimizers(self):
+        return pt.optim.Adam(self.parameters(), lr=1e-2)
+
+
+def test_trainer_fits_and_resumes(tmp_path):
+    torch.manual_seed(0)
+    ds = data.SyntheticImages(n=256, dim=16, classes=4)
+    dl = torch.utils.data.DataLoader(ds, batch_size=32, shuffle=False)
+    m = _Lit()
+    with torch.no_grad():
+        l0 = sum(float(m.training_step(b, 0)) for b in dl) / len(dl)
+    tr = trainer.Trainer(trainer.TrainerConfig(max_epochs=3, checkpoint_dir=str(tmp_path), gradient_clip_val=1.0, accumulate_grad_batches=2))
+    tr.fit(m, dl, dl)
+    with torch.no_grad():
+        l1 = sum(float(m.training_step(b, 0)) for b in dl) / len(dl)
+    assert l1 < l0
+    ck = str(tmp_path / "last.ckpt")
+    tr.save_checkpoint(m, ck)
+    m2 = _Lit()
+    tr2 = trainer.Trainer(trainer.TrainerConfig(max_epochs=1, checkpoint_dir=str(tmp_path)))
+    tr2.load_checkpoint(m2, ck)
+    for a, b in zip(m.parameters(), m2.parameters()):
+        assert torch.equal(a, b)
+
+
+def test_synthetic_tokens_dataset():
+    ds = data.SyntheticTokens(n=10, seq_len=8, vocab=50, seed=1)
+    x, y = ds[3]
+    assert x.shape == (8,) and y.shape == (8,) and int(x.max()) < 50 and torch.equal(x[1:], y[:-1])
+    md = data.MapDataset(ds, lambda s: (s[0] + 1, s[1]))
+    assert torch.equal(md[3][0], x + 1)
+
+
+# ----------------------------------------------------------------------------- quantization
+def test_4bit_and_int8_quantization():
+    torch.manual_seed(0)
+    w = torch.randn(64, 128)
+    for kind in ("nf4", "fp4"):
+        packed, absmax = Q.quantize_4bit(w, 64, kind)
+        assert packed.dtype == torch.uint8 and packed.numel() == w.numel() // 2
+        back = Q.dequantize_4bit(packed, absmax, w.shape, 64, kind)
+        assert (back - w).abs().mean() < 0.15
+    lin = nn.Linear(128, 64)
+    q = Q.Linear4bit(lin)
+    x = torch.randn(4, 128)
+    assert (q(x) - lin(x)).abs().mean() < 0.2
+    aq, asc = Q.quantize_per_tensor(x)
+    bq, bsc = Q.quantize_per_tensor(w)
+    assert (Q.int8_matmul(aq, asc, bq.t().contiguous(), bsc) - x @ w.t()).abs().max() < 0.5
+
+
+def test_qat_prepare_convert():
+    torch.manual_seed(0)
+    m = nn.Sequential(nn.Linear(8, 16), nn.ReLU(), nn.Linear(16, 4))
+    x = torch.randn(32, 8)
+    ref = m(x)
+    qm = Q.prepare_qat(m)
+    qm.train()
+    qm(x).sum().backward()                                   # observers see data, gradients flow through fake-quant
+    Q.freeze_observers(qm)
+    cm = Q.convert(qm)
+    cm.eval()
+    assert (cm(x) - ref).abs().max() < 0.2
+
+
+# ----------------------------------------------------------------------------- export / jit
+def test_exporters_write_files(tmp_path):
+    m = nn.Sequential(nn.Linear(8, 16), nn.ReLU(), nn.Linear(16, 4))
+    p = str(tmp_path / "m.onnx")
+    onnx.export_mlp(m, (1, 8), p)
+    assert os.path.getsize(p) > 8 * 16 * 4
+    txt = mlir.export(m, (1, 8), str(tmp_path / "m.mlir"))
+    assert "func.func" in txt and "linalg" in txt or "tosa" in txt or "arith" in txt
+    mp = str(tmp_path / "m.ptmb")
+    mobile.save(m, mp)
+    ex = mobile.Executor(mp)
+    x = torch.randn(3, 8)
+    assert torch.allclose(ex.run(x), m(x), atol=1e-5)
+
+
+def _affine(t: torch.Tensor) -> torch.Tensor:
+    return t * 2 + 1
+
+
+def test_jit_wrappers_keep_semantics():
+    m = nn.Sequential(nn.Linear(8, 8), nn.Tanh())
+    x = torch.randn(2, 8)
+    cm = jit.compile(m)
+    assert torch.allclose(cm(x), m(x))
+    f = jit.script(_affine)
+    assert torch.equal(f(x), x * 2 + 1)
+    g = jit.trace(lambda t: t.relu(), (x,))
+    assert torch.equal(g(x), x.relu())
+
+
+# ----------------------------------------------------------------------------- domain shims
+def test_text_tokenizers():
+    v = text.Vocab(["hello", "world"])
+    ids = v.encode("hello there world")
+    assert v.decode(ids) == "hello <unk> world"
+    bpe = text.BPETokenizer()
+    bpe.train(["low lower lowest", "new newer newest"] * 5, 60)
+    s = "lower newest"
+    assert bpe.decode(bpe.encode(s)) == s
+    wp = text.WordPieceTokenizer(["un", "##aff", "##able", "[UNK]"])
+    assert wp.tokenize("unaffable") == ["un", "##aff", "##able"]
+
+
+def test_audio_stft_roundtrip_and_wav(tmp_path):
+    t = torch.arange(16000) / 16000.0
+    x = torch.sin(2 * math.pi * 440 * t)
+    spec = audio.stft(x)
+    y = audio.istft(spec, length=x.numel())
+    assert (x - y)[400:-400].abs().max() < 1e-3
+    assert audio.mfcc(x).shape[0] == 13
+    assert audio.mel_filterbank(40, 400, 16000).shape == (40, 201)
+    assert abs(audio.resample(x, 16000, 8000).numel() - 8000) <= 1
+    p = str(tmp_path / "a.wav")
+    audio.save_wav(p, x, 16000)
+    z, sr = audio.load_wav(p)
+    assert sr == 16000 and (z - x).abs().max() < 1e-3
+
+
+def test_vision_models_forward():
+    from prometorch_b200 import vision
+    x = torch.randn(2, 3, 32, 32)
+    assert vision.ResNet20(num_classes=10)(x).shape == (2, 10)
+
+
+# ----------------------------------------------------------------------------- metrics / profiler
+def test_metrics_writer_and_profiler(tmp_path):
+    p = str(tmp_path / "m.jsonl")
+    w = metrics.MetricsWriter(p)
+    w.log(step=1, loss=2.5)
+    w.roofline("copy", seconds=1e-3, bytes_moved=1e9)
+    w.close()
+    rows = [json.loads(l) for l in open(p)]
+    assert rows[0]["loss"] == 2.5 and 0.1 < rows[1]["fraction"] < 0.2
+    prof = profiler.InferenceProfiler()
+    prof.enable(True)
+    prof.begin("qkv")
+    prof.end("qkv")
+    prof.count_tokens(3)
+    assert "qkv" in prof.totals()
+    t = profiler.Timer()
+    assert t.elapsed_ms() >= 0.0
+
+
+# ----------------------------------------------------------------------------- tokenizer / chat / model resolution
+def test_gguf_tokenizer_spm_and_gpt2():
+    toks = ["<unk>", "<s>", "</s>"] + [f"<0x{b:02X}>" for b in range(256)] + ["▁", "h", "e", "l", "o", "▁h", "el", "lo", "▁hel", "▁hello", "w", "▁w"]
+    scores = [0.0] * 259 + [-1.0, -2, -2, -2, -2, -1.5, -1.4, -1.3, -1.2, -1.0, -2, -1.6]
+    types = [2, 3, 3] + [6] * 256 + [1] * 12
+    tk = GGUFTokenizer(toks, "llama", scores, None, types, bos_id=1, eos_id=2, add_bos=True)
+    ids = tk.encode("hello w")
+    assert ids[0] == 1 and tk.decode(ids) == "hello w"
+    assert tk.decode(tk.encode("héllo", add_bos=False)) == "héllo"         # byte fallback
+    from prometorch_b200.io.tokenizer import _B2U
+    base = [_B2U[b] for b in range(256)]
+    merges = ["h e", "l l", "he ll", "hell o", "Ġ w"]
+    vocab = base + ["he", "ll", "hell", "hello", "Ġw", "<|im_start|>"]
+    g2 = GGUFTokenizer(vocab, "gpt2", None, merges, [1] * (len(vocab) - 1) + [3])
+    ids = g2.encode("<|im_start|>hello w")
+    assert ids[0] == len(vocab) - 1 and vocab[ids[1]] == "hello"
+    assert g2.decode(ids, skip_special=False) == "<|im_start|>hello w"
+
+
+def test_chat_templates():
+    q = chat.apply_chat_template("hi", "qwen3", no_think=True)
+    assert "/no_think<|im_end|>" in q and "<|im_start|>user\nhi<|im_end|>" in q and q.endswith("<|im_start|>assistant\n")
+    g = chat.apply_chat_template("hi", "gemma3")
+    assert "<start_of_turn>user" in g and g.rstrip().endswith("<start_of_turn>model")
+    l3 = chat.apply_chat_template("hi", "llama", model_name="llama3.1", system="be brief")
+    assert "<|start_header_id|>system<|end_header_id|>" in l3
+    r = chat.render_messages([{"role": "system", "content": "s"}, {"role": "user", "content": "u"}], "qwen3")
+    assert r.index("system") < r.index("user")
+    assert chat.strip_think("<think>plan</think>answer") == "answer"
+
+
+def test_ollama_resolution(tmp_path):
+    root = tmp_path / "models"
+    man = root / "manifests" / "registry.ollama.ai" / "library" / "qwen3"
+    man.mkdir(parents=True)
+    digest = "sha256:" + "ab" * 32
+    (man / "4b").write_text(json.dumps({"layers": [{"mediaType": "application/vnd.ollama.image.model", "digest": digest, "size": 4}]}))
+    (root / "blobs").mkdir()
+    blob = root / "blobs" / digest.replace(":", "-")
+    blob.write_bytes(b"GGUF")
+    assert ollama.resolve_model("qwen3:4b", str(root)) == str(blob)
+    direct = tmp_path / "x.gguf"
+    direct.write_bytes(b"GGUF")
+    assert ollama.resolve_model(str(direct)) == str(direct)
+    names = [m["name"] for m in ollama.list_models(str(root))]
+    assert "qwen3:4b" in names
+    with pytest.raises(FileNotFoundError):
+        ollama.resolve_model("nope:1b", str(root))

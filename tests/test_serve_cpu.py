@@ -1,0 +1,111 @@
+"""PromeServe over real sockets with a fake model backend: routes, NDJSON streaming, chat, errors, LLMEngine."""
+import http.client
+import json
+
+import pytest
+
+from prometorch_b200.serve import LLMEngine, ModelBackend, PromeServe, ServerConfig
+
+
+class EchoBackend(ModelBackend):
+    """Token = one character; generation spells a fixed answer."""
+    name, architecture, model_name, size, parameter_size = "echo:1b", "qwen3", "echo", 1234, "1B"
+    answer = "hello world"
+
+    def encode(self, text):
+        return [ord(c) for c in text]
+
+    def decode_token(self, tid):
+        return chr(tid)
+
+    def generate(self, prompt_ids, options, on_token):
+        self.last_prompt = "".join(chr(t) for t in prompt_ids)
+        self.last_options = dict(options)
+        for c in self.answer[:int(options.get("num_predict", 128))]:
+            if not on_token(ord(c)):
+                break
+        return 0.001, 0.002
+
+
+@pytest.fixture()
+def server():
+    be = EchoBackend()
+    srv = PromeServe(ServerConfig(host="127.0.0.1", port=0, worker_threads=2), {"echo:1b": be}).start()
+    yield srv, be
+    srv.stop()
+
+
+def _req(port, method, path, body=None):
+    c = http.client.HTTPConnection("127.0.0.1", port, timeout=20)
+    c.request(method, path, None if body is None else json.dumps(body), {"Content-Type": "application/json"})
+    r = c.getresponse()
+    data = r.read()
+    c.close()
+    return r.status, dict(r.getheaders()), data
+
+
+def test_basic_routes(server):
+    srv, _ = server
+    st, hdr, data = _req(srv.port, "GET", "/")
+    assert st == 200 and b"PromeServe is running" in data
+    st, hdr, data = _req(srv.port, "GET", "/api/version")
+    assert st == 200 and "version" in json.loads(data)
+    st, hdr, data = _req(srv.port, "GET", "/api/tags")
+    assert st == 200 and any(m["name"] == "echo:1b" for m in json.loads(data)["models"])
+    st, hdr, data = _req(srv.port, "POST", "/api/show", {"name": "echo:1b"})
+    assert st == 200
+    st, hdr, data = _req(srv.port, "POST", "/api/embeddings", {"model": "echo:1b", "prompt": "x"})
+    assert st == 501
+    st, hdr, data = _req(srv.port, "GET", "/nope")
+    assert st == 404
+    st, hdr, data = _req(srv.port, "OPTIONS", "/api/generate")
+    assert st == 204 and hdr.get("Access-Control-Allow-Origin") == "*"
+
+
+def test_generate_non_streaming_and_options(server):
+    srv, be = server
+    st, _, data = _req(srv.port, "POST", "/api/generate", {"model": "echo:1b", "prompt": "hi", "stream": False, "raw": True,
+                                                          "options": {"num_predict": 5, "temperature": 0.0}})
+    out = json.loads(data)
+    assert st == 200 and out["response"] == "hello" and out["done"] is True and out["eval_count"] == 5
+    assert be.last_prompt == "hi" and int(be.last_options["num_predict"]) == 5
+    assert out["model"] == "echo:1b" and "total_duration" in out
+
+
+def test_generate_streams_ndjson(server):
+    srv, _ = server
+    st, hdr, data = _req(srv.port, "POST", "/api/generate", {"model": "echo:1b", "prompt": "hi"})
+    assert st == 200 and "ndjson" in hdr.get("Content-Type", "")
+    lines = [json.loads(l) for l in data.decode().splitlines() if l.strip()]
+    assert "".join(l.get("response", "") for l in lines) == "hello world"
+    assert lines[-1]["done"] is True and all(not l["done"] for l in lines[:-1])
+
+
+def test_chat_applies_template(server):
+    srv, be = server
+    st, _, data = _req(srv.port, "POST", "/api/chat", {"model": "echo:1b", "stream": False,
+                                                      "messages": [{"role": "system", "content": "be brief"}, {"role": "user", "content": "hey"}]})
+    out = json.loads(data)
+    assert st == 200 and out["message"]["role"] == "assistant" and out["message"]["content"] == "hello world"
+    assert "<|im_start|>system\nbe brief<|im_end|>" in be.last_prompt and be.last_prompt.endswith("<|im_start|>assistant\n")
+
+
+def test_errors(server):
+    srv, _ = server
+    st, _, data = _req(srv.port, "POST", "/api/generate", {"model": "missing:7b", "prompt": "x", "stream": False})
+    assert st == 404 and "error" in json.loads(data)
+    c = http.client.HTTPConnection("127.0.0.1", srv.port, timeout=20)
+    c.request("POST", "/api/generate", "{not json", {"Content-Type": "application/json"})
+    r = c.getresponse()
+    assert r.status == 400
+    c.close()
+
+
+def test_llm_engine_queue():
+    eng = LLMEngine(EchoBackend())
+    a = eng.submit_request("one", max_tokens=3)
+    b = eng.submit_request("two", max_tokens=5)
+    assert eng.step() == 3
+    assert eng.poll_responses() == {a: [ord(c) for c in "hel"]}
+    assert eng.step() == 5 and list(eng.poll_responses()) == [b]
+    assert eng.generate(["x", "y"], max_tokens=4) == ["hell", "hell"]
