@@ -378,13 +378,21 @@ class GGUFModel:
             if n > 1:
                 self.run_script(prompt[:-1], 1)
             tok, pos = int(prompt[-1]), n - 1
-        from ..ops.sampling import sample_logits
+        from ..ops.sampling import MAX_DEVICE_TOP_K, DeviceSampler, sample_logits
         gen = torch.Generator(device=self.device)
         gen.manual_seed(seed)
         history = list(int(t) for t in (_history if _history is not None else prompt))
+        # top-k up to 64: the whole sampler is one kernel on the device (only the chosen id comes back);
+        # wider or unbounded top-k goes through tensor ops
+        sampler = None
+        if not greedy and 1 <= top_k <= MAX_DEVICE_TOP_K:
+            sampler = DeviceSampler(self.logits_view().numel(), self.device, seed=seed)
+            sampler.reset(history)
         for _ in range(max_new_tokens):
             nxt = self.forward_decode(tok, pos)
-            if not greedy:
+            if sampler is not None:
+                nxt = sampler.sample(self.logits_view(), temperature, top_k, top_p, repeat_penalty)
+            elif not greedy:
                 nxt = sample_logits(self.logits_view(), temperature, top_k, top_p, repeat_penalty, history, gen)
             out.append(nxt)
             history.append(nxt)

@@ -132,3 +132,40 @@ def test_engine_scripted_equals_stepped(tiny_model):
     b = m.generate(prompt, 20)
     assert a == b
     m.close()
+
+
+# ----------------------------------------------------------------------------- device sampler
+@pytest.mark.parametrize("V,top_k,top_p,temp,pen", [(151936, 40, 0.9, 0.7, 1.1), (32000, 64, 1.0, 1.3, 1.0), (1000, 5, 0.5, 0.2, 1.3),
+                                                    (4096, 1, 0.9, 0.8, 1.0), (151936, 40, 0.9, 0.0, 1.2)])
+def test_device_sampler_matches_oracle(V, top_k, top_p, temp, pen):
+    from prometorch_b200.ops.sampling import DeviceSampler, sample_reference
+    torch.manual_seed(V + top_k)
+    dev = torch.device("cuda", 0)
+    samp = DeviceSampler(V, dev, seed=1)
+    hist = torch.randint(0, V, (300,)).tolist()
+    samp.reset(hist)
+    for trial in range(6):
+        logits = (torch.randn(V) * 3).to(dev)
+        logits[hist[trial]] += 12.0                       # a history token at the top: the penalty matters
+        u = [0.0, 0.13, 0.5, 0.77, 0.95, 0.9999][trial]
+        got = samp.sample(logits, temp, top_k, top_p, pen, u=u)
+        want = sample_reference(logits, temp, top_k, top_p, pen, hist, u)
+        assert got == want, (trial, got, want)
+        hist.append(got)                                  # the kernel appended its choice to the device history
+
+
+def test_device_sampler_distribution():
+    from prometorch_b200.ops.sampling import DeviceSampler
+    dev = torch.device("cuda", 0)
+    V = 5000
+    logits = torch.full((V,), -20.0, device=dev)
+    logits[[7, 99, 4000]] = torch.tensor([2.0, 1.0, 0.0], device=dev)
+    samp = DeviceSampler(V, dev, seed=3)
+    counts = {}
+    for _ in range(600):
+        t = samp.sample(logits, 1.0, 3, 1.0)
+        counts[t] = counts.get(t, 0) + 1
+    p = torch.softmax(torch.tensor([2.0, 1.0, 0.0]), 0)
+    assert set(counts) <= {7, 99, 4000}
+    for tid, pi in zip([7, 99, 4000], p.tolist()):
+        assert abs(counts.get(tid, 0) / 600 - pi) < 0.07
