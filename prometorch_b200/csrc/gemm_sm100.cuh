@@ -105,28 +105,57 @@ __device__ __forceinline__ bool wait_staged(const Staging& S, int r0, int nrows,
 }
 
 // Stager CTA: copy 128-row blocks that belong to other ranks from their memory into the local buffer.
-__device__ __forceinline__ void run_stager(const Staging& S, int stager, int n_stagers) {
-    if (S.seq == 0) return;
+// One thread drives the TMA engine: bulk loads from the peer into a ring of shared-memory slots, bulk stores
+// from there to local memory, `NSLOT` pieces of up to `SLOT_BYTES` in flight, so that a handful of CTAs keeps
+// NVLink busy.  `bar`: NSLOT mbarriers initialised with count 1; `ring`: NSLOT slots of SLOT_STRIDE bytes.
+__device__ __forceinline__ void bulk_s2g(void* dst, const void* src_smem, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(smem_u32(src_smem)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+template <int N> __device__ __forceinline__ void bulk_wait() { asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <int NSLOT, int SLOT_STRIDE>
+__device__ __forceinline__ void run_stager(const Staging& S, int stager, int n_stagers, uint8_t* ring, uint64_t* bar, uint32_t& uses,
+                                           int* status) {
+    if (S.seq == 0 || threadIdx.x != 0) return;
+    constexpr uint32_t SLOT_BYTES = 32768;
+    static_assert(SLOT_STRIDE >= (int)SLOT_BYTES, "a pipeline stage must hold one staging piece");
     const int nblk = (S.stored_rows + STAGE_ROWS - 1) / STAGE_ROWS;
     for (int blk = stager; blk < nblk; blk += n_stagers) {
         const int r0 = blk * STAGE_ROWS, r1 = min(r0 + STAGE_ROWS, S.stored_rows);
         const int owner = r0 / S.shard_rows;
-        if (owner != S.rank && (int32_t)(ld_acquire_gpu(S.flags + blk) - S.seq) < 0) {
-            const uint4* src = S.peer[owner] + (long long)r0 * S.row_vec;
-            uint4* dst = S.local + (long long)r0 * S.row_vec;
-            const long long n = (long long)(r1 - r0) * S.row_vec;
-            for (long long i = threadIdx.x; i < n; i += 4 * THREADS) {      // four loads in flight per thread
-                uint4 v[4];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) if (i + u * THREADS < n) v[u] = __ldcg(src + i + u * THREADS);
-#pragma unroll
-                for (int u = 0; u < 4; ++u) if (i + u * THREADS < n) dst[i + u * THREADS] = v[u];
-            }
-            __threadfence();
+        if (owner == S.rank || (int32_t)(ld_acquire_gpu(S.flags + blk) - S.seq) >= 0) continue;
+        const uint8_t* src = reinterpret_cast<const uint8_t*>(S.peer[owner] + (long long)r0 * S.row_vec);
+        uint8_t* dst = reinterpret_cast<uint8_t*>(S.local + (long long)r0 * S.row_vec);
+        const long long total = (long long)(r1 - r0) * S.row_vec * 16;
+        const int npieces = (int)((total + SLOT_BYTES - 1) / SLOT_BYTES);
+        auto piece_bytes = [&](int q) { return (uint32_t)min((long long)SLOT_BYTES, total - (long long)q * SLOT_BYTES); };
+        auto load = [&](int q) {       // piece q of this block into slot (uses + q) % NSLOT
+            const uint32_t slot = (uses + (uint32_t)q) % NSLOT;
+            mbar_expect_tx(&bar[slot], piece_bytes(q));
+            bulk_g2s(ring + (size_t)slot * SLOT_STRIDE, src + (long long)q * SLOT_BYTES, piece_bytes(q), &bar[slot]);
+        };
+        for (int q = 0; q < min(NSLOT - 1, npieces); ++q) load(q);
+        bool ok = true;
+        for (int q = 0; q < npieces && ok; ++q) {
+            const uint32_t u = uses + (uint32_t)q, slot = u % NSLOT;
+            ok = mbar_wait(&bar[slot], (u / NSLOT) & 1u, status);
+            if (!ok) break;
             fence_proxy_async_all();
-            __syncthreads();
-            if (threadIdx.x == 0) st_release_gpu(S.flags + blk, S.seq);
+            bulk_s2g(dst + (long long)q * SLOT_BYTES, ring + (size_t)slot * SLOT_STRIDE, piece_bytes(q));
+            bulk_commit();
+            if (q + NSLOT - 1 < npieces) {
+                bulk_wait_read<1>();          // the store of piece q-1 has read its slot: that slot takes piece q+NSLOT-1
+                load(q + NSLOT - 1);
+            }
         }
+        uses += (uint32_t)npieces;
+        bulk_wait<0>();                       // every store of this block has completed
+        if (!ok) return;
+        fence_proxy_async_all();
+        __threadfence();
+        st_release_gpu(S.flags + blk, S.seq);
     }
 }
 
@@ -230,8 +259,10 @@ gemm_bf16_kernel(const __grid_constant__ Operand opA, const __grid_constant__ Op
     const int cta = (int)blockIdx.x - P.stager_ctas;
     if (cta < 0) {
         // ---------------------------------------------------------------------- stager CTA (no TMEM, no tiles)
-        run_stager(P.stA, blockIdx.x, P.stager_ctas);
-        run_stager(P.stB, blockIdx.x, P.stager_ctas);
+        __syncthreads();                      // the pipeline barriers are initialised
+        uint32_t uses = 0;
+        run_stager<STAGES, S::STAGE_BYTES>(P.stA, blockIdx.x, P.stager_ctas, smem, full, uses, P.status);
+        run_stager<STAGES, S::STAGE_BYTES>(P.stB, blockIdx.x, P.stager_ctas, smem, full, uses, P.status);
         return;
     }
     if (warp == 1) {
