@@ -79,6 +79,12 @@ def _declare(L: C.CDLL):
     L.ptb_engine_launches_per_token.restype = cl
     L.ptb_gemv_plan.argtypes = [ci, ci, ci, ci, ci, ci, C.POINTER(ci)]
     L.ptb_gemv_plan.restype = ci
+    L.ptb_engine_kv_cache.argtypes = [vp, ci, C.POINTER(vp), C.POINTER(vp)]
+    L.ptb_engine_kv_cache.restype = ci
+    L.ptb_dequant_segmajor.argtypes = [vp, ci, ci, ci, vp, vp]
+    L.ptb_dequant_segmajor.restype = ci
+    L.ptb_dequant_rows.argtypes = [vp, ci, ci, ci, vp, ci, cf, ci, vp, vp, vp]
+    L.ptb_dequant_rows.restype = ci
 
 
 def lib(build_if_missing: bool = True) -> C.CDLL:

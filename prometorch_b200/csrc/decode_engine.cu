@@ -836,6 +836,15 @@ PTB_API void* ptb_engine_stream(void* h) { return (void*)((Engine*)h)->stream; }
 PTB_API void* ptb_engine_logits(void* h) { return (void*)((Engine*)h)->logits; }
 PTB_API void* ptb_engine_hidden(void* h) { return (void*)((Engine*)h)->x; }
 PTB_API void* ptb_engine_result(void* h) { return (void*)((Engine*)h)->result; }
+// Device addresses of layer `layer`'s fp16 K and V caches, each [kv_heads][max_seq][head_dim].
+PTB_API int ptb_engine_kv_cache(void* h, int layer, void** k, void** v) {
+    Engine* e = (Engine*)h;
+    if (layer < 0 || layer >= e->m.n_layers) { ptb_set_error("layer %d out of range", layer); return -1; }
+    const size_t per = (size_t)e->m.n_kv_heads * e->m.max_seq * e->m.head_dim;
+    *k = e->kc + per * layer;
+    *v = e->vc + per * layer;
+    return 0;
+}
 PTB_API long ptb_engine_launches_per_token(void* h) { return ((Engine*)h)->launches_per_token; }
 PTB_API int ptb_engine_kv_bytes(void* h, long* out) {
     Engine* e = (Engine*)h;

@@ -872,7 +872,7 @@ struct EmbedParams {
     uint32_t* gen;       // bumped once per token (tensor-parallel generation counter) or null
 };
 
-__global__ void __launch_bounds__(256) embed_kernel(const __grid_constant__ EmbedParams P) {
+static __global__ void __launch_bounds__(256) embed_kernel(const __grid_constant__ EmbedParams P) {
     pdl_launch_dependents();
     pdl_wait();
     int tok = P.ctrl[CTRL_TOKEN];

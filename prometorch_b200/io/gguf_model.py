@@ -311,8 +311,8 @@ class GGUFModel:
         class _Arr:
             pass
         a = _Arr()
-        a.__cuda_array_interface__ = {"shape": (n,), "typestr": "<f4" if dtype == torch.float32 else "<i4",
-                                      "data": (addr, False), "version": 3}
+        typestr = {torch.float32: "<f4", torch.float16: "<f2", torch.int32: "<i4"}[dtype]
+        a.__cuda_array_interface__ = {"shape": (n,), "typestr": typestr, "data": (addr, False), "version": 3}
         return torch.as_tensor(a, device=self.device)
 
     def logits_view(self) -> torch.Tensor:
@@ -331,6 +331,99 @@ class GGUFModel:
         if t < 0:
             raise N.NativeError("decode step: " + self._lib.ptb_last_error().decode())
         return t
+
+    # ------------------------------------------------------------------ batched prompt pass
+    @property
+    def supports_prefill(self) -> bool:
+        """The batched prompt pass covers one GPU, full attention (no sliding window), head size 64/128."""
+        return self.tp_world == 1 and not self.cfg.swa_window and self.cfg.head_dim in (64, 128)
+
+    def _dequant(self, pw: "PackedWeight") -> torch.Tensor:
+        """bf16 ``[rows, cols]`` copy of a packed matrix in a scratch buffer shared by all matrices of that shape."""
+        key = (pw.rows, pw.cols)
+        buf = self._dq_scratch.get(key)
+        if buf is None:
+            buf = self._dq_scratch[key] = torch.empty(pw.rows, pw.cols, dtype=torch.bfloat16, device=self.device)
+        st = torch.cuda.current_stream(self.device).cuda_stream
+        N.check(self._lib.ptb_dequant_segmajor(pw.data.data_ptr(), pw.qtype, pw.rows, pw.cols, buf.data_ptr(), st), "dequant")
+        return buf
+
+    def _kv_views(self, layer: int):
+        k, v = C.c_void_p(), C.c_void_p()
+        N.check(self._lib.ptb_engine_kv_cache(self._engine, layer, C.byref(k), C.byref(v)), "kv_cache")
+        n = self.local_kv_heads * self.max_seq * self.cfg.head_dim
+        shape = (self.local_kv_heads, self.max_seq, self.cfg.head_dim)
+        return self._wrap(k.value, n, torch.float16).view(shape), self._wrap(v.value, n, torch.float16).view(shape)
+
+    @torch.no_grad()
+    def prefill(self, tokens: Sequence[int], pos0: int = 0):
+        """Run ``tokens`` at positions ``pos0 ..`` through the model in ONE batched pass that fills the KV cache:
+        weights are dequantised to bf16 layer by layer and every projection is a tcgen05 GEMM over all prompt
+        tokens, attention is the FlashAttention kernel.  Nothing is returned; decoding continues with
+        ``forward_decode(next_token, pos0 + len(tokens))``.  (Token-by-token prefill costs one decode step each.)"""
+        if not self.supports_prefill:
+            raise NotImplementedError("batched prefill: one GPU, no sliding window")
+        from ..ops import fused_ops as K
+        from ..ops.attention import flash_attention
+        from ..ops.gemm import linear
+        cfg, dev = self.cfg, self.device
+        T = len(tokens)
+        if T == 0:
+            return
+        if pos0 + T > self.max_seq:
+            raise ValueError(f"prompt of {T} tokens at {pos0} exceeds max_seq {self.max_seq}")
+        self.capture()
+        N.check(self._lib.ptb_engine_sync(self._engine), "sync")
+        if not hasattr(self, "_dq_scratch"):
+            self._dq_scratch, self._pf_status = {}, torch.zeros(1, dtype=torch.int32, device=dev)
+        H, d, hq, hkv = cfg.hidden_size, cfg.head_dim, self.local_heads, self.local_kv_heads
+        eps, bf = cfg.rms_norm_eps, torch.bfloat16
+        st = torch.cuda.current_stream(dev).cuda_stream
+        ids = torch.as_tensor(list(int(t) for t in tokens), dtype=torch.int32, device=dev)
+        x = torch.empty(T, H, dtype=bf, device=dev)
+        e = self.embed
+        N.check(self._lib.ptb_dequant_rows(e.data.data_ptr(), e.qtype, e.rowbytes, H, ids.data_ptr(), T, float(self._model_desc.emb_scale),
+                                           e.rows, self._pf_status.data_ptr(), x.data_ptr(), st), "dequant_rows")
+
+        def nw(L, name):          # bf16 norm weight (gemma stores w - 1)
+            key = name + "_bf16"
+            if key not in L:
+                w = L[name]
+                L[key] = None if w is None else ((w + 1.0) if cfg.gemma_norm_add_one else w).to(bf)
+            return L[key]
+
+        def proj(h, pw):
+            y = linear(h, self._dequant(pw), None)
+            return y if pw.bias is None else y + pw.bias.to(bf)
+
+        for i, L in enumerate(self.layers):
+            h = K.rms_norm(x, nw(L, "attn_norm"), eps)
+            q = proj(h, L["q"]).view(T, hq, d)
+            k = proj(h, L["k"]).view(T, hkv, d)
+            v = proj(h, L["v"]).view(T, hkv, d)
+            if L["q_norm"] is not None:
+                q = K.rms_norm(q.reshape(-1, d), nw(L, "q_norm"), eps).view(T, hq, d)
+                k = K.rms_norm(k.reshape(-1, d), nw(L, "k_norm"), eps).view(T, hkv, d)
+            q = K.rope(q.unsqueeze(0), self.cos, self.sin, bool(cfg.rope_neox), pos0)
+            k = K.rope(k.unsqueeze(0), self.cos, self.sin, bool(cfg.rope_neox), pos0)
+            kc, vc = self._kv_views(i)
+            kc[:, pos0:pos0 + T] = k[0].permute(1, 0, 2).to(torch.float16)
+            vc[:, pos0:pos0 + T] = v.permute(1, 0, 2).to(torch.float16)
+            if pos0 > 0:          # earlier positions come from the cache
+                k_all = kc[:, :pos0 + T].permute(1, 0, 2).to(bf).unsqueeze(0).contiguous()
+                v_all = vc[:, :pos0 + T].permute(1, 0, 2).to(bf).unsqueeze(0).contiguous()
+            else:
+                k_all, v_all = k, v.unsqueeze(0)
+            att = flash_attention(q, k_all, v_all, causal=True, q_offset=pos0).reshape(T, hq * d)
+            x = x + proj(att, L["o"])
+            h = K.rms_norm(x, nw(L, "ffn_norm"), eps)
+            g, u = proj(h, L["gate"]), proj(h, L["up"]).clone()       # gate and up share a scratch shape: keep one
+            act = torch.nn.functional.gelu(g.float(), approximate="tanh") if cfg.ffn_gelu else torch.nn.functional.silu(g.float())
+            x = x + proj((act * u.float()).to(bf), L["down"])
+        torch.cuda.current_stream(dev).synchronize()
+        if int(self._pf_status):
+            self._pf_status.zero_()
+            raise N.NativeError("prefill: a token id fell outside the vocabulary")
 
     def run_script(self, prompt: Sequence[int], n_new: int, pos0: int = 0, sync: bool = True) -> Optional[List[int]]:
         """Enqueue prompt + ``n_new`` greedy tokens as back-to-back graph replays with the
@@ -366,6 +459,9 @@ class GGUFModel:
             stop.add(self.cfg.eos_token_id)
         greedy = temperature <= 0.0 and repeat_penalty == 1.0
         if greedy and on_token is None and not stop and _pos0 is None:
+            if self.supports_prefill and len(prompt) - 1 >= 8:
+                self.prefill(prompt[:-1])
+                return self.run_script(prompt[-1:], max_new_tokens, pos0=len(prompt) - 1)
             return self.run_script(prompt, max_new_tokens)
         if not greedy and not self.want_logits:
             raise RuntimeError("sampling needs the model opened with want_logits=True")
@@ -376,7 +472,10 @@ class GGUFModel:
             tok, pos = int(prompt[-1]), int(_pos0)
         else:
             if n > 1:
-                self.run_script(prompt[:-1], 1)
+                if self.supports_prefill and n - 1 >= 8:
+                    self.prefill(prompt[:-1])                  # one batched pass over the prompt
+                else:
+                    self.run_script(prompt[:-1], 1)
             tok, pos = int(prompt[-1]), n - 1
         from ..ops.sampling import MAX_DEVICE_TOP_K, DeviceSampler, sample_logits
         gen = torch.Generator(device=self.device)
