@@ -1,0 +1,326 @@
+// FlashAttention forward on the 5th-generation tensor cores: both products of every 128 x 128 block run as
+// tcgen05.mma with accumulators in tensor memory, operands arrive by TMA.
+//
+// One CTA per (128 query rows, head, batch).  Ten warps:
+//   warp 8   TMA producer: the Q tile once, then K and V tiles of 128 keys through two-stage rings;
+//   warp 9   owns tensor memory and issues the MMAs: S(j) = Q K_j^T into one of two 128-column buffers,
+//            then O_j = P_j V_j into a third buffer once the softmax warps have written P_j;
+//   warps 0-7  softmax.  A thread owns one query row (its tensor-memory lane) and half of the block's
+//            columns: it reads its 64 scores with tcgen05.ld, exchanges the row maximum with its partner
+//            thread through shared memory, writes the bf16 probabilities into a 128-byte-swizzled
+//            shared-memory tile (the A operand of the second product) and keeps its half of the output
+//            row in registers, rescaled by the running maximum.  The read-back of O_{j-1} is deferred
+//            until after the scores of block j have been reduced, so that it overlaps the MMA of P_{j-1} V.
+// Causal masking and the sequence end are applied to the blocks that need them only.  Every wait is
+// bounded.  The reference's kernel is aten/src/ATen/cuda/FlashAttention.cu:83-258 (one thread per row).
+#include "gemm_sm100.cuh"
+
+int ptb_make_tmap_bf16(CUtensorMap* map, const void* base, long long inner, long long outer, long long ld, int box_inner, int box_outer);
+
+namespace ptb {
+namespace fa100 {
+
+using namespace ptb::gemm;
+
+constexpr int BQ = 128, BKV = 128;
+constexpr int NTHREADS = 320;
+
+struct Params {
+    __nv_bfloat16* O;        // [B, Tq, H, D]
+    float* lse;              // [B, H, Tq] natural-log sum of exponentials
+    int B, Tq, Tk, H, Hk;
+    int causal, q_offset;
+    float scale_log2;        // softmax scale x log2(e)
+    int* status;
+};
+
+template <int D>
+struct Sm {
+    static constexpr int Q_BYTES = BQ * D * 2;
+    static constexpr int KV_BYTES = BKV * D * 2;
+    static constexpr int P_BYTES = BQ * BKV * 2;
+    static constexpr int OFF_Q = 0;
+    static constexpr int OFF_K = OFF_Q + Q_BYTES;
+    static constexpr int OFF_V = OFF_K + 2 * KV_BYTES;
+    static constexpr int OFF_P = OFF_V + 2 * KV_BYTES;
+    static constexpr int OFF_RED = OFF_P + P_BYTES;          // 2 x 128 floats
+    static constexpr int OFF_BAR = OFF_RED + 2 * BQ * 4;
+    static constexpr int TOTAL = OFF_BAR + 256 + 1024;
+};
+
+__device__ __forceinline__ void softmax_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+template <int D>
+__global__ void __launch_bounds__(NTHREADS, 1)
+fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+           const __grid_constant__ Params P) {
+    using S = Sm<D>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* sq = smem + S::OFF_Q;
+    uint8_t* sk = smem + S::OFF_K;
+    uint8_t* sv = smem + S::OFF_V;
+    uint8_t* sp = smem + S::OFF_P;
+    float* red = reinterpret_cast<float*>(smem + S::OFF_RED);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::OFF_BAR);
+    uint64_t* q_full = bars;             // [1]
+    uint64_t* k_full = bars + 1;         // [2]
+    uint64_t* k_empty = bars + 3;        // [2]
+    uint64_t* v_full = bars + 5;         // [2]
+    uint64_t* v_empty = bars + 7;        // [2]
+    uint64_t* s_full = bars + 9;         // [2]
+    uint64_t* p_ready = bars + 11;       // [1], 8 arrivals (one per softmax warp)
+    uint64_t* o_full = bars + 12;        // [1]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int qb = (int)gridDim.x - 1 - (int)blockIdx.x;           // long (late) query blocks first
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int hk = h / (P.H / P.Hk);
+    const int q0 = qb * BQ;
+    // keys this block can see: [0, kv_end)
+    const int kv_end = P.causal ? min(P.Tk, q0 + BQ + P.q_offset) : P.Tk;
+    const int nblk = max(0, (kv_end + BKV - 1) / BKV);
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < 2; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); mbar_init(&s_full[s], 1); }
+        mbar_init(p_ready, 8);
+        mbar_init(o_full, 1);
+        *abort_flag = 0;
+        mbar_fence_init();
+        prefetch_tmap(&tmQ);
+        prefetch_tmap(&tmK);
+        prefetch_tmap(&tmV);
+    }
+    if (warp == 9) {
+        tmem_alloc(tmem_slot, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t TM_S = 0, TM_O = 256;                           // column offsets: S buffers at 0 and 128, O_j at 256
+
+    if (warp == 8) {
+        // ---------------------------------------------------------------------------- TMA producer
+        if (lane == 0 && nblk > 0) {
+            bool ok = true;
+            mbar_expect_tx(q_full, S::Q_BYTES);
+            for (int kb = 0; kb < D / 64; ++kb) tma_load_2d(sq + kb * (BQ * 128), &tmQ, h * D + kb * 64, b * P.Tq + q0, q_full);
+            for (int j = 0; j < nblk && ok; ++j) {
+                const int s = j & 1;
+                if (j >= 2) ok = mbar_wait(&k_empty[s], (uint32_t)(((j >> 1) - 1) & 1), P.status);
+                if (!ok) break;
+                mbar_expect_tx(&k_full[s], S::KV_BYTES);
+                for (int kb = 0; kb < D / 64; ++kb)
+                    tma_load_2d(sk + s * S::KV_BYTES + kb * (BKV * 128), &tmK, hk * D + kb * 64, b * P.Tk + j * BKV, &k_full[s]);
+                if (j >= 2) ok = mbar_wait(&v_empty[s], (uint32_t)(((j >> 1) - 1) & 1), P.status);
+                if (!ok) break;
+                mbar_expect_tx(&v_full[s], S::KV_BYTES);
+                for (int hh = 0; hh < 2; ++hh)                       // two halves of 64 keys, each D/64 chunks of [64 keys x 64 dims]
+                    for (int c = 0; c < D / 64; ++c)
+                        tma_load_2d(sv + s * S::KV_BYTES + hh * (D / 64) * 8192 + c * 8192, &tmV, hk * D + c * 64, b * P.Tk + j * BKV + hh * 64,
+                                    &v_full[s]);
+            }
+            if (!ok) *abort_flag = 1;
+        }
+    } else if (warp == 9) {
+        // ---------------------------------------------------------------------------- MMA issuer
+        if (lane == 0 && nblk > 0) {
+            constexpr uint32_t idesc_s = instr_desc(BQ, BKV, 0, 0);          // S = Q K^T: both K-major
+            constexpr uint32_t idesc_o = instr_desc(BQ, D, 0, 1);            // O = P V: P K-major, V MN-major
+            bool ok = mbar_wait(q_full, 0, P.status);
+            auto issue_s = [&](int j) {
+                const int s = j & 1;
+                if (!mbar_wait(&k_full[s], (uint32_t)((j >> 1) & 1), P.status)) return false;
+                tc_fence_after();
+                const uint32_t a0 = smem_u32(sq), b0 = smem_u32(sk + s * S::KV_BYTES);
+#pragma unroll
+                for (int kb = 0; kb < D / 64; ++kb)
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        umma_bf16(tmem_base + TM_S + (uint32_t)(s * BKV), smem_desc(a0 + kb * (BQ * 128) + k * 32, 16, 1024),
+                                  smem_desc(b0 + kb * (BKV * 128) + k * 32, 16, 1024), idesc_s, (kb > 0 || k > 0) ? 1u : 0u);
+                umma_commit(&k_empty[s]);
+                umma_commit(&s_full[s]);
+                return true;
+            };
+            if (ok) ok = issue_s(0);
+            if (ok && nblk > 1) ok = issue_s(1);
+            for (int j = 0; j < nblk && ok; ++j) {
+                const int s = j & 1;
+                ok = mbar_wait(p_ready, (uint32_t)(j & 1), P.status);        // P_j is in shared memory, O_{j-1} has been read
+                if (ok) ok = mbar_wait(&v_full[s], (uint32_t)((j >> 1) & 1), P.status);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a0 = smem_u32(sp), b0 = smem_u32(sv + s * S::KV_BYTES);
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh)
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        umma_bf16(tmem_base + TM_O, smem_desc(a0 + hh * (BQ * 128) + k * 32, 16, 1024),
+                                  smem_desc(b0 + hh * (D / 64) * 8192 + k * 2048, 8192, 1024), idesc_o, (hh > 0 || k > 0) ? 1u : 0u);
+                umma_commit(&v_empty[s]);
+                umma_commit(o_full);
+                if (j + 2 < nblk) ok = issue_s(j + 2);
+            }
+            if (!ok) *abort_flag = 1;
+        }
+    } else {
+        // ---------------------------------------------------------------------------- softmax warps
+        const int row = 32 * (warp & 3) + lane;          // query row inside the block = tensor-memory lane
+        const int hf = warp >> 2;                        // which 64 columns of S, which D/2 columns of O
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(32 * (warp & 3)) << 16);
+        const int q_pos = q0 + row + P.q_offset;         // position of this query among the keys
+        float o_acc[D / 2];
+#pragma unroll
+        for (int i = 0; i < D / 2; ++i) o_acc[i] = 0.f;
+        float m_run = -INFINITY, l_part = 0.f, alpha_prev = 1.f;
+        bool ok = true;
+        auto add_o = [&](float alpha) {                  // o_acc = o_acc * alpha + (my half of the row of O_j)
+#pragma unroll
+            for (int c = 0; c < D / 64; ++c) {
+                uint32_t r[32];
+                tmem_ld32(lane_addr + TM_O + (uint32_t)(hf * (D / 2) + c * 32), r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] = o_acc[c * 32 + i] * alpha + __uint_as_float(r[i]);
+            }
+        };
+        for (int j = 0; j < nblk; ++j) {
+            const int s = j & 1;
+            if (ok && !*abort_flag) ok = mbar_wait(&s_full[s], (uint32_t)((j >> 1) & 1), P.status);
+            else ok = false;
+            tc_fence_after();
+            float sc[64];
+            {
+                uint32_t r[32];
+                tmem_ld32(lane_addr + TM_S + (uint32_t)(s * BKV + hf * 64), r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) sc[i] = __uint_as_float(r[i]) * P.scale_log2;
+                tmem_ld32(lane_addr + TM_S + (uint32_t)(s * BKV + hf * 64 + 32), r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) sc[32 + i] = __uint_as_float(r[i]) * P.scale_log2;
+            }
+            const int key0 = j * BKV + hf * 64;
+            const bool need_mask = (key0 + 64 > P.Tk) || (P.causal && key0 + 63 > q0 + P.q_offset);
+            if (need_mask) {
+#pragma unroll
+                for (int i = 0; i < 64; ++i) {
+                    const int key = key0 + i;
+                    if (key >= P.Tk || (P.causal && key > q_pos)) sc[i] = -INFINITY;
+                }
+            }
+            float mx = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < 64; ++i) mx = fmaxf(mx, sc[i]);
+            red[hf * BQ + row] = mx;
+            softmax_sync();
+            const float m_blk = fmaxf(red[row], red[BQ + row]);
+            const float m_new = fmaxf(m_run, m_blk);
+            const float m_use = m_new == -INFINITY ? 0.f : m_new;
+            const float alpha = exp2f(m_run - m_use);
+            float lsum = 0.f;
+            uint32_t pk[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                const float p0 = exp2f(sc[2 * i] - m_use), p1 = exp2f(sc[2 * i + 1] - m_use);
+                lsum += p0 + p1;
+                const __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
+                pk[i] = *reinterpret_cast<const uint32_t*>(&h2);
+            }
+            l_part = l_part * alpha + lsum;
+            m_run = m_new;
+            // the deferred read-back of O_{j-1}; its MMA ran while the scores above were reduced
+            if (j > 0) {
+                if (ok) ok = mbar_wait(o_full, (uint32_t)((j - 1) & 1), P.status);
+                tc_fence_after();
+                add_o(alpha_prev);
+            }
+            alpha_prev = alpha;
+            // P_j -> shared memory, K-major with the 128-byte swizzle: sub-tile hf, row `row`, 16-byte chunk c at c ^ (row & 7)
+            {
+                uint8_t* prow = sp + hf * (BQ * 128) + row * 128;
+#pragma unroll
+                for (int c = 0; c < 8; ++c)
+                    *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) * 16)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+            }
+            fence_proxy_async();
+            tc_fence_before();
+            softmax_sync();                   // also keeps `red` from being overwritten before both partners have read it
+            if (lane == 0) mbar_arrive(p_ready);
+        }
+        if (nblk > 0) {
+            if (ok) ok = mbar_wait(o_full, (uint32_t)((nblk - 1) & 1), P.status);
+            tc_fence_after();
+            add_o(alpha_prev);
+        }
+        red[hf * BQ + row] = l_part;
+        softmax_sync();
+        const float l = red[row] + red[BQ + row];
+        const int q_idx = q0 + row;
+        if (q_idx < P.Tq && ok) {
+            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            __nv_bfloat16* op = P.O + (((size_t)b * P.Tq + q_idx) * P.H + h) * D + hf * (D / 2);
+#pragma unroll
+            for (int i = 0; i < D / 2; i += 8) {
+                uint4 o;
+                __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) oh[e] = __floats2bfloat162_rn(o_acc[i + 2 * e] * inv, o_acc[i + 2 * e + 1] * inv);
+                *reinterpret_cast<uint4*>(op + i) = o;
+            }
+            if (hf == 0) P.lse[((size_t)b * P.H + h) * P.Tq + q_idx] = l > 0.f ? m_run * 0.6931471805599453f + logf(l) : -INFINITY;
+        }
+        if (!ok) *abort_flag = 1;
+    }
+    // ---- teardown
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 9) tmem_dealloc(tmem_base, 512);
+}
+
+template <int D>
+static int launch(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Tq, int Tk, int H, int Hk, int causal,
+                  float scale, int q_offset, int* status, cudaStream_t st) {
+    CUtensorMap mq, mk, mv;
+    if (ptb_make_tmap_bf16(&mq, q, (long long)H * D, (long long)B * Tq, (long long)H * D, 64, BQ)) return -1;
+    if (ptb_make_tmap_bf16(&mk, k, (long long)Hk * D, (long long)B * Tk, (long long)Hk * D, 64, BKV)) return -1;
+    if (ptb_make_tmap_bf16(&mv, v, (long long)Hk * D, (long long)B * Tk, (long long)Hk * D, 64, 64)) return -1;
+    static bool attr = false;
+    if (!attr) {
+        PTB_CUDA_OK(cudaFuncSetAttribute(fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Sm<D>::TOTAL));
+        attr = true;
+    }
+    Params p;
+    p.O = (__nv_bfloat16*)o; p.lse = lse; p.B = B; p.Tq = Tq; p.Tk = Tk; p.H = H; p.Hk = Hk; p.causal = causal; p.q_offset = q_offset;
+    p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
+    dim3 grid((Tq + BQ - 1) / BQ, H, B);
+    fwd_kernel<D><<<grid, NTHREADS, Sm<D>::TOTAL, st>>>(mq, mk, mv, p);
+    PTB_CUDA_OK(cudaGetLastError());
+    return 0;
+}
+
+}  // namespace fa100
+}  // namespace ptb
+
+// q [B, Tq, H, D], k/v [B, Tk, Hk, D] bf16 contiguous, D in {64, 128}; o like q; lse [B, H, Tq] fp32 (natural log).
+// status: device int, set non-zero if a wait timed out.
+PTB_API int ptb_flash_attn_fwd_sm100(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Tq, int Tk, int H, int Hk,
+                                     int D, int causal, float scale, int q_offset, int* status, cudaStream_t st) {
+    if (H % Hk) { ptb_set_error("flash attention: %d query heads over %d KV heads", H, Hk); return -1; }
+    {
+        int dev = 0;
+        PTB_CUDA_OK(cudaGetDevice(&dev));
+        PTB_CUDA_OK(cudaSetDevice(dev));     // the tensor-map encoder is a driver call: bind the primary context to this thread
+    }
+    if (D == 128) return ptb::fa100::launch<128>(q, k, v, o, lse, B, Tq, Tk, H, Hk, causal, scale, q_offset, status, st);
+    if (D == 64) return ptb::fa100::launch<64>(q, k, v, o, lse, B, Tq, Tk, H, Hk, causal, scale, q_offset, status, st);
+    ptb_set_error("flash attention (tcgen05): head size %d not supported (64, 128)", D);
+    return -1;
+}

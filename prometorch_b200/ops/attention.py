@@ -1,9 +1,10 @@
 """Attention front end: ``flash_attention(q, k, v, causal)`` on ``[B, T, heads, D]`` tensors with
 grouped-query heads (``heads_q`` a multiple of ``heads_kv``).
 
-CUDA bf16 inputs with D in {64, 128} run the hand-written FlashAttention kernels
-(csrc/flash_attn.cu: tiled online-softmax forward that also returns the log-sum-exp, and a
-recompute-based backward with the GQA reduction of dK/dV done inside the kernel).  ``q_offset`` /
+CUDA bf16 inputs with D in {64, 128} run the hand-written FlashAttention kernels: the forward on
+tcgen05 tensor cores with TMEM accumulators and TMA-fed tiles (csrc/flash_attn_sm100.cu; it also returns the
+log-sum-exp), the recompute-based backward with the GQA reduction of dK/dV done inside the kernel
+(csrc/flash_attn.cu, which also holds an mma.sync forward selected by PTB_FA_SM100=0).  ``q_offset`` /
 ``return_lse`` are the hooks a ring/context-parallel wrapper needs: blocks of K/V can be processed
 separately and merged by log-sum-exp.  CPU tensors use the plain softmax formulation.  The layout
 matches the reference's kernel, which also takes ``[B, N, H, D]`` (aten/src/ATen/native/Attention.h:244-250)."""
@@ -26,6 +27,15 @@ def _decls(L):
         L.ptb_flash_attn_fwd.restype = ci
         L.ptb_flash_attn_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, cf, ci, vp]
         L.ptb_flash_attn_bwd.restype = ci
+    if hasattr(L, "ptb_flash_attn_fwd_sm100"):
+        L.ptb_flash_attn_fwd_sm100.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, cf, ci, vp, vp]
+        L.ptb_flash_attn_fwd_sm100.restype = ci
+
+
+def _use_tcgen05() -> bool:
+    """The forward runs on tcgen05/TMEM (csrc/flash_attn_sm100.cu) unless PTB_FA_SM100=0 selects the mma.sync kernel."""
+    import os
+    return os.environ.get("PTB_FA_SM100", "1") != "0" and hasattr(N.lib(), "ptb_flash_attn_fwd_sm100")
 
 
 def attention_reference(q, k, v, causal=True, q_offset: int = 0, scale: Optional[float] = None):
@@ -56,8 +66,14 @@ class _Flash(torch.autograd.Function):
         o = torch.empty_like(q)
         lse = torch.empty(B, H, Tq, dtype=torch.float32, device=q.device)
         st = torch.cuda.current_stream(q.device).cuda_stream
-        N.check(N.lib().ptb_flash_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), B, Tq, Tk, H, Hk,
-                                           D, int(causal), scale, q_offset, st), "flash_attn_fwd")
+        if _use_tcgen05():
+            from .gemm import _status
+            N.check(N.lib().ptb_flash_attn_fwd_sm100(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), B, Tq, Tk,
+                                                     H, Hk, D, int(causal), scale, q_offset, _status(q.device).data_ptr(), st),
+                    "flash_attn_fwd_sm100")
+        else:
+            N.check(N.lib().ptb_flash_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), B, Tq, Tk, H, Hk,
+                                               D, int(causal), scale, q_offset, st), "flash_attn_fwd")
         ctx.save_for_backward(q, k, v, o, lse)
         ctx.causal, ctx.q_offset, ctx.scale = causal, q_offset, scale
         ctx.mark_non_differentiable(lse)
