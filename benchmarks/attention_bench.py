@@ -31,21 +31,29 @@ def timeit(fn, iters):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--shapes", nargs="*", default=["llama-1b", "llama-7b", "long"])
+    ap.add_argument("--tcgen05-fwd-only", action="store_true", help="time only the tcgen05 forward (profiling runs)")
     a = ap.parse_args()
     from prometorch_b200.ops.attention import flash_attention
     from prometorch_b200.ops.gemm import check_status
-    for name, (B, T, H, Hk, D) in {"llama-1b": (2, 2048, 32, 4, 64), "llama-7b": (1, 4096, 32, 32, 128), "long": (1, 16384, 8, 8, 128)}.items():
+    all_shapes = {"llama-1b": (2, 2048, 32, 4, 64), "llama-7b": (1, 4096, 32, 32, 128), "long": (1, 16384, 8, 8, 128)}
+    for name in a.shapes:
+        B, T, H, Hk, D = all_shapes[name]
         q = torch.randn(B, T, H, D, device="cuda").bfloat16().requires_grad_()
         k = torch.randn(B, T, Hk, D, device="cuda").bfloat16().requires_grad_()
         v = torch.randn(B, T, Hk, D, device="cuda").bfloat16().requires_grad_()
         flops = 4.0 * B * H * T * T * D / 2
         res = {"shape": name, "B": B, "T": T, "H": H, "Hk": Hk, "D": D}
-        for impl in ("1", "0"):
+        for impl in (("1",) if a.tcgen05_fwd_only else ("1", "0")):
             os.environ["PTB_FA_SM100"] = impl
             with torch.no_grad():
                 ms = timeit(lambda: flash_attention(q, k, v, causal=True), a.iters)
             res["fwd_tcgen05" if impl == "1" else "fwd_mma_sync"] = {"us": round(ms * 1e3, 1), "tflops": round(flops / ms / 1e9, 1)}
         os.environ["PTB_FA_SM100"] = "1"
+        if a.tcgen05_fwd_only:
+            check_status()
+            print(json.dumps(res), flush=True)
+            continue
         o = flash_attention(q, k, v, causal=True)
         do = torch.randn_like(o)
         ms = timeit(lambda: torch.autograd.grad(o, (q, k, v), do, retain_graph=True), a.iters)
