@@ -56,8 +56,11 @@ def main():
             continue
         o = flash_attention(q, k, v, causal=True)
         do = torch.randn_like(o)
-        ms = timeit(lambda: torch.autograd.grad(o, (q, k, v), do, retain_graph=True), a.iters)
-        res["bwd_mma_sync"] = {"us": round(ms * 1e3, 1), "tflops": round(2.5 * flops / ms / 1e9, 1)}
+        for impl in ("1", "0"):
+            os.environ["PTB_FA_BWD_SM100"] = impl
+            ms = timeit(lambda: torch.autograd.grad(o, (q, k, v), do, retain_graph=True), a.iters)
+            res["bwd_tcgen05" if impl == "1" else "bwd_mma_sync"] = {"us": round(ms * 1e3, 1), "tflops": round(2.5 * flops / ms / 1e9, 1)}
+        os.environ["PTB_FA_BWD_SM100"] = "1"
         check_status()
         print(json.dumps(res), flush=True)
 

@@ -373,6 +373,18 @@ static int run_bwd(const BwdParams& p, const void* o, cudaStream_t st) {
     return 0;
 }
 
+// delta[b, h, t] = sum_d dO * O (fp32 [B, H, Tq]): the row term of the softmax backward.
+PTB_API int ptb_flash_attn_delta(const void* o, const void* dout, float* delta, int B, int Tq, int H, int D, cudaStream_t st) {
+    const long long rows = (long long)B * Tq * H;
+    if (rows == 0) return 0;
+    const unsigned grid = (unsigned)((rows * 32 + 255) / 256);
+    if (D == 64) delta_kernel<64><<<grid, 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, delta, rows, H, Tq);
+    else if (D == 128) delta_kernel<128><<<grid, 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, delta, rows, H, Tq);
+    else { ptb_set_error("flash attention: head_dim %d not supported", D); return -1; }
+    PTB_CUDA_OK(cudaGetLastError());
+    return 0;
+}
+
 // dq: fp32 [B,Tq,H,D] zero-initialised by the caller; delta: fp32 [B,H,Tq] scratch.
 PTB_API int ptb_flash_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
                                float* delta, float* dq, void* dk, void* dv, void* unused, int B, int Tq, int Tk, int H, int Hk, int D,

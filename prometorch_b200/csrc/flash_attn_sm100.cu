@@ -306,6 +306,304 @@ static int launch(const void* q, const void* k, const void* v, void* o, float* l
     return 0;
 }
 
+
+// ---------------------------------------------------------------------------------------------- backward
+// One CTA per (128 keys, KV head, batch); it keeps K_j and V_j in shared memory and dK_j, dV_j in tensor memory, and
+// walks the query blocks that see those keys (all query heads of the KV head's group).  Per query block i:
+//   S = Q_i K_j^T and dP = dO_i V_j^T               two tcgen05.mma groups into TMEM (128 columns each)
+//   P = exp2(S c - lse_i),  dS = P (dP - delta_i) scale   by the thread that owns the query row (= TMEM lane)
+//   dV_j += P^T dO_i,  dK_j += dS^T Q_i,  dQ_i = dS K_j   three groups; dQ_i lands in S's columns, is read back
+//                                                       and added to the fp32 dQ in global memory (vector red)
+// Every tile lives in shared memory in ONE layout, [64-column chunk][row][128 B, 128-byte swizzle], which the
+// descriptors read as a K-major operand (rows = M or N) or as an MN-major operand (rows = K): Q_i is the A operand
+// of S and the B operand of dK, dO_i the A operand of dP and the B operand of dV, K_j the B operand of S and of dQ,
+// and the P / dS tiles written by the threads are A operands in both orientations.
+struct BwdParams {
+    const float* lse;        // [B, H, Tq] natural log
+    const float* delta;      // [B, H, Tq]
+    float* dq;               // [B, Tq, H, D] fp32, zero-initialised
+    __nv_bfloat16* dk;       // [B, Tk, Hk, D]
+    __nv_bfloat16* dv;
+    int B, Tq, Tk, H, Hk;
+    int causal, q_offset;
+    float scale, scale_log2;
+    int* status;
+    int gsplit;              // CTAs per KV head: each takes group / gsplit query heads and writes its own dk / dv slice
+};
+
+template <int D>
+struct SmB {
+    static constexpr int TILE = 128 * D * 2;                 // K, V, Q, dO
+    static constexpr int PT = 128 * 128 * 2;                 // P, dS
+    static constexpr int OFF_K = 0;
+    static constexpr int OFF_V = OFF_K + TILE;
+    static constexpr int OFF_Q = OFF_V + TILE;
+    static constexpr int OFF_DO = OFF_Q + TILE;
+    static constexpr int OFF_P = OFF_DO + TILE;
+    static constexpr int OFF_DS = OFF_P + PT;
+    static constexpr int OFF_BAR = OFF_DS + PT;
+    static constexpr int TOTAL = OFF_BAR + 256 + 1024;
+};
+
+__device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+template <int D>
+__global__ void __launch_bounds__(NTHREADS, 1)
+bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+           const __grid_constant__ CUtensorMap tmDO, const __grid_constant__ BwdParams P) {
+    using S = SmB<D>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* sk = smem + S::OFF_K;
+    uint8_t* sv = smem + S::OFF_V;
+    uint8_t* sq = smem + S::OFF_Q;
+    uint8_t* sdo = smem + S::OFF_DO;
+    uint8_t* sp = smem + S::OFF_P;
+    uint8_t* sds = smem + S::OFF_DS;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::OFF_BAR);
+    uint64_t* kv_full = bars;            // K_j, V_j loaded (once)
+    uint64_t* qdo_full = bars + 1;       // Q_i, dO_i loaded
+    uint64_t* qdo_empty = bars + 2;      // the MMAs that read them have completed
+    uint64_t* sdp_full = bars + 3;       // S and dP are in TMEM
+    uint64_t* pds_ready = bars + 4;      // P and dS are in shared memory (8 arrivals)
+    uint64_t* dq_full = bars + 5;        // dV, dK updated, dQ_i in TMEM
+    uint64_t* dq_read = bars + 6;        // dQ_i has been read back (8 arrivals)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int jb = blockIdx.x, hk = blockIdx.y / P.gsplit, part = blockIdx.y % P.gsplit, b = blockIdx.z;
+    const int group = (P.H / P.Hk) / P.gsplit;          // query heads this CTA walks
+    const int head0 = hk * (P.H / P.Hk) + part * group;
+    const int key0 = jb * 128;
+    const int nq = (P.Tq + 127) / 128;
+    // first query block that sees key0: rows q with q + q_offset >= key0
+    const int i_start = P.causal ? max(0, (key0 - P.q_offset) / 128) : 0;
+    const int per_head = max(0, nq - i_start);
+    const int n_it = per_head * group;
+
+    if (threadIdx.x == 0) {
+        mbar_init(kv_full, 1); mbar_init(qdo_full, 1); mbar_init(qdo_empty, 1); mbar_init(sdp_full, 1);
+        mbar_init(pds_ready, 8); mbar_init(dq_full, 1); mbar_init(dq_read, 8);
+        *abort_flag = 0;
+        mbar_fence_init();
+        prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmDO);
+    }
+    if (warp == 9) {
+        tmem_alloc(tmem_slot, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    constexpr uint32_t TM_S = 0, TM_DP = 128, TM_DV = 256, TM_DK = 256 + D;      // dQ_i reuses S's columns
+
+    if (warp == 8) {
+        // ---------------------------------------------------------------------------- TMA producer
+        if (lane == 0 && n_it > 0) {
+            bool ok = true;
+            mbar_expect_tx(kv_full, 2 * S::TILE);
+            for (int c = 0; c < D / 64; ++c) {
+                tma_load_2d(sk + c * 16384, &tmK, hk * D + c * 64, b * P.Tk + key0, kv_full);
+                tma_load_2d(sv + c * 16384, &tmV, hk * D + c * 64, b * P.Tk + key0, kv_full);
+            }
+            for (int it = 0; it < n_it && ok; ++it) {
+                const int h = head0 + it / per_head, i = i_start + it % per_head;
+                if (it > 0) ok = mbar_wait(qdo_empty, (uint32_t)((it - 1) & 1), P.status);
+                if (!ok) break;
+                mbar_expect_tx(qdo_full, 2 * S::TILE);
+                for (int c = 0; c < D / 64; ++c) {
+                    tma_load_2d(sq + c * 16384, &tmQ, h * D + c * 64, b * P.Tq + i * 128, qdo_full);
+                    tma_load_2d(sdo + c * 16384, &tmDO, h * D + c * 64, b * P.Tq + i * 128, qdo_full);
+                }
+            }
+            if (!ok) *abort_flag = 1;
+        }
+    } else if (warp == 9) {
+        // ---------------------------------------------------------------------------- MMA issuer
+        if (lane == 0 && n_it > 0) {
+            constexpr uint32_t idesc_qk = instr_desc(128, 128, 0, 0);      // S, dP: A [q, D] and B [keys, D] both K-major
+            constexpr uint32_t idesc_tt = instr_desc(128, D, 1, 1);        // dV, dK: A = P / dS read MN-major, B = dO / Q MN-major
+            constexpr uint32_t idesc_dq = instr_desc(128, D, 0, 1);        // dQ: A = dS K-major, B = K MN-major
+            bool ok = mbar_wait(kv_full, 0, P.status);
+            const uint32_t aK = smem_u32(sk), aV = smem_u32(sv), aQ = smem_u32(sq), aDO = smem_u32(sdo), aP = smem_u32(sp), aDS = smem_u32(sds);
+            for (int it = 0; it < n_it && ok; ++it) {
+                ok = mbar_wait(qdo_full, (uint32_t)(it & 1), P.status);
+                if (ok && it > 0) ok = mbar_wait(dq_read, (uint32_t)((it - 1) & 1), P.status);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int c = 0; c < D / 64; ++c)
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        umma_bf16(tmem_base + TM_S, smem_desc(aQ + c * 16384 + k * 32, 16, 1024), smem_desc(aK + c * 16384 + k * 32, 16, 1024),
+                                  idesc_qk, (c > 0 || k > 0) ? 1u : 0u);
+                        umma_bf16(tmem_base + TM_DP, smem_desc(aDO + c * 16384 + k * 32, 16, 1024), smem_desc(aV + c * 16384 + k * 32, 16, 1024),
+                                  idesc_qk, (c > 0 || k > 0) ? 1u : 0u);
+                    }
+                umma_commit(sdp_full);
+                ok = mbar_wait(pds_ready, (uint32_t)(it & 1), P.status);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t acc = it > 0 ? 1u : 0u;
+#pragma unroll
+                for (int kq = 0; kq < 8; ++kq) {      // K dimension = the 128 query rows, 16 per step: 2048 B further down each chunk
+                    umma_bf16(tmem_base + TM_DV, smem_desc(aP + kq * 2048, 16384, 1024), smem_desc(aDO + kq * 2048, 16384, 1024), idesc_tt,
+                              (kq > 0) ? 1u : acc);
+                    umma_bf16(tmem_base + TM_DK, smem_desc(aDS + kq * 2048, 16384, 1024), smem_desc(aQ + kq * 2048, 16384, 1024), idesc_tt,
+                              (kq > 0) ? 1u : acc);
+                }
+#pragma unroll
+                for (int c = 0; c < 2; ++c)           // K dimension = the 128 keys: two 64-key chunks of dS, 16 keys = 32 B per step
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        umma_bf16(tmem_base + TM_S, smem_desc(aDS + c * 16384 + k * 32, 16, 1024),
+                                  smem_desc(aK + (c * 4 + k) * 2048, 16384, 1024), idesc_dq, (c > 0 || k > 0) ? 1u : 0u);
+                umma_commit(qdo_empty);
+                umma_commit(dq_full);
+            }
+            if (!ok) *abort_flag = 1;
+        }
+    } else {
+        // ---------------------------------------------------------------------------- compute warps
+        const int row = 32 * (warp & 3) + lane;          // query row of the block = TMEM lane (key row in the final read-out)
+        const int hf = warp >> 2;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(32 * (warp & 3)) << 16);
+        bool ok = true;
+        for (int it = 0; it < n_it; ++it) {
+            const int h = head0 + it / per_head, i = i_start + it % per_head;
+            const int q_idx = i * 128 + row;
+            const bool q_valid = q_idx < P.Tq;
+            const size_t stat = ((size_t)b * P.H + h) * P.Tq + q_idx;
+            const float lse2 = q_valid ? P.lse[stat] * 1.4426950408889634f : INFINITY;       // +inf: P = 0 for padded rows
+            const float dlt = q_valid ? P.delta[stat] : 0.f;
+            if (ok && !*abort_flag) ok = mbar_wait(sdp_full, (uint32_t)(it & 1), P.status);
+            else ok = false;
+            tc_fence_after();
+            const int kbase = key0 + hf * 64;
+            const int q_pos = q_idx + P.q_offset;
+            const bool need_mask = (kbase + 64 > P.Tk) || (P.causal && kbase + 63 > i * 128 + P.q_offset);
+            uint32_t pp[32], dd[32];
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                uint32_t rs[32], rd[32];
+                tmem_ld32(lane_addr + TM_S + (uint32_t)(hf * 64 + c * 32), rs);
+                tmem_ld32(lane_addr + TM_DP + (uint32_t)(hf * 64 + c * 32), rd);
+                tmem_ld_wait();
+#pragma unroll
+                for (int e = 0; e < 32; e += 2) {
+                    float p0 = exp2f(__uint_as_float(rs[e]) * P.scale_log2 - lse2), p1 = exp2f(__uint_as_float(rs[e + 1]) * P.scale_log2 - lse2);
+                    if (need_mask) {
+                        const int k0 = kbase + c * 32 + e;
+                        if (k0 >= P.Tk || (P.causal && k0 > q_pos)) p0 = 0.f;
+                        if (k0 + 1 >= P.Tk || (P.causal && k0 + 1 > q_pos)) p1 = 0.f;
+                    }
+                    const float d0 = p0 * (__uint_as_float(rd[e]) - dlt) * P.scale, d1 = p1 * (__uint_as_float(rd[e + 1]) - dlt) * P.scale;
+                    const __nv_bfloat162 ph = __floats2bfloat162_rn(p0, p1), dh = __floats2bfloat162_rn(d0, d1);
+                    pp[c * 16 + e / 2] = *reinterpret_cast<const uint32_t*>(&ph);
+                    dd[c * 16 + e / 2] = *reinterpret_cast<const uint32_t*>(&dh);
+                }
+            }
+            {
+                uint8_t* prow = sp + hf * 16384 + row * 128;
+                uint8_t* drow = sds + hf * 16384 + row * 128;
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const int off = (c ^ (row & 7)) * 16;
+                    *reinterpret_cast<uint4*>(prow + off) = make_uint4(pp[4 * c], pp[4 * c + 1], pp[4 * c + 2], pp[4 * c + 3]);
+                    *reinterpret_cast<uint4*>(drow + off) = make_uint4(dd[4 * c], dd[4 * c + 1], dd[4 * c + 2], dd[4 * c + 3]);
+                }
+            }
+            fence_proxy_async();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(pds_ready);
+            // ---- dQ_i: read back my half of the row and add it to global memory
+            if (ok) ok = mbar_wait(dq_full, (uint32_t)(it & 1), P.status);
+            tc_fence_after();
+            float* dqp = P.dq + (((size_t)b * P.Tq + q_idx) * P.H + h) * D + hf * (D / 2);
+#pragma unroll
+            for (int c = 0; c < D / 64; ++c) {
+                uint32_t r[32];
+                tmem_ld32(lane_addr + TM_S + (uint32_t)(hf * (D / 2) + c * 32), r);
+                tmem_ld_wait();
+                if (q_valid && ok) {
+#pragma unroll
+                    for (int e = 0; e < 32; e += 4)
+                        red_add_v4(dqp + c * 32 + e, __uint_as_float(r[e]), __uint_as_float(r[e + 1]), __uint_as_float(r[e + 2]), __uint_as_float(r[e + 3]));
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(dq_read);
+        }
+        // ---- dK_j, dV_j: lanes are key rows now
+        const int key = key0 + row;
+        if (n_it > 0 && ok && !*abort_flag) {
+            tc_fence_after();
+#pragma unroll
+            for (int which = 0; which < 2; ++which) {
+                __nv_bfloat16* outp = (which ? P.dk : P.dv) + (size_t)part * P.B * P.Tk * P.Hk * D + (((size_t)b * P.Tk + key) * P.Hk + hk) * D +
+                                      hf * (D / 2);
+#pragma unroll
+                for (int c = 0; c < D / 64; ++c) {
+                    uint32_t r[32];
+                    tmem_ld32(lane_addr + (which ? TM_DK : TM_DV) + (uint32_t)(hf * (D / 2) + c * 32), r);
+                    tmem_ld_wait();
+                    if (key < P.Tk) {
+#pragma unroll
+                        for (int e = 0; e < 32; e += 8) {
+                            uint4 o;
+                            __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+                            for (int x = 0; x < 4; ++x) oh[x] = __floats2bfloat162_rn(__uint_as_float(r[e + 2 * x]), __uint_as_float(r[e + 2 * x + 1]));
+                            *reinterpret_cast<uint4*>(outp + c * 32 + e) = o;
+                        }
+                    }
+                }
+            }
+        } else if (n_it == 0 && key < P.Tk) {
+            // no query block sees these keys: their gradients are zero
+            const size_t base = (size_t)part * P.B * P.Tk * P.Hk * D + (((size_t)b * P.Tk + key) * P.Hk + hk) * D;
+            for (int d = hf * (D / 2); d < (hf + 1) * (D / 2); ++d) {
+                P.dk[base + d] = __float2bfloat16_rn(0.f);
+                P.dv[base + d] = __float2bfloat16_rn(0.f);
+            }
+        }
+        if (!ok) *abort_flag = 1;
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 9) tmem_dealloc(tmem_base, 512);
+}
+
+template <int D>
+static int launch_bwd(const void* q, const void* k, const void* v, const void* dout, const float* lse, const float* delta, float* dq, void* dk,
+                      void* dv, int B, int Tq, int Tk, int H, int Hk, int causal, float scale, int q_offset, int gsplit, int* status,
+                      cudaStream_t st) {
+    CUtensorMap mq, mk, mv, mdo;
+    if (ptb_make_tmap_bf16(&mq, q, (long long)H * D, (long long)B * Tq, (long long)H * D, 64, 128)) return -1;
+    if (ptb_make_tmap_bf16(&mdo, dout, (long long)H * D, (long long)B * Tq, (long long)H * D, 64, 128)) return -1;
+    if (ptb_make_tmap_bf16(&mk, k, (long long)Hk * D, (long long)B * Tk, (long long)Hk * D, 64, 128)) return -1;
+    if (ptb_make_tmap_bf16(&mv, v, (long long)Hk * D, (long long)B * Tk, (long long)Hk * D, 64, 128)) return -1;
+    static bool attr = false;
+    if (!attr) {
+        PTB_CUDA_OK(cudaFuncSetAttribute(bwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmB<D>::TOTAL));
+        attr = true;
+    }
+    BwdParams p;
+    p.lse = lse; p.delta = delta; p.dq = dq; p.dk = (__nv_bfloat16*)dk; p.dv = (__nv_bfloat16*)dv;
+    p.B = B; p.Tq = Tq; p.Tk = Tk; p.H = H; p.Hk = Hk; p.causal = causal; p.q_offset = q_offset;
+    p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f; p.status = status; p.gsplit = gsplit;
+    dim3 grid((Tk + 127) / 128, Hk * gsplit, B);
+    bwd_kernel<D><<<grid, NTHREADS, SmB<D>::TOTAL, st>>>(mq, mk, mv, mdo, p);
+    PTB_CUDA_OK(cudaGetLastError());
+    return 0;
+}
+
 }  // namespace fa100
 }  // namespace ptb
 
@@ -321,6 +619,27 @@ PTB_API int ptb_flash_attn_fwd_sm100(const void* q, const void* k, const void* v
     }
     if (D == 128) return ptb::fa100::launch<128>(q, k, v, o, lse, B, Tq, Tk, H, Hk, causal, scale, q_offset, status, st);
     if (D == 64) return ptb::fa100::launch<64>(q, k, v, o, lse, B, Tq, Tk, H, Hk, causal, scale, q_offset, status, st);
+    ptb_set_error("flash attention (tcgen05): head size %d not supported (64, 128)", D);
+    return -1;
+}
+
+extern "C" int ptb_flash_attn_delta(const void* o, const void* dout, float* delta, int B, int Tq, int H, int D, cudaStream_t st);
+
+// Backward on tcgen05.  dq: fp32 [B, Tq, H, D] zero-initialised by the caller; delta: fp32 [B, H, Tq] scratch.
+// dk, dv: bf16 [gsplit][B, Tk, Hk, D]: with grouped-query heads the query heads of one KV head can be split over
+// `gsplit` CTAs (a divisor of H / Hk) so that small problems fill the GPU; the caller sums the slices.
+PTB_API int ptb_flash_attn_bwd_sm100(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
+                                     float* delta, float* dq, void* dk, void* dv, int B, int Tq, int Tk, int H, int Hk, int D, int causal,
+                                     float scale, int q_offset, int gsplit, int* status, cudaStream_t st) {
+    if (H % Hk || gsplit < 1 || (H / Hk) % gsplit) { ptb_set_error("flash attention: %d query heads over %d KV heads, split %d", H, Hk, gsplit); return -1; }
+    {
+        int dev = 0;
+        PTB_CUDA_OK(cudaGetDevice(&dev));
+        PTB_CUDA_OK(cudaSetDevice(dev));
+    }
+    if (ptb_flash_attn_delta(o, dout, delta, B, Tq, H, D, st)) return -1;
+    if (D == 128) return ptb::fa100::launch_bwd<128>(q, k, v, dout, lse, delta, dq, dk, dv, B, Tq, Tk, H, Hk, causal, scale, q_offset, gsplit, status, st);
+    if (D == 64) return ptb::fa100::launch_bwd<64>(q, k, v, dout, lse, delta, dq, dk, dv, B, Tq, Tk, H, Hk, causal, scale, q_offset, gsplit, status, st);
     ptb_set_error("flash attention (tcgen05): head size %d not supported (64, 128)", D);
     return -1;
 }

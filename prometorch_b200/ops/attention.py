@@ -30,6 +30,9 @@ def _decls(L):
     if hasattr(L, "ptb_flash_attn_fwd_sm100"):
         L.ptb_flash_attn_fwd_sm100.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, cf, ci, vp, vp]
         L.ptb_flash_attn_fwd_sm100.restype = ci
+    if hasattr(L, "ptb_flash_attn_bwd_sm100"):
+        L.ptb_flash_attn_bwd_sm100.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, cf, ci, ci, vp, vp]
+        L.ptb_flash_attn_bwd_sm100.restype = ci
 
 
 def _use_tcgen05() -> bool:
@@ -89,9 +92,26 @@ class _Flash(torch.autograd.Function):
         dk, dv = torch.empty_like(k), torch.empty_like(v)
         delta = torch.empty(B, H, Tq, dtype=torch.float32, device=q.device)
         st = torch.cuda.current_stream(q.device).cuda_stream
-        N.check(N.lib().ptb_flash_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
-                                           delta.data_ptr(), dq32.data_ptr(), dk.data_ptr(), dv.data_ptr(), 0, B, Tq, Tk, H, Hk, D,
-                                           int(ctx.causal), ctx.scale, ctx.q_offset, st), "flash_attn_bwd")
+        import os
+        if os.environ.get("PTB_FA_BWD_SM100", "1") != "0" and hasattr(N.lib(), "ptb_flash_attn_bwd_sm100"):
+            from .gemm import _status
+            # few KV heads: split each head's query group over several CTAs until the grid fills the GPU twice over
+            gs, base, group = 1, ((Tk + 127) // 128) * Hk * B, H // Hk
+            while base * gs < 296 and group % (gs * 2) == 0:
+                gs *= 2
+            if gs > 1:
+                dk = torch.empty((gs,) + tuple(k.shape), dtype=k.dtype, device=k.device)
+                dv = torch.empty((gs,) + tuple(v.shape), dtype=v.dtype, device=v.device)
+            N.check(N.lib().ptb_flash_attn_bwd_sm100(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
+                                                     delta.data_ptr(), dq32.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, Tq, Tk, H, Hk, D,
+                                                     int(ctx.causal), ctx.scale, ctx.q_offset, gs, _status(q.device).data_ptr(), st),
+                    "flash_attn_bwd_sm100")
+            if gs > 1:
+                dk, dv = dk.sum(0, dtype=torch.float32).to(k.dtype), dv.sum(0, dtype=torch.float32).to(v.dtype)
+        else:
+            N.check(N.lib().ptb_flash_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
+                                               delta.data_ptr(), dq32.data_ptr(), dk.data_ptr(), dv.data_ptr(), 0, B, Tq, Tk, H, Hk, D,
+                                               int(ctx.causal), ctx.scale, ctx.q_offset, st), "flash_attn_bwd")
         return dq32.to(q.dtype), dk, dv, None, None, None
 
 
