@@ -30,7 +30,7 @@ class LayerDesc(C.Structure):
                 ("gate", WeightDesc), ("up", WeightDesc), ("down", WeightDesc),
                 ("attn_norm", C.c_void_p), ("ffn_norm", C.c_void_p), ("q_norm", C.c_void_p),
                 ("k_norm", C.c_void_p), ("cos", C.c_void_p), ("sin", C.c_void_p),
-                ("window", C.c_int), ("pad", C.c_int)]
+                ("window", C.c_int), ("pad", C.c_int), ("post_attn_norm", C.c_void_p), ("post_ffn_norm", C.c_void_p)]
 
 
 class ModelDesc(C.Structure):

@@ -44,6 +44,8 @@ struct PtbLayerDesc {
     const float* sin;
     int window;
     int pad;
+    const float* post_attn_norm;   // gemma3: RMSNorm of the attention block's output before the residual add (or null)
+    const float* post_ffn_norm;    // ... and of the FFN block's output
 };
 struct PtbModelDesc {
     int n_layers, hidden, n_heads, n_kv_heads, head_dim, inter, vocab, max_seq;   // head counts are per rank
@@ -289,6 +291,8 @@ struct Engine {
     bool own_stream = true;
     // device buffers
     float *x = nullptr, *qkv = nullptr, *att = nullptr, *ffn = nullptr, *logits = nullptr;
+    float *x2 = nullptr, *tmp = nullptr;      // post-norm architectures: second residual buffer, raw projection output
+    float* x_final = nullptr;                 // where the residual stream ends up after the last layer
     __half *kc = nullptr, *vc = nullptr;
     float *part_o = nullptr, *part_ml = nullptr;
     unsigned* tickets = nullptr;      // [0] gemv, [1] spare, [8..] attention per kv head
@@ -324,6 +328,8 @@ static int engine_alloc(Engine* e) {
     const int splits = (m.max_seq + ATT_CHUNK - 1) / ATT_CHUNK;
     const int group = m.n_heads / m.n_kv_heads;
     PTB_CUDA_OK(cudaMalloc(&e->x, sizeof(float) * m.hidden));
+    PTB_CUDA_OK(cudaMalloc(&e->x2, sizeof(float) * m.hidden));
+    PTB_CUDA_OK(cudaMalloc(&e->tmp, sizeof(float) * m.hidden));
     PTB_CUDA_OK(cudaMalloc(&e->qkv, sizeof(float) * (qd + 2 * kvd)));
     PTB_CUDA_OK(cudaMalloc(&e->att, sizeof(float) * qd));
     PTB_CUDA_OK(cudaMalloc(&e->ffn, sizeof(float) * m.inter));
@@ -374,6 +380,21 @@ static int engine_plan(Engine* e) {
     const int n_ctas = e->n_sm * env_int("PTB_GEMV_CTAS_PER_SM", 2);
     const bool tp = m.tp_world > 1;
     e->gemvs.clear();
+    // post-norm architectures: a projection stores its raw output in `tmp`; the next kernel's prologue adds
+    // RMSNorm(tmp) to the residual stream, reading X[cur] and (CTA 0) writing X[cur ^ 1]
+    float* X[2] = {e->x, e->x2};
+    int cur = 0;
+    const float* pending_w = nullptr;          // post-norm weight of the projection whose output waits in `tmp`
+    bool bad = false;
+    auto take_pending = [&](GemvParams& p) {
+        p.x = X[cur];
+        if (pending_w) {
+            if (m.hidden > 4096) { ptb_set_error("post-norm architectures: hidden size %d above 4096 is not supported", m.hidden); bad = true; }
+            p.post_src = e->tmp; p.post_w = pending_w; p.x_out = X[cur ^ 1];
+            cur ^= 1;
+            pending_w = nullptr;
+        }
+    };
     for (int l = 0; l < m.n_layers; ++l) {
         const PtbLayerDesc& L = e->layers[l];
         {   // q, k, v from RMSNorm(x)
@@ -382,27 +403,31 @@ static int engine_plan(Engine* e) {
             set_job(g.p.job[0], L.q, nullptr, e->qkv);
             set_job(g.p.job[1], L.k, nullptr, e->qkv + qd);
             set_job(g.p.job[2], L.v, nullptr, e->qkv + qd + kvd);
-            g.p.x = e->x; g.p.norm_w = L.attn_norm; g.p.eps = m.eps; g.p.norm_add_one = m.norm_add_one;
+            take_pending(g.p);
+            g.p.norm_w = L.attn_norm; g.p.eps = m.eps; g.p.norm_add_one = m.norm_add_one;
             g.p.epilogue = EPI_STORE; g.p.status = e->status; g.p.peers.world = 1;
             if (plan_gemv(g, 3, m.hidden, n_ctas)) return -1;
             e->gemvs.push_back(g);
         }
-        {   // x += Wo att
+        {   // x += Wo att   (post-norm: tmp = Wo att, added by the next prologue)
             GemvLaunch g;
             memset(&g, 0, sizeof(g));
-            set_job(g.p.job[0], L.o, nullptr, e->x);
-            g.p.x = e->att; g.p.resid = e->x; g.p.status = e->status; g.p.ticket = e->tickets;
-            g.p.epilogue = tp ? EPI_ALLREDUCE : EPI_RESID;
+            const bool post = L.post_attn_norm != nullptr;
+            set_job(g.p.job[0], L.o, nullptr, post ? e->tmp : X[cur]);
+            g.p.x = e->att; g.p.resid = post ? nullptr : X[cur]; g.p.status = e->status; g.p.ticket = e->tickets;
+            g.p.epilogue = tp ? EPI_ALLREDUCE : (post ? EPI_STORE : EPI_RESID);
             g.p.peers.world = 1;
             if (tp) fill_peers(e, g.p, 0, l, m.n_layers);
             if (plan_gemv(g, 1, L.o.cols, n_ctas)) return -1;
             e->gemvs.push_back(g);
+            if (post) pending_w = L.post_attn_norm;
         }
         {   // ffn = act(Wg h) * (Wu h), h = RMSNorm(x)
             GemvLaunch g;
             memset(&g, 0, sizeof(g));
             set_job(g.p.job[0], L.gate, &L.up, e->ffn);
-            g.p.x = e->x; g.p.norm_w = L.ffn_norm; g.p.eps = m.eps; g.p.norm_add_one = m.norm_add_one;
+            take_pending(g.p);
+            g.p.norm_w = L.ffn_norm; g.p.eps = m.eps; g.p.norm_add_one = m.norm_add_one;
             g.p.epilogue = EPI_GATED; g.p.act_gelu = m.act_gelu; g.p.status = e->status; g.p.peers.world = 1;
             if (plan_gemv(g, 1, m.hidden, n_ctas)) return -1;
             e->gemvs.push_back(g);
@@ -410,20 +435,25 @@ static int engine_plan(Engine* e) {
         {   // x += Wd ffn
             GemvLaunch g;
             memset(&g, 0, sizeof(g));
-            set_job(g.p.job[0], L.down, nullptr, e->x);
-            g.p.x = e->ffn; g.p.resid = e->x; g.p.status = e->status; g.p.ticket = e->tickets;
-            g.p.epilogue = tp ? EPI_ALLREDUCE : EPI_RESID;
+            const bool post = L.post_ffn_norm != nullptr;
+            set_job(g.p.job[0], L.down, nullptr, post ? e->tmp : X[cur]);
+            g.p.x = e->ffn; g.p.resid = post ? nullptr : X[cur]; g.p.status = e->status; g.p.ticket = e->tickets;
+            g.p.epilogue = tp ? EPI_ALLREDUCE : (post ? EPI_STORE : EPI_RESID);
             g.p.peers.world = 1;
             if (tp) fill_peers(e, g.p, 1, l, m.n_layers);
             if (plan_gemv(g, 1, L.down.cols, n_ctas)) return -1;
             e->gemvs.push_back(g);
+            if (post) pending_w = L.post_ffn_norm;
         }
     }
     {   // lm_head with fused arg-max
         GemvLaunch g;
         memset(&g, 0, sizeof(g));
         set_job(g.p.job[0], m.lm_head, nullptr, e->logits);
-        g.p.x = e->x; g.p.norm_w = m.out_norm; g.p.eps = m.eps; g.p.norm_add_one = m.norm_add_one;
+        take_pending(g.p);
+        if (bad) return -1;
+        e->x_final = X[cur];
+        g.p.norm_w = m.out_norm; g.p.eps = m.eps; g.p.norm_add_one = m.norm_add_one;
         g.p.epilogue = EPI_ARGMAX; g.p.status = e->status;
         g.p.amax_val = e->amax_val; g.p.amax_idx = e->amax_idx; g.p.ticket = e->tickets + 1;
         g.p.logits = m.want_logits ? e->logits : nullptr;
@@ -708,7 +738,9 @@ PTB_API void* ptb_engine_create(const PtbModelDesc* m, const PtbLayerDesc* layer
     else if (cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) != cudaSuccess) { ptb_set_error("stream create failed"); delete e; return nullptr; }
     if (ensure_attrs() || engine_alloc(e) || engine_plan(e)) { delete e; return nullptr; }
     // one GPU: the whole token as one persistent launch (PTB_MEGA=1; the default is the kernel-per-op graph)
-    e->mega = m->tp_world <= 1 && env_int("PTB_MEGA", 0) != 0;
+    bool any_post = false;
+    for (int l = 0; l < m->n_layers; ++l) any_post = any_post || layers[l].post_attn_norm || layers[l].post_ffn_norm;
+    e->mega = m->tp_world <= 1 && !any_post && env_int("PTB_MEGA", 0) != 0;
     if (e->mega && engine_plan_mega(e)) { delete e; return nullptr; }
     return e;
 }
@@ -719,6 +751,7 @@ PTB_API void ptb_engine_destroy(void* h) {
     cudaStreamSynchronize(e->stream);
     if (e->exec) cudaGraphExecDestroy(e->exec);
     if (e->graph) cudaGraphDestroy(e->graph);
+    cudaFree(e->x2); cudaFree(e->tmp);
     cudaFree(e->x); cudaFree(e->qkv); cudaFree(e->att); cudaFree(e->ffn); cudaFree(e->logits);
     cudaFree(e->kc); cudaFree(e->vc); cudaFree(e->part_o); cudaFree(e->part_ml); cudaFree(e->tickets);
     cudaFree(e->amax_val); cudaFree(e->amax_idx); cudaFree(e->ctrl); cudaFree(e->result); cudaFree(e->token_log); cudaFree(e->script);
@@ -834,7 +867,7 @@ PTB_API int ptb_engine_read_trace(void* h, unsigned long long* out, int max_kern
 }
 PTB_API void* ptb_engine_stream(void* h) { return (void*)((Engine*)h)->stream; }
 PTB_API void* ptb_engine_logits(void* h) { return (void*)((Engine*)h)->logits; }
-PTB_API void* ptb_engine_hidden(void* h) { return (void*)((Engine*)h)->x; }
+PTB_API void* ptb_engine_hidden(void* h) { Engine* e = (Engine*)h; return (void*)(e->x_final ? e->x_final : e->x); }
 PTB_API void* ptb_engine_result(void* h) { return (void*)((Engine*)h)->result; }
 // Device addresses of layer `layer`'s fp16 K and V caches, each [kv_heads][max_seq][head_dim].
 PTB_API int ptb_engine_kv_cache(void* h, int layer, void** k, void** v) {

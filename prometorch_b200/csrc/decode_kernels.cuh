@@ -86,6 +86,11 @@ struct GemvParams {
     int stages, tile_bytes; // per-warp ring: `stages` slots of `tile_bytes`
     int acc_floats;         // shared-memory accumulators for K-split jobs (0 if every job has KS == 1)
     unsigned long long* trace;  // optional [8] %globaltimer stamps of CTA 0's phases (profiling aid)
+    // post-norm architectures (gemma3): the previous projection stored its raw output in `post_src`; this kernel's
+    // prologue first forms x' = x + RMSNorm(post_src; post_w), CTA 0 writes x' to `x_out`, and the input norm runs on x'
+    const float* post_src;
+    const float* post_w;
+    float* x_out;
 };
 
 // control block indices
@@ -218,10 +223,11 @@ __device__ __forceinline__ float block_sum(float v, float* buf) {
 // Load x[K] once into registers, optionally RMS-normalise, quantise to int8 blocks of 32.
 //   xq[K] int8, xs[K/32] block scales, xsf16[K/16] = scale * (sum of 16 int8), xsf32[K/32] = scale * (sum of 32).
 // Each thread keeps up to QIN_ITEMS 8-value items in registers: K <= QIN_ITEMS * 8 * blockDim.
-template <int QIN_ITEMS>
+template <int QIN_ITEMS, bool POST = false>
 __device__ __forceinline__ void quantize_input(const float* __restrict__ x, const float* __restrict__ norm_w, float eps,
                                                int add_one, int K, int8_t* xq, float* xs, float* xsf16, float* xsf32,
-                                               float* red) {
+                                               float* red, const float* __restrict__ post_src = nullptr,
+                                               const float* __restrict__ post_w = nullptr, float* __restrict__ x_out = nullptr) {
     const int tid = threadIdx.x, nt = blockDim.x;
     const int items = K / 8;
     float v[QIN_ITEMS][8];
@@ -236,9 +242,46 @@ __device__ __forceinline__ void quantize_input(const float* __restrict__ x, cons
 #pragma unroll
             for (int k = 0; k < 8; ++k) v[r][k] = 0.f;
         }
+    }
+    if (POST) {
+        // x' = x + RMSNorm(t; post_w): t is the raw output of the previous projection
+        float t[QIN_ITEMS][8];
+        float st = 0.f;
+#pragma unroll
+        for (int r = 0; r < QIN_ITEMS; ++r) {
+            const int i = r * nt + tid;
+            if (i < items) {
+                const float4 a = __ldcg(reinterpret_cast<const float4*>(post_src) + 2 * i), b = __ldcg(reinterpret_cast<const float4*>(post_src) + 2 * i + 1);
+                t[r][0] = a.x; t[r][1] = a.y; t[r][2] = a.z; t[r][3] = a.w; t[r][4] = b.x; t[r][5] = b.y; t[r][6] = b.z; t[r][7] = b.w;
+            } else {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) t[r][k] = 0.f;
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) st += t[r][k] * t[r][k];
+        }
+        st = block_sum(st, red);
+        const float rt = rsqrtf(st / (float)K + eps);
+#pragma unroll
+        for (int r = 0; r < QIN_ITEMS; ++r) {
+            const int i = r * nt + tid;
+            if (i < items) {
+                const float4 wa = __ldg(reinterpret_cast<const float4*>(post_w) + 2 * i), wb = __ldg(reinterpret_cast<const float4*>(post_w) + 2 * i + 1);
+                const float w[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+                for (int k = 0; k < 8; ++k) v[r][k] += t[r][k] * rt * (add_one ? 1.0f + w[k] : w[k]);
+                if (x_out && blockIdx.x == 0) {
+                    reinterpret_cast<float4*>(x_out)[2 * i] = make_float4(v[r][0], v[r][1], v[r][2], v[r][3]);
+                    reinterpret_cast<float4*>(x_out)[2 * i + 1] = make_float4(v[r][4], v[r][5], v[r][6], v[r][7]);
+                }
+            }
+        }
+        __syncthreads();        // `red` is reused by the next reduction
+    }
+#pragma unroll
+    for (int r = 0; r < QIN_ITEMS; ++r)
 #pragma unroll
         for (int k = 0; k < 8; ++k) ss += v[r][k] * v[r][k];
-    }
     float rs = 1.0f;
     if (norm_w) {
         ss = block_sum(ss, red);
@@ -381,7 +424,9 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32, 2) gemv_kernel(const __grid_c
     stamp(1);
 
     // the RMSNorm weights are parameters too: pull them towards L1/L2 before the dependency wait
-    if (K <= 2 * 8 * GEMV_THREADS) quantize_input<2>(P.x, P.norm_w, P.eps, P.norm_add_one, K, xq, xs, xsf, xsf32, misc);
+    if (P.post_src) quantize_input<(GEMV_WARPS >= 16 ? 1 : 2), true>(P.x, P.norm_w, P.eps, P.norm_add_one, K, xq, xs, xsf, xsf32, misc, P.post_src,
+                                                                      P.post_w, P.x_out);
+    else if (K <= 2 * 8 * GEMV_THREADS) quantize_input<2>(P.x, P.norm_w, P.eps, P.norm_add_one, K, xq, xs, xsf, xsf32, misc);
     else quantize_input<(GEMV_WARPS >= 16 ? 3 : 5)>(P.x, P.norm_w, P.eps, P.norm_add_one, K, xq, xs, xsf, xsf32, misc);
     stamp(2);
 

@@ -121,6 +121,17 @@ def qwen3_4b_config() -> TransformerConfig:
         context_length=40960, rope_freq_base=1e6, rms_norm_eps=1e-6, has_qk_norm=True, rope_neox=True)
 
 
+def tiny_gemma3_config(layers: int = 3, hidden: int = 1024, heads: int = 8, kv_heads: int = 4, inter: int = 2048, vocab: int = 2048,
+                       head_dim: int = 128, window: int = 0) -> TransformerConfig:
+    """A small model with gemma3's structure: post-attention / post-FFN norms, QK-norm, GELU-gated FFN, scaled and tied
+    embeddings, optional sliding-window layers (every 6th layer global)."""
+    return TransformerConfig(
+        architecture="gemma3", model_name="gemma3-tiny", vocab_size=vocab, hidden_size=hidden, num_layers=layers, num_heads=heads,
+        num_kv_heads=kv_heads, intermediate_size=inter, head_dim=head_dim, context_length=4096, rope_freq_base=1e6, rms_norm_eps=1e-6,
+        has_qk_norm=True, has_post_norm=True, ffn_gelu=True, scale_embeddings=True, tie_word_embeddings=True, rope_neox=True,
+        swa_window=window, swa_pattern=6 if window else 0)
+
+
 def tiny_qwen3_config(layers: int = 2, hidden: int = 512, heads: int = 8, kv_heads: int = 2,
                       inter: int = 1024, vocab: int = 1024, head_dim: int = 128) -> TransformerConfig:
     return TransformerConfig(

@@ -171,8 +171,8 @@ class GGUFModel:
                              f"divisible and FFN size ({cfg.intermediate_size}) a multiple of 256")
         if (cfg.num_heads // W * cfg.head_dim) % 256:
             raise ValueError("tensor parallel: per-rank attention width must be a multiple of 256")
-        if cfg.has_post_norm:
-            raise NotImplementedError("post-attention/post-FFN norms (gemma3) are not wired into the fused engine yet")
+        if cfg.has_post_norm and cfg.hidden_size > 4096:
+            raise NotImplementedError("post-attention/post-FFN norms are supported for hidden sizes up to 4096")
         torch.cuda.set_device(dev)
         hq, hkv, d = cfg.num_heads // W, cfg.num_kv_heads // W, cfg.head_dim
         fb0, fb1 = split_blocks(cfg.intermediate_size // 256, W, rk)
@@ -214,7 +214,8 @@ class GGUFModel:
                 up=mat(p + "ffn_up.weight", rows=(fb0 * 256, fb1 * 256)),
                 down=mat(p + "ffn_down.weight", kblocks=(fb0, fb1)),
                 attn_norm=vec(p + "attn_norm.weight"), ffn_norm=vec(p + "ffn_norm.weight"),
-                q_norm=vec(p + "attn_q_norm.weight"), k_norm=vec(p + "attn_k_norm.weight"))
+                q_norm=vec(p + "attn_q_norm.weight"), k_norm=vec(p + "attn_k_norm.weight"),
+                post_attn_norm=vec(p + "post_attention_norm.weight"), post_ffn_norm=vec(p + "post_ffw_norm.weight"))
             if L["gate"].qtype != L["up"].qtype:
                 raise NotImplementedError("ffn_gate and ffn_up with different quantisation types")
             swa = bool(cfg.swa_window and cfg.swa_pattern and (i + 1) % cfg.swa_pattern != 0)
@@ -224,6 +225,7 @@ class GGUFModel:
                 setattr(dsc, k, L[k].desc())
             dsc.attn_norm, dsc.ffn_norm = N.ptr(L["attn_norm"]), N.ptr(L["ffn_norm"])
             dsc.q_norm, dsc.k_norm = N.ptr(L["q_norm"]), N.ptr(L["k_norm"])
+            dsc.post_attn_norm, dsc.post_ffn_norm = N.ptr(L["post_attn_norm"]), N.ptr(L["post_ffn_norm"])
             use_swa_tab = swa and self.cos_swa is not None
             dsc.cos = (self.cos_swa if use_swa_tab else self.cos).data_ptr()
             dsc.sin = (self.sin_swa if use_swa_tab else self.sin).data_ptr()
@@ -415,11 +417,17 @@ class GGUFModel:
             else:
                 k_all, v_all = k, v.unsqueeze(0)
             att = flash_attention(q, k_all, v_all, causal=True, q_offset=pos0).reshape(T, hq * d)
-            x = x + proj(att, L["o"])
+            o = proj(att, L["o"])
+            if L["post_attn_norm"] is not None:
+                o = K.rms_norm(o, nw(L, "post_attn_norm"), eps)
+            x = x + o
             h = K.rms_norm(x, nw(L, "ffn_norm"), eps)
             g, u = proj(h, L["gate"]), proj(h, L["up"]).clone()       # gate and up share a scratch shape: keep one
             act = torch.nn.functional.gelu(g.float(), approximate="tanh") if cfg.ffn_gelu else torch.nn.functional.silu(g.float())
-            x = x + proj((act * u.float()).to(bf), L["down"])
+            dn = proj((act * u.float()).to(bf), L["down"])
+            if L["post_ffn_norm"] is not None:
+                dn = K.rms_norm(dn, nw(L, "post_ffn_norm"), eps)
+            x = x + dn
         torch.cuda.current_stream(dev).synchronize()
         if int(self._pf_status):
             self._pf_status.zero_()

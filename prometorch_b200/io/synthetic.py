@@ -57,6 +57,10 @@ def write_synthetic_gguf(path: str, cfg: TransformerConfig, seed: int = 0, devic
     w.add(f"{a}.attention.layer_norm_rms_epsilon", float(cfg.rms_norm_eps))
     w.add(f"{a}.attention.key_length", cfg.head_dim)
     w.add(f"{a}.attention.value_length", cfg.head_dim)
+    if cfg.swa_window:
+        w.add(f"{a}.attention.sliding_window", int(cfg.swa_window))
+        if cfg.swa_pattern:
+            w.add(f"{a}.attention.sliding_window_pattern", int(cfg.swa_pattern))
     if with_tokenizer:
         toks = _tokens_for(cfg.vocab_size)
         w.add("tokenizer.ggml.model", "llama")
@@ -91,10 +95,14 @@ def write_synthetic_gguf(path: str, cfg: TransformerConfig, seed: int = 0, devic
             w.add_tensor(p + "attn_q_norm.weight", (cfg.head_dim,), GGMLType.F32, norm(cfg.head_dim))
             w.add_tensor(p + "attn_k_norm.weight", (cfg.head_dim,), GGMLType.F32, norm(cfg.head_dim))
         w.add_tensor(p + "attn_output.weight", (H, Q), q_main, rnd(H, Q, q_main))
+        if cfg.has_post_norm:
+            w.add_tensor(p + "post_attention_norm.weight", (H,), GGMLType.F32, norm(H))
         w.add_tensor(p + "ffn_norm.weight", (H,), GGMLType.F32, norm(H))
         w.add_tensor(p + "ffn_gate.weight", (I, H), q_main, rnd(I, H, q_main))
         w.add_tensor(p + "ffn_up.weight", (I, H), q_main, rnd(I, H, q_main))
         w.add_tensor(p + "ffn_down.weight", (H, I), q_more, rnd(H, I, q_more))
+        if cfg.has_post_norm:
+            w.add_tensor(p + "post_ffw_norm.weight", (H,), GGMLType.F32, norm(H))
     w.add_tensor("output_norm.weight", (H,), GGMLType.F32, norm(H))
     if not cfg.tie_word_embeddings:
         w.add_tensor("output.weight", (V, H), q_more, rnd(V, H, q_more))

@@ -117,9 +117,17 @@ class OracleModel:
         x = self.tok[tokens]
         if cfg.scale_embeddings:
             x = x * math.sqrt(cfg.hidden_size)
-        cos, sin = self.cos[self.pos:self.pos + T], self.sin[self.pos:self.pos + T]
+        cos_g, sin_g = self.cos[self.pos:self.pos + T], self.sin[self.pos:self.pos + T]
+        cos_l = sin_l = None
+        if cfg.swa_window and cfg.rope_swa_freq_base != cfg.rope_freq_base:
+            if not hasattr(self, "_swa_tables"):
+                self._swa_tables = rope_tables(cfg, self.cos.shape[0], self.device, freq_base=cfg.rope_swa_freq_base)
+            cos_l, sin_l = self._swa_tables[0][self.pos:self.pos + T], self._swa_tables[1][self.pos:self.pos + T]
         group = cfg.num_heads // cfg.num_kv_heads
         for li, L in enumerate(self.layers):
+            # sliding-window layers (all but every swa_pattern-th): local RoPE base and a window over the keys
+            swa = bool(cfg.swa_window and cfg.swa_pattern and (li + 1) % cfg.swa_pattern != 0)
+            cos, sin = (cos_l, sin_l) if (swa and cos_l is not None) else (cos_g, sin_g)
             h = rms_norm(x, L["attn_norm"], cfg.rms_norm_eps, cfg.gemma_norm_add_one)
             q, k, v = self._lin(h, L["attn_q"]), self._lin(h, L["attn_k"]), self._lin(h, L["attn_v"])
             if "attn_q_b" in L:
@@ -143,7 +151,10 @@ class OracleModel:
             sc = torch.einsum("thd,hsd->hts", q, Kh) / math.sqrt(cfg.head_dim)
             qpos = torch.arange(self.pos, self.pos + T, device=self.device)[:, None]
             kpos = torch.arange(S, device=self.device)[None, :]
-            sc = sc.masked_fill((kpos > qpos)[None], float("-inf"))
+            hidden = kpos > qpos
+            if swa:
+                hidden = hidden | (kpos <= qpos - cfg.swa_window)         # a query sees the last `window` positions
+            sc = sc.masked_fill(hidden[None], float("-inf"))
             a = torch.einsum("hts,hsd->thd", sc.softmax(-1), Vh).reshape(T, cfg.q_dim)
             o = self._lin(a, L["attn_output"])
             if "post_attention_norm" in L:

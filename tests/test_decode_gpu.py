@@ -216,3 +216,37 @@ def test_prefill_matches_token_by_token(tmp_path):
     assert len(out) == 8
     a.close()
     b.close()
+
+
+# ----------------------------------------------------------------------------- gemma3 structure (post-norms, GELU gate, tied + scaled embeddings)
+@pytest.mark.parametrize("window", [0, 64])
+def test_gemma3_structure_matches_oracle(tmp_path, window):
+    from prometorch_b200.io.config import tiny_gemma3_config
+    from prometorch_b200.io.gguf_model import GGUFModel
+    from prometorch_b200.io.synthetic import write_synthetic_gguf
+    from prometorch_b200.models.gguf_oracle import OracleModel
+    cfg = tiny_gemma3_config(layers=7, window=window)
+    path = str(tmp_path / "g3.gguf")
+    write_synthetic_gguf(path, cfg, seed=5, device="cuda", std=0.05)
+    m = GGUFModel(path, max_seq=256, want_logits=True)
+    assert m.cfg.has_post_norm and m.cfg.ffn_gelu and m.cfg.scale_embeddings
+    o = OracleModel(path, device="cuda", max_seq=256, emulate_q8=True)
+    g = torch.Generator().manual_seed(1)
+    toks = torch.randint(0, 2048, (90 if window else 12,), generator=g).tolist()
+    for pos, t in enumerate(toks):
+        nxt = m.forward_decode(t, pos)
+        ref = o.forward([t])[0]
+        if pos % 8 == 0 or pos == len(toks) - 1:
+            cos = torch.nn.functional.cosine_similarity(m.logits_view(), ref, dim=0)
+            assert cos > 0.999, (pos, float(cos))
+    hid = m.hidden_view().clone()
+    assert torch.isfinite(hid).all()
+    m.check_status()
+    if not window:                                # batched prompt pass with post-norms
+        m2 = GGUFModel(path, max_seq=256, want_logits=True)
+        m2.prefill(toks[:-1])
+        m2.forward_decode(toks[-1], len(toks) - 1)
+        cos = torch.nn.functional.cosine_similarity(m2.logits_view(), m.logits_view(), dim=0)
+        assert cos > 0.995, float(cos)
+        m2.close()
+    m.close()
