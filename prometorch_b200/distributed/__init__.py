@@ -117,3 +117,58 @@ class SyncBatchNorm(torch.nn.SyncBatchNorm):
     def convert_sync_batchnorm(cls, module, process_group=None):
         g = process_group.group if isinstance(process_group, TorchProcessGroup) else None
         return torch.nn.SyncBatchNorm.convert_sync_batchnorm(module, g)
+
+
+# ----------------------------------------------------------------------------- remaining names of the reference's C++ surface
+from dataclasses import dataclass as _dataclass
+
+
+@_dataclass
+class DDPConfig:
+    """Connection settings of the reference's process-group singleton (torch/distributed/ddp.h:37-52)."""
+    rank: int = 0
+    world_size: int = 1
+    master_addr: str = "127.0.0.1"
+    master_port: int = 29500
+    timeout_sec: float = 300.0
+    backend: str = "gloo"
+
+    def init(self) -> ProcessGroup:
+        return init_process_group(self.backend, self.rank, self.world_size, self.master_addr, self.master_port, self.timeout_sec)
+
+
+def init_process_group_single_rank() -> ProcessGroup:
+    """A world of one (every collective is the identity)."""
+    return init_process_group("shared_memory", 0, 1)
+
+
+def all_gather_inplace(buffer: torch.Tensor):
+    """``buffer`` holds ``world_size`` equal slots; this rank's slot is filled in, the others arrive from their owners
+    (the in-place form of ddp.h's ``all_gather_inplace``)."""
+    pg = _pg()
+    w, r = pg.world_size, pg.rank
+    slots = list(buffer.view(w, -1).unbind(0))
+    mine = slots[r].clone()
+    pg.all_gather(slots, mine)
+    return buffer
+
+
+class _GatherHandle:
+    def __init__(self, work, buffer):
+        self.work, self.buffer = work, buffer
+
+
+def all_gather_post(buffer: torch.Tensor) -> _GatherHandle:
+    """Start an in-place all-gather; finish it with :func:`all_gather_wait` (overlaps with compute on NCCL)."""
+    pg = _pg()
+    if isinstance(pg, TorchProcessGroup) and pg.backend == "nccl":
+        mine = buffer.view(pg.world_size, -1)[pg.rank].clone()
+        return _GatherHandle(pg.all_gather_into(buffer.view(-1), mine, async_op=True), buffer)
+    all_gather_inplace(buffer)
+    return _GatherHandle(None, buffer)
+
+
+def all_gather_wait(handle: _GatherHandle) -> torch.Tensor:
+    if handle.work is not None:
+        handle.work.wait()
+    return handle.buffer

@@ -35,6 +35,13 @@ def collectives(rank, world):
     parts = [torch.zeros(2) for _ in range(world)]
     D.all_gather(parts, torch.full((2,), float(rank)))
     assert all(float(p[0]) == i for i, p in enumerate(parts))
+    buf = torch.zeros(world * 3)
+    buf.view(world, 3)[rank] = float(rank + 1)
+    D.all_gather_inplace(buf)
+    assert torch.equal(buf.view(world, 3)[:, 0], torch.arange(1.0, world + 1)), buf
+    buf2 = torch.zeros(world * 2)
+    buf2.view(world, 2)[rank] = float(10 + rank)
+    assert torch.equal(D.all_gather_wait(D.all_gather_post(buf2)).view(world, 2)[:, 1], torch.arange(10.0, 10 + world))
     out = torch.zeros(2)
     D.reduce_scatter(out, [torch.full((2,), float(k + rank)) for k in range(world)])
     assert torch.allclose(out, torch.full((2,), float(sum(rank + r for r in range(world)))))
