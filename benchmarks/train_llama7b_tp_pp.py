@@ -89,8 +89,8 @@ def main():
             q, k, v = self.qkv(self.attn_norm(x)).view(1, T, 3, hl, d).unbind(2)
             q, k = K.rope(q, cos, sin, True, 0), K.rope(k, cos, sin, True, 0)
             att = flash_attention(q, k, v, causal=True).reshape(T, hl * d)
-            x = x + self.o(att)
-            return x + self.down(K.swiglu(self.gate_up(self.mlp_norm(x)), False))
+            h, x = self.mlp_norm(self.o(att), x)             # residual add fused into the norm
+            return x + self.down(K.swiglu(self.gate_up(h), False))
 
     class Stage(nn.Module):
         def __init__(self, first, last, n_layers):

@@ -29,34 +29,7 @@ PTB_API const char* ptb_last_error() { return g_err; }
 using namespace ptb;
 
 // ------------------------------------------------------------------------------------------ C structs (mirrored in Python)
-struct PtbWeightDesc {
-    const void* w;
-    const void* bias;
-    int qtype, rows, cols, rowbytes;
-};
-struct PtbLayerDesc {
-    PtbWeightDesc q, k, v, o, gate, up, down;
-    const float* attn_norm;
-    const float* ffn_norm;
-    const float* q_norm;
-    const float* k_norm;
-    const float* cos;       // per-layer RoPE tables (sliding-window layers may use another base)
-    const float* sin;
-    int window;
-    int pad;
-    const float* post_attn_norm;   // gemma3: RMSNorm of the attention block's output before the residual add (or null)
-    const float* post_ffn_norm;    // ... and of the FFN block's output
-};
-struct PtbModelDesc {
-    int n_layers, hidden, n_heads, n_kv_heads, head_dim, inter, vocab, max_seq;   // head counts are per rank
-    float eps, emb_scale;
-    int neox, act_gelu, norm_add_one, want_logits;
-    PtbWeightDesc embed, lm_head;
-    const float* out_norm;
-    int tp_rank, tp_world, vocab_offset, pad;
-    void* peer_inbox[3][MAX_PEERS];     // three receive buffers (attention out, FFN down, lm_head pair)
-    int slot_elems, pad2;
-};
+#include "ptb200_types.h"
 
 static size_t g_gemv_max_dyn = 200 * 1024;
 static int env_int(const char* name, int dflt) {

@@ -216,25 +216,29 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                     if (key >= P.Tk || (P.causal && key > q_pos)) sc[i] = -INFINITY;
                 }
             }
-            float mx = -INFINITY;
+            // eight independent partial maxima: a 64-long dependent chain would stall the two warps a scheduler has
+            float m8[8];
 #pragma unroll
-            for (int i = 0; i < 64; ++i) mx = fmaxf(mx, sc[i]);
+            for (int i = 0; i < 8; ++i) m8[i] = sc[i];
+#pragma unroll
+            for (int i = 8; i < 64; ++i) m8[i & 7] = fmaxf(m8[i & 7], sc[i]);
+            const float mx = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])), fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7])));
             red[hf * BQ + row] = mx;
             softmax_sync();
             const float m_blk = fmaxf(red[row], red[BQ + row]);
             const float m_new = fmaxf(m_run, m_blk);
             const float m_use = m_new == -INFINITY ? 0.f : m_new;
             const float alpha = exp2f(m_run - m_use);
-            float lsum = 0.f;
+            float l4[4] = {0.f, 0.f, 0.f, 0.f};
             uint32_t pk[32];
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
                 const float p0 = exp2f(sc[2 * i] - m_use), p1 = exp2f(sc[2 * i + 1] - m_use);
-                lsum += p0 + p1;
+                l4[i & 3] += p0 + p1;
                 const __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
                 pk[i] = *reinterpret_cast<const uint32_t*>(&h2);
             }
-            l_part = l_part * alpha + lsum;
+            l_part = l_part * alpha + ((l4[0] + l4[1]) + (l4[2] + l4[3]));
             m_run = m_new;
             // the deferred read-back of O_{j-1}; its MMA ran while the scores above were reduced
             if (j > 0) {
@@ -335,11 +339,12 @@ template <int D>
 struct SmB {
     static constexpr int TILE = 128 * D * 2;                 // K, V, Q, dO
     static constexpr int PT = 128 * 128 * 2;                 // P, dS
+    static constexpr int NST = D == 64 ? 2 : 1;              // Q_i / dO_i stages: two where shared memory allows
     static constexpr int OFF_K = 0;
     static constexpr int OFF_V = OFF_K + TILE;
     static constexpr int OFF_Q = OFF_V + TILE;
-    static constexpr int OFF_DO = OFF_Q + TILE;
-    static constexpr int OFF_P = OFF_DO + TILE;
+    static constexpr int OFF_DO = OFF_Q + NST * TILE;
+    static constexpr int OFF_P = OFF_DO + NST * TILE;
     static constexpr int OFF_DS = OFF_P + PT;
     static constexpr int OFF_BAR = OFF_DS + PT;
     static constexpr int TOTAL = OFF_BAR + 256 + 1024;
@@ -363,14 +368,15 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     uint8_t* sp = smem + S::OFF_P;
     uint8_t* sds = smem + S::OFF_DS;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::OFF_BAR);
+    constexpr int NST = S::NST;
     uint64_t* kv_full = bars;            // K_j, V_j loaded (once)
-    uint64_t* qdo_full = bars + 1;       // Q_i, dO_i loaded
-    uint64_t* qdo_empty = bars + 2;      // the MMAs that read them have completed
-    uint64_t* sdp_full = bars + 3;       // S and dP are in TMEM
-    uint64_t* pds_ready = bars + 4;      // P and dS are in shared memory (8 arrivals)
-    uint64_t* dq_full = bars + 5;        // dV, dK updated, dQ_i in TMEM
-    uint64_t* dq_read = bars + 6;        // dQ_i has been read back (8 arrivals)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
+    uint64_t* qdo_full = bars + 1;       // [2] Q_i, dO_i loaded
+    uint64_t* qdo_empty = bars + 3;      // [2] the MMAs that read them have completed
+    uint64_t* sdp_full = bars + 5;       // S and dP are in TMEM
+    uint64_t* pds_ready = bars + 6;      // P and dS are in shared memory (8 arrivals)
+    uint64_t* dq_full = bars + 7;        // dV, dK updated, dQ_i in TMEM
+    uint64_t* dq_read = bars + 8;        // dQ_i has been read back (8 arrivals)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -385,7 +391,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     const int n_it = per_head * group;
 
     if (threadIdx.x == 0) {
-        mbar_init(kv_full, 1); mbar_init(qdo_full, 1); mbar_init(qdo_empty, 1); mbar_init(sdp_full, 1);
+        mbar_init(kv_full, 1); mbar_init(sdp_full, 1);
+        for (int st = 0; st < 2; ++st) { mbar_init(&qdo_full[st], 1); mbar_init(&qdo_empty[st], 1); }
         mbar_init(pds_ready, 8); mbar_init(dq_full, 1); mbar_init(dq_read, 8);
         *abort_flag = 0;
         mbar_fence_init();
@@ -412,12 +419,13 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             }
             for (int it = 0; it < n_it && ok; ++it) {
                 const int h = head0 + it / per_head, i = i_start + it % per_head;
-                if (it > 0) ok = mbar_wait(qdo_empty, (uint32_t)((it - 1) & 1), P.status);
+                const int stg = it % NST;
+                if (it >= NST) ok = mbar_wait(&qdo_empty[stg], (uint32_t)(((it / NST) - 1) & 1), P.status);
                 if (!ok) break;
-                mbar_expect_tx(qdo_full, 2 * S::TILE);
+                mbar_expect_tx(&qdo_full[stg], 2 * S::TILE);
                 for (int c = 0; c < D / 64; ++c) {
-                    tma_load_2d(sq + c * 16384, &tmQ, h * D + c * 64, b * P.Tq + i * 128, qdo_full);
-                    tma_load_2d(sdo + c * 16384, &tmDO, h * D + c * 64, b * P.Tq + i * 128, qdo_full);
+                    tma_load_2d(sq + stg * S::TILE + c * 16384, &tmQ, h * D + c * 64, b * P.Tq + i * 128, &qdo_full[stg]);
+                    tma_load_2d(sdo + stg * S::TILE + c * 16384, &tmDO, h * D + c * 64, b * P.Tq + i * 128, &qdo_full[stg]);
                 }
             }
             if (!ok) *abort_flag = 1;
@@ -429,9 +437,11 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             constexpr uint32_t idesc_tt = instr_desc(128, D, 1, 1);        // dV, dK: A = P / dS read MN-major, B = dO / Q MN-major
             constexpr uint32_t idesc_dq = instr_desc(128, D, 0, 1);        // dQ: A = dS K-major, B = K MN-major
             bool ok = mbar_wait(kv_full, 0, P.status);
-            const uint32_t aK = smem_u32(sk), aV = smem_u32(sv), aQ = smem_u32(sq), aDO = smem_u32(sdo), aP = smem_u32(sp), aDS = smem_u32(sds);
+            const uint32_t aK = smem_u32(sk), aV = smem_u32(sv), aP = smem_u32(sp), aDS = smem_u32(sds);
             for (int it = 0; it < n_it && ok; ++it) {
-                ok = mbar_wait(qdo_full, (uint32_t)(it & 1), P.status);
+                const int stg = it % NST;
+                const uint32_t aQ = smem_u32(sq + stg * S::TILE), aDO = smem_u32(sdo + stg * S::TILE);
+                ok = mbar_wait(&qdo_full[stg], (uint32_t)((it / NST) & 1), P.status);
                 if (ok && it > 0) ok = mbar_wait(dq_read, (uint32_t)((it - 1) & 1), P.status);
                 if (!ok) break;
                 tc_fence_after();
@@ -462,7 +472,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                     for (int k = 0; k < 4; ++k)
                         umma_bf16(tmem_base + TM_S, smem_desc(aDS + c * 16384 + k * 32, 16, 1024),
                                   smem_desc(aK + (c * 4 + k) * 2048, 16384, 1024), idesc_dq, (c > 0 || k > 0) ? 1u : 0u);
-                umma_commit(qdo_empty);
+                umma_commit(&qdo_empty[stg]);
                 umma_commit(dq_full);
             }
             if (!ok) *abort_flag = 1;

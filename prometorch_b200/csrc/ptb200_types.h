@@ -1,0 +1,50 @@
+// Plain-C structures that cross the library boundary (decode engine descriptors, GEMM staging request).
+// prometorch_b200/_native.py mirrors them with ctypes; keep the two in step.
+#pragma once
+
+#define PTB_MAX_PEERS 8
+
+// One quantised matrix in the layout its kernel streams.
+typedef struct PtbWeightDesc {
+    const void* w;          // GEMV streaming layout ([segment][row][segment bytes]) or, for tables, row-major rows
+    const void* bias;       // optional fp32 [rows]
+    int qtype;              // 0 = Q4_K, 1 = Q6_K (structure of arrays), tables also: 2 = fp16, 3 = fp32
+    int rows, cols;
+    int rowbytes;           // > 0 only for row-major tables (the embedding)
+} PtbWeightDesc;
+
+typedef struct PtbLayerDesc {
+    PtbWeightDesc q, k, v, o, gate, up, down;
+    const float* attn_norm;
+    const float* ffn_norm;
+    const float* q_norm;
+    const float* k_norm;
+    const float* cos;       // per-layer RoPE tables [max_seq][head_dim / 2] (sliding-window layers may use another base)
+    const float* sin;
+    int window;             // sliding-window width, 0 = full attention
+    int pad;
+    const float* post_attn_norm;   // RMSNorm of the attention block's output before the residual add (or null)
+    const float* post_ffn_norm;    // ... and of the FFN block's output
+} PtbLayerDesc;
+
+typedef struct PtbModelDesc {
+    int n_layers, hidden, n_heads, n_kv_heads, head_dim, inter, vocab, max_seq;   // head counts are per rank
+    float eps, emb_scale;
+    int neox, act_gelu, norm_add_one, want_logits;
+    PtbWeightDesc embed, lm_head;
+    const float* out_norm;
+    int tp_rank, tp_world, vocab_offset, pad;
+    void* peer_inbox[3][PTB_MAX_PEERS];     // tensor parallelism: three receive buffers (attention out, FFN down, lm_head pair)
+    int slot_elems, pad2;
+} PtbModelDesc;
+
+// Request to stage a row-sharded GEMM operand from the peers inside the launch.
+typedef struct PtbStaging {
+    void* peer[PTB_MAX_PEERS];   // peer r's full-size buffer as mapped on this GPU
+    void* local;                 // this GPU's full-size buffer
+    void* flags;                 // uint32 [ceil(stored_rows / 128)]: last sequence number staged per 128-row block
+    int rank, world, shard_rows, stored_rows;
+    long long row_bytes;
+    unsigned seq;                // 0 disables staging
+    int pad;
+} PtbStaging;

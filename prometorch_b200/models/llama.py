@@ -53,9 +53,16 @@ class LlamaBlock(nn.Module):
         self.mlp_norm = FusedRMSNorm(cfg.hidden_size, cfg.rms_eps)
         self.mlp = FusedSwiGLU(cfg.hidden_size, cfg.intermediate_size)
 
-    def forward(self, x):
-        x = x + self.attn(self.attn_norm(x))
-        return x + self.mlp(self.mlp_norm(x))
+    def forward(self, x, delta=None):
+        """``x``: the residual stream; ``delta``: the previous block's MLP output, not yet added.  Every residual
+        add is fused into the RMSNorm that follows it (one kernel reads both, writes the sum and the normalised
+        row); returns the updated stream and this block's pending MLP output."""
+        if delta is None:
+            h = self.attn_norm(x)
+        else:
+            h, x = self.attn_norm(delta, x)
+        h, x = self.mlp_norm(self.attn(h), x)
+        return x, self.mlp(h)
 
 
 class Llama(nn.Module):
@@ -78,10 +85,11 @@ class Llama(nn.Module):
                 nn.init.zeros_(m.bias)
 
     def forward(self, tokens: torch.Tensor, targets: Optional[torch.Tensor] = None):
-        x = self.embed(tokens)
+        x, delta = self.embed(tokens), None
         for blk in self.blocks:
-            x = blk(x)
-        logits = self.lm_head(self.norm(x))
+            x, delta = blk(x, delta)
+        h = self.norm(x) if delta is None else self.norm(delta, x)[0]
+        logits = self.lm_head(h)
         if targets is None:
             return logits
         return self.loss_fn(logits.view(-1, logits.shape[-1]), targets.reshape(-1))

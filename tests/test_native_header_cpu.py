@@ -20,6 +20,11 @@ def test_header_parses(tmp_path, lang, cc):
     assert r.returncode == 0, r.stderr
 
 
+def test_header_is_up_to_date():
+    from prometorch_b200 import _gen_header
+    assert open(os.path.join(CSRC, "ptb200.h")).read() == _gen_header.render(), "run `python -m prometorch_b200._gen_header`"
+
+
 def test_header_lists_every_entry_point():
     declared = set(re.findall(r"\b(ptb_\w+)\s*\(", open(os.path.join(CSRC, "ptb200.h")).read()))
     defined = set()
@@ -27,3 +32,11 @@ def test_header_lists_every_entry_point():
         if f.endswith(".cu"):
             defined |= set(re.findall(r"PTB_API[^;{]*?\b(ptb_\w+)\s*\(", open(os.path.join(CSRC, f)).read()))
     assert defined - declared == set(), sorted(defined - declared)
+
+
+@pytest.mark.skipif(shutil.which("g++") is None or not os.path.isdir(CUDA_INC), reason="needs g++ and the CUDA headers")
+def test_cpp_wrapper_parses(tmp_path):
+    src = tmp_path / "t.cpp"
+    src.write_text('#include "ptb200.hpp"\nint main() { ptb200::check(0, "x"); return 0; }\n')
+    r = subprocess.run(["g++", "-std=c++17", "-fsyntax-only", f"-I{CUDA_INC}", f"-I{CSRC}", str(src)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
