@@ -215,6 +215,81 @@ __global__ void rope_kernel(const T* __restrict__ x, T* __restrict__ y, const fl
     }
 }
 
+// Fused split + rotary embedding of a packed projection: qkv [rows, (H + 2 Hk) D] (q heads, then k heads, then v heads;
+// row = b * T + t) -> q [rows, H, D] and k [rows, Hk, D] rotated, v [rows, Hk, D] copied.  Backward (sign = -1) runs the
+// other way: dq, dk, dv -> dqkv with the inverse rotation.  16 bytes per access; one pass over the data instead of two
+// rotary launches and three strided copies.
+template <typename T, bool BWD>
+__global__ void qkv_rope_split_kernel(T* __restrict__ qkv, T* __restrict__ q, T* __restrict__ k, T* __restrict__ v,
+                                      const float* __restrict__ cs, const float* __restrict__ sn, long long rows, int Tlen, int H, int Hk,
+                                      int D, int neox, int pos_offset) {
+    const int half = D / 2, nh = H + Hk;
+    const int per_head = neox ? D / 16 : D / 8;                 // rotation items per head: a lo/hi vector pair, or one vector of 4 pairs
+    const long long n_rot = rows * nh * per_head, n_copy = rows * Hk * (D / 8);
+    const int ld = (H + 2 * Hk) * D;
+    const float sign = BWD ? -1.f : 1.f;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < n_rot + n_copy; idx += (long long)gridDim.x * blockDim.x) {
+        if (idx < n_rot) {
+            const int c = (int)(idx % per_head);
+            const long long rh = idx / per_head;
+            const int h = (int)(rh % nh);
+            const long long row = rh / nh;
+            const int t = (int)(row % Tlen) + pos_offset;
+            T* packed = qkv + row * ld + (size_t)h * D;
+            T* split = h < H ? q + (row * H + h) * D : k + (row * Hk + (h - H)) * D;
+            T* src = BWD ? split : packed;
+            T* dst = BWD ? packed : split;
+            if (neox) {
+                Vec8<T> lo, hi, olo, ohi;
+                float a[8], b[8], oa[8], ob[8];
+                lo.load(src + c * 8);
+                hi.load(src + half + c * 8);
+                lo.get(a);
+                hi.get(b);
+                const float4 c0 = reinterpret_cast<const float4*>(cs + (size_t)t * half + c * 8)[0], c1 = reinterpret_cast<const float4*>(cs + (size_t)t * half + c * 8)[1];
+                const float4 s0 = reinterpret_cast<const float4*>(sn + (size_t)t * half + c * 8)[0], s1 = reinterpret_cast<const float4*>(sn + (size_t)t * half + c * 8)[1];
+                const float cc[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+                const float ss[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    oa[j] = a[j] * cc[j] - b[j] * ss[j] * sign;
+                    ob[j] = b[j] * cc[j] + a[j] * ss[j] * sign;
+                }
+                olo.set(oa);
+                ohi.set(ob);
+                olo.store(dst + c * 8);
+                ohi.store(dst + half + c * 8);
+            } else {
+                Vec8<T> x, o;
+                float a[8], oa[8];
+                x.load(src + c * 8);
+                x.get(a);
+                const float4 c4 = *reinterpret_cast<const float4*>(cs + (size_t)t * half + c * 4);
+                const float4 s4 = *reinterpret_cast<const float4*>(sn + (size_t)t * half + c * 4);
+                const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, ss[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    oa[2 * j] = a[2 * j] * cc[j] - a[2 * j + 1] * ss[j] * sign;
+                    oa[2 * j + 1] = a[2 * j + 1] * cc[j] + a[2 * j] * ss[j] * sign;
+                }
+                o.set(oa);
+                o.store(dst + c * 8);
+            }
+        } else {
+            const long long i = idx - n_rot;
+            const int c = (int)(i % (D / 8));
+            const long long rh = i / (D / 8);
+            const int h = (int)(rh % Hk);
+            const long long row = rh / Hk;
+            T* packed = qkv + row * ld + (size_t)(H + Hk + h) * D + c * 8;
+            T* split = v + (row * Hk + h) * D + c * 8;
+            Vec8<T> x;
+            x.load(BWD ? split : packed);
+            x.store(BWD ? packed : split);
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------------------ gated activation
 // gu: [rows, 2*I] with the gate in columns [0, I) and the up projection in [I, 2I); out: [rows, I].
 template <typename T>
@@ -381,6 +456,23 @@ PTB_API int ptb_rope(const void* x, void* y, const float* cos, const float* sin,
     if (n_pairs == 0) return 0;
     const int grid = (int)std::min<long long>((n_pairs + 255) / 256, 148LL * 16);
     PTB_DISPATCH_T(bf16, rope_kernel<T><<<grid, 256, 0, st>>>((const T*)x, (T*)y, cos, sin, n_pairs, T_, heads, D, neox, backward ? -1.f : 1.f, pos_offset));
+    PTB_CUDA_OK(cudaGetLastError());
+    return 0;
+}
+
+// Forward: qkv -> (q, k rotated; v).  Backward (backward != 0): (dq, dk, dv) -> dqkv with the inverse rotation.
+// rows = B * T; cos/sin fp32 [>= pos_offset + T, D/2]; D a multiple of 16.
+PTB_API int ptb_qkv_rope_split(void* qkv, void* q, void* k, void* v, const float* cos, const float* sin, long long rows, int T_, int H, int Hk,
+                               int D, int neox, int pos_offset, int backward, int bf16, cudaStream_t st) {
+    if (D % 16) { ptb_set_error("qkv_rope_split: head size %d must be a multiple of 16", D); return -1; }
+    if (rows == 0) return 0;
+    const long long items = rows * (H + Hk) * (neox ? D / 16 : D / 8) + rows * Hk * (D / 8);
+    const int grid = (int)std::min<long long>((items + 255) / 256, 148LL * 16);
+    if (backward) {
+        PTB_DISPATCH_T(bf16, qkv_rope_split_kernel<T, true><<<grid, 256, 0, st>>>((T*)qkv, (T*)q, (T*)k, (T*)v, cos, sin, rows, T_, H, Hk, D, neox, pos_offset));
+    } else {
+        PTB_DISPATCH_T(bf16, qkv_rope_split_kernel<T, false><<<grid, 256, 0, st>>>((T*)qkv, (T*)q, (T*)k, (T*)v, cos, sin, rows, T_, H, Hk, D, neox, pos_offset));
+    }
     PTB_CUDA_OK(cudaGetLastError());
     return 0;
 }

@@ -79,10 +79,10 @@ class FlashSelfAttention(nn.Module):
     def forward(self, x, pos_offset: int = 0):
         from ..ops.attention import flash_attention
         B, T, _ = x.shape
-        qkv = self.qkv(x).view(B, T, self.h + 2 * self.kv, self.d)
-        q, k, v = qkv[:, :, :self.h], qkv[:, :, self.h:self.h + self.kv], qkv[:, :, self.h + self.kv:]
         if self.use_rope:
-            q = K.rope(q, self.cos, self.sin, self.neox, pos_offset)
-            k = K.rope(k, self.cos, self.sin, self.neox, pos_offset)
+            q, k, v = K.qkv_rope_split(self.qkv(x), self.h, self.kv, self.d, self.cos, self.sin, self.neox, pos_offset)
+        else:
+            qkv = self.qkv(x).view(B, T, self.h + 2 * self.kv, self.d)
+            q, k, v = qkv[:, :, :self.h], qkv[:, :, self.h:self.h + self.kv], qkv[:, :, self.h + self.kv:]
         o = flash_attention(q, k, v, causal=self.causal)
         return self.out(o.reshape(B, T, self.h * self.d))

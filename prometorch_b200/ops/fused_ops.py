@@ -23,6 +23,8 @@ def _decls(L):
     L.ptb_rmsnorm_fwd.argtypes = [vp, vp, vp, vp, ll, ci, cf, vp, vp, ci, vp]
     L.ptb_rmsnorm_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, ci, ll, ci, vp, ci, vp]
     L.ptb_rope.argtypes = [vp, vp, vp, vp, ll, ci, ci, ci, ci, ci, ci, ci, vp]
+    L.ptb_qkv_rope_split.argtypes = [vp, vp, vp, vp, vp, vp, ll, ci, ci, ci, ci, ci, ci, ci, ci, vp]
+    L.ptb_qkv_rope_split.restype = ci
     L.ptb_gated_act_fwd.argtypes = [vp, vp, ll, ci, ci, ci, vp]
     L.ptb_gated_act_bwd.argtypes = [vp, vp, vp, ll, ci, ci, ci, vp]
     L.ptb_xent.argtypes = [vp, vp, vp, vp, vp, ll, ci, ll, cf, ll, ci, vp]
@@ -148,6 +150,43 @@ def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, neox: bool = Tru
         return torch.cat([a * c - b * s, b * c + a * s], -1).to(x.dtype)
     a, b = xf[..., 0::2], xf[..., 1::2]
     return torch.stack([a * c - b * s, b * c + a * s], -1).flatten(-2).to(x.dtype)
+
+
+class _QkvRopeSplit(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, cos, sin, H, Hk, D, neox, pos_offset):
+        B, T = qkv.shape[0], qkv.shape[1]
+        p = qkv.contiguous().view(B * T, (H + 2 * Hk) * D)
+        q = torch.empty(B, T, H, D, dtype=qkv.dtype, device=qkv.device)
+        k = torch.empty(B, T, Hk, D, dtype=qkv.dtype, device=qkv.device)
+        v = torch.empty(B, T, Hk, D, dtype=qkv.dtype, device=qkv.device)
+        N.check(N.lib().ptb_qkv_rope_split(p.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), cos.data_ptr(), sin.data_ptr(), B * T, T, H,
+                                           Hk, D, int(neox), pos_offset, 0, _is_bf16(p), _stream(p)), "qkv_rope_split")
+        ctx.save_for_backward(cos, sin)
+        ctx.meta = (B, T, H, Hk, D, neox, pos_offset, qkv.shape)
+        return q, k, v
+
+    @staticmethod
+    def backward(ctx, dq, dk, dv):
+        cos, sin = ctx.saved_tensors
+        B, T, H, Hk, D, neox, pos_offset, shape = ctx.meta
+        dq, dk, dv = dq.contiguous(), dk.contiguous(), dv.contiguous()
+        dqkv = torch.empty(B * T, (H + 2 * Hk) * D, dtype=dq.dtype, device=dq.device)
+        N.check(N.lib().ptb_qkv_rope_split(dqkv.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), cos.data_ptr(), sin.data_ptr(), B * T, T,
+                                           H, Hk, D, int(neox), pos_offset, 1, _is_bf16(dq), _stream(dq)), "qkv_rope_split_bwd")
+        return dqkv.view(shape), None, None, None, None, None, None, None
+
+
+def qkv_rope_split(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, cos: torch.Tensor, sin: torch.Tensor,
+                   neox: bool = True, pos_offset: int = 0):
+    """``qkv [B, T, (H + 2 Hk) D]`` (q heads, k heads, v heads) -> rotated ``q [B, T, H, D]``, rotated ``k`` and ``v``
+    ``[B, T, Hk, D]``, contiguous, in one pass (the split, both rotary embeddings and the copies of the three slices)."""
+    H, Hk, D = num_heads, num_kv_heads, head_dim
+    if qkv.is_cuda and D % 16 == 0:
+        return _QkvRopeSplit.apply(qkv, cos.float().contiguous(), sin.float().contiguous(), H, Hk, D, neox, pos_offset)
+    B, T = qkv.shape[0], qkv.shape[1]
+    x = qkv.view(B, T, H + 2 * Hk, D)
+    return rope(x[:, :, :H], cos, sin, neox, pos_offset), rope(x[:, :, H:H + Hk], cos, sin, neox, pos_offset), x[:, :, H + Hk:]
 
 
 # ----------------------------------------------------------------------------- gated activation

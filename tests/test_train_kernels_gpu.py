@@ -102,6 +102,31 @@ def test_rope(neox):
     assert _rel(y, yr) < 1e-2 and _rel(x.grad, xr.grad) < 1e-2
 
 
+@pytest.mark.parametrize("neox,H,Hk,D,off", [(True, 8, 2, 128, 0), (False, 6, 6, 64, 3), (True, 4, 1, 64, 5)])
+def test_qkv_rope_split(neox, H, Hk, D, off):
+    """The fused split + rotary kernel against rope() on the three slices, forward and backward."""
+    from prometorch_b200.io.config import tiny_qwen3_config
+    from prometorch_b200.models.gguf_oracle import apply_rope, rope_tables
+    from prometorch_b200.ops.fused_ops import qkv_rope_split
+    cfg = tiny_qwen3_config(head_dim=D)
+    cos, sin = rope_tables(cfg, 64, "cuda")
+    B, T = 2, 40
+    qkv = torch.randn(B, T, (H + 2 * Hk) * D, device="cuda").bfloat16().requires_grad_()
+    q, k, v = qkv_rope_split(qkv, H, Hk, D, cos, sin, neox, off)
+    gq, gk, gv = torch.randn_like(q), torch.randn_like(k), torch.randn_like(v)
+    torch.autograd.backward([q, k, v], [gq, gk, gv])
+    r = qkv.detach().float().requires_grad_()
+    x = r.view(B, T, H + 2 * Hk, D)
+    c, s_ = cos[off:off + T], sin[off:off + T]
+    qr = torch.stack([apply_rope(x[b, :, :H], c, s_, neox) for b in range(B)])
+    kr = torch.stack([apply_rope(x[b, :, H:H + Hk], c, s_, neox) for b in range(B)])
+    vr = x[:, :, H + Hk:]
+    torch.autograd.backward([qr, kr, vr], [gq.float(), gk.float(), gv.float()])
+    assert q.is_contiguous() and k.is_contiguous() and v.is_contiguous()
+    assert _rel(q, qr) < 1e-2 and _rel(k, kr) < 1e-2 and torch.equal(v.float(), vr.detach().to(torch.bfloat16).float())
+    assert _rel(qkv.grad, r.grad) < 1e-2
+
+
 @pytest.mark.parametrize("gelu", [False, True])
 def test_swiglu(gelu):
     from prometorch_b200.ops.fused_ops import swiglu
