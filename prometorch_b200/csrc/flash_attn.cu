@@ -154,12 +154,15 @@ __global__ void __launch_bounds__(THREADS) fwd_kernel(const __grid_constant__ Fw
 // delta[b,h,t] = sum_d dO * O
 template <int D>
 __global__ void delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout, float* __restrict__ delta,
-                             long long rows, int H, int Tq) {
+                             long long rows, int H, int Tq, float* __restrict__ dq_zero = nullptr) {
     const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;     // one warp per (b, t, h) row
     const int lane = threadIdx.x & 31;
     if (w >= rows) return;
     const __nv_bfloat16* op = o + w * D;
     const __nv_bfloat16* dp = dout + w * D;
+    if (dq_zero) {          // the fp32 dQ accumulator has the same [B, Tq, H, D] rows: clear this one on the way
+        for (int i = lane * 4; i < D; i += 128) *reinterpret_cast<float4*>(dq_zero + w * D + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     float s = 0.f;
     for (int i = lane * 2; i < D; i += 64) {
         const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(op + i));
@@ -373,13 +376,14 @@ static int run_bwd(const BwdParams& p, const void* o, cudaStream_t st) {
     return 0;
 }
 
-// delta[b, h, t] = sum_d dO * O (fp32 [B, H, Tq]): the row term of the softmax backward.
-PTB_API int ptb_flash_attn_delta(const void* o, const void* dout, float* delta, int B, int Tq, int H, int D, cudaStream_t st) {
+// delta[b, h, t] = sum_d dO * O (fp32 [B, H, Tq]): the row term of the softmax backward.  dq_zero (optional): an fp32
+// [B, Tq, H, D] buffer cleared in the same pass (the dQ accumulator of the backward kernel).
+PTB_API int ptb_flash_attn_delta(const void* o, const void* dout, float* delta, int B, int Tq, int H, int D, float* dq_zero, cudaStream_t st) {
     const long long rows = (long long)B * Tq * H;
     if (rows == 0) return 0;
     const unsigned grid = (unsigned)((rows * 32 + 255) / 256);
-    if (D == 64) delta_kernel<64><<<grid, 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, delta, rows, H, Tq);
-    else if (D == 128) delta_kernel<128><<<grid, 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, delta, rows, H, Tq);
+    if (D == 64) delta_kernel<64><<<grid, 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, delta, rows, H, Tq, dq_zero);
+    else if (D == 128) delta_kernel<128><<<grid, 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, delta, rows, H, Tq, dq_zero);
     else { ptb_set_error("flash attention: head_dim %d not supported", D); return -1; }
     PTB_CUDA_OK(cudaGetLastError());
     return 0;

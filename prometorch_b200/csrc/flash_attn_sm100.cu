@@ -633,9 +633,9 @@ PTB_API int ptb_flash_attn_fwd_sm100(const void* q, const void* k, const void* v
     return -1;
 }
 
-extern "C" int ptb_flash_attn_delta(const void* o, const void* dout, float* delta, int B, int Tq, int H, int D, cudaStream_t st);
+extern "C" int ptb_flash_attn_delta(const void* o, const void* dout, float* delta, int B, int Tq, int H, int D, float* dq_zero, cudaStream_t st);
 
-// Backward on tcgen05.  dq: fp32 [B, Tq, H, D] zero-initialised by the caller; delta: fp32 [B, H, Tq] scratch.
+// Backward on tcgen05.  dq: fp32 [B, Tq, H, D] (cleared here, together with the delta pass); delta: fp32 [B, H, Tq] scratch.
 // dk, dv: bf16 [gsplit][B, Tk, Hk, D]: with grouped-query heads the query heads of one KV head can be split over
 // `gsplit` CTAs (a divisor of H / Hk) so that small problems fill the GPU; the caller sums the slices.
 PTB_API int ptb_flash_attn_bwd_sm100(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
@@ -647,7 +647,7 @@ PTB_API int ptb_flash_attn_bwd_sm100(const void* q, const void* k, const void* v
         PTB_CUDA_OK(cudaGetDevice(&dev));
         PTB_CUDA_OK(cudaSetDevice(dev));
     }
-    if (ptb_flash_attn_delta(o, dout, delta, B, Tq, H, D, st)) return -1;
+    if (ptb_flash_attn_delta(o, dout, delta, B, Tq, H, D, dq, st)) return -1;      // also clears dq
     if (D == 128) return ptb::fa100::launch_bwd<128>(q, k, v, dout, lse, delta, dq, dk, dv, B, Tq, Tk, H, Hk, causal, scale, q_offset, gsplit, status, st);
     if (D == 64) return ptb::fa100::launch_bwd<64>(q, k, v, dout, lse, delta, dq, dk, dv, B, Tq, Tk, H, Hk, causal, scale, q_offset, gsplit, status, st);
     ptb_set_error("flash attention (tcgen05): head size %d not supported (64, 128)", D);

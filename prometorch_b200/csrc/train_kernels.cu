@@ -196,6 +196,104 @@ template <> __global__ void colsum_kernel<__nv_bfloat16>(const float* __restrict
     out[c] = __float2bfloat16_rn(s);
 }
 
+// RMSNorm backward, one warp per row: the row's two reductions are warp shuffles (no block barrier per row), each lane
+// owns up to MAXI 8-element vectors of the row, x / dy are read twice (the second pass hits L1).  A CTA's eight warps
+// combine their dw sums through shared memory once, at the end.  H <= 256 * MAXI.
+template <typename T, int MAXI>
+__global__ void __launch_bounds__(256) rmsnorm_bwd_warp_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ dy,
+                                                               const float* __restrict__ rstd, T* __restrict__ dx,
+                                                               float* __restrict__ dw_partial, long long rows, int H,
+                                                               const T* __restrict__ dresid) {
+    __shared__ float sred[8][256];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nv = H / 8;
+    float dwacc[MAXI][8];
+#pragma unroll
+    for (int k = 0; k < MAXI; ++k)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) dwacc[k][j] = 0.f;
+    for (long long row = (long long)blockIdx.x * 8 + warp; row < rows; row += (long long)gridDim.x * 8) {
+        const T* xr = x + row * H;
+        const T* gr = dy + row * H;
+        float dot = 0.f;
+#pragma unroll
+        for (int k = 0; k < MAXI; ++k) {
+            const int i = k * 32 + lane;
+            if (i < nv) {
+                Vec8<T> a, b, c;
+                float xf[8], gf[8], wf[8];
+                a.load(xr + (size_t)i * 8); b.load(gr + (size_t)i * 8); c.load(w + (size_t)i * 8);
+                a.get(xf); b.get(gf); c.get(wf);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) dot += gf[j] * wf[j] * xf[j];
+            }
+        }
+        dot = warp_sum(dot);
+        const float rs = rstd[row];
+        const float cc = dot * rs * rs * rs / (float)H;
+#pragma unroll
+        for (int k = 0; k < MAXI; ++k) {
+            const int i = k * 32 + lane;
+            if (i < nv) {
+                Vec8<T> a, b, c, o;
+                float xf[8], gf[8], wf[8], of[8];
+                a.load(xr + (size_t)i * 8); b.load(gr + (size_t)i * 8); c.load(w + (size_t)i * 8);
+                a.get(xf); b.get(gf); c.get(wf);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    of[j] = rs * gf[j] * wf[j] - cc * xf[j];
+                    dwacc[k][j] += gf[j] * xf[j] * rs;
+                }
+                if (dresid) {
+                    Vec8<T> r;
+                    float rf[8];
+                    r.load(dresid + row * H + (size_t)i * 8);
+                    r.get(rf);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) of[j] += rf[j];
+                }
+                o.set(of);
+                o.store(dx + row * H + (size_t)i * 8);
+            }
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < MAXI; ++k) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sred[warp][lane * 8 + j] = dwacc[k][j];
+        __syncthreads();
+        {
+            const int e = threadIdx.x;                     // element e of this item's 256
+            const int i = k * 32 + (e >> 3);
+            if (i < nv) {
+                float t = 0.f;
+#pragma unroll
+                for (int ww = 0; ww < 8; ++ww) t += sred[ww][e];
+                dw_partial[(size_t)blockIdx.x * H + (size_t)i * 8 + (e & 7)] = t;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// out[c] = sum_p partial[p][c]: 32 columns per CTA, eight row groups summed in parallel, then combined.
+template <typename T>
+__global__ void __launch_bounds__(256) colsum2_kernel(const float* __restrict__ partial, int P, int H, T* __restrict__ out) {
+    __shared__ float sm[8][33];
+    const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+    const int c = blockIdx.x * 32 + cx;
+    float s = 0.f;
+    if (c < H)
+        for (int p = ry; p < P; p += 8) s += partial[(size_t)p * H + c];
+    sm[ry][cx] = s;
+    __syncthreads();
+    if (ry == 0 && c < H) {
+        float t = 0.f;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) t += sm[r][cx];
+        out[c] = (T)t;
+    }
+}
+
 // ------------------------------------------------------------------------------------------ rotary embedding
 // x: [B, T, heads, D] (contiguous), cos/sin: [T, D/2] fp32.  sign = +1 forward, -1 backward (the transpose).
 template <typename T>
@@ -439,13 +537,26 @@ PTB_API int ptb_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, 
     return 0;
 }
 
+// Both backward entry points (caller-provided scratch, static scratch) launch the same two kernels.
+template <typename T>
+static void launch_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rstd, void* dx, void* dw, float* dw_partial,
+                               int n_ctas, long long rows, int H, const void* dresid, cudaStream_t st) {
+    if (H <= 2048) {
+        rmsnorm_bwd_warp_kernel<T, 8><<<n_ctas, 256, 0, st>>>((const T*)x, (const T*)w, (const T*)dy, rstd, (T*)dx, dw_partial, rows, H, (const T*)dresid);
+    } else if (H <= 4096) {
+        rmsnorm_bwd_warp_kernel<T, 16><<<n_ctas, 256, 0, st>>>((const T*)x, (const T*)w, (const T*)dy, rstd, (T*)dx, dw_partial, rows, H, (const T*)dresid);
+    } else {
+        rmsnorm_bwd_kernel<T><<<n_ctas, rms_threads(H), 0, st>>>((const T*)x, (const T*)w, (const T*)dy, rstd, (T*)dx, dw_partial, (int)rows, H, (const T*)dresid);
+    }
+    colsum2_kernel<T><<<(H + 31) / 32, 256, 0, st>>>(dw_partial, n_ctas, H, (T*)dw);
+}
+
 // dw_partial: [n_ctas, H] fp32 scratch.
 PTB_API int ptb_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rstd, void* dx, void* dw, float* dw_partial,
                             int n_ctas, long long rows, int H, const void* dresid, int bf16, cudaStream_t st) {
     if (H % 8 || rms_threads(H) > 1024) { ptb_set_error("rmsnorm: hidden size %d not supported", H); return -1; }
     if (rows == 0) return 0;
-    PTB_DISPATCH_T(bf16, rmsnorm_bwd_kernel<T><<<n_ctas, rms_threads(H), 0, st>>>((const T*)x, (const T*)w, (const T*)dy, rstd, (T*)dx, dw_partial, (int)rows, H, (const T*)dresid);
-                   colsum_kernel<T><<<(H + 255) / 256, 256, 0, st>>>(dw_partial, n_ctas, H, (T*)dw));
+    PTB_DISPATCH_T(bf16, launch_rmsnorm_bwd<T>(x, w, dy, rstd, dx, dw, dw_partial, n_ctas, rows, H, dresid, st));
     PTB_CUDA_OK(cudaGetLastError());
     return 0;
 }
@@ -542,8 +653,7 @@ PTB_API int ptb_rmsnorm_bwd_static(const void* x, const void* w, const void* dy,
         }
         scratch = scratch_of[dev];
     }
-    PTB_DISPATCH_T(bf16, rmsnorm_bwd_kernel<T><<<n_ctas, rms_threads(H), 0, st>>>((const T*)x, (const T*)w, (const T*)dy, rstd, (T*)dx, scratch, (int)rows, H, (const T*)dresid);
-                   colsum_kernel<T><<<(H + 255) / 256, 256, 0, st>>>(scratch, n_ctas, H, (T*)dw));
+    PTB_DISPATCH_T(bf16, launch_rmsnorm_bwd<T>(x, w, dy, rstd, dx, dw, scratch, n_ctas, rows, H, dresid, st));
     PTB_CUDA_OK(cudaGetLastError());
     return 0;
 }

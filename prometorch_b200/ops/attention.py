@@ -88,12 +88,14 @@ class _Flash(torch.autograd.Function):
         B, Tq, H, D = q.shape
         Tk, Hk = k.shape[1], k.shape[2]
         do = do.contiguous()
-        dq32 = torch.zeros(B, Tq, H, D, dtype=torch.float32, device=q.device)
+        import os
+        sm100_bwd = os.environ.get("PTB_FA_BWD_SM100", "1") != "0" and hasattr(N.lib(), "ptb_flash_attn_bwd_sm100")
+        # the tcgen05 path clears the fp32 dQ accumulator inside its delta pass
+        dq32 = (torch.empty if sm100_bwd else torch.zeros)(B, Tq, H, D, dtype=torch.float32, device=q.device)
         dk, dv = torch.empty_like(k), torch.empty_like(v)
         delta = torch.empty(B, H, Tq, dtype=torch.float32, device=q.device)
         st = torch.cuda.current_stream(q.device).cuda_stream
-        import os
-        if os.environ.get("PTB_FA_BWD_SM100", "1") != "0" and hasattr(N.lib(), "ptb_flash_attn_bwd_sm100"):
+        if sm100_bwd:
             from .gemm import _status
             # few KV heads: split each head's query group over several CTAs until the grid fills the GPU twice over
             gs, base, group = 1, ((Tk + 127) // 128) * Hk * B, H // Hk

@@ -83,7 +83,7 @@ class _RMSNorm(torch.autograd.Function):
         dres2 = dres.contiguous().view(-1, H) if (ctx.has_resid and dres is not None) else None
         dx = torch.empty_like(h)
         dw = torch.empty_like(w)
-        n_ctas = min(rows, _sms(h.device) * 4)
+        n_ctas = max(1, min((rows + 7) // 8, _sms(h.device) * 2))      # eight rows (warps) per CTA
         part = torch.empty(n_ctas, H, dtype=torch.float32, device=h.device)
         N.check(N.lib().ptb_rmsnorm_bwd(h.data_ptr(), w.data_ptr(), dy2.data_ptr(), rstd.data_ptr(), dx.data_ptr(), dw.data_ptr(),
                                         part.data_ptr(), n_ctas, rows, H, N.ptr(dres2), _is_bf16(h), _stream(h)), "rmsnorm_bwd")
