@@ -52,7 +52,7 @@ static int launch(const Operand& ta, const Operand& tb, const Params& p, int n_s
         attr = true;
     }
     Params q = p;
-    int n_st = (q.stA.seq || q.stB.seq) ? std::min(16, std::max(1, n_sm / 8)) : 0;
+    int n_st = q.stager_ctas ? std::min(16, std::max(1, n_sm / 8)) : 0;      // stager_ctas arrives as a yes/no request
     // the stagers and the tile CTAs wait on one another, so the whole grid must be resident at once: one CTA per SM
     const int gemm_ctas = std::max(1, std::min(p.tiles_m * p.tiles_n, n_sm - n_st));
     q.stager_ctas = n_st;
@@ -150,6 +150,8 @@ PTB_API int ptb_gemm_bf16_ex(void* const* a_ptrs, int a_shards, int a_shard_rows
     if (!b_mn && b_shards > 1 && b_shard_rows % 256) BN = 128;
     fill_staging(p.stA, stage_a);
     fill_staging(p.stB, stage_b);
+    // stager CTAs are needed unless every staged operand is filled by an external copier
+    p.stager_ctas = ((p.stA.seq && !(stage_a && stage_a->external)) || (p.stB.seq && !(stage_b && stage_b->external))) ? 1 : 0;
     if ((p.stA.seq && (p.stA.shard_rows % STAGE_ROWS)) || (p.stB.seq && (p.stB.shard_rows % STAGE_ROWS))) {
         ptb_set_error("gemm: staged shards must be a multiple of %d rows", STAGE_ROWS);
         return -1;

@@ -46,5 +46,6 @@ typedef struct PtbStaging {
     int rank, world, shard_rows, stored_rows;
     long long row_bytes;
     unsigned seq;                // 0 disables staging
-    int pad;
+    int external;                // non-zero: someone else (copy engines on a side stream) copies the rows and raises the
+                                 // flags; the launch adds no stager CTAs and only waits on the flags
 } PtbStaging;

@@ -34,16 +34,58 @@ def _decls(L):
 class Staging(C.Structure):
     """Request to stage a row-sharded operand from the peers inside the GEMM launch (mirrors ``PtbStaging``)."""
     _fields_ = [("peer", C.c_void_p * 8), ("local", C.c_void_p), ("flags", C.c_void_p), ("rank", C.c_int), ("world", C.c_int),
-                ("shard_rows", C.c_int), ("stored_rows", C.c_int), ("row_bytes", C.c_longlong), ("seq", C.c_uint), ("pad", C.c_int)]
+                ("shard_rows", C.c_int), ("stored_rows", C.c_int), ("row_bytes", C.c_longlong), ("seq", C.c_uint), ("external", C.c_int)]
 
 
-def make_staging(buf, flags: torch.Tensor, rank: int, world: int, shard_rows: int, stored_rows: int, row_bytes: int, seq: int) -> Staging:
+def make_staging(buf, flags: torch.Tensor, rank: int, world: int, shard_rows: int, stored_rows: int, row_bytes: int, seq: int,
+                 external: bool = False) -> Staging:
     s = Staging()
     for r in range(world):
         s.peer[r] = buf.peer_ptr(r)
     s.local, s.flags = buf.peer_ptr(rank), flags.data_ptr()
     s.rank, s.world, s.shard_rows, s.stored_rows, s.row_bytes, s.seq = rank, world, shard_rows, stored_rows, row_bytes, seq
+    s.external = int(external)
     return s
+
+
+_COPY_STREAMS: Dict[int, "torch.cuda.Stream"] = {}
+
+
+def copy_stream(device) -> "torch.cuda.Stream":
+    """The side stream the peer copies run on (one per device)."""
+    idx = torch.device(device).index
+    if idx not in _COPY_STREAMS:
+        _COPY_STREAMS[idx] = torch.cuda.Stream(device=device)
+    return _COPY_STREAMS[idx]
+
+
+def peer_shard_views(buf, elem_cols: int, rank: int, world: int, shard_rows: int):
+    """(local full-size [shard_rows*world, cols] view, {peer: view of that peer's own shard in its buffer})."""
+    n = shard_rows
+    local = buf.tensor(torch.bfloat16)[:n * world * elem_cols].view(n * world, elem_cols)
+    peers = {}
+    for p in range(world):
+        if p != rank:
+            peers[p] = buf.tensor(torch.bfloat16, rank=p)[:n * world * elem_cols].view(n * world, elem_cols)[p * n:(p + 1) * n]
+    return local, peers
+
+
+def stage_with_copy_engines(local: torch.Tensor, peers, flags: torch.Tensor, rank: int, world: int, shard_rows: int, seq: int,
+                            device):
+    """Bring every peer's shard of a row-sharded bf16 matrix into the local full-size buffer with device-to-device
+    copies on the side stream (copy engines, no SM), raising the 128-row block flags of each shard as it lands.
+    A GEMM launched with an ``external`` staging request of the same ``seq`` waits on those flags tile by tile, so the
+    copies overlap its math and it keeps the whole grid for tiles.  The side stream first waits for what the
+    current stream has queued (the barrier that says every rank's rows are in place)."""
+    side = copy_stream(device)
+    side.wait_stream(torch.cuda.current_stream(device))
+    n = shard_rows
+    with torch.cuda.stream(side):
+        for d in range(1, world):
+            p = (rank + d) % world
+            local[p * n:(p + 1) * n].copy_(peers[p], non_blocking=True)
+            flags[p * n // 128:((p + 1) * n + 127) // 128].fill_(seq)
+    return side
 
 
 def gemm_ex(a_ptrs, a_shard_rows, lda, a_mn, b_ptrs, b_shard_rows, ldb, b_mn, M, Nn, K, device, out=None, c_peers=None,
@@ -88,15 +130,21 @@ class _Site:
         self.cols_act = cols_act
         self.stage_flags = torch.zeros((rows * W + 127) // 128, dtype=torch.int32, device=symm.device)
         self.stage_seq = 0
+        self._views = None
 
     def publish(self, x: torch.Tensor):
         """Put this rank's rows in place, wait until every rank has done so, and return (full view, staging)."""
         W, r, n = self.symm.world, self.symm.rank, self.rows
-        full = self.act.buf.tensor(torch.bfloat16)[:n * W * self.cols_act].view(n * W, self.cols_act)
+        if self._views is None:
+            self._views = peer_shard_views(self.act.buf, self.cols_act, r, W, n)
+        full, peers = self._views
         full[r * n:(r + 1) * n].copy_(x)
         self.barrier()
         self.stage_seq += 1
-        st = make_staging(self.act.buf, self.stage_flags, r, W, n, n * W, self.cols_act * 2, self.stage_seq)
+        ext = _external_staging()
+        if ext:
+            stage_with_copy_engines(full, peers, self.stage_flags, r, W, n, self.stage_seq, self.symm.device)
+        st = make_staging(self.act.buf, self.stage_flags, r, W, n, n * W, self.cols_act * 2, self.stage_seq, external=ext)
         return full, st
 
     def barrier(self):
@@ -104,6 +152,13 @@ class _Site:
         st = torch.cuda.current_stream(self.symm.device).cuda_stream
         N.check(N.lib().ptb_peer_barrier(ch.flag_ptrs, self.symm.rank, self.symm.world, ch.next_seq(), ch.ticket.data_ptr(),
                                          ch.status.data_ptr(), st), "peer_barrier")
+
+
+def _external_staging() -> bool:
+    """Peer rows are staged by copy engines on a side stream (default) or, with PTB_STAGE_IN_KERNEL=1, by stager CTAs
+    of the consuming GEMM launch."""
+    import os
+    return os.environ.get("PTB_STAGE_IN_KERNEL", "0") != "1"
 
 
 _SITES: Dict[Tuple, _Site] = {}

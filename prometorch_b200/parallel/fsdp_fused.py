@@ -29,7 +29,7 @@ import torch.nn as nn
 
 from .. import _native as N
 from ..distributed.ddp import PeerChannel
-from ..nn.parallel.fused_tp import gemm_ex, make_staging
+from ..nn.parallel.fused_tp import _external_staging, gemm_ex, make_staging, peer_shard_views, stage_with_copy_engines
 from ..optim import AdamW
 
 
@@ -40,8 +40,9 @@ class _ShardedLinearFn(torch.autograd.Function):
         x2 = x.reshape(-1, x.shape[-1])
         if x2.stride(1) != 1 or x2.stride(0) != x2.shape[1]:
             x2 = x2.contiguous()
-        # B = the local full-size buffer; rows owned by peers are staged from their memory by the stager CTAs of
-        # this same launch (each 128-row block crosses NVLink once per optimizer step), overlapped with the math
+        # B = the local full-size buffer; rows owned by peers cross NVLink once per optimizer step: copy engines
+        # start bringing them in as soon as the owner's optimizer kernel is done (or stager CTAs of this launch
+        # do), and the tile producers of this launch wait on the 128-row block flags, so transfer and math overlap
         y = gemm_ex([x2.data_ptr()], 0, x2.stride(0), False, [sh.full_ptr], 0, sh.inf, False, x2.shape[0], sh.out, sh.inf, x.device,
                     stage_b=sh.staging())
         ctx.save_for_backward(x2)
@@ -97,17 +98,30 @@ class ShardedLinear(nn.Module):
         self.symm = symm
         self._staged_seq = 0
         self.step_count = 0
+        self._views = None
         symm.barrier()
+        self.prefetch()
+
+    def prefetch(self):
+        """Start copying the peers' current shards into the local full-size buffer on the copy stream (the owners'
+        shards are final: the optimizer kernel ends with a barrier across the ranks).  The block flags rise as
+        the shards land; the first GEMM that reads the weight checks them."""
+        if not _external_staging() or self.symm.world == 1:
+            return
+        if self._views is None:
+            self._views = peer_shard_views(self.shard_ch.buf, self.inf, self.symm.rank, self.symm.world, self.S)
+        stage_with_copy_engines(self._views[0], self._views[1], self.stage_flags, self.symm.rank, self.symm.world, self.S,
+                                self.stage_seq, self.symm.device)
 
     def staging(self):
         """Staging request for the first GEMM that touches the weight after an optimizer step; ``None`` afterwards:
-        that launch copied every peer block (its stagers walk the whole matrix), later launches on the same
-        stream read the local copy with the full grid."""
+        by the end of that launch every peer block is local (it waited for, or copied, the whole matrix), so later
+        launches on the same stream read the local copy without looking at the flags."""
         if self._staged_seq == self.stage_seq:
             return None
         self._staged_seq = self.stage_seq
         return make_staging(self.shard_ch.buf, self.stage_flags, self.symm.rank, self.symm.world, self.S,
-                            self.S * self.symm.world, self.inf * 2, self.stage_seq)
+                            self.S * self.symm.world, self.inf * 2, self.stage_seq, external=_external_staging())
 
     def forward(self, x):
         return _ShardedLinearFn.apply(x, self)
@@ -123,7 +137,8 @@ class ShardedLinear(nn.Module):
                                           betas[0], betas[1], eps, wd, self.step_count, grad_scale, ch.next_seq(),
                                           ch.ticket.data_ptr(), ch.status.data_ptr(), n_ctas, st), "fsdp_rs_adamw")
         self.grad_full.zero_()
-        self.stage_seq += 1             # the peers' rows of w_full are stale now: the next GEMM restages them
+        self.stage_seq += 1             # the peers' rows of w_full are stale now
+        self.prefetch()
 
     def full_weight(self) -> torch.Tensor:
         """Gather the bf16 weight (checkpointing / tests)."""
