@@ -54,7 +54,7 @@ static int launch(const Operand& ta, const Operand& tb, const Params& p, int n_s
     Params q = p;
     int n_st = q.stager_ctas ? std::min(16, std::max(1, n_sm / 8)) : 0;      // stager_ctas arrives as a yes/no request
     // the stagers and the tile CTAs wait on one another, so the whole grid must be resident at once: one CTA per SM
-    const int gemm_ctas = std::max(1, std::min(p.tiles_m * p.tiles_n, n_sm - n_st));
+    const int gemm_ctas = std::max(1, std::min(p.tiles_m * p.tiles_n * std::max(1, p.splits), n_sm - n_st));
     q.stager_ctas = n_st;
     kern<<<gemm_ctas + n_st, THREADS, smem, st>>>(ta, tb, q);
     PTB_CUDA_OK(cudaGetLastError());
@@ -107,10 +107,12 @@ static void fill_staging(Staging& S, const PtbStaging* h) {
 
 // General entry point.  a_ptrs/b_ptrs: arrays of a_shards/b_shards device pointers.  c_peers (EPI_SCATTER_ADD):
 // `c_shards` fp32 buffers [out_shard_rows, ldc], one per rank.
-PTB_API int ptb_gemm_bf16_ex(void* const* a_ptrs, int a_shards, int a_shard_rows, long long lda, int a_mn, void* const* b_ptrs,
-                             int b_shards, int b_shard_rows, long long ldb, int b_mn, void* C, long long ldc, void* const* c_peers,
-                             int c_shards, int out_shard_rows, int M, int N, int K, const float* bias, int flags, int* status,
-                             int n_sm, cudaStream_t st, const PtbStaging* stage_a, const PtbStaging* stage_b) {
+struct SplitK { int splits; long long stride; };      // splits > 1: fp32 partials at C + s*stride, BN forced to 128
+
+static int gemm_core(void* const* a_ptrs, int a_shards, int a_shard_rows, long long lda, int a_mn, void* const* b_ptrs,
+                     int b_shards, int b_shard_rows, long long ldb, int b_mn, void* C, long long ldc, void* const* c_peers,
+                     int c_shards, int out_shard_rows, int M, int N, int K, const float* bias, int flags, int* status,
+                     int n_sm, cudaStream_t st, const PtbStaging* stage_a, const PtbStaging* stage_b, SplitK sk) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     {
         int dev = 0;
@@ -148,6 +150,12 @@ PTB_API int ptb_gemm_bf16_ex(void* const* a_ptrs, int a_shards, int a_shard_rows
         if (0.85 * eff(128) > eff(256)) BN = 128;
     }
     if (!b_mn && b_shards > 1 && b_shard_rows % 256) BN = 128;
+    if (sk.splits > 1) BN = 128;
+    const int kblocks = (K + BK - 1) / BK;
+    p.splits = std::max(1, sk.splits);
+    p.kb_per_split = (kblocks + p.splits - 1) / p.splits;
+    p.splits = (kblocks + p.kb_per_split - 1) / p.kb_per_split;          // no empty split
+    p.split_stride = sk.stride;
     fill_staging(p.stA, stage_a);
     fill_staging(p.stB, stage_b);
     // stager CTAs are needed unless every staged operand is filled by an external copier
@@ -164,6 +172,68 @@ PTB_API int ptb_gemm_bf16_ex(void* const* a_ptrs, int a_shards, int a_shard_rows
     p.tiles_n = (N + BN - 1) / BN;
     if (BN == 256) return launch_majors<256, 4>(a_mn, b_mn, oa, ob, p, n_sm, st);
     return launch_majors<128, 6>(a_mn, b_mn, oa, ob, p, n_sm, st);
+}
+
+PTB_API int ptb_gemm_bf16_ex(void* const* a_ptrs, int a_shards, int a_shard_rows, long long lda, int a_mn, void* const* b_ptrs,
+                             int b_shards, int b_shard_rows, long long ldb, int b_mn, void* C, long long ldc, void* const* c_peers,
+                             int c_shards, int out_shard_rows, int M, int N, int K, const float* bias, int flags, int* status,
+                             int n_sm, cudaStream_t st, const PtbStaging* stage_a, const PtbStaging* stage_b) {
+    return gemm_core(a_ptrs, a_shards, a_shard_rows, lda, a_mn, b_ptrs, b_shards, b_shard_rows, ldb, b_mn, C, ldc, c_peers, c_shards,
+                     out_shard_rows, M, N, K, bias, flags, status, n_sm, st, stage_a, stage_b, SplitK{1, 0});
+}
+
+// Sum the split-K partials, add the bias, apply GELU, round to bf16.  work: [splits][M][N] fp32; N a multiple of 4.
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ work, int splits, long long mn, int N,
+                                                            const float* __restrict__ bias, int gelu, __nv_bfloat16* __restrict__ C,
+                                                            long long ldc) {
+    const long long i4 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i4 >= mn) return;
+    float4 acc = *reinterpret_cast<const float4*>(work + i4);
+    for (int s = 1; s < splits; ++s) {
+        const float4 v = *reinterpret_cast<const float4*>(work + (size_t)s * mn + i4);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    const long long row = i4 / N;
+    const int col = (int)(i4 - row * N);
+    if (bias) { acc.x += bias[col]; acc.y += bias[col + 1]; acc.z += bias[col + 2]; acc.w += bias[col + 3]; }
+    if (gelu) { acc.x = gelu_tanh(acc.x); acc.y = gelu_tanh(acc.y); acc.z = gelu_tanh(acc.z); acc.w = gelu_tanh(acc.w); }
+    __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(C + row * ldc + col);
+    o[0] = __floats2bfloat162_rn(acc.x, acc.y);
+    o[1] = __floats2bfloat162_rn(acc.z, acc.w);
+}
+
+// How many K-splits a skinny GEMM (one row tile) should use so that its work items fill the machine: the makespan of
+// `waves` rounds of (k-blocks per item x per-block time + fixed cost) is minimised over 1..16 splits.
+PTB_API int ptb_gemm_pick_splits(int M, int N, int K, int n_sm) {
+    if (M > BM || n_sm <= 0) return 1;
+    const int tiles = (N + 127) / 128, kblocks = (K + BK - 1) / BK;
+    int best = 1;
+    double best_cost = 1e30;
+    for (int s = 1; s <= 16 && s <= kblocks; ++s) {
+        const int kbps = (kblocks + s - 1) / s, items = tiles * ((kblocks + kbps - 1) / kbps);
+        const int waves = (items + n_sm - 1) / n_sm;
+        const double cost = waves * (kbps * 0.25 + 2.0) + (s > 1 ? 2.5 : 0.0);      // microseconds, roughly; the reduce pass costs a launch
+        if (cost < best_cost - 1e-9) { best_cost = cost; best = s; }
+    }
+    return best;
+}
+
+// Skinny GEMM (M <= 128), K-major operands: C[M,N] bf16 = A[M,K] B[N,K]^T (+ bias, GELU) with `splits` K-splits whose
+// fp32 partials go through `work` ([splits][M][N] floats) and one reduce launch.  N must be a multiple of 4.
+PTB_API int ptb_gemm_bf16_splitk(const void* A, long long lda, const void* B, long long ldb, void* C, long long ldc, int M, int N, int K,
+                                 const float* bias, int gelu, int splits, float* work, int* status, int n_sm, cudaStream_t st) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    if (M > BM || (N & 3) || splits < 2 || !work) { ptb_set_error("gemm split-K: needs M <= %d, N %% 4 == 0, splits >= 2 and a workspace", BM); return -1; }
+    void* ap[1] = {const_cast<void*>(A)};
+    void* bp[1] = {const_cast<void*>(B)};
+    const long long mn = (long long)M * N;
+    if (gemm_core(ap, 1, 0, lda, 0, bp, 1, 0, ldb, 0, work, N, nullptr, 0, 0, M, N, K, nullptr, EPI_OUT_F32, status, n_sm, st, nullptr, nullptr,
+                  SplitK{splits, mn}))
+        return -1;
+    const int kblocks = (K + BK - 1) / BK, kbps = (kblocks + splits - 1) / splits, real = (kblocks + kbps - 1) / kbps;
+    splitk_reduce_kernel<<<(unsigned)((mn / 4 + 255) / 256), 256, 0, st>>>(work, real, mn, N, bias, gelu, (__nv_bfloat16*)C, ldc);
+    PTB_CUDA_OK(cudaGetLastError());
+    return 0;
 }
 
 // C[M,N] (+)= op(A) op(B)^T with bf16 operands and fp32 accumulation, all operands local.

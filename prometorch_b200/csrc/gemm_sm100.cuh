@@ -70,6 +70,10 @@ struct Params {
     int out_shard_rows;
     int scatter_rank;
     int stager_ctas;        // CTAs [0, stager_ctas) are stagers (lowest indices: dispatched first); the rest compute tiles
+    // split-K (skinny M: too few output tiles to fill the machine): work item = (tile, split); split s runs k-blocks
+    // [s*kb_per_split, (s+1)*kb_per_split) and stores its fp32 partial at C + s*split_stride; the caller sums them
+    int splits, kb_per_split;
+    long long split_stride;
     Staging stA, stB;
 };
 
@@ -244,7 +248,8 @@ gemm_bf16_kernel(const __grid_constant__ Operand opA, const __grid_constant__ Op
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int num_tiles = P.tiles_m * P.tiles_n;
+    const int tiles_mn = P.tiles_m * P.tiles_n;
+    const int num_tiles = tiles_mn * P.splits;
     const int kblocks = (P.K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
@@ -283,8 +288,10 @@ gemm_bf16_kernel(const __grid_constant__ Operand opA, const __grid_constant__ Op
             // seen all of its blocks staged, later tiles need not look at the flags again
             bool first_tile = true;
             for (int t = cta; t < num_tiles && ok; t += n_gemm, first_tile = false) {
-                const int m0 = (t % P.tiles_m) * BM, n0 = (t / P.tiles_m) * BN;
-                for (int kb = 0; kb < kblocks && ok; ++kb, ++it) {
+                const int tt = t % tiles_mn, sp = t / tiles_mn;
+                const int m0 = (tt % P.tiles_m) * BM, n0 = (tt / P.tiles_m) * BN;
+                const int kb_lo = sp * P.kb_per_split, kb_hi = min(kblocks, kb_lo + P.kb_per_split);
+                for (int kb = kb_lo; kb < kb_hi && ok; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (it >= STAGES) ok = mbar_wait(&empty[s], (uint32_t)(((it / STAGES) - 1) & 1), P.status);
                     if (!ok) break;
@@ -292,8 +299,8 @@ gemm_bf16_kernel(const __grid_constant__ Operand opA, const __grid_constant__ Op
                     uint8_t* sb = sa + S::A_BYTES;
                     mbar_expect_tx(&full[s], S::STAGE_BYTES);
                     // rows being staged from peers must have landed before the TMA engine reads them
-                    if (A_MN ? first_tile : kb == 0) ok = wait_staged(P.stA, A_MN ? kb * BK : m0, A_MN ? BK : BM, P.status);
-                    if (ok && (B_MN ? first_tile : kb == 0)) ok = wait_staged(P.stB, B_MN ? kb * BK : n0, B_MN ? BK : BN, P.status);
+                    if (A_MN ? first_tile : kb == kb_lo) ok = wait_staged(P.stA, A_MN ? kb * BK : m0, A_MN ? BK : BM, P.status);
+                    if (ok && (B_MN ? first_tile : kb == kb_lo)) ok = wait_staged(P.stB, B_MN ? kb * BK : n0, B_MN ? BK : BN, P.status);
                     if (!ok) break;
                     // the box's row coordinate selects the shard (and so the GPU) it is fetched from
                     if (A_MN) {
@@ -326,7 +333,8 @@ gemm_bf16_kernel(const __grid_constant__ Operand opA, const __grid_constant__ Op
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(b * BN);
-                for (int kb = 0; kb < kblocks && ok; ++kb, ++it) {
+                const int kb_lo = (t / tiles_mn) * P.kb_per_split, kb_hi = min(kblocks, kb_lo + P.kb_per_split);
+                for (int kb = kb_lo; kb < kb_hi && ok; ++kb, ++it) {
                     const int s = it % STAGES;
                     ok = mbar_wait(&full[s], (uint32_t)((it / STAGES) & 1), P.status);
                     if (!ok) break;
@@ -337,7 +345,7 @@ gemm_bf16_kernel(const __grid_constant__ Operand opA, const __grid_constant__ Op
                         // K-major: 16 bf16 = 32 B further along the swizzled row; MN-major: 16 k-rows = 2048 B further
                         const uint64_t da = A_MN ? smem_desc(sa + k * 2048, 8192, 1024) : smem_desc(sa + k * 32, 16, 1024);
                         const uint64_t db = B_MN ? smem_desc(sb + k * 2048, 8192, 1024) : smem_desc(sb + k * 32, 16, 1024);
-                        umma_bf16(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        umma_bf16(d_tmem, da, db, idesc, (kb > kb_lo || k > 0) ? 1u : 0u);
                     }
                     umma_commit(&empty[s]);          // frees the stage once these MMAs have read it
                 }
@@ -352,7 +360,8 @@ gemm_bf16_kernel(const __grid_constant__ Operand opA, const __grid_constant__ Op
         bool ok = true;
         for (int t = cta; t < num_tiles && ok; t += n_gemm, ++tl) {
             const int b = tl & 1;
-            const int m0 = (t % P.tiles_m) * BM, n0 = (t / P.tiles_m) * BN;
+            const int tt = t % tiles_mn, sp = t / tiles_mn;
+            const int m0 = (tt % P.tiles_m) * BM, n0 = (tt / P.tiles_m) * BN;
             ok = mbar_wait(&acc_full[b], (uint32_t)((tl >> 1) & 1), P.status);
             if (!ok) break;
             tc_fence_after();
@@ -397,7 +406,7 @@ gemm_bf16_kernel(const __grid_constant__ Operand opA, const __grid_constant__ Op
                             for (int j = 0; j < 32 && col + j < P.N; ++j) cp[j] = __float2bfloat16_rn(v[j]);
                         }
                     } else if (P.flags & EPI_OUT_F32) {
-                        float* cp = reinterpret_cast<float*>(P.C) + (size_t)row * P.ldc + col;
+                        float* cp = reinterpret_cast<float*>(P.C) + (size_t)sp * P.split_stride + (size_t)row * P.ldc + col;
                         if (col + 32 <= P.N) {
 #pragma unroll
                             for (int j = 0; j < 32; j += 4) {

@@ -8,6 +8,7 @@ M/N-major.  The reference's linear layers go through fp32 cublasSgemm
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Optional
 
 import torch
@@ -22,6 +23,11 @@ def _decls(L):
     vp, ci, ll = C.c_void_p, C.c_int, C.c_longlong
     L.ptb_gemm_bf16.argtypes = [vp, ll, ci, vp, ll, ci, vp, ll, ci, ci, ci, vp, ci, vp, ci, vp]
     L.ptb_gemm_bf16.restype = ci
+    if hasattr(L, "ptb_gemm_bf16_splitk"):
+        L.ptb_gemm_pick_splits.argtypes = [ci, ci, ci, ci]
+        L.ptb_gemm_pick_splits.restype = ci
+        L.ptb_gemm_bf16_splitk.argtypes = [vp, ll, vp, ll, vp, ll, ci, ci, ci, vp, ci, ci, vp, vp, ci, vp]
+        L.ptb_gemm_bf16_splitk.restype = ci
 
 
 _STATUS = {}
@@ -40,6 +46,17 @@ def check_status(dev=None):
             if int(s) != 0:
                 s.zero_()
                 raise N.NativeError("tcgen05 GEMM: a pipeline wait timed out (status %d)" % int(s))
+
+
+_SPLITK = os.environ.get("PTB_GEMM_SPLITK", "1") != "0"
+_SM_COUNT = {}
+
+
+def _sms(dev) -> int:
+    k = torch.device(dev).index or 0
+    if k not in _SM_COUNT:
+        _SM_COUNT[k] = torch.cuda.get_device_properties(k).multi_processor_count
+    return _SM_COUNT[k]
 
 
 def _rowmajor(t):
@@ -62,6 +79,16 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: boo
         if accumulate:
             raise ValueError("accumulate needs an output tensor")
         out = torch.empty(M, Nn, dtype=out_dtype, device=a.device)
+    if M <= 128 and not (a_mn or b_mn or accumulate) and out.dtype == torch.bfloat16 and Nn % 4 == 0 and _SPLITK:
+        # skinny M (decode batches): one row of tiles cannot fill the machine, so K is split over the idle SMs
+        splits = N.lib().ptb_gemm_pick_splits(M, Nn, K, _sms(a.device))
+        if splits > 1:
+            work = torch.empty(splits * M * Nn, dtype=torch.float32, device=a.device)
+            st = torch.cuda.current_stream(a.device).cuda_stream
+            N.check(N.lib().ptb_gemm_bf16_splitk(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), out.data_ptr(), out.stride(0), M, Nn,
+                                                 K, N.ptr(bias.float().contiguous() if bias is not None else None), int(gelu), splits,
+                                                 work.data_ptr(), _status(a.device).data_ptr(), 0, st), "gemm_bf16_splitk")
+            return out
     flags = (EPI_BIAS if bias is not None else 0) | (EPI_ACCUM if accumulate else 0) | \
         (EPI_OUT_F32 if out.dtype == torch.float32 else 0) | (EPI_GELU if gelu else 0)
     if bias is not None:

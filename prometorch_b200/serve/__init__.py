@@ -8,6 +8,9 @@ import collections
 from dataclasses import dataclass, field
 from typing import Deque, Dict, List, Optional
 
+from . import llm
+from .llm import GenerationConfig, LlamaConfig, LlamaWeights, PagedKVCache, load_safetensors, save_safetensors
+from .llm import LLMEngine as PagedLLMEngine
 from .server import ApiHandlers, GGUFBackend, HttpServer, ModelBackend, PromeServe, ServerConfig, StreamWriter, VERSION
 
 

@@ -1,0 +1,597 @@
+"""Continuous-batching engine for Hugging Face Llama checkpoints with a paged KV cache.
+
+Same public surface as the reference's ``LLMEngine`` (torch/serve/llm.h:33-57 for the request types, :299-334 for the
+64-token page pool, :352-437 for ``load / set_weights / generate / submit_request / step / poll_responses``).  The
+reference walks its active requests one after another on the CPU; here one ``step()`` is
+
+* a prompt pass for each newly admitted request (tcgen05 GEMMs, FlashAttention over the prompt, rotary + page write
+  in ``paged_rope_write_kernel``), and
+* ONE batched decode pass for all other active requests: a ``[B, hidden]`` activation runs through the layer GEMMs,
+  ``paged_attn_decode_kernel`` reads each request's pages through the page table, and the sampler picks the next ids
+  on the device.
+
+Pages come from one pool shared by all requests and go back to it when a request finishes.  CPU tensors take the
+plain torch path of every op, which is how the scheduling logic is tested without a GPU.
+"""
+from __future__ import annotations
+
+import collections
+import json
+import math
+import os
+import struct
+import time
+from dataclasses import dataclass, field
+from typing import Deque, Dict, List, Optional, Sequence, Union
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+from ..ops import paged as P
+
+PAGE = P.PAGE
+
+
+@dataclass
+class GenerationConfig:
+    max_new_tokens: int = 128
+    temperature: float = 0.8
+    top_p: float = 0.9
+    top_k: int = 50
+    repetition_penalty: float = 1.1
+    stop_tokens: List[int] = field(default_factory=list)
+
+
+@dataclass
+class Request:
+    request_id: int = 0
+    prompt: Union[str, Sequence[int]] = ""
+    config: GenerationConfig = field(default_factory=GenerationConfig)
+
+
+@dataclass
+class Response:
+    request_id: int = 0
+    output: str = ""
+    token_ids: List[int] = field(default_factory=list)
+    tokens_generated: int = 0
+    throughput_tok_per_s: float = 0.0
+
+
+@dataclass
+class LlamaConfig:
+    vocab_size: int = 32000
+    hidden_size: int = 4096
+    intermediate_size: int = 11008
+    num_hidden_layers: int = 32
+    num_attention_heads: int = 32
+    num_key_value_heads: int = 32
+    max_position_embeddings: int = 4096
+    rms_norm_eps: float = 1e-5
+    rope_theta: float = 10000.0
+    bos_token_id: int = 1
+    eos_token_id: int = 2
+    tie_word_embeddings: bool = False
+
+    @property
+    def head_dim(self) -> int:
+        return self.hidden_size // self.num_attention_heads
+
+    @classmethod
+    def from_json(cls, path: str) -> "LlamaConfig":
+        with open(path) as f:
+            d = json.load(f)
+        c = cls()
+        for k in cls.__dataclass_fields__:
+            if k in d and d[k] is not None:
+                v = d[k]
+                if k == "eos_token_id" and isinstance(v, list):
+                    v = v[0]
+                setattr(c, k, type(getattr(c, k))(v))
+        if "num_key_value_heads" not in d:
+            c.num_key_value_heads = c.num_attention_heads
+        return c
+
+
+# ------------------------------------------------------------------------------------------ safetensors
+_ST_DTYPES = {"F32": (torch.float32, np.float32), "F16": (torch.float16, np.float16), "BF16": (torch.bfloat16, np.uint16),
+              "I32": (torch.int32, np.int32), "I64": (torch.int64, np.int64), "U8": (torch.uint8, np.uint8)}
+
+
+def load_safetensors(path: str) -> Dict[str, torch.Tensor]:
+    """Read a ``.safetensors`` file: 8-byte little-endian header length, JSON header, raw tensor bytes."""
+    out: Dict[str, torch.Tensor] = {}
+    with open(path, "rb") as f:
+        (n,) = struct.unpack("<Q", f.read(8))
+        header = json.loads(f.read(n))
+        base = 8 + n
+    raw = np.memmap(path, dtype=np.uint8, mode="r", offset=base) if os.path.getsize(path) > base else np.zeros(0, np.uint8)
+    for name, meta in header.items():
+        if name == "__metadata__":
+            continue
+        tdt, ndt = _ST_DTYPES[meta["dtype"]]
+        lo, hi = meta["data_offsets"]
+        arr = np.frombuffer(raw[lo:hi].tobytes(), dtype=ndt).reshape(meta["shape"])
+        t = torch.from_numpy(arr.copy())
+        out[name] = t.view(torch.bfloat16) if tdt == torch.bfloat16 else t
+    return out
+
+
+def save_safetensors(tensors: Dict[str, torch.Tensor], path: str):
+    header, blobs, off = {}, [], 0
+    names = {v: k for k, (v, _) in _ST_DTYPES.items()}
+    for name, t in tensors.items():
+        t = t.detach().cpu().contiguous()
+        b = (t.view(torch.uint16) if t.dtype == torch.bfloat16 else t).numpy().tobytes()
+        header[name] = {"dtype": names[t.dtype], "shape": list(t.shape), "data_offsets": [off, off + len(b)]}
+        blobs.append(b)
+        off += len(b)
+    h = json.dumps(header).encode()
+    h += b" " * (-len(h) % 8)
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(h)))
+        f.write(h)
+        for b in blobs:
+            f.write(b)
+
+
+# ------------------------------------------------------------------------------------------ weights
+class LlamaWeights:
+    """Weights in the layout the engine runs: q/k/v packed into one matrix, gate/up packed into one."""
+
+    def __init__(self, cfg: LlamaConfig):
+        self.cfg = cfg
+        self.tok_emb: Optional[torch.Tensor] = None
+        self.layers: List[Dict[str, torch.Tensor]] = []
+        self.final_norm: Optional[torch.Tensor] = None
+        self.lm_head: Optional[torch.Tensor] = None
+
+    @classmethod
+    def random(cls, cfg: LlamaConfig, seed: int = 0, dtype=torch.float32) -> "LlamaWeights":
+        g = torch.Generator().manual_seed(seed)
+        D, I, H, Hk, Dh = cfg.hidden_size, cfg.intermediate_size, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+
+        def r(*s, scale):
+            return (torch.randn(*s, generator=g) * scale).to(dtype)
+        w = cls(cfg)
+        w.tok_emb = r(cfg.vocab_size, D, scale=1.0)
+        for _ in range(cfg.num_hidden_layers):
+            w.layers.append(dict(attn_norm=(1 + 0.1 * torch.randn(D, generator=g)).to(dtype),
+                                 wqkv=r((H + 2 * Hk) * Dh, D, scale=D ** -0.5), wo=r(D, H * Dh, scale=(H * Dh) ** -0.5),
+                                 ffn_norm=(1 + 0.1 * torch.randn(D, generator=g)).to(dtype),
+                                 w_gate_up=r(2 * I, D, scale=D ** -0.5), w_down=r(D, I, scale=I ** -0.5)))
+        w.final_norm = (1 + 0.1 * torch.randn(D, generator=g)).to(dtype)
+        w.lm_head = r(cfg.vocab_size, D, scale=D ** -0.5)
+        return w
+
+    @classmethod
+    def from_state_dict(cls, cfg: LlamaConfig, sd: Dict[str, torch.Tensor]) -> "LlamaWeights":
+        """Hugging Face names: ``model.layers.N.self_attn.{q,k,v,o}_proj.weight`` and so on."""
+        w = cls(cfg)
+        w.tok_emb = sd["model.embed_tokens.weight"]
+        for l in range(cfg.num_hidden_layers):
+            p = f"model.layers.{l}."
+            w.layers.append(dict(
+                attn_norm=sd[p + "input_layernorm.weight"],
+                wqkv=torch.cat([sd[p + "self_attn.q_proj.weight"], sd[p + "self_attn.k_proj.weight"], sd[p + "self_attn.v_proj.weight"]]),
+                wo=sd[p + "self_attn.o_proj.weight"], ffn_norm=sd[p + "post_attention_layernorm.weight"],
+                w_gate_up=torch.cat([sd[p + "mlp.gate_proj.weight"], sd[p + "mlp.up_proj.weight"]]), w_down=sd[p + "mlp.down_proj.weight"]))
+        w.final_norm = sd["model.norm.weight"]
+        w.lm_head = sd.get("lm_head.weight", w.tok_emb)
+        return w
+
+    def state_dict(self) -> Dict[str, torch.Tensor]:
+        c = self.cfg
+        H, Hk, Dh, I = c.num_attention_heads, c.num_key_value_heads, c.head_dim, c.intermediate_size
+        sd = {"model.embed_tokens.weight": self.tok_emb, "model.norm.weight": self.final_norm, "lm_head.weight": self.lm_head}
+        for l, L in enumerate(self.layers):
+            p = f"model.layers.{l}."
+            q, k, v = L["wqkv"].split([H * Dh, Hk * Dh, Hk * Dh])
+            g, u = L["w_gate_up"].split([I, I])
+            sd.update({p + "input_layernorm.weight": L["attn_norm"], p + "self_attn.q_proj.weight": q, p + "self_attn.k_proj.weight": k,
+                       p + "self_attn.v_proj.weight": v, p + "self_attn.o_proj.weight": L["wo"],
+                       p + "post_attention_layernorm.weight": L["ffn_norm"], p + "mlp.gate_proj.weight": g,
+                       p + "mlp.up_proj.weight": u, p + "mlp.down_proj.weight": L["w_down"]})
+        return sd
+
+    def to(self, device, dtype) -> "LlamaWeights":
+        w = LlamaWeights(self.cfg)
+        mv = lambda t: t.to(device=device, dtype=dtype).contiguous()
+        w.tok_emb, w.final_norm, w.lm_head = mv(self.tok_emb), mv(self.final_norm), mv(self.lm_head)
+        w.layers = [{k: mv(v) for k, v in L.items()} for L in self.layers]
+        return w
+
+
+class ByteTokenizer:
+    """Fallback when a checkpoint directory has no tokenizer files: one id per UTF-8 byte (offset 3)."""
+    bos_id, eos_id = 1, 2
+
+    def encode(self, text: str, add_bos: bool = True) -> List[int]:
+        return ([self.bos_id] if add_bos else []) + [b + 3 for b in text.encode("utf-8")]
+
+    def decode(self, ids) -> str:
+        return bytes(i - 3 for i in ids if 3 <= i < 259).decode("utf-8", errors="replace")
+
+
+def load_hf_tokenizer(model_dir: str):
+    """``vocab.json`` + ``merges.txt``, or the ``model`` section of ``tokenizer.json`` (byte-level BPE,
+    torch/serve/llm.h:94-297)."""
+    from ..io.tokenizer import GGUFTokenizer
+    vocab, merges = None, None
+    vj, mt, tj = (os.path.join(model_dir, n) for n in ("vocab.json", "merges.txt", "tokenizer.json"))
+    if os.path.exists(vj) and os.path.exists(mt):
+        with open(vj, encoding="utf-8") as f:
+            vocab = json.load(f)
+        with open(mt, encoding="utf-8") as f:
+            merges = [ln.rstrip("\n") for ln in f if ln.strip() and not ln.startswith("#version")]
+    elif os.path.exists(tj):
+        with open(tj, encoding="utf-8") as f:
+            m = json.load(f).get("model", {})
+        vocab = m.get("vocab")
+        merges = [x if isinstance(x, str) else " ".join(x) for x in m.get("merges", [])]
+    if not vocab:
+        return None
+    tokens = [""] * (max(vocab.values()) + 1)
+    for t, i in vocab.items():
+        tokens[i] = t
+    return GGUFTokenizer(tokens, "gpt2", merges=merges)
+
+
+# ------------------------------------------------------------------------------------------ KV pool
+class PagedKVCache:
+    """One pool of 64-token pages shared by all requests; a page id addresses the same slot in every layer."""
+
+    def __init__(self, num_layers: int, num_kv_heads: int, head_dim: int, max_pages: int, device, dtype, spare: bool = False):
+        n = max_pages + (1 if spare else 0)                # the spare page (id max_pages) is never handed out
+        self.k = [torch.zeros(n, num_kv_heads, PAGE, head_dim, device=device, dtype=dtype) for _ in range(num_layers)]
+        self.v = [torch.zeros(n, num_kv_heads, PAGE, head_dim, device=device, dtype=dtype) for _ in range(num_layers)]
+        self.max_pages = max_pages
+        self.spare_page = max_pages if spare else -1
+        self.free_pages: Deque[int] = collections.deque(range(max_pages))
+
+    def alloc_page(self) -> int:
+        return self.free_pages.popleft() if self.free_pages else -1
+
+    def free_page(self, p: int):
+        self.free_pages.append(p)
+
+    @property
+    def pages_in_use(self) -> int:
+        return self.max_pages - len(self.free_pages)
+
+
+@dataclass
+class RequestState:
+    request_id: int
+    config: GenerationConfig
+    input_ids: List[int]
+    prompt_len: int
+    t_start: float
+    prompt_ids: List[int] = field(default_factory=list)
+    row: int = -1                        # row of the page table while active
+    pages: List[int] = field(default_factory=list)
+    kv_position: int = 0
+    output_ids: List[int] = field(default_factory=list)
+    prefill_done: bool = False
+    done: bool = False
+    sampler: object = None
+
+
+class LLMEngine:
+    """``submit_request`` queues a prompt, ``step`` advances every active request by one token (the prompt pass for
+    new ones), ``poll_responses`` hands back what finished."""
+
+    def __init__(self, device=None, max_pages: int = 1024, max_active: int = 8, dtype=None, seed: int = 0, use_graphs: bool = True):
+        self.device = torch.device(device if device is not None else ("cuda" if torch.cuda.is_available() else "cpu"))
+        self.dtype = dtype if dtype is not None else (torch.bfloat16 if self.device.type == "cuda" else torch.float32)
+        self.max_pages, self.max_active = max_pages, max_active
+        self.cfg: Optional[LlamaConfig] = None
+        self.weights: Optional[LlamaWeights] = None
+        self.tokenizer = ByteTokenizer()
+        self.kv: Optional[PagedKVCache] = None
+        self.pending: Deque[RequestState] = collections.deque()
+        self.active: List[RequestState] = []
+        self.done: List[Response] = []
+        self.loaded = False
+        self._next_id = 0
+        self._gen = torch.Generator().manual_seed(seed)
+        self.steps = 0
+        self.launch_log: List[int] = []          # batch size of every decode pass (tests and metrics read it)
+        self.use_graphs = use_graphs
+        self._graphs: Dict[tuple, tuple] = {}
+
+    # -------------------------------------------------------------------------------------- loading
+    def load(self, model_dir: str) -> bool:
+        """A Hugging Face directory: ``config.json``, ``model.safetensors`` (or the shards its index lists), tokenizer."""
+        cj = os.path.join(model_dir, "config.json")
+        if not os.path.exists(cj):
+            return False
+        cfg = LlamaConfig.from_json(cj)
+        sd: Dict[str, torch.Tensor] = {}
+        single, index = os.path.join(model_dir, "model.safetensors"), os.path.join(model_dir, "model.safetensors.index.json")
+        if os.path.exists(single):
+            sd = load_safetensors(single)
+        elif os.path.exists(index):
+            with open(index) as f:
+                shards = sorted(set(json.load(f)["weight_map"].values()))
+            for s in shards:
+                sd.update(load_safetensors(os.path.join(model_dir, s)))
+        tok = load_hf_tokenizer(model_dir)
+        if tok is not None:
+            self.tokenizer = tok
+        if not sd:
+            self.cfg = cfg
+            return True                           # weights may still arrive through set_weights()
+        self.set_weights(LlamaWeights.from_state_dict(cfg, sd))
+        return True
+
+    def set_weights(self, w: LlamaWeights):
+        self.cfg = w.cfg
+        self.weights = w.to(self.device, self.dtype)
+        c = self.cfg
+        self.cos, self.sin = P.rope_tables(c.max_position_embeddings, c.head_dim, c.rope_theta, self.device)
+        self.kv = PagedKVCache(c.num_hidden_layers, c.num_key_value_heads, c.head_dim, self.max_pages, self.device, self.dtype, spare=True)
+        self.pt_stride = (c.max_position_embeddings + PAGE - 1) // PAGE
+        # one row per active request plus a spare one whose single page absorbs the writes of padding rows
+        self.page_table = torch.zeros(self.max_active + 1, self.pt_stride, dtype=torch.int32, device=self.device)
+        self.page_table[self.max_active].fill_(self.kv.spare_page)
+        self.free_rows = list(range(self.max_active))
+        self._graphs = {}
+        self.loaded = True
+
+    # -------------------------------------------------------------------------------------- public API
+    def generate(self, prompt, config: Optional[GenerationConfig] = None) -> Response:
+        rid = self._next_id
+        self.submit_request(Request(rid, prompt, config or GenerationConfig()))
+        mine = None
+        while mine is None:
+            self.step()
+            keep = []
+            for r in self.done:
+                if r.request_id == rid:
+                    mine = r
+                else:
+                    keep.append(r)
+            self.done = keep
+            if mine is None and self.num_active() == 0:
+                return Response(request_id=rid)
+        return mine
+
+    def submit_request(self, req: Request):
+        ids = self._encode(req.prompt)
+        self._next_id = max(self._next_id, req.request_id + 1)
+        limit = self.cfg.max_position_embeddings - 1
+        ids = ids[-limit:] if len(ids) > limit else ids
+        self.pending.append(RequestState(req.request_id, req.config, list(ids), len(ids), time.perf_counter(), prompt_ids=list(ids)))
+        self._admit_pending()
+
+    def poll_responses(self) -> List[Response]:
+        out, self.done = self.done, []
+        return out
+
+    def num_active(self) -> int:
+        return len(self.active) + len(self.pending)
+
+    @torch.no_grad()
+    def step(self):
+        self._admit_pending()
+        if not self.active:
+            return
+        self.steps += 1
+        fresh = [s for s in self.active if not s.prefill_done]
+        running = [s for s in self.active if s.prefill_done and not s.done]
+        for s in fresh:                                        # the prompt pass, one request at a time
+            if not self._ensure_pages(s, s.prompt_len - 1):
+                if len(self.active) > 1:                       # wait for a running request to give its pages back
+                    self.active.remove(s)
+                    self.free_rows.append(s.row)
+                    self.pending.appendleft(s)
+                    self._held = True
+                else:
+                    self._finish(s)                            # the pool cannot hold this prompt at all
+                continue
+            logits = self._forward_prompt(s)
+            s.kv_position = s.prompt_len
+            s.prefill_done = True
+            self._emit(s, self._sample([s], logits)[0])
+        running = [s for s in running if self._ensure_pages(s, s.kv_position) or self._finish(s)]
+        if running:                                            # one batched decode pass for everyone else
+            logits = self._forward_decode(running)
+            for s, t in zip(running, self._sample(running, logits)):
+                s.kv_position += 1
+                self._emit(s, t)
+        self._collect_done()
+        if self.device.type == "cuda":
+            P.check_status(self.device)
+
+    # -------------------------------------------------------------------------------------- scheduling
+    def _encode(self, prompt) -> List[int]:
+        if isinstance(prompt, str):
+            try:
+                ids = self.tokenizer.encode(prompt, add_bos=True)
+            except TypeError:
+                ids = self.tokenizer.encode(prompt)
+            if not ids or (self.cfg and ids[0] != self.cfg.bos_token_id and getattr(self.tokenizer, "bos_id", -1) < 0):
+                ids = [self.cfg.bos_token_id] + list(ids)
+            return [min(int(i), self.cfg.vocab_size - 1) for i in ids]
+        return [int(i) for i in prompt]
+
+    def _admit_pending(self):
+        if getattr(self, "_held", False) and self.active:      # a prompt is waiting for pages: admit nothing new
+            return
+        self._held = False
+        while self.pending and self.loaded and self.free_rows and len(self.active) < self.max_active:
+            s = self.pending.popleft()
+            s.row = self.free_rows.pop()
+            self.active.append(s)
+
+    def _ensure_pages(self, s: RequestState, pos: int) -> bool:
+        """Make sure the pages up to the one that holds ``pos`` exist; False when the pool is empty."""
+        need = pos // PAGE + 1
+        fresh = []
+        while len(s.pages) + len(fresh) < need:
+            p = self.kv.alloc_page()
+            if p < 0:
+                for q in fresh:
+                    self.kv.free_page(q)
+                return False
+            fresh.append(p)
+        if fresh:
+            lo = len(s.pages)
+            s.pages.extend(fresh)
+            self.page_table[s.row, lo:lo + len(fresh)] = torch.tensor(fresh, dtype=torch.int32, device=self.device)
+        return True
+
+    def _emit(self, s: RequestState, tok: int):
+        s.output_ids.append(tok)
+        s.input_ids = [tok]
+        c = s.config
+        if tok == self.cfg.eos_token_id or tok in c.stop_tokens or len(s.output_ids) >= c.max_new_tokens or \
+                s.kv_position + 1 >= self.cfg.max_position_embeddings:
+            s.done = True
+
+    def _finish(self, s: RequestState) -> bool:
+        s.done = True
+        return False
+
+    def _collect_done(self):
+        keep = []
+        for s in self.active:
+            if not s.done:
+                keep.append(s)
+                continue
+            for p in s.pages:
+                self.kv.free_page(p)
+            s.pages = []
+            self.free_rows.append(s.row)
+            dt = max(time.perf_counter() - s.t_start, 1e-9)
+            text = self.tokenizer.decode(s.output_ids)
+            self.done.append(Response(s.request_id, text, list(s.output_ids), len(s.output_ids), len(s.output_ids) / dt))
+        self.active = keep
+
+    # -------------------------------------------------------------------------------------- model
+    def _linear(self, x, w):
+        if x.is_cuda:
+            from ..ops.gemm import linear
+            return linear(x, w)
+        return F.linear(x, w)
+
+    def _norm(self, x, w):
+        from ..ops.fused_ops import rms_norm
+        return rms_norm(x, w, self.cfg.rms_norm_eps)
+
+    def _mlp(self, x, L):
+        from ..ops.fused_ops import swiglu
+        return self._linear(swiglu(self._linear(x, L["w_gate_up"])), L["w_down"])
+
+    def _forward_prompt(self, s: RequestState) -> torch.Tensor:
+        """All prompt tokens of one request; fills its pages; returns the logits of the last position ``[1, V]``."""
+        from ..ops.attention import flash_attention
+        c, w = self.cfg, self.weights
+        H, Hk, Dh = c.num_attention_heads, c.num_key_value_heads, c.head_dim
+        T = s.prompt_len
+        dev = self.device
+        ids = torch.tensor(s.input_ids, dtype=torch.long, device=dev)
+        pos = torch.arange(T, dtype=torch.int32, device=dev)
+        req = torch.full((T,), s.row, dtype=torch.int32, device=dev)
+        x = w.tok_emb[ids]
+        for l, L in enumerate(w.layers):
+            qkv = self._linear(self._norm(x, L["attn_norm"]), L["wqkv"]).contiguous()
+            k = P.paged_rope_write(qkv, H, Hk, Dh, pos, req, self.page_table, self.cos, self.sin, self.kv.k[l], self.kv.v[l], want_k=True)
+            q = qkv[:, :H * Dh].reshape(1, T, H, Dh)
+            v = qkv[:, (H + Hk) * Dh:].reshape(1, T, Hk, Dh)
+            a = flash_attention(q, k.view(1, T, Hk, Dh), v, causal=True).reshape(T, H * Dh)
+            x = x + self._linear(a, L["wo"])
+            x = x + self._mlp(self._norm(x, L["ffn_norm"]), L)
+        last = self._norm(x[-1:], w.final_norm)
+        return self._linear(last, w.lm_head).float()
+
+    def _decode_layers(self, meta: torch.Tensor, nsplit: int) -> torch.Tensor:
+        """The device work of a decode pass.  ``meta [B, 4]`` int32: token id, position, page-table row, cached length."""
+        from ..ops.fused_ops import add_rms_norm
+        c, w = self.cfg, self.weights
+        H, Hk, Dh = c.num_attention_heads, c.num_key_value_heads, c.head_dim
+        B = meta.shape[0]
+        ids, pos, rows, lens = meta[:, 0].long(), meta[:, 1].contiguous(), meta[:, 2].long(), meta[:, 3].contiguous()
+        table = self.page_table[rows]                          # [B, pt_stride] rows in batch order
+        req = torch.arange(B, dtype=torch.int32, device=meta.device)
+        x = w.tok_emb[ids]
+        h = self._norm(x, w.layers[0]["attn_norm"])
+        for l, L in enumerate(w.layers):
+            qkv = self._linear(h, L["wqkv"])
+            P.paged_rope_write(qkv, H, Hk, Dh, pos, req, table, self.cos, self.sin, self.kv.k[l], self.kv.v[l])
+            a = P.paged_attention_decode(qkv, H, Hk, Dh, lens, table, self.kv.k[l], self.kv.v[l], nsplit=nsplit)
+            h, x = add_rms_norm(self._linear(a, L["wo"]), x, L["ffn_norm"], c.rms_norm_eps)
+            nxt = w.layers[l + 1]["attn_norm"] if l + 1 < len(w.layers) else w.final_norm
+            h, x = add_rms_norm(self._mlp(h, L), x, nxt, c.rms_norm_eps)
+        return self._linear(h, w.lm_head).float()
+
+    def _forward_decode(self, batch: List[RequestState]) -> torch.Tensor:
+        """One new token for every request of the batch; returns logits ``[B, V]``.  On a GPU the pass is a CUDA graph
+        per (batch bucket, split count): the batch is padded to the bucket with rows that write to a spare page."""
+        dev = self.device
+        B = len(batch)
+        self.launch_log.append(B)
+        rows = [[s.input_ids[-1], s.kv_position, s.row, s.kv_position + 1] for s in batch]
+        max_len = max(r[3] for r in rows)
+        Hk = self.cfg.num_key_value_heads
+        if dev.type != "cuda" or not self.use_graphs:
+            meta = torch.tensor(rows, dtype=torch.int32)
+            meta = (meta.pin_memory() if dev.type == "cuda" else meta).to(dev, non_blocking=True)
+            return self._decode_layers(meta, P.pick_splits(B, Hk, max_len))
+        Bb = 1
+        while Bb < B:
+            Bb *= 2
+        nsplit = P.pick_splits(Bb, Hk, max_len)
+        rows += [[0, 0, self.max_active, 1]] * (Bb - B)        # padding: the spare row of the page table
+        key = (Bb, nsplit)
+        if key not in self._graphs:
+            self._graphs[key] = self._capture(Bb, nsplit, rows)
+        graph, meta_dev, meta_host, logits = self._graphs[key]
+        meta_host.copy_(torch.tensor(rows, dtype=torch.int32))
+        meta_dev.copy_(meta_host, non_blocking=True)
+        graph.replay()
+        return logits[:B]
+
+    def _capture(self, Bb: int, nsplit: int, rows):
+        dev = self.device
+        meta_host = torch.tensor(rows, dtype=torch.int32).pin_memory()
+        meta_dev = meta_host.to(dev)
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):                          # warm-up outside the capture (allocations, status words)
+            self._decode_layers(meta_dev, nsplit)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            logits = self._decode_layers(meta_dev, nsplit)
+        return graph, meta_dev, meta_host, logits
+
+    # -------------------------------------------------------------------------------------- sampling
+    def _sample(self, batch: List[RequestState], logits: torch.Tensor) -> List[int]:
+        """Greedy requests share one arg-max; the others go through the device sampler (top-k <= 64) or tensor ops."""
+        from ..ops.sampling import MAX_DEVICE_TOP_K, DeviceSampler, sample_logits
+        out: List[Optional[int]] = [None] * len(batch)
+        greedy = [i for i, s in enumerate(batch) if s.config.temperature <= 0.0 and s.config.repetition_penalty == 1.0]
+        if greedy:
+            am = logits[greedy].argmax(-1).tolist()
+            for i, t in zip(greedy, am):
+                out[i] = int(t)
+        for i, s in enumerate(batch):
+            if out[i] is not None:
+                continue
+            g = s.config
+            row = logits[i].contiguous()
+            if logits.is_cuda and 1 <= g.top_k <= MAX_DEVICE_TOP_K:
+                if s.sampler is None:
+                    s.sampler = DeviceSampler(self.cfg.vocab_size, self.device, max_history=self.cfg.max_position_embeddings,
+                                              seed=int(torch.randint(0, 2 ** 31 - 1, (1,), generator=self._gen)))
+                    s.sampler.reset(s.prompt_ids + s.output_ids)
+                out[i] = s.sampler.sample(row, g.temperature, g.top_k, g.top_p, g.repetition_penalty)
+            else:
+                hist = s.prompt_ids + s.output_ids
+                out[i] = sample_logits(row, g.temperature, g.top_k, g.top_p, g.repetition_penalty,
+                                       hist if g.repetition_penalty != 1.0 else None, generator=self._gen if not row.is_cuda else None)
+        return [int(t) for t in out]

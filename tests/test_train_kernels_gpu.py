@@ -60,6 +60,28 @@ def test_linear_autograd():
     assert _rel(y, yr) < 5e-3 and _rel(x.grad, xr.grad) < 5e-3 and _rel(w.grad, wr.grad) < 5e-3 and _rel(b.grad, br.grad) < 5e-3
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 2048, 2048), (3, 3072, 2048), (32, 2048, 5632), (64, 11264, 2048), (128, 512, 4096), (8, 32000, 2048)])
+def test_gemm_skinny_split_k(M, N, K):
+    """Decode-sized batches: the K dimension is split over the idle SMs and reduced by a second launch."""
+    from prometorch_b200 import _native as NL
+    from prometorch_b200.ops.gemm import check_status, gemm_bf16
+    g = torch.Generator(device="cuda").manual_seed(M * 3 + N + K)
+    A = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    B = torch.randn(N, K, device="cuda", generator=g).bfloat16()
+    bias = torch.randn(N, device="cuda", generator=g)
+    ref = A.float() @ B.float().t()
+    out = gemm_bf16(A, B)
+    torch.cuda.synchronize()
+    check_status()
+    assert _rel(out, ref) < 5e-3, _rel(out, ref)
+    assert _rel(gemm_bf16(A, B, bias=bias), ref + bias) < 5e-3
+    assert _rel(gemm_bf16(A, B, bias=bias, gelu=True), F.gelu(ref + bias, approximate="tanh")) < 8e-3
+    splits = NL.lib().ptb_gemm_pick_splits(M, N, K, 148)
+    assert 1 <= splits <= 16
+    if N <= 3072:
+        assert splits > 1                       # few tiles: the split path really ran
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("H", [384, 2048, 2560, 4096])
 def test_rmsnorm(dtype, H):
