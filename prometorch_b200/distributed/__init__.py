@@ -13,7 +13,7 @@ from typing import Optional
 
 import torch
 
-from .process_group import (BackendType, CollectiveTimeout, CountingPG, ProcessGroup, ReduceOp, SharedMemoryBackend,
+from .process_group import (BackendType, CollectiveTimeout, CountingPG, FileBackend, ProcessGroup, ReduceOp, SharedMemoryBackend,
                             SingleProcessGroup, TorchProcessGroup, make_shared_memory_groups)
 from .ddp import DDPNoSyncGuard, DistributedDataParallel, PeerChannel
 from .fsdp import (FSDPConfig, FullyShardedDataParallel, OffloadOptimizer, ShardingStrategy, ZeROOptimizer, ZeROStage3,

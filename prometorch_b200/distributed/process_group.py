@@ -19,6 +19,7 @@ from __future__ import annotations
 import datetime
 import os
 import threading
+import time
 from typing import List, Optional, Sequence
 
 import torch
@@ -180,6 +181,90 @@ class SharedMemoryBackend(ProcessGroup):
 def make_shared_memory_groups(world_size: int, timeout: float = 30.0) -> List[SharedMemoryBackend]:
     st = _SharedState(world_size, timeout)
     return [SharedMemoryBackend(st, r) for r in range(world_size)]
+
+
+class FileBackend(ProcessGroup):
+    """Ranks are separate processes that meet through a shared directory, no sockets and no daemon: every rank
+    publishes its contribution as ``{dir}/{tag}_g{gen}_r{rank}.bin`` (written to a temporary name and renamed, so a
+    reader never sees a partial file) followed by an empty ``.ready`` marker, then polls for the others' markers
+    every millisecond and raises :class:`CollectiveTimeout` when they do not show up in time.  This is the reference's
+    third transport (torch/nn/parallel/tensor_parallel.h:85-189, torch/distributed/fsdp.h:101-158); here it serves
+    CPU jobs and tests, the GPU paths use peer memory."""
+
+    def __init__(self, directory: str, rank: int, world_size: int, tag: str = "pg", timeout: float = 30.0, poll: float = 1e-3):
+        self.dir, self.rank, self.world_size, self.tag, self.timeout, self.poll = directory, rank, world_size, tag, timeout, poll
+        self.gen = 0
+        os.makedirs(directory, exist_ok=True)
+
+    def _path(self, gen: int, rank: int, kind: str = "bin") -> str:
+        return os.path.join(self.dir, f"{self.tag}_g{gen}_r{rank}.{kind}")
+
+    def _publish(self, gen: int, tensor: Optional[torch.Tensor]):
+        path = self._path(gen, self.rank)
+        tmp = path + f".tmp{os.getpid()}"
+        with open(tmp, "wb") as f:
+            if tensor is not None:
+                t = tensor.detach().cpu().contiguous()
+                f.write((t.view(torch.uint16) if t.dtype == torch.bfloat16 else t).numpy().tobytes())
+        os.replace(tmp, path)
+        open(self._path(gen, self.rank, "ready"), "wb").close()
+
+    def _fetch(self, gen: int, rank: int, like: torch.Tensor) -> torch.Tensor:
+        deadline = time.monotonic() + self.timeout
+        ready = self._path(gen, rank, "ready")
+        while not os.path.exists(ready):
+            if time.monotonic() > deadline:
+                raise CollectiveTimeout(f"rank {self.rank}: rank {rank} did not publish generation {gen} within {self.timeout}s")
+            time.sleep(self.poll)
+        with open(self._path(gen, rank), "rb") as f:
+            raw = f.read()
+        if like is None:
+            return None
+        src = torch.frombuffer(bytearray(raw), dtype=torch.uint16 if like.dtype == torch.bfloat16 else like.dtype)
+        src = src.view(torch.bfloat16) if like.dtype == torch.bfloat16 else src
+        return src.view(like.shape).clone()
+
+    def _exchange(self, tensor: Optional[torch.Tensor], like: Optional[torch.Tensor] = None, only: Optional[int] = None):
+        """Publish ``tensor`` (or nothing), read what rank ``only`` (or every rank) published; clean up two generations back."""
+        gen = self.gen
+        self.gen += 1
+        self._publish(gen, tensor)
+        like = like if like is not None else tensor
+        ranks = range(self.world_size) if only is None else [only]
+        got = {r: (tensor.detach().cpu().clone() if r == self.rank and tensor is not None else self._fetch(gen, r, like)) for r in ranks}
+        if only is not None:                                  # everyone must have read before anyone races ahead by two
+            for r in range(self.world_size):
+                self._fetch(gen, r, None)
+        for kind in ("bin", "ready"):                         # all ranks are past generation gen - 2 once they published gen
+            old = self._path(gen - 2, self.rank, kind)
+            if gen >= 2 and os.path.exists(old):
+                os.remove(old)
+        return got
+
+    def all_reduce(self, tensor, op=ReduceOp.SUM):
+        got = self._exchange(tensor)
+        s = torch.stack([got[r].to(torch.float32) if tensor.dtype == torch.bfloat16 else got[r] for r in range(self.world_size)])
+        r = s.sum(0) if op == ReduceOp.SUM else s.mean(0) if op == ReduceOp.AVG else s.amax(0) if op == ReduceOp.MAX else s.amin(0)
+        tensor.copy_(r.to(tensor.dtype))
+        return tensor
+
+    def broadcast(self, tensor, src=0):
+        got = self._exchange(tensor if self.rank == src else None, like=tensor, only=src)
+        tensor.copy_(got[src])
+        return tensor
+
+    def barrier(self):
+        self._exchange(None, like=None)
+
+    def all_gather(self, out, tensor):
+        got = self._exchange(tensor)
+        for r, o in enumerate(out):
+            o.copy_(got[r])
+
+    def reduce_scatter(self, out, inputs, op=ReduceOp.SUM):
+        got = self._exchange(torch.stack([t.detach() for t in inputs]))
+        r = torch.stack([got[k][self.rank] for k in range(self.world_size)]).sum(0)
+        out.copy_(r / (self.world_size if op == ReduceOp.AVG else 1))
 
 
 _TORCH_OPS = None

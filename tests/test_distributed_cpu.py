@@ -122,3 +122,48 @@ def test_distributed_sampler_disjoint():
 def test_parse_dist_args():
     a = D.parse_dist_args(["--rank", "2", "--world-size", "4", "--master-port", "1234", "--nprocs", "2"])
     assert (a.rank, a.world_size, a.master_port, a.nprocs) == (2, 4, 1234, 2)
+
+
+def test_file_backend_collectives_and_timeout(tmp_path):
+    """Ranks that meet through a directory: every collective, generations cleaned up, a missing rank times out."""
+    import threading
+    from prometorch_b200.distributed import CollectiveTimeout, FileBackend, ReduceOp
+    W = 3
+    results, errors = {}, []
+
+    def worker(r):
+        try:
+            pg = FileBackend(str(tmp_path / "sync"), r, W, timeout=20.0)
+            a = torch.arange(4, dtype=torch.float32) * (r + 1)
+            pg.all_reduce(a)
+            b = torch.full((3,), float(r))
+            pg.broadcast(b, src=1)
+            outs = [torch.zeros(2) for _ in range(W)]
+            pg.all_gather(outs, torch.tensor([r, r * 10.0]))
+            rs = torch.zeros(2)
+            pg.reduce_scatter(rs, [torch.full((2,), float(r + k)) for k in range(W)], op=ReduceOp.AVG)
+            h = torch.ones(5, dtype=torch.bfloat16) * (r + 1)
+            pg.all_reduce(h, op=ReduceOp.MAX)
+            for _ in range(4):
+                pg.barrier()
+            results[r] = (a, b, torch.stack(outs), rs, h)
+        except Exception as e:          # noqa: BLE001
+            errors.append(e)
+    ts = [threading.Thread(target=worker, args=(r,)) for r in range(W)]
+    for t in ts:
+        t.start()
+    for t in ts:
+        t.join(60)
+    assert not errors, errors
+    for r in range(W):
+        a, b, g, rs, h = results[r]
+        assert torch.equal(a, torch.arange(4, dtype=torch.float32) * 6)
+        assert torch.equal(b, torch.full((3,), 1.0))
+        assert torch.equal(g, torch.tensor([[0.0, 0.0], [1.0, 10.0], [2.0, 20.0]]))
+        assert torch.allclose(rs, torch.full((2,), (0 + 1 + 2) / 3 + r))
+        assert torch.equal(h.float(), torch.full((5,), 3.0))
+    left = sorted(p.name for p in (tmp_path / "sync").iterdir())
+    assert len(left) <= 2 * 2 * W, left                      # only the last two generations remain
+    lonely = FileBackend(str(tmp_path / "alone"), 0, 2, timeout=0.2)
+    with pytest.raises(CollectiveTimeout):
+        lonely.barrier()
