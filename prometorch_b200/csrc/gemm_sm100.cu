@@ -107,7 +107,7 @@ static void fill_staging(Staging& S, const PtbStaging* h) {
 
 // General entry point.  a_ptrs/b_ptrs: arrays of a_shards/b_shards device pointers.  c_peers (EPI_SCATTER_ADD):
 // `c_shards` fp32 buffers [out_shard_rows, ldc], one per rank.
-struct SplitK { int splits; long long stride; };      // splits > 1: fp32 partials at C + s*stride, BN forced to 128
+struct SplitK { int splits; long long stride; int bn; };      // splits > 1: fp32 partials at C + s*stride; bn: 0 or a forced tile width
 
 static int gemm_core(void* const* a_ptrs, int a_shards, int a_shard_rows, long long lda, int a_mn, void* const* b_ptrs,
                      int b_shards, int b_shard_rows, long long ldb, int b_mn, void* C, long long ldc, void* const* c_peers,
@@ -150,7 +150,7 @@ static int gemm_core(void* const* a_ptrs, int a_shards, int a_shard_rows, long l
         if (0.85 * eff(128) > eff(256)) BN = 128;
     }
     if (!b_mn && b_shards > 1 && b_shard_rows % 256) BN = 128;
-    if (sk.splits > 1) BN = 128;
+    if (sk.bn) BN = sk.bn;
     const int kblocks = (K + BK - 1) / BK;
     p.splits = std::max(1, sk.splits);
     p.kb_per_split = (kblocks + p.splits - 1) / p.splits;
@@ -179,7 +179,7 @@ PTB_API int ptb_gemm_bf16_ex(void* const* a_ptrs, int a_shards, int a_shard_rows
                              int c_shards, int out_shard_rows, int M, int N, int K, const float* bias, int flags, int* status,
                              int n_sm, cudaStream_t st, const PtbStaging* stage_a, const PtbStaging* stage_b) {
     return gemm_core(a_ptrs, a_shards, a_shard_rows, lda, a_mn, b_ptrs, b_shards, b_shard_rows, ldb, b_mn, C, ldc, c_peers, c_shards,
-                     out_shard_rows, M, N, K, bias, flags, status, n_sm, st, stage_a, stage_b, SplitK{1, 0});
+                     out_shard_rows, M, N, K, bias, flags, status, n_sm, st, stage_a, stage_b, SplitK{1, 0, 0});
 }
 
 // Sum the split-K partials, add the bias, apply GELU, round to bf16.  work: [splits][M][N] fp32; N a multiple of 4.
@@ -202,20 +202,124 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
     o[1] = __floats2bfloat162_rn(acc.z, acc.w);
 }
 
-// How many K-splits a skinny GEMM (one row tile) should use so that its work items fill the machine: the makespan of
-// `waves` rounds of (k-blocks per item x per-block time + fixed cost) is minimised over 1..16 splits.
-PTB_API int ptb_gemm_pick_splits(int M, int N, int K, int n_sm) {
+// Split-K sum fused with what follows a projection in a decoder layer, so the partials are read once and the layer
+// saves a launch: (a) residual add + RMSNorm after the attention-output and MLP-down projections, (b) the gated
+// activation after the packed gate/up projection.
+constexpr int SKN_THREADS = 256, SKN_MAXC = 8;            // up to 8 float4 chunks per thread: N <= 8192
+
+// One CTA per row.  h = sum_s work[s][row] + resid_in[row] (rounded to bf16, stored in resid_out); y = rmsnorm(h) * w.
+__global__ void __launch_bounds__(SKN_THREADS) splitk_reduce_norm_kernel(const float* __restrict__ work, int splits, long long mn, int N,
+                                                                         const __nv_bfloat16* __restrict__ resid_in,
+                                                                         __nv_bfloat16* __restrict__ resid_out,
+                                                                         const __nv_bfloat16* __restrict__ w, float eps,
+                                                                         __nv_bfloat16* __restrict__ y) {
+    __shared__ float red[32];
+    const size_t row = blockIdx.x;
+    const int nc = N / 4;
+    float4 h[SKN_MAXC];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < SKN_MAXC; ++k) {
+        const int c = k * SKN_THREADS + threadIdx.x;
+        if (c < nc) {
+            float4 a = *reinterpret_cast<const float4*>(work + row * N + (size_t)c * 4);
+            for (int s = 1; s < splits; ++s) {
+                const float4 v = *reinterpret_cast<const float4*>(work + (size_t)s * mn + row * N + (size_t)c * 4);
+                a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+            }
+            const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(resid_in + row * N + (size_t)c * 4);
+            const float2 r0 = __bfloat1622float2(r2[0]), r1 = __bfloat1622float2(r2[1]);
+            const __nv_bfloat162 o0 = __floats2bfloat162_rn(a.x + r0.x, a.y + r0.y), o1 = __floats2bfloat162_rn(a.z + r1.x, a.w + r1.y);
+            __nv_bfloat162* out2 = reinterpret_cast<__nv_bfloat162*>(resid_out + row * N + (size_t)c * 4);
+            out2[0] = o0; out2[1] = o1;
+            const float2 f0 = __bfloat1622float2(o0), f1 = __bfloat1622float2(o1);      // normalise what was stored
+            h[k] = make_float4(f0.x, f0.y, f1.x, f1.y);
+            ss += f0.x * f0.x + f0.y * f0.y + f1.x * f1.x + f1.y * f1.y;
+        }
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float t = (threadIdx.x & 31) < SKN_THREADS / 32 ? red[threadIdx.x & 31] : 0.f;
+    t = warp_sum(t);
+    const float rs = rsqrtf(t / (float)N + eps);
+#pragma unroll
+    for (int k = 0; k < SKN_MAXC; ++k) {
+        const int c = k * SKN_THREADS + threadIdx.x;
+        if (c < nc) {
+            const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(w + (size_t)c * 4);
+            const float2 w0 = __bfloat1622float2(w2[0]), w1 = __bfloat1622float2(w2[1]);
+            __nv_bfloat162* y2 = reinterpret_cast<__nv_bfloat162*>(y + row * N + (size_t)c * 4);
+            y2[0] = __floats2bfloat162_rn(h[k].x * rs * w0.x, h[k].y * rs * w0.y);
+            y2[1] = __floats2bfloat162_rn(h[k].z * rs * w1.x, h[k].w * rs * w1.y);
+        }
+    }
+}
+
+// out[row][c] = act(sum_s gate) * (sum_s up) for the packed projection [M, 2 I] (gate columns first).
+__global__ void __launch_bounds__(256) splitk_reduce_gated_kernel(const float* __restrict__ work, int splits, long long mn, int I, int gelu,
+                                                                  long long total4, __nv_bfloat16* __restrict__ out) {
+    const long long i4 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i4 >= total4) return;
+    const long long row = (i4 * 4) / I;
+    const int col = (int)(i4 * 4 - row * I);
+    const float* base = work + row * 2 * I + col;
+    float4 g = *reinterpret_cast<const float4*>(base), u = *reinterpret_cast<const float4*>(base + I);
+    for (int s = 1; s < splits; ++s) {
+        const float4 a = *reinterpret_cast<const float4*>(base + (size_t)s * mn), b = *reinterpret_cast<const float4*>(base + (size_t)s * mn + I);
+        g.x += a.x; g.y += a.y; g.z += a.z; g.w += a.w;
+        u.x += b.x; u.y += b.y; u.z += b.z; u.w += b.w;
+    }
+    auto act = [&](float x) { return gelu ? gelu_tanh(x) : silu(x); };
+    __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(out + row * I + col);
+    o[0] = __floats2bfloat162_rn(act(g.x) * u.x, act(g.y) * u.y);
+    o[1] = __floats2bfloat162_rn(act(g.z) * u.z, act(g.w) * u.w);
+}
+
+// Tile width and K-split count for a skinny GEMM (one row of tiles).  The CTAs are persistent and their TMA producers
+// run ahead across work items, so the makespan is about (items per SM) x (k-blocks per item) x (time per k-block) plus one
+// fixed cost and, with splits, the reduce launch.  A 256-wide tile moves twice the bytes per k-block at ~1.3x the time.
+// Returns splits | (BN == 256 ? 0x100 : 0).
+static int pick_skinny(int M, int N, int K, int n_sm) {
     if (M > BM || n_sm <= 0) return 1;
-    const int tiles = (N + 127) / 128, kblocks = (K + BK - 1) / BK;
+    const int kblocks = (K + BK - 1) / BK;
     int best = 1;
     double best_cost = 1e30;
-    for (int s = 1; s <= 16 && s <= kblocks; ++s) {
-        const int kbps = (kblocks + s - 1) / s, items = tiles * ((kblocks + kbps - 1) / kbps);
-        const int waves = (items + n_sm - 1) / n_sm;
-        const double cost = waves * (kbps * 0.25 + 2.0) + (s > 1 ? 2.5 : 0.0);      // microseconds, roughly; the reduce pass costs a launch
-        if (cost < best_cost - 1e-9) { best_cost = cost; best = s; }
+    for (int wide = 0; wide < 2; ++wide) {
+        if (wide && N <= 128) continue;
+        const int bn = wide ? 256 : 128, tiles = (N + bn - 1) / bn;
+        const double t_kb = wide ? 0.33 : 0.25;
+        for (int s = 1; s <= 16 && s <= kblocks; ++s) {
+            const int kbps = (kblocks + s - 1) / s, items = tiles * ((kblocks + kbps - 1) / kbps);
+            const int per_sm = (items + n_sm - 1) / n_sm;
+            // per item: its k-blocks plus an epilogue that is only partly hidden; the reduce pass reads every partial
+            const double cost = per_sm * (kbps * t_kb + 0.4) + 3.0 + (s > 1 ? 2.5 + (double)s * M * N * 4.0 / 4.0e6 : 0.0);
+            if (cost < best_cost - 1e-9) { best_cost = cost; best = s | (wide ? 0x100 : 0); }
+        }
     }
     return best;
+}
+
+PTB_API int ptb_gemm_pick_splits(int M, int N, int K, int n_sm) { return pick_skinny(M, N, K, n_sm) & 0xff; }
+
+static int skinny_partials(const void* A, long long lda, const void* B, long long ldb, int M, int N, int K, int splits, float* work,
+                           int* status, int n_sm, cudaStream_t st, int* real_splits) {
+    if (M > BM || (N & 3) || splits < 2 || !work) { ptb_set_error("gemm split-K: needs M <= %d, N %% 4 == 0, splits >= 2 and a workspace", BM); return -1; }
+    void* ap[1] = {const_cast<void*>(A)};
+    void* bp[1] = {const_cast<void*>(B)};
+    {
+        int dev = 0;
+        PTB_CUDA_OK(cudaGetDevice(&dev));
+        if (n_sm <= 0) PTB_CUDA_OK(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
+    }
+    const int choice = pick_skinny(M, N, K, n_sm);
+    const int bn = ((choice >> 8) && (choice & 0xff) == splits) ? 256 : 128;       // the wide tile only for the split count it was chosen with
+    if (gemm_core(ap, 1, 0, lda, 0, bp, 1, 0, ldb, 0, work, N, nullptr, 0, 0, M, N, K, nullptr, EPI_OUT_F32, status, n_sm, st, nullptr, nullptr,
+                  SplitK{splits, (long long)M * N, bn}))
+        return -1;
+    const int kblocks = (K + BK - 1) / BK, kbps = (kblocks + splits - 1) / splits;
+    *real_splits = (kblocks + kbps - 1) / kbps;
+    return 0;
 }
 
 // Skinny GEMM (M <= 128), K-major operands: C[M,N] bf16 = A[M,K] B[N,K]^T (+ bias, GELU) with `splits` K-splits whose
@@ -223,15 +327,38 @@ PTB_API int ptb_gemm_pick_splits(int M, int N, int K, int n_sm) {
 PTB_API int ptb_gemm_bf16_splitk(const void* A, long long lda, const void* B, long long ldb, void* C, long long ldc, int M, int N, int K,
                                  const float* bias, int gelu, int splits, float* work, int* status, int n_sm, cudaStream_t st) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
-    if (M > BM || (N & 3) || splits < 2 || !work) { ptb_set_error("gemm split-K: needs M <= %d, N %% 4 == 0, splits >= 2 and a workspace", BM); return -1; }
-    void* ap[1] = {const_cast<void*>(A)};
-    void* bp[1] = {const_cast<void*>(B)};
+    int real = 0;
+    if (skinny_partials(A, lda, B, ldb, M, N, K, splits, work, status, n_sm, st, &real)) return -1;
     const long long mn = (long long)M * N;
-    if (gemm_core(ap, 1, 0, lda, 0, bp, 1, 0, ldb, 0, work, N, nullptr, 0, 0, M, N, K, nullptr, EPI_OUT_F32, status, n_sm, st, nullptr, nullptr,
-                  SplitK{splits, mn}))
-        return -1;
-    const int kblocks = (K + BK - 1) / BK, kbps = (kblocks + splits - 1) / splits, real = (kblocks + kbps - 1) / kbps;
     splitk_reduce_kernel<<<(unsigned)((mn / 4 + 255) / 256), 256, 0, st>>>(work, real, mn, N, bias, gelu, (__nv_bfloat16*)C, ldc);
+    PTB_CUDA_OK(cudaGetLastError());
+    return 0;
+}
+
+// The same product followed, in the reduce launch, by `resid_out = P + resid_in` and `y = rmsnorm(resid_out) * norm_w`
+// (all bf16, [M, N] contiguous; N <= 8192).
+PTB_API int ptb_gemm_bf16_splitk_add_norm(const void* A, long long lda, const void* B, long long ldb, int M, int N, int K, int splits,
+                                          float* work, const void* resid_in, void* resid_out, const void* norm_w, float eps, void* y,
+                                          int* status, int n_sm, cudaStream_t st) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    if (N > 4 * SKN_THREADS * SKN_MAXC) { ptb_set_error("gemm split-K + norm: N %d above %d", N, 4 * SKN_THREADS * SKN_MAXC); return -1; }
+    int real = 0;
+    if (skinny_partials(A, lda, B, ldb, M, N, K, splits, work, status, n_sm, st, &real)) return -1;
+    splitk_reduce_norm_kernel<<<M, SKN_THREADS, 0, st>>>(work, real, (long long)M * N, N, (const __nv_bfloat16*)resid_in, (__nv_bfloat16*)resid_out,
+                                                         (const __nv_bfloat16*)norm_w, eps, (__nv_bfloat16*)y);
+    PTB_CUDA_OK(cudaGetLastError());
+    return 0;
+}
+
+// The packed gate/up projection (N = 2 I, gate columns first) followed by out[M, I] = act(gate) * up in the reduce launch.
+PTB_API int ptb_gemm_bf16_splitk_gated(const void* A, long long lda, const void* B, long long ldb, int M, int N, int K, int splits,
+                                       float* work, int gelu, void* out, int* status, int n_sm, cudaStream_t st) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    if (N & 7) { ptb_set_error("gemm split-K + gate: N must be a multiple of 8"); return -1; }
+    int real = 0;
+    if (skinny_partials(A, lda, B, ldb, M, N, K, splits, work, status, n_sm, st, &real)) return -1;
+    const long long total4 = (long long)M * (N / 2) / 4;
+    splitk_reduce_gated_kernel<<<(unsigned)((total4 + 255) / 256), 256, 0, st>>>(work, real, (long long)M * N, N / 2, gelu, total4, (__nv_bfloat16*)out);
     PTB_CUDA_OK(cudaGetLastError());
     return 0;
 }

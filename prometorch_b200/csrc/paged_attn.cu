@@ -91,7 +91,8 @@ struct PagedAttnParams {
 
 template <int D, int G>
 __global__ void __launch_bounds__(PA_THREADS) paged_attn_decode_kernel(const __grid_constant__ PagedAttnParams P) {
-    constexpr int DV = D / 32;                        // output dims per lane
+    constexpr int DV = D / 32;                        // output dims per lane (4 or 2)
+    static_assert(DV == 4 || DV == 2, "head size 128 or 64");
     __shared__ float q_s[G][D];
     __shared__ float p_s[PA_WARPS][G][PAGE];
     __shared__ float acc_s[PA_WARPS][G][D];
@@ -133,7 +134,7 @@ __global__ void __launch_bounds__(PA_THREADS) paged_attn_decode_kernel(const __g
             for (int g = 0; g < G; ++g) s[r][g] = 0.f;
             if (t < valid) {
                 const uint4* kr = reinterpret_cast<const uint4*>(kb + (size_t)t * D);
-#pragma unroll 4
+#pragma unroll 8
                 for (int c = 0; c < D / 8; ++c) {
                     const uint4 raw = kr[c];
                     const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
@@ -166,23 +167,31 @@ __global__ void __launch_bounds__(PA_THREADS) paged_attn_decode_kernel(const __g
             for (int i = 0; i < DV; ++i) acc[g][i] *= corr;
         }
         __syncwarp();
-        // P V: each lane owns DV consecutive output dims
-        for (int t = 0; t < valid; ++t) {
-            float vf[DV];
-            if constexpr (DV == 4) {
-                const uint2 raw = *reinterpret_cast<const uint2*>(vb + (size_t)t * D + lane * 4);
-                const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-                const float2 a = __bfloat1622float2(h2[0]), c = __bfloat1622float2(h2[1]);
-                vf[0] = a.x; vf[1] = a.y; vf[2] = c.x; vf[3] = c.y;
-            } else {
+        // P V: each lane owns DV consecutive output dims.  Eight rows are fetched before they are used so that eight
+        // loads are in flight per lane; rows past `valid` belong to the page (readable) and carry p = 0.
+        for (int t0 = 0; t0 < valid; t0 += 8) {
+            float vf[8][DV];
 #pragma unroll
-                for (int i = 0; i < DV; ++i) vf[i] = __bfloat162float(vb[(size_t)t * D + lane * DV + i]);
+            for (int u = 0; u < 8; ++u) {
+                const __nv_bfloat16* vr = vb + (size_t)(t0 + u) * D + lane * DV;
+                if constexpr (DV == 4) {
+                    const uint2 raw = *reinterpret_cast<const uint2*>(vr);
+                    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+                    const float2 a = __bfloat1622float2(h2[0]), c = __bfloat1622float2(h2[1]);
+                    vf[u][0] = a.x; vf[u][1] = a.y; vf[u][2] = c.x; vf[u][3] = c.y;
+                } else {
+                    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(vr));
+                    vf[u][0] = a.x; vf[u][1] = a.y;
+                }
             }
 #pragma unroll
-            for (int g = 0; g < G; ++g) {
-                const float p = p_s[warp][g][t];
+            for (int u = 0; u < 8; ++u) {
 #pragma unroll
-                for (int i = 0; i < DV; ++i) acc[g][i] += p * vf[i];
+                for (int g = 0; g < G; ++g) {
+                    const float p = p_s[warp][g][t0 + u];
+#pragma unroll
+                    for (int i = 0; i < DV; ++i) acc[g][i] += p * vf[u][i];
+                }
             }
         }
         __syncwarp();

@@ -28,6 +28,12 @@ def _decls(L):
         L.ptb_gemm_pick_splits.restype = ci
         L.ptb_gemm_bf16_splitk.argtypes = [vp, ll, vp, ll, vp, ll, ci, ci, ci, vp, ci, ci, vp, vp, ci, vp]
         L.ptb_gemm_bf16_splitk.restype = ci
+    if hasattr(L, "ptb_gemm_bf16_splitk_add_norm"):
+        cf = C.c_float
+        L.ptb_gemm_bf16_splitk_add_norm.argtypes = [vp, ll, vp, ll, ci, ci, ci, ci, vp, vp, vp, vp, cf, vp, vp, ci, vp]
+        L.ptb_gemm_bf16_splitk_add_norm.restype = ci
+        L.ptb_gemm_bf16_splitk_gated.argtypes = [vp, ll, vp, ll, ci, ci, ci, ci, vp, ci, vp, vp, ci, vp]
+        L.ptb_gemm_bf16_splitk_gated.restype = ci
 
 
 _STATUS = {}
@@ -132,3 +138,49 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     if x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 and weight.shape[0] % 8 == 0:
         return _Linear.apply(x, weight, bias)
     return torch.nn.functional.linear(x, weight, bias)
+
+
+def _skinny_splits(x: torch.Tensor, w: torch.Tensor) -> int:
+    """Split count for ``x [M, K] @ w[N, K]^T`` when the fused split-K path applies, else 0."""
+    if not (_SPLITK and x.is_cuda and x.dim() == 2 and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[0] <= 128
+            and x.stride(1) == 1 and w.stride(1) == 1 and x.shape[1] % 8 == 0 and w.shape[0] % 8 == 0
+            and hasattr(N.lib(), "ptb_gemm_bf16_splitk_add_norm")):
+        return 0
+    s = N.lib().ptb_gemm_pick_splits(x.shape[0], w.shape[0], x.shape[1], _sms(x.device))
+    return s if s > 1 else 0
+
+
+def linear_add_rms_norm(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor, norm_w: torch.Tensor, eps: float):
+    """``h = x W^T + resid``; returns ``(rmsnorm(h) * norm_w, h)``.  For decode-sized batches the sum of the split-K
+    partials, the residual add and the norm are one launch after the GEMM (inference path, no autograd)."""
+    splits = _skinny_splits(x, w)
+    if splits and w.shape[0] <= 8192 and resid.is_contiguous() and norm_w.dtype == torch.bfloat16 and not torch.is_grad_enabled():
+        M, K, Nn = x.shape[0], x.shape[1], w.shape[0]
+        work = torch.empty(splits * M * Nn, dtype=torch.float32, device=x.device)
+        h, y = torch.empty_like(resid), torch.empty_like(resid)
+        st = torch.cuda.current_stream(x.device).cuda_stream
+        N.check(N.lib().ptb_gemm_bf16_splitk_add_norm(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), M, Nn, K, splits, work.data_ptr(),
+                                                      resid.data_ptr(), h.data_ptr(), norm_w.data_ptr(), float(eps), y.data_ptr(),
+                                                      _status(x.device).data_ptr(), 0, st), "gemm_bf16_splitk_add_norm")
+        return y, h
+    from .fused_ops import add_rms_norm
+    return add_rms_norm(linear(x, w), resid, norm_w, eps)
+
+
+def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, gelu: bool = False) -> torch.Tensor:
+    """``act(x Wg^T) * (x Wu^T)`` for the packed weight ``[2 I, K]`` (gate rows first); the split-K sum and the gate
+    share a launch for decode-sized batches (inference path, no autograd)."""
+    splits = _skinny_splits(x, w_gate_up)
+    if splits and not torch.is_grad_enabled():
+        M, K, Nn = x.shape[0], x.shape[1], w_gate_up.shape[0]
+        work = torch.empty(splits * M * Nn, dtype=torch.float32, device=x.device)
+        out = torch.empty(M, Nn // 2, dtype=torch.bfloat16, device=x.device)
+        st = torch.cuda.current_stream(x.device).cuda_stream
+        N.check(N.lib().ptb_gemm_bf16_splitk_gated(x.data_ptr(), x.stride(0), w_gate_up.data_ptr(), w_gate_up.stride(0), M, Nn, K, splits,
+                                                   work.data_ptr(), int(gelu), out.data_ptr(), _status(x.device).data_ptr(), 0, st),
+                "gemm_bf16_splitk_gated")
+        return out
+    from .fused_ops import swiglu
+    if x.is_cuda:
+        return swiglu(linear(x, w_gate_up), gelu)
+    return swiglu(torch.nn.functional.linear(x, w_gate_up), gelu)

@@ -91,9 +91,14 @@ def paged_rope_write(qkv: torch.Tensor, H: int, Hk: int, D: int, pos: torch.Tens
 
 
 def pick_splits(B: int, Hk: int, max_len: int, sms: int = 148) -> int:
-    """Splits of the page walk so that a small batch still fills the machine."""
+    """Splits of the page walk.  A CTA is four warps with a few KB of loads in flight each, so the kernel wants about
+    eight CTAs per SM to saturate HBM; a split should still own two pages or more.  The page count is rounded up to a
+    power of two so that the choice (a key of the engine's graph cache) changes rarely as a context grows."""
     pages = max(1, (max_len + PAGE - 1) // PAGE)
-    return int(max(1, min(8, pages // 4, (2 * sms) // max(1, B * Hk))))
+    bucket = 1
+    while bucket < pages:
+        bucket *= 2
+    return int(max(1, min(16, bucket // 2, (8 * sms) // max(1, B * Hk))))
 
 
 def paged_attention_decode(q: torch.Tensor, H: int, Hk: int, D: int, lens: torch.Tensor, page_table: torch.Tensor,

@@ -509,7 +509,7 @@ class LLMEngine:
 
     def _decode_layers(self, meta: torch.Tensor, nsplit: int) -> torch.Tensor:
         """The device work of a decode pass.  ``meta [B, 4]`` int32: token id, position, page-table row, cached length."""
-        from ..ops.fused_ops import add_rms_norm
+        from ..ops.gemm import linear_add_rms_norm, linear_swiglu
         c, w = self.cfg, self.weights
         H, Hk, Dh = c.num_attention_heads, c.num_key_value_heads, c.head_dim
         B = meta.shape[0]
@@ -522,9 +522,9 @@ class LLMEngine:
             qkv = self._linear(h, L["wqkv"])
             P.paged_rope_write(qkv, H, Hk, Dh, pos, req, table, self.cos, self.sin, self.kv.k[l], self.kv.v[l])
             a = P.paged_attention_decode(qkv, H, Hk, Dh, lens, table, self.kv.k[l], self.kv.v[l], nsplit=nsplit)
-            h, x = add_rms_norm(self._linear(a, L["wo"]), x, L["ffn_norm"], c.rms_norm_eps)
+            h, x = linear_add_rms_norm(a, L["wo"], x, L["ffn_norm"], c.rms_norm_eps)
             nxt = w.layers[l + 1]["attn_norm"] if l + 1 < len(w.layers) else w.final_norm
-            h, x = add_rms_norm(self._mlp(h, L), x, nxt, c.rms_norm_eps)
+            h, x = linear_add_rms_norm(linear_swiglu(h, L["w_gate_up"]), L["w_down"], x, nxt, c.rms_norm_eps)
         return self._linear(h, w.lm_head).float()
 
     def _forward_decode(self, batch: List[RequestState]) -> torch.Tensor:

@@ -211,4 +211,4 @@ def test_paged_ops_reference_paths():
         s = torch.einsum("hd,nhd->hn", q[b].view(H, D), k) / math.sqrt(D)
         ref = torch.einsum("hn,nhd->hd", torch.softmax(s, -1), v).reshape(-1)
         assert torch.allclose(out[b], ref, atol=1e-5)
-    assert P.pick_splits(1, 8, 8192) >= 2 and P.pick_splits(64, 8, 8192) == 1
+    assert P.pick_splits(1, 8, 8192) == 16 and P.pick_splits(64, 8, 8192) == 2 and P.pick_splits(4, 4, 64) == 1

@@ -82,6 +82,38 @@ def test_gemm_skinny_split_k(M, N, K):
         assert splits > 1                       # few tiles: the split path really ran
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 2048, 2048), (32, 2048, 5632), (8, 4096, 4096), (128, 512, 1024)])
+def test_skinny_linear_add_rms_norm(M, N, K):
+    from prometorch_b200.ops.gemm import check_status, linear_add_rms_norm
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(N, K, device="cuda", generator=g) * K ** -0.5).bfloat16()
+    resid = torch.randn(M, N, device="cuda", generator=g).bfloat16()
+    nw = (1 + 0.1 * torch.randn(N, device="cuda", generator=g)).bfloat16()
+    with torch.no_grad():
+        y, h = linear_add_rms_norm(x, w, resid, nw, 1e-5)
+    torch.cuda.synchronize()
+    check_status()
+    h_ref = x.float() @ w.float().t() + resid.float()
+    y_ref = h_ref * torch.rsqrt(h_ref.pow(2).mean(-1, keepdim=True) + 1e-5) * nw.float()
+    assert _rel(h, h_ref) < 5e-3 and _rel(y, y_ref) < 8e-3, (_rel(h, h_ref), _rel(y, y_ref))
+
+
+@pytest.mark.parametrize("M,I,K,gelu", [(1, 5632, 2048, False), (32, 5632, 2048, False), (16, 1024, 512, True), (128, 11008, 4096, False)])
+def test_skinny_linear_swiglu(M, I, K, gelu):
+    from prometorch_b200.ops.gemm import check_status, linear_swiglu
+    g = torch.Generator(device="cuda").manual_seed(M + I + K)
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(2 * I, K, device="cuda", generator=g) * K ** -0.5).bfloat16()
+    with torch.no_grad():
+        out = linear_swiglu(x, w, gelu)
+    torch.cuda.synchronize()
+    check_status()
+    gu = x.float() @ w.float().t()
+    act = F.gelu(gu[:, :I], approximate="tanh") if gelu else F.silu(gu[:, :I])
+    assert out.shape == (M, I) and _rel(out, act * gu[:, I:]) < 8e-3, _rel(out, act * gu[:, I:])
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("H", [384, 2048, 2560, 4096])
 def test_rmsnorm(dtype, H):
