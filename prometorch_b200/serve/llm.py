@@ -19,12 +19,10 @@ import collections
 import json
 import math
 import os
-import struct
 import time
 from dataclasses import dataclass, field
 from typing import Deque, Dict, List, Optional, Sequence, Union
 
-import numpy as np
 import torch
 import torch.nn.functional as F
 
@@ -94,46 +92,7 @@ class LlamaConfig:
         return c
 
 
-# ------------------------------------------------------------------------------------------ safetensors
-_ST_DTYPES = {"F32": (torch.float32, np.float32), "F16": (torch.float16, np.float16), "BF16": (torch.bfloat16, np.uint16),
-              "I32": (torch.int32, np.int32), "I64": (torch.int64, np.int64), "U8": (torch.uint8, np.uint8)}
-
-
-def load_safetensors(path: str) -> Dict[str, torch.Tensor]:
-    """Read a ``.safetensors`` file: 8-byte little-endian header length, JSON header, raw tensor bytes."""
-    out: Dict[str, torch.Tensor] = {}
-    with open(path, "rb") as f:
-        (n,) = struct.unpack("<Q", f.read(8))
-        header = json.loads(f.read(n))
-        base = 8 + n
-    raw = np.memmap(path, dtype=np.uint8, mode="r", offset=base) if os.path.getsize(path) > base else np.zeros(0, np.uint8)
-    for name, meta in header.items():
-        if name == "__metadata__":
-            continue
-        tdt, ndt = _ST_DTYPES[meta["dtype"]]
-        lo, hi = meta["data_offsets"]
-        arr = np.frombuffer(raw[lo:hi].tobytes(), dtype=ndt).reshape(meta["shape"])
-        t = torch.from_numpy(arr.copy())
-        out[name] = t.view(torch.bfloat16) if tdt == torch.bfloat16 else t
-    return out
-
-
-def save_safetensors(tensors: Dict[str, torch.Tensor], path: str):
-    header, blobs, off = {}, [], 0
-    names = {v: k for k, (v, _) in _ST_DTYPES.items()}
-    for name, t in tensors.items():
-        t = t.detach().cpu().contiguous()
-        b = (t.view(torch.uint16) if t.dtype == torch.bfloat16 else t).numpy().tobytes()
-        header[name] = {"dtype": names[t.dtype], "shape": list(t.shape), "data_offsets": [off, off + len(b)]}
-        blobs.append(b)
-        off += len(b)
-    h = json.dumps(header).encode()
-    h += b" " * (-len(h) % 8)
-    with open(path, "wb") as f:
-        f.write(struct.pack("<Q", len(h)))
-        f.write(h)
-        for b in blobs:
-            f.write(b)
+from ..io.safetensors import load_checkpoint_dir, load_file as load_safetensors, save_file as save_safetensors  # noqa: E402,F401
 
 
 # ------------------------------------------------------------------------------------------ weights
@@ -169,6 +128,8 @@ class LlamaWeights:
     def from_state_dict(cls, cfg: LlamaConfig, sd: Dict[str, torch.Tensor]) -> "LlamaWeights":
         """Hugging Face names: ``model.layers.N.self_attn.{q,k,v,o}_proj.weight`` and so on."""
         w = cls(cfg)
+        if "embed_tokens.weight" in sd and "model.embed_tokens.weight" not in sd:          # a bare LlamaModel checkpoint
+            sd = {("model." + k if not k.startswith("lm_head") else k): v for k, v in sd.items()}
         w.tok_emb = sd["model.embed_tokens.weight"]
         for l in range(cfg.num_hidden_layers):
             p = f"model.layers.{l}."
@@ -308,15 +269,7 @@ class LLMEngine:
         if not os.path.exists(cj):
             return False
         cfg = LlamaConfig.from_json(cj)
-        sd: Dict[str, torch.Tensor] = {}
-        single, index = os.path.join(model_dir, "model.safetensors"), os.path.join(model_dir, "model.safetensors.index.json")
-        if os.path.exists(single):
-            sd = load_safetensors(single)
-        elif os.path.exists(index):
-            with open(index) as f:
-                shards = sorted(set(json.load(f)["weight_map"].values()))
-            for s in shards:
-                sd.update(load_safetensors(os.path.join(model_dir, s)))
+        sd = load_checkpoint_dir(model_dir)
         tok = load_hf_tokenizer(model_dir)
         if tok is not None:
             self.tokenizer = tok
