@@ -172,3 +172,27 @@ def all_gather_wait(handle: _GatherHandle) -> torch.Tensor:
     if handle.work is not None:
         handle.work.wait()
     return handle.buffer
+
+
+def scatter(tensor: torch.Tensor, rank: int, world_size: int) -> torch.Tensor:
+    """Rank ``rank``'s contiguous share of dim 0 (the last rank takes the remainder)."""
+    per = tensor.shape[0] // world_size
+    lo = rank * per
+    hi = tensor.shape[0] if rank == world_size - 1 else lo + per
+    return tensor[lo:hi]
+
+
+def data_parallel_step(fn, data: torch.Tensor, labels: torch.Tensor, params, world_size: int) -> float:
+    """One data-parallel step inside a single process (torch/distributed/distributed.h:1159-1215): the batch is cut into
+    ``world_size`` shards, ``fn(rank, data_shard, label_shard)`` runs forward + backward for each and returns its loss,
+    and the parameters end up with the AVERAGE of the shard gradients.  The shards share the parameters, so their
+    backward passes accumulate into the same ``.grad``; the ranks run one after another because autograd accumulation
+    into a shared tensor is not safe across threads."""
+    losses = []
+    for rank in range(world_size):
+        losses.append(float(fn(rank, scatter(data, rank, world_size), scatter(labels, rank, world_size))))
+    with torch.no_grad():
+        for p in params:
+            if p.requires_grad and p.grad is not None:
+                p.grad.div_(world_size)
+    return sum(losses) / max(len(losses), 1)

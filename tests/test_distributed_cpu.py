@@ -167,3 +167,23 @@ def test_file_backend_collectives_and_timeout(tmp_path):
     lonely = FileBackend(str(tmp_path / "alone"), 0, 2, timeout=0.2)
     with pytest.raises(CollectiveTimeout):
         lonely.barrier()
+
+
+def test_data_parallel_step_averages_shard_gradients():
+    from prometorch_b200.distributed import data_parallel_step
+    torch.manual_seed(0)
+    lin = torch.nn.Linear(6, 3)
+    x, y = torch.randn(8, 6), torch.randint(0, 3, (8,))
+
+    def fn(rank, xs, ys):
+        loss = torch.nn.functional.cross_entropy(lin(xs), ys)
+        loss.backward()
+        return loss.item()
+    loss = data_parallel_step(fn, x, y, list(lin.parameters()), 4)
+    got = [p.grad.clone() for p in lin.parameters()]
+    lin.zero_grad()
+    ref = torch.nn.functional.cross_entropy(lin(x), y)            # equal shards: the mean of shard means is the batch mean
+    ref.backward()
+    assert abs(loss - ref.item()) < 1e-6
+    for g, p in zip(got, lin.parameters()):
+        assert torch.allclose(g, p.grad, atol=1e-6)
