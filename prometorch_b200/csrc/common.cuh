@@ -9,11 +9,14 @@
 #include <cuda_bf16.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <string.h>
 
 #define PTB_API extern "C" __attribute__((visibility("default")))
 
 // Last error text, readable from Python through ptb_last_error().
 void ptb_set_error(const char* fmt, ...);
+// Whether chained kernels are launched with programmatic stream serialization (PTB_PDL=0 turns it off).
+bool ptb_pdl_enabled();
 
 #define PTB_CUDA_OK(expr)                                                                      \
     do {                                                                                       \
@@ -99,6 +102,24 @@ __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.
 // prologue.  Both are no-ops for a kernel launched without the attribute.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Host side: chained kernels are launched with programmatic stream serialization unless PTB_PDL=0.  A kernel that is
+// launched this way calls pdl_wait() before it touches global memory (every thread, before any early return).
+template <typename... KArgs, typename... Args>
+inline cudaError_t ptb_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl, Args&&... args) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
 
 // ---- system-scope flags (peer GPUs over NVLink) ---------------------------
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {

@@ -18,6 +18,11 @@
 #include <algorithm>
 
 static thread_local char g_err[1024];
+bool ptb_pdl_enabled() {
+    static const bool on = [] { const char* e = getenv("PTB_PDL"); return !(e && e[0] == '0'); }();
+    return on;
+}
+
 void ptb_set_error(const char* fmt, ...) {
     va_list ap;
     va_start(ap, fmt);

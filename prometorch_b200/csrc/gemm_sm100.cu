@@ -56,7 +56,7 @@ static int launch(const Operand& ta, const Operand& tb, const Params& p, int n_s
     // the stagers and the tile CTAs wait on one another, so the whole grid must be resident at once: one CTA per SM
     const int gemm_ctas = std::max(1, std::min(p.tiles_m * p.tiles_n * std::max(1, p.splits), n_sm - n_st));
     q.stager_ctas = n_st;
-    kern<<<gemm_ctas + n_st, THREADS, smem, st>>>(ta, tb, q);
+    PTB_CUDA_OK(ptb_launch(kern, dim3(gemm_ctas + n_st), dim3(THREADS), (size_t)smem, st, q.pdl != 0, ta, tb, q));
     PTB_CUDA_OK(cudaGetLastError());
     return 0;
 }
@@ -107,7 +107,7 @@ static void fill_staging(Staging& S, const PtbStaging* h) {
 
 // General entry point.  a_ptrs/b_ptrs: arrays of a_shards/b_shards device pointers.  c_peers (EPI_SCATTER_ADD):
 // `c_shards` fp32 buffers [out_shard_rows, ldc], one per rank.
-struct SplitK { int splits; long long stride; int bn; };      // splits > 1: fp32 partials at C + s*stride; bn: 0 or a forced tile width
+struct SplitK { int splits; long long stride; int bn; int pdl; };      // splits > 1: fp32 partials at C + s*stride; bn: 0 or a forced tile width
 
 static int gemm_core(void* const* a_ptrs, int a_shards, int a_shard_rows, long long lda, int a_mn, void* const* b_ptrs,
                      int b_shards, int b_shard_rows, long long ldb, int b_mn, void* C, long long ldc, void* const* c_peers,
@@ -134,6 +134,8 @@ static int gemm_core(void* const* a_ptrs, int a_shards, int a_shard_rows, long l
         }
         for (int r = 0; r < c_shards; ++r) p.c_peer[r] = (float*)c_peers[r];
         p.out_shard_rows = out_shard_rows;
+    } else if (flags & EPI_TRANS) {
+        if (!(flags & EPI_OUT_F32) || ((uintptr_t)C & 3)) { ptb_set_error("gemm: transposed output is fp32"); return -1; }
     } else {
         const int out_elem = (flags & EPI_OUT_F32) ? 4 : 2;
         if (((uintptr_t)C & 15) || ((ldc * out_elem) & 15)) { ptb_set_error("gemm: C needs a 16-byte aligned base and row pitch"); return -1; }
@@ -156,6 +158,7 @@ static int gemm_core(void* const* a_ptrs, int a_shards, int a_shard_rows, long l
     p.kb_per_split = (kblocks + p.splits - 1) / p.splits;
     p.splits = (kblocks + p.kb_per_split - 1) / p.kb_per_split;          // no empty split
     p.split_stride = sk.stride;
+    p.pdl = sk.pdl;
     fill_staging(p.stA, stage_a);
     fill_staging(p.stB, stage_b);
     // stager CTAs are needed unless every staged operand is filled by an external copier
@@ -170,6 +173,10 @@ static int gemm_core(void* const* a_ptrs, int a_shards, int a_shard_rows, long l
     p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.bias = bias; p.flags = flags; p.status = status;
     p.tiles_m = (M + BM - 1) / BM;
     p.tiles_n = (N + BN - 1) / BN;
+    if (BN == 32 || BN == 64) {
+        if (a_mn || b_mn || p.stA.seq || p.stB.seq) { ptb_set_error("gemm: narrow tiles take K-major, unstaged operands"); return -1; }
+        return BN == 32 ? launch<32, 10, false, false>(oa, ob, p, n_sm, st) : launch<64, 8, false, false>(oa, ob, p, n_sm, st);
+    }
     if (BN == 256) return launch_majors<256, 4>(a_mn, b_mn, oa, ob, p, n_sm, st);
     return launch_majors<128, 6>(a_mn, b_mn, oa, ob, p, n_sm, st);
 }
@@ -179,13 +186,15 @@ PTB_API int ptb_gemm_bf16_ex(void* const* a_ptrs, int a_shards, int a_shard_rows
                              int c_shards, int out_shard_rows, int M, int N, int K, const float* bias, int flags, int* status,
                              int n_sm, cudaStream_t st, const PtbStaging* stage_a, const PtbStaging* stage_b) {
     return gemm_core(a_ptrs, a_shards, a_shard_rows, lda, a_mn, b_ptrs, b_shards, b_shard_rows, ldb, b_mn, C, ldc, c_peers, c_shards,
-                     out_shard_rows, M, N, K, bias, flags, status, n_sm, st, stage_a, stage_b, SplitK{1, 0, 0});
+                     out_shard_rows, M, N, K, bias, flags, status, n_sm, st, stage_a, stage_b, SplitK{1, 0, 0, 0});
 }
 
 // Sum the split-K partials, add the bias, apply GELU, round to bf16.  work: [splits][M][N] fp32; N a multiple of 4.
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ work, int splits, long long mn, int N,
                                                             const float* __restrict__ bias, int gelu, __nv_bfloat16* __restrict__ C,
                                                             long long ldc) {
+    pdl_wait();
+    pdl_launch_dependents();
     const long long i4 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (i4 >= mn) return;
     float4 acc = *reinterpret_cast<const float4*>(work + i4);
@@ -214,6 +223,8 @@ __global__ void __launch_bounds__(SKN_THREADS) splitk_reduce_norm_kernel(const f
                                                                          const __nv_bfloat16* __restrict__ w, float eps,
                                                                          __nv_bfloat16* __restrict__ y) {
     __shared__ float red[32];
+    pdl_wait();
+    pdl_launch_dependents();
     const size_t row = blockIdx.x;
     const int nc = N / 4;
     float4 h[SKN_MAXC];
@@ -259,6 +270,8 @@ __global__ void __launch_bounds__(SKN_THREADS) splitk_reduce_norm_kernel(const f
 // out[row][c] = act(sum_s gate) * (sum_s up) for the packed projection [M, 2 I] (gate columns first).
 __global__ void __launch_bounds__(256) splitk_reduce_gated_kernel(const float* __restrict__ work, int splits, long long mn, int I, int gelu,
                                                                   long long total4, __nv_bfloat16* __restrict__ out) {
+    pdl_wait();
+    pdl_launch_dependents();
     const long long i4 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i4 >= total4) return;
     const long long row = (i4 * 4) / I;
@@ -276,35 +289,42 @@ __global__ void __launch_bounds__(256) splitk_reduce_gated_kernel(const float* _
     o[1] = __floats2bfloat162_rn(act(g.z) * u.z, act(g.w) * u.w);
 }
 
-// Tile width and K-split count for a skinny GEMM (one row of tiles).  The CTAs are persistent and their TMA producers
-// run ahead across work items, so the makespan is about (items per SM) x (k-blocks per item) x (time per k-block) plus one
-// fixed cost and, with splits, the reduce launch.  A 256-wide tile moves twice the bytes per k-block at ~1.3x the time.
-// Returns splits | (BN == 256 ? 0x100 : 0).
+// Shape of a skinny GEMM (M <= 128 rows of activations).  Returns 0 when the ordinary path should run, else
+// splits | mode << 8 with mode 0: 128-wide tiles, 1: 256-wide tiles, 2: swapped operands.
+//   swapped (M <= 64): the weight is the 128-row operand and the tokens are a 32- or 64-column tile, so a k-block moves
+//   16 KB of weights and 4-8 KB of activations, ten stages keep ~160 KB of weights in flight per SM and the tensor
+//   pipe does 128 x 32 x 64 instead of 128 x 128 x 64 per k-block; the result always goes through the reduce launch.
+// The CTAs are persistent and their TMA producers run ahead across work items, so the makespan is about
+// (items per SM) x (k-blocks per item x time per k-block + a partly hidden epilogue) + a fixed cost + the reduce pass.
 static int pick_skinny(int M, int N, int K, int n_sm) {
-    if (M > BM || n_sm <= 0) return 1;
+    if (M > BM || n_sm <= 0) return 0;
     const int kblocks = (K + BK - 1) / BK;
-    int best = 1;
+    int best = 0;
     double best_cost = 1e30;
-    for (int wide = 0; wide < 2; ++wide) {
-        if (wide && N <= 128) continue;
-        const int bn = wide ? 256 : 128, tiles = (N + bn - 1) / bn;
-        const double t_kb = wide ? 0.33 : 0.25;
+    for (int mode = 0; mode < 3; ++mode) {
+        if (mode == 1 && N <= 128) continue;
+        if (mode == 2 && M > 64) continue;
+        if (mode != 2 && M <= 64) continue;
+        const int bn = mode == 1 ? 256 : 128, tiles = (N + bn - 1) / bn;
+        const double t_kb = mode == 2 ? 0.15 : mode == 1 ? 0.33 : 0.25;
         for (int s = 1; s <= 16 && s <= kblocks; ++s) {
             const int kbps = (kblocks + s - 1) / s, items = tiles * ((kblocks + kbps - 1) / kbps);
             const int per_sm = (items + n_sm - 1) / n_sm;
-            // per item: its k-blocks plus an epilogue that is only partly hidden; the reduce pass reads every partial
-            const double cost = per_sm * (kbps * t_kb + 0.4) + 3.0 + (s > 1 ? 2.5 + (double)s * M * N * 4.0 / 4.0e6 : 0.0);
-            if (cost < best_cost - 1e-9) { best_cost = cost; best = s | (wide ? 0x100 : 0); }
+            const bool reduce = s > 1 || mode == 2;
+            const double cost = per_sm * (kbps * t_kb + 0.4) + 3.0 + (reduce ? 2.5 + (double)s * M * N * 4.0 / 4.0e6 : 0.0);
+            if (cost < best_cost - 1e-9) { best_cost = cost; best = s | (mode << 8); }
         }
     }
+    if ((best >> 8) != 2 && (best & 0xff) == 1) return 0;          // one split, ordinary tiles: nothing to reduce
     return best;
 }
 
+// 0: use the ordinary GEMM; otherwise the split count of the skinny path (1 or more; its result needs the reduce launch).
 PTB_API int ptb_gemm_pick_splits(int M, int N, int K, int n_sm) { return pick_skinny(M, N, K, n_sm) & 0xff; }
 
 static int skinny_partials(const void* A, long long lda, const void* B, long long ldb, int M, int N, int K, int splits, float* work,
                            int* status, int n_sm, cudaStream_t st, int* real_splits) {
-    if (M > BM || (N & 3) || splits < 2 || !work) { ptb_set_error("gemm split-K: needs M <= %d, N %% 4 == 0, splits >= 2 and a workspace", BM); return -1; }
+    if (M > BM || (N & 3) || splits < 1 || !work) { ptb_set_error("gemm split-K: needs M <= %d, N %% 4 == 0, splits >= 1 and a workspace", BM); return -1; }
     void* ap[1] = {const_cast<void*>(A)};
     void* bp[1] = {const_cast<void*>(B)};
     {
@@ -313,10 +333,18 @@ static int skinny_partials(const void* A, long long lda, const void* B, long lon
         if (n_sm <= 0) PTB_CUDA_OK(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
     }
     const int choice = pick_skinny(M, N, K, n_sm);
-    const int bn = ((choice >> 8) && (choice & 0xff) == splits) ? 256 : 128;       // the wide tile only for the split count it was chosen with
-    if (gemm_core(ap, 1, 0, lda, 0, bp, 1, 0, ldb, 0, work, N, nullptr, 0, 0, M, N, K, nullptr, EPI_OUT_F32, status, n_sm, st, nullptr, nullptr,
-                  SplitK{splits, (long long)M * N, bn}))
-        return -1;
+    const int mode = M <= 64 ? 2 : (((choice >> 8) == 1 && (choice & 0xff) == splits) ? 1 : 0);
+    int rc;
+    if (mode == 2) {
+        // swapped: "A" = the weight [N, K] (rows = output features), "B" = the activations [M, K]; partials are stored
+        // transposed, i.e. as [splits][M][N] like the other modes
+        rc = gemm_core(bp, 1, 0, ldb, 0, ap, 1, 0, lda, 0, work, N, nullptr, 0, 0, N, M, K, nullptr, EPI_OUT_F32 | EPI_TRANS, status, n_sm, st,
+                       nullptr, nullptr, SplitK{splits, (long long)M * N, M <= 32 ? 32 : 64, ptb_pdl_enabled() ? 1 : 0});
+    } else {
+        rc = gemm_core(ap, 1, 0, lda, 0, bp, 1, 0, ldb, 0, work, N, nullptr, 0, 0, M, N, K, nullptr, EPI_OUT_F32, status, n_sm, st, nullptr, nullptr,
+                       SplitK{splits, (long long)M * N, mode == 1 ? 256 : 128, ptb_pdl_enabled() ? 1 : 0});
+    }
+    if (rc) return -1;
     const int kblocks = (K + BK - 1) / BK, kbps = (kblocks + splits - 1) / splits;
     *real_splits = (kblocks + kbps - 1) / kbps;
     return 0;
@@ -330,7 +358,8 @@ PTB_API int ptb_gemm_bf16_splitk(const void* A, long long lda, const void* B, lo
     int real = 0;
     if (skinny_partials(A, lda, B, ldb, M, N, K, splits, work, status, n_sm, st, &real)) return -1;
     const long long mn = (long long)M * N;
-    splitk_reduce_kernel<<<(unsigned)((mn / 4 + 255) / 256), 256, 0, st>>>(work, real, mn, N, bias, gelu, (__nv_bfloat16*)C, ldc);
+    PTB_CUDA_OK(ptb_launch(splitk_reduce_kernel, dim3((unsigned)((mn / 4 + 255) / 256)), dim3(256), 0, st, ptb_pdl_enabled(), work, real, mn, N, bias,
+                           gelu, (__nv_bfloat16*)C, ldc));
     PTB_CUDA_OK(cudaGetLastError());
     return 0;
 }
@@ -344,8 +373,8 @@ PTB_API int ptb_gemm_bf16_splitk_add_norm(const void* A, long long lda, const vo
     if (N > 4 * SKN_THREADS * SKN_MAXC) { ptb_set_error("gemm split-K + norm: N %d above %d", N, 4 * SKN_THREADS * SKN_MAXC); return -1; }
     int real = 0;
     if (skinny_partials(A, lda, B, ldb, M, N, K, splits, work, status, n_sm, st, &real)) return -1;
-    splitk_reduce_norm_kernel<<<M, SKN_THREADS, 0, st>>>(work, real, (long long)M * N, N, (const __nv_bfloat16*)resid_in, (__nv_bfloat16*)resid_out,
-                                                         (const __nv_bfloat16*)norm_w, eps, (__nv_bfloat16*)y);
+    PTB_CUDA_OK(ptb_launch(splitk_reduce_norm_kernel, dim3(M), dim3(SKN_THREADS), 0, st, ptb_pdl_enabled(), work, real, (long long)M * N, N,
+                           (const __nv_bfloat16*)resid_in, (__nv_bfloat16*)resid_out, (const __nv_bfloat16*)norm_w, eps, (__nv_bfloat16*)y));
     PTB_CUDA_OK(cudaGetLastError());
     return 0;
 }
@@ -358,7 +387,8 @@ PTB_API int ptb_gemm_bf16_splitk_gated(const void* A, long long lda, const void*
     int real = 0;
     if (skinny_partials(A, lda, B, ldb, M, N, K, splits, work, status, n_sm, st, &real)) return -1;
     const long long total4 = (long long)M * (N / 2) / 4;
-    splitk_reduce_gated_kernel<<<(unsigned)((total4 + 255) / 256), 256, 0, st>>>(work, real, (long long)M * N, N / 2, gelu, total4, (__nv_bfloat16*)out);
+    PTB_CUDA_OK(ptb_launch(splitk_reduce_gated_kernel, dim3((unsigned)((total4 + 255) / 256)), dim3(256), 0, st, ptb_pdl_enabled(), work, real,
+                           (long long)M * N, N / 2, gelu, total4, (__nv_bfloat16*)out));
     PTB_CUDA_OK(cudaGetLastError());
     return 0;
 }

@@ -26,7 +26,8 @@ constexpr int TMEM_COLS = 512;
 
 constexpr int MAX_SHARDS = 8;
 
-enum EpiFlags : int { EPI_BIAS = 1, EPI_ACCUM = 2, EPI_OUT_F32 = 4, EPI_GELU = 8, EPI_SCATTER_ADD = 16, EPI_SCATTER_STORE = 32 };
+enum EpiFlags : int { EPI_BIAS = 1, EPI_ACCUM = 2, EPI_OUT_F32 = 4, EPI_GELU = 8, EPI_SCATTER_ADD = 16, EPI_SCATTER_STORE = 32,
+                      EPI_TRANS = 64 };   // EPI_TRANS: element (row, col) is stored at C[col * ldc + row] (fp32 only)
 
 // An operand whose stored matrix is split by rows over up to eight GPUs (each piece in that GPU's
 // memory, mapped here): piece r holds stored rows [r*shard_rows, (r+1)*shard_rows).  The producer warp
@@ -74,6 +75,7 @@ struct Params {
     // [s*kb_per_split, (s+1)*kb_per_split) and stores its fp32 partial at C + s*split_stride; the caller sums them
     int splits, kb_per_split;
     long long split_stride;
+    int pdl;                // launched with programmatic stream serialization: the producer waits for the previous kernel
     Staging stA, stB;
 };
 
@@ -260,14 +262,17 @@ gemm_bf16_kernel(const __grid_constant__ Operand opA, const __grid_constant__ Op
         prefetch_tmap(&opA.map[0]);
         prefetch_tmap(&opB.map[0]);
     }
+    if (P.pdl) pdl_launch_dependents();           // the next kernel may set itself up; it waits for this grid to finish
     const int n_gemm = (int)gridDim.x - P.stager_ctas;
     const int cta = (int)blockIdx.x - P.stager_ctas;
     if (cta < 0) {
         // ---------------------------------------------------------------------- stager CTA (no TMEM, no tiles)
         __syncthreads();                      // the pipeline barriers are initialised
-        uint32_t uses = 0;
-        run_stager<STAGES, S::STAGE_BYTES>(P.stA, blockIdx.x, P.stager_ctas, smem, full, uses, P.status);
-        run_stager<STAGES, S::STAGE_BYTES>(P.stB, blockIdx.x, P.stager_ctas, smem, full, uses, P.status);
+        if constexpr (S::STAGE_BYTES >= 32768) {          // narrow-tile instantiations are never launched with stagers
+            uint32_t uses = 0;
+            run_stager<STAGES, S::STAGE_BYTES>(P.stA, blockIdx.x, P.stager_ctas, smem, full, uses, P.status);
+            run_stager<STAGES, S::STAGE_BYTES>(P.stB, blockIdx.x, P.stager_ctas, smem, full, uses, P.status);
+        }
         return;
     }
     if (warp == 1) {
@@ -287,6 +292,7 @@ gemm_bf16_kernel(const __grid_constant__ Operand opA, const __grid_constant__ Op
             // an MN-major staged operand is walked along K in full by every tile: once the first tile has
             // seen all of its blocks staged, later tiles need not look at the flags again
             bool first_tile = true;
+            if (P.pdl) pdl_wait();                // nothing of this kernel touched global memory before this point
             for (int t = cta; t < num_tiles && ok; t += n_gemm, first_tile = false) {
                 const int tt = t % tiles_mn, sp = t / tiles_mn;
                 const int m0 = (tt % P.tiles_m) * BM, n0 = (tt / P.tiles_m) * BN;
@@ -385,7 +391,14 @@ gemm_bf16_kernel(const __grid_constant__ Operand opA, const __grid_constant__ Op
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
                     }
-                    if (P.flags & EPI_SCATTER_ADD) {
+                    if (P.flags & EPI_TRANS) {
+                        // swapped operands (rows = output features, columns = tokens): a warp's 32 lanes hold 32
+                        // consecutive features of one token, so each store instruction writes 128 contiguous bytes
+                        float* cp = reinterpret_cast<float*>(P.C) + (size_t)sp * P.split_stride + (size_t)col * P.ldc + row;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col + j < P.N) cp[(size_t)j * P.ldc] = v[j];
+                    } else if (P.flags & EPI_SCATTER_ADD) {
                         const int owner = row / P.out_shard_rows;
                         float* cp = P.c_peer[owner] + (size_t)(row - owner * P.out_shard_rows) * P.ldc + col;
                         for (int j = 0; j < 32 && col + j < P.N; ++j) atomicAdd(cp + j, v[j]);

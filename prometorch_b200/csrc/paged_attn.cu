@@ -35,6 +35,8 @@ struct PagedWriteParams {
 
 // One CTA per token.  Rotation pairs are (j, j + D/2) within a head (the Hugging Face Llama convention).
 __global__ void __launch_bounds__(256) paged_rope_write_kernel(const __grid_constant__ PagedWriteParams P) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int i = blockIdx.x;
     const int half = P.D / 2;
     const int pos = P.pos[i];
@@ -99,6 +101,8 @@ __global__ void __launch_bounds__(PA_THREADS) paged_attn_decode_kernel(const __g
     __shared__ float ml_s[PA_WARPS][G][2];
     const int kvh = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_wait();
+    pdl_launch_dependents();
     for (int e = threadIdx.x; e < G * D; e += PA_THREADS) {
         const int g = e / D, d = e % D;
         q_s[g][d] = __bfloat162float(P.q[(size_t)b * P.q_stride + (size_t)(kvh * G + g) * D + d]) * P.scale_log2;
@@ -229,6 +233,8 @@ __global__ void __launch_bounds__(PA_THREADS) paged_attn_decode_kernel(const __g
 
 // Combine the splits of one (request, head): grid (H, B), D threads.
 __global__ void paged_attn_merge_kernel(const float* __restrict__ work, __nv_bfloat16* __restrict__ out, int H, int D, int nsplit) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
     const float* wk = work + ((size_t)b * H + h) * nsplit * (D + 2);
     float M = -INFINITY;
@@ -246,13 +252,16 @@ __global__ void paged_attn_merge_kernel(const float* __restrict__ work, __nv_bfl
 template <int D>
 static int launch_decode(const PagedAttnParams& p, int G, cudaStream_t st) {
     dim3 grid(p.Hk, p.B, p.nsplit);
+    const bool pdl = ptb_pdl_enabled();
+    cudaError_t e;
     switch (G) {
-        case 1: paged_attn_decode_kernel<D, 1><<<grid, PA_THREADS, 0, st>>>(p); break;
-        case 2: paged_attn_decode_kernel<D, 2><<<grid, PA_THREADS, 0, st>>>(p); break;
-        case 4: paged_attn_decode_kernel<D, 4><<<grid, PA_THREADS, 0, st>>>(p); break;
-        case 8: paged_attn_decode_kernel<D, 8><<<grid, PA_THREADS, 0, st>>>(p); break;
+        case 1: e = ptb_launch(paged_attn_decode_kernel<D, 1>, grid, dim3(PA_THREADS), 0, st, pdl, p); break;
+        case 2: e = ptb_launch(paged_attn_decode_kernel<D, 2>, grid, dim3(PA_THREADS), 0, st, pdl, p); break;
+        case 4: e = ptb_launch(paged_attn_decode_kernel<D, 4>, grid, dim3(PA_THREADS), 0, st, pdl, p); break;
+        case 8: e = ptb_launch(paged_attn_decode_kernel<D, 8>, grid, dim3(PA_THREADS), 0, st, pdl, p); break;
         default: ptb_set_error("paged attention: group size %d not in {1, 2, 4, 8}", G); return -1;
     }
+    PTB_CUDA_OK(e);
     return 0;
 }
 
@@ -271,7 +280,7 @@ PTB_API int ptb_paged_rope_write(void* qkv, int n, int H, int Hk, int D, const i
     p.qkv = (__nv_bfloat16*)qkv; p.pos = pos; p.req = req; p.page_table = page_table; p.pt_stride = pt_stride; p.n_pages = n_pages;
     p.cos = cos; p.sin = sin; p.k_pages = (__nv_bfloat16*)k_pages; p.v_pages = (__nv_bfloat16*)v_pages; p.k_out = (__nv_bfloat16*)k_out;
     p.n = n; p.H = H; p.Hk = Hk; p.D = D; p.max_pos = max_pos; p.status = status;
-    paged_rope_write_kernel<<<n, 256, 0, st>>>(p);
+    PTB_CUDA_OK(ptb_launch(paged_rope_write_kernel, dim3(n), dim3(256), 0, st, ptb_pdl_enabled(), p));
     PTB_CUDA_OK(cudaGetLastError());
     return 0;
 }
@@ -295,7 +304,8 @@ PTB_API int ptb_paged_attn_decode(const void* q, long long q_stride, void* out, 
     else if (D == 64) rc = launch_decode<64>(p, H / Hk, st);
     else { ptb_set_error("paged attention: head size %d not in {64, 128}", D); return -1; }
     if (rc) return rc;
-    if (nsplit > 1) paged_attn_merge_kernel<<<dim3(H, B), D, 0, st>>>(work, (__nv_bfloat16*)out, H, D, nsplit);
+    if (nsplit > 1)
+        PTB_CUDA_OK(ptb_launch(paged_attn_merge_kernel, dim3(H, B), dim3(D), 0, st, ptb_pdl_enabled(), (const float*)work, (__nv_bfloat16*)out, H, D, nsplit));
     PTB_CUDA_OK(cudaGetLastError());
     return 0;
 }

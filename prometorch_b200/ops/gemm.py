@@ -86,9 +86,9 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: boo
             raise ValueError("accumulate needs an output tensor")
         out = torch.empty(M, Nn, dtype=out_dtype, device=a.device)
     if M <= 128 and not (a_mn or b_mn or accumulate) and out.dtype == torch.bfloat16 and Nn % 4 == 0 and _SPLITK:
-        # skinny M (decode batches): one row of tiles cannot fill the machine, so K is split over the idle SMs
-        splits = N.lib().ptb_gemm_pick_splits(M, Nn, K, _sms(a.device))
-        if splits > 1:
+        # skinny M (decode batches): swapped operands with a narrow token tile and / or K split over the idle SMs
+        splits = N.lib().ptb_gemm_pick_splits(M, Nn, K, _sms(a.device))         # 0: the ordinary kernel is the better choice
+        if splits > 0:
             work = torch.empty(splits * M * Nn, dtype=torch.float32, device=a.device)
             st = torch.cuda.current_stream(a.device).cuda_stream
             N.check(N.lib().ptb_gemm_bf16_splitk(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), out.data_ptr(), out.stride(0), M, Nn,
@@ -146,8 +146,7 @@ def _skinny_splits(x: torch.Tensor, w: torch.Tensor) -> int:
             and x.stride(1) == 1 and w.stride(1) == 1 and x.shape[1] % 8 == 0 and w.shape[0] % 8 == 0
             and hasattr(N.lib(), "ptb_gemm_bf16_splitk_add_norm")):
         return 0
-    s = N.lib().ptb_gemm_pick_splits(x.shape[0], w.shape[0], x.shape[1], _sms(x.device))
-    return s if s > 1 else 0
+    return N.lib().ptb_gemm_pick_splits(x.shape[0], w.shape[0], x.shape[1], _sms(x.device))
 
 
 def linear_add_rms_norm(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor, norm_w: torch.Tensor, eps: float):
