@@ -364,6 +364,16 @@ PTB_API int ptb_gemm_bf16_splitk(const void* A, long long lda, const void* B, lo
     return 0;
 }
 
+// Only the partials: work [splits'][M][N] fp32, where splits' (returned, >= 1) is the number of splits that really ran.
+// The caller's next kernel sums them (e.g. ptb_paged_rope_write_partials).  Returns -1 on error.
+PTB_API int ptb_gemm_bf16_splitk_partials(const void* A, long long lda, const void* B, long long ldb, int M, int N, int K, int splits,
+                                          float* work, int* status, int n_sm, cudaStream_t st) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    int real = 0;
+    if (skinny_partials(A, lda, B, ldb, M, N, K, splits, work, status, n_sm, st, &real)) return -1;
+    return real;
+}
+
 // The same product followed, in the reduce launch, by `resid_out = P + resid_in` and `y = rmsnorm(resid_out) * norm_w`
 // (all bf16, [M, N] contiguous; N <= 8192).
 PTB_API int ptb_gemm_bf16_splitk_add_norm(const void* A, long long lda, const void* B, long long ldb, int M, int N, int K, int splits,

@@ -31,7 +31,22 @@ struct PagedWriteParams {
     __nv_bfloat16* k_out;          // optional [n, Hk, D]: the rotated keys, contiguous (prompt pass)
     int n, H, Hk, D, max_pos;
     int* status;
+    // when `work` is set the projection arrives as split-K partials [splits][n][(H + 2 Hk) D] fp32 (qkv is unused) and
+    // the rotated q goes to q_out [n, H D] bf16
+    const float* work;
+    int splits;
+    long long split_stride;
+    __nv_bfloat16* q_out;
 };
+
+// Element `e` of token `i`'s projection row: from the bf16 row, or the sum of the split-K partials.
+__device__ __forceinline__ float proj_elem(const PagedWriteParams& P, const __nv_bfloat16* row, size_t i, int e, int width) {
+    if (!P.work) return __bfloat162float(row[e]);
+    const float* w = P.work + i * width + e;
+    float a = w[0];
+    for (int s = 1; s < P.splits; ++s) a += w[(size_t)s * P.split_stride];
+    return a;
+}
 
 // One CTA per token.  Rotation pairs are (j, j + D/2) within a head (the Hugging Face Llama convention).
 __global__ void __launch_bounds__(256) paged_rope_write_kernel(const __grid_constant__ PagedWriteParams P) {
@@ -40,7 +55,8 @@ __global__ void __launch_bounds__(256) paged_rope_write_kernel(const __grid_cons
     const int i = blockIdx.x;
     const int half = P.D / 2;
     const int pos = P.pos[i];
-    __nv_bfloat16* row = P.qkv + (size_t)i * (P.H + 2 * P.Hk) * P.D;
+    const int width = (P.H + 2 * P.Hk) * P.D;
+    __nv_bfloat16* row = P.qkv ? P.qkv + (size_t)i * width : nullptr;
     const int page_slot = pos / PAGE, in_page = pos % PAGE;
     const int page = P.page_table[(size_t)P.req[i] * P.pt_stride + min(page_slot, P.pt_stride - 1)];
     const bool ok = pos >= 0 && pos < P.max_pos && page_slot < P.pt_stride && page >= 0 && page < P.n_pages;
@@ -53,11 +69,11 @@ __global__ void __launch_bounds__(256) paged_rope_write_kernel(const __grid_cons
     const int n_rot = (P.H + P.Hk) * half;
     for (int e = threadIdx.x; e < n_rot; e += blockDim.x) {
         const int h = e / half, j = e % half;
-        __nv_bfloat16* hp = row + (size_t)h * P.D;
-        const float a = __bfloat162float(hp[j]), b = __bfloat162float(hp[j + half]);
+        const float a = proj_elem(P, row, i, h * P.D + j, width), b = proj_elem(P, row, i, h * P.D + j + half, width);
         const float c = cs[j], s = sn[j];
         const __nv_bfloat16 ra = __float2bfloat16_rn(a * c - b * s), rb = __float2bfloat16_rn(b * c + a * s);
         if (h < P.H) {
+            __nv_bfloat16* hp = P.work ? P.q_out + ((size_t)i * P.H + h) * P.D : row + (size_t)h * P.D;
             hp[j] = ra; hp[j + half] = rb;
         } else {
             const int kh = h - P.H;
@@ -69,10 +85,11 @@ __global__ void __launch_bounds__(256) paged_rope_write_kernel(const __grid_cons
             }
         }
     }
-    const __nv_bfloat16* vrow = row + (size_t)(P.H + P.Hk) * P.D;
+    const int v0 = (P.H + P.Hk) * P.D;
     for (int e = threadIdx.x; e < P.Hk * P.D; e += blockDim.x) {
         const int kh = e / P.D, d = e % P.D;
-        P.v_pages[(((size_t)page * P.Hk + kh) * PAGE + in_page) * P.D + d] = vrow[e];
+        P.v_pages[(((size_t)page * P.Hk + kh) * PAGE + in_page) * P.D + d] =
+            P.work ? __float2bfloat16_rn(proj_elem(P, row, i, v0 + e, width)) : row[v0 + e];
     }
 }
 
@@ -271,18 +288,36 @@ using namespace ptb;
 
 // Rotate q and k of `n` new tokens, store k and v in their page slots.  qkv: [n, (H + 2 Hk) D] bf16 (q rotated in
 // place); pos / req: [n]; page_table: [requests, pt_stride]; cos / sin: [max_pos, D/2] fp32; k_out optional.
-PTB_API int ptb_paged_rope_write(void* qkv, int n, int H, int Hk, int D, const int* pos, const int* req, const int* page_table,
-                                 int pt_stride, int n_pages, const float* cos, const float* sin, int max_pos, void* k_pages,
-                                 void* v_pages, void* k_out, int* status, cudaStream_t st) {
+static int rope_write(void* qkv, const float* work, int splits, void* q_out, int n, int H, int Hk, int D, const int* pos, const int* req,
+                      const int* page_table, int pt_stride, int n_pages, const float* cos, const float* sin, int max_pos, void* k_pages,
+                      void* v_pages, void* k_out, int* status, cudaStream_t st) {
     if (n <= 0) return 0;
     if (D % 2) { ptb_set_error("paged_rope_write: odd head size"); return -1; }
     PagedWriteParams p;
+    p.work = work; p.splits = splits; p.split_stride = (long long)n * (H + 2 * Hk) * D; p.q_out = (__nv_bfloat16*)q_out;
     p.qkv = (__nv_bfloat16*)qkv; p.pos = pos; p.req = req; p.page_table = page_table; p.pt_stride = pt_stride; p.n_pages = n_pages;
     p.cos = cos; p.sin = sin; p.k_pages = (__nv_bfloat16*)k_pages; p.v_pages = (__nv_bfloat16*)v_pages; p.k_out = (__nv_bfloat16*)k_out;
     p.n = n; p.H = H; p.Hk = Hk; p.D = D; p.max_pos = max_pos; p.status = status;
     PTB_CUDA_OK(ptb_launch(paged_rope_write_kernel, dim3(n), dim3(256), 0, st, ptb_pdl_enabled(), p));
     PTB_CUDA_OK(cudaGetLastError());
     return 0;
+}
+
+PTB_API int ptb_paged_rope_write(void* qkv, int n, int H, int Hk, int D, const int* pos, const int* req, const int* page_table,
+                                 int pt_stride, int n_pages, const float* cos, const float* sin, int max_pos, void* k_pages,
+                                 void* v_pages, void* k_out, int* status, cudaStream_t st) {
+    return rope_write(qkv, nullptr, 0, nullptr, n, H, Hk, D, pos, req, page_table, pt_stride, n_pages, cos, sin, max_pos, k_pages, v_pages, k_out,
+                      status, st);
+}
+
+// The same, reading the projection as split-K partials `work` [splits][n][(H + 2 Hk) D] fp32 (what ptb_gemm_bf16_splitk_partials
+// leaves) and writing the rotated q to q_out [n, H D] bf16: the sum of the partials costs no launch of its own.
+PTB_API int ptb_paged_rope_write_partials(const float* work, int splits, void* q_out, int n, int H, int Hk, int D, const int* pos,
+                                          const int* req, const int* page_table, int pt_stride, int n_pages, const float* cos,
+                                          const float* sin, int max_pos, void* k_pages, void* v_pages, int* status, cudaStream_t st) {
+    if (!work || splits < 1 || !q_out) { ptb_set_error("paged_rope_write_partials: needs partials and an output for q"); return -1; }
+    return rope_write(nullptr, work, splits, q_out, n, H, Hk, D, pos, req, page_table, pt_stride, n_pages, cos, sin, max_pos, k_pages, v_pages,
+                      nullptr, status, st);
 }
 
 // Floats of workspace ptb_paged_attn_decode needs for `nsplit` > 1.

@@ -27,6 +27,11 @@ def _decls(L):
         L.ptb_paged_attn_decode.restype = ci
         L.ptb_paged_attn_work_floats.argtypes = [ci, ci, ci, ci]
         L.ptb_paged_attn_work_floats.restype = cll
+    if hasattr(L, "ptb_paged_rope_write_partials"):
+        L.ptb_paged_rope_write_partials.argtypes = [vp, ci, vp, ci, ci, ci, ci, vp, vp, vp, ci, ci, vp, vp, ci, vp, vp, vp, vp]
+        L.ptb_paged_rope_write_partials.restype = ci
+        L.ptb_gemm_bf16_splitk_partials.argtypes = [vp, cll, vp, cll, ci, ci, ci, ci, vp, vp, ci, vp]
+        L.ptb_gemm_bf16_splitk_partials.restype = ci
 
 
 _STATUS = {}
@@ -88,6 +93,33 @@ def paged_rope_write(qkv: torch.Tensor, H: int, Hk: int, D: int, pos: torch.Tens
     if want_k:
         k_out.copy_(rot[:, H:])
     return k_out
+
+
+def qkv_rope_write(h: torch.Tensor, wqkv: torch.Tensor, H: int, Hk: int, D: int, pos, req, page_table, cos, sin, k_pages, v_pages,
+                   fuse_sum: bool = False):
+    """``qkv = h Wqkv^T`` followed by :func:`paged_rope_write`; returns a tensor whose first ``H D`` columns are the rotated q.  For
+    decode-sized CUDA batches the projection stays as split-K partials and the rotary kernel sums them while it
+    reads (no reduce launch, no bf16 round trip of k and v) when ``fuse_sum`` is set.  That is off by default: the
+    rotary kernel is one CTA per token and sums the partials with scalar loads, and the decode pass of the 16-layer
+    2048-wide model measured 1.24 ms with it against 1.15 ms with the separate, vectorised reduce launch."""
+    from .gemm import _skinny_splits, _status as gemm_status, linear
+    splits = _skinny_splits(h, wqkv) if h.is_cuda else 0
+    if fuse_sum and splits and hasattr(N.lib(), "ptb_paged_rope_write_partials") and not torch.is_grad_enabled():
+        n, K, width = h.shape[0], h.shape[1], wqkv.shape[0]
+        work = torch.empty(splits * n * width, dtype=torch.float32, device=h.device)
+        q = torch.empty(n, H * D, dtype=torch.bfloat16, device=h.device)
+        st = torch.cuda.current_stream(h.device).cuda_stream
+        real = N.lib().ptb_gemm_bf16_splitk_partials(h.data_ptr(), h.stride(0), wqkv.data_ptr(), wqkv.stride(0), n, width, K, splits,
+                                                     work.data_ptr(), gemm_status(h.device).data_ptr(), 0, st)
+        N.check(min(real, 0), "gemm_bf16_splitk_partials")
+        N.check(N.lib().ptb_paged_rope_write_partials(work.data_ptr(), real, q.data_ptr(), n, H, Hk, D, pos.data_ptr(), req.data_ptr(),
+                                                      page_table.data_ptr(), page_table.stride(0), k_pages.shape[0], cos.data_ptr(),
+                                                      sin.data_ptr(), cos.shape[0], k_pages.data_ptr(), v_pages.data_ptr(),
+                                                      _status(h.device).data_ptr(), st), "paged_rope_write_partials")
+        return q
+    qkv = linear(h, wqkv) if h.is_cuda else torch.nn.functional.linear(h, wqkv)
+    paged_rope_write(qkv, H, Hk, D, pos, req, page_table, cos, sin, k_pages, v_pages)
+    return qkv
 
 
 def pick_splits(B: int, Hk: int, max_len: int, sms: int = 148) -> int:

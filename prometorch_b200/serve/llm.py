@@ -472,9 +472,8 @@ class LLMEngine:
         x = w.tok_emb[ids]
         h = self._norm(x, w.layers[0]["attn_norm"])
         for l, L in enumerate(w.layers):
-            qkv = self._linear(h, L["wqkv"])
-            P.paged_rope_write(qkv, H, Hk, Dh, pos, req, table, self.cos, self.sin, self.kv.k[l], self.kv.v[l])
-            a = P.paged_attention_decode(qkv, H, Hk, Dh, lens, table, self.kv.k[l], self.kv.v[l], nsplit=nsplit)
+            q = P.qkv_rope_write(h, L["wqkv"], H, Hk, Dh, pos, req, table, self.cos, self.sin, self.kv.k[l], self.kv.v[l])
+            a = P.paged_attention_decode(q, H, Hk, Dh, lens, table, self.kv.k[l], self.kv.v[l], nsplit=nsplit)
             h, x = linear_add_rms_norm(a, L["wo"], x, L["ffn_norm"], c.rms_norm_eps)
             nxt = w.layers[l + 1]["attn_norm"] if l + 1 < len(w.layers) else w.final_norm
             h, x = linear_add_rms_norm(linear_swiglu(h, L["w_gate_up"]), L["w_down"], x, nxt, c.rms_norm_eps)

@@ -125,3 +125,26 @@ def test_engine_logits_and_batching_match_cpu_engine():
             res.update({r.request_id: r.token_ids for r in e.poll_responses()})
         outs.append(res)
     assert outs[0] == outs[1] and len(outs[0]) == 3
+
+
+def test_qkv_projection_fused_with_rope_write():
+    """Split-K partials summed inside the rotary kernel give the same q and pages as projection + bf16 round trip."""
+    from prometorch_b200.ops import paged as P
+    dev = "cuda"
+    torch.manual_seed(5)
+    H, Hk, D, K, n = 16, 4, 128, 2048, 8
+    w = (torch.randn((H + 2 * Hk) * D, K, device=dev) * K ** -0.5).bfloat16()
+    h = torch.randn(n, K, device=dev).bfloat16()
+    cos, sin = P.rope_tables(512, D, 10000.0, dev)
+    pos = torch.tensor([0, 5, 63, 64, 100, 127, 128, 300], dtype=torch.int32, device=dev)
+    req = torch.arange(n, dtype=torch.int32, device=dev)
+    table = torch.arange(n * 8, dtype=torch.int32, device=dev).view(n, 8)
+    pools = [[torch.zeros(n * 8, Hk, P.PAGE, D, device=dev, dtype=torch.bfloat16) for _ in range(2)] for _ in range(2)]
+    with torch.no_grad():
+        q = P.qkv_rope_write(h, w, H, Hk, D, pos, req, table, cos, sin, pools[0][0], pools[0][1], fuse_sum=True)
+        qkv = (h.float() @ w.float().t()).bfloat16()
+        P.paged_rope_write(qkv, H, Hk, D, pos, req, table, cos, sin, pools[1][0], pools[1][1])
+    torch.cuda.synchronize()
+    P.check_status(dev)
+    assert q.shape == (n, H * D) and _rel(q, qkv[:, :H * D]) < 6e-3
+    assert _rel(pools[0][0], pools[1][0]) < 6e-3 and _rel(pools[0][1], pools[1][1]) < 6e-3
