@@ -11,6 +11,8 @@ from typing import Deque, Dict, List, Optional
 from . import llm
 from .llm import GenerationConfig, LlamaConfig, LlamaWeights, PagedKVCache, load_safetensors, save_safetensors
 from .llm import LLMEngine as PagedLLMEngine
+from .llm import EngineServer  # noqa: F401
+from .server import PagedBackend  # noqa: F401
 from .server import ApiHandlers, GGUFBackend, HttpServer, ModelBackend, PromeServe, ServerConfig, StreamWriter, VERSION
 
 

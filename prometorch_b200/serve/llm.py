@@ -21,7 +21,7 @@ import math
 import os
 import time
 from dataclasses import dataclass, field
-from typing import Deque, Dict, List, Optional, Sequence, Union
+from typing import Callable, Deque, Dict, List, Optional, Sequence, Union
 
 import torch
 import torch.nn.functional as F
@@ -46,6 +46,7 @@ class Request:
     request_id: int = 0
     prompt: Union[str, Sequence[int]] = ""
     config: GenerationConfig = field(default_factory=GenerationConfig)
+    on_token: Optional[Callable[[int], bool]] = None     # called with every generated id; returning False ends the request
 
 
 @dataclass
@@ -237,6 +238,7 @@ class RequestState:
     prefill_done: bool = False
     done: bool = False
     sampler: object = None
+    on_token: Optional[Callable[[int], bool]] = None
 
 
 class LLMEngine:
@@ -316,7 +318,8 @@ class LLMEngine:
         self._next_id = max(self._next_id, req.request_id + 1)
         limit = self.cfg.max_position_embeddings - 1
         ids = ids[-limit:] if len(ids) > limit else ids
-        self.pending.append(RequestState(req.request_id, req.config, list(ids), len(ids), time.perf_counter(), prompt_ids=list(ids)))
+        self.pending.append(RequestState(req.request_id, req.config, list(ids), len(ids), time.perf_counter(), prompt_ids=list(ids),
+                                         on_token=req.on_token))
         self._admit_pending()
 
     def poll_responses(self) -> List[Response]:
@@ -402,6 +405,8 @@ class LLMEngine:
         c = s.config
         if tok == self.cfg.eos_token_id or tok in c.stop_tokens or len(s.output_ids) >= c.max_new_tokens or \
                 s.kv_position + 1 >= self.cfg.max_position_embeddings:
+            s.done = True
+        if s.on_token is not None and not s.on_token(tok):
             s.done = True
 
     def _finish(self, s: RequestState) -> bool:
@@ -547,3 +552,90 @@ class LLMEngine:
                 out[i] = sample_logits(row, g.temperature, g.top_k, g.top_p, g.repetition_penalty,
                                        hist if g.repetition_penalty != 1.0 else None, generator=self._gen if not row.is_cuda else None)
         return [int(t) for t in out]
+
+
+class EngineServer:
+    """Runs an :class:`LLMEngine` on a thread of its own so that many callers (HTTP workers) share its decode batches:
+    ``submit`` is thread-safe and returns at once, the scheduler thread admits the request at the next step, calls its
+    ``on_token`` for every generated id and sets the returned handle's event when the request is finished."""
+
+    class Handle:
+        def __init__(self):
+            import threading
+            self.event = threading.Event()
+            self.response: Optional[Response] = None
+            self.t_submit = time.perf_counter()
+            self.t_first: Optional[float] = None
+
+        def wait(self, timeout: Optional[float] = None) -> Optional[Response]:
+            self.event.wait(timeout)
+            return self.response
+
+    def __init__(self, engine: LLMEngine):
+        import threading
+        self.engine = engine
+        self._cv = threading.Condition()
+        self._inbox: List[tuple] = []
+        self._handles: Dict[int, "EngineServer.Handle"] = {}
+        self._next = 0
+        self._stop = False
+        self.max_batch_seen = 0
+        self._thread = threading.Thread(target=self._run, name="llm-engine", daemon=True)
+        self._thread.start()
+
+    def submit(self, prompt, config: GenerationConfig, on_token: Optional[Callable[[int], bool]] = None) -> "EngineServer.Handle":
+        h = EngineServer.Handle()
+
+        def hook(tok: int) -> bool:
+            if h.t_first is None:
+                h.t_first = time.perf_counter()
+            return on_token(tok) if on_token is not None else True
+        with self._cv:
+            rid = self._next
+            self._next += 1
+            self._handles[rid] = h
+            self._inbox.append(Request(rid, prompt, config, hook))
+            self._cv.notify()
+        return h
+
+    def close(self):
+        with self._cv:
+            self._stop = True
+            self._cv.notify()
+        self._thread.join(10)
+
+    def _run(self):
+        eng = self.engine
+        if eng.device.type == "cuda":
+            torch.cuda.set_device(eng.device)
+        while True:
+            with self._cv:
+                while not self._stop and not self._inbox and eng.num_active() == 0:
+                    self._cv.wait()
+                if self._stop:
+                    return
+                inbox, self._inbox = self._inbox, []
+            for req in inbox:
+                try:
+                    eng.submit_request(req)
+                except Exception:                                    # a bad prompt ends that request, not the thread
+                    eng.done.append(Response(request_id=req.request_id))
+            if eng.num_active():
+                try:
+                    eng.step()
+                except Exception:
+                    for s in eng.active + list(eng.pending):          # fail what is in flight, keep serving
+                        eng.done.append(Response(request_id=s.request_id, token_ids=list(s.output_ids), tokens_generated=len(s.output_ids)))
+                    eng.active, eng.pending = [], collections.deque()
+                    eng.free_rows = list(range(eng.max_active))
+                    if eng.kv is not None:
+                        eng.kv.free_pages = collections.deque(range(eng.kv.max_pages))
+                if eng.launch_log:
+                    self.max_batch_seen = max(self.max_batch_seen, eng.launch_log[-1])
+                    del eng.launch_log[:-1]
+            for r in eng.poll_responses():
+                with self._cv:
+                    h = self._handles.pop(r.request_id, None)
+                if h is not None:
+                    h.response = r
+                    h.event.set()

@@ -137,6 +137,59 @@ class GGUFBackend(ModelBackend):
         return t1 - t0, time.perf_counter() - t1
 
 
+class PagedBackend(ModelBackend):
+    """A Hugging Face Llama directory served by the continuous-batching engine (``serve/llm.py``).  ``concurrent``:
+    the handlers do not serialise generations for this backend, so requests that arrive together share decode
+    batches (the reference's server takes one generation at a time, promeserve/api_handlers.h:769-790)."""
+    concurrent = True
+    architecture = "llama"
+
+    def __init__(self, model_dir: str, name: str, device: str = "cuda", max_active: int = 16, max_pages: int = 2048):
+        import os
+        from .llm import EngineServer, LLMEngine
+        dev = device if (device != "cuda" or __import__("torch").cuda.is_available()) else "cpu"
+        self.engine = LLMEngine(device=dev, max_pages=max_pages, max_active=max_active)
+        if not self.engine.load(model_dir) or not self.engine.loaded:
+            raise KeyError(f"'{model_dir}' is not a loadable Hugging Face Llama directory")
+        self.server = EngineServer(self.engine)
+        self.name, self.path, self.model_name = name, model_dir, os.path.basename(os.path.normpath(model_dir))
+        self.size = sum(os.path.getsize(os.path.join(model_dir, f)) for f in os.listdir(model_dir) if f.endswith(".safetensors"))
+        n = sum(t.numel() for L in self.engine.weights.layers for t in L.values()) + self.engine.weights.tok_emb.numel()
+        self.parameter_size = f"{n / 1e9:.1f}B"
+
+    def encode(self, text):
+        return self.engine._encode(text)
+
+    def decode_token(self, tid):
+        return self.engine.tokenizer.decode([tid])
+
+    def generate(self, prompt_ids, options, on_token):
+        from .llm import GenerationConfig
+        cfg = GenerationConfig(max_new_tokens=int(options.get("num_predict", 128)), temperature=float(options.get("temperature", 0.7)),
+                               top_k=int(options.get("top_k", 40)), top_p=float(options.get("top_p", 0.9)),
+                               repetition_penalty=float(options.get("repeat_penalty", 1.05)))
+        # the scheduler thread only queues the ids; this (HTTP worker) thread runs the caller's hook, so a slow
+        # client socket never stalls the decode batches of the other requests
+        import queue
+        q: "queue.Queue" = queue.Queue()
+        stop = {"flag": False}
+
+        def hook(tok: int) -> bool:
+            q.put(tok)
+            return not stop["flag"]
+        h = self.server.submit(list(prompt_ids), cfg, hook)
+        while not (h.event.is_set() and q.empty()):
+            try:
+                tok = q.get(timeout=0.05)
+            except queue.Empty:
+                continue
+            if not stop["flag"] and not on_token(tok):
+                stop["flag"] = True
+        t_end = time.perf_counter()
+        t_first = h.t_first if h.t_first is not None else t_end
+        return t_first - h.t_submit, t_end - t_first
+
+
 class ApiHandlers:
     def __init__(self, config: ServerConfig, backends: Optional[Dict[str, ModelBackend]] = None,
                  loader: Optional[Callable[[str], ModelBackend]] = None):
@@ -203,7 +256,8 @@ class ApiHandlers:
             pieces.append(piece)
             return emit(piece)
 
-        with self.generate_mutex:
+        import contextlib
+        with (contextlib.nullcontext() if getattr(backend, "concurrent", False) else self.generate_mutex):
             pe, ev = backend.generate(ids, options, on_token)
         stats = {"total_duration": int((pe + ev) * 1e9), "load_duration": 0, "prompt_eval_count": len(ids),
                  "prompt_eval_duration": int(pe * 1e9), "eval_count": state["n"], "eval_duration": int(ev * 1e9)}
@@ -427,6 +481,8 @@ class PromeServe:
         def loader(name: str) -> ModelBackend:
             from ..io.ollama import resolve_model
             import os
+            if os.path.isdir(name) and os.path.isfile(os.path.join(name, "config.json")):
+                return PagedBackend(name, name, self.config.device)      # a Hugging Face directory: the paged engine serves it
             path = name if os.path.isfile(name) else None
             if path is None:
                 for d in self.config.model_dirs:

@@ -109,3 +109,83 @@ def test_llm_engine_queue():
     assert eng.poll_responses() == {a: [ord(c) for c in "hel"]}
     assert eng.step() == 5 and list(eng.poll_responses()) == [b]
     assert eng.generate(["x", "y"], max_tokens=4) == ["hell", "hell"]
+
+
+def _tiny_hf_dir(tmp_path):
+    import json
+    import torch
+    from prometorch_b200.serve.llm import LlamaConfig, LlamaWeights, save_safetensors
+    cfg = LlamaConfig(vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, max_position_embeddings=256, eos_token_id=2)
+    w = LlamaWeights.random(cfg, seed=21)
+    d = tmp_path / "hf"
+    d.mkdir()
+    (d / "config.json").write_text(json.dumps({k: getattr(cfg, k) for k in cfg.__dataclass_fields__}))
+    save_safetensors(w.state_dict(), str(d / "model.safetensors"))
+    return str(d), w
+
+
+def test_engine_server_batches_concurrent_callers(tmp_path):
+    """Requests submitted from several threads share decode batches and each gets its own tokens."""
+    import threading
+    from prometorch_b200.serve.llm import EngineServer, GenerationConfig, LLMEngine
+    d, w = _tiny_hf_dir(tmp_path)
+    eng = LLMEngine(device="cpu", max_pages=32, max_active=4)
+    assert eng.load(d)
+    srv = EngineServer(eng)
+    greedy = dict(temperature=0.0, repetition_penalty=1.0, top_k=1)
+    prompts = [[1, 5 + i, 9, 40 + i] for i in range(4)]
+    seen = {i: [] for i in range(4)}
+    handles = {}
+    gate = threading.Barrier(4)
+
+    def client(i):
+        gate.wait()
+        handles[i] = srv.submit(prompts[i], GenerationConfig(max_new_tokens=12, **greedy), lambda t, i=i: seen[i].append(t) or True)
+    ts = [threading.Thread(target=client, args=(i,)) for i in range(4)]
+    for t in ts:
+        t.start()
+    for t in ts:
+        t.join()
+    for i in range(4):
+        r = handles[i].wait(60)
+        assert r is not None and r.token_ids == seen[i] and 1 <= len(seen[i]) <= 12
+    # one by one on a fresh engine: the same tokens
+    solo = LLMEngine(device="cpu", max_pages=32, max_active=1)
+    solo.load(d)
+    for i in range(4):
+        assert solo.generate(prompts[i], GenerationConfig(max_new_tokens=12, **greedy)).token_ids == seen[i]
+    assert srv.max_batch_seen >= 2
+    # a hook that says stop ends its request early
+    h = srv.submit(prompts[0], GenerationConfig(max_new_tokens=12, **greedy), lambda t: False)
+    assert len(h.wait(60).token_ids) == 1
+    srv.close()
+
+
+def test_rest_server_serves_hf_directory_concurrently(tmp_path):
+    import json
+    import threading
+    import urllib.request
+    from prometorch_b200.serve import PromeServe, ServerConfig
+    d, _ = _tiny_hf_dir(tmp_path)
+    srv = PromeServe(ServerConfig(port=0, device="cpu", worker_threads=4)).start()
+    try:
+        out = {}
+
+        def call(i):
+            body = json.dumps({"model": d, "prompt": f"hello {i}", "stream": False, "raw": True,
+                               "options": {"num_predict": 6, "temperature": 0.0, "repeat_penalty": 1.0, "top_k": 1}}).encode()
+            req = urllib.request.Request(f"http://127.0.0.1:{srv.port}/api/generate", data=body, headers={"Content-Type": "application/json"})
+            out[i] = json.loads(urllib.request.urlopen(req, timeout=60).read())
+        ts = [threading.Thread(target=call, args=(i,)) for i in range(3)]
+        for t in ts:
+            t.start()
+        for t in ts:
+            t.join()
+        assert all(out[i]["done"] and 1 <= out[i]["eval_count"] <= 6 and isinstance(out[i]["response"], str) for i in range(3))
+        show = json.loads(urllib.request.urlopen(urllib.request.Request(
+            f"http://127.0.0.1:{srv.port}/api/show", data=json.dumps({"model": d}).encode(), headers={"Content-Type": "application/json"}),
+            timeout=30).read())
+        assert show["details"]["family"] == "llama"
+    finally:
+        srv.stop()
