@@ -109,7 +109,7 @@ struct PagedAttnParams {
 };
 
 template <int D, int G>
-__global__ void __launch_bounds__(PA_THREADS) paged_attn_decode_kernel(const __grid_constant__ PagedAttnParams P) {
+__global__ void __launch_bounds__(PA_THREADS, (G <= 4 ? 8 : 6)) paged_attn_decode_kernel(const __grid_constant__ PagedAttnParams P) {
     constexpr int DV = D / 32;                        // output dims per lane (4 or 2)
     static_assert(DV == 4 || DV == 2, "head size 128 or 64");
     __shared__ float q_s[G][D];
@@ -188,30 +188,36 @@ __global__ void __launch_bounds__(PA_THREADS) paged_attn_decode_kernel(const __g
             for (int i = 0; i < DV; ++i) acc[g][i] *= corr;
         }
         __syncwarp();
-        // P V: each lane owns DV consecutive output dims.  Eight rows are fetched before they are used so that eight
-        // loads are in flight per lane; rows past `valid` belong to the page (readable) and carry p = 0.
-        for (int t0 = 0; t0 < valid; t0 += 8) {
-            float vf[8][DV];
+        // P V: each lane owns DV consecutive output dims.  Sixteen rows are fetched (kept packed) before they are used so
+        // that sixteen loads are in flight per lane; rows past `valid` belong to the page (readable) and carry p = 0.
+        constexpr int PF = 16;
+        for (int t0 = 0; t0 < valid; t0 += PF) {
+            if constexpr (DV == 4) {
+                uint2 raw[PF];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const __nv_bfloat16* vr = vb + (size_t)(t0 + u) * D + lane * DV;
-                if constexpr (DV == 4) {
-                    const uint2 raw = *reinterpret_cast<const uint2*>(vr);
-                    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+                for (int u = 0; u < PF; ++u) raw[u] = *reinterpret_cast<const uint2*>(vb + (size_t)(t0 + u) * D + lane * 4);
+#pragma unroll
+                for (int u = 0; u < PF; ++u) {
+                    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw[u]);
                     const float2 a = __bfloat1622float2(h2[0]), c = __bfloat1622float2(h2[1]);
-                    vf[u][0] = a.x; vf[u][1] = a.y; vf[u][2] = c.x; vf[u][3] = c.y;
-                } else {
-                    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(vr));
-                    vf[u][0] = a.x; vf[u][1] = a.y;
+#pragma unroll
+                    for (int g = 0; g < G; ++g) {
+                        const float p = p_s[warp][g][t0 + u];
+                        acc[g][0] += p * a.x; acc[g][1] += p * a.y; acc[g][2] += p * c.x; acc[g][3] += p * c.y;
+                    }
                 }
-            }
+            } else {
+                uint32_t raw[PF];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
+                for (int u = 0; u < PF; ++u) raw[u] = *reinterpret_cast<const uint32_t*>(vb + (size_t)(t0 + u) * D + lane * 2);
 #pragma unroll
-                for (int g = 0; g < G; ++g) {
-                    const float p = p_s[warp][g][t0 + u];
+                for (int u = 0; u < PF; ++u) {
+                    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw[u]));
 #pragma unroll
-                    for (int i = 0; i < DV; ++i) acc[g][i] += p * vf[u][i];
+                    for (int g = 0; g < G; ++g) {
+                        const float p = p_s[warp][g][t0 + u];
+                        acc[g][0] += p * a.x; acc[g][1] += p * a.y;
+                    }
                 }
             }
         }
