@@ -17,7 +17,6 @@ from __future__ import annotations
 
 import collections
 import json
-import math
 import os
 import time
 from dataclasses import dataclass, field

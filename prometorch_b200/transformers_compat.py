@@ -15,7 +15,6 @@ GELU), ``GPT2Model`` (pre-LN decoder, learned positions, ``Conv1D`` weights stor
 from __future__ import annotations
 
 import json
-import math
 import os
 from typing import Dict, List, Optional
 

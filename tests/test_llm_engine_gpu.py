@@ -148,3 +148,30 @@ def test_qkv_projection_fused_with_rope_write():
     P.check_status(dev)
     assert q.shape == (n, H * D) and _rel(q, qkv[:, :H * D]) < 6e-3
     assert _rel(pools[0][0], pools[1][0]) < 6e-3 and _rel(pools[0][1], pools[1][1]) < 6e-3
+
+
+def test_hf_compat_models_on_gpu_match_cpu():
+    """The Hugging Face shim's three architectures on CUDA bf16 (tcgen05 GEMM, FlashAttention, fused norms) vs CPU fp32."""
+    from prometorch_b200.transformers_compat import BertModel, GPT2Model, LlamaModel
+    torch.manual_seed(0)
+    cases = [
+        (LlamaModel, dict(vocab_size=512, hidden_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                          intermediate_size=512, rms_norm_eps=1e-5, rope_theta=10000.0)),
+        (GPT2Model, dict(vocab_size=512, n_embd=256, n_layer=2, n_head=4, n_positions=256)),
+        (BertModel, dict(vocab_size=512, hidden_size=256, num_hidden_layers=2, num_attention_heads=4, intermediate_size=512,
+                         max_position_embeddings=256)),
+    ]
+    ids = torch.randint(0, 512, (2, 136))
+    for cls, cfg in cases:
+        cpu = cls(cfg).eval()
+        with torch.no_grad():
+            for p in cpu.parameters():
+                if p.dim() > 1:
+                    p.normal_(0, 0.05)
+                p.copy_(p.bfloat16().float())                       # both sides hold bf16-representable weights
+            want = cpu(ids)
+            gpu = cls(cfg).eval()
+            gpu.load_state_dict(cpu.state_dict())
+            got = gpu.to(device="cuda", dtype=torch.bfloat16)(ids.cuda())
+        torch.cuda.synchronize()
+        assert got.shape == want.shape and _rel(got, want) < 4e-2, (cls.__name__, _rel(got, want))
