@@ -296,3 +296,29 @@ def test_ollama_resolution(tmp_path):
     assert "qwen3:4b" in names
     with pytest.raises(FileNotFoundError):
         ollama.resolve_model("nope:1b", str(root))
+
+
+def test_linear_scan_reference_and_gradients():
+    """h[t] = g[t] h[t-1] + x[t]: the op's CPU path against a closed form, and its autograd gradients against finite sums."""
+    import torch
+    from prometorch_b200.ops.scan import linear_scan, parallel_scan
+    torch.manual_seed(0)
+    g = torch.rand(2, 5, 3, dtype=torch.float64).requires_grad_()
+    x = torch.randn(2, 5, 3, dtype=torch.float64).requires_grad_()
+    h = linear_scan(g.float(), x.float())
+    want = torch.zeros(2, 5, 3)
+    for t in range(5):
+        for s in range(t + 1):
+            want[:, t] += x[:, s].float() * torch.prod(g[:, s + 1:t + 1].float(), dim=1)
+    assert torch.allclose(h, want, atol=1e-5) and parallel_scan is linear_scan
+    gf, xf = g.detach().float().requires_grad_(), x.detach().float().requires_grad_()
+    linear_scan(gf, xf).square().sum().backward()
+    # dx[t] = dh[t] + g[t+1] dx[t+1], dg[t] = dx[t] h[t-1]
+    dh = 2 * h.detach()
+    dx = torch.zeros_like(dh)
+    for t in reversed(range(5)):
+        dx[:, t] = dh[:, t] + (gf.detach()[:, t + 1] * dx[:, t + 1] if t + 1 < 5 else 0)
+    hprev = torch.cat([torch.zeros(2, 1, 3), h.detach()[:, :-1]], 1)
+    assert torch.allclose(xf.grad, dx, atol=1e-4) and torch.allclose(gf.grad, dx * hprev, atol=1e-4)
+    with pytest.raises(ValueError):
+        linear_scan(gf, xf[:, :4])
