@@ -189,3 +189,27 @@ def test_rest_server_serves_hf_directory_concurrently(tmp_path):
         assert show["details"]["family"] == "llama"
     finally:
         srv.stop()
+
+
+def test_engine_server_survives_a_failing_step(tmp_path):
+    """An exception inside a step ends the requests in flight with what they have and the thread keeps serving."""
+    from prometorch_b200.serve.llm import EngineServer, GenerationConfig, LLMEngine
+    d, _ = _tiny_hf_dir(tmp_path)
+    eng = LLMEngine(device="cpu", max_pages=16, max_active=2)
+    assert eng.load(d)
+    srv = EngineServer(eng)
+    greedy = dict(temperature=0.0, repetition_penalty=1.0, top_k=1)
+    real = eng._forward_decode
+    state = {"fail": True}
+
+    def flaky(batch):
+        if state["fail"]:
+            state["fail"] = False
+            raise RuntimeError("injected on the host")
+        return real(batch)
+    eng._forward_decode = flaky
+    r1 = srv.submit([1, 7, 8], GenerationConfig(max_new_tokens=6, **greedy)).wait(60)
+    assert r1 is not None and len(r1.token_ids) <= 6                 # ended early, not hung
+    r2 = srv.submit([1, 7, 8], GenerationConfig(max_new_tokens=6, **greedy)).wait(60)
+    assert r2 is not None and 1 <= len(r2.token_ids) <= 6 and eng.kv.pages_in_use == 0
+    srv.close()
