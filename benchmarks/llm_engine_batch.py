@@ -26,6 +26,8 @@ def main():
     ap.add_argument("--kv-heads", type=int, default=4)
     ap.add_argument("--inter", type=int, default=5632)
     ap.add_argument("--vocab", type=int, default=32000)
+    ap.add_argument("--spec", type=int, default=0, help="n-gram speculative decoding: ids proposed per greedy request and pass")
+    ap.add_argument("--repeat-prompt", type=int, default=0, help="build each prompt from a random piece of this length, repeated")
     a = ap.parse_args()
     cfg = LlamaConfig(vocab_size=a.vocab, hidden_size=a.hidden, intermediate_size=a.inter, num_hidden_layers=a.layers,
                       num_attention_heads=a.heads, num_key_value_heads=a.kv_heads, max_position_embeddings=a.prompt + a.new + 64,
@@ -35,13 +37,18 @@ def main():
     g = torch.Generator().manual_seed(0)
     for B in [int(x) for x in a.batches.split(",")]:
         pages = B * ((a.prompt + a.new) // 64 + 2)
-        eng = LLMEngine(device="cuda", max_pages=pages, max_active=B)
+        eng = LLMEngine(device="cuda", max_pages=pages, max_active=B, spec_tokens=a.spec)
         eng.set_weights(w)
         eng.generate(torch.randint(3, a.vocab, (16,), generator=g).tolist(), GenerationConfig(max_new_tokens=4, temperature=0.0,
                                                                                                repetition_penalty=1.0, top_k=1))
         for rep in range(2):                             # the first round captures the graphs; the second is timed
             for i in range(B):
-                eng.submit_request(Request(rep * B + i, torch.randint(3, a.vocab, (a.prompt,), generator=g).tolist(), greedy))
+                if a.repeat_prompt:
+                    piece = torch.randint(3, a.vocab, (a.repeat_prompt,), generator=g).tolist()
+                    prompt = (piece * (a.prompt // a.repeat_prompt + 1))[:a.prompt]
+                else:
+                    prompt = torch.randint(3, a.vocab, (a.prompt,), generator=g).tolist()
+                eng.submit_request(Request(rep * B + i, prompt, greedy))
             e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
             torch.cuda.synchronize()
             e0.record()
@@ -72,6 +79,7 @@ def main():
                           "prompt_tok_per_s": round(B * a.prompt / e0.elapsed_time(e1) * 1e3, 1),
                           "decode_ms_per_step": round(e1.elapsed_time(e2) / max(steps, 1), 3),
                           "decode_tok_per_s": round(toks / e1.elapsed_time(e2) * 1e3, 1), "graph_replay_ms": replay_ms,
+                          "spec_tokens": a.spec, "spec_accept_rate": round(eng.spec_accepted / max(eng.spec_drafted, 1), 3),
                           "model": f"llama {a.layers}L/{a.hidden}/{a.heads}h/{a.kv_heads}kv ffn{a.inter} bf16"}), flush=True)
         del eng
         torch.cuda.empty_cache()

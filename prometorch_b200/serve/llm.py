@@ -238,13 +238,17 @@ class RequestState:
     done: bool = False
     sampler: object = None
     on_token: Optional[Callable[[int], bool]] = None
+    ngram_hist: Optional[List[int]] = None               # speculative decoding: history and its n-gram index
+    ngram_index: Optional[Dict[tuple, int]] = None
+    ngram_done: int = 0
 
 
 class LLMEngine:
     """``submit_request`` queues a prompt, ``step`` advances every active request by one token (the prompt pass for
     new ones), ``poll_responses`` hands back what finished."""
 
-    def __init__(self, device=None, max_pages: int = 1024, max_active: int = 8, dtype=None, seed: int = 0, use_graphs: bool = True):
+    def __init__(self, device=None, max_pages: int = 1024, max_active: int = 8, dtype=None, seed: int = 0, use_graphs: bool = True,
+                 spec_tokens: int = 0):
         self.device = torch.device(device if device is not None else ("cuda" if torch.cuda.is_available() else "cpu"))
         self.dtype = dtype if dtype is not None else (torch.bfloat16 if self.device.type == "cuda" else torch.float32)
         self.max_pages, self.max_active = max_pages, max_active
@@ -262,6 +266,10 @@ class LLMEngine:
         self.launch_log: List[int] = []          # batch size of every decode pass (tests and metrics read it)
         self.use_graphs = use_graphs
         self._graphs: Dict[tuple, tuple] = {}
+        # speculative decoding for greedy requests: up to `spec_tokens` ids proposed by an n-gram look-up in the request's
+        # own history are verified in the same decode pass (one extra batch row per proposed id)
+        self.spec_tokens = spec_tokens
+        self.spec_drafted = self.spec_accepted = 0
 
     # -------------------------------------------------------------------------------------- loading
     def load(self, model_dir: str) -> bool:
@@ -351,7 +359,9 @@ class LLMEngine:
             s.prefill_done = True
             self._emit(s, self._sample([s], logits)[0])
         running = [s for s in running if self._ensure_pages(s, s.kv_position) or self._finish(s)]
-        if running:                                            # one batched decode pass for everyone else
+        if running and self.spec_tokens > 0:
+            self._step_speculative(running)
+        elif running:                                          # one batched decode pass for everyone else
             logits = self._forward_decode(running)
             for s, t in zip(running, self._sample(running, logits)):
                 s.kv_position += 1
@@ -359,6 +369,64 @@ class LLMEngine:
         self._collect_done()
         if self.device.type == "cuda":
             P.check_status(self.device)
+
+    # -------------------------------------------------------------------------------------- speculative decoding
+    def _draft(self, s: RequestState, k: int) -> List[int]:
+        """Prompt look-up: find the latest earlier occurrence of the last 3 (then 2, then 1) ids in the request's own
+        history and propose the ids that followed it (the reference drafts the same way on the CPU,
+        torch/io/speculative_draft.h).  The request keeps an index from n-gram to the position after its latest
+        occurrence, extended by the ids that arrived since the last call, so a look-up costs O(new ids)."""
+        hist = s.prompt_ids + s.output_ids if s.ngram_hist is None else s.ngram_hist
+        if s.ngram_hist is None:
+            s.ngram_hist, s.ngram_index, s.ngram_done = hist, {}, 0
+        else:
+            hist.extend(s.output_ids[len(hist) - len(s.prompt_ids):])
+        L = len(hist)
+        for q in range(s.ngram_done, L - 1):                  # n-grams that end before the last id
+            for n in (1, 2, 3):
+                if q + 1 >= n:
+                    s.ngram_index[tuple(hist[q + 1 - n:q + 1])] = q + 1
+        s.ngram_done = max(s.ngram_done, L - 1)
+        for n in (3, 2, 1):
+            if L > n:
+                at = s.ngram_index.get(tuple(hist[L - n:]))
+                if at is not None:
+                    return hist[at:at + k]
+        return []
+
+    def _step_speculative(self, running: List[RequestState]):
+        """One decode pass in which a greedy request contributes 1 + d rows: its last id and d proposed ids at the next
+        positions (row j attends to the cache up to its own position, so the rows are causal among themselves).  Row j
+        is valid when all proposals before it matched the model's own choice; the request advances by 1 + matches."""
+        rows, spans = [], []
+        for s in running:
+            greedy = s.config.temperature <= 0.0 and s.config.repetition_penalty == 1.0
+            draft = self._draft(s, self.spec_tokens) if greedy else []
+            room = min(s.config.max_new_tokens - len(s.output_ids) - 1, self.cfg.max_position_embeddings - 2 - s.kv_position)
+            draft = draft[:max(room, 0)]
+            while draft and not self._ensure_pages(s, s.kv_position + len(draft)):
+                draft.pop()
+            spans.append((s, len(rows), draft, greedy))
+            for j, t in enumerate([s.input_ids[-1]] + draft):
+                rows.append([t, s.kv_position + j, s.row, s.kv_position + j + 1])
+        self.launch_log.append(len(running))
+        logits = self._forward_rows(rows, min_rows=len(running) * (self.spec_tokens + 1))
+        choice = logits.argmax(-1).tolist()
+        for s, start, draft, greedy in spans:
+            if not greedy:
+                s.kv_position += 1
+                self._emit(s, self._sample([s], logits[start:start + 1])[0])
+                continue
+            j = 0
+            while True:
+                tok = int(choice[start + j])
+                s.kv_position += 1
+                self._emit(s, tok)
+                if s.done or j >= len(draft) or draft[j] != tok:
+                    break
+                j += 1
+            self.spec_drafted += len(draft)
+            self.spec_accepted += j
 
     # -------------------------------------------------------------------------------------- scheduling
     def _encode(self, prompt) -> List[int]:
@@ -486,10 +554,15 @@ class LLMEngine:
     def _forward_decode(self, batch: List[RequestState]) -> torch.Tensor:
         """One new token for every request of the batch; returns logits ``[B, V]``.  On a GPU the pass is a CUDA graph
         per (batch bucket, split count): the batch is padded to the bucket with rows that write to a spare page."""
+        self.launch_log.append(len(batch))
+        return self._forward_rows([[s.input_ids[-1], s.kv_position, s.row, s.kv_position + 1] for s in batch])
+
+    def _forward_rows(self, rows: List[List[int]], min_rows: int = 0) -> torch.Tensor:
+        """``rows``: [token id, position, page-table row, cached length] per batch row; returns logits ``[len(rows), V]``.
+        ``min_rows`` keeps the graph bucket stable when the row count varies from pass to pass (speculative decoding)."""
         dev = self.device
-        B = len(batch)
-        self.launch_log.append(B)
-        rows = [[s.input_ids[-1], s.kv_position, s.row, s.kv_position + 1] for s in batch]
+        B = len(rows)
+        rows = list(rows)
         max_len = max(r[3] for r in rows)
         Hk = self.cfg.num_key_value_heads
         if dev.type != "cuda" or not self.use_graphs:
@@ -497,7 +570,7 @@ class LLMEngine:
             meta = (meta.pin_memory() if dev.type == "cuda" else meta).to(dev, non_blocking=True)
             return self._decode_layers(meta, P.pick_splits(B, Hk, max_len))
         Bb = 1
-        while Bb < B:
+        while Bb < max(B, min_rows):
             Bb *= 2
         nsplit = P.pick_splits(Bb, Hk, max_len)
         rows += [[0, 0, self.max_active, 1]] * (Bb - B)        # padding: the spare row of the page table

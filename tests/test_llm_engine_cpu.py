@@ -212,3 +212,34 @@ def test_paged_ops_reference_paths():
         ref = torch.einsum("hn,nhd->hd", torch.softmax(s, -1), v).reshape(-1)
         assert torch.allclose(out[b], ref, atol=1e-5)
     assert P.pick_splits(1, 8, 8192) == 16 and P.pick_splits(64, 8, 8192) == 2 and P.pick_splits(4, 4, 64) == 1
+
+
+def test_speculative_decoding_gives_the_same_greedy_tokens():
+    """N-gram proposals verified inside the decode pass: identical output, fewer passes, mixed with a sampled request."""
+    w = LlamaWeights.random(tiny_cfg(), seed=17)
+    g = torch.Generator().manual_seed(5)
+    base = torch.randint(3, 97, (12,), generator=g).tolist()
+    prompts = [[1] + base * 4, [1] + torch.randint(3, 97, (20,), generator=g).tolist(), [1] + base[:5] * 9]
+    want = [dense_generate(w, p, 24) for p in prompts]
+    plain = LLMEngine(device="cpu", max_pages=32, max_active=4)
+    spec = LLMEngine(device="cpu", max_pages=32, max_active=4, spec_tokens=4)
+    outs = []
+    for eng in (plain, spec):
+        eng.set_weights(w)
+        for i, p in enumerate(prompts):
+            eng.submit_request(Request(i, p, GenerationConfig(max_new_tokens=24, **GREEDY)))
+        eng.submit_request(Request(9, prompts[0], GenerationConfig(max_new_tokens=8, temperature=0.8, top_k=10, repetition_penalty=1.1)))
+        got = {}
+        while eng.num_active():
+            eng.step()
+            got.update({r.request_id: r.token_ids for r in eng.poll_responses()})
+        outs.append(got)
+        assert eng.kv.pages_in_use == 0
+    for i in range(3):
+        assert outs[0][i] == want[i] and outs[1][i] == want[i]
+    assert 1 <= len(outs[1][9]) <= 8
+    assert spec.spec_drafted > 0 and spec.spec_accepted > 0 and spec.steps < plain.steps
+    # the proposal never runs past max_new_tokens or the position limit
+    short = LLMEngine(device="cpu", max_pages=8, max_active=1, spec_tokens=8)
+    short.set_weights(w)
+    assert short.generate(prompts[0], GenerationConfig(max_new_tokens=3, **GREEDY)).token_ids == want[0][:3]
