@@ -269,6 +269,7 @@ class LLMEngine:
         # speculative decoding for greedy requests: up to `spec_tokens` ids proposed by an n-gram look-up in the request's
         # own history are verified in the same decode pass (one extra batch row per proposed id)
         self.spec_tokens = spec_tokens
+        self.max_prompt_tokens = 16384           # tokens of new requests that share one prompt pass
         self.spec_drafted = self.spec_accepted = 0
 
     # -------------------------------------------------------------------------------------- loading
@@ -344,7 +345,8 @@ class LLMEngine:
         self.steps += 1
         fresh = [s for s in self.active if not s.prefill_done]
         running = [s for s in self.active if s.prefill_done and not s.done]
-        for s in fresh:                                        # the prompt pass, one request at a time
+        ready: List[RequestState] = []
+        for s in fresh:
             if not self._ensure_pages(s, s.prompt_len - 1):
                 if len(self.active) > 1:                       # wait for a running request to give its pages back
                     self.active.remove(s)
@@ -354,10 +356,17 @@ class LLMEngine:
                 else:
                     self._finish(s)                            # the pool cannot hold this prompt at all
                 continue
-            logits = self._forward_prompt(s)
-            s.kv_position = s.prompt_len
-            s.prefill_done = True
-            self._emit(s, self._sample([s], logits)[0])
+            ready.append(s)
+        while ready:                                           # prompt passes: as many new requests as the token cap allows
+            chunk, total = [], 0
+            while ready and (not chunk or total + ready[0].prompt_len <= self.max_prompt_tokens):
+                total += ready[0].prompt_len
+                chunk.append(ready.pop(0))
+            logits = self._forward_prompts(chunk)
+            for i, s in enumerate(chunk):
+                s.kv_position = s.prompt_len
+                s.prefill_done = True
+                self._emit(s, self._sample([s], logits[i:i + 1])[0])
         running = [s for s in running if self._ensure_pages(s, s.kv_position) or self._finish(s)]
         if running and self.spec_tokens > 0:
             self._step_speculative(running)
@@ -512,25 +521,44 @@ class LLMEngine:
 
     def _forward_prompt(self, s: RequestState) -> torch.Tensor:
         """All prompt tokens of one request; fills its pages; returns the logits of the last position ``[1, V]``."""
+        return self._forward_prompts([s])
+
+    def _forward_prompts(self, batch: List[RequestState]) -> torch.Tensor:
+        """The prompt pass of several new requests at once: their tokens are concatenated, so every projection is one
+        GEMM over all of them; attention runs per request (requests of equal length share a call).  Fills the pages;
+        returns the logits of each request's last position ``[len(batch), V]``."""
         from ..ops.attention import flash_attention
         c, w = self.cfg, self.weights
         H, Hk, Dh = c.num_attention_heads, c.num_key_value_heads, c.head_dim
-        T = s.prompt_len
         dev = self.device
-        ids = torch.tensor(s.input_ids, dtype=torch.long, device=dev)
-        pos = torch.arange(T, dtype=torch.int32, device=dev)
-        req = torch.full((T,), s.row, dtype=torch.int32, device=dev)
+        lens = [s.prompt_len for s in batch]
+        offs = [0]
+        for n in lens:
+            offs.append(offs[-1] + n)
+        ids = torch.tensor([t for s in batch for t in s.input_ids], dtype=torch.long)
+        pos = torch.cat([torch.arange(n, dtype=torch.int32) for n in lens])
+        req = torch.cat([torch.full((n,), s.row, dtype=torch.int32) for s, n in zip(batch, lens)])
+        ids, pos, req = ids.to(dev), pos.to(dev), req.to(dev)
+        groups: Dict[int, List[int]] = {}
+        for i, n in enumerate(lens):
+            groups.setdefault(n, []).append(i)
+        consecutive = all(g == list(range(g[0], g[0] + len(g))) for g in groups.values())
         x = w.tok_emb[ids]
         for l, L in enumerate(w.layers):
             qkv = self._linear(self._norm(x, L["attn_norm"]), L["wqkv"]).contiguous()
             k = P.paged_rope_write(qkv, H, Hk, Dh, pos, req, self.page_table, self.cos, self.sin, self.kv.k[l], self.kv.v[l], want_k=True)
-            q = qkv[:, :H * Dh].reshape(1, T, H, Dh)
-            v = qkv[:, (H + Hk) * Dh:].reshape(1, T, Hk, Dh)
-            a = flash_attention(q, k.view(1, T, Hk, Dh), v, causal=True).reshape(T, H * Dh)
+            a = torch.empty(qkv.shape[0], H * Dh, dtype=qkv.dtype, device=dev)
+            for n, members in groups.items():
+                runs = [members] if consecutive else [[i] for i in members]      # equal lengths side by side: one call
+                for run in runs:
+                    lo, hi, nb = offs[run[0]], offs[run[-1] + 1], len(run)
+                    q = qkv[lo:hi, :H * Dh].reshape(nb, n, H, Dh)
+                    v = qkv[lo:hi, (H + Hk) * Dh:].reshape(nb, n, Hk, Dh)
+                    a[lo:hi] = flash_attention(q, k[lo:hi].view(nb, n, Hk, Dh), v, causal=True).reshape(nb * n, H * Dh)
             x = x + self._linear(a, L["wo"])
             x = x + self._mlp(self._norm(x, L["ffn_norm"]), L)
-        last = self._norm(x[-1:], w.final_norm)
-        return self._linear(last, w.lm_head).float()
+        last = x[torch.tensor([o - 1 for o in offs[1:]], device=dev)]
+        return self._linear(self._norm(last, w.final_norm), w.lm_head).float()
 
     def _decode_layers(self, meta: torch.Tensor, nsplit: int) -> torch.Tensor:
         """The device work of a decode pass.  ``meta [B, 4]`` int32: token id, position, page-table row, cached length."""

@@ -243,3 +243,26 @@ def test_speculative_decoding_gives_the_same_greedy_tokens():
     short = LLMEngine(device="cpu", max_pages=8, max_active=1, spec_tokens=8)
     short.set_weights(w)
     assert short.generate(prompts[0], GenerationConfig(max_new_tokens=3, **GREEDY)).token_ids == want[0][:3]
+
+
+def test_batched_prompt_pass_groups_and_token_cap():
+    """New requests share a prompt pass (equal lengths share the attention call); a token cap splits the pass."""
+    w = LlamaWeights.random(tiny_cfg(), seed=19)
+    g = torch.Generator().manual_seed(8)
+    prompts = [[1] + torch.randint(3, 97, (n,), generator=g).tolist() for n in (20, 20, 20, 7, 66, 66)]
+    want = [dense_generate(w, p, 5) for p in prompts]
+    for cap in (16384, 50):
+        eng = LLMEngine(device="cpu", max_pages=32, max_active=6)
+        eng.set_weights(w)
+        eng.max_prompt_tokens = cap
+        calls = []
+        real = eng._forward_prompts
+        eng._forward_prompts = lambda batch, real=real: calls.append(len(batch)) or real(batch)
+        for i, p in enumerate(prompts):
+            eng.submit_request(Request(i, p, GenerationConfig(max_new_tokens=5, **GREEDY)))
+        got = {}
+        while eng.num_active():
+            eng.step()
+            got.update({r.request_id: r.token_ids for r in eng.poll_responses()})
+        assert got == {i: want[i] for i in range(6)}
+        assert calls == ([6] if cap == 16384 else [2, 2, 1, 1]), calls        # 21+21 | 21+8 | 67 | 67 tokens under a cap of 50
