@@ -439,15 +439,17 @@ class LLMEngine:
 
     # -------------------------------------------------------------------------------------- scheduling
     def _encode(self, prompt) -> List[int]:
-        if isinstance(prompt, str):
-            try:
-                ids = self.tokenizer.encode(prompt, add_bos=True)
-            except TypeError:
-                ids = self.tokenizer.encode(prompt)
-            if not ids or (self.cfg and ids[0] != self.cfg.bos_token_id and getattr(self.tokenizer, "bos_id", -1) < 0):
-                ids = [self.cfg.bos_token_id] + list(ids)
-            return [min(int(i), self.cfg.vocab_size - 1) for i in ids]
-        return [int(i) for i in prompt]
+        """Text goes through the tokenizer and starts with the BOS id; a list of ids is taken as it is."""
+        if not isinstance(prompt, str):
+            return [int(i) for i in prompt]
+        try:
+            ids = list(self.tokenizer.encode(prompt, add_bos=False))
+        except TypeError:                                      # a tokenizer without the add_bos switch
+            ids = list(self.tokenizer.encode(prompt))
+        bos = self.cfg.bos_token_id
+        if not ids or ids[0] != bos:
+            ids = [bos] + ids
+        return [min(max(int(i), 0), self.cfg.vocab_size - 1) for i in ids]
 
     def _admit_pending(self):
         if getattr(self, "_held", False) and self.active:      # a prompt is waiting for pages: admit nothing new
