@@ -16,6 +16,7 @@ import torch
 from .process_group import (BackendType, CollectiveTimeout, CountingPG, FileBackend, ProcessGroup, ReduceOp, SharedMemoryBackend,
                             SingleProcessGroup, TorchProcessGroup, make_shared_memory_groups)
 from .ddp import DDPNoSyncGuard, DistributedDataParallel, PeerChannel
+from .checkpoint import load_sharded, save_sharded  # noqa: F401
 from .fsdp import (FSDPConfig, FullyShardedDataParallel, OffloadOptimizer, ShardingStrategy, ZeROOptimizer, ZeROStage3,
                    ZeROStage3Config)
 from .launcher import DistArgs, launch, parse_dist_args

@@ -179,6 +179,7 @@ class FusedFSDP(nn.Module):
                 self.rest_grads.append(flat[off:off + p.numel()].view_as(p))
                 off += p.numel()
             masters = [nn.Parameter(m, requires_grad=False) for m in self.rest_master]
+            self.rest_master_params = masters
             self.rest_opt = AdamW(masters, lr=lr, betas=betas, eps=eps, weight_decay=0.0, fused=True)
             for mp, g, p in zip(masters, self.rest_grads, rest):
                 self.rest_opt.set_grad_source(mp, g)
@@ -225,6 +226,93 @@ class FusedFSDP(nn.Module):
     def zero_grad(self):
         for p in self.rest:
             p.grad = None
+
+    # ------------------------------------------------------------------ sharded checkpoints
+    def save_sharded(self, directory: str, extra: Optional[dict] = None):
+        """One ``.safetensors`` file per rank (fp32 master shard and AdamW moments of every sharded weight) plus, from rank 0,
+        the replicated parameters with their optimizer state and ``manifest.json``.  Every rank calls this."""
+        import json
+        import os
+        from ..distributed.checkpoint import _opt_state_tensors, _rank_file
+        from ..io.safetensors import save_file
+        os.makedirs(directory, exist_ok=True)
+        r, W = self.symm.rank, self.symm.world
+        torch.cuda.synchronize(self.symm.device)
+        t: Dict[str, torch.Tensor] = {}
+        for i, sl in enumerate(self.sharded):
+            t[f"layer.{i}.master"], t[f"layer.{i}.m"], t[f"layer.{i}.v"] = sl.master.cpu(), sl.m.cpu(), sl.v.cpu()
+        if r == 0 and self.rest_opt is not None:
+            for j, mp in enumerate(self.rest_master_params):
+                t[f"rest.{j}.master"] = mp.data.cpu()
+            t.update({"rest." + k: v for k, v in _opt_state_tensors(self.rest_opt, self.rest_master_params).items()})
+        save_file(t, _rank_file(directory, r) + ".tmp", metadata={"rank": str(r), "world": str(W)})
+        os.replace(_rank_file(directory, r) + ".tmp", _rank_file(directory, r))
+        if r == 0:
+            groups = [{k: v for k, v in g.items() if k != "params" and isinstance(v, (int, float, bool, str, list, tuple))}
+                      for g in (self.rest_opt.param_groups if self.rest_opt is not None else [])]
+            manifest = {"format": "ptb-fused-fsdp-1", "world_size": W,
+                        "layers": [{"out": sl.out, "in": sl.inf, "shard_rows": sl.S, "step_count": sl.step_count} for sl in self.sharded],
+                        "rest": [list(p.shape) for p in self.rest], "rest_param_groups": groups,
+                        "param_groups": [{k: (list(v) if isinstance(v, tuple) else v) for k, v in g.items() if k != "params"}
+                                         for g in self.param_groups], "extra": extra or {}}
+            with open(os.path.join(directory, "manifest.json.tmp"), "w") as f:
+                json.dump(manifest, f, indent=1)
+            os.replace(os.path.join(directory, "manifest.json.tmp"), os.path.join(directory, "manifest.json"))
+        self.symm.barrier()
+
+    @torch.no_grad()
+    def load_sharded(self, directory: str) -> dict:
+        """Restore what :meth:`save_sharded` wrote, also when this run has a different number of ranks (each rank re-cuts
+        its rows from the writers' files).  Returns the manifest's ``extra``."""
+        import json
+        import os
+        from ..distributed.checkpoint import _rank_file
+        from ..io.safetensors import SafeTensorsFile
+        with open(os.path.join(directory, "manifest.json")) as f:
+            man = json.load(f)
+        if man.get("format") != "ptb-fused-fsdp-1":
+            raise ValueError(f"{directory}: not a fused-FSDP checkpoint")
+        if len(man["layers"]) != len(self.sharded) or any(m["out"] != sl.out or m["in"] != sl.inf for m, sl in zip(man["layers"], self.sharded)):
+            raise ValueError(f"{directory}: the sharded layers of the checkpoint do not match this model")
+        r, oldW = self.symm.rank, int(man["world_size"])
+        files = [SafeTensorsFile(_rank_file(directory, q)) for q in range(oldW)]
+        try:
+            for i, (sl, meta) in enumerate(zip(self.sharded, man["layers"])):
+                So = int(meta["shard_rows"])
+                lo, hi = r * sl.S, (r + 1) * sl.S
+                for key, dst in (("master", sl.master), ("m", sl.m), ("v", sl.v)):
+                    buf = torch.zeros(sl.S, sl.inf)
+                    for q in range(lo // So, min(oldW, (hi - 1) // So + 1)):
+                        a, b = max(lo, q * So), min(hi, (q + 1) * So)
+                        buf[a - lo:b - lo] = files[q].get_tensor(f"layer.{i}.{key}")[a - q * So:b - q * So]
+                    buf[max(0, min(hi, sl.out) - lo):] = 0                     # rows past the weight are padding
+                    dst.copy_(buf)
+                sl.shard.copy_(sl.master)
+                sl.step_count = int(meta["step_count"])
+            if self.rest_opt is not None:
+                for j, (mp, p) in enumerate(zip(self.rest_master_params, self.rest)):
+                    mp.data.copy_(files[0].get_tensor(f"rest.{j}.master"))
+                    p.data.copy_(mp.data)
+                    st = self.rest_opt.state[mp]
+                    for k in [k for k in files[0].keys() if k.startswith(f"rest.opt.{j}.")]:
+                        v = files[0].get_tensor(k)
+                        name = k[len(f"rest.opt.{j}."):]
+                        st[name] = v.to(mp.device).view_as(mp) if v.dim() else (st[name].new_tensor(float(v)) if torch.is_tensor(st.get(name)) else torch.tensor(float(v)))
+                for g, saved in zip(self.rest_opt.param_groups, man.get("rest_param_groups", [])):
+                    for k, v in saved.items():
+                        g[k] = tuple(v) if isinstance(g.get(k), tuple) and isinstance(v, list) else v
+        finally:
+            for f in files:
+                f.close()
+        for g, saved in zip(self.param_groups, man.get("param_groups", [])):
+            for k, v in saved.items():
+                g[k] = tuple(v) if k == "betas" else v
+        torch.cuda.synchronize(self.symm.device)
+        self.symm.barrier()                                   # every owner's bf16 shard is in place
+        for sl in self.sharded:
+            sl.stage_seq += 1                                 # the peers' rows held locally are stale
+            sl.prefetch()
+        return man.get("extra", {})
 
     def check(self):
         for sl in self.sharded:

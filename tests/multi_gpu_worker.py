@@ -158,7 +158,51 @@ def case_tp_sp_fused(rank, world, dev, symm, pg):
     return res
 
 
-CASES = dict(staged_gemm=case_staged_gemm, ddp_fused=case_ddp_fused, fsdp_fused=case_fsdp_fused, tp_sp_fused=case_tp_sp_fused)
+def case_fsdp_checkpoint(rank, world, dev, symm, pg):
+    """Fused FSDP: 2 steps, save, 2 more steps == a fresh engine that loads the checkpoint and takes the same 2 steps."""
+    import copy
+    import tempfile
+    from prometorch_b200.models.llama import Llama, LlamaConfig
+    from prometorch_b200.parallel.fsdp_fused import FusedFSDP
+    cfg = LlamaConfig.tiny(hidden_size=256, num_heads=4, num_kv_heads=2, intermediate_size=768, vocab_size=1024, num_layers=2, max_seq=256)
+    torch.manual_seed(0)
+    base = Llama(cfg).to(dev).to(torch.bfloat16)
+    fresh = copy.deepcopy(base)
+    box = [tempfile.mkdtemp(prefix="ptb_ckpt_") if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    d = box[0]
+    g = torch.Generator().manual_seed(70 + rank)
+    toks = [torch.randint(0, cfg.vocab_size, (2, 257), generator=g).to(dev) for _ in range(4)]
+
+    def run(eng, batch):
+        out = []
+        for tok in batch:
+            loss = eng(tok[:, :-1], tok[:, 1:])
+            loss.backward()
+            eng.step()
+            eng.zero_grad()
+            out.append(float(loss))
+        return out
+    a = FusedFSDP(base, symm, pg, lr=1e-3, betas=(0.9, 0.95), weight_decay=0.0, min_shard_numel=1 << 14)
+    run(a, toks[:2])
+    a.save_sharded(d, extra={"step": 2})
+    la = run(a, toks[2:])
+    b = FusedFSDP(fresh, symm, pg, lr=5e-4, betas=(0.9, 0.95), weight_decay=0.0, min_shard_numel=1 << 14)
+    extra = b.load_sharded(d)
+    assert extra == {"step": 2} and b.param_groups[0]["lr"] == 1e-3 and b.sharded[0].step_count == 2
+    lb = run(b, toks[2:])
+    torch.cuda.synchronize()
+    a.check()
+    b.check()
+    assert all(abs(x - y) < 2e-3 * abs(x) for x, y in zip(la, lb)), (la, lb)
+    for sa, sb in zip(a.sharded, b.sharded):
+        assert _rel(sb.master, sa.master) < 1e-4 and _rel(sb.full_weight(), sa.full_weight()) < 1e-3
+    for pa, pb in zip(a.rest, b.rest):
+        assert _rel(pb, pa) < 1e-3
+    return la, lb
+
+
+CASES = dict(fsdp_checkpoint=case_fsdp_checkpoint, staged_gemm=case_staged_gemm, ddp_fused=case_ddp_fused, fsdp_fused=case_fsdp_fused, tp_sp_fused=case_tp_sp_fused)
 
 
 def main():

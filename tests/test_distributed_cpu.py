@@ -187,3 +187,71 @@ def test_data_parallel_step_averages_shard_gradients():
     assert abs(loss - ref.item()) < 1e-6
     for g, p in zip(got, lin.parameters()):
         assert torch.allclose(g, p.grad, atol=1e-6)
+
+
+def _fsdp_train(world, steps, ckpt_dir=None, load_dir=None, seed=0, resume_steps=0):
+    """Thread ranks: ``steps`` AdamW steps of a tiny MLP under FSDP; optionally save at the end / load at the start.
+    Returns (full parameters after training, extra from the manifest)."""
+    import threading
+    from prometorch_b200 import optim
+    from prometorch_b200.distributed import FullyShardedDataParallel, make_shared_memory_groups
+    from prometorch_b200.distributed.checkpoint import load_sharded, save_sharded
+    groups = make_shared_memory_groups(world, timeout=60.0)
+    out, errs = {}, []
+    torch.manual_seed(seed)
+    X, Y = torch.randn(24, 10), torch.randn(24, 3)
+    init = torch.nn.Sequential(torch.nn.Linear(10, 17), torch.nn.Tanh(), torch.nn.Linear(17, 3)).state_dict()   # one RNG user
+
+    def worker(r):
+        try:
+            model = torch.nn.Sequential(torch.nn.Linear(10, 17), torch.nn.Tanh(), torch.nn.Linear(17, 3))
+            model.load_state_dict(init)
+            fsdp = FullyShardedDataParallel(model, process_group=groups[r])
+            opt = optim.AdamW(fsdp.local_shards(), lr=1e-2, weight_decay=0.01)
+            extra = {}
+            if load_dir:
+                extra = load_sharded(load_dir, fsdp, opt)
+            for it in range(steps):
+                fsdp.all_gather_params()
+                loss = torch.nn.functional.mse_loss(fsdp(X), Y)        # every rank sees the whole batch: world-size independent
+                loss.backward()
+                fsdp.reduce_scatter_grads()
+                opt.step()
+                opt.zero_grad()
+            if ckpt_dir:
+                save_sharded(ckpt_dir, fsdp, opt, extra={"step": steps + resume_steps, "note": "ok"})
+            fsdp.all_gather_params()
+            out[r] = ({k: v.clone() for k, v in fsdp.full_state_dict().items()}, extra)
+        except Exception as e:          # noqa: BLE001
+            import traceback
+            errs.append(traceback.format_exc())
+    ts = [threading.Thread(target=worker, args=(r,)) for r in range(world)]
+    for t in ts:
+        t.start()
+    for t in ts:
+        t.join(120)
+    assert not errs, errs[0]
+    return out[0]
+
+
+def test_sharded_checkpoint_resume_and_reshard(tmp_path):
+    """6 steps straight == 3 steps, save (2 ranks), load and 3 more steps, with 2 ranks and re-cut for 3 ranks."""
+    straight, _ = _fsdp_train(2, 6)
+    d = str(tmp_path / "ckpt")
+    _fsdp_train(2, 3, ckpt_dir=d)
+    import json
+    import os
+    man = json.load(open(os.path.join(d, "manifest.json")))
+    assert man["format"] == "ptb-sharded-1" and man["world_size"] == 2 and len(man["params"]) == 4 and man["extra"]["step"] == 3
+    assert sorted(os.listdir(d)) == ["manifest.json", "rank00000.safetensors", "rank00001.safetensors"]
+    same, extra = _fsdp_train(2, 3, load_dir=d)
+    other, extra3 = _fsdp_train(3, 3, load_dir=d)
+    assert extra == {"step": 3, "note": "ok"} and extra3 == extra
+    for k in straight:
+        assert torch.allclose(same[k], straight[k], atol=1e-6), k
+        assert torch.allclose(other[k], straight[k], atol=1e-5), k
+    from prometorch_b200.distributed import FullyShardedDataParallel
+    from prometorch_b200.distributed.checkpoint import load_sharded
+    wrong = FullyShardedDataParallel(torch.nn.Linear(3, 3))
+    with pytest.raises(ValueError):
+        load_sharded(d, wrong)
