@@ -35,9 +35,38 @@ def _decls(L):
     L.ptb_enable_peer_access.restype = C.c_int
 
 
+GUARD = 256                      # bytes of canary words before and after every symmetric buffer
+_CANARY = 0x5AFEC0DE
+
+
 class SymmBuffer:
+    """``nbytes`` of this rank's memory that every peer can address, between two guard regions filled with a known
+    word.  Kernels of the peers write into it through raw pointers; :meth:`check_canaries` tells on the host whether
+    anything wrote past either end."""
+
     def __init__(self, group: "SymmGroup", nbytes: int, local: int, peers: List[int]):
-        self.group, self.nbytes, self.local, self._peers = group, nbytes, local, peers
+        # `local` / `peers` are the allocation bases; the usable region starts GUARD bytes in
+        self.group, self.nbytes = group, nbytes
+        self._base_local, self._base_peers = local, peers
+        self.local, self._peers = local + GUARD, [p + GUARD if p else 0 for p in peers]
+        self._guard_view(0).fill_(_CANARY)
+        self._guard_view(1).fill_(_CANARY)
+
+    def _guard_view(self, which: int) -> torch.Tensor:
+        class _A:
+            pass
+        a = _A()
+        addr = self._base_local if which == 0 else self._base_local + GUARD + self.nbytes
+        a.__cuda_array_interface__ = {"shape": (GUARD // 4,), "typestr": "<i4", "data": (addr, False), "version": 3}
+        return torch.as_tensor(a, device=self.group.device)
+
+    def check_canaries(self):
+        """Raise if a guard word changed (someone wrote outside the buffer)."""
+        for which, name in ((0, "before"), (1, "after")):
+            g = self._guard_view(which)
+            bad = (g != _CANARY).nonzero()
+            if bad.numel():
+                raise RuntimeError(f"symmetric buffer of {self.nbytes} bytes: guard word {int(bad[0])} {name} the buffer was overwritten")
 
     def peer_ptr(self, rank: int) -> int:
         return self._peers[rank]
@@ -58,12 +87,12 @@ class SymmBuffer:
 
     def free(self):
         lib = N.lib()
-        for r, p in enumerate(self._peers):
+        for r, p in enumerate(self._base_peers):
             if r != self.group.rank and p:
                 lib.ptb_symm_close(p)
-        if self.local:
-            lib.ptb_symm_free(self.local)
-        self.local, self._peers = 0, []
+        if self._base_local:
+            lib.ptb_symm_free(self._base_local)
+        self.local, self._peers, self._base_local, self._base_peers = 0, [], 0, []
 
 
 class SymmGroup:
@@ -84,7 +113,7 @@ class SymmGroup:
         nbytes = (int(nbytes) + 255) // 256 * 256
         ptr = C.c_void_p()
         handle = (C.c_ubyte * 64)()
-        N.check(lib.ptb_symm_alloc(nbytes, C.byref(ptr), handle), "symm alloc")
+        N.check(lib.ptb_symm_alloc(nbytes + 2 * GUARD, C.byref(ptr), handle), "symm alloc")
         handles: List[Optional[bytes]] = [None] * self.world
         self.dist.all_gather_object(handles, bytes(handle), group=self.pg)
         peers = []
@@ -104,6 +133,13 @@ class SymmGroup:
     def barrier(self):
         torch.cuda.synchronize(self.device)
         self.dist.barrier(group=self.pg)
+
+    def check_canaries(self):
+        """Check the guard words of every buffer of this group (call between steps, e.g. from tests or a debug run)."""
+        torch.cuda.synchronize(self.device)
+        for b in self._bufs:
+            if b.local:
+                b.check_canaries()
 
     def close(self):
         self.barrier()

@@ -220,6 +220,8 @@ def main():
         try:
             out = CASES[nme](rank, world, dev, symm, pg)
             torch.cuda.synchronize()
+            dist.barrier()
+            symm.check_canaries()                        # nobody wrote outside a symmetric buffer
             if rank == 0:
                 print(f"[{nme}] ok {out}", flush=True)
         except Exception as e:                           # report and keep the other ranks out of a hang

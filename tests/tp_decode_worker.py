@@ -50,6 +50,8 @@ def main():
         ok = False
         print("scripted tokens differ across ranks", flush=True)
     tp.check_status()
+    dist.barrier()
+    symm.check_canaries()                                # the all-reduce slots stayed inside their buffers
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     tp.close()
