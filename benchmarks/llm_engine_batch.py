@@ -26,6 +26,7 @@ def main():
     ap.add_argument("--kv-heads", type=int, default=4)
     ap.add_argument("--inter", type=int, default=5632)
     ap.add_argument("--vocab", type=int, default=32000)
+    ap.add_argument("--sampled", action="store_true", help="temperature 0.8, top-k 50, top-p 0.9, repetition penalty 1.1 instead of greedy")
     ap.add_argument("--spec", type=int, default=0, help="n-gram speculative decoding: ids proposed per greedy request and pass")
     ap.add_argument("--repeat-prompt", type=int, default=0, help="build each prompt from a random piece of this length, repeated")
     a = ap.parse_args()
@@ -34,6 +35,8 @@ def main():
                       eos_token_id=-1)
     w = LlamaWeights.random(cfg, seed=0, dtype=torch.bfloat16)
     greedy = GenerationConfig(max_new_tokens=a.new, temperature=0.0, repetition_penalty=1.0, top_k=1)
+    if a.sampled:
+        greedy = GenerationConfig(max_new_tokens=a.new, temperature=0.8, top_k=50, top_p=0.9, repetition_penalty=1.1)
     g = torch.Generator().manual_seed(0)
     for B in [int(x) for x in a.batches.split(",")]:
         pages = B * ((a.prompt + a.new) // 64 + 2)
@@ -79,7 +82,7 @@ def main():
                           "prompt_tok_per_s": round(B * a.prompt / e0.elapsed_time(e1) * 1e3, 1),
                           "decode_ms_per_step": round(e1.elapsed_time(e2) / max(steps, 1), 3),
                           "decode_tok_per_s": round(toks / e1.elapsed_time(e2) * 1e3, 1), "graph_replay_ms": replay_ms,
-                          "spec_tokens": a.spec, "spec_accept_rate": round(eng.spec_accepted / max(eng.spec_drafted, 1), 3),
+                          "sampled": a.sampled, "spec_tokens": a.spec, "spec_accept_rate": round(eng.spec_accepted / max(eng.spec_drafted, 1), 3),
                           "model": f"llama {a.layers}L/{a.hidden}/{a.heads}h/{a.kv_heads}kv ffn{a.inter} bf16"}), flush=True)
         del eng
         torch.cuda.empty_cache()

@@ -49,3 +49,15 @@ typedef struct PtbStaging {
     int external;                // non-zero: someone else (copy engines on a side stream) copies the rows and raises the
                                  // flags; the launch adds no stager CTAs and only waits on the flags
 } PtbStaging;
+
+// One request of ptb_sample_logits_batch: a row of fp32 logits, the request's id history (the chosen id is appended at
+// history[n_hist] when it fits), its scratch (ptb_sample_scratch_bytes, zeroed once) and where the result goes
+// (out[0] = id, out[1] = float bits of its probability).  `u` is the uniform number of the draw.
+typedef struct PtbSampleRequest {
+    const float* logits;
+    int* history;
+    void* scratch;
+    int* out;
+    int n_hist, hist_cap, top_k, pad;
+    float repeat_penalty, temperature, top_p, u;
+} PtbSampleRequest;

@@ -7,7 +7,9 @@
 // by one CTA, and temperature, the top-p cut and an inverse-CDF draw (uniform number from the caller)
 // finish the job.  Two passes over the logits (L2-resident), three short launches.
 #include "common.cuh"
+#include "ptb200_types.h"
 #include <algorithm>
+#include <vector>
 
 namespace ptb {
 
@@ -40,7 +42,7 @@ __device__ __forceinline__ uint32_t ordered_key(float x) {
 }
 
 // Pass 1: penalised logits and the histogram of their keys.
-__global__ void __launch_bounds__(SAMP_THREADS) sample_hist_kernel(const __grid_constant__ SampleParams P) {
+__device__ __forceinline__ void sample_hist_body(const SampleParams& P) {
     __shared__ uint32_t sh[SAMP_BINS];
     const int tid = threadIdx.x;
     for (int i = tid; i < SAMP_BINS; i += SAMP_THREADS) sh[i] = 0u;
@@ -71,7 +73,11 @@ __global__ void __launch_bounds__(SAMP_THREADS) sample_hist_kernel(const __grid_
 }
 
 // Pass 2: every CTA finds the bin that holds the k-th largest key, then collects the elements of that bin and above.
-__global__ void __launch_bounds__(SAMP_THREADS) sample_collect_kernel(const __grid_constant__ SampleParams P) {
+__global__ void __launch_bounds__(SAMP_THREADS) sample_hist_kernel(const __grid_constant__ SampleParams P) { sample_hist_body(P); }
+// Batched form: one grid row (blockIdx.y) per request, parameters read from device memory.
+__global__ void __launch_bounds__(SAMP_THREADS) sample_hist_batch_kernel(const SampleParams* __restrict__ ps) { sample_hist_body(ps[blockIdx.y]); }
+
+__device__ __forceinline__ void sample_collect_body(const SampleParams& P) {
     __shared__ uint32_t part[SAMP_THREADS];
     __shared__ int thr_bin;
     const int tid = threadIdx.x;
@@ -111,6 +117,9 @@ __global__ void __launch_bounds__(SAMP_THREADS) sample_collect_kernel(const __gr
     }
 }
 
+__global__ void __launch_bounds__(SAMP_THREADS) sample_collect_kernel(const __grid_constant__ SampleParams P) { sample_collect_body(P); }
+__global__ void __launch_bounds__(SAMP_THREADS) sample_collect_batch_kernel(const SampleParams* __restrict__ ps) { sample_collect_body(ps[blockIdx.y]); }
+
 // Bitonic sort, descending by value (ties: lower index first), `n` a power of two, in shared memory.
 __device__ __forceinline__ void bitonic_desc(float* v, int* ix, int n, int tid, int nthreads) {
     for (int k = 2; k <= n; k <<= 1) {
@@ -131,7 +140,7 @@ __device__ __forceinline__ void bitonic_desc(float* v, int* ix, int n, int tid, 
 }
 
 // Pass 3 (one CTA): sort the candidates, temperature softmax over the k best, top-p cut, inverse-CDF draw.
-__global__ void __launch_bounds__(1024) sample_final_kernel(const __grid_constant__ SampleParams P) {
+__device__ __forceinline__ void sample_final_body(const SampleParams& P) {
     __shared__ float sv[SAMP_MAX_CAND];
     __shared__ int si[SAMP_MAX_CAND];
     const int tid = threadIdx.x;
@@ -183,9 +192,25 @@ __global__ void __launch_bounds__(1024) sample_final_kernel(const __grid_constan
     }
 }
 
+__global__ void __launch_bounds__(1024) sample_final_kernel(const __grid_constant__ SampleParams P) { sample_final_body(P); }
+__global__ void __launch_bounds__(1024) sample_final_batch_kernel(const SampleParams* __restrict__ ps) { sample_final_body(ps[blockIdx.x]); }
+
 }  // namespace ptb
 
 using namespace ptb;
+
+static void fill_sample_params(SampleParams& p, const float* logits, int V, int* history, int n_hist, int hist_cap, float repeat_penalty,
+                               float temperature, int top_k, float top_p, float u, void* scratch, int* out, int* ctrl_token) {
+    p.logits = logits; p.V = V; p.history = history; p.n_hist = n_hist; p.hist_cap = hist_cap; p.repeat_penalty = repeat_penalty;
+    p.temperature = temperature; p.top_p = top_p; p.u = u; p.top_k = top_k;
+    uint8_t* s = (uint8_t*)scratch;
+    p.counters = (unsigned*)s;
+    p.hist = (unsigned*)(s + 64);
+    p.cand_val = (float*)(s + 64 + SAMP_BINS * 4);
+    p.cand_idx = (int*)(s + 64 + SAMP_BINS * 4 + SAMP_MAX_CAND * 4);
+    p.xp = (float*)(s + 64 + SAMP_BINS * 4 + SAMP_MAX_CAND * 8);
+    p.out = out; p.ctrl_token = ctrl_token;
+}
 
 // Bytes of scratch for a vocabulary of V entries (zero it once before the first call).
 PTB_API long long ptb_sample_scratch_bytes(int V) { return 64 + (long long)SAMP_BINS * 4 + (long long)SAMP_MAX_CAND * 8 + (long long)V * 4; }
@@ -198,19 +223,36 @@ PTB_API int ptb_sample_logits(const float* logits, int V, int* history, int n_hi
     if (top_k < 1 || top_k > SAMP_MAX_K) { ptb_set_error("sample: top_k %d outside 1..%d", top_k, SAMP_MAX_K); return -1; }
     if (V < 1) { ptb_set_error("sample: empty vocabulary"); return -1; }
     SampleParams p;
-    p.logits = logits; p.V = V; p.history = history; p.n_hist = n_hist; p.hist_cap = hist_cap; p.repeat_penalty = repeat_penalty;
-    p.temperature = temperature; p.top_p = top_p; p.u = u; p.top_k = top_k;
-    uint8_t* s = (uint8_t*)scratch;
-    p.counters = (unsigned*)s;
-    p.hist = (unsigned*)(s + 64);
-    p.cand_val = (float*)(s + 64 + SAMP_BINS * 4);
-    p.cand_idx = (int*)(s + 64 + SAMP_BINS * 4 + SAMP_MAX_CAND * 4);
-    p.xp = (float*)(s + 64 + SAMP_BINS * 4 + SAMP_MAX_CAND * 8);
-    p.out = out; p.ctrl_token = ctrl_token;
+    fill_sample_params(p, logits, V, history, n_hist, hist_cap, repeat_penalty, temperature, top_k, top_p, u, scratch, out, ctrl_token);
     const int grid = std::max(1, std::min(148, (V + 1023) / 1024));
     sample_hist_kernel<<<grid, SAMP_THREADS, 0, st>>>(p);
     sample_collect_kernel<<<grid, SAMP_THREADS, 0, st>>>(p);
     sample_final_kernel<<<1, 1024, 0, st>>>(p);
+    PTB_CUDA_OK(cudaGetLastError());
+    return grid;
+}
+
+// Sample `n` requests in three launches (grid row = request).  `reqs`: host array; `d_params`: device scratch of
+// ptb_sample_batch_param_bytes(n) bytes that receives the kernel parameters (one stream-ordered copy).
+PTB_API long long ptb_sample_batch_param_bytes(int n) { return (long long)n * sizeof(SampleParams); }
+
+PTB_API int ptb_sample_logits_batch(const PtbSampleRequest* reqs, int n, int V, void* d_params, cudaStream_t st) {
+    if (n <= 0) return 0;
+    if (V < 1 || n > 4096) { ptb_set_error("sample batch: bad vocabulary or more than 4096 requests"); return -1; }
+    static thread_local std::vector<SampleParams> host;
+    host.resize(n);
+    for (int i = 0; i < n; ++i) {
+        const PtbSampleRequest& r = reqs[i];
+        if (r.top_k < 1 || r.top_k > SAMP_MAX_K) { ptb_set_error("sample batch: top_k %d outside 1..%d", r.top_k, SAMP_MAX_K); return -1; }
+        fill_sample_params(host[i], r.logits, V, r.history, r.n_hist, r.hist_cap, r.repeat_penalty, r.temperature, r.top_k, r.top_p, r.u,
+                           r.scratch, r.out, nullptr);
+    }
+    PTB_CUDA_OK(cudaMemcpyAsync(d_params, host.data(), (size_t)n * sizeof(SampleParams), cudaMemcpyHostToDevice, st));
+    const int grid = std::max(1, std::min(148, (V + 1023) / 1024));
+    const SampleParams* dp = (const SampleParams*)d_params;
+    sample_hist_batch_kernel<<<dim3(grid, n), SAMP_THREADS, 0, st>>>(dp);
+    sample_collect_batch_kernel<<<dim3(grid, n), SAMP_THREADS, 0, st>>>(dp);
+    sample_final_batch_kernel<<<n, 1024, 0, st>>>(dp);
     PTB_CUDA_OK(cudaGetLastError());
     return grid;
 }

@@ -23,6 +23,52 @@ def _decls(L):
     if hasattr(L, "ptb_sample_logits"):
         L.ptb_sample_logits.argtypes = [vp, ci, vp, ci, ci, cf, cf, ci, cf, cf, vp, vp, vp, vp]
         L.ptb_sample_logits.restype = ci
+    if hasattr(L, "ptb_sample_logits_batch"):
+        L.ptb_sample_logits_batch.argtypes = [vp, ci, ci, vp, vp]
+        L.ptb_sample_logits_batch.restype = ci
+        L.ptb_sample_batch_param_bytes.argtypes = [ci]
+        L.ptb_sample_batch_param_bytes.restype = C.c_longlong
+
+
+class SampleRequest(C.Structure):
+    """Mirrors ``PtbSampleRequest`` (csrc/ptb200_types.h)."""
+    _fields_ = [("logits", C.c_void_p), ("history", C.c_void_p), ("scratch", C.c_void_p), ("out", C.c_void_p), ("n_hist", C.c_int),
+                ("hist_cap", C.c_int), ("top_k", C.c_int), ("pad", C.c_int), ("repeat_penalty", C.c_float), ("temperature", C.c_float),
+                ("top_p", C.c_float), ("u", C.c_float)]
+
+
+_BATCH_PARAMS = {}
+
+
+def sample_batch(samplers, logits: torch.Tensor, configs) -> list:
+    """Sample one id for each of ``len(samplers)`` requests in three launches (grid row = request) and one host
+    synchronisation.  ``logits``: ``[n, V]`` fp32 contiguous; ``configs``: per request ``(temperature, top_k, top_p,
+    repeat_penalty)``.  Every :class:`DeviceSampler` keeps its own history and scratch, as with :meth:`DeviceSampler.sample`."""
+    n = len(samplers)
+    if n == 0:
+        return []
+    assert logits.is_cuda and logits.dtype == torch.float32 and logits.is_contiguous() and logits.shape[0] == n
+    dev = logits.device
+    V = logits.shape[1]
+    reqs = (SampleRequest * n)()
+    for i, (s, (temperature, top_k, top_p, repeat_penalty)) in enumerate(zip(samplers, configs)):
+        assert 1 <= top_k <= MAX_DEVICE_TOP_K and s.V == V
+        if not s._u:
+            s._u = torch.rand(4096, generator=s.gen).tolist()
+        r = reqs[i]
+        r.logits, r.history, r.scratch, r.out = logits[i].data_ptr(), s.hist.data_ptr(), s.scratch.data_ptr(), s.out.data_ptr()
+        r.n_hist, r.hist_cap, r.top_k = s.n_hist, s.hist.numel(), int(top_k)
+        r.repeat_penalty, r.temperature, r.top_p, r.u = float(repeat_penalty), float(temperature), float(top_p), float(s._u.pop())
+    key = (dev.index, n)
+    need = int(N.lib().ptb_sample_batch_param_bytes(n))
+    if key not in _BATCH_PARAMS or _BATCH_PARAMS[key].numel() < need:
+        _BATCH_PARAMS[key] = torch.empty(need, dtype=torch.uint8, device=dev)
+    st = torch.cuda.current_stream(dev).cuda_stream
+    N.check(min(0, N.lib().ptb_sample_logits_batch(C.addressof(reqs), n, V, _BATCH_PARAMS[key].data_ptr(), st)), "sample_logits_batch")
+    for s in samplers:
+        if s.n_hist < s.hist.numel():
+            s.n_hist += 1                                     # the kernel appended its choice
+    return torch.stack([s.out for s in samplers])[:, 0].tolist()
 
 
 class DeviceSampler:
@@ -50,8 +96,10 @@ class DeviceSampler:
             self.hist[self.n_hist] = int(tid)
             self.n_hist += 1
 
-    def sample(self, logits: torch.Tensor, temperature: float, top_k: int, top_p: float, repeat_penalty: float = 1.0,
-               u: Optional[float] = None, ctrl_token_ptr: int = 0) -> int:
+    def sample_async(self, logits: torch.Tensor, temperature: float, top_k: int, top_p: float, repeat_penalty: float = 1.0,
+                     u: Optional[float] = None, ctrl_token_ptr: int = 0) -> torch.Tensor:
+        """Launch the sampling kernels and return the device tensor ``[id, probability bits]`` without waiting for it, so
+        that a batch of samplers costs one host synchronisation."""
         assert logits.is_cuda and logits.dtype == torch.float32 and logits.is_contiguous() and 1 <= top_k <= MAX_DEVICE_TOP_K
         if u is None:
             if not self._u:
@@ -64,7 +112,11 @@ class DeviceSampler:
                 "sample_logits")
         if self.n_hist < self.hist.numel():
             self.n_hist += 1                                  # the kernel appended its choice
-        return int(self.out[0])
+        return self.out
+
+    def sample(self, logits: torch.Tensor, temperature: float, top_k: int, top_p: float, repeat_penalty: float = 1.0,
+               u: Optional[float] = None, ctrl_token_ptr: int = 0) -> int:
+        return int(self.sample_async(logits, temperature, top_k, top_p, repeat_penalty, u, ctrl_token_ptr)[0])
 
 
 def sample_reference(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, repeat_penalty: float, history, u: float) -> int:

@@ -631,13 +631,14 @@ class LLMEngine:
     # -------------------------------------------------------------------------------------- sampling
     def _sample(self, batch: List[RequestState], logits: torch.Tensor) -> List[int]:
         """Greedy requests share one arg-max; the others go through the device sampler (top-k <= 64) or tensor ops."""
-        from ..ops.sampling import MAX_DEVICE_TOP_K, DeviceSampler, sample_logits
+        from ..ops.sampling import MAX_DEVICE_TOP_K, DeviceSampler, sample_batch, sample_logits
         out: List[Optional[int]] = [None] * len(batch)
         greedy = [i for i, s in enumerate(batch) if s.config.temperature <= 0.0 and s.config.repetition_penalty == 1.0]
         if greedy:
             am = logits[greedy].argmax(-1).tolist()
             for i, t in zip(greedy, am):
                 out[i] = int(t)
+        waiting = []                                           # indices of the requests that go through the device sampler
         for i, s in enumerate(batch):
             if out[i] is not None:
                 continue
@@ -648,11 +649,17 @@ class LLMEngine:
                     s.sampler = DeviceSampler(self.cfg.vocab_size, self.device, max_history=self.cfg.max_position_embeddings,
                                               seed=int(torch.randint(0, 2 ** 31 - 1, (1,), generator=self._gen)))
                     s.sampler.reset(s.prompt_ids + s.output_ids)
-                out[i] = s.sampler.sample(row, g.temperature, g.top_k, g.top_p, g.repetition_penalty)
+                waiting.append(i)
             else:
                 hist = s.prompt_ids + s.output_ids
                 out[i] = sample_logits(row, g.temperature, g.top_k, g.top_p, g.repetition_penalty,
                                        hist if g.repetition_penalty != 1.0 else None, generator=self._gen if not row.is_cuda else None)
+        if waiting:                                            # three launches and one synchronisation for all of them
+            rows = logits[waiting].contiguous() if len(waiting) != len(batch) else logits.contiguous()
+            cfgs = [(batch[i].config.temperature, batch[i].config.top_k, batch[i].config.top_p, batch[i].config.repetition_penalty)
+                    for i in waiting]
+            for i, t in zip(waiting, sample_batch([batch[i].sampler for i in waiting], rows, cfgs)):
+                out[i] = int(t)
         return [int(t) for t in out]
 
 

@@ -250,3 +250,24 @@ def test_gemma3_structure_matches_oracle(tmp_path, window):
         assert cos > 0.995, float(cos)
         m2.close()
     m.close()
+
+
+def test_batched_sampler_matches_single_request_sampler():
+    """``sample_batch`` (grid row per request) picks what each request's own ``DeviceSampler.sample`` picks."""
+    from prometorch_b200.ops.sampling import DeviceSampler, sample_batch
+    V, n = 5000, 6
+    torch.manual_seed(3)
+    logits = (torch.randn(n, V, device="cuda") * 3).contiguous()
+    hists = [[int(x) for x in torch.randint(0, V, (k,))] for k in (0, 3, 40, 7, 1, 100)]
+    cfgs = [(0.8, 40, 0.9, 1.1), (0.0, 1, 1.0, 1.0), (1.3, 64, 0.5, 1.3), (0.7, 5, 1.0, 1.0), (0.0, 8, 0.9, 1.2), (1.0, 50, 0.95, 1.05)]
+    a = [DeviceSampler(V, "cuda", max_history=256, seed=10 + i) for i in range(n)]
+    b = [DeviceSampler(V, "cuda", max_history=256, seed=10 + i) for i in range(n)]
+    for s, t, h in zip(a, b, hists):
+        s.reset(h)
+        t.reset(h)
+    for rnd in range(3):
+        got = sample_batch(a, logits, cfgs)
+        want = [t.sample(logits[i].contiguous(), *cfgs[i][:3], cfgs[i][3]) for i, t in enumerate(b)]
+        assert got == want, (rnd, got, want)
+        assert all(0 <= g < V for g in got)
+    assert [s.n_hist for s in a] == [t.n_hist for t in b] and all(torch.equal(s.hist[:s.n_hist], t.hist[:t.n_hist]) for s, t in zip(a, b))
