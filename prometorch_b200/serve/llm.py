@@ -375,8 +375,11 @@ class LLMEngine:
             for s, t in zip(running, self._sample(running, logits)):
                 s.kv_position += 1
                 self._emit(s, t)
+        finished = any(s.done for s in self.active)
         self._collect_done()
-        if self.device.type == "cuda":
+        # the kernels' status word (a page id or position outside its extent) costs a device round trip to read: look at it
+        # when a request finishes and every 32 steps, not after every token
+        if self.device.type == "cuda" and (finished or self.steps % 32 == 0):
             P.check_status(self.device)
 
     # -------------------------------------------------------------------------------------- speculative decoding
