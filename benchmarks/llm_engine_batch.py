@@ -33,7 +33,7 @@ def main():
     cfg = LlamaConfig(vocab_size=a.vocab, hidden_size=a.hidden, intermediate_size=a.inter, num_hidden_layers=a.layers,
                       num_attention_heads=a.heads, num_key_value_heads=a.kv_heads, max_position_embeddings=a.prompt + a.new + 64,
                       eos_token_id=-1)
-    w = LlamaWeights.random(cfg, seed=0, dtype=torch.bfloat16)
+    w = LlamaWeights.random(cfg, seed=0, dtype=torch.bfloat16, device="cuda")
     greedy = GenerationConfig(max_new_tokens=a.new, temperature=0.0, repetition_penalty=1.0, top_k=1)
     if a.sampled:
         greedy = GenerationConfig(max_new_tokens=a.new, temperature=0.8, top_k=50, top_p=0.9, repetition_penalty=1.1)

@@ -107,20 +107,23 @@ class LlamaWeights:
         self.lm_head: Optional[torch.Tensor] = None
 
     @classmethod
-    def random(cls, cfg: LlamaConfig, seed: int = 0, dtype=torch.float32) -> "LlamaWeights":
-        g = torch.Generator().manual_seed(seed)
+    def random(cls, cfg: LlamaConfig, seed: int = 0, dtype=torch.float32, device="cpu") -> "LlamaWeights":
+        """Random weights of the right scales (benchmarks and tests); drawn on ``device`` so a large model never sits in
+        host memory."""
+        g = torch.Generator(device=device).manual_seed(seed)
         D, I, H, Hk, Dh = cfg.hidden_size, cfg.intermediate_size, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
 
         def r(*s, scale):
-            return (torch.randn(*s, generator=g) * scale).to(dtype)
+            return (torch.randn(*s, generator=g, device=device) * scale).to(dtype)
+
+        def norm_w():
+            return (1 + 0.1 * torch.randn(D, generator=g, device=device)).to(dtype)
         w = cls(cfg)
         w.tok_emb = r(cfg.vocab_size, D, scale=1.0)
         for _ in range(cfg.num_hidden_layers):
-            w.layers.append(dict(attn_norm=(1 + 0.1 * torch.randn(D, generator=g)).to(dtype),
-                                 wqkv=r((H + 2 * Hk) * Dh, D, scale=D ** -0.5), wo=r(D, H * Dh, scale=(H * Dh) ** -0.5),
-                                 ffn_norm=(1 + 0.1 * torch.randn(D, generator=g)).to(dtype),
-                                 w_gate_up=r(2 * I, D, scale=D ** -0.5), w_down=r(D, I, scale=I ** -0.5)))
-        w.final_norm = (1 + 0.1 * torch.randn(D, generator=g)).to(dtype)
+            w.layers.append(dict(attn_norm=norm_w(), wqkv=r((H + 2 * Hk) * Dh, D, scale=D ** -0.5), wo=r(D, H * Dh, scale=(H * Dh) ** -0.5),
+                                 ffn_norm=norm_w(), w_gate_up=r(2 * I, D, scale=D ** -0.5), w_down=r(D, I, scale=I ** -0.5)))
+        w.final_norm = norm_w()
         w.lm_head = r(cfg.vocab_size, D, scale=D ** -0.5)
         return w
 
