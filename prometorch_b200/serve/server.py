@@ -146,8 +146,9 @@ class PagedBackend(ModelBackend):
 
     def __init__(self, model_dir: str, name: str, device: str = "cuda", max_active: int = 16, max_pages: int = 2048):
         import os
+        import torch
         from .llm import EngineServer, LLMEngine
-        dev = device if (device != "cuda" or __import__("torch").cuda.is_available()) else "cpu"
+        dev = "cpu" if (device == "cuda" and not torch.cuda.is_available()) else device
         self.engine = LLMEngine(device=dev, max_pages=max_pages, max_active=max_active)
         if not self.engine.load(model_dir) or not self.engine.loaded:
             raise KeyError(f"'{model_dir}' is not a loadable Hugging Face Llama directory")
