@@ -7,6 +7,8 @@ from .tokenizer import GGUFTokenizer
 from .chat import apply_chat_template, render_messages, strip_think
 from .ollama import list_models, resolve_model
 from .synthetic import write_synthetic_gguf
+from .model_loader import ModelWeights, detect_format, load_model, read_tensor  # noqa: F401
+from . import safetensors  # noqa: F401
 
 
 def __getattr__(name):

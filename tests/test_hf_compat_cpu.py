@@ -134,3 +134,54 @@ def test_tokenizers(tmp_path):
     assert ids == [vocab["hello"]] and tok.decode(ids) == "hello"
     with pytest.raises(FileNotFoundError):
         AutoTokenizer.from_pretrained(str(tmp_path / "nothing"))
+
+
+def test_model_loader_sniffs_and_describes_every_container(tmp_path):
+    """detect_format by content, tensor metadata, inferred architecture / shape parameters, lazy tensor reads."""
+    from prometorch_b200 import serialization
+    from prometorch_b200.io.model_loader import detect_format, find_shard_files, infer_architecture, load_model, read_tensor
+    from prometorch_b200.io.config import tiny_qwen3_config
+    from prometorch_b200.io.synthetic import write_synthetic_gguf
+    from prometorch_b200.serve.llm import LlamaConfig, LlamaWeights
+    cfg = LlamaConfig(vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, max_position_embeddings=256)
+    sd = LlamaWeights.random(cfg, seed=1).state_dict()
+    st = str(tmp_path / "weights.bin")                      # wrong extension on purpose: content decides
+    save_file(sd, st)
+    pt, ptor = str(tmp_path / "m.safetensors.pt"), str(tmp_path / "m.ptor")
+    serialization.save_pytorch(dict(sd), pt)
+    serialization.save_state_dict(dict(sd), ptor)
+    gg = str(tmp_path / "tiny.gguf")
+    write_synthetic_gguf(gg, tiny_qwen3_config(), seed=0)
+    assert [detect_format(p) for p in (st, pt, ptor, gg)] == ["safetensors", "pytorch", "ptor", "gguf"]
+    (tmp_path / "junk.dat").write_bytes(b"\\x00\\x01\\x02\\x03 not a model")
+    assert detect_format(str(tmp_path / "junk.dat")) == "unknown" and detect_format(str(tmp_path / "missing")) == "unknown"
+    for path in (st, pt, ptor):
+        mw = load_model(path)
+        assert mw.architecture == "llama" and len(mw.tensors) == len(sd) and mw.total_parameters() == sum(t.numel() for t in sd.values())
+        c = mw.config
+        assert (c.vocab_size, c.hidden_size, c.num_layers, c.intermediate_size) == (300, 64, 2, 96) and not c.tie_word_embeddings
+        assert torch.equal(read_tensor(mw, "model.norm.weight"), sd["model.norm.weight"])
+    g = load_model(gg)
+    assert g.format == "gguf" and g.architecture == "qwen3" and g.config.num_layers >= 1 and g.config.num_heads >= 1
+    assert read_tensor(g, "token_embd.weight").shape[1] == g.config.hidden_size
+    # a Hugging Face directory with two shards and a config
+    d = tmp_path / "hf"
+    d.mkdir()
+    names = sorted(sd)
+    save_file({k: sd[k] for k in names[:7]}, str(d / "model-00001-of-00002.safetensors"))
+    save_file({k: sd[k] for k in names[7:]}, str(d / "model-00002-of-00002.safetensors"))
+    (d / "model.safetensors.index.json").write_text(json.dumps(
+        {"weight_map": {k: f"model-0000{1 if i < 7 else 2}-of-00002.safetensors" for i, k in enumerate(names)}}))
+    (d / "config.json").write_text(json.dumps({"model_type": "llama", "hidden_size": 64, "num_hidden_layers": 2, "num_attention_heads": 4,
+                                               "num_key_value_heads": 2, "intermediate_size": 96, "vocab_size": 300, "rope_theta": 5e5,
+                                               "max_position_embeddings": 256}))
+    assert detect_format(str(d)) == "hf_dir" and len(find_shard_files(str(d))) == 2
+    h = load_model(str(d))
+    assert h.architecture == "llama" and len(h.tensors) == len(sd) and h.config.num_kv_heads == 2 and h.config.head_dim == 16
+    assert h.config.rope_freq_base == 5e5 and h.config.context_length == 256
+    assert torch.equal(read_tensor(h, names[-1]), sd[names[-1]])
+    assert infer_architecture(["bert.encoder.layer.0.attention.self.query.weight"]) == "bert"
+    assert infer_architecture(["transformer.h.0.attn.c_attn.weight"]) == "gpt2"
+    with pytest.raises(ValueError):
+        load_model(str(tmp_path / "junk.dat"))
