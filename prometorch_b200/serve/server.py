@@ -82,6 +82,7 @@ class ModelBackend:
 
     name = "model"
     architecture = "llama"
+    format = "gguf"
     model_name = ""
     size = 0
     parameter_size = ""
@@ -143,6 +144,7 @@ class PagedBackend(ModelBackend):
     batches (the reference's server takes one generation at a time, promeserve/api_handlers.h:769-790)."""
     concurrent = True
     architecture = "llama"
+    format = "safetensors"
 
     def __init__(self, model_dir: str, name: str, device: str = "cuda", max_active: int = 16, max_pages: int = 2048):
         import os
@@ -220,7 +222,7 @@ class ApiHandlers:
         for name, b in self.backends.items():
             seen.add(name)
             models.append({"name": name, "model": name, "modified_at": _now(), "size": b.size, "digest": "",
-                           "details": {"family": b.architecture, "format": "gguf", "parameter_size": b.parameter_size}})
+                           "details": {"family": b.architecture, "format": b.format, "parameter_size": b.parameter_size}})
         try:
             for m in list_models(extra_dirs=self.config.model_dirs):
                 if m["name"] not in seen:
@@ -232,7 +234,7 @@ class ApiHandlers:
 
     def show(self, body):
         b = self.ensure_model(body.get("model") or body.get("name") or "")
-        return {"modelfile": "", "parameters": "", "template": "", "details": {"family": b.architecture, "format": "gguf",
+        return {"modelfile": "", "parameters": "", "template": "", "details": {"family": b.architecture, "format": b.format,
                                                                                  "parameter_size": b.parameter_size},
                 "model_info": {"general.architecture": b.architecture, "general.name": b.model_name}}
 

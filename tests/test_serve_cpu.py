@@ -186,7 +186,9 @@ def test_rest_server_serves_hf_directory_concurrently(tmp_path):
         show = json.loads(urllib.request.urlopen(urllib.request.Request(
             f"http://127.0.0.1:{srv.port}/api/show", data=json.dumps({"model": d}).encode(), headers={"Content-Type": "application/json"}),
             timeout=30).read())
-        assert show["details"]["family"] == "llama"
+        assert show["details"]["family"] == "llama" and show["details"]["format"] == "safetensors"
+        tags = json.loads(urllib.request.urlopen(f"http://127.0.0.1:{srv.port}/api/tags", timeout=30).read())
+        assert any(m["name"] == d and m["details"]["format"] == "safetensors" for m in tags["models"])
     finally:
         srv.stop()
 
