@@ -185,3 +185,21 @@ def test_model_loader_sniffs_and_describes_every_container(tmp_path):
     assert infer_architecture(["transformer.h.0.attn.c_attn.weight"]) == "gpt2"
     with pytest.raises(ValueError):
         load_model(str(tmp_path / "junk.dat"))
+
+
+def test_legacy_pytorch_model_bin_directory(tmp_path):
+    """A directory that only has ``pytorch_model.bin`` (written by torch.save) loads through the restricted .pt reader."""
+    from prometorch_b200.io.model_loader import load_model
+    cfg = transformers.GPT2Config(vocab_size=90, n_embd=32, n_layer=1, n_head=2, n_positions=32, resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0)
+    torch.manual_seed(4)
+    ref = transformers.GPT2Model(cfg).eval()
+    d = tmp_path / "legacy"
+    d.mkdir()
+    (d / "config.json").write_text(json.dumps(cfg.to_dict()))
+    torch.save({k: v.clone() for k, v in ref.state_dict().items()}, str(d / "pytorch_model.bin"))
+    ours = AutoModel.from_pretrained(str(d))
+    ids = _ids(90, T=9, seed=6)
+    with torch.no_grad():
+        assert torch.allclose(ours(ids), ref(input_ids=ids).last_hidden_state, atol=2e-5)
+    mw = load_model(str(d))
+    assert mw.architecture == "gpt2" and mw.config.num_layers == 1 and mw.config.hidden_size == 32 and mw.format == "pytorch"
