@@ -324,6 +324,21 @@ class LLMEngine:
                 return Response(request_id=rid)
         return mine
 
+    def stream(self, prompt, config: Optional[GenerationConfig] = None):
+        """Generator over the ids of one request as they are produced (other queued requests keep advancing with it)."""
+        rid = self._next_id
+        fresh: List[int] = []
+        self.submit_request(Request(rid, prompt, config or GenerationConfig(), lambda t: fresh.append(t) or True))
+        while True:
+            alive = any(s.request_id == rid for s in self.active) or any(s.request_id == rid for s in self.pending)
+            if not alive and not fresh:
+                break
+            if alive:
+                self.step()
+            while fresh:
+                yield fresh.pop(0)
+        self.done = [r for r in self.done if r.request_id != rid]
+
     def submit_request(self, req: Request):
         ids = self._encode(req.prompt)
         self._next_id = max(self._next_id, req.request_id + 1)

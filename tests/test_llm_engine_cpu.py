@@ -266,3 +266,19 @@ def test_batched_prompt_pass_groups_and_token_cap():
             got.update({r.request_id: r.token_ids for r in eng.poll_responses()})
         assert got == {i: want[i] for i in range(6)}
         assert calls == ([6] if cap == 16384 else [2, 2, 1, 1]), calls        # 21+21 | 21+8 | 67 | 67 tokens under a cap of 50
+
+
+def test_stream_yields_tokens_as_they_come():
+    w = LlamaWeights.random(tiny_cfg(), seed=23)
+    eng = LLMEngine(device="cpu", max_pages=8, max_active=2)
+    eng.set_weights(w)
+    prompt = [1, 9, 33, 7]
+    eng.submit_request(Request(50, [1, 2, 3], GenerationConfig(max_new_tokens=4, **GREEDY)))      # a neighbour in the batch
+    seen = []
+    for t in eng.stream(prompt, GenerationConfig(max_new_tokens=7, **GREEDY)):
+        seen.append(t)
+        assert eng.steps >= len(seen)                                 # ids arrive step by step, not at the end
+    assert seen == dense_generate(w, prompt, 7)
+    while eng.num_active():
+        eng.step()
+    assert [r.request_id for r in eng.poll_responses()] == [50]
