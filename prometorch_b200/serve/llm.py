@@ -546,7 +546,27 @@ class LLMEngine:
         """All prompt tokens of one request; fills its pages; returns the logits of the last position ``[1, V]``."""
         return self._forward_prompts([s])
 
-    def _forward_prompts(self, batch: List[RequestState]) -> torch.Tensor:
+    @torch.no_grad()
+    def embed(self, prompt) -> torch.Tensor:
+        """Mean of the final-norm hidden states over the prompt's tokens, L2-normalised ``[hidden]`` fp32 (a sentence
+        embedding from the decoder; the reference's server answers 501 to ``/api/embeddings``).  Call it from the thread
+        that runs the engine, between steps; it borrows a page-table row and returns its pages when it is done."""
+        ids = self._encode(prompt)[: self.cfg.max_position_embeddings - 1]
+        if not self.free_rows:
+            raise RuntimeError("embed: every page-table row is in use")
+        s = RequestState(-1, GenerationConfig(), list(ids), len(ids), time.perf_counter(), prompt_ids=list(ids))
+        s.row = self.free_rows.pop()
+        try:
+            if not self._ensure_pages(s, s.prompt_len - 1):
+                raise RuntimeError("embed: the page pool cannot hold this prompt now")
+            h = self._forward_prompts([s], hidden=True).float().mean(0)
+            return h / h.norm().clamp_min(1e-12)
+        finally:
+            for p in s.pages:
+                self.kv.free_page(p)
+            self.free_rows.append(s.row)
+
+    def _forward_prompts(self, batch: List[RequestState], hidden: bool = False) -> torch.Tensor:
         """The prompt pass of several new requests at once: their tokens are concatenated, so every projection is one
         GEMM over all of them; attention runs per request (requests of equal length share a call).  Fills the pages;
         returns the logits of each request's last position ``[len(batch), V]``."""
@@ -580,6 +600,8 @@ class LLMEngine:
                     a[lo:hi] = flash_attention(q, k[lo:hi].view(nb, n, Hk, Dh), v, causal=True).reshape(nb * n, H * Dh)
             x = x + self._linear(a, L["wo"])
             x = x + self._mlp(self._norm(x, L["ffn_norm"]), L)
+        if hidden:                                             # the embedding path: every position after the final norm
+            return self._norm(x, w.final_norm)
         last = x[torch.tensor([o - 1 for o in offs[1:]], device=dev)]
         return self._linear(self._norm(last, w.final_norm), w.lm_head).float()
 
@@ -706,6 +728,7 @@ class EngineServer:
         self.engine = engine
         self._cv = threading.Condition()
         self._inbox: List[tuple] = []
+        self._calls: List[tuple] = []
         self._handles: Dict[int, "EngineServer.Handle"] = {}
         self._next = 0
         self._stop = False
@@ -728,6 +751,19 @@ class EngineServer:
             self._cv.notify()
         return h
 
+    def call(self, fn, timeout: Optional[float] = 60.0):
+        """Run ``fn(engine)`` on the scheduler thread between two steps and return its result (or raise what it raised)."""
+        import threading
+        box = {"done": threading.Event()}
+        with self._cv:
+            self._calls.append((fn, box))
+            self._cv.notify()
+        if not box["done"].wait(timeout):
+            raise TimeoutError("the engine thread did not get to the call in time")
+        if "error" in box:
+            raise box["error"]
+        return box.get("value")
+
     def close(self):
         with self._cv:
             self._stop = True
@@ -740,11 +776,18 @@ class EngineServer:
             torch.cuda.set_device(eng.device)
         while True:
             with self._cv:
-                while not self._stop and not self._inbox and eng.num_active() == 0:
+                while not self._stop and not self._inbox and not self._calls and eng.num_active() == 0:
                     self._cv.wait()
                 if self._stop:
                     return
                 inbox, self._inbox = self._inbox, []
+                calls, self._calls = self._calls, []
+            for fn, box in calls:
+                try:
+                    box["value"] = fn(eng)
+                except Exception as e:                                # noqa: BLE001
+                    box["error"] = e
+                box["done"].set()
             for req in inbox:
                 try:
                     eng.submit_request(req)

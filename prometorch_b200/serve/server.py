@@ -166,6 +166,10 @@ class PagedBackend(ModelBackend):
     def decode_token(self, tid):
         return self.engine.tokenizer.decode([tid])
 
+    def embed(self, text: str):
+        """Sentence embedding of ``text`` (list of floats), computed on the engine's thread between decode steps."""
+        return self.server.call(lambda eng: eng.embed(text).cpu().tolist())
+
     def generate(self, prompt_ids, options, on_token):
         from .llm import GenerationConfig
         cfg = GenerationConfig(max_new_tokens=int(options.get("num_predict", 128)), temperature=float(options.get("temperature", 0.7)),
@@ -446,7 +450,23 @@ class HttpServer:
         if method == "GET" and path == "/api/tags":
             return self._send(wfile, 200, json.dumps(H.tags()).encode())
         if method == "POST" and path in ("/api/embeddings", "/api/embed"):
-            return self._send(wfile, 501, json.dumps({"error": "embeddings are not implemented"}).encode())
+            # backends that can embed (the paged engine) answer; for the others this stays 501 as in the reference
+            try:
+                req = json.loads(raw or b"{}")
+                backend = H.ensure_model(req.get("model", ""))
+            except Exception:                                         # noqa: BLE001
+                backend = None
+            if backend is None or not hasattr(backend, "embed"):
+                return self._send(wfile, 501, json.dumps({"error": "embeddings are not implemented"}).encode())
+            text = req.get("prompt") if req.get("prompt") is not None else req.get("input", "")
+            try:
+                if isinstance(text, list):
+                    out = {"model": req.get("model", ""), "embeddings": [backend.embed(str(t)) for t in text]}
+                else:
+                    out = {"model": req.get("model", ""), "embedding": backend.embed(str(text))}
+            except Exception as e:                                    # noqa: BLE001
+                return self._send(wfile, 500, json.dumps({"error": str(e)}).encode())
+            return self._send(wfile, 200, json.dumps(out).encode(), "application/json")
         if method == "POST" and path in ("/api/generate", "/api/chat", "/api/show"):
             try:
                 body = json.loads(raw.decode("utf-8") or "{}")

@@ -282,3 +282,14 @@ def test_stream_yields_tokens_as_they_come():
     while eng.num_active():
         eng.step()
     assert [r.request_id for r in eng.poll_responses()] == [50]
+
+
+def test_embed_returns_pages_and_matches_dense_hidden_mean():
+    w = LlamaWeights.random(tiny_cfg(), seed=29)
+    eng = LLMEngine(device="cpu", max_pages=4, max_active=1)
+    eng.set_weights(w)
+    ids = [1, 7, 50, 3, 3, 90]
+    e = eng.embed(ids)
+    assert e.shape == (64,) and abs(float(e.norm()) - 1.0) < 1e-5 and eng.kv.pages_in_use == 0 and eng.free_rows == [0]
+    assert torch.allclose(e, eng.embed(ids)) and not torch.allclose(e, eng.embed(ids[:-1] + [91]))
+    assert eng.generate(ids, GenerationConfig(max_new_tokens=3, **GREEDY)).token_ids == dense_generate(w, ids, 3)   # the engine still serves

@@ -187,6 +187,13 @@ def test_rest_server_serves_hf_directory_concurrently(tmp_path):
             f"http://127.0.0.1:{srv.port}/api/show", data=json.dumps({"model": d}).encode(), headers={"Content-Type": "application/json"}),
             timeout=30).read())
         assert show["details"]["family"] == "llama" and show["details"]["format"] == "safetensors"
+        def post(path, body):
+            req = urllib.request.Request(f"http://127.0.0.1:{srv.port}{path}", data=json.dumps(body).encode(), headers={"Content-Type": "application/json"})
+            return json.loads(urllib.request.urlopen(req, timeout=60).read())
+        e1 = post("/api/embeddings", {"model": d, "prompt": "hello world"})["embedding"]
+        e2 = post("/api/embed", {"model": d, "input": ["hello world", "something else"]})["embeddings"]
+        assert len(e1) == 64 and abs(sum(x * x for x in e1) - 1.0) < 1e-3 and len(e2) == 2
+        assert max(abs(a - b) for a, b in zip(e1, e2[0])) < 1e-5 and max(abs(a - b) for a, b in zip(e1, e2[1])) > 1e-3
         tags = json.loads(urllib.request.urlopen(f"http://127.0.0.1:{srv.port}/api/tags", timeout=30).read())
         assert any(m["name"] == d and m["details"]["format"] == "safetensors" for m in tags["models"])
     finally:
