@@ -96,6 +96,8 @@ def test_engine_logits_and_batching_match_cpu_engine():
         for s, l in zip(e.active, lc):
             s.input_ids = [int(l.argmax())]
             assert e._ensure_pages(s, s.kv_position)
+    eg, ec = gpu.embed(prompts[0]), cpu.embed(prompts[0])            # one page-table row is still free on both
+    assert float(torch.nn.functional.cosine_similarity(eg.cpu(), ec, dim=0)) > 0.995
     dg, dc = gpu._forward_decode(gpu.active).float().cpu(), cpu._forward_decode(cpu.active)
     assert dg.shape == (3, 1024) and _rel(dg, dc) < 3e-2, _rel(dg, dc)
     # a full run: sampled and greedy requests together, pages come back
