@@ -1,4 +1,6 @@
-"""Serving: PromeServe (Ollama-compatible REST, :mod:`.server`) and ``LLMEngine`` (request queue over one model).
+"""Serving: PromeServe (Ollama-compatible REST, :mod:`.server`), ``LLMEngine`` (request queue over one GGUF model) and
+the continuous-batching engine over a paged KV cache for Hugging Face Llama directories (:mod:`.llm`: ``PagedLLMEngine``,
+``EngineServer``; the server's ``PagedBackend`` uses it).
 
 ``python -m prometorch_b200.serve --port 11434 --device cuda --model NAME --workers N --queue-depth N --timeout-ms MS``
 starts the server (same flags as the reference's ``promeserve`` binary, promeserve/main.cpp:40-105)."""
