@@ -266,6 +266,7 @@ class LLMEngine:
         self._next_id = 0
         self._gen = torch.Generator().manual_seed(seed)
         self.steps = 0
+        self.tokens_generated = 0
         self.launch_log: List[int] = []          # batch size of every decode pass (tests and metrics read it)
         self.use_graphs = use_graphs
         self._graphs: Dict[tuple, tuple] = {}
@@ -347,6 +348,30 @@ class LLMEngine:
         self.pending.append(RequestState(req.request_id, req.config, list(ids), len(ids), time.perf_counter(), prompt_ids=list(ids),
                                          on_token=req.on_token))
         self._admit_pending()
+
+    def cancel(self, request_id: int) -> bool:
+        """Drop a queued request or end a running one at the next step (its pages go back to the pool; it still gets a
+        response with what it produced).  Returns whether the id was found."""
+        for s in list(self.pending):
+            if s.request_id == request_id:
+                self.pending.remove(s)
+                self.done.append(Response(request_id=request_id))
+                return True
+        for s in self.active:
+            if s.request_id == request_id:
+                s.done = True
+                if not s.prefill_done:                     # never ran: nothing to decode, and no prompt pass either
+                    s.prefill_done = True
+                self._collect_done()
+                return True
+        return False
+
+    def stats(self) -> Dict[str, float]:
+        """Counters for logs and dashboards."""
+        return {"active": len(self.active), "pending": len(self.pending), "steps": self.steps,
+                "pages_in_use": self.kv.pages_in_use if self.kv is not None else 0, "pages_total": self.max_pages,
+                "tokens_generated": self.tokens_generated, "graphs": len(self._graphs),
+                "spec_drafted": self.spec_drafted, "spec_accepted": self.spec_accepted}
 
     def poll_responses(self) -> List[Response]:
         out, self.done = self.done, []
@@ -499,6 +524,7 @@ class LLMEngine:
         return True
 
     def _emit(self, s: RequestState, tok: int):
+        self.tokens_generated += 1
         s.output_ids.append(tok)
         s.input_ids = [tok]
         c = s.config

@@ -293,3 +293,25 @@ def test_embed_returns_pages_and_matches_dense_hidden_mean():
     assert e.shape == (64,) and abs(float(e.norm()) - 1.0) < 1e-5 and eng.kv.pages_in_use == 0 and eng.free_rows == [0]
     assert torch.allclose(e, eng.embed(ids)) and not torch.allclose(e, eng.embed(ids[:-1] + [91]))
     assert eng.generate(ids, GenerationConfig(max_new_tokens=3, **GREEDY)).token_ids == dense_generate(w, ids, 3)   # the engine still serves
+
+
+def test_cancel_and_stats():
+    w = LlamaWeights.random(tiny_cfg(), seed=31)
+    eng = LLMEngine(device="cpu", max_pages=8, max_active=1)
+    eng.set_weights(w)
+    eng.submit_request(Request(1, [1, 4, 5], GenerationConfig(max_new_tokens=50, **GREEDY)))
+    eng.submit_request(Request(2, [1, 6, 7], GenerationConfig(max_new_tokens=5, **GREEDY)))      # waits: one slot only
+    for _ in range(3):
+        eng.step()
+    st = eng.stats()
+    assert st["active"] == 1 and st["pending"] == 1 and st["pages_in_use"] == 1 and st["tokens_generated"] == 3 and st["steps"] == 3
+    assert eng.cancel(1) and not eng.cancel(99)
+    got = {r.request_id: r.token_ids for r in eng.poll_responses()}
+    assert len(got[1]) == 3 and eng.kv.pages_in_use == 0
+    while eng.num_active():
+        eng.step()
+    got.update({r.request_id: r.token_ids for r in eng.poll_responses()})
+    assert got[2] == dense_generate(w, [1, 6, 7], 5)
+    eng.submit_request(Request(3, [1, 2], GenerationConfig(max_new_tokens=5, **GREEDY)))
+    eng.submit_request(Request(4, [1, 3], GenerationConfig(max_new_tokens=5, **GREEDY)))
+    assert eng.cancel(4) and [r.request_id for r in eng.poll_responses()] == [4]               # cancelled while queued
