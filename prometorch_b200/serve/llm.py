@@ -741,6 +741,7 @@ class EngineServer:
         def __init__(self):
             import threading
             self.event = threading.Event()
+            self.request_id = -1
             self.response: Optional[Response] = None
             self.t_submit = time.perf_counter()
             self.t_first: Optional[float] = None
@@ -772,6 +773,7 @@ class EngineServer:
         with self._cv:
             rid = self._next
             self._next += 1
+            h.request_id = rid
             self._handles[rid] = h
             self._inbox.append(Request(rid, prompt, config, hook))
             self._cv.notify()

@@ -191,7 +191,12 @@ class PagedBackend(ModelBackend):
             except queue.Empty:
                 continue
             if not stop["flag"] and not on_token(tok):
-                stop["flag"] = True
+                stop["flag"] = True                               # the client is gone or timed out: end the request now,
+                rid = h.request_id                                # not after one more decode pass
+                try:
+                    self.server.call(lambda eng: eng.cancel(rid), timeout=30.0)
+                except TimeoutError:
+                    pass                                          # the hook's False ends it at the next token anyway
         t_end = time.perf_counter()
         t_first = h.t_first if h.t_first is not None else t_end
         return t_first - h.t_submit, t_end - t_first

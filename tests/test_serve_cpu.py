@@ -222,3 +222,15 @@ def test_engine_server_survives_a_failing_step(tmp_path):
     r2 = srv.submit([1, 7, 8], GenerationConfig(max_new_tokens=6, **greedy)).wait(60)
     assert r2 is not None and 1 <= len(r2.token_ids) <= 6 and eng.kv.pages_in_use == 0
     srv.close()
+
+
+def test_paged_backend_stops_when_the_client_hook_says_so(tmp_path):
+    from prometorch_b200.serve.server import PagedBackend
+    d, _ = _tiny_hf_dir(tmp_path)
+    b = PagedBackend(d, "tiny", device="cpu", max_active=2, max_pages=16)
+    seen = []
+    pe, ev = b.generate([1, 5, 9], {"num_predict": 40, "temperature": 0.0, "repeat_penalty": 1.0, "top_k": 1},
+                        lambda t: seen.append(t) or len(seen) < 3)
+    assert len(seen) == 3 and pe >= 0 and ev >= 0
+    assert b.server.call(lambda eng: (eng.num_active(), eng.kv.pages_in_use)) == (0, 0)
+    b.server.close()
