@@ -112,6 +112,11 @@ class Optimizer(torch.optim.Optimizer):
             _, idx, name = key.split(".", 2)
             st = self.state[params[int(idx)]]
             st[name] = v.clone() if name != "step" else torch.as_tensor(float(v))
+        # the bias corrections and first-step rules read the group's counter: resume it from the restored steps
+        for g in self.param_groups:
+            steps = [float(self.state[p]["step"]) for p in g["params"] if "step" in self.state.get(p, {})]
+            if steps:
+                g["_step"] = int(max(steps))
 
     def set_grad_source(self, param: torch.Tensor, grad: Optional[torch.Tensor]):
         """Read this parameter's gradient from ``grad`` instead of ``param.grad``.  PyTorch only lets
@@ -151,12 +156,14 @@ class Optimizer(torch.optim.Optimizer):
             ps = [p for p in group["params"] if self._grad(p) is not None]
             if not ps:
                 continue
+            if "_step" not in group:        # state restored by another route: continue from its step count
+                group["_step"] = int(max((float(self.state[p]["step"]) for p in ps if "step" in self.state[p]), default=0))
             for p in ps:
                 st = self.state[p]
                 if "step" not in st:
                     st.update(self._init_state(p, group))
                     st["step"] = torch.tensor(0.0)
-            group["_step"] = group.get("_step", 0) + 1
+            group["_step"] = group["_step"] + 1
             step = group["_step"]
             for p in ps:
                 self.state[p]["step"] += 1

@@ -6,7 +6,7 @@ from .server import PromeServe, ServerConfig
 
 def main():
     ap = argparse.ArgumentParser("promeserve")
-    ap.add_argument("--host", default="0.0.0.0")
+    ap.add_argument("--host", default="127.0.0.1", help="bind address; 0.0.0.0 serves other machines")
     ap.add_argument("--port", type=int, default=11434)
     ap.add_argument("--device", default="cuda")
     ap.add_argument("--model", default=None)
@@ -15,8 +15,18 @@ def main():
     ap.add_argument("--timeout-ms", type=int, default=60000)
     ap.add_argument("--model-dir", action="append", default=[])
     ap.add_argument("--max-seq", type=int, default=4096)
+    ap.add_argument("--max-models", type=int, default=2, help="models kept loaded at once")
+    ap.add_argument("--allow-model-paths", action="store_true", help="let requests name models by filesystem path")
     a = ap.parse_args()
-    srv = PromeServe(ServerConfig(a.host, a.port, a.workers, a.queue_depth, a.timeout_ms, a.device, a.model, a.model_dir, a.max_seq)).start()
+    # --model comes from the operator, so it may be a path even when requests may not name paths
+    cfg = ServerConfig(a.host, a.port, a.workers, a.queue_depth, a.timeout_ms, a.device, None, a.model_dir, a.max_seq,
+                       a.max_models, allow_model_paths=True)
+    srv = PromeServe(cfg)
+    if a.model:
+        srv.handlers.ensure_model(a.model)
+        srv.handlers.pinned.add(a.model)
+    cfg.allow_model_paths = a.allow_model_paths
+    srv.start()
     print(f"[PromeServe] listening on {a.host}:{srv.port}")
     try:
         while True:

@@ -29,7 +29,7 @@ VERSION = "0.1.0-promeserve"
 
 @dataclass
 class ServerConfig:
-    host: str = "0.0.0.0"
+    host: str = "127.0.0.1"             # loopback by default; pass 0.0.0.0 to serve other machines
     port: int = 11434
     worker_threads: int = 4
     max_queue_depth: int = 128
@@ -38,6 +38,9 @@ class ServerConfig:
     model: Optional[str] = None
     model_dirs: List[str] = field(default_factory=list)
     max_seq: int = 4096
+    max_loaded_models: int = 2          # models resident on the GPU at once; the least recently used one is dropped
+    max_body_bytes: int = 8 << 20       # larger request bodies are answered 413
+    allow_model_paths: bool = False     # let a request name a model by filesystem path (off: names only)
 
 
 def _now() -> str:
@@ -100,6 +103,9 @@ class ModelBackend:
 
 
 class GGUFBackend(ModelBackend):
+    def close(self):
+        self.model.close()
+
     def __init__(self, path: str, name: str, device: str = "cuda", max_seq: int = 4096):
         import os
         from ..io.gguf_model import GGUFModel
@@ -209,21 +215,41 @@ class ApiHandlers:
         self.backends: Dict[str, ModelBackend] = dict(backends or {})
         self.loader = loader
         self.generate_mutex = threading.Lock()
+        self.load_mutex = threading.Lock()
+        self.pinned = set(self.backends)          # backends handed in by the host program are never evicted
         self.tools_max_iters = 5
 
     # ------------------------------------------------------------------ model management
-    def ensure_model(self, name: str) -> ModelBackend:
+    def _lookup(self, name: str) -> Optional[ModelBackend]:
         if name in self.backends:
+            self.backends[name] = self.backends.pop(name)       # most recently used goes last
             return self.backends[name]
         base = name.split(":")[0]
         for k, b in self.backends.items():
             if k.split(":")[0] == base:
                 return b
+        return None
+
+    def ensure_model(self, name: str) -> ModelBackend:
+        b = self._lookup(name)
+        if b is not None:
+            return b
         if self.loader is None:
             raise KeyError(f"model '{name}' not found")
-        b = self.loader(name)
-        self.backends[name] = b
-        return b
+        with self.load_mutex:                    # one load at a time; a second request for the same name finds it cached
+            b = self._lookup(name)
+            if b is not None:
+                return b
+            loaded = [k for k in self.backends if k not in self.pinned]
+            while loaded and len(loaded) >= max(1, self.config.max_loaded_models):
+                with self.generate_mutex:        # never drop a model in the middle of its generation
+                    old = self.backends.pop(loaded.pop(0))
+                    close = getattr(old, "close", None)
+                    if close:
+                        close()
+            b = self.loader(name)
+            self.backends[name] = b
+            return b
 
     def tags(self):
         from ..io.ollama import list_models
@@ -414,7 +440,7 @@ class HttpServer:
 
     # ------------------------------------------------------------------ HTTP
     @staticmethod
-    def _read_request(rfile):
+    def _read_request(rfile, max_body: int = 8 << 20):
         line = rfile.readline(65536).decode("latin1").strip()
         if not line:
             return None
@@ -426,7 +452,12 @@ class HttpServer:
                 break
             k, _, v = h.partition(":")
             headers[k.strip().lower()] = v.strip()
-        n = int(headers.get("content-length", "0") or 0)
+        try:
+            n = int(headers.get("content-length", "0") or 0)
+        except ValueError:
+            n = -1
+        if n < 0 or n > max_body:
+            return method.upper(), path.split("?")[0], headers, None       # the caller answers 413
         body = rfile.read(n) if n else b""
         return method.upper(), path.split("?")[0], headers, body
 
@@ -439,11 +470,13 @@ class HttpServer:
 
     def _handle(self, conn):
         rfile, wfile = conn.makefile("rb"), conn.makefile("wb")
-        req = self._read_request(rfile)
+        req = self._read_request(rfile, self.config.max_body_bytes)
         if req is None:
             return
         method, path, headers, raw = req
         H = self.handlers
+        if raw is None:
+            return self._send(wfile, 413, json.dumps({"error": "request body too large"}).encode())
         if method == "OPTIONS":
             return self._send(wfile, 204, b"")
         if method == "HEAD":
@@ -509,14 +542,21 @@ class PromeServe:
         def loader(name: str) -> ModelBackend:
             from ..io.ollama import resolve_model
             import os
-            if os.path.isdir(name) and os.path.isfile(os.path.join(name, "config.json")):
-                return PagedBackend(name, name, self.config.device)      # a Hugging Face directory: the paged engine serves it
-            path = name if os.path.isfile(name) else None
+            path = None
+            if self.config.allow_model_paths:
+                if os.path.isdir(name) and os.path.isfile(os.path.join(name, "config.json")):
+                    return PagedBackend(name, name, self.config.device)  # a Hugging Face directory: the paged engine serves it
+                path = name if os.path.isfile(name) else None
+            elif os.path.isabs(name) or ".." in name.replace("\\", "/").split("/") or "/" in name or "\\" in name:
+                # a request names models, not files: only model_dirs and the Ollama store are searched
+                raise KeyError(f"model '{name}' not found (paths are not accepted as model names)")
             if path is None:
                 for d in self.config.model_dirs:
-                    cand = os.path.join(d, name.split(":")[0] + ".gguf")
-                    if os.path.isfile(cand):
-                        path = cand
+                    stem = os.path.join(d, name.split(":")[0])
+                    if os.path.isfile(stem + ".gguf"):
+                        path = stem + ".gguf"
+                    elif os.path.isfile(os.path.join(stem, "config.json")):
+                        return PagedBackend(stem, name, self.config.device)
             if path is None:
                 try:
                     path = resolve_model(name)

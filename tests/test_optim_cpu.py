@@ -112,6 +112,27 @@ def test_param_groups_and_state_dict_roundtrip():
         assert torch.allclose(a, b, atol=1e-7)
 
 
+@pytest.mark.parametrize("make", [lambda ps: O.Adam(ps, lr=1e-2), lambda ps: O.SGD(ps, lr=1e-2, momentum=0.9),
+                                  lambda ps: O.RAdam(ps, lr=1e-2)])
+def test_flat_state_resume_continues_the_run(make):
+    """save -> load_flat_state_dict -> step must equal the uninterrupted run (bias correction, momentum buffer)."""
+    import copy
+    ps, loss = _problem(3)
+    opt = make(ps)
+    for _ in range(5):
+        opt.zero_grad(); loss().backward(); opt.step()
+    flat = copy.deepcopy(opt.flat_state_dict())
+    ps2, loss2 = _problem(3)
+    for a, b in zip(ps2, ps):
+        a.data.copy_(b.data)
+    opt2 = make(ps2)
+    opt2.load_flat_state_dict(flat)
+    for o, l in ((opt, loss), (opt2, loss2)):
+        o.zero_grad(); l().backward(); o.step()
+    for a, b in zip(ps, ps2):
+        assert torch.allclose(a, b, atol=1e-7)
+
+
 def test_ema():
     p = torch.nn.Parameter(torch.ones(2))
     e = O.EMA([p], decay=0.9)

@@ -167,8 +167,10 @@ def test_rest_server_serves_hf_directory_concurrently(tmp_path):
     import threading
     import urllib.request
     from prometorch_b200.serve import PromeServe, ServerConfig
-    d, _ = _tiny_hf_dir(tmp_path)
-    srv = PromeServe(ServerConfig(port=0, device="cpu", worker_threads=4)).start()
+    full, _ = _tiny_hf_dir(tmp_path)
+    import os
+    d = os.path.basename(os.path.normpath(full))            # requests name the model; the server looks in model_dirs
+    srv = PromeServe(ServerConfig(port=0, device="cpu", worker_threads=4, model_dirs=[os.path.dirname(os.path.normpath(full))])).start()
     try:
         out = {}
 
@@ -234,3 +236,43 @@ def test_paged_backend_stops_when_the_client_hook_says_so(tmp_path):
     assert len(seen) == 3 and pe >= 0 and ev >= 0
     assert b.server.call(lambda eng: (eng.num_active(), eng.kv.pages_in_use)) == (0, 0)
     b.server.close()
+
+
+def test_server_rejects_paths_big_bodies_and_caps_loaded_models(tmp_path):
+    """A request cannot make the server open arbitrary files, post unbounded bodies or pile up models."""
+    import json
+    import urllib.error
+    import urllib.request
+    from prometorch_b200.serve.server import ApiHandlers, ModelBackend, PromeServe, ServerConfig
+    srv = PromeServe(ServerConfig(port=0, device="cpu", max_body_bytes=1024)).start()
+    try:
+        def post(body: bytes):
+            req = urllib.request.Request(f"http://127.0.0.1:{srv.port}/api/generate", data=body, headers={"Content-Type": "application/json"})
+            try:
+                return urllib.request.urlopen(req, timeout=30).status
+            except urllib.error.HTTPError as e:
+                return e.code
+        assert srv.config.host == "127.0.0.1"
+        for name in ("/etc/passwd", "../../secret", "a/b"):
+            assert post(json.dumps({"model": name, "prompt": "x", "stream": False}).encode()) == 404
+        assert post(b"{" + b" " * 4096 + b"}") == 413
+    finally:
+        srv.stop()
+
+    closed, loads = [], []
+
+    class Fake(ModelBackend):
+        def __init__(self, n):
+            self.name = n
+
+        def close(self):
+            closed.append(self.name)
+
+    def loader(n):
+        loads.append(n)
+        return Fake(n)
+    h = ApiHandlers(ServerConfig(max_loaded_models=2), {"pinned": Fake("pinned")}, loader)
+    for n in ("a", "b", "a", "c"):
+        h.ensure_model(n)
+    assert loads == ["a", "b", "c"] and closed == ["b"]          # "a" was used more recently than "b"
+    assert set(h.backends) == {"pinned", "a", "c"}
