@@ -22,7 +22,7 @@ class NativeError(RuntimeError):
 
 class WeightDesc(C.Structure):
     _fields_ = [("w", C.c_void_p), ("bias", C.c_void_p), ("qtype", C.c_int), ("rows", C.c_int),
-                ("cols", C.c_int), ("rowbytes", C.c_int)]
+                ("cols", C.c_int), ("rowbytes", C.c_int), ("layout", C.c_int), ("pad", C.c_int)]
 
 
 class LayerDesc(C.Structure):
@@ -51,7 +51,7 @@ def lib_path() -> Path:
 def _declare(L: C.CDLL):
     vp, ci, cf, cl = C.c_void_p, C.c_int, C.c_float, C.c_long
     L.ptb_last_error.restype = C.c_char_p
-    L.ptb_gemv.argtypes = [vp, vp, ci, ci, ci, ci, vp, vp, cf, vp, vp, vp, ci, ci, ci, vp, vp, vp]
+    L.ptb_gemv.argtypes = [vp, vp, ci, ci, ci, ci, ci, vp, vp, cf, vp, vp, vp, ci, ci, ci, vp, vp, vp]
     L.ptb_gemv.restype = ci
     L.ptb_attn_decode.argtypes = [vp] * 14 + [ci, ci, ci, ci, cf, ci, vp]
     L.ptb_attn_decode.restype = ci
@@ -77,12 +77,12 @@ def _declare(L: C.CDLL):
         getattr(L, name).restype = vp
     L.ptb_engine_launches_per_token.argtypes = [vp]
     L.ptb_engine_launches_per_token.restype = cl
-    L.ptb_gemv_plan.argtypes = [ci, ci, ci, ci, ci, ci, C.POINTER(ci)]
+    L.ptb_gemv_plan.argtypes = [ci, ci, ci, ci, ci, ci, ci, C.POINTER(ci)]
     L.ptb_gemv_plan.restype = ci
     L.ptb_engine_kv_cache.argtypes = [vp, ci, C.POINTER(vp), C.POINTER(vp)]
     L.ptb_engine_kv_cache.restype = ci
-    L.ptb_dequant_segmajor.argtypes = [vp, ci, ci, ci, vp, vp]
-    L.ptb_dequant_segmajor.restype = ci
+    L.ptb_dequant_weight.argtypes = [vp, ci, ci, ci, ci, vp, vp]
+    L.ptb_dequant_weight.restype = ci
     L.ptb_dequant_rows.argtypes = [vp, ci, ci, ci, vp, ci, cf, ci, vp, vp, vp]
     L.ptb_dequant_rows.restype = ci
 

@@ -14,9 +14,12 @@
 //  * allgather_kernel        — push a local shard into every peer's full buffer.
 //
 // Synchronisation is two flag barriers per call (arrival counters in symmetric
-// memory, release/acquire at system scope).  Every wait is bounded: on expiry
-// the kernel records PTB_ERR_FLAG_TIMEOUT and returns.
+// memory, release/acquire at system scope).  Every wait is bounded by a wall-clock
+// budget (ptb_set_collective_timeout_ms, default 10 s or PTB_COLLECTIVE_TIMEOUT_MS):
+// on expiry the kernel records PTB_ERR_FLAG_TIMEOUT, skips its work, still signals
+// its peers and resets its ticket, so the channel can be used again, and returns.
 #include "common.cuh"
+#include <stdlib.h>
 
 namespace ptb {
 
@@ -25,19 +28,22 @@ constexpr int COLL_THREADS = 512;
 struct PeerSet {
     void* buf[8];             // peer r's data buffer (same layout on every rank)
     uint32_t* flag[8];        // peer r's flag block: [2][8] arrival words (phase, source rank)
+    void* buf2[8];            // optional second buffer per peer (fp32 master gradients of the bucket all-reduce)
     int rank, world;
+    unsigned long long budget_ns;
 };
 
 // All CTAs call this.  `phase` 0: only signals from CTA 0; every CTA waits for all peers.
 __device__ __forceinline__ bool barrier_in(const PeerSet& P, uint32_t seq, int* status) {
     if (blockIdx.x == 0 && threadIdx.x < P.world) st_release_sys(P.flag[threadIdx.x] + 0 * 8 + P.rank, seq);
     bool ok = true;
-    if (threadIdx.x < P.world) ok = wait_flag_ge(P.flag[P.rank] + 0 * 8 + threadIdx.x, seq, status);
+    if (threadIdx.x < P.world) ok = wait_flag_ge(P.flag[P.rank] + 0 * 8 + threadIdx.x, seq, status, P.budget_ns);
     return __syncthreads_and(ok);
 }
 
-// After all CTAs of this rank are done: the last one tells every peer and waits for every peer.
-__device__ __forceinline__ void barrier_out(const PeerSet& P, uint32_t seq, unsigned* ticket, int* status) {
+// After all CTAs of this rank are done: the last one tells every peer and waits for every peer.  `ok` false (the
+// entry barrier ran out of time): the peers are still told and the ticket is still reset, without waiting again.
+__device__ __forceinline__ void barrier_out(const PeerSet& P, uint32_t seq, unsigned* ticket, int* status, bool ok = true) {
     __shared__ bool last;
     __threadfence_system();
     __syncthreads();
@@ -51,7 +57,7 @@ __device__ __forceinline__ void barrier_out(const PeerSet& P, uint32_t seq, unsi
     if (threadIdx.x < P.world) {
         __threadfence_system();
         st_release_sys(P.flag[threadIdx.x] + 1 * 8 + P.rank, seq);
-        wait_flag_ge(P.flag[P.rank] + 1 * 8 + threadIdx.x, seq, status);
+        if (ok) wait_flag_ge(P.flag[P.rank] + 1 * 8 + threadIdx.x, seq, status, P.budget_ns);
     }
     __syncthreads();
     if (threadIdx.x == 0) *ticket = 0u;
@@ -76,12 +82,15 @@ __device__ __forceinline__ void slice_of(long long n_vec, int rank, int world, l
     v1 = n_vec * (rank + 1) / world;
 }
 
-template <bool BF16>
+// MASTER (bf16 buckets only): the reduced, scaled slice is written as fp32 into every peer's second buffer (the
+// master-gradient bucket an fp32 optimizer reads) instead of back into the bf16 bucket: the cast costs no extra pass.
+template <bool BF16, bool MASTER>
 __global__ void __launch_bounds__(COLL_THREADS) ddp_allreduce_kernel(const __grid_constant__ PeerSet P, long long n_vec, float scale,
                                                                    uint32_t seq, unsigned* ticket, int* status) {
-    if (!barrier_in(P, seq, status)) return;
+    const bool ok = barrier_in(P, seq, status);
     long long v0, v1;
     slice_of(n_vec, P.rank, P.world, v0, v1);
+    if (!ok) v1 = v0;
     for (long long v = v0 + (long long)blockIdx.x * COLL_THREADS + threadIdx.x; v < v1; v += (long long)gridDim.x * COLL_THREADS) {
         float acc[8];
 #pragma unroll
@@ -109,6 +118,17 @@ __global__ void __launch_bounds__(COLL_THREADS) ddp_allreduce_kernel(const __gri
         if (BF16) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) acc[j] *= scale;
+            if (MASTER) {
+                const uint4 lo = make_uint4(__float_as_uint(acc[0]), __float_as_uint(acc[1]), __float_as_uint(acc[2]), __float_as_uint(acc[3]));
+                const uint4 hi = make_uint4(__float_as_uint(acc[4]), __float_as_uint(acc[5]), __float_as_uint(acc[6]), __float_as_uint(acc[7]));
+#pragma unroll
+                for (int p = 0; p < 8; ++p)
+                    if (p < P.world) {
+                        reinterpret_cast<uint4*>(P.buf2[p])[2 * v] = lo;
+                        reinterpret_cast<uint4*>(P.buf2[p])[2 * v + 1] = hi;
+                    }
+                continue;
+            }
             out = f32_to_bf16x8(acc);
         } else {
             float* o = reinterpret_cast<float*>(&out);
@@ -119,7 +139,7 @@ __global__ void __launch_bounds__(COLL_THREADS) ddp_allreduce_kernel(const __gri
         for (int p = 0; p < 8; ++p)
             if (p < P.world) reinterpret_cast<uint4*>(P.buf[p])[v] = out;
     }
-    barrier_out(P, seq, ticket, status);
+    barrier_out(P, seq, ticket, status, ok);
 }
 
 struct AdamWArgs {
@@ -133,9 +153,10 @@ struct AdamWArgs {
 // Gradient buffers are bf16 [n_vec * 8] on every rank; rank r owns vectors slice_of(r).
 __global__ void __launch_bounds__(COLL_THREADS) fsdp_rs_adamw_kernel(const __grid_constant__ PeerSet P, const __grid_constant__ AdamWArgs A,
                                                                    long long n_vec, uint32_t seq, unsigned* ticket, int* status) {
-    if (!barrier_in(P, seq, status)) return;
+    const bool ok = barrier_in(P, seq, status);
     long long v0, v1;
     slice_of(n_vec, P.rank, P.world, v0, v1);
+    if (!ok) v1 = v0;          // no update from gradients that are not known to be complete
     for (long long v = v0 + (long long)blockIdx.x * COLL_THREADS + threadIdx.x; v < v1; v += (long long)gridDim.x * COLL_THREADS) {
         float g[8];
 #pragma unroll
@@ -177,13 +198,14 @@ __global__ void __launch_bounds__(COLL_THREADS) fsdp_rs_adamw_kernel(const __gri
         *reinterpret_cast<float4*>(A.v + e + 4) = *reinterpret_cast<float4*>(vv + 4);
         reinterpret_cast<uint4*>(A.shard_out)[v - v0] = f32_to_bf16x8(pw);
     }
-    barrier_out(P, seq, ticket, status);
+    barrier_out(P, seq, ticket, status, ok);
 }
 
 // Copy my shard (shard_vec vectors) into slot [rank] of every peer's full buffer.
 __global__ void __launch_bounds__(COLL_THREADS) allgather_kernel(const __grid_constant__ PeerSet P, const uint4* __restrict__ shard,
                                                                long long shard_vec, uint32_t seq, unsigned* ticket, int* status) {
-    if (!barrier_in(P, seq, status)) return;
+    const bool ok = barrier_in(P, seq, status);
+    if (!ok) shard_vec = 0;
     for (long long v = (long long)blockIdx.x * COLL_THREADS + threadIdx.x; v < shard_vec; v += (long long)gridDim.x * COLL_THREADS) {
         const uint4 x = shard[v];
 #pragma unroll
@@ -195,18 +217,32 @@ __global__ void __launch_bounds__(COLL_THREADS) allgather_kernel(const __grid_co
 
 // A flag barrier on its own (tests of the timeout path, and `tp_barrier`).
 __global__ void peer_barrier_kernel(const __grid_constant__ PeerSet P, uint32_t seq, unsigned* ticket, int* status) {
-    if (!barrier_in(P, seq, status)) return;
-    barrier_out(P, seq, ticket, status);
+    const bool ok = barrier_in(P, seq, status);
+    barrier_out(P, seq, ticket, status, ok);
 }
 
 }  // namespace ptb
 
 using namespace ptb;
 
-static void fill(PeerSet& P, void* const* bufs, void* const* flags, int rank, int world) {
-    for (int i = 0; i < 8; ++i) { P.buf[i] = i < world ? bufs[i] : nullptr; P.flag[i] = i < world ? (uint32_t*)flags[i] : nullptr; }
+// Wall-clock budget of every wait in these kernels.
+static unsigned long long g_budget_ns = [] {
+    const char* e = getenv("PTB_COLLECTIVE_TIMEOUT_MS");
+    const long ms = e && *e ? atol(e) : 10000;
+    return (unsigned long long)(ms > 0 ? ms : 1) * 1000000ull;
+}();
+PTB_API void ptb_set_collective_timeout_ms(int ms) { g_budget_ns = (unsigned long long)(ms > 0 ? ms : 1) * 1000000ull; }
+PTB_API int ptb_get_collective_timeout_ms() { return (int)(g_budget_ns / 1000000ull); }
+
+static void fill(PeerSet& P, void* const* bufs, void* const* flags, int rank, int world, void* const* bufs2 = nullptr) {
+    for (int i = 0; i < 8; ++i) {
+        P.buf[i] = i < world ? bufs[i] : nullptr;
+        P.flag[i] = i < world ? (uint32_t*)flags[i] : nullptr;
+        P.buf2[i] = (bufs2 && i < world) ? bufs2[i] : nullptr;
+    }
     P.rank = rank;
     P.world = world;
+    P.budget_ns = g_budget_ns;
 }
 
 // bufs/flags: host arrays of `world` device pointers (this rank's view of every peer's buffer / flag block).
@@ -218,8 +254,22 @@ PTB_API int ptb_ddp_allreduce(void* const* bufs, void* const* flags, int rank, i
     if (numel % per) { ptb_set_error("bucket length %lld must be a multiple of %d", numel, per); return -1; }
     PeerSet P;
     fill(P, bufs, flags, rank, world);
-    if (bf16) ddp_allreduce_kernel<true><<<n_ctas, COLL_THREADS, 0, st>>>(P, numel / per, scale, seq, ticket, status);
-    else ddp_allreduce_kernel<false><<<n_ctas, COLL_THREADS, 0, st>>>(P, numel / per, scale, seq, ticket, status);
+    if (bf16) ddp_allreduce_kernel<true, false><<<n_ctas, COLL_THREADS, 0, st>>>(P, numel / per, scale, seq, ticket, status);
+    else ddp_allreduce_kernel<false, false><<<n_ctas, COLL_THREADS, 0, st>>>(P, numel / per, scale, seq, ticket, status);
+    PTB_CUDA_OK(cudaGetLastError());
+    return 0;
+}
+
+// The same reduction of a bf16 bucket with the result cast to fp32: every rank's `master_bufs` buffer (fp32, `numel`
+// elements, symmetric like the bucket) receives the reduced, scaled gradients; the bf16 bucket keeps its local values.
+PTB_API int ptb_ddp_allreduce_master(void* const* bufs, void* const* master_bufs, void* const* flags, int rank, int world,
+                                     long long numel, float scale, unsigned seq, unsigned* ticket, int* status, int n_ctas,
+                                     cudaStream_t st) {
+    if (world > 8) { ptb_set_error("at most 8 peers"); return -1; }
+    if (numel % 8) { ptb_set_error("bucket length %lld must be a multiple of 8", numel); return -1; }
+    PeerSet P;
+    fill(P, bufs, flags, rank, world, master_bufs);
+    ddp_allreduce_kernel<true, true><<<n_ctas, COLL_THREADS, 0, st>>>(P, numel / 8, scale, seq, ticket, status);
     PTB_CUDA_OK(cudaGetLastError());
     return 0;
 }
@@ -252,6 +302,7 @@ PTB_API int ptb_allgather(void* const* bufs, void* const* flags, int rank, int w
 }
 
 PTB_API int ptb_peer_barrier(void* const* flags, int rank, int world, unsigned seq, unsigned* ticket, int* status, cudaStream_t st) {
+    if (world < 1 || world > 8) { ptb_set_error("peer barrier: %d ranks; 1 to 8 are supported", world); return -1; }
     PeerSet P;
     void* none[8] = {0};
     fill(P, none, flags, rank, world);

@@ -78,11 +78,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait.  Returns false (and records PTB_ERR_MBARRIER_TIMEOUT) if the
-// phase did not complete within `limit` polls.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, uint32_t limit = 4000000u) {
-    for (uint32_t i = 0; i < limit; ++i)
+// Bounded wait.  Returns false (and records PTB_ERR_MBARRIER_TIMEOUT) if the phase did not complete within
+// `budget_ns` of wall-clock time (%globaltimer, read every 256 polls, so the budget does not depend on the SM clock).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, uint64_t budget_ns = 2000000000ull) {
+    for (uint32_t i = 0; i < 256u; ++i)
         if (mbar_try_wait(bar, parity)) return true;
+    uint64_t t0;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    for (;;) {
+        for (uint32_t i = 0; i < 256u; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        uint64_t t1;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+        if (t1 - t0 > budget_ns) break;
+    }
     if (status) atomicExch(status, PTB_ERR_MBARRIER_TIMEOUT);
     return false;
 }
@@ -179,6 +188,28 @@ __device__ __forceinline__ uint32_t wait_ll(const uint2* p, uint32_t seq, int* s
     }
     if (status) atomicExch(status, PTB_ERR_FLAG_TIMEOUT);
     return 0u;
+}
+
+// Two neighbouring slots in one 16-byte access (each 8-byte half stays whole, so each carries its own check).
+__device__ __forceinline__ void st_ll2(uint2* p, uint32_t d0, uint32_t d1, uint32_t seq) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(d0), "r"(seq), "r"(d1), "r"(seq) : "memory");
+}
+__device__ __forceinline__ uint4 ld_ll2(const uint2* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+// Eight consecutive slots (64 bytes, 16-byte aligned) -> eight floats; true when all eight carry `seq`.
+__device__ __forceinline__ bool ll_try8(const uint2* p, uint32_t seq, float* v) {
+    const uint4 a = ld_ll2(p), b = ld_ll2(p + 2), c = ld_ll2(p + 4), d = ld_ll2(p + 6);
+    v[0] = __uint_as_float(a.x); v[1] = __uint_as_float(a.z); v[2] = __uint_as_float(b.x); v[3] = __uint_as_float(b.z);
+    v[4] = __uint_as_float(c.x); v[5] = __uint_as_float(c.z); v[6] = __uint_as_float(d.x); v[7] = __uint_as_float(d.z);
+    return a.y == seq && a.w == seq && b.y == seq && b.w == seq && c.y == seq && c.w == seq && d.y == seq && d.w == seq;
+}
+__device__ __forceinline__ uint64_t global_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
 }
 
 __device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }

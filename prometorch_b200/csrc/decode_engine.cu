@@ -8,8 +8,18 @@
 // captured on token 2, replayed afterwards, arg-max in a separate launch plus an
 // 8-byte device-to-host copy per token.  Here a layer is five kernels, the
 // arg-max is the lm_head epilogue and a run of tokens needs no host round trip.
+//
+// Dataflow between the kernels of a token: every activation vector is a buffer of
+// {value, sequence} slots.  A kernel is launched as soon as all CTAs of its predecessor
+// have started, streams its weights into shared memory and polls its input slots; it
+// never waits for the predecessor to drain.  The only hard boundary is the start of a
+// token (the embedding kernel is launched without a programmatic edge), which is also
+// what makes it safe to reuse the slot buffers: sequence numbers grow with the token
+// generation counter.  Partial sums of the K-split projections (all ranks' under tensor
+// parallelism, one at world size 1) land in inbox slots and are added, in rank order,
+// by the prologue of whichever kernel consumes the residual stream next.
 #include "decode_kernels.cuh"
-#include "decode_mega.cuh"
+#include "decode_gemv_mma.cuh"
 #include <stdarg.h>
 #include <stdlib.h>
 #include <string.h>
@@ -46,11 +56,12 @@ struct GemvLaunch {
     GemvParams p;
     int grid;
     size_t smem;
+    int t16;          // weights in the tiles-of-16-rows layout: launch the tensor-pipe kernel
 };
 
 // Fill job geometry, CTA split, tile ring and shared memory size.  `jobs` already carry
 // w/w2/out/bias/qtype/N/nblk/KS/seg_base/seg_rem.
-static int plan_gemv(GemvLaunch& L, int njobs, int K, int n_ctas) {
+static int plan_gemv_seg(GemvLaunch& L, int njobs, int K, int n_ctas) {
     const int want_stages = env_int("PTB_GEMV_STAGES", 4);
     const int tile_cap = env_int("PTB_GEMV_TILE_KB", 6) * 1024;
     const size_t budget = (size_t)env_int("PTB_GEMV_SMEM_KB", 100) * 1024;
@@ -59,6 +70,8 @@ static int plan_gemv(GemvLaunch& L, int njobs, int K, int n_ctas) {
     p.K = K;
     const int warps = env_int("PTB_GEMV_WARPS", 8) >= 16 ? 16 : 8;
     p.warps = warps;
+    p.wait_ns = (unsigned long long)env_int("PTB_WAIT_MS", 2000) * 1000000ull;
+    p.hard_wait = env_int("PTB_DATAFLOW", 1) == 0;
     if (K % 256 || K > 5 * 8 * 256) {
         ptb_set_error("gemv: input length %d must be a multiple of 256 and at most %d", K, 5 * 8 * 256);
         return -1;
@@ -118,8 +131,85 @@ static int plan_gemv(GemvLaunch& L, int njobs, int K, int n_ctas) {
     return 0;
 }
 
+static int g_job_layout = 0;      // layout of the job set_job() filled last (a launch never mixes layouts)
+// Tiles-of-16-rows layout: CTAs own whole row tiles (split over the jobs in proportion to their bytes); the K
+// dimension of a tile is cut into KG groups so that a CTA has enough (tile, K-group) items for its warps.
+static int plan_gemv16(GemvLaunch& L, int njobs, int K, int n_ctas) {
+    GemvParams& p = L.p;
+    p.njobs = njobs;
+    p.K = K;
+    // one CTA of 16 warps per SM: half as many CTAs repeat the input gather as with two CTAs of 8 warps
+    const int warps = env_int("PTB_GEMV_WARPS", 16) >= 16 ? 16 : 8;
+    p.warps = warps;
+    p.wait_ns = (unsigned long long)env_int("PTB_WAIT_MS", 2000) * 1000000ull;
+    p.hard_wait = env_int("PTB_DATAFLOW", 1) == 0;
+    if (K % 256 || K > 5 * 8 * 256) {
+        ptb_set_error("gemv: input length %d must be a multiple of 256 and at most %d", K, 5 * 8 * 256);
+        return -1;
+    }
+    double total = 0;
+    auto bytes_of = [](const GemvJob& j) { return (double)((j.N + 15) / 16) * j.nblk * t16_block_bytes(j.qtype) * (j.w2 ? 2 : 1); };
+    for (int i = 0; i < njobs; ++i) total += bytes_of(p.job[i]);
+    int left = n_ctas, begin = 0;
+    double left_bytes = total;
+    for (int i = 0; i < njobs; ++i) {
+        GemvJob& j = p.job[i];
+        const double b = bytes_of(j);
+        int c = (i == njobs - 1) ? left : (int)(left * b / left_bytes + 0.5);
+        c = std::max(1, std::min(c, left - (njobs - 1 - i)));
+        c = std::min(c, (j.N + 15) / 16);
+        j.cta_begin = begin;
+        j.cta_count = c;
+        begin += c;
+        left -= c;
+        left_bytes -= b;
+    }
+    L.grid = begin;
+    int tile_bytes = 0, acc_floats = 0;
+    const int force_kg = env_int("PTB_GEMV_KG", 0);
+    for (int i = 0; i < njobs; ++i) {
+        GemvJob& j = p.job[i];
+        const int pairs = j.w2 ? 2 : 1;
+        const int ntile = (j.N + 15) / 16;
+        const int tiles_cta = (ntile + j.cta_count - 1) / j.cta_count;
+        // K-groups: minimise the per-warp critical path, counted in block visits (+1 per item for its reduction)
+        double best = 1e30;
+        int bestKG = 1;
+        for (int kg = 1; kg <= j.nblk; ++kg) {
+            const int rounds = (tiles_cta * kg + warps - 1) / warps;
+            const double cost = rounds * ((double)((j.nblk + kg - 1) / kg) * pairs + 1.0) + (kg > 1 ? 0.5 : 0.0);
+            if (cost < best - 1e-9) { best = cost; bestKG = kg; }
+        }
+        if (force_kg > 0) bestKG = std::min(force_kg, j.nblk);
+        j.KS = bestKG;
+        j.seg_base = j.nblk / bestKG;
+        j.seg_rem = j.nblk % bestKG;
+        j.RW = 16;
+        tile_bytes = std::max(tile_bytes, pairs * t16_block_bytes(j.qtype));
+        if (bestKG > 1) acc_floats = std::max(acc_floats, tiles_cta * bestKG * pairs * 16);
+    }
+    tile_bytes = (tile_bytes + 127) / 128 * 128;
+    const size_t budget = (size_t)env_int("PTB_GEMV_SMEM_KB", warps >= 16 ? 200 : 100) * 1024;
+    int stages = std::min(env_int("PTB_GEMV_STAGES", 8), 16);
+    while (stages > 2 && gemv_smem_layout(K, warps, stages, tile_bytes, acc_floats).total > budget) --stages;
+    p.stages = stages;
+    p.tile_bytes = tile_bytes;
+    p.acc_floats = acc_floats;
+    L.smem = gemv_smem_layout(K, warps, stages, tile_bytes, acc_floats).total;
+    L.t16 = 1;
+    if (L.smem > g_gemv_max_dyn) {
+        ptb_set_error("gemv: %zu B of shared memory needed (K=%d, tile %d B x %d stages x %d warps, %d accumulators)", L.smem, K,
+                      tile_bytes, stages, warps, acc_floats);
+        return -1;
+    }
+    return 0;
+}
+
+static int plan_gemv(GemvLaunch& L, int njobs, int K, int n_ctas);
+
 static void set_job(GemvJob& j, const PtbWeightDesc& w, const PtbWeightDesc* w2, float* out) {
     memset(&j, 0, sizeof(j));
+    g_job_layout = w.layout;
     j.w = (const uint8_t*)w.w;
     j.w2 = w2 ? (const uint8_t*)w2->w : nullptr;
     j.bias = (const float*)w.bias;
@@ -130,6 +220,35 @@ static void set_job(GemvJob& j, const PtbWeightDesc& w, const PtbWeightDesc* w2,
     j.KS = (j.nblk + GEMV_SEG_BLOCKS - 1) / GEMV_SEG_BLOCKS;
     j.seg_base = j.nblk / j.KS;
     j.seg_rem = j.nblk % j.KS;
+}
+
+static int plan_gemv(GemvLaunch& L, int njobs, int K, int n_ctas) {
+    return g_job_layout == 1 ? plan_gemv16(L, njobs, K, n_ctas) : plan_gemv_seg(L, njobs, K, n_ctas);
+}
+
+// Bytes of one matrix in the streaming layout.
+static size_t job_bytes(const GemvJob& j) {
+    if (j.RW == 16) return (size_t)((j.N + 15) / 16) * j.nblk * t16_block_bytes(j.qtype);
+    size_t b = 0;
+    for (int s = 0; s < j.KS; ++s) b += (size_t)j.N * seg_bytes(j.qtype, j.seg_base + (s < j.seg_rem ? 1 : 0));
+    return b;
+}
+
+// Make launch `a` prefetch (into L2) the weights launch `b` is going to stream, up to `cap` bytes.
+static void set_prefetch(GemvLaunch& a, const GemvLaunch& b, size_t cap) {
+    int r = 0;
+    for (int i = 0; i < b.p.njobs && r < 4; ++i) {
+        const GemvJob& j = b.p.job[i];
+        const uint8_t* ptrs[2] = {j.w, j.w2};
+        for (int k = 0; k < 2 && r < 4; ++k) {
+            if (!ptrs[k] || cap < 16) continue;
+            const size_t n = std::min(job_bytes(j), cap) & ~(size_t)15;
+            a.p.pf_ptr[r] = ptrs[k];
+            a.p.pf_bytes[r] = (unsigned)n;
+            cap -= n;
+            ++r;
+        }
+    }
 }
 
 static bool g_attr_done = false;
@@ -144,6 +263,8 @@ static int ensure_attrs() {
     g_gemv_max_dyn = (size_t)optin - fa.sharedSizeBytes;
     PTB_CUDA_OK(cudaFuncSetAttribute(gemv_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_gemv_max_dyn));
     PTB_CUDA_OK(cudaFuncSetAttribute(gemv_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_gemv_max_dyn));
+    PTB_CUDA_OK(cudaFuncSetAttribute(gemv16_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_gemv_max_dyn));
+    PTB_CUDA_OK(cudaFuncSetAttribute(gemv16_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_gemv_max_dyn));
     g_attr_done = true;
     return 0;
 }
@@ -200,6 +321,10 @@ static cudaError_t launch_attn(const AttnParams& a, int n_kv_heads, cudaStream_t
 }
 
 static cudaError_t launch_gemv(const GemvLaunch& L, cudaStream_t st, bool pdl) {
+    if (L.t16) {
+        if (L.p.warps == 16) return launch_pdl(gemv16_kernel<16>, dim3(L.grid), dim3(512), L.smem, st, pdl, L.p);
+        return launch_pdl(gemv16_kernel<8>, dim3(L.grid), dim3(256), L.smem, st, pdl, L.p);
+    }
     if (L.p.warps == 16) return launch_pdl(gemv_kernel<16>, dim3(L.grid), dim3(512), L.smem, st, pdl, L.p);
     return launch_pdl(gemv_kernel<8>, dim3(L.grid), dim3(256), L.smem, st, pdl, L.p);
 }
@@ -207,15 +332,15 @@ static cudaError_t launch_gemv(const GemvLaunch& L, cudaStream_t st, bool pdl) {
 // ------------------------------------------------------------------------------------------ standalone op entry points (tests, benches)
 
 // y = epilogue(W x).  Device pointers; w2/norm_w/resid/bias may be null.
-PTB_API int ptb_gemv(const void* w, const void* w2, int qtype, int rows, int cols, int rowbytes, const float* x,
+PTB_API int ptb_gemv(const void* w, const void* w2, int qtype, int rows, int cols, int rowbytes, int layout, const float* x,
                      const float* norm_w, float eps, const float* bias, const float* resid, float* out, int epilogue,
                      int act_gelu, int n_ctas, void* scratch /* >= 16 + 8*n_ctas bytes, zeroed */, int* status,
                      cudaStream_t stream) {
     if (ensure_attrs()) return -1;
     GemvLaunch L;
     memset(&L, 0, sizeof(L));
-    PtbWeightDesc d{w, bias, qtype, rows, cols, rowbytes};
-    PtbWeightDesc d2{w2, nullptr, qtype, rows, cols, rowbytes};
+    PtbWeightDesc d{w, bias, qtype, rows, cols, rowbytes, layout, 0};
+    PtbWeightDesc d2{w2, nullptr, qtype, rows, cols, rowbytes, layout, 0};
     set_job(L.p.job[0], d, w2 ? &d2 : nullptr, out);
     L.p.x = x;
     L.p.norm_w = norm_w;
@@ -289,15 +414,13 @@ struct Engine {
     bool use_pdl = true;
     unsigned long long* trace = nullptr;   // PTB_TRACE=1: [kernels per token][8] phase stamps of the last token
     long launches_per_token = 0;
-    // persistent single-launch path (one GPU): op list on the device, arrival counter, launch geometry
-    bool mega = false;
-    MegaParams mp;
-    MegaOp* d_ops = nullptr;
-    unsigned* d_bar = nullptr;        // [0] spare, [1] token generation
-    uint2 *x_ll = nullptr, *qkv_ll = nullptr, *att_ll = nullptr, *ffn_ll = nullptr, *part_o_ll = nullptr, *part_ml_ll = nullptr;
-    size_t mega_smem = 0;
-    int mega_warps = 15;
-    int n_ops = 0;
+    // dataflow buffers of {value, sequence} slots
+    uint2* x_ll[2] = {nullptr, nullptr};      // residual stream, ping-pong
+    uint2 *qkv_ll = nullptr, *att_ll = nullptr, *ffn_ll = nullptr;
+    uint2* own_inbox[2] = {nullptr, nullptr}; // world size 1: the partial-sum inboxes live here (else in symmetric memory)
+    uint4* rec[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};   // quantised-input records of qkv, o, gate/up, down, lm_head
+    unsigned long long wait_ns = 2000000000ull;
+    bool dataflow = false;
 };
 
 static int engine_alloc(Engine* e) {
@@ -324,7 +447,34 @@ static int engine_alloc(Engine* e) {
     PTB_CUDA_OK(cudaMalloc(&e->amax_val, sizeof(float) * 4096));
     PTB_CUDA_OK(cudaMalloc(&e->amax_idx, sizeof(int) * 4096));
     PTB_CUDA_OK(cudaMalloc(&e->ctrl, sizeof(int) * CTRL_WORDS));
-    PTB_CUDA_OK(cudaMemset(e->ctrl, 0, sizeof(int) * CTRL_WORDS));
+    {
+        int c[CTRL_WORDS] = {0};
+        c[CTRL_GEN] = 1;              // sequence numbers start above the zero the slot buffers are cleared to
+        PTB_CUDA_OK(cudaMemcpy(e->ctrl, c, sizeof(c), cudaMemcpyHostToDevice));
+    }
+    auto ll_alloc = [](uint2** p, size_t n) {
+        return cudaMalloc(p, n * sizeof(uint2)) != cudaSuccess || cudaMemset(*p, 0, n * sizeof(uint2)) != cudaSuccess;
+    };
+    if (ll_alloc(&e->x_ll[0], m.hidden) || ll_alloc(&e->x_ll[1], m.hidden) || ll_alloc(&e->qkv_ll, qd + 2 * kvd) ||
+        ll_alloc(&e->att_ll, qd) || ll_alloc(&e->ffn_ll, m.inter)) {
+        ptb_set_error("decode engine: slot buffer allocation failed");
+        return -1;
+    }
+    if (m.tp_world <= 1 && (ll_alloc(&e->own_inbox[0], m.hidden) || ll_alloc(&e->own_inbox[1], m.hidden))) {
+        ptb_set_error("decode engine: inbox allocation failed");
+        return -1;
+    }
+    e->wait_ns = (unsigned long long)env_int("PTB_WAIT_MS", 2000) * 1000000ull;
+    if (env_int("PTB_RECORDS", 1)) {
+        const int klen[5] = {m.hidden, qd, m.hidden, m.inter, m.hidden};
+        for (int i = 0; i < 5; ++i) {
+            const size_t bytes = (size_t)(klen[i] / 32) * 64;
+            if (cudaMalloc(&e->rec[i], bytes) != cudaSuccess || cudaMemset(e->rec[i], 0, bytes) != cudaSuccess) {
+                ptb_set_error("decode engine: record buffer allocation failed");
+                return -1;
+            }
+        }
+    }
     PTB_CUDA_OK(cudaMalloc(&e->result, sizeof(int) * 4));
     PTB_CUDA_OK(cudaMemset(e->result, 0, sizeof(int) * 4));
     e->log_cap = 1 << 16;
@@ -332,6 +482,10 @@ static int engine_alloc(Engine* e) {
     PTB_CUDA_OK(cudaMalloc(&e->script, sizeof(int) * m.max_seq));
     PTB_CUDA_OK(cudaMalloc(&e->status, sizeof(int)));
     PTB_CUDA_OK(cudaMemset(e->status, 0, sizeof(int)));
+    if (2 * m.n_layers + 2 >= (int)LL_SEQ_MUL) {
+        ptb_set_error("decode engine: %d layers exceed the %u writes per token a sequence number can index", m.n_layers, LL_SEQ_MUL);
+        return -1;
+    }
     if (env_int("PTB_TRACE", 0)) {
         PTB_CUDA_OK(cudaMalloc(&e->trace, 8 * sizeof(unsigned long long) * (5 * m.n_layers + 4)));
         PTB_CUDA_OK(cudaMemset(e->trace, 0, 8 * sizeof(unsigned long long) * (5 * m.n_layers + 4)));
@@ -341,22 +495,27 @@ static int engine_alloc(Engine* e) {
     return 0;
 }
 
-static void fill_peers(const Engine* e, GemvParams& p, int which, int call_idx, int calls_per_token) {
+// Where the partial sums of projection `which` (0: attention output, 1: FFN down; 2: the arg-max pair) go.
+static void fill_peers(const Engine* e, GemvParams& p, int which) {
     const PtbModelDesc& m = e->m;
-    p.peers.rank = m.tp_rank;
-    p.peers.world = m.tp_world;
-    p.peers.slot_elems = m.slot_elems;
-    for (int r = 0; r < m.tp_world; ++r) p.peers.inbox[r] = (uint2*)m.peer_inbox[which][r];
+    p.peers.rank = m.tp_world > 1 ? m.tp_rank : 0;
+    p.peers.world = std::max(1, m.tp_world);
+    if (m.tp_world > 1) {
+        p.peers.slot_elems = m.slot_elems;
+        for (int r = 0; r < m.tp_world; ++r) p.peers.inbox[r] = (uint2*)m.peer_inbox[which][r];
+    } else {
+        p.peers.slot_elems = m.hidden;
+        p.peers.inbox[0] = which < 2 ? e->own_inbox[which] : nullptr;
+    }
     p.gen = (const uint32_t*)(e->ctrl + CTRL_GEN);
-    p.peers.seq_mul = (uint32_t)calls_per_token;
-    p.peers.seq_add = (uint32_t)call_idx;
 }
 
-static int engine_plan(Engine* e) {
+// Plain flow (one GPU): every kernel waits for its predecessor at the launch boundary and the vectors between them
+// are ordinary fp32 arrays; the residual stream is updated in place by the projections' epilogues.
+static int engine_plan_plain(Engine* e) {
     const PtbModelDesc& m = e->m;
     const int qd = m.n_heads * m.head_dim, kvd = m.n_kv_heads * m.head_dim;
     const int n_ctas = e->n_sm * env_int("PTB_GEMV_CTAS_PER_SM", 2);
-    const bool tp = m.tp_world > 1;
     e->gemvs.clear();
     // post-norm architectures: a projection stores its raw output in `tmp`; the next kernel's prologue adds
     // RMSNorm(tmp) to the residual stream, reading X[cur] and (CTA 0) writing X[cur ^ 1]
@@ -393,9 +552,8 @@ static int engine_plan(Engine* e) {
             const bool post = L.post_attn_norm != nullptr;
             set_job(g.p.job[0], L.o, nullptr, post ? e->tmp : X[cur]);
             g.p.x = e->att; g.p.resid = post ? nullptr : X[cur]; g.p.status = e->status; g.p.ticket = e->tickets;
-            g.p.epilogue = tp ? EPI_ALLREDUCE : (post ? EPI_STORE : EPI_RESID);
+            g.p.epilogue = post ? EPI_STORE : EPI_RESID;
             g.p.peers.world = 1;
-            if (tp) fill_peers(e, g.p, 0, l, m.n_layers);
             if (plan_gemv(g, 1, L.o.cols, n_ctas)) return -1;
             e->gemvs.push_back(g);
             if (post) pending_w = L.post_attn_norm;
@@ -416,9 +574,8 @@ static int engine_plan(Engine* e) {
             const bool post = L.post_ffn_norm != nullptr;
             set_job(g.p.job[0], L.down, nullptr, post ? e->tmp : X[cur]);
             g.p.x = e->ffn; g.p.resid = post ? nullptr : X[cur]; g.p.status = e->status; g.p.ticket = e->tickets;
-            g.p.epilogue = tp ? EPI_ALLREDUCE : (post ? EPI_STORE : EPI_RESID);
+            g.p.epilogue = post ? EPI_STORE : EPI_RESID;
             g.p.peers.world = 1;
-            if (tp) fill_peers(e, g.p, 1, l, m.n_layers);
             if (plan_gemv(g, 1, L.down.cols, n_ctas)) return -1;
             e->gemvs.push_back(g);
             if (post) pending_w = L.post_ffn_norm;
@@ -437,7 +594,7 @@ static int engine_plan(Engine* e) {
         g.p.logits = m.want_logits ? e->logits : nullptr;
         g.p.result = e->result; g.p.ctrl = e->ctrl; g.p.token_log = e->token_log; g.p.token_script = e->script; g.p.row_offset = m.vocab_offset;
         g.p.peers.world = 1;
-        if (tp) fill_peers(e, g.p, 2, 0, 1);
+        g.p.gen = (const uint32_t*)(e->ctrl + CTRL_GEN);
         if (plan_gemv(g, 1, m.hidden, std::min(n_ctas, 4096))) return -1;
         e->gemvs.push_back(g);
     }
@@ -445,198 +602,130 @@ static int engine_plan(Engine* e) {
 }
 
 
-// ------------------------------------------------------------------------------------------ persistent single-launch path
-// CTA split and rows-per-tile of one GEMV op of the persistent kernel (same rules as plan_gemv, one CTA per SM).
-static int plan_mega_gemv(MegaOp& op, int njobs, int K, int n_ctas, int warps, int slot_bytes, int* acc_floats) {
-    op.kind = MK_GEMV;
-    op.njobs = njobs;
-    op.K = K;
-    if (K % 256 || K > 10240) { ptb_set_error("persistent decode: input length %d must be a multiple of 256 and at most 10240", K); return -1; }
-    double total = 0;
-    for (int i = 0; i < njobs; ++i) total += (double)op.job[i].N * op.job[i].nblk * (op.job[i].qtype == QT_Q4K ? 144 : 210) * (op.job[i].w2 ? 2 : 1);
-    int left = n_ctas, begin = 0;
-    double left_bytes = total;
-    for (int i = 0; i < njobs; ++i) {
-        GemvJob& j = op.job[i];
-        const double b = (double)j.N * j.nblk * (j.qtype == QT_Q4K ? 144 : 210) * (j.w2 ? 2 : 1);
-        int c = (i == njobs - 1) ? left : (int)(left * b / left_bytes + 0.5);
-        c = std::max(1, std::min(c, left - (njobs - 1 - i)));
-        c = std::min(c, j.N);
-        j.cta_begin = begin;
-        j.cta_count = c;
-        begin += c;
-        left -= c;
-        left_bytes -= b;
-    }
-    for (int i = 0; i < njobs; ++i) {
-        GemvJob& j = op.job[i];
-        const int pairs = j.w2 ? 2 : 1;
-        const int nb = j.seg_base + (j.seg_rem ? 1 : 0);
-        const int sz = seg_bytes(j.qtype, nb);
-        const int rows_cta = (j.N + j.cta_count - 1) / j.cta_count;
-        double best = 1e30;
-        int bestRW = 0;
-        for (int RW = 8; RW >= 1; RW >>= 1) {
-            if (RW * sz * pairs > slot_bytes) continue;
-            const int gprw = 8 / RW;
-            const int items = ((rows_cta + RW - 1) / RW) * j.KS;
-            const int rounds = (items + warps - 1) / warps;
-            const double cost = rounds * ((double)((nb + gprw - 1) / gprw) * pairs + 1.0);
-            if (cost < best - 1e-9) { best = cost; bestRW = RW; }
-        }
-        if (!bestRW) { ptb_set_error("persistent decode: a %d-byte segment does not fit a %d-byte ring slot", sz * pairs, slot_bytes); return -1; }
-        j.RW = bestRW;
-        if (j.KS > 1) *acc_floats = std::max(*acc_floats, rows_cta * j.KS * pairs);
-    }
-    return 0;
-}
-
-template <int NCONS>
-static cudaError_t launch_mega_n(const MegaParams& p, int grid, size_t smem, cudaStream_t st) {
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(decode_mega_kernel<NCONS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        attr_done = true;
-    }
-    decode_mega_kernel<NCONS><<<grid, (NCONS + 1) * 32, smem, st>>>(p);
-    return cudaGetLastError();
-}
-static cudaError_t launch_mega(const MegaParams& p, int warps, int grid, size_t smem, cudaStream_t st) {
-    // consumer warps + the producer warp fill whole register-allocation groups of four warps: 11+1 or 15+1
-    switch (warps) {
-        case 11: return launch_mega_n<11>(p, grid, smem, st);
-        default: return launch_mega_n<15>(p, grid, smem, st);
-    }
-}
-
-static size_t mega_attn_smem(int group) {
-    switch (group) {
-        case 1: return sizeof(MegaAttnShared<1>);
-        case 2: return sizeof(MegaAttnShared<2>);
-        case 4: return sizeof(MegaAttnShared<4>);
-        default: return sizeof(MegaAttnShared<8>);
-    }
-}
-
-// Build the op list of one token and the shared-memory layout; upload the list.
-static int engine_plan_mega(Engine* e) {
+// Dataflow (any number of GPUs).
+static int engine_plan_dataflow(Engine* e) {
     const PtbModelDesc& m = e->m;
     const int qd = m.n_heads * m.head_dim, kvd = m.n_kv_heads * m.head_dim;
-    const int n_ctas = e->n_sm;
-    e->mega_warps = env_int("PTB_MEGA_WARPS", 15) <= 11 ? 11 : 15;
-    const int slot_bytes = (env_int("PTB_MEGA_SLOT_KB", 6) * 1024 + 127) / 128 * 128;
-    {
-        const int splits = (m.max_seq + ATT_CHUNK - 1) / ATT_CHUNK, group = m.n_heads / m.n_kv_heads;
-        if (m.n_kv_heads > n_ctas) { ptb_set_error("persistent decode: %d KV heads exceed the %d CTAs", m.n_kv_heads, n_ctas); return -1; }
-        auto ll_alloc = [](uint2** p, size_t n) { return cudaMalloc(p, n * sizeof(uint2)) != cudaSuccess || cudaMemset(*p, 0, n * sizeof(uint2)) != cudaSuccess; };
-        if (ll_alloc(&e->x_ll, m.hidden) || ll_alloc(&e->qkv_ll, qd + 2 * kvd) || ll_alloc(&e->att_ll, qd) || ll_alloc(&e->ffn_ll, m.inter) ||
-            ll_alloc(&e->part_o_ll, (size_t)m.n_kv_heads * splits * group * ATT_D) || ll_alloc(&e->part_ml_ll, (size_t)m.n_kv_heads * splits * group * 2)) {
-            ptb_set_error("persistent decode: slot buffer allocation failed");
-            return -1;
+    const int n_ctas = e->n_sm * env_int("PTB_GEMV_CTAS_PER_SM", e->layers[0].q.layout == 1 ? 1 : 2);
+    const bool tp = m.tp_world > 1;
+    const int world = std::max(1, m.tp_world);
+    const uint32_t* gen = (const uint32_t*)(e->ctrl + CTRL_GEN);
+    e->gemvs.clear();
+    // The residual stream lives in two slot buffers used in turn.  Update number u (1, 2, ... within a token; the
+    // embedding is write 0 into buffer 0) is formed by the prologue of the kernel that consumes it, from buffer
+    // (u - 1) & 1 plus the partial sums of the projection before it, and published by that kernel's CTA 0 into
+    // buffer u & 1 with sequence index u.
+    int upd = 0;
+    auto consume_residual = [&](GemvParams& p, int inbox, int layer_seq, const float* post_w) {
+        p.x_ll = e->x_ll[upd & 1];
+        p.x_seq_add = (uint32_t)upd;
+        if (inbox >= 0) {
+            p.part_ll = tp ? (const uint2*)m.peer_inbox[inbox][m.tp_rank] : e->own_inbox[inbox];
+            p.nparts = world;
+            p.part_stride = tp ? m.slot_elems : m.hidden;
+            p.part_seq_add = (uint32_t)layer_seq;
+            p.post_w = post_w;
+            ++upd;
+            p.x_out_ll = e->x_ll[upd & 1];
+            p.x_out_seq_add = (uint32_t)upd;
         }
-    }
-    std::vector<MegaOp> ops;
-    int acc_floats = 0, kmax = 256;
-    int last_x_op = 0;               // index of the op that produced the current residual stream
-    auto gemv_op = [&](int njobs, int K) -> MegaOp& { ops.emplace_back(); MegaOp& o = ops.back(); memset(&o, 0, sizeof(o)); o.kind = MK_GEMV; o.njobs = njobs; o.K = K; kmax = std::max(kmax, K); return o; };
-    {
-        MegaOp o;
-        memset(&o, 0, sizeof(o));
-        o.kind = MK_EMBED;
-        ops.push_back(o);
-    }
+    };
+    int pending_inbox = -1, pending_seq = 0;       // the projection whose partial sums wait to be folded in
+    const float* pending_w = nullptr;              // ... and its post-norm weight (gemma3) or null
     for (int l = 0; l < m.n_layers; ++l) {
         const PtbLayerDesc& L = e->layers[l];
-        {
-            MegaOp& o = gemv_op(3, m.hidden);
-            set_job(o.job[0], L.q, nullptr, e->qkv);
-            set_job(o.job[1], L.k, nullptr, e->qkv + qd);
-            set_job(o.job[2], L.v, nullptr, e->qkv + qd + kvd);
-            o.x_ll = e->x_ll; o.src_op = last_x_op; o.norm_w = L.attn_norm; o.eps = m.eps; o.norm_add_one = m.norm_add_one; o.epilogue = EPI_STORE;
-            o.out_ll[0] = e->qkv_ll; o.out_ll[1] = e->qkv_ll + qd; o.out_ll[2] = e->qkv_ll + qd + kvd;
-            if (plan_mega_gemv(o, 3, m.hidden, n_ctas, e->mega_warps, slot_bytes, &acc_floats)) return -1;
+        if ((L.post_attn_norm || L.post_ffn_norm) && m.hidden > 4096) {
+            ptb_set_error("post-norm architectures: hidden size %d above 4096 is not supported", m.hidden);
+            return -1;
         }
-        {
-            MegaOp o;
-            memset(&o, 0, sizeof(o));
-            o.kind = MK_ATTN;
-            o.q_norm = L.q_norm; o.k_norm = L.k_norm; o.cos = L.cos; o.sin = L.sin; o.window = L.window;
-            o.k_cache = e->kc + (size_t)l * m.n_kv_heads * m.max_seq * m.head_dim;
-            o.v_cache = e->vc + (size_t)l * m.n_kv_heads * m.max_seq * m.head_dim;
-            ops.push_back(o);
+        {   // q, k, v from RMSNorm(x)
+            GemvLaunch g;
+            memset(&g, 0, sizeof(g));
+            set_job(g.p.job[0], L.q, nullptr, nullptr);
+            set_job(g.p.job[1], L.k, nullptr, nullptr);
+            set_job(g.p.job[2], L.v, nullptr, nullptr);
+            g.p.job[0].out_ll = e->qkv_ll; g.p.job[1].out_ll = e->qkv_ll + qd; g.p.job[2].out_ll = e->qkv_ll + qd + kvd;
+            consume_residual(g.p, pending_inbox, pending_seq, pending_w);
+            g.p.out_seq_add = (uint32_t)(l + 1);
+            g.p.norm_w = L.attn_norm; g.p.eps = m.eps; g.p.norm_add_one = m.norm_add_one;
+            g.p.epilogue = EPI_STORE; g.p.status = e->status; g.p.peers.world = 1; g.p.gen = gen;
+            g.p.rec = e->rec[0];
+            if (plan_gemv(g, 3, m.hidden, n_ctas)) return -1;
+            e->gemvs.push_back(g);
         }
-        {
-            MegaOp& o = gemv_op(1, L.o.cols);
-            set_job(o.job[0], L.o, nullptr, e->x);
-            o.x_ll = e->att_ll; o.src_op = (int)ops.size() - 2; o.resid_ll = e->x_ll; o.out_ll[0] = e->x_ll; o.epilogue = EPI_RESID;
-            if (plan_mega_gemv(o, 1, L.o.cols, n_ctas, e->mega_warps, slot_bytes, &acc_floats)) return -1;
-            last_x_op = (int)ops.size() - 1;
+        {   // partial sums of Wo att -> inbox 0
+            GemvLaunch g;
+            memset(&g, 0, sizeof(g));
+            set_job(g.p.job[0], L.o, nullptr, nullptr);
+            g.p.x_ll = e->att_ll; g.p.x_seq_add = (uint32_t)(l + 1);
+            g.p.status = e->status;
+            g.p.epilogue = EPI_PARTIAL; g.p.out_seq_add = (uint32_t)(l + 1);
+            fill_peers(e, g.p, 0);
+            g.p.rec = e->rec[1];
+            if (plan_gemv(g, 1, L.o.cols, n_ctas)) return -1;
+            e->gemvs.push_back(g);
+            pending_inbox = 0; pending_seq = l + 1; pending_w = L.post_attn_norm;
         }
-        {
-            MegaOp& o = gemv_op(1, m.hidden);
-            set_job(o.job[0], L.gate, &L.up, e->ffn);
-            o.x_ll = e->x_ll; o.src_op = last_x_op; o.norm_w = L.ffn_norm; o.eps = m.eps; o.norm_add_one = m.norm_add_one; o.epilogue = EPI_GATED;
-            o.act_gelu = m.act_gelu; o.out_ll[0] = e->ffn_ll;
-            if (plan_mega_gemv(o, 1, m.hidden, n_ctas, e->mega_warps, slot_bytes, &acc_floats)) return -1;
+        {   // ffn = act(Wg h) * (Wu h), h = RMSNorm(x)
+            GemvLaunch g;
+            memset(&g, 0, sizeof(g));
+            set_job(g.p.job[0], L.gate, &L.up, nullptr);
+            g.p.job[0].out_ll = e->ffn_ll;
+            consume_residual(g.p, pending_inbox, pending_seq, pending_w);
+            g.p.out_seq_add = (uint32_t)(l + 1);
+            g.p.norm_w = L.ffn_norm; g.p.eps = m.eps; g.p.norm_add_one = m.norm_add_one;
+            g.p.epilogue = EPI_GATED; g.p.act_gelu = m.act_gelu; g.p.status = e->status; g.p.peers.world = 1; g.p.gen = gen;
+            g.p.rec = e->rec[2];
+            if (plan_gemv(g, 1, m.hidden, n_ctas)) return -1;
+            e->gemvs.push_back(g);
         }
-        {
-            MegaOp& o = gemv_op(1, L.down.cols);
-            set_job(o.job[0], L.down, nullptr, e->x);
-            o.x_ll = e->ffn_ll; o.src_op = (int)ops.size() - 2; o.resid_ll = e->x_ll; o.out_ll[0] = e->x_ll; o.epilogue = EPI_RESID;
-            if (plan_mega_gemv(o, 1, L.down.cols, n_ctas, e->mega_warps, slot_bytes, &acc_floats)) return -1;
-            last_x_op = (int)ops.size() - 1;
+        {   // partial sums of Wd ffn -> inbox 1
+            GemvLaunch g;
+            memset(&g, 0, sizeof(g));
+            set_job(g.p.job[0], L.down, nullptr, nullptr);
+            g.p.x_ll = e->ffn_ll; g.p.x_seq_add = (uint32_t)(l + 1);
+            g.p.status = e->status;
+            g.p.epilogue = EPI_PARTIAL; g.p.out_seq_add = (uint32_t)(l + 1);
+            fill_peers(e, g.p, 1);
+            g.p.rec = e->rec[3];
+            if (plan_gemv(g, 1, L.down.cols, n_ctas)) return -1;
+            e->gemvs.push_back(g);
+            pending_inbox = 1; pending_seq = l + 1; pending_w = L.post_ffn_norm;
         }
     }
-    {
-        MegaOp& o = gemv_op(1, m.hidden);
-        set_job(o.job[0], m.lm_head, nullptr, e->logits);
-        o.x_ll = e->x_ll; o.src_op = last_x_op; o.norm_w = m.out_norm; o.eps = m.eps; o.norm_add_one = m.norm_add_one; o.epilogue = EPI_ARGMAX;
-        if (plan_mega_gemv(o, 1, m.hidden, n_ctas, e->mega_warps, slot_bytes, &acc_floats)) return -1;
+    {   // lm_head with fused arg-max
+        GemvLaunch g;
+        memset(&g, 0, sizeof(g));
+        set_job(g.p.job[0], m.lm_head, nullptr, e->logits);
+        consume_residual(g.p, pending_inbox, pending_seq, pending_w);
+        g.p.x_out = e->x;                   // the final hidden state, also as a plain vector (tests, embeddings)
+        e->x_final = e->x;
+        g.p.norm_w = m.out_norm; g.p.eps = m.eps; g.p.norm_add_one = m.norm_add_one;
+        g.p.epilogue = EPI_ARGMAX; g.p.status = e->status;
+        g.p.amax_val = e->amax_val; g.p.amax_idx = e->amax_idx; g.p.ticket = e->tickets + 1;
+        g.p.logits = m.want_logits ? e->logits : nullptr;
+        g.p.result = e->result; g.p.ctrl = e->ctrl; g.p.token_log = e->token_log; g.p.token_script = e->script; g.p.row_offset = m.vocab_offset;
+        g.p.out_seq_add = 1;
+        fill_peers(e, g.p, 2);
+        if (!tp) g.p.peers.world = 1;
+        g.p.rec = e->rec[4];
+        if (plan_gemv(g, 1, m.hidden, std::min(n_ctas, 4096))) return -1;
+        e->gemvs.push_back(g);
     }
-    e->n_ops = (int)ops.size();
-    PTB_CUDA_OK(cudaMalloc(&e->d_ops, sizeof(MegaOp) * ops.size()));
-    PTB_CUDA_OK(cudaMemcpy(e->d_ops, ops.data(), sizeof(MegaOp) * ops.size(), cudaMemcpyHostToDevice));
-    PTB_CUDA_OK(cudaMalloc(&e->d_bar, 64));
-    PTB_CUDA_OK(cudaMemset(e->d_bar, 0, 64));
-
-    MegaParams& p = e->mp;
-    memset(&p, 0, sizeof(p));
-    p.ops = e->d_ops; p.n_ops = e->n_ops; p.gen = e->d_bar + 1; p.status = e->status; p.ctrl = e->ctrl;
-    p.x = e->x; p.x_ll = e->x_ll; p.qkv_ll = e->qkv_ll; p.att_ll = e->att_ll;
-    p.emb_table = (const uint8_t*)m.embed.w; p.emb_qtype = m.embed.qtype; p.emb_rowbytes = m.embed.rowbytes; p.emb_nblk = m.embed.cols / 256;
-    p.hidden = m.hidden; p.vocab = m.embed.rows; p.emb_scale = m.emb_scale;
-    p.part_o = e->part_o_ll; p.part_ml = e->part_ml_ll;
-    p.n_heads = m.n_heads; p.n_kv_heads = m.n_kv_heads; p.group = m.n_heads / m.n_kv_heads; p.max_seq = m.max_seq;
-    p.max_splits = (m.max_seq + ATT_CHUNK - 1) / ATT_CHUNK; p.neox = m.neox; p.attn_eps = m.eps; p.scale = 1.0f / sqrtf((float)m.head_dim);
-    p.amax_val = e->amax_val; p.amax_idx = e->amax_idx; p.ticket = e->tickets + 1; p.logits = m.want_logits ? e->logits : nullptr;
-    p.result = e->result; p.row_offset = m.vocab_offset; p.token_log = e->token_log; p.token_script = e->script;
-    // shared memory: barriers | misc | quantised input | K-split accumulators | attention scratch | ring
-    int optin = 0;
-    PTB_CUDA_OK(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, e->dev));
-    const size_t cap = (size_t)optin - 1024;          // room for the kernel's static shared memory
-    const int max_slots = 64;
-    size_t off = align_up((size_t)2 * max_slots * 8, 128);
-    p.off_misc = (int)off; off += 512;
-    p.off_xq = (int)off; off += (size_t)kmax;
-    p.off_xs = (int)off; off += (size_t)(kmax / 32) * 4;
-    p.off_xsf = (int)off; off += (size_t)(kmax / 16) * 4;
-    p.off_xsf32 = (int)off; off += (size_t)(kmax / 32) * 4;
-    p.off_acc = (int)off; off += (size_t)acc_floats * 4;
-    off = align_up(off, 16);
-    p.off_attn = (int)off; off += mega_attn_smem(p.group);
-    off = align_up(off, 128);
-    p.off_ring = (int)off;
-    if (off + 4 * (size_t)slot_bytes > cap) { ptb_set_error("persistent decode: %zu B of fixed shared memory leave no room for the ring", off); return -1; }
-    p.slot_bytes = slot_bytes;
-    p.nslots = (int)std::min<size_t>(max_slots, (cap - off) / slot_bytes);
-    const int want = env_int("PTB_MEGA_SLOTS", 0);
-    if (want >= 16 && want < p.nslots) p.nslots = want;
-    if (p.nslots < 16) { ptb_set_error("persistent decode: only %d ring slots fit; at least 16 are needed", p.nslots); return -1; }
-    e->mega_smem = off + (size_t)p.nslots * slot_bytes;
-    if (e->trace) p.trace = e->trace;
     return 0;
 }
+
+static int engine_plan(Engine* e) {
+    // PTB_DECODE_FLOW: "plain" (launch-boundary waits, one GPU only) or "dataflow"; default: plain on one GPU
+    const char* f = getenv("PTB_DECODE_FLOW");
+    e->dataflow = e->m.tp_world > 1 || (f && !strcmp(f, "dataflow"));
+    if (e->dataflow ? engine_plan_dataflow(e) : engine_plan_plain(e)) return -1;
+    const size_t pf_cap = (size_t)env_int("PTB_PREFETCH_MB", 0) << 20;
+    if (pf_cap)
+        for (size_t i = 0; i < e->gemvs.size(); ++i) set_prefetch(e->gemvs[i], e->gemvs[(i + 1) % e->gemvs.size()], pf_cap);
+    return 0;
+}
+
 
 // Enqueue one token's kernels on the engine stream.
 static int engine_enqueue(Engine* e) {
@@ -645,17 +734,14 @@ static int engine_enqueue(Engine* e) {
     const int splits = (m.max_seq + ATT_CHUNK - 1) / ATT_CHUNK;
     const bool pdl = e->use_pdl;
     long n = 0;
-    if (e->mega) {
-        PTB_CUDA_OK(launch_mega(e->mp, e->mega_warps, e->n_sm, e->mega_smem, e->stream));
-        e->launches_per_token = 1;
-        return 0;
-    }
     EmbedParams ep;
     memset(&ep, 0, sizeof(ep));
     ep.table = (const uint8_t*)m.embed.w; ep.qtype = m.embed.qtype; ep.rowbytes = m.embed.rowbytes;
-    ep.nblk = m.embed.cols / 256; ep.H = m.hidden; ep.scale = m.emb_scale; ep.out = e->x; ep.ctrl = e->ctrl;
+    ep.nblk = m.embed.cols / 256; ep.H = m.hidden; ep.scale = m.emb_scale; ep.ctrl = e->ctrl;
+    if (e->dataflow) ep.out_ll = e->x_ll[0];
+    else ep.out = e->x;
     ep.vocab = m.embed.rows; ep.status = e->status;
-    ep.gen = m.tp_world > 1 ? (uint32_t*)(e->ctrl + CTRL_GEN) : nullptr;
+    ep.gen = (const uint32_t*)(e->ctrl + CTRL_GEN);
     // the first kernel of a token is launched without the programmatic edge: it must not
     // overlap the previous token's lm_head, whose epilogue updates the control block
     PTB_CUDA_OK(launch_pdl(embed_kernel, dim3((m.hidden + 255) / 256), dim3(256), 0, e->stream, false, ep));
@@ -668,7 +754,15 @@ static int engine_enqueue(Engine* e) {
         PTB_CUDA_OK(launch_gemv(g0, e->stream, pdl));
         AttnParams a;
         memset(&a, 0, sizeof(a));
-        a.q = e->qkv; a.k = e->qkv + qd; a.v = e->qkv + qd + kvd;
+        if (e->dataflow) {
+            a.q_ll = e->qkv_ll; a.k_ll = e->qkv_ll + qd; a.v_ll = e->qkv_ll + qd + kvd;
+            a.out_ll = e->att_ll; a.in_seq_add = (uint32_t)(l + 1); a.out_seq_add = (uint32_t)(l + 1);
+        } else {
+            a.q = e->qkv; a.k = e->qkv + qd; a.v = e->qkv + qd + kvd;
+            a.out = e->att;
+        }
+        a.gen = (const uint32_t*)(e->ctrl + CTRL_GEN); a.status = e->status; a.wait_ns = e->wait_ns;
+        a.hard_wait = env_int("PTB_DATAFLOW", 1) == 0;
         a.q_norm = L.q_norm; a.k_norm = L.k_norm; a.cos = L.cos; a.sin = L.sin;
         a.k_cache = e->kc + (size_t)l * m.n_kv_heads * m.max_seq * m.head_dim;
         a.v_cache = e->vc + (size_t)l * m.n_kv_heads * m.max_seq * m.head_dim;
@@ -715,11 +809,6 @@ PTB_API void* ptb_engine_create(const PtbModelDesc* m, const PtbLayerDesc* layer
     if (ext_stream) { e->stream = (cudaStream_t)ext_stream; e->own_stream = false; }
     else if (cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) != cudaSuccess) { ptb_set_error("stream create failed"); delete e; return nullptr; }
     if (ensure_attrs() || engine_alloc(e) || engine_plan(e)) { delete e; return nullptr; }
-    // one GPU: the whole token as one persistent launch (PTB_MEGA=1; the default is the kernel-per-op graph)
-    bool any_post = false;
-    for (int l = 0; l < m->n_layers; ++l) any_post = any_post || layers[l].post_attn_norm || layers[l].post_ffn_norm;
-    e->mega = m->tp_world <= 1 && !any_post && env_int("PTB_MEGA", 0) != 0;
-    if (e->mega && engine_plan_mega(e)) { delete e; return nullptr; }
     return e;
 }
 
@@ -734,8 +823,9 @@ PTB_API void ptb_engine_destroy(void* h) {
     cudaFree(e->kc); cudaFree(e->vc); cudaFree(e->part_o); cudaFree(e->part_ml); cudaFree(e->tickets);
     cudaFree(e->amax_val); cudaFree(e->amax_idx); cudaFree(e->ctrl); cudaFree(e->result); cudaFree(e->token_log); cudaFree(e->script);
     cudaFree(e->status);
-    cudaFree(e->d_ops); cudaFree(e->d_bar);
-    cudaFree(e->x_ll); cudaFree(e->qkv_ll); cudaFree(e->att_ll); cudaFree(e->ffn_ll); cudaFree(e->part_o_ll); cudaFree(e->part_ml_ll);
+    cudaFree(e->x_ll[0]); cudaFree(e->x_ll[1]); cudaFree(e->qkv_ll); cudaFree(e->att_ll); cudaFree(e->ffn_ll);
+    cudaFree(e->own_inbox[0]); cudaFree(e->own_inbox[1]);
+    for (int i = 0; i < 5; ++i) cudaFree(e->rec[i]);
     cudaFreeHost(e->h_pinned);
     if (e->own_stream) cudaStreamDestroy(e->stream);
     delete e;
@@ -864,10 +954,10 @@ PTB_API int ptb_engine_kv_bytes(void* h, long* out) {
 }
 
 // Geometry report for one GEMV (tests and notes): rows per tile, stages, grid, smem, tile bytes.
-PTB_API int ptb_gemv_plan(int qtype, int rows, int cols, int rowbytes, int paired, int n_ctas, int* out5) {
+PTB_API int ptb_gemv_plan(int qtype, int rows, int cols, int rowbytes, int layout, int paired, int n_ctas, int* out5) {
     GemvLaunch L;
     memset(&L, 0, sizeof(L));
-    PtbWeightDesc d{(const void*)16, nullptr, qtype, rows, cols, rowbytes};
+    PtbWeightDesc d{(const void*)16, nullptr, qtype, rows, cols, rowbytes, layout, 0};
     set_job(L.p.job[0], d, paired ? &d : nullptr, nullptr);
     if (plan_gemv(L, 1, cols, n_ctas)) return -1;
     out5[0] = L.p.job[0].RW; out5[1] = L.p.stages; out5[2] = L.grid; out5[3] = (int)L.smem; out5[4] = L.p.tile_bytes;

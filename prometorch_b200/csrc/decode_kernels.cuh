@@ -6,8 +6,14 @@
 //    it), the input vector is RMS-normalised and quantised to int8 blocks of 32
 //    in the prologue, and the dot products run on dp4a.  Epilogues: plain store,
 //    residual add, SiLU/GELU-gated product of a gate/up pair, arg-max over the
-//    whole output (two-stage, last CTA finishes), and the tensor-parallel
-//    variant that pushes partial sums to every peer GPU and reduces them.
+//    whole output (two-stage, last CTA finishes), and the partial-sum push:
+//    the result goes to slot [rank] of every GPU's inbox and the CONSUMING
+//    kernel adds the partial sums (and the residual) while it loads its input.
+//  * Inside the engine the kernels of a token do not wait for each other at
+//    launch boundaries: every vector that passes from one kernel to the next is
+//    a buffer of {value, sequence} slots, the consumer is already resident
+//    (launched early, its weights on their way into shared memory) and polls
+//    the slots, so a hand-over costs one store-to-load latency through L2.
 //  * attn_decode_kernel: per-KV-head split-KV attention for one new token with
 //    the per-head QK RMSNorm, RoPE and the fp16 KV-cache write fused in.
 //  * embed_kernel: dequantise one embedding row chosen by a device-side token id.
@@ -26,7 +32,8 @@ constexpr int GEMV_SEG_BLOCKS = 10;             // K is cut into segments of at 
 constexpr int MAX_PEERS = 8;
 
 enum QType : int { QT_Q4K = 0, QT_Q6K = 1 };
-enum Epilogue : int { EPI_STORE = 0, EPI_RESID = 1, EPI_GATED = 2, EPI_ARGMAX = 3, EPI_ALLREDUCE = 4 };
+enum Epilogue : int { EPI_STORE = 0, EPI_RESID = 1, EPI_GATED = 2, EPI_ARGMAX = 3, EPI_PARTIAL = 4 };
+constexpr uint32_t LL_SEQ_MUL = 256;            // sequence number = token generation * LL_SEQ_MUL + index of the write within the token
 
 // Weight layout in device memory (produced once at load time), "segment-major":
 //   K is cut into KS = ceil(nblk / 10) segments (the first nblk % KS of them one block longer);
@@ -42,31 +49,50 @@ struct GemvJob {
     const uint8_t* w;
     const uint8_t* w2;      // second matrix of a gated pair (same shape and type) or null
     const float* bias;      // optional [N]
-    float* out;
+    float* out;             // plain fp32 output, or
+    uint2* out_ll;          // {value, sequence} slots (engine dataflow)
     int qtype, N, nblk;
     int KS, seg_base, seg_rem;
     int RW;                 // rows per warp tile: 1, 2, 4 or 8 (8/RW four-lane groups share a row)
     int cta_begin, cta_count;
 };
 
-struct PeerInfo {           // tensor-parallel all-reduce wiring (EPI_ALLREDUCE, row-split arg-max)
+struct PeerInfo {           // where partial sums go (EPI_PARTIAL) and the row-split arg-max pair exchange
     uint2* inbox[MAX_PEERS];        // inbox[p]: rank p's receive buffer [world][slot_elems] of {payload, sequence}
     int rank, world;                //           slots; inbox[rank] is this GPU's own buffer
     int slot_elems;
-    uint32_t seq_mul, seq_add;      // sequence number of this call = generation * seq_mul + seq_add (never 0)
+    uint32_t seq_add;               // sequence number of this call = generation * LL_SEQ_MUL + seq_add (never 0)
 };
 
 struct GemvParams {
     GemvJob job[GEMV_MAX_JOBS];
     int njobs;
-    const float* x;         // input vector [K] fp32
+    const float* x;         // input vector [K] fp32 (plain mode: the kernel waits for its predecessor), or
+    const uint2* x_ll;      // input vector [K] as {value, sequence} slots with sequence gen * LL_SEQ_MUL + x_seq_add
+    uint32_t x_seq_add;
+    // partial sums to fold into the input: x' = x + sum_p part_ll[p][0..K) (rank order), nparts slots of part_stride
+    const uint2* part_ll;
+    int nparts, part_stride;
+    uint32_t part_seq_add;
+    uint2* x_out_ll;        // CTA 0 publishes x' here (sequence gen * LL_SEQ_MUL + x_out_seq_add) for the next consumer
+    uint32_t x_out_seq_add;
+    uint32_t out_seq_add;   // sequence of this kernel's own outputs (out_ll, EPI_PARTIAL, arg-max pair, records)
+    // Quantised-input records, one 64-byte record per 32 input values (see reduce_block).  When set, a few warps of
+    // the lowest CTAs form the input once (gather, residual update, int8 quantisation) and every CTA copies the
+    // records, instead of every CTA gathering and quantising the whole vector on its own.
+    uint4* rec;
+    unsigned long long wait_ns;   // budget of every poll loop
+    int hard_wait;                // also wait for the predecessor to finish (PTB_DATAFLOW=0: for comparisons)
+    // weights of the kernel that runs next: pulled towards L2 while this kernel works (its own came the same way)
+    const uint8_t* pf_ptr[4];
+    unsigned pf_bytes[4];
     const float* norm_w;    // RMSNorm weight [K] or null (no normalisation)
     float eps;
     int norm_add_one;
     int K;
     int epilogue;
     int act_gelu;
-    const float* resid;     // EPI_RESID / EPI_ALLREDUCE: added to the result
+    const float* resid;     // EPI_RESID: added to the result (plain mode)
     // EPI_ARGMAX scratch
     float* amax_val;        // [grid]
     int* amax_idx;          // [grid]
@@ -78,16 +104,16 @@ struct GemvParams {
     int* ctrl;
     int* token_log;
     const int* token_script;   // self_feed == 2: tokens to feed (a prompt) before switching to the arg-max
-    // EPI_ALLREDUCE
+    // EPI_PARTIAL / arg-max pair
     PeerInfo peers;
-    const uint32_t* gen;    // device generation counter (monotonic, one per token)
+    const uint32_t* gen;    // device generation counter (monotonic, bumped by the token's last kernel)
     int* status;
     int warps;              // warps per CTA (8 or 16): selects the kernel instantiation
     int stages, tile_bytes; // per-warp ring: `stages` slots of `tile_bytes`
     int acc_floats;         // shared-memory accumulators for K-split jobs (0 if every job has KS == 1)
     unsigned long long* trace;  // optional [8] %globaltimer stamps of CTA 0's phases (profiling aid)
-    // post-norm architectures (gemma3): the previous projection stored its raw output in `post_src`; this kernel's
-    // prologue first forms x' = x + RMSNorm(post_src; post_w), CTA 0 writes x' to `x_out`, and the input norm runs on x'
+    // post-norm architectures (gemma3): the previous projection's raw output t (plain `post_src`, or the sum of the
+    // partial slots) is normalised first: x' = x + RMSNorm(t; post_w); CTA 0 writes x' to `x_out` / `x_out_ll`
     const float* post_src;
     const float* post_w;
     float* x_out;
@@ -220,63 +246,165 @@ __device__ __forceinline__ float block_sum(float v, float* buf) {
     return t;
 }
 
-// Load x[K] once into registers, optionally RMS-normalise, quantise to int8 blocks of 32.
+// Where a kernel's input vector comes from.  Plain mode: `x` (and `post_src`) are fp32 arrays that the predecessor
+// finished writing before this kernel passed its dependency wait.  Dataflow mode: `x_ll` and the `nparts` partial-sum
+// slots of `part_ll` are {value, sequence} buffers that the producers may still be filling; the loads below poll them.
+struct InputSrc {
+    const float* x;
+    const uint2* x_ll;
+    uint32_t x_seq;
+    const uint2* part_ll;
+    int nparts, part_stride;
+    uint32_t part_seq;
+    const float* post_src;
+    const float* post_w;
+    float* x_out;
+    uint2* x_out_ll;
+    uint32_t x_out_seq;
+    int* status;
+    unsigned long long wait_ns;
+};
+
+// Load x[K] once into registers (adding the partial sums of the previous projection and, for post-norm
+// architectures, normalising them first), optionally RMS-normalise, quantise to int8 blocks of 32.
 //   xq[K] int8, xs[K/32] block scales, xsf16[K/16] = scale * (sum of 16 int8), xsf32[K/32] = scale * (sum of 32).
 // Each thread keeps up to QIN_ITEMS 8-value items in registers: K <= QIN_ITEMS * 8 * blockDim.
 template <int QIN_ITEMS, bool POST = false>
-__device__ __forceinline__ void quantize_input(const float* __restrict__ x, const float* __restrict__ norm_w, float eps,
+__device__ __forceinline__ void quantize_input(const InputSrc& I, const float* __restrict__ norm_w, float eps,
                                                int add_one, int K, int8_t* xq, float* xs, float* xsf16, float* xsf32,
-                                               float* red, const float* __restrict__ post_src = nullptr,
-                                               const float* __restrict__ post_w = nullptr, float* __restrict__ x_out = nullptr) {
+                                               float* red) {
     const int tid = threadIdx.x, nt = blockDim.x;
     const int items = K / 8;
     float v[QIN_ITEMS][8];
+    float t[POST ? QIN_ITEMS : 1][8];
     float ss = 0.f;
+    if (I.x_ll || I.part_ll) {
+        // ---- dataflow mode.  A status word that is already set means an earlier kernel gave up: do not wait again.
+        const unsigned long long budget = (*reinterpret_cast<volatile int*>(I.status) != 0) ? 0ull : I.wait_ns;
+        unsigned done = 0;
+        uint64_t t0 = 0;
+        for (int round = 0;; ++round) {
+            bool all = true;
 #pragma unroll
-    for (int r = 0; r < QIN_ITEMS; ++r) {
-        const int i = r * nt + tid;
-        if (i < items) {
-            const float4 a = __ldcg(reinterpret_cast<const float4*>(x) + 2 * i), b = __ldcg(reinterpret_cast<const float4*>(x) + 2 * i + 1);
-            v[r][0] = a.x; v[r][1] = a.y; v[r][2] = a.z; v[r][3] = a.w; v[r][4] = b.x; v[r][5] = b.y; v[r][6] = b.z; v[r][7] = b.w;
-        } else {
+            for (int r = 0; r < QIN_ITEMS; ++r) {
+                const int i = r * nt + tid;
+                if (i < items && !((done >> r) & 1u)) {
+                    float a[8], ps[8];
+                    bool ok = true;
+                    if (I.x_ll) ok = ll_try8(I.x_ll + 8 * (size_t)i, I.x_seq, a);
+                    else {
+                        const float4 lo = __ldcg(reinterpret_cast<const float4*>(I.x) + 2 * i), hi = __ldcg(reinterpret_cast<const float4*>(I.x) + 2 * i + 1);
+                        a[0] = lo.x; a[1] = lo.y; a[2] = lo.z; a[3] = lo.w; a[4] = hi.x; a[5] = hi.y; a[6] = hi.z; a[7] = hi.w;
+                    }
 #pragma unroll
-            for (int k = 0; k < 8; ++k) v[r][k] = 0.f;
+                    for (int k = 0; k < 8; ++k) ps[k] = 0.f;
+                    for (int p = 0; p < I.nparts; ++p) {        // rank order: every GPU forms bitwise the same sum
+                        float b[8];
+                        ok = ll_try8(I.part_ll + (size_t)p * I.part_stride + 8 * (size_t)i, I.part_seq, b) && ok;
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) ps[k] += b[k];
+                    }
+                    if (ok) {
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) {
+                            v[r][k] = POST ? a[k] : a[k] + ps[k];
+                            if (POST) t[r][k] = ps[k];
+                        }
+                        done |= 1u << r;
+                    } else all = false;
+                }
+            }
+            if (!__syncthreads_or(!all)) break;
+            // Not there yet.  Back off to a cheap probe by one warp (32 slots spread over the vector) so that the CTAs
+            // do not hammer L2 with full-vector reads while the producers are at work; thread 0 keeps the clock.
+            bool expired = false;
+            if (tid < 32) {
+                const int si = tid * (K / 32);
+                if (round == 0 && tid == 0) t0 = global_ns();
+                t0 = __shfl_sync(0xffffffffu, t0, 0);
+                for (;;) {
+                    bool ok = true;
+                    if (I.x_ll) ok = ld_ll(I.x_ll + si).y == I.x_seq;
+                    for (int p = 0; p < I.nparts; ++p) ok = ok && ld_ll(I.part_ll + (size_t)p * I.part_stride + si).y == I.part_seq;
+                    if (__all_sync(0xffffffffu, ok)) break;
+                    expired = global_ns() - t0 > budget;
+                    if (__any_sync(0xffffffffu, expired)) { expired = true; break; }
+                    __nanosleep(40);
+                }
+                // the probe can pass while other slots are still missing: the clock also bounds the outer rounds
+                if (!expired && round > 0) expired = __any_sync(0xffffffffu, global_ns() - t0 > budget);
+            }
+            if (__syncthreads_or(expired)) {
+                if (tid == 0) atomicExch(I.status, PTB_ERR_FLAG_TIMEOUT);
+                break;
+            }
         }
-    }
-    if (POST) {
-        // x' = x + RMSNorm(t; post_w): t is the raw output of the previous projection
-        float t[QIN_ITEMS][8];
-        float st = 0.f;
+#pragma unroll
+        for (int r = 0; r < QIN_ITEMS; ++r)
+            if (!((done >> r) & 1u)) {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) { v[r][k] = 0.f; if (POST) t[r][k] = 0.f; }
+            }
+    } else {
 #pragma unroll
         for (int r = 0; r < QIN_ITEMS; ++r) {
             const int i = r * nt + tid;
             if (i < items) {
-                const float4 a = __ldcg(reinterpret_cast<const float4*>(post_src) + 2 * i), b = __ldcg(reinterpret_cast<const float4*>(post_src) + 2 * i + 1);
-                t[r][0] = a.x; t[r][1] = a.y; t[r][2] = a.z; t[r][3] = a.w; t[r][4] = b.x; t[r][5] = b.y; t[r][6] = b.z; t[r][7] = b.w;
+                const float4 a = __ldcg(reinterpret_cast<const float4*>(I.x) + 2 * i), b = __ldcg(reinterpret_cast<const float4*>(I.x) + 2 * i + 1);
+                v[r][0] = a.x; v[r][1] = a.y; v[r][2] = a.z; v[r][3] = a.w; v[r][4] = b.x; v[r][5] = b.y; v[r][6] = b.z; v[r][7] = b.w;
             } else {
 #pragma unroll
-                for (int k = 0; k < 8; ++k) t[r][k] = 0.f;
+                for (int k = 0; k < 8; ++k) v[r][k] = 0.f;
             }
+            if (POST) {
+                if (i < items) {
+                    const float4 a = __ldcg(reinterpret_cast<const float4*>(I.post_src) + 2 * i), b = __ldcg(reinterpret_cast<const float4*>(I.post_src) + 2 * i + 1);
+                    t[r][0] = a.x; t[r][1] = a.y; t[r][2] = a.z; t[r][3] = a.w; t[r][4] = b.x; t[r][5] = b.y; t[r][6] = b.z; t[r][7] = b.w;
+                } else {
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) t[r][k] = 0.f;
+                }
+            }
+        }
+    }
+    if (POST) {
+        // x' = x + RMSNorm(t; post_w): t is the raw output of the previous projection
+        float st = 0.f;
+#pragma unroll
+        for (int r = 0; r < QIN_ITEMS; ++r)
 #pragma unroll
             for (int k = 0; k < 8; ++k) st += t[r][k] * t[r][k];
-        }
         st = block_sum(st, red);
         const float rt = rsqrtf(st / (float)K + eps);
 #pragma unroll
         for (int r = 0; r < QIN_ITEMS; ++r) {
             const int i = r * nt + tid;
             if (i < items) {
-                const float4 wa = __ldg(reinterpret_cast<const float4*>(post_w) + 2 * i), wb = __ldg(reinterpret_cast<const float4*>(post_w) + 2 * i + 1);
+                const float4 wa = __ldg(reinterpret_cast<const float4*>(I.post_w) + 2 * i), wb = __ldg(reinterpret_cast<const float4*>(I.post_w) + 2 * i + 1);
                 const float w[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
 #pragma unroll
                 for (int k = 0; k < 8; ++k) v[r][k] += t[r][k] * rt * (add_one ? 1.0f + w[k] : w[k]);
-                if (x_out && blockIdx.x == 0) {
-                    reinterpret_cast<float4*>(x_out)[2 * i] = make_float4(v[r][0], v[r][1], v[r][2], v[r][3]);
-                    reinterpret_cast<float4*>(x_out)[2 * i + 1] = make_float4(v[r][4], v[r][5], v[r][6], v[r][7]);
-                }
             }
         }
         __syncthreads();        // `red` is reused by the next reduction
+    }
+    if (blockIdx.x == 0 && (I.x_out || I.x_out_ll)) {
+        // the updated residual stream, published once for the consumer after next
+#pragma unroll
+        for (int r = 0; r < QIN_ITEMS; ++r) {
+            const int i = r * nt + tid;
+            if (i < items) {
+                if (I.x_out) {
+                    reinterpret_cast<float4*>(I.x_out)[2 * i] = make_float4(v[r][0], v[r][1], v[r][2], v[r][3]);
+                    reinterpret_cast<float4*>(I.x_out)[2 * i + 1] = make_float4(v[r][4], v[r][5], v[r][6], v[r][7]);
+                }
+                if (I.x_out_ll) {
+                    uint2* o = I.x_out_ll + 8 * (size_t)i;
+#pragma unroll
+                    for (int k = 0; k < 8; k += 2) st_ll2(o + k, __float_as_uint(v[r][k]), __float_as_uint(v[r][k + 1]), I.x_out_seq);
+                }
+            }
+        }
     }
 #pragma unroll
     for (int r = 0; r < QIN_ITEMS; ++r)
@@ -321,6 +449,99 @@ __device__ __forceinline__ void quantize_input(const float* __restrict__ x, cons
     __syncthreads();
 }
 
+// ---- quantised-input records --------------------------------------------------------------------------------
+// Record of block b (values 32b .. 32b+31), four 16-byte quarters, each {12 bytes payload, sequence number} written
+// and read as one 16-byte access, so a quarter that shows the expected sequence number is complete:
+//   quarter 0: int8 values 0-11      quarter 1: int8 values 12-23
+//   quarter 2: int8 values 24-31, block scale
+//   quarter 3: scale * (sum of int8 values 0-15), scale * (sum of values 16-31), sum of squares of the fp32 values
+// The int8 values quantise x * norm_w (no 1/rms factor): the consumer derives 1/rms from the sums of squares and
+// applies it to its dot products, so forming a block needs nothing from the other blocks.
+__device__ __forceinline__ void st_rec(uint4* p, uint32_t a, uint32_t b, uint32_t c, uint32_t seq) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(seq) : "memory");
+}
+__device__ __forceinline__ uint4 ld_rec(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
+struct GemvParams;
+// One warp forms block b: polls its sources (the input slots plus the partial-sum slots of every rank, summed in rank
+// order), publishes the updated residual stream, quantises and publishes the record.
+__device__ __forceinline__ void reduce_block(const GemvParams& P, int b, uint32_t gen, int lane, unsigned long long budget);
+
+// Every thread copies its share of the records into the shared-memory arrays the dot products read, polling until
+// each quarter carries `seq`.  Returns the block-wide sum of the per-block sums of squares.
+template <int MAXQ>
+__device__ __forceinline__ float copy_records(const uint4* rec, int nblk, uint32_t seq, int8_t* xq, float* xs, float* xsf16,
+                                              float* xsf32, int* status, unsigned long long budget, float* red) {
+    const int tid = threadIdx.x, nt = blockDim.x;
+    const int nq = 4 * nblk;
+    const int rot = (int)((blockIdx.x * 97u) % (unsigned)nq);     // CTAs sweep the records in different orders
+    unsigned done = 0;
+    float ssq = 0.f;
+    uint64_t t0 = 0;
+    for (int round = 0;; ++round) {
+        bool all = true;
+#pragma unroll
+        for (int r = 0; r < MAXQ; ++r) {
+            const int it = r * nt + tid;
+            if (it < nq && !((done >> r) & 1u)) {
+                int qi = it + rot;
+                if (qi >= nq) qi -= nq;
+                const uint4 v = ld_rec(rec + qi);
+                if (v.w == seq) {
+                    const int blk = qi >> 2, part = qi & 3;
+                    uint32_t* q32 = reinterpret_cast<uint32_t*>(xq + 32 * blk);
+                    if (part == 0) { q32[0] = v.x; q32[1] = v.y; q32[2] = v.z; }
+                    else if (part == 1) { q32[3] = v.x; q32[4] = v.y; q32[5] = v.z; }
+                    else if (part == 2) { q32[6] = v.x; q32[7] = v.y; xs[blk] = __uint_as_float(v.z); }
+                    else {
+                        const float a = __uint_as_float(v.x), bsum = __uint_as_float(v.y);
+                        xsf16[2 * blk] = a; xsf16[2 * blk + 1] = bsum; xsf32[blk] = a + bsum;
+                        ssq += __uint_as_float(v.z);
+                    }
+                    done |= 1u << r;
+                } else all = false;
+            }
+        }
+        if (!__syncthreads_or(!all)) break;
+        bool expired = false;          // not there yet: one warp probes a few records, thread 0 keeps the clock
+        if (tid < 32) {
+            if (round == 0 && tid == 0) t0 = global_ns();
+            t0 = __shfl_sync(0xffffffffu, t0, 0);
+            const int si = (int)(((long long)tid * nq) / 32);
+            for (;;) {
+                const bool ok = ld_rec(rec + si).w == seq;
+                if (__all_sync(0xffffffffu, ok)) break;
+                if (__any_sync(0xffffffffu, global_ns() - t0 > budget)) { expired = true; break; }
+                __nanosleep(20);
+            }
+            if (!expired && round > 0) expired = __any_sync(0xffffffffu, global_ns() - t0 > budget);
+        }
+        if (__syncthreads_or(expired)) {
+            if (tid == 0) atomicExch(status, PTB_ERR_FLAG_TIMEOUT);
+            // fill what never came with zeros so that the kernel can finish
+            for (int r = 0; r < MAXQ; ++r) {
+                const int it = r * nt + tid;
+                if (it < nq && !((done >> r) & 1u)) {
+                    int qi = it + rot;
+                    if (qi >= nq) qi -= nq;
+                    const int blk = qi >> 2, part = qi & 3;
+                    uint32_t* q32 = reinterpret_cast<uint32_t*>(xq + 32 * blk);
+                    if (part == 0) { q32[0] = q32[1] = q32[2] = 0; }
+                    else if (part == 1) { q32[3] = q32[4] = q32[5] = 0; }
+                    else if (part == 2) { q32[6] = q32[7] = 0; xs[blk] = 0.f; }
+                    else { xsf16[2 * blk] = xsf16[2 * blk + 1] = xsf32[blk] = 0.f; }
+                }
+            }
+            break;
+        }
+    }
+    return block_sum(ssq, red);
+}
+
 __host__ __device__ __forceinline__ size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // Shared memory carve-up, used by the kernel and by the host-side planner.
@@ -341,8 +562,183 @@ __host__ __device__ __forceinline__ GemvSmem gemv_smem_layout(int K, int warps, 
     return L;
 }
 
+__device__ __forceinline__ void reduce_block(const GemvParams& P, int b, uint32_t gen, int lane, unsigned long long budget) {
+    const int e = 32 * b + lane;
+    const uint32_t xseq = gen * LL_SEQ_MUL + P.x_seq_add, pseq = gen * LL_SEQ_MUL + P.part_seq_add;
+    const int nparts = P.part_ll ? P.nparts : 0;
+    float v = 0.f;
+    uint64_t t0 = 0;
+    for (int round = 0;; ++round) {
+        const uint2 a = ld_ll(P.x_ll + e);
+        bool ok = a.y == xseq;
+        float ps = 0.f;
+        for (int p = 0; p < nparts; ++p) {              // rank order: every GPU forms bitwise the same sum
+            const uint2 sl = ld_ll(P.part_ll + (size_t)p * P.part_stride + e);
+            ok = ok && sl.y == pseq;
+            ps += __uint_as_float(sl.x);
+        }
+        if (__all_sync(0xffffffffu, ok)) { v = __uint_as_float(a.x) + ps; break; }
+        if (round == 0) t0 = global_ns();
+        if (__any_sync(0xffffffffu, global_ns() - t0 > budget)) {
+            if (lane == 0) atomicExch(P.status, PTB_ERR_FLAG_TIMEOUT);
+            break;
+        }
+        __nanosleep(20);
+    }
+    if (nparts > 0 && P.x_out_ll) st_ll(P.x_out_ll + e, __float_as_uint(v), gen * LL_SEQ_MUL + P.x_out_seq_add);
+    if (P.x_out) P.x_out[e] = v;
+    const float ssq = warp_sum(v * v);
+    float y = v;
+    if (P.norm_w) {
+        const float w = __ldg(P.norm_w + e);
+        y = v * (P.norm_add_one ? 1.0f + w : w);
+    }
+    const float am = warp_max(fabsf(y));
+    const float sc = am / 127.0f, inv = am > 0.f ? 127.0f / am : 0.f;
+    const int q = __float2int_rn(y * inv);
+    int s16 = q;
+#pragma unroll
+    for (int o = 1; o < 16; o <<= 1) s16 += __shfl_xor_sync(0xffffffffu, s16, o);      // lanes 0-15 / 16-31: the two halves
+    const float sf = sc * (float)s16;
+    const float sfa = __shfl_sync(0xffffffffu, sf, 0), sfb = __shfl_sync(0xffffffffu, sf, 16);
+    // four consecutive values per word: lane j < 8 assembles word j
+    const uint32_t byte = (uint32_t)q & 0xffu;
+    const int j4 = 4 * (lane & 7);
+    const uint32_t pk = __shfl_sync(0xffffffffu, byte, j4) | (__shfl_sync(0xffffffffu, byte, j4 + 1) << 8) |
+                        (__shfl_sync(0xffffffffu, byte, j4 + 2) << 16) | (__shfl_sync(0xffffffffu, byte, j4 + 3) << 24);
+    uint32_t w0 = __shfl_sync(0xffffffffu, pk, min(3 * lane, 7));
+    uint32_t w1 = __shfl_sync(0xffffffffu, pk, min(3 * lane + 1, 7));
+    uint32_t w2 = __shfl_sync(0xffffffffu, pk, min(3 * lane + 2, 7));
+    if (lane == 2) w2 = __float_as_uint(sc);
+    if (lane == 3) { w0 = __float_as_uint(sfa); w1 = __float_as_uint(sfb); w2 = __float_as_uint(ssq); }
+    if (lane < 4) st_rec(P.rec + 4 * (size_t)b + lane, w0, w1, w2, gen * LL_SEQ_MUL + P.out_seq_add);
+}
+
+// The input side of a GEMV kernel: fills the shared-memory arrays the dot products read (int8 values, block scales,
+// scaled block sums) from whichever source the launch names, and returns the factor the dot products still have to be
+// multiplied with (1/rms of the input when the records carry the un-normalised vector, else 1).
 template <int GEMV_WARPS>
-__global__ void __launch_bounds__(GEMV_WARPS * 32, 2) gemv_kernel(const __grid_constant__ GemvParams P) {
+__device__ __forceinline__ float gemv_input(const GemvParams& P, uint32_t gen, uint32_t seq, int K, int8_t* xq, float* xs, float* xsf,
+                                            float* xsf32, float* misc, int warp, int lane) {
+    constexpr int GEMV_THREADS = GEMV_WARPS * 32;
+    float in_scale = 1.0f;            // 1/rms of the input when the records carry the un-normalised vector
+    if (P.rec && !P.post_w) {
+        const unsigned long long budget = (*reinterpret_cast<volatile int*>(P.status) != 0) ? 0ull : P.wait_ns;
+        const int nblk32 = K / 32;
+        // the lowest CTAs start first: two of their warps each form blocks
+        if (warp < 2)
+            for (int b = blockIdx.x * 2 + warp; b < nblk32; b += gridDim.x * 2) reduce_block(P, b, gen, lane, budget);
+        const float ssq = copy_records<(GEMV_WARPS >= 16 ? 3 : 5)>(P.rec, nblk32, seq, xq, xs, xsf, xsf32, P.status, budget, misc);
+        if (P.norm_w) in_scale = rsqrtf(ssq / (float)K + P.eps);
+        __syncthreads();
+    } else {
+        InputSrc I;
+        I.x = P.x; I.x_ll = P.x_ll; I.x_seq = gen * LL_SEQ_MUL + P.x_seq_add;
+        I.part_ll = P.part_ll; I.nparts = P.part_ll ? P.nparts : 0; I.part_stride = P.part_stride;
+        I.part_seq = gen * LL_SEQ_MUL + P.part_seq_add;
+        I.post_src = P.post_src; I.post_w = P.post_w; I.x_out = P.x_out; I.x_out_ll = P.x_out_ll;
+        I.x_out_seq = gen * LL_SEQ_MUL + P.x_out_seq_add;
+        I.status = P.status; I.wait_ns = P.wait_ns;
+        if (P.post_w) quantize_input<(GEMV_WARPS >= 16 ? 1 : 2), true>(I, P.norm_w, P.eps, P.norm_add_one, K, xq, xs, xsf, xsf32, misc);
+        else if (K <= 2 * 8 * GEMV_THREADS) quantize_input<2>(I, P.norm_w, P.eps, P.norm_add_one, K, xq, xs, xsf, xsf32, misc);
+        else quantize_input<(GEMV_WARPS >= 16 ? 3 : 5)>(I, P.norm_w, P.eps, P.norm_add_one, K, xq, xs, xsf, xsf32, misc);
+    }
+    return in_scale;
+}
+
+// Arg-max over the whole output: CTA-level reduction, then the last CTA to arrive reduces across CTAs (and, under
+// tensor parallelism, exchanges {value, id} pairs with the other ranks), records the id and advances the decode
+// control block for the next token.
+template <int GEMV_WARPS>
+__device__ __forceinline__ void gemv_argmax_tail(const GemvParams& P, float best_v, int best_i, float* misc, uint32_t gen, uint32_t seq) {
+    constexpr int GEMV_THREADS = GEMV_WARPS * 32;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (P.epilogue == EPI_ARGMAX) {
+        // CTA arg-max (ties -> lowest index), then the last CTA to arrive finishes across CTAs.
+        __syncthreads();
+        float* sv = misc;
+        int* si = reinterpret_cast<int*>(misc + 32);
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best_v, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+            if (ov > best_v || (ov == best_v && oi < best_i)) { best_v = ov; best_i = oi; }
+        }
+        if (lane == 0) { sv[warp] = best_v; si[warp] = best_i; }
+        __syncthreads();
+        __shared__ bool is_last;
+        if (tid == 0) {
+            for (int w = 1; w < GEMV_WARPS; ++w)
+                if (sv[w] > best_v || (sv[w] == best_v && si[w] < best_i)) { best_v = sv[w]; best_i = si[w]; }
+            P.amax_val[blockIdx.x] = best_v;
+            P.amax_idx[blockIdx.x] = best_i;
+            __threadfence();
+            const unsigned t = atomicAdd(P.ticket, 1u);
+            is_last = (t == gridDim.x - 1);
+        }
+        __syncthreads();
+        if (is_last) {
+            __threadfence();
+            float bv = -INFINITY;
+            int bi = 0x7fffffff;
+            for (int i = tid; i < (int)gridDim.x; i += GEMV_THREADS) {
+                const float v = __ldcg(P.amax_val + i);
+                const int ix = __ldcg(P.amax_idx + i);
+                if (v > bv || (v == bv && ix < bi)) { bv = v; bi = ix; }
+            }
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+            }
+            __syncthreads();
+            if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
+            __syncthreads();
+            if (tid == 0) {
+                for (int w = 1; w < GEMV_WARPS; ++w)
+                    if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) { bv = sv[w]; bi = si[w]; }
+                *P.ticket = 0u;
+                bi += P.row_offset;
+                const PeerInfo& pi = P.peers;
+                if (pi.world > 1) {
+                    // every rank holds a slice of the vocabulary: exchange {value, id} and let each rank
+                    // pick the same winner
+                    for (int p = 0; p < pi.world; ++p) {
+                        uint2* slot = pi.inbox[p] + (size_t)pi.rank * pi.slot_elems;
+                        st_ll(slot, __float_as_uint(bv), seq);
+                        st_ll(slot + 1, (uint32_t)bi, seq);
+                    }
+                    bv = -INFINITY;
+                    bi = 0x7fffffff;
+                    for (int p = 0; p < pi.world; ++p) {
+                        const uint2* slot = pi.inbox[pi.rank] + (size_t)p * pi.slot_elems;
+                        const float v = __uint_as_float(wait_ll(slot, seq, P.status, P.wait_ns));
+                        const int ix = (int)wait_ll(slot + 1, seq, P.status, P.wait_ns);
+                        if (v > bv || (v == bv && ix < bi)) { bv = v; bi = ix; }
+                    }
+                }
+                P.result[0] = bi;
+                reinterpret_cast<float*>(P.result)[1] = bv;
+                if (P.ctrl) {
+                    int* ctrl = P.ctrl;
+                    const int step = ctrl[CTRL_STEP];
+                    if (P.token_log && step < ctrl[CTRL_LOG_CAP]) P.token_log[step] = bi;
+                    ctrl[CTRL_STEP] = step + 1;
+                    ctrl[CTRL_GEN] = (int)(gen + 1u);      // the token is over: every slot of the next one carries a new sequence
+                    const int mode = ctrl[CTRL_SELF_FEED];
+                    if (mode) {
+                        const bool scripted = mode == 2 && P.token_script && step + 1 < ctrl[CTRL_SCRIPT_LEN];
+                        ctrl[CTRL_TOKEN] = scripted ? P.token_script[step + 1] : bi;
+                        ctrl[CTRL_POS] += 1;
+                    }
+                }
+            }
+        }
+    }
+
+}
+
+template <int GEMV_WARPS>
+__global__ void __launch_bounds__(GEMV_WARPS * 32, GEMV_WARPS >= 16 ? 1 : 2) gemv_kernel(const __grid_constant__ GemvParams P) {
     constexpr int GEMV_THREADS = GEMV_WARPS * 32;
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -418,16 +814,29 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32, 2) gemv_kernel(const __grid_c
         for (int i = tid * 32; i < K; i += GEMV_THREADS * 32)
             asm volatile("prefetch.global.L2 [%0];" ::"l"(P.norm_w + i));
     }
+    if (lane == 1) {
+        // this CTA's share of the next kernel's weights, 16 KB bulk prefetches spread over the warps
+        constexpr unsigned CH = 16384;
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const unsigned nch = (P.pf_bytes[r] + CH - 1) / CH;
+            for (unsigned c = blockIdx.x * GEMV_WARPS + warp; c < nch; c += gridDim.x * GEMV_WARPS) {
+                const unsigned off = c * CH, len = min(CH, P.pf_bytes[r] - off);
+                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(P.pf_ptr[r] + off), "r"(len) : "memory");
+            }
+        }
+    }
     pdl_launch_dependents();
-    pdl_wait();
+    const bool dataflow = P.x_ll != nullptr;
+    // plain mode: the input is complete once the predecessor has finished.  Dataflow mode: never wait for the
+    // launch boundary, the input slots validate themselves.
+    if (!dataflow || P.hard_wait) pdl_wait();
     __syncthreads();
     stamp(1);
+    const uint32_t gen = P.gen ? *reinterpret_cast<const volatile uint32_t*>(P.gen) : 0u;
+    const uint32_t seq = gen * LL_SEQ_MUL + P.out_seq_add;
 
-    // the RMSNorm weights are parameters too: pull them towards L1/L2 before the dependency wait
-    if (P.post_src) quantize_input<(GEMV_WARPS >= 16 ? 1 : 2), true>(P.x, P.norm_w, P.eps, P.norm_add_one, K, xq, xs, xsf, xsf32, misc, P.post_src,
-                                                                      P.post_w, P.x_out);
-    else if (K <= 2 * 8 * GEMV_THREADS) quantize_input<2>(P.x, P.norm_w, P.eps, P.norm_add_one, K, xq, xs, xsf, xsf32, misc);
-    else quantize_input<(GEMV_WARPS >= 16 ? 3 : 5)>(P.x, P.norm_w, P.eps, P.norm_add_one, K, xq, xs, xsf, xsf32, misc);
+    const float in_scale = gemv_input<GEMV_WARPS>(P, gen, seq, K, xq, xs, xsf, xsf32, misc, warp, lane);
     stamp(2);
 
     // eight 4-lane groups per warp; neighbouring groups take neighbouring rows (same x addresses -> broadcast)
@@ -438,23 +847,29 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32, 2) gemv_kernel(const __grid_c
     int best_i = 0x7fffffff;
     bool ok = true;
 
-    const uint32_t seq = (P.peers.world > 1) ? (*P.gen * P.peers.seq_mul + P.peers.seq_add) : 0u;
     auto epilogue = [&](int n, float v0, float v1) {
+        v0 *= in_scale;
+        v1 *= in_scale;
         if (J.bias) v0 += J.bias[n];
+        float r = v0;
         switch (P.epilogue) {
-            case EPI_STORE: J.out[n] = v0; break;
-            case EPI_RESID: J.out[n] = P.resid[n] + v0; break;
-            case EPI_GATED: J.out[n] = (P.act_gelu ? gelu_tanh(v0) : silu(v0)) * v1; break;
+            case EPI_STORE: break;
+            case EPI_RESID: r = P.resid[n] + v0; break;
+            case EPI_GATED: r = (P.act_gelu ? gelu_tanh(v0) : silu(v0)) * v1; break;
             case EPI_ARGMAX:
                 if (P.logits) P.logits[n] = v0;
                 if (v0 > best_v || (v0 == best_v && n < best_i)) { best_v = v0; best_i = n; }
-                break;
-            case EPI_ALLREDUCE: {
-                // push {partial sum, sequence number} for element n into slot [rank][n] of every rank's inbox
+                return;
+            case EPI_PARTIAL: {
+                // {partial sum, sequence number} for element n into slot [rank][n] of every rank's inbox; whoever
+                // consumes the vector adds the slots up in rank order
                 const PeerInfo& pi = P.peers;
                 for (int p = 0; p < pi.world; ++p) st_ll(pi.inbox[p] + (size_t)pi.rank * pi.slot_elems + n, __float_as_uint(v0), seq);
-            } break;
+                return;
+            }
         }
+        if (J.out_ll) st_ll(J.out_ll + n, __float_as_uint(r), seq);
+        else J.out[n] = r;
     };
 
     int k = 0;
@@ -515,101 +930,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32, 2) gemv_kernel(const __grid_c
     }
 
     stamp(5);
-    if (P.epilogue == EPI_ARGMAX) {
-        // CTA arg-max (ties -> lowest index), then the last CTA to arrive finishes across CTAs.
-        __syncthreads();
-        float* sv = misc;
-        int* si = reinterpret_cast<int*>(misc + 32);
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, best_v, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
-            if (ov > best_v || (ov == best_v && oi < best_i)) { best_v = ov; best_i = oi; }
-        }
-        if (lane == 0) { sv[warp] = best_v; si[warp] = best_i; }
-        __syncthreads();
-        __shared__ bool is_last;
-        if (tid == 0) {
-            for (int w = 1; w < GEMV_WARPS; ++w)
-                if (sv[w] > best_v || (sv[w] == best_v && si[w] < best_i)) { best_v = sv[w]; best_i = si[w]; }
-            P.amax_val[blockIdx.x] = best_v;
-            P.amax_idx[blockIdx.x] = best_i;
-            __threadfence();
-            const unsigned t = atomicAdd(P.ticket, 1u);
-            is_last = (t == gridDim.x - 1);
-        }
-        __syncthreads();
-        if (is_last) {
-            __threadfence();
-            float bv = -INFINITY;
-            int bi = 0x7fffffff;
-            for (int i = tid; i < (int)gridDim.x; i += GEMV_THREADS) {
-                const float v = __ldcg(P.amax_val + i);
-                const int ix = __ldcg(P.amax_idx + i);
-                if (v > bv || (v == bv && ix < bi)) { bv = v; bi = ix; }
-            }
-            for (int o = 16; o > 0; o >>= 1) {
-                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-                if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-            }
-            __syncthreads();
-            if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
-            __syncthreads();
-            if (tid == 0) {
-                for (int w = 1; w < GEMV_WARPS; ++w)
-                    if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) { bv = sv[w]; bi = si[w]; }
-                *P.ticket = 0u;
-                bi += P.row_offset;
-                const PeerInfo& pi = P.peers;
-                if (pi.world > 1) {
-                    // every rank holds a slice of the vocabulary: exchange {value, id} and let each rank
-                    // pick the same winner
-                    for (int p = 0; p < pi.world; ++p) {
-                        uint2* slot = pi.inbox[p] + (size_t)pi.rank * pi.slot_elems;
-                        st_ll(slot, __float_as_uint(bv), seq);
-                        st_ll(slot + 1, (uint32_t)bi, seq);
-                    }
-                    bv = -INFINITY;
-                    bi = 0x7fffffff;
-                    for (int p = 0; p < pi.world; ++p) {
-                        const uint2* slot = pi.inbox[pi.rank] + (size_t)p * pi.slot_elems;
-                        const float v = __uint_as_float(wait_ll(slot, seq, P.status));
-                        const int ix = (int)wait_ll(slot + 1, seq, P.status);
-                        if (v > bv || (v == bv && ix < bi)) { bv = v; bi = ix; }
-                    }
-                }
-                P.result[0] = bi;
-                reinterpret_cast<float*>(P.result)[1] = bv;
-                if (P.ctrl) {
-                    int* ctrl = P.ctrl;
-                    const int step = ctrl[CTRL_STEP];
-                    if (P.token_log && step < ctrl[CTRL_LOG_CAP]) P.token_log[step] = bi;
-                    ctrl[CTRL_STEP] = step + 1;
-                    const int mode = ctrl[CTRL_SELF_FEED];
-                    if (mode) {
-                        const bool scripted = mode == 2 && P.token_script && step + 1 < ctrl[CTRL_SCRIPT_LEN];
-                        ctrl[CTRL_TOKEN] = scripted ? P.token_script[step + 1] : bi;
-                        ctrl[CTRL_POS] += 1;
-                    }
-                }
-            }
-        }
-    }
-
-    if (P.epilogue == EPI_ALLREDUCE) {
-        // Every CTA reduces its own slice of the output: poll the `world` slots of each element (they are
-        // filled by CTAs of this kernel on every rank), sum in rank order so that all ranks get bitwise the
-        // same vector, add the residual.  No fence, ticket or flag: the sequence number travels with the data.
-        const PeerInfo& pi = P.peers;
-        const int N = J.N;
-        const int n0 = (int)(((long long)N * blockIdx.x) / gridDim.x), n1 = (int)(((long long)N * (blockIdx.x + 1)) / gridDim.x);
-        for (int n = n0 + tid; n < n1; n += GEMV_THREADS) {
-            float v = P.resid ? P.resid[n] : 0.f;
-            for (int p = 0; p < pi.world; ++p)
-                v += __uint_as_float(wait_ll(pi.inbox[pi.rank] + (size_t)p * pi.slot_elems + n, seq, P.status));
-            J.out[n] = v;
-        }
-    }
+    if (P.epilogue == EPI_ARGMAX) gemv_argmax_tail<GEMV_WARPS>(P, best_v, best_i, misc, gen, seq);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -623,9 +944,18 @@ constexpr int ATT_D = 128;
 constexpr int ATT_MAX_GROUP = 8;
 
 struct AttnParams {
-    const float* q;          // [heads*d]
+    const float* q;          // [heads*d]      plain inputs (the kernel waits for its predecessor), or
     const float* k;          // [kv_heads*d]
     const float* v;          // [kv_heads*d]
+    const uint2* q_ll;       // the same three vectors as {value, sequence} slots (engine dataflow)
+    const uint2* k_ll;
+    const uint2* v_ll;
+    uint2* out_ll;           // [heads*d] output slots
+    uint32_t in_seq_add, out_seq_add;
+    const uint32_t* gen;
+    int* status;
+    unsigned long long wait_ns;
+    int hard_wait;
     const float* q_norm;     // [d] or null
     const float* k_norm;     // [d] or null
     const float* cos;        // [max_seq][d/2]
@@ -647,12 +977,33 @@ struct AttnParams {
     unsigned long long* trace;   // optional [8] %globaltimer stamps (profiling aid)
 };
 
-__device__ __forceinline__ void norm_rope_head(const float* src, const float* nw, float eps, const float* cs, const float* sn,
+// A vector that is either a plain fp32 array or a buffer of {value, sequence} slots polled until it is filled.
+struct VecSrc {
+    const float* p;
+    const uint2* ll;
+    uint32_t seq;
+    int* status;
+    unsigned long long budget;
+    __device__ __forceinline__ float get(int i) const {
+        return ll ? __uint_as_float(wait_ll(ll + i, seq, status, budget)) : p[i];
+    }
+    // four elements at once: the loads are issued together, a slot that is not filled yet is then waited for alone
+    __device__ __forceinline__ void get4(int i0, int i1, int i2, int i3, float* v) const {
+        if (!ll) { v[0] = p[i0]; v[1] = p[i1]; v[2] = p[i2]; v[3] = p[i3]; return; }
+        const uint2 a = ld_ll(ll + i0), b = ld_ll(ll + i1), c = ld_ll(ll + i2), d = ld_ll(ll + i3);
+        v[0] = a.y == seq ? __uint_as_float(a.x) : get(i0);
+        v[1] = b.y == seq ? __uint_as_float(b.x) : get(i1);
+        v[2] = c.y == seq ? __uint_as_float(c.x) : get(i2);
+        v[3] = d.y == seq ? __uint_as_float(d.x) : get(i3);
+    }
+};
+
+__device__ __forceinline__ void norm_rope_head(const VecSrc& src, const float* nw, float eps, const float* cs, const float* sn,
                                                int neox, float mul, float* dst /*smem [128]*/, int lane) {
     // one warp processes one head of 128 values: lane holds 4 values
     float v[4];
-    if (neox) { v[0] = src[lane]; v[1] = src[lane + 32]; v[2] = src[lane + 64]; v[3] = src[lane + 96]; }
-    else { const float4 t = reinterpret_cast<const float4*>(src)[lane]; v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w; }
+    if (neox) src.get4(lane, lane + 32, lane + 64, lane + 96, v);
+    else src.get4(4 * lane, 4 * lane + 1, 4 * lane + 2, 4 * lane + 3, v);
     if (nw) {
         float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
         ss = warp_sum(ss);
@@ -707,10 +1058,14 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
     };
     stamp(0);
     pdl_launch_dependents();
-    pdl_wait();
+    const bool dataflow = P.q_ll != nullptr;
+    if (!dataflow || P.hard_wait) pdl_wait();
     stamp(1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t gen = P.gen ? *reinterpret_cast<const volatile uint32_t*>(P.gen) : 0u;
+    const uint32_t in_seq = gen * LL_SEQ_MUL + P.in_seq_add, out_seq = gen * LL_SEQ_MUL + P.out_seq_add;
+    const unsigned long long budget = (dataflow && *reinterpret_cast<volatile int*>(P.status) != 0) ? 0ull : P.wait_ns;
     const int crank = (int)cluster.block_rank();
     const int kvh = blockIdx.x / ATT_CLUSTER;
     const int pos = min(P.ctrl[CTRL_POS], P.max_seq - 1);
@@ -729,15 +1084,24 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
     // ---- prologue: q heads of this group (normalised, rotated, pre-scaled by 1/sqrt(d) * log2(e));
     //      the CTA whose chunk holds `pos` normalises/rotates the new K and writes K,V into the cache
     const bool owns_new = active && ((pos / ATT_CHUNK) % ATT_CLUSTER == crank);
-    if (active && warp < G)
-        norm_rope_head(P.q + (size_t)(kvh * G + warp) * ATT_D, P.q_norm, P.eps, cs, sn, P.neox, P.scale * 1.4426950408889634f,
-                       sh.qs[warp], lane);
+    if (active && warp < G) {
+        const size_t o = (size_t)(kvh * G + warp) * ATT_D;
+        const VecSrc qs{P.q ? P.q + o : nullptr, dataflow ? P.q_ll + o : nullptr, in_seq, P.status, budget};
+        norm_rope_head(qs, P.q_norm, P.eps, cs, sn, P.neox, P.scale * 1.4426950408889634f, sh.qs[warp], lane);
+    }
     if (owns_new && warp == ATT_THREADS / 32 - 1) {
-        norm_rope_head(P.k + (size_t)kvh * ATT_D, P.k_norm, P.eps, cs, sn, P.neox, 1.0f, sh.kn, lane);
+        const size_t o = (size_t)kvh * ATT_D;
+        const VecSrc ks{P.k ? P.k + o : nullptr, dataflow ? P.k_ll + o : nullptr, in_seq, P.status, budget};
+        const VecSrc vs{P.v ? P.v + o : nullptr, dataflow ? P.v_ll + o : nullptr, in_seq, P.status, budget};
+        norm_rope_head(ks, P.k_norm, P.eps, cs, sn, P.neox, 1.0f, sh.kn, lane);
         __syncwarp();
-        for (int i = lane; i < ATT_D; i += 32) {
+        float vv[4];
+        vs.get4(lane, lane + 32, lane + 64, lane + 96, vv);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int i = lane + 32 * k;
             kc[(size_t)pos * ATT_D + i] = __float2half_rn(sh.kn[i]);
-            vc[(size_t)pos * ATT_D + i] = __float2half_rn(P.v[(size_t)kvh * ATT_D + i]);
+            vc[(size_t)pos * ATT_D + i] = __float2half_rn(vv[k]);
         }
     }
     if (tid < ATT_MAX_GROUP) { sh.M[tid] = -INFINITY; sh.L[tid] = 0.f; }
@@ -896,7 +1260,9 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
                     Ot += w * ps->O[g][d];
                 }
             }
-            P.out[(size_t)(kvh * G + g) * ATT_D + d] = Ot / Lt;
+            const size_t oi = (size_t)(kvh * G + g) * ATT_D + d;
+            if (P.out_ll) st_ll(P.out_ll + oi, __float_as_uint(Ot / Lt), out_seq);
+            else P.out[oi] = Ot / Lt;
         }
     }
     cluster.sync();      // peers may still be reading this CTA's shared memory
@@ -910,11 +1276,12 @@ struct EmbedParams {
     const uint8_t* table;
     int qtype, rowbytes, nblk, H;
     float scale;
-    float* out;
+    float* out;          // plain fp32 row, or
+    uint2* out_ll;       // {value, sequence} slots with sequence gen * LL_SEQ_MUL (the first write of the token)
     const int* ctrl;
     int vocab;
     int* status;
-    uint32_t* gen;       // bumped once per token (tensor-parallel generation counter) or null
+    const uint32_t* gen; // token generation counter (bumped by the token's last kernel)
 };
 
 static __global__ void __launch_bounds__(256) embed_kernel(const __grid_constant__ EmbedParams P) {
@@ -925,7 +1292,7 @@ static __global__ void __launch_bounds__(256) embed_kernel(const __grid_constant
         if (threadIdx.x == 0) atomicExch(P.status, PTB_ERR_BOUNDS);
         tok = 0;
     }
-    if (P.gen && blockIdx.x == 0 && threadIdx.x == 0) *P.gen = *P.gen + 1;
+    const uint32_t seq = (P.gen ? *reinterpret_cast<const volatile uint32_t*>(P.gen) : 0u) * LL_SEQ_MUL;
     const uint8_t* row = P.table + (size_t)tok * P.rowbytes;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < P.H; i += gridDim.x * blockDim.x) {
         float v;
@@ -957,7 +1324,8 @@ static __global__ void __launch_bounds__(256) embed_kernel(const __grid_constant
         } else {
             v = reinterpret_cast<const float*>(row)[i];
         }
-        P.out[i] = v * P.scale;
+        if (P.out_ll) st_ll(P.out_ll + i, __float_as_uint(v * P.scale), seq);
+        else P.out[i] = v * P.scale;
     }
 }
 

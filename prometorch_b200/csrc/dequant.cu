@@ -53,6 +53,31 @@ __global__ void __launch_bounds__(256) dequant_segmajor_kernel(const uint8_t* __
     }
 }
 
+// The tiles-of-16-rows layout of the tensor-pipe GEMV (decode_gemv_mma.cuh).  grid (nblk, ceil(N / 4)), 256 threads.
+__global__ void __launch_bounds__(256) dequant_t16_kernel(const uint8_t* __restrict__ w, int qtype, int N, int nblk,
+                                                          __nv_bfloat16* __restrict__ out) {
+    const int b = blockIdx.x, e = threadIdx.x;
+    for (int r = blockIdx.y * 4; r < min(N, (int)blockIdx.y * 4 + 4); ++r) {
+        const int tile = r >> 4, rr = r & 15;
+        float v;
+        if (qtype == QT_Q4K) {
+            v = q4k_value(w + (((size_t)tile * nblk + b) * 16 + rr) * 144, e);
+        } else {
+            const uint8_t* blk = w + ((size_t)tile * nblk + b) * 3360;
+            const int n = e >> 7, r7 = e & 127, quad = r7 >> 5, l = r7 & 31;
+            const int qi = n * 64 + (quad & 1) * 32 + l, hi = n * 32 + l;
+            const uint8_t qlb = blk[rr * 128 + ((((qi >> 4) ^ (rr & 7)) << 4) | (qi & 15))];
+            const uint8_t qhb = blk[2048 + rr * 64 + ((((hi >> 4) ^ ((rr >> 1) & 3)) << 4) | (hi & 15))];
+            const int lo4 = (quad >> 1) ? (qlb >> 4) : (qlb & 0xF);
+            const int q = (lo4 | (((qhb >> (2 * quad)) & 3) << 4)) - 32;
+            const int8_t scv = reinterpret_cast<const int8_t*>(blk + 3072 + rr * 16)[e >> 4];
+            const float d = __half2float(*reinterpret_cast<const __half*>(blk + 3328 + rr * 2));
+            v = d * scv * q;
+        }
+        out[(size_t)r * nblk * 256 + (size_t)b * 256 + e] = __float2bfloat16_rn(v);
+    }
+}
+
 // grid (nblk, T), 256 threads: row ids[t] of a row-major table (Q4_K bytes / Q6_K SoA rows / fp16 / fp32)
 __global__ void __launch_bounds__(256) dequant_rows_kernel(const uint8_t* __restrict__ table, int qtype, int rowbytes, int nblk,
                                                            const int* __restrict__ ids, float scale, int vocab, int* status,
@@ -77,11 +102,17 @@ __global__ void __launch_bounds__(256) dequant_rows_kernel(const uint8_t* __rest
 
 using namespace ptb;
 
-// w: a matrix of N rows x cols in the GEMV streaming layout -> out bf16 [N, cols] row-major.
-PTB_API int ptb_dequant_segmajor(const void* w, int qtype, int N, int cols, void* out, cudaStream_t st) {
+// w: a matrix of N rows x cols in a GEMV streaming layout -> out bf16 [N, cols] row-major.
+// layout: 0 = [segment][row][segment bytes], 1 = tiles of 16 rows.
+PTB_API int ptb_dequant_weight(const void* w, int qtype, int layout, int N, int cols, void* out, cudaStream_t st) {
     if (cols % 256 || N <= 0) { ptb_set_error("dequant: %d x %d not supported", N, cols); return -1; }
     if (qtype != QT_Q4K && qtype != QT_Q6K) { ptb_set_error("dequant: unknown quantisation type %d", qtype); return -1; }
     const int nblk = cols / 256;
+    if (layout == 1) {
+        dequant_t16_kernel<<<dim3(nblk, (N + 3) / 4), 256, 0, st>>>((const uint8_t*)w, qtype, N, nblk, (__nv_bfloat16*)out);
+        PTB_CUDA_OK(cudaGetLastError());
+        return 0;
+    }
     const int KS = (nblk + GEMV_SEG_BLOCKS - 1) / GEMV_SEG_BLOCKS;
     dequant_segmajor_kernel<<<dim3(nblk, (N + 3) / 4), 256, 0, st>>>((const uint8_t*)w, qtype, N, nblk, KS, nblk / KS, nblk % KS,
                                                                     (__nv_bfloat16*)out);

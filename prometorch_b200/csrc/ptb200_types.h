@@ -6,11 +6,13 @@
 
 // One quantised matrix in the layout its kernel streams.
 typedef struct PtbWeightDesc {
-    const void* w;          // GEMV streaming layout ([segment][row][segment bytes]) or, for tables, row-major rows
+    const void* w;          // a GEMV streaming layout (see `layout`) or, for tables, row-major rows
     const void* bias;       // optional fp32 [rows]
     int qtype;              // 0 = Q4_K, 1 = Q6_K (structure of arrays), tables also: 2 = fp16, 3 = fp32
     int rows, cols;
     int rowbytes;           // > 0 only for row-major tables (the embedding)
+    int layout;             // 0: [segment][row][segment bytes] (dp4a kernel); 1: tiles of 16 rows (tensor-pipe kernel)
+    int pad;
 } PtbWeightDesc;
 
 typedef struct PtbLayerDesc {

@@ -25,7 +25,8 @@ struct SampleParams {
     int n_hist, hist_cap;    // the chosen id is appended at history[n_hist] when it fits
     float repeat_penalty, temperature, top_p, u;
     int top_k;
-    unsigned* counters;      // [0] number of candidates; zero between calls
+    unsigned* counters;      // [0] number of candidates; zero between calls.  [1] candidates dropped so far because more
+                             // than SAMP_MAX_CAND logits fell into the threshold bin (sticky; see ptb_sample_dropped)
     unsigned* hist;          // [SAMP_BINS], zero between calls
     float* cand_val;         // [SAMP_MAX_CAND]
     int* cand_idx;
@@ -145,6 +146,7 @@ __device__ __forceinline__ void sample_final_body(const SampleParams& P) {
     __shared__ int si[SAMP_MAX_CAND];
     const int tid = threadIdx.x;
     const int n_cand = (int)min(*P.counters, (unsigned)SAMP_MAX_CAND);
+    if (tid == 0 && *P.counters > (unsigned)SAMP_MAX_CAND) P.counters[1] += *P.counters - (unsigned)SAMP_MAX_CAND;
     int n = 64;
     while (n < n_cand) n <<= 1;
     for (int i = tid; i < n; i += 1024) {
@@ -213,6 +215,13 @@ static void fill_sample_params(SampleParams& p, const float* logits, int V, int*
 }
 
 // Bytes of scratch for a vocabulary of V entries (zero it once before the first call).
+// How many candidates the sampler behind `scratch` has dropped since the scratch was zeroed (0 unless thousands of
+// logits are tied at the top-k boundary); a non-zero count means some draws ignored tied candidates.
+PTB_API int ptb_sample_dropped(const void* scratch, unsigned* out) {
+    PTB_CUDA_OK(cudaMemcpy(out, (const unsigned*)scratch + 1, sizeof(unsigned), cudaMemcpyDeviceToHost));
+    return 0;
+}
+
 PTB_API long long ptb_sample_scratch_bytes(int V) { return 64 + (long long)SAMP_BINS * 4 + (long long)SAMP_MAX_CAND * 8 + (long long)V * 4; }
 
 // history: device array of `hist_cap` ids of which the first n_hist are valid; the chosen id is appended.

@@ -43,6 +43,19 @@ def _decls(L):
     L.ptb_allgather.restype = ci
     L.ptb_peer_barrier.argtypes = [pp, ci, ci, cu, vp, vp, vp]
     L.ptb_peer_barrier.restype = ci
+    L.ptb_ddp_allreduce_master.argtypes = [pp, pp, pp, ci, ci, ll, cf, cu, vp, vp, ci, vp]
+    L.ptb_ddp_allreduce_master.restype = ci
+    L.ptb_set_collective_timeout_ms.argtypes = [ci]
+    L.ptb_set_collective_timeout_ms.restype = None
+    L.ptb_get_collective_timeout_ms.argtypes = []
+    L.ptb_get_collective_timeout_ms.restype = ci
+
+
+def set_collective_timeout(seconds: float):
+    """Wall-clock budget of every wait inside the fused collective kernels (default 10 s, or the environment variable
+    PTB_COLLECTIVE_TIMEOUT_MS).  A peer that is further behind than this makes the kernel give up: it records a status
+    code, leaves the data untouched and the next status check raises ``CollectiveTimeout``."""
+    N.lib().ptb_set_collective_timeout_ms(int(seconds * 1000))
 
 
 def _ptr_array(ptrs):
@@ -52,45 +65,75 @@ def _ptr_array(ptrs):
 class PeerChannel:
     """A symmetric buffer plus its flag block and launch bookkeeping for the fused collectives."""
 
-    def __init__(self, symm, nbytes: int):
+    def __init__(self, symm, nbytes: int, status: Optional[torch.Tensor] = None):
+        """``status``: share one status word between several channels (one host read then covers all of them)."""
         self.symm = symm
         self.buf = symm.alloc(nbytes)
         self.flags = symm.alloc(2 * 8 * 4)
         self.bufs = _ptr_array([self.buf.peer_ptr(r) for r in range(symm.world)])
         self.flag_ptrs = _ptr_array([self.flags.peer_ptr(r) for r in range(symm.world)])
         self.ticket = torch.zeros(1, dtype=torch.int32, device=symm.device)
-        self.status = torch.zeros(1, dtype=torch.int32, device=symm.device)
+        self.status = status if status is not None else torch.zeros(1, dtype=torch.int32, device=symm.device)
+        self._host_status = torch.zeros(1, dtype=torch.int32).pin_memory() if symm.device.type == "cuda" else None
         self.seq = 0
 
     def next_seq(self) -> int:
         self.seq += 1
         return self.seq
 
-    def check(self):
-        s = int(self.status)
+    def stage_status(self, stream=None):
+        """Queue a copy of the status word to pinned host memory behind the kernels already on ``stream``; returns the
+        event that marks its arrival.  ``raise_if_failed(event)`` then costs no more than waiting for that event."""
+        st = stream if stream is not None else torch.cuda.current_stream(self.status.device)
+        with torch.cuda.stream(st):
+            self._host_status.copy_(self.status, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(st)
+        return ev
+
+    def raise_if_failed(self, event=None):
+        if event is not None:
+            event.synchronize()
+            s = int(self._host_status[0])
+        else:
+            s = int(self.status)
         if s:
             self.status.zero_()
             from .process_group import CollectiveTimeout
             raise CollectiveTimeout(f"fused collective: a peer GPU did not arrive within the wait budget (status {s})")
 
+    def check(self):
+        self.raise_if_failed()
+
 
 class _Bucket:
-    def __init__(self, params: List[nn.Parameter], dtype, device, symm):
+    def __init__(self, params: List[nn.Parameter], dtype, device, symm, fp32_master: bool = False):
         self.params = params
         n = sum(p.numel() for p in params)
         self.numel = (n + 63) // 64 * 64
         self.channel = None
+        self.master = None             # fp32 copy of the reduced gradients (bf16 buckets with fp32_master_grads)
+        self.master_views = None
         if symm is not None and device.type == "cuda":
             self.channel = PeerChannel(symm, self.numel * torch.empty(0, dtype=dtype).element_size())
             self.flat = self.channel.buf.tensor(dtype)[:self.numel]
+            if fp32_master and dtype == torch.bfloat16:
+                self.master_buf = symm.alloc(self.numel * 4)
+                self.master_ptrs = _ptr_array([self.master_buf.peer_ptr(r) for r in range(symm.world)])
+                self.master = self.master_buf.tensor(torch.float32)[:self.numel]
+                self.master.zero_()
         else:
             self.flat = torch.zeros(self.numel, dtype=dtype, device=device)
         self.flat.zero_()
         off = 0
         self.views = []
+        if self.master is not None:
+            self.master_views = []
         for p in params:
             v = self.flat[off:off + p.numel()].view_as(p)
             self.views.append(v)
+            if self.master is not None:
+                self.master_views.append(self.master[off:off + p.numel()].view_as(p))
             off += p.numel()
         self.pending = len(params)
         self.work = None
@@ -100,8 +143,16 @@ class _Bucket:
 
 class DistributedDataParallel(nn.Module):
     def __init__(self, module: nn.Module, process_group: Optional[ProcessGroup] = None, broadcast_parameters: bool = True,
-                 bucket_mb: float = 25.0, symm=None, comm_ctas: int = 32):
+                 bucket_mb: float = 25.0, symm=None, comm_ctas: int = 32, check_every: int = 1,
+                 fp32_master_grads: bool = False):
+        """``check_every``: with the fused (symmetric-memory) reduction, every that many calls
+        ``finish_gradient_synchronization()`` waits for the reductions and raises ``CollectiveTimeout`` if a kernel
+        gave up waiting for a peer, so the optimizer never steps on gradients that were not reduced (0 = only
+        ``check()`` looks).  ``fp32_master_grads``: bf16 buckets are reduced into fp32 copies
+        (``master_grad(param)``) by the same kernel, for optimizers that keep fp32 master weights."""
         super().__init__()
+        self.check_every, self._finish_calls = int(check_every), 0
+        self.fp32_master_grads = bool(fp32_master_grads)
         self.module = module
         if process_group is None:
             import torch.distributed as dist
@@ -143,7 +194,7 @@ class DistributedDataParallel(nn.Module):
         if cur:
             groups.append(cur)
         for g in groups:
-            b = _Bucket(g, g[0].dtype, g[0].device, self.symm)
+            b = _Bucket(g, g[0].dtype, g[0].device, self.symm, self.fp32_master_grads)
             for p, v in zip(g, b.views):
                 p.grad = v                          # the gradient IS the bucket slice
                 self._bucket_of[id(p)] = b
@@ -172,9 +223,15 @@ class DistributedDataParallel(nn.Module):
             self._comm_stream.wait_stream(cur)
             with torch.cuda.stream(self._comm_stream):
                 ch = b.channel
-                N.check(N.lib().ptb_ddp_allreduce(ch.bufs, ch.flag_ptrs, self.rank, self.world_size, b.numel,
-                                                  int(b.flat.dtype == torch.bfloat16), scale, ch.next_seq(), ch.ticket.data_ptr(),
-                                                  ch.status.data_ptr(), self.comm_ctas, self._comm_stream.cuda_stream), "ddp_allreduce")
+                if b.master is not None:
+                    N.check(N.lib().ptb_ddp_allreduce_master(ch.bufs, b.master_ptrs, ch.flag_ptrs, self.rank, self.world_size,
+                                                             b.numel, scale, ch.next_seq(), ch.ticket.data_ptr(),
+                                                             ch.status.data_ptr(), self.comm_ctas,
+                                                             self._comm_stream.cuda_stream), "ddp_allreduce_master")
+                else:
+                    N.check(N.lib().ptb_ddp_allreduce(ch.bufs, ch.flag_ptrs, self.rank, self.world_size, b.numel,
+                                                      int(b.flat.dtype == torch.bfloat16), scale, ch.next_seq(), ch.ticket.data_ptr(),
+                                                      ch.status.data_ptr(), self.comm_ctas, self._comm_stream.cuda_stream), "ddp_allreduce")
                 b.event = torch.cuda.Event()
                 b.event.record(self._comm_stream)
         elif isinstance(self.process_group, TorchProcessGroup) and b.flat.is_cuda:
@@ -195,12 +252,27 @@ class DistributedDataParallel(nn.Module):
             for b in self.buckets:
                 if not b.launched:
                     self._launch(b)
+        self._finish_calls += 1
+        look = self.check_every > 0 and self._finish_calls % self.check_every == 0
+        staged = []
         for b in self.buckets:
             if b.event is not None:
                 torch.cuda.current_stream(b.flat.device).wait_event(b.event)
                 b.event = None
+                if look and b.channel is not None:
+                    staged.append((b.channel, b.channel.stage_status(self._comm_stream)))
             b.launched = False
             b.pending = len(b.params)
+        # a reduction kernel that ran out of time left its bucket unreduced: say so before anybody steps on it
+        for ch, ev in staged:
+            ch.raise_if_failed(ev)
+
+    def master_grad(self, param):
+        """The fp32 reduced gradient of ``param`` (``fp32_master_grads=True`` and a bf16 parameter), else None."""
+        b = self._bucket_of.get(id(param))
+        if b is None or b.master_views is None:
+            return None
+        return b.master_views[[id(q) for q in b.params].index(id(param))]
 
     def sync_gradients(self):
         """Reduce every bucket now, regardless of hooks (the reference's explicit entry point)."""

@@ -83,16 +83,51 @@ def segment_major(raw: torch.Tensor, qtype: GGMLType, b0: int, b1: int) -> torch
     return torch.cat(out).contiguous()
 
 
+LAYOUT_SEGMENT, LAYOUT_T16 = 0, 1
+
+
+def tile16_major(raw: torch.Tensor, qtype: GGMLType, b0: int, b1: int) -> torch.Tensor:
+    """The tensor-pipe GEMV's layout over blocks ``[b0, b1)`` of every row: rows padded with zero blocks to a multiple
+    of 16, then ``[tile of 16 rows][block][row in tile][block bytes]``.  Q6_K blocks are split into their arrays
+    (``ql[16][128] | qh[16][64] | scales[16][16] | d[16]``) and the 16-byte chunks of a ``ql`` row are stored at
+    ``chunk ^ (row & 7)``, those of a ``qh`` row at ``chunk ^ ((row >> 1) & 3)``: the kernel's shared-memory loads then
+    fall on distinct banks (csrc/decode_gemv_mma.cuh)."""
+    n = raw.shape[0]
+    bb = 144 if qtype == GGMLType.Q4_K else 210
+    blk = raw.reshape(n, -1, bb)[:, b0:b1]
+    nb = blk.shape[1]
+    n16 = (n + 15) // 16 * 16
+    if n16 != n:
+        blk = torch.cat([blk, torch.zeros(n16 - n, nb, bb, dtype=torch.uint8, device=blk.device)])
+    t = blk.reshape(n16 // 16, 16, nb, bb).permute(0, 2, 1, 3)             # [tile, block, row, bytes]
+    if qtype == GGMLType.Q4_K:
+        return t.contiguous().reshape(-1)
+    dev = blk.device
+    row = torch.arange(16, device=dev)
+    ql = t[..., 0:128].reshape(-1, nb, 16, 8, 16)
+    qh = t[..., 128:192].reshape(-1, nb, 16, 4, 16)
+    # destination chunk c holds source chunk c ^ key(row) (xor is its own inverse)
+    idx_l = (torch.arange(8, device=dev)[None, :] ^ (row & 7)[:, None])                 # [16, 8]
+    idx_h = (torch.arange(4, device=dev)[None, :] ^ ((row >> 1) & 3)[:, None])          # [16, 4]
+    ql = torch.gather(ql, 3, idx_l[None, None, :, :, None].expand(ql.shape[0], nb, 16, 8, 16))
+    qh = torch.gather(qh, 3, idx_h[None, None, :, :, None].expand(qh.shape[0], nb, 16, 4, 16))
+    parts = [ql.reshape(-1, nb, 16 * 128), qh.reshape(-1, nb, 16 * 64), t[..., 192:208].reshape(-1, nb, 16 * 16),
+             t[..., 208:210].reshape(-1, nb, 16 * 2)]
+    return torch.cat(parts, dim=2).contiguous().reshape(-1)
+
+
 class PackedWeight:
     """A quantised matrix in the layout its kernel streams (``rowbytes`` > 0 only for row-major tables)."""
 
     def __init__(self, data: torch.Tensor, qtype: int, rows: int, cols: int, bias: Optional[torch.Tensor] = None,
-                 rowbytes: int = 0):
+                 rowbytes: int = 0, layout: int = LAYOUT_SEGMENT):
         self.data, self.qtype, self.rows, self.cols, self.bias, self.rowbytes = data, qtype, rows, cols, bias, rowbytes
+        self.layout = layout
         assert data.data_ptr() % 16 == 0
 
     def desc(self) -> N.WeightDesc:
-        return N.WeightDesc(self.data.data_ptr(), N.ptr(self.bias), self.qtype, self.rows, self.cols, self.rowbytes)
+        return N.WeightDesc(self.data.data_ptr(), N.ptr(self.bias), self.qtype, self.rows, self.cols, self.rowbytes,
+                            self.layout, 0)
 
     @property
     def nbytes(self) -> int:
@@ -108,20 +143,27 @@ def _to_kernel_type(raw: torch.Tensor, qtype: GGMLType, cols: int):
     return raw, qtype
 
 
+def default_layout() -> int:
+    """Tiles of 16 rows (tensor-pipe kernel) unless PTB_GEMV_LAYOUT=segment asks for the dp4a kernel's layout."""
+    import os
+    return LAYOUT_SEGMENT if os.environ.get("PTB_GEMV_LAYOUT", "t16") == "segment" else LAYOUT_T16
+
+
 def pack_weight(raw: torch.Tensor, qtype: GGMLType, cols: int, device, rows=None, kblocks=None,
-                bias: Optional[torch.Tensor] = None) -> PackedWeight:
+                bias: Optional[torch.Tensor] = None, layout: Optional[int] = None) -> PackedWeight:
     """``raw``: uint8 ``[N, row_bytes]`` as stored in the file -> GEMV streaming layout on ``device``.
     ``rows=(r0,r1)`` row-slices, ``kblocks=(b0,b1)`` slices super-blocks along K."""
+    layout = default_layout() if layout is None else layout
     if rows is not None:
         raw = raw[rows[0]:rows[1]]
     raw, qtype = _to_kernel_type(raw.to(device, non_blocking=True), qtype, cols)
     b0, b1 = kblocks if kblocks is not None else (0, cols // 256)
-    data = segment_major(raw, qtype, b0, b1)
+    data = tile16_major(raw, qtype, b0, b1) if layout == LAYOUT_T16 else segment_major(raw, qtype, b0, b1)
     if bias is not None:
         bias = bias.to(device).float().contiguous()
         if rows is not None:
             bias = bias[rows[0]:rows[1]].contiguous()
-    return PackedWeight(data, QT_Q4K if qtype == GGMLType.Q4_K else QT_Q6K, raw.shape[0], (b1 - b0) * 256, bias)
+    return PackedWeight(data, QT_Q4K if qtype == GGMLType.Q4_K else QT_Q6K, raw.shape[0], (b1 - b0) * 256, bias, layout=layout)
 
 
 def pack_table(raw: torch.Tensor, qtype: GGMLType, cols: int, device) -> PackedWeight:
@@ -347,7 +389,7 @@ class GGUFModel:
         if buf is None:
             buf = self._dq_scratch[key] = torch.empty(pw.rows, pw.cols, dtype=torch.bfloat16, device=self.device)
         st = torch.cuda.current_stream(self.device).cuda_stream
-        N.check(self._lib.ptb_dequant_segmajor(pw.data.data_ptr(), pw.qtype, pw.rows, pw.cols, buf.data_ptr(), st), "dequant")
+        N.check(self._lib.ptb_dequant_weight(pw.data.data_ptr(), pw.qtype, pw.layout, pw.rows, pw.cols, buf.data_ptr(), st), "dequant")
         return buf
 
     def _kv_views(self, layer: int):

@@ -88,10 +88,16 @@ class GGUFTokenizer:
         text = text.replace(" ", "▁")
         if prefix_space and not text.startswith("▁"):
             text = "▁" + text
+        if not text:
+            return []
+        # whole-word shortcut: a text made only of words that are vocabulary entries themselves needs no merging
+        # (also reaches entries no merge chain leads to, like the reference's longest-match fallback, tokenizer.h:463)
+        if text.startswith("▁"):
+            ids = [self.vocab.get("▁" + w) for w in text[1:].split("▁")]
+            if all(t is not None for t in ids):
+                return ids
         syms = list(text)
         n = len(syms)
-        if n == 0:
-            return []
         prev, nxt, alive = list(range(-1, n - 1)), list(range(1, n + 1)), [True] * n
         heap = []
 

@@ -47,7 +47,7 @@ def quant_gemv(w: PackedWeight, x: torch.Tensor, *, w2: Optional[PackedWeight] =
     scratch = torch.zeros(64 + 8 * n_ctas + 64, dtype=torch.uint8, device=dev)
     status = _status(dev)
     st = torch.cuda.current_stream(dev).cuda_stream
-    N.check(lib.ptb_gemv(w.data.data_ptr(), N.ptr(w2.data) if w2 is not None else 0, w.qtype, w.rows, w.cols, w.rowbytes,
+    N.check(lib.ptb_gemv(w.data.data_ptr(), N.ptr(w2.data) if w2 is not None else 0, w.qtype, w.rows, w.cols, w.rowbytes, w.layout,
                          x.data_ptr(), N.ptr(norm_weight), eps, N.ptr(w.bias), N.ptr(resid), out.data_ptr(), epi,
                          int(gelu), n_ctas, scratch.data_ptr(), status.data_ptr(), st), "quant_gemv")
     if argmax:

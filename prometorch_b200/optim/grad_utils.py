@@ -70,6 +70,7 @@ class GradNormClipper:
             coef = (self.max_norm / (norm + 1e-6)).clamp(max=1.0) if self.max_norm > 0 else torch.ones_like(norm)
             self.out = torch.stack([norm, coef * extra_scale])
             self.found_inf = (~torch.isfinite(norm)).to(torch.int32).reshape(1)
+            self._last = ("tensor_ops", list(ps))      # scale_grads() multiplies with tensor ops for this call
             return self.out
         bf16 = bool(groups[1])
         sub = groups[1] if bf16 else groups[0]
@@ -87,6 +88,10 @@ class GradNormClipper:
     def scale_grads(self):
         """Multiply the gradients by the coefficient computed by :meth:`compute` (device-side)."""
         tab, bf16 = self._last
+        if tab == "tensor_ops":
+            for p in bf16:
+                p.grad.mul_(self.out[1].to(p.grad.dtype))
+            return
         dev = self.out.device
         st = torch.cuda.current_stream(dev).cuda_stream
         N.check(N.lib().ptb_multi_tensor_scale(tab.rows.data_ptr(), tab.chunks.data_ptr(), tab.n_chunks, int(bf16),

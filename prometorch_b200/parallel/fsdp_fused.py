@@ -3,12 +3,16 @@
 Every ``nn.Linear`` weight ``W[out, in]`` is sharded by rows over the ranks (shard height rounded up to
 128 rows so GEMM tiles never straddle shards).  Each rank keeps, per weight:
 
-* its bf16 shard in symmetric memory — what every rank's GEMMs read;
-* the fp32 master shard and AdamW moments;
+* a full-size bf16 weight buffer in symmetric memory: this rank's shard is its own rows of it (what the peers read),
+  the other rows are a staged copy of the peers' shards, refreshed after every optimizer step;
+* the fp32 master shard and AdamW moments (sharded: 1/world of the model per rank);
 * a full-size bf16 gradient buffer in symmetric memory.
 
-Forward  ``y = x W^T``: one tcgen05 GEMM whose TMA producer fetches each B tile from the rank that owns
-those rows (parameter all-gather fused into the consuming GEMM; no gathered copy ever exists).
+Forward  ``y = x W^T``: one tcgen05 GEMM over the full-size buffer.  The peers' rows arrive block by block
+(128 rows) while the GEMM runs: copy engines on a side stream (the default) or stager CTAs of the same launch
+(``PTB_STAGE_IN_KERNEL=1``) copy them exactly once and raise a per-block flag; the GEMM's TMA producer waits for the
+flags of the rows it is about to read, so the all-gather overlaps the math tile by tile.  The price is the full-size
+bf16 copy per weight on every rank (masters and moments stay sharded).
 Backward ``dX = dY W``: the same, with ``W`` read as an N-major operand sharded along K.
 ``dW = dY^T X`` accumulates into the local full-size gradient buffer.
 Step: one kernel per weight reads slice *r* of every peer's gradient buffer, sums in fp32 and applies
@@ -69,7 +73,7 @@ class _ShardedLinearFn(torch.autograd.Function):
 class ShardedLinear(nn.Module):
     """Drop-in for a bias-free ``nn.Linear`` whose weight lives row-sharded across the ranks."""
 
-    def __init__(self, lin: nn.Linear, symm, pg):
+    def __init__(self, lin: nn.Linear, symm, pg, status: Optional[torch.Tensor] = None):
         super().__init__()
         if lin.bias is not None:
             raise NotImplementedError("ShardedLinear: bias-free layers only")
@@ -92,7 +96,7 @@ class ShardedLinear(nn.Module):
         self.full_ptr = self.shard_ch.buf.peer_ptr(r)
         self.stage_flags = torch.zeros((self.S * W + 127) // 128, dtype=torch.int32, device=dev)
         self.stage_seq = 1
-        self.grad_ch = PeerChannel(symm, self.S * W * self.inf * 2)
+        self.grad_ch = PeerChannel(symm, self.S * W * self.inf * 2, status=status)
         self.grad_full = self.grad_ch.buf.tensor(torch.bfloat16)[:self.S * W * self.inf].view(self.S * W, self.inf)
         self.grad_full.zero_()
         self.symm = symm
@@ -153,9 +157,14 @@ class FusedFSDP(nn.Module):
     replicated-parameter AdamW; hyper-parameters follow an optional LR scheduler through ``param_groups``."""
 
     def __init__(self, model: nn.Module, symm, pg, lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1,
-                 min_shard_numel: int = 1 << 16):
+                 min_shard_numel: int = 1 << 16, check_every: int = 1):
+        """``check_every``: every that many ``step()`` calls the host reads the one status word all the fused kernels of
+        this wrapper share and raises ``CollectiveTimeout`` if one of them gave up waiting for a peer (a kernel that
+        gives up applies no update).  0 leaves the check to ``check()``."""
         super().__init__()
         self.symm, self.pg = symm, pg
+        self.check_every, self._steps = int(check_every), 0
+        self.status = torch.zeros(1, dtype=torch.int32, device=symm.device)
         self.sharded: List[ShardedLinear] = []
         self._replace(model, min_shard_numel)
         self.model = model
@@ -171,7 +180,7 @@ class FusedFSDP(nn.Module):
         self.bucket_numel = (n + 63) // 64 * 64
         self.rest_opt = None
         if rest:
-            self.bucket = PeerChannel(symm, self.bucket_numel * 2)
+            self.bucket = PeerChannel(symm, self.bucket_numel * 2, status=self.status)
             flat = self.bucket.buf.tensor(torch.bfloat16)[:self.bucket_numel]
             flat.zero_()
             self.rest_grads, off = [], 0
@@ -192,7 +201,7 @@ class FusedFSDP(nn.Module):
         for name, child in list(mod.named_children()):
             if isinstance(child, nn.Linear) and child.bias is None and child.weight.numel() >= min_numel \
                     and child.in_features % 64 == 0:
-                sl = ShardedLinear(child, self.symm, self.pg)
+                sl = ShardedLinear(child, self.symm, self.pg, self.status)
                 setattr(mod, name, sl)
                 self.sharded.append(sl)
             else:
@@ -222,6 +231,10 @@ class FusedFSDP(nn.Module):
             for mp, p in self._copy_back:
                 p.data.copy_(mp.data)
             self.flat.zero_()
+        self._steps += 1
+        if self.check_every > 0 and self._steps % self.check_every == 0 and self.sharded:
+            ch = self.sharded[0].grad_ch
+            ch.raise_if_failed(ch.stage_status())
 
     def zero_grad(self):
         for p in self.rest:
@@ -315,7 +328,7 @@ class FusedFSDP(nn.Module):
         return man.get("extra", {})
 
     def check(self):
-        for sl in self.sharded:
-            sl.grad_ch.check()
-        if self.rest_opt is not None:
+        if self.sharded:
+            self.sharded[0].grad_ch.check()        # one status word serves every channel of this wrapper
+        elif self.rest_opt is not None:
             self.bucket.check()

@@ -144,7 +144,7 @@ class Trainer:
         module.load_state_dict(serialization.load_state_dict(path), strict=strict)
         sp = path + ".state"
         if os.path.exists(sp):
-            extra = torch.load(sp, weights_only=False)
+            extra = torch.load(sp, weights_only=True)
             self.current_epoch, self.global_step = extra["epoch"] + 1, extra["global_step"]
             torch.set_rng_state(extra["rng"])
             if self.optimizer is not None and extra.get("optimizer") is not None:

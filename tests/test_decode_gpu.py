@@ -11,30 +11,33 @@ from prometorch_b200.io.config import tiny_qwen3_config
 from prometorch_b200.io.synthetic import write_synthetic_gguf
 
 
-def _packed(rows, cols, qt, seed=0):
+def _packed(rows, cols, qt, seed=0, layout=None):
     from prometorch_b200.io.gguf_model import pack_weight
     g = torch.Generator(device="cuda").manual_seed(seed)
     w = torch.randn(rows, cols, device="cuda", generator=g) * 0.02
     raw = Q.quantize(w, qt)
     wd = Q.dequantize(raw, qt, cols)
-    return pack_weight(raw, qt, cols, "cuda"), wd
+    return pack_weight(raw, qt, cols, "cuda", layout=layout), wd
 
 
 def _rel(a, b):
     return float((a - b).norm() / b.norm())
 
 
+@pytest.mark.parametrize("layout", [0, 1], ids=["segment-dp4a", "tile16-mma"])
 @pytest.mark.parametrize("qt", [Q.GGMLType.Q4_K, Q.GGMLType.Q6_K])
 @pytest.mark.parametrize("rows,cols", [(4096, 2560), (2560, 9728), (1024, 2560), (2560, 4096), (300, 512), (7, 256)])
-def test_gemv_matches_fp32(qt, rows, cols):
+def test_gemv_matches_fp32(qt, rows, cols, layout):
     from prometorch_b200.ops.quant_gemv import quant_gemv
-    pw, wd = _packed(rows, cols, qt, seed=rows + cols)
-    x = torch.randn(cols, device="cuda")
+    pw, wd = _packed(rows, cols, qt, seed=rows + cols, layout=layout)
+    x = torch.randn(cols, device="cuda", generator=torch.Generator(device="cuda").manual_seed(rows * 7 + cols))
     y = quant_gemv(pw, x)
     torch.cuda.synchronize()
     ref_q8 = wd @ Q.quantize_activation_q8(x)        # same activation rounding as the kernel
     ref = wd @ x
-    assert _rel(y, ref_q8) < 2e-4, _rel(y, ref_q8)
+    # one int8 step on a single activation (x * (127 / amax) against x / (amax / 127) at a rounding boundary) moves the
+    # result by ~3e-4 of its norm at these sizes; anything systematic is orders of magnitude above that
+    assert _rel(y, ref_q8) < 8e-4, _rel(y, ref_q8)
     assert _rel(y, ref) < 2e-2, _rel(y, ref)
 
 
@@ -185,7 +188,7 @@ def test_dequant_segmajor_matches_oracle(tmp_path):
         ref = dequantize(raw, qt, cols).to(dev)
         pw = pack_weight(raw.view(70, -1), qt, cols, dev)
         out = torch.empty(70, cols, dtype=torch.bfloat16, device=dev)
-        N.check(N.lib().ptb_dequant_segmajor(pw.data.data_ptr(), pw.qtype, 70, cols, out.data_ptr(), torch.cuda.current_stream().cuda_stream))
+        N.check(N.lib().ptb_dequant_weight(pw.data.data_ptr(), pw.qtype, pw.layout, 70, cols, out.data_ptr(), torch.cuda.current_stream().cuda_stream))
         torch.cuda.synchronize()
         assert torch.equal(out, ref.to(torch.bfloat16))
 

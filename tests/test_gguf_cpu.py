@@ -108,3 +108,33 @@ def test_synthetic_model_and_oracle(tmp_path):
     inc = torch.cat([m.forward([t]) for t in toks])
     assert full.shape == (4, 300)
     assert torch.allclose(full, inc, atol=1e-4), (full - inc).abs().max()
+
+
+def test_tile16_layout_round_trip():
+    """The tensor-pipe GEMV's weight layout, rebuilt from its description, gives back the file's blocks."""
+    import torch
+    from prometorch_b200.io.gguf import GGMLType
+    from prometorch_b200.io.gguf_model import tile16_major
+    g = torch.Generator().manual_seed(3)
+    for qt, bb in ((GGMLType.Q4_K, 144), (GGMLType.Q6_K, 210)):
+        n, nblk, b0, b1 = 37, 5, 1, 4
+        raw = torch.randint(0, 256, (n, nblk * bb), generator=g, dtype=torch.uint8)
+        packed = tile16_major(raw, qt, b0, b1)
+        nb, ntile = b1 - b0, (n + 15) // 16
+        assert packed.numel() == ntile * nb * 16 * bb
+        want = raw.reshape(n, nblk, bb)[:, b0:b1]
+        units = packed.reshape(ntile, nb, 16 * bb)
+        for r in (0, 5, 15, 16, 36):
+            tile, rr = divmod(r, 16)
+            for b in range(nb):
+                u = units[tile, b]
+                if qt == GGMLType.Q4_K:
+                    got = u[rr * 144:(rr + 1) * 144]
+                else:
+                    ql = u[rr * 128:(rr + 1) * 128].reshape(8, 16)
+                    qh = u[2048 + rr * 64:2048 + (rr + 1) * 64].reshape(4, 16)
+                    ql = torch.stack([ql[c ^ (rr & 7)] for c in range(8)]).reshape(-1)       # logical chunk c sits at c ^ key
+                    qh = torch.stack([qh[c ^ ((rr >> 1) & 3)] for c in range(4)]).reshape(-1)
+                    got = torch.cat([ql, qh, u[3072 + rr * 16:3072 + (rr + 1) * 16], u[3328 + rr * 2:3328 + (rr + 1) * 2]])
+                assert torch.equal(got, want[r, b]), (qt, r, b)
+        assert int(units[ntile - 1].reshape(nb, 16, -1)[:, 0].sum()) >= 0       # padded rows exist (zeros)
