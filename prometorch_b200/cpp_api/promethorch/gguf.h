@@ -1,0 +1,433 @@
+// promethorch C++ API: GGUF models on the native decode engine.
+//
+//   promethorch::io::gguf::GGUFReader   memory-mapped GGUF v2/v3 reader (metadata, tensor directory, raw blocks)
+//   promethorch::io::GGUFModel          load(path) / forward_decode(token, pos) / generate(prompt ids, n)
+//
+// GGUFModel is the C++ face of what the Python class of the same name does: parse the file, repack the quantised
+// matrices into the decode kernels' streaming layout (tiles of 16 rows, csrc/decode_gemv_mma.cuh), upload them, and
+// drive the engine of libptb200 (CUDA graph per token, arg-max fed back on the device).  The reference's counterpart is
+// torch::io::GGUFModel (torch/io/gguf_model.h: load / forward_decode / generate).  This header covers dense decoder
+// architectures with Q4_K / Q6_K matrices (llama, mistral, qwen2, qwen3: what a Q4_K_M file of those holds); other
+// files go through the Python loader, which also transcodes the remaining block types.
+//
+// Link with libptb200.so and the CUDA runtime.  Needs no libtorch.
+#pragma once
+#include <cuda_runtime.h>
+#include <fcntl.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <map>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "../../csrc/ptb200.h"
+
+namespace promethorch {
+namespace io {
+namespace gguf {
+
+enum GGMLType : uint32_t { F32 = 0, F16 = 1, Q4_0 = 2, Q8_0 = 8, Q2_K = 10, Q3_K = 11, Q4_K = 12, Q5_K = 13, Q6_K = 14, BF16 = 30 };
+
+struct Value {                       // one metadata value: a scalar, a string or an array of them
+    uint32_t type = 0;
+    uint64_t u = 0;
+    int64_t i = 0;
+    double f = 0;
+    bool b = false;
+    std::string s;
+    std::vector<Value> arr;
+    double as_float() const { return type == 6 || type == 12 ? f : (type == 5 || type == 3 || type == 1 || type == 11 ? (double)i : (double)u); }
+    int64_t as_int() const { return type == 6 || type == 12 ? (int64_t)f : (type == 5 || type == 3 || type == 1 || type == 11 ? i : (int64_t)u); }
+};
+
+struct TensorInfo {
+    std::string name;
+    std::vector<int64_t> shape;      // torch order (GGML stores the dimensions reversed)
+    uint32_t type = 0;
+    uint64_t offset = 0;             // from the start of the data section
+    uint64_t nbytes = 0;
+};
+
+inline void block_geometry(uint32_t type, int& elems, int& bytes) {
+    switch (type) {
+        case F32: elems = 1; bytes = 4; break;
+        case F16: case BF16: elems = 1; bytes = 2; break;
+        case Q4_0: elems = 32; bytes = 18; break;
+        case Q8_0: elems = 32; bytes = 34; break;
+        case Q2_K: elems = 256; bytes = 84; break;
+        case Q3_K: elems = 256; bytes = 110; break;
+        case Q4_K: elems = 256; bytes = 144; break;
+        case Q5_K: elems = 256; bytes = 176; break;
+        case Q6_K: elems = 256; bytes = 210; break;
+        default: throw std::runtime_error("GGUF: unsupported tensor type " + std::to_string(type));
+    }
+}
+
+class GGUFReader {
+ public:
+    GGUFReader() = default;
+    explicit GGUFReader(const std::string& path) { open(path); }
+    ~GGUFReader() { close(); }
+    GGUFReader(const GGUFReader&) = delete;
+    GGUFReader& operator=(const GGUFReader&) = delete;
+
+    void open(const std::string& path) {
+        close();
+        fd_ = ::open(path.c_str(), O_RDONLY);
+        if (fd_ < 0) throw std::runtime_error("GGUF: cannot open " + path);
+        struct stat st;
+        ::fstat(fd_, &st);
+        size_ = (size_t)st.st_size;
+        base_ = (const uint8_t*)::mmap(nullptr, size_, PROT_READ, MAP_PRIVATE, fd_, 0);
+        if (base_ == MAP_FAILED) { base_ = nullptr; throw std::runtime_error("GGUF: mmap failed for " + path); }
+        size_t p = 0;
+        if (rd<uint32_t>(p) != 0x46554747u) throw std::runtime_error("GGUF: bad magic in " + path);
+        const uint32_t version = rd<uint32_t>(p);
+        if (version < 2 || version > 3) throw std::runtime_error("GGUF: unsupported version " + std::to_string(version));
+        const uint64_t n_tensors = rd<uint64_t>(p), n_kv = rd<uint64_t>(p);
+        for (uint64_t k = 0; k < n_kv; ++k) {
+            const std::string key = rd_str(p);
+            const uint32_t type = rd<uint32_t>(p);
+            metadata_[key] = rd_value(p, type);
+        }
+        for (uint64_t t = 0; t < n_tensors; ++t) {
+            TensorInfo ti;
+            ti.name = rd_str(p);
+            const uint32_t nd = rd<uint32_t>(p);
+            std::vector<int64_t> dims(nd);
+            for (auto& d : dims) d = (int64_t)rd<uint64_t>(p);
+            ti.shape.assign(dims.rbegin(), dims.rend());
+            ti.type = rd<uint32_t>(p);
+            ti.offset = rd<uint64_t>(p);
+            int be, bb;
+            block_geometry(ti.type, be, bb);
+            int64_t n = 1;
+            for (auto d : dims) n *= d;
+            ti.nbytes = (uint64_t)(n / be) * bb;
+            tensors_[ti.name] = ti;
+        }
+        const uint64_t align = has("general.alignment") ? (uint64_t)get("general.alignment").as_int() : 32;
+        data_ = (p + align - 1) / align * align;
+    }
+    void close() {
+        if (base_) ::munmap((void*)base_, size_);
+        if (fd_ >= 0) ::close(fd_);
+        base_ = nullptr;
+        fd_ = -1;
+        metadata_.clear();
+        tensors_.clear();
+    }
+    bool has(const std::string& key) const { return metadata_.count(key) != 0; }
+    const Value& get(const std::string& key) const {
+        auto it = metadata_.find(key);
+        if (it == metadata_.end()) throw std::runtime_error("GGUF: no metadata key " + key);
+        return it->second;
+    }
+    std::string arch() const { return has("general.architecture") ? get("general.architecture").s : "llama"; }
+    double arch_float(const std::string& k, double dflt) const { return has(arch() + "." + k) ? get(arch() + "." + k).as_float() : dflt; }
+    int64_t arch_int(const std::string& k, int64_t dflt) const { return has(arch() + "." + k) ? get(arch() + "." + k).as_int() : dflt; }
+    bool has_tensor(const std::string& n) const { return tensors_.count(n) != 0; }
+    const TensorInfo& tensor(const std::string& n) const {
+        auto it = tensors_.find(n);
+        if (it == tensors_.end()) throw std::runtime_error("GGUF: no tensor " + n);
+        return it->second;
+    }
+    const uint8_t* data(const TensorInfo& t) const {
+        if (data_ + t.offset + t.nbytes > size_) throw std::runtime_error("GGUF: tensor " + t.name + " runs past the end of the file");
+        return base_ + data_ + t.offset;
+    }
+    const std::map<std::string, TensorInfo>& tensors() const { return tensors_; }
+    const std::map<std::string, Value>& metadata() const { return metadata_; }
+
+ private:
+    template <typename T>
+    T rd(size_t& p) const {
+        if (p + sizeof(T) > size_) throw std::runtime_error("GGUF: truncated file");
+        T v;
+        std::memcpy(&v, base_ + p, sizeof(T));
+        p += sizeof(T);
+        return v;
+    }
+    std::string rd_str(size_t& p) const {
+        const uint64_t n = rd<uint64_t>(p);
+        if (p + n > size_) throw std::runtime_error("GGUF: truncated string");
+        std::string s((const char*)base_ + p, n);
+        p += n;
+        return s;
+    }
+    Value rd_value(size_t& p, uint32_t type) const {
+        Value v;
+        v.type = type;
+        switch (type) {
+            case 0: v.u = rd<uint8_t>(p); break;
+            case 1: v.i = rd<int8_t>(p); break;
+            case 2: v.u = rd<uint16_t>(p); break;
+            case 3: v.i = rd<int16_t>(p); break;
+            case 4: v.u = rd<uint32_t>(p); break;
+            case 5: v.i = rd<int32_t>(p); break;
+            case 6: v.f = rd<float>(p); break;
+            case 7: v.b = rd<uint8_t>(p) != 0; v.u = v.b; break;
+            case 8: v.s = rd_str(p); break;
+            case 9: {
+                const uint32_t et = rd<uint32_t>(p);
+                const uint64_t n = rd<uint64_t>(p);
+                v.arr.reserve(n);
+                for (uint64_t k = 0; k < n; ++k) v.arr.push_back(rd_value(p, et));
+                break;
+            }
+            case 10: v.u = rd<uint64_t>(p); break;
+            case 11: v.i = rd<int64_t>(p); break;
+            case 12: v.f = rd<double>(p); break;
+            default: throw std::runtime_error("GGUF: unknown metadata type " + std::to_string(type));
+        }
+        return v;
+    }
+    int fd_ = -1;
+    const uint8_t* base_ = nullptr;
+    size_t size_ = 0, data_ = 0;
+    std::map<std::string, Value> metadata_;
+    std::map<std::string, TensorInfo> tensors_;
+};
+
+}  // namespace gguf
+
+struct TransformerConfig {
+    std::string architecture = "llama";
+    int vocab_size = 0, hidden_size = 0, num_layers = 0, num_heads = 0, num_kv_heads = 0, intermediate_size = 0, head_dim = 0;
+    int context_length = 8192;
+    double rope_freq_base = 10000.0, rms_norm_eps = 1e-6;
+    bool has_qk_norm = false, rope_neox = false, tie_word_embeddings = false;
+    void parse(const gguf::GGUFReader& r) {
+        architecture = r.arch();
+        hidden_size = (int)r.arch_int("embedding_length", 0);
+        num_layers = (int)r.arch_int("block_count", 0);
+        num_heads = (int)r.arch_int("attention.head_count", 0);
+        num_kv_heads = (int)r.arch_int("attention.head_count_kv", num_heads);
+        intermediate_size = (int)r.arch_int("feed_forward_length", 0);
+        context_length = (int)r.arch_int("context_length", 8192);
+        rope_freq_base = r.arch_float("rope.freq_base", 10000.0);
+        rms_norm_eps = r.arch_float("attention.layer_norm_rms_epsilon", 1e-6);
+        const int key_len = (int)r.arch_int("attention.key_length", 0);
+        head_dim = key_len > 0 ? key_len : hidden_size / std::max(num_heads, 1);
+        vocab_size = (int)r.tensor("token_embd.weight").shape[0];
+        tie_word_embeddings = !r.has_tensor("output.weight");
+        has_qk_norm = architecture == "qwen3";
+        rope_neox = architecture == "qwen2" || architecture == "qwen3" || architecture == "phi3" || architecture == "gemma";
+        if (!(architecture == "llama" || architecture == "mistral" || architecture == "qwen2" || architecture == "qwen3"))
+            throw std::runtime_error("GGUFModel (C++): architecture '" + architecture + "' is served by the Python loader");
+    }
+};
+
+class GGUFModel {
+ public:
+    GGUFModel() = default;
+    ~GGUFModel() { close(); }
+    GGUFModel(const GGUFModel&) = delete;
+    GGUFModel& operator=(const GGUFModel&) = delete;
+
+    TransformerConfig config;
+
+    // Parse, repack, upload and create the engine on the current CUDA device.
+    void load(const std::string& path, int max_seq = 4096) {
+        close();
+        reader_.open(path);
+        config.parse(reader_);
+        max_seq_ = std::min(max_seq, config.context_length);
+        const auto& c = config;
+        std::vector<PtbLayerDesc> layers((size_t)c.num_layers);
+        std::memset(layers.data(), 0, sizeof(PtbLayerDesc) * layers.size());
+        rope_tables();
+        for (int l = 0; l < c.num_layers; ++l) {
+            const std::string p = "blk." + std::to_string(l) + ".";
+            PtbLayerDesc& L = layers[(size_t)l];
+            L.q = matrix(p + "attn_q.weight");
+            L.k = matrix(p + "attn_k.weight");
+            L.v = matrix(p + "attn_v.weight");
+            L.o = matrix(p + "attn_output.weight");
+            L.gate = matrix(p + "ffn_gate.weight");
+            L.up = matrix(p + "ffn_up.weight");
+            L.down = matrix(p + "ffn_down.weight");
+            if (L.gate.qtype != L.up.qtype) throw std::runtime_error("GGUFModel: ffn_gate and ffn_up with different quantisation types");
+            L.attn_norm = vector_f32(p + "attn_norm.weight");
+            L.ffn_norm = vector_f32(p + "ffn_norm.weight");
+            L.q_norm = reader_.has_tensor(p + "attn_q_norm.weight") ? vector_f32(p + "attn_q_norm.weight") : nullptr;
+            L.k_norm = reader_.has_tensor(p + "attn_k_norm.weight") ? vector_f32(p + "attn_k_norm.weight") : nullptr;
+            L.cos = cos_;
+            L.sin = sin_;
+        }
+        PtbModelDesc m;
+        std::memset(&m, 0, sizeof(m));
+        m.n_layers = c.num_layers; m.hidden = c.hidden_size; m.n_heads = c.num_heads; m.n_kv_heads = c.num_kv_heads;
+        m.head_dim = c.head_dim; m.inter = c.intermediate_size; m.vocab = c.vocab_size; m.max_seq = max_seq_;
+        m.eps = (float)c.rms_norm_eps; m.emb_scale = 1.0f; m.neox = c.rope_neox ? 1 : 0;
+        m.embed = table("token_embd.weight");
+        m.lm_head = matrix(c.tie_word_embeddings ? "token_embd.weight" : "output.weight");
+        m.out_norm = vector_f32("output_norm.weight");
+        m.tp_rank = 0; m.tp_world = 1;
+        check_cuda(cudaDeviceSynchronize(), "upload");
+        engine_ = ptb_engine_create(&m, layers.data(), nullptr);
+        if (!engine_) throw std::runtime_error(std::string("GGUFModel: ") + ptb_last_error());
+    }
+    void close() {
+        if (engine_) ptb_engine_destroy(engine_);
+        engine_ = nullptr;
+        for (void* p : device_) cudaFree(p);
+        device_.clear();
+        captured_ = false;
+        cos_ = sin_ = nullptr;
+    }
+    // One decode step fed from the host: returns the arg-max id of the next token.
+    int forward_decode(int token, int pos) {
+        ensure_captured();
+        const int t = ptb_engine_step(engine_, token, pos);
+        if (t < 0) throw std::runtime_error(std::string("forward_decode: ") + ptb_last_error());
+        check_status();
+        return t;
+    }
+    // Greedy generation: the prompt and n_new tokens as back-to-back graph replays, no host round trip in between.
+    std::vector<int> generate(const std::vector<int>& prompt, int n_new) {
+        if (prompt.empty()) throw std::runtime_error("generate: empty prompt");
+        ensure_captured();
+        if (ptb_engine_begin_script(engine_, prompt.data(), (int)prompt.size(), 0)) fail("begin_script");
+        if (ptb_engine_run(engine_, (int)prompt.size() + n_new - 1)) fail("run");
+        std::vector<int> log(prompt.size() + (size_t)n_new);
+        const int steps = ptb_engine_read_log(engine_, log.data(), (int)log.size());
+        if (steps < 0) fail("read_log");
+        check_status();
+        return std::vector<int>(log.begin() + (long)(prompt.size() - 1), log.begin() + std::min<long>(steps, (long)log.size()));
+    }
+    size_t weight_bytes() const { return weight_bytes_; }
+    const gguf::GGUFReader& reader() const { return reader_; }
+
+ private:
+    static void check_cuda(cudaError_t e, const char* what) {
+        if (e != cudaSuccess) throw std::runtime_error(std::string("GGUFModel: ") + what + ": " + cudaGetErrorString(e));
+    }
+    [[noreturn]] void fail(const char* what) { throw std::runtime_error(std::string(what) + ": " + ptb_last_error()); }
+    void check_status() {
+        const int s = ptb_engine_status(engine_);
+        if (s != 0) throw std::runtime_error("GGUFModel: the decode engine reported status " + std::to_string(s));
+    }
+    void ensure_captured() {
+        if (captured_) return;
+        if (ptb_engine_set_ctrl(engine_, 0, 0, 0, 1) || ptb_engine_run(engine_, 1) || ptb_engine_sync(engine_)) fail("warm-up token");
+        check_status();
+        if (ptb_engine_capture(engine_)) fail("graph capture");
+        captured_ = true;
+    }
+    void* upload(const void* host, size_t n) {
+        void* d = nullptr;
+        check_cuda(cudaMalloc(&d, n), "cudaMalloc");
+        check_cuda(cudaMemcpy(d, host, n, cudaMemcpyHostToDevice), "cudaMemcpy");
+        device_.push_back(d);
+        return d;
+    }
+    const float* vector_f32(const std::string& name) {
+        const auto& t = reader_.tensor(name);
+        if (t.type != gguf::F32) throw std::runtime_error("GGUFModel: " + name + " is expected to be F32");
+        return (const float*)upload(reader_.data(t), t.nbytes);
+    }
+    // A matrix in the tiles-of-16-rows streaming layout.
+    PtbWeightDesc matrix(const std::string& name) {
+        const auto& t = reader_.tensor(name);
+        if (t.type != gguf::Q4_K && t.type != gguf::Q6_K)
+            throw std::runtime_error("GGUFModel (C++): " + name + " has block type " + std::to_string(t.type) + "; only Q4_K and Q6_K are handled here");
+        const int rows = (int)t.shape[0], cols = (int)t.shape[1], nblk = cols / 256;
+        const int bb = t.type == gguf::Q4_K ? 144 : 210;
+        const int ntile = (rows + 15) / 16;
+        std::vector<uint8_t> out((size_t)ntile * nblk * 16 * bb, 0);
+        const uint8_t* src = reader_.data(t);
+        for (int r = 0; r < rows; ++r) {
+            const int tile = r >> 4, rr = r & 15;
+            for (int b = 0; b < nblk; ++b) {
+                const uint8_t* blk = src + ((size_t)r * nblk + b) * bb;
+                uint8_t* unit = out.data() + ((size_t)tile * nblk + b) * 16 * bb;
+                if (t.type == gguf::Q4_K) {
+                    std::memcpy(unit + rr * 144, blk, 144);
+                } else {
+                    // ql[16][128] | qh[16][64] | scales[16][16] | d[16]; 16-byte chunks of a row stored at chunk ^ key(row)
+                    for (int ch = 0; ch < 8; ++ch) std::memcpy(unit + rr * 128 + ((ch ^ (rr & 7)) << 4), blk + ch * 16, 16);
+                    for (int ch = 0; ch < 4; ++ch) std::memcpy(unit + 2048 + rr * 64 + ((ch ^ ((rr >> 1) & 3)) << 4), blk + 128 + ch * 16, 16);
+                    std::memcpy(unit + 3072 + rr * 16, blk + 192, 16);
+                    std::memcpy(unit + 3328 + rr * 2, blk + 208, 2);
+                }
+            }
+        }
+        PtbWeightDesc d;
+        std::memset(&d, 0, sizeof(d));
+        d.w = upload(out.data(), out.size());
+        d.qtype = t.type == gguf::Q4_K ? 0 : 1;
+        d.rows = rows;
+        d.cols = cols;
+        d.layout = 1;
+        weight_bytes_ += out.size();
+        return d;
+    }
+    // Row-major rows for look-ups (the embedding): Q4_K as in the file; Q6_K rows as ql | qh | scales | d(+pad to 16).
+    PtbWeightDesc table(const std::string& name) {
+        const auto& t = reader_.tensor(name);
+        const int rows = (int)t.shape[0], cols = (int)t.shape[1], nblk = cols / 256;
+        PtbWeightDesc d;
+        std::memset(&d, 0, sizeof(d));
+        d.rows = rows;
+        d.cols = cols;
+        const uint8_t* src = reader_.data(t);
+        if (t.type == gguf::Q4_K) {
+            d.qtype = 0;
+            d.rowbytes = nblk * 144;
+            d.w = upload(src, (size_t)rows * d.rowbytes);
+        } else if (t.type == gguf::Q6_K) {
+            const int pad = (16 - (nblk * 2) % 16) % 16;
+            d.qtype = 1;
+            d.rowbytes = nblk * 210 + pad;
+            std::vector<uint8_t> out((size_t)rows * d.rowbytes, 0);
+            for (int r = 0; r < rows; ++r)
+                for (int b = 0; b < nblk; ++b) {
+                    const uint8_t* blk = src + ((size_t)r * nblk + b) * 210;
+                    uint8_t* row = out.data() + (size_t)r * d.rowbytes;
+                    std::memcpy(row + b * 128, blk, 128);
+                    std::memcpy(row + nblk * 128 + b * 64, blk + 128, 64);
+                    std::memcpy(row + nblk * 192 + b * 16, blk + 192, 16);
+                    std::memcpy(row + nblk * 208 + b * 2, blk + 208, 2);
+                }
+            d.w = upload(out.data(), out.size());
+        } else if (t.type == gguf::F16 || t.type == gguf::F32) {
+            d.qtype = t.type == gguf::F16 ? 2 : 3;
+            d.rowbytes = cols * (t.type == gguf::F16 ? 2 : 4);
+            d.w = upload(src, (size_t)rows * d.rowbytes);
+        } else {
+            throw std::runtime_error("GGUFModel (C++): embedding table of block type " + std::to_string(t.type) + " is not handled here");
+        }
+        return d;
+    }
+    void rope_tables() {
+        const int half = config.head_dim / 2;
+        std::vector<float> c((size_t)max_seq_ * half), s((size_t)max_seq_ * half);
+        for (int i = 0; i < half; ++i) {
+            const double inv = std::pow(config.rope_freq_base, -2.0 * i / config.head_dim);
+            for (int p = 0; p < max_seq_; ++p) {
+                c[(size_t)p * half + i] = (float)std::cos(p * inv);
+                s[(size_t)p * half + i] = (float)std::sin(p * inv);
+            }
+        }
+        cos_ = (const float*)upload(c.data(), c.size() * 4);
+        sin_ = (const float*)upload(s.data(), s.size() * 4);
+    }
+
+    gguf::GGUFReader reader_;
+    void* engine_ = nullptr;
+    std::vector<void*> device_;
+    const float *cos_ = nullptr, *sin_ = nullptr;
+    int max_seq_ = 0;
+    bool captured_ = false;
+    size_t weight_bytes_ = 0;
+};
+
+}  // namespace io
+}  // namespace promethorch

@@ -515,7 +515,7 @@ static void fill_peers(const Engine* e, GemvParams& p, int which) {
 static int engine_plan_plain(Engine* e) {
     const PtbModelDesc& m = e->m;
     const int qd = m.n_heads * m.head_dim, kvd = m.n_kv_heads * m.head_dim;
-    const int n_ctas = e->n_sm * env_int("PTB_GEMV_CTAS_PER_SM", 2);
+    const int n_ctas = e->n_sm * env_int("PTB_GEMV_CTAS_PER_SM", e->layers[0].q.layout == 1 ? 1 : 2);
     e->gemvs.clear();
     // post-norm architectures: a projection stores its raw output in `tmp`; the next kernel's prologue adds
     // RMSNorm(tmp) to the residual stream, reading X[cur] and (CTA 0) writing X[cur ^ 1]

@@ -274,3 +274,35 @@ def test_batched_sampler_matches_single_request_sampler():
         assert got == want, (rnd, got, want)
         assert all(0 <= g < V for g in got)
     assert [s.n_hist for s in a] == [t.n_hist for t in b] and all(torch.equal(s.hist[:s.n_hist], t.hist[:t.n_hist]) for s, t in zip(a, b))
+
+
+def test_cpp_gguf_model_generates_the_same_ids(tmp_path):
+    """promethorch/gguf.h (C++ reader, repack and engine driver) against the Python GGUFModel on the same file."""
+    import os
+    import shutil
+    import subprocess
+    from prometorch_b200.io.config import tiny_qwen3_config
+    from prometorch_b200.io.gguf_model import GGUFModel
+    from prometorch_b200.io.synthetic import write_synthetic_gguf
+    if shutil.which("g++") is None:
+        pytest.skip("needs g++")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    lib = os.path.join(root, "prometorch_b200", "lib")
+    cuda = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    exe = str(tmp_path / "gguf_generate")
+    cmd = ["g++", "-std=c++17", "-O1", os.path.join(root, "tests", "cpp", "gguf_generate.cpp"), "-o", exe,
+           f"-I{root}/prometorch_b200/cpp_api", f"-I{cuda}/include", f"-L{lib}", "-lptb200", f"-L{cuda}/lib64", "-lcudart",
+           f"-Wl,-rpath,{lib}", f"-Wl,-rpath,{cuda}/lib64"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-3000:]
+    path = str(tmp_path / "cpp.gguf")
+    write_synthetic_gguf(path, tiny_qwen3_config(layers=2, hidden=512, heads=8, kv_heads=2, inter=1024, vocab=1024), seed=3, device="cpu")
+    prompt = [5, 300, 77, 1000, 12]
+    m = GGUFModel(path, device="cuda", max_seq=256)
+    want = m.run_script(prompt, 8)
+    m.close()
+    r = subprocess.run([exe, path, "8"] + [str(t) for t in prompt], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    ids = [int(x) for x in [ln for ln in r.stdout.splitlines() if ln.startswith("IDS")][0].split()[1:]]
+    step = int([ln for ln in r.stdout.splitlines() if ln.startswith("STEP")][0].split()[1])
+    assert ids == want and step == want[0], (ids, want, step)
