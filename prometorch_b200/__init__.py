@@ -15,6 +15,7 @@ from torch import (Tensor, arange, bmm, cat, chunk, clamp, cos, cumsum, device, 
 from torch import bfloat16, bool, float16, float32, float64, int8, int16, int32, int64, uint8  # noqa: F401
 from torch import enable_grad, is_grad_enabled, manual_seed, no_grad, set_grad_enabled  # noqa: F401
 from torch.autograd import backward, grad  # noqa: F401
+from torch.nn.utils.rnn import pack_padded_sequence, pack_sequence, pad_packed_sequence, pad_sequence  # noqa: F401
 
 __version__ = "0.1.0"
 

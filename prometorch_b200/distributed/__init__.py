@@ -197,3 +197,11 @@ def data_parallel_step(fn, data: torch.Tensor, labels: torch.Tensor, params, wor
             if p.requires_grad and p.grad is not None:
                 p.grad.div_(world_size)
     return sum(losses) / max(len(losses), 1)
+
+
+def __getattr__(name):
+    # the pipeline schedule classes live with the other nn.parallel modules (which import this package): resolved lazily
+    if name in ("Pipeline1F1BStage", "PipelineScheduleConfig", "Pipeline"):
+        from ..nn.parallel import pipeline as _p
+        return getattr(_p, name)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

@@ -309,6 +309,48 @@ def dequantize_q4_0(b: torch.Tensor, k: int) -> torch.Tensor:
     return (d[:, None] * q).reshape(*lead, k)
 
 
+def dequantize_q2_k(b: torch.Tensor, k: int) -> torch.Tensor:
+    """Q2_K: 84 bytes per 256 values = scales[16] (low nibble: scale, high nibble: min, per 16 values) | qs[64]
+    (2-bit values) | fp16 d | fp16 dmin.  Value order as ggml stores it: each 128-value half uses 32 bytes of ``qs``;
+    within a half, the four 2-bit planes (shift 0, 2, 4, 6) give 32 values each.  The reference's own routine
+    (torch/io/gguf_dequant.h:437-468) walks the bits byte by byte instead, which does not match files written by
+    ggml; this one does."""
+    lead = b.shape[:-1]
+    blk = b.reshape(-1, 84)
+    sc = blk[:, 0:16].to(torch.int32)
+    qs = blk[:, 16:80].to(torch.int32).reshape(-1, 2, 32)                      # [blocks, half, byte]
+    d, dmin = _bytes_f16(blk[:, 80:82]), _bytes_f16(blk[:, 82:84])
+    shifts = torch.tensor([0, 2, 4, 6], device=b.device, dtype=torch.int32)
+    q = (qs[:, :, None, :] >> shifts[None, None, :, None]) & 3                   # [blocks, half, plane, 32]
+    q = q.reshape(-1, 16, 16).float()                                            # 16 groups of 16, in value order
+    dl = d[:, None] * (sc & 0xF).float()
+    ml = dmin[:, None] * (sc >> 4).float()
+    return (dl[:, :, None] * q - ml[:, :, None]).reshape(*lead, k)
+
+
+def dequantize_q3_k(b: torch.Tensor, k: int) -> torch.Tensor:
+    """Q3_K: 110 bytes per 256 values = hmask[32] (the third bit, one plane per bit position) | qs[64] (low two bits,
+    laid out as in Q2_K) | scales[12] (sixteen 6-bit scales, stored minus 32) | fp16 d.
+    value = d * (scale - 32) * (low2 - (0 if the high bit is set else 4))."""
+    lead = b.shape[:-1]
+    blk = b.reshape(-1, 110)
+    hm = blk[:, 0:32].to(torch.int32)
+    qs = blk[:, 32:96].to(torch.int32).reshape(-1, 2, 32)
+    sr = blk[:, 96:108].to(torch.int32)
+    d = _bytes_f16(blk[:, 108:110])
+    # scales: low 4 bits in bytes 0-7 (two per byte: low nibbles -> scales 0-7, high nibbles -> 8-15), high 2 bits in bytes 8-11
+    lo = torch.cat([sr[:, 0:8] & 0xF, sr[:, 0:8] >> 4], dim=1)                   # [blocks, 16]
+    hi_bytes = sr[:, 8:12]
+    hi = torch.cat([(hi_bytes >> s) & 3 for s in (0, 2, 4, 6)], dim=1)           # scales j, j+4, j+8, j+12 from byte j
+    scales = (lo | (hi << 4)).float() - 32.0
+    shifts = torch.tensor([0, 2, 4, 6], device=b.device, dtype=torch.int32)
+    low2 = (qs[:, :, None, :] >> shifts[None, None, :, None]) & 3               # [blocks, half, plane, 32]
+    bit = torch.arange(8, device=b.device, dtype=torch.int32).reshape(2, 4)      # mask bit of (half, plane)
+    high = (hm[:, None, None, :] >> bit[None, :, :, None]) & 1
+    q = (low2 - 4 * (1 - high)).reshape(-1, 16, 16).float()
+    return (d[:, None, None] * scales[:, :, None] * q).reshape(*lead, k)
+
+
 # --------------------------------------------------------------------------- dispatch
 
 
@@ -348,6 +390,8 @@ def dequantize(b: torch.Tensor, qtype: GGMLType, cols: int) -> torch.Tensor:
         GGMLType.Q6_K: dequantize_q6_k,
         GGMLType.Q8_0: dequantize_q8_0,
         GGMLType.Q4_0: dequantize_q4_0,
+        GGMLType.Q2_K: dequantize_q2_k,
+        GGMLType.Q3_K: dequantize_q3_k,
     }.get(qtype)
     if fn is None:
         raise NotImplementedError(f"dequantize: {qtype.name}")

@@ -73,6 +73,7 @@ class OracleModel:
 
     def __init__(self, path_or_reader, device="cpu", max_seq: int = 4096, emulate_q8: bool = False):
         r = path_or_reader if isinstance(path_or_reader, GGUFReader) else GGUFReader(path_or_reader)
+        self.reader = r
         self.cfg = TransformerConfig.from_gguf(r)
         self.device = device
         self.emulate_q8 = emulate_q8

@@ -322,3 +322,58 @@ def test_linear_scan_reference_and_gradients():
     assert torch.allclose(xf.grad, dx, atol=1e-4) and torch.allclose(gf.grad, dx * hprev, atol=1e-4)
     with pytest.raises(ValueError):
         linear_scan(gf, xf[:, :4])
+
+
+def test_every_native_switch_is_registered():
+    """Every PTB_* environment variable read anywhere in the sources has an entry in utils/env.py."""
+    import os
+    import re
+    from prometorch_b200.utils.env import NATIVE_ENV
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    read = set()
+    pat = re.compile(r'(?:getenv|env_int|environ\.get|environ\[)\(?\s*"(PTB_[A-Z0-9_]+)"')
+    for base in ("prometorch_b200", "benchmarks"):
+        for dp, _, fs in os.walk(os.path.join(root, base)):
+            for f in fs:
+                if f.endswith((".py", ".cu", ".cuh", ".h", ".hpp")):
+                    read |= set(pat.findall(open(os.path.join(dp, f), errors="ignore").read()))
+    read |= set(pat.findall(open(os.path.join(root, "bench.py")).read()))
+    assert read, "the pattern found nothing: the test is broken"
+    assert read <= set(NATIVE_ENV), sorted(read - set(NATIVE_ENV))
+
+
+def test_reference_name_lists_resolve():
+    """The reference's public names (nn modules, functional, top-level ops, optimizers, schedulers, distributed) exist."""
+    import prometorch_b200 as pt
+    nn_names = """ReLU ReLU6 LeakyReLU PReLU ELU SELU GELU Sigmoid Tanh Softmax LogSoftmax Softplus Softsign Hardtanh Hardsigmoid
+        Hardswish SiLU Mish Threshold MultiheadAttention Sequential ModuleList ModuleDict ParameterList ParameterDict Conv1d Conv2d
+        Conv3d ConvTranspose2d Dropout Dropout1d Dropout2d Dropout3d AlphaDropout FeatureAlphaDropout Identity Linear Bilinear
+        LazyLinear Flatten Unflatten LowRankLinear L1Loss MSELoss SmoothL1Loss HuberLoss BCELoss BCEWithLogitsLoss NLLLoss
+        CrossEntropyLoss KLDivLoss CosineEmbeddingLoss MarginRankingLoss TripletMarginLoss MultiMarginLoss PoissonNLLLoss
+        GaussianNLLLoss CTCLoss FocalLoss DiceLoss BatchNorm1d BatchNorm2d LayerNorm GroupNorm InstanceNorm2d RMSNorm MaxPool1d
+        MaxPool2d AvgPool1d AvgPool2d AdaptiveAvgPool1d AdaptiveAvgPool2d AdaptiveMaxPool2d GlobalAvgPool2d RNNCell LSTMCell
+        GRUCell RNN LSTM GRU Embedding EmbeddingBag PositionalEncoding TransformerEncoderLayer TransformerEncoder
+        TransformerDecoderLayer TransformerDecoder Transformer Upsample SyncBatchNorm""".split()
+    missing = [n for n in nn_names if not hasattr(pt.nn, n)]
+    assert not missing, missing
+    top = """tensor empty zeros ones full rand randn randint arange linspace eye zeros_like ones_like from_numpy cat stack split
+        chunk mm bmm matmul dot sum mean max min sqrt exp log sin cos tanh sigmoid relu softmax clamp where cumsum rsqrt norm topk
+        sort nan_to_num isinf isnan isfinite multinomial einsum gather scatter masked_fill pad_sequence pack_sequence
+        pack_padded_sequence pad_packed_sequence backward grad is_grad_enabled set_grad_enabled no_grad enable_grad save load
+        save_state_dict load_state_dict save_pytorch load_pytorch cuda_is_available cuda_device_count compile manual_seed""".split()
+    missing = [n for n in top if not hasattr(pt, n)]
+    assert not missing, missing
+    opt = "SGD Adam AdamW RMSprop Lion SophiaG LAMB Adafactor NAdam RAdam Adagrad Adadelta Adamax AdamKiller ASGD LBFGS EMA ParamGroup".split()
+    sch = """StepLR MultiStepLR ExponentialLR CosineAnnealingLR LinearLR ConstantLR ReduceLROnPlateau WarmupCosineAnnealingLR OneCycleLR
+        CosineAnnealingWarmRestarts CyclicLR PolynomialLR LambdaLR MultiplicativeLR SequentialLR ChainedScheduler""".split()
+    missing = [n for n in opt + sch if not hasattr(pt.optim, n)]
+    assert not missing, missing
+    dist = """init_process_group destroy_process_group is_initialized get_rank get_world_size all_reduce broadcast barrier
+        DistributedDataParallel DDPNoSyncGuard DDPConfig ProcessGroup ReduceOp BackendType FSDPConfig FullyShardedDataParallel
+        ZeROOptimizer ZeROStage3 OffloadOptimizer Pipeline1F1BStage PipelineScheduleConfig launch parse_dist_args DistArgs
+        SyncBatchNorm""".split()
+    missing = [n for n in dist if not hasattr(pt.distributed, n)]
+    assert not missing, missing
+    par = "TPConfig ColumnParallelLinear RowParallelLinear Pipeline tp_all_gather tp_all_reduce_sum tp_barrier".split()
+    missing = [n for n in par if not hasattr(pt.nn.parallel, n)]
+    assert not missing, missing

@@ -138,3 +138,66 @@ def test_tile16_layout_round_trip():
                     got = torch.cat([ql, qh, u[3072 + rr * 16:3072 + (rr + 1) * 16], u[3328 + rr * 2:3328 + (rr + 1) * 2]])
                 assert torch.equal(got, want[r, b]), (qt, r, b)
         assert int(units[ntile - 1].reshape(nb, 16, -1)[:, 0].sum()) >= 0       # padded rows exist (zeros)
+
+
+def _ggml_q2_k_scalar(block: bytes):
+    """ggml's dequantize_row_q2_K, one block, written out as scalar loops (the golden order of values)."""
+    import numpy as np
+    scales, qs = block[0:16], block[16:80]
+    d = float(np.frombuffer(block[80:82], dtype=np.float16)[0])
+    dmin = float(np.frombuffer(block[82:84], dtype=np.float16)[0])
+    y, is_, q = [], 0, 0
+    for _n in range(0, 256, 128):
+        shift = 0
+        for _j in range(4):
+            for off in (0, 16):
+                sc = scales[is_]
+                is_ += 1
+                dl, ml = d * (sc & 0xF), dmin * (sc >> 4)
+                y += [dl * ((qs[q + off + l] >> shift) & 3) - ml for l in range(16)]
+            shift += 2
+        q += 32
+    return y
+
+
+def _ggml_q3_k_scalar(block: bytes):
+    import numpy as np
+    hm, qs, sr = block[0:32], block[32:96], block[96:108]
+    d = float(np.frombuffer(block[108:110], dtype=np.float16)[0])
+    aux = list(np.frombuffer(bytes(sr), dtype=np.uint32).astype(np.uint64))
+    k1, k2 = 0x03030303, 0x0f0f0f0f
+    tmp = int(aux[2])
+    a0, a1 = int(aux[0]), int(aux[1])
+    w = [(a0 & k2) | (((tmp >> 0) & k1) << 4), (a1 & k2) | (((tmp >> 2) & k1) << 4),
+         ((a0 >> 4) & k2) | (((tmp >> 4) & k1) << 4), ((a1 >> 4) & k2) | (((tmp >> 6) & k1) << 4)]
+    scales = np.frombuffer(np.array(w, dtype=np.uint32).tobytes(), dtype=np.int8).astype(int)
+    y, is_, q, m = [], 0, 0, 1
+    for _n in range(0, 256, 128):
+        shift = 0
+        for _j in range(4):
+            for off in (0, 16):
+                dl = d * (scales[is_] - 32)
+                is_ += 1
+                y += [dl * (((qs[q + off + l] >> shift) & 3) - (0 if hm[off + l] & m else 4)) for l in range(16)]
+            shift += 2
+            m <<= 1
+        q += 32
+    return y
+
+
+def test_q2k_q3k_dequant_follow_ggml_order():
+    import numpy as np
+    import torch
+    from prometorch_b200.io.gguf import GGMLType
+    from prometorch_b200.io.gguf_quant import dequantize
+    rng = np.random.default_rng(0)
+    for qt, nbytes, scalar, dpos in ((GGMLType.Q2_K, 84, _ggml_q2_k_scalar, (80, 82)), (GGMLType.Q3_K, 110, _ggml_q3_k_scalar, (108,))):
+        raw = rng.integers(0, 256, size=(3, 2 * nbytes), dtype=np.uint8)
+        for r in range(3):
+            for blk in range(2):
+                for p in dpos:      # sane fp16 scales
+                    raw[r, blk * nbytes + p:blk * nbytes + p + 2] = np.frombuffer(np.float16(rng.uniform(0.01, 0.1)).tobytes(), dtype=np.uint8)
+        got = dequantize(torch.from_numpy(raw), qt, 512)
+        for r in range(3):
+            want = scalar(raw[r, :nbytes].tobytes()) + scalar(raw[r, nbytes:].tobytes())
+            assert torch.allclose(got[r], torch.tensor(want, dtype=torch.float32), atol=1e-6), (qt, r)
