@@ -510,12 +510,14 @@ static void fill_peers(const Engine* e, GemvParams& p, int which) {
     p.gen = (const uint32_t*)(e->ctrl + CTRL_GEN);
 }
 
-// Plain flow (one GPU): every kernel waits for its predecessor at the launch boundary and the vectors between them
-// are ordinary fp32 arrays; the residual stream is updated in place by the projections' epilogues.
+// Plain flow: every kernel waits for its predecessor at the launch boundary and the vectors between them are ordinary
+// fp32 arrays; the residual stream is updated in place by the projections' epilogues.  Under tensor parallelism the
+// K-split projections push their partial sums to every rank and reduce them before they exit (producer-side all-reduce).
 static int engine_plan_plain(Engine* e) {
     const PtbModelDesc& m = e->m;
     const int qd = m.n_heads * m.head_dim, kvd = m.n_kv_heads * m.head_dim;
     const int n_ctas = e->n_sm * env_int("PTB_GEMV_CTAS_PER_SM", e->layers[0].q.layout == 1 ? 1 : 2);
+    const bool tp = m.tp_world > 1;
     e->gemvs.clear();
     // post-norm architectures: a projection stores its raw output in `tmp`; the next kernel's prologue adds
     // RMSNorm(tmp) to the residual stream, reading X[cur] and (CTA 0) writing X[cur ^ 1]
@@ -552,8 +554,9 @@ static int engine_plan_plain(Engine* e) {
             const bool post = L.post_attn_norm != nullptr;
             set_job(g.p.job[0], L.o, nullptr, post ? e->tmp : X[cur]);
             g.p.x = e->att; g.p.resid = post ? nullptr : X[cur]; g.p.status = e->status; g.p.ticket = e->tickets;
-            g.p.epilogue = post ? EPI_STORE : EPI_RESID;
+            g.p.epilogue = tp ? EPI_ALLREDUCE : (post ? EPI_STORE : EPI_RESID);
             g.p.peers.world = 1;
+            if (tp) { fill_peers(e, g.p, 0); g.p.out_seq_add = (uint32_t)(l + 1); }
             if (plan_gemv(g, 1, L.o.cols, n_ctas)) return -1;
             e->gemvs.push_back(g);
             if (post) pending_w = L.post_attn_norm;
@@ -574,8 +577,9 @@ static int engine_plan_plain(Engine* e) {
             const bool post = L.post_ffn_norm != nullptr;
             set_job(g.p.job[0], L.down, nullptr, post ? e->tmp : X[cur]);
             g.p.x = e->ffn; g.p.resid = post ? nullptr : X[cur]; g.p.status = e->status; g.p.ticket = e->tickets;
-            g.p.epilogue = post ? EPI_STORE : EPI_RESID;
+            g.p.epilogue = tp ? EPI_ALLREDUCE : (post ? EPI_STORE : EPI_RESID);
             g.p.peers.world = 1;
+            if (tp) { fill_peers(e, g.p, 1); g.p.out_seq_add = (uint32_t)(l + 1); }
             if (plan_gemv(g, 1, L.down.cols, n_ctas)) return -1;
             e->gemvs.push_back(g);
             if (post) pending_w = L.post_ffn_norm;
@@ -595,6 +599,7 @@ static int engine_plan_plain(Engine* e) {
         g.p.result = e->result; g.p.ctrl = e->ctrl; g.p.token_log = e->token_log; g.p.token_script = e->script; g.p.row_offset = m.vocab_offset;
         g.p.peers.world = 1;
         g.p.gen = (const uint32_t*)(e->ctrl + CTRL_GEN);
+        if (tp) { fill_peers(e, g.p, 2); g.p.out_seq_add = 1; }
         if (plan_gemv(g, 1, m.hidden, std::min(n_ctas, 4096))) return -1;
         e->gemvs.push_back(g);
     }
@@ -716,9 +721,11 @@ static int engine_plan_dataflow(Engine* e) {
 }
 
 static int engine_plan(Engine* e) {
-    // PTB_DECODE_FLOW: "plain" (launch-boundary waits, one GPU only) or "dataflow"; default: plain on one GPU
+    // PTB_DECODE_FLOW: "plain" (launch-boundary waits; producer-side all-reduce under tensor parallelism) or "dataflow"
+    // (slot hand-over, consumer-side all-reduce).  Measured on B200: plain is ahead up to 4 GPUs, dataflow at 8, where
+    // the per-kernel hand-over latency is all that is left of a step.
     const char* f = getenv("PTB_DECODE_FLOW");
-    e->dataflow = e->m.tp_world > 1 || (f && !strcmp(f, "dataflow"));
+    e->dataflow = f ? !strcmp(f, "dataflow") : e->m.tp_world >= 8;
     if (e->dataflow ? engine_plan_dataflow(e) : engine_plan_plain(e)) return -1;
     const size_t pf_cap = (size_t)env_int("PTB_PREFETCH_MB", 0) << 20;
     if (pf_cap)

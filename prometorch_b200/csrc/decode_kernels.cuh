@@ -32,7 +32,7 @@ constexpr int GEMV_SEG_BLOCKS = 10;             // K is cut into segments of at 
 constexpr int MAX_PEERS = 8;
 
 enum QType : int { QT_Q4K = 0, QT_Q6K = 1 };
-enum Epilogue : int { EPI_STORE = 0, EPI_RESID = 1, EPI_GATED = 2, EPI_ARGMAX = 3, EPI_PARTIAL = 4 };
+enum Epilogue : int { EPI_STORE = 0, EPI_RESID = 1, EPI_GATED = 2, EPI_ARGMAX = 3, EPI_PARTIAL = 4, EPI_ALLREDUCE = 5 };
 constexpr uint32_t LL_SEQ_MUL = 256;            // sequence number = token generation * LL_SEQ_MUL + index of the write within the token
 
 // Weight layout in device memory (produced once at load time), "segment-major":
@@ -860,6 +860,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32, GEMV_WARPS >= 16 ? 1 : 2) gem
                 if (P.logits) P.logits[n] = v0;
                 if (v0 > best_v || (v0 == best_v && n < best_i)) { best_v = v0; best_i = n; }
                 return;
+            case EPI_ALLREDUCE:
             case EPI_PARTIAL: {
                 // {partial sum, sequence number} for element n into slot [rank][n] of every rank's inbox; whoever
                 // consumes the vector adds the slots up in rank order
@@ -931,6 +932,21 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32, GEMV_WARPS >= 16 ? 1 : 2) gem
 
     stamp(5);
     if (P.epilogue == EPI_ARGMAX) gemv_argmax_tail<GEMV_WARPS>(P, best_v, best_i, misc, gen, seq);
+    if (P.epilogue == EPI_ALLREDUCE) {
+        // Producer-side all-reduce (plain flow under tensor parallelism): every CTA reduces its own slice of the output.
+        // It polls the `world` slots of each element (filled by CTAs of this kernel on every rank), sums them in rank
+        // order so that all ranks get bitwise the same vector, adds the residual and stores the plain result.
+        const PeerInfo& pi = P.peers;
+        const int N = J.N;
+        const int n0 = (int)(((long long)N * blockIdx.x) / gridDim.x), n1 = (int)(((long long)N * (blockIdx.x + 1)) / gridDim.x);
+        for (int n = n0 + tid; n < n1; n += GEMV_THREADS) {
+            float v = P.resid ? P.resid[n] : 0.f;
+            for (int p = 0; p < pi.world; ++p)
+                v += __uint_as_float(wait_ll(pi.inbox[pi.rank] + (size_t)p * pi.slot_elems + n, seq, P.status, P.wait_ns));
+            J.out[n] = v;
+        }
+    }
+
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -21,6 +21,7 @@ constexpr int OPT_THREADS = 512;
 enum OptKind : int {
     OPT_SGD = 0, OPT_ADAM = 1, OPT_ADAMW = 2, OPT_RMSPROP = 3, OPT_LION = 4, OPT_SOPHIA = 5, OPT_NADAM = 6,
     OPT_RADAM = 7, OPT_ADAGRAD = 8, OPT_ADADELTA = 9, OPT_ADAMAX = 10, OPT_ASGD = 11,
+    OPT_LAMB = 12,          // three launches, see lamb_stage1_kernel
 };
 
 struct OptTensor {          // one row of the device-side table
@@ -255,9 +256,99 @@ __global__ void __launch_bounds__(OPT_THREADS) multi_tensor_scale_kernel(const O
     }
 }
 
+// ---- LAMB (torch/optim/lamb.h of the reference): the step size of a tensor is scaled by the trust ratio
+// ||w|| / ||update||, a per-tensor quantity, so the step is three launches over the same table:
+//   stage 1, per chunk: moments, the update direction u = m_hat / (sqrt(v_hat) + eps) + wd * w (kept in slot s2) and the
+//            chunk's sums of w^2 and u^2;
+//   stage 2, one warp per tensor: the partial sums of the tensor's chunks folded in a fixed order -> trust ratio;
+//   stage 3, per chunk: w -= lr * trust * u (and the optional bf16 copy).
+// h: lr, beta1, beta2, eps, weight_decay, bias_corr1, bias_corr2
+template <bool BF16>
+__global__ void __launch_bounds__(OPT_THREADS) lamb_stage1_kernel(const __grid_constant__ OptArgs A, float* __restrict__ partial) {
+    __shared__ float red[2][OPT_THREADS / 32];
+    if (A.skip && *A.skip) return;
+    const int2 ck = A.chunks[blockIdx.x];
+    const OptTensor T = A.tensors[ck.x];
+    const long long base = (long long)ck.y * OPT_CHUNK;
+    const long long end = min(base + OPT_CHUNK, T.numel);
+    const float gs = A.grad_scale ? *A.grad_scale : 1.f;
+    const float b1 = A.h[1], b2 = A.h[2], eps = A.h[3], wd = A.h[4], bc1 = A.h[5], bc2 = A.h[6];
+    float sw = 0.f, su = 0.f;
+    for (long long i = base + threadIdx.x; i < end; i += OPT_THREADS) {
+        const float p = T.p[i];
+        const float g = load_grad<BF16>(T.g, i) * gs;
+        const float m = b1 * T.s0[i] + (1.f - b1) * g;
+        const float v = b2 * T.s1[i] + (1.f - b2) * g * g;
+        T.s0[i] = m;
+        T.s1[i] = v;
+        const float u = (m / bc1) / (sqrtf(v / bc2) + eps) + wd * p;
+        T.s2[i] = u;
+        sw += p * p;
+        su += u * u;
+    }
+    sw = warp_sum(sw);
+    su = warp_sum(su);
+    if ((threadIdx.x & 31) == 0) { red[0][threadIdx.x >> 5] = sw; red[1][threadIdx.x >> 5] = su; }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float a = threadIdx.x < OPT_THREADS / 32 ? red[0][threadIdx.x] : 0.f, b = threadIdx.x < OPT_THREADS / 32 ? red[1][threadIdx.x] : 0.f;
+        a = warp_sum(a);
+        b = warp_sum(b);
+        if (threadIdx.x == 0) { partial[2 * blockIdx.x] = a; partial[2 * blockIdx.x + 1] = b; }
+    }
+}
+// chunk_start[t] .. chunk_start[t+1]: the chunks of tensor t.  One warp per tensor.
+__global__ void lamb_trust_kernel(const int* __restrict__ chunk_start, int n_tensors, const float* __restrict__ partial,
+                                  float* __restrict__ trust, const int* skip) {
+    if (skip && *skip) return;
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= n_tensors) return;
+    float a = 0.f, b = 0.f;
+    for (int c = chunk_start[t] + lane; c < chunk_start[t + 1]; c += 32) { a += partial[2 * c]; b += partial[2 * c + 1]; }
+    a = warp_sum(a);
+    b = warp_sum(b);
+    if (lane == 0) trust[t] = (a > 0.f && b > 0.f) ? sqrtf(a) / sqrtf(b) : 1.f;
+}
+__global__ void __launch_bounds__(OPT_THREADS) lamb_stage3_kernel(const __grid_constant__ OptArgs A, const float* __restrict__ trust) {
+    if (A.skip && *A.skip) return;
+    const int2 ck = A.chunks[blockIdx.x];
+    const OptTensor T = A.tensors[ck.x];
+    const long long base = (long long)ck.y * OPT_CHUNK;
+    const long long end = min(base + OPT_CHUNK, T.numel);
+    const float step = A.h[0] * trust[ck.x];
+    for (long long i = base + threadIdx.x; i < end; i += OPT_THREADS) {
+        const float p = T.p[i] - step * T.s2[i];
+        T.p[i] = p;
+        if (T.p_lowp) T.p_lowp[i] = __float2bfloat16_rn(p);
+    }
+}
+
 }  // namespace ptb
 
 using namespace ptb;
+
+// Fused LAMB step.  chunk_start: device int [n_tensors + 1] (prefix sums of the chunk counts, in table order);
+// partial: 2 * n_chunks floats of scratch; trust: n_tensors floats (the trust ratios of this step, readable afterwards).
+// Every row of the table needs all three state slots (moments and the update buffer).
+PTB_API int ptb_multi_tensor_lamb(const void* tensors, const void* chunks, int n_chunks, const int* chunk_start, int n_tensors,
+                                  int grad_bf16, const float* h, const float* grad_scale, const int* skip, float* partial,
+                                  float* trust, cudaStream_t stream) {
+    if (n_chunks <= 0) return 0;
+    OptArgs a;
+    a.tensors = (const OptTensor*)tensors;
+    a.chunks = (const int2*)chunks;
+    a.kind = OPT_LAMB;
+    a.grad_bf16 = grad_bf16;
+    for (int i = 0; i < 16; ++i) a.h[i] = h[i];
+    a.grad_scale = grad_scale;
+    a.skip = skip;
+    if (grad_bf16) lamb_stage1_kernel<true><<<n_chunks, OPT_THREADS, 0, stream>>>(a, partial);
+    else lamb_stage1_kernel<false><<<n_chunks, OPT_THREADS, 0, stream>>>(a, partial);
+    lamb_trust_kernel<<<(n_tensors + 7) / 8, 256, 0, stream>>>(chunk_start, n_tensors, partial, trust, skip);
+    lamb_stage3_kernel<<<n_chunks, OPT_THREADS, 0, stream>>>(a, trust);
+    PTB_CUDA_OK(cudaGetLastError());
+    return 0;
+}
 
 PTB_API int ptb_opt_chunk() { return OPT_CHUNK; }
 PTB_API int ptb_opt_tensor_bytes() { return (int)sizeof(OptTensor); }

@@ -24,7 +24,7 @@ __all__ = ["Optimizer", "SGD", "Adam", "AdamW", "RMSprop", "Lion", "SophiaG", "S
            "RAdam", "Adagrad", "Adadelta", "Adamax", "AdamKiller", "ASGD", "LBFGS", "EMA", "ParamGroup"]
 
 (OPT_SGD, OPT_ADAM, OPT_ADAMW, OPT_RMSPROP, OPT_LION, OPT_SOPHIA, OPT_NADAM, OPT_RADAM, OPT_ADAGRAD, OPT_ADADELTA,
- OPT_ADAMAX, OPT_ASGD) = range(12)
+ OPT_ADAMAX, OPT_ASGD, OPT_LAMB) = range(13)
 
 
 @N.register_decls
@@ -38,6 +38,8 @@ def _decls(L):
     L.ptb_multi_tensor_grad_norm.restype = ci
     L.ptb_multi_tensor_scale.argtypes = [vp, vp, ci, ci, vp, vp]
     L.ptb_multi_tensor_scale.restype = ci
+    L.ptb_multi_tensor_lamb.argtypes = [vp, vp, ci, vp, ci, ci, C.POINTER(cf), vp, vp, vp, vp, vp]
+    L.ptb_multi_tensor_lamb.restype = ci
 
 
 def ParamGroup(params, **overrides) -> dict:
@@ -77,6 +79,11 @@ class TensorTable:
         self.rows = rows.to(device)
         self.chunks = torch.tensor(ck, dtype=torch.int32).reshape(-1, 2).to(device)
         self.n_chunks = len(ck)
+        # first chunk of every tensor (+ the total): what a per-tensor reduction over chunk partials needs
+        starts = [0]
+        for p in ps:
+            starts.append(starts[-1] + (p.numel() + chunk - 1) // chunk)
+        self.chunk_start = torch.tensor(starts, dtype=torch.int32).to(device)
         self.key = key
 
 
@@ -494,10 +501,39 @@ class ASGD(Optimizer):
 
 
 class LAMB(Optimizer):
-    slots = ("exp_avg", "exp_avg_sq")
+    """Layer-wise adaptive moments (torch/optim/lamb.h).  On CUDA the step is three launches over the whole parameter
+    group (moments + update direction + partial norms, per-tensor trust ratios, apply); ``lamb_update`` is the buffer
+    that carries the update direction between them."""
 
-    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-6, weight_decay=0.01, bias_correction=True):
-        super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, bias_correction=bias_correction))
+    kind, slots = OPT_LAMB, ("exp_avg", "exp_avg_sq", "lamb_update")
+
+    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-6, weight_decay=0.01, bias_correction=True, fused=None):
+        super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, bias_correction=bias_correction),
+                         fused)
+
+    def _init_state(self, p, group):
+        st = {"exp_avg": torch.zeros_like(p), "exp_avg_sq": torch.zeros_like(p)}
+        if p.is_cuda and self.fused is not False:
+            st["lamb_update"] = torch.zeros_like(p)
+        return st
+
+    def _fused_step(self, key, ps, h, bf16):
+        lib = N.lib()
+        dev = ps[0].device
+        for p in ps:
+            if "lamb_update" not in self.state[p]:
+                self.state[p]["lamb_update"] = torch.zeros_like(p)
+        tab = self._tables.setdefault(key, TensorTable())
+        slots = [tuple(self.state[p][n] for n in self.slots) for p in ps]
+        tab.build(ps, [self._grad(p) for p in ps], slots, [self.lowp_params.get(id(p)) for p in ps], dev)
+        if getattr(tab, "lamb_partial", None) is None or tab.lamb_partial.numel() < 2 * tab.n_chunks:
+            tab.lamb_partial = torch.empty(2 * max(tab.n_chunks, 1), device=dev)
+            tab.lamb_trust = torch.ones(len(ps), device=dev)
+        harr = (C.c_float * 16)(*(list(h) + [0.0] * (16 - len(h))))
+        st = torch.cuda.current_stream(dev).cuda_stream
+        N.check(lib.ptb_multi_tensor_lamb(tab.rows.data_ptr(), tab.chunks.data_ptr(), tab.n_chunks, tab.chunk_start.data_ptr(),
+                                          len(ps), int(bf16), harr, N.ptr(self.grad_scale), N.ptr(self.skip_flag),
+                                          tab.lamb_partial.data_ptr(), tab.lamb_trust.data_ptr(), st), "multi_tensor_lamb")
 
     def _scalars(self, g, step):
         b1, b2 = g["betas"]
