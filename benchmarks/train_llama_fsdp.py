@@ -34,6 +34,7 @@ def run(impl="fused", steps=5, warmup=3, seqs_per_gpu=8, micro=2, seq_len=2048, 
     torch.manual_seed(0)
     model = Llama(cfg).to(dev).to(torch.bfloat16)
     nparams = model.num_parameters()
+    sharded = sum(m.weight.numel() for m in model.modules() if isinstance(m, torch.nn.Linear) and m.bias is None and m.weight.numel() >= (1 << 16))
     symm = None
     if impl == "fused":
         from prometorch_b200.parallel.fsdp_fused import FusedFSDP
@@ -96,7 +97,6 @@ def run(impl="fused", steps=5, warmup=3, seqs_per_gpu=8, micro=2, seq_len=2048, 
     # bytes this rank moves over NVLink per step: it gathers the (world-1)/world of every sharded bf16 weight it does
     # not own once per micro-batch pass that needs it (forward + backward re-use the staged copy within a step: once),
     # and reads (world-1) peers' slices of the bf16 gradient for its own shard
-    sharded = sum(p.numel() for n_, p in model.named_parameters() if p.dim() == 2)
     nv_bytes = 2.0 * sharded * (world - 1) / world * 2
     out = {"metric": "Llama-1.1B-shape FSDP train tokens/s", "value": round(tokens / (ms / 1e3), 1), "unit": "tok/s",
            "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": round(ms / steps, 2),
