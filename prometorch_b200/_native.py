@@ -53,7 +53,7 @@ def _declare(L: C.CDLL):
     L.ptb_last_error.restype = C.c_char_p
     L.ptb_gemv.argtypes = [vp, vp, ci, ci, ci, ci, ci, vp, vp, cf, vp, vp, vp, ci, ci, ci, vp, vp, vp]
     L.ptb_gemv.restype = ci
-    L.ptb_attn_decode.argtypes = [vp] * 14 + [ci, ci, ci, ci, cf, ci, vp]
+    L.ptb_attn_decode.argtypes = [vp] * 14 + [ci, ci, ci, ci, ci, cf, ci, vp]
     L.ptb_attn_decode.restype = ci
     L.ptb_engine_create.argtypes = [C.POINTER(ModelDesc), C.POINTER(LayerDesc), vp]
     L.ptb_engine_create.restype = vp
@@ -75,6 +75,12 @@ def _declare(L: C.CDLL):
     for name in ("ptb_engine_stream", "ptb_engine_logits", "ptb_engine_hidden", "ptb_engine_result"):
         getattr(L, name).argtypes = [vp]
         getattr(L, name).restype = vp
+    L.ptb_engine_enqueue_range.argtypes = [vp, ci, ci]
+    L.ptb_engine_enqueue_range.restype = ci
+    L.ptb_engine_buffer.argtypes = [vp, ci]
+    L.ptb_engine_buffer.restype = vp
+    L.ptb_engine_finish_token.argtypes = [vp, vp, ci]
+    L.ptb_engine_finish_token.restype = ci
     L.ptb_engine_launches_per_token.argtypes = [vp]
     L.ptb_engine_launches_per_token.restype = cl
     L.ptb_gemv_plan.argtypes = [ci, ci, ci, ci, ci, ci, ci, C.POINTER(ci)]

@@ -134,12 +134,12 @@ static int plan_gemv_seg(GemvLaunch& L, int njobs, int K, int n_ctas) {
 static int g_job_layout = 0;      // layout of the job set_job() filled last (a launch never mixes layouts)
 // Tiles-of-16-rows layout: CTAs own whole row tiles (split over the jobs in proportion to their bytes); the K
 // dimension of a tile is cut into KG groups so that a CTA has enough (tile, K-group) items for its warps.
-static int plan_gemv16(GemvLaunch& L, int njobs, int K, int n_ctas) {
+static int plan_gemv16(GemvLaunch& L, int njobs, int K, int n_ctas, int force_warps = 0) {
     GemvParams& p = L.p;
     p.njobs = njobs;
     p.K = K;
     // one CTA of 16 warps per SM: half as many CTAs repeat the input gather as with two CTAs of 8 warps
-    const int warps = env_int("PTB_GEMV_WARPS", 16) >= 16 ? 16 : 8;
+    const int warps = force_warps ? force_warps : env_int("PTB_GEMV_WARPS", 16) >= 16 ? 16 : 8;
     p.warps = warps;
     p.wait_ns = (unsigned long long)env_int("PTB_WAIT_MS", 2000) * 1000000ull;
     p.hard_wait = env_int("PTB_DATAFLOW", 1) == 0;
@@ -197,6 +197,8 @@ static int plan_gemv16(GemvLaunch& L, int njobs, int K, int n_ctas) {
     p.acc_floats = acc_floats;
     L.smem = gemv_smem_layout(K, warps, stages, tile_bytes, acc_floats).total;
     L.t16 = 1;
+    // wide tiles (paired Q8_0) do not fit sixteen rings of two slots: plan again with eight warps
+    if (L.smem > g_gemv_max_dyn && warps == 16) return plan_gemv16(L, njobs, K, n_ctas, 8);
     if (L.smem > g_gemv_max_dyn) {
         ptb_set_error("gemv: %zu B of shared memory needed (K=%d, tile %d B x %d stages x %d warps, %d accumulators)", L.smem, K,
                       tile_bytes, stages, warps, acc_floats);
@@ -216,13 +218,21 @@ static void set_job(GemvJob& j, const PtbWeightDesc& w, const PtbWeightDesc* w2,
     j.out = out;
     j.qtype = w.qtype;
     j.N = w.rows;
-    j.nblk = w.cols / 256;
+    j.nblk = w.cols / (w.layout == 1 ? t16_block_vals(w.qtype) : 256);
     j.KS = (j.nblk + GEMV_SEG_BLOCKS - 1) / GEMV_SEG_BLOCKS;
     j.seg_base = j.nblk / j.KS;
     j.seg_rem = j.nblk % j.KS;
 }
 
 static int plan_gemv(GemvLaunch& L, int njobs, int K, int n_ctas) {
+    for (int i = 0; i < njobs; ++i) {
+        const int q = L.p.job[i].qtype;
+        const bool ok = q == QT_Q4K || q == QT_Q6K || (g_job_layout == 1 && (q == QT_Q5K || q == QT_Q8_0 || q == QT_F16));
+        if (!ok) {
+            ptb_set_error("gemv: weight type %d is not available in layout %d (Q5_K, Q8_0 and fp16 need the 16-row tile layout)", q, g_job_layout);
+            return -1;
+        }
+    }
     return g_job_layout == 1 ? plan_gemv16(L, njobs, K, n_ctas) : plan_gemv_seg(L, njobs, K, n_ctas);
 }
 
@@ -285,11 +295,11 @@ static cudaError_t launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cud
     return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
-template <int G>
-static cudaError_t launch_attn_g(const AttnParams& a, int n_kv_heads, cudaStream_t st, bool pdl) {
+template <int G, int D>
+static cudaError_t launch_attn_gd(const AttnParams& a, int n_kv_heads, cudaStream_t st, bool pdl) {
     static bool attr_done = false;
     if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(AttnShared));
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<G, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(AttnShared<D>));
         if (e != cudaSuccess) return e;
         attr_done = true;
     }
@@ -297,7 +307,7 @@ static cudaError_t launch_attn_g(const AttnParams& a, int n_kv_heads, cudaStream
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3(n_kv_heads * ATT_CLUSTER);
     cfg.blockDim = dim3(ATT_THREADS);
-    cfg.dynamicSmemBytes = sizeof(AttnShared);
+    cfg.dynamicSmemBytes = sizeof(AttnShared<D>);
     cfg.stream = st;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -308,14 +318,24 @@ static cudaError_t launch_attn_g(const AttnParams& a, int n_kv_heads, cudaStream
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 2 : 1;
-    return cudaLaunchKernelEx(&cfg, attn_decode_kernel<G>, a);
+    return cudaLaunchKernelEx(&cfg, attn_decode_kernel<G, D>, a);
 }
-static cudaError_t launch_attn(const AttnParams& a, int n_kv_heads, cudaStream_t st, bool pdl) {
+template <int D>
+static cudaError_t launch_attn_d(const AttnParams& a, int n_kv_heads, cudaStream_t st, bool pdl) {
     switch (a.group) {
-        case 1: return launch_attn_g<1>(a, n_kv_heads, st, pdl);
-        case 2: return launch_attn_g<2>(a, n_kv_heads, st, pdl);
-        case 4: return launch_attn_g<4>(a, n_kv_heads, st, pdl);
-        case 8: return launch_attn_g<8>(a, n_kv_heads, st, pdl);
+        case 1: return launch_attn_gd<1, D>(a, n_kv_heads, st, pdl);
+        case 2: return launch_attn_gd<2, D>(a, n_kv_heads, st, pdl);
+        case 4: return launch_attn_gd<4, D>(a, n_kv_heads, st, pdl);
+        case 8: return launch_attn_gd<8, D>(a, n_kv_heads, st, pdl);
+        default: return cudaErrorInvalidValue;
+    }
+}
+static bool attn_head_dim_ok(int d) { return d == 64 || d == 128 || d == 256; }
+static cudaError_t launch_attn(const AttnParams& a, int n_kv_heads, cudaStream_t st, bool pdl) {
+    switch (a.head_dim) {
+        case 64: return launch_attn_d<64>(a, n_kv_heads, st, pdl);
+        case 128: return launch_attn_d<128>(a, n_kv_heads, st, pdl);
+        case 256: return launch_attn_d<256>(a, n_kv_heads, st, pdl);
         default: return cudaErrorInvalidValue;
     }
 }
@@ -367,8 +387,12 @@ PTB_API int ptb_gemv(const void* w, const void* w2, int qtype, int rows, int col
 
 PTB_API int ptb_attn_decode(const float* q, const float* k, const float* v, const float* q_norm, const float* k_norm,
                             const float* cos, const float* sin, void* k_cache, void* v_cache, float* out, float* part_o,
-                            float* part_ml, unsigned* ticket, const int* ctrl, int n_kv_heads, int group, int max_seq,
-                            int neox, float eps, int window, cudaStream_t stream) {
+                            float* part_ml, unsigned* ticket, const int* ctrl, int n_kv_heads, int group, int head_dim,
+                            int max_seq, int neox, float eps, int window, cudaStream_t stream) {
+    if (!attn_head_dim_ok(head_dim)) {
+        ptb_set_error("attn_decode: head size %d; supported: 64, 128, 256", head_dim);
+        return -1;
+    }
     if (!(group == 1 || group == 2 || group == 4 || group == 8)) {
         ptb_set_error("attn_decode: %d query heads per KV head; supported: 1, 2, 4, %d", group, ATT_MAX_GROUP);
         return -1;
@@ -379,7 +403,8 @@ PTB_API int ptb_attn_decode(const float* q, const float* k, const float* v, cons
     a.k_cache = (__half*)k_cache; a.v_cache = (__half*)v_cache; a.out = out; a.part_o = part_o; a.part_ml = part_ml;
     a.ticket = ticket; a.ctrl = ctrl; a.group = group; a.max_seq = max_seq;
     a.max_splits = (max_seq + ATT_CHUNK - 1) / ATT_CHUNK;
-    a.neox = neox; a.eps = eps; a.scale = 1.0f / sqrtf((float)ATT_D); a.window = window;
+    a.head_dim = head_dim;
+    a.neox = neox; a.eps = eps; a.scale = 1.0f / sqrtf((float)head_dim); a.window = window;
     PTB_CUDA_OK(launch_attn(a, n_kv_heads, stream, false));
     return 0;
 }
@@ -390,6 +415,7 @@ struct Engine {
     PtbModelDesc m;
     std::vector<PtbLayerDesc> layers;
     int dev = 0, n_sm = 148;
+    bool external = false;      // tensor-parallel sums are done by the caller between launch ranges (the NCCL arm)
     cudaStream_t stream = nullptr;
     bool own_stream = true;
     // device buffers
@@ -440,7 +466,7 @@ static int engine_alloc(Engine* e) {
     PTB_CUDA_OK(cudaMalloc(&e->vc, kvbytes));
     PTB_CUDA_OK(cudaMemset(e->kc, 0, kvbytes));
     PTB_CUDA_OK(cudaMemset(e->vc, 0, kvbytes));
-    PTB_CUDA_OK(cudaMalloc(&e->part_o, sizeof(float) * (size_t)m.n_kv_heads * splits * group * ATT_D));
+    PTB_CUDA_OK(cudaMalloc(&e->part_o, sizeof(float) * (size_t)m.n_kv_heads * splits * group * m.head_dim));
     PTB_CUDA_OK(cudaMalloc(&e->part_ml, sizeof(float) * (size_t)m.n_kv_heads * splits * group * 2));
     PTB_CUDA_OK(cudaMalloc(&e->tickets, sizeof(unsigned) * (8 + m.n_kv_heads)));
     PTB_CUDA_OK(cudaMemset(e->tickets, 0, sizeof(unsigned) * (8 + m.n_kv_heads)));
@@ -517,8 +543,16 @@ static int engine_plan_plain(Engine* e) {
     const PtbModelDesc& m = e->m;
     const int qd = m.n_heads * m.head_dim, kvd = m.n_kv_heads * m.head_dim;
     const int n_ctas = e->n_sm * env_int("PTB_GEMV_CTAS_PER_SM", e->layers[0].q.layout == 1 ? 1 : 2);
-    const bool tp = m.tp_world > 1;
+    const bool ext = e->external;                // partial sums are all-reduced by the caller, in place, in the residual buffer
+    const bool tp = m.tp_world > 1 && !ext;
+    // external sums: rank 0 adds the residual to its partial sums, the others store theirs, and the caller's all-reduce
+    // over the residual buffer then leaves x + sum of partials on every rank
+    const int ext_epi = m.tp_rank == 0 ? EPI_RESID : EPI_STORE;
     e->gemvs.clear();
+    if (ext && (e->layers[0].post_attn_norm || e->layers[0].post_ffn_norm)) {
+        ptb_set_error("external all-reduce flow: post-norm architectures are not supported");
+        return -1;
+    }
     // post-norm architectures: a projection stores its raw output in `tmp`; the next kernel's prologue adds
     // RMSNorm(tmp) to the residual stream, reading X[cur] and (CTA 0) writing X[cur ^ 1]
     float* X[2] = {e->x, e->x2};
@@ -554,7 +588,7 @@ static int engine_plan_plain(Engine* e) {
             const bool post = L.post_attn_norm != nullptr;
             set_job(g.p.job[0], L.o, nullptr, post ? e->tmp : X[cur]);
             g.p.x = e->att; g.p.resid = post ? nullptr : X[cur]; g.p.status = e->status; g.p.ticket = e->tickets;
-            g.p.epilogue = tp ? EPI_ALLREDUCE : (post ? EPI_STORE : EPI_RESID);
+            g.p.epilogue = tp ? EPI_ALLREDUCE : ext ? ext_epi : (post ? EPI_STORE : EPI_RESID);
             g.p.peers.world = 1;
             if (tp) { fill_peers(e, g.p, 0); g.p.out_seq_add = (uint32_t)(l + 1); }
             if (plan_gemv(g, 1, L.o.cols, n_ctas)) return -1;
@@ -577,7 +611,7 @@ static int engine_plan_plain(Engine* e) {
             const bool post = L.post_ffn_norm != nullptr;
             set_job(g.p.job[0], L.down, nullptr, post ? e->tmp : X[cur]);
             g.p.x = e->ffn; g.p.resid = post ? nullptr : X[cur]; g.p.status = e->status; g.p.ticket = e->tickets;
-            g.p.epilogue = tp ? EPI_ALLREDUCE : (post ? EPI_STORE : EPI_RESID);
+            g.p.epilogue = tp ? EPI_ALLREDUCE : ext ? ext_epi : (post ? EPI_STORE : EPI_RESID);
             g.p.peers.world = 1;
             if (tp) { fill_peers(e, g.p, 1); g.p.out_seq_add = (uint32_t)(l + 1); }
             if (plan_gemv(g, 1, L.down.cols, n_ctas)) return -1;
@@ -599,6 +633,7 @@ static int engine_plan_plain(Engine* e) {
         g.p.result = e->result; g.p.ctrl = e->ctrl; g.p.token_log = e->token_log; g.p.token_script = e->script; g.p.row_offset = m.vocab_offset;
         g.p.peers.world = 1;
         g.p.gen = (const uint32_t*)(e->ctrl + CTRL_GEN);
+        if (ext) { g.p.ctrl = nullptr; g.p.token_log = nullptr; }      // this rank's {id, value} only; ptb_engine_finish_token ends the token
         if (tp) { fill_peers(e, g.p, 2); g.p.out_seq_add = 1; }
         if (plan_gemv(g, 1, m.hidden, std::min(n_ctas, 4096))) return -1;
         e->gemvs.push_back(g);
@@ -724,7 +759,10 @@ static int engine_plan(Engine* e) {
     // PTB_DECODE_FLOW: "plain" (launch-boundary waits; producer-side all-reduce under tensor parallelism) or "dataflow"
     // (slot hand-over, consumer-side all-reduce).  Measured on B200: plain is ahead up to 4 GPUs, dataflow at 8, where
     // the per-kernel hand-over latency is all that is left of a step.
+    // "external" (tensor parallel only): the plain flow without any in-kernel exchange; the caller enqueues launch ranges
+    // and all-reduces the residual buffer between them (ptb_engine_enqueue_range), which is how the NCCL baseline runs.
     const char* f = getenv("PTB_DECODE_FLOW");
+    e->external = f && !strcmp(f, "external") && e->m.tp_world > 1;
     e->dataflow = f ? !strcmp(f, "dataflow") : e->m.tp_world >= 8;
     if (e->dataflow ? engine_plan_dataflow(e) : engine_plan_plain(e)) return -1;
     const size_t pf_cap = (size_t)env_int("PTB_PREFETCH_MB", 0) << 20;
@@ -734,8 +772,11 @@ static int engine_plan(Engine* e) {
 }
 
 
-// Enqueue one token's kernels on the engine stream.
-static int engine_enqueue(Engine* e) {
+// Enqueue launches [first, last) of one token's kernels on the engine stream.  Launch 0 is the embedding, launches
+// 1 + 5 l .. 5 + 5 l are layer l's {qkv, attention, o, gate/up, down}, the last one is the lm_head.
+static int engine_enqueue_range(Engine* e, long first, long last);
+static int engine_enqueue(Engine* e) { return engine_enqueue_range(e, 0, 1L << 40); }
+static int engine_enqueue_range(Engine* e, long first, long last) {
     const PtbModelDesc& m = e->m;
     const int qd = m.n_heads * m.head_dim, kvd = m.n_kv_heads * m.head_dim;
     const int splits = (m.max_seq + ATT_CHUNK - 1) / ATT_CHUNK;
@@ -751,14 +792,15 @@ static int engine_enqueue(Engine* e) {
     ep.gen = (const uint32_t*)(e->ctrl + CTRL_GEN);
     // the first kernel of a token is launched without the programmatic edge: it must not
     // overlap the previous token's lm_head, whose epilogue updates the control block
-    PTB_CUDA_OK(launch_pdl(embed_kernel, dim3((m.hidden + 255) / 256), dim3(256), 0, e->stream, false, ep));
+    auto want = [&](long idx) { return idx >= first && idx < last; };
+    if (want(0)) PTB_CUDA_OK(launch_pdl(embed_kernel, dim3((m.hidden + 255) / 256), dim3(256), 0, e->stream, false, ep));
     ++n;
     size_t gi = 0;
     for (int l = 0; l < m.n_layers; ++l) {
         const PtbLayerDesc& L = e->layers[l];
         GemvLaunch& g0 = e->gemvs[gi++];
         if (e->trace) g0.p.trace = e->trace + 8 * (1 + 5 * l);
-        PTB_CUDA_OK(launch_gemv(g0, e->stream, pdl));
+        if (want(n)) PTB_CUDA_OK(launch_gemv(g0, e->stream, pdl));
         AttnParams a;
         memset(&a, 0, sizeof(a));
         if (e->dataflow) {
@@ -775,27 +817,28 @@ static int engine_enqueue(Engine* e) {
         a.v_cache = e->vc + (size_t)l * m.n_kv_heads * m.max_seq * m.head_dim;
         a.out = e->att; a.part_o = e->part_o; a.part_ml = e->part_ml; a.ticket = e->tickets + 8; a.ctrl = e->ctrl;
         a.group = m.n_heads / m.n_kv_heads; a.max_seq = m.max_seq; a.max_splits = splits; a.neox = m.neox;
+        a.head_dim = m.head_dim;
         a.eps = m.eps; a.scale = 1.0f / sqrtf((float)m.head_dim); a.window = L.window;
         if (e->trace) a.trace = e->trace + 8 * (2 + 5 * l);
-        PTB_CUDA_OK(launch_attn(a, m.n_kv_heads, e->stream, pdl));
+        if (want(n + 1)) PTB_CUDA_OK(launch_attn(a, m.n_kv_heads, e->stream, pdl));
         for (int k = 0; k < 3; ++k) {
             GemvLaunch& g = e->gemvs[gi++];
             if (e->trace) g.p.trace = e->trace + 8 * (3 + k + 5 * l);
-            PTB_CUDA_OK(launch_gemv(g, e->stream, pdl));
+            if (want(n + 2 + k)) PTB_CUDA_OK(launch_gemv(g, e->stream, pdl));
         }
         n += 5;
     }
     GemvLaunch& gl = e->gemvs[gi++];
     if (e->trace) gl.p.trace = e->trace + 8 * (1 + 5 * m.n_layers);
-    PTB_CUDA_OK(launch_gemv(gl, e->stream, pdl));
+    if (want(n)) PTB_CUDA_OK(launch_gemv(gl, e->stream, pdl));
     ++n;
     e->launches_per_token = n;
     return 0;
 }
 
 PTB_API void* ptb_engine_create(const PtbModelDesc* m, const PtbLayerDesc* layers, void* ext_stream) {
-    if (m->head_dim != ATT_D) {
-        ptb_set_error("decode engine: head_dim %d not supported (kernels are built for %d)", m->head_dim, ATT_D);
+    if (!attn_head_dim_ok(m->head_dim)) {
+        ptb_set_error("decode engine: head size %d not supported (the attention kernel is built for 64, 128 and 256)", m->head_dim);
         return nullptr;
     }
     const int grp_ = m->n_kv_heads ? m->n_heads / m->n_kv_heads : 0;
@@ -842,6 +885,10 @@ PTB_API void ptb_engine_destroy(void* h) {
 PTB_API int ptb_engine_capture(void* h) {
     Engine* e = (Engine*)h;
     if (e->exec) return 0;
+    if (e->external) {
+        ptb_set_error("external all-reduce flow: the caller captures ptb_engine_enqueue_range calls and its own collectives");
+        return -1;
+    }
     PTB_CUDA_OK(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
     if (engine_enqueue(e)) {
         cudaGraph_t g = nullptr;
@@ -851,6 +898,41 @@ PTB_API int ptb_engine_capture(void* h) {
     }
     PTB_CUDA_OK(cudaStreamEndCapture(e->stream, &e->graph));
     PTB_CUDA_OK(cudaGraphInstantiate(&e->exec, e->graph, 0));
+    return 0;
+}
+
+// External all-reduce flow (PTB_DECODE_FLOW=external under tensor parallelism).  A token is
+//   enqueue_range(0, 4) | all-reduce x | (2) | all-reduce x | (3) | ... | lm_head | all-gather result | finish_token
+// where the residual vector x is ptb_engine_buffer(h, 0) (hidden floats) and this rank's {id, value bits} pair is
+// ptb_engine_buffer(h, 1).  Everything is enqueued on the engine stream, so the caller can capture it in a graph.
+PTB_API int ptb_engine_enqueue_range(void* h, int first, int count) {
+    Engine* e = (Engine*)h;
+    if (e->exec) { ptb_set_error("enqueue_range: the engine already owns a captured graph"); return -1; }
+    return engine_enqueue_range(e, first, (long)first + count);
+}
+PTB_API void* ptb_engine_buffer(void* h, int which) {
+    Engine* e = (Engine*)h;
+    return which == 0 ? (void*)e->x : which == 1 ? (void*)e->result : nullptr;
+}
+static __global__ void finish_token_kernel(const int* __restrict__ pairs, int world, int* result, int* ctrl, int* token_log,
+                                           const int* script) {
+    if (threadIdx.x || blockIdx.x) return;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int p = 0; p < world; ++p) {
+        const int ix = pairs[2 * p];
+        const float v = __int_as_float(pairs[2 * p + 1]);
+        if (v > bv || (v == bv && ix < bi)) { bv = v; bi = ix; }
+    }
+    result[0] = bi;
+    result[1] = __float_as_int(bv);
+    advance_token(ctrl, token_log, script, bi, (uint32_t)ctrl[CTRL_GEN]);
+}
+// pairs: device array [world][2] of every rank's {id, value bits} (the all-gathered result buffers).
+PTB_API int ptb_engine_finish_token(void* h, const void* pairs, int world) {
+    Engine* e = (Engine*)h;
+    finish_token_kernel<<<1, 32, 0, e->stream>>>((const int*)pairs, world, e->result, e->ctrl, e->token_log, e->script);
+    PTB_CUDA_OK(cudaGetLastError());
     return 0;
 }
 

@@ -20,6 +20,11 @@
 //   Q6_K: [tile][super-block]{ ql[16][128] | qh[16][64] | int8 scales[16][16] | fp16 d[16] }  -> 3360 bytes;
 //         the 16-byte chunks of a ql row are stored at chunk ^ (row & 7), those of a qh row at chunk ^ ((row >> 1) & 3),
 //         which spreads the eight rows a load instruction touches over all banks.
+//   Q5_K: as Q4_K with the file's 176-byte blocks                                      -> 2816 bytes per (tile, block)
+//   Q8_0: [tile][256 values]{ q[16][256] int8, the 32-byte unit u of a row stored at u ^ (row & 7) | fp16 d[16][8] }
+//         -> 4352 bytes (eight 32-value GGUF blocks per row)
+//   F16:  [tile][64 values][16][64] halves, the 32-byte unit u of a row stored at u ^ (row & 3)   -> 2048 bytes;
+//         here a "block" is 64 values, so such a job counts K / 64 blocks
 // One (tile, block) unit is one untiled TMA bulk copy; a warp streams the blocks of its items through a private ring.
 //
 // Reference counterparts: q4km_persistent_gemv_kernel / q6k_gemv_kernel (aten/src/ATen/cuda/CUDAQuantGemv.cu:168-313,
@@ -27,10 +32,22 @@
 #pragma once
 #include "decode_kernels.cuh"
 
+#include <type_traits>
+
 namespace ptb {
 
 constexpr int T16_ROWS = 16;
-__host__ __device__ __forceinline__ int t16_block_bytes(int qtype) { return qtype == QT_Q4K ? 16 * 144 : 16 * 210; }
+__host__ __device__ __forceinline__ int t16_block_bytes(int qtype) {
+    switch (qtype) {
+        case QT_Q4K: return 16 * 144;
+        case QT_Q5K: return 16 * 176;
+        case QT_Q8_0: return 16 * 272;
+        case QT_F16: return 16 * 128;
+        default: return 16 * 210;
+    }
+}
+// values of one row that a block holds
+__host__ __device__ __forceinline__ int t16_block_vals(int qtype) { return qtype == QT_F16 ? 64 : 256; }
 
 // D += A (16x32, u8, row-major fragments) * B (32x8, s8, column fragments), s32 accumulate.
 __device__ __forceinline__ void mma_u8s8_k32(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -39,33 +56,75 @@ __device__ __forceinline__ void mma_u8s8_k32(int (&c)[4], uint32_t a0, uint32_t 
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ void mma_s8s8_k32(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// D += A (16x16 f16) * B (16x8 f16), f32 accumulate.
+__device__ __forceinline__ void mma_f16_k16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
 // Row of the tile that MMA row g (0..7) stands for in the Q4_K path (and g + 8 -> that row + 8).  With a row pitch of
 // 144 bytes, taking rows 0,2,4,6 for lanes 0-15 and 1,3,5,7 for lanes 16-31 keeps each half-warp's 8-byte loads on
 // distinct banks.
 __device__ __forceinline__ int q4k_row_of(int g) { return 2 * (g & 3) + (g >> 2); }
 
-// One Q4_K super-block of 16 rows.  `blk`: 16 x 144 bytes.  xq_b: the block's 256 int8 activations, xs_b[8] their
-// scales, xsf32_b[8] = scale * (sum of the 32 int8 values).  Lane (g, t) adds to acc0 / acc8 its share (sub-blocks 2t,
-// 2t+1) of the dot products of rows q4k_row_of(g) and q4k_row_of(g) + 8.
-__device__ __forceinline__ void q4k_block_mma(const uint8_t* blk, const int8_t* xq_b, const float* xs_b, const float* xsf32_b, int g,
-                                              int t, float& acc0, float& acc8) {
-    const uint8_t* r0 = blk + q4k_row_of(g) * 144;
-    const uint8_t* r8 = r0 + 8 * 144;
+// Bit BIT of every byte of h moved to bit 4 of that byte.
+template <int BIT>
+__device__ __forceinline__ uint32_t bit_to_4(uint32_t h) {
+    return (BIT <= 4 ? (h << (4 - (BIT <= 4 ? BIT : 4))) : (h >> ((BIT > 4 ? BIT : 4) - 4))) & 0x10101010u;
+}
+
+// One Q4_K (Q5 = false, 144-byte blocks) or Q5_K (Q5 = true, 176-byte blocks: 32 bytes of fifth bits between the
+// scales and the nibbles) super-block of 16 rows.  xq_b: the block's 256 int8 activations, xs_b[8] their scales,
+// xsf32_b[8] = scale * (sum of the 32 int8 values).  Lane (g, t) adds to acc0 / acc8 its share (sub-blocks 2t, 2t+1)
+// of the dot products of rows q4k_row_of(g) and q4k_row_of(g) + 8.
+template <bool Q5>
+__device__ __forceinline__ void q45k_block_mma(const uint8_t* blk, const int8_t* xq_b, const float* xs_b, const float* xsf32_b, int g,
+                                               int t, float& acc0, float& acc8) {
+    constexpr int PITCH = Q5 ? 176 : 144, QS = Q5 ? 48 : 16;
+    const uint8_t* r0 = blk + q4k_row_of(g) * PITCH;
+    const uint8_t* r8 = r0 + 8 * PITCH;
     // my column's activations: sub-block g, bytes 8t .. 8t+7 (k slots 4t.. and 16+4t.. of the MMA)
     const uint2 xb = *reinterpret_cast<const uint2*>(xq_b + g * 32 + 8 * t);
-    int c[4] = {0, 0, 0, 0};
-#pragma unroll
-    for (int ch = 0; ch < 4; ++ch) {
-        const uint2 wa = *reinterpret_cast<const uint2*>(r0 + 16 + ch * 32 + 8 * t);
-        const uint2 wb = *reinterpret_cast<const uint2*>(r8 + 16 + ch * 32 + 8 * t);
-        const bool lo = g == 2 * ch, hi = g == 2 * ch + 1;
-        // low nibbles: sub-block 2ch -> column 2ch; high nibbles (kept in place, i.e. 16 x value): sub-block 2ch+1
-        mma_u8s8_k32(c, wa.x & 0x0F0F0F0Fu, wb.x & 0x0F0F0F0Fu, wa.y & 0x0F0F0F0Fu, wb.y & 0x0F0F0F0Fu, lo ? xb.x : 0u, lo ? xb.y : 0u);
-        mma_u8s8_k32(c, wa.x & 0xF0F0F0F0u, wb.x & 0xF0F0F0F0u, wa.y & 0xF0F0F0F0u, wb.y & 0xF0F0F0F0u, hi ? xb.x : 0u, hi ? xb.y : 0u);
+    uint2 ha = make_uint2(0, 0), hb = make_uint2(0, 0);
+    if (Q5) {
+        // byte l of the 32 holds the fifth bit of value l of sub-block s in bit s
+        ha = *reinterpret_cast<const uint2*>(r0 + 16 + 8 * t);
+        hb = *reinterpret_cast<const uint2*>(r8 + 16 + 8 * t);
     }
-    // c[0], c[2]: sub-block 2t of rows g, g+8;  c[1], c[3]: 16 x sub-block 2t+1 (exact multiples of 16)
-    c[1] >>= 4;
-    c[3] >>= 4;
+    int c[4] = {0, 0, 0, 0};
+    constexpr uint32_t LO = 0x0F0F0F0Fu;
+    auto chunk = [&](auto chc) {
+        constexpr int ch = decltype(chc)::value;
+        const uint2 wa = *reinterpret_cast<const uint2*>(r0 + QS + ch * 32 + 8 * t);
+        const uint2 wb = *reinterpret_cast<const uint2*>(r8 + QS + ch * 32 + 8 * t);
+        const bool lo = g == 2 * ch, hi = g == 2 * ch + 1;
+        if (!Q5) {
+            // low nibbles: sub-block 2ch -> column 2ch; high nibbles (kept in place, i.e. 16 x value): sub-block 2ch+1
+            mma_u8s8_k32(c, wa.x & LO, wb.x & LO, wa.y & LO, wb.y & LO, lo ? xb.x : 0u, lo ? xb.y : 0u);
+            mma_u8s8_k32(c, wa.x & ~LO, wb.x & ~LO, wa.y & ~LO, wb.y & ~LO, hi ? xb.x : 0u, hi ? xb.y : 0u);
+        } else {
+            mma_u8s8_k32(c, (wa.x & LO) | bit_to_4<2 * ch>(ha.x), (wb.x & LO) | bit_to_4<2 * ch>(hb.x),
+                         (wa.y & LO) | bit_to_4<2 * ch>(ha.y), (wb.y & LO) | bit_to_4<2 * ch>(hb.y), lo ? xb.x : 0u, lo ? xb.y : 0u);
+            mma_u8s8_k32(c, ((wa.x >> 4) & LO) | bit_to_4<2 * ch + 1>(ha.x), ((wb.x >> 4) & LO) | bit_to_4<2 * ch + 1>(hb.x),
+                         ((wa.y >> 4) & LO) | bit_to_4<2 * ch + 1>(ha.y), ((wb.y >> 4) & LO) | bit_to_4<2 * ch + 1>(hb.y),
+                         hi ? xb.x : 0u, hi ? xb.y : 0u);
+        }
+    };
+    chunk(std::integral_constant<int, 0>{});
+    chunk(std::integral_constant<int, 1>{});
+    chunk(std::integral_constant<int, 2>{});
+    chunk(std::integral_constant<int, 3>{});
+    // c[0], c[2]: sub-block 2t of rows g, g+8;  c[1], c[3]: sub-block 2t+1 (Q4_K: 16 x it, exact multiples of 16)
+    if (!Q5) {
+        c[1] >>= 4;
+        c[3] >>= 4;
+    }
     const float2 xs2 = *reinterpret_cast<const float2*>(xs_b + 2 * t);
     const float2 sm2 = *reinterpret_cast<const float2*>(xsf32_b + 2 * t);
     const int sh = 16 * (t & 1);
@@ -83,6 +142,60 @@ __device__ __forceinline__ void q4k_block_mma(const uint8_t* blk, const int8_t* 
     };
     acc0 += row_value(r0, c[0], c[1]);
     acc8 += row_value(r8, c[2], c[3]);
+}
+
+// 256 values of 16 Q8_0 rows (eight 32-value blocks per row).  Sub-block s goes to output column s, so lane (g, t)
+// ends up with sub-blocks 2t and 2t+1 of rows g and g + 8 and applies d[row][sub-block] * activation scale.
+__device__ __forceinline__ void q80_block_mma(const uint8_t* blk, const int8_t* xq_b, const float* xs_b, int g, int t, float& acc0,
+                                              float& acc8) {
+    const uint8_t* r0 = blk + g * 256;
+    const uint8_t* r8 = r0 + 8 * 256;
+    const uint2 xb = *reinterpret_cast<const uint2*>(xq_b + g * 32 + 8 * t);
+    int c[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+        const int u = ((s ^ (g & 7)) << 5) + 8 * t;
+        const uint2 wa = *reinterpret_cast<const uint2*>(r0 + u);
+        const uint2 wb = *reinterpret_cast<const uint2*>(r8 + u);
+        const bool mine = g == s;
+        mma_s8s8_k32(c, wa.x, wb.x, wa.y, wb.y, mine ? xb.x : 0u, mine ? xb.y : 0u);
+    }
+    const float2 d0 = __half22float2(*reinterpret_cast<const __half2*>(blk + 4096 + g * 16 + 4 * t));
+    const float2 d8 = __half22float2(*reinterpret_cast<const __half2*>(blk + 4096 + (g + 8) * 16 + 4 * t));
+    const float2 xs2 = *reinterpret_cast<const float2*>(xs_b + 2 * t);
+    acc0 += d0.x * xs2.x * (float)c[0] + d0.y * xs2.y * (float)c[1];
+    acc8 += d8.x * xs2.x * (float)c[2] + d8.y * xs2.y * (float)c[3];
+}
+
+// 64 values of 16 fp16 rows.  The B operand carries the int8 activations as halves (exact) in column 0 only; the
+// activation scale of each 32-value group is applied to the fp32 result, so nothing can overflow fp16.  Lanes with
+// t == 0 receive rows g and g + 8, the other lanes add zeros.
+__device__ __forceinline__ void f16_block_mma(const uint8_t* blk, const int8_t* xq_b, const float* xs_b, int g, int t, float& acc0,
+                                              float& acc8) {
+    const uint8_t* r0 = blk + g * 128;
+    const uint8_t* r8 = r0 + 8 * 128;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int mm = 0; mm < 2; ++mm) {
+            const int m = 2 * h + mm;                     // 16 values = one 32-byte unit of each row
+            const int u = ((m ^ (g & 3)) << 5) + 8 * t;
+            const uint2 wa = *reinterpret_cast<const uint2*>(r0 + u);       // values 16m + 4t .. 16m + 4t + 3
+            const uint2 wb = *reinterpret_cast<const uint2*>(r8 + u);
+            uint32_t b0 = 0u, b1 = 0u;
+            if (g == 0) {
+                const char4 x4 = *reinterpret_cast<const char4*>(xq_b + 16 * m + 4 * t);
+                const __half2 p0 = __halves2half2(__int2half_rn(x4.x), __int2half_rn(x4.y));
+                const __half2 p1 = __halves2half2(__int2half_rn(x4.z), __int2half_rn(x4.w));
+                b0 = *reinterpret_cast<const uint32_t*>(&p0);
+                b1 = *reinterpret_cast<const uint32_t*>(&p1);
+            }
+            mma_f16_k16(c, wa.x, wb.x, wa.y, wb.y, b0, b1);
+        }
+        acc0 += xs_b[h] * c[0];
+        acc8 += xs_b[h] * c[2];
+    }
 }
 
 // One Q6_K super-block of 16 rows (layout in the header comment).  xsf16_b[16] = scale * (sum of 16 int8 values).
@@ -236,51 +349,63 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32, GEMV_WARPS >= 16 ? 1 : 2) gem
     };
 
     const int g = lane >> 2, t = lane & 3;
-    const int row_a = qtype == QT_Q4K ? q4k_row_of(g) : g;       // the tile row MMA row g stands for
+    const int row_a = (qtype == QT_Q4K || qtype == QT_Q5K) ? q4k_row_of(g) : g;       // the tile row MMA row g stands for
     const int npair = paired ? 2 : 1;
-    bool ok = true;
-    int k = 0;
-    for (int it = warp; it < nitems; it += GEMV_WARPS) {
-        int tile, kb0, nb, kg;
-        item_geom(it, tile, kb0, nb, kg);
-        float a0 = 0.f, a8 = 0.f, b0 = 0.f, b8 = 0.f;
-        for (int b = 0; b < nb; ++b, ++k) {
-            const int slot = k % S;
-            if (ok) ok = mbar_wait(&full[slot], (uint32_t)((k / S) & 1), P.status);
-            if (k == 0) stamp(3);
-            if (ok) {
-                const uint8_t* tp = ring + (size_t)slot * P.tile_bytes;
-                const int blk = kb0 + b;
-                if (qtype == QT_Q4K) {
-                    q4k_block_mma(tp, xq + blk * 256, xs + blk * 8, xsf32 + blk * 8, g, t, a0, a8);
-                    if (paired) q4k_block_mma(tp + bb, xq + blk * 256, xs + blk * 8, xsf32 + blk * 8, g, t, b0, b8);
+    // The item loop is instantiated once per weight type, so that the block loop of a launch holds one type's code only.
+    auto run_items = [&](auto qt_c) {
+        constexpr int QT = decltype(qt_c)::value;
+        auto block = [&](const uint8_t* tp, int blk, float& r0, float& r8) {
+            if constexpr (QT == QT_Q4K) q45k_block_mma<false>(tp, xq + blk * 256, xs + blk * 8, xsf32 + blk * 8, g, t, r0, r8);
+            else if constexpr (QT == QT_Q5K) q45k_block_mma<true>(tp, xq + blk * 256, xs + blk * 8, xsf32 + blk * 8, g, t, r0, r8);
+            else if constexpr (QT == QT_Q8_0) q80_block_mma(tp, xq + blk * 256, xs + blk * 8, g, t, r0, r8);
+            else if constexpr (QT == QT_F16) f16_block_mma(tp, xq + blk * 64, xs + blk * 2, g, t, r0, r8);
+            else q6k_block_mma(tp, xq + blk * 256, xs + blk * 8, xsf + blk * 16, g, t, r0, r8);
+        };
+        bool ok = true;
+        int k = 0;
+        for (int it = warp; it < nitems; it += GEMV_WARPS) {
+            int tile, kb0, nb, kg;
+            item_geom(it, tile, kb0, nb, kg);
+            float a0 = 0.f, a8 = 0.f, b0 = 0.f, b8 = 0.f;
+            for (int b = 0; b < nb; ++b, ++k) {
+                const int slot = k % S;
+                if (ok) ok = mbar_wait(&full[slot], (uint32_t)((k / S) & 1), P.status);
+                if (k == 0) stamp(3);
+                if (ok) {
+                    const uint8_t* tp = ring + (size_t)slot * P.tile_bytes;
+                    block(tp, kb0 + b, a0, a8);
+                    if (paired) block(tp + bb, kb0 + b, b0, b8);
+                }
+                __syncwarp();
+                if (lane == 0) issue_next(slot);
+            }
+            // the four lanes of a row hold its sub-block shares
+            a0 += __shfl_xor_sync(0xffffffffu, a0, 1); a0 += __shfl_xor_sync(0xffffffffu, a0, 2);
+            a8 += __shfl_xor_sync(0xffffffffu, a8, 1); a8 += __shfl_xor_sync(0xffffffffu, a8, 2);
+            if (paired) {
+                b0 += __shfl_xor_sync(0xffffffffu, b0, 1); b0 += __shfl_xor_sync(0xffffffffu, b0, 2);
+                b8 += __shfl_xor_sync(0xffffffffu, b8, 1); b8 += __shfl_xor_sync(0xffffffffu, b8, 2);
+            }
+            if (t == 0) {
+                if (KG == 1) {
+                    const int n0 = tile * T16_ROWS + row_a;
+                    if (n0 < J.N) epilogue(n0, a0, b0);
+                    if (n0 + 8 < J.N) epilogue(n0 + 8, a8, b8);
                 } else {
-                    q6k_block_mma(tp, xq + blk * 256, xs + blk * 8, xsf + blk * 16, g, t, a0, a8);
-                    if (paired) q6k_block_mma(tp + bb, xq + blk * 256, xs + blk * 8, xsf + blk * 16, g, t, b0, b8);
+                    float* ap = acc + ((size_t)((tile - t0) * KG + kg) * npair) * T16_ROWS;
+                    ap[row_a] = a0;
+                    ap[row_a + 8] = a8;
+                    if (paired) { ap[T16_ROWS + row_a] = b0; ap[T16_ROWS + row_a + 8] = b8; }
                 }
             }
-            __syncwarp();
-            if (lane == 0) issue_next(slot);
         }
-        // the four lanes of a row hold its sub-block shares
-        a0 += __shfl_xor_sync(0xffffffffu, a0, 1); a0 += __shfl_xor_sync(0xffffffffu, a0, 2);
-        a8 += __shfl_xor_sync(0xffffffffu, a8, 1); a8 += __shfl_xor_sync(0xffffffffu, a8, 2);
-        if (paired) {
-            b0 += __shfl_xor_sync(0xffffffffu, b0, 1); b0 += __shfl_xor_sync(0xffffffffu, b0, 2);
-            b8 += __shfl_xor_sync(0xffffffffu, b8, 1); b8 += __shfl_xor_sync(0xffffffffu, b8, 2);
-        }
-        if (t == 0) {
-            if (KG == 1) {
-                const int n0 = tile * T16_ROWS + row_a;
-                if (n0 < J.N) epilogue(n0, a0, b0);
-                if (n0 + 8 < J.N) epilogue(n0 + 8, a8, b8);
-            } else {
-                float* ap = acc + ((size_t)((tile - t0) * KG + kg) * npair) * T16_ROWS;
-                ap[row_a] = a0;
-                ap[row_a + 8] = a8;
-                if (paired) { ap[T16_ROWS + row_a] = b0; ap[T16_ROWS + row_a + 8] = b8; }
-            }
-        }
+    };
+    switch (qtype) {
+        case QT_Q4K: run_items(std::integral_constant<int, QT_Q4K>{}); break;
+        case QT_Q5K: run_items(std::integral_constant<int, QT_Q5K>{}); break;
+        case QT_Q8_0: run_items(std::integral_constant<int, QT_Q8_0>{}); break;
+        case QT_F16: run_items(std::integral_constant<int, QT_F16>{}); break;
+        default: run_items(std::integral_constant<int, QT_Q6K>{}); break;
     }
     stamp(4);
     if (KG > 1) {

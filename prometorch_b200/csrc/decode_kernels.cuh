@@ -31,7 +31,8 @@ constexpr int GEMV_MAX_JOBS = 3;
 constexpr int GEMV_SEG_BLOCKS = 10;             // K is cut into segments of at most this many 256-value super-blocks
 constexpr int MAX_PEERS = 8;
 
-enum QType : int { QT_Q4K = 0, QT_Q6K = 1 };
+// 2 / 3: fp16 / fp32 (row tables; fp16 also as a GEMV weight in the tile layout); Q5_K and Q8_0 exist in the tile layout only
+enum QType : int { QT_Q4K = 0, QT_Q6K = 1, QT_F16 = 2, QT_F32 = 3, QT_Q5K = 4, QT_Q8_0 = 5 };
 enum Epilogue : int { EPI_STORE = 0, EPI_RESID = 1, EPI_GATED = 2, EPI_ARGMAX = 3, EPI_PARTIAL = 4, EPI_ALLREDUCE = 5 };
 constexpr uint32_t LL_SEQ_MUL = 256;            // sequence number = token generation * LL_SEQ_MUL + index of the write within the token
 
@@ -649,6 +650,21 @@ __device__ __forceinline__ float gemv_input(const GemvParams& P, uint32_t gen, u
 // Arg-max over the whole output: CTA-level reduction, then the last CTA to arrive reduces across CTAs (and, under
 // tensor parallelism, exchanges {value, id} pairs with the other ranks), records the id and advances the decode
 // control block for the next token.
+// End of a token: log the chosen id, bump the step and generation counters and, in the self-feeding modes, make the
+// id (or the next scripted prompt token) the input of the next token.  One thread.
+__device__ __forceinline__ void advance_token(int* ctrl, int* token_log, const int* token_script, int id, uint32_t gen) {
+    const int step = ctrl[CTRL_STEP];
+    if (token_log && step < ctrl[CTRL_LOG_CAP]) token_log[step] = id;
+    ctrl[CTRL_STEP] = step + 1;
+    ctrl[CTRL_GEN] = (int)(gen + 1u);      // the token is over: every slot of the next one carries a new sequence
+    const int mode = ctrl[CTRL_SELF_FEED];
+    if (mode) {
+        const bool scripted = mode == 2 && token_script && step + 1 < ctrl[CTRL_SCRIPT_LEN];
+        ctrl[CTRL_TOKEN] = scripted ? token_script[step + 1] : id;
+        ctrl[CTRL_POS] += 1;
+    }
+}
+
 template <int GEMV_WARPS>
 __device__ __forceinline__ void gemv_argmax_tail(const GemvParams& P, float best_v, int best_i, float* misc, uint32_t gen, uint32_t seq) {
     constexpr int GEMV_THREADS = GEMV_WARPS * 32;
@@ -718,19 +734,7 @@ __device__ __forceinline__ void gemv_argmax_tail(const GemvParams& P, float best
                 }
                 P.result[0] = bi;
                 reinterpret_cast<float*>(P.result)[1] = bv;
-                if (P.ctrl) {
-                    int* ctrl = P.ctrl;
-                    const int step = ctrl[CTRL_STEP];
-                    if (P.token_log && step < ctrl[CTRL_LOG_CAP]) P.token_log[step] = bi;
-                    ctrl[CTRL_STEP] = step + 1;
-                    ctrl[CTRL_GEN] = (int)(gen + 1u);      // the token is over: every slot of the next one carries a new sequence
-                    const int mode = ctrl[CTRL_SELF_FEED];
-                    if (mode) {
-                        const bool scripted = mode == 2 && P.token_script && step + 1 < ctrl[CTRL_SCRIPT_LEN];
-                        ctrl[CTRL_TOKEN] = scripted ? P.token_script[step + 1] : bi;
-                        ctrl[CTRL_POS] += 1;
-                    }
-                }
+                if (P.ctrl) advance_token(P.ctrl, P.token_log, P.token_script, bi, gen);
             }
         }
     }
@@ -956,7 +960,6 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32, GEMV_WARPS >= 16 ? 1 : 2) gem
 // the CTA owning the split that contains `pos` normalises/rotates K and writes K,V to the fp16 cache.
 constexpr int ATT_THREADS = 256;
 constexpr int ATT_CHUNK = 128;
-constexpr int ATT_D = 128;
 constexpr int ATT_MAX_GROUP = 8;
 
 struct AttnParams {
@@ -984,6 +987,7 @@ struct AttnParams {
     unsigned* ticket;        // [kv_heads]
     const int* ctrl;
     int group;               // q heads per kv head
+    int head_dim;            // 64, 128 or 256
     int max_seq;
     int max_splits;
     int neox;
@@ -1003,66 +1007,84 @@ struct VecSrc {
     __device__ __forceinline__ float get(int i) const {
         return ll ? __uint_as_float(wait_ll(ll + i, seq, status, budget)) : p[i];
     }
-    // four elements at once: the loads are issued together, a slot that is not filled yet is then waited for alone
-    __device__ __forceinline__ void get4(int i0, int i1, int i2, int i3, float* v) const {
-        if (!ll) { v[0] = p[i0]; v[1] = p[i1]; v[2] = p[i2]; v[3] = p[i3]; return; }
-        const uint2 a = ld_ll(ll + i0), b = ld_ll(ll + i1), c = ld_ll(ll + i2), d = ld_ll(ll + i3);
-        v[0] = a.y == seq ? __uint_as_float(a.x) : get(i0);
-        v[1] = b.y == seq ? __uint_as_float(b.x) : get(i1);
-        v[2] = c.y == seq ? __uint_as_float(c.x) : get(i2);
-        v[3] = d.y == seq ? __uint_as_float(d.x) : get(i3);
+    // N elements at once: the loads are issued together, a slot that is not filled yet is then waited for alone
+    template <int N>
+    __device__ __forceinline__ void getn(const int* idx, float* v) const {
+        if (!ll) {
+#pragma unroll
+            for (int k = 0; k < N; ++k) v[k] = p[idx[k]];
+            return;
+        }
+        uint2 r[N];
+#pragma unroll
+        for (int k = 0; k < N; ++k) r[k] = ld_ll(ll + idx[k]);
+#pragma unroll
+        for (int k = 0; k < N; ++k) v[k] = r[k].y == seq ? __uint_as_float(r[k].x) : get(idx[k]);
     }
 };
 
+// One warp normalises (optional RMS norm over the head), rotates and scales one head of D values into dst[D].
+// NeoX pairing is (i, i + D/2) and a lane owns i = lane + 32 k; the interleaved pairing is (2i, 2i+1) and a lane
+// owns D/32 consecutive values.
+template <int D>
 __device__ __forceinline__ void norm_rope_head(const VecSrc& src, const float* nw, float eps, const float* cs, const float* sn,
-                                               int neox, float mul, float* dst /*smem [128]*/, int lane) {
-    // one warp processes one head of 128 values: lane holds 4 values
-    float v[4];
-    if (neox) src.get4(lane, lane + 32, lane + 64, lane + 96, v);
-    else src.get4(4 * lane, 4 * lane + 1, 4 * lane + 2, 4 * lane + 3, v);
+                                               int neox, float mul, float* dst /*smem [D]*/, int lane) {
+    constexpr int VPL = D / 32;
+    float v[VPL];
+    int idx[VPL];
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) idx[k] = neox ? lane + 32 * k : VPL * lane + k;
+    src.getn<VPL>(idx, v);
     if (nw) {
-        float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+        float ss = 0.f;
+#pragma unroll
+        for (int k = 0; k < VPL; ++k) ss += v[k] * v[k];
         ss = warp_sum(ss);
-        const float rs = rsqrtf(ss / 128.0f + eps);
-        if (neox) { v[0] *= rs * nw[lane]; v[1] *= rs * nw[lane + 32]; v[2] *= rs * nw[lane + 64]; v[3] *= rs * nw[lane + 96]; }
-        else { const float4 w = reinterpret_cast<const float4*>(nw)[lane]; v[0] *= rs * w.x; v[1] *= rs * w.y; v[2] *= rs * w.z; v[3] *= rs * w.w; }
+        const float rs = rsqrtf(ss / (float)D + eps);
+#pragma unroll
+        for (int k = 0; k < VPL; ++k) v[k] *= rs * nw[idx[k]];
     }
     if (neox) {
-        // pairs (i, i+64): lane owns i = lane and lane+32
-        const float c0 = cs[lane], s0 = sn[lane], c1 = cs[lane + 32], s1 = sn[lane + 32];
-        dst[lane] = (v[0] * c0 - v[2] * s0) * mul;
-        dst[lane + 64] = (v[2] * c0 + v[0] * s0) * mul;
-        dst[lane + 32] = (v[1] * c1 - v[3] * s1) * mul;
-        dst[lane + 96] = (v[3] * c1 + v[1] * s1) * mul;
+#pragma unroll
+        for (int k = 0; k < VPL / 2; ++k) {
+            const int i = lane + 32 * k;
+            const float c = cs[i], s_ = sn[i];
+            dst[i] = (v[k] * c - v[k + VPL / 2] * s_) * mul;
+            dst[i + D / 2] = (v[k + VPL / 2] * c + v[k] * s_) * mul;
+        }
     } else {
-        // pairs (2i, 2i+1): lane owns i = 2*lane, 2*lane+1
-        const float c0 = cs[2 * lane], s0 = sn[2 * lane], c1 = cs[2 * lane + 1], s1 = sn[2 * lane + 1];
-        dst[4 * lane + 0] = (v[0] * c0 - v[1] * s0) * mul;
-        dst[4 * lane + 1] = (v[1] * c0 + v[0] * s0) * mul;
-        dst[4 * lane + 2] = (v[2] * c1 - v[3] * s1) * mul;
-        dst[4 * lane + 3] = (v[3] * c1 + v[2] * s1) * mul;
+#pragma unroll
+        for (int k = 0; k < VPL / 2; ++k) {
+            const int j = VPL / 2 * lane + k;          // pair index
+            const float c = cs[j], s_ = sn[j];
+            dst[2 * j] = (v[2 * k] * c - v[2 * k + 1] * s_) * mul;
+            dst[2 * j + 1] = (v[2 * k + 1] * c + v[2 * k] * s_) * mul;
+        }
     }
 }
 
 // One thread-block cluster of ATT_CLUSTER CTAs per KV head.  CTA r of the cluster walks cache chunks
 // r, r+CL, r+2CL, ... (128 positions each) with an online softmax, then the CTAs exchange their partial
 // {max, sum, output} through distributed shared memory and each writes 1/CL of the head group's output.
+// D (head size) is 64, 128 or 256; G is the number of query heads per KV head.
 constexpr int ATT_CLUSTER = 8;
 
+template <int D>
 struct AttnShared {
-    float qs[ATT_MAX_GROUP][ATT_D];                         // normalised, rotated, pre-scaled queries
-    float kn[ATT_D];
+    float qs[ATT_MAX_GROUP][D];                             // normalised, rotated, pre-scaled queries
+    float kn[D];
     float sc[ATT_MAX_GROUP][ATT_CHUNK];                     // scores, then probabilities of the current chunk
     float hm[ATT_MAX_GROUP], hl[ATT_MAX_GROUP];             // chunk max / sum
     float M[ATT_MAX_GROUP], L[ATT_MAX_GROUP];               // running max / sum of this CTA (read by peers)
-    float O[ATT_MAX_GROUP][ATT_D];                          // this CTA's unnormalised output (read by peers)
-    float red[ATT_THREADS / 32][ATT_MAX_GROUP][ATT_D];      // cross-warp reduction
+    float O[ATT_MAX_GROUP][D];                              // this CTA's unnormalised output (read by peers)
+    float red[ATT_THREADS / 32][ATT_MAX_GROUP][D];          // cross-warp reduction
 };
 
-template <int G>
+template <int G, int D>
 __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_constant__ AttnParams P) {
     extern __shared__ __align__(16) uint8_t att_smem_raw[];
-    AttnShared& sh = *reinterpret_cast<AttnShared*>(att_smem_raw);
+    using Shared = AttnShared<D>;
+    Shared& sh = *reinterpret_cast<Shared*>(att_smem_raw);
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
     auto stamp = [&](int k) {
@@ -1078,6 +1100,11 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
     if (!dataflow || P.hard_wait) pdl_wait();
     stamp(1);
 
+    constexpr int VPL = D / 32;                    // values of one head per lane
+    constexpr int KU4 = D / 16;                    // 16-byte loads per thread for half a K row
+    constexpr int DC = D / 8;                      // P@V: column threads (8 dims each) ...
+    constexpr int RG = ATT_THREADS / DC;           // ... x row groups
+    constexpr int VU4 = ATT_CHUNK / RG;            // 16-byte V loads per thread and chunk
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t gen = P.gen ? *reinterpret_cast<const volatile uint32_t*>(P.gen) : 0u;
     const uint32_t in_seq = gen * LL_SEQ_MUL + P.in_seq_add, out_seq = gen * LL_SEQ_MUL + P.out_seq_add;
@@ -1089,42 +1116,45 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
     const int lo = (P.window > 0 && T > P.window) ? T - P.window : 0;     // first visible position
     const int first_chunk = lo / ATT_CHUNK;
     const int nchunk = (T + ATT_CHUNK - 1) / ATT_CHUNK;
-    const float* cs = P.cos + (size_t)pos * (ATT_D / 2);
-    const float* sn = P.sin + (size_t)pos * (ATT_D / 2);
-    __half* kc = P.k_cache + (size_t)kvh * P.max_seq * ATT_D;
-    __half* vc = P.v_cache + (size_t)kvh * P.max_seq * ATT_D;
+    const float* cs = P.cos + (size_t)pos * (D / 2);
+    const float* sn = P.sin + (size_t)pos * (D / 2);
+    __half* kc = P.k_cache + (size_t)kvh * P.max_seq * D;
+    __half* vc = P.v_cache + (size_t)kvh * P.max_seq * D;
     // my first chunk: the smallest c >= first_chunk with c % CL == crank
     int c0 = first_chunk + ((crank - first_chunk) % ATT_CLUSTER + ATT_CLUSTER) % ATT_CLUSTER;
     const bool active = c0 < nchunk;
 
-    // ---- prologue: q heads of this group (normalised, rotated, pre-scaled by 1/sqrt(d) * log2(e));
+    // ---- prologue: q heads of this group (normalised, rotated, pre-scaled by scale * log2(e));
     //      the CTA whose chunk holds `pos` normalises/rotates the new K and writes K,V into the cache
     const bool owns_new = active && ((pos / ATT_CHUNK) % ATT_CLUSTER == crank);
     if (active && warp < G) {
-        const size_t o = (size_t)(kvh * G + warp) * ATT_D;
+        const size_t o = (size_t)(kvh * G + warp) * D;
         const VecSrc qs{P.q ? P.q + o : nullptr, dataflow ? P.q_ll + o : nullptr, in_seq, P.status, budget};
-        norm_rope_head(qs, P.q_norm, P.eps, cs, sn, P.neox, P.scale * 1.4426950408889634f, sh.qs[warp], lane);
+        norm_rope_head<D>(qs, P.q_norm, P.eps, cs, sn, P.neox, P.scale * 1.4426950408889634f, sh.qs[warp], lane);
     }
     if (owns_new && warp == ATT_THREADS / 32 - 1) {
-        const size_t o = (size_t)kvh * ATT_D;
+        const size_t o = (size_t)kvh * D;
         const VecSrc ks{P.k ? P.k + o : nullptr, dataflow ? P.k_ll + o : nullptr, in_seq, P.status, budget};
         const VecSrc vs{P.v ? P.v + o : nullptr, dataflow ? P.v_ll + o : nullptr, in_seq, P.status, budget};
-        norm_rope_head(ks, P.k_norm, P.eps, cs, sn, P.neox, 1.0f, sh.kn, lane);
+        norm_rope_head<D>(ks, P.k_norm, P.eps, cs, sn, P.neox, 1.0f, sh.kn, lane);
         __syncwarp();
-        float vv[4];
-        vs.get4(lane, lane + 32, lane + 64, lane + 96, vv);
+        float vv[VPL];
+        int idx[VPL];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
+        for (int k = 0; k < VPL; ++k) idx[k] = lane + 32 * k;
+        vs.getn<VPL>(idx, vv);
+#pragma unroll
+        for (int k = 0; k < VPL; ++k) {
             const int i = lane + 32 * k;
-            kc[(size_t)pos * ATT_D + i] = __float2half_rn(sh.kn[i]);
-            vc[(size_t)pos * ATT_D + i] = __float2half_rn(vv[k]);
+            kc[(size_t)pos * D + i] = __float2half_rn(sh.kn[i]);
+            vc[(size_t)pos * D + i] = __float2half_rn(vv[k]);
         }
     }
     if (tid < ATT_MAX_GROUP) { sh.M[tid] = -INFINITY; sh.L[tid] = 0.f; }
     __syncthreads();
     stamp(2);
 
-    const int rg = tid >> 4, dc = tid & 15;          // P@V mapping: 16 row-groups x 16 column-threads (8 dims each)
+    const int rg = tid / DC, dc = tid % DC;          // P@V mapping: RG row-groups x DC column-threads (8 dims each)
     float acc[G][8];
 #pragma unroll
     for (int g = 0; g < G; ++g)
@@ -1137,52 +1167,48 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
     for (int c = c0; c < nchunk; c += ATT_CLUSTER) {
         const int base = c * ATT_CHUNK;
         const int t0 = max(base, lo), t1 = min(base + ATT_CHUNK, T);
-        // ---- scores: two threads per cache position, 64 dims each; all loads issued before any math
+        // ---- scores: two threads per cache position, D/2 dims each; all loads issued before any math
         {
             const int tl = tid >> 1, hf = tid & 1;
             const int t = base + tl;
             const bool valid = t >= t0 && t < t1;
-            uint4 raw[8];
+            uint4 raw[KU4];
             if (valid) {
-                const uint4* kp = reinterpret_cast<const uint4*>(kc + (size_t)t * ATT_D + hf * 64);
+                const uint4* kp = reinterpret_cast<const uint4*>(kc + (size_t)t * D + hf * (D / 2));
 #pragma unroll
-                for (int i = 0; i < 8; ++i) raw[i] = kp[i];
+                for (int i = 0; i < KU4; ++i) raw[i] = kp[i];
             }
             float s[G];
 #pragma unroll
             for (int g = 0; g < G; ++g) s[g] = 0.f;
             if (valid) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
+                for (int i = 0; i < KU4; ++i) {
                     const __half2* h2 = reinterpret_cast<const __half2*>(&raw[i]);
                     float kf[8];
 #pragma unroll
                     for (int k = 0; k < 4; ++k) { const float2 f = __half22float2(h2[k]); kf[2 * k] = f.x; kf[2 * k + 1] = f.y; }
 #pragma unroll
                     for (int g = 0; g < G; ++g) {
-                        {
-                            const float4 qa = *reinterpret_cast<const float4*>(&sh.qs[g][hf * 64 + i * 8]);
-                            const float4 qb = *reinterpret_cast<const float4*>(&sh.qs[g][hf * 64 + i * 8 + 4]);
-                            s[g] += kf[0] * qa.x + kf[1] * qa.y + kf[2] * qa.z + kf[3] * qa.w + kf[4] * qb.x + kf[5] * qb.y +
-                                    kf[6] * qb.z + kf[7] * qb.w;
-                        }
+                        const float4 qa = *reinterpret_cast<const float4*>(&sh.qs[g][hf * (D / 2) + i * 8]);
+                        const float4 qb = *reinterpret_cast<const float4*>(&sh.qs[g][hf * (D / 2) + i * 8 + 4]);
+                        s[g] += kf[0] * qa.x + kf[1] * qa.y + kf[2] * qa.z + kf[3] * qa.w + kf[4] * qb.x + kf[5] * qb.y +
+                                kf[6] * qb.z + kf[7] * qb.w;
                     }
                 }
             }
 #pragma unroll
             for (int g = 0; g < G; ++g) {
-                {
-                    const float tot = s[g] + __shfl_xor_sync(0xffffffffu, s[g], 1);
-                    if (hf == 0) sh.sc[g][tl] = valid ? tot : -INFINITY;
-                }
+                const float tot = s[g] + __shfl_xor_sync(0xffffffffu, s[g], 1);
+                if (hf == 0) sh.sc[g][tl] = valid ? tot : -INFINITY;
             }
         }
         // V for this chunk: issue the loads now, they land while the softmax statistics are computed
-        uint4 vraw[ATT_CHUNK / 16];
+        uint4 vraw[VU4];
 #pragma unroll
-        for (int i = 0; i < ATT_CHUNK / 16; ++i) {
-            const int t = base + rg + 16 * i;
-            vraw[i] = (t >= t0 && t < t1) ? *reinterpret_cast<const uint4*>(vc + (size_t)t * ATT_D + dc * 8) : make_uint4(0, 0, 0, 0);
+        for (int i = 0; i < VU4; ++i) {
+            const int t = base + rg + RG * i;
+            vraw[i] = (t >= t0 && t < t1) ? *reinterpret_cast<const uint4*>(vc + (size_t)t * D + dc * 8) : make_uint4(0, 0, 0, 0);
         }
         __syncthreads();
         // ---- softmax statistics of this chunk (base 2): warp g handles head g
@@ -1203,47 +1229,45 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
         // ---- merge the chunk into the running state and accumulate P @ V
 #pragma unroll
         for (int g = 0; g < G; ++g) {
-            {
-                const float mc = sh.hm[g];
-                const float mn = fmaxf(run_m[g], mc);
-                const float so = exp2f(run_m[g] - mn), sc_ = exp2f(mc - mn);    // exp2f(-inf) = 0 on the first chunk
-                run_m[g] = mn;
-                if (tid == g) { sh.L[g] = sh.L[g] * so + sh.hl[g] * sc_; sh.M[g] = mn; }
+            const float mc = sh.hm[g];
+            const float mn = fmaxf(run_m[g], mc);
+            const float so = exp2f(run_m[g] - mn), sc_ = exp2f(mc - mn);    // exp2f(-inf) = 0 on the first chunk
+            run_m[g] = mn;
+            if (tid == g) { sh.L[g] = sh.L[g] * so + sh.hl[g] * sc_; sh.M[g] = mn; }
 #pragma unroll
-                for (int k = 0; k < 8; ++k) acc[g][k] *= so;
+            for (int k = 0; k < 8; ++k) acc[g][k] *= so;
 #pragma unroll
-                for (int i = 0; i < ATT_CHUNK / 16; ++i) {
-                    const float p = sh.sc[g][rg + 16 * i] * sc_;
-                    const __half2* h2 = reinterpret_cast<const __half2*>(&vraw[i]);
+            for (int i = 0; i < VU4; ++i) {
+                const float p = sh.sc[g][rg + RG * i] * sc_;
+                const __half2* h2 = reinterpret_cast<const __half2*>(&vraw[i]);
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        const float2 f = __half22float2(h2[k]);
-                        acc[g][2 * k] += p * f.x;
-                        acc[g][2 * k + 1] += p * f.y;
-                    }
+                for (int k = 0; k < 4; ++k) {
+                    const float2 f = __half22float2(h2[k]);
+                    acc[g][2 * k] += p * f.x;
+                    acc[g][2 * k + 1] += p * f.y;
                 }
             }
         }
         __syncthreads();       // sc/hm/hl are rewritten by the next chunk
     }
     stamp(3);
-    // ---- combine the 16 row-groups: lanes l and l+16 first, then the 8 warps through shared memory
+    // ---- combine the row-groups: first those that share a warp (32 / DC of them), then the 8 warps through shared memory
     if (active) {
 #pragma unroll
-        for (int g = 0; g < G; ++g)
-#pragma unroll
-            for (int k = 0; k < 8; ++k) acc[g][k] += __shfl_xor_sync(0xffffffffu, acc[g][k], 16);
-        if (lane < 16) {
+        for (int off = 16; off >= DC; off >>= 1)
 #pragma unroll
             for (int g = 0; g < G; ++g)
-                {
 #pragma unroll
-                    for (int k = 0; k < 8; ++k) sh.red[warp][g][dc * 8 + k] = acc[g][k];
-                }
+                for (int k = 0; k < 8; ++k) acc[g][k] += __shfl_xor_sync(0xffffffffu, acc[g][k], off);
+        if (lane < DC) {
+#pragma unroll
+            for (int g = 0; g < G; ++g)
+#pragma unroll
+                for (int k = 0; k < 8; ++k) sh.red[warp][g][(lane % DC) * 8 + k] = acc[g][k];
         }
         __syncthreads();
-        for (int i = tid; i < G * ATT_D; i += ATT_THREADS) {
-            const int g = i / ATT_D, d = i - g * ATT_D;
+        for (int i = tid; i < G * D; i += ATT_THREADS) {
+            const int g = i / D, d = i - g * D;
             float o = 0.f;
 #pragma unroll
             for (int w = 0; w < ATT_THREADS / 32; ++w) o += sh.red[w][g][d];
@@ -1252,17 +1276,18 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
     }
     cluster.sync();
     stamp(4);
-    // ---- cluster merge: this CTA finishes G*128/CL outputs from every peer's {M, L, O}
+    // ---- cluster merge: this CTA finishes G*D/CL outputs from every peer's {M, L, O}
     {
-        const int per = G * ATT_D / ATT_CLUSTER;
+        constexpr int per = G * D / ATT_CLUSTER;
+        static_assert(per <= ATT_THREADS, "one thread per merged output");
         if (tid < per) {
             const int i = crank * per + tid;
-            const int g = i / ATT_D, d = i - g * ATT_D;
+            const int g = i / D, d = i - g * D;
             float Mx = -INFINITY;
             float pm[ATT_CLUSTER];
 #pragma unroll
             for (int p = 0; p < ATT_CLUSTER; ++p) {
-                const AttnShared* ps = cluster.map_shared_rank(&sh, p);
+                const Shared* ps = cluster.map_shared_rank(&sh, p);
                 pm[p] = ps->M[g];
                 Mx = fmaxf(Mx, pm[p]);
             }
@@ -1270,13 +1295,13 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
 #pragma unroll
             for (int p = 0; p < ATT_CLUSTER; ++p) {
                 if (pm[p] > -INFINITY) {
-                    const AttnShared* ps = cluster.map_shared_rank(&sh, p);
+                    const Shared* ps = cluster.map_shared_rank(&sh, p);
                     const float w = exp2f(pm[p] - Mx);
                     Lt += w * ps->L[g];
                     Ot += w * ps->O[g][d];
                 }
             }
-            const size_t oi = (size_t)(kvh * G + g) * ATT_D + d;
+            const size_t oi = (size_t)(kvh * G + g) * D + d;
             if (P.out_ll) st_ll(P.out_ll + oi, __float_as_uint(Ot / Lt), out_seq);
             else P.out[oi] = Ot / Lt;
         }

@@ -62,6 +62,29 @@ __global__ void __launch_bounds__(256) dequant_t16_kernel(const uint8_t* __restr
         float v;
         if (qtype == QT_Q4K) {
             v = q4k_value(w + (((size_t)tile * nblk + b) * 16 + rr) * 144, e);
+        } else if (qtype == QT_Q5K) {
+            // Q4_K with a fifth bit per value: bit (sub-block) of byte (value in sub-block) of the 32 bytes at offset 16
+            const uint8_t* bp = w + (((size_t)tile * nblk + b) * 16 + rr) * 176;
+            const float d = __half2float(*reinterpret_cast<const __half*>(bp));
+            const float dmin = __half2float(*reinterpret_cast<const __half*>(bp + 2));
+            const uint8_t* s = bp + 4;
+            const int is = e >> 5;
+            int scv, mv;
+            if (is < 4) { scv = s[is] & 63; mv = s[is + 4] & 63; }
+            else { scv = (s[is + 4] & 0xF) | ((s[is - 4] >> 6) << 4); mv = (s[is + 4] >> 4) | ((s[is] >> 6) << 4); }
+            const uint8_t qb = bp[48 + (e >> 6) * 32 + (e & 31)];
+            const int q = ((is & 1) ? (qb >> 4) : (qb & 0xF)) | (((bp[16 + (e & 31)] >> is) & 1) << 4);
+            v = d * scv * q - dmin * mv;
+        } else if (qtype == QT_Q8_0) {
+            const uint8_t* blk = w + ((size_t)tile * nblk + b) * 4352;
+            const int u = e >> 5;
+            const int8_t q = reinterpret_cast<const int8_t*>(blk + rr * 256)[((u ^ (rr & 7)) << 5) | (e & 31)];
+            v = __half2float(*reinterpret_cast<const __half*>(blk + 4096 + rr * 16 + u * 2)) * (float)q;
+        } else if (qtype == QT_F16) {
+            // four 64-value blocks of 2048 bytes make up these 256 values
+            const uint8_t* blk = w + ((size_t)tile * (nblk * 4) + (size_t)b * 4 + (e >> 6)) * 2048;
+            const int i = e & 63, u = i >> 4;
+            v = __half2float(reinterpret_cast<const __half*>(blk + rr * 128)[((u ^ (rr & 3)) << 4) | (i & 15)]);
         } else {
             const uint8_t* blk = w + ((size_t)tile * nblk + b) * 3360;
             const int n = e >> 7, r7 = e & 127, quad = r7 >> 5, l = r7 & 31;
@@ -106,7 +129,11 @@ using namespace ptb;
 // layout: 0 = [segment][row][segment bytes], 1 = tiles of 16 rows.
 PTB_API int ptb_dequant_weight(const void* w, int qtype, int layout, int N, int cols, void* out, cudaStream_t st) {
     if (cols % 256 || N <= 0) { ptb_set_error("dequant: %d x %d not supported", N, cols); return -1; }
-    if (qtype != QT_Q4K && qtype != QT_Q6K) { ptb_set_error("dequant: unknown quantisation type %d", qtype); return -1; }
+    const bool tile_only = qtype == QT_Q5K || qtype == QT_Q8_0 || qtype == QT_F16;
+    if (!(qtype == QT_Q4K || qtype == QT_Q6K || (tile_only && layout == 1))) {
+        ptb_set_error("dequant: quantisation type %d is not available in layout %d", qtype, layout);
+        return -1;
+    }
     const int nblk = cols / 256;
     if (layout == 1) {
         dequant_t16_kernel<<<dim3(nblk, (N + 3) / 4), 256, 0, st>>>((const uint8_t*)w, qtype, N, nblk, (__nv_bfloat16*)out);

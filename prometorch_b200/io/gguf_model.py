@@ -30,7 +30,7 @@ from .config import TransformerConfig
 from .gguf import GGUFReader
 from .gguf_quant import GGMLType, dequantize, quantize
 
-QT_Q4K, QT_Q6K, QT_F16, QT_F32 = 0, 1, 2, 3
+QT_Q4K, QT_Q6K, QT_F16, QT_F32, QT_Q5K, QT_Q8_0 = 0, 1, 2, 3, 4, 5
 
 
 def split_blocks(nblk: int, world: int, rank: int):
@@ -86,30 +86,60 @@ def segment_major(raw: torch.Tensor, qtype: GGMLType, b0: int, b1: int) -> torch
 LAYOUT_SEGMENT, LAYOUT_T16 = 0, 1
 
 
+# bytes of one row's block as stored in the file, and values per block, for the types the tile layout takes natively
+_FILE_BLOCK = {GGMLType.Q4_K: (144, 256), GGMLType.Q6_K: (210, 256), GGMLType.Q5_K: (176, 256), GGMLType.Q8_0: (34, 32),
+               GGMLType.F16: (2, 1)}
+_KERNEL_TYPE = {GGMLType.Q4_K: QT_Q4K, GGMLType.Q6_K: QT_Q6K, GGMLType.Q5_K: QT_Q5K, GGMLType.Q8_0: QT_Q8_0,
+                GGMLType.F16: QT_F16}
+
+
+def _swizzle_units(x: torch.Tensor, mask: int) -> torch.Tensor:
+    """``x[..., row(16), unit, bytes]``: destination unit ``u`` takes source unit ``u ^ (row & mask)``."""
+    dev = x.device
+    nu = x.shape[-2]
+    idx = torch.arange(nu, device=dev)[None, :] ^ (torch.arange(16, device=dev) & mask)[:, None]        # [16, nu]
+    shape = [1] * (x.dim() - 3) + [16, nu, 1]
+    return torch.gather(x, x.dim() - 2, idx.reshape(shape).expand_as(x))
+
+
 def tile16_major(raw: torch.Tensor, qtype: GGMLType, b0: int, b1: int) -> torch.Tensor:
-    """The tensor-pipe GEMV's layout over blocks ``[b0, b1)`` of every row: rows padded with zero blocks to a multiple
-    of 16, then ``[tile of 16 rows][block][row in tile][block bytes]``.  Q6_K blocks are split into their arrays
-    (``ql[16][128] | qh[16][64] | scales[16][16] | d[16]``) and the 16-byte chunks of a ``ql`` row are stored at
-    ``chunk ^ (row & 7)``, those of a ``qh`` row at ``chunk ^ ((row >> 1) & 3)``: the kernel's shared-memory loads then
-    fall on distinct banks (csrc/decode_gemv_mma.cuh)."""
+    """The tensor-pipe GEMV's layout over the 256-value blocks ``[b0, b1)`` of every row: rows padded with zeros to a
+    multiple of 16, then ``[tile of 16 rows][block][row in tile][block bytes]`` (csrc/decode_gemv_mma.cuh):
+
+    * Q4_K / Q5_K: the file's 144 / 176-byte blocks unchanged;
+    * Q6_K: split into arrays (``ql[16][128] | qh[16][64] | scales[16][16] | d[16]``), the 16-byte chunks of a ``ql``
+      row stored at ``chunk ^ (row & 7)``, those of a ``qh`` row at ``chunk ^ ((row >> 1) & 3)``;
+    * Q8_0: eight file blocks per row and unit: ``q[16][256]`` with the 32-byte unit ``u`` of a row at ``u ^ (row & 7)``,
+      then ``d[16][8]``;
+    * F16: blocks of 64 values, ``[16][64]`` halves with the 32-byte unit ``u`` of a row at ``u ^ (row & 3)``.
+
+    The swizzles put the eight rows one shared-memory load touches on distinct banks."""
+    qtype = GGMLType(qtype)
     n = raw.shape[0]
-    bb = 144 if qtype == GGMLType.Q4_K else 210
-    blk = raw.reshape(n, -1, bb)[:, b0:b1]
+    bb, per = _FILE_BLOCK[qtype]
+    raw = raw.reshape(n, -1)
+    blk = raw.reshape(n, -1, bb * (256 // per))[:, b0:b1]                  # [n, 256-value blocks, bytes]
     nb = blk.shape[1]
     n16 = (n + 15) // 16 * 16
     if n16 != n:
-        blk = torch.cat([blk, torch.zeros(n16 - n, nb, bb, dtype=torch.uint8, device=blk.device)])
-    t = blk.reshape(n16 // 16, 16, nb, bb).permute(0, 2, 1, 3)             # [tile, block, row, bytes]
-    if qtype == GGMLType.Q4_K:
+        blk = torch.cat([blk, torch.zeros(n16 - n, nb, blk.shape[2], dtype=torch.uint8, device=blk.device)])
+    t = blk.reshape(n16 // 16, 16, nb, -1).permute(0, 2, 1, 3)             # [tile, block, row, bytes]
+    if qtype in (GGMLType.Q4_K, GGMLType.Q5_K):
         return t.contiguous().reshape(-1)
+    if qtype == GGMLType.Q8_0:
+        f = t.reshape(-1, nb, 16, 8, 34)
+        q = _swizzle_units(f[..., 2:34].contiguous(), 7)                  # [tile, block, 16, 8, 32]
+        d = f[..., 0:2]
+        return torch.cat([q.reshape(-1, nb, 16 * 256), d.reshape(-1, nb, 16 * 16)], dim=2).contiguous().reshape(-1)
+    if qtype == GGMLType.F16:
+        f = t.reshape(-1, nb, 16, 4, 4, 32).permute(0, 1, 3, 2, 4, 5)     # [tile, block, quarter(64 values), row, unit, 32 B]
+        return _swizzle_units(f.contiguous(), 3).reshape(-1)
+    ql = _swizzle_units(t[..., 0:128].reshape(-1, nb, 16, 8, 16), 7)
+    # qh chunk key is (row >> 1) & 3
     dev = blk.device
     row = torch.arange(16, device=dev)
-    ql = t[..., 0:128].reshape(-1, nb, 16, 8, 16)
     qh = t[..., 128:192].reshape(-1, nb, 16, 4, 16)
-    # destination chunk c holds source chunk c ^ key(row) (xor is its own inverse)
-    idx_l = (torch.arange(8, device=dev)[None, :] ^ (row & 7)[:, None])                 # [16, 8]
     idx_h = (torch.arange(4, device=dev)[None, :] ^ ((row >> 1) & 3)[:, None])          # [16, 4]
-    ql = torch.gather(ql, 3, idx_l[None, None, :, :, None].expand(ql.shape[0], nb, 16, 8, 16))
     qh = torch.gather(qh, 3, idx_h[None, None, :, :, None].expand(qh.shape[0], nb, 16, 4, 16))
     parts = [ql.reshape(-1, nb, 16 * 128), qh.reshape(-1, nb, 16 * 64), t[..., 192:208].reshape(-1, nb, 16 * 16),
              t[..., 208:210].reshape(-1, nb, 16 * 2)]
@@ -134,13 +164,21 @@ class PackedWeight:
         return self.data.numel()
 
 
-def _to_kernel_type(raw: torch.Tensor, qtype: GGMLType, cols: int):
-    """Types other than Q4_K/Q6_K are transcoded to Q6_K blocks (the only lossy step, and only for such files)."""
+def _to_kernel_type(raw: torch.Tensor, qtype: GGMLType, cols: int, layout: int = 0):
+    """Bytes and type the kernels take.  The tile layout streams Q4_K, Q5_K, Q6_K, Q8_0 and F16 as they are (BF16 and
+    F32 matrices become F16); anything else, and every type but Q4_K/Q6_K in the segment layout, is transcoded to Q6_K
+    blocks (the only lossy step, and only for such files)."""
     qtype = GGMLType(qtype)
-    if qtype not in (GGMLType.Q4_K, GGMLType.Q6_K):
-        raw = quantize(dequantize(raw, qtype, cols), GGMLType.Q6_K)
-        qtype = GGMLType.Q6_K
-    return raw, qtype
+    if qtype in (GGMLType.Q4_K, GGMLType.Q6_K):
+        return raw, qtype
+    if layout == LAYOUT_T16:
+        if qtype in (GGMLType.Q5_K, GGMLType.Q8_0, GGMLType.F16):
+            return raw, qtype
+        if qtype in (GGMLType.BF16, GGMLType.F32):
+            w = dequantize(raw, qtype, cols).to(torch.float16).contiguous()
+            return w.view(torch.uint8).reshape(w.shape[0], -1), GGMLType.F16
+    raw = quantize(dequantize(raw, qtype, cols), GGMLType.Q6_K)
+    return raw, GGMLType.Q6_K
 
 
 def default_layout() -> int:
@@ -156,23 +194,28 @@ def pack_weight(raw: torch.Tensor, qtype: GGMLType, cols: int, device, rows=None
     layout = default_layout() if layout is None else layout
     if rows is not None:
         raw = raw[rows[0]:rows[1]]
-    raw, qtype = _to_kernel_type(raw.to(device, non_blocking=True), qtype, cols)
+    raw, qtype = _to_kernel_type(raw.to(device, non_blocking=True), qtype, cols, layout)
     b0, b1 = kblocks if kblocks is not None else (0, cols // 256)
     data = tile16_major(raw, qtype, b0, b1) if layout == LAYOUT_T16 else segment_major(raw, qtype, b0, b1)
     if bias is not None:
         bias = bias.to(device).float().contiguous()
         if rows is not None:
             bias = bias[rows[0]:rows[1]].contiguous()
-    return PackedWeight(data, QT_Q4K if qtype == GGMLType.Q4_K else QT_Q6K, raw.shape[0], (b1 - b0) * 256, bias, layout=layout)
+    return PackedWeight(data, _KERNEL_TYPE[qtype], raw.shape[0], (b1 - b0) * 256, bias, layout=layout)
 
 
 def pack_table(raw: torch.Tensor, qtype: GGMLType, cols: int, device) -> PackedWeight:
-    """Row-major layout for row lookups (the embedding table)."""
-    raw, qtype = _to_kernel_type(raw.to(device, non_blocking=True), qtype, cols)
+    """Row-major layout for row lookups (the embedding table): Q4_K rows as in the file, Q6_K rows as a structure of
+    arrays, every other type as an fp16 table."""
+    qtype = GGMLType(qtype)
+    raw = raw.to(device, non_blocking=True)
     if qtype == GGMLType.Q4_K:
         data, qt = raw.contiguous(), QT_Q4K
-    else:
+    elif qtype == GGMLType.Q6_K:
         data, qt = repack_q6k(raw), QT_Q6K
+    else:
+        w = (raw.view(torch.float16) if qtype == GGMLType.F16 else dequantize(raw, qtype, cols).to(torch.float16)).contiguous()
+        data, qt = w.view(torch.uint8).reshape(w.shape[0], -1), QT_F16
     return PackedWeight(data, qt, data.shape[0], cols, None, rowbytes=data.shape[1])
 
 
@@ -379,8 +422,9 @@ class GGUFModel:
     # ------------------------------------------------------------------ batched prompt pass
     @property
     def supports_prefill(self) -> bool:
-        """The batched prompt pass covers one GPU, full attention (no sliding window), head size 64/128."""
-        return self.tp_world == 1 and not self.cfg.swa_window and self.cfg.head_dim in (64, 128)
+        """The batched prompt pass covers full attention (no sliding window) with head size 64 or 128, on one GPU or,
+        under tensor parallelism, on every rank over its own heads and FFN columns with two all-reduces per layer."""
+        return not self.cfg.swa_window and self.cfg.head_dim in (64, 128)
 
     def _dequant(self, pw: "PackedWeight") -> torch.Tensor:
         """bf16 ``[rows, cols]`` copy of a packed matrix in a scratch buffer shared by all matrices of that shape."""
@@ -404,9 +448,10 @@ class GGUFModel:
         """Run ``tokens`` at positions ``pos0 ..`` through the model in ONE batched pass that fills the KV cache:
         weights are dequantised to bf16 layer by layer and every projection is a tcgen05 GEMM over all prompt
         tokens, attention is the FlashAttention kernel.  Nothing is returned; decoding continues with
-        ``forward_decode(next_token, pos0 + len(tokens))``.  (Token-by-token prefill costs one decode step each.)"""
+        ``forward_decode(next_token, pos0 + len(tokens))``.  (Token-by-token prefill costs one decode step each.)
+        Under tensor parallelism the call is collective: every rank runs it with the same tokens."""
         if not self.supports_prefill:
-            raise NotImplementedError("batched prefill: one GPU, no sliding window")
+            raise NotImplementedError("batched prefill: no sliding window, head size 64 or 128")
         from ..ops import fused_ops as K
         from ..ops.attention import flash_attention
         from ..ops.gemm import linear
@@ -440,6 +485,16 @@ class GGUFModel:
             y = linear(h, self._dequant(pw), None)
             return y if pw.bias is None else y + pw.bias.to(bf)
 
+        def ksplit(h, pw):
+            """A projection split along K over the ranks (attention output, FFN down): every rank multiplies its own
+            columns and the partial results are summed in fp32 across the ranks (collective: all ranks prefill together)."""
+            y = proj(h, pw)
+            if self.tp_world > 1:
+                y32 = y.float()
+                self.symm.dist.all_reduce(y32, group=self.symm.pg)
+                y = y32.to(bf)
+            return y
+
         for i, L in enumerate(self.layers):
             h = K.rms_norm(x, nw(L, "attn_norm"), eps)
             q = proj(h, L["q"]).view(T, hq, d)
@@ -459,14 +514,14 @@ class GGUFModel:
             else:
                 k_all, v_all = k, v.unsqueeze(0)
             att = flash_attention(q, k_all, v_all, causal=True, q_offset=pos0).reshape(T, hq * d)
-            o = proj(att, L["o"])
+            o = ksplit(att, L["o"])
             if L["post_attn_norm"] is not None:
                 o = K.rms_norm(o, nw(L, "post_attn_norm"), eps)
             x = x + o
             h = K.rms_norm(x, nw(L, "ffn_norm"), eps)
             g, u = proj(h, L["gate"]), proj(h, L["up"]).clone()       # gate and up share a scratch shape: keep one
             act = torch.nn.functional.gelu(g.float(), approximate="tanh") if cfg.ffn_gelu else torch.nn.functional.silu(g.float())
-            dn = proj((act * u.float()).to(bf), L["down"])
+            dn = ksplit((act * u.float()).to(bf), L["down"])
             if L["post_ffn_norm"] is not None:
                 dn = K.rms_norm(dn, nw(L, "post_ffn_norm"), eps)
             x = x + dn

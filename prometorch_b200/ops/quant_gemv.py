@@ -59,7 +59,7 @@ def quant_gemv(w: PackedWeight, x: torch.Tensor, *, w2: Optional[PackedWeight] =
 def attn_decode(q, k, v, k_cache, v_cache, pos: int, cos, sin, *, q_norm=None, k_norm=None, neox=True, eps=1e-6,
                 window: int = 0):
     """One-token attention: writes the new K/V (after optional per-head RMSNorm and RoPE) at
-    ``pos`` into the fp16 caches ``[kv_heads, max_seq, 128]`` and returns ``[heads*128]``."""
+    ``pos`` into the fp16 caches ``[kv_heads, max_seq, d]`` (d = 64, 128 or 256) and returns ``[heads*d]``."""
     _require_cuda(q)
     lib = N.lib()
     dev = q.device
@@ -76,6 +76,6 @@ def attn_decode(q, k, v, k_cache, v_cache, pos: int, cos, sin, *, q_norm=None, k
     st = torch.cuda.current_stream(dev).cuda_stream
     N.check(lib.ptb_attn_decode(q.data_ptr(), k.data_ptr(), v.data_ptr(), N.ptr(q_norm), N.ptr(k_norm), cos.data_ptr(),
                                 sin.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
-                                part_o.data_ptr(), part_ml.data_ptr(), ticket.data_ptr(), ctrl.data_ptr(), kvh, group,
+                                part_o.data_ptr(), part_ml.data_ptr(), ticket.data_ptr(), ctrl.data_ptr(), kvh, group, d,
                                 max_seq, int(neox), eps, window, st), "attn_decode")
     return out

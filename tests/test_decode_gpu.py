@@ -41,6 +41,32 @@ def test_gemv_matches_fp32(qt, rows, cols, layout):
     assert _rel(y, ref) < 2e-2, _rel(y, ref)
 
 
+@pytest.mark.parametrize("qt", [Q.GGMLType.Q5_K, Q.GGMLType.Q8_0, Q.GGMLType.F16], ids=["q5_k", "q8_0", "f16"])
+@pytest.mark.parametrize("rows,cols", [(4096, 2560), (2560, 9728), (300, 512), (7, 256)])
+def test_gemv_native_q5k_q8_0_f16(qt, rows, cols):
+    """Q5_K, Q8_0 and fp16 matrices are streamed as they are (16-row tile layout), not transcoded."""
+    from prometorch_b200.io.gguf_model import QT_F16, QT_Q5K, QT_Q8_0
+    from prometorch_b200.ops.quant_gemv import quant_gemv
+    pw, wd = _packed(rows, cols, qt, seed=rows + cols, layout=1)
+    assert pw.qtype == {Q.GGMLType.Q5_K: QT_Q5K, Q.GGMLType.Q8_0: QT_Q8_0, Q.GGMLType.F16: QT_F16}[qt]
+    x = torch.randn(cols, device="cuda", generator=torch.Generator(device="cuda").manual_seed(rows * 7 + cols))
+    y = quant_gemv(pw, x)
+    torch.cuda.synchronize()
+    ref_q8 = wd.float() @ Q.quantize_activation_q8(x)
+    assert _rel(y, ref_q8) < 8e-4, _rel(y, ref_q8)
+    # the gated pair and the prompt path's dequantisation read the same layout
+    pw2, wd2 = _packed(rows, cols, qt, seed=rows + cols + 1, layout=1)
+    y = quant_gemv(pw, x, w2=pw2)
+    xq = Q.quantize_activation_q8(x)
+    assert _rel(y, torch.nn.functional.silu(wd.float() @ xq) * (wd2.float() @ xq)) < 2e-3
+    from prometorch_b200 import _native as N
+    out = torch.empty(rows, cols, dtype=torch.bfloat16, device="cuda")
+    N.check(N.lib().ptb_dequant_weight(pw.data.data_ptr(), pw.qtype, pw.layout, rows, cols, out.data_ptr(),
+                                       torch.cuda.current_stream().cuda_stream), "dequant")
+    torch.cuda.synchronize()
+    assert torch.equal(out, wd.to(torch.bfloat16))
+
+
 def test_gemv_norm_resid_gated_argmax():
     from prometorch_b200.ops.quant_gemv import quant_gemv
     cols, rows = 2560, 1536
@@ -64,11 +90,12 @@ def test_gemv_norm_resid_gated_argmax():
 
 @pytest.mark.parametrize("pos", [0, 5, 127, 128, 300, 1023])
 @pytest.mark.parametrize("neox", [True, False])
-def test_attn_decode(pos, neox):
+@pytest.mark.parametrize("d,H,KV", [(128, 8, 2), (64, 8, 8), (64, 4, 2), (256, 8, 4), (256, 8, 1)])
+def test_attn_decode(pos, neox, d, H, KV):
     from prometorch_b200.models.gguf_oracle import apply_rope, rms_norm, rope_tables
     from prometorch_b200.ops.quant_gemv import attn_decode
-    cfg = tiny_qwen3_config()
-    H, KV, d, S = 8, 2, 128, 1024
+    cfg = tiny_qwen3_config(head_dim=d)
+    S = 1024
     cos, sin = rope_tables(cfg, S, "cuda")
     torch.manual_seed(pos)
     kc = (torch.randn(KV, S, d, device="cuda") * 0.5).half()
@@ -108,6 +135,49 @@ def test_engine_matches_oracle(tiny_model):
     o = OracleModel(tiny_model, device="cuda", max_seq=512, emulate_q8=True)
     toks = [3, 77, 500, 999, 12, 64, 5, 5, 901]
     for pos, t in enumerate(toks):
+        nxt = m.forward_decode(t, pos)
+        lg = m.logits_view().clone()
+        ref = o.forward([t])[0]
+        cos = torch.nn.functional.cosine_similarity(lg, ref, dim=0)
+        assert cos > 0.9995, (pos, float(cos))
+        assert nxt == int(lg.argmax())
+    m.check_status()
+    m.close()
+
+
+@pytest.mark.parametrize("head_dim,heads,kv", [(64, 8, 4), (256, 4, 2)])
+def test_engine_other_head_sizes(tmp_path, head_dim, heads, kv):
+    """Head sizes 64 and 256 (small llamas, gemma) through the whole engine against the fp32 oracle."""
+    from prometorch_b200.io.gguf_model import GGUFModel
+    from prometorch_b200.models.gguf_oracle import OracleModel
+    cfg = tiny_qwen3_config(layers=2, hidden=512, heads=heads, kv_heads=kv, inter=1024, vocab=1000, head_dim=head_dim)
+    p = str(tmp_path / "hd.gguf")
+    write_synthetic_gguf(p, cfg, seed=5, device="cuda", std=0.05)
+    m = GGUFModel(p, max_seq=512, want_logits=True)
+    o = OracleModel(p, device="cuda", max_seq=512, emulate_q8=True)
+    for pos, t in enumerate([3, 77, 500, 999, 12, 64]):
+        nxt = m.forward_decode(t, pos)
+        lg = m.logits_view().clone()
+        ref = o.forward([t])[0]
+        cos = torch.nn.functional.cosine_similarity(lg, ref, dim=0)
+        assert cos > 0.9995, (pos, float(cos))
+        assert nxt == int(lg.argmax())
+    m.check_status()
+    m.close()
+
+
+@pytest.mark.parametrize("q_main,q_more", [(Q.GGMLType.Q5_K, Q.GGMLType.Q8_0), (Q.GGMLType.Q8_0, Q.GGMLType.F16)],
+                         ids=["q5k+q8_0", "q8_0+f16"])
+def test_engine_other_weight_types(tmp_path, q_main, q_more):
+    """Files whose matrices are Q5_K / Q8_0 / F16 decode from those bytes and agree with the fp32 oracle."""
+    from prometorch_b200.io.gguf_model import GGUFModel
+    from prometorch_b200.models.gguf_oracle import OracleModel
+    cfg = tiny_qwen3_config(layers=2, hidden=512, heads=8, kv_heads=2, inter=1024, vocab=1000)
+    p = str(tmp_path / "wt.gguf")
+    write_synthetic_gguf(p, cfg, seed=6, device="cuda", std=0.05, q_main=q_main, q_more=q_more)
+    m = GGUFModel(p, max_seq=512, want_logits=True)
+    o = OracleModel(p, device="cuda", max_seq=512, emulate_q8=True)
+    for pos, t in enumerate([3, 77, 500, 999, 12, 64]):
         nxt = m.forward_decode(t, pos)
         lg = m.logits_view().clone()
         ref = o.forward([t])[0]

@@ -140,6 +140,40 @@ def test_tile16_layout_round_trip():
         assert int(units[ntile - 1].reshape(nb, 16, -1)[:, 0].sum()) >= 0       # padded rows exist (zeros)
 
 
+def test_tile16_layout_of_q5k_q8_0_f16():
+    """Q5_K keeps the file's blocks; Q8_0 and F16 are rebuilt from the swizzle rule in the layout's description."""
+    import torch
+    from prometorch_b200.io.gguf import GGMLType
+    from prometorch_b200.io.gguf_model import tile16_major
+    g = torch.Generator().manual_seed(4)
+    n, nblk, b0, b1 = 21, 4, 1, 3
+    nb, ntile = b1 - b0, 2
+    raw = torch.randint(0, 256, (n, nblk * 176), generator=g, dtype=torch.uint8)
+    units = tile16_major(raw, GGMLType.Q5_K, b0, b1).reshape(ntile, nb, 16, 176)
+    assert torch.equal(units[1, 1, 4], raw.reshape(n, nblk, 176)[20, b0 + 1])
+    assert int(units[1, :, 5:].sum()) == 0                                   # rows 21..31 are padding
+    raw = torch.randint(0, 256, (n, nblk * 8 * 34), generator=g, dtype=torch.uint8)
+    units = tile16_major(raw, GGMLType.Q8_0, b0, b1).reshape(ntile, nb, 4352)
+    want = raw.reshape(n, nblk, 8, 34)
+    for r in (0, 7, 13, 20):
+        tile, rr = divmod(r, 16)
+        for b in range(nb):
+            u = units[tile, b]
+            q = u[rr * 256:(rr + 1) * 256].reshape(8, 32)
+            for s in range(8):
+                assert torch.equal(q[s ^ (rr & 7)], want[r, b0 + b, s, 2:]), (r, b, s)
+                assert torch.equal(u[4096 + rr * 16 + 2 * s:4096 + rr * 16 + 2 * s + 2], want[r, b0 + b, s, :2])
+    raw = torch.randint(0, 256, (n, nblk * 512), generator=g, dtype=torch.uint8)
+    units = tile16_major(raw, GGMLType.F16, b0, b1).reshape(ntile, nb * 4, 16, 4, 32)      # [tile][64-value block][row][unit][32 B]
+    want = raw.reshape(n, nblk, 4, 4, 32)                                                   # [row][256 block][quarter][unit][32 B]
+    for r in (0, 6, 15, 17):
+        tile, rr = divmod(r, 16)
+        for b in range(nb):
+            for qtr in range(4):
+                for u in range(4):
+                    assert torch.equal(units[tile, b * 4 + qtr, rr, u ^ (rr & 3)], want[r, b0 + b, qtr, u]), (r, b, qtr, u)
+
+
 def _ggml_q2_k_scalar(block: bytes):
     """ggml's dequantize_row_q2_K, one block, written out as scalar loops (the golden order of values)."""
     import numpy as np

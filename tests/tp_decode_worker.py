@@ -50,6 +50,44 @@ def main():
         ok = False
         print("scripted tokens differ across ranks", flush=True)
     tp.check_status()
+    # batched prompt pass under tensor parallelism (collective): the cache it writes must continue like the stepped one
+    hid_step = None
+    for pos, t in enumerate(toks):
+        tp.forward_decode(t, pos)
+    hid_step = tp.hidden_view().clone()
+    if not tp.supports_prefill:
+        ok = False
+        print("tensor-parallel model reports no batched prefill", flush=True)
+    else:
+        tp.prefill(toks[:-1])
+        tp.forward_decode(toks[-1], len(toks) - 1)
+        cos = float(torch.nn.functional.cosine_similarity(tp.hidden_view(), hid_step, dim=0))
+        if cos < 0.995:
+            ok = False
+            print(f"prefill + decode against stepped decode: hidden cosine {cos}", flush=True)
+    # the NCCL-only arm (external all-reduce flow) runs the same shards and must land on the same hidden state
+    import ctypes as C
+    from benchmarks.decode_tp_nccl import NcclTokenGraph
+    from prometorch_b200 import _native as N
+    os.environ["PTB_DECODE_FLOW"] = "external"
+    ext = GGUFModel(path, device=str(dev), max_seq=256, tp_rank=rank, tp_world=world, symm=symm)
+    del os.environ["PTB_DECODE_FLOW"]
+    tg = NcclTokenGraph(ext, dist, world)
+    tg.capture()
+    arr = (C.c_int * len(toks))(*toks)
+    N.check(ext._lib.ptb_engine_begin_script(ext._engine, arr, len(toks), 0), "begin_script")
+    tg.run(len(toks))
+    ext.stream.synchronize()
+    ext.check_status()
+    cos = float(torch.nn.functional.cosine_similarity(ext.hidden_view(), hid_step, dim=0))
+    ids_ext = ext.read_generated(len(toks), 1)
+    got = torch.tensor(ids_ext, device=dev)
+    lst = [torch.zeros_like(got) for _ in range(world)]
+    dist.all_gather(lst, got)
+    if cos < 0.9995 or any(not torch.equal(lst[0], x) for x in lst):
+        ok = False
+        print(f"external all-reduce flow: hidden cosine {cos}, ids {[int(x) for x in lst]}", flush=True)
+    ext.close()
     dist.barrier()
     symm.check_canaries()                                # the all-reduce slots stayed inside their buffers
     flag = torch.tensor([1 if ok else 0], device=dev)
