@@ -78,6 +78,25 @@ def main(argv=None) -> int:
     if a.profile:
         os.environ["PTB_TRACE"] = "1"
     t0 = time.time()
+    from .io.gguf import GGUFReader
+    if GGUFReader(path).arch() == "deepseek2":
+        # latent attention + mixture of experts: the tensor-program model (greedy), on the GPU in bf16 or on the CPU in fp32
+        from .models.deepseek2 import DeepSeek2Model
+        model = DeepSeek2Model(path, device="cuda" if use_cuda else "cpu", max_seq=min(4096, a.max_tokens + 2048),
+                               dtype=torch.bfloat16 if use_cuda else torch.float32)
+        tok = GGUFTokenizer.from_reader(model.reader)
+        c = model.cfg
+        say(f"[Model] deepseek2 {c.num_layers} layers, hidden {c.hidden_size}, {c.expert_count} experts ({c.expert_used_count} used), "
+            f"latent cache {model.cache_bytes_per_token} B/token, loaded in {time.time() - t0:.1f} s")
+        text = apply_chat_template(prompt, "deepseek2", "") if (a.chat and not a.raw) else prompt
+        ids = tok.encode(text)
+        say(f"[Generate] Prompt tokens: {len(ids)}")
+        t1 = time.time()
+        out = model.generate(ids, max_new_tokens=a.max_tokens)
+        say(tok.decode(out, strip_leading_space=False))
+        dt = time.time() - t1
+        say(f"\n[Generate] {len(out)} tokens in {dt:.2f}s ({len(out) / max(dt, 1e-9):.1f} tok/s, prompt included)")
+        return 0
     if use_cuda:
         from .io.gguf_model import GGUFModel
         symm = None

@@ -48,11 +48,21 @@ class TransformerConfig:
     yarn_beta_slow: float = 1.0
     yarn_orig_ctx: int = 0
     rope_attn_factor: float = 1.0
-    rope_factors_short: Optional[List[float]] = None
+    rope_factors_short: Optional[List[float]] = None     # phi-3 LongRoPE: inv_freq[i] /= factor[i]
     rope_factors_long: Optional[List[float]] = None
+    rope_orig_ctx: int = 0                                # sequences up to this length use the short factors
     bos_token_id: int = -1
     eos_token_id: int = -1
     extra_stop_ids: List[int] = field(default_factory=list)
+
+    def rope_factors_for(self, seq_len: int) -> Optional[List[float]]:
+        """LongRoPE selector (the reference's rule, torch/io/gguf_model.h:285-296): the short factors while the sequence
+        fits the original context, the long ones beyond it; None for models without factor tensors."""
+        if self.rope_factors_short is None and self.rope_factors_long is None:
+            return None
+        if self.rope_orig_ctx <= 0 or seq_len <= self.rope_orig_ctx:
+            return self.rope_factors_short
+        return self.rope_factors_long if self.rope_factors_long is not None else self.rope_factors_short
 
     @property
     def q_dim(self) -> int:
@@ -88,6 +98,11 @@ class TransformerConfig:
             c.yarn_beta_slow = float(g("rope.scaling.yarn_beta_slow", 1.0))
             c.yarn_orig_ctx = int(g("rope.scaling.original_context_length", 0))
         c.rope_attn_factor = float(g("rope.scaling.attn_factor", 1.0))
+        c.rope_orig_ctx = int(g("rope.scaling.original_context_length", 0))
+        for which in ("short", "long"):
+            name = f"rope_factors_{which}.weight"
+            if name in reader.tensors:
+                setattr(c, f"rope_factors_{which}", [float(v) for v in reader.load(name).reshape(-1).tolist()])
         c.swa_window = int(g("attention.sliding_window", 0))
         c.swa_pattern = int(g("attention.sliding_window_pattern", 0))
         if "token_embd.weight" in reader.tensors:
@@ -111,6 +126,33 @@ class TransformerConfig:
         c.bos_token_id = int(reader.get("tokenizer.ggml.bos_token_id", -1))
         c.eos_token_id = int(reader.get("tokenizer.ggml.eos_token_id", -1))
         return c
+
+
+def layer_matrix_sources(reader, cfg: "TransformerConfig", layer: int):
+    """Where the seven matrices of a decoder layer live in the file: ``{q, k, v, o, gate, up, down} -> (tensor name,
+    (row0, row1) or None)``.  phi-3 / phi-2 / starcoder2 files store Q, K and V merged as ``attn_qkv`` and gate and up
+    merged as an ``ffn_up`` of twice the FFN width (gate rows first); the merged tensors are addressed by row ranges,
+    as the reference splits them (torch/io/gguf_model.h:1624-1653)."""
+    p = f"blk.{layer}."
+    src = {"o": (p + "attn_output.weight", None), "down": (p + "ffn_down.weight", None)}
+    if reader.has_tensor(p + "attn_q.weight"):
+        for k in ("q", "k", "v"):
+            src[k] = (p + f"attn_{k}.weight", None)
+    elif reader.has_tensor(p + "attn_qkv.weight"):
+        Q, KV = cfg.q_dim, cfg.kv_dim
+        n = p + "attn_qkv.weight"
+        src.update(q=(n, (0, Q)), k=(n, (Q, Q + KV)), v=(n, (Q + KV, Q + 2 * KV)))
+    else:
+        raise KeyError(f"layer {layer}: neither attn_q nor attn_qkv")
+    up = p + "ffn_up.weight"
+    if reader.has_tensor(p + "ffn_gate.weight"):
+        src.update(gate=(p + "ffn_gate.weight", None), up=(up, None))
+    elif reader.has_tensor(up) and reader.tensors[up].shape[0] == 2 * cfg.intermediate_size:
+        I = cfg.intermediate_size
+        src.update(gate=(up, (0, I)), up=(up, (I, 2 * I)))
+    else:
+        raise KeyError(f"layer {layer}: no ffn_gate and ffn_up is not a merged gate+up")
+    return src
 
 
 # Shapes named by the benchmark configs.

@@ -26,7 +26,7 @@ from typing import Callable, Iterable, List, Optional, Sequence
 import torch
 
 from .. import _native as N
-from .config import TransformerConfig
+from .config import TransformerConfig, layer_matrix_sources
 from .gguf import GGUFReader
 from .gguf_quant import GGMLType, dequantize, quantize
 
@@ -264,10 +264,21 @@ class GGUFModel:
         ob0, ob1 = rk * hq * d // 256, (rk + 1) * hq * d // 256
         self.local_heads, self.local_kv_heads, self.local_inter = hq, hkv, (fb1 - fb0) * 256
 
-        def mat(name, rows=None, kblocks=None, bias_name=None):
+        def mat(name, rows=None, kblocks=None, bias_name=None, base=None):
+            """``base=(r0, r1)``: the matrix is rows r0..r1 of a merged tensor (phi-3 attn_qkv / gate+up); ``rows`` then
+            counts from r0, and a bias comes from the merged tensor's bias."""
             ti = r.tensors[name]
             bias = r.load(bias_name) if bias_name and r.has_tensor(bias_name) else None
-            pw = pack_weight(r.raw(name), ti.qtype, ti.shape[-1], dev, rows, kblocks, bias)
+            if base is None:
+                pw = pack_weight(r.raw(name), ti.qtype, ti.shape[-1], dev, rows, kblocks, bias)
+            else:
+                merged_bias = name[:-len("weight")] + "bias"
+                if r.has_tensor(merged_bias):
+                    bias = r.load(merged_bias)[base[0]:base[1]]
+                lo, hi = rows if rows is not None else (0, base[1] - base[0])
+                pw = pack_weight(r.raw(name), ti.qtype, ti.shape[-1], dev, (base[0] + lo, base[0] + hi), kblocks, None)
+                if bias is not None:
+                    pw.bias = bias[lo:hi].to(dev).float().contiguous()
             self.weight_bytes += pw.nbytes
             return pw
 
@@ -290,14 +301,15 @@ class GGUFModel:
         descs = (N.LayerDesc * cfg.num_layers)()
         for i in range(cfg.num_layers):
             p = f"blk.{i}."
+            src = layer_matrix_sources(r, cfg, i)           # separate tensors, or row ranges of merged qkv / gate+up
             L = dict(
-                q=mat(p + "attn_q.weight", rows=(rk * hq * d, (rk + 1) * hq * d), bias_name=p + "attn_q.bias"),
-                k=mat(p + "attn_k.weight", rows=(rk * hkv * d, (rk + 1) * hkv * d), bias_name=p + "attn_k.bias"),
-                v=mat(p + "attn_v.weight", rows=(rk * hkv * d, (rk + 1) * hkv * d), bias_name=p + "attn_v.bias"),
-                o=mat(p + "attn_output.weight", kblocks=(ob0, ob1)),
-                gate=mat(p + "ffn_gate.weight", rows=(fb0 * 256, fb1 * 256)),
-                up=mat(p + "ffn_up.weight", rows=(fb0 * 256, fb1 * 256)),
-                down=mat(p + "ffn_down.weight", kblocks=(fb0, fb1)),
+                q=mat(src["q"][0], rows=(rk * hq * d, (rk + 1) * hq * d), bias_name=p + "attn_q.bias", base=src["q"][1]),
+                k=mat(src["k"][0], rows=(rk * hkv * d, (rk + 1) * hkv * d), bias_name=p + "attn_k.bias", base=src["k"][1]),
+                v=mat(src["v"][0], rows=(rk * hkv * d, (rk + 1) * hkv * d), bias_name=p + "attn_v.bias", base=src["v"][1]),
+                o=mat(src["o"][0], kblocks=(ob0, ob1)),
+                gate=mat(src["gate"][0], rows=(fb0 * 256, fb1 * 256), base=src["gate"][1]),
+                up=mat(src["up"][0], rows=(fb0 * 256, fb1 * 256), base=src["up"][1]),
+                down=mat(src["down"][0], kblocks=(fb0, fb1)),
                 attn_norm=vec(p + "attn_norm.weight"), ffn_norm=vec(p + "ffn_norm.weight"),
                 q_norm=vec(p + "attn_q_norm.weight"), k_norm=vec(p + "attn_k_norm.weight"),
                 post_attn_norm=vec(p + "post_attention_norm.weight"), post_ffn_norm=vec(p + "post_ffw_norm.weight"))

@@ -15,7 +15,7 @@ from typing import List, Optional
 import torch
 import torch.nn.functional as F
 
-from ..io.config import TransformerConfig
+from ..io.config import TransformerConfig, layer_matrix_sources
 from ..io.gguf import GGUFReader
 from ..io.gguf_quant import quantize_activation_q8
 
@@ -45,7 +45,7 @@ def rope_tables(cfg: TransformerConfig, max_pos: int, device="cpu", freq_base: O
         mscale = 0.1 * math.log(cfg.yarn_factor) + 1.0
     elif cfg.rope_scale != 1.0:
         inv_freq = inv_freq / cfg.rope_scale
-    factors = cfg.rope_factors_short
+    factors = cfg.rope_factors_for(max_pos)          # phi-3 LongRoPE: short or long factors by sequence length
     if factors is not None:
         inv_freq = inv_freq / torch.tensor(factors, dtype=torch.float64)
     pos = torch.arange(max_pos, dtype=torch.float64)
@@ -85,8 +85,12 @@ class OracleModel:
         self.layers = []
         for i in range(cfg.num_layers):
             p = f"blk.{i}."
-            L = {k: ld(p + k + ".weight") for k in
-                 ("attn_norm", "attn_q", "attn_k", "attn_v", "attn_output", "ffn_norm", "ffn_gate", "ffn_up", "ffn_down")}
+            L = {k: ld(p + k + ".weight") for k in ("attn_norm", "ffn_norm")}
+            names = {"q": "attn_q", "k": "attn_k", "v": "attn_v", "o": "attn_output", "gate": "ffn_gate", "up": "ffn_up",
+                     "down": "ffn_down"}
+            for key, (tname, rows) in layer_matrix_sources(r, cfg, i).items():      # merged qkv / gate+up are row ranges
+                w = ld(tname)
+                L[names[key]] = w if rows is None else w[rows[0]:rows[1]]
             for opt in ("attn_q_norm", "attn_k_norm", "post_attention_norm", "post_ffw_norm"):
                 if r.has_tensor(p + opt + ".weight"):
                     L[opt] = ld(p + opt + ".weight")

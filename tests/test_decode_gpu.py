@@ -188,6 +188,26 @@ def test_engine_other_weight_types(tmp_path, q_main, q_more):
     m.close()
 
 
+def test_engine_merged_qkv_gate_up_longrope(tmp_path):
+    """phi-3 style file: Q/K/V and gate/up merged, LongRoPE factors; the engine shards the merged tensors by rows."""
+    from prometorch_b200.io.gguf_model import GGUFModel
+    from prometorch_b200.models.gguf_oracle import OracleModel
+    cfg = tiny_qwen3_config(layers=2, hidden=512, heads=8, kv_heads=2, inter=1024, vocab=1000)
+    p = str(tmp_path / "phi.gguf")
+    write_synthetic_gguf(p, cfg, seed=8, device="cuda", std=0.05, merged=True,
+                         rope_factors=([1.0 + 0.02 * i for i in range(64)], [3.0] * 64), rope_orig_ctx=4096)
+    m = GGUFModel(p, max_seq=512, want_logits=True)
+    o = OracleModel(p, device="cuda", max_seq=512, emulate_q8=True)
+    for pos, t in enumerate([3, 77, 500, 999, 12, 64]):
+        nxt = m.forward_decode(t, pos)
+        lg = m.logits_view().clone()
+        cos = torch.nn.functional.cosine_similarity(lg, o.forward([t])[0], dim=0)
+        assert cos > 0.9995, (pos, float(cos))
+        assert nxt == int(lg.argmax())
+    m.check_status()
+    m.close()
+
+
 def test_engine_scripted_equals_stepped(tiny_model):
     from prometorch_b200.io.gguf_model import GGUFModel
     m = GGUFModel(tiny_model, max_seq=512)

@@ -235,3 +235,48 @@ def test_q2k_q3k_dequant_follow_ggml_order():
         for r in range(3):
             want = scalar(raw[r, :nbytes].tobytes()) + scalar(raw[r, nbytes:].tobytes())
             assert torch.allclose(got[r], torch.tensor(want, dtype=torch.float32), atol=1e-6), (qt, r)
+
+
+def test_merged_qkv_and_gate_up_and_longrope(tmp_path):
+    """A phi-3 style file (attn_qkv, ffn_up of twice the FFN width, LongRoPE factor tensors) decodes like the same
+    weights stored as separate tensors, and the factor set follows the sequence length."""
+    import torch
+    from prometorch_b200.io.config import TransformerConfig, tiny_qwen3_config
+    from prometorch_b200.io.gguf import GGMLType, GGUFReader, GGUFWriter
+    from prometorch_b200.io.synthetic import write_synthetic_gguf
+    from prometorch_b200.models.gguf_oracle import OracleModel, rope_tables
+    cfg = tiny_qwen3_config(layers=2, hidden=256, heads=4, kv_heads=2, inter=512, vocab=300, head_dim=64)
+    merged = str(tmp_path / "merged.gguf")
+    short = [1.0 + 0.01 * i for i in range(32)]
+    long = [2.0 + 0.1 * i for i in range(32)]
+    write_synthetic_gguf(merged, cfg, seed=2, device="cpu", merged=True, rope_factors=(short, long), rope_orig_ctx=64)
+    r = GGUFReader(merged)
+    c = TransformerConfig.from_gguf(r)
+    assert c.rope_orig_ctx == 64 and c.rope_factors_for(64) == pytest.approx(short) and c.rope_factors_for(65) == pytest.approx(long)
+    cos_s, _ = rope_tables(c, 64)
+    cos_l, _ = rope_tables(c, 128)
+    assert not torch.allclose(cos_s[:64], cos_l[:64])
+    # the same bytes, split into separate tensors
+    split = str(tmp_path / "split.gguf")
+    w = GGUFWriter(split)
+    for k, v in r.metadata.items():
+        if not k.startswith("general.alignment"):
+            w.add(k, v)
+    Q, KV, I = c.q_dim, c.kv_dim, c.intermediate_size
+    for name, ti in r.tensors.items():
+        raw = r.raw(name).clone()
+        if name.endswith("attn_qkv.weight"):
+            p = name[:-len("attn_qkv.weight")]
+            for part, (a, b) in (("attn_q", (0, Q)), ("attn_k", (Q, Q + KV)), ("attn_v", (Q + KV, Q + 2 * KV))):
+                w.add_tensor(p + part + ".weight", (b - a, ti.shape[-1]), ti.qtype, (lambda x=raw[a:b].contiguous(): x))
+        elif name.endswith("ffn_up.weight"):
+            p = name[:-len("ffn_up.weight")]
+            w.add_tensor(p + "ffn_gate.weight", (I, ti.shape[-1]), ti.qtype, (lambda x=raw[:I].contiguous(): x))
+            w.add_tensor(p + "ffn_up.weight", (I, ti.shape[-1]), ti.qtype, (lambda x=raw[I:].contiguous(): x))
+        else:
+            w.add_tensor(name, ti.shape, ti.qtype, (lambda x=raw: x))
+    w.write()
+    toks = [5, 17, 200, 31, 8]
+    a = OracleModel(merged, max_seq=64).forward(toks)
+    b = OracleModel(split, max_seq=64).forward(toks)
+    assert torch.equal(a, b)
