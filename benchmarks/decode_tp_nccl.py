@@ -71,6 +71,16 @@ class NcclTokenGraph:
             for _ in range(n):
                 self.graph.replay()
 
+    def release(self):
+        """Drop the captured graph.  It holds NCCL kernels: the communicator must not be torn down while it exists
+        (destroying the process group first blocks forever)."""
+        import gc
+        import torch
+        self.m.stream.synchronize()
+        self.graph = None
+        gc.collect()
+        torch.cuda.synchronize()
+
 
 def timed(model, run, dist, dev, prompt, warmup, steps, repeats):
     """tok/s of `steps` decode steps after the prompt and `warmup` more, median of `repeats` regions, max over ranks."""
@@ -156,6 +166,7 @@ def main():
         tg.capture()
         out["nccl_tok_s"], ids["nccl"] = timed(m, tg.run, dist, dev, prompt, args.warmup, args.steps, args.repeats)
         out["nccl_tok_s"] = round(out["nccl_tok_s"], 1)
+        tg.release()
         m.close()
     if len(ids) == 2:
         a, b = ids["fused"], ids["nccl"]
@@ -169,7 +180,11 @@ def main():
     if rank == 0:
         print(json.dumps(out), flush=True)
     dist.barrier()
-    dist.destroy_process_group()
+    torch.cuda.synchronize()
+    sys.stdout.flush()
+    # leave without tearing the communicator down: a process that captured NCCL kernels into a graph has been seen to block
+    # in the teardown even after the graph was released
+    os._exit(0)
 
 
 if __name__ == "__main__":

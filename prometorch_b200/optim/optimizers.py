@@ -25,6 +25,8 @@ __all__ = ["Optimizer", "SGD", "Adam", "AdamW", "RMSprop", "Lion", "SophiaG", "S
 
 (OPT_SGD, OPT_ADAM, OPT_ADAMW, OPT_RMSPROP, OPT_LION, OPT_SOPHIA, OPT_NADAM, OPT_RADAM, OPT_ADAGRAD, OPT_ADADELTA,
  OPT_ADAMAX, OPT_ASGD, OPT_LAMB) = range(13)
+OPT_ADAMKILLER = 13      # multi-launch, see AdamKiller._fused_step
+OPT_ADAFACTOR = 14       # per-parameter launches, see Adafactor._fused_step
 
 
 @N.register_decls
@@ -40,6 +42,10 @@ def _decls(L):
     L.ptb_multi_tensor_scale.restype = ci
     L.ptb_multi_tensor_lamb.argtypes = [vp, vp, ci, vp, ci, ci, C.POINTER(cf), vp, vp, vp, vp, vp]
     L.ptb_multi_tensor_lamb.restype = ci
+    L.ptb_multi_tensor_adamkiller.argtypes = [vp, vp, vp, ci, vp, ci, ci, C.POINTER(cf), vp, vp, vp, vp, vp]
+    L.ptb_multi_tensor_adamkiller.restype = ci
+    L.ptb_adafactor_step.argtypes = [vp, vp, ci, vp, vp, vp, vp, vp, ci, ci, C.POINTER(cf), vp, vp, vp, vp, vp]
+    L.ptb_adafactor_step.restype = ci
 
 
 def ParamGroup(params, **overrides) -> dict:
@@ -553,11 +559,55 @@ class LAMB(Optimizer):
 
 
 class Adafactor(Optimizer):
+    """Factored second moments (torch/optim/adafactor.h).  On CUDA a matrix or vector parameter steps in seven small
+    launches (row sums and weight norm, column sums, the fold that advances both vectors and sets the step size, the norm
+    of the update, its clip factor, apply) with no value coming back to the host; parameters of more than two
+    dimensions take the tensor program."""
+
+    kind = OPT_ADAFACTOR
+
     def __init__(self, params, lr=0.0, eps1=1e-30, eps2=1e-3, clip_threshold=1.0, decay_rate=-0.8, beta1=0.0,
-                 weight_decay=0.0, scale_parameter=True, relative_step=True, warmup_init=False):
+                 weight_decay=0.0, scale_parameter=True, relative_step=True, warmup_init=False, fused=None):
         super().__init__(params, dict(lr=lr, eps1=eps1, eps2=eps2, clip_threshold=clip_threshold, decay_rate=decay_rate,
                                       beta1=beta1, weight_decay=weight_decay, scale_parameter=scale_parameter,
-                                      relative_step=relative_step, warmup_init=warmup_init))
+                                      relative_step=relative_step, warmup_init=warmup_init), fused)
+
+    def _fused_step(self, key, ps, h, bf16):
+        lib = N.lib()
+        dev = ps[0].device
+        group = next(g for g in self.param_groups if any(q is ps[0] for q in g["params"]))
+        t = h[0]
+        lr_t = group["lr"]
+        if group["relative_step"] or lr_t <= 0:
+            lr_t = min(1e-6 * t if group["warmup_init"] else 1e-2, 1 / math.sqrt(t))
+        hh = [lr_t, group["eps1"], group["eps2"], group["clip_threshold"], 1 - t ** group["decay_rate"], group["beta1"],
+              group["weight_decay"], float(group["scale_parameter"])]
+        harr = (C.c_float * 16)(*(hh + [0.0] * (16 - len(hh))))
+        st = torch.cuda.current_stream(dev).cuda_stream
+        def scratch_floats(p):          # row sums + column sums per split of 256 rows + two partial-sum arrays
+            rows = p.shape[0] if p.dim() == 2 else 1
+            return rows + (rows + 255) // 256 * p.shape[-1] + 2 * 592
+        need = max((scratch_floats(p) for p in ps if 1 <= p.dim() <= 2), default=0)
+        if need and (getattr(self, "_af_scratch", None) is None or self._af_scratch.numel() < need):
+            self._af_scratch = torch.empty(need, device=dev)
+        for p in ps:
+            s_ = self.state[p]
+            g = self._grad(p)
+            if p.dim() > 2 or p.dim() == 0:
+                gg = g.float() if g.dtype != p.dtype else g
+                if self.grad_scale is not None:
+                    gg = gg * self.grad_scale
+                self._update(p, gg, s_, h, group)
+                continue
+            if "af_scalars" not in s_:
+                s_["af_scalars"] = torch.zeros(8, device=dev)
+            rows, cols = (p.shape[0], p.shape[1]) if p.dim() == 2 else (1, p.numel())
+            fact = p.dim() == 2
+            N.check(lib.ptb_adafactor_step(p.data_ptr(), g.data_ptr(), int(bf16), N.ptr(s_["exp_avg_sq_row"]) if fact else None,
+                                           N.ptr(s_["exp_avg_sq_col"]) if fact else None, None if fact else N.ptr(s_["exp_avg_sq"]),
+                                           N.ptr(s_.get("exp_avg")), N.ptr(self.lowp_params.get(id(p))), rows, cols, harr,
+                                           N.ptr(self.grad_scale), N.ptr(self.skip_flag), self._af_scratch.data_ptr(),
+                                           s_["af_scalars"].data_ptr(), st), "adafactor_step")
 
     def _init_state(self, p, group):
         st = {}
@@ -610,14 +660,51 @@ class AdamKiller(Optimizer):
     """Curvature-adaptive momentum, per-layer trust ratio, gradient lookahead and update clipping
     (torch/optim/adamkiller.h:29-62 for the options, :92-340 for the rule)."""
 
+    kind = OPT_ADAMKILLER
+
     def __init__(self, params, lr=1e-3, beta1_min=0.7, beta1_max=0.95, beta2=0.999, eps=1e-8, weight_decay=0.01,
                  use_adaptive_momentum=True, use_per_layer_lr=True, use_gradient_prediction=True, use_warm_restarts=False,
-                 restart_period=1000, max_grad_norm=1.0, lr_scale_min=0.5, lr_scale_max=2.0):
+                 restart_period=1000, max_grad_norm=1.0, lr_scale_min=0.5, lr_scale_max=2.0, fused=None):
         super().__init__(params, dict(lr=lr, beta1_min=beta1_min, beta1_max=beta1_max, beta2=beta2, eps=eps,
                                       weight_decay=weight_decay, use_adaptive_momentum=use_adaptive_momentum,
                                       use_per_layer_lr=use_per_layer_lr, use_gradient_prediction=use_gradient_prediction,
                                       use_warm_restarts=use_warm_restarts, restart_period=restart_period,
-                                      max_grad_norm=max_grad_norm, lr_scale_min=lr_scale_min, lr_scale_max=lr_scale_max))
+                                      max_grad_norm=max_grad_norm, lr_scale_min=lr_scale_min, lr_scale_max=lr_scale_max), fused)
+
+    def _fused_step(self, key, ps, h, bf16):
+        """Four element-wise launches over the whole group with a one-warp-per-tensor fold between them (per-tensor
+        clipping, momentum coefficient, step size and update cap are formed on the device)."""
+        lib = N.lib()
+        dev = ps[0].device
+        o = next(g for g in self.param_groups if any(q is ps[0] for q in g["params"]))
+        t = int(h[0])
+        has_prev = all("prev_grad" in self.state[p] for p in ps)
+        for p in ps:
+            s_ = self.state[p]
+            if "prev_grad" not in s_:
+                s_["prev_grad"] = torch.zeros_like(p)
+            if "ak_scratch" not in s_:
+                s_["ak_scratch"] = torch.empty_like(p)
+        tab_a = self._tables.setdefault(key, TensorTable())
+        tab_b = self._tables.setdefault(("b", key), TensorTable())
+        grads = [self._grad(p) for p in ps]
+        lowp = [self.lowp_params.get(id(p)) for p in ps]
+        tab_a.build(ps, grads, [(self.state[p]["m"], self.state[p]["v"], None) for p in ps], lowp, dev)
+        tab_b.build(ps, grads, [(self.state[p]["prev_grad"], self.state[p].get("grad_diff_ema"), self.state[p]["ak_scratch"]) for p in ps],
+                    [None] * len(ps), dev)
+        if getattr(tab_a, "ak_partial", None) is None or tab_a.ak_partial.numel() < 3 * tab_a.n_chunks:
+            tab_a.ak_partial = torch.empty(3 * max(tab_a.n_chunks, 1), device=dev)
+            tab_a.ak_scalars = torch.zeros(len(ps), 8, device=dev)
+        restart = bool(o["use_warm_restarts"] and t % o["restart_period"] == 0)
+        hh = [o["lr"], o["beta1_min"], o["beta1_max"], o["beta2"], o["eps"], o["weight_decay"], float(o["use_adaptive_momentum"]),
+              float(o["use_per_layer_lr"]), float(o["use_gradient_prediction"]), float(restart), o["max_grad_norm"], o["lr_scale_min"],
+              o["lr_scale_max"], float(t), float(has_prev)]
+        harr = (C.c_float * 16)(*(hh + [0.0] * (16 - len(hh))))
+        st = torch.cuda.current_stream(dev).cuda_stream
+        N.check(lib.ptb_multi_tensor_adamkiller(tab_a.rows.data_ptr(), tab_b.rows.data_ptr(), tab_a.chunks.data_ptr(), tab_a.n_chunks,
+                                                tab_a.chunk_start.data_ptr(), len(ps), int(bf16), harr, N.ptr(self.grad_scale),
+                                                N.ptr(self.skip_flag), tab_a.ak_partial.data_ptr(), tab_a.ak_scalars.data_ptr(), st),
+                "multi_tensor_adamkiller")
 
     def _init_state(self, p, group):
         st = {"m": torch.zeros_like(p), "v": torch.zeros_like(p)}

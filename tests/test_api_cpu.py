@@ -377,3 +377,44 @@ def test_reference_name_lists_resolve():
     par = "TPConfig ColumnParallelLinear RowParallelLinear Pipeline tp_all_gather tp_all_reduce_sum tp_barrier".split()
     missing = [n for n in par if not hasattr(pt.nn.parallel, n)]
     assert not missing, missing
+
+
+def test_collective_metrics_bytes_and_roofline(tmp_path):
+    """Bytes on the wire per collective, bus bandwidth and the roofline fraction of a fused compute+collective step."""
+    import json
+    from prometorch_b200.utils.metrics import MetricsWriter, measured_peaks, wire_bytes
+    assert wire_bytes("all_reduce", 1 << 30, 8) == 2 * (1 << 30) * 7 / 8
+    assert wire_bytes("reduce_scatter", 800, 4) == 600 and wire_bytes("all_gather", 800, 4) == 600
+    assert wire_bytes("all_reduce", 100, 1) == 0
+    w = MetricsWriter(str(tmp_path / "m.jsonl"))
+    rec = w.collective("grad all-reduce", seconds=2e-3, payload_bytes=770e6, world=2)          # 770 MB over 770 GB/s = 1 ms
+    assert rec["fraction"] == pytest.approx(0.5) and rec["gbps_per_direction"] == pytest.approx(385.0)
+    rec = w.collective("gemm + reduce-scatter", seconds=1e-3, payload_bytes=1e6, world=8, kind="reduce_scatter", flops=1.391e12 / 2)
+    assert rec["roofline_seconds"] == pytest.approx(0.5e-3) and rec["fraction"] == pytest.approx(0.5)
+    w.close()
+    lines = [json.loads(l) for l in open(tmp_path / "m.jsonl")]
+    assert [l["name"] for l in lines] == ["grad all-reduce", "gemm + reduce-scatter"]
+    p = tmp_path / "peaks.json"
+    p.write_text(json.dumps({"hbm_gbs": 6000, "bf16_tflops": 1500, "bf16_tflops_sustained": 1300}))
+    assert measured_peaks(str(p)) == {"hbm_bw": 6e12, "flops_burst": 1.5e15, "flops_sustained": 1.3e15}
+
+
+def test_kernels_are_dispatcher_ops():
+    """torch.ops.ptb200.* resolve by schema; gradients flow through an op call (CPU tensors take the plain-math path)."""
+    import torch
+    from prometorch_b200.ops import library
+    library.register()
+    library.register()                                    # idempotent
+    x = torch.randn(4, 32, requires_grad=True)
+    w = torch.randn(32, requires_grad=True)
+    y = torch.ops.ptb200.rms_norm(x, w, 1e-6)
+    ref = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6) * w
+    assert torch.allclose(y, ref, atol=1e-5)
+    y.sum().backward()
+    assert x.grad is not None and w.grad is not None
+    lin = torch.ops.ptb200.linear(torch.randn(3, 32), torch.randn(8, 32), None)
+    assert lin.shape == (3, 8)
+    gu = torch.randn(5, 16)
+    assert torch.allclose(torch.ops.ptb200.swiglu(gu, False), torch.nn.functional.silu(gu[:, :8]) * gu[:, 8:], atol=1e-6)
+    for name in library.SCHEMAS:
+        assert hasattr(torch.ops.ptb200, name)

@@ -280,3 +280,32 @@ def test_merged_qkv_and_gate_up_and_longrope(tmp_path):
     a = OracleModel(merged, max_seq=64).forward(toks)
     b = OracleModel(split, max_seq=64).forward(toks)
     assert torch.equal(a, b)
+
+
+def test_lowrank_output_projection_finds_the_exact_argmax():
+    """A matrix with a decaying spectrum: the exact winner is among the low-rank candidates, so the speculative head
+    returns the full arg-max; sampling stays inside the exact top-k."""
+    import torch
+    from prometorch_b200.io.gguf_quant import GGMLType, dequantize, quantize
+    from prometorch_b200.io.speculative import LowRankOutputProj
+    g = torch.Generator().manual_seed(0)
+    vocab, hidden = 3000, 256
+    A, B = torch.randn(vocab, 48, generator=g), torch.randn(48, hidden, generator=g)
+    W = A @ B / 7 + 0.02 * torch.randn(vocab, hidden, generator=g)
+    raw = quantize(W, GGMLType.Q6_K)
+    Wq = dequantize(raw, GGMLType.Q6_K, hidden)
+    lr = LowRankOutputProj(rank=64, candidate_k=32).init_from_quantized(raw, GGMLType.Q6_K, hidden)
+    assert lr.valid and lr.U.shape == (vocab, 64) and lr.V.shape == (64, hidden)
+    hits = 0
+    for i in range(40):
+        x = torch.randn(hidden, generator=g)
+        want = int((Wq @ x).argmax())
+        got = lr.decode_greedy(x)
+        hits += got == want
+        assert float(lr.last_exact.max()) == pytest.approx(float((Wq @ x)[got]), rel=1e-5)
+        t = lr.decode_sample(x, temperature=0.8, top_k=5, generator=g)
+        assert t in set((Wq @ x)[lr.last_candidates].topk(5).indices.tolist() and lr.last_candidates[lr.last_exact.topk(5).indices].tolist())
+    assert hits >= 38, hits
+    f = LowRankOutputProj(rank=32, candidate_k=16).init_from_float(W)
+    x = torch.randn(hidden, generator=g)
+    assert 0 <= f.decode_greedy(x) < vocab

@@ -21,6 +21,10 @@ CASES = [
     (O.Adamax, dict(lr=2e-3)),
     (O.ASGD, dict(lr=0.05, t0=2)),
     (O.LAMB, dict(lr=1e-2, weight_decay=0.05)),
+    (O.AdamKiller, dict(lr=1e-2, weight_decay=0.02, use_warm_restarts=True, restart_period=3)),
+    (O.AdamKiller, dict(lr=5e-3, use_gradient_prediction=False, use_per_layer_lr=False, max_grad_norm=100.0)),
+    (O.Adafactor, dict()),
+    (O.Adafactor, dict(lr=1e-2, relative_step=False, scale_parameter=False, beta1=0.9, weight_decay=0.01, clip_threshold=0.5)),
 ]
 
 
@@ -49,7 +53,7 @@ def test_fused_matches_tensor_ops(cls, kw, gdtype):
         assert torch.allclose(p, q, atol=3e-6, rtol=2e-5), (cls.__name__, (p - q).abs().max())
     for p, q in zip(a, b):
         for k in oa.state[p]:
-            if k not in ("step", "lamb_update"):
+            if k not in ("step", "lamb_update", "ak_scratch", "af_scalars"):
                 assert torch.allclose(oa.state[p][k], ob.state[q][k], atol=3e-6, rtol=2e-5), (cls.__name__, k)
 
 

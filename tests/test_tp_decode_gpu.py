@@ -20,5 +20,5 @@ def test_tp_decode_matches_single_gpu(tmp_path, world, flow):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", PTB_DECODE_FLOW=flow)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
            "127.0.0.1", "--master-port", str(29600 + os.getpid() % 300), worker, str(tmp_path / "tp.gguf")]
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
     assert r.returncode == 0 and "TP_DECODE_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]

@@ -10,6 +10,10 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+
+    def stage(msg):                     # progress on stderr: shows where a run stopped if it has to be killed
+        if rank == 0:
+            print(f"[tp worker] {msg}", file=sys.stderr, flush=True)
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
@@ -27,6 +31,7 @@ def main():
     ref = GGUFModel(path, device=str(dev), max_seq=256) if rank == 0 else None
     toks = [7, 99, 1500, 3, 2047, 640, 12, 12, 800, 77, 5, 1023]
     ok = True
+    stage("models loaded; stepped decode against the 1-GPU engine")
     for pos, t in enumerate(toks):
         nxt = tp.forward_decode(t, pos)
         if rank == 0:
@@ -41,6 +46,7 @@ def main():
         if len({int(x) for x in lst}) != 1:
             ok = False
             print(f"pos {pos}: ranks disagree on the token: {[int(x) for x in lst]}", flush=True)
+    stage("scripted run")
     # a scripted run must agree across ranks as well
     out = tp.run_script(toks[:4], 16)
     got = torch.tensor(out, device=dev)
@@ -51,6 +57,7 @@ def main():
         print("scripted tokens differ across ranks", flush=True)
     tp.check_status()
     # batched prompt pass under tensor parallelism (collective): the cache it writes must continue like the stepped one
+    stage("batched prefill under tensor parallelism")
     hid_step = None
     for pos, t in enumerate(toks):
         tp.forward_decode(t, pos)
@@ -66,6 +73,7 @@ def main():
             ok = False
             print(f"prefill + decode against stepped decode: hidden cosine {cos}", flush=True)
     # the NCCL-only arm (external all-reduce flow) runs the same shards and must land on the same hidden state
+    stage("external all-reduce flow (NCCL arm)")
     import ctypes as C
     from benchmarks.decode_tp_nccl import NcclTokenGraph
     from prometorch_b200 import _native as N
@@ -74,6 +82,7 @@ def main():
     del os.environ["PTB_DECODE_FLOW"]
     tg = NcclTokenGraph(ext, dist, world)
     tg.capture()
+    stage("NCCL token graph captured")
     arr = (C.c_int * len(toks))(*toks)
     N.check(ext._lib.ptb_engine_begin_script(ext._engine, arr, len(toks), 0), "begin_script")
     tg.run(len(toks))
@@ -87,6 +96,8 @@ def main():
     if cos < 0.9995 or any(not torch.equal(lst[0], x) for x in lst):
         ok = False
         print(f"external all-reduce flow: hidden cosine {cos}, ids {[int(x) for x in lst]}", flush=True)
+    stage("NCCL arm checked; teardown")
+    tg.release()                                         # the graph holds NCCL kernels: drop it before any teardown
     ext.close()
     dist.barrier()
     symm.check_canaries()                                # the all-reduce slots stayed inside their buffers
@@ -96,10 +107,14 @@ def main():
     if ref is not None:
         ref.close()
     dist.barrier()
-    dist.destroy_process_group()
+    torch.cuda.synchronize()
     if rank == 0:
         print("TP_DECODE_OK" if int(flag) == 1 else "TP_DECODE_FAIL", flush=True)
-    sys.exit(0 if int(flag) == 1 else 1)
+    sys.stdout.flush()
+    sys.stderr.flush()
+    # no destroy_process_group: this process captured NCCL kernels into a CUDA graph, and tearing the communicator down
+    # afterwards has been seen to block
+    os._exit(0 if int(flag) == 1 else 1)
 
 
 if __name__ == "__main__":
