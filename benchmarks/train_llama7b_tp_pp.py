@@ -90,7 +90,7 @@ def main():
             q, k = K.rope(q, cos, sin, True, 0), K.rope(k, cos, sin, True, 0)
             att = flash_attention(q, k, v, causal=True).reshape(T, hl * d)
             h, x = self.mlp_norm(self.o(att), x)             # residual add fused into the norm
-            return x + self.down(K.swiglu(self.gate_up(h), False))
+            return self.down(K.swiglu(self.gate_up(h), False), residual=x)     # the add rides in the slot-sum kernel
 
     class Stage(nn.Module):
         def __init__(self, first, last, n_layers):

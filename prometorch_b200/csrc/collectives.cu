@@ -20,6 +20,7 @@
 // its peers and resets its ticket, so the channel can be used again, and returns.
 #include "common.cuh"
 #include <stdlib.h>
+#include <algorithm>
 
 namespace ptb {
 
@@ -270,6 +271,85 @@ PTB_API int ptb_ddp_allreduce_master(void* const* bufs, void* const* master_bufs
     PeerSet P;
     fill(P, bufs, flags, rank, world, master_bufs);
     ddp_allreduce_kernel<true, true><<<n_ctas, COLL_THREADS, 0, st>>>(P, numel / 8, scale, seq, ticket, status);
+    PTB_CUDA_OK(cudaGetLastError());
+    return 0;
+}
+
+// Reduce-scatter into an fp32 accumulator: slice `rank` of every peer's bf16 gradient buffer is summed in fp32, scaled and
+// ADDED to `acc` (this rank's 1/world of the gradient).  The buffers can be reused as soon as the kernel is over (its
+// closing barrier says every rank has read), which is what a gradient window shared by all layers needs; the optimizer
+// then steps from `acc` once per iteration.
+__global__ void __launch_bounds__(COLL_THREADS) fsdp_rs_accum_kernel(const __grid_constant__ PeerSet P, float* __restrict__ acc, float scale,
+                                                                   long long n_vec, uint32_t seq, unsigned* ticket, int* status) {
+    const bool ok = barrier_in(P, seq, status);
+    long long v0, v1;
+    slice_of(n_vec, P.rank, P.world, v0, v1);
+    if (!ok) v1 = v0;
+    for (long long v = v0 + (long long)blockIdx.x * COLL_THREADS + threadIdx.x; v < v1; v += (long long)gridDim.x * COLL_THREADS) {
+        float g[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) g[j] = 0.f;
+        uint4 in[8];
+#pragma unroll
+        for (int p = 0; p < 8; ++p)
+            if (p < P.world) in[p] = __ldcg(reinterpret_cast<const uint4*>(P.buf[p]) + v);
+#pragma unroll
+        for (int p = 0; p < 8; ++p) {
+            if (p < P.world) {
+                float f[8];
+                bf16x8_to_f32(in[p], f);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) g[j] += f[j];
+            }
+        }
+        float* a = acc + (v - v0) * 8;
+        float4 a0 = *reinterpret_cast<float4*>(a), a1 = *reinterpret_cast<float4*>(a + 4);
+        a0.x += g[0] * scale; a0.y += g[1] * scale; a0.z += g[2] * scale; a0.w += g[3] * scale;
+        a1.x += g[4] * scale; a1.y += g[5] * scale; a1.z += g[6] * scale; a1.w += g[7] * scale;
+        *reinterpret_cast<float4*>(a) = a0;
+        *reinterpret_cast<float4*>(a + 4) = a1;
+    }
+    barrier_out(P, seq, ticket, status, ok);
+}
+
+// Owner side of the row-parallel GEMM's scatter-store epilogue: the `world` bf16 partial tiles that the ranks stored into this
+// rank's slots are summed in fp32 in one pass (optionally on top of a residual) and written once as bf16.
+__global__ void __launch_bounds__(256) slot_sum_kernel(const uint4* __restrict__ parts, int world, long long slot_vec,
+                                                       const uint4* __restrict__ resid, uint4* __restrict__ out) {
+    for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < slot_vec; v += (long long)gridDim.x * blockDim.x) {
+        float acc[8];
+        if (resid) bf16x8_to_f32(resid[v], acc);
+        else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        }
+        for (int p = 0; p < world; ++p) {
+            float f[8];
+            bf16x8_to_f32(parts[(long long)p * slot_vec + v], f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] += f[j];
+        }
+        out[v] = f32_to_bf16x8(acc);
+    }
+}
+// parts: [world][slot_elems] bf16 (local memory); resid (optional) and out: [slot_elems] bf16.
+PTB_API int ptb_slot_sum(const void* parts, int world, long long slot_elems, const void* resid, void* out, cudaStream_t st) {
+    if (world < 1 || slot_elems % 8) { ptb_set_error("slot sum: %lld elements per slot must be a multiple of 8", slot_elems); return -1; }
+    const long long nv = slot_elems / 8;
+    if (nv == 0) return 0;
+    const int blocks = (int)std::min<long long>((nv + 255) / 256, 148 * 8);
+    slot_sum_kernel<<<blocks, 256, 0, st>>>((const uint4*)parts, world, nv, (const uint4*)resid, (uint4*)out);
+    PTB_CUDA_OK(cudaGetLastError());
+    return 0;
+}
+
+// numel: elements of the full gradient (a multiple of 8 * world); acc: numel / world floats.
+PTB_API int ptb_fsdp_rs_accum(void* const* bufs, void* const* flags, int rank, int world, long long numel, float* acc, float scale,
+                              unsigned seq, unsigned* ticket, int* status, int n_ctas, cudaStream_t st) {
+    if (world < 1 || world > 8 || numel % (8LL * world)) { ptb_set_error("fsdp accumulate: length %lld must be a multiple of 8*world", numel); return -1; }
+    PeerSet P;
+    fill(P, bufs, flags, rank, world);
+    fsdp_rs_accum_kernel<<<n_ctas, COLL_THREADS, 0, st>>>(P, acc, scale, numel / 8, seq, ticket, status);
     PTB_CUDA_OK(cudaGetLastError());
     return 0;
 }

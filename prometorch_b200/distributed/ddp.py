@@ -39,6 +39,8 @@ def _decls(L):
     L.ptb_ddp_allreduce.restype = ci
     L.ptb_fsdp_rs_adamw.argtypes = [pp, pp, ci, ci, ll, vp, vp, vp, vp, cf, cf, cf, cf, cf, ci, cf, cu, vp, vp, ci, vp]
     L.ptb_fsdp_rs_adamw.restype = ci
+    L.ptb_fsdp_rs_accum.argtypes = [pp, pp, ci, ci, ll, vp, cf, cu, vp, vp, ci, vp]
+    L.ptb_fsdp_rs_accum.restype = ci
     L.ptb_allgather.argtypes = [pp, pp, ci, ci, vp, ll, cu, vp, vp, ci, vp]
     L.ptb_allgather.restype = ci
     L.ptb_peer_barrier.argtypes = [pp, ci, ci, cu, vp, vp, vp]

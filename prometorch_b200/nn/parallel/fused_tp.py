@@ -29,6 +29,8 @@ def _decls(L):
     pp = C.POINTER(C.c_void_p)
     L.ptb_gemm_bf16_ex.argtypes = [pp, ci, ci, ll, ci, pp, ci, ci, ll, ci, vp, ll, pp, ci, ci, ci, ci, ci, vp, ci, vp, ci, vp, vp, vp]
     L.ptb_gemm_bf16_ex.restype = ci
+    L.ptb_slot_sum.argtypes = [vp, ci, ll, vp, vp, vp]
+    L.ptb_slot_sum.restype = ci
 
 
 class Staging(C.Structure):
@@ -217,7 +219,7 @@ class _RowSP(torch.autograd.Function):
     """y[tokens_local, out] = reduce_scatter_tokens(z @ Wr^T)."""
 
     @staticmethod
-    def forward(ctx, z, w, tp, key):
+    def forward(ctx, z, w, tp, key, resid=None):
         nfull, Kl = z.shape
         W = tp.world_size
         n, out = nfull // W, w.shape[0]
@@ -231,7 +233,14 @@ class _RowSP(torch.autograd.Function):
         site.barrier()                                   # every rank's partial tiles have landed
         ctx.save_for_backward(z, w)
         ctx.site, ctx.tp, ctx.n = site, tp, n
-        return parts.sum(0, dtype=torch.float32).to(torch.bfloat16)
+        ctx.has_resid = resid is not None
+        # the owner's sum over the ranks' slots (fp32 accumulation, one pass, the residual folded in when given)
+        y = torch.empty(n, out, dtype=torch.bfloat16, device=z.device)
+        if resid is not None:
+            resid = resid.reshape(n, out).contiguous()
+        N.check(N.lib().ptb_slot_sum(parts.data_ptr(), W, n * out, N.ptr(resid), y.data_ptr(),
+                                     torch.cuda.current_stream(z.device).cuda_stream), "slot_sum")
+        return y
 
     @staticmethod
     def backward(ctx, dy):
@@ -244,7 +253,7 @@ class _RowSP(torch.autograd.Function):
         # dWr[out, in/W] = gather(dY)^T Z : A = gathered dY (now local) read MN-major, B = Z MN-major
         dw = gemm_ex([full.data_ptr()], 0, out, True, [z.data_ptr()], 0, z.stride(0), True, out, w.shape[1], n * W, dev)
         site.barrier()                                   # peers are done reading my dY before it is reused
-        return dz, dw, None, None
+        return dz, dw, None, None, (dy if ctx.has_resid else None)
 
 
 _counter = [0]
@@ -257,8 +266,11 @@ def column_sp_forward(x, w, bias, tp, key=None):
     return fused_linear(_GatherTokens.apply(x, tp), w, bias)
 
 
-def row_sp_forward(z, w, tp, key=None):
-    if _fused_ok(z, tp) and (z.shape[0] // tp.world_size) % 128 == 0:
-        return _RowSP.apply(z, w, tp, key if key is not None else id(w))
+def row_sp_forward(z, w, tp, key=None, resid=None):
+    """``resid`` (optional, ``[tokens_local, out]`` bf16): returned value is ``resid + reduce_scatter(z @ w^T)``, the
+    addition done by the kernel that sums the ranks' partial tiles."""
+    if _fused_ok(z, tp) and (z.shape[0] // tp.world_size) % 128 == 0 and (z.shape[0] // tp.world_size * w.shape[0]) % 8 == 0:
+        return _RowSP.apply(z, w, tp, key if key is not None else id(w), resid)
     from .tensor_parallel import _ScatterTokens
-    return _ScatterTokens.apply(fused_linear(z, w, None), tp)
+    y = _ScatterTokens.apply(fused_linear(z, w, None), tp)
+    return y if resid is None else y + resid

@@ -195,17 +195,23 @@ class RowParallelLinear(nn.Module):
             self.weight = nn.Parameter(w[:, r * self.shard:(r + 1) * self.shard].clone().to(device=device, dtype=dtype))
             self.bias = nn.Parameter(b.clone().to(device=device, dtype=dtype)) if bias else None       # added once, after the reduction
 
-    def forward(self, x):
+    def forward(self, x, residual=None):
+        """``residual`` (optional): returns ``residual + layer(x)``; on the fused sequence-parallel path the addition is
+        part of the kernel that sums the ranks' partial tiles."""
         tp = self.tp
         if not self.input_is_parallel and tp.world_size > 1:
             x = x[..., tp.rank * self.shard:(tp.rank + 1) * self.shard]
         if self.sequence_parallel and tp.world_size > 1:
             from .fused_tp import row_sp_forward
-            y = row_sp_forward(x.reshape(-1, x.shape[-1]), self.weight, tp)              # [tokens_local, out]
+            y = row_sp_forward(x.reshape(-1, x.shape[-1]), self.weight, tp, resid=residual)      # [tokens_local, out]
+            if residual is not None:
+                y = y.view(residual.shape)
         else:
             y = fused_linear(x, self.weight, None)
             if tp.world_size > 1:
                 y = _ReduceFromRegion.apply(y, tp)
+            if residual is not None:
+                y = y + residual
         return y + self.bias if self.bias is not None else y
 
     def extra_repr(self):

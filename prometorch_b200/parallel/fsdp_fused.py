@@ -20,6 +20,9 @@ AdamW to the master shard, writing the new bf16 shard in the same pass (reduce-s
 sharded optimizer).  Small replicated parameters (norm weights, embeddings) ride in one bucket that is
 all-reduced by the DDP kernel and stepped by the fused multi-tensor AdamW.
 
+``FusedFSDP(window=K)`` trades the per-layer full-size copies for a window of K gathered weights and a few gradient
+slots shared by all layers (:class:`WindowPool`): ZeRO-3 memory, two gathers per step.
+
 Compare the reference: all parameters gathered before forward, never resharded, reduce-scatter by
 reading every rank's full gradient file (torch/distributed/fsdp.h:227-322).
 """
@@ -33,7 +36,7 @@ import torch.nn as nn
 
 from .. import _native as N
 from ..distributed.ddp import PeerChannel
-from ..nn.parallel.fused_tp import _external_staging, gemm_ex, make_staging, peer_shard_views, stage_with_copy_engines
+from ..nn.parallel.fused_tp import Staging, _external_staging, gemm_ex, make_staging, peer_shard_views, stage_with_copy_engines
 from ..optim import AdamW
 
 
@@ -47,8 +50,10 @@ class _ShardedLinearFn(torch.autograd.Function):
         # B = the local full-size buffer; rows owned by peers cross NVLink once per optimizer step: copy engines
         # start bringing them in as soon as the owner's optimizer kernel is done (or stager CTAs of this launch
         # do), and the tile producers of this launch wait on the 128-row block flags, so transfer and math overlap
-        y = gemm_ex([x2.data_ptr()], 0, x2.stride(0), False, [sh.full_ptr], 0, sh.inf, False, x2.shape[0], sh.out, sh.inf, x.device,
-                    stage_b=sh.staging())
+        wptr, stg = sh.weight_operand(forward=True)
+        y = gemm_ex([x2.data_ptr()], 0, x2.stride(0), False, [wptr], 0, sh.inf, False, x2.shape[0], sh.out, sh.inf, x.device,
+                    stage_b=stg)
+        sh.weight_used()
         ctx.save_for_backward(x2)
         ctx.sh, ctx.xshape = sh, x.shape
         return y.view(*x.shape[:-1], sh.out)
@@ -62,19 +67,140 @@ class _ShardedLinearFn(torch.autograd.Function):
             dy2 = dy2.contiguous()
         dev = dy.device
         # dX[M, in] = dY[M, out] W[out, in]: W stored [K=out (row-sharded over ranks), N=in], read N-major
-        dx = gemm_ex([dy2.data_ptr()], 0, dy2.stride(0), False, [sh.full_ptr], 0, sh.inf, True, dy2.shape[0], sh.inf, sh.out, dev,
-                     stage_b=sh.staging())
-        # dW[out, in] += dY^T X into the local full-size gradient buffer
+        wptr, stg = sh.weight_operand(forward=False)
+        dx = gemm_ex([dy2.data_ptr()], 0, dy2.stride(0), False, [wptr], 0, sh.inf, True, dy2.shape[0], sh.inf, sh.out, dev,
+                     stage_b=stg)
+        sh.weight_used()
+        # dW[out, in] (+)= dY^T X into the local full-size gradient buffer, or into a slot of the gradient window, whose
+        # reduce-scatter into this rank's fp32 gradient shard starts right behind it on the reduce stream
+        target, accumulate = sh.grad_target()
         gemm_ex([dy2.data_ptr()], 0, dy2.stride(0), True, [x2.data_ptr()], 0, x2.stride(0), True, sh.out, sh.inf, dy2.shape[0], dev,
-                out=sh.grad_full[:sh.out], accumulate=True)
+                out=target[:sh.out], accumulate=accumulate)
+        sh.grad_written()
         return dx.view(ctx.xshape), None
+
+
+class WindowPool:
+    """Staging shared by all sharded layers of a ``FusedFSDP(window=K)``: ZeRO-3 memory.
+
+    * ``K`` weight slots (plain device memory, each as large as the largest gathered weight).  A layer's weight is
+      gathered into a slot right before the GEMM that reads it (own rows by a local copy, the peers' rows by the copy
+      engines on the side stream, 128-row block flags raised as they land, the GEMM's producer waiting on those
+      flags), the next layer's gather is queued before this layer's GEMM is launched, and a slot is taken over by
+      another layer once the GEMMs that read it are done.  Backward gathers again.
+    * ``G`` gradient slots (symmetric memory, same size).  A layer's dW goes into a slot, and a reduce-scatter kernel
+      on the reduce stream adds slice *r* of every rank's slot into rank *r*'s fp32 gradient shard; the slot is free
+      again when that kernel is over (its closing barrier says every rank has read).
+
+    Per rank this leaves the bf16 shard, the fp32 master / moments / gradient shard (all 1/world of the model) and
+    ``K + G`` layer-sized buffers, instead of a full-size bf16 weight and gradient copy of every layer."""
+
+    def __init__(self, symm, n_weight: int, n_grad: int, status: torch.Tensor):
+        self.symm, self.n_weight, self.n_grad, self.status = symm, max(int(n_weight), 1), max(int(n_grad), 1), status
+        self.layers: List["ShardedLinear"] = []
+        self.wslots: List[dict] = []
+        self.gslots: List[PeerChannel] = []
+        self.g_events: List[Optional[torch.cuda.Event]] = []
+        self._w_next = self._g_next = 0
+        self.reduce_stream = None
+        self.gathers = 0                      # how many times a weight was brought in (tests, metrics)
+
+    def register(self, sl: "ShardedLinear"):
+        sl.index = len(self.layers)
+        self.layers.append(sl)
+
+    def allocate(self):
+        """Called once every layer is registered: the slots take the size of the largest layer."""
+        dev, W = self.symm.device, self.symm.world
+        self.max_numel = max(sl.S * W * sl.inf for sl in self.layers)
+        max_rows = max(sl.S * W for sl in self.layers)
+        for _ in range(self.n_weight):
+            self.wslots.append(dict(buf=torch.empty(self.max_numel, dtype=torch.bfloat16, device=dev),
+                                    flags=torch.zeros((max_rows + 127) // 128, dtype=torch.int32, device=dev), seq=0, owner=None,
+                                    owner_seq=-1, event=None))
+        for _ in range(self.n_grad):
+            self.gslots.append(PeerChannel(self.symm, self.max_numel * 2, status=self.status))
+            self.g_events.append(None)
+        self.reduce_stream = torch.cuda.Stream(device=dev)
+        self.symm.barrier()
+
+    @property
+    def window_bytes(self) -> int:
+        return (self.n_weight + self.n_grad) * self.max_numel * 2
+
+    # ---- weights
+    def _resident(self, sl):
+        for s in self.wslots:
+            if s["owner"] is sl and s["owner_seq"] == sl.stage_seq:
+                return s
+        return None
+
+    def _gather(self, sl) -> dict:
+        dev, W, r, n = self.symm.device, self.symm.world, self.symm.rank, sl.S
+        s = self.wslots[self._w_next]
+        self._w_next = (self._w_next + 1) % len(self.wslots)
+        cur = torch.cuda.current_stream(dev)
+        if s["event"] is not None:
+            cur.wait_event(s["event"])        # the GEMMs that read the slot's previous tenant
+        s["seq"] += 1
+        s["owner"], s["owner_seq"] = sl, sl.stage_seq
+        view = s["buf"][:n * W * sl.inf].view(n * W, sl.inf)
+        view[r * n:(r + 1) * n].copy_(sl.shard)      # own rows: the GEMM does not look at flags for them
+        if W > 1:
+            stage_with_copy_engines(view, sl.peer_views, s["flags"], r, W, n, s["seq"], dev)
+        s["view"] = view
+        self.gathers += 1
+        return s
+
+    def weight(self, sl, forward: bool) -> dict:
+        s = self._resident(sl) or self._gather(sl)
+        # queue the neighbour's gather before this layer's GEMM goes onto the compute stream
+        j = sl.index + (1 if forward else -1)
+        if len(self.wslots) > 1 and 0 <= j < len(self.layers) and self._resident(self.layers[j]) is None:
+            nxt = self.wslots[self._w_next]
+            if nxt is not s:
+                self._gather(self.layers[j])
+        return s
+
+    def used(self, s: dict):
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(self.symm.device))
+        s["event"] = ev
+
+    # ---- gradients
+    def grad_slot(self, sl):
+        i = self._g_next
+        self._g_next = (i + 1) % len(self.gslots)
+        if self.g_events[i] is not None:
+            torch.cuda.current_stream(self.symm.device).wait_event(self.g_events[i])
+        ch = self.gslots[i]
+        W = self.symm.world
+        view = ch.buf.tensor(torch.bfloat16)[:sl.S * W * sl.inf].view(sl.S * W, sl.inf)
+        if sl.out < sl.S * W:
+            view[sl.out:].zero_()             # padding rows take part in the sum
+        return i, view
+
+    def reduce(self, sl, i: int, n_ctas: int = 64):
+        dev = self.symm.device
+        ch = self.gslots[i]
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(dev))
+        rs = self.reduce_stream
+        rs.wait_event(ev)
+        N.check(N.lib().ptb_fsdp_rs_accum(ch.bufs, ch.flag_ptrs, self.symm.rank, self.symm.world, sl.S * self.symm.world * sl.inf,
+                                          sl.gacc.data_ptr(), 1.0, ch.next_seq(), ch.ticket.data_ptr(), ch.status.data_ptr(), n_ctas,
+                                          rs.cuda_stream), "fsdp_rs_accum")
+        done = torch.cuda.Event()
+        done.record(rs)
+        self.g_events[i] = done
 
 
 class ShardedLinear(nn.Module):
     """Drop-in for a bias-free ``nn.Linear`` whose weight lives row-sharded across the ranks."""
 
-    def __init__(self, lin: nn.Linear, symm, pg, status: Optional[torch.Tensor] = None):
+    def __init__(self, lin: nn.Linear, symm, pg, status: Optional[torch.Tensor] = None, pool: Optional[WindowPool] = None):
         super().__init__()
+        self.pool = pool
         if lin.bias is not None:
             raise NotImplementedError("ShardedLinear: bias-free layers only")
         W, r = symm.world, symm.rank
@@ -87,6 +213,22 @@ class ShardedLinear(nn.Module):
         padded[:self.out] = full
         self.master = padded[r * self.S:(r + 1) * self.S].clone().contiguous()
         self.m, self.v = torch.zeros_like(self.master), torch.zeros_like(self.master)
+        self.symm = symm
+        self.stage_seq = 1
+        self.step_count = 0
+        if pool is not None:
+            # window mode: only this rank's shard lives here (in symmetric memory, the peers gather from it) plus the fp32
+            # gradient shard the reduce-scatter kernels add into
+            self.shard_ch = PeerChannel(symm, self.S * self.inf * 2)
+            self.shard = self.shard_ch.buf.tensor(torch.bfloat16)[:self.S * self.inf].view(self.S, self.inf)
+            self.shard.copy_(self.master)
+            self.peer_views = {q: self.shard_ch.buf.tensor(torch.bfloat16, rank=q)[:self.S * self.inf].view(self.S, self.inf)
+                               for q in range(W) if q != r}
+            self.gacc = torch.zeros_like(self.master)
+            self._slot = self._gslot = None
+            pool.register(self)
+            symm.barrier()
+            return
         # full-size symmetric buffer; this rank's shard is rows [r*S, (r+1)*S) of it (what peers read)
         self.shard_ch = PeerChannel(symm, self.S * W * self.inf * 2)
         self.w_full = self.shard_ch.buf.tensor(torch.bfloat16)[:self.S * W * self.inf].view(self.S * W, self.inf)
@@ -95,13 +237,10 @@ class ShardedLinear(nn.Module):
         self.shard.copy_(self.master)
         self.full_ptr = self.shard_ch.buf.peer_ptr(r)
         self.stage_flags = torch.zeros((self.S * W + 127) // 128, dtype=torch.int32, device=dev)
-        self.stage_seq = 1
         self.grad_ch = PeerChannel(symm, self.S * W * self.inf * 2, status=status)
         self.grad_full = self.grad_ch.buf.tensor(torch.bfloat16)[:self.S * W * self.inf].view(self.S * W, self.inf)
         self.grad_full.zero_()
-        self.symm = symm
         self._staged_seq = 0
-        self.step_count = 0
         self._views = None
         symm.barrier()
         self.prefetch()
@@ -110,7 +249,7 @@ class ShardedLinear(nn.Module):
         """Start copying the peers' current shards into the local full-size buffer on the copy stream (the owners'
         shards are final: the optimizer kernel ends with a barrier across the ranks).  The block flags rise as
         the shards land; the first GEMM that reads the weight checks them."""
-        if not _external_staging() or self.symm.world == 1:
+        if self.pool is not None or not _external_staging() or self.symm.world == 1:
             return
         if self._views is None:
             self._views = peer_shard_views(self.shard_ch.buf, self.inf, self.symm.rank, self.symm.world, self.S)
@@ -126,6 +265,38 @@ class ShardedLinear(nn.Module):
         self._staged_seq = self.stage_seq
         return make_staging(self.shard_ch.buf, self.stage_flags, self.symm.rank, self.symm.world, self.S,
                             self.S * self.symm.world, self.inf * 2, self.stage_seq, external=_external_staging())
+
+    # ---- what the GEMMs of the autograd function read and write
+    def weight_operand(self, forward: bool):
+        """(address of the gathered ``[S * world, in]`` bf16 weight, staging request or None)."""
+        if self.pool is None:
+            return self.full_ptr, self.staging()
+        s = self._slot = self.pool.weight(self, forward)
+        W = self.symm.world
+        if W == 1:
+            return s["view"].data_ptr(), None
+        stg = Staging()
+        for q in range(W):
+            stg.peer[q] = s["view"].data_ptr()        # unused: the copy engines bring the rows in (external staging)
+        stg.local, stg.flags = s["view"].data_ptr(), s["flags"].data_ptr()
+        stg.rank, stg.world, stg.shard_rows, stg.stored_rows = self.symm.rank, W, self.S, self.S * W
+        stg.row_bytes, stg.seq, stg.external = self.inf * 2, s["seq"], 1
+        return s["view"].data_ptr(), stg
+
+    def weight_used(self):
+        if self.pool is not None:
+            self.pool.used(self._slot)
+
+    def grad_target(self):
+        """(``[S * world, in]`` bf16 buffer the dW GEMM writes, whether it accumulates)."""
+        if self.pool is None:
+            return self.grad_full, True
+        self._gslot, view = self.pool.grad_slot(self)
+        return view, False
+
+    def grad_written(self):
+        if self.pool is not None:
+            self.pool.reduce(self, self._gslot)
 
     def forward(self, x):
         return _ShardedLinearFn.apply(x, self)
@@ -146,6 +317,9 @@ class ShardedLinear(nn.Module):
 
     def full_weight(self) -> torch.Tensor:
         """Gather the bf16 weight (checkpointing / tests)."""
+        if self.pool is not None:
+            parts = [self.shard.clone() if k == self.symm.rank else self.peer_views[k].clone() for k in range(self.symm.world)]
+            return torch.cat(parts)[:self.out]
         parts = [self.shard_ch.buf.tensor(torch.bfloat16, rank=k)[:self.S * self.symm.world * self.inf]
                  .view(self.S * self.symm.world, self.inf)[k * self.S:(k + 1) * self.S].clone() for k in range(self.symm.world)]
         return torch.cat(parts)[:self.out]
@@ -157,16 +331,28 @@ class FusedFSDP(nn.Module):
     replicated-parameter AdamW; hyper-parameters follow an optional LR scheduler through ``param_groups``."""
 
     def __init__(self, model: nn.Module, symm, pg, lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1,
-                 min_shard_numel: int = 1 << 16, check_every: int = 1):
+                 min_shard_numel: int = 1 << 16, check_every: int = 1, window: int = 0, grad_window: int = 2):
         """``check_every``: every that many ``step()`` calls the host reads the one status word all the fused kernels of
         this wrapper share and raises ``CollectiveTimeout`` if one of them gave up waiting for a peer (a kernel that
-        gives up applies no update).  0 leaves the check to ``check()``."""
+        gives up applies no update).  0 leaves the check to ``check()``.
+
+        ``window`` = K > 0 selects ZeRO-3 memory (:class:`WindowPool`): gathered weights live in K slots shared by all
+        layers and are re-gathered in backward (the reference's ``reshard_params`` / ``drop_full_param``,
+        torch/distributed/fsdp.h:200-213,255-262), gradients pass through ``grad_window`` slots and are reduce-scattered
+        layer by layer during backward.  ``window`` = 0 keeps a gathered bf16 copy and a full gradient buffer per layer
+        (ZeRO-3 traffic with ZeRO-2 memory; one gather per step instead of two)."""
         super().__init__()
         self.symm, self.pg = symm, pg
         self.check_every, self._steps = int(check_every), 0
         self.status = torch.zeros(1, dtype=torch.int32, device=symm.device)
         self.sharded: List[ShardedLinear] = []
+        self.pool = WindowPool(symm, window, grad_window, self.status) if window > 0 else None
         self._replace(model, min_shard_numel)
+        if self.pool is not None and self.sharded:
+            self.pool.allocate()
+            self.bar_ch = PeerChannel(symm, 256, status=self.status)
+            self._win_table = None
+            self._win_scale = torch.ones(1, device=symm.device)
         self.model = model
         self.param_groups = [dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, params=[])]
         rest = [p for p in model.parameters() if p.requires_grad]
@@ -201,7 +387,7 @@ class FusedFSDP(nn.Module):
         for name, child in list(mod.named_children()):
             if isinstance(child, nn.Linear) and child.bias is None and child.weight.numel() >= min_numel \
                     and child.in_features % 64 == 0:
-                sl = ShardedLinear(child, self.symm, self.pg, self.status)
+                sl = ShardedLinear(child, self.symm, self.pg, self.status, self.pool)
                 setattr(mod, name, sl)
                 self.sharded.append(sl)
             else:
@@ -213,8 +399,11 @@ class FusedFSDP(nn.Module):
     @torch.no_grad()
     def step(self, grad_scale: float = 1.0):
         g = self.param_groups[0]
-        for sl in self.sharded:
-            sl.step(g["lr"], g["betas"], g["eps"], g["weight_decay"], grad_scale / self.symm.world)
+        if self.pool is not None and self.sharded:
+            self._window_step(g, grad_scale)
+        else:
+            for sl in self.sharded:
+                sl.step(g["lr"], g["betas"], g["eps"], g["weight_decay"], grad_scale / self.symm.world)
         if self.rest_opt is not None:
             # fold .grad of the replicated parameters into the symmetric bucket, all-reduce it in one kernel
             for p, gv in zip(self.rest, self.rest_grads):
@@ -233,8 +422,50 @@ class FusedFSDP(nn.Module):
             self.flat.zero_()
         self._steps += 1
         if self.check_every > 0 and self._steps % self.check_every == 0 and self.sharded:
-            ch = self.sharded[0].grad_ch
+            ch = self.pool.gslots[0] if self.pool is not None else self.sharded[0].grad_ch
             ch.raise_if_failed(ch.stage_status())
+
+    @torch.no_grad()
+    def _window_step(self, g, grad_scale: float):
+        """Window mode: the reduce-scatters have run during backward; one fused multi-tensor AdamW steps every fp32
+        master shard from its fp32 gradient shard and writes the bf16 shards, then a barrier across the ranks keeps
+        anyone from gathering a shard its owner has not written yet."""
+        import ctypes as C
+        from ..optim.optimizers import OPT_ADAMW, TensorTable
+        dev = self.symm.device
+        cur = torch.cuda.current_stream(dev)
+        cur.wait_stream(self.pool.reduce_stream)
+        if self._win_table is None:
+            self._win_table = TensorTable()
+        ps = [sl.master for sl in self.sharded]
+        self._win_table.build(ps, [sl.gacc for sl in self.sharded], [(sl.m, sl.v, None) for sl in self.sharded],
+                              [sl.shard for sl in self.sharded], dev)
+        for sl in self.sharded:
+            sl.step_count += 1
+        t = self.sharded[0].step_count
+        b1, b2 = g["betas"]
+        self._win_scale.fill_(grad_scale / self.symm.world)
+        h = [g["lr"], b1, b2, g["eps"], g["weight_decay"], 1 - b1 ** t, 1 - b2 ** t, 0.0]
+        harr = (C.c_float * 16)(*(h + [0.0] * (16 - len(h))))
+        tab = self._win_table
+        N.check(N.lib().ptb_multi_tensor_opt(tab.rows.data_ptr(), tab.chunks.data_ptr(), tab.n_chunks, OPT_ADAMW, 0, harr,
+                                             self._win_scale.data_ptr(), None, cur.cuda_stream), "multi_tensor_opt")
+        for sl in self.sharded:
+            sl.gacc.zero_()
+            sl.stage_seq += 1                 # what the window slots hold of this layer is stale now
+        ch = self.bar_ch
+        N.check(N.lib().ptb_peer_barrier(ch.flag_ptrs, self.symm.rank, self.symm.world, ch.next_seq(), ch.ticket.data_ptr(),
+                                         ch.status.data_ptr(), cur.cuda_stream), "peer_barrier")
+
+    def memory_report(self) -> Dict[str, int]:
+        """Bytes this rank holds for the sharded layers: what scales with 1/world, and the fixed window (or, without a
+        window, the full-size copies)."""
+        shard = sum(sl.master.numel() * (4 * 3 + 2) for sl in self.sharded)            # master, m, v, bf16 shard
+        if self.pool is not None:
+            shard += sum(sl.gacc.numel() * 4 for sl in self.sharded)
+            return {"sharded_state": shard, "window": self.pool.window_bytes, "full_copies": 0}
+        full = sum(sl.w_full.numel() * 2 + sl.grad_full.numel() * 2 for sl in self.sharded)
+        return {"sharded_state": shard - sum(sl.master.numel() * 2 for sl in self.sharded), "window": 0, "full_copies": full}
 
     def zero_grad(self):
         for p in self.rest:
@@ -328,7 +559,9 @@ class FusedFSDP(nn.Module):
         return man.get("extra", {})
 
     def check(self):
-        if self.sharded:
+        if self.sharded and self.pool is not None:
+            self.pool.gslots[0].check()
+        elif self.sharded:
             self.sharded[0].grad_ch.check()        # one status word serves every channel of this wrapper
         elif self.rest_opt is not None:
             self.bucket.check()

@@ -129,6 +129,53 @@ def case_fsdp_fused(rank, world, dev, symm, pg):
     return losses, ref_losses, cos
 
 
+def case_fsdp_window(rank, world, dev, symm, pg):
+    """FusedFSDP(window=2): ZeRO-3 memory.  Same losses as the per-layer full copies on the same data (both sum the same
+    gradients in fp32), every weight gathered twice per step, per-rank state = 1/world of the model plus the window."""
+    import copy
+    from prometorch_b200.models.llama import Llama, LlamaConfig
+    from prometorch_b200.parallel.fsdp_fused import FusedFSDP
+    cfg = LlamaConfig.tiny(hidden_size=256, num_heads=4, num_kv_heads=2, intermediate_size=768, vocab_size=1024, num_layers=3, max_seq=256)
+    torch.manual_seed(0)
+    base = Llama(cfg).to(dev).to(torch.bfloat16)
+    twin = copy.deepcopy(base)
+    kw = dict(lr=1e-3, betas=(0.9, 0.95), weight_decay=0.05, min_shard_numel=1 << 14)
+    full = FusedFSDP(twin, symm, pg, **kw)
+    free0 = torch.cuda.mem_get_info(dev)[0]
+    win = FusedFSDP(base, symm, pg, window=2, grad_window=2, **kw)
+    torch.cuda.synchronize()
+    held = free0 - torch.cuda.mem_get_info(dev)[0]
+    rep, rep_full = win.memory_report(), full.memory_report()
+    n_sharded = sum(sl.S * world * sl.inf for sl in win.sharded)
+    largest = max(sl.S * world * sl.inf for sl in win.sharded)
+    # 18 bytes per sharded element / world (bf16 shard, fp32 master, two moments, fp32 gradient shard) + 4 layer-sized bf16 slots
+    assert rep["sharded_state"] == 18 * n_sharded // world and rep["window"] == 4 * largest * 2 and rep["full_copies"] == 0
+    assert rep_full["full_copies"] == 4 * n_sharded
+    assert rep["sharded_state"] + rep["window"] < rep_full["sharded_state"] + rep_full["full_copies"]
+    g = torch.Generator().manual_seed(70 + rank)
+    la, lb = [], []
+    for step in range(4):
+        for micro in range(2):                             # gradient accumulation: the reduce-scatter runs per micro-batch
+            tok = torch.randint(0, cfg.vocab_size, (2, 129), generator=g).to(dev)
+            a = win(tok[:, :-1], tok[:, 1:]) / 2
+            a.backward()
+            b = full(tok[:, :-1], tok[:, 1:]) / 2
+            b.backward()
+            la.append(float(a)); lb.append(float(b))
+        win.step(); win.zero_grad()
+        full.step(); full.zero_grad()
+    torch.cuda.synchronize()
+    win.check(); full.check()
+    assert all(abs(x - y) < 0.02 * abs(y) + 1e-3 for x, y in zip(la, lb)), (la, lb)
+    assert la[-1] < la[0]
+    # 3 layers x 7 sharded matrices, gathered for forward and again for backward in every micro-batch
+    assert win.pool.gathers >= (2 * len(win.sharded) - 4) * 8, (win.pool.gathers, len(win.sharded))
+    wa, wb = win.sharded[0].full_weight().float(), full.sharded[0].full_weight().float()
+    cos = float(torch.nn.functional.cosine_similarity(wa.flatten(), wb.flatten(), dim=0))
+    assert cos > 0.9999, cos
+    return la[-1], lb[-1], cos, held, rep
+
+
 def case_tp_sp_fused(rank, world, dev, symm, pg):
     """Sequence-parallel column -> row pair with the collectives inside the GEMMs == unsharded layers."""
     from prometorch_b200.nn.parallel import ColumnParallelLinear, RowParallelLinear, TPConfig
@@ -155,6 +202,15 @@ def case_tp_sp_fused(rank, world, dev, symm, pg):
                _rel(col.weight.grad, colf.weight.grad[rank * s:(rank + 1) * s]),
                _rel(row.weight.grad, rowf.weight.grad[:, rank * row.shard:(rank + 1) * row.shard])]
         assert max(res) < 3e-2, (it, res)
+    # the residual rides in the kernel that sums the ranks' partial tiles, and gets the output's gradient
+    xl = x[rank * n:(rank + 1) * n].clone()
+    resid = (torch.randn(n, H, device=dev) * 0.3).to(torch.bfloat16).requires_grad_()
+    with torch.no_grad():
+        plain = row(torch.relu(col(xl)))
+    y = row(torch.relu(col(xl)), residual=resid)
+    assert _rel(y, plain.float() + resid.float()) < 1e-2
+    y.float().sum().backward()
+    assert torch.allclose(resid.grad.float(), torch.ones_like(resid.grad.float()))
     return res
 
 
@@ -202,7 +258,8 @@ def case_fsdp_checkpoint(rank, world, dev, symm, pg):
     return la, lb
 
 
-CASES = dict(fsdp_checkpoint=case_fsdp_checkpoint, staged_gemm=case_staged_gemm, ddp_fused=case_ddp_fused, fsdp_fused=case_fsdp_fused, tp_sp_fused=case_tp_sp_fused)
+CASES = dict(fsdp_checkpoint=case_fsdp_checkpoint, staged_gemm=case_staged_gemm, ddp_fused=case_ddp_fused, fsdp_fused=case_fsdp_fused, fsdp_window=case_fsdp_window,
+             tp_sp_fused=case_tp_sp_fused)
 
 
 def main():

@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.multigpu
-@pytest.mark.parametrize("case", ["staged_gemm", "ddp_fused", "fsdp_fused", "fsdp_checkpoint", "tp_sp_fused"])
+@pytest.mark.parametrize("case", ["staged_gemm", "ddp_fused", "fsdp_fused", "fsdp_window", "fsdp_checkpoint", "tp_sp_fused"])
 def test_fused_multi_gpu(case):
     world = 2
     if torch.cuda.device_count() < world:
