@@ -19,7 +19,7 @@ import torch
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
-def run(impl="fused", steps=5, warmup=3, seqs_per_gpu=8, micro=2, seq_len=2048, model_name="llama-1b"):
+def run(impl="fused", steps=5, warmup=3, seqs_per_gpu=8, micro=2, seq_len=2048, model_name="llama-1b", window=0):
     """One measurement inside an initialised process group; returns the result dict on every rank."""
     import torch.distributed as dist
     from prometorch_b200.distributed import TorchProcessGroup
@@ -40,7 +40,7 @@ def run(impl="fused", steps=5, warmup=3, seqs_per_gpu=8, micro=2, seq_len=2048, 
         from prometorch_b200.parallel.fsdp_fused import FusedFSDP
         from prometorch_b200.parallel.symm import SymmGroup
         symm = SymmGroup(dist.group.WORLD, dev)
-        eng = FusedFSDP(model, symm, pg, lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1)
+        eng = FusedFSDP(model, symm, pg, lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1, window=window)
         sched = WarmupCosineAnnealingLR(eng, warmup_epochs=100, total_epochs=10000)
     else:
         # the baseline: the same model, the same kernels and the same fused multi-tensor AdamW, with the
@@ -128,6 +128,7 @@ def main():
     ap.add_argument("--micro", type=int, default=2)
     ap.add_argument("--seq-len", type=int, default=2048)
     ap.add_argument("--model", default="llama-1b", choices=["llama-1b", "tiny"])
+    ap.add_argument("--window", type=int, default=0, help="ZeRO-3 memory: gathered weights live in this many shared slots (0 = one resident copy per layer)")
     args = ap.parse_args()
     import torch.distributed as dist
     rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
@@ -137,7 +138,8 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", "29511")
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
-    out = run(args.impl, args.steps, args.warmup, args.seqs_per_gpu, args.micro, args.seq_len, args.model)
+    out = run(args.impl, args.steps, args.warmup, args.seqs_per_gpu, args.micro, args.seq_len, args.model, args.window)
+    out["window"] = args.window
     if rank == 0:
         print(json.dumps(out))
     dist.barrier()

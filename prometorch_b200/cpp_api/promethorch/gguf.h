@@ -7,7 +7,7 @@
 // matrices into the decode kernels' streaming layout (tiles of 16 rows, csrc/decode_gemv_mma.cuh), upload them, and
 // drive the engine of libptb200 (CUDA graph per token, arg-max fed back on the device).  The reference's counterpart is
 // torch::io::GGUFModel (torch/io/gguf_model.h: load / forward_decode / generate).  This header covers dense decoder
-// architectures with Q4_K / Q6_K matrices (llama, mistral, qwen2, qwen3: what a Q4_K_M file of those holds); other
+// architectures with Q4_K / Q5_K / Q6_K / Q8_0 / F16 matrices (llama, mistral, qwen2, qwen3); other
 // files go through the Python loader, which also transcodes the remaining block types.
 //
 // Link with libptb200.so and the CUDA runtime.  Needs no libtorch.
@@ -333,36 +333,60 @@ class GGUFModel {
         if (t.type != gguf::F32) throw std::runtime_error("GGUFModel: " + name + " is expected to be F32");
         return (const float*)upload(reader_.data(t), t.nbytes);
     }
-    // A matrix in the tiles-of-16-rows streaming layout.
+    // A matrix in the tiles-of-16-rows streaming layout (csrc/decode_gemv_mma.cuh): Q4_K / Q5_K blocks as in the file,
+    // Q6_K split into swizzled arrays, Q8_0 as q[16][256] (32-byte units at unit ^ (row & 7)) + d[16][8], F16 in blocks of
+    // 64 values (32-byte units at unit ^ (row & 3)).
     PtbWeightDesc matrix(const std::string& name) {
         const auto& t = reader_.tensor(name);
-        if (t.type != gguf::Q4_K && t.type != gguf::Q6_K)
-            throw std::runtime_error("GGUFModel (C++): " + name + " has block type " + std::to_string(t.type) + "; only Q4_K and Q6_K are handled here");
+        int qt, bb;              // engine type code, bytes of one (tile, 256-value block) unit / 16
+        switch (t.type) {
+            case gguf::Q4_K: qt = 0; bb = 144; break;
+            case gguf::Q6_K: qt = 1; bb = 210; break;
+            case gguf::Q5_K: qt = 4; bb = 176; break;
+            case gguf::Q8_0: qt = 5; bb = 272; break;
+            case gguf::F16: qt = 2; bb = 512; break;
+            default:
+                throw std::runtime_error("GGUFModel (C++): " + name + " has block type " + std::to_string(t.type) +
+                                         "; Q4_K, Q5_K, Q6_K, Q8_0 and F16 are handled here");
+        }
         const int rows = (int)t.shape[0], cols = (int)t.shape[1], nblk = cols / 256;
-        const int bb = t.type == gguf::Q4_K ? 144 : 210;
+        if (cols % 256) throw std::runtime_error("GGUFModel: " + name + ": row length must be a multiple of 256");
         const int ntile = (rows + 15) / 16;
         std::vector<uint8_t> out((size_t)ntile * nblk * 16 * bb, 0);
         const uint8_t* src = reader_.data(t);
         for (int r = 0; r < rows; ++r) {
             const int tile = r >> 4, rr = r & 15;
             for (int b = 0; b < nblk; ++b) {
-                const uint8_t* blk = src + ((size_t)r * nblk + b) * bb;
+                const uint8_t* blk = src + ((size_t)r * nblk + b) * bb;          // the row's bytes for these 256 values
                 uint8_t* unit = out.data() + ((size_t)tile * nblk + b) * 16 * bb;
-                if (t.type == gguf::Q4_K) {
-                    std::memcpy(unit + rr * 144, blk, 144);
-                } else {
-                    // ql[16][128] | qh[16][64] | scales[16][16] | d[16]; 16-byte chunks of a row stored at chunk ^ key(row)
-                    for (int ch = 0; ch < 8; ++ch) std::memcpy(unit + rr * 128 + ((ch ^ (rr & 7)) << 4), blk + ch * 16, 16);
-                    for (int ch = 0; ch < 4; ++ch) std::memcpy(unit + 2048 + rr * 64 + ((ch ^ ((rr >> 1) & 3)) << 4), blk + 128 + ch * 16, 16);
-                    std::memcpy(unit + 3072 + rr * 16, blk + 192, 16);
-                    std::memcpy(unit + 3328 + rr * 2, blk + 208, 2);
+                switch (t.type) {
+                    case gguf::Q4_K: std::memcpy(unit + rr * 144, blk, 144); break;
+                    case gguf::Q5_K: std::memcpy(unit + rr * 176, blk, 176); break;
+                    case gguf::Q8_0:
+                        for (int u = 0; u < 8; ++u) {                             // eight {fp16 d, 32 x int8} file blocks
+                            std::memcpy(unit + rr * 256 + ((u ^ (rr & 7)) << 5), blk + u * 34 + 2, 32);
+                            std::memcpy(unit + 4096 + rr * 16 + u * 2, blk + u * 34, 2);
+                        }
+                        break;
+                    case gguf::F16:
+                        for (int q = 0; q < 4; ++q)                               // four 64-value blocks of 2048 bytes
+                            for (int u = 0; u < 4; ++u)
+                                std::memcpy(unit + q * 2048 + rr * 128 + ((u ^ (rr & 3)) << 5), blk + q * 128 + u * 32, 32);
+                        break;
+                    default:
+                        // ql[16][128] | qh[16][64] | scales[16][16] | d[16]; 16-byte chunks of a row stored at chunk ^ key(row)
+                        for (int ch = 0; ch < 8; ++ch) std::memcpy(unit + rr * 128 + ((ch ^ (rr & 7)) << 4), blk + ch * 16, 16);
+                        for (int ch = 0; ch < 4; ++ch) std::memcpy(unit + 2048 + rr * 64 + ((ch ^ ((rr >> 1) & 3)) << 4), blk + 128 + ch * 16, 16);
+                        std::memcpy(unit + 3072 + rr * 16, blk + 192, 16);
+                        std::memcpy(unit + 3328 + rr * 2, blk + 208, 2);
+                        break;
                 }
             }
         }
         PtbWeightDesc d;
         std::memset(&d, 0, sizeof(d));
         d.w = upload(out.data(), out.size());
-        d.qtype = t.type == gguf::Q4_K ? 0 : 1;
+        d.qtype = qt;
         d.rows = rows;
         d.cols = cols;
         d.layout = 1;
