@@ -39,6 +39,8 @@ def main(argv=None) -> int:
     ap.add_argument("--top-k", type=int, default=40)
     ap.add_argument("--top-p", type=float, default=0.9)
     ap.add_argument("--repeat-penalty", type=float, default=1.05)
+    ap.add_argument("--draft", default=None, help="a smaller GGUF model over the same vocabulary: greedy speculative decoding")
+    ap.add_argument("--spec-k", type=int, default=4, help="tokens the draft proposes per verification pass")
     ap.add_argument("--nprocs", type=int, default=1)
     ap.add_argument("--rank", type=int, default=0)
     ap.add_argument("--master-addr", "--master_addr", default="127.0.0.1")
@@ -133,8 +135,18 @@ def main(argv=None) -> int:
         for s in ("<|im_end|>", "<|eot_id|>", "<end_of_turn>", "<|end|>", "<|endoftext|>", "</s>"):
             if s in tok.vocab:
                 stops.add(tok.vocab[s])
-        model.generate(ids, max_new_tokens=a.max_tokens, temperature=a.temp, top_k=a.top_k, top_p=a.top_p,
-                       repeat_penalty=a.repeat_penalty, stop_ids=stops, on_token=on_token)
+        if a.draft and world == 1 and a.temp <= 0.0 and a.repeat_penalty == 1.0:
+            from .io.gguf_model import GGUFModel as _G
+            from .io.speculative import speculative_generate
+            draft = _G(a.draft, device=f"cuda:{torch.cuda.current_device()}", max_seq=model.max_seq)
+            toks, st = speculative_generate(model, draft, ids, max_new_tokens=a.max_tokens, k=a.spec_k, stop_ids=stops)
+            for t in toks:
+                on_token(t)
+            say(f"\n[Speculative] {st['accepted']} of {st['proposed']} proposals accepted, {st['target_passes']} target passes")
+            draft.close()
+        else:
+            model.generate(ids, max_new_tokens=a.max_tokens, temperature=a.temp, top_k=a.top_k, top_p=a.top_p,
+                           repeat_penalty=a.repeat_penalty, stop_ids=stops, on_token=on_token)
     else:
         for t in model.generate_greedy(ids, a.max_tokens):
             on_token(t)

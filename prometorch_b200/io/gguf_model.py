@@ -456,12 +456,14 @@ class GGUFModel:
         return self._wrap(k.value, n, torch.float16).view(shape), self._wrap(v.value, n, torch.float16).view(shape)
 
     @torch.no_grad()
-    def prefill(self, tokens: Sequence[int], pos0: int = 0):
+    def prefill(self, tokens: Sequence[int], pos0: int = 0, return_logits: bool = False):
         """Run ``tokens`` at positions ``pos0 ..`` through the model in ONE batched pass that fills the KV cache:
         weights are dequantised to bf16 layer by layer and every projection is a tcgen05 GEMM over all prompt
         tokens, attention is the FlashAttention kernel.  Nothing is returned; decoding continues with
         ``forward_decode(next_token, pos0 + len(tokens))``.  (Token-by-token prefill costs one decode step each.)
-        Under tensor parallelism the call is collective: every rank runs it with the same tokens."""
+        Under tensor parallelism the call is collective: every rank runs it with the same tokens.
+        ``return_logits=True`` also applies the output norm and the lm_head to every position and returns fp32 logits
+        ``[T, vocab rows of this rank]`` (what a speculative verifier needs)."""
         if not self.supports_prefill:
             raise NotImplementedError("batched prefill: no sliding window, head size 64 or 128")
         from ..ops import fused_ops as K
@@ -470,7 +472,7 @@ class GGUFModel:
         cfg, dev = self.cfg, self.device
         T = len(tokens)
         if T == 0:
-            return
+            return None
         if pos0 + T > self.max_seq:
             raise ValueError(f"prompt of {T} tokens at {pos0} exceeds max_seq {self.max_seq}")
         self.capture()
@@ -537,10 +539,17 @@ class GGUFModel:
             if L["post_ffn_norm"] is not None:
                 dn = K.rms_norm(dn, nw(L, "post_ffn_norm"), eps)
             x = x + dn
+        logits = None
+        if return_logits:
+            if not hasattr(self, "_out_norm_bf16"):
+                w = self.out_norm
+                self._out_norm_bf16 = ((w + 1.0) if cfg.gemma_norm_add_one else w).to(bf)
+            logits = linear(K.rms_norm(x, self._out_norm_bf16, eps), self._dequant(self.lm_head), None).float()
         torch.cuda.current_stream(dev).synchronize()
         if int(self._pf_status):
             self._pf_status.zero_()
             raise N.NativeError("prefill: a token id fell outside the vocabulary")
+        return logits
 
     def run_script(self, prompt: Sequence[int], n_new: int, pos0: int = 0, sync: bool = True) -> Optional[List[int]]:
         """Enqueue prompt + ``n_new`` greedy tokens as back-to-back graph replays with the

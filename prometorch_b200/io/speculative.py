@@ -1,4 +1,7 @@
-"""Low-rank speculative output projection: pick the next token without computing every logit exactly.
+"""Speculative decoding: a low-rank output projection, and a draft model verified in batched passes.
+
+*Low-rank output projection* (the reference's ``LowRankOutputProj``): pick the next token without computing every logit
+exactly.
 
 ``W[vocab, hidden]`` is approximated once by ``U[vocab, r] @ V[r, hidden]`` (randomised range finder with two power
 iterations, then an SVD of the small projected matrix).  A decode step computes ``z = V x`` and the approximate logits
@@ -9,6 +12,11 @@ token is ``vocab * r`` (bf16) instead of the whole quantised matrix.
 Same contract as the reference's ``LowRankOutputProj`` (torch/io/speculative_decode.h:72-500: ``init_from_float``,
 ``init_from_quantized``, ``decode_greedy``, ``decode_sample`` with softmax over the exact candidates); the factorisation
 and both passes are tensor programs here and run on the model's device.
+
+*Draft model* (:func:`speculative_generate`): a small GGUF model proposes ``k`` greedy tokens with its decode engine, the
+target model scores all of them in ONE batched prompt pass (tcgen05 GEMMs + FlashAttention, logits at every position) and
+keeps the longest agreeing prefix plus its own next token.  The output is the target's greedy continuation under the
+batched pass; rejected positions of either KV cache are simply overwritten later.
 """
 from __future__ import annotations
 
@@ -98,3 +106,54 @@ class LowRankOutputProj:
         v, j = exact.topk(k)
         p = torch.softmax(v / temperature, dim=0)
         return int(idx[j[torch.multinomial(p, 1, generator=generator)]])
+
+
+@torch.no_grad()
+def speculative_generate(target, draft, prompt, max_new_tokens: int = 64, k: int = 4, stop_ids=()):
+    """Greedy generation of ``target`` (a ``GGUFModel`` with batched prefill) sped up by ``draft`` (a smaller
+    ``GGUFModel`` over the same vocabulary).  Returns ``(tokens, stats)`` with ``stats = {"target_passes", "accepted",
+    "proposed"}``."""
+    if not target.supports_prefill:
+        raise NotImplementedError("the target model has no batched prompt pass")
+    prompt = [int(t) for t in prompt]
+    stop = set(int(s) for s in stop_ids)
+    out = []
+    stats = {"target_passes": 0, "accepted": 0, "proposed": 0}
+    # the target scores the whole prompt once; its arg-max at the last position is the first new token
+    logits = target.prefill(prompt, 0, return_logits=True)
+    stats["target_passes"] += 1
+    nxt = int(logits[-1].argmax())
+    for pos, t in enumerate(prompt):                       # the draft's cache follows the same tokens
+        draft.forward_decode(t, pos)
+    n_ctx = len(prompt)                                    # positions whose KV both models hold
+    while len(out) < max_new_tokens and nxt not in stop:
+        out.append(nxt)
+        if len(out) >= max_new_tokens or n_ctx + k + 1 >= min(target.max_seq, draft.max_seq):
+            break
+        # draft proposes k tokens after `nxt`
+        prop, t = [], nxt
+        for i in range(k):
+            t = draft.forward_decode(t, n_ctx + i)
+            prop.append(t)
+        stats["proposed"] += k
+        # target scores [nxt, prop[0], ..., prop[k-1]] in one pass: row i predicts the token after position n_ctx + i
+        lg = target.prefill([nxt] + prop, n_ctx, return_logits=True)
+        stats["target_passes"] += 1
+        choice = lg.argmax(-1).tolist()
+        a = 0
+        while a < k and prop[a] == choice[a]:
+            a += 1
+        stats["accepted"] += a
+        hit_stop = False
+        for tok in prop[:a]:
+            if tok in stop or len(out) >= max_new_tokens:
+                hit_stop = True
+                break
+            out.append(tok)
+        if hit_stop:
+            break
+        nxt = choice[a]
+        if a == k:                                         # the draft has not seen its own last proposal yet
+            draft.forward_decode(prop[-1], n_ctx + k)
+        n_ctx += a + 1
+    return out[:max_new_tokens], stats

@@ -396,3 +396,44 @@ def test_cpp_gguf_model_generates_the_same_ids(tmp_path):
     ids = [int(x) for x in [ln for ln in r.stdout.splitlines() if ln.startswith("IDS")][0].split()[1:]]
     step = int([ln for ln in r.stdout.splitlines() if ln.startswith("STEP")][0].split()[1])
     assert ids == want and step == want[0], (ids, want, step)
+
+
+def test_draft_model_speculative_generation(tmp_path):
+    """A draft model proposes, the target verifies k tokens per batched pass: the result equals the target's own greedy
+    continuation under the batched pass, with fewer target passes than tokens when the draft agrees (here the draft is the
+    target itself, so every proposal is accepted up to rounding of the two numeric paths)."""
+    from prometorch_b200.io.gguf_model import GGUFModel
+    from prometorch_b200.io.speculative import speculative_generate
+    cfg = tiny_qwen3_config(layers=2, hidden=512, heads=8, kv_heads=2, inter=1024, vocab=1000)
+    p = str(tmp_path / "t.gguf")
+    write_synthetic_gguf(p, cfg, seed=21, device="cuda", std=0.05)
+    small = tiny_qwen3_config(layers=1, hidden=256, heads=4, kv_heads=2, inter=512, vocab=1000)
+    q = str(tmp_path / "d.gguf")
+    write_synthetic_gguf(q, small, seed=22, device="cuda", std=0.05)
+    target, same, other = GGUFModel(p, max_seq=256), GGUFModel(p, max_seq=256), GGUFModel(q, max_seq=256)
+    prompt = [5, 77, 300, 901, 12, 64, 8, 8, 440, 3]
+    # reference: the target alone, one batched pass per token
+    ref, gaps, ctx = [], [], list(prompt)
+    lg = target.prefill(ctx, 0, return_logits=True)
+    for _ in range(12):
+        top = lg[-1].topk(2).values
+        gaps.append(float(top[0] - top[1]) / max(float(top[0].abs()), 1e-6))
+        t = int(lg[-1].argmax())
+        ref.append(t)
+        lg = target.prefill([t, t], len(ctx), return_logits=True)[:1]     # two rows: the one-row GEMM is a different kernel
+        ctx.append(t)
+
+    def same_up_to_near_ties(got):
+        # the batched pass sums in a different order for a different number of rows: only a near-tie may flip
+        for i, (g_, r_) in enumerate(zip(got, ref)):
+            if g_ != r_:
+                return gaps[i] < 2e-2
+        return len(got) == len(ref)
+    out, st = speculative_generate(target, same, prompt, max_new_tokens=12, k=4)
+    assert same_up_to_near_ties(out), (out, ref, gaps)
+    assert st["target_passes"] < 12 and st["accepted"] >= 4, st           # an identical draft is accepted most of the time
+    out2, st2 = speculative_generate(target, other, prompt, max_new_tokens=12, k=3)
+    assert same_up_to_near_ties(out2), (out2, ref, gaps)                   # an unrelated draft costs passes, never tokens
+    for m in (target, same, other):
+        m.check_status()
+        m.close()
