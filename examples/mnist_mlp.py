@@ -7,9 +7,7 @@
 synthetic set of the same shape (ten noisy class prototypes), since no dataset ships with the package.
 """
 import argparse
-import gzip
 import os
-import struct
 import sys
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
@@ -17,27 +15,11 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 import promethorch as pt  # noqa: E402
 
 
-def read_idx(path):
-    op = gzip.open if path.endswith(".gz") else open
-    with op(path, "rb") as f:
-        magic, = struct.unpack(">I", f.read(4))
-        dims = [struct.unpack(">I", f.read(4))[0] for _ in range(magic & 0xFF)]
-        return pt.tensor(list(f.read()), dtype=pt.uint8).reshape(dims)
-
-
 def load(data_dir, n_train, n_test):
-    if data_dir:
-        def find(stem):
-            for ext in ("", ".gz"):
-                p = os.path.join(data_dir, stem + ext)
-                if os.path.exists(p):
-                    return p
-            raise FileNotFoundError(stem)
-        xtr = read_idx(find("train-images-idx3-ubyte")).float().div(255).reshape(-1, 784)
-        ytr = read_idx(find("train-labels-idx1-ubyte")).long()
-        xte = read_idx(find("t10k-images-idx3-ubyte")).float().div(255).reshape(-1, 784)
-        yte = read_idx(find("t10k-labels-idx1-ubyte")).long()
-        return xtr, ytr, xte, yte
+    if data_dir:                        # the four IDX files of MNIST / Fashion-MNIST (optionally .gz)
+        from prometorch_b200.data import MNIST
+        tr, te = MNIST(data_dir, train=True, flatten=True), MNIST(data_dir, train=False, flatten=True)
+        return tr.images.reshape(-1, 784), tr.labels, te.images.reshape(-1, 784), te.labels
     pt.manual_seed(1234)
     protos = pt.rand(10, 784)
 

@@ -189,7 +189,9 @@ static int plan_gemv16(GemvLaunch& L, int njobs, int K, int n_ctas, int force_wa
         if (bestKG > 1) acc_floats = std::max(acc_floats, tiles_cta * bestKG * pairs * 16);
     }
     tile_bytes = (tile_bytes + 127) / 128 * 128;
-    const size_t budget = (size_t)env_int("PTB_GEMV_SMEM_KB", warps >= 16 ? 200 : 100) * 1024;
+    // ring depth: measured on B200 (Qwen3-4B shape), rings of two or three slots per warp (budgets of 48 to 160 KB) decode
+    // 1.4 % faster than the deepest rings that fit (184 to 200 KB per CTA), so the default budget is 128 KB
+    const size_t budget = (size_t)env_int("PTB_GEMV_SMEM_KB", warps >= 16 ? 128 : 100) * 1024;
     int stages = std::min(env_int("PTB_GEMV_STAGES", 8), 16);
     while (stages > 2 && gemv_smem_layout(K, warps, stages, tile_bytes, acc_floats).total > budget) --stages;
     p.stages = stages;

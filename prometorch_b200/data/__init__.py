@@ -50,3 +50,88 @@ class SyntheticImages(Dataset):
 
     def __getitem__(self, i):
         return self.x[i], self.y[i]
+
+
+def read_idx(path: str) -> torch.Tensor:
+    """An IDX file (the MNIST container: magic ``00 00 <dtype> <ndim>``, big-endian dims, raw data; ``.gz`` accepted)
+    as a tensor.  The reference's MNIST programs parse the same files by hand (examples/mnist/train_mnist_mlp.cpp)."""
+    import gzip
+    import struct
+    import numpy as np
+    opener = gzip.open if path.endswith(".gz") else open
+    with opener(path, "rb") as f:
+        raw = f.read()
+    zero, dtype_code, ndim = struct.unpack(">HBB", raw[:4])
+    if zero != 0:
+        raise ValueError(f"{path}: not an IDX file")
+    dtypes = {0x08: np.uint8, 0x09: np.int8, 0x0B: np.dtype(">i2"), 0x0C: np.dtype(">i4"), 0x0D: np.dtype(">f4"), 0x0E: np.dtype(">f8")}
+    if dtype_code not in dtypes:
+        raise ValueError(f"{path}: unknown IDX element type {dtype_code:#x}")
+    dims = struct.unpack(">" + "I" * ndim, raw[4:4 + 4 * ndim])
+    arr = np.frombuffer(raw, dtype=dtypes[dtype_code], offset=4 + 4 * ndim)
+    n = 1
+    for d in dims:
+        n *= d
+    if arr.size != n:
+        raise ValueError(f"{path}: {arr.size} elements, header says {dims}")
+    return torch.from_numpy(arr.astype(arr.dtype.newbyteorder("=")).reshape(dims).copy())
+
+
+class MNIST(Dataset):
+    """MNIST / Fashion-MNIST from the four IDX files in ``root`` (``train-images-idx3-ubyte`` ..., optionally ``.gz``):
+    images as float ``[1, 28, 28]`` in [0, 1] (or flattened), labels as int64."""
+
+    def __init__(self, root: str, train: bool = True, flatten: bool = False, transform=None):
+        import os
+        stem = "train" if train else "t10k"
+
+        def find(name):
+            for cand in (name, name + ".gz", name.replace("-idx", ".idx"), name.replace("-idx", ".idx") + ".gz"):
+                p = os.path.join(root, cand)
+                if os.path.exists(p):
+                    return p
+            raise FileNotFoundError(f"{name}[.gz] not found under {root}")
+        self.images = read_idx(find(f"{stem}-images-idx3-ubyte")).float().div_(255.0)
+        self.labels = read_idx(find(f"{stem}-labels-idx1-ubyte")).long()
+        if self.images.shape[0] != self.labels.shape[0]:
+            raise ValueError("MNIST: image and label counts differ")
+        self.flatten, self.transform = flatten, transform
+
+    def __len__(self):
+        return self.images.shape[0]
+
+    def __getitem__(self, i):
+        x = self.images[i]
+        x = x.reshape(-1) if self.flatten else x.unsqueeze(0)
+        if self.transform is not None:
+            x = self.transform(x)
+        return x, self.labels[i]
+
+
+class CharTextDataset(Dataset):
+    """Character-level language-model samples from a text file: windows of ``block_size + 1`` characters, split into
+    input and next-character target (the data of the reference's shakespeare example)."""
+
+    def __init__(self, path_or_text: str, block_size: int = 128, stride: int = 1, is_text: bool = False):
+        text = path_or_text if is_text else open(path_or_text, encoding="utf-8").read()
+        self.chars = sorted(set(text))
+        self.stoi = {c: i for i, c in enumerate(self.chars)}
+        self.data = torch.tensor([self.stoi[c] for c in text], dtype=torch.long)
+        self.block_size, self.stride = block_size, stride
+        if self.data.numel() <= block_size:
+            raise ValueError("CharTextDataset: the text is shorter than one block")
+
+    @property
+    def vocab_size(self) -> int:
+        return len(self.chars)
+
+    def decode(self, ids) -> str:
+        return "".join(self.chars[int(i)] for i in ids)
+
+    def __len__(self):
+        return (self.data.numel() - self.block_size - 1) // self.stride + 1
+
+    def __getitem__(self, i):
+        s = i * self.stride
+        w = self.data[s:s + self.block_size + 1]
+        return w[:-1], w[1:]

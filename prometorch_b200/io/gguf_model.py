@@ -431,6 +431,27 @@ class GGUFModel:
             raise N.NativeError("decode step: " + self._lib.ptb_last_error().decode())
         return t
 
+    # ------------------------------------------------------------------ low-rank speculative output projection
+    def lowrank_head(self, rank: int = 256, candidate_k: int = 64):
+        """Build the low-rank approximation of the output projection (io/speculative.py) from the file's quantised rows.
+        ``next_token_lowrank()`` then picks the next token from the engine's final hidden state with ``rank`` instead of
+        ``hidden`` multiply-adds per vocabulary row plus ``candidate_k`` exact rows."""
+        from .speculative import LowRankOutputProj
+        if self.tp_world != 1:
+            raise NotImplementedError("low-rank output projection: one GPU")
+        name = "output.weight" if self.reader.has_tensor("output.weight") else "token_embd.weight"
+        ti = self.reader.tensors[name]
+        self._lowrank = LowRankOutputProj(rank, candidate_k, dtype=torch.bfloat16).init_from_quantized(
+            self.reader.raw(name), ti.qtype, ti.shape[-1], device=self.device)
+        return self._lowrank
+
+    def next_token_lowrank(self) -> int:
+        """Arg-max over the vocabulary through the low-rank projection, from the hidden state of the last decode step."""
+        x = self.hidden_view().float()
+        w = (self.out_norm + 1.0) if self.cfg.gemma_norm_add_one else self.out_norm
+        x = x * torch.rsqrt(x.pow(2).mean() + self.cfg.rms_norm_eps) * w
+        return self._lowrank.decode_greedy(x)
+
     # ------------------------------------------------------------------ batched prompt pass
     @property
     def supports_prefill(self) -> bool:

@@ -22,7 +22,7 @@ NATIVE_ENV: Dict[str, str] = {
     "PTB_GEMV_WARPS": "warps per CTA of the decode GEMV: 8 or 16 (default 16 for the tile layout, 8 for the segment layout)",
     "PTB_GEMV_CTAS_PER_SM": "CTAs per SM of the decode GEMV (default 1 for the tile layout, 2 for the segment layout)",
     "PTB_GEMV_STAGES": "ring depth per warp of the decode GEMV (default: as many as fit, at most 8; 4 for the segment layout)",
-    "PTB_GEMV_SMEM_KB": "shared-memory budget per GEMV CTA in KB (default 200 at 16 warps, 100 at 8)",
+    "PTB_GEMV_SMEM_KB": "shared-memory budget per GEMV CTA in KB (default 128 at 16 warps, 100 at 8)",
     "PTB_GEMV_TILE_KB": "segment layout: upper bound of a warp tile in KB (default 6)",
     "PTB_GEMV_KG": "tile layout: force the number of K-groups per row tile (default: chosen by the planner)",
     "PTB_DECODE_FLOW": "plain (default on one GPU: kernels wait at launch boundaries) or dataflow (slot hand-over; always used under tensor parallelism)",

@@ -418,3 +418,31 @@ def test_kernels_are_dispatcher_ops():
     assert torch.allclose(torch.ops.ptb200.swiglu(gu, False), torch.nn.functional.silu(gu[:, :8]) * gu[:, 8:], atol=1e-6)
     for name in library.SCHEMAS:
         assert hasattr(torch.ops.ptb200, name)
+
+
+def test_idx_reader_mnist_and_char_dataset(tmp_path):
+    import gzip
+    import struct
+    import numpy as np
+    import torch
+    from prometorch_b200.data import MNIST, CharTextDataset, DataLoader, read_idx
+    rng = np.random.default_rng(0)
+    imgs = rng.integers(0, 256, (12, 28, 28), dtype=np.uint8)
+    labs = rng.integers(0, 10, (12,), dtype=np.uint8)
+    with open(tmp_path / "train-images-idx3-ubyte", "wb") as f:
+        f.write(struct.pack(">HBB", 0, 0x08, 3) + struct.pack(">III", 12, 28, 28) + imgs.tobytes())
+    with gzip.open(tmp_path / "train-labels-idx1-ubyte.gz", "wb") as f:
+        f.write(struct.pack(">HBB", 0, 0x08, 1) + struct.pack(">I", 12) + labs.tobytes())
+    assert torch.equal(read_idx(str(tmp_path / "train-images-idx3-ubyte")), torch.from_numpy(imgs))
+    ds = MNIST(str(tmp_path), train=True, flatten=True)
+    x, y = ds[5]
+    assert len(ds) == 12 and x.shape == (784,) and int(y) == int(labs[5]) and float(x.max()) <= 1.0
+    xb, yb = next(iter(DataLoader(ds, batch_size=4)))
+    assert xb.shape == (4, 784) and yb.dtype == torch.int64
+    f32 = np.arange(6, dtype=">f4").reshape(2, 3)
+    with open(tmp_path / "f.idx", "wb") as f:
+        f.write(struct.pack(">HBB", 0, 0x0D, 2) + struct.pack(">II", 2, 3) + f32.tobytes())
+    assert read_idx(str(tmp_path / "f.idx")).tolist() == [[0.0, 1.0, 2.0], [3.0, 4.0, 5.0]]
+    c = CharTextDataset("hello world, hello there", block_size=5, is_text=True)
+    a, b = c[3]
+    assert c.decode(a) == "lo wo" and c.decode(b) == "o wor" and len(c) == len("hello world, hello there") - 5

@@ -437,3 +437,18 @@ def test_draft_model_speculative_generation(tmp_path):
     for m in (target, same, other):
         m.check_status()
         m.close()
+
+
+def test_lowrank_head_agrees_with_the_engine(tiny_model):
+    """The low-rank output projection, fed with the engine's final hidden state, names the engine's own arg-max whenever
+    that token is among its candidates (a random 1000 x 512 head has a flat spectrum, so many candidates are kept)."""
+    from prometorch_b200.io.gguf_model import GGUFModel
+    m = GGUFModel(tiny_model, max_seq=128)
+    m.lowrank_head(rank=256, candidate_k=200)
+    hits = 0
+    for pos, t in enumerate([3, 77, 500, 999, 12, 64, 5, 901]):
+        nxt = m.forward_decode(t, pos)
+        hits += m.next_token_lowrank() == nxt
+    assert hits >= 6, hits
+    m.check_status()
+    m.close()
