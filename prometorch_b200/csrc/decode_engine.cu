@@ -759,13 +759,13 @@ static int engine_plan_dataflow(Engine* e) {
 
 static int engine_plan(Engine* e) {
     // PTB_DECODE_FLOW: "plain" (launch-boundary waits; producer-side all-reduce under tensor parallelism) or "dataflow"
-    // (slot hand-over, consumer-side all-reduce).  Measured on B200: plain is ahead up to 4 GPUs, dataflow at 8, where
+    // (slot hand-over, consumer-side all-reduce).  Measured on B200: plain is ahead on 1 and 2 GPUs, dataflow from 4 (790 vs 784 tok/s at 4, 868 vs 787 at 8), where
     // the per-kernel hand-over latency is all that is left of a step.
     // "external" (tensor parallel only): the plain flow without any in-kernel exchange; the caller enqueues launch ranges
     // and all-reduces the residual buffer between them (ptb_engine_enqueue_range), which is how the NCCL baseline runs.
     const char* f = getenv("PTB_DECODE_FLOW");
     e->external = f && !strcmp(f, "external") && e->m.tp_world > 1;
-    e->dataflow = f ? !strcmp(f, "dataflow") : e->m.tp_world >= 8;
+    e->dataflow = f ? !strcmp(f, "dataflow") : e->m.tp_world >= 4;
     if (e->dataflow ? engine_plan_dataflow(e) : engine_plan_plain(e)) return -1;
     const size_t pf_cap = (size_t)env_int("PTB_PREFETCH_MB", 0) << 20;
     if (pf_cap)

@@ -25,7 +25,7 @@ NATIVE_ENV: Dict[str, str] = {
     "PTB_GEMV_SMEM_KB": "shared-memory budget per GEMV CTA in KB (default 128 at 16 warps, 100 at 8)",
     "PTB_GEMV_TILE_KB": "segment layout: upper bound of a warp tile in KB (default 6)",
     "PTB_GEMV_KG": "tile layout: force the number of K-groups per row tile (default: chosen by the planner)",
-    "PTB_DECODE_FLOW": "plain (default on one GPU: kernels wait at launch boundaries) or dataflow (slot hand-over; always used under tensor parallelism)",
+    "PTB_DECODE_FLOW": "plain (kernels wait at launch boundaries, producer-side all-reduce), dataflow (slot hand-over, consumer-side all-reduce) or external (tensor parallel only: no in-kernel exchange, the caller all-reduces between launch ranges); the default follows the number of ranks",
     "PTB_DATAFLOW": "0 = dataflow kernels also wait for their predecessor at the launch boundary (comparison aid; default 1)",
     "PTB_RECORDS": "0 = every CTA gathers and quantises its input itself instead of copying the quantised-input records (default 1)",
     "PTB_PREFETCH_MB": "MB of the next kernel's weights each decode GEMV prefetches into L2 (default 0 = off)",
