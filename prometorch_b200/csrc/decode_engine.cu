@@ -268,15 +268,20 @@ static int ensure_attrs() {
     if (g_attr_done) return 0;
     // 227 KB per CTA is shared between the kernel's static and dynamic shared memory
     cudaFuncAttributes fa;
-    PTB_CUDA_OK(cudaFuncGetAttributes(&fa, gemv_kernel<8>));
+    PTB_CUDA_OK(cudaFuncGetAttributes(&fa, (gemv_kernel<8, false>)));
     int optin = 0, dev = 0;
     PTB_CUDA_OK(cudaGetDevice(&dev));
     PTB_CUDA_OK(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
     g_gemv_max_dyn = (size_t)optin - fa.sharedSizeBytes;
-    PTB_CUDA_OK(cudaFuncSetAttribute(gemv_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_gemv_max_dyn));
-    PTB_CUDA_OK(cudaFuncSetAttribute(gemv_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_gemv_max_dyn));
-    PTB_CUDA_OK(cudaFuncSetAttribute(gemv16_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_gemv_max_dyn));
-    PTB_CUDA_OK(cudaFuncSetAttribute(gemv16_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g_gemv_max_dyn));
+    const int dyn = (int)g_gemv_max_dyn;
+    PTB_CUDA_OK(cudaFuncSetAttribute((gemv_kernel<8, false>), cudaFuncAttributeMaxDynamicSharedMemorySize, dyn));
+    PTB_CUDA_OK(cudaFuncSetAttribute((gemv_kernel<16, false>), cudaFuncAttributeMaxDynamicSharedMemorySize, dyn));
+    PTB_CUDA_OK(cudaFuncSetAttribute((gemv16_kernel<8, false>), cudaFuncAttributeMaxDynamicSharedMemorySize, dyn));
+    PTB_CUDA_OK(cudaFuncSetAttribute((gemv16_kernel<16, false>), cudaFuncAttributeMaxDynamicSharedMemorySize, dyn));
+    PTB_CUDA_OK(cudaFuncSetAttribute((gemv_kernel<8, true>), cudaFuncAttributeMaxDynamicSharedMemorySize, dyn));
+    PTB_CUDA_OK(cudaFuncSetAttribute((gemv_kernel<16, true>), cudaFuncAttributeMaxDynamicSharedMemorySize, dyn));
+    PTB_CUDA_OK(cudaFuncSetAttribute((gemv16_kernel<8, true>), cudaFuncAttributeMaxDynamicSharedMemorySize, dyn));
+    PTB_CUDA_OK(cudaFuncSetAttribute((gemv16_kernel<16, true>), cudaFuncAttributeMaxDynamicSharedMemorySize, dyn));
     g_attr_done = true;
     return 0;
 }
@@ -342,13 +347,30 @@ static cudaError_t launch_attn(const AttnParams& a, int n_kv_heads, cudaStream_t
     }
 }
 
+// A launch that uses none of the slot hand-over, the input records or the L2 prefetch runs the lean instantiation.
+static bool gemv_is_lean(const GemvParams& p) {
+    static const int on = env_int("PTB_GEMV_LEAN", 1);
+    if (!on || p.x_ll || p.part_ll || p.rec || p.x_out_ll) return false;
+    for (int i = 0; i < p.njobs; ++i)
+        if (p.job[i].out_ll) return false;
+    for (int i = 0; i < 4; ++i)
+        if (p.pf_bytes[i]) return false;
+    return true;
+}
 static cudaError_t launch_gemv(const GemvLaunch& L, cudaStream_t st, bool pdl) {
+    const bool lean = gemv_is_lean(L.p);
     if (L.t16) {
-        if (L.p.warps == 16) return launch_pdl(gemv16_kernel<16>, dim3(L.grid), dim3(512), L.smem, st, pdl, L.p);
-        return launch_pdl(gemv16_kernel<8>, dim3(L.grid), dim3(256), L.smem, st, pdl, L.p);
+        if (L.p.warps == 16)
+            return lean ? launch_pdl(gemv16_kernel<16, true>, dim3(L.grid), dim3(512), L.smem, st, pdl, L.p)
+                        : launch_pdl(gemv16_kernel<16, false>, dim3(L.grid), dim3(512), L.smem, st, pdl, L.p);
+        return lean ? launch_pdl(gemv16_kernel<8, true>, dim3(L.grid), dim3(256), L.smem, st, pdl, L.p)
+                    : launch_pdl(gemv16_kernel<8, false>, dim3(L.grid), dim3(256), L.smem, st, pdl, L.p);
     }
-    if (L.p.warps == 16) return launch_pdl(gemv_kernel<16>, dim3(L.grid), dim3(512), L.smem, st, pdl, L.p);
-    return launch_pdl(gemv_kernel<8>, dim3(L.grid), dim3(256), L.smem, st, pdl, L.p);
+    if (L.p.warps == 16)
+        return lean ? launch_pdl(gemv_kernel<16, true>, dim3(L.grid), dim3(512), L.smem, st, pdl, L.p)
+                    : launch_pdl(gemv_kernel<16, false>, dim3(L.grid), dim3(512), L.smem, st, pdl, L.p);
+    return lean ? launch_pdl(gemv_kernel<8, true>, dim3(L.grid), dim3(256), L.smem, st, pdl, L.p)
+                : launch_pdl(gemv_kernel<8, false>, dim3(L.grid), dim3(256), L.smem, st, pdl, L.p);
 }
 
 // ------------------------------------------------------------------------------------------ standalone op entry points (tests, benches)

@@ -270,7 +270,7 @@ struct InputSrc {
 // architectures, normalising them first), optionally RMS-normalise, quantise to int8 blocks of 32.
 //   xq[K] int8, xs[K/32] block scales, xsf16[K/16] = scale * (sum of 16 int8), xsf32[K/32] = scale * (sum of 32).
 // Each thread keeps up to QIN_ITEMS 8-value items in registers: K <= QIN_ITEMS * 8 * blockDim.
-template <int QIN_ITEMS, bool POST = false>
+template <int QIN_ITEMS, bool POST = false, bool LL = true>
 __device__ __forceinline__ void quantize_input(const InputSrc& I, const float* __restrict__ norm_w, float eps,
                                                int add_one, int K, int8_t* xq, float* xs, float* xsf16, float* xsf32,
                                                float* red) {
@@ -279,7 +279,7 @@ __device__ __forceinline__ void quantize_input(const InputSrc& I, const float* _
     float v[QIN_ITEMS][8];
     float t[POST ? QIN_ITEMS : 1][8];
     float ss = 0.f;
-    if (I.x_ll || I.part_ll) {
+    if (LL && (I.x_ll || I.part_ll)) {
         // ---- dataflow mode.  A status word that is already set means an earlier kernel gave up: do not wait again.
         const unsigned long long budget = (*reinterpret_cast<volatile int*>(I.status) != 0) ? 0ull : I.wait_ns;
         unsigned done = 0;
@@ -389,7 +389,7 @@ __device__ __forceinline__ void quantize_input(const InputSrc& I, const float* _
         }
         __syncthreads();        // `red` is reused by the next reduction
     }
-    if (blockIdx.x == 0 && (I.x_out || I.x_out_ll)) {
+    if (blockIdx.x == 0 && (I.x_out || (LL && I.x_out_ll))) {
         // the updated residual stream, published once for the consumer after next
 #pragma unroll
         for (int r = 0; r < QIN_ITEMS; ++r) {
@@ -399,7 +399,7 @@ __device__ __forceinline__ void quantize_input(const InputSrc& I, const float* _
                     reinterpret_cast<float4*>(I.x_out)[2 * i] = make_float4(v[r][0], v[r][1], v[r][2], v[r][3]);
                     reinterpret_cast<float4*>(I.x_out)[2 * i + 1] = make_float4(v[r][4], v[r][5], v[r][6], v[r][7]);
                 }
-                if (I.x_out_ll) {
+                if (LL && I.x_out_ll) {
                     uint2* o = I.x_out_ll + 8 * (size_t)i;
 #pragma unroll
                     for (int k = 0; k < 8; k += 2) st_ll2(o + k, __float_as_uint(v[r][k]), __float_as_uint(v[r][k + 1]), I.x_out_seq);
@@ -618,12 +618,12 @@ __device__ __forceinline__ void reduce_block(const GemvParams& P, int b, uint32_
 // The input side of a GEMV kernel: fills the shared-memory arrays the dot products read (int8 values, block scales,
 // scaled block sums) from whichever source the launch names, and returns the factor the dot products still have to be
 // multiplied with (1/rms of the input when the records carry the un-normalised vector, else 1).
-template <int GEMV_WARPS>
+template <int GEMV_WARPS, bool LEAN = false>
 __device__ __forceinline__ float gemv_input(const GemvParams& P, uint32_t gen, uint32_t seq, int K, int8_t* xq, float* xs, float* xsf,
                                             float* xsf32, float* misc, int warp, int lane) {
     constexpr int GEMV_THREADS = GEMV_WARPS * 32;
     float in_scale = 1.0f;            // 1/rms of the input when the records carry the un-normalised vector
-    if (P.rec && !P.post_w) {
+    if (!LEAN && P.rec && !P.post_w) {
         const unsigned long long budget = (*reinterpret_cast<volatile int*>(P.status) != 0) ? 0ull : P.wait_ns;
         const int nblk32 = K / 32;
         // the lowest CTAs start first: two of their warps each form blocks
@@ -640,9 +640,9 @@ __device__ __forceinline__ float gemv_input(const GemvParams& P, uint32_t gen, u
         I.post_src = P.post_src; I.post_w = P.post_w; I.x_out = P.x_out; I.x_out_ll = P.x_out_ll;
         I.x_out_seq = gen * LL_SEQ_MUL + P.x_out_seq_add;
         I.status = P.status; I.wait_ns = P.wait_ns;
-        if (P.post_w) quantize_input<(GEMV_WARPS >= 16 ? 1 : 2), true>(I, P.norm_w, P.eps, P.norm_add_one, K, xq, xs, xsf, xsf32, misc);
-        else if (K <= 2 * 8 * GEMV_THREADS) quantize_input<2>(I, P.norm_w, P.eps, P.norm_add_one, K, xq, xs, xsf, xsf32, misc);
-        else quantize_input<(GEMV_WARPS >= 16 ? 3 : 5)>(I, P.norm_w, P.eps, P.norm_add_one, K, xq, xs, xsf, xsf32, misc);
+        if (P.post_w) quantize_input<(GEMV_WARPS >= 16 ? 1 : 2), true, !LEAN>(I, P.norm_w, P.eps, P.norm_add_one, K, xq, xs, xsf, xsf32, misc);
+        else if (K <= 2 * 8 * GEMV_THREADS) quantize_input<2, false, !LEAN>(I, P.norm_w, P.eps, P.norm_add_one, K, xq, xs, xsf, xsf32, misc);
+        else quantize_input<(GEMV_WARPS >= 16 ? 3 : 5), false, !LEAN>(I, P.norm_w, P.eps, P.norm_add_one, K, xq, xs, xsf, xsf32, misc);
     }
     return in_scale;
 }
@@ -741,7 +741,9 @@ __device__ __forceinline__ void gemv_argmax_tail(const GemvParams& P, float best
 
 }
 
-template <int GEMV_WARPS>
+// LEAN: the plain flow only (fp32 vectors in and out, launch-boundary wait): the slot hand-over, the input records and the
+// L2 prefetch of the next weights are compiled out, which keeps the block loop's registers free of their state.
+template <int GEMV_WARPS, bool LEAN = false>
 __global__ void __launch_bounds__(GEMV_WARPS * 32, GEMV_WARPS >= 16 ? 1 : 2) gemv_kernel(const __grid_constant__ GemvParams P) {
     constexpr int GEMV_THREADS = GEMV_WARPS * 32;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -818,7 +820,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32, GEMV_WARPS >= 16 ? 1 : 2) gem
         for (int i = tid * 32; i < K; i += GEMV_THREADS * 32)
             asm volatile("prefetch.global.L2 [%0];" ::"l"(P.norm_w + i));
     }
-    if (lane == 1) {
+    if (!LEAN && lane == 1) {
         // this CTA's share of the next kernel's weights, 16 KB bulk prefetches spread over the warps
         constexpr unsigned CH = 16384;
 #pragma unroll
@@ -831,7 +833,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32, GEMV_WARPS >= 16 ? 1 : 2) gem
         }
     }
     pdl_launch_dependents();
-    const bool dataflow = P.x_ll != nullptr;
+    const bool dataflow = !LEAN && P.x_ll != nullptr;
     // plain mode: the input is complete once the predecessor has finished.  Dataflow mode: never wait for the
     // launch boundary, the input slots validate themselves.
     if (!dataflow || P.hard_wait) pdl_wait();
@@ -840,7 +842,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32, GEMV_WARPS >= 16 ? 1 : 2) gem
     const uint32_t gen = P.gen ? *reinterpret_cast<const volatile uint32_t*>(P.gen) : 0u;
     const uint32_t seq = gen * LL_SEQ_MUL + P.out_seq_add;
 
-    const float in_scale = gemv_input<GEMV_WARPS>(P, gen, seq, K, xq, xs, xsf, xsf32, misc, warp, lane);
+    const float in_scale = gemv_input<GEMV_WARPS, LEAN>(P, gen, seq, K, xq, xs, xsf, xsf32, misc, warp, lane);
     stamp(2);
 
     // eight 4-lane groups per warp; neighbouring groups take neighbouring rows (same x addresses -> broadcast)
@@ -873,7 +875,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32, GEMV_WARPS >= 16 ? 1 : 2) gem
                 return;
             }
         }
-        if (J.out_ll) st_ll(J.out_ll + n, __float_as_uint(r), seq);
+        if (!LEAN && J.out_ll) st_ll(J.out_ll + n, __float_as_uint(r), seq);
         else J.out[n] = r;
     };
 
