@@ -268,20 +268,24 @@ static int ensure_attrs() {
     if (g_attr_done) return 0;
     // 227 KB per CTA is shared between the kernel's static and dynamic shared memory
     cudaFuncAttributes fa;
-    PTB_CUDA_OK(cudaFuncGetAttributes(&fa, (gemv_kernel<8, false>)));
+    PTB_CUDA_OK(cudaFuncGetAttributes(&fa, (gemv_kernel<8, 0>)));
     int optin = 0, dev = 0;
     PTB_CUDA_OK(cudaGetDevice(&dev));
     PTB_CUDA_OK(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
     g_gemv_max_dyn = (size_t)optin - fa.sharedSizeBytes;
     const int dyn = (int)g_gemv_max_dyn;
-    PTB_CUDA_OK(cudaFuncSetAttribute((gemv_kernel<8, false>), cudaFuncAttributeMaxDynamicSharedMemorySize, dyn));
-    PTB_CUDA_OK(cudaFuncSetAttribute((gemv_kernel<16, false>), cudaFuncAttributeMaxDynamicSharedMemorySize, dyn));
-    PTB_CUDA_OK(cudaFuncSetAttribute((gemv16_kernel<8, false>), cudaFuncAttributeMaxDynamicSharedMemorySize, dyn));
-    PTB_CUDA_OK(cudaFuncSetAttribute((gemv16_kernel<16, false>), cudaFuncAttributeMaxDynamicSharedMemorySize, dyn));
-    PTB_CUDA_OK(cudaFuncSetAttribute((gemv_kernel<8, true>), cudaFuncAttributeMaxDynamicSharedMemorySize, dyn));
-    PTB_CUDA_OK(cudaFuncSetAttribute((gemv_kernel<16, true>), cudaFuncAttributeMaxDynamicSharedMemorySize, dyn));
-    PTB_CUDA_OK(cudaFuncSetAttribute((gemv16_kernel<8, true>), cudaFuncAttributeMaxDynamicSharedMemorySize, dyn));
-    PTB_CUDA_OK(cudaFuncSetAttribute((gemv16_kernel<16, true>), cudaFuncAttributeMaxDynamicSharedMemorySize, dyn));
+    PTB_CUDA_OK(cudaFuncSetAttribute((gemv_kernel<8, 0>), cudaFuncAttributeMaxDynamicSharedMemorySize, dyn));
+    PTB_CUDA_OK(cudaFuncSetAttribute((gemv_kernel<16, 0>), cudaFuncAttributeMaxDynamicSharedMemorySize, dyn));
+    PTB_CUDA_OK(cudaFuncSetAttribute((gemv16_kernel<8, 0>), cudaFuncAttributeMaxDynamicSharedMemorySize, dyn));
+    PTB_CUDA_OK(cudaFuncSetAttribute((gemv16_kernel<16, 0>), cudaFuncAttributeMaxDynamicSharedMemorySize, dyn));
+    PTB_CUDA_OK(cudaFuncSetAttribute((gemv_kernel<8, 1>), cudaFuncAttributeMaxDynamicSharedMemorySize, dyn));
+    PTB_CUDA_OK(cudaFuncSetAttribute((gemv_kernel<16, 1>), cudaFuncAttributeMaxDynamicSharedMemorySize, dyn));
+    PTB_CUDA_OK(cudaFuncSetAttribute((gemv16_kernel<8, 1>), cudaFuncAttributeMaxDynamicSharedMemorySize, dyn));
+    PTB_CUDA_OK(cudaFuncSetAttribute((gemv16_kernel<16, 1>), cudaFuncAttributeMaxDynamicSharedMemorySize, dyn));
+    PTB_CUDA_OK(cudaFuncSetAttribute((gemv_kernel<8, 2>), cudaFuncAttributeMaxDynamicSharedMemorySize, dyn));
+    PTB_CUDA_OK(cudaFuncSetAttribute((gemv_kernel<16, 2>), cudaFuncAttributeMaxDynamicSharedMemorySize, dyn));
+    PTB_CUDA_OK(cudaFuncSetAttribute((gemv16_kernel<8, 2>), cudaFuncAttributeMaxDynamicSharedMemorySize, dyn));
+    PTB_CUDA_OK(cudaFuncSetAttribute((gemv16_kernel<16, 2>), cudaFuncAttributeMaxDynamicSharedMemorySize, dyn));
     g_attr_done = true;
     return 0;
 }
@@ -347,31 +351,29 @@ static cudaError_t launch_attn(const AttnParams& a, int n_kv_heads, cudaStream_t
     }
 }
 
-// A launch that uses none of the slot hand-over, the input records or the L2 prefetch runs the lean instantiation.
-static bool gemv_is_lean(const GemvParams& p) {
+// Which instantiation serves a launch: 1 (lean) if it uses none of the slot hand-over, the input records or the L2
+// prefetch; 2 if its input comes as records and nothing else is needed; 0 otherwise.
+static int gemv_mode(const GemvParams& p) {
     static const int on = env_int("PTB_GEMV_LEAN", 1);
-    if (!on || p.x_ll || p.part_ll || p.rec || p.x_out_ll) return false;
-    for (int i = 0; i < p.njobs; ++i)
-        if (p.job[i].out_ll) return false;
+    if (!on) return 0;
     for (int i = 0; i < 4; ++i)
-        if (p.pf_bytes[i]) return false;
-    return true;
+        if (p.pf_bytes[i]) return 0;
+    if (p.rec && !p.post_w && !p.post_src) return 2;
+    if (p.x_ll || p.part_ll || p.rec || p.x_out_ll) return 0;
+    for (int i = 0; i < p.njobs; ++i)
+        if (p.job[i].out_ll) return 0;
+    return 1;
 }
+#define PTB_GEMV_DISPATCH(KERN, W, THREADS)                                                                              \
+    (mode == 1   ? launch_pdl(KERN<W, 1>, dim3(L.grid), dim3(THREADS), L.smem, st, pdl, L.p)                             \
+     : mode == 2 ? launch_pdl(KERN<W, 2>, dim3(L.grid), dim3(THREADS), L.smem, st, pdl, L.p)                             \
+                 : launch_pdl(KERN<W, 0>, dim3(L.grid), dim3(THREADS), L.smem, st, pdl, L.p))
 static cudaError_t launch_gemv(const GemvLaunch& L, cudaStream_t st, bool pdl) {
-    const bool lean = gemv_is_lean(L.p);
-    if (L.t16) {
-        if (L.p.warps == 16)
-            return lean ? launch_pdl(gemv16_kernel<16, true>, dim3(L.grid), dim3(512), L.smem, st, pdl, L.p)
-                        : launch_pdl(gemv16_kernel<16, false>, dim3(L.grid), dim3(512), L.smem, st, pdl, L.p);
-        return lean ? launch_pdl(gemv16_kernel<8, true>, dim3(L.grid), dim3(256), L.smem, st, pdl, L.p)
-                    : launch_pdl(gemv16_kernel<8, false>, dim3(L.grid), dim3(256), L.smem, st, pdl, L.p);
-    }
-    if (L.p.warps == 16)
-        return lean ? launch_pdl(gemv_kernel<16, true>, dim3(L.grid), dim3(512), L.smem, st, pdl, L.p)
-                    : launch_pdl(gemv_kernel<16, false>, dim3(L.grid), dim3(512), L.smem, st, pdl, L.p);
-    return lean ? launch_pdl(gemv_kernel<8, true>, dim3(L.grid), dim3(256), L.smem, st, pdl, L.p)
-                : launch_pdl(gemv_kernel<8, false>, dim3(L.grid), dim3(256), L.smem, st, pdl, L.p);
+    const int mode = gemv_mode(L.p);
+    if (L.t16) return L.p.warps == 16 ? PTB_GEMV_DISPATCH(gemv16_kernel, 16, 512) : PTB_GEMV_DISPATCH(gemv16_kernel, 8, 256);
+    return L.p.warps == 16 ? PTB_GEMV_DISPATCH(gemv_kernel, 16, 512) : PTB_GEMV_DISPATCH(gemv_kernel, 8, 256);
 }
+#undef PTB_GEMV_DISPATCH
 
 // ------------------------------------------------------------------------------------------ standalone op entry points (tests, benches)
 
@@ -781,7 +783,7 @@ static int engine_plan_dataflow(Engine* e) {
 
 static int engine_plan(Engine* e) {
     // PTB_DECODE_FLOW: "plain" (launch-boundary waits; producer-side all-reduce under tensor parallelism) or "dataflow"
-    // (slot hand-over, consumer-side all-reduce).  Measured on B200: plain is ahead on 1 and 2 GPUs, dataflow from 4 (790 vs 784 tok/s at 4, 868 vs 787 at 8), where
+    // (slot hand-over, consumer-side all-reduce).  Measured on B200: plain is ahead on 1 and 2 GPUs (758 vs 736 tok/s at 2), level at 4 (841 vs 840) and behind at 8 (787 vs 868), where
     // the per-kernel hand-over latency is all that is left of a step.
     // "external" (tensor parallel only): the plain flow without any in-kernel exchange; the caller enqueues launch ranges
     // and all-reduces the residual buffer between them (ptb_engine_enqueue_range), which is how the NCCL baseline runs.

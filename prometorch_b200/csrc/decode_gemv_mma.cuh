@@ -247,9 +247,10 @@ __device__ __forceinline__ void q6k_block_mma(const uint8_t* blk, const int8_t* 
 // Job geometry for this kernel (GemvJob fields reused): KS = K-groups per row tile, seg_base / seg_rem = blocks per
 // K-group (the first seg_rem groups one block longer); a CTA owns whole row tiles and its warps take (tile, K-group)
 // items in turn, each warp streaming the blocks of its items through its private ring, one block per ring slot.
-template <int GEMV_WARPS, bool LEAN = false>
+template <int GEMV_WARPS, int MODE = 0>
 __global__ void __launch_bounds__(GEMV_WARPS * 32, GEMV_WARPS >= 16 ? 1 : 2) gemv16_kernel(const __grid_constant__ GemvParams P) {
     constexpr int GEMV_THREADS = GEMV_WARPS * 32;
+    constexpr bool LEAN = MODE == 1;
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int K = P.K, S = P.stages;
@@ -313,13 +314,13 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32, GEMV_WARPS >= 16 ? 1 : 2) gem
         for (int i = tid * 32; i < K; i += GEMV_THREADS * 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(P.norm_w + i));
     }
     pdl_launch_dependents();
-    const bool dataflow = !LEAN && P.x_ll != nullptr;
+    const bool dataflow = MODE == 2 || (!LEAN && P.x_ll != nullptr);
     if (!dataflow || P.hard_wait) pdl_wait();
     __syncthreads();
     stamp(1);
     const uint32_t gen = P.gen ? *reinterpret_cast<const volatile uint32_t*>(P.gen) : 0u;
     const uint32_t seq = gen * LL_SEQ_MUL + P.out_seq_add;
-    const float in_scale = gemv_input<GEMV_WARPS, LEAN>(P, gen, seq, K, xq, xs, xsf, xsf32, misc, warp, lane);
+    const float in_scale = gemv_input<GEMV_WARPS, MODE>(P, gen, seq, K, xq, xs, xsf, xsf32, misc, warp, lane);
     stamp(2);
 
     float best_v = -INFINITY;

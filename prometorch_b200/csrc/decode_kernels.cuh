@@ -618,12 +618,13 @@ __device__ __forceinline__ void reduce_block(const GemvParams& P, int b, uint32_
 // The input side of a GEMV kernel: fills the shared-memory arrays the dot products read (int8 values, block scales,
 // scaled block sums) from whichever source the launch names, and returns the factor the dot products still have to be
 // multiplied with (1/rms of the input when the records carry the un-normalised vector, else 1).
-template <int GEMV_WARPS, bool LEAN = false>
+template <int GEMV_WARPS, int MODE = 0>
 __device__ __forceinline__ float gemv_input(const GemvParams& P, uint32_t gen, uint32_t seq, int K, int8_t* xq, float* xs, float* xsf,
                                             float* xsf32, float* misc, int warp, int lane) {
     constexpr int GEMV_THREADS = GEMV_WARPS * 32;
+    constexpr bool LEAN = MODE == 1;
     float in_scale = 1.0f;            // 1/rms of the input when the records carry the un-normalised vector
-    if (!LEAN && P.rec && !P.post_w) {
+    if (MODE == 2 || (!LEAN && P.rec && !P.post_w)) {
         const unsigned long long budget = (*reinterpret_cast<volatile int*>(P.status) != 0) ? 0ull : P.wait_ns;
         const int nblk32 = K / 32;
         // the lowest CTAs start first: two of their warps each form blocks
@@ -632,7 +633,7 @@ __device__ __forceinline__ float gemv_input(const GemvParams& P, uint32_t gen, u
         const float ssq = copy_records<(GEMV_WARPS >= 16 ? 3 : 5)>(P.rec, nblk32, seq, xq, xs, xsf, xsf32, P.status, budget, misc);
         if (P.norm_w) in_scale = rsqrtf(ssq / (float)K + P.eps);
         __syncthreads();
-    } else {
+    } else if (MODE != 2) {
         InputSrc I;
         I.x = P.x; I.x_ll = P.x_ll; I.x_seq = gen * LL_SEQ_MUL + P.x_seq_add;
         I.part_ll = P.part_ll; I.nparts = P.part_ll ? P.nparts : 0; I.part_stride = P.part_stride;
@@ -741,11 +742,13 @@ __device__ __forceinline__ void gemv_argmax_tail(const GemvParams& P, float best
 
 }
 
-// LEAN: the plain flow only (fp32 vectors in and out, launch-boundary wait): the slot hand-over, the input records and the
-// L2 prefetch of the next weights are compiled out, which keeps the block loop's registers free of their state.
-template <int GEMV_WARPS, bool LEAN = false>
+// MODE 0: everything.  MODE 1 ("lean"): the plain flow only (fp32 vectors in and out, launch-boundary wait); the slot
+// hand-over, the input records and the L2 prefetch of the next weights are compiled out, which frees the block loop of
+// their registers (no spills).  MODE 2: the dataflow with input records only (no plain or slot-polled input path).
+template <int GEMV_WARPS, int MODE = 0>
 __global__ void __launch_bounds__(GEMV_WARPS * 32, GEMV_WARPS >= 16 ? 1 : 2) gemv_kernel(const __grid_constant__ GemvParams P) {
     constexpr int GEMV_THREADS = GEMV_WARPS * 32;
+    constexpr bool LEAN = MODE == 1;
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int K = P.K, S = P.stages;
@@ -820,7 +823,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32, GEMV_WARPS >= 16 ? 1 : 2) gem
         for (int i = tid * 32; i < K; i += GEMV_THREADS * 32)
             asm volatile("prefetch.global.L2 [%0];" ::"l"(P.norm_w + i));
     }
-    if (!LEAN && lane == 1) {
+    if (MODE == 0 && lane == 1) {
         // this CTA's share of the next kernel's weights, 16 KB bulk prefetches spread over the warps
         constexpr unsigned CH = 16384;
 #pragma unroll
@@ -833,7 +836,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32, GEMV_WARPS >= 16 ? 1 : 2) gem
         }
     }
     pdl_launch_dependents();
-    const bool dataflow = !LEAN && P.x_ll != nullptr;
+    const bool dataflow = MODE == 2 || (!LEAN && P.x_ll != nullptr);
     // plain mode: the input is complete once the predecessor has finished.  Dataflow mode: never wait for the
     // launch boundary, the input slots validate themselves.
     if (!dataflow || P.hard_wait) pdl_wait();
@@ -842,7 +845,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32, GEMV_WARPS >= 16 ? 1 : 2) gem
     const uint32_t gen = P.gen ? *reinterpret_cast<const volatile uint32_t*>(P.gen) : 0u;
     const uint32_t seq = gen * LL_SEQ_MUL + P.out_seq_add;
 
-    const float in_scale = gemv_input<GEMV_WARPS, LEAN>(P, gen, seq, K, xq, xs, xsf, xsf32, misc, warp, lane);
+    const float in_scale = gemv_input<GEMV_WARPS, MODE>(P, gen, seq, K, xq, xs, xsf, xsf32, misc, warp, lane);
     stamp(2);
 
     // eight 4-lane groups per warp; neighbouring groups take neighbouring rows (same x addresses -> broadcast)

@@ -182,15 +182,15 @@ def _to_kernel_type(raw: torch.Tensor, qtype: GGMLType, cols: int, layout: int =
 
 
 def default_layout(tp_world: int = 1) -> int:
-    """PTB_GEMV_LAYOUT (t16 / segment) if set.  Otherwise by measurement on the Qwen3-4B shape: one and two GPUs stream
-    tiles of 16 rows through the tensor-pipe kernel (635 vs 627 tok/s on one GPU, 729 vs 697 on two); from four ranks on,
-    where a rank's matrices are a quarter of the size or less and a step is latency-bound, the dp4a kernel's segment
-    layout with two 8-warp CTAs per SM is ahead (790 vs 762 tok/s at 4 GPUs)."""
+    """PTB_GEMV_LAYOUT (t16 / segment) if set.  Otherwise by measurement on the Qwen3-4B shape: one GPU streams tiles of
+    16 rows through the tensor-pipe kernel (660 vs 629 tok/s); tensor-parallel ranks, whose matrices are a fraction of the
+    size and whose steps are latency-bound, run the dp4a kernel's segment layout with two 8-warp CTAs per SM (758 vs 752
+    tok/s at 2 GPUs, 840 vs 798 at 4)."""
     import os
     v = os.environ.get("PTB_GEMV_LAYOUT")
     if v is not None:
         return LAYOUT_SEGMENT if v == "segment" else LAYOUT_T16
-    return LAYOUT_T16 if tp_world <= 2 else LAYOUT_SEGMENT
+    return LAYOUT_T16 if tp_world <= 1 else LAYOUT_SEGMENT
 
 
 def pack_weight(raw: torch.Tensor, qtype: GGMLType, cols: int, device, rows=None, kblocks=None,

@@ -21,6 +21,7 @@ NATIVE_ENV: Dict[str, str] = {
     "PTB_GEMV_LAYOUT": "t16 (default: tiles of 16 rows, tensor-pipe GEMV) or segment (dp4a GEMV): weight layout chosen at load",
     "PTB_GEMV_WARPS": "warps per CTA of the decode GEMV: 8 or 16 (default 16 for the tile layout, 8 for the segment layout)",
     "PTB_GEMV_CTAS_PER_SM": "CTAs per SM of the decode GEMV (default 1 for the tile layout, 2 for the segment layout)",
+    "PTB_GEMV_LEAN": "1 (default): a decode GEMV launch runs the instantiation that holds only the flow it uses (plain, or dataflow with input records); 0: the all-purpose instantiation",
     "PTB_GEMV_STAGES": "ring depth per warp of the decode GEMV (default: as many as fit, at most 8; 4 for the segment layout)",
     "PTB_GEMV_SMEM_KB": "shared-memory budget per GEMV CTA in KB (default 128 at 16 warps, 100 at 8)",
     "PTB_GEMV_TILE_KB": "segment layout: upper bound of a warp tile in KB (default 6)",
