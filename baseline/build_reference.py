@@ -49,7 +49,8 @@ def build(src: str, jobs: int = 8, build_dir: str | None = None, log=sys.stdout)
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--src", default=os.environ.get("PROMETORCH_REFERENCE_SRC", "/root/reference"))
+    ap.add_argument("--src", default=os.environ.get("PROMETORCH_REFERENCE_SRC"), required="PROMETORCH_REFERENCE_SRC" not in os.environ,
+                    help="checkout of the reference project (or set PROMETORCH_REFERENCE_SRC)")
     ap.add_argument("--jobs", type=int, default=os.cpu_count() or 8)
     ap.add_argument("--build-dir", default=None)
     a = ap.parse_args()
