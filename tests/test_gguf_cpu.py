@@ -309,3 +309,14 @@ def test_lowrank_output_projection_finds_the_exact_argmax():
     f = LowRankOutputProj(rank=32, candidate_k=16).init_from_float(W)
     x = torch.randn(hidden, generator=g)
     assert 0 <= f.decode_greedy(x) < vocab
+
+
+def test_weight_layout_follows_the_number_of_ranks(monkeypatch):
+    from prometorch_b200.io.gguf_model import LAYOUT_SEGMENT, LAYOUT_T16, default_layout
+    monkeypatch.delenv("PTB_GEMV_LAYOUT", raising=False)
+    assert default_layout(1) == LAYOUT_T16
+    assert [default_layout(w) for w in (2, 4, 8)] == [LAYOUT_SEGMENT] * 3
+    monkeypatch.setenv("PTB_GEMV_LAYOUT", "t16")
+    assert default_layout(8) == LAYOUT_T16
+    monkeypatch.setenv("PTB_GEMV_LAYOUT", "segment")
+    assert default_layout(1) == LAYOUT_SEGMENT
