@@ -425,10 +425,87 @@ class GGUFModel {
             d.qtype = t.type == gguf::F16 ? 2 : 3;
             d.rowbytes = cols * (t.type == gguf::F16 ? 2 : 4);
             d.w = upload(src, (size_t)rows * d.rowbytes);
+        } else if (t.type == gguf::Q8_0 || t.type == gguf::Q5_K) {
+            // other block types become an fp16 table, as in the Python loader (rows are looked up one at a time)
+            std::vector<float> out((size_t)rows * cols);
+            for (int r = 0; r < rows; ++r) {
+                float* y = out.data() + (size_t)r * cols;
+                if (t.type == gguf::Q8_0) {
+                    const uint8_t* row = src + (size_t)r * (cols / 32) * 34;
+                    for (int b = 0; b < cols / 32; ++b) {
+                        const float dd = half_to_float(row + b * 34);
+                        const int8_t* q = (const int8_t*)(row + b * 34 + 2);
+                        for (int i = 0; i < 32; ++i) y[b * 32 + i] = dd * (float)q[i];
+                    }
+                } else {
+                    const uint8_t* row = src + (size_t)r * nblk * 176;
+                    for (int b = 0; b < nblk; ++b) {
+                        const uint8_t* blk = row + b * 176;
+                        const float dd = half_to_float(blk), dmin = half_to_float(blk + 2);
+                        const uint8_t *sc = blk + 4, *qh = blk + 16, *qs = blk + 48;
+                        for (int is = 0; is < 8; ++is) {          // sub-block of 32 values: 6-bit scale and minimum
+                            int scv, mv;
+                            if (is < 4) { scv = sc[is] & 63; mv = sc[is + 4] & 63; }
+                            else { scv = (sc[is + 4] & 0xF) | ((sc[is - 4] >> 6) << 4); mv = (sc[is + 4] >> 4) | ((sc[is] >> 6) << 4); }
+                            for (int l = 0; l < 32; ++l) {
+                                const uint8_t qb = qs[(is >> 1) * 32 + l];
+                                const int q = ((is & 1) ? (qb >> 4) : (qb & 0xF)) | (((qh[l] >> is) & 1) << 4);
+                                y[b * 256 + is * 32 + l] = dd * scv * q - dmin * mv;
+                            }
+                        }
+                    }
+                }
+            }
+            std::vector<uint16_t> h(out.size());
+            for (size_t i = 0; i < out.size(); ++i) h[i] = float_to_half(out[i]);
+            d.qtype = 2;
+            d.rowbytes = cols * 2;
+            d.w = upload(h.data(), h.size() * 2);
         } else {
             throw std::runtime_error("GGUFModel (C++): embedding table of block type " + std::to_string(t.type) + " is not handled here");
         }
         return d;
+    }
+    static uint16_t float_to_half(float f) {          // round to nearest even, like torch's conversion
+        uint32_t x;
+        std::memcpy(&x, &f, 4);
+        const uint32_t sign = (x >> 16) & 0x8000u;
+        x &= 0x7FFFFFFFu;
+        if (x >= 0x7F800000u) return (uint16_t)(sign | 0x7C00u | (x > 0x7F800000u ? 0x200u : 0u));
+        if (x >= 0x477FF000u) return (uint16_t)(sign | 0x7C00u);                     // rounds to infinity
+        if (x < 0x38800000u) {                                                       // subnormal half or zero
+            if (x < 0x33000000u) return (uint16_t)sign;
+            const int e = (int)(x >> 23);
+            uint32_t m = (x & 0x7FFFFFu) | 0x800000u;
+            const int shift = 126 - e;                                               // 14 .. 24
+            uint32_t hm = m >> shift;
+            const uint32_t rem = m & ((1u << shift) - 1u), halfway = 1u << (shift - 1);
+            if (rem > halfway || (rem == halfway && (hm & 1u))) ++hm;
+            return (uint16_t)(sign | hm);
+        }
+        uint32_t hm = ((x - 0x38000000u) >> 13);
+        const uint32_t rem = x & 0x1FFFu;
+        if (rem > 0x1000u || (rem == 0x1000u && (hm & 1u))) ++hm;
+        return (uint16_t)(sign | hm);
+    }
+    static float half_to_float(const uint8_t* p) {
+        uint16_t h;
+        std::memcpy(&h, p, 2);
+        const uint32_t sign = (uint32_t)(h & 0x8000u) << 16, exp = (h >> 10) & 0x1F, man = h & 0x3FFu;
+        uint32_t bits;
+        if (exp == 0) {
+            if (man == 0) bits = sign;
+            else {                                    // subnormal: normalise
+                int e = -1;
+                uint32_t m = man;
+                do { ++e; m <<= 1; } while (!(m & 0x400u));
+                bits = sign | ((uint32_t)(127 - 15 - e) << 23) | ((m & 0x3FFu) << 13);
+            }
+        } else if (exp == 31) bits = sign | 0x7F800000u | (man << 13);
+        else bits = sign | ((exp + 112) << 23) | (man << 13);
+        float f;
+        std::memcpy(&f, &bits, 4);
+        return f;
     }
     void rope_tables() {
         const int half = config.head_dim / 2;

@@ -366,8 +366,11 @@ def test_batched_sampler_matches_single_request_sampler():
     assert [s.n_hist for s in a] == [t.n_hist for t in b] and all(torch.equal(s.hist[:s.n_hist], t.hist[:t.n_hist]) for s, t in zip(a, b))
 
 
-def test_cpp_gguf_model_generates_the_same_ids(tmp_path):
-    """promethorch/gguf.h (C++ reader, repack and engine driver) against the Python GGUFModel on the same file."""
+@pytest.mark.parametrize("q_main,q_more", [(Q.GGMLType.Q4_K, Q.GGMLType.Q6_K), (Q.GGMLType.Q5_K, Q.GGMLType.Q8_0),
+                                           (Q.GGMLType.Q8_0, Q.GGMLType.F16)], ids=["q4_k_m", "q5k+q8_0", "q8_0+f16"])
+def test_cpp_gguf_model_generates_the_same_ids(tmp_path, q_main, q_more):
+    """promethorch/gguf.h (C++ reader, repack of every streamed weight type, engine driver) against the Python GGUFModel
+    on the same file."""
     import os
     import shutil
     import subprocess
@@ -386,7 +389,8 @@ def test_cpp_gguf_model_generates_the_same_ids(tmp_path):
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stderr[-3000:]
     path = str(tmp_path / "cpp.gguf")
-    write_synthetic_gguf(path, tiny_qwen3_config(layers=2, hidden=512, heads=8, kv_heads=2, inter=1024, vocab=1024), seed=3, device="cpu")
+    write_synthetic_gguf(path, tiny_qwen3_config(layers=2, hidden=512, heads=8, kv_heads=2, inter=1024, vocab=1024), seed=3, device="cpu",
+                         q_main=q_main, q_more=q_more)
     prompt = [5, 300, 77, 1000, 12]
     m = GGUFModel(path, device="cuda", max_seq=256)
     want = m.run_script(prompt, 8)
