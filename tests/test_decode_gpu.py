@@ -456,3 +456,35 @@ def test_lowrank_head_agrees_with_the_engine(tiny_model):
     assert hits >= 6, hits
     m.check_status()
     m.close()
+
+
+def test_deepseek2_on_the_gpu_matches_the_cpu_model(tmp_path):
+    """The latent-attention + mixture-of-experts decoder in bf16 on the GPU against its fp32 run on the CPU."""
+    from prometorch_b200.io.synthetic import write_synthetic_deepseek2
+    from prometorch_b200.models.deepseek2 import DeepSeek2Model
+    p = str(tmp_path / "ds2.gguf")
+    write_synthetic_deepseek2(p, seed=9)
+    cpu = DeepSeek2Model(p, device="cpu", max_seq=64)
+    gpu = DeepSeek2Model(p, device="cuda", max_seq=64, dtype=torch.bfloat16)
+    toks = [5, 100, 17, 250, 31, 8]
+    a = cpu.forward(toks)
+    b = torch.cat([gpu.forward(toks[:4]), gpu.forward(toks[4:])]).cpu()
+    cos = torch.nn.functional.cosine_similarity(a, b, dim=-1)
+    assert float(cos.min()) > 0.99, cos
+    assert len(gpu.generate(toks[:3], max_new_tokens=4)) <= 4
+
+
+def test_generate_cli_with_a_draft_model(tmp_path):
+    """`python -m prometorch_b200.generate --draft`: greedy speculative decoding from the command line."""
+    import subprocess
+    import sys
+    import os
+    cfg = tiny_qwen3_config(layers=2, hidden=512, heads=8, kv_heads=2, inter=1024, vocab=1000)
+    t, d = str(tmp_path / "t.gguf"), str(tmp_path / "d.gguf")
+    write_synthetic_gguf(t, cfg, seed=31, device="cuda", std=0.05)
+    write_synthetic_gguf(d, tiny_qwen3_config(layers=1, hidden=256, heads=4, kv_heads=2, inter=512, vocab=1000), seed=32, device="cuda", std=0.05)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-m", "prometorch_b200.generate", t, "t300 t301 t302 t303 t304 t305 t306 t307 t308 t309", "--greedy",
+                        "--max-tokens", "10", "--draft", d, "--spec-k", "3"], capture_output=True, text=True, timeout=300, cwd=root)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "[Speculative]" in r.stdout and "target passes" in r.stdout, r.stdout[-1500:]
