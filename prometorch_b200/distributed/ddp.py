@@ -146,13 +146,17 @@ class _Bucket:
 class DistributedDataParallel(nn.Module):
     def __init__(self, module: nn.Module, process_group: Optional[ProcessGroup] = None, broadcast_parameters: bool = True,
                  bucket_mb: float = 25.0, symm=None, comm_ctas: int = 32, check_every: int = 1,
-                 fp32_master_grads: bool = False):
+                 fp32_master_grads: bool = False, metrics=None):
         """``check_every``: with the fused (symmetric-memory) reduction, every that many calls
         ``finish_gradient_synchronization()`` waits for the reductions and raises ``CollectiveTimeout`` if a kernel
         gave up waiting for a peer, so the optimizer never steps on gradients that were not reduced (0 = only
         ``check()`` looks).  ``fp32_master_grads``: bf16 buckets are reduced into fp32 copies
-        (``master_grad(param)``) by the same kernel, for optimizers that keep fp32 master weights."""
+        (``master_grad(param)``) by the same kernel, for optimizers that keep fp32 master weights.
+        ``metrics``: a ``utils.metrics.MetricsWriter``; every bucket reduction is then timed (CUDA events on the
+        communication stream, the host clock on CPU) and logged with its bytes on the wire, GB/s and fraction of the
+        NVLink roofline when ``finish_gradient_synchronization()`` collects it (this waits for the reductions)."""
         super().__init__()
+        self.metrics = metrics
         self.check_every, self._finish_calls = int(check_every), 0
         self.fp32_master_grads = bool(fp32_master_grads)
         self.module = module
@@ -220,10 +224,18 @@ class DistributedDataParallel(nn.Module):
     def _launch(self, b: _Bucket):
         b.launched = True
         scale = 1.0 / self.world_size
+        timed = self.metrics is not None
+        b.t0 = b.seconds = None
+
+        def start_event():
+            if timed:
+                b.t0 = torch.cuda.Event(enable_timing=True)
+                b.t0.record(self._comm_stream)
         if b.channel is not None:
             cur = torch.cuda.current_stream(b.flat.device)
             self._comm_stream.wait_stream(cur)
             with torch.cuda.stream(self._comm_stream):
+                start_event()
                 ch = b.channel
                 if b.master is not None:
                     N.check(N.lib().ptb_ddp_allreduce_master(ch.bufs, b.master_ptrs, ch.flag_ptrs, self.rank, self.world_size,
@@ -234,18 +246,22 @@ class DistributedDataParallel(nn.Module):
                     N.check(N.lib().ptb_ddp_allreduce(ch.bufs, ch.flag_ptrs, self.rank, self.world_size, b.numel,
                                                       int(b.flat.dtype == torch.bfloat16), scale, ch.next_seq(), ch.ticket.data_ptr(),
                                                       ch.status.data_ptr(), self.comm_ctas, self._comm_stream.cuda_stream), "ddp_allreduce")
-                b.event = torch.cuda.Event()
+                b.event = torch.cuda.Event(enable_timing=timed)
                 b.event.record(self._comm_stream)
         elif isinstance(self.process_group, TorchProcessGroup) and b.flat.is_cuda:
             cur = torch.cuda.current_stream(b.flat.device)
             self._comm_stream.wait_stream(cur)
             with torch.cuda.stream(self._comm_stream):
+                start_event()
                 self.process_group.all_reduce(b.flat, ReduceOp.AVG)
-                b.event = torch.cuda.Event()
+                b.event = torch.cuda.Event(enable_timing=timed)
                 b.event.record(self._comm_stream)
         else:
+            import time
+            t0 = time.perf_counter()
             self.process_group.all_reduce(b.flat, ReduceOp.SUM)
             b.flat.mul_(scale)
+            b.seconds = time.perf_counter() - t0
 
     def finish_gradient_synchronization(self):
         """Wait for the in-flight bucket reductions (and reduce buckets whose hooks never completed,
@@ -257,12 +273,19 @@ class DistributedDataParallel(nn.Module):
         self._finish_calls += 1
         look = self.check_every > 0 and self._finish_calls % self.check_every == 0
         staged = []
-        for b in self.buckets:
+        for i, b in enumerate(self.buckets):
             if b.event is not None:
                 torch.cuda.current_stream(b.flat.device).wait_event(b.event)
+                if self.metrics is not None and getattr(b, "t0", None) is not None:
+                    b.event.synchronize()
+                    b.seconds = b.t0.elapsed_time(b.event) / 1e3
                 b.event = None
                 if look and b.channel is not None:
                     staged.append((b.channel, b.channel.stage_status(self._comm_stream)))
+            if self.metrics is not None and getattr(b, "seconds", None) is not None:
+                self.metrics.collective(f"ddp bucket {i}", b.seconds, b.numel * b.flat.element_size(), self.world_size,
+                                        kind="all_reduce", fused=b.channel is not None)
+                b.seconds = None
             b.launched = False
             b.pending = len(b.params)
         # a reduction kernel that ran out of time left its bucket unreduced: say so before anybody steps on it

@@ -59,6 +59,25 @@ def test_no_sync_with_counting_pg():
     assert pg.all_reduce_calls == 2 * nb
 
 
+def test_ddp_logs_every_bucket_reduction(tmp_path):
+    """With a metrics writer, each bucket's all-reduce is logged with its bytes on the wire and a roofline fraction."""
+    import json
+    from prometorch_b200.utils.metrics import MetricsWriter
+    pg = D.CountingPG(rank=0, world_size=2)
+    model = nn.Sequential(nn.Linear(4, 4), nn.Linear(4, 2))
+    w = MetricsWriter(str(tmp_path / "m.jsonl"))
+    ddp = D.DistributedDataParallel(model, pg, broadcast_parameters=False, bucket_mb=1e-5, metrics=w)
+    ddp(torch.randn(3, 4)).sum().backward()
+    ddp.finish_gradient_synchronization()
+    w.close()
+    recs = [json.loads(l) for l in open(tmp_path / "m.jsonl")]
+    assert len(recs) == len(ddp.buckets) == pg.all_reduce_calls
+    total = sum(p.numel() for p in model.parameters())
+    assert all(r["kind"] == "collective" and r["op"] == "all_reduce" and r["world"] == 2 and r["seconds"] >= 0 for r in recs)
+    assert sum(r["payload_bytes"] for r in recs) >= 4 * total                   # buckets are padded to 64 elements
+    assert all(r["wire_bytes_per_gpu"] == r["payload_bytes"] for r in recs)     # 2 (n - 1) / n = 1 at two ranks
+
+
 def test_shared_memory_backend_threads():
     groups = D.make_shared_memory_groups(3, timeout=10)
     out = [None] * 3
