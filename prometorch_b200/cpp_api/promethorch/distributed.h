@@ -270,6 +270,34 @@ inline void all_reduce_inplace(float* p, int64_t n) {
 }
 inline void broadcast(Tensor& t, int src = 0) { if (default_group()) default_group()->broadcast(t, src); }
 inline void barrier() { if (default_group()) default_group()->barrier(); }
+inline void init_process_group_single_rank() { default_group() = ProcessGroupPtr(new SingleProcessGroup()); }
+// buf holds world_size slices of `per_rank` floats; this rank's slice is filled in, the others are received.
+inline void all_gather_inplace(float* buf, int64_t per_rank) {
+    if (!default_group() || default_group()->world_size() <= 1) return;
+    const int r = default_group()->rank();
+    Tensor mine = torch::from_blob(buf + (int64_t)r * per_rank, {per_rank}, torch::kFloat).clone();
+    auto parts = default_group()->all_gather(mine);
+    for (size_t k = 0; k < parts.size(); ++k) std::memcpy(buf + (int64_t)k * per_rank, parts[k].data_ptr(), sizeof(float) * (size_t)per_rank);
+}
+// Split form: post starts the gather on a helper thread, wait joins it (overlap with independent work in between; no
+// other collective of the same group may run until wait returns).
+struct AllGatherHandle {
+    std::shared_ptr<std::thread> worker;
+    std::shared_ptr<std::exception_ptr> error;
+};
+inline AllGatherHandle all_gather_post(float* buf, int64_t per_rank) {
+    AllGatherHandle h;
+    h.error = std::make_shared<std::exception_ptr>();
+    auto err = h.error;
+    h.worker = std::make_shared<std::thread>([buf, per_rank, err] {
+        try { all_gather_inplace(buf, per_rank); } catch (...) { *err = std::current_exception(); }
+    });
+    return h;
+}
+inline void all_gather_wait(AllGatherHandle& h) {
+    if (h.worker && h.worker->joinable()) h.worker->join();
+    if (h.error && *h.error) std::rethrow_exception(*h.error);
+}
 
 // DistributedDataParallel: parameters and buffers are broadcast from rank 0 at construction; after backward,
 // allreduce_grads() (alias finish_gradient_synchronization / sync_gradients) averages every gradient over the ranks,

@@ -3,7 +3,9 @@
 // A torch-style C++ surface over libtorch (tensors, autograd, nn modules are libtorch's) plus what the reference adds
 // on top: its sixteen optimizers and sixteen learning-rate schedulers with their option structs and parameter groups,
 // the distributed API (process group, DistributedDataParallel with no_sync, tensor-parallel linear layers, launcher,
-// DistributedSampler), the PTOR checkpoint container and PyTorch-compatible checkpoints, and (gguf.h, separate because
+// DistributedSampler, sharded data parallelism with ZeRO / offload optimizers, GPipe and 1F1B pipelines), GradScaler and
+// autocast guards, datasets and a prefetching DataLoader, the PTOR checkpoint container and PyTorch-compatible
+// checkpoints, and (gguf.h, separate because
 // it needs the CUDA runtime and libptb200 instead of libtorch) GGUF models on the native decode engine.
 //
 // Code written against the reference's headers keeps its spelling with the namespace swapped:
@@ -15,9 +17,13 @@
 #pragma once
 #include <torch/torch.h>
 
+#include "amp.h"
+#include "data.h"
 #include "distributed.h"
+#include "fsdp.h"
 #include "lr_scheduler.h"
 #include "optim.h"
+#include "pipeline.h"
 #include "serialization.h"
 
 namespace promethorch {

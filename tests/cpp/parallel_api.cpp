@@ -1,0 +1,251 @@
+// Exercises the rest of the C++ API on the CPU: GradScaler and autocast guards, datasets / samplers / DataLoader with
+// worker threads, the GPipe pipeline, and (over forked ranks) FullyShardedDataParallel with a ZeRO optimizer, the offload
+// optimizer, the split all-gather, and a two-stage 1F1B pipeline whose gradients equal the single-process model's.
+#include <promethorch/torch.h>
+
+#include <cstdio>
+#include <iostream>
+
+namespace pt = promethorch;
+namespace dist = promethorch::distributed;
+
+#define CHECK(cond)                                                              \
+    do {                                                                         \
+        if (!(cond)) { std::printf("FAIL %s:%d %s\n", __FILE__, __LINE__, #cond); return 1; } \
+    } while (0)
+
+struct MLPImpl : pt::nn::Module {
+    MLPImpl(int in, int hid, int out) {
+        l1 = register_module("l1", pt::nn::Linear(in, hid));
+        l2 = register_module("l2", pt::nn::Linear(hid, out));
+    }
+    pt::Tensor forward(const pt::Tensor& x) { return l2(pt::tanh(l1(x))); }
+    pt::nn::Linear l1{nullptr}, l2{nullptr};
+};
+TORCH_MODULE(MLP);
+
+static bool close(const pt::Tensor& a, const pt::Tensor& b, double tol = 1e-5) { return (a - b).abs().max().item<double>() <= tol; }
+
+// ---- two ranks: sharded data parallelism
+static int fsdp_rank(const dist::DistArgs& a) {
+    dist::DDPConfig cfg;
+    cfg.rank = a.rank; cfg.world_size = a.world_size; cfg.master_addr = a.master_addr; cfg.master_port = a.master_port; cfg.timeout_sec = 60;
+    dist::init_process_group(cfg);
+    pt::manual_seed(7);
+    MLP net(12, 9, 5), ref(12, 9, 5);                       // 9 and 5 do not divide by 2: shards are padded
+    {
+        pt::NoGradGuard ng;
+        auto rp = ref->parameters();
+        auto np = net->parameters();
+        for (size_t i = 0; i < rp.size(); ++i) rp[i].copy_(np[i]);
+    }
+    dist::FullyShardedDataParallel<MLP> fsdp(net);
+    CHECK(fsdp.sharded_numel() * 2 >= fsdp.full_numel() && fsdp.sharded_numel() < fsdp.full_numel());
+    dist::ZeROOptimizer<MLP, pt::optim::Adam> zero(fsdp, pt::optim::AdamOptions(1e-2));
+    pt::optim::Adam ref_opt(ref->parameters(), pt::optim::AdamOptions(1e-2));
+    pt::manual_seed(100);
+    auto X = pt::randn({2, 6, 12});                          // one batch per rank, the same on both processes
+    auto Y = pt::randn({2, 6, 5});
+    for (int step = 0; step < 3; ++step) {
+        zero.zero_grad();
+        pt::mse_loss(fsdp.forward(X[a.rank]), Y[a.rank]).backward();
+        zero.step();
+        fsdp.reshard_params();
+        CHECK(!fsdp.params_gathered() && net->parameters()[0].numel() == 0);      // the full parameters are gone
+        ref_opt.zero_grad();
+        ((pt::mse_loss(ref->forward(X[0]), Y[0]) + pt::mse_loss(ref->forward(X[1]), Y[1])) / 2).backward();
+        ref_opt.step();
+        fsdp.all_gather_params();
+        auto rp = ref->parameters();
+        auto np = net->parameters();
+        for (size_t i = 0; i < rp.size(); ++i) CHECK(close(rp[i], np[i], 2e-5));
+    }
+    // split all-gather
+    std::vector<float> buf(2 * 3, -1.f);
+    for (int k = 0; k < 3; ++k) buf[a.rank * 3 + k] = (float)(10 * a.rank + k);
+    auto h = dist::all_gather_post(buf.data(), 3);
+    dist::all_gather_wait(h);
+    for (int r = 0; r < 2; ++r)
+        for (int k = 0; k < 3; ++k) CHECK(buf[r * 3 + k] == (float)(10 * r + k));
+    dist::barrier();
+    dist::destroy_process_group();
+    return 0;
+}
+
+// ---- two ranks: a two-stage 1F1B pipeline
+struct StageAImpl : pt::nn::Module {
+    StageAImpl() { l = register_module("l", pt::nn::Linear(8, 16)); }
+    pt::Tensor forward(const pt::Tensor& x) { return pt::tanh(l(x)); }
+    pt::nn::Linear l{nullptr};
+};
+TORCH_MODULE(StageA);
+struct StageBImpl : pt::nn::Module {
+    StageBImpl() { l = register_module("l", pt::nn::Linear(16, 4)); }
+    pt::Tensor forward(const pt::Tensor& x) { return l(x); }
+    pt::nn::Linear l{nullptr};
+};
+TORCH_MODULE(StageB);
+
+static int pipeline_rank(const dist::DistArgs& a) {
+    pt::manual_seed(3);
+    StageA sa;                                               // both processes build both stages from the same seed
+    StageB sb;
+    pt::manual_seed(4);
+    const int M = 4;
+    auto X = pt::randn({M * 3, 8}), Y = pt::randn({M * 3, 4});
+    auto xs = X.chunk(M, 0), ys = Y.chunk(M, 0);
+    // single-process gradients of the whole model: mean over the micro-batches of the per-micro-batch loss
+    pt::Tensor total = pt::zeros({});
+    for (int i = 0; i < M; ++i) total = total + pt::mse_loss(sb->forward(sa->forward(xs[i])), ys[i]) / (double)M;
+    total.backward();
+    std::vector<pt::Tensor> want;
+    for (auto& p : (a.rank == 0 ? sa->parameters() : sb->parameters())) { want.push_back(p.grad().clone()); }
+    sa->zero_grad();
+    sb->zero_grad();
+    dist::PipelineScheduleConfig cfg;
+    cfg.num_stages = 2; cfg.num_micros = M; cfg.base_port = a.master_port + 7; cfg.timeout_ms = 30000;
+    auto loss_fn = [](const pt::Tensor& o, const pt::Tensor& t) { return pt::mse_loss(o, t); };
+    double loss = 0;
+    int alive = 0;
+    std::vector<pt::Tensor> got;
+    if (a.rank == 0) {
+        dist::Pipeline1F1BStage<StageA> st(sa, 0, cfg);
+        loss = st.train_step({xs.begin(), xs.end()}, {}, nullptr);
+        alive = st.max_alive_micro_batches();
+        for (auto& p : sa->parameters()) got.push_back(p.grad());
+        CHECK(alive == 2 && loss == 0.0);
+    } else {
+        dist::Pipeline1F1BStage<StageB> st(sb, 1, cfg);
+        loss = st.train_step({}, {ys.begin(), ys.end()}, loss_fn);
+        alive = st.max_alive_micro_batches();
+        for (auto& p : sb->parameters()) got.push_back(p.grad());
+        CHECK(alive == 1 && std::abs(loss - total.item<double>()) < 1e-5);
+    }
+    for (size_t i = 0; i < want.size(); ++i) CHECK(close(want[i], got[i], 1e-5));
+    return 0;
+}
+
+static int single_process() {
+    // GradScaler
+    {
+        auto w = pt::ones({3}).set_requires_grad(true);
+        pt::optim::SGD opt({w}, pt::optim::SGDOptions(0.5));
+        pt::amp::GradScaler sc(pt::amp::GradScalerOptions().init_scale(8.0).growth_interval(2));
+        sc.scale((w * 2).sum()).backward();                  // gradient 2 * 8
+        CHECK(close(w.grad(), pt::full({3}, 16.0)));
+        CHECK(sc.step(opt));                                 // unscaled to 2, w = 1 - 0.5 * 2
+        CHECK(close(w.detach(), pt::zeros({3})));
+        sc.update();
+        CHECK(sc.get_scale() == 8.0);
+        opt.zero_grad();
+        (w * std::numeric_limits<float>::infinity()).sum().backward();
+        CHECK(!sc.step(opt) && sc.found_inf());              // skipped
+        CHECK(close(w.detach(), pt::zeros({3})));
+        sc.update();
+        CHECK(sc.get_scale() == 4.0);                        // backed off
+        for (int i = 0; i < 2; ++i) {
+            opt.zero_grad();
+            sc.scale(w.sum()).backward();
+            CHECK(sc.step(opt));
+            sc.update();
+        }
+        CHECK(sc.get_scale() == 8.0);                        // grew after two clean steps
+        auto sd = sc.state_dict();
+        pt::amp::GradScaler other;
+        other.load_state_dict(sd);
+        CHECK(other.get_scale() == 8.0);
+    }
+    // autocast
+    {
+        auto a = pt::randn({4, 4}), b = pt::randn({4, 4});
+        {
+            pt::amp::AutocastCPUGuard g(pt::kBFloat16);
+            CHECK(pt::matmul(a, b).scalar_type() == pt::kBFloat16);
+        }
+        CHECK(pt::matmul(a, b).scalar_type() == pt::kFloat);
+    }
+    // datasets, samplers, loader
+    {
+        auto X = pt::arange(20, pt::kFloat).reshape({10, 2});
+        auto Y = pt::arange(10);
+        auto ds = std::make_shared<pt::data::TensorDataset>(X, Y);
+        pt::data::DataLoader seq(ds, pt::data::DataLoaderOptions(4));
+        CHECK(seq.size() == 3);
+        std::vector<int64_t> seen;
+        size_t nb = 0;
+        for (auto& b : seq) {
+            ++nb;
+            for (int64_t i = 0; i < b.target.size(0); ++i) seen.push_back(b.target[i].item<int64_t>());
+            CHECK(b.data.size(1) == 2);
+        }
+        CHECK(nb == 3 && seen.size() == 10 && seen[0] == 0 && seen[9] == 9);
+        pt::data::DataLoader dropped(ds, pt::data::DataLoaderOptions(4).drop_last(true));
+        nb = 0;
+        for (auto& b : dropped) { ++nb; CHECK(b.target.size(0) == 4); }
+        CHECK(nb == 2);
+        // the same seed gives the same shuffle; worker threads keep the sampler's order
+        auto order = [&](size_t workers) {
+            pt::data::DataLoader dl(ds, pt::data::DataLoaderOptions(3).shuffle(true).seed(5).num_workers(workers));
+            std::vector<int64_t> v;
+            for (auto& b : dl)
+                for (int64_t i = 0; i < b.target.size(0); ++i) v.push_back(b.target[i].item<int64_t>());
+            return v;
+        };
+        auto o0 = order(0), o3 = order(3);
+        CHECK(o0.size() == 10 && o0 == o3);
+        std::vector<int64_t> sorted = o0;
+        std::sort(sorted.begin(), sorted.end());
+        for (int i = 0; i < 10; ++i) CHECK(sorted[i] == i);
+        CHECK(o0 != sorted);
+        auto sub = std::make_shared<pt::data::Subset>(ds, std::vector<size_t>{7, 2});
+        auto cat = std::make_shared<pt::data::ConcatDataset>(std::vector<pt::data::DatasetPtr>{sub, ds});
+        CHECK(cat->size() == 12 && cat->get(0).target.item<int64_t>() == 7 && cat->get(2).target.item<int64_t>() == 0);
+        auto mapped = std::make_shared<pt::data::MapDataset>(ds, [](pt::data::Example e) { e.data = e.data * 2; return e; });
+        CHECK(mapped->get(3).data[1].item<float>() == 14.0f);
+        pt::data::WeightedRandomSampler ws({0.0, 1.0, 0.0}, 5, 1);
+        for (size_t i : ws.indices()) CHECK(i == 1);
+        pt::data::DistributedSampler s0(10, 2, 0, true, 3), s1(10, 2, 1, true, 3);
+        s0.set_epoch(1);
+        s1.set_epoch(1);
+        auto i0 = s0.indices(), i1 = s1.indices();
+        CHECK(i0.size() == 5 && i1.size() == 5);
+    }
+    // GPipe == the stages in sequence
+    {
+        pt::manual_seed(1);
+        pt::nn::Sequential a(pt::nn::Linear(6, 8), pt::nn::Tanh()), b(pt::nn::Linear(8, 3));
+        auto pipe = pt::nn::parallel::Pipeline::from_modules({a, b}, 4);
+        auto x = pt::randn({8, 6});
+        CHECK(close(pipe.forward(x), b->forward(a->forward(x)), 1e-6) && pipe.num_stages() == 2);
+        pipe.forward(x).sum().backward();
+        CHECK(a->parameters()[0].grad().defined());
+    }
+    // offload optimizer == the plain optimizer
+    {
+        pt::manual_seed(2);
+        auto w1 = pt::randn({4, 3}).set_requires_grad(true);
+        auto w2 = w1.detach().clone().set_requires_grad(true);
+        pt::deepspeed::OffloadOptimizer<pt::optim::AdamW> off({w1}, pt::optim::AdamWOptions(1e-2));
+        pt::optim::AdamW plain({w2}, pt::optim::AdamWOptions(1e-2));
+        for (int i = 0; i < 3; ++i) {
+            off.zero_grad();
+            plain.zero_grad();
+            (w1 * w1).sum().backward();
+            (w2 * w2).sum().backward();
+            off.step();
+            plain.step();
+        }
+        CHECK(close(w1.detach(), w2.detach(), 1e-6) && off.master_params()[0].device().is_cpu());
+    }
+    return 0;
+}
+
+int main(int argc, char** argv) {
+    const int port = argc > 1 ? std::atoi(argv[1]) : 29800;
+    // the forked parts first: a child forked after libtorch has started its worker threads would inherit their locks
+    if (dist::launch(2, fsdp_rank, "127.0.0.1", port) != 0) { std::printf("FAIL fsdp ranks\n"); return 1; }
+    if (dist::launch(2, pipeline_rank, "127.0.0.1", port + 20) != 0) { std::printf("FAIL pipeline ranks\n"); return 1; }
+    if (single_process() != 0) return 1;
+    std::printf("CPP_PARALLEL_API_OK\n");
+    return 0;
+}

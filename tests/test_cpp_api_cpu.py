@@ -26,3 +26,17 @@ def test_cpp_api_trains_and_synchronises(tmp_path):
     assert r.returncode == 0, r.stderr[-3000:]
     r = subprocess.run([exe, str(29750 + os.getpid() % 200)], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0 and "CPP_API_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+@pytest.mark.skipif(shutil.which("g++") is None, reason="needs g++")
+def test_cpp_api_amp_data_fsdp_pipeline(tmp_path):
+    """GradScaler / autocast guards, datasets + DataLoader with worker threads, GPipe, and over forked ranks: sharded data
+    parallelism with a ZeRO optimizer against a replica, the offload optimizer, the split all-gather, a 1F1B pipeline whose
+    stage gradients equal the single-process model's."""
+    exe = str(tmp_path / "parallel_api")
+    cmd = ["g++", "-std=c++17", "-O1", os.path.join(ROOT, "tests", "cpp", "parallel_api.cpp"), "-o", exe,
+           f"-I{ROOT}/prometorch_b200/cpp_api"] + _torch_flags() + ["-lpthread"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stderr[-3000:]
+    r = subprocess.run([exe, str(30050 + os.getpid() % 200)], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "CPP_PARALLEL_API_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
