@@ -25,6 +25,7 @@
 #include "optim.h"
 #include "pipeline.h"
 #include "serialization.h"
+#include "sync_batchnorm.h"
 
 namespace promethorch {
 

@@ -11,7 +11,7 @@ namespace dist = promethorch::distributed;
 
 #define CHECK(cond)                                                              \
     do {                                                                         \
-        if (!(cond)) { std::printf("FAIL %s:%d %s\n", __FILE__, __LINE__, #cond); return 1; } \
+        if (!(cond)) { std::printf("FAIL %s:%d %s\n", __FILE__, __LINE__, #cond); std::fflush(stdout); return 1; } \
     } while (0)
 
 struct MLPImpl : pt::nn::Module {
@@ -59,6 +59,40 @@ static int fsdp_rank(const dist::DistArgs& a) {
         auto rp = ref->parameters();
         auto np = net->parameters();
         for (size_t i = 0; i < rp.size(); ++i) CHECK(close(rp[i], np[i], 2e-5));
+    }
+    // SyncBatchNorm over the two ranks == BatchNorm over the concatenated batch, forward and backward
+    {
+        pt::manual_seed(11);
+        auto full = pt::randn({8, 3, 5});
+        auto go = pt::randn({8, 3, 5});
+        pt::nn::BatchNorm1d bn(3);
+        {
+            pt::NoGradGuard ng;
+            bn->weight.copy_(pt::tensor({1.5f, 0.5f, 2.0f}));
+            bn->bias.copy_(pt::tensor({0.1f, -0.2f, 0.3f}));
+        }
+        pt::nn::Sequential holder(pt::nn::BatchNorm1d(3));
+        {
+            pt::NoGradGuard ng;
+            auto* inner = holder->ptr(0)->as<pt::nn::BatchNorm1dImpl>();
+            inner->weight.copy_(bn->weight);
+            inner->bias.copy_(bn->bias);
+        }
+        holder = dist::convert_sync_batchnorm(holder);
+        auto xf = full.clone().set_requires_grad(true);
+        auto yf = bn->forward(xf);
+        (yf * go).sum().backward();
+        auto xl = full.narrow(0, a.rank * 4, 4).clone().set_requires_grad(true);
+        auto yl = holder->forward(xl);
+        (yl * go.narrow(0, a.rank * 4, 4)).sum().backward();
+        CHECK(close(yl, yf.narrow(0, a.rank * 4, 4), 1e-5));
+        CHECK(close(xl.grad(), xf.grad().narrow(0, a.rank * 4, 4), 1e-5));
+        auto* sbn = holder->ptr(0)->as<dist::SyncBatchNormImpl>();
+        CHECK(sbn != nullptr && close(sbn->running_mean, bn->running_mean, 1e-6) && close(sbn->running_var, bn->running_var, 1e-5));
+        // the weight gradient is a per-rank partial sum, as any data-parallel gradient: the two ranks' sums add up
+        auto gw = sbn->weight.grad().clone();
+        dist::all_reduce(gw);
+        CHECK(close(gw, bn->weight.grad(), 1e-4));
     }
     // split all-gather
     std::vector<float> buf(2 * 3, -1.f);
