@@ -26,6 +26,7 @@
 #include "pipeline.h"
 #include "serialization.h"
 #include "sync_batchnorm.h"
+#include "trainer.h"
 
 namespace promethorch {
 

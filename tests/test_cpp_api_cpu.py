@@ -38,5 +38,5 @@ def test_cpp_api_amp_data_fsdp_pipeline(tmp_path):
            f"-I{ROOT}/prometorch_b200/cpp_api"] + _torch_flags() + ["-lpthread"]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, r.stderr[-3000:]
-    r = subprocess.run([exe, str(30050 + os.getpid() % 200)], capture_output=True, text=True, timeout=300)
+    r = subprocess.run([exe, str(30050 + os.getpid() % 200), str(tmp_path / "ckpt")], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0 and "CPP_PARALLEL_API_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
