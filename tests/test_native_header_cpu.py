@@ -35,8 +35,9 @@ def test_header_lists_every_entry_point():
 
 
 @pytest.mark.skipif(shutil.which("g++") is None or not os.path.isdir(CUDA_INC), reason="needs g++ and the CUDA headers")
-def test_cpp_wrapper_parses(tmp_path):
+def test_c_header_parses_in_a_cpp_program(tmp_path):
+    """The public header is plain C that a C++ program can include (the C++ GGUFModel of cpp_api/promethorch/gguf.h does)."""
     src = tmp_path / "t.cpp"
-    src.write_text('#include "ptb200.hpp"\nint main() { ptb200::check(0, "x"); return 0; }\n')
+    src.write_text('#include "ptb200.h"\nint main() { return ptb_last_error() == nullptr; }\n')
     r = subprocess.run(["g++", "-std=c++17", "-fsyntax-only", f"-I{CUDA_INC}", f"-I{CSRC}", str(src)], capture_output=True, text=True)
     assert r.returncode == 0, r.stderr
