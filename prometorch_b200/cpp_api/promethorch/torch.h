@@ -18,12 +18,14 @@
 #include <torch/torch.h>
 
 #include "amp.h"
+#include "checkpoint.h"
 #include "data.h"
 #include "distributed.h"
 #include "fsdp.h"
 #include "lr_scheduler.h"
 #include "optim.h"
 #include "pipeline.h"
+#include "quantization.h"
 #include "serialization.h"
 #include "sync_batchnorm.h"
 #include "trainer.h"

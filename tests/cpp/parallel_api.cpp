@@ -203,6 +203,70 @@ static int trainer_test(const std::string& dir) {
     return 0;
 }
 
+static int quant_and_checkpoint() {
+    namespace q = pt::quantization;
+    pt::manual_seed(9);
+    // fake quantisation: values land on the 8-bit grid, gradients pass inside the range and stop outside
+    {
+        q::FakeQuantize fq(8);
+        auto x = pt::linspace(-1, 1, 41).set_requires_grad(true);
+        auto y = fq(x);
+        const double scale = 1.0 / 127;
+        CHECK(((y / scale) - pt::round(y / scale)).abs().max().item<double>() < 1e-4);
+        CHECK((y - x).abs().max().item<double>() <= scale / 2 + 1e-6);
+        y.sum().backward();
+        CHECK(close(x.grad(), pt::ones({41})));
+        fq->freeze();
+        auto big = pt::tensor({5.0f, 0.5f}).set_requires_grad(true);
+        fq(big).sum().backward();
+        CHECK(big.grad()[0].item<float>() == 0.0f && big.grad()[1].item<float>() == 1.0f);      // 5.0 is clipped
+    }
+    // QAT linear trains; int8 inference layer and 4-bit layers stay close to the float layer
+    {
+        pt::nn::Linear lin(16, 8);
+        q::QATLinear qat(lin, 8);
+        auto x = pt::randn({32, 16});
+        CHECK((qat(x) - lin(x)).abs().max().item<double>() < 0.1);
+        qat(x).pow(2).mean().backward();
+        CHECK(lin->weight.grad().defined());
+        q::QuantizedLinear ql(lin);
+        CHECK((ql(x) - lin(x)).abs().max().item<double>() < 0.05 && ql->weight_q.scalar_type() == pt::kChar);
+        pt::nn::Linear wide(64, 8);
+        q::Linear4bit nf(wide, 64, "nf4"), i4(wide, 64, "int4");
+        auto xw = pt::randn({4, 64});
+        const double ref = wide(xw).abs().mean().item<double>();
+        CHECK((nf(xw) - wide(xw)).abs().mean().item<double>() < 0.2 * ref && (i4(xw) - wide(xw)).abs().mean().item<double>() < 0.25 * ref);
+        CHECK(nf->packed.numel() == 64 * 8 / 2 && nf->absmax.numel() == 8);
+        auto rt = q::dequantize_4bit(nf->packed, nf->absmax, {8, 64});
+        CHECK((rt - wide->weight).abs().max().item<double>() < 0.15 * wide->weight.abs().max().item<double>());
+        auto a = q::quantize_per_tensor(pt::randn({8, 16})), b = q::quantize_per_tensor(pt::randn({16, 4}));
+        auto exact = (a.first.to(pt::kFloat) * a.second).matmul(b.first.to(pt::kFloat) * b.second);
+        CHECK(close(q::int8_matmul(a.first, a.second, b.first, b.second), exact, 1e-5));
+    }
+    // checkpoint: the same output and gradients as the plain graph, for inputs and for parameters
+    {
+        pt::nn::Linear l1(6, 6), l2(6, 3);
+        auto stage1 = [l1](const pt::Tensor& t) mutable { return pt::tanh(l1(t)); };
+        auto stage2 = [l2](const pt::Tensor& t) mutable { return l2(t); };
+        auto x1 = pt::randn({5, 6}).set_requires_grad(true);
+        auto x2 = x1.detach().clone().set_requires_grad(true);
+        auto plain = stage2(stage1(x1));
+        plain.pow(2).sum().backward();
+        auto gw = l1->weight.grad().clone(), gx = x1.grad().clone();
+        l1->zero_grad();
+        l2->zero_grad();
+        auto ck = pt::utils::checkpoint_sequential({stage1, stage1, stage2}, 2, x2);      // (stage1, stage1) checkpointed, stage2 plain
+        auto want = stage2(stage1(stage1(x1.detach())));
+        CHECK(close(ck, want, 1e-6));
+        auto one = pt::utils::checkpoint(std::function<pt::Tensor(const pt::Tensor&)>(stage1), x2);
+        l1->zero_grad();
+        l2->zero_grad();
+        stage2(one).pow(2).sum().backward();
+        CHECK(close(l1->weight.grad(), gw, 1e-5) && close(x2.grad(), gx, 1e-5));
+    }
+    return 0;
+}
+
 static int single_process() {
     // GradScaler
     {
@@ -324,6 +388,7 @@ int main(int argc, char** argv) {
     if (dist::launch(2, fsdp_rank, "127.0.0.1", port) != 0) { std::printf("FAIL fsdp ranks\n"); return 1; }
     if (dist::launch(2, pipeline_rank, "127.0.0.1", port + 20) != 0) { std::printf("FAIL pipeline ranks\n"); return 1; }
     if (single_process() != 0) return 1;
+    if (quant_and_checkpoint() != 0) return 1;
     if (trainer_test(argc > 2 ? argv[2] : "/tmp/ptb_cpp_trainer") != 0) return 1;
     std::printf("CPP_PARALLEL_API_OK\n");
     return 0;
