@@ -23,6 +23,7 @@
 #include "distributed.h"
 #include "fsdp.h"
 #include "lr_scheduler.h"
+#include "nn_extra.h"
 #include "optim.h"
 #include "pipeline.h"
 #include "quantization.h"

@@ -267,6 +267,69 @@ static int quant_and_checkpoint() {
     return 0;
 }
 
+static int nn_extras() {
+    namespace F = pt::nn::functional;
+    pt::manual_seed(21);
+    auto p = pt::rand({4, 10}) * 0.9 + 0.05, y = (pt::rand({4, 10}) > 0.5).to(pt::kFloat);
+    {   // focal loss with gamma 0 and alpha 0.5 is half the binary cross entropy
+        pt::nn::FocalLoss fl("mean", 0.5, 0.0);
+        CHECK(close(fl(p, y), 0.5 * pt::binary_cross_entropy(p, y), 1e-5));
+        pt::nn::DiceLoss dl;
+        CHECK(std::fabs(dl(y, y).item<double>()) < 1e-6 && dl(p, y).item<double>() > 0);
+        pt::nn::GaussianNLLLoss gl;
+        auto x = pt::randn({6}), t = pt::randn({6}), v = pt::rand({6}) + 0.1;
+        CHECK(close(gl(x, t, v), (0.5 * (v.log() + (x - t).pow(2) / v)).mean(), 1e-6));
+    }
+    {
+        pt::nn::GlobalAvgPool2d gap;
+        auto x = pt::randn({2, 3, 4, 5});
+        CHECK(close(gap(x), x.mean({2, 3}), 1e-6));
+        pt::nn::PositionalEncoding pe(8, 0.0, 32);
+        auto z = pt::zeros({5, 2, 8});
+        auto out = pe(z);
+        CHECK(std::fabs(out[3][1][0].item<double>() - std::sin(3.0)) < 1e-5 && std::fabs(out[3][0][1].item<double>() - std::cos(3.0)) < 1e-5);
+        pt::nn::Dropout1d d1(0.5);
+        auto o = d1(pt::ones({8, 16, 6}));
+        auto per_channel = o.amax(2) - o.amin(2);
+        CHECK(per_channel.abs().max().item<double>() == 0.0 && (o == 0).any().item<bool>());      // whole channels at once
+        d1->eval();
+        CHECK(close(d1(pt::ones({16, 6})), pt::ones({16, 6})));
+        pt::nn::LazyLinear lazy(7);
+        CHECK(lazy->has_uninitialized_params());
+        CHECK(lazy(pt::randn({3, 11})).sizes() == at::IntArrayRef({3, 7}) && lazy->weight.size(1) == 11 && lazy->parameters().size() == 2);
+        pt::nn::Conv2d conv(pt::nn::Conv2dOptions(3, 6, 3).padding(1).stride(2));
+        pt::nn::QuantizedConv2d qc(conv);
+        auto img = pt::randn({2, 3, 9, 9});
+        CHECK(qc(img).sizes() == conv(img).sizes() && (qc(img) - conv(img)).abs().max().item<double>() < 0.05);
+        CHECK(pt::nn::num_parameters(*conv) == 6 * 3 * 9 + 6);
+    }
+    {
+        auto x = pt::randn({5, 6}), w1 = pt::randn({8, 6}), b1 = pt::randn({8}), w2 = pt::randn({3, 8});
+        CHECK(close(F::fused_mlp(x, {w1, w2}, {b1}), pt::relu(x.matmul(w1.t()) + b1).matmul(w2.t()), 1e-5));
+        CHECK(close(F::fused_linear_relu(x, w1, b1), pt::relu(x.matmul(w1.t()) + b1), 1e-5));
+        auto g = pt::rand({6});
+        CHECK(close(F::rms_norm(x, g), x / (x.pow(2).mean(-1, true) + 1e-6).sqrt() * g, 1e-5));
+        // rotation keeps the norm of each (i, i + half) pair and is the identity at position 0
+        auto q = pt::randn({2, 4, 8}), pos = pt::arange(4);
+        auto r = F::rotary_embedding(q, pos);
+        CHECK(close(r.select(1, 0), q.select(1, 0), 1e-6));
+        CHECK(close(r.slice(-1, 0, 4).pow(2) + r.slice(-1, 4, 8).pow(2), q.slice(-1, 0, 4).pow(2) + q.slice(-1, 4, 8).pow(2), 1e-5));
+        // scan against the loop, with a gradient through it
+        auto a = (pt::rand({3, 13}) * 0.9).set_requires_grad(true), b = pt::randn({3, 13});
+        auto h = F::parallel_scan(a, b);
+        auto ref = pt::zeros({3, 13});
+        auto prev = pt::zeros({3});
+        for (int t = 0; t < 13; ++t) {
+            prev = a.detach().select(1, t) * prev + b.select(1, t);
+            ref.select(1, t).copy_(prev);
+        }
+        CHECK(close(h, ref, 1e-5));
+        h.sum().backward();
+        CHECK(a.grad().defined() && a.grad().abs().sum().item<double>() > 0);
+    }
+    return 0;
+}
+
 static int single_process() {
     // GradScaler
     {
@@ -389,6 +452,7 @@ int main(int argc, char** argv) {
     if (dist::launch(2, pipeline_rank, "127.0.0.1", port + 20) != 0) { std::printf("FAIL pipeline ranks\n"); return 1; }
     if (single_process() != 0) return 1;
     if (quant_and_checkpoint() != 0) return 1;
+    if (nn_extras() != 0) return 1;
     if (trainer_test(argc > 2 ? argv[2] : "/tmp/ptb_cpp_trainer") != 0) return 1;
     std::printf("CPP_PARALLEL_API_OK\n");
     return 0;
