@@ -29,6 +29,38 @@ class AutocastCPUGuard(AutocastGuard):
         super().__init__("cpu", dtype, enabled)
 
 
+class CastPolicy:
+    """The four autocast categories (torch/amp/autocast_policy.h:30-60)."""
+    LOWER_PRECISION = "lower_precision"      # runs in the autocast dtype
+    FP32 = "fp32"                            # runs in fp32 whatever the inputs are
+    PROMOTE = "promote"                      # runs in the widest input dtype
+    UNCHANGED = "unchanged"                  # takes the dtype of its inputs
+
+
+_LOWER = ("linear matmul mm bmm addmm addbmm baddbmm addmv mv conv1d conv2d conv3d conv_transpose1d conv_transpose2d "
+          "conv_transpose3d scaled_dot_product_attention flash_attention prelu gru lstm rnn gru_cell lstm_cell rnn_tanh_cell "
+          "rnn_relu_cell").split()
+_FP32 = ("softmax log_softmax layer_norm batch_norm group_norm instance_norm cross_entropy nll_loss mse_loss l1_loss "
+         "smooth_l1_loss huber_loss binary_cross_entropy binary_cross_entropy_with_logits kl_div poisson_nll_loss exp exp2 "
+         "expm1 log log2 log10 log1p pow reciprocal rsqrt gelu tanh sum mean prod cumsum cumprod norm").split()
+_PROMOTE = "add sub mul div cat stack addcmul addcdiv where bilinear dot".split()
+AUTOCAST_POLICY = {**{n: CastPolicy.LOWER_PRECISION for n in _LOWER}, **{n: CastPolicy.FP32 for n in _FP32},
+                   **{n: CastPolicy.PROMOTE for n in _PROMOTE}}
+
+
+def get_autocast_policy(op_name: str) -> str:
+    """Category of an op under autocast; ops that are not in the table keep their inputs' dtype."""
+    return AUTOCAST_POLICY.get(op_name, CastPolicy.UNCHANGED)
+
+
+def is_autocast_enabled(device_type: str = "cuda") -> bool:
+    return torch.is_autocast_enabled(device_type)
+
+
+def get_autocast_dtype(device_type: str = "cuda") -> torch.dtype:
+    return torch.get_autocast_dtype(device_type)
+
+
 class GradScaler:
     def __init__(self, init_scale: float = 65536.0, growth_factor: float = 2.0, backoff_factor: float = 0.5,
                  growth_interval: int = 2000, enabled: bool = True):

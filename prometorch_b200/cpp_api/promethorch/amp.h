@@ -93,6 +93,33 @@ class GradScaler {
 };
 
 // Autocast for the lifetime of the guard; restores the previous setting.
+// The four autocast categories and the op-name table behind them (torch/amp/autocast_policy.h:30-170 of the reference).
+enum class CastPolicy { LowerPrecision, FP32, Promote, Unchanged };
+inline const std::map<std::string, CastPolicy>& autocast_policy_table() {
+    static const std::map<std::string, CastPolicy> table = [] {
+        std::map<std::string, CastPolicy> t;
+        for (const char* n : {"linear", "matmul", "mm", "bmm", "addmm", "addbmm", "baddbmm", "addmv", "mv", "conv1d", "conv2d", "conv3d",
+                              "conv_transpose1d", "conv_transpose2d", "conv_transpose3d", "scaled_dot_product_attention", "flash_attention",
+                              "prelu", "gru", "lstm", "rnn", "gru_cell", "lstm_cell", "rnn_tanh_cell", "rnn_relu_cell"})
+            t[n] = CastPolicy::LowerPrecision;
+        for (const char* n : {"softmax", "log_softmax", "layer_norm", "batch_norm", "group_norm", "instance_norm", "cross_entropy", "nll_loss",
+                              "mse_loss", "l1_loss", "smooth_l1_loss", "huber_loss", "binary_cross_entropy", "binary_cross_entropy_with_logits",
+                              "kl_div", "poisson_nll_loss", "exp", "exp2", "expm1", "log", "log2", "log10", "log1p", "pow", "reciprocal",
+                              "rsqrt", "gelu", "tanh", "sum", "mean", "prod", "cumsum", "cumprod", "norm"})
+            t[n] = CastPolicy::FP32;
+        for (const char* n : {"add", "sub", "mul", "div", "cat", "stack", "addcmul", "addcdiv", "where", "bilinear", "dot"}) t[n] = CastPolicy::Promote;
+        return t;
+    }();
+    return table;
+}
+// Ops that are not in the table keep their inputs' dtype.
+inline CastPolicy get_autocast_policy(const std::string& op) {
+    auto it = autocast_policy_table().find(op);
+    return it == autocast_policy_table().end() ? CastPolicy::Unchanged : it->second;
+}
+inline bool is_autocast_enabled(c10::DeviceType device = c10::kCUDA) { return at::autocast::is_autocast_enabled(device); }
+inline c10::ScalarType get_autocast_dtype(c10::DeviceType device = c10::kCUDA) { return at::autocast::get_autocast_dtype(device); }
+
 class AutocastGuard {
  public:
     AutocastGuard(c10::DeviceType device, c10::ScalarType dtype, bool enabled = true) : device_(device) {

@@ -22,6 +22,7 @@
 #include "data.h"
 #include "distributed.h"
 #include "fsdp.h"
+#include "hooks.h"
 #include "lr_scheduler.h"
 #include "nn_extra.h"
 #include "optim.h"

@@ -13,6 +13,10 @@ namespace dist = promethorch::distributed;
     do {                                                                         \
         if (!(cond)) { std::printf("FAIL %s:%d %s\n", __FILE__, __LINE__, #cond); std::fflush(stdout); return 1; } \
     } while (0)
+#define CHECK_VOID(cond)                                                         \
+    do {                                                                         \
+        if (!(cond)) { std::printf("FAIL %s:%d %s\n", __FILE__, __LINE__, #cond); std::fflush(stdout); std::exit(1); } \
+    } while (0)
 
 struct MLPImpl : pt::nn::Module {
     MLPImpl(int in, int hid, int out) {
@@ -330,6 +334,33 @@ static int nn_extras() {
     return 0;
 }
 
+static int module_hooks() {
+    pt::manual_seed(5);
+    pt::nn::Hooked<pt::nn::Linear> lin(pt::nn::Linear(4, 3));
+    int pre_calls = 0, fwd_calls = 0, bwd_calls = 0;
+    pt::Tensor seen_gin, seen_gout;
+    int pre = lin.register_forward_pre_hook([&](pt::nn::Module&, std::vector<pt::Tensor>& in) { ++pre_calls; in[0] = in[0] * 2; });
+    int fwd = lin.register_forward_hook([&](pt::nn::Module&, const std::vector<pt::Tensor>&, const pt::Tensor& out) { ++fwd_calls; CHECK_VOID(out.size(1) == 3); });
+    int ret = lin.register_forward_hook_with_return([&](pt::nn::Module&, const std::vector<pt::Tensor>&, const pt::Tensor& out) { return out + 1; });
+    int bwd = lin.register_backward_hook([&](pt::nn::Module&, const std::vector<pt::Tensor>& gin, const pt::Tensor& gout) { ++bwd_calls; seen_gin = gin[0]; seen_gout = gout; });
+    auto x = pt::randn({5, 4}).set_requires_grad(true);
+    auto y = lin(x);
+    CHECK(close(y, lin.module()(x.detach() * 2) + 1, 1e-6) && pre_calls == 1 && fwd_calls == 1);
+    y.sum().backward();
+    CHECK(bwd_calls == 1 && close(seen_gout, pt::ones({5, 3})));
+    CHECK(close(seen_gin, pt::ones({5, 3}).matmul(lin->weight.detach()), 1e-6));        // the gradient at the (doubled) input of the layer
+    CHECK(close(x.grad(), 2 * seen_gin, 1e-6));
+    CHECK(lin.remove_hook(pre) && lin.remove_hook(ret) && !lin.remove_hook(ret) && lin.num_hooks() == 2);
+    auto y2 = lin(x.detach());                                                           // no input wants a gradient: fires on the output's
+    CHECK(close(y2, lin.module()(x.detach()), 1e-6));
+    y2.sum().backward();
+    CHECK(bwd_calls == 2 && !seen_gin.defined());
+    lin.remove_hook(fwd);
+    lin.remove_hook(bwd);
+    CHECK(lin.num_hooks() == 0);
+    return 0;
+}
+
 static int single_process() {
     // GradScaler
     {
@@ -366,7 +397,15 @@ static int single_process() {
         {
             pt::amp::AutocastCPUGuard g(pt::kBFloat16);
             CHECK(pt::matmul(a, b).scalar_type() == pt::kBFloat16);
+            CHECK(pt::amp::is_autocast_enabled(c10::kCPU) && pt::amp::get_autocast_dtype(c10::kCPU) == pt::kBFloat16);
+            // the table says what the guard does: matmul-like ops in the low dtype, losses back in fp32
+            CHECK(pt::amp::get_autocast_policy("matmul") == pt::amp::CastPolicy::LowerPrecision);
+            CHECK(pt::amp::get_autocast_policy("mse_loss") == pt::amp::CastPolicy::FP32);
+            CHECK(pt::mse_loss(pt::matmul(a, b), pt::matmul(a, b)).scalar_type() == pt::kFloat);
+            CHECK(pt::amp::get_autocast_policy("relu") == pt::amp::CastPolicy::Unchanged && pt::relu(pt::matmul(a, b)).scalar_type() == pt::kBFloat16);
+            CHECK(pt::amp::get_autocast_policy("cat") == pt::amp::CastPolicy::Promote);
         }
+        CHECK(!pt::amp::is_autocast_enabled(c10::kCPU));
         CHECK(pt::matmul(a, b).scalar_type() == pt::kFloat);
     }
     // datasets, samplers, loader
@@ -453,6 +492,7 @@ int main(int argc, char** argv) {
     if (single_process() != 0) return 1;
     if (quant_and_checkpoint() != 0) return 1;
     if (nn_extras() != 0) return 1;
+    if (module_hooks() != 0) return 1;
     if (trainer_test(argc > 2 ? argv[2] : "/tmp/ptb_cpp_trainer") != 0) return 1;
     std::printf("CPP_PARALLEL_API_OK\n");
     return 0;

@@ -62,6 +62,28 @@ def test_grad_scaler_skips_on_inf_and_backs_off():
     assert sc2.get_scale() == 512.0
 
 
+def test_autocast_policy_table_matches_what_autocast_does():
+    import torch.nn.functional as F
+    from prometorch_b200 import amp
+    a, b = torch.randn(4, 4), torch.randn(4, 4)
+    calls = {"matmul": lambda: torch.matmul(a, b), "linear": lambda: F.linear(a, b), "mm": lambda: torch.mm(a, b),
+             "bmm": lambda: torch.bmm(a[None], b[None]), "conv1d": lambda: F.conv1d(a[None], b[None, :, :2]),
+             "mse_loss": lambda: F.mse_loss(torch.matmul(a, b), torch.matmul(a, b)),
+             "relu": lambda: torch.relu(torch.matmul(a, b)), "cat": lambda: torch.cat([torch.matmul(a, b), a])}
+    with amp.AutocastCPUGuard(torch.bfloat16):
+        assert amp.is_autocast_enabled("cpu") and amp.get_autocast_dtype("cpu") == torch.bfloat16
+        for name, call in calls.items():
+            policy, dtype = amp.get_autocast_policy(name), call().dtype
+            if policy == amp.CastPolicy.LOWER_PRECISION:
+                assert dtype == torch.bfloat16, name
+            elif policy in (amp.CastPolicy.FP32, amp.CastPolicy.PROMOTE):
+                assert dtype == torch.float32, name
+            else:
+                assert dtype == torch.bfloat16, name            # takes the dtype of its (bf16) input
+    assert not amp.is_autocast_enabled("cpu")
+    assert amp.get_autocast_policy("softmax") == amp.CastPolicy.FP32 and amp.get_autocast_policy("view") == amp.CastPolicy.UNCHANGED
+
+
 def test_autocast_guard_cpu():
     a, b = torch.randn(8, 8), torch.randn(8, 8)
     with amp.AutocastGuard("cpu", torch.bfloat16):
