@@ -26,6 +26,10 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--use_fast_math", "-Xcompiler",
               "--expt-relaxed-constexpr", "-Xptxas", "-v"]
 
 
+APPS = ROOT / "cpp_api" / "apps"
+PROMESERVE = LIBDIR / "promeserve"
+
+
 def _nvcc() -> str:
     for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
         if cand and os.path.exists(cand):
@@ -81,3 +85,22 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 if __name__ == "__main__":
     p = build(force="--force" in sys.argv, verbose="-v" in sys.argv)
     print(p)
+
+
+def build_promeserve(force: bool = False) -> Path:
+    """The native server (``cpp_api/apps/promeserve.cpp``: C++ HTTP server + tokenizer + the CUDA decode engine) as
+    ``lib/promeserve``, linked against ``lib/libptb200.so`` and the CUDA runtime."""
+    build()
+    src = APPS / "promeserve.cpp"
+    hdrs = list((ROOT / "cpp_api" / "promethorch").glob("*.h")) + [CSRC / "ptb200.h", CSRC / "ptb200_types.h"]
+    newest = max([src.stat().st_mtime, LIB.stat().st_mtime] + [h.stat().st_mtime for h in hdrs if h.exists()])
+    if not force and PROMESERVE.exists() and PROMESERVE.stat().st_mtime >= newest:
+        return PROMESERVE
+    cuda = Path(_nvcc()).resolve().parent.parent
+    cxx = os.environ.get("CXX") or shutil.which("g++") or "g++"
+    cmd = [cxx, "-std=c++17", "-O2", str(src), "-o", str(PROMESERVE), f"-I{ROOT / 'cpp_api'}", f"-I{cuda / 'include'}", f"-L{LIBDIR}", "-lptb200",
+           f"-L{cuda / 'lib64'}", "-lcudart", "-lpthread", "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{cuda / 'lib64'}"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"building promeserve failed:\n{r.stdout}\n{r.stderr}")
+    return PROMESERVE

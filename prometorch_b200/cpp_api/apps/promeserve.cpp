@@ -1,0 +1,72 @@
+// promeserve: the Ollama-compatible server as a native program.
+//
+//   promeserve --port 11434 --device cuda --model NAME --workers N --queue-depth N --timeout-ms MS --model-dir DIR
+//
+// The flags are the reference's (promeserve/main.cpp:40-105) plus --host, --model-dir (repeatable), --max-seq and
+// --max-models.  --model is loaded before the port opens and stays resident; it may be a path to a .gguf file (requests may
+// only use names).  Build: g++ -std=c++17 -O2 promeserve.cpp -I<cpp_api> -I<cuda>/include -L<lib> -lptb200 -lcudart -lpthread
+#include <csignal>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
+#include "promethorch/gguf_backend.h"
+
+namespace ps = promethorch::serve;
+
+static volatile std::sig_atomic_t g_stop = 0;
+static void on_signal(int) { g_stop = 1; }
+
+int main(int argc, char** argv) {
+    ps::ServerConfig cfg;
+    std::string model;
+    for (int i = 1; i < argc; ++i) {
+        const std::string a = argv[i];
+        auto val = [&]() -> std::string {
+            if (i + 1 >= argc) { std::fprintf(stderr, "promeserve: %s needs a value\n", a.c_str()); std::exit(2); }
+            return argv[++i];
+        };
+        if (a == "--host") cfg.host = val();
+        else if (a == "--port") cfg.port = std::atoi(val().c_str());
+        else if (a == "--device") cfg.device = val();
+        else if (a == "--model") model = val();
+        else if (a == "--workers") cfg.worker_threads = std::atoi(val().c_str());
+        else if (a == "--queue-depth") cfg.max_queue_depth = std::atoi(val().c_str());
+        else if (a == "--timeout-ms") cfg.server_timeout_ms = std::atoi(val().c_str());
+        else if (a == "--model-dir") cfg.model_dirs.push_back(val());
+        else if (a == "--max-seq") cfg.max_seq = std::atoi(val().c_str());
+        else if (a == "--max-models") cfg.max_loaded_models = std::atoi(val().c_str());
+        else if (a == "--fp16-weights") {}                       // accepted for compatibility: weights stay in their file format
+        else if (a == "--help" || a == "-h") {
+            std::printf("usage: promeserve [--host A] [--port N] [--device cuda] [--model NAME|FILE.gguf] [--workers N] [--queue-depth N]\n"
+                        "                  [--timeout-ms MS] [--model-dir DIR]... [--max-seq N] [--max-models N]\n");
+            return 0;
+        } else { std::fprintf(stderr, "promeserve: unknown flag %s\n", a.c_str()); return 2; }
+    }
+    if (cfg.device != "cuda") { std::fprintf(stderr, "promeserve: this build serves on CUDA devices only (--device cuda)\n"); return 2; }
+    try {
+        ps::PromeServe srv(cfg, ps::gguf_loader(cfg));
+        if (!model.empty()) {
+            if (ps::store::is_file(model)) {
+                std::string name = model.substr(model.find_last_of('/') + 1);
+                if (name.size() > 5 && name.compare(name.size() - 5, 5, ".gguf") == 0) name.resize(name.size() - 5);
+                srv.handlers().add_backend(name, std::make_shared<ps::GGUFBackend>(model, name, cfg.max_seq));
+                std::printf("[PromeServe] loaded %s as '%s'\n", model.c_str(), name.c_str());
+            } else {
+                srv.handlers().add_backend(model, std::make_shared<ps::GGUFBackend>(ps::store::resolve(model, cfg.model_dirs), model, cfg.max_seq));
+                std::printf("[PromeServe] loaded '%s'\n", model.c_str());
+            }
+        }
+        srv.start();
+        std::printf("[PromeServe] listening on %s:%d\n", cfg.host.c_str(), srv.port());
+        std::fflush(stdout);
+        std::signal(SIGINT, on_signal);
+        std::signal(SIGTERM, on_signal);
+        while (!g_stop) ::usleep(100000);
+        srv.stop();
+    } catch (const std::exception& e) {
+        std::fprintf(stderr, "promeserve: %s\n", e.what());
+        return 1;
+    }
+    return 0;
+}

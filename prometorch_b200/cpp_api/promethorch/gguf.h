@@ -1,7 +1,7 @@
 // promethorch C++ API: GGUF models on the native decode engine.
 //
 //   promethorch::io::gguf::GGUFReader   memory-mapped GGUF v2/v3 reader (metadata, tensor directory, raw blocks)
-//   promethorch::io::GGUFModel          load(path) / forward_decode(token, pos) / generate(prompt ids, n)
+//   promethorch::io::GGUFModel          load(path) / forward_decode(token, pos) / generate(prompt ids, n) / run_prompt / sample
 //
 // GGUFModel is the C++ face of what the Python class of the same name does: parse the file, repack the quantised
 // matrices into the decode kernels' streaming layout (tiles of 16 rows, csrc/decode_gemv_mma.cuh), upload them, and
@@ -27,175 +27,10 @@
 #include <vector>
 
 #include "../../csrc/ptb200.h"
+#include "gguf_reader.h"
 
 namespace promethorch {
 namespace io {
-namespace gguf {
-
-enum GGMLType : uint32_t { F32 = 0, F16 = 1, Q4_0 = 2, Q8_0 = 8, Q2_K = 10, Q3_K = 11, Q4_K = 12, Q5_K = 13, Q6_K = 14, BF16 = 30 };
-
-struct Value {                       // one metadata value: a scalar, a string or an array of them
-    uint32_t type = 0;
-    uint64_t u = 0;
-    int64_t i = 0;
-    double f = 0;
-    bool b = false;
-    std::string s;
-    std::vector<Value> arr;
-    double as_float() const { return type == 6 || type == 12 ? f : (type == 5 || type == 3 || type == 1 || type == 11 ? (double)i : (double)u); }
-    int64_t as_int() const { return type == 6 || type == 12 ? (int64_t)f : (type == 5 || type == 3 || type == 1 || type == 11 ? i : (int64_t)u); }
-};
-
-struct TensorInfo {
-    std::string name;
-    std::vector<int64_t> shape;      // torch order (GGML stores the dimensions reversed)
-    uint32_t type = 0;
-    uint64_t offset = 0;             // from the start of the data section
-    uint64_t nbytes = 0;
-};
-
-inline void block_geometry(uint32_t type, int& elems, int& bytes) {
-    switch (type) {
-        case F32: elems = 1; bytes = 4; break;
-        case F16: case BF16: elems = 1; bytes = 2; break;
-        case Q4_0: elems = 32; bytes = 18; break;
-        case Q8_0: elems = 32; bytes = 34; break;
-        case Q2_K: elems = 256; bytes = 84; break;
-        case Q3_K: elems = 256; bytes = 110; break;
-        case Q4_K: elems = 256; bytes = 144; break;
-        case Q5_K: elems = 256; bytes = 176; break;
-        case Q6_K: elems = 256; bytes = 210; break;
-        default: throw std::runtime_error("GGUF: unsupported tensor type " + std::to_string(type));
-    }
-}
-
-class GGUFReader {
- public:
-    GGUFReader() = default;
-    explicit GGUFReader(const std::string& path) { open(path); }
-    ~GGUFReader() { close(); }
-    GGUFReader(const GGUFReader&) = delete;
-    GGUFReader& operator=(const GGUFReader&) = delete;
-
-    void open(const std::string& path) {
-        close();
-        fd_ = ::open(path.c_str(), O_RDONLY);
-        if (fd_ < 0) throw std::runtime_error("GGUF: cannot open " + path);
-        struct stat st;
-        ::fstat(fd_, &st);
-        size_ = (size_t)st.st_size;
-        base_ = (const uint8_t*)::mmap(nullptr, size_, PROT_READ, MAP_PRIVATE, fd_, 0);
-        if (base_ == MAP_FAILED) { base_ = nullptr; throw std::runtime_error("GGUF: mmap failed for " + path); }
-        size_t p = 0;
-        if (rd<uint32_t>(p) != 0x46554747u) throw std::runtime_error("GGUF: bad magic in " + path);
-        const uint32_t version = rd<uint32_t>(p);
-        if (version < 2 || version > 3) throw std::runtime_error("GGUF: unsupported version " + std::to_string(version));
-        const uint64_t n_tensors = rd<uint64_t>(p), n_kv = rd<uint64_t>(p);
-        for (uint64_t k = 0; k < n_kv; ++k) {
-            const std::string key = rd_str(p);
-            const uint32_t type = rd<uint32_t>(p);
-            metadata_[key] = rd_value(p, type);
-        }
-        for (uint64_t t = 0; t < n_tensors; ++t) {
-            TensorInfo ti;
-            ti.name = rd_str(p);
-            const uint32_t nd = rd<uint32_t>(p);
-            std::vector<int64_t> dims(nd);
-            for (auto& d : dims) d = (int64_t)rd<uint64_t>(p);
-            ti.shape.assign(dims.rbegin(), dims.rend());
-            ti.type = rd<uint32_t>(p);
-            ti.offset = rd<uint64_t>(p);
-            int be, bb;
-            block_geometry(ti.type, be, bb);
-            int64_t n = 1;
-            for (auto d : dims) n *= d;
-            ti.nbytes = (uint64_t)(n / be) * bb;
-            tensors_[ti.name] = ti;
-        }
-        const uint64_t align = has("general.alignment") ? (uint64_t)get("general.alignment").as_int() : 32;
-        data_ = (p + align - 1) / align * align;
-    }
-    void close() {
-        if (base_) ::munmap((void*)base_, size_);
-        if (fd_ >= 0) ::close(fd_);
-        base_ = nullptr;
-        fd_ = -1;
-        metadata_.clear();
-        tensors_.clear();
-    }
-    bool has(const std::string& key) const { return metadata_.count(key) != 0; }
-    const Value& get(const std::string& key) const {
-        auto it = metadata_.find(key);
-        if (it == metadata_.end()) throw std::runtime_error("GGUF: no metadata key " + key);
-        return it->second;
-    }
-    std::string arch() const { return has("general.architecture") ? get("general.architecture").s : "llama"; }
-    double arch_float(const std::string& k, double dflt) const { return has(arch() + "." + k) ? get(arch() + "." + k).as_float() : dflt; }
-    int64_t arch_int(const std::string& k, int64_t dflt) const { return has(arch() + "." + k) ? get(arch() + "." + k).as_int() : dflt; }
-    bool has_tensor(const std::string& n) const { return tensors_.count(n) != 0; }
-    const TensorInfo& tensor(const std::string& n) const {
-        auto it = tensors_.find(n);
-        if (it == tensors_.end()) throw std::runtime_error("GGUF: no tensor " + n);
-        return it->second;
-    }
-    const uint8_t* data(const TensorInfo& t) const {
-        if (data_ + t.offset + t.nbytes > size_) throw std::runtime_error("GGUF: tensor " + t.name + " runs past the end of the file");
-        return base_ + data_ + t.offset;
-    }
-    const std::map<std::string, TensorInfo>& tensors() const { return tensors_; }
-    const std::map<std::string, Value>& metadata() const { return metadata_; }
-
- private:
-    template <typename T>
-    T rd(size_t& p) const {
-        if (p + sizeof(T) > size_) throw std::runtime_error("GGUF: truncated file");
-        T v;
-        std::memcpy(&v, base_ + p, sizeof(T));
-        p += sizeof(T);
-        return v;
-    }
-    std::string rd_str(size_t& p) const {
-        const uint64_t n = rd<uint64_t>(p);
-        if (p + n > size_) throw std::runtime_error("GGUF: truncated string");
-        std::string s((const char*)base_ + p, n);
-        p += n;
-        return s;
-    }
-    Value rd_value(size_t& p, uint32_t type) const {
-        Value v;
-        v.type = type;
-        switch (type) {
-            case 0: v.u = rd<uint8_t>(p); break;
-            case 1: v.i = rd<int8_t>(p); break;
-            case 2: v.u = rd<uint16_t>(p); break;
-            case 3: v.i = rd<int16_t>(p); break;
-            case 4: v.u = rd<uint32_t>(p); break;
-            case 5: v.i = rd<int32_t>(p); break;
-            case 6: v.f = rd<float>(p); break;
-            case 7: v.b = rd<uint8_t>(p) != 0; v.u = v.b; break;
-            case 8: v.s = rd_str(p); break;
-            case 9: {
-                const uint32_t et = rd<uint32_t>(p);
-                const uint64_t n = rd<uint64_t>(p);
-                v.arr.reserve(n);
-                for (uint64_t k = 0; k < n; ++k) v.arr.push_back(rd_value(p, et));
-                break;
-            }
-            case 10: v.u = rd<uint64_t>(p); break;
-            case 11: v.i = rd<int64_t>(p); break;
-            case 12: v.f = rd<double>(p); break;
-            default: throw std::runtime_error("GGUF: unknown metadata type " + std::to_string(type));
-        }
-        return v;
-    }
-    int fd_ = -1;
-    const uint8_t* base_ = nullptr;
-    size_t size_ = 0, data_ = 0;
-    std::map<std::string, Value> metadata_;
-    std::map<std::string, TensorInfo> tensors_;
-};
-
-}  // namespace gguf
 
 struct TransformerConfig {
     std::string architecture = "llama";
@@ -234,8 +69,10 @@ class GGUFModel {
     TransformerConfig config;
 
     // Parse, repack, upload and create the engine on the current CUDA device.
-    void load(const std::string& path, int max_seq = 4096) {
+    // want_logits: keep the fp32 logits of every step on the device (needed by sample()).
+    void load(const std::string& path, int max_seq = 4096, bool want_logits = false) {
         close();
+        want_logits_ = want_logits;
         reader_.open(path);
         config.parse(reader_);
         max_seq_ = std::min(max_seq, config.context_length);
@@ -270,6 +107,7 @@ class GGUFModel {
         m.lm_head = matrix(c.tie_word_embeddings ? "token_embd.weight" : "output.weight");
         m.out_norm = vector_f32("output_norm.weight");
         m.tp_rank = 0; m.tp_world = 1;
+        m.want_logits = want_logits ? 1 : 0;
         check_cuda(cudaDeviceSynchronize(), "upload");
         engine_ = ptb_engine_create(&m, layers.data(), nullptr);
         if (!engine_) throw std::runtime_error(std::string("GGUFModel: ") + ptb_last_error());
@@ -281,6 +119,8 @@ class GGUFModel {
         device_.clear();
         captured_ = false;
         cos_ = sin_ = nullptr;
+        samp_hist_ = samp_scratch_ = samp_out_ = nullptr;
+        samp_n_hist_ = 0;
     }
     // One decode step fed from the host: returns the arg-max id of the next token.
     int forward_decode(int token, int pos) {
@@ -302,6 +142,56 @@ class GGUFModel {
         check_status();
         return std::vector<int>(log.begin() + (long)(prompt.size() - 1), log.begin() + std::min<long>(steps, (long)log.size()));
     }
+    // The prompt as one scripted run (no host round trip between its tokens); returns the arg-max after its last token.
+    int run_prompt(const std::vector<int>& prompt, int pos0 = 0) {
+        if (prompt.empty()) throw std::runtime_error("run_prompt: empty prompt");
+        if (pos0 + (int)prompt.size() + 1 > max_seq_) throw std::runtime_error("run_prompt: the prompt does not fit max_seq");
+        ensure_captured();
+        if (ptb_engine_begin_script(engine_, prompt.data(), (int)prompt.size(), pos0)) fail("begin_script");
+        if (ptb_engine_run(engine_, (int)prompt.size())) fail("run");
+        std::vector<int> log(prompt.size());
+        if (ptb_engine_read_log(engine_, log.data(), (int)log.size()) < (int)log.size()) fail("read_log");
+        check_status();
+        return log.back();
+    }
+    // Device pointer to the fp32 logits of the last step ([vocab]); valid when loaded with want_logits.
+    const float* logits() const { return want_logits_ ? (const float*)ptb_engine_logits(engine_) : nullptr; }
+    // Start a sampled continuation: the ids that count for the repetition penalty, and the seed of the draws.
+    void sampler_reset(const std::vector<int>& history, uint64_t seed = 42) {
+        if (!want_logits_) throw std::runtime_error("sampling needs the model loaded with want_logits = true");
+        if (!samp_hist_) {
+            check_cuda(cudaMalloc(&samp_hist_, sizeof(int) * kHistCap), "cudaMalloc");
+            const size_t sb = (size_t)ptb_sample_scratch_bytes(config.vocab_size);
+            check_cuda(cudaMalloc(&samp_scratch_, sb), "cudaMalloc");
+            check_cuda(cudaMemset(samp_scratch_, 0, sb), "cudaMemset");
+            check_cuda(cudaMalloc(&samp_out_, 2 * sizeof(int)), "cudaMalloc");
+            device_.push_back(samp_hist_);
+            device_.push_back(samp_scratch_);
+            device_.push_back(samp_out_);
+        }
+        const size_t n = std::min(history.size(), (size_t)kHistCap);
+        if (n) check_cuda(cudaMemcpy(samp_hist_, history.data() + (history.size() - n), n * sizeof(int), cudaMemcpyHostToDevice), "cudaMemcpy");
+        samp_n_hist_ = (int)n;
+        rng_state_ = seed * 0x9E3779B97F4A7C15ull + 0xD1B54A32D192ED03ull;
+    }
+    // One draw from the logits of the last step on the device (penalty, temperature, top-k <= 64, top-p, inverse-CDF draw);
+    // only the chosen id crosses to the host.  The id is appended to the penalty history.
+    int sample(double temperature, int top_k, double top_p, double repeat_penalty) {
+        if (!samp_hist_) sampler_reset({});
+        top_k = top_k < 1 || top_k > 64 ? 64 : top_k;
+        rng_state_ ^= rng_state_ << 13; rng_state_ ^= rng_state_ >> 7; rng_state_ ^= rng_state_ << 17;      // xorshift64
+        const float u = (float)((rng_state_ >> 40) * (1.0 / 16777216.0));
+        cudaStream_t st = (cudaStream_t)ptb_engine_stream(engine_);
+        if (ptb_sample_logits(logits(), config.vocab_size, (int*)samp_hist_, samp_n_hist_, kHistCap, (float)repeat_penalty, (float)temperature, top_k,
+                              (float)top_p, u, samp_scratch_, (int*)samp_out_, nullptr, st) < 0)
+            fail("sample_logits");
+        int host[2] = {0, 0};
+        check_cuda(cudaMemcpyAsync(host, samp_out_, sizeof host, cudaMemcpyDeviceToHost, st), "cudaMemcpyAsync");
+        check_cuda(cudaStreamSynchronize(st), "cudaStreamSynchronize");
+        if (samp_n_hist_ < kHistCap) ++samp_n_hist_;
+        return host[0];
+    }
+    int max_seq() const { return max_seq_; }
     size_t weight_bytes() const { return weight_bytes_; }
     const gguf::GGUFReader& reader() const { return reader_; }
 
@@ -526,8 +416,12 @@ class GGUFModel {
     std::vector<void*> device_;
     const float *cos_ = nullptr, *sin_ = nullptr;
     int max_seq_ = 0;
-    bool captured_ = false;
+    bool captured_ = false, want_logits_ = false;
     size_t weight_bytes_ = 0;
+    static constexpr int kHistCap = 1 << 16;
+    void *samp_hist_ = nullptr, *samp_scratch_ = nullptr, *samp_out_ = nullptr;
+    int samp_n_hist_ = 0;
+    uint64_t rng_state_ = 42;
 };
 
 }  // namespace io

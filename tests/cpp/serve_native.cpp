@@ -1,0 +1,171 @@
+// Test program for the native serving stack (json.h, tokenizer.h, chat.h, serve.h): no GPU, no libtorch.
+//   serve_native tokenize SPEC.json        ids / decoded text / pre-tokeniser pieces for every text of the spec
+//   serve_native gguf-tokenize FILE.gguf TEXTS.json
+//   serve_native chat SPEC.json            rendered prompts
+//   serve_native json FILE.json            parse and dump again
+//   serve_native serve [--workers N] [--queue-depth N] [--timeout-ms MS] [--model-dir DIR] [--max-body N]
+//                                          serves fake backends on a free port, prints "PORT n", runs until stdin closes
+#include <fstream>
+#include <iostream>
+#include <sstream>
+#include <thread>
+
+#include "promethorch/serve.h"
+#include "promethorch/tokenizer.h"
+
+namespace pj = promethorch::json;
+namespace ps = promethorch::serve;
+namespace pio = promethorch::io;
+
+static std::string slurp(const std::string& path) {
+    std::ifstream f(path, std::ios::binary);
+    std::stringstream ss;
+    ss << f.rdbuf();
+    return ss.str();
+}
+static pj::Value ids_json(const std::vector<int>& ids) {
+    pj::Value a = pj::Value::array();
+    for (int i : ids) a.push_back(i);
+    return a;
+}
+static pj::Value run_texts(const pio::GGUFTokenizer& tok, const pj::Value& texts) {
+    pj::Value out = pj::Value::object(), all_ids = pj::Value::array(), decoded = pj::Value::array(), pieces = pj::Value::array(), single = pj::Value::array();
+    for (const auto& t : texts.items()) {
+        const std::vector<int> ids = tok.encode(t.as_string());
+        all_ids.push_back(ids_json(ids));
+        decoded.push_back(tok.decode(ids));
+        pj::Value p = pj::Value::array(), s = pj::Value::array();
+        for (const auto& x : pio::GGUFTokenizer::gpt2_pieces(t.as_string())) p.push_back(x);
+        for (int id : ids) s.push_back(tok.decode_token(id));
+        pieces.push_back(p);
+        single.push_back(s);
+    }
+    out.set("ids", all_ids);
+    out.set("decoded", decoded);
+    out.set("pieces", pieces);
+    out.set("single", single);
+    return out;
+}
+
+// Token = one byte.  "echo" spells a fixed answer, "mirror" answers with the prompt it was given, "slow" takes 30 ms a token.
+class FakeBackend : public ps::ModelBackend {
+ public:
+    explicit FakeBackend(std::string kind) : kind_(std::move(kind)) {
+        architecture = "qwen3";
+        model_name = kind_;
+        size = 1234;
+        parameter_size = "1B";
+    }
+    std::vector<int> encode(const std::string& text) override {
+        std::vector<int> ids;
+        for (unsigned char c : text) ids.push_back(c);
+        return ids;
+    }
+    std::string decode_token(int id) override { return std::string(1, (char)id); }
+    std::pair<double, double> generate(const std::vector<int>& prompt, const ps::GenerateOptions& opt, const std::function<bool(int)>& on_token) override {
+        std::string answer = "hello world";
+        if (kind_ == "mirror") {
+            answer.clear();
+            for (int t : prompt) answer.push_back((char)t);
+            answer += "|" + std::to_string(opt.top_k) + "|" + std::to_string((int)(opt.temperature * 100));
+        }
+        if (kind_ == "slow") answer = std::string(200, 'z');
+        if (kind_ == "tool") answer = "sure {\"tool_call\": {\"name\": \"add\", \"arguments\": {\"a\": 1, \"b\": 2}}} done";
+        int n = 0;
+        for (char c : answer) {
+            if (n++ >= opt.num_predict) break;
+            if (kind_ == "slow") std::this_thread::sleep_for(std::chrono::milliseconds(30));
+            if (!on_token((unsigned char)c)) break;
+        }
+        return {0.001, 0.002};
+    }
+
+ private:
+    std::string kind_;
+};
+
+int main(int argc, char** argv) {
+    if (argc < 2) return 2;
+    const std::string mode = argv[1];
+    try {
+        if (mode == "json") {
+            std::cout << pj::parse(slurp(argv[2])).dump() << "\n";
+            return 0;
+        }
+        if (mode == "tokenize") {
+            const pj::Value spec = pj::parse(slurp(argv[2]));
+            std::vector<std::string> tokens, merges;
+            std::vector<float> scores;
+            std::vector<int> types;
+            for (const auto& v : spec["tokens"].items()) tokens.push_back(v.as_string());
+            for (const auto& v : spec["merges"].items()) merges.push_back(v.as_string());
+            for (const auto& v : spec["scores"].items()) scores.push_back((float)v.as_double());
+            for (const auto& v : spec["types"].items()) types.push_back((int)v.as_int());
+            pio::GGUFTokenizer tok(tokens, spec["model"].as_string(), scores, merges, types, (int)spec["bos"].as_int(-1), (int)spec["eos"].as_int(-1),
+                                   spec["add_bos"].as_bool());
+            std::cout << run_texts(tok, spec["texts"]).dump() << "\n";
+            return 0;
+        }
+        if (mode == "gguf-tokenize") {
+            pio::gguf::GGUFReader reader(argv[2]);
+            const pio::GGUFTokenizer tok = pio::GGUFTokenizer::from_reader(reader);
+            std::cout << run_texts(tok, pj::parse(slurp(argv[3]))).dump() << "\n";
+            return 0;
+        }
+        if (mode == "chat") {
+            const pj::Value spec = pj::parse(slurp(argv[2]));
+            pj::Value out = pj::Value::array();
+            for (const auto& c : spec.items()) {
+                if (c["messages"].is_array()) {
+                    std::vector<pio::chat::Message> ms;
+                    for (const auto& m : c["messages"].items()) ms.push_back({m["role"].as_string(), m["content"].as_string()});
+                    out.push_back(pio::chat::render_messages(ms, c["arch"].as_string(), c["name"].as_string()));
+                } else if (c["strip"].is_string()) {
+                    out.push_back(pio::chat::strip_think(c["strip"].as_string()));
+                } else {
+                    const std::string sys = c["system"].as_string();
+                    out.push_back(pio::chat::apply_chat_template(c["prompt"].as_string(), c["arch"].as_string(), c["name"].as_string(),
+                                                                 c["system"].is_string() ? &sys : nullptr, c["no_think"].is_null() ? -1 : (int)c["no_think"].as_bool()));
+                }
+            }
+            std::cout << out.dump() << "\n";
+            return 0;
+        }
+        if (mode == "serve") {
+            ps::ServerConfig cfg;
+            cfg.port = 0;
+            cfg.worker_threads = 2;
+            for (int i = 2; i + 1 < argc; i += 2) {
+                const std::string a = argv[i];
+                if (a == "--workers") cfg.worker_threads = std::atoi(argv[i + 1]);
+                if (a == "--queue-depth") cfg.max_queue_depth = std::atoi(argv[i + 1]);
+                if (a == "--timeout-ms") cfg.server_timeout_ms = std::atoi(argv[i + 1]);
+                if (a == "--model-dir") cfg.model_dirs.push_back(argv[i + 1]);
+                if (a == "--max-body") cfg.max_body_bytes = (size_t)std::atol(argv[i + 1]);
+                if (a == "--max-models") cfg.max_loaded_models = std::atoi(argv[i + 1]);
+            }
+            int loads = 0;
+            // names found on disk load as fakes that remember how many loads there were (no GPU in this program)
+            ps::PromeServe srv(cfg, [&cfg, &loads](const std::string& name) -> std::shared_ptr<ps::ModelBackend> {
+                const std::string path = ps::store::resolve(name, cfg.model_dirs);
+                auto b = std::make_shared<FakeBackend>("echo");
+                b->size = ps::store::file_size(path);
+                b->parameter_size = "load#" + std::to_string(++loads);
+                return b;
+            });
+            for (const char* k : {"echo", "mirror", "slow", "tool"}) srv.handlers().add_backend(std::string(k) + ":1b", std::make_shared<FakeBackend>(k));
+            srv.start();
+            std::cout << "PORT " << srv.port() << std::endl;
+            std::string line;
+            while (std::getline(std::cin, line)) {
+                if (line == "loaded") std::cout << "LOADED " << srv.handlers().loaded_models() << std::endl;
+            }
+            srv.stop();
+            return 0;
+        }
+    } catch (const std::exception& e) {
+        std::cerr << "error: " << e.what() << "\n";
+        return 1;
+    }
+    return 2;
+}

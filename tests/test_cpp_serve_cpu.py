@@ -1,0 +1,367 @@
+"""The native serving stack of the C++ API (json.h, tokenizer.h, chat.h, serve.h) against the Python implementations:
+same token ids, same prompts, same wire format.  The test program serves fake backends, so no GPU is involved."""
+import http.client
+import json
+import os
+import shutil
+import socket
+import subprocess
+import threading
+import time
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+TEXTS = ["Hello world", " leading space", "it's we're I'll they've I'm he'd don't 'quoted'", "tabs\tand\nnewlines\n\n  and   runs  ",
+         "numbers 12345 and 3.14 and x2y", "punctuation!!! (really?) -- yes; no: [ok] {fine} <tag> a.b,c", "Привет, мир! Как дела?",
+         "日本語のテキスト、それと English。", "café naïve über straße", "emoji \U0001F600 and ☃ snow — dash “quotes”",
+         "<|im_start|>user\nhi<|im_end|>\n<|im_start|>assistant\n", "mixed<|endoftext|>tail", "", " ", "  ", "a", "\n", "trailing space ",
+         "مرحبا بالعالم ١٢٣", "x² + y³ = ½", "  \n x"]
+
+
+@pytest.fixture(scope="module")
+def exe(tmp_path_factory):
+    if shutil.which("g++") is None:
+        pytest.skip("needs g++")
+    out = str(tmp_path_factory.mktemp("serve_native") / "serve_native")
+    cmd = ["g++", "-std=c++17", "-O1", "-Wall", "-Werror", os.path.join(ROOT, "tests", "cpp", "serve_native.cpp"), "-o", out,
+           f"-I{ROOT}/prometorch_b200/cpp_api", "-lpthread"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-4000:]
+    return out
+
+
+def _run(exe, *args):
+    r = subprocess.run([exe, *args], capture_output=True, timeout=120)
+    assert r.returncode == 0, r.stderr.decode()[-2000:]
+    return json.loads(r.stdout.decode("utf-8"))
+
+
+def _train_bpe(corpus, n_merges):
+    """A small byte-level BPE vocabulary in GPT-2's spelling (bytes mapped to printable code points)."""
+    from prometorch_b200.io.tokenizer import _B2U, _GPT2_PAT
+    words = {}
+    for piece in _GPT2_PAT.findall(corpus):
+        w = tuple(_B2U[b] for b in piece.encode("utf-8"))
+        words[w] = words.get(w, 0) + 1
+    merges = []
+    for _ in range(n_merges):
+        pairs = {}
+        for w, c in words.items():
+            for a, b in zip(w, w[1:]):
+                pairs[(a, b)] = pairs.get((a, b), 0) + c
+        if not pairs:
+            break
+        (a, b), _ = max(sorted(pairs.items()), key=lambda kv: kv[1])
+        merges.append(f"{a} {b}")
+        new = {}
+        for w, c in words.items():
+            out, i = [], 0
+            while i < len(w):
+                if i + 1 < len(w) and w[i] == a and w[i + 1] == b:
+                    out.append(a + b)
+                    i += 2
+                else:
+                    out.append(w[i])
+                    i += 1
+            new[tuple(out)] = new.get(tuple(out), 0) + c
+        words = new
+    tokens = [_B2U[b] for b in range(256)] + [m.replace(" ", "") for m in merges]
+    return tokens, merges
+
+
+def _check_tokenizer(exe, tmp_path, spec, texts):
+    from prometorch_b200.io.tokenizer import GGUFTokenizer
+    py = GGUFTokenizer(spec["tokens"], spec["model"], spec["scores"] or None, spec["merges"] or None, spec["types"] or None, spec["bos"], spec["eos"],
+                       spec["add_bos"])
+    spec = dict(spec, texts=texts)
+    p = tmp_path / "spec.json"
+    p.write_text(json.dumps(spec, ensure_ascii=False), encoding="utf-8")
+    got = _run(exe, "tokenize", str(p))
+    for i, t in enumerate(texts):
+        want = py.encode(t)
+        assert got["ids"][i] == want, (t, got["ids"][i], want)
+        assert got["decoded"][i] == py.decode(want), t
+        assert got["single"][i] == [py.decode_token(x) for x in want], t
+    return got
+
+
+def test_gpt2_tokenizer_matches_python(exe, tmp_path):
+    from prometorch_b200.io.tokenizer import _GPT2_PAT
+    corpus = " ".join(TEXTS) * 3 + " the quick brown fox jumps over the lazy dog " * 20 + " hello hello world world 123 123 "
+    tokens, merges = _train_bpe(corpus, 300)
+    tokens += ["<|im_start|>", "<|im_end|>", "<|endoftext|>"]
+    types = [1] * (len(tokens) - 3) + [3, 3, 3]
+    spec = {"tokens": tokens, "model": "gpt2", "scores": [], "merges": merges, "types": types, "bos": -1, "eos": len(tokens) - 1, "add_bos": False}
+    got = _check_tokenizer(exe, tmp_path, spec, TEXTS)
+    for i, t in enumerate(TEXTS):                       # the hand-written scanner against the pattern
+        assert got["pieces"][i] == _GPT2_PAT.findall(t), t
+
+
+def test_spm_tokenizer_matches_python(exe, tmp_path):
+    bar = "▁"
+    base = ["<unk>", "<s>", "</s>"] + [f"<0x{b:02X}>" for b in range(256)]
+    chars = sorted(set("".join(TEXTS).replace(" ", bar) + bar + "abcdefghijklmnopqrstuvwxyz"))
+    chars = [c for c in chars if c not in "\n\t"]       # left to the byte fall-back
+    words = [bar + "Hello", bar + "world", bar + "the", "ing", "er", bar + "a", "ll", "he", bar + "he", "llo", bar + "hello", "or", "ld", "wor", bar + "wor",
+             bar + bar, "an", bar + "an", bar + "and", "nd", "num", "ber", "bers", bar + "num", bar + "numbers", "12", "123", "45", bar + "мир", "При", "вет",
+             "日本", "日本語", "<|im_start|>", "<|im_end|>", "<|endoftext|>", "user", bar + "user", "ass", "ist", "ant", "assistant"]
+    tokens = base + chars + [w for w in words if w not in chars]
+    scores = [0.0] * len(base) + [-100.0 - i for i in range(len(chars))] + [-1.0 - 0.5 * i for i in range(len(tokens) - len(base) - len(chars))]
+    types = [2, 3, 3] + [6] * 256 + [1] * (len(tokens) - 259)
+    for s in ("<|im_start|>", "<|im_end|>", "<|endoftext|>"):
+        types[tokens.index(s)] = 4
+    spec = {"tokens": tokens, "model": "llama", "scores": scores, "merges": [], "types": types, "bos": 1, "eos": 2, "add_bos": True}
+    _check_tokenizer(exe, tmp_path, spec, TEXTS + ["Hello world the hello", "numbers and numbers", "hellohello"])
+    spec["add_bos"] = False
+    _check_tokenizer(exe, tmp_path, spec, ["Hello", bar + "already marked", "tie breaks: aaaa llll"])
+
+
+def test_tokenizer_from_a_gguf_file(exe, tmp_path):
+    from prometorch_b200.io.config import tiny_qwen3_config
+    from prometorch_b200.io.gguf import GGUFReader
+    from prometorch_b200.io.synthetic import write_synthetic_gguf
+    from prometorch_b200.io.tokenizer import GGUFTokenizer
+    path = str(tmp_path / "tok.gguf")
+    write_synthetic_gguf(path, tiny_qwen3_config(layers=1, hidden=256, heads=4, kv_heads=2, inter=512, vocab=512), seed=1, device="cpu")
+    reader = GGUFReader(path)
+    if reader.get("tokenizer.ggml.tokens") is None:
+        pytest.skip("the synthetic writer put no tokenizer into the file")
+    py = GGUFTokenizer.from_reader(reader)
+    texts = ["hello world", "abc 123", "tok5 tok17", "éè", "x"]
+    t = tmp_path / "texts.json"
+    t.write_text(json.dumps(texts), encoding="utf-8")
+    got = _run(exe, "gguf-tokenize", path, str(t))
+    for i, s in enumerate(texts):
+        assert got["ids"][i] == py.encode(s), s
+        assert got["decoded"][i] == py.decode(py.encode(s)), s
+
+
+def test_json_roundtrip(exe, tmp_path):
+    doc = {"a": [1, -2, 3.5, 1e-7, 12345678901234, True, False, None], "s": "quote \" slash \\ nl \n tab \t uni é 中 \U0001F600 ctl \u0001",
+           "nested": {"empty_obj": {}, "empty_arr": [], "k": {"deep": [[[]]]}}, "order": 1, "z": 0, "b": 2}
+    p = tmp_path / "doc.json"
+    p.write_text(json.dumps(doc), encoding="utf-8")              # ensure_ascii: exercises \uXXXX and surrogate pairs
+    got = _run(exe, "json", str(p))
+    assert got == doc and list(got) == list(doc)
+    p.write_text(json.dumps(doc, ensure_ascii=False), encoding="utf-8")
+    assert _run(exe, "json", str(p)) == doc
+    p.write_text('{"a": [1, 2,, 3]}')
+    r = subprocess.run([exe, "json", str(p)], capture_output=True, timeout=60)
+    assert r.returncode == 1 and b"JSON" in r.stderr
+
+
+def test_chat_templates_match_python(exe, tmp_path, monkeypatch):
+    from prometorch_b200.io.chat import apply_chat_template, render_messages, strip_think
+    for k in ("PT_SYSTEM_PROMPT", "PROMETHORCH_SYSTEM_PROMPT", "PT_NO_THINK", "PROMETHORCH_NO_THINK"):
+        monkeypatch.delenv(k, raising=False)
+    cases, want = [], []
+    for arch, name in [("qwen3", ""), ("qwen2", ""), ("phi3", ""), ("gemma3", ""), ("llama", "Meta Llama 3"), ("llama", "Mistral-7B"), ("other", "")]:
+        for system in (None, "", "be brief"):
+            for no_think in (None, True, False):
+                c = {"prompt": "what is 2+2?", "arch": arch, "name": name}
+                if system is not None:
+                    c["system"] = system
+                if no_think is not None:
+                    c["no_think"] = no_think
+                cases.append(c)
+                want.append(apply_chat_template("what is 2+2?", arch, name, system, no_think))
+        for msgs in ([{"role": "user", "content": "hi"}],
+                     [{"role": "system", "content": "S1"}, {"role": "system", "content": "S2"}, {"role": "user", "content": "q1"},
+                      {"role": "assistant", "content": "a1"}, {"role": "tool", "content": "t1"}, {"role": "user", "content": "q2"}],
+                     [{"role": "system", "content": "only system"}], [{"role": "system", "content": ""}, {"role": "user", "content": "u"}], []):
+            cases.append({"messages": msgs, "arch": arch, "name": name})
+            want.append(render_messages(msgs, arch, name))
+    for s in ("<think>plan</think>\n\nanswer", "no blocks", "<think>a</think>x<think>b</think>  y", "<think>unclosed"):
+        cases.append({"strip": s})
+        want.append(strip_think(s))
+    p = tmp_path / "chat.json"
+    p.write_text(json.dumps(cases), encoding="utf-8")
+    got = _run(exe, "chat", str(p))
+    for c, g, w in zip(cases, got, want):
+        assert g == w, c
+    monkeypatch.setenv("PT_SYSTEM_PROMPT", "from env")
+    monkeypatch.setenv("PROMETHORCH_NO_THINK", "1")
+    p.write_text(json.dumps([{"prompt": "q", "arch": "qwen3", "name": ""}]))
+    assert _run(exe, "chat", str(p)) == [apply_chat_template("q", "qwen3")]
+
+
+# ------------------------------------------------------------------------------------------------------------- server
+class Server:
+    def __init__(self, exe, *flags, env=None):
+        self.p = subprocess.Popen([exe, "serve", *flags], stdin=subprocess.PIPE, stdout=subprocess.PIPE, stderr=subprocess.PIPE, env=env)
+        line = self.p.stdout.readline().decode()
+        assert line.startswith("PORT "), line + self.p.stderr.read().decode()
+        self.port = int(line.split()[1])
+
+    def ask(self, word):
+        self.p.stdin.write((word + "\n").encode())
+        self.p.stdin.flush()
+        return self.p.stdout.readline().decode().strip()
+
+    def close(self):
+        try:
+            self.p.stdin.close()
+            self.p.wait(timeout=20)
+        except Exception:
+            self.p.kill()
+
+
+@pytest.fixture()
+def server(exe):
+    s = Server(exe)
+    yield s
+    s.close()
+
+
+def _req(port, method, path, body=None, raw=None):
+    c = http.client.HTTPConnection("127.0.0.1", port, timeout=30)
+    c.request(method, path, raw if raw is not None else (None if body is None else json.dumps(body)), {"Content-Type": "application/json"})
+    r = c.getresponse()
+    data = r.read()
+    c.close()
+    return r.status, dict(r.getheaders()), data
+
+
+def test_native_server_routes(server):
+    port = server.port
+    st, hdr, data = _req(port, "GET", "/")
+    assert st == 200 and b"PromeServe is running" in data
+    st, hdr, data = _req(port, "GET", "/api/version")
+    assert st == 200 and json.loads(data) == {"version": "0.1.0-promeserve"}
+    st, hdr, data = _req(port, "GET", "/api/tags")
+    tags = json.loads(data)["models"]
+    e = [m for m in tags if m["name"] == "echo:1b"][0]
+    assert st == 200 and e["model"] == "echo:1b" and e["size"] == 1234 and e["details"] == {"family": "qwen3", "format": "gguf", "parameter_size": "1B"}
+    assert set(e) == {"name", "model", "modified_at", "size", "digest", "details"}
+    st, hdr, data = _req(port, "POST", "/api/show", {"name": "echo:1b"})
+    assert st == 200 and json.loads(data)["model_info"]["general.architecture"] == "qwen3"
+    assert _req(port, "POST", "/api/show", {"model": "echo"})[0] == 200                      # the tag is optional
+    assert _req(port, "POST", "/api/embeddings", {"model": "echo:1b", "prompt": "x"})[0] == 501
+    assert _req(port, "GET", "/nope")[0] == 404
+    st, hdr, data = _req(port, "OPTIONS", "/api/generate")
+    assert st == 204 and hdr.get("Access-Control-Allow-Origin") == "*" and hdr.get("Access-Control-Allow-Methods") == "POST, GET, OPTIONS"
+    assert hdr.get("Access-Control-Allow-Headers") == "Content-Type, Authorization"
+    assert _req(port, "HEAD", "/api/tags")[0] == 200 and _req(port, "HEAD", "/other")[0] == 404
+
+
+def test_native_server_generate_and_stream(server):
+    port = server.port
+    st, _, data = _req(port, "POST", "/api/generate", {"model": "echo:1b", "prompt": "hi", "stream": False, "raw": True,
+                                                      "options": {"num_predict": 5, "temperature": 0.0}})
+    out = json.loads(data)
+    assert st == 200 and out["response"] == "hello" and out["done"] is True and out["eval_count"] == 5 and out["prompt_eval_count"] == 2
+    assert out["model"] == "echo:1b" and out["load_duration"] == 0 and out["total_duration"] == out["prompt_eval_duration"] + out["eval_duration"]
+    # options reach the backend; a raw prompt is not templated
+    st, _, data = _req(port, "POST", "/api/generate", {"model": "mirror:1b", "prompt": "abc", "stream": False, "raw": True,
+                                                      "options": {"top_k": 7, "temperature": 0.25}})
+    assert json.loads(data)["response"] == "abc|7|25"
+    st, _, data = _req(port, "POST", "/api/generate", {"model": "mirror:1b", "prompt": "abc", "stream": False, "system": "S"})
+    assert json.loads(data)["response"].startswith("<|im_start|>system\nS<|im_end|>\n<|im_start|>user\nabc<|im_end|>\n<|im_start|>assistant\n|40|")
+    # streaming: chunked NDJSON, one object per token, then the statistics
+    st, hdr, data = _req(port, "POST", "/api/generate", {"model": "echo:1b", "prompt": "hi"})
+    assert st == 200 and hdr.get("Content-Type") == "application/x-ndjson" and hdr.get("Transfer-Encoding") == "chunked"
+    lines = [json.loads(l) for l in data.decode().splitlines() if l.strip()]
+    assert "".join(l.get("response", "") for l in lines) == "hello world" and len(lines) == 12
+    assert lines[-1]["done"] is True and all(not l["done"] for l in lines[:-1]) and lines[-1]["eval_count"] == 11
+    assert all(set(l) == {"model", "created_at", "response", "done"} for l in lines[:-1])
+
+
+def test_native_server_chat_and_tools(server):
+    port = server.port
+    msgs = [{"role": "system", "content": "be brief"}, {"role": "user", "content": "hey"}]
+    st, _, data = _req(port, "POST", "/api/chat", {"model": "mirror:1b", "stream": False, "messages": msgs})
+    out = json.loads(data)
+    assert st == 200 and out["message"]["role"] == "assistant"
+    assert out["message"]["content"].startswith("<|im_start|>system\nbe brief<|im_end|>\n<|im_start|>user\nhey<|im_end|>\n<|im_start|>assistant\n")
+    st, hdr, data = _req(port, "POST", "/api/chat", {"model": "echo:1b", "messages": msgs})
+    lines = [json.loads(l) for l in data.decode().splitlines() if l.strip()]
+    assert "".join(l["message"]["content"] for l in lines) == "hello world" and lines[-1]["done"] and lines[-1]["message"]["content"] == ""
+    tools = [{"type": "function", "function": {"name": "add", "parameters": {}}}]
+    st, _, data = _req(port, "POST", "/api/chat", {"model": "tool:1b", "stream": False, "messages": msgs, "tools": tools})
+    out = json.loads(data)
+    assert out["message"]["tool_calls"] == [{"function": {"name": "add", "arguments": {"a": 1, "b": 2}}}]
+
+
+def test_native_server_errors_and_limits(exe, tmp_path):
+    s = Server(exe, "--max-body", "2000")
+    try:
+        st, _, data = _req(s.port, "POST", "/api/generate", {"model": "missing:7b", "prompt": "x", "stream": False})
+        assert st == 404 and "error" in json.loads(data)
+        assert _req(s.port, "POST", "/api/generate", raw="{not json")[0] == 400
+        assert _req(s.port, "POST", "/api/generate", {"model": "echo:1b", "prompt": "x" * 5000})[0] == 413
+        for bad in ("/etc/passwd", "../x", "a/b", "..", "a\\b"):
+            st, _, data = _req(s.port, "POST", "/api/generate", {"model": bad, "prompt": "x", "stream": False})
+            assert st == 404, bad
+    finally:
+        s.close()
+
+
+def test_native_server_timeout_and_backpressure(exe):
+    s = Server(exe, "--timeout-ms", "300", "--workers", "1", "--queue-depth", "1")
+    try:
+        t0 = time.time()
+        st, _, data = _req(s.port, "POST", "/api/generate", {"model": "slow:1b", "prompt": "x", "raw": True, "options": {"num_predict": 200}})
+        lines = [json.loads(l) for l in data.decode().splitlines() if l.strip()]
+        assert st == 200 and lines[-1] == {"error": "timeout", "done": True} and 2 <= len(lines) < 40 and time.time() - t0 < 5
+        # one worker busy, one connection queued: the next one is turned away
+        socks = []
+        for _ in range(2):
+            c = socket.create_connection(("127.0.0.1", s.port), timeout=10)
+            body = json.dumps({"model": "slow:1b", "prompt": "x", "raw": True, "options": {"num_predict": 200}})
+            c.sendall(f"POST /api/generate HTTP/1.1\r\nHost: x\r\nContent-Length: {len(body)}\r\n\r\n{body}".encode())
+            socks.append(c)
+            time.sleep(0.05)
+        st, hdr, _ = _req(s.port, "GET", "/api/version")
+        assert st == 503 and hdr.get("Retry-After") == "1"
+        for c in socks:
+            c.close()
+        time.sleep(0.8)
+        assert _req(s.port, "GET", "/api/version")[0] == 200                          # and recovers
+    finally:
+        s.close()
+
+
+def test_native_server_finds_models_on_disk(exe, tmp_path):
+    """Model directories and the Ollama store: listing, loading by name, eviction of the least recently used."""
+    d = tmp_path / "models"
+    d.mkdir()
+    for n in ("alpha", "beta", "gamma"):
+        (d / f"{n}.gguf").write_bytes(b"x" * (10 + len(n)))
+    store = tmp_path / "ollama"
+    lib = store / "manifests" / "registry.ollama.ai" / "library" / "tiny"
+    lib.mkdir(parents=True)
+    (store / "blobs").mkdir()
+    (store / "blobs" / "sha256-abc").write_bytes(b"y" * 77)
+    (lib / "latest").write_text(json.dumps({"layers": [{"mediaType": "application/vnd.ollama.image.license", "digest": "sha256:zzz"},
+                                                       {"mediaType": "application/vnd.ollama.image.model", "digest": "sha256:abc"}]}))
+    other = store / "manifests" / "registry.ollama.ai" / "library" / "busted"
+    other.mkdir(parents=True)
+    (other / "latest").write_text(json.dumps({"layers": [{"mediaType": "application/vnd.ollama.image.model", "digest": "sha256:nope"}]}))
+    s = Server(exe, "--model-dir", str(d), "--max-models", "2", env=dict(os.environ, OLLAMA_MODELS=str(store)))
+    try:
+        names = {m["name"]: m for m in json.loads(_req(s.port, "GET", "/api/tags")[2])["models"]}
+        assert {"alpha", "beta", "gamma", "tiny:latest", "echo:1b"} <= set(names) and "busted:latest" not in names
+        assert names["alpha"]["size"] == 15 and names["tiny:latest"]["size"] == 77
+        show = json.loads(_req(s.port, "POST", "/api/show", {"model": "tiny"})[2])
+        assert show["details"]["parameter_size"] == "load#1"
+        assert _req(s.port, "POST", "/api/generate", {"model": "busted", "prompt": "x", "stream": False})[0] == 404
+        base = int(s.ask("loaded").split()[1])
+        for n in ("alpha", "beta", "alpha", "gamma"):                                   # gamma pushes out beta (alpha was used after it); tiny went first
+            out = json.loads(_req(s.port, "POST", "/api/generate", {"model": n, "prompt": "x", "stream": False, "raw": True})[2])
+            assert out["response"] == "hello world"
+        assert int(s.ask("loaded").split()[1]) == base - 1 + 2
+        tags = {m["name"]: m for m in json.loads(_req(s.port, "GET", "/api/tags")[2])["models"]}
+        assert tags["alpha"]["details"]["parameter_size"] == "load#2" and tags["gamma"]["details"]["parameter_size"] == "load#4"
+        assert tags["beta"]["details"]["parameter_size"] == ""                          # listed from disk again, not loaded
+        # concurrent requests for a new name load it once
+        out = []
+        ts = [threading.Thread(target=lambda: out.append(json.loads(_req(s.port, "POST", "/api/show", {"model": "beta"})[2]))) for _ in range(4)]
+        for t in ts:
+            t.start()
+        for t in ts:
+            t.join()
+        assert {o["details"]["parameter_size"] for o in out} == {"load#5"}
+    finally:
+        s.close()
