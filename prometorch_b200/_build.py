@@ -28,6 +28,7 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--use_fast_math", "-Xcompiler",
 
 APPS = ROOT / "cpp_api" / "apps"
 PROMESERVE = LIBDIR / "promeserve"
+GGUF_GENERATE = LIBDIR / "gguf_generate"
 
 
 def _nvcc() -> str:
@@ -90,8 +91,18 @@ if __name__ == "__main__":
 def build_promeserve(force: bool = False) -> Path:
     """The native server (``cpp_api/apps/promeserve.cpp``: C++ HTTP server + tokenizer + the CUDA decode engine) as
     ``lib/promeserve``, linked against ``lib/libptb200.so`` and the CUDA runtime."""
+    return build_app("promeserve", force)
+
+
+def build_generate(force: bool = False) -> Path:
+    """The native generation CLI (``cpp_api/apps/gguf_generate.cpp``) as ``lib/gguf_generate``."""
+    return build_app("gguf_generate", force)
+
+
+def build_app(name: str, force: bool = False) -> Path:
     build()
-    src = APPS / "promeserve.cpp"
+    src = APPS / f"{name}.cpp"
+    PROMESERVE = LIBDIR / name
     hdrs = list((ROOT / "cpp_api" / "promethorch").glob("*.h")) + [CSRC / "ptb200.h", CSRC / "ptb200_types.h"]
     newest = max([src.stat().st_mtime, LIB.stat().st_mtime] + [h.stat().st_mtime for h in hdrs if h.exists()])
     if not force and PROMESERVE.exists() and PROMESERVE.stat().st_mtime >= newest:
@@ -102,5 +113,5 @@ def build_promeserve(force: bool = False) -> Path:
            f"-L{cuda / 'lib64'}", "-lcudart", "-lpthread", "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{cuda / 'lib64'}"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
-        raise RuntimeError(f"building promeserve failed:\n{r.stdout}\n{r.stderr}")
+        raise RuntimeError(f"building {name} failed:\n{r.stdout}\n{r.stderr}")
     return PROMESERVE

@@ -191,6 +191,8 @@ class GGUFModel {
         if (samp_n_hist_ < kHistCap) ++samp_n_hist_;
         return host[0];
     }
+    // Phase stamps of the last token (PTB_TRACE=1 at load): [kernels][8] nanoseconds; returns the kernel count.
+    int read_trace(unsigned long long* out, int max_kernels) { return ptb_engine_read_trace(engine_, out, max_kernels); }
     int max_seq() const { return max_seq_; }
     size_t weight_bytes() const { return weight_bytes_; }
     const gguf::GGUFReader& reader() const { return reader_; }

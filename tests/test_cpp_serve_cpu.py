@@ -365,3 +365,28 @@ def test_native_server_finds_models_on_disk(exe, tmp_path):
         assert {o["details"]["parameter_size"] for o in out} == {"load#5"}
     finally:
         s.close()
+
+
+def test_native_generate_cli_prints_metadata_and_tensors(tmp_path):
+    """`gguf_generate --info / --tensors` read the file without touching a GPU."""
+    if shutil.which("nvcc") is None and not os.path.exists("/usr/local/cuda/bin/nvcc"):
+        pytest.skip("needs nvcc to link the program against the native library")
+    from prometorch_b200 import _build
+    from prometorch_b200.io.config import tiny_qwen3_config
+    from prometorch_b200.io.gguf import GGUFReader
+    from prometorch_b200.io.synthetic import write_synthetic_gguf
+    exe = str(_build.build_generate())
+    path = str(tmp_path / "cli.gguf")
+    write_synthetic_gguf(path, tiny_qwen3_config(layers=1, hidden=256, heads=4, kv_heads=2, inter=512, vocab=512), seed=2, device="cpu")
+    r = subprocess.run([exe, path, "--info", "--tensors"], capture_output=True, text=True, timeout=60)
+    assert r.returncode == 0, r.stderr
+    assert "general.architecture = 'qwen3'" in r.stdout and "architecture qwen3, 1 layers, hidden 256, 4 heads (2 kv), ffn 512" in r.stdout
+    reader = GGUFReader(path)
+    listed = {ln.split()[0]: ln for ln in r.stdout.splitlines() if ln.startswith(("blk.", "token_embd", "output"))}
+    assert set(listed) == set(reader.tensors)
+    for name, t in reader.tensors.items():
+        assert listed[name].split()[-2] == str(t.nbytes) and t.qtype.name in listed[name]
+    assert subprocess.run([exe], capture_output=True).returncode == 2
+    assert subprocess.run([exe, path, "--bogus"], capture_output=True).returncode == 2
+    r = subprocess.run([exe, str(tmp_path / "missing.gguf"), "--info"], capture_output=True, text=True)
+    assert r.returncode == 1 and "cannot open" in r.stderr

@@ -72,3 +72,41 @@ def test_native_promeserve_serves_a_gguf_file(tmp_path):
             p.wait(timeout=30)
         except subprocess.TimeoutExpired:
             p.kill()
+
+
+def test_native_generate_cli_matches_the_python_model(tmp_path):
+    """`lib/gguf_generate` (C++ from the file to the printed text) against the Python model and tokenizer."""
+    from prometorch_b200 import _build
+    from prometorch_b200.io.config import tiny_qwen3_config
+    from prometorch_b200.io.gguf_model import GGUFModel
+    from prometorch_b200.io.synthetic import write_synthetic_gguf
+    from prometorch_b200.io.tokenizer import GGUFTokenizer
+    exe = str(_build.build_generate())
+    path = str(tmp_path / "tiny.gguf")
+    write_synthetic_gguf(path, tiny_qwen3_config(layers=2, hidden=512, heads=8, kv_heads=2, inter=1024, vocab=1024), seed=6, device="cpu")
+    m = GGUFModel(path, device="cuda", max_seq=256)
+    tok = GGUFTokenizer.from_reader(m.reader)
+    prompt = "t400 t401 t27 t900 t5"
+    ids = tok.encode(prompt)
+    want = m.run_script(ids, 10)
+    m.close()
+    stop = {tok.eos_id} | {tok.vocab[t] for t in ("<|im_end|>", "<|eot_id|>", "<end_of_turn>", "<|end|>", "<|endoftext|>") if t in tok.vocab}
+    for i, t in enumerate(want):
+        if t in stop:
+            want = want[:i + 1]
+            break
+    r = subprocess.run([exe, path, prompt, "--greedy", "--max-tokens", "10", "--profile"], capture_output=True, text=True, timeout=240)
+    assert r.returncode == 0, r.stdout[-1000:] + r.stderr[-2000:]
+    got = [int(x) for x in [ln for ln in r.stdout.splitlines() if ln.startswith("[Ids]")][0].split()[1:]]
+    assert got == want, (got, want)
+    assert f"[Generate] Prompt tokens: {len(ids)}" in r.stdout and "tok/s" in r.stdout
+    assert "[Profile] qkv" in r.stdout and "[Profile] lm_head" in r.stdout
+    # sampled on the device: the seed decides the draw
+    runs = []
+    for seed in ("3", "3", "4"):
+        r = subprocess.run([exe, path, prompt, "--max-tokens", "12", "--temp", "1.5", "--top-k", "50", "--top-p", "0.95", "--seed", seed, "--chat"],
+                           capture_output=True, text=True, timeout=240)
+        assert r.returncode == 0, r.stderr[-2000:]
+        runs.append([int(x) for x in [ln for ln in r.stdout.splitlines() if ln.startswith("[Ids]")][0].split()[1:]])
+        assert 1 <= len(runs[-1]) <= 12 and all(0 <= t < 1024 for t in runs[-1])
+    assert runs[0] == runs[1]
