@@ -277,6 +277,49 @@ def served_figure(path, dev, prompt_ids, n_new):
         backend.model.close()
 
 
+def served_native_figure(path, prompt_ids, n_new):
+    """The same request against the native server (lib/promeserve: C++ HTTP front end, tokenizer and decode loop on the same
+    engine), started as a child process on the same GPU; tok/s from the final chunk's eval_count / eval_duration."""
+    import http.client
+    from prometorch_b200 import _build
+    exe = _build.build_promeserve()
+    p = subprocess.Popen([str(exe), "--model", path, "--port", "0", "--max-seq", "4096"], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+    try:
+        port, t0 = None, time.time()
+        while time.time() - t0 < 120:
+            line = p.stdout.readline()
+            if not line:
+                break
+            if "listening on" in line:
+                port = int(line.rsplit(":", 1)[1])
+                break
+        if port is None:
+            return {"error": "the native server did not come up: " + p.stderr.read()[-200:]}
+        body = json.dumps({"model": os.path.basename(path)[:-5], "prompt": " ".join(f"t{i}" for i in prompt_ids), "raw": True, "stream": True,
+                           "options": {"num_predict": n_new, "temperature": 0.0, "repeat_penalty": 1.0}})
+        best = None
+        for _ in range(2):                       # the first request captures the graph
+            c = http.client.HTTPConnection("127.0.0.1", port, timeout=300)
+            t1 = time.perf_counter()
+            c.request("POST", "/api/generate", body, {"Content-Type": "application/json"})
+            lines = [json.loads(ln) for ln in c.getresponse().read().decode().splitlines() if ln.strip().startswith("{")]
+            wall = time.perf_counter() - t1
+            c.close()
+            last = lines[-1] if lines else {}
+            if "eval_count" not in last:
+                return {"error": str(last)[:200]}
+            best = {"value": round(last["eval_count"] / (last["eval_duration"] / 1e9), 2), "unit": "tok/s", "eval_count": last["eval_count"],
+                    "prompt_eval_count": last["prompt_eval_count"], "chunks": len(lines), "request_wall_s": round(wall, 3),
+                    "route": "POST /api/generate (stream), native server (lib/promeserve)"}
+        return best
+    finally:
+        p.terminate()
+        try:
+            p.wait(timeout=30)
+        except subprocess.TimeoutExpired:
+            p.kill()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -396,6 +439,10 @@ def main():
                 served = served_figure(path, dev, prompt, K + Wm)
             except Exception as e:      # the served figure is an extra: never lose the bench line to it
                 served = {"error": repr(e)[:300]}
+            try:
+                served["native"] = served_native_figure(path, prompt, K + Wm)
+            except Exception as e:      # noqa: BLE001
+                served["native"] = {"error": repr(e)[:300]}
         else:
             served = {"unavailable": "the HTTP server drives a single-GPU engine"}
 
