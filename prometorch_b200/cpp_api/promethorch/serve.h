@@ -1,8 +1,8 @@
 // promethorch C++ API: PromeServe, an Ollama-compatible HTTP server (native counterpart of the reference's
 // promeserve/{http_server,api_handlers,model_manager}.h).
 //
-// Routes: GET / (liveness text), GET /api/version, GET /api/tags, POST /api/show, POST /api/generate, POST /api/chat,
-// POST /api/embeddings (501), HEAD, OPTIONS with CORS.  Streaming answers are chunked application/x-ndjson: one object
+// Routes: GET / (liveness text), GET /api/version, GET /api/tags, GET /api/ps (loaded models and counters), POST /api/show,
+// POST /api/generate, POST /api/chat, POST /api/embeddings (501), HEAD, OPTIONS with CORS.  Streaming answers are chunked application/x-ndjson: one object
 // per token ({"model","created_at","response","done":false}, or "message":{"role","content"} for chat) and a final
 // object with total_duration, load_duration, prompt_eval_count, prompt_eval_duration, eval_count, eval_duration in
 // nanoseconds.  Back-pressure: a bounded queue in front of a fixed pool of workers; a full queue answers 503 with
@@ -302,6 +302,25 @@ class ApiHandlers {
         out.set("models", models);
         return out;
     }
+    // Loaded models and the server's counters (the shape of Ollama's /api/ps, plus "stats").
+    json::Value ps() {
+        json::Value models = json::Value::array();
+        std::lock_guard<std::mutex> g(table_mutex_);
+        for (const auto& kv : backends_) {
+            json::Value m = model_entry(kv.first, kv.second->size, kv.second->architecture, kv.second->format, kv.second->parameter_size);
+            m.set("expires_at", "");
+            m.set("size_vram", kv.second->size);
+            models.push_back(m);
+        }
+        json::Value out = json::Value::object(), st = json::Value::object();
+        st.set("requests", (long long)requests_.load());
+        st.set("tokens_generated", (long long)tokens_generated_.load());
+        st.set("prompt_tokens", (long long)prompt_tokens_.load());
+        st.set("timeouts", (long long)timeouts_.load());
+        out.set("models", models);
+        out.set("stats", st);
+        return out;
+    }
     json::Value show(const json::Value& body) {
         const std::string name = body["model"].is_string() ? body["model"].as_string() : body["name"].as_string();
         auto b = ensure_model(name);
@@ -480,6 +499,10 @@ class ApiHandlers {
         r.n_prompt = (int)ids.size();
         r.prompt_s = t.first;
         r.eval_s = t.second;
+        ++requests_;
+        tokens_generated_ += r.n_eval;
+        prompt_tokens_ += r.n_prompt;
+        timeouts_ += r.timed_out ? 1 : 0;
         return r;
     }
 
@@ -488,6 +511,7 @@ class ApiHandlers {
     std::vector<std::pair<std::string, std::shared_ptr<ModelBackend>>> backends_;      // least recently used first
     std::set<std::string> pinned_;
     std::mutex table_mutex_, load_mutex_, generate_mutex_;
+    std::atomic<long long> requests_{0}, tokens_generated_{0}, prompt_tokens_{0}, timeouts_{0};
 };
 
 // ---------------------------------------------------------------------------------------------- HTTP
@@ -646,6 +670,7 @@ class HttpServer {
             return;
         }
         if (r.method == "GET" && r.path == "/api/tags") { net::send_response(fd, 200, h_.tags().dump()); return; }
+        if (r.method == "GET" && r.path == "/api/ps") { net::send_response(fd, 200, h_.ps().dump()); return; }
         if (r.method == "POST" && (r.path == "/api/embeddings" || r.path == "/api/embed")) {
             net::send_response(fd, 501, error_json("embeddings are not implemented"));
             return;

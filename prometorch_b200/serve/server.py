@@ -1,7 +1,7 @@
 """PromeServe: an Ollama-compatible HTTP server in front of the native decode engine.
 
 Routes and wire format follow promeserve/api_handlers.h:351-394 and http_server.h of the reference:
-``GET /`` (liveness text), ``GET /api/version``, ``GET /api/tags``, ``POST /api/show``,
+``GET /`` (liveness text), ``GET /api/version``, ``GET /api/tags``, ``GET /api/ps`` (loaded models and counters), ``POST /api/show``,
 ``POST /api/generate``, ``POST /api/chat``, ``POST /api/embeddings`` (501), ``HEAD``/``OPTIONS`` with CORS.
 Streaming responses are chunked ``application/x-ndjson``: one object per token
 (``{"model","created_at","response","done":false}`` or, for chat, ``"message":{"role","content"}``) and a
@@ -218,6 +218,7 @@ class ApiHandlers:
         self.load_mutex = threading.Lock()
         self.pinned = set(self.backends)          # backends handed in by the host program are never evicted
         self.tools_max_iters = 5
+        self.stats = {"requests": 0, "tokens_generated": 0, "prompt_tokens": 0, "timeouts": 0}
 
     # ------------------------------------------------------------------ model management
     def _lookup(self, name: str) -> Optional[ModelBackend]:
@@ -267,6 +268,13 @@ class ApiHandlers:
             pass
         return {"models": models}
 
+    def ps(self):
+        """Loaded models and the server's counters (Ollama's ``/api/ps`` shape, plus ``stats``)."""
+        models = [{"name": name, "model": name, "size": b.size, "digest": "", "expires_at": "", "size_vram": int(getattr(b, "size_vram", b.size)),
+                   "details": {"family": b.architecture, "format": b.format, "parameter_size": b.parameter_size}}
+                  for name, b in self.backends.items()]
+        return {"models": models, "stats": dict(self.stats)}
+
     def show(self, body):
         b = self.ensure_model(body.get("model") or body.get("name") or "")
         return {"modelfile": "", "parameters": "", "template": "", "details": {"family": b.architecture, "format": b.format,
@@ -297,6 +305,11 @@ class ApiHandlers:
         import contextlib
         with (contextlib.nullcontext() if getattr(backend, "concurrent", False) else self.generate_mutex):
             pe, ev = backend.generate(ids, options, on_token)
+        with self.load_mutex:
+            self.stats["requests"] += 1
+            self.stats["tokens_generated"] += state["n"]
+            self.stats["prompt_tokens"] += len(ids)
+            self.stats["timeouts"] += int(state["timeout"])
         stats = {"total_duration": int((pe + ev) * 1e9), "load_duration": 0, "prompt_eval_count": len(ids),
                  "prompt_eval_duration": int(pe * 1e9), "eval_count": state["n"], "eval_duration": int(ev * 1e9)}
         return "".join(pieces), stats, state["timeout"]
@@ -487,6 +500,8 @@ class HttpServer:
             return self._send(wfile, 200, json.dumps({"version": VERSION}).encode())
         if method == "GET" and path == "/api/tags":
             return self._send(wfile, 200, json.dumps(H.tags()).encode())
+        if method == "GET" and path == "/api/ps":
+            return self._send(wfile, 200, json.dumps(H.ps()).encode())
         if method == "POST" and path in ("/api/embeddings", "/api/embed"):
             # backends that can embed (the paged engine) answer; for the others this stays 501 as in the reference
             try:

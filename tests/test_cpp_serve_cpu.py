@@ -266,6 +266,9 @@ def test_native_server_generate_and_stream(server):
     assert "".join(l.get("response", "") for l in lines) == "hello world" and len(lines) == 12
     assert lines[-1]["done"] is True and all(not l["done"] for l in lines[:-1]) and lines[-1]["eval_count"] == 11
     assert all(set(l) == {"model", "created_at", "response", "done"} for l in lines[:-1])
+    ps = json.loads(_req(port, "GET", "/api/ps")[2])
+    assert {m["name"] for m in ps["models"]} >= {"echo:1b", "mirror:1b"} and ps["stats"]["requests"] == 4 and ps["stats"]["timeouts"] == 0
+    assert ps["stats"]["tokens_generated"] >= 5 + 8 + 11 and ps["stats"]["prompt_tokens"] >= 2 + 3 + 2
 
 
 def test_native_server_chat_and_tools(server):

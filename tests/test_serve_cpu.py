@@ -70,6 +70,9 @@ def test_generate_non_streaming_and_options(server):
     assert st == 200 and out["response"] == "hello" and out["done"] is True and out["eval_count"] == 5
     assert be.last_prompt == "hi" and int(be.last_options["num_predict"]) == 5
     assert out["model"] == "echo:1b" and "total_duration" in out
+    st, _, data = _req(srv.port, "GET", "/api/ps")
+    ps = json.loads(data)
+    assert st == 200 and ps["models"][0]["name"] == "echo:1b" and ps["stats"] == {"requests": 1, "tokens_generated": 5, "prompt_tokens": 2, "timeouts": 0}
 
 
 def test_generate_streams_ndjson(server):
