@@ -135,7 +135,10 @@ class GGUFBackend(ModelBackend):
         n_new = max(0, min(n_new, room))
         t0 = time.perf_counter()
         if len(prompt_ids) > 1:
-            m.run_script(prompt_ids[:-1], 1)
+            if m.supports_prefill and len(prompt_ids) - 1 >= 8:
+                m.prefill(prompt_ids[:-1])      # one batched pass over the prompt (tcgen05 GEMMs + FlashAttention); returns when it is done
+            else:
+                m.run_script(prompt_ids[:-1], 1)
         t1 = time.perf_counter()
         m.generate(prompt_ids[-1:], max_new_tokens=n_new, temperature=float(options.get("temperature", 0.7)),
                    top_k=int(options.get("top_k", 40)), top_p=float(options.get("top_p", 0.9)),
