@@ -13,7 +13,7 @@ from torch import (Tensor, arange, bmm, cat, chunk, clamp, cos, cumsum, device, 
                    nan_to_num, norm, ones, ones_like, rand, randint, randn, relu, rsqrt, scatter, sigmoid, sin, softmax, sort, split,
                    sqrt, stack, sum, tanh, tensor, topk, where, zeros, zeros_like)
 from torch import bfloat16, bool, float16, float32, float64, int8, int16, int32, int64, uint8  # noqa: F401
-from torch import enable_grad, is_grad_enabled, manual_seed, no_grad, set_grad_enabled  # noqa: F401
+from torch import Generator, enable_grad, is_grad_enabled, manual_seed, no_grad, set_grad_enabled  # noqa: F401
 from torch.autograd import backward, grad  # noqa: F401
 from torch.nn.utils.rnn import pack_padded_sequence, pack_sequence, pad_packed_sequence, pad_sequence  # noqa: F401
 

@@ -468,3 +468,15 @@ def test_idx_reader_mnist_and_char_dataset(tmp_path):
     c = CharTextDataset("hello world, hello there", block_size=5, is_text=True)
     a, b = c[3]
     assert c.decode(a) == "lo wo" and c.decode(b) == "o wor" and len(c) == len("hello world, hello there") - 5
+
+
+def test_ten_model_zoo_trains():
+    """examples/train_10_models.py: regression, classification, recurrent cells and the save / load round trip all reach their
+    thresholds in the quick setting."""
+    import importlib.util
+    import os
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples", "train_10_models.py")
+    spec = importlib.util.spec_from_file_location("train_10_models", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    assert len(mod.TASKS) == 10 and mod.main(["--quick"]) == 0
