@@ -17,3 +17,7 @@ _sys.modules["promethorch.safetensors_reader"] = safetensors_reader
 _sys.modules["promethorch.serve.llm"] = _llm
 _sys.modules["promethorch.nn.parallel"] = _impl.nn.parallel
 _sys.modules["promethorch.nn.functional"] = _impl.nn.functional
+
+
+def __getattr__(name: str):
+    return getattr(_impl, name)

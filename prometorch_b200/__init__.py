@@ -28,6 +28,16 @@ from .jit import compile  # noqa: E402
 TensorOptions = dict
 
 
+def __getattr__(name: str):
+    """Every other tensor function or factory (``randn_like``, ``full_like``, ``tril``, ...) is PyTorch's."""
+    if name.startswith("__"):
+        raise AttributeError(name)
+    try:
+        return getattr(_torch, name)
+    except AttributeError:
+        raise AttributeError(f"module 'prometorch_b200' has no attribute '{name}'") from None
+
+
 class DeviceType:
     CPU, CUDA = "cpu", "cuda"
 

@@ -480,3 +480,29 @@ def test_ten_model_zoo_trains():
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
     assert len(mod.TASKS) == 10 and mod.main(["--quick"]) == 0
+
+
+def test_generative_and_vision_examples_train():
+    """examples/generative_and_vision.py: VAE, GAN, ResNet-20, ViT and the sequence-to-sequence transformer all move."""
+    import importlib.util
+    import os
+    import warnings
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples", "generative_and_vision.py")
+    spec = importlib.util.spec_from_file_location("generative_and_vision", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        out = mod.main(["all"])
+    assert out["vae"][1] < 0.95 * out["vae"][0]
+    assert out["gan"][1] < out["gan"][0] - 1.0
+    for name in ("resnet", "vit", "transformer"):
+        assert out[name][1] < 0.7 * out[name][0], (name, out[name])
+
+
+def test_top_level_falls_back_to_torch():
+    import promethorch as pt
+    import prometorch_b200 as ptb
+    assert pt.randn_like(pt.zeros(3)).shape == (3,) and ptb.full_like(ptb.ones(2), 7.0).tolist() == [7.0, 7.0] and pt.Generator is torch.Generator
+    with pytest.raises(AttributeError):
+        ptb.no_such_function
