@@ -21,6 +21,7 @@ from .fsdp import (FSDPConfig, FullyShardedDataParallel, OffloadOptimizer, Shard
                    ZeROStage3Config)
 from .launcher import DistArgs, launch, parse_dist_args
 from .watchdog import DictStore, Heartbeat, RankFailure
+from .local_sgd import LocalSGD  # noqa: F401
 
 _current_pg: Optional[ProcessGroup] = None
 

@@ -218,3 +218,127 @@ def mlp_ddp_config1(rank, world):
     assert all(torch.allclose(parts[0], p, atol=1e-6) for p in parts)
     _fin()
     return 0
+
+
+def local_sgd_averages(rank, world):
+    """Ranks drift apart for sync_every - 1 steps, meet on the average at the next; with sync_every = 1 and plain SGD the run
+    equals gradient averaging."""
+    from .. import distributed as D
+    from ..optim import SGD
+    _init(rank, world)
+    torch.manual_seed(5)
+    X, Y = torch.randn(8 * world, 16), torch.randn(8 * world, 4)
+    xs, ys = X[rank::world], Y[rank::world]
+    model = D.LocalSGD(_mlp(3 + rank), sync_every=3)                 # different init per rank: the constructor broadcasts rank 0's
+    opt = SGD(model.parameters(), lr=0.05)
+    flat = lambda m: torch.cat([p.detach().reshape(-1) for p in m.parameters()])     # noqa: E731
+
+    def spread():
+        f = flat(model)
+        parts = [torch.zeros_like(f) for _ in range(world)]
+        D.all_gather(parts, f)
+        return max(float((p - parts[0]).abs().max()) for p in parts)
+    assert spread() == 0.0
+    did = []
+    for step in range(6):
+        opt.zero_grad()
+        ((model(xs) - ys) ** 2).mean().backward()
+        opt.step()
+        did.append(model.step_done())
+        assert (spread() == 0.0) == did[-1], (step, spread(), did)
+    assert did == [False, False, True, False, False, True] and model.syncs == 2
+    # sync_every = 1 with SGD: averaging parameters after the step == averaging gradients before it
+    ref, m1 = _mlp(9), D.LocalSGD(_mlp(9), sync_every=1)
+    ro, o1 = SGD(ref.parameters(), lr=0.1), SGD(m1.parameters(), lr=0.1)
+    for _ in range(3):
+        ro.zero_grad()
+        ((ref(X) - Y) ** 2).mean().backward()
+        ro.step()
+        o1.zero_grad()
+        ((m1(xs) - ys) ** 2).mean().backward()
+        o1.step()
+        assert m1.step_done()
+    assert torch.allclose(flat(ref), flat(m1), atol=1e-5), float((flat(ref) - flat(m1)).abs().max())
+    # outer momentum: the averaged point moves by outer_lr * (momentum * v + displacement)
+    m2 = D.LocalSGD(_mlp(11), sync_every=2, outer_momentum=0.5, outer_lr=1.0)
+    o2 = SGD(m2.parameters(), lr=0.05)
+    start = flat(m2).clone()
+    moved = []
+    for step in range(4):
+        o2.zero_grad()
+        ((m2(xs) - ys) ** 2).mean().backward()
+        o2.step()
+        if m2.step_done():
+            moved.append(flat(m2).clone())
+    assert len(moved) == 2 and spread() >= 0.0
+    f2 = flat(m2)
+    parts = [torch.zeros_like(f2) for _ in range(world)]
+    D.all_gather(parts, f2)
+    assert all(torch.equal(p, parts[0]) for p in parts) and not torch.equal(moved[0], start)
+    _fin()
+    return 0
+
+
+def ring_attention_matches_full(rank, world):
+    """Context parallelism: output and gradients of ring attention over sequence blocks == attention over the whole sequence."""
+    import torch.distributed as dist
+    from ..nn.parallel import ring_attention, shard_sequence
+    _init(rank, world)
+    torch.manual_seed(17)
+    B, H, T, Dh = 2, 3, 8 * world, 16
+    for causal in (True, False):
+        q, k, v = (torch.randn(B, H, T, Dh, dtype=torch.float64) for _ in range(3))
+        w = torch.randn(B, H, T, Dh, dtype=torch.float64)                  # weights of the scalar the gradients are taken of
+        qf, kf, vf = (t.clone().requires_grad_(True) for t in (q, k, v))
+        ref = torch.nn.functional.scaled_dot_product_attention(qf, kf, vf, is_causal=causal)
+        (ref * w).sum().backward()
+        ql, kl, vl = (shard_sequence(t, 2).clone().requires_grad_(True) for t in (q, k, v))
+        out = ring_attention(ql, kl, vl, causal=causal)
+        (out * shard_sequence(w, 2)).sum().backward()
+        assert torch.allclose(out, shard_sequence(ref.detach(), 2), atol=1e-5), float((out - shard_sequence(ref.detach(), 2)).abs().max())
+        for got, want, name in ((ql.grad, qf.grad, "dq"), (kl.grad, kf.grad, "dk"), (vl.grad, vf.grad, "dv")):
+            assert torch.allclose(got, shard_sequence(want, 2), atol=1e-5), (name, causal, float((got - shard_sequence(want, 2)).abs().max()))
+    _fin()
+    return 0
+
+
+def expert_parallel_matches_dense(rank, world):
+    """Expert parallelism: tokens routed over all-to-all to the ranks' experts == every expert in one process, gradients too."""
+    import torch.distributed as dist
+    from ..nn.parallel import Expert, ExpertParallelMoE
+    _init(rank, world)
+    dim, hidden, E, k = 16, 24, 2 * world, 2
+    moe = ExpertParallelMoE(dim, hidden, E, top_k=k, seed=40)
+    # the dense oracle holds every expert, built from the same per-expert seeds
+    experts = []
+    for e in range(E):
+        ex = Expert(dim, hidden)
+        g = torch.Generator().manual_seed(40 + 1 + e)
+        with torch.no_grad():
+            for p in ex.parameters():
+                p.copy_(torch.randn(p.shape, generator=g) * p.shape[1] ** -0.5)
+        experts.append(ex)
+    router = moe.router.weight.detach().clone().requires_grad_(True)
+    torch.manual_seed(100 + rank)
+    x = torch.randn(5 + rank, 3, dim, requires_grad=True)                 # a different number of tokens per rank
+    xr = x.detach().clone().requires_grad_(True)
+    y = moe(x)
+    want = ExpertParallelMoE.dense_forward(xr, router, experts, k)
+    assert torch.allclose(y, want, atol=1e-5), float((y - want).abs().max())
+    assert int(moe.last_tokens_per_expert.sum()) == x.shape[0] * x.shape[1] * k
+    w = torch.randn_like(y)
+    (y * w).sum().backward()
+    (want * w).sum().backward()
+    assert torch.allclose(x.grad, xr.grad, atol=1e-5)
+    # an expert's gradient is the sum over the tokens of every rank that chose it; the router's is this rank's share
+    for e in range(E):                                                     # the same collectives in the same order on every rank
+        local = list(moe.experts[e % moe.local].parameters()) if e // moe.local == rank else None
+        for i, p_dense in enumerate(experts[e].parameters()):
+            total = p_dense.grad.clone() if p_dense.grad is not None else torch.zeros_like(p_dense)
+            dist.all_reduce(total)                                         # the oracle on each rank saw only that rank's tokens
+            if local is not None:
+                assert torch.allclose(local[i].grad, total, atol=1e-5), (e, i, float((local[i].grad - total).abs().max()))
+    assert torch.allclose(moe.router.weight.grad, router.grad, atol=1e-5)
+    assert float(moe.load_balance_loss(x.detach())) > 0.5
+    _fin()
+    return 0

@@ -22,6 +22,32 @@ def test_two_ranks(fn):
     assert _launch(fn, 2) == 0
 
 
+@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("fn", [W.ring_attention_matches_full, W.expert_parallel_matches_dense], ids=lambda f: f.__name__)
+def test_context_and_expert_parallel(fn, world):
+    assert _launch(fn, world) == 0
+
+
+def test_local_sgd():
+    assert _launch(W.local_sgd_averages, 2) == 0
+
+
+def test_ring_attention_and_moe_without_a_process_group():
+    """One process: ring attention is plain attention, the expert-parallel layer runs all experts locally."""
+    from prometorch_b200.nn.parallel import ExpertParallelMoE, ring_attention
+    torch.manual_seed(3)
+    q, k, v = (torch.randn(2, 2, 12, 8) for _ in range(3))
+    for causal in (True, False):
+        assert torch.allclose(ring_attention(q, k, v, causal=causal), torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=causal), atol=1e-5)
+    moe = ExpertParallelMoE(8, 12, 4, top_k=2, seed=1)
+    x = torch.randn(7, 8, requires_grad=True)
+    y = moe(x)
+    want = ExpertParallelMoE.dense_forward(x, moe.router.weight, list(moe.experts), 2)
+    assert torch.allclose(y, want, atol=1e-5)
+    y.sum().backward()
+    assert x.grad is not None and all(p.grad is not None for p in moe.parameters())
+
+
 def test_dead_rank_is_detected_not_hung():
     assert _launch(W.rank_that_dies, 2, timeout=60) == 0
 
