@@ -47,9 +47,10 @@ def attention_reference(q, k, v, causal=True, q_offset: int = 0, scale: Optional
     Tk, Hk = k.shape[1], k.shape[2]
     g = H // Hk
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
-    qf = q.float().permute(0, 2, 1, 3)
-    kf = k.float().permute(0, 2, 1, 3).repeat_interleave(g, dim=1)
-    vf = v.float().permute(0, 2, 1, 3).repeat_interleave(g, dim=1)
+    wide = torch.float64 if q.dtype == torch.float64 else torch.float32       # fp32 math, except that double inputs stay double
+    qf = q.to(wide).permute(0, 2, 1, 3)
+    kf = k.to(wide).permute(0, 2, 1, 3).repeat_interleave(g, dim=1)
+    vf = v.to(wide).permute(0, 2, 1, 3).repeat_interleave(g, dim=1)
     s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
     if causal:
         qi = torch.arange(Tq, device=q.device)[:, None] + q_offset

@@ -92,8 +92,8 @@ class _RMSNorm(torch.autograd.Function):
 
 
 def _rms_ref(x, w, eps):
-    v = x.float()
-    return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * w.float()).to(x.dtype)
+    v = x if x.dtype == torch.float64 else x.float()          # fp32 math, except that double inputs stay double
+    return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * w.to(v.dtype)).to(x.dtype)
 
 
 def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
@@ -141,9 +141,10 @@ def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, neox: bool = Tru
     if x.is_cuda:
         return _Rope.apply(x, cos.float().contiguous(), sin.float().contiguous(), neox, pos_offset)
     T = x.shape[1]
-    c = cos[pos_offset:pos_offset + T].float()[None, :, None, :]
-    s = sin[pos_offset:pos_offset + T].float()[None, :, None, :]
-    xf = x.float()
+    wide = torch.float64 if x.dtype == torch.float64 else torch.float32       # fp32 math, except that double inputs stay double
+    c = cos[pos_offset:pos_offset + T].to(wide)[None, :, None, :]
+    s = sin[pos_offset:pos_offset + T].to(wide)[None, :, None, :]
+    xf = x.to(wide)
     if neox:
         h = x.shape[-1] // 2
         a, b = xf[..., :h], xf[..., h:]
