@@ -40,3 +40,51 @@ def test_cpp_api_amp_data_fsdp_pipeline(tmp_path):
     assert r.returncode == 0, r.stderr[-3000:]
     r = subprocess.run([exe, str(30050 + os.getpid() % 200), str(tmp_path / "ckpt")], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0 and "CPP_PARALLEL_API_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+@pytest.mark.skipif(shutil.which("g++") is None, reason="needs g++")
+def test_cpp_and_python_optimizers_walk_the_same_path(tmp_path):
+    """The C++ and the Python optimizers are separate implementations of the reference's update rules: on the same start
+    point and the same sequence of gradients they must end at the same parameters."""
+    import math
+    from prometorch_b200 import optim as O
+    exe = str(tmp_path / "optim_trajectories")
+    cmd = ["g++", "-std=c++17", "-O1", os.path.join(ROOT, "tests", "cpp", "optim_trajectories.cpp"), "-o", exe,
+           f"-I{ROOT}/prometorch_b200/cpp_api"] + _torch_flags()
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stderr[-3000:]
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    got = {ln.split()[0]: [float(v) for v in ln.split()[1:]] for ln in r.stdout.splitlines() if ln.strip()}
+
+    def start(shape, phase):
+        n = math.prod(shape)
+        i = torch.arange(n, dtype=torch.float64)
+        return (torch.sin(i * 0.37 + phase) + 0.1 * i / n).float().reshape(shape)
+
+    def gradient(shape, step, phase):
+        n = math.prod(shape)
+        i = torch.arange(n, dtype=torch.float64)
+        return (torch.cos(i * 0.21 + 0.9 * step + phase) * (1.0 + 0.1 * step)).float().reshape(shape)
+    cases = {"SGD": (O.SGD, dict(lr=0.05, momentum=0.9, nesterov=True, weight_decay=0.01)), "SGD_plain": (O.SGD, dict(lr=0.05)),
+             "Adam": (O.Adam, dict(lr=1e-2)), "Adam_amsgrad": (O.Adam, dict(lr=1e-2, amsgrad=True, weight_decay=0.1)), "AdamW": (O.AdamW, dict(lr=1e-2)),
+             "RMSprop": (O.RMSprop, dict(lr=1e-2)), "RMSprop_centered": (O.RMSprop, dict(lr=1e-2, centered=True, momentum=0.5)),
+             "Lion": (O.Lion, dict(lr=3e-3, weight_decay=0.1)), "SophiaG": (O.SophiaG, dict(lr=1e-2)), "LAMB": (O.LAMB, dict(lr=1e-2)),
+             "Adafactor": (O.Adafactor, dict()), "Adafactor_fixed": (O.Adafactor, dict(lr=1e-2, relative_step=False, scale_parameter=False, beta1=0.9)),
+             "NAdam": (O.NAdam, dict(lr=1e-2)), "RAdam": (O.RAdam, dict(lr=2e-2)), "Adagrad": (O.Adagrad, dict(lr=0.1)), "Adadelta": (O.Adadelta, dict()),
+             "Adamax": (O.Adamax, dict(lr=2e-2)), "AdamKiller": (O.AdamKiller, dict(lr=1e-2)), "ASGD": (O.ASGD, dict(lr=0.05))}
+    assert set(got) == set(cases)
+    worst = {}
+    for name, (cls, kw) in cases.items():
+        w, b = torch.nn.Parameter(start((6, 5), 0.0)), torch.nn.Parameter(start((5,), 1.0))
+        opt = cls([w, b], fused=False, **kw)
+        for s in range(9 if name == "RAdam" else 6):
+            w.grad, b.grad = gradient((6, 5), s, 0.0), gradient((5,), s, 2.0)
+            opt.step()
+        want = torch.cat([w.detach().reshape(-1), b.detach().reshape(-1)]).double()
+        have = torch.tensor(got[name], dtype=torch.float64)
+        worst[name] = float((want - have).abs().max())
+        moved = float((want - torch.cat([start((6, 5), 0.0).reshape(-1), start((5,), 1.0).reshape(-1)]).double()).abs().max())
+        assert moved > 1e-4, name
+    bad = {k: v for k, v in worst.items() if v > 2e-5}
+    assert not bad, bad
