@@ -37,8 +37,55 @@ static void run(const char* name, Options o, int steps = 6) {
     std::printf("\n");
 }
 
+// One learning-rate sequence per scheduler: "S:NAME lr lr lr ..." (the rate after construction, then after every step).
+template <typename Make>
+static void schedule(const char* name, Make make, int steps = 24) {
+    using namespace pt::optim;
+    auto w = pt::zeros({2}).requires_grad_(true);
+    SGD opt({w}, SGDOptions(0.5));
+    auto stepper = make(opt);
+    std::printf("S:%s %.12g", name, opt.get_lr(0));
+    for (int i = 0; i < steps; ++i) {
+        stepper(i);
+        std::printf(" %.12g", opt.get_lr(0));
+    }
+    std::printf("\n");
+}
+
+static void schedulers() {
+    using namespace pt::optim;
+    auto plain = [](auto sched) { return [sched](int) { sched->step(); }; };
+    schedule("StepLR", [&](SGD& o) { return plain(std::make_shared<StepLR>(o, 5, 0.5)); });
+    schedule("MultiStepLR", [&](SGD& o) { return plain(std::make_shared<MultiStepLR>(o, std::vector<int64_t>{3, 7, 15}, 0.3)); });
+    schedule("ExponentialLR", [&](SGD& o) { return plain(std::make_shared<ExponentialLR>(o, 0.9)); });
+    schedule("CosineAnnealingLR", [&](SGD& o) { return plain(std::make_shared<CosineAnnealingLR>(o, 10, 0.01)); });
+    schedule("LinearLR", [&](SGD& o) { return plain(std::make_shared<LinearLR>(o, 0.25, 1.0, 8)); });
+    schedule("ConstantLR", [&](SGD& o) { return plain(std::make_shared<ConstantLR>(o, 0.2, 6)); });
+    schedule("WarmupCosineAnnealingLR", [&](SGD& o) { return plain(std::make_shared<WarmupCosineAnnealingLR>(o, 4, 20, 0.05)); });
+    schedule("OneCycleLR", [&](SGD& o) { return plain(std::make_shared<OneCycleLR>(o, 1.0, 24, 0.25)); });
+    schedule("CosineAnnealingWarmRestarts", [&](SGD& o) { return plain(std::make_shared<CosineAnnealingWarmRestarts>(o, 4, 2, 0.02)); });
+    schedule("CyclicLR", [&](SGD& o) { return plain(std::make_shared<CyclicLR>(o, 0.1, 0.9, 3, 5)); });
+    schedule("CyclicLR_triangular2", [&](SGD& o) { return plain(std::make_shared<CyclicLR>(o, 0.1, 0.9, 2, -1, CyclicLR::Mode::Triangular2)); });
+    schedule("PolynomialLR", [&](SGD& o) { return plain(std::make_shared<PolynomialLR>(o, 12, 2.0)); });
+    schedule("LambdaLR", [&](SGD& o) { return plain(std::make_shared<LambdaLR>(o, [](int64_t e) { return 1.0 / (1.0 + 0.5 * e); })); });
+    schedule("MultiplicativeLR", [&](SGD& o) { return plain(std::make_shared<MultiplicativeLR>(o, [](int64_t e) { return e % 3 == 0 ? 0.8 : 1.0; })); });
+    schedule("ReduceLROnPlateau", [&](SGD& o) {
+        auto s = std::make_shared<ReduceLROnPlateau>(o, ReduceLROnPlateau::Mode::Min, 0.5, 2, 1e-3, 0.01);
+        return [s](int i) { s->step(i < 5 ? 1.0 - 0.1 * i : 0.7); };
+    });
+    schedule("SequentialLR", [&](SGD& o) {
+        std::vector<std::shared_ptr<LRScheduler>> parts{std::make_shared<LinearLR>(o, 0.1, 1.0, 5), std::make_shared<ExponentialLR>(o, 0.8)};
+        return plain(std::make_shared<SequentialLR>(o, parts, std::vector<int64_t>{5}));
+    });
+    schedule("ChainedScheduler", [&](SGD& o) {
+        std::vector<std::shared_ptr<LRScheduler>> parts{std::make_shared<StepLR>(o, 4, 0.5), std::make_shared<ExponentialLR>(o, 0.95)};
+        return plain(std::make_shared<ChainedScheduler>(o, parts));
+    });
+}
+
 int main() {
     using namespace pt::optim;
+    schedulers();
     run<SGD>("SGD", SGDOptions(0.05).momentum_(0.9).nesterov_(true).weight_decay_(0.01));
     run<SGD>("SGD_plain", SGDOptions(0.05));
     run<Adam>("Adam", AdamOptions(1e-2));

@@ -42,10 +42,47 @@ def test_cpp_api_amp_data_fsdp_pipeline(tmp_path):
     assert r.returncode == 0 and "CPP_PARALLEL_API_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
 
 
+def _check_schedulers(sched):
+    """The learning-rate sequences of the C++ schedulers against the Python ones (same constructor arguments)."""
+    from prometorch_b200 import optim as O
+    L = O
+
+    def seq(make, steps=24, metric=None):
+        w = torch.nn.Parameter(torch.zeros(2))
+        opt = O.SGD([w], lr=0.5)
+        s = make(opt)
+        out = [opt.param_groups[0]["lr"]]
+        for i in range(steps):
+            s.step(metric(i)) if metric else s.step()
+            out.append(opt.param_groups[0]["lr"])
+        return out
+    want = {
+        "StepLR": seq(lambda o: L.StepLR(o, 5, 0.5)), "MultiStepLR": seq(lambda o: L.MultiStepLR(o, [3, 7, 15], 0.3)),
+        "ExponentialLR": seq(lambda o: L.ExponentialLR(o, 0.9)), "CosineAnnealingLR": seq(lambda o: L.CosineAnnealingLR(o, 10, 0.01)),
+        "LinearLR": seq(lambda o: L.LinearLR(o, 0.25, 1.0, 8)), "ConstantLR": seq(lambda o: L.ConstantLR(o, 0.2, 6)),
+        "WarmupCosineAnnealingLR": seq(lambda o: L.WarmupCosineAnnealingLR(o, 4, 20, 0.05)), "OneCycleLR": seq(lambda o: L.OneCycleLR(o, 1.0, 24, 0.25)),
+        "CosineAnnealingWarmRestarts": seq(lambda o: L.CosineAnnealingWarmRestarts(o, 4, 2, 0.02)), "CyclicLR": seq(lambda o: L.CyclicLR(o, 0.1, 0.9, 3, 5)),
+        "CyclicLR_triangular2": seq(lambda o: L.CyclicLR(o, 0.1, 0.9, 2, -1, "triangular2")), "PolynomialLR": seq(lambda o: L.PolynomialLR(o, 12, 2.0)),
+        "LambdaLR": seq(lambda o: L.LambdaLR(o, lambda e: 1.0 / (1.0 + 0.5 * e))),
+        "MultiplicativeLR": seq(lambda o: L.MultiplicativeLR(o, lambda e: 0.8 if e % 3 == 0 else 1.0)),
+        "ReduceLROnPlateau": seq(lambda o: L.ReduceLROnPlateau(o, "min", 0.5, 2, 1e-3, 0.01), metric=lambda i: 1.0 - 0.1 * i if i < 5 else 0.7),
+        "SequentialLR": seq(lambda o: L.SequentialLR(o, [L.LinearLR(o, 0.1, 1.0, 5), L.ExponentialLR(o, 0.8)], [5])),
+        "ChainedScheduler": seq(lambda o: L.ChainedScheduler(o, [L.StepLR(o, 4, 0.5), L.ExponentialLR(o, 0.95)])),
+    }
+    assert set(sched) == set(want), set(sched) ^ set(want)
+    bad = {}
+    for name, w in want.items():
+        diff = max(abs(a - b) for a, b in zip(w, sched[name]))
+        if len(w) != len(sched[name]) or diff > 1e-9:
+            bad[name] = (diff, [round(v, 6) for v in w[:8]], [round(v, 6) for v in sched[name][:8]])
+    assert not bad, bad
+
+
 @pytest.mark.skipif(shutil.which("g++") is None, reason="needs g++")
 def test_cpp_and_python_optimizers_walk_the_same_path(tmp_path):
     """The C++ and the Python optimizers are separate implementations of the reference's update rules: on the same start
-    point and the same sequence of gradients they must end at the same parameters."""
+    point and the same sequence of gradients they must end at the same parameters; the sixteen schedulers must produce the
+    same learning-rate sequences."""
     import math
     from prometorch_b200 import optim as O
     exe = str(tmp_path / "optim_trajectories")
@@ -55,7 +92,10 @@ def test_cpp_and_python_optimizers_walk_the_same_path(tmp_path):
     assert r.returncode == 0, r.stderr[-3000:]
     r = subprocess.run([exe], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stderr[-2000:]
-    got = {ln.split()[0]: [float(v) for v in ln.split()[1:]] for ln in r.stdout.splitlines() if ln.strip()}
+    lines = [ln for ln in r.stdout.splitlines() if ln.strip()]
+    got = {ln.split()[0]: [float(v) for v in ln.split()[1:]] for ln in lines if not ln.startswith("S:")}
+    sched = {ln.split()[0][2:]: [float(v) for v in ln.split()[1:]] for ln in lines if ln.startswith("S:")}
+    _check_schedulers(sched)
 
     def start(shape, phase):
         n = math.prod(shape)
