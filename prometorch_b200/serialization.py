@@ -122,4 +122,9 @@ def save_pytorch(obj, path: str):
 
 def load_pytorch(path: str, map_location="cpu"):
     """Read a PyTorch ``.pt``/``.pth`` checkpoint; only tensors and plain containers are accepted."""
-    return torch.load(path, map_location=map_location, weights_only=True)
+    # libtorch's C++ pickler wraps dictionaries in torch.jit._pickle.restore_type_tag(value, type string), which returns the
+    # value unchanged; allowing that one function lets files written by the C++ API (save_pytorch) load under the same
+    # tensors-and-plain-containers policy
+    from torch.jit._pickle import restore_type_tag
+    with torch.serialization.safe_globals([restore_type_tag]):
+        return torch.load(path, map_location=map_location, weights_only=True)

@@ -83,8 +83,27 @@ static void schedulers() {
     });
 }
 
-int main() {
+// Checkpoints across the two languages: read what Python wrote (PTOR container and a PyTorch zip), print name, dtype, shape and
+// sums, then write the same tensors back for Python to read.
+static int checkpoints(const std::string& dir) {
+    for (const char* kind : {"ptor", "pt"}) {
+        const std::string path = dir + "/py." + kind;
+        auto sd = std::string(kind) == "ptor" ? pt::load_state_dict(path) : pt::load_pytorch(path);
+        for (const auto& kv : sd) {
+            std::printf("C:%s %s %s", kind, kv.first.c_str(), c10::toString(kv.second.scalar_type()));
+            for (auto d : kv.second.sizes()) std::printf(" %lld", (long long)d);
+            std::printf(" | %.9g %.9g\n", kv.second.to(pt::kDouble).sum().item<double>(),
+                        kv.second.numel() ? kv.second.to(pt::kDouble).abs().max().item<double>() : 0.0);
+        }
+        if (std::string(kind) == "ptor") pt::save_state_dict(sd, dir + "/cpp.ptor");
+        else pt::save_pytorch(sd, dir + "/cpp.pt");
+    }
+    return 0;
+}
+
+int main(int argc, char** argv) {
     using namespace pt::optim;
+    if (argc > 2 && std::string(argv[1]) == "io") return checkpoints(argv[2]);
     schedulers();
     run<SGD>("SGD", SGDOptions(0.05).momentum_(0.9).nesterov_(true).weight_decay_(0.01));
     run<SGD>("SGD_plain", SGDOptions(0.05));

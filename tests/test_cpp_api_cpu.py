@@ -42,6 +42,41 @@ def test_cpp_api_amp_data_fsdp_pipeline(tmp_path):
     assert r.returncode == 0 and "CPP_PARALLEL_API_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
 
 
+def _check_checkpoints(exe, tmp_path):
+    """PTOR containers and PyTorch zips written by Python are read by the C++ API and written back unchanged."""
+    from collections import OrderedDict
+    from prometorch_b200 import serialization as S
+    g = torch.Generator().manual_seed(4)
+    sd = OrderedDict([("layer.weight", torch.randn(5, 7, generator=g)), ("layer.bias", torch.randn(7, generator=g)),
+                      ("half", torch.randn(3, 2, generator=g).half()), ("bf16", torch.randn(4, generator=g).bfloat16()),
+                      ("ids", torch.arange(6).reshape(2, 3)), ("scalar", torch.tensor(3.5)), ("bytes", torch.arange(10, dtype=torch.uint8)),
+                      ("double", torch.randn(2, 2, generator=g, dtype=torch.float64)), ("empty", torch.zeros(0, 4))])
+    d = tmp_path / "ckpt_io"
+    d.mkdir()
+    S.save_state_dict(sd, str(d / "py.ptor"))
+    S.save_pytorch(dict(sd), str(d / "py.pt"))
+    r = subprocess.run([exe, "io", str(d)], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stdout[-1000:] + r.stderr[-2000:]
+    seen = {"ptor": {}, "pt": {}}
+    for ln in r.stdout.splitlines():
+        head, sums = ln.split(" | ")
+        kind, name, dtype, *shape = head.split()
+        seen[kind[2:]][name] = (dtype, [int(x) for x in shape], float(sums.split()[0]), float(sums.split()[1]))
+    names = {torch.float32: "Float", torch.float16: "Half", torch.bfloat16: "BFloat16", torch.int64: "Long", torch.uint8: "Byte", torch.float64: "Double"}
+    for kind in ("ptor", "pt"):
+        assert list(seen[kind]) == list(sd) if kind == "ptor" else set(seen[kind]) == set(sd)
+        for k, t in sd.items():
+            dtype, shape, total, amax = seen[kind][k]
+            assert dtype == names[t.dtype] and shape == list(t.shape), (kind, k, dtype, shape)
+            assert abs(total - float(t.double().sum())) < 1e-6 and abs(amax - float(t.double().abs().max() if t.numel() else 0.0)) < 1e-6, (kind, k)
+    back = S.load_state_dict(str(d / "cpp.ptor"))
+    back_pt = S.load_pytorch(str(d / "cpp.pt"))
+    assert list(back) == list(sd)
+    for k, t in sd.items():
+        assert back[k].dtype == t.dtype and torch.equal(back[k], t), k
+        assert back_pt[k].dtype == t.dtype and torch.equal(back_pt[k], t), k
+
+
 def _check_schedulers(sched):
     """The learning-rate sequences of the C++ schedulers against the Python ones (same constructor arguments)."""
     from prometorch_b200 import optim as O
@@ -92,6 +127,7 @@ def test_cpp_and_python_optimizers_walk_the_same_path(tmp_path):
     assert r.returncode == 0, r.stderr[-3000:]
     r = subprocess.run([exe], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stderr[-2000:]
+    _check_checkpoints(exe, tmp_path)
     lines = [ln for ln in r.stdout.splitlines() if ln.strip()]
     got = {ln.split()[0]: [float(v) for v in ln.split()[1:]] for ln in lines if not ln.startswith("S:")}
     sched = {ln.split()[0][2:]: [float(v) for v in ln.split()[1:]] for ln in lines if ln.startswith("S:")}
