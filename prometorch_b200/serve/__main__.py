@@ -17,6 +17,8 @@ def main():
     ap.add_argument("--max-seq", type=int, default=4096)
     ap.add_argument("--max-models", type=int, default=2, help="models kept loaded at once")
     ap.add_argument("--allow-model-paths", action="store_true", help="let requests name models by filesystem path")
+    ap.add_argument("--fp16-weights", "--fp16_weights", action="store_true",
+                    help="accepted for compatibility with the reference's CLI: weights stay in their file format here")
     a = ap.parse_args()
     # --model comes from the operator, so it may be a path even when requests may not name paths
     cfg = ServerConfig(a.host, a.port, a.workers, a.queue_depth, a.timeout_ms, a.device, None, a.model_dir, a.max_seq,
