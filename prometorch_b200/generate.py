@@ -39,8 +39,9 @@ def main(argv=None) -> int:
     ap.add_argument("--top-k", type=int, default=40)
     ap.add_argument("--top-p", type=float, default=0.9)
     ap.add_argument("--repeat-penalty", type=float, default=1.05)
-    ap.add_argument("--draft", default=None, help="a smaller GGUF model over the same vocabulary: greedy speculative decoding")
-    ap.add_argument("--spec-k", type=int, default=4, help="tokens the draft proposes per verification pass")
+    from .utils.env import env_int, env_str
+    ap.add_argument("--draft", default=env_str("SPEC_DRAFT_PATH"), help="a smaller GGUF model over the same vocabulary: greedy speculative decoding")
+    ap.add_argument("--spec-k", type=int, default=env_int("SPEC_K", 4), help="tokens the draft proposes per verification pass")
     ap.add_argument("--nprocs", type=int, default=1)
     ap.add_argument("--rank", type=int, default=0)
     ap.add_argument("--master-addr", "--master_addr", default="127.0.0.1")
@@ -121,6 +122,9 @@ def main(argv=None) -> int:
     text = apply_chat_template(prompt, cfg.architecture, cfg.model_name) if (a.chat and not a.raw) else prompt
     ids = tok.encode(text)
     say(f"[Generate] Prompt tokens: {len(ids)}")
+    debug_tokens = env_int("DEBUG_TOKENS", 0) == 1
+    if debug_tokens:
+        say(f"[Tokens] prompt {ids}")
     t1 = time.time()
     out = []
 
@@ -152,6 +156,8 @@ def main(argv=None) -> int:
             on_token(t)
     dt = time.time() - t1
     say(f"\n\n[Generate] {len(out)} tokens in {dt:.2f}s ({len(out) / max(dt, 1e-9):.1f} tok/s, prompt included)")
+    if debug_tokens:
+        say(f"[Tokens] generated {out}")
     if a.profile and use_cuda and world == 1:
         import ctypes as C
         n_k = 5 * cfg.num_layers + 2

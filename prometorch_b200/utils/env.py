@@ -10,6 +10,9 @@ ENV: Dict[str, str] = {
     "SYSTEM_PROMPT": "default system prompt of the chat templates (empty string disables it)",
     "NO_THINK": "1 = append /no_think to the qwen3 system block",
     "OLLAMA_MODELS": "root of the Ollama model store",
+    "SPEC_DRAFT_PATH": "generate CLI: a smaller GGUF model over the same vocabulary for greedy speculative decoding (default of --draft)",
+    "SPEC_K": "generate CLI: tokens the draft proposes per verification pass (default of --spec-k)",
+    "DEBUG_TOKENS": "generate CLI: 1 = also print the prompt's and the generated token ids",
 }
 
 # Switches the native library reads with getenv() (spelled PTB_*).  Every one is listed here; the test suite checks

@@ -320,3 +320,21 @@ def test_weight_layout_follows_the_number_of_ranks(monkeypatch):
     assert default_layout(8) == LAYOUT_T16
     monkeypatch.setenv("PTB_GEMV_LAYOUT", "segment")
     assert default_layout(1) == LAYOUT_SEGMENT
+
+
+def test_generate_cli_on_the_cpu_oracle(tmp_path, monkeypatch, capsys):
+    """`python -m prometorch_b200.generate --device cpu`: the fp32 oracle behind the reference CLI's flags, the token-id dump
+    switch under the reference's spelling, and `--info` / `--tensors` without a model load."""
+    from prometorch_b200 import generate as G
+    from prometorch_b200.io.config import tiny_qwen3_config
+    from prometorch_b200.io.synthetic import write_synthetic_gguf
+    p = str(tmp_path / "cli.gguf")
+    write_synthetic_gguf(p, tiny_qwen3_config(layers=1, hidden=256, heads=4, kv_heads=2, inter=512, vocab=512), seed=4, device="cpu")
+    monkeypatch.setenv("PT_DEBUG_TOKENS", "1")
+    assert G.main([p, "t300 t301 t400", "--device", "cpu", "--greedy", "--max-tokens", "3"]) == 0
+    out = capsys.readouterr().out
+    assert "[Generate] Prompt tokens: 3" in out and "[Tokens] prompt [300, 301, 400]" in out and "[Tokens] generated [" in out and "tok/s" in out
+    monkeypatch.delenv("PT_DEBUG_TOKENS")
+    assert G.main([p, "--info", "--tensors"]) == 0
+    out = capsys.readouterr().out
+    assert "general.architecture = 'qwen3'" in out and "blk.0.attn_q.weight" in out and "[Tokens]" not in out
