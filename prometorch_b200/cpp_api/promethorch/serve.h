@@ -514,6 +514,87 @@ class ApiHandlers {
     std::atomic<long long> requests_{0}, tokens_generated_{0}, prompt_tokens_{0}, timeouts_{0};
 };
 
+// ---------------------------------------------------------------------------------------------- request queue
+// submit_request / step / poll_responses / generate over one backend (the call names of the reference's
+// torch::serve::LLMEngine, torch/serve/llm.h:299-420).  Requests are served in arrival order, one per step().
+class LLMEngine {
+ public:
+    struct Request {
+        int id = 0;
+        std::vector<int> prompt, output;
+        GenerateOptions options;
+        bool done = false;
+    };
+    explicit LLMEngine(std::shared_ptr<ModelBackend> backend) : backend_(std::move(backend)) {}
+
+    int submit_request(const std::vector<int>& prompt_ids, int max_tokens = 32, double temperature = 0.0, int top_k = 0) {
+        Request r;
+        r.id = next_++;
+        r.prompt = prompt_ids;
+        r.options.num_predict = max_tokens;
+        r.options.temperature = temperature;
+        r.options.top_k = top_k > 0 ? top_k : 40;
+        r.options.repeat_penalty = 1.0;
+        std::lock_guard<std::mutex> g(m_);
+        queue_.push_back(std::move(r));
+        return queue_.back().id;
+    }
+    int submit_request(const std::string& prompt, int max_tokens = 32, double temperature = 0.0, int top_k = 0) {
+        return submit_request(backend_->encode(prompt), max_tokens, temperature, top_k);
+    }
+    size_t num_pending() { std::lock_guard<std::mutex> g(m_); return queue_.size(); }
+    // Serves the oldest request; returns how many tokens it produced (0 when the queue is empty).
+    int step() {
+        Request r;
+        {
+            std::lock_guard<std::mutex> g(m_);
+            if (queue_.empty()) return 0;
+            r = std::move(queue_.front());
+            queue_.pop_front();
+        }
+        backend_->generate(r.prompt, r.options, [&r](int id) {
+            r.output.push_back(id);
+            return (int)r.output.size() < r.options.num_predict;
+        });
+        r.done = true;
+        const int n = (int)r.output.size();
+        std::lock_guard<std::mutex> g(m_);
+        finished_[r.id] = std::move(r);
+        return n;
+    }
+    // Finished requests since the last call: id -> generated ids.
+    std::map<int, std::vector<int>> poll_responses() {
+        std::map<int, std::vector<int>> out;
+        std::lock_guard<std::mutex> g(m_);
+        for (auto& kv : finished_) out[kv.first] = std::move(kv.second.output);
+        finished_.clear();
+        return out;
+    }
+    std::vector<std::string> generate(const std::vector<std::string>& prompts, int max_tokens = 32, double temperature = 0.0, int top_k = 0) {
+        std::vector<int> ids;
+        for (const auto& p : prompts) ids.push_back(submit_request(p, max_tokens, temperature, top_k));
+        std::map<int, std::vector<int>> res;
+        while (num_pending()) {
+            step();
+            for (auto& kv : poll_responses()) res[kv.first] = std::move(kv.second);
+        }
+        std::vector<std::string> out;
+        for (int id : ids) {
+            std::string text;
+            for (int t : res[id]) text += backend_->decode_token(t);
+            out.push_back(text);
+        }
+        return out;
+    }
+
+ private:
+    std::shared_ptr<ModelBackend> backend_;
+    std::deque<Request> queue_;
+    std::map<int, Request> finished_;
+    std::mutex m_;
+    int next_ = 0;
+};
+
 // ---------------------------------------------------------------------------------------------- HTTP
 // Blocking accept loop + fixed worker pool + bounded queue (503 when full).
 class HttpServer {

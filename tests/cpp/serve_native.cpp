@@ -131,6 +131,27 @@ int main(int argc, char** argv) {
             std::cout << out.dump() << "\n";
             return 0;
         }
+        if (mode == "engine") {                      // the request queue over a fake backend
+            ps::LLMEngine eng(std::make_shared<FakeBackend>("echo"));
+            const int a = eng.submit_request("one", 3), b = eng.submit_request(std::vector<int>{'t', 'w', 'o'}, 5);
+            pj::Value out = pj::Value::object();
+            out.set("pending", (long long)eng.num_pending());
+            out.set("first_step", eng.step());
+            pj::Value polled = pj::Value::object();
+            for (auto& kv : eng.poll_responses()) polled.set(std::to_string(kv.first), ids_json(kv.second));
+            out.set("after_first", polled);
+            out.set("second_step", eng.step());
+            pj::Value polled2 = pj::Value::object();
+            for (auto& kv : eng.poll_responses()) polled2.set(std::to_string(kv.first), ids_json(kv.second));
+            out.set("after_second", polled2);
+            out.set("empty_step", eng.step());
+            out.set("ids", ids_json({a, b}));
+            pj::Value texts = pj::Value::array();
+            for (const auto& t : eng.generate({"x", "y"}, 4)) texts.push_back(t);
+            out.set("generate", texts);
+            std::cout << out.dump() << "\n";
+            return 0;
+        }
         if (mode == "serve") {
             ps::ServerConfig cfg;
             cfg.port = 0;

@@ -187,6 +187,22 @@ def test_chat_templates_match_python(exe, tmp_path, monkeypatch):
     assert _run(exe, "chat", str(p)) == [apply_chat_template("q", "qwen3")]
 
 
+def test_native_request_queue(exe):
+    """serve::LLMEngine (submit_request / step / poll_responses / generate) behaves like the Python queue of the same name."""
+    from prometorch_b200.serve import LLMEngine
+    from test_serve_cpu import EchoBackend
+    got = _run(exe, "engine")
+    eng = LLMEngine(EchoBackend())
+    a, b = eng.submit_request("one", max_tokens=3), eng.submit_request([ord(c) for c in "two"], max_tokens=5)
+    assert got["ids"] == [a, b] and got["pending"] == 2
+    assert got["first_step"] == eng.step() == 3
+    assert got["after_first"] == {str(k): v for k, v in eng.poll_responses().items()} == {"0": [ord(c) for c in "hel"]}
+    assert got["second_step"] == eng.step() == 5
+    assert got["after_second"] == {str(k): v for k, v in eng.poll_responses().items()}
+    assert got["empty_step"] == eng.step() == 0
+    assert got["generate"] == eng.generate(["x", "y"], max_tokens=4) == ["hell", "hell"]
+
+
 # ------------------------------------------------------------------------------------------------------------- server
 class Server:
     def __init__(self, exe, *flags, env=None):
