@@ -50,6 +50,7 @@ class Value {
     // arrays
     size_t size() const { return kind_ == Array ? a_.size() : (kind_ == Object ? o_.size() : 0); }
     const Value& operator[](size_t i) const { return a_.at(i); }
+    const Value& at(size_t i) const { return a_.at(i); }                       // for literal indices (0 is also a null pointer constant)
     void push_back(Value v) { if (kind_ != Array) { *this = array(); } a_.push_back(std::move(v)); }
     const std::vector<Value>& items() const { return a_; }
     // objects

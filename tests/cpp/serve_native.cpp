@@ -10,6 +10,7 @@
 #include <sstream>
 #include <thread>
 
+#include "promethorch/model_loader.h"
 #include "promethorch/serve.h"
 #include "promethorch/tokenizer.h"
 
@@ -128,6 +129,50 @@ int main(int argc, char** argv) {
                                                                  c["system"].is_string() ? &sys : nullptr, c["no_think"].is_null() ? -1 : (int)c["no_think"].as_bool()));
                 }
             }
+            std::cout << out.dump() << "\n";
+            return 0;
+        }
+        if (mode == "model") {                       // model_loader.h: what a path holds
+            namespace L = pio::loader;
+            pj::Value out = pj::Value::object();
+            out.set("detected", L::detect_format(argv[2]));
+            const L::ModelWeights mw = L::load_model(argv[2]);
+            out.set("format", mw.format);
+            out.set("architecture", mw.architecture);
+            pj::Value cfg = pj::Value::object(), tensors = pj::Value::object(), files = pj::Value::array();
+            const auto& c = mw.config;
+            cfg.set("hidden_size", (long long)c.hidden_size);
+            cfg.set("num_layers", (long long)c.num_layers);
+            cfg.set("num_heads", (long long)c.num_heads);
+            cfg.set("num_kv_heads", (long long)c.num_kv_heads);
+            cfg.set("intermediate_size", (long long)c.intermediate_size);
+            cfg.set("vocab_size", (long long)c.vocab_size);
+            cfg.set("head_dim", (long long)c.head_dim);
+            cfg.set("context_length", (long long)c.context_length);
+            cfg.set("rms_norm_eps", c.rms_norm_eps);
+            cfg.set("rope_freq_base", c.rope_freq_base);
+            cfg.set("tie_word_embeddings", c.tie_word_embeddings);
+            out.set("config", cfg);
+            for (const auto& name : mw.order) {
+                const auto& t = mw.tensors.at(name);
+                pj::Value e = pj::Value::object(), shape = pj::Value::array();
+                for (auto d : t.shape) shape.push_back((long long)d);
+                e.set("dtype", t.dtype);
+                e.set("shape", shape);
+                e.set("file", t.file);
+                if (argc > 3) {                      // byte sums on request
+                    unsigned long long sum = 0;
+                    const auto bytes = L::read_tensor_bytes(mw, name);
+                    for (uint8_t b : bytes) sum += b;
+                    e.set("nbytes", (long long)bytes.size());
+                    e.set("byte_sum", (long long)sum);
+                }
+                tensors.set(name, e);
+            }
+            out.set("tensors", tensors);
+            for (const auto& f : mw.files) files.push_back(f);
+            out.set("files", files);
+            out.set("total_parameters", (long long)mw.total_parameters());
             std::cout << out.dump() << "\n";
             return 0;
         }

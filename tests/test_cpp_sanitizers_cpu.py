@@ -84,6 +84,47 @@ def test_tokenizer_json_and_chat_under_asan(asan_exe, tmp_path):
     _clean(subprocess.run([asan_exe, "chat", str(q)], capture_output=True, timeout=60, env=ENV))
 
 
+def test_model_loader_on_damaged_files_under_asan(asan_exe, tmp_path):
+    """Truncated and corrupted containers are reported as errors; the loader never reads out of bounds."""
+    import struct
+    import torch
+    from prometorch_b200 import serialization as Ser
+    from prometorch_b200.io.config import tiny_qwen3_config
+    from prometorch_b200.io.safetensors import save_file
+    from prometorch_b200.io.synthetic import write_synthetic_gguf
+    good = {}
+    good["st"] = tmp_path / "a.safetensors"
+    save_file({"model.embed_tokens.weight": torch.randn(10, 8), "model.layers.0.self_attn.q_proj.weight": torch.randn(64, 8)}, str(good["st"]))
+    good["ptor"] = tmp_path / "a.ptor"
+    Ser.save_state_dict({"w": torch.randn(4, 4), "b": torch.zeros(4)}, str(good["ptor"]))
+    good["gguf"] = tmp_path / "a.gguf"
+    write_synthetic_gguf(str(good["gguf"]), tiny_qwen3_config(layers=1, hidden=256, heads=4, kv_heads=2, inter=512, vocab=512), seed=3, device="cpu")
+    cases = []
+    for kind, path in good.items():
+        raw = path.read_bytes()
+        _clean(subprocess.run([asan_exe, "model", str(path), "bytes"], capture_output=True, timeout=120, env=ENV))
+        for cut in (5, 9, 17, 40, len(raw) // 2, len(raw) - 1):
+            q = tmp_path / f"{kind}_cut{cut}"
+            q.write_bytes(raw[:cut])
+            cases.append(q)
+        flipped = bytearray(raw)
+        for i in range(8, min(len(flipped), 200), 7):
+            flipped[i] ^= 0xFF
+        q = tmp_path / f"{kind}_flipped"
+        q.write_bytes(bytes(flipped))
+        cases.append(q)
+    huge = tmp_path / "huge_header.safetensors"
+    huge.write_bytes(struct.pack("<Q", 50 * 1024 * 1024) + b'{"a": 1}')
+    bad_off = tmp_path / "bad_offsets.safetensors"
+    hdr = b'{"w": {"dtype": "F32", "shape": [2], "data_offsets": [0, 800]}}'
+    bad_off.write_bytes(struct.pack("<Q", len(hdr)) + hdr + b"\x00" * 8)
+    cases += [huge, bad_off]
+    for q in cases:
+        r = subprocess.run([asan_exe, "model", str(q), "bytes"], capture_output=True, timeout=120, env=ENV)
+        err = r.stderr.decode(errors="replace")
+        assert r.returncode in (0, 1) and "Sanitizer" not in err and "runtime error" not in err, (q.name, err[-1500:])
+
+
 def _hammer(exe, env, flags=()):
     s = S.Server(exe, *flags, env=env)
     try:

@@ -10,6 +10,7 @@ import threading
 import time
 
 import pytest
+import torch
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
@@ -185,6 +186,88 @@ def test_chat_templates_match_python(exe, tmp_path, monkeypatch):
     monkeypatch.setenv("PROMETHORCH_NO_THINK", "1")
     p.write_text(json.dumps([{"prompt": "q", "arch": "qwen3", "name": ""}]))
     assert _run(exe, "chat", str(p)) == [apply_chat_template("q", "qwen3")]
+
+
+def test_native_model_loader_matches_python(exe, tmp_path):
+    """model_loader.h against io/model_loader.py on every container: detected format, architecture, inferred shape parameters,
+    tensor directory, shard discovery, and the stored bytes of every tensor."""
+    import dataclasses
+    from collections import OrderedDict
+    from prometorch_b200 import serialization as S
+    from prometorch_b200.io import model_loader as ML
+    from prometorch_b200.io.config import tiny_qwen3_config
+    from prometorch_b200.io.safetensors import save_file
+    from prometorch_b200.io.synthetic import write_synthetic_gguf
+    g = torch.Generator().manual_seed(8)
+
+    def llama_like(qk_norm=False, bias=False, layers=2, hidden=128, heads=2, kv=1, inter=192, vocab=300):
+        sd = OrderedDict()
+        sd["model.embed_tokens.weight"] = torch.randn(vocab, hidden, generator=g)
+        for i in range(layers):
+            p = f"model.layers.{i}."
+            sd[p + "self_attn.q_proj.weight"] = torch.randn(heads * 64, hidden, generator=g).bfloat16()
+            sd[p + "self_attn.k_proj.weight"] = torch.randn(kv * 64, hidden, generator=g).bfloat16()
+            sd[p + "self_attn.v_proj.weight"] = torch.randn(kv * 64, hidden, generator=g).half()
+            sd[p + "self_attn.o_proj.weight"] = torch.randn(hidden, heads * 64, generator=g)
+            if qk_norm:
+                sd[p + "self_attn.q_norm.weight"] = torch.ones(64)
+            if bias:
+                sd[p + "self_attn.q_proj.bias"] = torch.zeros(heads * 64)
+            sd[p + "mlp.up_proj.weight"] = torch.randn(inter, hidden, generator=g)
+            sd[p + "mlp.down_proj.weight"] = torch.randn(hidden, inter, generator=g)
+            sd[p + "input_layernorm.weight"] = torch.ones(hidden)
+        sd["model.norm.weight"] = torch.ones(hidden)
+        return sd
+    paths = {}
+    paths["gguf"] = str(tmp_path / "m.gguf")
+    write_synthetic_gguf(paths["gguf"], tiny_qwen3_config(layers=2, hidden=256, heads=4, kv_heads=2, inter=512, vocab=512), seed=3, device="cpu")
+    paths["st"] = str(tmp_path / "single.safetensors")
+    save_file(llama_like(qk_norm=True), paths["st"])
+    paths["st_noext"] = str(tmp_path / "weights.bin")                              # content decides, not the extension
+    save_file(llama_like(bias=True), paths["st_noext"])
+    paths["ptor"] = str(tmp_path / "m.ptor")
+    S.save_state_dict(llama_like(), paths["ptor"])
+    hf = tmp_path / "hf"
+    hf.mkdir()
+    full = llama_like(layers=3)
+    names = list(full)
+    shard_a, shard_b = OrderedDict((k, full[k]) for k in names[:10]), OrderedDict((k, full[k]) for k in names[10:])
+    save_file(shard_a, str(hf / "model-00001-of-00002.safetensors"))
+    save_file(shard_b, str(hf / "model-00002-of-00002.safetensors"))
+    (hf / "model.safetensors.index.json").write_text(json.dumps({"weight_map": {**{k: "model-00001-of-00002.safetensors" for k in shard_a},
+                                                                                 **{k: "model-00002-of-00002.safetensors" for k in shard_b}}}))
+    (hf / "config.json").write_text(json.dumps({"model_type": "llama", "hidden_size": 128, "num_hidden_layers": 3, "num_attention_heads": 2,
+                                                "num_key_value_heads": 1, "intermediate_size": 192, "vocab_size": 300, "rms_norm_eps": 1e-5,
+                                                "rope_theta": 500000.0, "max_position_embeddings": 2048, "tie_word_embeddings": True}))
+    paths["hf_dir"] = str(hf)
+    paths["shard"] = str(hf / "model-00002-of-00002.safetensors")                 # naming a shard finds its siblings
+    for key, path in paths.items():
+        got = _run(exe, "model", path, "bytes")
+        want = ML.load_model(path)
+        assert got["detected"] == got["format"] == want.format == ML.detect_format(path), key
+        assert got["architecture"] == want.architecture, (key, got["architecture"], want.architecture)
+        wc = dataclasses.asdict(want.config)
+        wc.pop("extra")
+        assert got["config"] == pytest.approx(wc), (key, got["config"], wc)
+        assert set(got["tensors"]) == set(want.tensors), key
+        if key in ("st", "st_noext", "ptor"):                                      # file order is kept for the containers that have one
+            assert list(got["tensors"]) == list(want.tensors), key
+        assert got["files"] == want.files and got["total_parameters"] == want.total_parameters(), key
+        for name, info in want.tensors.items():
+            e = got["tensors"][name]
+            assert e["dtype"] == info.dtype and e["shape"] == info.shape and e["file"] == info.file, (key, name, e, info)
+            if want.format != "gguf":
+                raw = ML.read_tensor(want, name).contiguous().reshape(-1).view(torch.uint8)
+                assert e["nbytes"] == raw.numel() and e["byte_sum"] == int(raw.long().sum()), (key, name)
+    # a .pt zip and a pickle are recognised; junk and short files are not
+    pt_path = str(tmp_path / "m.pt")
+    torch.save({"w": torch.ones(2)}, pt_path)
+    assert _run(exe, "model", pt_path)["format"] == "pytorch"
+    (tmp_path / "junk.dat").write_bytes(b"\x00" * 64)
+    (tmp_path / "short").write_bytes(b"ab")
+    for bad in ("junk.dat", "short", "nothing-here"):
+        r = subprocess.run([exe, "model", str(tmp_path / bad)], capture_output=True, timeout=60)
+        assert r.returncode == 1 and b"unknown model format" in r.stderr, bad
 
 
 def test_native_request_queue(exe):
