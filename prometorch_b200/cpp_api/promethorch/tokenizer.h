@@ -13,8 +13,10 @@
 #include <algorithm>
 #include <cstdint>
 #include <cstdio>
+#include <fstream>
 #include <map>
 #include <queue>
+#include <sstream>
 #include <string>
 #include <tuple>
 #include <unordered_map>
@@ -22,6 +24,7 @@
 #include <vector>
 
 #include "gguf_reader.h"
+#include "json.h"
 
 namespace promethorch {
 namespace io {
@@ -414,6 +417,48 @@ class GGUFTokenizer {
     std::string byte_to_unicode_[256];
     std::unordered_map<uint32_t, unsigned char> unicode_to_byte_;
 };
+
+// The byte-level BPE tokenizer of a Hugging Face checkpoint directory: vocab.json + merges.txt, or the "model" section of
+// tokenizer.json (merges as "a b" strings or as pairs).  Returns false when the directory has neither (torch/serve/llm.h:94-297).
+inline bool load_hf_tokenizer(const std::string& model_dir, GGUFTokenizer& out) {
+    auto slurp = [](const std::string& p, std::string& text) {
+        std::ifstream f(p, std::ios::binary);
+        if (!f) return false;
+        std::stringstream ss;
+        ss << f.rdbuf();
+        text = ss.str();
+        return true;
+    };
+    std::string vj, mt, tj;
+    json::Value vocab;
+    std::vector<std::string> merges;
+    if (slurp(model_dir + "/vocab.json", vj) && slurp(model_dir + "/merges.txt", mt)) {
+        vocab = json::parse(vj);
+        std::istringstream lines(mt);
+        std::string ln;
+        while (std::getline(lines, ln)) {
+            if (!ln.empty() && ln.back() == '\r') ln.pop_back();
+            const bool blank = ln.find_first_not_of(" \t") == std::string::npos;
+            if (!blank && ln.compare(0, 8, "#version") != 0) merges.push_back(ln);
+        }
+    } else if (slurp(model_dir + "/tokenizer.json", tj)) {
+        const json::Value doc = json::parse(tj);
+        vocab = doc["model"]["vocab"];
+        for (const auto& m : doc["model"]["merges"].items()) {
+            if (m.is_string()) merges.push_back(m.as_string());
+            else if (m.is_array() && m.size() == 2) merges.push_back(m.at(0).as_string() + " " + m.at(1).as_string());
+        }
+    }
+    if (!vocab.is_object() || vocab.size() == 0) return false;
+    long long top = -1;
+    for (const auto& kv : vocab.members()) top = std::max(top, kv.second.as_int(-1));
+    if (top < 0 || top > (1ll << 24)) return false;
+    std::vector<std::string> tokens((size_t)top + 1);
+    for (const auto& kv : vocab.members())
+        if (kv.second.as_int(-1) >= 0) tokens[(size_t)kv.second.as_int()] = kv.first;
+    out = GGUFTokenizer(std::move(tokens), "gpt2", {}, merges);
+    return true;
+}
 
 }  // namespace io
 }  // namespace promethorch

@@ -113,6 +113,12 @@ int main(int argc, char** argv) {
             std::cout << run_texts(tok, pj::parse(slurp(argv[3]))).dump() << "\n";
             return 0;
         }
+        if (mode == "hf-tokenize") {                 // DIR TEXTS.json
+            pio::GGUFTokenizer tok;
+            if (!pio::load_hf_tokenizer(argv[2], tok)) { std::cout << "null\n"; return 0; }
+            std::cout << run_texts(tok, pj::parse(slurp(argv[3]))).dump() << "\n";
+            return 0;
+        }
         if (mode == "chat") {
             const pj::Value spec = pj::parse(slurp(argv[2]));
             pj::Value out = pj::Value::array();

@@ -139,6 +139,30 @@ def test_tokenizer_from_a_gguf_file(exe, tmp_path):
         assert got["decoded"][i] == py.decode(py.encode(s)), s
 
 
+def test_hf_tokenizer_files(exe, tmp_path):
+    """vocab.json + merges.txt and tokenizer.json (both spellings of the merges) give the ids of the Python loader."""
+    from prometorch_b200.serve.llm import load_hf_tokenizer
+    tokens, merges = _train_bpe(" ".join(TEXTS) + " the quick brown fox jumps over the lazy dog " * 10, 150)
+    vocab = {t: i for i, t in enumerate(tokens)}
+    texts = [t for t in TEXTS if "<|" not in t]
+    tj = tmp_path / "texts.json"
+    tj.write_text(json.dumps(texts, ensure_ascii=False), encoding="utf-8")
+    a, b, c, d = (tmp_path / n for n in ("a", "b", "c", "d"))
+    for x in (a, b, c, d):
+        x.mkdir()
+    (a / "vocab.json").write_text(json.dumps(vocab, ensure_ascii=False), encoding="utf-8")
+    (a / "merges.txt").write_text("#version: 0.2\n" + "\n".join(merges) + "\n\n", encoding="utf-8")
+    (b / "tokenizer.json").write_text(json.dumps({"model": {"type": "BPE", "vocab": vocab, "merges": merges}}), encoding="utf-8")
+    (c / "tokenizer.json").write_text(json.dumps({"model": {"type": "BPE", "vocab": vocab, "merges": [m.split(" ") for m in merges]}}), encoding="utf-8")
+    for folder in (a, b, c):
+        py = load_hf_tokenizer(str(folder))
+        got = _run(exe, "hf-tokenize", str(folder), str(tj))
+        for i, t in enumerate(texts):
+            assert got["ids"][i] == py.encode(t), (folder.name, t)
+            assert got["decoded"][i] == py.decode(py.encode(t)), (folder.name, t)
+    assert load_hf_tokenizer(str(d)) is None and _run(exe, "hf-tokenize", str(d), str(tj)) is None
+
+
 def test_json_roundtrip(exe, tmp_path):
     doc = {"a": [1, -2, 3.5, 1e-7, 12345678901234, True, False, None], "s": "quote \" slash \\ nl \n tab \t uni é 中 \U0001F600 ctl \u0001",
            "nested": {"empty_obj": {}, "empty_arr": [], "k": {"deep": [[[]]]}}, "order": 1, "z": 0, "b": 2}
