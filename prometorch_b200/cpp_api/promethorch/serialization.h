@@ -7,6 +7,7 @@
 //  * save_pytorch / load_pytorch: PyTorch zip checkpoints through libtorch's restricted unpickler (tensors and plain
 //    containers only; it executes no code from the file), the policy of torch/serialization_pytorch.h:734-878.
 #pragma once
+#include "model_loader.h"
 #include <torch/torch.h>
 
 #include <cstdint>
@@ -176,6 +177,92 @@ inline OrderedStateDict load_pytorch(const std::string& path) {
         throw std::runtime_error("load_pytorch: only tensors and name -> tensor dictionaries are accepted");
     }
     return out;
+}
+
+// ---- safetensors (u64 header length, JSON header, raw little-endian data) to and from name -> tensor dictionaries
+namespace detail {
+inline c10::ScalarType safetensors_dtype(const std::string& d) {
+    if (d == "f64") return c10::kDouble;
+    if (d == "f32") return c10::kFloat;
+    if (d == "f16") return c10::kHalf;
+    if (d == "bf16") return c10::kBFloat16;
+    if (d == "i64") return c10::kLong;
+    if (d == "i32") return c10::kInt;
+    if (d == "i16") return c10::kShort;
+    if (d == "i8") return c10::kChar;
+    if (d == "u8") return c10::kByte;
+    if (d == "bool") return c10::kBool;
+    throw std::runtime_error("safetensors: unsupported dtype " + d);
+}
+inline const char* safetensors_name(c10::ScalarType t) {
+    switch (t) {
+        case c10::kDouble: return "F64";
+        case c10::kFloat: return "F32";
+        case c10::kHalf: return "F16";
+        case c10::kBFloat16: return "BF16";
+        case c10::kLong: return "I64";
+        case c10::kInt: return "I32";
+        case c10::kShort: return "I16";
+        case c10::kChar: return "I8";
+        case c10::kByte: return "U8";
+        case c10::kBool: return "BOOL";
+        default: throw std::runtime_error("safetensors: unsupported tensor dtype");
+    }
+}
+}  // namespace detail
+
+inline OrderedStateDict load_safetensors(const std::string& path) {
+    io::loader::SafeTensorsFile f(path);
+    std::ifstream in(path, std::ios::binary);
+    OrderedStateDict out;
+    for (const auto& name : f.keys()) {
+        const auto& info = f.info(name);
+        Tensor t = torch::empty(info.shape, torch::TensorOptions().dtype(detail::safetensors_dtype(info.dtype)));
+        if ((uint64_t)t.nbytes() != info.nbytes) throw std::runtime_error("safetensors: size of " + name + " does not match its shape");
+        in.seekg((std::streamoff)info.offset);
+        in.read((char*)t.data_ptr(), (std::streamsize)info.nbytes);
+        if (!in) throw std::runtime_error("safetensors: short read of " + name);
+        out.emplace_back(name, t);
+    }
+    return out;
+}
+// Every file of a Hugging Face directory (or the siblings of a shard).
+inline OrderedStateDict load_safetensors_sharded(const std::string& path) {
+    OrderedStateDict out;
+    for (const auto& file : io::loader::find_shard_files(path))
+        for (auto& kv : load_safetensors(file)) out.push_back(std::move(kv));
+    return out;
+}
+inline void save_safetensors(const OrderedStateDict& sd, const std::string& path, const std::map<std::string, std::string>& metadata = {}) {
+    json::Value header = json::Value::object();
+    if (!metadata.empty()) {
+        json::Value m = json::Value::object();
+        for (const auto& kv : metadata) m.set(kv.first, kv.second);
+        header.set("__metadata__", m);
+    }
+    std::vector<Tensor> data;
+    uint64_t offset = 0;
+    for (const auto& kv : sd) {
+        Tensor t = kv.second.detach().cpu().contiguous();
+        json::Value e = json::Value::object(), shape = json::Value::array(), off = json::Value::array();
+        for (auto d : t.sizes()) shape.push_back((long long)d);
+        off.push_back((long long)offset);
+        off.push_back((long long)(offset + t.nbytes()));
+        e.set("dtype", detail::safetensors_name(t.scalar_type()));
+        e.set("shape", shape);
+        e.set("data_offsets", off);
+        header.set(kv.first, e);
+        offset += t.nbytes();
+        data.push_back(t);
+    }
+    std::string h = header.dump();
+    while (h.size() % 8) h.push_back(' ');               // the data section starts on an 8-byte boundary
+    std::ofstream f(path, std::ios::binary);
+    if (!f) throw std::runtime_error("serialization: cannot open " + path);
+    const uint64_t n = h.size();
+    f.write((const char*)&n, 8);
+    f.write(h.data(), (std::streamsize)h.size());
+    for (const auto& t : data) f.write((const char*)t.data_ptr(), (std::streamsize)t.nbytes());
 }
 
 }  // namespace promethorch

@@ -24,6 +24,7 @@
 #include "fsdp.h"
 #include "hooks.h"
 #include "lr_scheduler.h"
+#include "models.h"
 #include "nn_extra.h"
 #include "optim.h"
 #include "pipeline.h"

@@ -1,6 +1,9 @@
-// Every element-wise optimizer of the C++ API run for a few steps on a fixed, formula-made sequence of gradients; the final
-// parameters are printed so that the Python optimizers can be run on the same sequence and compared (the two are separate
-// implementations of the same rules).  Output: one line per optimizer, "NAME v v v ...".
+// What the C++ API computes, printed so that the Python package can compute the same and compare (the two are separate
+// implementations of the same rules):
+//   (no arguments)          every element-wise optimizer for a few steps on a fixed, formula-made sequence of gradients
+//                           ("NAME v v v ..."), and the learning-rate sequence of every scheduler ("S:NAME lr lr ...")
+//   io DIR                  checkpoints written by Python read and written back (PTOR container, PyTorch zip)
+//   llama DIR OUT           a Hugging Face Llama directory: logits, greedy and sampled continuation, safetensors written back
 #include <cmath>
 #include <cstdio>
 
@@ -101,9 +104,36 @@ static int checkpoints(const std::string& dir) {
     return 0;
 }
 
+// A Hugging Face Llama directory: logits of a prompt, greedy continuation, and the safetensors round trip.
+static int llama(const std::string& dir, const std::string& out_path) {
+    auto cfg = pt::models::LlamaConfig::from_json(dir + "/config.json");
+    pt::models::Llama model(cfg);
+    model->load_hf(dir);
+    model->eval();
+    pt::NoGradGuard ng;
+    const std::vector<int64_t> prompt{1, 17, 250, 3, 99, 42};
+    auto logits = model->forward(pt::tensor(prompt, pt::kLong).unsqueeze(0));
+    std::printf("L:shape %lld %lld %lld\n", (long long)logits.size(0), (long long)logits.size(1), (long long)logits.size(2));
+    std::printf("L:last");
+    auto last = logits[0][(int64_t)prompt.size() - 1].to(pt::kDouble);
+    for (int64_t i = 0; i < 16; ++i) std::printf(" %.7g", last[i].item<double>());
+    std::printf("\nL:argmax");
+    auto am = logits[0].argmax(-1);
+    for (int64_t i = 0; i < am.numel(); ++i) std::printf(" %lld", (long long)am[i].item<int64_t>());
+    std::printf("\nL:greedy");
+    for (auto t : model->generate(prompt, 10, 0.0, 0, false)) std::printf(" %lld", (long long)t);
+    std::printf("\nL:sampled");
+    pt::manual_seed(3);
+    for (auto t : model->generate(prompt, 6, 0.9, 20, false)) std::printf(" %lld", (long long)t);
+    std::printf("\n");
+    pt::save_safetensors(model->hf_state_dict(), out_path, {{"format", "pt"}});
+    return 0;
+}
+
 int main(int argc, char** argv) {
     using namespace pt::optim;
     if (argc > 2 && std::string(argv[1]) == "io") return checkpoints(argv[2]);
+    if (argc > 3 && std::string(argv[1]) == "llama") return llama(argv[2], argv[3]);
     schedulers();
     run<SGD>("SGD", SGDOptions(0.05).momentum_(0.9).nesterov_(true).weight_decay_(0.01));
     run<SGD>("SGD_plain", SGDOptions(0.05));

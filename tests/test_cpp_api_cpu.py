@@ -77,6 +77,65 @@ def _check_checkpoints(exe, tmp_path):
         assert back_pt[k].dtype == t.dtype and torch.equal(back_pt[k], t), k
 
 
+def _check_llama(exe, tmp_path):
+    """models::Llama (libtorch tensor code) on a Hugging Face directory against the Python engine's weights: logits of a
+    prompt, greedy continuation with the key / value cache, and safetensors written by C++ read back by Python."""
+    import json
+    from prometorch_b200.io.safetensors import load_file
+    from prometorch_b200.serve.llm import GenerationConfig, LlamaConfig, LlamaWeights, LLMEngine, save_safetensors
+    cfg = LlamaConfig(vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                      max_position_embeddings=128, eos_token_id=2)
+    w = LlamaWeights.random(cfg, seed=31)
+    d = tmp_path / "hf_llama"
+    d.mkdir()
+    (d / "config.json").write_text(json.dumps({k: getattr(cfg, k) for k in cfg.__dataclass_fields__}))
+    sd = w.state_dict()
+    save_safetensors(sd, str(d / "model.safetensors"))
+    out_file = str(tmp_path / "from_cpp.safetensors")
+    r = subprocess.run([exe, "llama", str(d), out_file], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-1000:] + r.stderr[-2000:]
+    got = {ln.split()[0]: ln.split()[1:] for ln in r.stdout.splitlines() if ln.startswith("L:")}
+    prompt = [1, 17, 250, 3, 99, 42]
+    eng = LLMEngine(device="cpu", max_pages=16, max_active=2)
+    assert eng.load(str(d))
+    greedy = eng.generate(prompt, GenerationConfig(max_new_tokens=10, temperature=0.0, repetition_penalty=1.0, top_k=1, stop_at_eos=False)
+                          if "stop_at_eos" in GenerationConfig.__dataclass_fields__ else
+                          GenerationConfig(max_new_tokens=10, temperature=0.0, repetition_penalty=1.0, top_k=1)).token_ids
+    cpp = [int(t) for t in got["L:greedy"]]
+    assert cpp[:len(greedy)] == greedy, (cpp, greedy)                      # the engine may stop at its end-of-sequence id
+    assert [int(x) for x in got["L:shape"]] == [1, 6, 300] and len(got["L:sampled"]) == 6 and all(0 <= int(t) < 300 for t in got["L:sampled"])
+    # the same logits from plain tensor code over the Python weights
+    import torch.nn.functional as F
+    H, Hk, Dh = 4, 2, 16
+    ids = torch.tensor(prompt)
+    h = sd["model.embed_tokens.weight"][ids]
+    inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, Dh, 2, dtype=torch.float64) / Dh))
+    ang = torch.arange(len(prompt), dtype=torch.float64)[:, None] * inv[None]
+    cos, sin = ang.cos().float()[:, None], ang.sin().float()[:, None]
+
+    def rms(x, wt):
+        return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + cfg.rms_norm_eps) * wt
+
+    def rope(x):
+        a, b = x[..., :Dh // 2], x[..., Dh // 2:]
+        return torch.cat([a * cos - b * sin, b * cos + a * sin], -1)
+    for l in range(2):
+        p = f"model.layers.{l}."
+        x = rms(h, sd[p + "input_layernorm.weight"])
+        q = rope((x @ sd[p + "self_attn.q_proj.weight"].t()).view(-1, H, Dh))
+        k = rope((x @ sd[p + "self_attn.k_proj.weight"].t()).view(-1, Hk, Dh)).repeat_interleave(H // Hk, 1)
+        v = (x @ sd[p + "self_attn.v_proj.weight"].t()).view(-1, Hk, Dh).repeat_interleave(H // Hk, 1)
+        a = F.scaled_dot_product_attention(q.transpose(0, 1)[None], k.transpose(0, 1)[None], v.transpose(0, 1)[None], is_causal=True)[0].transpose(0, 1).reshape(len(prompt), -1)
+        h = h + a @ sd[p + "self_attn.o_proj.weight"].t()
+        x = rms(h, sd[p + "post_attention_layernorm.weight"])
+        h = h + (F.silu(x @ sd[p + "mlp.gate_proj.weight"].t()) * (x @ sd[p + "mlp.up_proj.weight"].t())) @ sd[p + "mlp.down_proj.weight"].t()
+    logits = rms(h, sd["model.norm.weight"]) @ sd.get("lm_head.weight", sd["model.embed_tokens.weight"]).t()
+    assert [int(t) for t in got["L:argmax"]] == logits.argmax(-1).tolist()
+    assert torch.allclose(torch.tensor([float(v) for v in got["L:last"]]), logits[-1, :16], atol=2e-4, rtol=1e-4)
+    back = load_file(out_file)
+    assert set(back) == set(sd) and all(torch.equal(back[k], sd[k]) for k in sd)
+
+
 def _check_schedulers(sched):
     """The learning-rate sequences of the C++ schedulers against the Python ones (same constructor arguments)."""
     from prometorch_b200 import optim as O
@@ -114,20 +173,22 @@ def _check_schedulers(sched):
 
 
 @pytest.mark.skipif(shutil.which("g++") is None, reason="needs g++")
-def test_cpp_and_python_optimizers_walk_the_same_path(tmp_path):
+def test_cpp_and_python_implementations_agree(tmp_path):
     """The C++ and the Python optimizers are separate implementations of the reference's update rules: on the same start
     point and the same sequence of gradients they must end at the same parameters; the sixteen schedulers must produce the
-    same learning-rate sequences."""
+    same learning-rate sequences; checkpoints written by one side load on the other; the C++ Llama gives the logits and the
+    greedy continuation of the Python engine on the same Hugging Face directory."""
     import math
     from prometorch_b200 import optim as O
-    exe = str(tmp_path / "optim_trajectories")
-    cmd = ["g++", "-std=c++17", "-O1", os.path.join(ROOT, "tests", "cpp", "optim_trajectories.cpp"), "-o", exe,
+    exe = str(tmp_path / "cross_language")
+    cmd = ["g++", "-std=c++17", "-O1", os.path.join(ROOT, "tests", "cpp", "cross_language.cpp"), "-o", exe,
            f"-I{ROOT}/prometorch_b200/cpp_api"] + _torch_flags()
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, r.stderr[-3000:]
     r = subprocess.run([exe], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stderr[-2000:]
     _check_checkpoints(exe, tmp_path)
+    _check_llama(exe, tmp_path)
     lines = [ln for ln in r.stdout.splitlines() if ln.strip()]
     got = {ln.split()[0]: [float(v) for v in ln.split()[1:]] for ln in lines if not ln.startswith("S:")}
     sched = {ln.split()[0][2:]: [float(v) for v in ln.split()[1:]] for ln in lines if ln.startswith("S:")}
