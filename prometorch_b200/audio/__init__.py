@@ -64,3 +64,91 @@ def load_wav(path: str):
     n = struct.unpack_from("<I", b, i + 4)[0]
     x = torch.frombuffer(bytearray(b[i + 8:i + 8 + n]), dtype=torch.int16).float() / 32767.0
     return x, sr
+
+
+# ---------------------------------------------------------------------------------------------- functional (torch/audio/functional.h)
+def hann_window(n: int, device=None) -> torch.Tensor:
+    return torch.hann_window(n, device=device)
+
+
+def spectrogram(x: torch.Tensor, n_fft: int = 400, hop_length: int = 160, window: torch.Tensor = None, power: float = 2.0) -> torch.Tensor:
+    """|STFT|^power, ``[..., n_fft/2 + 1, frames]`` (power None: the complex STFT)."""
+    s = stft(x, n_fft, hop_length, window)
+    return s if power is None else s.abs() ** power
+
+
+def melscale_fbanks(n_freqs: int, n_mels: int, sample_rate: int) -> torch.Tensor:
+    """Triangular mel filters as ``[n_freqs, n_mels]`` (the orientation of the reference's function; ``mel_filterbank`` is its transpose)."""
+    return mel_filterbank(n_mels, (n_freqs - 1) * 2, sample_rate).t().contiguous()
+
+
+def amplitude_to_db(x: torch.Tensor, multiplier: float = 10.0, amin: float = 1e-10, db_multiplier: float = 0.0, top_db: float = None) -> torch.Tensor:
+    db = multiplier * torch.log10(x.clamp_min(amin)) - multiplier * db_multiplier
+    if top_db is not None:
+        db = torch.maximum(db, db.amax() - top_db)
+    return db
+
+
+def mu_law_encoding(x: torch.Tensor, quantization_channels: int = 256) -> torch.Tensor:
+    """Signal in [-1, 1] -> integers in [0, quantization_channels)."""
+    mu = quantization_channels - 1.0
+    y = torch.sign(x) * torch.log1p(mu * x.abs().clamp(max=1.0)) / math.log1p(mu)
+    return ((y + 1) / 2 * mu + 0.5).to(torch.int64)
+
+
+def mu_law_decoding(q: torch.Tensor, quantization_channels: int = 256) -> torch.Tensor:
+    mu = quantization_channels - 1.0
+    y = q.to(torch.float32) / mu * 2 - 1
+    return torch.sign(y) * (torch.exp(y.abs() * math.log1p(mu)) - 1) / mu
+
+
+# ---------------------------------------------------------------------------------------------- transforms (torch/audio/transforms.h)
+class Spectrogram(torch.nn.Module):
+    def __init__(self, n_fft: int = 400, hop_length: int = None, power: float = 2.0):
+        super().__init__()
+        self.n_fft, self.hop_length, self.power = n_fft, hop_length or n_fft // 2, power
+        self.register_buffer("window", torch.hann_window(n_fft))
+
+    def forward(self, x):
+        return spectrogram(x, self.n_fft, self.hop_length, self.window, self.power)
+
+
+class MelSpectrogram(torch.nn.Module):
+    def __init__(self, sample_rate: int = 16000, n_fft: int = 400, hop_length: int = None, n_mels: int = 128):
+        super().__init__()
+        self.spec = Spectrogram(n_fft, hop_length, 2.0)
+        self.register_buffer("fb", mel_filterbank(n_mels, n_fft, sample_rate))
+
+    def forward(self, x):
+        return torch.matmul(self.fb, self.spec(x))
+
+
+class AmplitudeToDB(torch.nn.Module):
+    def __init__(self, stype: str = "power", top_db: float = None):
+        super().__init__()
+        self.multiplier, self.top_db = (10.0 if stype == "power" else 20.0), top_db
+
+    def forward(self, x):
+        return amplitude_to_db(x, self.multiplier, top_db=self.top_db)
+
+
+class MFCC(torch.nn.Module):
+    def __init__(self, sample_rate: int = 16000, n_mfcc: int = 40, n_mels: int = 128, n_fft: int = 400, hop_length: int = None):
+        super().__init__()
+        self.mel, self.to_db = MelSpectrogram(sample_rate, n_fft, hop_length, n_mels), AmplitudeToDB("power", 80.0)
+        n = torch.arange(n_mels)
+        dct = torch.cos(math.pi / n_mels * (n[None, :] + 0.5) * torch.arange(n_mfcc)[:, None]) * math.sqrt(2.0 / n_mels)
+        dct[0] *= 1.0 / math.sqrt(2.0)                                  # orthonormal DCT-II
+        self.register_buffer("dct", dct)
+
+    def forward(self, x):
+        return torch.matmul(self.dct, self.to_db(self.mel(x)))
+
+
+class Resample(torch.nn.Module):
+    def __init__(self, orig_freq: int = 16000, new_freq: int = 16000):
+        super().__init__()
+        self.orig_freq, self.new_freq = orig_freq, new_freq
+
+    def forward(self, x):
+        return x if self.orig_freq == self.new_freq else resample(x, self.orig_freq, self.new_freq)

@@ -506,3 +506,61 @@ def test_top_level_falls_back_to_torch():
     assert pt.randn_like(pt.zeros(3)).shape == (3,) and ptb.full_like(ptb.ones(2), 7.0).tolist() == [7.0, 7.0] and pt.Generator is torch.Generator
     with pytest.raises(AttributeError):
         ptb.no_such_function
+
+
+def test_ecosystem_shims_cover_the_reference_surface(tmp_path):
+    """audio (functional + transform modules), text (tokenizers, datasets, batching) and vision (image files) additions."""
+    from prometorch_b200 import vision
+    # ---- audio
+    t = torch.linspace(0, 1, 16000)
+    x = torch.sin(2 * math.pi * 440 * t)
+    spec = audio.spectrogram(x, 400, 160)
+    assert spec.shape[0] == 201 and int(spec.mean(1).argmax()) == round(440 * 400 / 16000)
+    assert torch.allclose(audio.Spectrogram(400, 160)(x), spec) and audio.melscale_fbanks(201, 40, 16000).shape == (201, 40)
+    mel = audio.MelSpectrogram(16000, 400, 160, 64)(x)
+    assert mel.shape[0] == 64 and audio.MFCC(16000, 13, 64, 400, 160)(x).shape[0] == 13
+    db = audio.AmplitudeToDB("power", top_db=80.0)(mel)
+    assert float(db.max() - db.min()) <= 80.0 + 1e-4
+    q = audio.mu_law_encoding(x)
+    assert q.dtype == torch.int64 and int(q.min()) >= 0 and int(q.max()) <= 255
+    assert float((audio.mu_law_decoding(q) - x).abs().max()) < 0.05
+    assert audio.Resample(16000, 8000)(x).shape[-1] == 8000 and audio.hann_window(8).shape == (8,)
+    # ---- text
+    assert text.BasicTokenizer().tokenize("Hello, World! it's") == ["hello", ",", "world", "!", "it", "'", "s"]
+    ct = text.CharTokenizer("hello world")
+    assert ct.decode(ct.encode("hello")) == "hello" and ct.encode("z") == [0] and len(ct) == 9
+    (tmp_path / "a.txt").write_text("first line\n\nsecond line\n")
+    ds = text.TextFileDataset(str(tmp_path / "a.txt"), labels=[0, 1])
+    assert len(ds) == 2 and ds[1] == ("second line", 1)
+    (tmp_path / "a.csv").write_text("text,label\ngood film,pos\nbad film,neg\n")
+    cs = text.CSVDataset(str(tmp_path / "a.csv"), label_column="label")
+    assert len(cs) == 2 and cs[0] == (["good film"], "pos") and cs.header == ["text", "label"]
+    (tmp_path / "a.jsonl").write_text('{"t": "one", "y": 1}\n{"t": "two", "y": 0}\n')
+    js = text.JSONLDataset(str(tmp_path / "a.jsonl"), "t", "y")
+    assert js[1] == ("two", 0) and text.JSONLDataset(str(tmp_path / "a.jsonl"))[0] == {"t": "one", "y": 1}
+    batch = [[1, 2, 3], [4], [5, 6]]
+    assert text.pad_sequence(batch).tolist() == [[1, 2, 3], [4, 0, 0], [5, 6, 0]] and text.pad_sequence(batch, batch_first=False).shape == (3, 3)
+    assert text.pad_sequence(batch, padding_value=9, max_len=2).tolist() == [[1, 2], [4, 9], [5, 6]]
+    assert text.sequence_lengths(batch).tolist() == [3, 1, 2] and text.padding_mask(batch).tolist() == [[False] * 3, [False, True, True], [False, False, True]]
+    packed = text.pack_padded_sequence(text.pad_sequence(batch).unsqueeze(-1).float(), [3, 1, 2])
+    assert packed.batch_sizes.tolist() == [3, 2, 1]
+    # ---- vision
+    img = torch.rand(3, 5, 7)
+    vision.save_pnm(str(tmp_path / "c.ppm"), img)
+    back = vision.load_image(str(tmp_path / "c.ppm"))
+    assert back.shape == (3, 5, 7) and float((back - img).abs().max()) <= 0.5 / 255 + 1e-6
+    (tmp_path / "g.pgm").write_bytes(b"P2\n# a comment\n3 2\n15\n0 5 10\n15 1 2\n")
+    g = vision.load_pnm(str(tmp_path / "g.pgm"))
+    assert g.shape == (1, 2, 3) and torch.allclose(g[0, 1], torch.tensor([15, 1, 2]) / 15)
+    for cls in ("cats", "dogs"):
+        (tmp_path / "set" / cls).mkdir(parents=True)
+        for i in range(2):
+            vision.save_pnm(str(tmp_path / "set" / cls / f"{i}.pgm"), torch.rand(1, 4, 4))
+    torch.save(torch.rand(1, 4, 4), str(tmp_path / "set" / "cats" / "t.pt"))
+    folder = vision.ImageFolder(str(tmp_path / "set"), transform=vision.transforms.Resize(8))
+    assert len(folder) == 5 and folder.classes == ["cats", "dogs"] and folder.class_to_idx == {"cats": 0, "dogs": 1}
+    xi, yi = folder[4]
+    assert xi.shape == (1, 8, 8) and yi == 1
+    assert vision.ConvBNReLU(3, 8, stride=2)(torch.rand(2, 3, 8, 8)).shape == (2, 8, 4, 4)
+    with pytest.raises(ValueError):
+        vision.load_image(str(tmp_path / "a.txt"))
