@@ -8,6 +8,7 @@ on CUDA the unscale + inf/nan check is one multi-tensor kernel and the skip deci
 device when the optimizer is one of this package's fused optimizers."""
 from __future__ import annotations
 
+from dataclasses import dataclass
 from typing import Optional
 
 import torch
@@ -59,6 +60,66 @@ def is_autocast_enabled(device_type: str = "cuda") -> bool:
 
 def get_autocast_dtype(device_type: str = "cuda") -> torch.dtype:
     return torch.get_autocast_dtype(device_type)
+
+
+# the reference's free functions over the autocast state (torch/amp/autocast.h)
+get_autocast_category = get_autocast_policy
+policy_for = get_autocast_policy
+
+
+def is_autocast_cpu_enabled() -> bool:
+    return torch.is_autocast_enabled("cpu")
+
+
+def set_autocast_enabled(enabled: bool, device_type: str = "cuda"):
+    torch.set_autocast_enabled(device_type, bool(enabled))
+
+
+def set_autocast_dtype(dtype: torch.dtype, device_type: str = "cuda"):
+    torch.set_autocast_dtype(device_type, dtype)
+
+
+def set_autocast_cpu_enabled(enabled: bool):
+    set_autocast_enabled(enabled, "cpu")
+
+
+def set_autocast_cpu_dtype(dtype: torch.dtype):
+    set_autocast_dtype(dtype, "cpu")
+
+
+def has_tensor_cores() -> bool:
+    """Whether the current CUDA device has tensor cores (compute capability 7.0 or later)."""
+    return torch.cuda.is_available() and torch.cuda.get_device_capability()[0] >= 7
+
+
+def autocast_matmul(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """A matrix product under the lower-precision policy whatever the surrounding autocast state is."""
+    dev = a.device.type
+    dt = torch.get_autocast_dtype(dev) if torch.is_autocast_enabled(dev) else (torch.bfloat16 if dev == "cpu" else torch.float16)
+    return torch.matmul(a.to(dt), b.to(dt))
+
+
+def autocast_softmax(x: torch.Tensor, dim: int = -1) -> torch.Tensor:
+    """Softmax under the fp32 policy: computed in float32 whatever the input dtype."""
+    return torch.softmax(x.float(), dim)
+
+
+@dataclass
+class GradScalerOptions:
+    init_scale: float = 65536.0
+    growth_factor: float = 2.0
+    backoff_factor: float = 0.5
+    growth_interval: int = 2000
+    enabled: bool = True
+
+
+def make_grad_scaler(options: "GradScalerOptions" = None) -> "GradScaler":
+    o = options or GradScalerOptions()
+    return GradScaler(o.init_scale, o.growth_factor, o.backoff_factor, o.growth_interval, o.enabled)
+
+
+def make_disabled_scaler() -> "GradScaler":
+    return GradScaler(enabled=False)
 
 
 class GradScaler:

@@ -135,3 +135,112 @@ class CharTextDataset(Dataset):
         s = i * self.stride
         w = self.data[s:s + self.block_size + 1]
         return w[:-1], w[1:]
+
+
+# ---------------------------------------------------------------------------------------------- the reference's helper names (torch/data/*.h)
+from dataclasses import dataclass as _dataclass  # noqa: E402
+from typing import Any as _Any, Callable as _Callable, Optional as _Optional, Sequence as _Sequence  # noqa: E402
+
+
+@_dataclass
+class DataLoaderOptions:
+    """The fields of the reference's options struct; ``make_loader(dataset, options)`` builds a loader from them."""
+    batch_size: int = 1
+    shuffle: bool = False
+    num_workers: int = 0
+    prefetch_factor: int = 2
+    drop_last: bool = False
+    pin_memory: bool = False
+    seed: _Optional[int] = None
+
+
+def make_loader(dataset, options: DataLoaderOptions = None, sampler=None, collate_fn=None) -> DataLoader:
+    o = options or DataLoaderOptions()
+    gen = torch.Generator().manual_seed(o.seed) if o.seed is not None else None
+    return DataLoader(dataset, batch_size=o.batch_size, shuffle=o.shuffle and sampler is None, sampler=sampler, num_workers=o.num_workers,
+                      prefetch_factor=o.prefetch_factor if o.num_workers > 0 else None, drop_last=o.drop_last, pin_memory=o.pin_memory,
+                      generator=gen, collate_fn=collate_fn)
+
+
+@_dataclass
+class Example:
+    """One sample: data and target."""
+    data: _Any
+    target: _Any = None
+
+
+@_dataclass
+class Batch:
+    """A collated batch: ``data [B, ...]`` and ``target [B, ...]``."""
+    data: torch.Tensor
+    target: _Optional[torch.Tensor] = None
+
+    def to(self, device, non_blocking: bool = False) -> "Batch":
+        return Batch(self.data.to(device, non_blocking=non_blocking), None if self.target is None else self.target.to(device, non_blocking=non_blocking))
+
+    def __iter__(self):
+        return iter((self.data, self.target))
+
+
+class DefaultCollate:
+    """Stack ``Example``s or ``(data, target)`` pairs into a :class:`Batch`."""
+
+    def __call__(self, samples) -> Batch:
+        pairs = [(s.data, s.target) if isinstance(s, Example) else (s if isinstance(s, (tuple, list)) else (s, None)) for s in samples]
+        data = torch.stack([torch.as_tensor(d) for d, _ in pairs])
+        target = None if pairs[0][1] is None else torch.stack([torch.as_tensor(t) for _, t in pairs])
+        return Batch(data, target)
+
+
+class Transform:
+    def __call__(self, x):
+        raise NotImplementedError
+
+
+class Compose(Transform):
+    def __init__(self, transforms: _Sequence[_Callable]):
+        self.transforms = list(transforms)
+
+    def __call__(self, x):
+        for t in self.transforms:
+            x = t(x)
+        return x
+
+
+class Lambda(Transform):
+    def __init__(self, fn: _Callable):
+        self.fn = fn
+
+    def __call__(self, x):
+        return self.fn(x)
+
+
+class Normalize(Transform):
+    """``(x - mean) / std`` with scalars or per-channel values (broadcast over the trailing dimensions)."""
+
+    def __init__(self, mean, std):
+        self.mean, self.std = torch.as_tensor(mean, dtype=torch.float32), torch.as_tensor(std, dtype=torch.float32)
+
+    def __call__(self, x):
+        m, s = self.mean, self.std
+        if m.dim() == 1 and x.dim() > 1:
+            shape = [-1] + [1] * (x.dim() - 1)
+            m, s = m.view(shape), s.view(shape)
+        return (x - m) / s
+
+
+class Flatten(Transform):
+    def __call__(self, x):
+        return x.reshape(-1)
+
+
+def make_sequential_sampler(dataset) -> Sampler:
+    return SequentialSampler(dataset)
+
+
+def make_random_sampler(dataset, seed: _Optional[int] = None) -> Sampler:
+    return RandomSampler(dataset, generator=torch.Generator().manual_seed(seed) if seed is not None else None)
+
+
+def make_batch_sampler(sampler, batch_size: int, drop_last: bool = False) -> BatchSampler:
+    return BatchSampler(sampler, batch_size, drop_last)

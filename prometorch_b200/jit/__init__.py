@@ -57,3 +57,11 @@ def trace(fn, example_inputs):
 
 def script(fn):
     return torch.jit.script(fn)
+
+
+CompiledFn = CompiledModule                # the reference's name for what compile() returns
+
+
+def tracing_active() -> bool:
+    """Whether a CUDA-graph capture is in progress on the current stream (the recorder state of the reference's tracer)."""
+    return torch.cuda.is_available() and torch.cuda.is_current_stream_capturing()

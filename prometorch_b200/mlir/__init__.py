@@ -22,3 +22,6 @@ def export(model: nn.Module, input_shape, path: str = None) -> str:
         with open(path, "w") as f:
             f.write(text)
     return text
+
+
+export_mlir = export                       # the reference's name (torch/mlir/export.h)

@@ -62,3 +62,7 @@ class Executor:
         for kind, w, b in self.ops:
             x = torch.nn.functional.linear(x, w, b) if kind == 1 else fns[kind](x)
         return x
+
+
+MobileExecutor = Executor                  # the reference's names (torch/mobile/executor.h)
+export_model = save

@@ -75,3 +75,13 @@ def export(model: nn.Module, args, path: str, **kw):
     except Exception:
         shape = list(args.shape if torch.is_tensor(args) else args[0].shape)
         return export_mlp(model, shape, path)
+
+
+def export_model(model: nn.Module, input_shape, path: str, opset: int = 13):
+    """The reference's entry point (torch/onnx/export.h): ``export_model(model, input shape, path)``."""
+    return export(model, torch.zeros(*input_shape), path, opset_version=opset) if not _is_chain(model) else export_mlp(model, list(input_shape), path, opset)
+
+
+def _is_chain(model: nn.Module) -> bool:
+    leaves = [m for m in model.modules() if not list(m.children())]
+    return all(isinstance(m, (nn.Linear, nn.ReLU, nn.Sigmoid, nn.Tanh, nn.Softmax, nn.Identity, nn.Flatten, nn.Dropout)) for m in leaves)

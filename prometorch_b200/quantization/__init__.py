@@ -164,3 +164,163 @@ class Linear4bit(nn.Module):
     def forward(self, x):
         w = dequantize_4bit(self.packed, self.absmax, self.shape, self.block, self.kind).to(x.dtype)
         return F.linear(x, w, self.bias)
+
+
+# ----------------------------------------------------------------------------- post-training static quantisation (torch/quantization/quantize.h)
+from dataclasses import dataclass as _dataclass  # noqa: E402
+
+Observer = MinMaxObserver                  # the reference's base-class name
+
+
+@_dataclass
+class QConfig:
+    """What to observe and how to quantise: bit width, symmetric or affine, one scale per tensor or per output channel."""
+    bits: int = 8
+    symmetric: bool = True
+    per_channel: bool = False
+    momentum: float = 0.0                  # 0: running min / max; > 0: moving average of the batch extremes
+
+
+def default_qconfig() -> QConfig:
+    return QConfig()
+
+
+def default_per_channel_qconfig() -> QConfig:
+    return QConfig(per_channel=True)
+
+
+@_dataclass
+class QuantizedTensor:
+    """Integer values with the scale (and zero point) that maps them back: ``(q - zero_point) * scale``."""
+    q: torch.Tensor
+    scale: torch.Tensor
+    zero_point: torch.Tensor
+    axis: int = -1                         # -1: one scale for the tensor; otherwise the channel axis of `scale`
+
+    def dequantize(self) -> torch.Tensor:
+        if self.axis < 0:
+            return (self.q.float() - self.zero_point) * self.scale
+        shape = [1] * self.q.dim()
+        shape[self.axis] = -1
+        return (self.q.float() - self.zero_point.view(shape)) * self.scale.view(shape)
+
+
+def quantize_per_channel(x: torch.Tensor, axis: int = 0, bits: int = 8) -> QuantizedTensor:
+    """Symmetric quantisation with one scale per slice along ``axis``."""
+    qmax = 2 ** (bits - 1) - 1
+    dims = [d for d in range(x.dim()) if d != axis]
+    scale = x.abs().amax(dim=dims).clamp_min(1e-12) / qmax
+    shape = [1] * x.dim()
+    shape[axis] = -1
+    q = torch.round(x / scale.view(shape)).clamp(-qmax, qmax).to(torch.int8)
+    return QuantizedTensor(q, scale, torch.zeros_like(scale), axis)
+
+
+def fake_quantize_qdq(x: torch.Tensor, scale, zero_point=0.0, qmin: float = -128, qmax: float = 127) -> torch.Tensor:
+    """Quantise and dequantise in one go (no gradient treatment)."""
+    return (torch.clamp(torch.round(x / scale) + zero_point, qmin, qmax) - zero_point) * scale
+
+
+def fake_quantize_ste(x: torch.Tensor, scale, zero_point=0.0, qmin: float = -128, qmax: float = 127) -> torch.Tensor:
+    """The same values as :func:`fake_quantize_qdq`; the gradient passes unchanged inside the representable range and is zero
+    outside it (straight-through estimator)."""
+    return _FakeQuantSTE.apply(x, torch.as_tensor(scale, dtype=x.dtype), torch.as_tensor(zero_point, dtype=x.dtype), qmin, qmax)
+
+
+class _Observed(nn.Module):
+    """A layer with an observer on its input (what ``prepare`` puts in place of a Linear / Conv2d)."""
+
+    def __init__(self, layer: nn.Module, qconfig: QConfig):
+        super().__init__()
+        self.layer, self.qconfig = layer, qconfig
+        self.observer = MinMaxObserver(qconfig.bits, qconfig.symmetric, qconfig.momentum)
+
+    def forward(self, x):
+        return self.layer(self.observer(x))
+
+
+def prepare(model: nn.Module, qconfig: QConfig = None) -> nn.Module:
+    """Wrap every Linear / Conv2d so that calibration batches record the range of its input."""
+    qconfig = qconfig or default_qconfig()
+    for name, ch in list(model.named_children()):
+        if isinstance(ch, (nn.Linear, nn.Conv2d)):
+            setattr(model, name, _Observed(ch, qconfig))
+        elif not isinstance(ch, _Observed):
+            prepare(ch, qconfig)
+    return model
+
+
+@torch.no_grad()
+def calibrate(model: nn.Module, batches) -> int:
+    """Run the calibration batches through a prepared model; returns how many there were."""
+    model.eval()
+    n = 0
+    for b in batches:
+        model(*(b if isinstance(b, (tuple, list)) else (b,)))
+        n += 1
+    return n
+
+
+@_dataclass
+class QuantizationResult:
+    model: nn.Module
+    num_quantized: int
+    fp32_bytes: int
+    int8_bytes: int
+
+    @property
+    def compression(self) -> float:
+        return self.fp32_bytes / max(self.int8_bytes, 1)
+
+
+def _convert_prepared(model: nn.Module) -> int:
+    n = 0
+    for name, ch in list(model.named_children()):
+        if isinstance(ch, _Observed):
+            layer = ch.layer
+            q = QuantizedLinear.from_float(layer) if isinstance(layer, nn.Linear) else QuantizedConv2d(layer)
+            scale, zp = ch.observer.qparams()
+            q.register_buffer("input_scale", scale.detach().clone())          # the calibrated activation range travels with the layer
+            q.register_buffer("input_zero_point", zp.detach().clone())
+            setattr(model, name, q)
+            n += 1
+        else:
+            n += _convert_prepared(ch)
+    return n
+
+
+def quantize_model(model: nn.Module, calibration_batches=(), qconfig: QConfig = None) -> QuantizationResult:
+    """prepare -> calibrate -> convert: int8 weights per output channel, calibrated input ranges stored on the layers."""
+    fp32 = sum(p.numel() * p.element_size() for p in model.parameters())
+    prepare(model, qconfig)
+    calibrate(model, calibration_batches)
+    n = _convert_prepared(model)
+    small = sum(b.numel() * b.element_size() for b in model.buffers()) + sum(p.numel() * p.element_size() for p in model.parameters())
+    return QuantizationResult(model, n, fp32, small)
+
+
+# ----------------------------------------------------------------------------- 4-bit blocks under the reference's names (torch/quantization/quant4.h)
+@_dataclass
+class Int4Block:
+    """64 values as 32 packed bytes and one scale: ``value = (nibble - 8) / 7 * absmax``."""
+    packed: torch.Tensor
+    absmax: torch.Tensor
+
+
+@_dataclass
+class NF4Block:
+    """64 values as 32 packed bytes indexing the 16 NormalFloat levels, and one scale."""
+    packed: torch.Tensor
+    absmax: torch.Tensor
+
+
+def pack_nibble(lo: torch.Tensor, hi: torch.Tensor) -> torch.Tensor:
+    return (lo.to(torch.uint8) & 0xF) | ((hi.to(torch.uint8) & 0xF) << 4)
+
+
+def dequantize_int4(packed: torch.Tensor, absmax: torch.Tensor, shape, block: int = 64) -> torch.Tensor:
+    return dequantize_4bit(packed, absmax, shape, block, "int4")
+
+
+def dequantize_nf4(packed: torch.Tensor, absmax: torch.Tensor, shape, block: int = 64) -> torch.Tensor:
+    return dequantize_4bit(packed, absmax, shape, block, "nf4")

@@ -564,3 +564,61 @@ def test_ecosystem_shims_cover_the_reference_surface(tmp_path):
     assert vision.ConvBNReLU(3, 8, stride=2)(torch.rand(2, 3, 8, 8)).shape == (2, 8, 4, 4)
     with pytest.raises(ValueError):
         vision.load_image(str(tmp_path / "a.txt"))
+
+
+def test_reference_helper_names_of_quantization_data_amp_and_exporters(tmp_path):
+    # ---- post-training static quantisation
+    torch.manual_seed(0)
+    net = nn.Sequential(nn.Linear(16, 32), nn.ReLU(), nn.Sequential(nn.Linear(32, 8)))
+    x = torch.randn(64, 16)
+    want = net(x)
+    res = Q.quantize_model(net, [x[:32], x[32:]], Q.default_per_channel_qconfig())
+    assert res.num_quantized == 2 and res.compression > 2.5 and isinstance(res.model[0], nn.Module)
+    assert float((res.model(x) - want).abs().max()) < 0.1 and float(res.model[0].input_scale) > 0
+    prepared = Q.prepare(nn.Sequential(nn.Linear(4, 4)), Q.QConfig(bits=8, symmetric=False))
+    assert Q.calibrate(prepared, [torch.rand(5, 4)]) == 1 and float(prepared[0].observer.min_val) >= 0
+    w = torch.randn(6, 10)
+    qt = Q.quantize_per_channel(w, axis=0)
+    assert qt.q.dtype == torch.int8 and qt.scale.shape == (6,) and float((qt.dequantize() - w).abs().max()) <= float(qt.scale.max()) / 2 + 1e-6
+    assert Q.QuantizedTensor(torch.tensor([2, 4]), torch.tensor(0.5), torch.tensor(0.0)).dequantize().tolist() == [1.0, 2.0]
+    t = torch.linspace(-2, 2, 9, requires_grad=True)
+    y = Q.fake_quantize_ste(t, 0.01, 0.0, -128, 127)
+    assert torch.allclose(y, Q.fake_quantize_qdq(t.detach(), 0.01, 0.0, -128, 127))
+    y.sum().backward()
+    assert t.grad.tolist() == [0, 0, 1, 1, 1, 1, 1, 0, 0]                      # +-1.27 is the representable range
+    packed, absmax = Q.quantize_4bit(torch.randn(2, 64), 64, "int4")
+    assert torch.equal(Q.dequantize_int4(packed, absmax, (2, 64)), Q.dequantize_4bit(packed, absmax, (2, 64), 64, "int4"))
+    assert Q.pack_nibble(torch.tensor([3]), torch.tensor([10])).tolist() == [0xA3] and Q.Observer is Q.MinMaxObserver
+    assert Q.NF4Block(packed, absmax).absmax is absmax and Q.dequantize_nf4(*Q.quantize_4bit(torch.randn(64), 64, "nf4"), (64,)).shape == (64,)
+    # ---- data helpers
+    ds = data.TensorDataset(torch.arange(10.0).view(10, 1), torch.arange(10))
+    loader = data.make_loader(ds, data.DataLoaderOptions(batch_size=4, shuffle=True, drop_last=True, seed=3), collate_fn=data.DefaultCollate())
+    batches = list(loader)
+    assert len(batches) == 2 and isinstance(batches[0], data.Batch) and batches[0].data.shape == (4, 1) and batches[0].target.shape == (4,)
+    again = [b.target.tolist() for b in data.make_loader(ds, data.DataLoaderOptions(batch_size=4, shuffle=True, drop_last=True, seed=3), collate_fn=data.DefaultCollate())]
+    assert again == [b.target.tolist() for b in batches]
+    d0, t0 = batches[0].to("cpu")
+    assert d0.shape == (4, 1) and data.DefaultCollate()([data.Example(torch.ones(2), torch.tensor(1))]).target.tolist() == [1]
+    tf = data.Compose([data.Lambda(lambda v: v * 2), data.Normalize([1.0, 2.0], [2.0, 4.0]), data.Flatten()])
+    assert tf(torch.ones(2, 3)).tolist() == [0.5, 0.5, 0.5, 0.0, 0.0, 0.0]
+    assert list(data.make_batch_sampler(data.make_sequential_sampler(ds), 4)) == [[0, 1, 2, 3], [4, 5, 6, 7], [8, 9]]
+    assert sorted(data.make_random_sampler(ds, seed=1)) == list(range(10))
+    # ---- amp state
+    assert amp.get_autocast_category("matmul") == amp.CastPolicy.LOWER_PRECISION and amp.policy_for("softmax") == amp.CastPolicy.FP32
+    amp.set_autocast_cpu_dtype(torch.bfloat16)
+    amp.set_autocast_cpu_enabled(True)
+    try:
+        assert amp.is_autocast_cpu_enabled() and torch.mm(torch.ones(2, 2), torch.ones(2, 2)).dtype == torch.bfloat16
+    finally:
+        amp.set_autocast_cpu_enabled(False)
+    assert not amp.is_autocast_cpu_enabled() and amp.has_tensor_cores() in (True, False)
+    assert amp.autocast_matmul(torch.ones(2, 2), torch.ones(2, 2)).dtype == torch.bfloat16 and amp.autocast_softmax(torch.ones(3).half()).dtype == torch.float32
+    s1 = amp.make_grad_scaler(amp.GradScalerOptions(init_scale=8.0, growth_interval=1))
+    assert s1.get_scale() == 8.0 and not amp.make_disabled_scaler().enabled
+    # ---- exporter and jit names
+    mlp = nn.Sequential(nn.Linear(4, 3), nn.ReLU(), nn.Linear(3, 2))
+    assert os.path.getsize(onnx.export_model(mlp, (1, 4), str(tmp_path / "m.onnx"))) > 50
+    assert "func.func" in mlir.export_mlir(mlp, (1, 4)) and mobile.MobileExecutor is mobile.Executor
+    mobile.export_model(mlp, str(tmp_path / "m.ptmb"))
+    assert torch.allclose(mobile.MobileExecutor(str(tmp_path / "m.ptmb")).run(torch.ones(1, 4)), mlp(torch.ones(1, 4)), atol=1e-6)
+    assert jit.CompiledFn is jit.CompiledModule and jit.tracing_active() is False
