@@ -17,11 +17,12 @@ from .process_group import (BackendType, CollectiveTimeout, CountingPG, FileBack
                             SingleProcessGroup, TorchProcessGroup, make_shared_memory_groups)
 from .ddp import DDPNoSyncGuard, DistributedDataParallel, PeerChannel
 from .checkpoint import load_sharded, save_sharded  # noqa: F401
-from .fsdp import (FSDPConfig, FullyShardedDataParallel, OffloadOptimizer, ShardingStrategy, ZeROOptimizer, ZeROStage3,
+from .fsdp import (FSDPConfig, FullyShardedDataParallel, OffloadOptimizer, OffloadStateBag, ShardingStrategy, ZeROOptimizer, ZeROStage3,
                    ZeROStage3Config)
 from .launcher import DistArgs, launch, parse_dist_args
 from .watchdog import DictStore, Heartbeat, RankFailure
 from .local_sgd import LocalSGD  # noqa: F401
+from .process_group import TorchProcessGroup as NCCLBackend  # noqa: F401  (the reference's name for the NCCL-backed group)
 
 _current_pg: Optional[ProcessGroup] = None
 
@@ -206,3 +207,19 @@ def __getattr__(name):
         from ..nn.parallel import pipeline as _p
         return getattr(_p, name)
     raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
+
+
+@_dataclass
+class DistributedContext:
+    """Rank, world size and process group in one object (what the reference threads through its distributed helpers)."""
+    rank: int = 0
+    world_size: int = 1
+    process_group: object = None
+
+    @classmethod
+    def current(cls) -> "DistributedContext":
+        return cls(get_rank(), get_world_size(), _pg()) if is_initialized() else cls()
+
+    @property
+    def is_main(self) -> bool:
+        return self.rank == 0

@@ -206,6 +206,10 @@ class ZeROStage3:
             torch.cuda.current_stream().wait_stream(self._stream)
 
 
+class OffloadStateBag(dict):
+    """The host-side state of one offloaded parameter: fp32 master copy plus whatever the inner optimizer keeps for it."""
+
+
 class OffloadOptimizer:
     """Keeps optimizer state (and fp32 master copies) in pinned host memory; each step moves gradients to
     the host, steps there and copies parameters back (torch/distributed/deepspeed_offload.h:53-176)."""
@@ -230,6 +234,10 @@ class OffloadOptimizer:
             d.grad = None
         for h in self.host_params:
             h.grad = None
+
+    def state_bags(self):
+        """One :class:`OffloadStateBag` per parameter: ``master`` (the fp32 host copy) plus the inner optimizer's state tensors."""
+        return [OffloadStateBag(master=h.detach(), **{k: v for k, v in self.inner.state.get(h, {}).items()}) for h in self.host_params]
 
     def state_dict(self):
         return self.inner.state_dict()

@@ -157,3 +157,91 @@ def speculative_generate(target, draft, prompt, max_new_tokens: int = 64, k: int
             draft.forward_decode(prop[-1], n_ctx + k)
         n_ctx += a + 1
     return out[:max_new_tokens], stats
+
+
+# ---------------------------------------------------------------------------------------------- n-gram draft and statistics
+from dataclasses import dataclass as _dataclass  # noqa: E402
+from typing import Dict as _Dict, List as _List, Sequence as _Sequence, Tuple as _Tuple  # noqa: E402
+
+
+@_dataclass
+class SpecStats:
+    """Counters of a speculative run (torch/io/speculative_decode.h): proposals made, proposals the target agreed with, and
+    target passes taken."""
+    proposed: int = 0
+    accepted: int = 0
+    target_passes: int = 0
+
+    @property
+    def acceptance_rate(self) -> float:
+        return self.accepted / self.proposed if self.proposed else 0.0
+
+    def tokens_per_pass(self, generated: int) -> float:
+        return generated / self.target_passes if self.target_passes else 0.0
+
+
+class NgramDraft:
+    """A draft "model" that needs no weights: it proposes the ids that followed the most recent earlier occurrence of the
+    last ``n`` ids (longest n first) in the sequence so far.  The index is kept incrementally, so a proposal costs a few
+    dictionary look-ups (torch/io/speculative_draft.h; the batching engine uses the same scheme, serve/llm.py)."""
+
+    def __init__(self, max_n: int = 3, min_n: int = 1):
+        self.max_n, self.min_n = max_n, min_n
+        self.hist: _List[int] = []
+        self.index: _Dict[_Tuple[int, ...], int] = {}
+        self.done = 0
+
+    def reset(self, history: _Sequence[int] = ()):
+        self.hist, self.index, self.done = list(history), {}, 0
+
+    def append(self, token: int):
+        self.hist.append(int(token))
+
+    def _update(self):
+        L = len(self.hist)
+        for q in range(self.done, L - 1):                        # n-grams that end before the last id
+            for n in range(self.min_n, self.max_n + 1):
+                if q + 1 - n >= 0:
+                    self.index[tuple(self.hist[q + 1 - n:q + 1])] = q + 1
+        self.done = max(self.done, L - 1)
+
+    def propose(self, k: int) -> _List[int]:
+        """Up to ``k`` ids that followed the latest earlier match of the current suffix; empty when nothing matches."""
+        self._update()
+        L = len(self.hist)
+        for n in range(min(self.max_n, L), self.min_n - 1, -1):
+            at = self.index.get(tuple(self.hist[L - n:]))
+            if at is not None:
+                return self.hist[at:at + k]
+        return []
+
+
+class SlidingWindowAttention:
+    """Decode attention over the last ``window`` positions plus one summary position per KV head: the running mean of the
+    keys and of the values that left the window (a lossy approximation for long contexts, torch/io/sliding_window_attn.h).
+    ``window = 0`` is full attention.  One instance per layer; ``step(q, k, v)`` takes the new token's ``q [H, D]``,
+    ``k [Hk, D]``, ``v [Hk, D]`` and returns the attention output ``[H, D]``."""
+
+    def __init__(self, n_heads: int, n_kv_heads: int, head_dim: int, window: int = 512):
+        self.H, self.Hk, self.D, self.window = n_heads, n_kv_heads, head_dim, window
+        self.k: _List[torch.Tensor] = []
+        self.v: _List[torch.Tensor] = []
+        self.k_summary = torch.zeros(n_kv_heads, head_dim)
+        self.v_summary = torch.zeros(n_kv_heads, head_dim)
+        self.n_summarized = 0
+
+    def step(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+        self.k.append(k.float())
+        self.v.append(v.float())
+        if self.window and len(self.k) > self.window:            # the oldest position moves into the running means
+            ko, vo = self.k.pop(0), self.v.pop(0)
+            self.n_summarized += 1
+            self.k_summary += (ko - self.k_summary) / self.n_summarized
+            self.v_summary += (vo - self.v_summary) / self.n_summarized
+        K, V = torch.stack(self.k, 1), torch.stack(self.v, 1)    # [Hk, T, D]
+        if self.n_summarized:
+            K, V = torch.cat([self.k_summary[:, None], K], 1), torch.cat([self.v_summary[:, None], V], 1)
+        g = self.H // self.Hk
+        qh = q.float().view(self.Hk, g, self.D)
+        s = torch.einsum("kgd,ktd->kgt", qh, K) / self.D ** 0.5
+        return torch.einsum("kgt,ktd->kgd", torch.softmax(s, -1), V).reshape(self.H, self.D).to(q.dtype)

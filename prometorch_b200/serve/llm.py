@@ -840,3 +840,27 @@ class EngineServer:
                 if h is not None:
                     h.response = r
                     h.event.set()
+
+
+# the reference's class names for the same things (torch/serve/llm.h)
+KVCache = PagedKVCache
+LlamaLayerWeights = Dict[str, torch.Tensor]          # one layer of LlamaWeights.layers: attn_norm, wqkv, wo, ffn_norm, w_gate_up, w_down
+
+
+class ByteBPETokenizer:
+    """Byte-level BPE from ``vocab.json`` + ``merges.txt`` or ``tokenizer.json`` of a checkpoint directory; falls back to one id
+    per byte when the directory has neither."""
+
+    def __init__(self, model_dir: str = None):
+        self.inner = load_hf_tokenizer(model_dir) if model_dir else None
+        self.fallback = ByteTokenizer()
+
+    @property
+    def vocab_size(self) -> int:
+        return self.inner.vocab_size if self.inner is not None else 259
+
+    def encode(self, text: str) -> List[int]:
+        return self.inner.encode(text) if self.inner is not None else self.fallback.encode(text)
+
+    def decode(self, ids) -> str:
+        return self.inner.decode(list(ids)) if self.inner is not None else self.fallback.decode(ids)

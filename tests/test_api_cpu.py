@@ -622,3 +622,47 @@ def test_reference_helper_names_of_quantization_data_amp_and_exporters(tmp_path)
     mobile.export_model(mlp, str(tmp_path / "m.ptmb"))
     assert torch.allclose(mobile.MobileExecutor(str(tmp_path / "m.ptmb")).run(torch.ones(1, 4)), mlp(torch.ones(1, 4)), atol=1e-6)
     assert jit.CompiledFn is jit.CompiledModule and jit.tracing_active() is False
+
+
+def test_draft_statistics_sliding_window_and_remaining_reference_names(tmp_path):
+    from prometorch_b200 import distributed as D, io
+    from prometorch_b200.serve import llm
+    # n-gram draft: proposes what followed the latest earlier occurrence of the current suffix
+    d = io.NgramDraft(max_n=3)
+    d.reset([1, 2, 3, 4, 5, 1, 2, 3])
+    assert d.propose(3) == [4, 5, 1]
+    d.append(4)
+    assert d.propose(2) == [5, 1]
+    d.reset([7, 8, 9])
+    assert d.propose(4) == []
+    st = io.SpecStats(proposed=8, accepted=6, target_passes=4)
+    assert st.acceptance_rate == 0.75 and st.tokens_per_pass(10) == 2.5 and io.SpecStats().acceptance_rate == 0.0
+    # sliding window: exact while everything fits, exact again when the window covers what matters, summary otherwise
+    torch.manual_seed(0)
+    H, Hk, Dh, T = 4, 2, 8, 12
+    qs, ks, vs = torch.randn(T, H, Dh), torch.randn(T, Hk, Dh), torch.randn(T, Hk, Dh)
+
+    def full(t):
+        K, V = ks[:t + 1].transpose(0, 1), vs[:t + 1].transpose(0, 1)
+        s = torch.einsum("kgd,ktd->kgt", qs[t].view(Hk, H // Hk, Dh), K) / Dh ** 0.5
+        return torch.einsum("kgt,ktd->kgd", torch.softmax(s, -1), V).reshape(H, Dh)
+    exact, windowed = io.SlidingWindowAttention(H, Hk, Dh, window=0), io.SlidingWindowAttention(H, Hk, Dh, window=5)
+    for t in range(T):
+        a, b = exact.step(qs[t], ks[t], vs[t]), windowed.step(qs[t], ks[t], vs[t])
+        assert torch.allclose(a, full(t), atol=1e-5)
+        if t < 5:
+            assert torch.allclose(b, a, atol=1e-5)
+    assert windowed.n_summarized == T - 5 and len(windowed.k) == 5 and torch.allclose(windowed.k_summary, ks[:T - 5].mean(0), atol=1e-5)
+    assert float((b - a).abs().max()) < 2.0                       # an approximation, but of the same scale
+    # names
+    assert io.GGUFTPConfig(1, 4).kwargs() == {"tp_rank": 1, "tp_world": 4} and io.InferenceProfiler is not None and io.LowRankOutputProj is not None
+    assert io.GGUFTensorInfo is not None and io.QuantizedWeight is io.PackedWeight
+    ctx = D.DistributedContext.current()
+    assert ctx.rank == 0 and ctx.world_size == 1 and ctx.is_main and D.NCCLBackend is not None
+    p = nn.Parameter(torch.ones(3))
+    off = D.OffloadOptimizer([p], torch.optim.SGD, lr=0.1, momentum=0.9)
+    p.grad = torch.ones(3)
+    off.step()
+    bag = off.state_bags()[0]
+    assert isinstance(bag, D.OffloadStateBag) and torch.allclose(bag["master"], torch.full((3,), 0.9)) and "momentum_buffer" in bag
+    assert llm.KVCache is llm.PagedKVCache and llm.ByteBPETokenizer().decode(llm.ByteBPETokenizer().encode("hé")) .endswith("hé")
