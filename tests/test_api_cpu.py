@@ -666,3 +666,30 @@ def test_draft_statistics_sliding_window_and_remaining_reference_names(tmp_path)
     bag = off.state_bags()[0]
     assert isinstance(bag, D.OffloadStateBag) and torch.allclose(bag["master"], torch.full((3,), 0.9)) and "momentum_buffer" in bag
     assert llm.KVCache is llm.PagedKVCache and llm.ByteBPETokenizer().decode(llm.ByteBPETokenizer().encode("hé")) .endswith("hé")
+
+
+def test_promepile_names_train_and_decode_steps():
+    torch.manual_seed(0)
+    net = nn.Sequential(nn.Linear(8, 16), nn.Tanh(), nn.Linear(16, 1))
+    x, y = torch.randn(64, 8), torch.randn(64, 1)
+    step = jit.promepile_train(net, pt.optim.Adam(net.parameters(), lr=1e-2), nn.functional.mse_loss, max_grad_norm=1.0)
+    losses = [float(step(x, target=y)) for _ in range(40)]
+    assert step.steps == 40 and losses[-1] < 0.5 * losses[0] and isinstance(step, jit.CompiledTrainingStep)
+    scaled = jit.promepile_train(net, pt.optim.SGD(net.parameters(), lr=1e-2), nn.functional.mse_loss, scaler=amp.GradScaler(init_scale=4.0))
+    before = float(nn.functional.mse_loss(net(x), y))
+    scaled(x, target=y)
+    assert float(nn.functional.mse_loss(net(x), y)) < before
+    fwd = jit.promepile(net)
+    assert isinstance(fwd, jit.CompiledForward) and torch.allclose(fwd(x), net(x))
+
+    class FakeModel:
+        captured = 0
+
+        def capture(self):
+            self.captured += 1
+
+        def forward_decode(self, token, pos):
+            return token + pos
+    m = FakeModel()
+    dec = jit.CompiledDecodeStep(m)
+    assert m.captured == 1 and dec(5, 7) == 12
