@@ -21,6 +21,7 @@
 #include "checkpoint.h"
 #include "data.h"
 #include "distributed.h"
+#include "ecosystem.h"
 #include "fsdp.h"
 #include "hooks.h"
 #include "lr_scheduler.h"

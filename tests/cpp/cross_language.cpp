@@ -130,8 +130,68 @@ static int llama(const std::string& dir, const std::string& out_path) {
     return 0;
 }
 
+// vision / text / audio helpers on inputs the Python test wrote into DIR; results as "E:name v v v ..." lines and files.
+static void line(const char* name, const pt::Tensor& t) {
+    std::printf("E:%s", name);
+    auto f = t.reshape(-1).to(pt::kDouble);
+    for (int64_t i = 0; i < f.numel(); ++i) std::printf(" %.9g", f[i].item<double>());
+    std::printf("\n");
+}
+static int ecosystem(const std::string& dir) {
+    namespace V = pt::vision;
+    namespace T = pt::text;
+    namespace A = pt::audio;
+    auto img = V::load_pnm(dir + "/py.ppm");
+    line("ppm_shape", pt::tensor({img.size(0), img.size(1), img.size(2)}));
+    line("ppm_sum", img.sum());
+    line("pgm_ascii", V::load_pnm(dir + "/ascii.pgm"));
+    V::save_pnm(dir + "/cpp.ppm", img);
+    auto tf = V::transforms::Compose({V::transforms::Resize(6, 8), V::transforms::CenterCrop(4), V::transforms::Normalize({0.5, 0.4, 0.3}, {0.2, 0.3, 0.4})});
+    line("transformed", tf(img));
+    line("random_crop_shape", pt::tensor({V::transforms::RandomCrop(3, 2, 1)(img).size(1), V::transforms::RandomCrop(3, 2, 1)(img).size(2)}));
+    line("flip", V::transforms::RandomHorizontalFlip(1.0)(img).slice(0, 0, 1).slice(1, 0, 1));
+    V::ImageFolder folder(dir + "/set", V::transforms::Resize(8));
+    line("folder", pt::tensor({(int64_t)folder.size(), (int64_t)folder.classes.size(), folder.get(folder.size() - 1).second, folder.get(0).first.size(1)}));
+    std::printf("E:classes %s %s\n", folder.classes[0].c_str(), folder.classes[1].c_str());
+    // text
+    auto vocab = T::Vocab::build({"the cat sat", "the dog sat down", "a cat"}, 1);
+    line("vocab_encode", pt::tensor(vocab.encode("the cat flew down")));
+    std::printf("E:vocab_decode %s\n", vocab.decode({2, 4, 3}).c_str());
+    std::printf("E:basic");
+    for (const auto& t : T::BasicTokenizer().tokenize("Hello, World! it's")) std::printf(" %s", t.c_str());
+    std::printf("\n");
+    T::CharTokenizer ct("hello world");
+    line("char", pt::tensor(ct.encode("held z")));
+    T::WordPieceTokenizer wp({"[UNK]", "un", "##aff", "##able", "play", "##ing", "##ed"});
+    line("wordpiece", pt::tensor(wp.encode("unaffable playing xyz played")));
+    std::vector<std::vector<int64_t>> batch{{1, 2, 3}, {4}, {5, 6}};
+    line("pad", T::pad_sequence(batch, 9, true, 2));
+    line("pad_tb", T::pad_sequence(batch, 0, false));
+    line("lengths", T::sequence_lengths(batch));
+    line("mask", T::padding_mask(batch).to(pt::kLong));
+    // audio
+    auto t = pt::linspace(0, 1, 16000);
+    auto x = pt::sin(2 * M_PI * 440 * t);
+    auto spec = A::spectrogram(x, 400, 160);
+    line("spec_shape", pt::tensor({spec.size(0), spec.size(1)}));
+    line("spec_peak", spec.mean(1).argmax());
+    line("spec_probe", spec.slice(0, 9, 13).slice(1, 10, 12));
+    line("fbanks_sum", A::melscale_fbanks(201, 40, 16000).sum(0));
+    line("mfcc_probe", A::mfcc(x).slice(0, 0, 4).slice(1, 5, 7));
+    auto q = A::mu_law_encoding(x.slice(0, 0, 64));
+    line("mulaw", q);
+    line("mulaw_back", A::mu_law_decoding(q));
+    line("db", A::amplitude_to_db(spec.slice(0, 9, 13).slice(1, 10, 12), 10.0, 1e-10, 0.0, 20.0));
+    line("resample", A::resample(x.slice(0, 0, 100), 16000, 8000));
+    auto wav = A::load_wav(dir + "/py.wav");
+    line("wav", pt::tensor({(double)wav.second, (double)wav.first.numel(), wav.first.abs().max().item<double>()}));
+    A::save_wav(dir + "/cpp.wav", x.slice(0, 0, 800), 8000);
+    return 0;
+}
+
 int main(int argc, char** argv) {
     using namespace pt::optim;
+    if (argc > 2 && std::string(argv[1]) == "ecosystem") return ecosystem(argv[2]);
     if (argc > 2 && std::string(argv[1]) == "io") return checkpoints(argv[2]);
     if (argc > 3 && std::string(argv[1]) == "llama") return llama(argv[2], argv[3]);
     schedulers();

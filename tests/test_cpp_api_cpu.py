@@ -136,6 +136,69 @@ def _check_llama(exe, tmp_path):
     assert set(back) == set(sd) and all(torch.equal(back[k], sd[k]) for k in sd)
 
 
+def _check_ecosystem(exe, tmp_path):
+    """ecosystem.h (vision / text / audio over libtorch) against the Python modules of the same names on the same inputs."""
+    import math
+    from prometorch_b200 import audio, text, vision
+    from prometorch_b200.vision import transforms as VT
+    d = tmp_path / "eco"
+    (d / "set" / "cats").mkdir(parents=True)
+    (d / "set" / "dogs").mkdir()
+    g = torch.Generator().manual_seed(2)
+    img = torch.rand(3, 5, 7, generator=g)
+    vision.save_pnm(str(d / "py.ppm"), img)
+    (d / "ascii.pgm").write_bytes(b"P2\n# note\n3 2\n15\n0 5 10\n15 1 2\n")
+    for cls in ("cats", "dogs"):
+        for i in range(2):
+            vision.save_pnm(str(d / "set" / cls / f"{i}.pgm"), torch.rand(1, 4, 4, generator=g))
+    t = torch.linspace(0, 1, 16000)
+    x = torch.sin(2 * math.pi * 440 * t)
+    audio.save_wav(str(d / "py.wav"), x[:1600], 16000)
+    r = subprocess.run([exe, "ecosystem", str(d)], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-1000:] + r.stderr[-2000:]
+    raw = {ln.split()[0][2:]: ln.split()[1:] for ln in r.stdout.splitlines() if ln.startswith("E:")}
+    num = lambda k: torch.tensor([float(v) for v in raw[k]], dtype=torch.float64)           # noqa: E731
+
+    def same(key, want, tol=1e-5):
+        w = torch.as_tensor(want).double().reshape(-1)
+        assert num(key).shape == w.shape and torch.allclose(num(key), w, atol=tol, rtol=tol), (key, num(key)[:6], w[:6])
+    loaded = vision.load_pnm(str(d / "py.ppm"))
+    same("ppm_shape", [3, 5, 7])
+    same("ppm_sum", loaded.sum())
+    same("pgm_ascii", vision.load_pnm(str(d / "ascii.pgm")))
+    assert torch.equal(vision.load_pnm(str(d / "cpp.ppm")), loaded)
+    same("transformed", VT.Compose([VT.Resize((6, 8)), VT.CenterCrop(4), VT.Normalize([0.5, 0.4, 0.3], [0.2, 0.3, 0.4])])(loaded))
+    same("random_crop_shape", [3, 2])
+    same("flip", loaded.flip(-1)[:1, :1])
+    same("folder", [4, 2, 1, 8])
+    assert raw["classes"] == ["cats", "dogs"]
+    vocab = text.Vocab.build(["the cat sat", "the dog sat down", "a cat"], 1)
+    same("vocab_encode", vocab.encode("the cat flew down"))
+    assert " ".join(raw["vocab_decode"]) == vocab.decode([2, 4, 3]) and raw["basic"] == text.BasicTokenizer().tokenize("Hello, World! it's")
+    same("char", text.CharTokenizer("hello world").encode("held z"))
+    same("wordpiece", text.WordPieceTokenizer(["[UNK]", "un", "##aff", "##able", "play", "##ing", "##ed"]).encode("unaffable playing xyz played"))
+    batch = [[1, 2, 3], [4], [5, 6]]
+    same("pad", text.pad_sequence(batch, 9, True, 2))
+    same("pad_tb", text.pad_sequence(batch, 0, False))
+    same("lengths", text.sequence_lengths(batch))
+    same("mask", text.padding_mask(batch).long())
+    spec = audio.spectrogram(x, 400, 160)
+    same("spec_shape", list(spec.shape))
+    same("spec_peak", spec.mean(1).argmax())
+    same("spec_probe", spec[9:13, 10:12], 1e-3)
+    same("fbanks_sum", audio.melscale_fbanks(201, 40, 16000).sum(0), 1e-4)
+    same("mfcc_probe", audio.mfcc(x)[:4, 5:7], 2e-3)
+    q = audio.mu_law_encoding(x[:64])
+    same("mulaw", q)
+    same("mulaw_back", audio.mu_law_decoding(q))
+    same("db", audio.amplitude_to_db(spec[9:13, 10:12], 10.0, 1e-10, 0.0, 20.0), 1e-3)
+    same("resample", audio.resample(x[:100], 16000, 8000))
+    wav, sr = audio.load_wav(str(d / "py.wav"))
+    same("wav", [sr, wav.numel(), wav.abs().max()])
+    back, sr2 = audio.load_wav(str(d / "cpp.wav"))
+    assert sr2 == 8000 and back.numel() == 800 and float((back - x[:800]).abs().max()) < 1e-3
+
+
 def _check_schedulers(sched):
     """The learning-rate sequences of the C++ schedulers against the Python ones (same constructor arguments)."""
     from prometorch_b200 import optim as O
@@ -189,6 +252,7 @@ def test_cpp_and_python_implementations_agree(tmp_path):
     assert r.returncode == 0, r.stderr[-2000:]
     _check_checkpoints(exe, tmp_path)
     _check_llama(exe, tmp_path)
+    _check_ecosystem(exe, tmp_path)
     lines = [ln for ln in r.stdout.splitlines() if ln.strip()]
     got = {ln.split()[0]: [float(v) for v in ln.split()[1:]] for ln in lines if not ln.startswith("S:")}
     sched = {ln.split()[0][2:]: [float(v) for v in ln.split()[1:]] for ln in lines if ln.startswith("S:")}
