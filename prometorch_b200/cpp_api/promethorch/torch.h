@@ -22,6 +22,7 @@
 #include "data.h"
 #include "distributed.h"
 #include "ecosystem.h"
+#include "export.h"
 #include "fsdp.h"
 #include "hooks.h"
 #include "lr_scheduler.h"

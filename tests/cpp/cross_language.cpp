@@ -189,8 +189,29 @@ static int ecosystem(const std::string& dir) {
     return 0;
 }
 
+// The exporters: a Sequential built from the weights Python saved in DIR/mlp.ptor, written as ONNX, MLIR and PTMB; the PTMB
+// file Python wrote is run by the C++ executor.
+static int exporters(const std::string& dir) {
+    auto sd = pt::load_state_dict(dir + "/mlp.ptor");
+    // (libtorch cannot nest a Sequential in a Sequential; the Python model nests one, the op order is the same)
+    pt::nn::Sequential seq(pt::nn::Linear(6, 5), pt::nn::ReLU(), pt::nn::Linear(5, 4), pt::nn::Tanh(), pt::nn::Linear(pt::nn::LinearOptions(4, 3).bias(false)), pt::nn::Softmax(-1));
+    pt::NoGradGuard ng;
+    auto params = seq->parameters();
+    if (params.size() != sd.size()) { std::printf("FAIL %zu parameters against %zu tensors\n", params.size(), sd.size()); return 1; }
+    for (size_t i = 0; i < params.size(); ++i) params[i].copy_(sd[i].second);
+    pt::onnx::export_model(*seq, {2, 6}, dir + "/cpp.onnx");
+    pt::mlir::export_mlir(*seq, {2, 6}, dir + "/cpp.mlir");
+    pt::mobile::export_model(*seq, dir + "/cpp.ptmb");
+    pt::mobile::MobileExecutor exec(dir + "/py.ptmb");
+    auto x = pt::arange(12, pt::kFloat).reshape({2, 6}) / 10.0;
+    line("mobile", exec.run(x));
+    line("direct", seq->forward(x));
+    return 0;
+}
+
 int main(int argc, char** argv) {
     using namespace pt::optim;
+    if (argc > 2 && std::string(argv[1]) == "export") return exporters(argv[2]);
     if (argc > 2 && std::string(argv[1]) == "ecosystem") return ecosystem(argv[2]);
     if (argc > 2 && std::string(argv[1]) == "io") return checkpoints(argv[2]);
     if (argc > 3 && std::string(argv[1]) == "llama") return llama(argv[2], argv[3]);

@@ -199,6 +199,31 @@ def _check_ecosystem(exe, tmp_path):
     assert sr2 == 8000 and back.numel() == 800 and float((back - x[:800]).abs().max()) < 1e-3
 
 
+def _check_exporters(exe, tmp_path):
+    """export.h: ONNX, MLIR and PTMB files written by C++ are byte-identical to the Python exporters' for the same model, and
+    the C++ executor runs the file Python wrote."""
+    import torch.nn as nn
+    from prometorch_b200 import mlir, mobile, onnx
+    from prometorch_b200 import serialization as S
+    torch.manual_seed(12)
+    net = nn.Sequential(nn.Linear(6, 5), nn.ReLU(), nn.Sequential(nn.Linear(5, 4), nn.Tanh()), nn.Linear(4, 3, bias=False), nn.Softmax(-1))
+    d = tmp_path / "export"
+    d.mkdir()
+    S.save_state_dict(dict(net.state_dict()), str(d / "mlp.ptor"))
+    onnx.export_mlp(net, [2, 6], str(d / "py.onnx"))
+    mlir.export(net, [2, 6], str(d / "py.mlir"))
+    mobile.save(net, str(d / "py.ptmb"))
+    r = subprocess.run([exe, "export", str(d)], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-1000:] + r.stderr[-2000:]
+    for kind in ("onnx", "mlir", "ptmb"):
+        assert (d / f"cpp.{kind}").read_bytes() == (d / f"py.{kind}").read_bytes(), kind
+    raw = {ln.split()[0][2:]: torch.tensor([float(v) for v in ln.split()[1:]]) for ln in r.stdout.splitlines() if ln.startswith("E:")}
+    x = torch.arange(12.0).reshape(2, 6) / 10.0
+    want = net(x).detach().reshape(-1)
+    assert torch.allclose(raw["mobile"], want, atol=1e-6) and torch.allclose(raw["direct"], want, atol=1e-6)
+    assert torch.allclose(mobile.Executor(str(d / "cpp.ptmb")).run(x).reshape(-1), want, atol=1e-6)
+
+
 def _check_schedulers(sched):
     """The learning-rate sequences of the C++ schedulers against the Python ones (same constructor arguments)."""
     from prometorch_b200 import optim as O
@@ -253,6 +278,7 @@ def test_cpp_and_python_implementations_agree(tmp_path):
     _check_checkpoints(exe, tmp_path)
     _check_llama(exe, tmp_path)
     _check_ecosystem(exe, tmp_path)
+    _check_exporters(exe, tmp_path)
     lines = [ln for ln in r.stdout.splitlines() if ln.strip()]
     got = {ln.split()[0]: [float(v) for v in ln.split()[1:]] for ln in lines if not ln.startswith("S:")}
     sched = {ln.split()[0][2:]: [float(v) for v in ln.split()[1:]] for ln in lines if ln.startswith("S:")}
