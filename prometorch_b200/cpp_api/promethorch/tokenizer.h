@@ -82,12 +82,23 @@ inline std::string sanitize(const std::string& s) {
 class GGUFTokenizer {
  public:
     enum CharClass { Space, Letter, Number, Other };
+    // Which split pattern the vocabulary was trained with (tokenizer.ggml.pre): GPT-2's, the qwen2 one (single digits, one leading
+    // symbol joins a word, newlines close a run) or the llama-3 one (digits in groups of up to three).
+    enum PreStyle { GPT2, Qwen2, Llama3 };
+    static PreStyle style_of(std::string pre) {
+        for (auto& c : pre) c = (char)std::tolower((unsigned char)c);
+        for (const char* n : {"qwen2", "qwen", "deepseek-r1-qwen", "qwen3"})
+            if (pre == n) return Qwen2;
+        for (const char* n : {"llama3", "llama-bpe", "llama-v3", "llama4", "smaug-bpe"})
+            if (pre == n) return Llama3;
+        return GPT2;
+    }
 
     GGUFTokenizer() = default;
     GGUFTokenizer(std::vector<std::string> tokens, std::string model = "llama", std::vector<float> scores = {}, const std::vector<std::string>& merges = {},
-                  std::vector<int> token_types = {}, int bos_id = -1, int eos_id = -1, bool add_bos = false)
+                  std::vector<int> token_types = {}, int bos_id = -1, int eos_id = -1, bool add_bos = false, const std::string& pre = "")
         : tokens_(std::move(tokens)), model_(std::move(model)), scores_(std::move(scores)), types_(std::move(token_types)), bos_id_(bos_id),
-          eos_id_(eos_id), add_bos_(add_bos) {
+          eos_id_(eos_id), add_bos_(add_bos), style_(style_of(pre)) {
         if (scores_.size() != tokens_.size()) scores_.assign(tokens_.size(), 0.0f);
         if (types_.size() != tokens_.size()) types_.assign(tokens_.size(), 1);
         for (size_t i = 0; i < tokens_.size(); ++i) vocab_[tokens_[i]] = (int)i;        // a repeated entry keeps its last id
@@ -125,7 +136,8 @@ class GGUFTokenizer {
         auto geti = [&](const char* k) { return r.has(k) ? (int)r.get(k).as_int() : -1; };
         const bool add_bos = r.has("tokenizer.ggml.add_bos_token") && r.get("tokenizer.ggml.add_bos_token").b;
         return GGUFTokenizer(std::move(tokens), r.has("tokenizer.ggml.model") ? r.get("tokenizer.ggml.model").s : "llama", std::move(scores), merges,
-                             std::move(types), geti("tokenizer.ggml.bos_token_id"), geti("tokenizer.ggml.eos_token_id"), add_bos);
+                             std::move(types), geti("tokenizer.ggml.bos_token_id"), geti("tokenizer.ggml.eos_token_id"), add_bos,
+                             r.has("tokenizer.ggml.pre") ? r.get("tokenizer.ggml.pre").s : "");
     }
 
     int vocab_size() const { return (int)tokens_.size(); }
@@ -235,6 +247,77 @@ class GGUFTokenizer {
         for (const auto& r : other)
             if (c >= r[0] && c <= r[1]) return Other;
         return Letter;
+    }
+
+    // The pieces of the newer patterns (qwen2, llama-3):
+    //   contraction (either case) | one optional char that is no CR / LF / letter / number, then letters+ | one number (qwen2) or
+    //   up to three (llama-3) | optional space, others+, then CR / LF* | spaces* ending in CR / LF+ | spaces+(?!non-space) | spaces+
+    static std::vector<std::string> pieces(const std::string& text, PreStyle style) {
+        if (style == GPT2) return gpt2_pieces(text);
+        struct Cp { size_t at; uint32_t c; CharClass k; };
+        std::vector<Cp> cps;
+        for (size_t i = 0; i < text.size();) {
+            int len;
+            const uint32_t c = utf8::next(text, i, len);
+            cps.push_back({i, c, classify(c)});
+            i += (size_t)len;
+        }
+        const size_t n = cps.size();
+        std::vector<std::string> out;
+        auto cut = [&](size_t a, size_t b) { out.push_back(text.substr(cps[a].at, (b < n ? cps[b].at : text.size()) - cps[a].at)); };
+        auto lower = [](uint32_t c) { return c >= 'A' && c <= 'Z' ? c + 32 : c; };
+        auto newline = [&](size_t i) { return cps[i].c == '\r' || cps[i].c == '\n'; };
+        size_t i = 0;
+        while (i < n) {
+            if (cps[i].c == '\'' && i + 1 < n) {                           // contractions, either case
+                const uint32_t a = lower(cps[i + 1].c), b = i + 2 < n ? lower(cps[i + 2].c) : 0;
+                size_t take = 0;
+                if (a == 's' || a == 't' || a == 'm' || a == 'd') take = 2;
+                if ((a == 'r' && b == 'e') || (a == 'v' && b == 'e') || (a == 'l' && b == 'l')) take = 3;
+                if (take) { cut(i, i + take); i += take; continue; }
+            }
+            {                                                              // one optional leading symbol or blank, then letters
+                size_t j = i;
+                if (cps[i].k != Letter && cps[i].k != Number && !newline(i) && i + 1 < n && cps[i + 1].k == Letter) j = i + 1;
+                if (cps[j].k == Letter) {
+                    size_t e = j;
+                    while (e < n && cps[e].k == Letter) ++e;
+                    cut(i, e);
+                    i = e;
+                    continue;
+                }
+            }
+            if (cps[i].k == Number) {
+                size_t e = i + 1;
+                if (style == Llama3)
+                    while (e < n && e < i + 3 && cps[e].k == Number) ++e;
+                cut(i, e);
+                i = e;
+                continue;
+            }
+            {                                                              // optional space, symbols, then the newlines that follow
+                size_t j = i;
+                if (cps[i].c == ' ' && i + 1 < n && cps[i + 1].k == Other) j = i + 1;
+                if (cps[j].k == Other) {
+                    size_t e = j;
+                    while (e < n && cps[e].k == Other) ++e;
+                    while (e < n && newline(e)) ++e;
+                    cut(i, e);
+                    i = e;
+                    continue;
+                }
+            }
+            size_t e = i;                                                  // a run of white space
+            while (e < n && cps[e].k == Space) ++e;
+            size_t last_nl = n;
+            for (size_t k = i; k < e; ++k)
+                if (newline(k)) last_nl = k;
+            if (last_nl != n) e = last_nl + 1;                             // up to the last newline of the run
+            else if (e < n && e - i > 1) --e;                              // leave the last blank for the piece that follows
+            cut(i, e);
+            i = e;
+        }
+        return out;
     }
 
     // The pieces the GPT-2 pattern cuts `text` into:
@@ -376,7 +459,7 @@ class GGUFTokenizer {
         }
     }
     void encode_gpt2(const std::string& part, std::vector<int>& out) const {
-        for (const std::string& piece : gpt2_pieces(part)) {
+        for (const std::string& piece : pieces(part, style_)) {
             std::vector<std::string> word;
             for (unsigned char b : piece) word.push_back(byte_to_unicode_[b]);
             while (word.size() > 1) {
@@ -410,6 +493,7 @@ class GGUFTokenizer {
     std::vector<int> types_;
     int bos_id_ = -1, eos_id_ = -1;
     bool add_bos_ = false;
+    PreStyle style_ = GPT2;
     std::unordered_map<std::string, int> vocab_;
     std::unordered_map<std::string, int> ranks_;
     int byte_ids_[256];

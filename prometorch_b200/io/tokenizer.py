@@ -11,9 +11,24 @@ from typing import Dict, Iterable, List, Optional, Tuple
 try:
     import regex as _re
     _GPT2_PAT = _re.compile(r"""'s|'t|'re|'ve|'m|'ll|'d| ?\p{L}+| ?\p{N}+| ?[^\s\p{L}\p{N}]+|\s+(?!\S)|\s+""")
+    # the pre-tokenisers newer byte-level vocabularies were trained with (the file names one in tokenizer.ggml.pre)
+    _QWEN2_PAT = _re.compile(r"""(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}| ?[^\s\p{L}\p{N}]+[\r\n]*|\s*[\r\n]+|\s+(?!\S)|\s+""")
+    _LLAMA3_PAT = _re.compile(r"""(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}{1,3}| ?[^\s\p{L}\p{N}]+[\r\n]*|\s*[\r\n]+|\s+(?!\S)|\s+""")
 except Exception:  # pragma: no cover
     _re = re
     _GPT2_PAT = re.compile(r"""'s|'t|'re|'ve|'m|'ll|'d| ?[A-Za-z]+| ?[0-9]+| ?[^\sA-Za-z0-9]+|\s+(?!\S)|\s+""")
+    _QWEN2_PAT = _LLAMA3_PAT = _GPT2_PAT
+
+
+def pretokenizer_pattern(pre: str):
+    """The split pattern for a ``tokenizer.ggml.pre`` name: qwen2-style (single digits, one leading symbol joins a word,
+    newlines close a run), llama-3-style (digits in groups of up to three), else GPT-2's."""
+    pre = (pre or "").lower()
+    if pre in ("qwen2", "qwen", "deepseek-r1-qwen", "qwen3"):
+        return _QWEN2_PAT
+    if pre in ("llama3", "llama-bpe", "llama-v3", "llama4", "smaug-bpe"):
+        return _LLAMA3_PAT
+    return _GPT2_PAT
 
 
 def _bytes_to_unicode() -> Dict[int, str]:
@@ -35,8 +50,9 @@ _U2B = {v: k for k, v in _B2U.items()}
 class GGUFTokenizer:
     def __init__(self, tokens: List[str], model: str = "llama", scores: Optional[List[float]] = None,
                  merges: Optional[List[str]] = None, token_types: Optional[List[int]] = None, bos_id: int = -1, eos_id: int = -1,
-                 add_bos: bool = False):
+                 add_bos: bool = False, pre: str = ""):
         self.tokens, self.model = list(tokens), model
+        self.pre, self._pat = pre or "", pretokenizer_pattern(pre)
         self.vocab: Dict[str, int] = {t: i for i, t in enumerate(self.tokens)}
         self.scores = list(scores) if scores is not None else [0.0] * len(self.tokens)
         self.token_types = list(token_types) if token_types is not None else [1] * len(self.tokens)
@@ -59,7 +75,7 @@ class GGUFTokenizer:
         scores, types = g("tokenizer.ggml.scores"), g("tokenizer.ggml.token_type")
         return cls(list(toks), g("tokenizer.ggml.model", "llama"), None if scores is None else list(scores), g("tokenizer.ggml.merges"),
                    None if types is None else list(types), int(g("tokenizer.ggml.bos_token_id", -1)),
-                   int(g("tokenizer.ggml.eos_token_id", -1)), bool(g("tokenizer.ggml.add_bos_token", False)))
+                   int(g("tokenizer.ggml.eos_token_id", -1)), bool(g("tokenizer.ggml.add_bos_token", False)), str(g("tokenizer.ggml.pre", "") or ""))
 
     @property
     def vocab_size(self) -> int:
@@ -149,7 +165,7 @@ class GGUFTokenizer:
 
     def _encode_gpt2(self, text: str) -> List[int]:
         out = []
-        for piece in _GPT2_PAT.findall(text):
+        for piece in self._pat.findall(text):
             mapped = "".join(_B2U[b] for b in piece.encode("utf-8"))
             for tok in self._bpe(tuple(mapped)):
                 tid = self.vocab.get(tok)

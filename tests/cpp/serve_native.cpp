@@ -103,8 +103,18 @@ int main(int argc, char** argv) {
             for (const auto& v : spec["scores"].items()) scores.push_back((float)v.as_double());
             for (const auto& v : spec["types"].items()) types.push_back((int)v.as_int());
             pio::GGUFTokenizer tok(tokens, spec["model"].as_string(), scores, merges, types, (int)spec["bos"].as_int(-1), (int)spec["eos"].as_int(-1),
-                                   spec["add_bos"].as_bool());
-            std::cout << run_texts(tok, spec["texts"]).dump() << "\n";
+                                   spec["add_bos"].as_bool(), spec["pre"].as_string());
+            pj::Value out = run_texts(tok, spec["texts"]);
+            if (spec["pre"].is_string()) {                               // the pieces of the named pattern too
+                pj::Value styled = pj::Value::array();
+                for (const auto& t : spec["texts"].items()) {
+                    pj::Value p = pj::Value::array();
+                    for (const auto& x : pio::GGUFTokenizer::pieces(t.as_string(), pio::GGUFTokenizer::style_of(spec["pre"].as_string()))) p.push_back(x);
+                    styled.push_back(p);
+                }
+                out.set("styled_pieces", styled);
+            }
+            std::cout << out.dump() << "\n";
             return 0;
         }
         if (mode == "gguf-tokenize") {

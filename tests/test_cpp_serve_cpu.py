@@ -75,7 +75,7 @@ def _train_bpe(corpus, n_merges):
 def _check_tokenizer(exe, tmp_path, spec, texts):
     from prometorch_b200.io.tokenizer import GGUFTokenizer
     py = GGUFTokenizer(spec["tokens"], spec["model"], spec["scores"] or None, spec["merges"] or None, spec["types"] or None, spec["bos"], spec["eos"],
-                       spec["add_bos"])
+                       spec["add_bos"], spec.get("pre", ""))
     spec = dict(spec, texts=texts)
     p = tmp_path / "spec.json"
     p.write_text(json.dumps(spec, ensure_ascii=False), encoding="utf-8")
@@ -98,6 +98,27 @@ def test_gpt2_tokenizer_matches_python(exe, tmp_path):
     got = _check_tokenizer(exe, tmp_path, spec, TEXTS)
     for i, t in enumerate(TEXTS):                       # the hand-written scanner against the pattern
         assert got["pieces"][i] == _GPT2_PAT.findall(t), t
+
+
+@pytest.mark.parametrize("pre", ["qwen2", "llama3", "llama-bpe", "unknown-name"])
+def test_newer_pretokenizer_patterns_match_python(exe, tmp_path, pre):
+    """tokenizer.ggml.pre: the qwen2 and llama-3 split patterns (hand-written scanner in C++, `regex` in Python) cut every text
+    into the same pieces and give the same ids; an unknown name falls back to GPT-2's pattern on both sides."""
+    from prometorch_b200.io.tokenizer import pretokenizer_pattern
+    extra = ["Hello!world it'S I'LL we'Re 12345 a\n\n  b\t\tc  \n x !!\r\n", "x=1+22*333/4444;\n\n\nif (a<b) {\r\n\treturn 7;}", "  \n", "\n \n  ",
+             "(привет) 2024год №5", "a\tb \tc", "\'\'\'quote\'\'\' ...\n", "tab\t\n\tafter", " 7 days", "end \n"]
+    texts = TEXTS + extra
+    tokens, merges = _train_bpe(" ".join(texts) * 2, 200)
+    tokens += ["<|im_start|>", "<|im_end|>", "<|endoftext|>"]
+    spec = {"tokens": tokens, "model": "gpt2", "scores": [], "merges": merges, "types": [1] * (len(tokens) - 3) + [3, 3, 3], "bos": -1, "eos": -1,
+            "add_bos": False, "pre": pre}
+    got = _check_tokenizer(exe, tmp_path, spec, texts)
+    pat = pretokenizer_pattern(pre)
+    for i, t in enumerate(texts):
+        if "<|" in t:
+            continue                                                      # special tokens are cut out before the pattern runs
+        assert got["styled_pieces"][i] == pat.findall(t), (pre, t, got["styled_pieces"][i], pat.findall(t))
+        assert "".join(got["styled_pieces"][i]) == t
 
 
 def test_spm_tokenizer_matches_python(exe, tmp_path):
