@@ -315,3 +315,28 @@ def test_cpp_and_python_implementations_agree(tmp_path):
         assert moved > 1e-4, name
     bad = {k: v for k, v in worst.items() if v > 2e-5}
     assert not bad, bad
+
+
+@pytest.mark.skipif(shutil.which("g++") is None, reason="needs g++")
+def test_cpp_headers_are_self_contained(tmp_path):
+    """Every header of the C++ API compiles when it is the only include of a translation unit (no header leans on what
+    another one happened to include before it)."""
+    import concurrent.futures as cf
+    import glob
+    cuda = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    headers = sorted(glob.glob(os.path.join(ROOT, "prometorch_b200", "cpp_api", "promethorch", "*.h")))
+    assert len(headers) >= 26
+    flags = [f for f in _torch_flags() if f.startswith(("-I", "-D"))] + [f"-I{ROOT}/prometorch_b200/cpp_api", f"-I{cuda}/include"]
+
+    def check(h):
+        name = os.path.basename(h)
+        if name in ("gguf.h", "gguf_backend.h") and not os.path.exists(os.path.join(cuda, "include", "cuda_runtime.h")):
+            return name, 0, ""                                   # these two need the CUDA runtime's header
+        src = tmp_path / (name + ".cpp")
+        src.write_text(f'#include "promethorch/{name}"\nint main() {{ return 0; }}\n')
+        r = subprocess.run(["g++", "-std=c++17", "-fsyntax-only", str(src)] + flags, capture_output=True, text=True, timeout=900)
+        return name, r.returncode, r.stderr[-1500:]
+    with cf.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 2)) as ex:
+        results = list(ex.map(check, headers))
+    bad = {n: err for n, rc, err in results if rc != 0}
+    assert not bad, bad
