@@ -124,6 +124,41 @@ def test_shared_memory_backend_threads():
         g1[0].barrier()
 
 
+def test_flag_protocol_model_survives_a_missing_peer_and_a_withheld_flag():
+    """The CPU model of the fused collectives' flag protocol: a healthy call reduces; a rank that never launches, a flag write
+    that is withheld and a rank that is late beyond the budget each end with a timeout status on the ranks that waited (and
+    nobody hangs); the next sequence number on the same channel works again and reduces correctly."""
+    from prometorch_b200.testing.symm_fake import ERR_FLAG_TIMEOUT, OK, FakeSymmChannel
+    world, n = 3, 12
+    ch = FakeSymmChannel(world, n, budget_s=0.4)
+    vals = {r: [float(r + 1)] * n for r in range(world)}
+    assert ch.run(1, vals) == {0: OK, 1: OK, 2: OK}
+    assert all(ch.mem[r].data == [6.0] * n for r in range(world))
+    # rank 2 never launches: the others time out, skip the reduction, leave their buffers alone
+    t0 = __import__("time").monotonic()
+    st = ch.run(2, vals, skip=(2,))
+    assert st == {0: ERR_FLAG_TIMEOUT, 1: ERR_FLAG_TIMEOUT} and __import__("time").monotonic() - t0 < 5.0
+    assert ch.mem[0].data == [1.0] * n and ch.mem[0].ticket == 0 and ch.mem[1].ticket == 0
+    for r in range(world):
+        ch.clear_status(r)
+    assert ch.run(3, vals) == {0: OK, 1: OK, 2: OK} and ch.mem[1].data == [6.0] * n          # the channel is usable again
+    # one flag write is withheld (rank 0's entry word at rank 1): rank 1 gives up, the others finish their slices
+    ch.drop = lambda writer, target, phase, seq: seq == 4 and writer == 0 and target == 1 and phase == 0
+    st = ch.run(4, vals)
+    assert st[1] == ERR_FLAG_TIMEOUT and ch.mem[1].ticket == 0
+    ch.drop = None
+    for r in range(world):
+        ch.clear_status(r)
+    assert ch.run(5, vals, scale=0.5) == {0: OK, 1: OK, 2: OK} and ch.mem[2].data == [3.0] * n
+    # a rank that is late but inside the budget is waited for; beyond the budget the waiters give up and still recover
+    assert ch.run(6, vals, delays={1: 0.05}) == {0: OK, 1: OK, 2: OK}
+    st = ch.run(7, vals, delays={1: 1.2})
+    assert st[0] == ERR_FLAG_TIMEOUT and st[2] == ERR_FLAG_TIMEOUT
+    for r in range(world):
+        ch.clear_status(r)
+    assert ch.run(8, vals) == {0: OK, 1: OK, 2: OK} and ch.mem[0].data == [6.0] * n
+
+
 def test_heartbeat_detects_silent_rank():
     store = D.DictStore()
     a = D.Heartbeat(store, 0, 2, interval=0.05, timeout=0.4).start()
