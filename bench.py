@@ -291,7 +291,7 @@ def served_native_figure(path, prompt_ids, n_new):
             if not line:
                 break
             if "listening on" in line:
-                port = int(line.rsplit(":", 1)[1])
+                port = int(line.rsplit(":", 1)[1].split()[0])
                 break
         if port is None:
             return {"error": "the native server did not come up: " + p.stderr.read()[-200:]}

@@ -45,7 +45,7 @@ def main():
             if not line:
                 break
             if "listening on" in line:
-                port = int(line.rsplit(":", 1)[1])
+                port = int(line.rsplit(":", 1)[1].split()[0])
                 break
         if port is None:
             raise RuntimeError("the server did not come up: " + p.stderr.read()[-500:])

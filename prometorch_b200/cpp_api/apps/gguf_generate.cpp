@@ -1,7 +1,7 @@
 // gguf_generate: text generation from a GGUF file as a native program (C++ reader, tokenizer, chat templates, CUDA decode
 // engine).  The flags are those of the reference's test_gguf_inference (examples/gguf/test_gguf_inference.cpp:76-120):
 //
-//   gguf_generate MODEL [PROMPT] [--device cuda] [--greedy] [--max-tokens N] [--temp T] [--top-k K] [--top-p P]
+//   gguf_generate MODEL [PROMPT] [--device cuda|cpu] [--greedy] [--max-tokens N] [--temp T] [--top-k K] [--top-p P]
 //                 [--repeat-penalty R] [--seed S] [--chat | --raw] [--info] [--tensors] [--profile]
 //
 // MODEL is a .gguf path or an Ollama model name.  --info prints the metadata and the parsed configuration, --tensors the
@@ -13,8 +13,10 @@
 #include <cstdlib>
 #include <cstring>
 #include <map>
+#include <memory>
 
 #include "promethorch/gguf_backend.h"
+#include "promethorch/gguf_cpu.h"
 
 namespace pio = promethorch::io;
 namespace ps = promethorch::serve;
@@ -104,15 +106,21 @@ int main(int argc, char** argv) {
                 }
             return 0;
         }
-        if (device != "cuda" && device != "gpu") { std::fprintf(stderr, "gguf_generate: this program decodes on CUDA devices only\n"); return 2; }
+        if (device != "cuda" && device != "gpu" && device != "cpu") { std::fprintf(stderr, "gguf_generate: --device is cuda or cpu\n"); return 2; }
+        const bool on_cpu = device == "cpu";
         if (greedy) { opt.temperature = 0.0; opt.repeat_penalty = 1.0; }
-        if (profile) ::setenv("PTB_TRACE", "1", 1);
+        if (profile && !on_cpu) ::setenv("PTB_TRACE", "1", 1);
         using clock = std::chrono::steady_clock;
         const auto t0 = clock::now();
-        ps::GGUFBackend backend(path, "cli", std::min(4096, opt.num_predict + 2048));
-        const auto& c = backend.model().config;
-        std::printf("[Model] %s %d layers, hidden %d, loaded in %.1f s on CUDA\n", c.architecture.c_str(), c.num_layers, c.hidden_size,
-                    std::chrono::duration<double>(clock::now() - t0).count());
+        const int max_seq = std::min(4096, opt.num_predict + 2048);
+        std::unique_ptr<ps::GGUFBackend> gpu;
+        std::unique_ptr<ps::CpuBackend> cpu;
+        if (on_cpu) cpu.reset(new ps::CpuBackend(path, "cli", max_seq));
+        else gpu.reset(new ps::GGUFBackend(path, "cli", max_seq));
+        ps::ModelBackend& backend = on_cpu ? static_cast<ps::ModelBackend&>(*cpu) : static_cast<ps::ModelBackend&>(*gpu);
+        const pio::TransformerConfig& c = on_cpu ? cpu->model().config : gpu->model().config;
+        std::printf("[Model] %s %d layers, hidden %d, loaded in %.1f s on %s\n", c.architecture.c_str(), c.num_layers, c.hidden_size,
+                    std::chrono::duration<double>(clock::now() - t0).count(), on_cpu ? "CPU" : "CUDA");
         const std::string text = (chat && !raw) ? pio::chat::apply_chat_template(prompt, backend.architecture, backend.model_name) : prompt;
         std::vector<int> ids = backend.encode(text);
         if (ids.empty()) ids.push_back(0);
@@ -132,10 +140,10 @@ int main(int argc, char** argv) {
         std::printf("[Ids]");
         for (int id : out) std::printf(" %d", id);
         std::printf("\n");
-        if (profile) {
+        if (profile && !on_cpu) {
             const int n_k = 5 * c.num_layers + 2;
             std::vector<unsigned long long> buf((size_t)8 * n_k);
-            const int got = backend.model().read_trace(buf.data(), n_k);
+            const int got = gpu->model().read_trace(buf.data(), n_k);
             static const char* per_layer[5] = {"qkv", "attention", "o", "gate/up", "down"};
             std::map<std::string, std::pair<double, int>> tot;
             std::vector<std::string> order;

@@ -1,6 +1,6 @@
 // promeserve: the Ollama-compatible server as a native program.
 //
-//   promeserve --port 11434 --device cuda --model NAME --workers N --queue-depth N --timeout-ms MS --model-dir DIR
+//   promeserve --port 11434 --device cuda|cpu --model NAME --workers N --queue-depth N --timeout-ms MS --model-dir DIR
 //
 // The flags are the reference's (promeserve/main.cpp:40-105) plus --host, --model-dir (repeatable), --max-seq and
 // --max-models.  --model is loaded before the port opens and stays resident; it may be a path to a .gguf file (requests may
@@ -11,6 +11,7 @@
 #include <cstring>
 
 #include "promethorch/gguf_backend.h"
+#include "promethorch/gguf_cpu.h"
 
 namespace ps = promethorch::serve;
 
@@ -38,27 +39,32 @@ int main(int argc, char** argv) {
         else if (a == "--max-models") cfg.max_loaded_models = std::atoi(val().c_str());
         else if (a == "--fp16-weights") {}                       // accepted for compatibility: weights stay in their file format
         else if (a == "--help" || a == "-h") {
-            std::printf("usage: promeserve [--host A] [--port N] [--device cuda] [--model NAME|FILE.gguf] [--workers N] [--queue-depth N]\n"
+            std::printf("usage: promeserve [--host A] [--port N] [--device cuda|cpu] [--model NAME|FILE.gguf] [--workers N] [--queue-depth N]\n"
                         "                  [--timeout-ms MS] [--model-dir DIR]... [--max-seq N] [--max-models N]\n");
             return 0;
         } else { std::fprintf(stderr, "promeserve: unknown flag %s\n", a.c_str()); return 2; }
     }
-    if (cfg.device != "cuda") { std::fprintf(stderr, "promeserve: this build serves on CUDA devices only (--device cuda)\n"); return 2; }
+    if (cfg.device != "cuda" && cfg.device != "cpu") { std::fprintf(stderr, "promeserve: --device is cuda or cpu\n"); return 2; }
+    const bool on_cpu = cfg.device == "cpu";                  // the fp32 reference decoder: for checking and for machines without a GPU
+    auto make = [&](const std::string& path, const std::string& name) -> std::shared_ptr<ps::ModelBackend> {
+        if (on_cpu) return std::make_shared<ps::CpuBackend>(path, name, cfg.max_seq);
+        return std::make_shared<ps::GGUFBackend>(path, name, cfg.max_seq);
+    };
     try {
-        ps::PromeServe srv(cfg, ps::gguf_loader(cfg));
+        ps::PromeServe srv(cfg, [&](const std::string& name) { return make(ps::store::resolve(name, cfg.model_dirs), name); });
         if (!model.empty()) {
             if (ps::store::is_file(model)) {
                 std::string name = model.substr(model.find_last_of('/') + 1);
                 if (name.size() > 5 && name.compare(name.size() - 5, 5, ".gguf") == 0) name.resize(name.size() - 5);
-                srv.handlers().add_backend(name, std::make_shared<ps::GGUFBackend>(model, name, cfg.max_seq));
+                srv.handlers().add_backend(name, make(model, name));
                 std::printf("[PromeServe] loaded %s as '%s'\n", model.c_str(), name.c_str());
             } else {
-                srv.handlers().add_backend(model, std::make_shared<ps::GGUFBackend>(ps::store::resolve(model, cfg.model_dirs), model, cfg.max_seq));
+                srv.handlers().add_backend(model, make(ps::store::resolve(model, cfg.model_dirs), model));
                 std::printf("[PromeServe] loaded '%s'\n", model.c_str());
             }
         }
         srv.start();
-        std::printf("[PromeServe] listening on %s:%d\n", cfg.host.c_str(), srv.port());
+        std::printf("[PromeServe] listening on %s:%d (%s)\n", cfg.host.c_str(), srv.port(), on_cpu ? "cpu" : "cuda");
         std::fflush(stdout);
         std::signal(SIGINT, on_signal);
         std::signal(SIGTERM, on_signal);

@@ -32,33 +32,6 @@
 namespace promethorch {
 namespace io {
 
-struct TransformerConfig {
-    std::string architecture = "llama";
-    int vocab_size = 0, hidden_size = 0, num_layers = 0, num_heads = 0, num_kv_heads = 0, intermediate_size = 0, head_dim = 0;
-    int context_length = 8192;
-    double rope_freq_base = 10000.0, rms_norm_eps = 1e-6;
-    bool has_qk_norm = false, rope_neox = false, tie_word_embeddings = false;
-    void parse(const gguf::GGUFReader& r) {
-        architecture = r.arch();
-        hidden_size = (int)r.arch_int("embedding_length", 0);
-        num_layers = (int)r.arch_int("block_count", 0);
-        num_heads = (int)r.arch_int("attention.head_count", 0);
-        num_kv_heads = (int)r.arch_int("attention.head_count_kv", num_heads);
-        intermediate_size = (int)r.arch_int("feed_forward_length", 0);
-        context_length = (int)r.arch_int("context_length", 8192);
-        rope_freq_base = r.arch_float("rope.freq_base", 10000.0);
-        rms_norm_eps = r.arch_float("attention.layer_norm_rms_epsilon", 1e-6);
-        const int key_len = (int)r.arch_int("attention.key_length", 0);
-        head_dim = key_len > 0 ? key_len : hidden_size / std::max(num_heads, 1);
-        vocab_size = (int)r.tensor("token_embd.weight").shape[0];
-        tie_word_embeddings = !r.has_tensor("output.weight");
-        has_qk_norm = architecture == "qwen3";
-        rope_neox = architecture == "qwen2" || architecture == "qwen3" || architecture == "phi3" || architecture == "gemma";
-        if (!(architecture == "llama" || architecture == "mistral" || architecture == "qwen2" || architecture == "qwen3"))
-            throw std::runtime_error("GGUFModel (C++): architecture '" + architecture + "' is served by the Python loader");
-    }
-};
-
 class GGUFModel {
  public:
     GGUFModel() = default;

@@ -10,6 +10,7 @@
 #include <sstream>
 #include <thread>
 
+#include "promethorch/gguf_cpu.h"
 #include "promethorch/model_loader.h"
 #include "promethorch/serve.h"
 #include "promethorch/tokenizer.h"
@@ -148,6 +149,25 @@ int main(int argc, char** argv) {
             std::cout << out.dump() << "\n";
             return 0;
         }
+        if (mode == "cpu-generate") {                // FILE N id id id ...: greedy ids and a few logits of the CPU decoder
+            pio::GGUFCpuModel m;
+            m.load(argv[2], 256);
+            const int n_new = std::atoi(argv[3]);
+            std::vector<int> prompt;
+            for (int i = 4; i < argc; ++i) prompt.push_back(std::atoi(argv[i]));
+            pj::Value out = pj::Value::object(), first = pj::Value::array();
+            int pos = 0;
+            for (int t : prompt) m.forward(t, pos++);
+            const auto& lg = m.forward(prompt.back(), pos);          // one more step so that the probe is not the prompt's last
+            for (int i = 0; i < 24; ++i) first.push_back((double)lg[(size_t)i]);
+            out.set("probe_logits", first);
+            out.set("probe_argmax", m.argmax());
+            pio::GGUFCpuModel fresh;
+            fresh.load(argv[2], 256);
+            out.set("ids", ids_json(fresh.generate(prompt, n_new)));
+            std::cout << out.dump() << "\n";
+            return 0;
+        }
         if (mode == "model") {                       // model_loader.h: what a path holds
             namespace L = pio::loader;
             pj::Value out = pj::Value::object();
@@ -217,6 +237,7 @@ int main(int argc, char** argv) {
             ps::ServerConfig cfg;
             cfg.port = 0;
             cfg.worker_threads = 2;
+            std::string gguf_file;
             for (int i = 2; i + 1 < argc; i += 2) {
                 const std::string a = argv[i];
                 if (a == "--workers") cfg.worker_threads = std::atoi(argv[i + 1]);
@@ -225,6 +246,7 @@ int main(int argc, char** argv) {
                 if (a == "--model-dir") cfg.model_dirs.push_back(argv[i + 1]);
                 if (a == "--max-body") cfg.max_body_bytes = (size_t)std::atol(argv[i + 1]);
                 if (a == "--max-models") cfg.max_loaded_models = std::atoi(argv[i + 1]);
+                if (a == "--gguf") gguf_file = argv[i + 1];
             }
             int loads = 0;
             // names found on disk load as fakes that remember how many loads there were (no GPU in this program)
@@ -236,6 +258,7 @@ int main(int argc, char** argv) {
                 return b;
             });
             for (const char* k : {"echo", "mirror", "slow", "tool"}) srv.handlers().add_backend(std::string(k) + ":1b", std::make_shared<FakeBackend>(k));
+            if (!gguf_file.empty()) srv.handlers().add_backend("cpu-model", std::make_shared<ps::CpuBackend>(gguf_file, "cpu-model", 256));   // a real file on the CPU decoder
             srv.start();
             std::cout << "PORT " << srv.port() << std::endl;
             std::string line;

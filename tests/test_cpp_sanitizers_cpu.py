@@ -125,6 +125,20 @@ def test_model_loader_on_damaged_files_under_asan(asan_exe, tmp_path):
         assert r.returncode in (0, 1) and "Sanitizer" not in err and "runtime error" not in err, (q.name, err[-1500:])
 
 
+def test_cpu_decoder_under_asan(asan_exe, tmp_path):
+    """The C++ CPU decoder (block dequantisers, threads over rows, key / value cache) on a small file under ASan + UBSan."""
+    from prometorch_b200.io import gguf_quant as GQ
+    from prometorch_b200.io.config import tiny_qwen3_config
+    from prometorch_b200.io.synthetic import write_synthetic_gguf
+    for tag, q_main, q_more in (("a", GQ.GGMLType.Q4_K, GQ.GGMLType.Q6_K), ("b", GQ.GGMLType.Q5_K, GQ.GGMLType.Q8_0)):
+        path = str(tmp_path / f"{tag}.gguf")
+        write_synthetic_gguf(path, tiny_qwen3_config(layers=1, hidden=256, heads=4, kv_heads=2, inter=512, vocab=512), seed=3, device="cpu",
+                             q_main=q_main, q_more=q_more)
+        r = subprocess.run([asan_exe, "cpu-generate", path, "4", "300", "301", "17"], capture_output=True, timeout=300, env=ENV)
+        _clean(r)
+        assert len(json.loads(r.stdout)["ids"]) == 4
+
+
 def _hammer(exe, env, flags=()):
     s = S.Server(exe, *flags, env=env)
     try:

@@ -315,6 +315,84 @@ def test_native_model_loader_matches_python(exe, tmp_path):
         assert r.returncode == 1 and b"unknown model format" in r.stderr, bad
 
 
+def test_native_cpu_decoder_matches_the_python_oracle(exe, tmp_path):
+    """gguf_cpu.h: the C++ CPU decoder (blocks dequantised on the fly) gives the logits and the greedy ids of the fp32 oracle of
+    the Python package, for the default quantisation mix and for Q5_K + Q8_0 and Q8_0 + F16 files."""
+    from prometorch_b200.io import gguf_quant as GQ
+    from prometorch_b200.io.config import tiny_qwen3_config
+    from prometorch_b200.io.synthetic import write_synthetic_gguf
+    from prometorch_b200.models.gguf_oracle import OracleModel
+    prompt = [300, 301, 17, 260, 5]
+    for tag, q_main, q_more in (("q4km", GQ.GGMLType.Q4_K, GQ.GGMLType.Q6_K), ("q5k_q80", GQ.GGMLType.Q5_K, GQ.GGMLType.Q8_0),
+                                ("q80_f16", GQ.GGMLType.Q8_0, GQ.GGMLType.F16)):
+        path = str(tmp_path / f"{tag}.gguf")
+        write_synthetic_gguf(path, tiny_qwen3_config(layers=2, hidden=256, heads=4, kv_heads=2, inter=512, vocab=512), seed=11, device="cpu",
+                             q_main=q_main, q_more=q_more, std=0.05)
+        got = _run(exe, "cpu-generate", path, "8", *[str(t) for t in prompt])
+        oracle = OracleModel(path, max_seq=256)
+        oracle.forward(prompt)
+        probe = oracle.forward([prompt[-1]])[-1]
+        assert torch.allclose(torch.tensor(got["probe_logits"]), probe[:24], atol=2e-3, rtol=2e-3), tag
+        assert got["probe_argmax"] == int(probe.argmax()), tag
+        want, gaps = [], []
+        oracle.reset()
+        lg = oracle.forward(prompt)
+        for _ in range(8):
+            top = lg[-1].topk(2).values
+            gaps.append(float(top[0] - top[1]))
+            want.append(int(lg[-1].argmax()))
+            lg = oracle.forward([want[-1]])
+        for i, (a, b) in enumerate(zip(got["ids"], want)):                         # only a near-tie may split the two
+            if a != b:
+                assert gaps[i] < 1e-3, (tag, i, got["ids"], want, gaps)
+                break
+        else:
+            assert got["ids"] == want, tag
+
+
+def test_native_server_serves_a_gguf_file_on_the_cpu(exe, tmp_path):
+    """The whole native stack without a GPU: HTTP -> C++ tokenizer -> C++ CPU decoder -> detokenised NDJSON; greedy answers equal
+    the Python oracle with the Python tokenizer, sampled answers are reproducible per seed."""
+    from prometorch_b200.io.config import tiny_qwen3_config
+    from prometorch_b200.io.gguf import GGUFReader
+    from prometorch_b200.io.synthetic import write_synthetic_gguf
+    from prometorch_b200.io.tokenizer import GGUFTokenizer
+    from prometorch_b200.models.gguf_oracle import OracleModel
+    path = str(tmp_path / "served.gguf")
+    write_synthetic_gguf(path, tiny_qwen3_config(layers=2, hidden=256, heads=4, kv_heads=2, inter=512, vocab=512), seed=12, device="cpu", std=0.05)
+    tok = GGUFTokenizer.from_reader(GGUFReader(path))
+    prompt = "t300 t301 t400 t260"
+    ids = tok.encode(prompt)
+    want = OracleModel(path, max_seq=256).generate_greedy(ids, 6)
+    stop = {tok.eos_id}
+    for i, t in enumerate(want):
+        if t in stop:
+            want = want[:i + 1]
+            break
+    s = Server(exe, "--gguf", path)
+    try:
+        greedy = {"num_predict": 6, "temperature": 0.0, "repeat_penalty": 1.0}
+        st, _, data = _req(s.port, "POST", "/api/generate", {"model": "cpu-model", "prompt": prompt, "raw": True, "stream": False, "options": greedy})
+        out = json.loads(data)
+        assert st == 200 and out["prompt_eval_count"] == len(ids) and out["eval_count"] == len(want), (out, want)
+        assert out["response"] == "".join(tok.decode_token(t) for t in want)
+        show = json.loads(_req(s.port, "POST", "/api/show", {"model": "cpu-model"})[2])
+        assert show["details"]["family"] == "qwen3" and show["model_info"]["general.name"] == "qwen3-tiny"
+        sampled = {"num_predict": 8, "temperature": 1.2, "top_k": 30, "top_p": 0.95, "repeat_penalty": 1.1}
+        runs = []
+        for seed in (5, 5, 6):
+            st, _, data = _req(s.port, "POST", "/api/generate", {"model": "cpu-model", "prompt": prompt, "raw": True, "options": dict(sampled, seed=seed)})
+            lines = [json.loads(l) for l in data.decode().splitlines() if l.strip()]
+            assert st == 200 and lines[-1]["done"] and 1 <= lines[-1]["eval_count"] <= 8
+            runs.append("".join(l.get("response", "") for l in lines))
+        assert runs[0] == runs[1]
+        st, _, data = _req(s.port, "POST", "/api/chat", {"model": "cpu-model", "stream": False, "messages": [{"role": "user", "content": "t300"}],
+                                                        "options": {"num_predict": 3, "temperature": 0.0, "repeat_penalty": 1.0}})
+        assert st == 200 and json.loads(data)["message"]["role"] == "assistant" and json.loads(data)["eval_count"] >= 1
+    finally:
+        s.close()
+
+
 def test_native_request_queue(exe):
     """serve::LLMEngine (submit_request / step / poll_responses / generate) behaves like the Python queue of the same name."""
     from prometorch_b200.serve import LLMEngine
@@ -537,3 +615,54 @@ def test_native_generate_cli_prints_metadata_and_tensors(tmp_path):
     assert subprocess.run([exe, path, "--bogus"], capture_output=True).returncode == 2
     r = subprocess.run([exe, str(tmp_path / "missing.gguf"), "--info"], capture_output=True, text=True)
     assert r.returncode == 1 and "cannot open" in r.stderr
+
+
+def test_native_programs_run_on_the_cpu(tmp_path):
+    """`lib/gguf_generate --device cpu` and `lib/promeserve --device cpu`: the shipped programs end to end without a GPU, against
+    the fp32 oracle and the tokenizer of the Python package."""
+    if shutil.which("nvcc") is None and not os.path.exists("/usr/local/cuda/bin/nvcc"):
+        pytest.skip("needs nvcc to link the programs against the native library")
+    from prometorch_b200 import _build
+    from prometorch_b200.io.config import tiny_qwen3_config
+    from prometorch_b200.io.gguf import GGUFReader
+    from prometorch_b200.io.synthetic import write_synthetic_gguf
+    from prometorch_b200.io.tokenizer import GGUFTokenizer
+    from prometorch_b200.models.gguf_oracle import OracleModel
+    path = str(tmp_path / "prog.gguf")
+    write_synthetic_gguf(path, tiny_qwen3_config(layers=2, hidden=256, heads=4, kv_heads=2, inter=512, vocab=512), seed=13, device="cpu", std=0.05)
+    tok = GGUFTokenizer.from_reader(GGUFReader(path))
+    prompt = "t300 t301 t400 t260"
+    ids = tok.encode(prompt)
+    want = OracleModel(path, max_seq=256).generate_greedy(ids, 6)
+    for i, t in enumerate(want):
+        if t == tok.eos_id:
+            want = want[:i + 1]
+            break
+    r = subprocess.run([str(_build.build_generate()), path, prompt, "--device", "cpu", "--greedy", "--max-tokens", "6"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    got = [int(x) for x in [ln for ln in r.stdout.splitlines() if ln.startswith("[Ids]")][0].split()[1:]]
+    assert got == want and "on CPU" in r.stdout and f"Prompt tokens: {len(ids)}" in r.stdout
+    p = subprocess.Popen([str(_build.build_promeserve()), "--device", "cpu", "--model", path, "--port", "0", "--max-seq", "256"], stdout=subprocess.PIPE,
+                         stderr=subprocess.PIPE, text=True)
+    try:
+        port = None
+        for _ in range(50):
+            line = p.stdout.readline()
+            if not line:
+                break
+            if "listening on" in line:
+                port = int(line.split(":")[-1].split()[0])
+                assert "(cpu)" in line
+                break
+        assert port, p.stderr.read()[-2000:]
+        st, _, data = _req(port, "POST", "/api/generate", {"model": "prog", "prompt": prompt, "raw": True, "stream": False,
+                                                         "options": {"num_predict": 6, "temperature": 0.0, "repeat_penalty": 1.0}})
+        out = json.loads(data)
+        assert st == 200 and out["eval_count"] == len(want) and out["response"] == "".join(tok.decode_token(t) for t in want)
+        assert any(m["name"] == "prog" for m in json.loads(_req(port, "GET", "/api/ps")[2])["models"])
+    finally:
+        p.terminate()
+        try:
+            p.wait(timeout=20)
+        except subprocess.TimeoutExpired:
+            p.kill()

@@ -50,7 +50,7 @@ def test_native_promeserve_serves_a_gguf_file(tmp_path):
             if not line:
                 break
             if "listening on" in line:
-                port = int(line.rsplit(":", 1)[1])
+                port = int(line.rsplit(":", 1)[1].split()[0])
                 break
         assert port, p.stderr.read()[-2000:]
         greedy = {"num_predict": 12, "temperature": 0.0, "repeat_penalty": 1.0}
