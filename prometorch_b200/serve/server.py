@@ -147,6 +147,57 @@ class GGUFBackend(ModelBackend):
         return t1 - t0, time.perf_counter() - t1
 
 
+class OracleBackend(ModelBackend):
+    """A GGUF file on the fp32 CPU oracle (``models/gguf_oracle.py``): what ``--device cpu`` serves.  For checking and for
+    machines without a GPU; sampling runs on the host."""
+
+    def __init__(self, path: str, name: str, max_seq: int = 4096):
+        import os
+        from ..io.tokenizer import GGUFTokenizer
+        from ..models.gguf_oracle import OracleModel
+        self.model = OracleModel(path, device="cpu", max_seq=max_seq)
+        self.max_seq = max_seq
+        self.tokenizer = GGUFTokenizer.from_reader(self.model.reader)
+        self.name, self.path = name, path
+        self.architecture, self.model_name = self.model.cfg.architecture, self.model.cfg.model_name
+        self.size = os.path.getsize(path)
+        n = sum(t.nbytes for t in self.model.reader.tensors.values())
+        self.parameter_size = f"{n / 0.5625 / 1e9:.1f}B"
+        self.stop_ids = {self.model.cfg.eos_token_id} - {-1}
+        for t in ("<|im_end|>", "<|eot_id|>", "<end_of_turn>", "<|end|>", "<|endoftext|>"):
+            if t in self.tokenizer.vocab:
+                self.stop_ids.add(self.tokenizer.vocab[t])
+
+    def encode(self, text):
+        return self.tokenizer.encode(text)
+
+    def decode_token(self, tid):
+        return self.tokenizer.decode([tid], strip_leading_space=False)
+
+    def generate(self, prompt_ids, options, on_token):
+        import torch
+        from ..ops.sampling import sample_logits
+        m = self.model
+        n_new = max(0, min(int(options.get("num_predict", 128)), self.max_seq - len(prompt_ids) - 1))
+        gen = torch.Generator().manual_seed(int(options.get("seed", 42)))
+        t0 = time.perf_counter()
+        m.reset()
+        logits = m.forward(prompt_ids)
+        t1 = time.perf_counter()
+        history = list(prompt_ids)
+        for _ in range(n_new):
+            nxt = sample_logits(logits[-1], float(options.get("temperature", 0.7)), int(options.get("top_k", 40)), float(options.get("top_p", 0.9)),
+                                float(options.get("repeat_penalty", 1.05)), history, gen)
+            history.append(nxt)
+            if on_token(nxt) is False or nxt in self.stop_ids:
+                break
+            logits = m.forward([nxt])
+        return t1 - t0, time.perf_counter() - t1
+
+    def close(self):
+        pass
+
+
 class PagedBackend(ModelBackend):
     """A Hugging Face Llama directory served by the continuous-batching engine (``serve/llm.py``).  ``concurrent``:
     the handlers do not serialise generations for this backend, so requests that arrive together share decode
@@ -580,6 +631,8 @@ class PromeServe:
                     path = resolve_model(name)
                 except FileNotFoundError as e:
                     raise KeyError(str(e))
+            if self.config.device == "cpu":
+                return OracleBackend(path, name, self.config.max_seq)
             return GGUFBackend(path, name, self.config.device, self.config.max_seq)
         self.handlers = ApiHandlers(self.config, backends, loader)
         self.http = HttpServer(self.config, self.handlers)

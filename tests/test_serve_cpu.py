@@ -279,3 +279,35 @@ def test_server_rejects_paths_big_bodies_and_caps_loaded_models(tmp_path):
         h.ensure_model(n)
     assert loads == ["a", "b", "c"] and closed == ["b"]          # "a" was used more recently than "b"
     assert set(h.backends) == {"pinned", "a", "c"}
+
+
+def test_python_server_serves_a_gguf_file_on_the_cpu(tmp_path):
+    """`--device cpu`: a GGUF file behind the fp32 oracle; greedy answers equal the oracle's own continuation."""
+    from prometorch_b200.io.config import tiny_qwen3_config
+    from prometorch_b200.io.synthetic import write_synthetic_gguf
+    from prometorch_b200.models.gguf_oracle import OracleModel
+    from prometorch_b200.serve.server import OracleBackend
+    d = tmp_path / "models"
+    d.mkdir()
+    path = str(d / "tiny.gguf")
+    write_synthetic_gguf(path, tiny_qwen3_config(layers=2, hidden=256, heads=4, kv_heads=2, inter=512, vocab=512), seed=14, device="cpu", std=0.05)
+    srv = PromeServe(ServerConfig(port=0, device="cpu", model_dirs=[str(d)], max_seq=256)).start()
+    try:
+        prompt = "t300 t301 t400"
+        st, _, data = _req(srv.port, "POST", "/api/generate", {"model": "tiny", "prompt": prompt, "raw": True, "stream": False,
+                                                              "options": {"num_predict": 5, "temperature": 0.0, "repeat_penalty": 1.0}})
+        out = json.loads(data)
+        backend = srv.handlers.backends["tiny"]
+        assert st == 200 and isinstance(backend, OracleBackend)
+        ids = backend.encode(prompt)
+        want = OracleModel(path, max_seq=256).generate_greedy(ids, 5)
+        for i, t in enumerate(want):
+            if t in backend.stop_ids:
+                want = want[:i + 1]
+                break
+        assert out["eval_count"] == len(want) and out["response"] == "".join(backend.decode_token(t) for t in want)
+        st, _, data = _req(srv.port, "POST", "/api/generate", {"model": "tiny", "prompt": prompt, "raw": True, "options": {"num_predict": 4, "seed": 3}})
+        lines = [json.loads(l) for l in data.decode().splitlines() if l.strip()]
+        assert st == 200 and lines[-1]["done"] and 1 <= lines[-1]["eval_count"] <= 4
+    finally:
+        srv.stop()
