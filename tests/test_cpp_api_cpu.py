@@ -340,3 +340,25 @@ def test_cpp_headers_are_self_contained(tmp_path):
         results = list(ex.map(check, headers))
     bad = {n: err for n, rc, err in results if rc != 0}
     assert not bad, bad
+
+
+@pytest.mark.skipif(shutil.which("g++") is None or shutil.which("make") is None, reason="needs g++ and make")
+def test_cpp_example_programs_build_and_run(tmp_path):
+    """examples/cpp: the Makefile builds both programs; the MLP trains, the serving-side example reads a GGUF file, tokenises
+    and continues a prompt on the CPU decoder."""
+    from prometorch_b200.io.config import tiny_qwen3_config
+    from prometorch_b200.io.synthetic import write_synthetic_gguf
+    work = tmp_path / "cpp"
+    shutil.copytree(os.path.join(ROOT, "examples", "cpp"), work)
+    api = os.path.join(ROOT, "prometorch_b200", "cpp_api")
+    r = subprocess.run(["make", "-C", str(work), "all", f"API={api}"], capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-3000:]
+    r = subprocess.run([str(work / "mlp"), "1"], capture_output=True, text=True, timeout=600, cwd=str(work))
+    assert r.returncode == 0 and "saved mlp.ptor (535818 parameters)" in r.stdout, r.stdout + r.stderr[-1500:]
+    acc = float(r.stdout.split("test accuracy")[1].split("%")[0])
+    assert acc > 90.0
+    path = str(tmp_path / "ex.gguf")
+    write_synthetic_gguf(path, tiny_qwen3_config(layers=1, hidden=256, heads=4, kv_heads=2, inter=512, vocab=512), seed=2, device="cpu")
+    r = subprocess.run([str(work / "tokenize"), path, "t300 t301", "--generate", "3"], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stderr
+    assert "format gguf, architecture qwen3" in r.stdout and "round trip: t300 t301" in r.stdout and "greedy continuation on the CPU decoder:" in r.stdout
