@@ -30,30 +30,30 @@ class Hooked {
     using ForwardHookWithReturn = std::function<Tensor(Module&, const std::vector<Tensor>&, const Tensor&)>;
     using BackwardHook = std::function<void(Module&, const std::vector<Tensor>&, const Tensor&)>;
 
-    explicit Hooked(Holder m) : m_(std::move(m)) {}
-    Holder& module() { return m_; }
-    auto operator->() { return m_.operator->(); }
+    explicit Hooked(Holder m) : s_(std::make_shared<State>(std::move(m))) {}
+    Holder& module() { return s_->m; }
+    auto operator->() { return s_->m.operator->(); }
 
-    int register_forward_pre_hook(PreHook h) { pre_[next_] = std::move(h); return next_++; }
+    int register_forward_pre_hook(PreHook h) { s_->pre[s_->next] = std::move(h); return s_->next++; }
     int register_forward_hook(ForwardHook h) {
-        fwd_[next_] = [h](Module& m, const std::vector<Tensor>& in, const Tensor& out) { h(m, in, out); return Tensor(); };
-        return next_++;
+        s_->fwd[s_->next] = [h](Module& m, const std::vector<Tensor>& in, const Tensor& out) { h(m, in, out); return Tensor(); };
+        return s_->next++;
     }
     // The hook's result, when defined, replaces the output.
-    int register_forward_hook_with_return(ForwardHookWithReturn h) { fwd_[next_] = std::move(h); return next_++; }
-    int register_backward_hook(BackwardHook h) { bwd_[next_] = std::move(h); return next_++; }
-    bool remove_hook(int id) { return pre_.erase(id) + fwd_.erase(id) + bwd_.erase(id) > 0; }
-    size_t num_hooks() const { return pre_.size() + fwd_.size() + bwd_.size(); }
+    int register_forward_hook_with_return(ForwardHookWithReturn h) { s_->fwd[s_->next] = std::move(h); return s_->next++; }
+    int register_backward_hook(BackwardHook h) { s_->bwd[s_->next] = std::move(h); return s_->next++; }
+    bool remove_hook(int id) { return s_->pre.erase(id) + s_->fwd.erase(id) + s_->bwd.erase(id) > 0; }
+    size_t num_hooks() const { return s_->pre.size() + s_->fwd.size() + s_->bwd.size(); }
 
     template <class... Args>
     Tensor operator()(Args&&... args) {
         std::vector<Tensor> inputs{Tensor(std::forward<Args>(args))...};
-        for (auto& kv : pre_) kv.second(*m_.ptr(), inputs);
+        for (auto& kv : s_->pre) kv.second(*s_->m.ptr(), inputs);
         std::shared_ptr<CallState> st;
-        if (!bwd_.empty() && torch::GradMode::is_enabled()) st = watch_inputs(inputs);
+        if (!s_->bwd.empty() && torch::GradMode::is_enabled()) st = watch_inputs(inputs);
         Tensor out = call(inputs, std::make_index_sequence<sizeof...(Args)>());
-        for (auto& kv : fwd_) {
-            Tensor r = kv.second(*m_.ptr(), inputs, out);
+        for (auto& kv : s_->fwd) {
+            Tensor r = kv.second(*s_->m.ptr(), inputs, out);
             if (r.defined()) out = r;
         }
         if (st && out.requires_grad()) out = watch_output(out, st);
@@ -62,27 +62,38 @@ class Hooked {
 
  private:
     template <size_t... I>
-    Tensor call(std::vector<Tensor>& in, std::index_sequence<I...>) { return m_->forward(in[I]...); }
+    Tensor call(std::vector<Tensor>& in, std::index_sequence<I...>) { return s_->m->forward(in[I]...); }
 
+    // The module and its hooks live in shared state: the gradient hooks of a call keep it alive, so a backward pass that runs
+    // after the wrapper went out of scope still finds its hooks.
+    struct State {
+        explicit State(Holder h) : m(std::move(h)) {}
+        Holder m;
+        std::map<int, PreHook> pre;
+        std::map<int, ForwardHookWithReturn> fwd;
+        std::map<int, BackwardHook> bwd;
+        int next = 0;
+    };
     struct CallState {
         std::vector<Tensor> grad_inputs;
         Tensor grad_output;
         int waiting = 0;
     };
-    void fire(const std::shared_ptr<CallState>& st) {
-        for (auto& kv : bwd_) kv.second(*m_.ptr(), st->grad_inputs, st->grad_output);
+    static void fire(const std::shared_ptr<State>& s, const std::shared_ptr<CallState>& st) {
+        for (auto& kv : s->bwd) kv.second(*s->m.ptr(), st->grad_inputs, st->grad_output);
     }
     // Gradients are watched on views made for this call, so no hook stays on the caller's own tensors.
     std::shared_ptr<CallState> watch_inputs(std::vector<Tensor>& inputs) {
         auto st = std::make_shared<CallState>();
         st->grad_inputs.resize(inputs.size());
+        auto s = s_;
         for (size_t i = 0; i < inputs.size(); ++i) {
             if (!inputs[i].defined() || !inputs[i].requires_grad()) continue;
             inputs[i] = inputs[i].view_as(inputs[i]);
             ++st->waiting;
-            inputs[i].register_hook([this, st, i](const Tensor& g) {
+            inputs[i].register_hook([s, st, i](const Tensor& g) {
                 st->grad_inputs[i] = g;
-                if (--st->waiting == 0) fire(st);
+                if (--st->waiting == 0) fire(s, st);
             });
         }
         return st;
@@ -90,18 +101,15 @@ class Hooked {
     Tensor watch_output(const Tensor& out, const std::shared_ptr<CallState>& st) {
         Tensor o = out.view_as(out);
         const bool none = st->waiting == 0;
-        o.register_hook([this, st, none](const Tensor& g) {
+        auto s = s_;
+        o.register_hook([s, st, none](const Tensor& g) {
             st->grad_output = g;
-            if (none) fire(st);
+            if (none) fire(s, st);
         });
         return o;
     }
 
-    Holder m_;
-    std::map<int, PreHook> pre_;
-    std::map<int, ForwardHookWithReturn> fwd_;
-    std::map<int, BackwardHook> bwd_;
-    int next_ = 0;
+    std::shared_ptr<State> s_;
 };
 
 }  // namespace nn

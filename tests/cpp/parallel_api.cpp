@@ -358,6 +358,17 @@ static int module_hooks() {
     lin.remove_hook(fwd);
     lin.remove_hook(bwd);
     CHECK(lin.num_hooks() == 0);
+    // a backward pass that runs after the wrapper is gone still finds the hooks (they live in shared state)
+    int late = 0;
+    pt::Tensor out_late;
+    auto x3 = pt::randn({2, 4}).set_requires_grad(true);
+    {
+        pt::nn::Hooked<pt::nn::Linear> scoped(pt::nn::Linear(4, 2));
+        scoped.register_backward_hook([&](pt::nn::Module&, const std::vector<pt::Tensor>&, const pt::Tensor&) { ++late; });
+        out_late = scoped(x3);
+    }
+    out_late.sum().backward();
+    CHECK(late == 1 && x3.grad().defined());
     return 0;
 }
 
