@@ -741,6 +741,10 @@ class HttpServer {
         Request r;
         if (!read_request(fd, r)) return;
         if (r.too_large) { net::send_response(fd, 413, error_json("request body too large")); return; }
+        if (lower(r.headers["transfer-encoding"]).find("chunked") != std::string::npos) {
+            net::send_response(fd, 400, error_json("chunked request bodies are not supported: send Content-Length"));
+            return;
+        }
         if (r.method == "OPTIONS") { net::send_response(fd, 204, ""); return; }
         if (r.method == "HEAD") { net::send_response(fd, (r.path == "/" || r.path == "/api/version" || r.path == "/api/tags") ? 200 : 404, ""); return; }
         if (r.method == "GET" && r.path == "/") { net::send_response(fd, 200, "PromeServe is running", "text/plain"); return; }

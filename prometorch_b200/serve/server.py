@@ -544,6 +544,8 @@ class HttpServer:
         H = self.handlers
         if raw is None:
             return self._send(wfile, 413, json.dumps({"error": "request body too large"}).encode())
+        if "chunked" in headers.get("transfer-encoding", "").lower():
+            return self._send(wfile, 400, json.dumps({"error": "chunked request bodies are not supported: send Content-Length"}).encode())
         if method == "OPTIONS":
             return self._send(wfile, 204, b"")
         if method == "HEAD":

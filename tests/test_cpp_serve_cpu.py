@@ -515,6 +515,10 @@ def test_native_server_errors_and_limits(exe, tmp_path):
         st, _, data = _req(s.port, "POST", "/api/generate", {"model": "missing:7b", "prompt": "x", "stream": False})
         assert st == 404 and "error" in json.loads(data)
         assert _req(s.port, "POST", "/api/generate", raw="{not json")[0] == 400
+        c = socket.create_connection(("127.0.0.1", s.port), timeout=10)
+        c.sendall(b"POST /api/generate HTTP/1.1\r\nHost: x\r\nTransfer-Encoding: chunked\r\n\r\n5\r\nhello\r\n0\r\n\r\n")
+        assert c.recv(4096).startswith(b"HTTP/1.1 400") 
+        c.close()
         assert _req(s.port, "POST", "/api/generate", {"model": "echo:1b", "prompt": "x" * 5000})[0] == 413
         for bad in ("/etc/passwd", "../x", "a/b", "..", "a\\b"):
             st, _, data = _req(s.port, "POST", "/api/generate", {"model": bad, "prompt": "x", "stream": False})

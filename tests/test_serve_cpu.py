@@ -102,6 +102,11 @@ def test_errors(server):
     r = c.getresponse()
     assert r.status == 400
     c.close()
+    import socket
+    k = socket.create_connection(("127.0.0.1", srv.port), timeout=10)
+    k.sendall(b"POST /api/generate HTTP/1.1\r\nHost: x\r\nTransfer-Encoding: chunked\r\n\r\n5\r\nhello\r\n0\r\n\r\n")
+    assert k.recv(4096).startswith(b"HTTP/1.1 400")
+    k.close()
 
 
 def test_llm_engine_queue():
