@@ -202,3 +202,45 @@ def test_clip_grad_norm_cpu():
     assert float(n) == pytest.approx(5.0) and float(p.grad.norm()) == pytest.approx(1.0, abs=1e-5)
     O.clip_grad_value_([p], 0.1)
     assert float(p.grad.abs().max()) <= 0.1 + 1e-7
+
+
+def test_option_defaults_are_the_reference_table():
+    """The default of every optimizer option and scheduler argument, pinned (the reference's option structs, torch/optim/*.h)."""
+    import inspect
+    from prometorch_b200 import optim as O
+    want = {
+        "SGD": dict(lr=0.01, momentum=0.0, dampening=0.0, weight_decay=0.0, nesterov=False),
+        "Adam": dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, amsgrad=False),
+        "AdamW": dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, amsgrad=False),
+        "RMSprop": dict(lr=0.01, alpha=0.99, eps=1e-8, weight_decay=0.0, momentum=0.0, centered=False),
+        "Lion": dict(lr=1e-4, betas=(0.9, 0.99), weight_decay=0.0),
+        "SophiaG": dict(lr=1e-4, betas=(0.965, 0.99), eps=1e-12, weight_decay=0.0, rho=0.04, hessian_update_interval=10),
+        "LAMB": dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-6, weight_decay=0.01, bias_correction=True),
+        "Adafactor": dict(lr=0.0, eps1=1e-30, eps2=1e-3, clip_threshold=1.0, decay_rate=-0.8, beta1=0.0, weight_decay=0.0, scale_parameter=True,
+                          relative_step=True, warmup_init=False),
+        "NAdam": dict(lr=2e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, momentum_decay=0.004),
+        "RAdam": dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0),
+        "Adagrad": dict(lr=0.01, lr_decay=0.0, weight_decay=0.0, eps=1e-10, initial_accumulator_value=0.0),
+        "Adadelta": dict(lr=1.0, rho=0.9, eps=1e-6, weight_decay=0.0),
+        "Adamax": dict(lr=2e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0),
+        "AdamKiller": dict(lr=1e-3, beta1_min=0.7, beta1_max=0.95, beta2=0.999, eps=1e-8, weight_decay=0.01, use_adaptive_momentum=True),
+        "ASGD": dict(lr=0.01, lambd=1e-4, alpha=0.75, t0=1e6, weight_decay=0.0),
+        "LBFGS": dict(lr=1.0, max_iter=20, max_eval=25, tolerance_grad=1e-7, tolerance_change=1e-9, history_size=100),
+        "StepLR": dict(gamma=0.1), "MultiStepLR": dict(gamma=0.1), "CosineAnnealingLR": dict(eta_min=0.0),
+        "LinearLR": dict(start_factor=1 / 3, end_factor=1.0, total_iters=5), "ConstantLR": dict(factor=1 / 3, total_iters=5),
+        "ReduceLROnPlateau": dict(mode="min", factor=0.1, patience=10, threshold=1e-4, min_lr=0.0),
+        "WarmupCosineAnnealingLR": dict(eta_min=0.0), "OneCycleLR": dict(pct_start=0.3, div_factor=25.0, final_div_factor=1e4),
+        "CosineAnnealingWarmRestarts": dict(T_mult=1, eta_min=0.0), "CyclicLR": dict(step_size_up=2000, step_size_down=-1, mode="triangular", gamma=1.0),
+        "PolynomialLR": dict(power=1.0),
+    }
+    bad = {}
+    for name, defaults in want.items():
+        sig = inspect.signature(getattr(O, name).__init__).parameters
+        for k, v in defaults.items():
+            got = sig[k].default if k in sig else "<missing>"
+            same = (got == pytest.approx(v)) if isinstance(v, float) else (tuple(got) == v if isinstance(v, tuple) and got != "<missing>" else got == v)
+            if not same:
+                bad[f"{name}.{k}"] = (got, v)
+    assert not bad, bad
+    ema = O.EMA([torch.nn.Parameter(torch.ones(2))])
+    assert ema.decay == 0.999 and all(hasattr(ema, m) for m in ("update", "apply_shadow", "restore", "set_decay"))
