@@ -186,3 +186,93 @@ class OracleModel:
             out.append(t)
             logits = self.forward([t])
         return out
+
+
+class TPOracleModel(OracleModel):
+    """The oracle cut for tensor parallelism with the partition rule of the decode engine (io/gguf_model.py): rank r holds the
+    query heads ``[r H/W, (r+1) H/W)`` with their KV heads, the FFN columns of its share of 256-wide blocks (``split_blocks``: the
+    first ``blocks % W`` ranks take one more), the matching input columns of the attention-output and FFN-down projections, and
+    rows ``[V r / W, V (r+1) / W)`` of the output head.  The two partial sums per layer are all-reduced over the process group
+    and the logits are all-gathered, which is what the reference's CPU tensor-parallel decode does
+    (torch/io/gguf_model.h:6197-6225, 6442, 6512).  Runs on CPU ranks (gloo); checked against the single-process oracle."""
+
+    def __init__(self, path_or_reader, tp_rank: int, tp_world: int, group=None, max_seq: int = 4096):
+        super().__init__(path_or_reader, device="cpu", max_seq=max_seq)
+        from ..io.gguf_model import split_blocks
+        cfg, W, rk = self.cfg, tp_world, tp_rank
+        if cfg.num_heads % W or cfg.num_kv_heads % W or cfg.intermediate_size % 256:
+            raise ValueError(f"tensor parallel {W}: needs heads ({cfg.num_heads}) and KV heads ({cfg.num_kv_heads}) divisible "
+                             f"and an FFN size ({cfg.intermediate_size}) that is a multiple of 256")
+        self.tp_rank, self.tp_world, self.group = rk, W, group
+        d = cfg.head_dim
+        self.hq, self.hkv = cfg.num_heads // W, cfg.num_kv_heads // W
+        fb0, fb1 = split_blocks(cfg.intermediate_size // 256, W, rk)
+        q0, q1 = rk * self.hq * d, (rk + 1) * self.hq * d
+        k0, k1 = rk * self.hkv * d, (rk + 1) * self.hkv * d
+        f0, f1 = fb0 * 256, fb1 * 256
+        for L in self.layers:
+            L["attn_q"], L["attn_k"], L["attn_v"] = L["attn_q"][q0:q1], L["attn_k"][k0:k1], L["attn_v"][k0:k1]
+            L["attn_output"] = L["attn_output"][:, q0:q1]
+            L["ffn_gate"], L["ffn_up"], L["ffn_down"] = L["ffn_gate"][f0:f1], L["ffn_up"][f0:f1], L["ffn_down"][:, f0:f1]
+            for b, (lo, hi) in (("attn_q_b", (q0, q1)), ("attn_k_b", (k0, k1)), ("attn_v_b", (k0, k1))):
+                if b in L:
+                    L[b] = L[b][lo:hi]
+        V = cfg.vocab_size
+        self.v0, self.v1 = V * rk // W, V * (rk + 1) // W
+        self.out = self.out[self.v0:self.v1]
+        self.local_inter = f1 - f0
+
+    def _allreduce(self, t):
+        if self.tp_world > 1:
+            import torch.distributed as dist
+            dist.all_reduce(t, group=self.group)
+        return t
+
+    @torch.no_grad()
+    def forward(self, tokens) -> torch.Tensor:
+        cfg = self.cfg
+        tokens = torch.as_tensor(tokens, dtype=torch.long)
+        T = tokens.numel()
+        x = self.tok[tokens]
+        if cfg.scale_embeddings:
+            x = x * math.sqrt(cfg.hidden_size)
+        cos, sin = self.cos[self.pos:self.pos + T], self.sin[self.pos:self.pos + T]
+        group = self.hq // self.hkv
+        for li, L in enumerate(self.layers):
+            h = rms_norm(x, L["attn_norm"], cfg.rms_norm_eps, cfg.gemma_norm_add_one)
+            q, k, v = h @ L["attn_q"].t(), h @ L["attn_k"].t(), h @ L["attn_v"].t()
+            if "attn_q_b" in L:
+                q, k, v = q + L["attn_q_b"], k + L["attn_k_b"], v + L["attn_v_b"]
+            q, k, v = q.view(T, self.hq, cfg.head_dim), k.view(T, self.hkv, cfg.head_dim), v.view(T, self.hkv, cfg.head_dim)
+            if "attn_q_norm" in L:
+                q, k = rms_norm(q, L["attn_q_norm"], cfg.rms_norm_eps), rms_norm(k, L["attn_k_norm"], cfg.rms_norm_eps)
+            q, k = apply_rope(q, cos, sin, cfg.rope_neox), apply_rope(k, cos, sin, cfg.rope_neox)
+            k, v = k.half().float(), v.half().float()
+            self.k_cache[li] = k if self.k_cache[li] is None else torch.cat([self.k_cache[li], k], 0)
+            self.v_cache[li] = v if self.v_cache[li] is None else torch.cat([self.v_cache[li], v], 0)
+            K, Vc = self.k_cache[li], self.v_cache[li]
+            S = K.shape[0]
+            Kh, Vh = K.repeat_interleave(group, dim=1).permute(1, 0, 2), Vc.repeat_interleave(group, dim=1).permute(1, 0, 2)
+            sc = torch.einsum("thd,hsd->hts", q, Kh) / math.sqrt(cfg.head_dim)
+            qpos, kpos = torch.arange(self.pos, self.pos + T)[:, None], torch.arange(S)[None, :]
+            sc = sc.masked_fill((kpos > qpos)[None], float("-inf"))
+            a = torch.einsum("hts,hsd->thd", sc.softmax(-1), Vh).reshape(T, self.hq * cfg.head_dim)
+            x = x + self._allreduce(a @ L["attn_output"].t())                 # partial sums over this rank's heads
+            h = rms_norm(x, L["ffn_norm"], cfg.rms_norm_eps, cfg.gemma_norm_add_one)
+            g, u = h @ L["ffn_gate"].t(), h @ L["ffn_up"].t()
+            act = F.gelu(g, approximate="tanh") if cfg.ffn_gelu else F.silu(g)
+            x = x + self._allreduce((act * u) @ L["ffn_down"].t())             # partial sums over this rank's FFN columns
+        self.pos += T
+        x = rms_norm(x, self.out_norm, cfg.rms_norm_eps, cfg.gemma_norm_add_one)
+        local = x @ self.out.t()                                               # this rank's rows of the vocabulary
+        if self.tp_world == 1:
+            return local
+        import torch.distributed as dist
+        V, W = cfg.vocab_size, self.tp_world
+        sizes = [V * (r + 1) // W - V * r // W for r in range(W)]
+        pad = max(sizes)
+        buf = torch.zeros(T, pad)
+        buf[:, :local.shape[1]] = local
+        parts = [torch.zeros(T, pad) for _ in range(W)]
+        dist.all_gather(parts, buf, group=self.group)
+        return torch.cat([p[:, :n] for p, n in zip(parts, sizes)], dim=1)

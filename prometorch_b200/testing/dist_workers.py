@@ -342,3 +342,43 @@ def expert_parallel_matches_dense(rank, world):
     assert float(moe.load_balance_loss(x.detach())) > 0.5
     _fin()
     return 0
+
+
+def gguf_tp_oracle_matches_single(rank, world):
+    """Tensor-parallel GGUF decode on CPU ranks: the sharded oracle (heads, FFN blocks split unevenly, vocabulary rows) gives
+    the single-process logits and the same greedy ids."""
+    import tempfile
+    from .. import distributed as D
+    from ..io.config import tiny_qwen3_config
+    from ..io.synthetic import write_synthetic_gguf
+    from ..models.gguf_oracle import OracleModel, TPOracleModel
+    _init(rank, world)
+    path = os.path.join(tempfile.gettempdir(), f"ptb_tp_oracle_{os.environ['MASTER_PORT']}.gguf")
+    if rank == 0:
+        # 5 FFN blocks of 256: uneven over 2 and 4 ranks; a vocabulary that does not divide by the number of ranks
+        write_synthetic_gguf(path, tiny_qwen3_config(layers=2, hidden=256, heads=8, kv_heads=4, inter=1280, vocab=515), seed=21, device="cpu", std=0.05)
+    D.barrier()
+    prompt = [300, 301, 17, 260, 5, 401]
+    tp = TPOracleModel(path, rank, world, max_seq=64)
+    assert sum([tp.local_inter]) > 0
+    inter = torch.tensor([float(tp.local_inter)])
+    D.all_reduce(inter)
+    assert int(inter) == 1280
+    single = OracleModel(path, max_seq=64)
+    want = single.forward(prompt)
+    got = tp.forward(prompt)
+    assert got.shape == want.shape and torch.allclose(got, want, atol=2e-4, rtol=2e-4), float((got - want).abs().max())
+    cos = torch.nn.functional.cosine_similarity(got[-1], want[-1], dim=0)
+    assert float(cos) > 0.99999
+    ids_tp, ids_one = [], []
+    lt, lo = got, want
+    for _ in range(5):
+        ids_tp.append(int(lt[-1].argmax()))
+        ids_one.append(int(lo[-1].argmax()))
+        lt, lo = tp.forward([ids_one[-1]]), single.forward([ids_one[-1]])
+    assert ids_tp == ids_one, (ids_tp, ids_one)
+    D.barrier()
+    if rank == 0:
+        os.remove(path)
+    _fin()
+    return 0

@@ -28,6 +28,11 @@ def test_context_and_expert_parallel(fn, world):
     assert _launch(fn, world) == 0
 
 
+@pytest.mark.parametrize("world", [2, 4])
+def test_gguf_tensor_parallel_oracle_on_cpu_ranks(world):
+    assert _launch(W.gguf_tp_oracle_matches_single, world) == 0
+
+
 def test_local_sgd():
     assert _launch(W.local_sgd_averages, 2) == 0
 
