@@ -9,7 +9,7 @@ prompt in the model's chat template, ``--profile`` prints per-kernel phase times
 runs tensor-parallel over N processes.  Where the reference's tensor parallelism is CPU-only, here ``--nprocs`` drives
 N GPUs (one process per GPU, re-launched under ``torch.distributed.run``) with the fused GEMV + all-reduce kernels.
 ``--fp16-weights`` and ``--llama-gemv`` select kernels that have no counterpart here and are accepted and ignored.
-``--device cpu`` runs the fp32 oracle (slow; for checking).
+``--device cpu`` runs the fp32 oracle (slow; for checking); with ``--nprocs N`` it runs tensor-parallel over N CPU processes (gloo).
 """
 from __future__ import annotations
 
@@ -111,6 +111,13 @@ def main(argv=None) -> int:
             symm = SymmGroup(dist.group.WORLD, torch.device("cuda", torch.cuda.current_device()))
         model = GGUFModel(path, device=f"cuda:{torch.cuda.current_device()}", max_seq=min(4096, a.max_tokens + 2048), tp_rank=rank,
                           tp_world=world, symm=symm, want_logits=a.temp > 0 or a.repeat_penalty != 1.0)
+        reader, cfg = model.reader, model.cfg
+    elif world > 1:
+        # tensor parallel on CPU ranks (gloo): the sharded fp32 oracle, the shape of the reference's own --nprocs path
+        import torch.distributed as dist
+        from .models.gguf_oracle import TPOracleModel
+        dist.init_process_group("gloo")
+        model = TPOracleModel(path, rank, world, max_seq=min(4096, a.max_tokens + 2048))
         reader, cfg = model.reader, model.cfg
     else:
         from .models.gguf_oracle import OracleModel

@@ -338,3 +338,26 @@ def test_generate_cli_on_the_cpu_oracle(tmp_path, monkeypatch, capsys):
     assert G.main([p, "--info", "--tensors"]) == 0
     out = capsys.readouterr().out
     assert "general.architecture = 'qwen3'" in out and "blk.0.attn_q.weight" in out and "[Tokens]" not in out
+
+
+def test_generate_cli_tensor_parallel_on_cpu_ranks(tmp_path):
+    """`generate --device cpu --nprocs 2`: the CLI re-launches itself under torch.distributed.run and decodes with the sharded
+    oracle over gloo; the ids equal the single-process run's."""
+    import os
+    import subprocess
+    import sys
+    from prometorch_b200.io.config import tiny_qwen3_config
+    from prometorch_b200.io.synthetic import write_synthetic_gguf
+    p = str(tmp_path / "tp.gguf")
+    write_synthetic_gguf(p, tiny_qwen3_config(layers=2, hidden=256, heads=4, kv_heads=2, inter=768, vocab=512), seed=8, device="cpu", std=0.05)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, PT_DEBUG_TOKENS="1", PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    outs = []
+    for extra in ([], ["--nprocs", "2", "--master-port", str(29900 + os.getpid() % 90)]):
+        r = subprocess.run([sys.executable, "-m", "prometorch_b200.generate", p, "t300 t301 t400", "--device", "cpu", "--greedy", "--max-tokens", "4"] + extra,
+                           capture_output=True, text=True, timeout=300, env=env, cwd=root)
+        assert r.returncode == 0, r.stdout[-1000:] + r.stderr[-2000:]
+        line = [ln for ln in r.stdout.splitlines() if ln.startswith("[Tokens] generated")]
+        assert len(line) == 1, r.stdout                                         # only rank 0 prints
+        outs.append(line[0])
+    assert outs[0] == outs[1]
