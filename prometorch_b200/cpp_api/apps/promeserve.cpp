@@ -2,13 +2,15 @@
 //
 //   promeserve --port 11434 --device cuda|cpu --model NAME --workers N --queue-depth N --timeout-ms MS --model-dir DIR
 //
-// The flags are the reference's (promeserve/main.cpp:40-105) plus --host, --model-dir (repeatable), --max-seq and
-// --max-models.  --model is loaded before the port opens and stays resident; it may be a path to a .gguf file (requests may
+// The flags are the reference's (promeserve/main.cpp:40-105) plus --host, --model-dir (repeatable), --max-seq,
+// --max-models and --web-root (the folder whose index.html a browser gets at /; by default web/ beside the program,
+// else ../serve/web, which is where the page sits in the source tree).  --model is loaded before the port opens and stays resident; it may be a path to a .gguf file (requests may
 // only use names).  Build: g++ -std=c++17 -O2 promeserve.cpp -I<cpp_api> -I<cuda>/include -L<lib> -lptb200 -lcudart -lpthread
 #include <csignal>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <unistd.h>
 
 #include "promethorch/gguf_backend.h"
 #include "promethorch/gguf_cpu.h"
@@ -37,12 +39,23 @@ int main(int argc, char** argv) {
         else if (a == "--model-dir") cfg.model_dirs.push_back(val());
         else if (a == "--max-seq") cfg.max_seq = std::atoi(val().c_str());
         else if (a == "--max-models") cfg.max_loaded_models = std::atoi(val().c_str());
+        else if (a == "--web-root") cfg.web_root = val();
         else if (a == "--fp16-weights") {}                       // accepted for compatibility: weights stay in their file format
         else if (a == "--help" || a == "-h") {
             std::printf("usage: promeserve [--host A] [--port N] [--device cuda|cpu] [--model NAME|FILE.gguf] [--workers N] [--queue-depth N]\n"
-                        "                  [--timeout-ms MS] [--model-dir DIR]... [--max-seq N] [--max-models N]\n");
+                        "                  [--timeout-ms MS] [--model-dir DIR]... [--max-seq N] [--max-models N] [--web-root DIR]\n");
             return 0;
         } else { std::fprintf(stderr, "promeserve: unknown flag %s\n", a.c_str()); return 2; }
+    }
+    if (cfg.web_root.empty()) {
+        char exe[4096];
+        const ssize_t n = ::readlink("/proc/self/exe", exe, sizeof exe - 1);
+        if (n > 0) {
+            std::string dir(exe, (size_t)n);
+            dir.resize(dir.find_last_of('/'));
+            for (const char* rel : {"/web", "/../serve/web"})
+                if (ps::store::is_file(dir + rel + "/index.html")) { cfg.web_root = dir + rel; break; }
+        }
     }
     if (cfg.device != "cuda" && cfg.device != "cpu") { std::fprintf(stderr, "promeserve: --device is cuda or cpu\n"); return 2; }
     const bool on_cpu = cfg.device == "cpu";                  // the fp32 reference decoder: for checking and for machines without a GPU

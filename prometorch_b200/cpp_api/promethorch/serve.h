@@ -1,7 +1,7 @@
 // promethorch C++ API: PromeServe, an Ollama-compatible HTTP server (native counterpart of the reference's
 // promeserve/{http_server,api_handlers,model_manager}.h).
 //
-// Routes: GET / (liveness text), GET /api/version, GET /api/tags, GET /api/ps (loaded models and counters), POST /api/show,
+// Routes: GET / (the chat page of web_root for a browser, liveness text otherwise), GET /api/version, GET /api/tags, GET /api/ps (loaded models and counters), POST /api/show,
 // POST /api/generate, POST /api/chat, POST /api/embeddings (501), HEAD, OPTIONS with CORS.  Streaming answers are chunked application/x-ndjson: one object
 // per token ({"model","created_at","response","done":false}, or "message":{"role","content"} for chat) and a final
 // object with total_duration, load_duration, prompt_eval_count, prompt_eval_duration, eval_count, eval_duration in
@@ -91,6 +91,7 @@ struct ServerConfig {
     int max_seq = 4096;
     int max_loaded_models = 2;               // resident at once; the least recently used one is dropped
     size_t max_body_bytes = 8u << 20;        // larger request bodies are answered 413
+    std::string web_root;                    // folder whose index.html answers a browser's GET /; empty = liveness text only
 };
 
 class NotFound : public std::runtime_error {
@@ -688,6 +689,15 @@ class HttpServer {
         bool too_large = false;
     };
     static std::string lower(std::string s) { for (auto& c : s) c = (char)std::tolower((unsigned char)c); return s; }
+    static bool read_file(const std::string& path, std::string& out) {
+        std::FILE* f = std::fopen(path.c_str(), "rb");
+        if (!f) return false;
+        char buf[16384];
+        size_t n;
+        while ((n = std::fread(buf, 1, sizeof buf, f)) > 0) out.append(buf, n);
+        std::fclose(f);
+        return true;
+    }
     static std::string trim(const std::string& s) {
         size_t a = 0, b = s.size();
         while (a < b && std::isspace((unsigned char)s[a])) ++a;
@@ -747,7 +757,15 @@ class HttpServer {
         }
         if (r.method == "OPTIONS") { net::send_response(fd, 204, ""); return; }
         if (r.method == "HEAD") { net::send_response(fd, (r.path == "/" || r.path == "/api/version" || r.path == "/api/tags") ? 200 : 404, ""); return; }
-        if (r.method == "GET" && r.path == "/") { net::send_response(fd, 200, "PromeServe is running", "text/plain"); return; }
+        if (r.method == "GET" && (r.path == "/" || r.path == "/index.html")) {
+            // a browser gets the chat page (the reference serves promeserve/web/index.html, api_handlers.h:400-430); other clients the liveness text
+            const bool wants_page = r.path != "/" || r.headers["accept"].find("text/html") != std::string::npos;
+            std::string page;
+            if (wants_page && !cfg_.web_root.empty() && read_file(cfg_.web_root + "/index.html", page)) net::send_response(fd, 200, page, "text/html; charset=utf-8");
+            else if (r.path != "/") net::send_response(fd, 404, error_json("not found"));
+            else net::send_response(fd, 200, "PromeServe is running", "text/plain");
+            return;
+        }
         if (r.method == "GET" && r.path == "/api/version") {
             json::Value o = json::Value::object();
             o.set("version", version());

@@ -19,10 +19,11 @@ def main():
     ap.add_argument("--allow-model-paths", action="store_true", help="let requests name models by filesystem path")
     ap.add_argument("--fp16-weights", "--fp16_weights", action="store_true",
                     help="accepted for compatibility with the reference's CLI: weights stay in their file format here")
+    ap.add_argument("--web-root", default=None, help="folder whose index.html a browser gets at /; default: the page shipped with the package")
     a = ap.parse_args()
     # --model comes from the operator, so it may be a path even when requests may not name paths
     cfg = ServerConfig(a.host, a.port, a.workers, a.queue_depth, a.timeout_ms, a.device, None, a.model_dir, a.max_seq,
-                       a.max_models, allow_model_paths=True)
+                       a.max_models, allow_model_paths=True, web_root=a.web_root)
     srv = PromeServe(cfg)
     if a.model:
         srv.handlers.ensure_model(a.model)

@@ -1,7 +1,7 @@
 """PromeServe: an Ollama-compatible HTTP server in front of the native decode engine.
 
 Routes and wire format follow promeserve/api_handlers.h:351-394 and http_server.h of the reference:
-``GET /`` (liveness text), ``GET /api/version``, ``GET /api/tags``, ``GET /api/ps`` (loaded models and counters), ``POST /api/show``,
+``GET /`` (the chat page of ``serve/web`` for a browser, liveness text otherwise), ``GET /api/version``, ``GET /api/tags``, ``GET /api/ps`` (loaded models and counters), ``POST /api/show``,
 ``POST /api/generate``, ``POST /api/chat``, ``POST /api/embeddings`` (501), ``HEAD``/``OPTIONS`` with CORS.
 Streaming responses are chunked ``application/x-ndjson``: one object per token
 (``{"model","created_at","response","done":false}`` or, for chat, ``"message":{"role","content"}``) and a
@@ -41,6 +41,7 @@ class ServerConfig:
     max_loaded_models: int = 2          # models resident on the GPU at once; the least recently used one is dropped
     max_body_bytes: int = 8 << 20       # larger request bodies are answered 413
     allow_model_paths: bool = False     # let a request name a model by filesystem path (off: names only)
+    web_root: Optional[str] = None      # folder whose index.html answers a browser's GET /; None = the page shipped in serve/web
 
 
 def _now() -> str:
@@ -528,6 +529,16 @@ class HttpServer:
         body = rfile.read(n) if n else b""
         return method.upper(), path.split("?")[0], headers, body
 
+    def _web_page(self) -> Optional[bytes]:
+        """index.html of the configured folder, or None when there is none (read per request: the page can be edited live)."""
+        import os
+        root = self.config.web_root or os.path.join(os.path.dirname(os.path.abspath(__file__)), "web")
+        try:
+            with open(os.path.join(root, "index.html"), "rb") as f:
+                return f.read()
+        except OSError:
+            return None
+
     @staticmethod
     def _send(wfile, status: int, body: bytes, ctype="application/json", extra=None):
         reason = HTTPStatus(status).phrase
@@ -550,7 +561,13 @@ class HttpServer:
             return self._send(wfile, 204, b"")
         if method == "HEAD":
             return self._send(wfile, 200 if path in ("/", "/api/version", "/api/tags") else 404, b"")
-        if method == "GET" and path == "/":
+        if method == "GET" and path in ("/", "/index.html"):
+            # a browser gets the chat page (the reference serves promeserve/web/index.html, api_handlers.h:400-430); other clients the liveness text
+            page = self._web_page() if (path != "/" or "text/html" in headers.get("accept", "")) else None
+            if page is not None:
+                return self._send(wfile, 200, page, "text/html; charset=utf-8")
+            if path != "/":
+                return self._send(wfile, 404, json.dumps({"error": "not found"}).encode())
             return self._send(wfile, 200, b"PromeServe is running", "text/plain")
         if method == "GET" and path == "/api/version":
             return self._send(wfile, 200, json.dumps({"version": VERSION}).encode())

@@ -664,6 +664,14 @@ def test_native_programs_run_on_the_cpu(tmp_path):
         out = json.loads(data)
         assert st == 200 and out["eval_count"] == len(want) and out["response"] == "".join(tok.decode_token(t) for t in want)
         assert any(m["name"] == "prog" for m in json.loads(_req(port, "GET", "/api/ps")[2])["models"])
+        # a browser gets the chat page shipped in serve/web (found relative to the program); anything else the liveness text
+        c = http.client.HTTPConnection("127.0.0.1", port, timeout=30)
+        c.request("GET", "/", None, {"Accept": "text/html,application/xhtml+xml"})
+        r = c.getresponse()
+        page = r.read()
+        c.close()
+        assert r.status == 200 and r.getheader("Content-Type").startswith("text/html") and b"/api/chat" in page and b"/api/tags" in page
+        assert _req(port, "GET", "/")[2] == b"PromeServe is running"
     finally:
         p.terminate()
         try:

@@ -62,6 +62,36 @@ def test_basic_routes(server):
     assert st == 204 and hdr.get("Access-Control-Allow-Origin") == "*"
 
 
+def test_chat_page_for_browsers(tmp_path):
+    """GET / with ``Accept: text/html`` answers the chat page (the shipped one, or ``web_root``'s); other clients keep the liveness text."""
+    def get(port, path, accept=None):
+        c = http.client.HTTPConnection("127.0.0.1", port, timeout=20)
+        c.request("GET", path, None, {"Accept": accept} if accept else {})
+        r = c.getresponse()
+        data = r.read()
+        c.close()
+        return r.status, r.getheader("Content-Type"), data
+    srv = PromeServe(ServerConfig(host="127.0.0.1", port=0, worker_threads=2), {"echo:1b": EchoBackend()}).start()
+    try:
+        st, ct, page = get(srv.port, "/", "text/html,application/xhtml+xml")
+        assert st == 200 and ct.startswith("text/html") and b"/api/chat" in page and b"/api/tags" in page and b"<script src" not in page
+        assert get(srv.port, "/index.html")[1].startswith("text/html")
+        assert get(srv.port, "/")[2] == b"PromeServe is running" and get(srv.port, "/", "application/json")[2] == b"PromeServe is running"
+    finally:
+        srv.stop()
+    (tmp_path / "index.html").write_text("<html>mine</html>")
+    srv = PromeServe(ServerConfig(host="127.0.0.1", port=0, worker_threads=2, web_root=str(tmp_path)), {"echo:1b": EchoBackend()}).start()
+    try:
+        assert get(srv.port, "/", "text/html")[2] == b"<html>mine</html>"
+    finally:
+        srv.stop()
+    srv = PromeServe(ServerConfig(host="127.0.0.1", port=0, worker_threads=2, web_root=str(tmp_path / "absent")), {"echo:1b": EchoBackend()}).start()
+    try:
+        assert get(srv.port, "/", "text/html")[2] == b"PromeServe is running" and get(srv.port, "/index.html")[0] == 404
+    finally:
+        srv.stop()
+
+
 def test_generate_non_streaming_and_options(server):
     srv, be = server
     st, _, data = _req(srv.port, "POST", "/api/generate", {"model": "echo:1b", "prompt": "hi", "stream": False, "raw": True,
