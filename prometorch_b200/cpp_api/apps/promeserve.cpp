@@ -4,8 +4,10 @@
 //
 // The flags are the reference's (promeserve/main.cpp:40-105) plus --host, --model-dir (repeatable), --max-seq,
 // --max-models and --web-root (the folder whose index.html a browser gets at /; by default web/ beside the program,
-// else ../serve/web, which is where the page sits in the source tree).  --model is loaded before the port opens and stays resident; it may be a path to a .gguf file (requests may
-// only use names).  Build: g++ -std=c++17 -O2 promeserve.cpp -I<cpp_api> -I<cuda>/include -L<lib> -lptb200 -lcudart -lpthread
+// else ../serve/web, which is where the page sits in the source tree).  --model is loaded before the port opens and stays
+// resident; it may be a path to a .gguf file or, with --device cpu, to a Hugging Face directory (config.json, safetensors,
+// tokenizer files); requests may only use names.
+// Build: g++ -std=c++17 -O2 promeserve.cpp -I<cpp_api> -I<cuda>/include -L<lib> -lptb200 -lcudart -lpthread
 #include <csignal>
 #include <cstdio>
 #include <cstdlib>
@@ -61,12 +63,15 @@ int main(int argc, char** argv) {
     const bool on_cpu = cfg.device == "cpu";                  // the fp32 reference decoder: for checking and for machines without a GPU
     auto make = [&](const std::string& path, const std::string& name) -> std::shared_ptr<ps::ModelBackend> {
         if (on_cpu) return std::make_shared<ps::CpuBackend>(path, name, cfg.max_seq);
+        if (ps::store::is_dir(path))
+            throw std::runtime_error(path + " is a Hugging Face directory: this program serves those with --device cpu (on a GPU, python -m prometorch_b200.serve does)");
         return std::make_shared<ps::GGUFBackend>(path, name, cfg.max_seq);
     };
     try {
         ps::PromeServe srv(cfg, [&](const std::string& name) { return make(ps::store::resolve(name, cfg.model_dirs), name); });
         if (!model.empty()) {
-            if (ps::store::is_file(model)) {
+            if (ps::store::is_file(model) || ps::store::is_file(model + "/config.json")) {     // a .gguf file, or a Hugging Face directory
+                while (model.size() > 1 && model.back() == '/') model.pop_back();
                 std::string name = model.substr(model.find_last_of('/') + 1);
                 if (name.size() > 5 && name.compare(name.size() - 5, 5, ".gguf") == 0) name.resize(name.size() - 5);
                 srv.handlers().add_backend(name, make(model, name));

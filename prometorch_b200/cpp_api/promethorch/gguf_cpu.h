@@ -2,8 +2,10 @@
 //
 //   io::GGUFCpuModel     load(path) / forward(token, pos) -> logits / generate(prompt, n): fp32 math over the quantised
 //                        blocks of the file (dequantised on the fly, row by row, from the memory map), fp16-rounded
-//                        key / value cache, rows of every projection spread over the machine's threads
-//   serve::CpuBackend    ModelBackend (serve.h) = GGUFCpuModel + the file's tokenizer + sampling on the host
+//                        key / value cache, rows of every projection spread over the machine's threads.  `path` may also
+//                        be a Hugging Face directory (config.json + *.safetensors in F32 / F16 / BF16, sharded or not):
+//                        the tensors are read in place from the mapped files under their Hugging Face names
+//   serve::CpuBackend    ModelBackend (serve.h) = GGUFCpuModel + the file's (or the directory's) tokenizer + sampling on the host
 //
 // This is the reference path of the native programs (`--device cpu`): the same computation as the fp32 oracle of the Python
 // package (models/gguf_oracle.py) and as the reference's CPU decode (torch/io/gguf_model.h:7300-7340), for checking and for
@@ -15,14 +17,21 @@
 #include <cmath>
 #include <cstdint>
 #include <cstring>
+#include <fcntl.h>
 #include <functional>
+#include <map>
+#include <memory>
 #include <random>
 #include <set>
 #include <string>
+#include <sys/mman.h>
+#include <sys/stat.h>
 #include <thread>
+#include <unistd.h>
 #include <vector>
 
 #include "gguf_reader.h"
+#include "model_loader.h"
 #include "serve.h"
 #include "tokenizer.h"
 
@@ -147,10 +156,11 @@ class GGUFCpuModel {
     TransformerConfig config;
 
     void load(const std::string& path, int max_seq = 4096, int threads = 0) {
+        threads_ = threads > 0 ? threads : (int)std::max(1u, std::thread::hardware_concurrency());
+        if (loader::detail::is_dir(path) || loader::detect_format(path) == "safetensors") { load_hf(path, max_seq); return; }
         reader_.open(path);
         config.parse(reader_);
         max_seq_ = std::min(max_seq, config.context_length);
-        threads_ = threads > 0 ? threads : (int)std::max(1u, std::thread::hardware_concurrency());
         const auto& c = config;
         layers_.assign((size_t)c.num_layers, Layer());
         for (int l = 0; l < c.num_layers; ++l) {
@@ -168,17 +178,12 @@ class GGUFCpuModel {
         embed_ = mat("token_embd.weight");
         head_ = c.tie_word_embeddings ? embed_ : mat("output.weight");
         out_norm_ = vec("output_norm.weight");
-        const int half = c.head_dim / 2;
-        cos_.assign((size_t)max_seq_ * half, 0.f);
-        sin_.assign((size_t)max_seq_ * half, 0.f);
-        for (int i = 0; i < half; ++i) {
-            const double inv = std::pow(c.rope_freq_base, -2.0 * i / c.head_dim);
-            for (int p = 0; p < max_seq_; ++p) { cos_[(size_t)p * half + i] = (float)std::cos(p * inv); sin_[(size_t)p * half + i] = (float)std::sin(p * inv); }
-        }
-        logits_.assign((size_t)c.vocab_size, 0.f);
+        finish_load();
     }
     int max_seq() const { return max_seq_; }
-    const gguf::GGUFReader& reader() const { return reader_; }
+    bool from_hf() const { return !hf_.tensors.empty(); }
+    const gguf::GGUFReader& reader() const { return reader_; }                 // of a GGUF file (empty for a Hugging Face directory)
+    const loader::ModelWeights& hf_weights() const { return hf_; }             // of a Hugging Face directory (empty for a GGUF file)
 
     // One token at position `pos` (positions must be fed in order from 0): the logits of the next token.
     const std::vector<float>& forward(int token, int pos) {
@@ -260,6 +265,115 @@ class GGUFCpuModel {
         Matrix q, k, v, o, gate, up, down;
         std::vector<float> attn_norm, ffn_norm, q_norm, k_norm, qb, kb, vb, kc, vc;
     };
+    // A read-only mapping of one weight file of a Hugging Face directory.
+    struct Mapped {
+        const uint8_t* base = nullptr;
+        size_t size = 0;
+        Mapped() = default;
+        Mapped(const Mapped&) = delete;
+        Mapped& operator=(const Mapped&) = delete;
+        ~Mapped() { if (base) ::munmap((void*)base, size); }
+        void open(const std::string& path) {
+            const int fd = ::open(path.c_str(), O_RDONLY);
+            if (fd < 0) throw std::runtime_error("GGUFCpuModel: cannot open " + path);
+            struct stat st;
+            if (::fstat(fd, &st) != 0 || st.st_size <= 0) { ::close(fd); throw std::runtime_error("GGUFCpuModel: cannot size " + path); }
+            size = (size_t)st.st_size;
+            void* p = ::mmap(nullptr, size, PROT_READ, MAP_PRIVATE, fd, 0);
+            ::close(fd);
+            if (p == MAP_FAILED) throw std::runtime_error("GGUFCpuModel: mmap failed for " + path);
+            base = (const uint8_t*)p;
+        }
+    };
+    void finish_load() {
+        const auto& c = config;
+        const int half = c.head_dim / 2;
+        cos_.assign((size_t)max_seq_ * half, 0.f);
+        sin_.assign((size_t)max_seq_ * half, 0.f);
+        for (int i = 0; i < half; ++i) {
+            const double inv = std::pow(c.rope_freq_base, -2.0 * i / c.head_dim);
+            for (int p = 0; p < max_seq_; ++p) { cos_[(size_t)p * half + i] = (float)std::cos(p * inv); sin_[(size_t)p * half + i] = (float)std::sin(p * inv); }
+        }
+        logits_.assign((size_t)c.vocab_size, 0.f);
+    }
+    // A Hugging Face directory (or one .safetensors file beside its config.json): Llama-family names
+    // (model.layers.N.self_attn.q_proj.weight ...), rotary halves split as in the checkpoint (first half / second half).
+    void load_hf(const std::string& path, int max_seq) {
+        hf_ = loader::load_model(path);
+        const loader::ModelConfig& m = hf_.config;
+        const std::string& a = hf_.architecture;
+        if (!(a == "llama" || a == "mistral" || a == "qwen2" || a == "qwen3"))
+            throw std::runtime_error("GGUFCpuModel: architecture '" + a + "' of " + path + " is not a dense Llama-family decoder");
+        pre_ = hf_.tensors.count("model.embed_tokens.weight") ? "model." : "";
+        if (!hf_.tensors.count(pre_ + "embed_tokens.weight")) throw std::runtime_error("GGUFCpuModel: no embed_tokens.weight in " + path);
+        config.architecture = a;
+        config.hidden_size = (int)m.hidden_size; config.num_layers = (int)m.num_layers; config.num_heads = (int)m.num_heads;
+        config.num_kv_heads = (int)(m.num_kv_heads ? m.num_kv_heads : m.num_heads); config.intermediate_size = (int)m.intermediate_size;
+        config.head_dim = (int)(m.head_dim ? m.head_dim : m.hidden_size / std::max<int64_t>(m.num_heads, 1));
+        config.context_length = m.context_length > 0 ? (int)m.context_length : 8192;
+        config.rope_freq_base = m.rope_freq_base; config.rms_norm_eps = m.rms_norm_eps;
+        config.vocab_size = (int)hf_.tensors.at(pre_ + "embed_tokens.weight").shape.at(0);
+        config.tie_word_embeddings = !hf_.tensors.count("lm_head.weight");
+        config.rope_neox = true;
+        config.has_qk_norm = hf_.tensors.count(pre_ + "layers.0.self_attn.q_norm.weight") > 0;
+        if (config.hidden_size <= 0 || config.num_layers <= 0 || config.num_heads <= 0 || config.intermediate_size <= 0)
+            throw std::runtime_error("GGUFCpuModel: " + path + " has no usable config.json");
+        max_seq_ = std::min(max_seq, config.context_length);
+        const auto& c = config;
+        layers_.assign((size_t)c.num_layers, Layer());
+        for (int l = 0; l < c.num_layers; ++l) {
+            const std::string p = pre_ + "layers." + std::to_string(l) + ".";
+            Layer& L = layers_[(size_t)l];
+            L.q = hf_mat(p + "self_attn.q_proj.weight"); L.k = hf_mat(p + "self_attn.k_proj.weight"); L.v = hf_mat(p + "self_attn.v_proj.weight");
+            L.o = hf_mat(p + "self_attn.o_proj.weight");
+            L.gate = hf_mat(p + "mlp.gate_proj.weight"); L.up = hf_mat(p + "mlp.up_proj.weight"); L.down = hf_mat(p + "mlp.down_proj.weight");
+            L.attn_norm = hf_vec(p + "input_layernorm.weight"); L.ffn_norm = hf_vec(p + "post_attention_layernorm.weight");
+            if (c.has_qk_norm) { L.q_norm = hf_vec(p + "self_attn.q_norm.weight"); L.k_norm = hf_vec(p + "self_attn.k_norm.weight"); }
+            if (hf_.tensors.count(p + "self_attn.q_proj.bias")) {
+                L.qb = hf_vec(p + "self_attn.q_proj.bias"); L.kb = hf_vec(p + "self_attn.k_proj.bias"); L.vb = hf_vec(p + "self_attn.v_proj.bias");
+            }
+            L.kc.assign((size_t)max_seq_ * c.num_kv_heads * c.head_dim, 0.f);
+            L.vc.assign((size_t)max_seq_ * c.num_kv_heads * c.head_dim, 0.f);
+        }
+        embed_ = hf_mat(pre_ + "embed_tokens.weight");
+        head_ = c.tie_word_embeddings ? embed_ : hf_mat("lm_head.weight");
+        out_norm_ = hf_vec(pre_ + "norm.weight");
+        finish_load();
+    }
+    const uint8_t* hf_bytes(const loader::TensorInfo& t, uint32_t& type) {
+        if (t.dtype == "f32") type = gguf::F32;
+        else if (t.dtype == "f16") type = gguf::F16;
+        else if (t.dtype == "bf16") type = gguf::BF16;
+        else throw std::runtime_error("GGUFCpuModel: " + t.name + " has dtype " + t.dtype + " (F32, F16 and BF16 are read)");
+        auto& mp = maps_[t.file];
+        if (!mp) { mp.reset(new Mapped()); mp->open(t.file); }
+        const size_t width = type == gguf::F32 ? 4 : 2;
+        if (t.nbytes != (uint64_t)t.numel() * width || t.offset + t.nbytes > mp->size) throw std::runtime_error("GGUFCpuModel: " + t.name + " lies outside " + t.file);
+        return mp->base + t.offset;
+    }
+    Matrix hf_mat(const std::string& name) {
+        auto it = hf_.tensors.find(name);
+        if (it == hf_.tensors.end()) throw std::runtime_error("GGUFCpuModel: no tensor " + name);
+        if (it->second.shape.size() != 2) throw std::runtime_error("GGUFCpuModel: " + name + " is not a matrix");
+        Matrix m;
+        m.data = hf_bytes(it->second, m.type);
+        m.rows = (int)it->second.shape[0];
+        m.cols = (int)it->second.shape[1];
+        m.block_elems = 1;
+        m.block_bytes = m.type == gguf::F32 ? 4 : 2;
+        m.row_bytes = (size_t)m.cols * m.block_bytes;
+        return m;
+    }
+    std::vector<float> hf_vec(const std::string& name) {
+        auto it = hf_.tensors.find(name);
+        if (it == hf_.tensors.end()) throw std::runtime_error("GGUFCpuModel: no tensor " + name);
+        uint32_t type = 0;
+        const uint8_t* p = hf_bytes(it->second, type);
+        const int bb = type == gguf::F32 ? 4 : 2;
+        std::vector<float> out((size_t)it->second.numel());
+        for (size_t i = 0; i < out.size(); ++i) cpu_detail::dequant_block(type, p + i * bb, &out[i]);
+        return out;
+    }
     Matrix mat(const std::string& name) {
         const auto& t = reader_.tensor(name);
         if (t.shape.size() != 2) throw std::runtime_error("GGUFCpuModel: " + name + " is not a matrix");
@@ -301,6 +415,13 @@ class GGUFCpuModel {
             for (int r = r0; r < r1; ++r) {
                 const uint8_t* p = m.data + (size_t)r * m.row_bytes;
                 double acc = 0;
+                if (m.block_elems == 1) {                      // plain F32 / F16 / BF16 rows: the same products and sums without the per-block call
+                    if (m.type == gguf::F32) for (int c = 0; c < m.cols; ++c) { float w; std::memcpy(&w, p + 4 * (size_t)c, 4); acc += w * x[c]; }
+                    else if (m.type == gguf::F16) for (int c = 0; c < m.cols; ++c) acc += cpu_detail::half_to_float(cpu_detail::rd16(p + 2 * (size_t)c)) * x[c];
+                    else for (int c = 0; c < m.cols; ++c) { const uint32_t b = (uint32_t)cpu_detail::rd16(p + 2 * (size_t)c) << 16; float w; std::memcpy(&w, &b, 4); acc += w * x[c]; }
+                    y[r] = (float)acc;
+                    continue;
+                }
                 for (int c = 0; c < m.cols; c += m.block_elems, p += m.block_bytes) {
                     const int n = cpu_detail::dequant_block(m.type, p, tmp);
                     float part = 0;
@@ -334,6 +455,9 @@ class GGUFCpuModel {
     gguf::GGUFReader reader_;
     std::vector<Layer> layers_;
     Matrix embed_, head_;
+    loader::ModelWeights hf_;
+    std::string pre_;
+    std::map<std::string, std::unique_ptr<Mapped>> maps_;
     std::vector<float> out_norm_, cos_, sin_, logits_;
     int max_seq_ = 0, threads_ = 1;
 };
@@ -348,15 +472,33 @@ class CpuBackend : public ModelBackend {
  public:
     CpuBackend(const std::string& path, const std::string& name_, int max_seq = 4096) {
         model_.load(path, max_seq);
-        tok_ = io::GGUFTokenizer::from_reader(model_.reader());
         name = name_;
         architecture = model_.config.architecture;
-        model_name = model_.reader().has("general.name") ? model_.reader().get("general.name").s : "";
-        size = store::file_size(path);
-        unsigned long long bytes = 0;
-        for (const auto& kv : model_.reader().tensors()) bytes += kv.second.nbytes;
         char buf[32];
-        std::snprintf(buf, sizeof buf, "%.1fB", (double)bytes / 0.5625 / 1e9);
+        if (model_.from_hf()) {
+            // a Hugging Face directory: its byte-level BPE files, the end-of-sequence ids of config.json / generation_config.json
+            namespace L = io::loader::detail;
+            const std::string dir = L::is_dir(path) ? path : L::dirname(path);
+            if (!io::load_hf_tokenizer(dir, tok_)) throw std::runtime_error("CpuBackend: " + dir + " has neither vocab.json + merges.txt nor tokenizer.json");
+            model_name = L::basename(dir);
+            size = 0;
+            for (const auto& f : model_.hf_weights().files) size += store::file_size(f);
+            std::snprintf(buf, sizeof buf, "%.1fB", (double)model_.hf_weights().total_parameters() / 1e9);
+            for (const char* f : {"/generation_config.json", "/config.json"}) {
+                if (!L::is_file(dir + f)) continue;
+                const json::Value e = json::parse(L::slurp(dir + f))["eos_token_id"];
+                if (e.is_number()) stop_.insert((int)e.as_int());
+                if (e.is_array()) for (const auto& v : e.items()) if (v.is_number()) stop_.insert((int)v.as_int());
+                if (!stop_.empty()) break;
+            }
+        } else {
+            tok_ = io::GGUFTokenizer::from_reader(model_.reader());
+            model_name = model_.reader().has("general.name") ? model_.reader().get("general.name").s : "";
+            size = store::file_size(path);
+            unsigned long long bytes = 0;
+            for (const auto& kv : model_.reader().tensors()) bytes += kv.second.nbytes;
+            std::snprintf(buf, sizeof buf, "%.1fB", (double)bytes / 0.5625 / 1e9);
+        }
         parameter_size = buf;
         if (tok_.eos_id() >= 0) stop_.insert(tok_.eos_id());
         for (const char* t : {"<|im_end|>", "<|eot_id|>", "<end_of_turn>", "<|end|>", "<|endoftext|>"})

@@ -149,7 +149,7 @@ int main(int argc, char** argv) {
             std::cout << out.dump() << "\n";
             return 0;
         }
-        if (mode == "cpu-generate") {                // FILE N id id id ...: greedy ids and a few logits of the CPU decoder
+        if (mode == "cpu-generate") {                // FILE|DIR N id id id ...: greedy ids and a few logits of the CPU decoder
             pio::GGUFCpuModel m;
             m.load(argv[2], 256);
             const int n_new = std::atoi(argv[3]);

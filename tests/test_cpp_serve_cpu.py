@@ -678,3 +678,91 @@ def test_native_programs_run_on_the_cpu(tmp_path):
             p.wait(timeout=20)
         except subprocess.TimeoutExpired:
             p.kill()
+
+
+def test_native_cpu_decoder_reads_hugging_face_directories(exe, tmp_path):
+    """gguf_cpu.h on a Hugging Face directory (config.json + safetensors, read in place): logits and greedy ids of transformers' own
+    modules on the same weights, for Llama (F32, sharded), Qwen2 (biases, BF16) and Qwen3 (query / key norms, F16, tied head); then
+    `lib/gguf_generate DIR --device cpu` end to end with the directory's tokenizer files."""
+    transformers = pytest.importorskip("transformers")
+    from prometorch_b200.io.safetensors import save_file
+    prompt = [1, 17, 93, 4, 55]
+    common = dict(vocab_size=400, hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, intermediate_size=96,
+                  max_position_embeddings=128, rms_norm_eps=1e-5)
+    cases = (("llama", transformers.LlamaConfig(**common, tie_word_embeddings=False), transformers.LlamaForCausalLM, torch.float32),
+             ("qwen2", transformers.Qwen2Config(**common, tie_word_embeddings=False), transformers.Qwen2ForCausalLM, torch.bfloat16),
+             ("qwen3", transformers.Qwen3Config(**common, head_dim=32, tie_word_embeddings=True), transformers.Qwen3ForCausalLM, torch.float16))
+    refs = {}
+    for tag, cfg, cls, dtype in cases:
+        torch.manual_seed(5)
+        ref = refs[tag] = cls(cfg).eval()
+        with torch.no_grad():
+            for n, p in ref.named_parameters():
+                if n.endswith("bias") or "norm" in n:
+                    p.add_(0.1 * torch.randn_like(p))                  # biases start at zero and norms at one: make them count
+                p.copy_(p.to(dtype).float())                           # the values the file will hold
+        d = tmp_path / tag
+        d.mkdir()
+        cfg.save_pretrained(str(d))
+        sd = {k: v.to(dtype).contiguous() for k, v in ref.state_dict().items() if not (cfg.tie_word_embeddings and k == "lm_head.weight")}
+        if tag == "llama":                                             # two shards with an index
+            names = sorted(sd)
+            parts = {"model-00001-of-00002.safetensors": names[:len(names) // 2], "model-00002-of-00002.safetensors": names[len(names) // 2:]}
+            for fn, ks in parts.items():
+                save_file({k: sd[k] for k in ks}, str(d / fn))
+            (d / "model.safetensors.index.json").write_text(json.dumps({"metadata": {}, "weight_map": {k: fn for fn, ks in parts.items() for k in ks}}))
+        else:
+            save_file(sd, str(d / "model.safetensors"))
+        got = _run(exe, "cpu-generate", str(d), "8", *[str(t) for t in prompt])
+        with torch.no_grad():
+            lg = ref(torch.tensor([prompt + [prompt[-1]]])).logits[0, -1]
+            want = ref.generate(torch.tensor([prompt]), max_new_tokens=8, do_sample=False, eos_token_id=None, pad_token_id=0)[0, len(prompt):].tolist()
+        assert torch.allclose(torch.tensor(got["probe_logits"]), lg[:24], atol=3e-3, rtol=3e-3), (tag, got["probe_logits"][:4], lg[:4])
+        assert got["probe_argmax"] == int(lg.argmax()) and got["ids"] == want, (tag, got["ids"], want)
+    # the shipped program on the Llama directory: tokenizer files of the directory, greedy ids of transformers
+    if shutil.which("nvcc") is None and not os.path.exists("/usr/local/cuda/bin/nvcc"):
+        return
+    from prometorch_b200 import _build
+    from prometorch_b200.serve.llm import load_hf_tokenizer
+    d = tmp_path / "llama"
+    tokens, merges = _train_bpe(" ".join(TEXTS) + " the quick brown fox jumps over the lazy dog " * 10, 100)
+    assert len(tokens) <= 400
+    (d / "vocab.json").write_text(json.dumps({t: i for i, t in enumerate(tokens)}))
+    (d / "merges.txt").write_text("#version: 0.2\n" + "\n".join(merges) + "\n")
+    text = "the quick brown fox"
+    ids = load_hf_tokenizer(str(d)).encode(text)
+    r = subprocess.run([str(_build.build_generate()), str(d), text, "--device", "cpu", "--greedy", "--max-tokens", "6"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    got_ids = [int(x) for x in [ln for ln in r.stdout.splitlines() if ln.startswith("[Ids]")][0].split()[1:]]
+    ref = refs["llama"]
+    with torch.no_grad():
+        want = ref.generate(torch.tensor([ids]), max_new_tokens=6, do_sample=False, eos_token_id=None, pad_token_id=0)[0, len(ids):].tolist()
+    eos = ref.config.eos_token_id
+    want = want[:want.index(eos) + 1] if eos in want else want
+    assert got_ids == want and f"Prompt tokens: {len(ids)}" in r.stdout, (got_ids, want, r.stdout[-500:])
+    # and the server program with the directory as its model
+    tok = load_hf_tokenizer(str(d))
+    p = subprocess.Popen([str(_build.build_promeserve()), "--device", "cpu", "--model", str(d) + "/", "--port", "0", "--max-seq", "128"], stdout=subprocess.PIPE,
+                         stderr=subprocess.PIPE, text=True)
+    try:
+        port = None
+        for _ in range(50):
+            line = p.stdout.readline()
+            if not line:
+                break
+            if "listening on" in line:
+                port = int(line.split(":")[-1].split()[0])
+                break
+        assert port, p.stderr.read()[-2000:]
+        st, _, data = _req(port, "POST", "/api/generate", {"model": "llama", "prompt": text, "raw": True, "stream": False,
+                                                         "options": {"num_predict": 6, "temperature": 0.0, "repeat_penalty": 1.0}})
+        out = json.loads(data)
+        assert st == 200 and out["prompt_eval_count"] == len(ids) and out["response"] == "".join(tok.decode_token(t) for t in want), out
+        tags = json.loads(_req(port, "GET", "/api/tags")[2])["models"]
+        assert any(m["name"] == "llama" and m["details"]["family"] == "llama" for m in tags), tags
+    finally:
+        p.terminate()
+        try:
+            p.wait(timeout=20)
+        except subprocess.TimeoutExpired:
+            p.kill()
