@@ -9,8 +9,8 @@
 //
 // This is the reference path of the native programs (`--device cpu`): the same computation as the fp32 oracle of the Python
 // package (models/gguf_oracle.py) and as the reference's CPU decode (torch/io/gguf_model.h:7300-7340), for checking and for
-// machines without a GPU; it is not fast.  Dense decoders only (llama, mistral, qwen2, qwen3) with F32 / F16 / BF16 / Q8_0 /
-// Q4_K / Q5_K / Q6_K tensors.
+// machines without a GPU; it is not fast.  Dense decoders only (llama, mistral, qwen2, qwen3) with F32 / F16 / BF16 / Q4_0 /
+// Q8_0 / Q2_K / Q3_K / Q4_K / Q5_K / Q6_K tensors.
 #pragma once
 #include <algorithm>
 #include <chrono>
@@ -100,6 +100,42 @@ inline int dequant_block(uint32_t type, const uint8_t* p, float* y) {
             const int8_t* q = (const int8_t*)(p + 2);
             for (int i = 0; i < 32; ++i) y[i] = d * q[i];
             return 32;
+        }
+        case gguf::Q4_0: {                                   // fp16 d | 16 bytes: low nibbles are values 0-15, high nibbles 16-31, stored plus 8
+            const float d = half_to_float(rd16(p));
+            for (int i = 0; i < 16; ++i) { y[i] = d * ((int)(p[2 + i] & 0xF) - 8); y[i + 16] = d * ((int)(p[2 + i] >> 4) - 8); }
+            return 32;
+        }
+        case gguf::Q2_K: {                                   // scales[16] (low nibble scale, high nibble min, per 16 values) | qs[64] | fp16 d | fp16 dmin
+            const uint8_t *sc = p, *qs = p + 16;
+            const float d = half_to_float(rd16(p + 80)), dmin = half_to_float(rd16(p + 82));
+            for (int half = 0; half < 2; ++half)             // 128 values use 32 bytes; the four bit planes give 32 values each
+                for (int plane = 0; plane < 4; ++plane)
+                    for (int l = 0; l < 32; ++l) {
+                        const int idx = half * 128 + plane * 32 + l, grp = idx / 16;
+                        const int q = (qs[half * 32 + l] >> (2 * plane)) & 3;
+                        y[idx] = d * (float)(sc[grp] & 0xF) * (float)q - dmin * (float)(sc[grp] >> 4);
+                    }
+            return 256;
+        }
+        case gguf::Q3_K: {                                   // hmask[32] | qs[64] (low two bits, planes as in Q2_K) | scales[12] (sixteen 6-bit, minus 32) | fp16 d
+            const uint8_t *hm = p, *qs = p + 32, *sr = p + 96;
+            const float d = half_to_float(rd16(p + 108));
+            int scales[16];
+            for (int j = 0; j < 16; ++j) {
+                const int lo = j < 8 ? (sr[j] & 0xF) : (sr[j - 8] >> 4);
+                const int hi = (sr[8 + (j % 4)] >> (2 * (j / 4))) & 3;
+                scales[j] = (lo | (hi << 4)) - 32;
+            }
+            for (int half = 0; half < 2; ++half)
+                for (int plane = 0; plane < 4; ++plane)
+                    for (int l = 0; l < 32; ++l) {
+                        const int idx = half * 128 + plane * 32 + l;
+                        const int low2 = (qs[half * 32 + l] >> (2 * plane)) & 3;
+                        const int high = (hm[l] >> (half * 4 + plane)) & 1;
+                        y[idx] = d * (float)scales[idx / 16] * (float)(low2 - (high ? 0 : 4));
+                    }
+            return 256;
         }
         case gguf::Q4_K: {
             const float d = half_to_float(rd16(p)), dmin = half_to_float(rd16(p + 2));

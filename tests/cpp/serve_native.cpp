@@ -149,6 +149,21 @@ int main(int argc, char** argv) {
             std::cout << out.dump() << "\n";
             return 0;
         }
+        if (mode == "dequant") {                     // TYPE FILE: the file's bytes as consecutive blocks of that GGML type, dequantised
+            const uint32_t type = (uint32_t)std::atoi(argv[2]);
+            std::ifstream f(argv[3], std::ios::binary);
+            std::vector<uint8_t> raw((std::istreambuf_iterator<char>(f)), std::istreambuf_iterator<char>());
+            int be, bb;
+            pio::gguf::block_geometry(type, be, bb);
+            pj::Value out = pj::Value::array();
+            float y[256];
+            for (size_t o = 0; o + (size_t)bb <= raw.size(); o += (size_t)bb) {
+                const int n = pio::cpu_detail::dequant_block(type, raw.data() + o, y);
+                for (int i = 0; i < n; ++i) out.push_back((double)y[i]);
+            }
+            std::cout << out.dump() << "\n";
+            return 0;
+        }
         if (mode == "cpu-generate") {                // FILE|DIR N id id id ...: greedy ids and a few logits of the CPU decoder
             pio::GGUFCpuModel m;
             m.load(argv[2], 256);

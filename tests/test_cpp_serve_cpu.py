@@ -315,6 +315,28 @@ def test_native_model_loader_matches_python(exe, tmp_path):
         assert r.returncode == 1 and b"unknown model format" in r.stderr, bad
 
 
+def test_native_block_dequantisers_match_python(exe, tmp_path):
+    """gguf_cpu.h: every block format the C++ decoder reads, on random block bytes (scale fields set to finite halves), against the
+    dequantisers of the Python package; Q2_K and Q3_K have no quantiser here, so random bytes are their only source."""
+    from prometorch_b200.io import gguf_quant as GQ
+    g = torch.Generator().manual_seed(7)
+    half_fields = {GQ.GGMLType.Q4_0: [0], GQ.GGMLType.Q8_0: [0], GQ.GGMLType.Q2_K: [80, 82], GQ.GGMLType.Q3_K: [108], GQ.GGMLType.Q4_K: [0, 2],
+                   GQ.GGMLType.Q5_K: [0, 2], GQ.GGMLType.Q6_K: [208]}
+    for qt, fields in half_fields.items():
+        bb = GQ.row_bytes(qt, 256) // (256 // (32 if qt in (GQ.GGMLType.Q4_0, GQ.GGMLType.Q8_0) else 256))
+        n_blocks = 24
+        raw = torch.randint(0, 256, (n_blocks, bb), generator=g, dtype=torch.int32).to(torch.uint8)
+        scales = (torch.rand(n_blocks, len(fields), generator=g) * 0.1 - 0.03).to(torch.float16)
+        for j, off in enumerate(fields):
+            raw[:, off:off + 2] = scales[:, j:j + 1].contiguous().view(torch.uint8)
+        f = tmp_path / f"blocks_{int(qt)}.bin"
+        f.write_bytes(raw.numpy().tobytes())
+        got = torch.tensor(_run(exe, "dequant", str(int(qt)), str(f)))
+        elems = 32 if qt in (GQ.GGMLType.Q4_0, GQ.GGMLType.Q8_0) else 256
+        want = GQ.dequantize(raw.reshape(1, -1), qt, n_blocks * elems).reshape(-1)
+        assert got.numel() == want.numel() and torch.allclose(got, want, atol=1e-6, rtol=1e-6), (qt, float((got - want).abs().max()))
+
+
 def test_native_cpu_decoder_matches_the_python_oracle(exe, tmp_path):
     """gguf_cpu.h: the C++ CPU decoder (blocks dequantised on the fly) gives the logits and the greedy ids of the fp32 oracle of
     the Python package, for the default quantisation mix and for Q5_K + Q8_0 and Q8_0 + F16 files."""
@@ -324,7 +346,7 @@ def test_native_cpu_decoder_matches_the_python_oracle(exe, tmp_path):
     from prometorch_b200.models.gguf_oracle import OracleModel
     prompt = [300, 301, 17, 260, 5]
     for tag, q_main, q_more in (("q4km", GQ.GGMLType.Q4_K, GQ.GGMLType.Q6_K), ("q5k_q80", GQ.GGMLType.Q5_K, GQ.GGMLType.Q8_0),
-                                ("q80_f16", GQ.GGMLType.Q8_0, GQ.GGMLType.F16)):
+                                ("q80_f16", GQ.GGMLType.Q8_0, GQ.GGMLType.F16), ("q40_q80", GQ.GGMLType.Q4_0, GQ.GGMLType.Q8_0)):
         path = str(tmp_path / f"{tag}.gguf")
         write_synthetic_gguf(path, tiny_qwen3_config(layers=2, hidden=256, heads=4, kv_heads=2, inter=512, vocab=512), seed=11, device="cpu",
                              q_main=q_main, q_more=q_more, std=0.05)
