@@ -4,10 +4,10 @@
 //   gguf_generate MODEL [PROMPT] [--device cuda|cpu] [--greedy] [--max-tokens N] [--temp T] [--top-k K] [--top-p P]
 //                 [--repeat-penalty R] [--seed S] [--chat | --raw] [--info] [--tensors] [--profile]
 //
-// MODEL is a .gguf path or an Ollama model name.  --info prints the metadata and the parsed configuration, --tensors the
-// tensor directory (neither touches the GPU), --chat wraps the prompt in the model's chat template, --profile prints
-// per-kernel phase times of the last token.  --fp16-weights and --llama-gemv select kernels that have no counterpart here
-// and are accepted and ignored.
+// MODEL is a .gguf path, an Ollama model name or (with --device cpu, --info or --tensors) a Hugging Face directory.
+// --info prints the metadata and the parsed configuration, --tensors the tensor directory (neither touches the GPU),
+// --chat wraps the prompt in the model's chat template, --profile prints per-kernel phase times of the last token.
+// --fp16-weights and --llama-gemv select kernels that have no counterpart here and are accepted and ignored.
 #include <chrono>
 #include <cstdio>
 #include <cstdlib>
@@ -84,6 +84,23 @@ int main(int argc, char** argv) {
     try {
         const bool is_path = model.find('/') != std::string::npos || (model.size() > 5 && model.compare(model.size() - 5, 5, ".gguf") == 0);
         const std::string path = is_path ? model : ps::store::resolve_ollama(model);
+        if ((info || tensors) && ps::store::is_dir(path)) {            // a Hugging Face directory: what the model loader sees
+            const pio::loader::ModelWeights mw = pio::loader::load_model(path);
+            const auto& m = mw.config;
+            if (info)
+                std::printf("architecture %s (%s), %lld layers, hidden %lld, %lld heads (%lld kv), ffn %lld, context %lld, %lld parameters in %zu file(s)\n",
+                            mw.architecture.c_str(), mw.format.c_str(), (long long)m.num_layers, (long long)m.hidden_size, (long long)m.num_heads, (long long)m.num_kv_heads,
+                            (long long)m.intermediate_size, (long long)m.context_length, (long long)mw.total_parameters(), mw.files.size());
+            if (tensors)
+                for (const auto& name : mw.order) {
+                    const auto& t = mw.tensors.at(name);
+                    std::string shape = "(";
+                    for (size_t d = 0; d < t.shape.size(); ++d) shape += (d ? ", " : "") + std::to_string(t.shape[d]);
+                    shape += ")";
+                    std::printf("%-48s %-24s %-6s %llu B\n", name.c_str(), shape.c_str(), t.dtype.c_str(), (unsigned long long)t.nbytes);
+                }
+            return 0;
+        }
         if (info || tensors) {
             pio::gguf::GGUFReader r(path);
             if (info) {

@@ -9,6 +9,7 @@
 namespace pt = promethorch;
 namespace dist = promethorch::distributed;
 
+#undef CHECK
 #define CHECK(cond)                                                              \
     do {                                                                         \
         if (!(cond)) { std::printf("FAIL %s:%d %s\n", __FILE__, __LINE__, #cond); std::fflush(stdout); return 1; } \

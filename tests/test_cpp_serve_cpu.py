@@ -762,6 +762,9 @@ def test_native_cpu_decoder_reads_hugging_face_directories(exe, tmp_path):
     eos = ref.config.eos_token_id
     want = want[:want.index(eos) + 1] if eos in want else want
     assert got_ids == want and f"Prompt tokens: {len(ids)}" in r.stdout, (got_ids, want, r.stdout[-500:])
+    r = subprocess.run([str(_build.build_generate()), str(d), "--info", "--tensors"], capture_output=True, text=True, timeout=60)
+    assert r.returncode == 0 and "architecture llama (hf_dir), 2 layers, hidden 64, 4 heads (2 kv), ffn 96" in r.stdout, r.stdout[:400] + r.stderr[-400:]
+    assert any(ln.startswith("model.layers.1.mlp.down_proj.weight") and "(64, 96)" in ln and "f32" in ln for ln in r.stdout.splitlines())
     # and the server program with the directory as its model
     tok = load_hf_tokenizer(str(d))
     p = subprocess.Popen([str(_build.build_promeserve()), "--device", "cpu", "--model", str(d) + "/", "--port", "0", "--max-seq", "128"], stdout=subprocess.PIPE,
