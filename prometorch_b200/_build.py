@@ -109,7 +109,7 @@ def build_app(name: str, force: bool = False) -> Path:
         return PROMESERVE
     cuda = Path(_nvcc()).resolve().parent.parent
     cxx = os.environ.get("CXX") or shutil.which("g++") or "g++"
-    cmd = [cxx, "-std=c++17", "-O2", str(src), "-o", str(PROMESERVE), f"-I{ROOT / 'cpp_api'}", f"-I{cuda / 'include'}", f"-L{LIBDIR}", "-lptb200",
+    cmd = [cxx, "-std=c++17", "-O3", str(src), "-o", str(PROMESERVE), f"-I{ROOT / 'cpp_api'}", f"-I{cuda / 'include'}", f"-L{LIBDIR}", "-lptb200",
            f"-L{cuda / 'lib64'}", "-lcudart", "-lpthread", "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{cuda / 'lib64'}"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:

@@ -21,6 +21,8 @@
 #include <functional>
 #include <map>
 #include <memory>
+#include <mutex>
+#include <condition_variable>
 #include <random>
 #include <set>
 #include <string>
@@ -185,6 +187,102 @@ inline int dequant_block(uint32_t type, const uint8_t* p, float* y) {
         default: throw std::runtime_error("GGUFCpuModel: tensor type " + std::to_string(type) + " is not supported on this path");
     }
 }
+// Rows [r0, r1) of y = M x for block-quantised rows: each block is dequantised into a small buffer and multiplied into sixteen
+// running sums (a form the compiler turns into vector code), blocks are added up in double.  Compiled twice on x86-64 (AVX2 + FMA
+// and baseline) and picked at load time by the CPU's features; sanitizer builds keep the single baseline version.
+#if defined(__x86_64__) && defined(__GNUC__) && !defined(__clang__) && !defined(__SANITIZE_THREAD__) && !defined(__SANITIZE_ADDRESS__)
+#define PROMETHORCH_CPU_CLONES __attribute__((target_clones("arch=haswell", "default")))
+#else
+#define PROMETHORCH_CPU_CLONES
+#endif
+PROMETHORCH_CPU_CLONES
+static void block_rows(const uint8_t* data, uint32_t type, size_t row_bytes, int cols, int block_elems, int block_bytes, const float* x, float* y, int r0, int r1) {
+    float tmp[256];
+    for (int r = r0; r < r1; ++r) {
+        const uint8_t* p = data + (size_t)r * row_bytes;
+        double acc = 0;
+        for (int c = 0; c < cols; c += block_elems, p += block_bytes) {
+            const int n = dequant_block(type, p, tmp);            // 32 or 256 values
+            float lane[16] = {0};
+            for (int i = 0; i < n; i += 16)
+                for (int j = 0; j < 16; ++j) lane[j] += tmp[i + j] * x[c + i + j];
+            float part = 0;
+            for (int j = 0; j < 16; ++j) part += lane[j];
+            acc += part;
+        }
+        y[r] = (float)acc;
+    }
+}
+
+// A fixed set of worker threads that run the parts of one job at a time; the caller works too and returns when every part is done.
+class Pool {
+ public:
+    explicit Pool(int n) {
+        for (int i = 1; i < n; ++i) ts_.emplace_back([this] { loop(); });
+    }
+    ~Pool() {
+        {
+            std::lock_guard<std::mutex> l(m_);
+            stop_ = true;
+            ++gen_;
+        }
+        cv_.notify_all();
+        for (auto& t : ts_) t.join();
+    }
+    Pool(const Pool&) = delete;
+    Pool& operator=(const Pool&) = delete;
+    void run(int parts, const std::function<void(int)>& fn) {
+        {
+            std::lock_guard<std::mutex> l(m_);
+            fn_ = &fn;
+            parts_ = parts;
+            next_ = 0;
+            pending_ = parts;
+            ++gen_;
+        }
+        cv_.notify_all();
+        drain();
+        std::unique_lock<std::mutex> l(m_);
+        done_.wait(l, [&] { return pending_ == 0; });
+        fn_ = nullptr;
+    }
+
+ private:
+    void drain() {
+        for (;;) {
+            int part;
+            const std::function<void(int)>* fn;
+            {
+                std::lock_guard<std::mutex> l(m_);
+                if (!fn_ || next_ >= parts_) return;
+                part = next_++;
+                fn = fn_;
+            }
+            (*fn)(part);
+            std::lock_guard<std::mutex> l(m_);
+            if (--pending_ == 0) done_.notify_all();
+        }
+    }
+    void loop() {
+        unsigned long long seen = 0;
+        for (;;) {
+            {
+                std::unique_lock<std::mutex> l(m_);
+                cv_.wait(l, [&] { return gen_ != seen; });
+                seen = gen_;
+                if (stop_) return;
+            }
+            drain();
+        }
+    }
+    std::vector<std::thread> ts_;
+    std::mutex m_;
+    std::condition_variable cv_, done_;
+    const std::function<void(int)>* fn_ = nullptr;
+    int parts_ = 0, next_ = 0, pending_ = 0;
+    unsigned long long gen_ = 0;
+    bool stop_ = false;
+};
 }  // namespace cpu_detail
 
 class GGUFCpuModel {
@@ -331,6 +429,7 @@ class GGUFCpuModel {
             for (int p = 0; p < max_seq_; ++p) { cos_[(size_t)p * half + i] = (float)std::cos(p * inv); sin_[(size_t)p * half + i] = (float)std::sin(p * inv); }
         }
         logits_.assign((size_t)c.vocab_size, 0.f);
+        pool_.reset(threads_ > 1 ? new cpu_detail::Pool(threads_) : nullptr);
     }
     // A Hugging Face directory (or one .safetensors file beside its config.json): Llama-family names
     // (model.layers.N.self_attn.q_proj.weight ...), rotary halves split as in the checkpoint (first half / second half).
@@ -444,34 +543,22 @@ class GGUFCpuModel {
         const uint8_t* p = m.data + (size_t)r * m.row_bytes;
         for (int c = 0; c < m.cols; c += m.block_elems, p += m.block_bytes) cpu_detail::dequant_block(m.type, p, y + c);
     }
-    // y = M x, rows spread over the threads; every row is dequantised block by block into a small buffer.
+    // y = M x, rows spread over the pool's threads.
     void matvec(const Matrix& m, const float* x, float* y) const {
         auto work = [&](int r0, int r1) {
-            float tmp[256];
-            for (int r = r0; r < r1; ++r) {
+            if (m.block_elems != 1) { cpu_detail::block_rows(m.data, m.type, m.row_bytes, m.cols, m.block_elems, m.block_bytes, x, y, r0, r1); return; }
+            for (int r = r0; r < r1; ++r) {                    // plain F32 / F16 / BF16 rows: products in float, sums in double
                 const uint8_t* p = m.data + (size_t)r * m.row_bytes;
                 double acc = 0;
-                if (m.block_elems == 1) {                      // plain F32 / F16 / BF16 rows: the same products and sums without the per-block call
-                    if (m.type == gguf::F32) for (int c = 0; c < m.cols; ++c) { float w; std::memcpy(&w, p + 4 * (size_t)c, 4); acc += w * x[c]; }
-                    else if (m.type == gguf::F16) for (int c = 0; c < m.cols; ++c) acc += cpu_detail::half_to_float(cpu_detail::rd16(p + 2 * (size_t)c)) * x[c];
-                    else for (int c = 0; c < m.cols; ++c) { const uint32_t b = (uint32_t)cpu_detail::rd16(p + 2 * (size_t)c) << 16; float w; std::memcpy(&w, &b, 4); acc += w * x[c]; }
-                    y[r] = (float)acc;
-                    continue;
-                }
-                for (int c = 0; c < m.cols; c += m.block_elems, p += m.block_bytes) {
-                    const int n = cpu_detail::dequant_block(m.type, p, tmp);
-                    float part = 0;
-                    for (int i = 0; i < n; ++i) part += tmp[i] * x[c + i];
-                    acc += part;
-                }
+                if (m.type == gguf::F32) for (int c = 0; c < m.cols; ++c) { float w; std::memcpy(&w, p + 4 * (size_t)c, 4); acc += w * x[c]; }
+                else if (m.type == gguf::F16) for (int c = 0; c < m.cols; ++c) acc += cpu_detail::half_to_float(cpu_detail::rd16(p + 2 * (size_t)c)) * x[c];
+                else for (int c = 0; c < m.cols; ++c) { const uint32_t b = (uint32_t)cpu_detail::rd16(p + 2 * (size_t)c) << 16; float w; std::memcpy(&w, &b, 4); acc += w * x[c]; }
                 y[r] = (float)acc;
             }
         };
         const int nt = (int)std::min<int64_t>(threads_, std::max<int64_t>(1, (int64_t)m.rows * m.cols / (1 << 16)));
-        if (nt <= 1) { work(0, m.rows); return; }
-        std::vector<std::thread> ts;
-        for (int t = 0; t < nt; ++t) ts.emplace_back(work, (int)((int64_t)m.rows * t / nt), (int)((int64_t)m.rows * (t + 1) / nt));
-        for (auto& t : ts) t.join();
+        if (nt <= 1 || !pool_) { work(0, m.rows); return; }
+        pool_->run(nt, [&](int t) { work((int)((int64_t)m.rows * t / nt), (int)((int64_t)m.rows * (t + 1) / nt)); });
     }
     void rms(const float* x, const float* w, float* y, int n) const {
         double ss = 0;
@@ -494,6 +581,7 @@ class GGUFCpuModel {
     loader::ModelWeights hf_;
     std::string pre_;
     std::map<std::string, std::unique_ptr<Mapped>> maps_;
+    std::unique_ptr<cpu_detail::Pool> pool_;
     std::vector<float> out_norm_, cos_, sin_, logits_;
     int max_seq_ = 0, threads_ = 1;
 };
