@@ -319,8 +319,9 @@ class GGUFCpuModel {
     const gguf::GGUFReader& reader() const { return reader_; }                 // of a GGUF file (empty for a Hugging Face directory)
     const loader::ModelWeights& hf_weights() const { return hf_; }             // of a Hugging Face directory (empty for a GGUF file)
 
-    // One token at position `pos` (positions must be fed in order from 0): the logits of the next token.
-    const std::vector<float>& forward(int token, int pos) {
+    // One token at position `pos` (positions must be fed in order from 0): the logits of the next token.  With want_logits false the
+    // output projection is skipped and the returned vector is stale: for prompt tokens before the last.
+    const std::vector<float>& forward(int token, int pos, bool want_logits = true) {
         const auto& c = config;
         if (pos < 0 || pos >= max_seq_) throw std::runtime_error("GGUFCpuModel: position outside the cache");
         if (token < 0 || token >= c.vocab_size) throw std::runtime_error("GGUFCpuModel: token id outside the vocabulary");
@@ -375,6 +376,7 @@ class GGUFCpuModel {
             matvec(L.down, gate.data(), dn.data());
             for (int i = 0; i < D; ++i) x[(size_t)i] += dn[(size_t)i];
         }
+        if (!want_logits) return logits_;                       // a prompt token that is not the last: only its keys and values are needed
         rms(x.data(), out_norm_.data(), h.data(), D);
         matvec(head_, h.data(), logits_.data());
         return logits_;
@@ -384,7 +386,7 @@ class GGUFCpuModel {
     std::vector<int> generate(const std::vector<int>& prompt, int n_new) {
         std::vector<int> out;
         int pos = 0;
-        for (int t : prompt) forward(t, pos++);
+        for (size_t i = 0; i < prompt.size(); ++i, ++pos) forward(prompt[i], pos, i + 1 == prompt.size());
         for (int i = 0; i < n_new && pos < max_seq_; ++i) {
             const int t = argmax();
             out.push_back(t);
@@ -636,7 +638,7 @@ class CpuBackend : public ModelBackend {
         if (n + 2 > model_.max_seq()) throw std::runtime_error("the prompt does not fit the context of " + std::to_string(model_.max_seq()) + " tokens");
         const int n_new = std::max(0, std::min(opt.num_predict, model_.max_seq() - n - 1));
         const auto t0 = clock::now();
-        for (int i = 0; i + 1 < n; ++i) model_.forward(prompt[(size_t)i], i);
+        for (int i = 0; i + 1 < n; ++i) model_.forward(prompt[(size_t)i], i, false);
         const auto t1 = clock::now();
         std::vector<int> history = prompt;
         std::mt19937_64 rng((uint64_t)opt.seed);
