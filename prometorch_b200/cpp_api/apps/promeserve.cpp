@@ -7,7 +7,7 @@
 // else ../serve/web, which is where the page sits in the source tree).  --model is loaded before the port opens and stays
 // resident; it may be a path to a .gguf file or, with --device cpu, to a Hugging Face directory (config.json, safetensors,
 // tokenizer files); requests may only use names.
-// Build: g++ -std=c++17 -O2 promeserve.cpp -I<cpp_api> -I<cuda>/include -L<lib> -lptb200 -lcudart -lpthread
+// Build: g++ -std=c++17 -O3 promeserve.cpp -I<cpp_api> -I<cuda>/include -L<lib> -lptb200 -lcudart -lpthread
 #include <csignal>
 #include <cstdio>
 #include <cstdlib>
