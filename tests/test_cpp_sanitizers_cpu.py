@@ -139,6 +139,18 @@ def test_cpu_decoder_under_asan(asan_exe, tmp_path):
         assert len(json.loads(r.stdout)["ids"]) == 4
 
 
+def test_cpu_decoder_thread_pool_under_tsan(tsan_exe, tmp_path):
+    """The worker pool that spreads the rows of every projection (job hand-over, part counter, completion wait) under TSan, with the
+    same ids as the ASan build's single baseline path."""
+    from prometorch_b200.io.config import tiny_qwen3_config
+    from prometorch_b200.io.synthetic import write_synthetic_gguf
+    path = str(tmp_path / "pool.gguf")
+    write_synthetic_gguf(path, tiny_qwen3_config(layers=2, hidden=256, heads=4, kv_heads=2, inter=512, vocab=512), seed=3, device="cpu")
+    r = subprocess.run([tsan_exe, "cpu-generate", path, "6", "300", "301", "17"], capture_output=True, timeout=300, env=ENV)
+    _clean(r)
+    assert len(json.loads(r.stdout)["ids"]) == 6
+
+
 def _hammer(exe, env, flags=()):
     s = S.Server(exe, *flags, env=env)
     try:
